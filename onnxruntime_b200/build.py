@@ -92,7 +92,7 @@ def write_ninja(kernels_only: bool = False) -> str:
             "rule cxxlink",
             f"  command = $cxx -shared -o $out $in -L{torch_lib} -L{LIBDIR} -L{cuda}/lib64 "
             "-lc10 -ltorch_cpu -ltorch -ltorch_python -lc10_cuda -ltorch_cuda -lcudart -lortb200_kernels "
-            f"-Wl,-rpath,{torch_lib} -Wl,-rpath,$$ORIGIN/lib -Wl,-rpath,{cuda}/lib64",
+            f"-Wl,-rpath,{torch_lib} -Wl,-rpath,'$$ORIGIN/lib' -Wl,-rpath,{cuda}/lib64",
             "  description = LINK $out",
         ]
         cobjs = []

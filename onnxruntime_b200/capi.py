@@ -1,0 +1,669 @@
+"""Python API shell over the native runtime (``_core``).
+
+Keeps the user-facing contract of the reference's Python package
+(onnxruntime/python/onnxruntime_inference_collection.py: ``InferenceSession``
+:469, ``Session.run`` :308, ``IOBinding`` :888, ``OrtValue`` :1022,
+``OrtDevice`` :1362): ``InferenceSession(path_or_bytes, sess_options, providers,
+provider_options).run(output_names, feeds)``, ``SessionOptions`` / ``RunOptions``
+properties, ``io_binding()`` with device-resident inputs and outputs, and the
+exception classes.  Tensors are ``torch.Tensor`` underneath, so an ``OrtValue``
+can wrap CUDA memory, bf16 and fp8 without a copy.
+"""
+from __future__ import annotations
+
+import os
+import threading
+from enum import IntEnum
+from typing import Any, Dict, List, Optional, Sequence, Tuple, Union
+
+import numpy as np
+import torch
+
+from . import _core as C
+
+__all__ = [
+    "InferenceSession", "SessionOptions", "RunOptions", "IOBinding", "OrtValue", "OrtDevice", "NodeArg",
+    "ModelMetadata", "GraphOptimizationLevel", "ExecutionMode", "ExecutionOrder", "get_available_providers",
+    "get_all_providers", "get_device", "set_default_logger_severity", "set_default_logger_verbosity",
+]
+
+
+# ------------------------------------------------------------------ exceptions
+class OrtException(Exception):
+    """Base of the runtime's exceptions."""
+
+
+class Fail(OrtException, RuntimeError): pass
+class InvalidArgument(OrtException, ValueError): pass
+class NoSuchFile(OrtException, FileNotFoundError): pass
+class NoModel(OrtException): pass
+class EngineError(OrtException): pass
+class RuntimeException(OrtException, RuntimeError): pass
+class InvalidProtobuf(OrtException): pass
+class ModelLoaded(OrtException): pass
+class NotImplemented(OrtException, NotImplementedError): pass  # noqa: A001 (name kept for API parity)
+class InvalidGraph(OrtException): pass
+class EPFail(OrtException): pass
+class ModelLoadCanceled(OrtException): pass
+class ModelRequiresCompilation(OrtException): pass
+class NotFound(OrtException): pass
+
+
+_CODE_NAMES = {1: "FAIL", 2: "INVALID_ARGUMENT", 3: "NO_SUCHFILE", 4: "NO_MODEL", 5: "ENGINE_ERROR",
+               6: "RUNTIME_EXCEPTION", 7: "INVALID_PROTOBUF", 8: "MODEL_LOADED", 9: "NOT_IMPLEMENTED",
+               10: "INVALID_GRAPH", 11: "EP_FAIL", 12: "MODEL_LOAD_CANCELED", 13: "MODEL_REQUIRES_COMPILATION",
+               14: "NOT_FOUND"}
+_CODE_CLASSES = {1: Fail, 2: InvalidArgument, 3: NoSuchFile, 4: NoModel, 5: EngineError, 6: RuntimeException,
+                 7: InvalidProtobuf, 8: ModelLoaded, 9: NotImplemented, 10: InvalidGraph, 11: EPFail,
+                 12: ModelLoadCanceled, 13: ModelRequiresCompilation, 14: NotFound}
+
+
+def _make_error(code: int, message: str) -> Exception:
+    cls = _CODE_CLASSES.get(code, Fail)
+    return cls(f"[ONNXRuntimeError] : {code} : {_CODE_NAMES.get(code, 'FAIL')} : {message}")
+
+
+C.set_error_factory(_make_error)
+
+
+# ----------------------------------------------------------------------- enums
+class GraphOptimizationLevel(IntEnum):
+    ORT_DISABLE_ALL = 0
+    ORT_ENABLE_BASIC = 1
+    ORT_ENABLE_EXTENDED = 2
+    ORT_ENABLE_LAYOUT = 3
+    ORT_ENABLE_ALL = 99
+
+
+class ExecutionMode(IntEnum):
+    ORT_SEQUENTIAL = 0
+    ORT_PARALLEL = 1
+
+
+class ExecutionOrder(IntEnum):
+    DEFAULT = 0
+    PRIORITY_BASED = 1
+    MEMORY_EFFICIENT = 2
+
+
+_ALL_PROVIDERS = ["CUDAExecutionProvider", "CPUExecutionProvider"]
+_default_logger_severity = 2
+_default_logger_verbosity = 0
+
+
+def get_all_providers() -> List[str]:
+    return list(_ALL_PROVIDERS)
+
+
+def get_available_providers() -> List[str]:
+    out = []
+    if torch.cuda.is_available():
+        out.append("CUDAExecutionProvider")
+    out.append("CPUExecutionProvider")
+    return out
+
+
+def get_device() -> str:
+    return "GPU" if torch.cuda.is_available() else "CPU"
+
+
+def set_default_logger_severity(severity: int) -> None:
+    global _default_logger_severity
+    if not 0 <= severity <= 4:
+        raise InvalidArgument("severity must be in [0, 4]")
+    _default_logger_severity = severity
+
+
+def set_default_logger_verbosity(verbosity: int) -> None:
+    global _default_logger_verbosity
+    _default_logger_verbosity = verbosity
+
+
+# ------------------------------------------------------------------ type names
+_TORCH_TO_TYPESTR = {
+    torch.float32: "tensor(float)", torch.float16: "tensor(float16)", torch.bfloat16: "tensor(bfloat16)",
+    torch.float64: "tensor(double)", torch.int64: "tensor(int64)", torch.int32: "tensor(int32)",
+    torch.int16: "tensor(int16)", torch.int8: "tensor(int8)", torch.uint8: "tensor(uint8)", torch.bool: "tensor(bool)",
+    torch.uint16: "tensor(uint16)", torch.uint32: "tensor(uint32)", torch.uint64: "tensor(uint64)",
+    torch.float8_e4m3fn: "tensor(float8e4m3fn)", torch.float8_e5m2: "tensor(float8e5m2)",
+}
+_ONNX_ELEM_TO_TORCH = {
+    1: torch.float32, 2: torch.uint8, 3: torch.int8, 4: torch.uint16, 5: torch.int16, 6: torch.int32, 7: torch.int64,
+    9: torch.bool, 10: torch.float16, 11: torch.float64, 12: torch.uint32, 13: torch.uint64, 16: torch.bfloat16,
+    17: torch.float8_e4m3fn, 19: torch.float8_e5m2,
+}
+
+
+def _to_torch(value: Any) -> torch.Tensor:
+    if isinstance(value, OrtValue):
+        return value._tensor
+    if isinstance(value, torch.Tensor):
+        return value
+    if isinstance(value, np.ndarray):
+        if not value.flags.c_contiguous:
+            value = np.ascontiguousarray(value)
+        if not value.flags.writeable:
+            value = value.copy()
+        return torch.from_numpy(value)
+    if isinstance(value, (list, tuple)) and value and isinstance(value[0], (np.ndarray, torch.Tensor, OrtValue)):
+        return [_to_torch(v) for v in value]  # sequence input
+    return torch.as_tensor(np.asarray(value))
+
+
+def _to_numpy(t: Any) -> Any:
+    if t is None:
+        return None
+    if isinstance(t, list):
+        return [_to_numpy(x) for x in t]
+    t = t.detach()
+    if t.is_cuda:
+        t = t.cpu()
+    if t.dtype in (torch.bfloat16, torch.float8_e4m3fn, torch.float8_e5m2):
+        t = t.float()  # numpy has no such dtype
+    return t.numpy()
+
+
+# --------------------------------------------------------------------- OrtDevice
+class OrtDevice:
+    """Device descriptor ("cpu" or "cuda", device id)."""
+
+    def __init__(self, device_type: str = "cpu", device_id: int = 0):
+        self._type = device_type.lower()
+        self._id = device_id
+
+    @staticmethod
+    def cpu() -> str:
+        return "cpu"
+
+    @staticmethod
+    def cuda() -> str:
+        return "cuda"
+
+    @staticmethod
+    def make(ort_device_name: str, device_id: int) -> "OrtDevice":
+        return OrtDevice(ort_device_name, device_id)
+
+    def device_id(self) -> int:
+        return self._id
+
+    def device_type(self) -> str:
+        return self._type
+
+    def _torch(self) -> torch.device:
+        return torch.device("cuda", self._id) if self._type == "cuda" else torch.device("cpu")
+
+
+# ---------------------------------------------------------------------- OrtValue
+class OrtValue:
+    """A tensor owned by (or shared with) the runtime; wraps a ``torch.Tensor``."""
+
+    def __init__(self, tensor: torch.Tensor):
+        self._tensor = tensor
+
+    @staticmethod
+    def ortvalue_from_numpy(numpy_obj: np.ndarray, device_type: str = "cpu", device_id: int = 0) -> "OrtValue":
+        t = _to_torch(numpy_obj)
+        if device_type.lower() == "cuda":
+            t = t.to(torch.device("cuda", device_id))
+        return OrtValue(t)
+
+    @staticmethod
+    def ortvalue_from_shape_and_type(shape: Sequence[int], element_type=np.float32, device_type: str = "cpu",
+                                     device_id: int = 0) -> "OrtValue":
+        if isinstance(element_type, int):
+            dt = _ONNX_ELEM_TO_TORCH[element_type]
+        elif isinstance(element_type, torch.dtype):
+            dt = element_type
+        else:
+            dt = torch.from_numpy(np.zeros((), dtype=element_type)).dtype
+        dev = torch.device("cuda", device_id) if device_type.lower() == "cuda" else torch.device("cpu")
+        return OrtValue(torch.empty(tuple(shape), dtype=dt, device=dev))
+
+    @staticmethod
+    def ortvalue_from_torch(tensor: torch.Tensor) -> "OrtValue":
+        return OrtValue(tensor)
+
+    @staticmethod
+    def from_dlpack(data, is_bool_tensor: bool = False) -> "OrtValue":
+        t = torch.utils.dlpack.from_dlpack(data)
+        if is_bool_tensor:
+            t = t.view(torch.bool)
+        return OrtValue(t)
+
+    def __dlpack__(self, stream=None):
+        return self._tensor.__dlpack__() if stream is None else self._tensor.__dlpack__(stream=stream)
+
+    def __dlpack_device__(self):
+        return self._tensor.__dlpack_device__()
+
+    def to_dlpack(self):
+        return torch.utils.dlpack.to_dlpack(self._tensor)
+
+    def as_torch(self) -> torch.Tensor:
+        return self._tensor
+
+    def data_ptr(self) -> int:
+        return self._tensor.data_ptr()
+
+    def device_name(self) -> str:
+        return "cuda" if self._tensor.is_cuda else "cpu"
+
+    def shape(self) -> List[int]:
+        return list(self._tensor.shape)
+
+    def data_type(self) -> str:
+        return _TORCH_TO_TYPESTR.get(self._tensor.dtype, "tensor(unknown)")
+
+    def element_type(self) -> int:
+        for k, v in _ONNX_ELEM_TO_TORCH.items():
+            if v == self._tensor.dtype:
+                return k
+        return 0
+
+    def has_value(self) -> bool:
+        return self._tensor is not None
+
+    def is_tensor(self) -> bool:
+        return True
+
+    def is_sparse_tensor(self) -> bool:
+        return False
+
+    def is_tensor_sequence(self) -> bool:
+        return False
+
+    def numpy(self) -> np.ndarray:
+        return _to_numpy(self._tensor)
+
+    def update_inplace(self, np_arr: np.ndarray) -> None:
+        self._tensor.copy_(_to_torch(np_arr))
+
+
+class NodeArg:
+    """Name, type string and shape of a model input or output."""
+
+    def __init__(self, meta):
+        self.name = meta.name
+        self.type = meta.type
+        if meta.has_shape:
+            self.shape = [d if d >= 0 else (s if s else None) for d, s in zip(meta.shape, meta.sym)]
+        else:
+            self.shape = None
+
+    def __repr__(self) -> str:
+        return f"NodeArg(name='{self.name}', type='{self.type}', shape={self.shape})"
+
+
+class ModelMetadata:
+    def __init__(self, d: Dict[str, Any]):
+        self.producer_name = d["producer_name"]
+        self.graph_name = d["graph_name"]
+        self.domain = d["domain"]
+        self.description = d["description"]
+        self.graph_description = d["graph_description"]
+        self.version = d["version"]
+        self.custom_metadata_map = dict(d["custom_metadata_map"])
+
+
+# ----------------------------------------------------------------- SessionOptions
+class SessionOptions:
+    """Session configuration; property names follow the reference's pybind ``SessionOptions``."""
+
+    _FIELDS = ("enable_cpu_mem_arena", "enable_mem_pattern", "enable_mem_reuse", "enable_profiling",
+               "profile_file_prefix", "optimized_model_filepath", "logid", "log_severity_level", "log_verbosity_level",
+               "intra_op_num_threads", "inter_op_num_threads", "use_deterministic_compute", "use_per_session_threads")
+
+    def __init__(self):
+        object.__setattr__(self, "_c", C.SessionOptions())
+        object.__setattr__(self, "_custom_op_libraries", [])
+        object.__setattr__(self, "_keepalive", [])
+        self._c.log_severity_level = _default_logger_severity
+
+    def __getattr__(self, name):
+        if name in SessionOptions._FIELDS:
+            return getattr(self._c, name)
+        raise AttributeError(name)
+
+    def __setattr__(self, name, value):
+        if name in SessionOptions._FIELDS:
+            setattr(self._c, name, value)
+        elif name in ("execution_mode", "execution_order", "graph_optimization_level"):
+            setattr(self._c, name, int(value))
+        else:
+            raise AttributeError(f"SessionOptions has no attribute '{name}'")
+
+    @property
+    def execution_mode(self) -> ExecutionMode:
+        return ExecutionMode(self._c.execution_mode)
+
+    @property
+    def execution_order(self) -> ExecutionOrder:
+        return ExecutionOrder(self._c.execution_order)
+
+    @property
+    def graph_optimization_level(self) -> GraphOptimizationLevel:
+        return GraphOptimizationLevel(self._c.graph_optimization_level)
+
+    def add_session_config_entry(self, key: str, value: str) -> None:
+        self._c.add_config(key, str(value))
+
+    def get_session_config_entry(self, key: str) -> str:
+        v = self._c.get_config(key)
+        if v is None:
+            raise RuntimeException(f"Session config entry '{key}' was not found.")
+        return v
+
+    def add_free_dimension_override_by_name(self, name: str, value: int) -> None:
+        self._c.add_free_dim_by_name(name, int(value))
+
+    def add_free_dimension_override_by_denotation(self, denotation: str, value: int) -> None:
+        self._c.add_free_dim_by_denotation(denotation, int(value))
+
+    def add_initializer(self, name: str, ort_value: OrtValue) -> None:
+        self._c.add_initializer(name, _to_torch(ort_value))
+
+    def add_external_initializers(self, names: Sequence[str], ort_values: Sequence[Any]) -> None:
+        if len(names) != len(ort_values):
+            raise InvalidArgument("names and ort_values differ in length")
+        for n, v in zip(names, ort_values):
+            self._c.add_external_initializer(n, _to_torch(v))
+
+    def register_custom_ops_library(self, path: str) -> None:
+        if not os.path.exists(path):
+            raise NoSuchFile(f"custom op library {path} not found")
+        raise NotImplemented("custom op shared libraries (OrtCustomOp C ABI) are not supported; "  # noqa: F901
+                             "register Python custom ops with onnxruntime_b200.custom_ops instead")
+
+
+class RunOptions:
+    def __init__(self):
+        self._c = C.RunOptions()
+
+    log_severity_level = property(lambda s: s._c.log_severity_level, lambda s, v: setattr(s._c, "log_severity_level", v))
+    log_verbosity_level = property(lambda s: s._c.log_verbosity_level, lambda s, v: setattr(s._c, "log_verbosity_level", v))
+    logid = property(lambda s: s._c.logid, lambda s, v: setattr(s._c, "logid", v))
+    terminate = property(lambda s: s._c.terminate, lambda s, v: setattr(s._c, "terminate", bool(v)))
+    only_execute_path_to_fetches = property(lambda s: s._c.only_execute_path_to_fetches,
+                                            lambda s, v: setattr(s._c, "only_execute_path_to_fetches", bool(v)))
+
+    def add_run_config_entry(self, key: str, value: str) -> None:
+        self._c.add_config(key, str(value))
+
+    def get_run_config_entry(self, key: str) -> str:
+        v = self._c.get_config(key)
+        if v is None:
+            raise RuntimeException(f"Run config entry '{key}' was not found.")
+        return v
+
+
+# --------------------------------------------------------------- provider args
+def check_and_normalize_provider_args(providers, provider_options, available) -> Tuple[List[str], List[Dict[str, str]]]:
+    """Same contract as the reference helper (onnxruntime_inference_collection.py:119)."""
+    if providers is None:
+        return [], []
+    if not isinstance(providers, Sequence) or isinstance(providers, str):
+        raise ValueError("'providers' should be a sequence.")
+    names: List[str] = []
+    opts: List[Dict[str, str]] = []
+
+    def add(name, options):
+        if name not in _ALL_PROVIDERS:
+            raise ValueError(f"Specified provider '{name}' is not in available provider names."
+                             f"Available providers: '{', '.join(available)}'")
+        if name in names:
+            return
+        names.append(name)
+        opts.append({str(k): str(v) for k, v in (options or {}).items()})
+
+    if provider_options is not None:
+        if not isinstance(provider_options, Sequence) or len(provider_options) != len(providers):
+            raise ValueError("'provider_options' should be a sequence with the same length as 'providers'.")
+        for p, o in zip(providers, provider_options):
+            if not isinstance(p, str) or not isinstance(o, dict):
+                raise ValueError("'providers' values must be strings and 'provider_options' values must be dicts")
+            add(p, o)
+    else:
+        for p in providers:
+            if isinstance(p, str):
+                add(p, {})
+            elif isinstance(p, tuple) and len(p) == 2 and isinstance(p[0], str) and isinstance(p[1], dict):
+                add(p[0], p[1])
+            else:
+                raise ValueError("'providers' values must be either provider names or (name, options dict) tuples.")
+    return names, opts
+
+
+# ------------------------------------------------------------- InferenceSession
+class InferenceSession:
+    """Load an ONNX model and run it.
+
+    ``InferenceSession(path_or_bytes, sess_options=None, providers=None, provider_options=None)``;
+    keyword extras: ``disabled_optimizers`` (list of pass names), ``enable_fallback``.
+    """
+
+    def __init__(self, path_or_bytes: Union[str, bytes, os.PathLike], sess_options: Optional[SessionOptions] = None,
+                 providers=None, provider_options=None, **kwargs):
+        self._sess_options = sess_options if sess_options is not None else SessionOptions()
+        self._enable_fallback = bool(kwargs.get("enable_fallback", True))
+        disabled = list(kwargs.get("disabled_optimizers") or [])
+        if isinstance(path_or_bytes, (str, os.PathLike)):
+            self._model_path = os.fspath(path_or_bytes)
+            self._model_bytes = None
+        elif isinstance(path_or_bytes, (bytes, bytearray, memoryview)):
+            self._model_path = None
+            self._model_bytes = bytes(path_or_bytes)
+        else:
+            raise TypeError(f"Unable to load from type '{type(path_or_bytes)}'")
+        available = get_available_providers()
+        names, opts = check_and_normalize_provider_args(providers, provider_options, available)
+        if not names:
+            names, opts = ["CPUExecutionProvider"], [{}]
+        self._fallback_providers = ["CPUExecutionProvider"]
+        self._dist = kwargs.get("dist")
+        try:
+            self._create(names, opts, disabled)
+        except (EPFail, RuntimeException) as e:
+            if not self._enable_fallback or names == self._fallback_providers:
+                raise
+            import warnings
+            warnings.warn(f"EP Error {e} when using {names}; falling back to {self._fallback_providers} and retrying.")
+            self._create(self._fallback_providers, [{}], disabled)
+        self._lock = threading.Lock()
+
+    def _create(self, names, opts, disabled) -> None:
+        if "CUDAExecutionProvider" in names and not torch.cuda.is_available():
+            if names == ["CUDAExecutionProvider"] and not self._enable_fallback:
+                raise EPFail("CUDAExecutionProvider requested but no CUDA device is available")
+            pairs = [(n, o) for n, o in zip(names, opts) if n != "CUDAExecutionProvider"]
+            names, opts = [p[0] for p in pairs] or ["CPUExecutionProvider"], [p[1] for p in pairs] or [{}]
+        sess = C.InferenceSession(self._sess_options._c)
+        if self._model_path is not None:
+            sess.load(self._model_path)
+        else:
+            sess.load_bytes(self._model_bytes)
+        dist = self._dist
+        if dist is not None:
+            sess.dist_group = dist.group_name
+            sess.rank = dist.rank
+            sess.world_size = dist.world_size
+        sess.initialize(list(zip(names, opts)), disabled)
+        self._sess = sess
+        self._providers = sess.providers()
+        self._provider_options = sess.provider_options()
+        self._inputs_meta = [NodeArg(m) for m in sess.inputs_meta()]
+        self._outputs_meta = [NodeArg(m) for m in sess.outputs_meta()]
+        self._overridable = [NodeArg(m) for m in sess.overridable_initializers_meta()]
+        self._input_names = [m.name for m in self._inputs_meta]
+
+    # --- metadata
+    def get_session_options(self) -> SessionOptions:
+        return self._sess_options
+
+    def get_inputs(self) -> List[NodeArg]:
+        return self._inputs_meta
+
+    def get_outputs(self) -> List[NodeArg]:
+        return self._outputs_meta
+
+    def get_overridable_initializers(self) -> List[NodeArg]:
+        return self._overridable
+
+    def get_modelmeta(self) -> ModelMetadata:
+        return ModelMetadata(self._sess.model_meta())
+
+    def get_providers(self) -> List[str]:
+        return list(self._providers)
+
+    def get_provider_options(self) -> Dict[str, Dict[str, str]]:
+        return {k: dict(v) for k, v in self._provider_options.items()}
+
+    def set_providers(self, providers=None, provider_options=None) -> None:
+        names, opts = check_and_normalize_provider_args(providers, provider_options, get_available_providers())
+        self._create(names or ["CPUExecutionProvider"], opts or [{}], [])
+
+    def get_provider_graph_assignment_info(self):
+        return self._sess.node_assignments()
+
+    def get_profiling_start_time_ns(self) -> int:
+        return self._sess.profiling_start_time_ns()
+
+    def end_profiling(self) -> str:
+        return self._sess.end_profiling()
+
+    # --- running
+    def _validate_input(self, feed_names: Sequence[str]) -> None:
+        missing = [n for n in self._input_names if n not in feed_names]
+        if missing:
+            raise ValueError(f"Required inputs ({missing}) are missing from input feed ({list(feed_names)}).")
+
+    def run(self, output_names: Optional[Sequence[str]], input_feed: Dict[str, Any],
+            run_options: Optional[RunOptions] = None) -> List[Any]:
+        self._validate_input(list(input_feed.keys()))
+        ro = run_options._c if run_options is not None else C.RunOptions()
+        names = list(input_feed.keys())
+        feeds = [_to_torch(v) for v in input_feed.values()]
+        outs = self._sess.run(ro, names, feeds, list(output_names or []))
+        return [_to_numpy(o) for o in outs]
+
+    def run_with_ort_values(self, output_names: Optional[Sequence[str]], input_dict_ort_values: Dict[str, OrtValue],
+                            run_options: Optional[RunOptions] = None) -> List[OrtValue]:
+        self._validate_input(list(input_dict_ort_values.keys()))
+        ro = run_options._c if run_options is not None else C.RunOptions()
+        names = list(input_dict_ort_values.keys())
+        feeds = [_to_torch(v) for v in input_dict_ort_values.values()]
+        outs = self._sess.run(ro, names, feeds, list(output_names or []))
+        return [OrtValue(o) for o in outs]
+
+    def run_async(self, output_names, input_feed, callback, user_data, run_options=None) -> None:
+        def work():
+            try:
+                res = self.run(output_names, input_feed, run_options)
+                callback(res, user_data, "")
+            except Exception as e:  # the callback receives the error text, as in the reference
+                callback(None, user_data, str(e))
+        threading.Thread(target=work, daemon=True).start()
+
+    def io_binding(self) -> "IOBinding":
+        return IOBinding(self)
+
+    def run_with_iobinding(self, iobinding: "IOBinding", run_options: Optional[RunOptions] = None) -> None:
+        ro = run_options._c if run_options is not None else C.RunOptions()
+        self._sess.run_with_binding(ro, iobinding._c)
+
+    # --- extras of this runtime
+    def graph_nodes(self) -> List[Dict[str, Any]]:
+        """The optimized, partitioned graph as a list of node dicts (op_type, domain, inputs, outputs, ep, attrs)."""
+        return self._sess.graph_nodes()
+
+    def serialize_optimized_model(self) -> bytes:
+        return self._sess.serialize_model()
+
+    def kernel_launch_count(self) -> int:
+        return self._sess.kernel_launch_count()
+
+    def check_device_status(self) -> None:
+        self._sess.check_device_status()
+
+
+# --------------------------------------------------------------------- IOBinding
+class IOBinding:
+    """Bind model inputs/outputs to caller-owned (possibly device) buffers."""
+
+    def __init__(self, session: InferenceSession):
+        self._session = session
+        self._c = C.IOBinding(session._sess)
+        self._keep: List[Any] = []
+
+    def bind_cpu_input(self, name: str, arr_on_cpu: np.ndarray) -> None:
+        self._c.bind_input(name, _to_torch(arr_on_cpu))
+
+    def bind_input(self, name: str, device_type: str, device_id: int, element_type, shape: Sequence[int],
+                   buffer_ptr: int) -> None:
+        t = _tensor_from_pointer(buffer_ptr, element_type, shape, device_type, device_id)
+        self._keep.append(t)
+        self._c.bind_input(name, t)
+
+    def bind_ortvalue_input(self, name: str, ortvalue: OrtValue) -> None:
+        self._c.bind_input(name, _to_torch(ortvalue))
+
+    def bind_torch_input(self, name: str, tensor: torch.Tensor) -> None:
+        self._c.bind_input(name, tensor)
+
+    def bind_output(self, name: str, device_type: str = "cpu", device_id: int = 0, element_type=None,
+                    shape: Optional[Sequence[int]] = None, buffer_ptr: Optional[int] = None) -> None:
+        if buffer_ptr is None:
+            self._c.bind_output_to_device(name, device_type.lower(), device_id)
+            return
+        if element_type is None or shape is None:
+            raise InvalidArgument("`element_type` and `shape` are to be provided if pre-allocated memory is provided")
+        t = _tensor_from_pointer(buffer_ptr, element_type, shape, device_type, device_id)
+        self._keep.append(t)
+        self._c.bind_output(name, t)
+
+    def bind_ortvalue_output(self, name: str, ortvalue: OrtValue) -> None:
+        self._c.bind_output(name, _to_torch(ortvalue))
+
+    def bind_torch_output(self, name: str, tensor: torch.Tensor) -> None:
+        self._c.bind_output(name, tensor)
+
+    def synchronize_inputs(self) -> None:
+        self._c.synchronize_inputs()
+
+    def synchronize_outputs(self) -> None:
+        self._c.synchronize_outputs()
+
+    def get_outputs(self) -> List[OrtValue]:
+        return [OrtValue(t) for t in self._c.results()]
+
+    def copy_outputs_to_cpu(self) -> List[np.ndarray]:
+        return [_to_numpy(t) for t in self._c.results()]
+
+    def clear_binding_inputs(self) -> None:
+        self._c.clear_inputs()
+
+    def clear_binding_outputs(self) -> None:
+        self._c.clear_outputs()
+        self._keep.clear()
+
+
+def _tensor_from_pointer(ptr: int, element_type, shape, device_type: str, device_id: int) -> torch.Tensor:
+    """Wrap foreign memory (no copy) as a torch tensor."""
+    if isinstance(element_type, int):
+        dt = _ONNX_ELEM_TO_TORCH[element_type]
+    elif isinstance(element_type, torch.dtype):
+        dt = element_type
+    else:
+        dt = torch.from_numpy(np.zeros((), dtype=element_type)).dtype
+    numel = int(np.prod(shape)) if len(shape) else 1
+    nbytes = numel * torch.empty((), dtype=dt).element_size()
+    if device_type.lower() == "cuda":
+        class _Holder:
+            pass
+        h = _Holder()
+        h.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (int(ptr), False), "version": 2}
+        raw = torch.as_tensor(h, device=torch.device("cuda", device_id))
+    else:
+        import ctypes
+        buf = (ctypes.c_uint8 * nbytes).from_address(int(ptr))
+        raw = torch.frombuffer(buf, dtype=torch.uint8)
+    return raw.view(dt).reshape(tuple(shape))

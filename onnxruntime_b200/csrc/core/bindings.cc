@@ -1,0 +1,325 @@
+// pybind11 module `onnxruntime_b200._core`: the native runtime exposed to the
+// Python API shell (reference: onnxruntime/python/onnxruntime_pybind_state.cc).
+#include <pybind11/functional.h>
+#include <pybind11/stl.h>
+#include <torch/extension.h>
+
+#include "executor.h"
+#include "graph.h"
+#include "kernel.h"
+#include "session.h"
+#include "sharding_spec.h"
+
+namespace py = pybind11;
+using namespace ortb;
+
+namespace {
+
+struct PyOrtError {
+  int code;
+  std::string msg;
+};
+
+py::object g_error_factory;  // python callable (code:int, message:str) -> exception instance
+
+void TranslateAndThrow(const OrtError& e) {
+  if (g_error_factory && !g_error_factory.is_none()) {
+    py::object exc = g_error_factory(static_cast<int>(e.code()), std::string(e.what()));
+    PyErr_SetObject(reinterpret_cast<PyObject*>(Py_TYPE(exc.ptr())), exc.ptr());
+    throw py::error_already_set();
+  }
+  throw std::runtime_error(e.what());
+}
+
+std::vector<Value> ToValues(const std::vector<py::object>& objs) {
+  std::vector<Value> out;
+  out.reserve(objs.size());
+  for (auto& o : objs) {
+    Value v;
+    if (o.is_none()) {
+    } else if (py::isinstance<py::list>(o) || py::isinstance<py::tuple>(o)) {
+      v.seq = std::make_shared<std::vector<at::Tensor>>(o.cast<std::vector<at::Tensor>>());
+    } else {
+      v.t = o.cast<at::Tensor>();
+    }
+    out.push_back(std::move(v));
+  }
+  return out;
+}
+
+py::object FromValue(const Value& v) {
+  if (v.seq) return py::cast(*v.seq);
+  if (v.t.defined()) return py::cast(v.t);
+  return py::none();
+}
+
+py::dict NodeToDict(const Node& n) {
+  py::dict d;
+  d["name"] = n.name;
+  d["op_type"] = n.op_type;
+  d["domain"] = n.domain;
+  d["inputs"] = n.inputs;
+  d["outputs"] = n.outputs;
+  d["ep"] = n.ep;
+  py::dict attrs;
+  for (auto& kv : n.attrs) {
+    const auto& a = kv.second;
+    switch (a.type) {
+      case pb::ATTR_INT: attrs[kv.first.c_str()] = a.i; break;
+      case pb::ATTR_FLOAT: attrs[kv.first.c_str()] = a.f; break;
+      case pb::ATTR_STRING: attrs[kv.first.c_str()] = py::bytes(a.s); break;
+      case pb::ATTR_INTS: attrs[kv.first.c_str()] = a.ints; break;
+      case pb::ATTR_FLOATS: attrs[kv.first.c_str()] = a.floats; break;
+      case pb::ATTR_STRINGS: attrs[kv.first.c_str()] = a.strings; break;
+      case pb::ATTR_TENSOR: attrs[kv.first.c_str()] = n.attr_tensor(kv.first); break;
+      default: attrs[kv.first.c_str()] = py::none();
+    }
+  }
+  d["attrs"] = attrs;
+  return d;
+}
+
+template <typename F>
+auto Guard(F&& f) -> decltype(f()) {
+  try {
+    return f();
+  } catch (const OrtError& e) {
+    TranslateAndThrow(e);
+    throw;
+  } catch (const c10::Error& e) {
+    TranslateAndThrow(OrtError(StatusCode::RUNTIME_EXCEPTION, e.what_without_backtrace()));
+    throw;
+  }
+}
+
+}  // namespace
+
+PYBIND11_MODULE(_core, m) {
+  m.doc() = "onnxruntime_b200 native runtime";
+  m.def("set_error_factory", [](py::object f) { g_error_factory = f; });
+  m.def("registered_ops", [](const std::string& which) {
+    EnsureKernelsRegistered();
+    return which == "cuda" ? KernelRegistry::Cuda().ListOps() : KernelRegistry::Generic().ListOps();
+  });
+
+  py::class_<SessionOptions>(m, "SessionOptions")
+      .def(py::init<>())
+      .def_readwrite("enable_cpu_mem_arena", &SessionOptions::enable_cpu_mem_arena)
+      .def_readwrite("enable_mem_pattern", &SessionOptions::enable_mem_pattern)
+      .def_readwrite("enable_mem_reuse", &SessionOptions::enable_mem_reuse)
+      .def_readwrite("enable_profiling", &SessionOptions::enable_profiling)
+      .def_readwrite("profile_file_prefix", &SessionOptions::profile_file_prefix)
+      .def_readwrite("optimized_model_filepath", &SessionOptions::optimized_model_filepath)
+      .def_readwrite("logid", &SessionOptions::logid)
+      .def_readwrite("log_severity_level", &SessionOptions::log_severity_level)
+      .def_readwrite("log_verbosity_level", &SessionOptions::log_verbosity_level)
+      .def_readwrite("intra_op_num_threads", &SessionOptions::intra_op_num_threads)
+      .def_readwrite("inter_op_num_threads", &SessionOptions::inter_op_num_threads)
+      .def_readwrite("execution_mode", &SessionOptions::execution_mode)
+      .def_readwrite("execution_order", &SessionOptions::execution_order)
+      .def_readwrite("graph_optimization_level", &SessionOptions::graph_optimization_level)
+      .def_readwrite("use_deterministic_compute", &SessionOptions::use_deterministic_compute)
+      .def_readwrite("use_per_session_threads", &SessionOptions::use_per_session_threads)
+      .def("add_config", [](SessionOptions& s, const std::string& k, const std::string& v) { s.config.entries[k] = v; })
+      .def("get_config", [](SessionOptions& s, const std::string& k) -> py::object {
+        auto it = s.config.entries.find(k);
+        if (it == s.config.entries.end()) return py::none();
+        return py::cast(it->second);
+      })
+      .def("config_entries", [](SessionOptions& s) { return s.config.entries; })
+      .def("add_free_dim_by_name", [](SessionOptions& s, const std::string& k, int64_t v) { s.free_dim_by_name[k] = v; })
+      .def("add_free_dim_by_denotation", [](SessionOptions& s, const std::string& k, int64_t v) { s.free_dim_by_denotation[k] = v; })
+      .def("add_initializer", [](SessionOptions& s, const std::string& k, const at::Tensor& t) { s.initializers[k] = t; })
+      .def("add_external_initializer", [](SessionOptions& s, const std::string& k, const at::Tensor& t) { s.external_initializers[k] = t; });
+
+  py::class_<RunOptions>(m, "RunOptions")
+      .def(py::init<>())
+      .def_readwrite("log_severity_level", &RunOptions::log_severity_level)
+      .def_readwrite("log_verbosity_level", &RunOptions::log_verbosity_level)
+      .def_readwrite("logid", &RunOptions::logid)
+      .def_readwrite("only_execute_path_to_fetches", &RunOptions::only_execute_path_to_fetches)
+      .def_property("terminate", [](RunOptions& r) { return r.terminate->load(); },
+                    [](RunOptions& r, bool v) { r.terminate->store(v); })
+      .def("add_config", [](RunOptions& r, const std::string& k, const std::string& v) { r.config.entries[k] = v; })
+      .def("get_config", [](RunOptions& r, const std::string& k) -> py::object {
+        auto it = r.config.entries.find(k);
+        if (it == r.config.entries.end()) return py::none();
+        return py::cast(it->second);
+      });
+
+  py::class_<NodeArgMeta>(m, "NodeArgMeta")
+      .def_readonly("name", &NodeArgMeta::name)
+      .def_readonly("type", &NodeArgMeta::type)
+      .def_readonly("has_shape", &NodeArgMeta::has_shape)
+      .def_readonly("shape", &NodeArgMeta::shape)
+      .def_readonly("sym", &NodeArgMeta::sym);
+
+  py::class_<InferenceSession>(m, "InferenceSession")
+      .def(py::init<const SessionOptions&>())
+      .def("load", [](InferenceSession& s, const std::string& path) { Guard([&] { s.Load(path); return 0; }); })
+      .def("load_bytes", [](InferenceSession& s, py::bytes b) {
+        std::string bytes = b;
+        Guard([&] { s.LoadFromBytes(bytes); return 0; });
+      })
+      .def("initialize",
+           [](InferenceSession& s, const std::vector<std::pair<std::string, ProviderOptions>>& providers,
+              const std::vector<std::string>& disabled) {
+             py::gil_scoped_release rel;
+             try {
+               s.Initialize(providers, disabled);
+             } catch (const OrtError& e) {
+               py::gil_scoped_acquire acq;
+               TranslateAndThrow(e);
+             } catch (const c10::Error& e) {
+               py::gil_scoped_acquire acq;
+               TranslateAndThrow(OrtError(StatusCode::RUNTIME_EXCEPTION, e.what_without_backtrace()));
+             }
+           })
+      .def("run",
+           [](InferenceSession& s, const RunOptions& ro, const std::vector<std::string>& names,
+              const std::vector<py::object>& feeds, const std::vector<std::string>& outputs) {
+             std::vector<Value> vals = ToValues(feeds);
+             std::vector<Value> res;
+             {
+               py::gil_scoped_release rel;
+               try {
+                 res = s.Run(ro, names, vals, outputs);
+               } catch (const OrtError& e) {
+                 py::gil_scoped_acquire acq;
+                 TranslateAndThrow(e);
+               } catch (const c10::Error& e) {
+                 py::gil_scoped_acquire acq;
+                 TranslateAndThrow(OrtError(StatusCode::RUNTIME_EXCEPTION, e.what_without_backtrace()));
+               }
+             }
+             py::list out;
+             for (auto& v : res) out.append(FromValue(v));
+             return out;
+           })
+      .def("run_with_binding",
+           [](InferenceSession& s, const RunOptions& ro, IOBinding& b) {
+             py::gil_scoped_release rel;
+             try {
+               s.RunWithBinding(ro, b);
+             } catch (const OrtError& e) {
+               py::gil_scoped_acquire acq;
+               TranslateAndThrow(e);
+             } catch (const c10::Error& e) {
+               py::gil_scoped_acquire acq;
+               TranslateAndThrow(OrtError(StatusCode::RUNTIME_EXCEPTION, e.what_without_backtrace()));
+             }
+           })
+      .def("inputs_meta", &InferenceSession::InputsMeta)
+      .def("outputs_meta", &InferenceSession::OutputsMeta)
+      .def("overridable_initializers_meta", &InferenceSession::OverridableInitializersMeta)
+      .def("providers", &InferenceSession::Providers)
+      .def("provider_options", &InferenceSession::ProviderOptionsMap)
+      .def("end_profiling", &InferenceSession::EndProfiling)
+      .def("profiling_start_time_ns", &InferenceSession::ProfilingStartTimeNs)
+      .def("node_assignments", &InferenceSession::NodeAssignments)
+      .def("num_captured_graphs", &InferenceSession::NumCapturedGraphs)
+      .def("kernel_launch_count", &InferenceSession::KernelLaunchCount)
+      .def("check_device_status", [](InferenceSession& s) { Guard([&] { s.CheckDeviceStatus(); return 0; }); })
+      .def("uses_gpu", &InferenceSession::uses_gpu)
+      .def_readwrite("dist_group", &InferenceSession::dist_group)
+      .def_readwrite("rank", &InferenceSession::rank)
+      .def_readwrite("world_size", &InferenceSession::world_size)
+      .def("serialize_model", [](InferenceSession& s) { return py::bytes(s.model().Serialize()); })
+      .def("model_meta", [](InferenceSession& s) {
+        const Model& mm = s.model();
+        py::dict d;
+        d["producer_name"] = mm.producer_name;
+        d["graph_name"] = mm.graph_name;
+        d["domain"] = mm.domain;
+        d["description"] = mm.doc_string;
+        d["graph_description"] = std::string();
+        d["version"] = mm.model_version;
+        d["custom_metadata_map"] = mm.metadata;
+        return d;
+      })
+      .def("graph_nodes", [](InferenceSession& s) {
+        py::list out;
+        for (Node* n : s.model().MainGraph().TopologicalOrder()) out.append(NodeToDict(*n));
+        return out;
+      });
+
+  py::class_<IOBinding>(m, "IOBinding")
+      .def(py::init<InferenceSession*>(), py::keep_alive<1, 2>())
+      .def("bind_input", [](IOBinding& b, const std::string& n, const at::Tensor& t) { Guard([&] { b.BindInput(n, t); return 0; }); })
+      .def("bind_output", [](IOBinding& b, const std::string& n, const at::Tensor& t) { Guard([&] { b.BindOutput(n, t); return 0; }); })
+      .def("bind_output_to_device", [](IOBinding& b, const std::string& n, const std::string& dev, int id) {
+        Guard([&] {
+          b.BindOutputToDevice(n, dev == "cuda" ? c10::Device(c10::kCUDA, static_cast<c10::DeviceIndex>(id)) : c10::Device(c10::kCPU));
+          return 0;
+        });
+      })
+      .def("clear_inputs", &IOBinding::ClearInputs)
+      .def("clear_outputs", &IOBinding::ClearOutputs)
+      .def("synchronize_inputs", [](IOBinding& b) { Guard([&] { b.SynchronizeInputs(); return 0; }); })
+      .def("synchronize_outputs", [](IOBinding& b) { Guard([&] { b.SynchronizeOutputs(); return 0; }); })
+      .def("output_names", &IOBinding::OutputNames)
+      .def("results", [](IOBinding& b) {
+        py::list out;
+        for (auto& v : b.Results()) out.append(FromValue(v));
+        return out;
+      });
+
+  // ---- model / graph utilities (used by the Python tools and tests)
+  m.def("model_roundtrip", [](py::bytes b) {
+    std::string bytes = b;
+    return Guard([&] {
+      auto model = Model::LoadFromBytes(std::make_shared<std::string>(bytes), "");
+      return py::bytes(model->Serialize());
+    });
+  });
+  m.def("optimize_model", [](py::bytes b, int level, const std::vector<std::string>& disabled, bool gpu) {
+    std::string bytes = b;
+    return Guard([&] {
+      EnsureKernelsRegistered();
+      auto model = Model::LoadFromBytes(std::make_shared<std::string>(bytes), "");
+      std::set<std::string> dis(disabled.begin(), disabled.end());
+      ConfigOptions cfg;
+      OptimizerStats st = OptimizeGraph(model->MainGraph(), level, dis, gpu, cfg, 1);
+      return py::make_tuple(py::bytes(model->Serialize()), st.applied);
+    });
+  });
+  m.def("model_nodes", [](py::bytes b) {
+    std::string bytes = b;
+    return Guard([&] {
+      auto model = Model::LoadFromBytes(std::make_shared<std::string>(bytes), "");
+      py::list out;
+      for (Node* n : model->MainGraph().TopologicalOrder()) out.append(NodeToDict(*n));
+      return out;
+    });
+  });
+  m.def("tensor_from_proto", [](py::bytes b) {
+    std::string bytes = b;
+    return Guard([&] {
+      pb::TensorProto t;
+      pb::ParseTensor(bytes.data(), bytes.size(), &t);
+      return TensorFromProto(t, "");
+    });
+  });
+  m.def("tensor_to_proto", [](const at::Tensor& t, const std::string& name) {
+    return Guard([&] { return py::bytes(pb::SerializeTensor(TensorToProto(t, name))); });
+  });
+
+  // ---- sharding-spec algebra of the Distributed* operators
+  m.def("parse_shard_spec", [](const std::string& spec, const std::vector<int64_t>& mesh_elements,
+                               const std::vector<int64_t>& mesh_shape) {
+    return Guard([&] {
+      TensorPartitionSpec s = TensorPartitionSpec::Parse(spec, DeviceMesh{mesh_elements, mesh_shape});
+      py::dict d;
+      d["spec"] = s.ToString();
+      d["sharded_axis"] = s.ShardedAxis();
+      d["num_shards"] = s.NumShards();
+      return d;
+    });
+  });
+  m.def("shard_shape", [](const std::vector<int64_t>& shape, const std::string& spec, const std::vector<int64_t>& mesh_elements,
+                          const std::vector<int64_t>& mesh_shape) {
+    return Guard([&] {
+      return TensorPartitionSpec::Parse(spec, DeviceMesh{mesh_elements, mesh_shape}).ShardShape(shape);
+    });
+  });
+}

@@ -1,0 +1,21 @@
+// Helpers shared by the GPU op wrappers (kernels_cuda*.cc).
+#pragma once
+#include <ATen/ATen.h>
+
+#include "kernel.h"
+
+namespace ortb {
+
+void CheckLaunch(int rc, const char* what);
+
+// out[M,N] = act(alpha * x[M,K] @ w_nk[N,K]^T + bias) + residual on the tcgen05 GEMM kernel.
+// act == SWIGLU: w_nk holds gate rows then up rows, `dual_offset` rows apart.
+at::Tensor LaunchGemm(OpKernelContext& ctx, const at::Tensor& x2d, const at::Tensor& w_nk, int64_t n_out,
+                      int64_t dual_offset, const at::Tensor& bias, const at::Tensor& residual2d, int act, float alpha);
+
+// Sum `partial` over the ranks of the session's process group and add `residual` (may be undefined).
+at::Tensor GemmAllReduce(OpKernelContext& ctx, const at::Tensor& partial, const at::Tensor& residual);
+
+void RegisterMoreCudaKernels(KernelRegistry& r);
+
+}  // namespace ortb

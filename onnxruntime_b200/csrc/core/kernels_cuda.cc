@@ -1,0 +1,206 @@
+// GPU execution provider: op kernels that launch the hand-written sm_100a
+// kernels of libortb200_kernels (csrc/cuda).  Each class parses its attributes
+// and pre-packs constant weights once at session initialisation; Compute()
+// only fills an argument struct and launches on the current torch stream, so a
+// whole decode step is a flat, CUDA-graph-capturable launch sequence.
+//
+// Reference counterparts: onnxruntime/core/providers/cuda/math/matmul.cc,
+// onnxruntime/contrib_ops/cuda/bert/{skip_layer_norm.cc,rotary_embedding.cc,
+// group_query_attention.cc,fast_gelu.cc}, quantization/matmul_nbits.cc, moe/moe.cc.
+#include <ATen/ATen.h>
+#include <ATen/cuda/CUDAContext.h>
+
+#include "cuda_ops.h"
+#include "kernel.h"
+#include "ortb200_kernels.h"
+#include "session.h"
+
+namespace ortb {
+
+namespace {
+
+using Ctx = OpKernelContext;
+constexpr int kMax = 1 << 30;
+constexpr const char* MS = kMSDomain;
+constexpr const char* kFusedDomain = "com.ortb200";
+
+int DtypeCode(at::ScalarType t) {
+  if (t == at::kHalf) return ORTB200_F16;
+  if (t == at::kBFloat16) return ORTB200_BF16;
+  if (t == at::kFloat) return ORTB200_F32;
+  ORTB_THROW(NOT_IMPLEMENTED, "dtype not supported by the GPU kernels");
+}
+
+int ActCode(const std::string& a) {
+  if (a == "none" || a.empty()) return ORTB200_ACT_NONE;
+  if (a == "gelu") return ORTB200_ACT_GELU;
+  if (a == "fastgelu") return ORTB200_ACT_FASTGELU;
+  if (a == "relu") return ORTB200_ACT_RELU;
+  if (a == "silu") return ORTB200_ACT_SILU;
+  if (a == "quickgelu") return ORTB200_ACT_QUICKGELU;
+  if (a == "swiglu") return ORTB200_ACT_SWIGLU;
+  ORTB_THROW(INVALID_ARGUMENT, "unknown activation ", a);
+}
+
+bool HalfType(at::ScalarType t) { return t == at::kHalf || t == at::kBFloat16; }
+
+}  // namespace
+
+void CheckLaunch(int rc, const char* what) {
+  if (rc != 0) ORTB_THROW(EP_FAIL, what, " rejected its arguments (code ", rc, ")");
+}
+
+// out[M,N] = act(x[M,K] @ w_nk[N,K]^T + bias) + residual on the tcgen05 GEMM.
+at::Tensor LaunchGemm(Ctx& ctx, const at::Tensor& x2d, const at::Tensor& w_nk, int64_t n_out, int64_t dual_offset,
+                      const at::Tensor& bias, const at::Tensor& residual2d, int act, float alpha) {
+  InferenceSession* s = ctx.session();
+  const int64_t M = x2d.size(0), K = x2d.size(1);
+  at::Tensor out = at::empty({M, n_out}, x2d.options());
+  if (M == 0) return out;
+  const int64_t ws_bytes = ortb200_gemm_workspace_bytes(static_cast<int>(M), static_cast<int>(n_out), static_cast<int>(K), act);
+  at::Tensor& ws = s->GemmWorkspace(ws_bytes);
+  ortb200_gemm_args a{};
+  a.x = x2d.data_ptr();
+  a.w = w_nk.data_ptr();
+  a.out = out.data_ptr();
+  a.bias = bias.defined() ? bias.data_ptr() : nullptr;
+  a.residual = residual2d.defined() ? residual2d.data_ptr() : nullptr;
+  a.ldo = n_out;
+  a.ldr = residual2d.defined() ? residual2d.stride(0) : 0;
+  a.M = static_cast<int>(M);
+  a.N = static_cast<int>(n_out);
+  a.K = static_cast<int>(K);
+  a.w_rows = static_cast<int>(w_nk.size(0));
+  a.dual_offset = static_cast<int>(dual_offset);
+  a.dtype = DtypeCode(x2d.scalar_type());
+  a.act = act;
+  a.alpha = alpha;
+  a.workspace = ws.data_ptr();
+  a.workspace_bytes = ws.numel();
+  a.status = s->StatusWord().data_ptr<int>();
+  a.use_pdl = s->config().Get("ortb200.pdl", "0") == "1" ? 1 : 0;
+  CheckLaunch(ortb200_gemm(&a, ctx.cuda_stream()), "ortb200_gemm");
+  s->AddLaunches(1);
+  return out;
+}
+
+namespace {
+
+at::Tensor Flatten2D(const at::Tensor& x) { return x.reshape({-1, x.size(-1)}).contiguous(); }
+
+std::vector<int64_t> OutShape(const at::Tensor& x, int64_t n) {
+  std::vector<int64_t> s = x.sizes().vec();
+  s.back() = n;
+  return s;
+}
+
+// MatMul / FusedGemm / Gemm with a constant fp16/bf16 weight.
+class GemmKernel final : public OpKernel {
+ public:
+  explicit GemmKernel(const OpKernelInfo& info) : OpKernel(info) {
+    const Node& n = info.node;
+    const at::Tensor* w = info.constant_input(1);
+    ORTB_ENFORCE(w != nullptr, "GEMM kernel needs a constant weight");
+    bool w_is_nk = false;
+    if (n.op_type == "Gemm") {
+      w_is_nk = n.attr_i("transB", 0) != 0;
+      alpha_ = n.attr_f("alpha", 1.f);
+      bias_idx_ = 2;
+    } else if (n.op_type == "FusedMatMul") {
+      w_is_nk = n.attr_i("transB", 0) != 0;
+      alpha_ = n.attr_f("alpha", 1.f);
+    } else if (n.op_type == "FusedGemm") {
+      bias_idx_ = 2;
+      residual_idx_ = 3;
+      act_ = ActCode(n.attr_s("activation", "none"));
+      all_reduce_ = n.attr_i("all_reduce", 0) != 0;
+    }
+    w_nk_ = w_is_nk ? w->contiguous() : w->t().contiguous();  // pre-pack: [N, K], K contiguous
+    N_ = w_nk_.size(0);
+  }
+  void Compute(Ctx& ctx) const override {
+    const at::Tensor& x = ctx.RequiredInput(0);
+    at::Tensor x2 = Flatten2D(x);
+    at::Tensor bias = bias_idx_ >= 0 && ctx.HasInput(bias_idx_) ? ctx.Input(bias_idx_) : at::Tensor();
+    at::Tensor res = residual_idx_ >= 0 && ctx.HasInput(residual_idx_) ? Flatten2D(ctx.Input(residual_idx_)) : at::Tensor();
+    if (all_reduce_ && ctx.session()->world_size > 1) {
+      // row-parallel: partial product, sum over ranks, then the residual
+      at::Tensor y = LaunchGemm(ctx, x2, w_nk_, N_, 0, bias, at::Tensor(), act_, alpha_);
+      y = GemmAllReduce(ctx, y, res);
+      ctx.SetOutput(0, y.reshape(OutShape(x, N_)));
+      return;
+    }
+    at::Tensor y = LaunchGemm(ctx, x2, w_nk_, N_, 0, bias, res, act_, alpha_);
+    ctx.SetOutput(0, y.reshape(OutShape(x, N_)));
+  }
+
+ private:
+  at::Tensor w_nk_;
+  int64_t N_ = 0;
+  int bias_idx_ = -1, residual_idx_ = -1;
+  int act_ = ORTB200_ACT_NONE;
+  float alpha_ = 1.f;
+  bool all_reduce_ = false;
+};
+
+bool GemmSupports(const Node& n, const Graph& g) {
+  if (n.inputs.size() < 2) return false;
+  const at::Tensor* w = g.GetConstant(n.inputs[1]);
+  if (!w || w->dim() != 2 || !HalfType(w->scalar_type())) return false;
+  if (g.GetConstant(n.inputs[0])) return false;
+  const bool nk = (n.op_type == "Gemm" || n.op_type == "FusedMatMul") && n.attr_i("transB", 0) != 0;
+  const int64_t K = nk ? w->size(1) : w->size(0);
+  if (K % 8 != 0) return false;
+  if (n.op_type == "Gemm" && (n.attr_i("transA", 0) != 0 || n.attr_f("beta", 1.f) != 1.f)) return false;
+  if (n.op_type == "Gemm" && n.has_input(2)) {
+    const at::Tensor* c = g.GetConstant(n.inputs[2]);
+    if (!c || c->dim() != 1) return false;
+  }
+  if (n.op_type == "FusedMatMul" && (n.attr_i("transA", 0) || n.attr_i("transBatchA", 0) || n.attr_i("transBatchB", 0))) return false;
+  return true;
+}
+
+class GemmSwiGLUKernel final : public OpKernel {
+ public:
+  explicit GemmSwiGLUKernel(const OpKernelInfo& info) : OpKernel(info) {
+    const at::Tensor* wg = info.constant_input(1);
+    const at::Tensor* wu = info.constant_input(2);
+    ORTB_ENFORCE(wg && wu, "GemmSwiGLU needs constant weights");
+    I_ = wg->size(1);
+    w_ = at::cat({wg->t(), wu->t()}, 0).contiguous();  // [2I, K]: gate rows then up rows
+  }
+  void Compute(Ctx& ctx) const override {
+    const at::Tensor& x = ctx.RequiredInput(0);
+    at::Tensor y = LaunchGemm(ctx, Flatten2D(x), w_, I_, I_, at::Tensor(), at::Tensor(), ORTB200_ACT_SWIGLU, 1.f);
+    ctx.SetOutput(0, y.reshape(OutShape(x, I_)));
+  }
+
+ private:
+  at::Tensor w_;
+  int64_t I_ = 0;
+};
+
+template <typename K>
+void RegisterClass(KernelRegistry& r, const std::string& domain, const std::string& op,
+                   std::function<bool(const Node&, const Graph&)> supports = nullptr, std::vector<int> host = {}) {
+  KernelDef d;
+  d.domain = domain;
+  d.op_type = op;
+  d.supports = std::move(supports);
+  d.host_inputs = std::move(host);
+  d.factory = [](const OpKernelInfo& info) { return std::make_unique<K>(info); };
+  r.Register(std::move(d));
+}
+
+}  // namespace
+
+void RegisterCudaKernels(KernelRegistry& r) {
+  RegisterClass<GemmKernel>(r, "", "MatMul", GemmSupports);
+  RegisterClass<GemmKernel>(r, "", "Gemm", GemmSupports);
+  RegisterClass<GemmKernel>(r, MS, "FusedMatMul", GemmSupports);
+  RegisterClass<GemmKernel>(r, kFusedDomain, "FusedGemm", GemmSupports);
+  RegisterClass<GemmSwiGLUKernel>(r, kFusedDomain, "GemmSwiGLU");
+  RegisterMoreCudaKernels(r);
+}
+
+}  // namespace ortb

@@ -1,0 +1,226 @@
+// GPU-only lowering passes: rewrite GEMM chains onto the fused sm_100a kernels.
+//
+//  * GemmEpilogueFusion:  MatMul(x, W) [+ bias] [+ activation] [+ residual]
+//        -> com.ortb200.FusedGemm(x, W, bias, residual) {activation}
+//    one tcgen05 GEMM whose epilogue applies bias, activation and the residual
+//    add (the reference runs cuBLAS followed by separate BiasGelu / Add kernels).
+//  * SwiGLUFusion:  Mul(silu(MatMul(x, Wg)), MatMul(x, Wu)) -> com.ortb200.GemmSwiGLU(x, Wg, Wu)
+//    one kernel with two TMEM accumulators sharing the activation tile.
+//  * MatMulAllReduceFusion:  AllReduce(GEMM) -> the GEMM carries all_reduce=1 and
+//    its kernel finishes the row-parallel sum over NVLink itself.
+#include "optimizer.h"
+
+namespace ortb {
+namespace opt {
+
+namespace {
+
+constexpr const char* kFusedDomain = "com.ortb200";
+
+bool IsHalfWeight2D(const Graph& g, const std::string& name) {
+  const at::Tensor* w = g.GetConstant(name);
+  if (!w || w->dim() != 2) return false;
+  if (w->scalar_type() != at::kHalf && w->scalar_type() != at::kBFloat16) return false;
+  return w->size(0) % 8 == 0;  // K: TMA row pitch must be a multiple of 16 bytes
+}
+
+Node* SoleConsumer(const Graph& g, const std::string& v) {
+  if (g.IsGraphOutput(v)) return nullptr;
+  auto cs = g.Consumers(v);
+  return cs.size() == 1 ? cs[0] : nullptr;
+}
+
+// y * sigmoid(y) rooted at a Mul node; returns y's name
+bool MatchSilu(const Graph& g, Node* mul, std::string* y, Node** sigmoid) {
+  if (mul->op_type != "Mul" || !mul->domain.empty() || mul->inputs.size() != 2) return false;
+  for (int s = 0; s < 2; ++s) {
+    Node* sg = g.Producer(mul->inputs[s]);
+    if (sg && sg->op_type == "Sigmoid" && sg->domain.empty() && sg->inputs[0] == mul->inputs[1 - s] &&
+        g.NumConsumers(sg->outputs[0]) == 1) {
+      *y = mul->inputs[1 - s];
+      *sigmoid = sg;
+      return true;
+    }
+  }
+  return false;
+}
+
+int SwiGLUFusion(PassContext& c) {
+  Graph& g = c.g;
+  int count = 0;
+  for (Node* top : g.Nodes()) {
+    if (top->op_type != "Mul" || !top->domain.empty() || top->inputs.size() != 2) continue;
+    for (int s = 0; s < 2; ++s) {
+      Node* silu = g.Producer(top->inputs[s]);
+      Node* up = g.Producer(top->inputs[1 - s]);
+      if (!silu || !up) continue;
+      std::string gate_out;
+      Node* sig = nullptr;
+      if (!MatchSilu(g, silu, &gate_out, &sig)) continue;
+      Node* gate = g.Producer(gate_out);
+      if (!gate || gate->op_type != "MatMul" || !gate->domain.empty() || up->op_type != "MatMul" || !up->domain.empty()) continue;
+      if (gate->inputs[0] != up->inputs[0]) continue;
+      if (!IsHalfWeight2D(g, gate->inputs[1]) || !IsHalfWeight2D(g, up->inputs[1])) continue;
+      if (g.GetConstant(gate->inputs[1])->sizes() != g.GetConstant(up->inputs[1])->sizes()) continue;
+      if (g.NumConsumers(gate_out) != 2 || g.NumConsumers(up->outputs[0]) != 1 || g.NumConsumers(silu->outputs[0]) != 1) continue;
+      g.AddNode("GemmSwiGLU", {gate->inputs[0], gate->inputs[1], up->inputs[1]}, {top->outputs[0]}, kFusedDomain,
+                g.UniqueName("GemmSwiGLU"));
+      g.RemoveNode(top);
+      g.RemoveNode(silu);
+      g.RemoveNode(sig);
+      g.RemoveNode(gate);
+      g.RemoveNode(up);
+      ++count;
+      break;
+    }
+  }
+  return count;
+}
+
+int GemmEpilogueFusion(PassContext& c) {
+  Graph& g = c.g;
+  int count = 0;
+  for (Node* mm : g.Nodes()) {
+    if (mm->op_type != "MatMul" || !mm->domain.empty()) continue;
+    if (!IsHalfWeight2D(g, mm->inputs[1]) || g.GetConstant(mm->inputs[0])) continue;
+    const int64_t N = g.GetConstant(mm->inputs[1])->size(1);
+    std::vector<Node*> chain;
+    std::string cur = mm->outputs[0];
+    std::string bias, residual, act = "none";
+    float alpha = 1.702f;
+    Node* n = SoleConsumer(g, cur);
+    // bias
+    if (n && n->op_type == "Add" && n->domain.empty()) {
+      for (int s = 0; s < 2; ++s) {
+        int64_t len = 0;
+        if (n->inputs[1 - s] == cur && IsConst1D(g, n->inputs[s], &len) && len == N) {
+          bias = n->inputs[s];
+          chain.push_back(n);
+          cur = n->outputs[0];
+          n = SoleConsumer(g, cur);
+          break;
+        }
+      }
+    }
+    // activation
+    if (n) {
+      std::string a;
+      if (n->domain == kMSDomain && n->op_type == "FastGelu" && !n->has_input(1)) a = "fastgelu";
+      else if (n->domain == kMSDomain && n->op_type == "Gelu") a = "gelu";
+      else if (n->domain.empty() && n->op_type == "Gelu") a = n->attr_s("approximate", "none") == "tanh" ? "fastgelu" : "gelu";
+      else if (n->domain.empty() && n->op_type == "Relu") a = "relu";
+      else if (n->domain == kMSDomain && n->op_type == "QuickGelu") { a = "quickgelu"; alpha = n->attr_f("alpha", 1.702f); }
+      else if (bias.empty() && n->domain == kMSDomain && (n->op_type == "BiasGelu" || (n->op_type == "FastGelu" && n->has_input(1))) &&
+               n->inputs[0] == cur) {
+        int64_t len = 0;
+        if (IsConst1D(g, n->inputs[1], &len) && len == N) {
+          bias = n->inputs[1];
+          a = n->op_type == "BiasGelu" ? "gelu" : "fastgelu";
+        }
+      }
+      if (!a.empty() && !(a == "quickgelu" && std::abs(alpha - 1.702f) > 1e-4f)) {
+        act = a;
+        chain.push_back(n);
+        cur = n->outputs[0];
+        n = SoleConsumer(g, cur);
+      }
+    }
+    // silu written as y * sigmoid(y): two consumers of cur
+    if (act == "none" && !g.IsGraphOutput(cur) && g.NumConsumers(cur) == 2) {
+      for (Node* cand : g.Consumers(cur)) {
+        std::string y;
+        Node* sig = nullptr;
+        if (MatchSilu(g, cand, &y, &sig) && y == cur) {
+          act = "silu";
+          chain.push_back(sig);
+          chain.push_back(cand);
+          cur = cand->outputs[0];
+          n = SoleConsumer(g, cur);
+          break;
+        }
+      }
+    }
+    // residual
+    if (n && n->op_type == "Add" && n->domain.empty() && n->inputs.size() == 2) {
+      for (int s = 0; s < 2; ++s) {
+        if (n->inputs[1 - s] == cur && !g.GetConstant(n->inputs[s]) && n->inputs[s] != cur) {
+          residual = n->inputs[s];
+          chain.push_back(n);
+          cur = n->outputs[0];
+          break;
+        }
+      }
+    }
+    if (chain.empty()) continue;
+    std::vector<std::string> ins = {mm->inputs[0], mm->inputs[1], bias, residual};
+    while (!ins.empty() && ins.back().empty()) ins.pop_back();
+    Node* f = g.AddNode("FusedGemm", ins, {cur}, kFusedDomain, g.UniqueName("FusedGemm"));
+    f->set_attr_s("activation", act);
+    g.RemoveNode(mm);
+    for (Node* x : chain) g.RemoveNode(x);
+    ++count;
+  }
+  return count;
+}
+
+int MatMulAllReduceFusion(PassContext& c) {
+  Graph& g = c.g;
+  int count = 0;
+  if (c.world_size <= 1) return 0;
+  for (Node* ar : g.Nodes()) {
+    if (ar->op_type != "AllReduce" || ar->domain != kMSDomain || ar->inputs.size() != 1) continue;
+    Node* p = g.Producer(ar->inputs[0]);
+    if (!p || g.NumConsumers(p->outputs[0]) != 1) continue;
+    if (p->domain.empty() && p->op_type == "MatMul" && IsHalfWeight2D(g, p->inputs[1]) && !g.GetConstant(p->inputs[0])) {
+      Node* f = g.AddNode("FusedGemm", {p->inputs[0], p->inputs[1]}, {ar->outputs[0]}, kFusedDomain, g.UniqueName("GemmAllReduce"));
+      f->set_attr_s("activation", "none");
+      f->set_attr_i("all_reduce", 1);
+      g.RemoveNode(p);
+      g.RemoveNode(ar);
+      ++count;
+    } else if (p->domain == kFusedDomain && p->op_type == "FusedGemm" && !p->has_input(3) && !p->has_input(2) &&
+               p->attr_s("activation", "none") == "none") {
+      p->set_attr_i("all_reduce", 1);
+      p->outputs[0] = ar->outputs[0];
+      g.RemoveNode(ar);
+      g.Invalidate();
+      ++count;
+    }
+  }
+  return count;
+}
+
+// After MatMulAllReduceFusion: a residual Add directly behind an all-reducing GEMM is applied after the sum.
+int AllReduceResidualFusion(PassContext& c) {
+  Graph& g = c.g;
+  int count = 0;
+  for (Node* f : g.Nodes()) {
+    if (f->domain != kFusedDomain || f->op_type != "FusedGemm" || f->attr_i("all_reduce", 0) == 0 || f->has_input(3)) continue;
+    Node* add = SoleConsumer(g, f->outputs[0]);
+    if (!add || add->op_type != "Add" || !add->domain.empty()) continue;
+    for (int s = 0; s < 2; ++s) {
+      if (add->inputs[1 - s] == f->outputs[0] && !g.GetConstant(add->inputs[s]) && add->inputs[s] != f->outputs[0]) {
+        f->inputs.resize(4);
+        f->inputs[3] = add->inputs[s];
+        f->outputs[0] = add->outputs[0];
+        g.RemoveNode(add);
+        g.Invalidate();
+        ++count;
+        break;
+      }
+    }
+  }
+  return count;
+}
+
+}  // namespace
+
+void AddGpuPasses(std::vector<Pass>& v) {
+  v.push_back({"SwiGLUFusion", 2, true, SwiGLUFusion});
+  v.push_back({"MatMulAllReduceFusion", 2, true, MatMulAllReduceFusion});
+  v.push_back({"AllReduceResidualFusion", 2, true, AllReduceResidualFusion});
+  v.push_back({"GemmEpilogueFusion", 2, true, GemmEpilogueFusion});
+}
+
+}  // namespace opt
+}  // namespace ortb

@@ -1,0 +1,500 @@
+#include "session.h"
+
+#include <ATen/cuda/CUDAContext.h>
+#include <ATen/cuda/CUDAGraph.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <c10/cuda/CUDAStream.h>
+#include <cuda_runtime_api.h>
+#include <unistd.h>
+
+#include <ctime>
+#include <fstream>
+#include <iomanip>
+#include <sstream>
+
+#include "executor.h"
+
+namespace ortb {
+
+// ---------------------------------------------------------------- Profiler
+void Profiler::Start(const std::string& prefix) {
+  std::time_t t = std::time(nullptr);
+  std::tm tm_buf;
+  localtime_r(&t, &tm_buf);
+  std::ostringstream ss;
+  ss << prefix << "_" << std::put_time(&tm_buf, "%Y-%m-%d_%H-%M-%S") << ".json";
+  path_ = ss.str();
+  t0_ = std::chrono::steady_clock::now();
+  enabled_ = true;
+  events_.clear();
+}
+
+int64_t Profiler::NowUs() const {
+  return std::chrono::duration_cast<std::chrono::microseconds>(std::chrono::steady_clock::now() - t0_).count();
+}
+
+void Profiler::Record(const std::string& cat, const std::string& name, int64_t ts_us, int64_t dur_us,
+                      std::map<std::string, std::string> args) {
+  if (!enabled_) return;
+  std::lock_guard<std::mutex> lk(mu_);
+  if (events_.size() >= max_events_) return;  // capped like the reference's max_num_events_
+  events_.push_back({cat, name, ts_us, dur_us, std::move(args)});
+}
+
+static std::string JsonEscape(const std::string& s) {
+  std::string o;
+  for (char c : s) {
+    if (c == '"' || c == '\\') { o.push_back('\\'); o.push_back(c); }
+    else if (c == '\n') o += "\\n";
+    else if (static_cast<unsigned char>(c) < 0x20) o += ' ';
+    else o.push_back(c);
+  }
+  return o;
+}
+
+std::string Profiler::End() {
+  if (!enabled_) return "";
+  std::lock_guard<std::mutex> lk(mu_);
+  std::ofstream f(path_);
+  const int pid = static_cast<int>(::getpid());
+  f << "[\n";
+  for (size_t i = 0; i < events_.size(); ++i) {
+    auto& e = events_[i];
+    f << "{\"cat\" : \"" << e.cat << "\",\"pid\" :" << pid << ",\"tid\" :" << 0 << ",\"dur\" :" << e.dur_us
+      << ",\"ts\" :" << e.ts_us << ",\"ph\" : \"X\",\"name\" :\"" << JsonEscape(e.name) << "\",\"args\" : {";
+    bool first = true;
+    for (auto& kv : e.args) {
+      if (!first) f << ",";
+      first = false;
+      f << "\"" << JsonEscape(kv.first) << "\" : \"" << JsonEscape(kv.second) << "\"";
+    }
+    f << "}}" << (i + 1 < events_.size() ? ",\n" : "\n");
+  }
+  f << "]\n";
+  enabled_ = false;
+  return path_;
+}
+
+// ------------------------------------------------------- InferenceSession
+struct InferenceSession::CapturedGraph {
+  at::cuda::CUDAGraph graph;
+  std::vector<Value> slots;            // slot vector captured with the graph (static addresses)
+  std::vector<at::Tensor> static_in;   // per runtime input: tensor whose storage the graph reads
+  std::vector<std::vector<int64_t>> in_shapes;
+  bool captured = false;
+  int warm_runs = 0;
+};
+
+InferenceSession::InferenceSession(const SessionOptions& so) : so_(so) {
+  EnsureKernelsRegistered();
+  if (so_.enable_profiling) {
+    profiler_.Start(so_.profile_file_prefix);
+    profiling_start_ns_ =
+        std::chrono::duration_cast<std::chrono::nanoseconds>(std::chrono::steady_clock::now().time_since_epoch()).count();
+  }
+}
+
+InferenceSession::~InferenceSession() {
+  cuda_graphs_.clear();
+  exec_.reset();
+}
+
+void InferenceSession::Load(const std::string& path) {
+  if (model_) ORTB_THROW(MODEL_LOADED, "This session already contains a loaded model.");
+  const int64_t t0 = profiler_.NowUs();
+  model_ = Model::Load(path);
+  profiler_.Record("Session", "model_loading_uri", t0, profiler_.NowUs() - t0);
+}
+
+void InferenceSession::LoadFromBytes(const std::string& bytes) {
+  if (model_) ORTB_THROW(MODEL_LOADED, "This session already contains a loaded model.");
+  const int64_t t0 = profiler_.NowUs();
+  model_ = Model::LoadFromBytes(std::make_shared<std::string>(bytes), "");
+  profiler_.Record("Session", "model_loading_array", t0, profiler_.NowUs() - t0);
+}
+
+static void ApplyFreeDimOverrides(Graph& g, const SessionOptions& so) {
+  if (so.free_dim_by_name.empty() && so.free_dim_by_denotation.empty()) return;
+  for (auto& v : g.Inputs()) {
+    for (auto& d : v.type.dims) {
+      if (d.has_value) continue;
+      auto it = so.free_dim_by_name.find(d.param);
+      if (!d.param.empty() && it != so.free_dim_by_name.end()) {
+        d.has_value = true;
+        d.value = it->second;
+        continue;
+      }
+      auto dt = so.free_dim_by_denotation.find(d.denotation);
+      if (!d.denotation.empty() && dt != so.free_dim_by_denotation.end()) {
+        d.has_value = true;
+        d.value = dt->second;
+      }
+    }
+  }
+}
+
+void InferenceSession::Initialize(const std::vector<std::pair<std::string, ProviderOptions>>& providers,
+                                  const std::vector<std::string>& disabled_optimizers) {
+  if (!model_) ORTB_THROW(NO_MODEL, "Model was not loaded.");
+  if (initialized_) ORTB_THROW(MODEL_LOADED, "Session has already been initialized.");
+  const int64_t t0 = profiler_.NowUs();
+
+  providers_.clear();
+  device_ = c10::Device(c10::kCPU);
+  for (auto& p : providers) {
+    if (p.first == kCudaEP) {
+      int dev_id = 0;
+      auto it = p.second.find("device_id");
+      if (it != p.second.end()) dev_id = std::stoi(it->second);
+      if (!at::hasCUDA() || dev_id >= static_cast<int>(at::cuda::device_count()))
+        ORTB_THROW(EP_FAIL, "CUDAExecutionProvider: no usable CUDA device ", dev_id);
+      device_ = c10::Device(c10::kCUDA, static_cast<c10::DeviceIndex>(dev_id));
+      auto g = p.second.find("enable_cuda_graph");
+      enable_cuda_graph_ = g != p.second.end() && (g->second == "1" || g->second == "true" || g->second == "True");
+      providers_.push_back(kCudaEP);
+      provider_options_[kCudaEP] = p.second;
+      provider_options_[kCudaEP]["device_id"] = std::to_string(dev_id);
+    } else if (p.first == kCpuEP) {
+      providers_.push_back(kCpuEP);
+      provider_options_[kCpuEP] = p.second;
+    } else {
+      ORTB_THROW(INVALID_ARGUMENT, "Unknown execution provider ", p.first);
+    }
+  }
+  if (std::find(providers_.begin(), providers_.end(), kCpuEP) == providers_.end()) {
+    providers_.push_back(kCpuEP);  // the CPU provider is always present, last
+    provider_options_[kCpuEP];
+  }
+
+  Graph& g = model_->MainGraph();
+  // session-supplied initializers
+  for (auto& kv : so_.initializers) {
+    if (!g.IsInitializer(kv.first)) ORTB_THROW(INVALID_ARGUMENT, "add_initializer: '", kv.first, "' is not an initializer of the model");
+    g.AddInitializer(kv.first, kv.second);
+    g.PendingExternal().erase(kv.first);
+  }
+  for (auto& kv : so_.external_initializers) {
+    if (!g.IsInitializer(kv.first))
+      ORTB_THROW(INVALID_ARGUMENT, "add_external_initializers: '", kv.first, "' is not an initializer of the model");
+    g.AddInitializer(kv.first, kv.second);
+    g.PendingExternal().erase(kv.first);
+  }
+  for (auto& name : g.PendingExternal()) {
+    ORTB_THROW(INVALID_ARGUMENT, "initializer '", name, "' expects its data from the session (add_external_initializers)");
+  }
+  ApplyFreeDimOverrides(g, so_);
+
+  c10::cuda::OptionalCUDAGuard guard;
+  if (device_.is_cuda()) guard.set_device(device_);
+
+  std::set<std::string> disabled(disabled_optimizers.begin(), disabled_optimizers.end());
+  {
+    std::istringstream ss(so_.config.Get("optimization.disable_specified_optimizers"));
+    std::string tok;
+    while (std::getline(ss, tok, ',')) if (!tok.empty()) disabled.insert(tok);
+  }
+  OptimizeGraph(g, so_.graph_optimization_level, disabled, device_.is_cuda(), so_.config, world_size);
+
+  if (!so_.optimized_model_filepath.empty()) model_->Save(so_.optimized_model_filepath);
+
+  auto exec = std::make_unique<GraphExecutor>(this, &g, nullptr);
+  exec->Build();
+  input_names_ = exec->input_names();
+  output_names_ = exec->output_names();
+  input_device_ = exec->input_devices();
+  graph_capturable_ = exec->capturable();
+  exec_ = std::move(exec);
+  initialized_ = true;
+  profiler_.Record("Session", "session_initialization", t0, profiler_.NowUs() - t0);
+}
+
+std::vector<std::string> InferenceSession::Providers() const { return providers_; }
+
+static NodeArgMeta MetaOf(const ValueInfo& v) {
+  NodeArgMeta m;
+  m.name = v.name;
+  const pb::TypeProto* t = &v.type;
+  std::string wrap_open, wrap_close;
+  if (t->which == 4) { wrap_open = "seq("; wrap_close = ")"; if (t->elem) t = t->elem.get(); }
+  else if (t->which == 9) { wrap_open = "optional("; wrap_close = ")"; if (t->elem) t = t->elem.get(); }
+  m.type = wrap_open + "tensor(" + pb::DataTypeName(t->elem_type) + ")" + wrap_close;
+  m.has_shape = t->has_shape;
+  for (auto& d : t->dims) {
+    m.shape.push_back(d.has_value ? d.value : -1);
+    m.sym.push_back(d.has_value ? "" : d.param);
+  }
+  return m;
+}
+
+std::vector<NodeArgMeta> InferenceSession::InputsMeta() const {
+  std::vector<NodeArgMeta> out;
+  const Graph& g = *model_->graph_;
+  for (auto& v : g.Inputs())
+    if (!g.IsInitializer(v.name)) out.push_back(MetaOf(v));
+  return out;
+}
+
+std::vector<NodeArgMeta> InferenceSession::OutputsMeta() const {
+  std::vector<NodeArgMeta> out;
+  for (auto& v : model_->graph_->Outputs()) out.push_back(MetaOf(v));
+  return out;
+}
+
+std::vector<NodeArgMeta> InferenceSession::OverridableInitializersMeta() const {
+  std::vector<NodeArgMeta> out;
+  const Graph& g = *model_->graph_;
+  for (auto& v : g.Inputs())
+    if (g.IsInitializer(v.name) && !g.IsConstant(v.name)) out.push_back(MetaOf(v));
+  return out;
+}
+
+std::vector<std::tuple<std::string, std::string, std::string>> InferenceSession::NodeAssignments() const {
+  std::vector<std::tuple<std::string, std::string, std::string>> out;
+  GraphExecutor* ex = exec_.get();
+  if (!ex) return out;
+  for (auto& st : ex->steps()) out.emplace_back(st.node->name, st.node->op_type, st.node->ep);
+  return out;
+}
+
+at::Tensor& InferenceSession::GemmWorkspace(int64_t nbytes) {
+  if (!gemm_ws_.defined() || gemm_ws_.numel() < nbytes) {
+    const int64_t sz = std::max<int64_t>(nbytes, 64 << 20);
+    gemm_ws_ = at::zeros({sz}, at::TensorOptions().dtype(at::kByte).device(device_));
+  }
+  return gemm_ws_;
+}
+
+at::Tensor& InferenceSession::StatusWord() {
+  if (!status_word_.defined()) status_word_ = at::zeros({4}, at::TensorOptions().dtype(at::kInt).device(device_));
+  return status_word_;
+}
+
+void InferenceSession::CheckDeviceStatus() {
+  if (!status_word_.defined()) return;
+  const int code = status_word_.cpu().data_ptr<int>()[0];
+  if (code != 0) {
+    status_word_.zero_();
+    ORTB_THROW(EP_FAIL, "a GPU kernel reported status ", code, " (a bounded wait ran out); the run's outputs are invalid");
+  }
+}
+
+static void ValidateFeed(const ValueInfo& vi, const at::Tensor& t) {
+  if (vi.type.which != 1) return;
+  if (vi.type.elem_type != 0) {
+    at::ScalarType want = ToTorchType(vi.type.elem_type);
+    if (want != t.scalar_type())
+      ORTB_THROW(INVALID_ARGUMENT, "Unexpected input data type. Actual: (tensor(", pb::DataTypeName(ToOnnxType(t.scalar_type())),
+                 ")) , expected: (tensor(", pb::DataTypeName(vi.type.elem_type), ")) for input '", vi.name, "'");
+  }
+  if (vi.type.has_shape) {
+    if (static_cast<int64_t>(vi.type.dims.size()) != t.dim())
+      ORTB_THROW(INVALID_ARGUMENT, "Invalid rank for input: ", vi.name, " Got: ", t.dim(), " Expected: ", vi.type.dims.size(),
+                 " Please fix either the inputs/outputs or the model.");
+    for (size_t i = 0; i < vi.type.dims.size(); ++i)
+      if (vi.type.dims[i].has_value && vi.type.dims[i].value != t.size(i))
+        ORTB_THROW(INVALID_ARGUMENT, "Got invalid dimensions for input: ", vi.name, " for the following indices\n index: ", i,
+                   " Got: ", t.size(i), " Expected: ", vi.type.dims[i].value,
+                   "\n Please fix either the inputs/outputs or the model.");
+  }
+}
+
+std::vector<Value> InferenceSession::RunImpl(const RunOptions& ro, const std::vector<std::string>& feed_names,
+                                             const std::vector<Value>& feeds,
+                                             const std::vector<std::string>& output_names_in,
+                                             const std::vector<Value>* bound_outputs) {
+  if (!initialized_) ORTB_THROW(FAIL, "Session not initialized.");
+  ORTB_ENFORCE_ARG(feed_names.size() == feeds.size(), "feed names and values differ in length");
+  std::lock_guard<std::mutex> run_lock(run_mu_);
+  GraphExecutor* ex = exec_.get();
+  const int64_t t_run0 = profiler_.NowUs();
+  c10::cuda::OptionalCUDAGuard guard;
+  if (device_.is_cuda()) guard.set_device(device_);
+
+  std::vector<std::string> output_names = output_names_in.empty() ? output_names_ : output_names_in;
+  for (auto& n : output_names)
+    if (std::find(output_names_.begin(), output_names_.end(), n) == output_names_.end())
+      ORTB_THROW(INVALID_ARGUMENT, "Invalid output name:", n);
+
+  // order the feeds as the plan expects and validate them
+  const Graph& g = *model_->graph_;
+  std::vector<Value> inputs(input_names_.size());
+  for (size_t i = 0; i < feed_names.size(); ++i) {
+    auto it = std::find(input_names_.begin(), input_names_.end(), feed_names[i]);
+    if (it == input_names_.end()) ORTB_THROW(INVALID_ARGUMENT, "Invalid input name: ", feed_names[i]);
+    const size_t idx = static_cast<size_t>(it - input_names_.begin());
+    if (feeds[i].t.defined()) {
+      for (auto& vi : g.Inputs())
+        if (vi.name == feed_names[i]) ValidateFeed(vi, feeds[i].t);
+      const c10::Device want = input_device_[idx];
+      inputs[idx].t = feeds[i].t.device() == want ? feeds[i].t : feeds[i].t.to(want, /*non_blocking=*/true);
+    } else {
+      inputs[idx] = feeds[i];
+    }
+  }
+  for (size_t i = 0; i < inputs.size(); ++i)
+    if (!inputs[i].defined() && !g.IsInitializer(input_names_[i]))
+      ORTB_THROW(INVALID_ARGUMENT, "Required inputs ([", input_names_[i], "]) are missing from input feed.");
+
+  std::vector<Value> results;
+  int64_t graph_id = -1;
+  if (enable_cuda_graph_ && graph_capturable_) {
+    const std::string id = ro.config.Get("gpu_graph_id", "0");
+    graph_id = std::stoll(id);
+  }
+
+  if (graph_id >= 0) {
+    auto& cg_ptr = cuda_graphs_[graph_id];
+    if (!cg_ptr) cg_ptr = std::make_unique<CapturedGraph>();
+    CapturedGraph& cg = *cg_ptr;
+    if (!cg.captured) {
+      // one eager run first (lazy initialisation, workspace allocation), then capture
+      results = ex->Run(ro, inputs, nullptr, output_names);
+      cudaStreamSynchronize(at::cuda::getCurrentCUDAStream(device_.index()).stream());
+      CheckDeviceStatus();
+      cg.static_in.clear();
+      cg.in_shapes.clear();
+      for (auto& v : inputs) {
+        cg.static_in.push_back(v.t);
+        cg.in_shapes.push_back(v.t.defined() ? v.t.sizes().vec() : std::vector<int64_t>{});
+      }
+      cg.slots = ex->NewSlots();
+      for (size_t i = 0; i < inputs.size(); ++i) {
+        const int s = ex->SlotOf(input_names_[i]);
+        if (inputs[i].defined()) cg.slots[s] = inputs[i];
+      }
+      c10::cuda::CUDAStream side = c10::cuda::getStreamFromPool(false, device_.index());
+      {
+        c10::cuda::CUDAStreamGuard sg(side);
+        cg.graph.capture_begin();
+        try {
+          ex->ExecuteSteps(ro, cg.slots);
+        } catch (...) {
+          cg.graph.capture_end();
+          cuda_graphs_.erase(graph_id);
+          throw;
+        }
+        cg.graph.capture_end();
+      }
+      cg.captured = true;
+      cg.graph.replay();  // the capture itself executed nothing
+    } else {
+      for (size_t i = 0; i < inputs.size(); ++i) {
+        if (!inputs[i].t.defined()) continue;
+        ORTB_ENFORCE_ARG(inputs[i].t.sizes().vec() == cg.in_shapes[i], "input '", input_names_[i],
+                         "' changed shape after CUDA graph capture; use a different gpu_graph_id per shape");
+        if (inputs[i].t.data_ptr() != cg.static_in[i].data_ptr()) cg.static_in[i].copy_(inputs[i].t, true);
+      }
+      cg.graph.replay();
+    }
+    results.clear();
+    for (auto& n : output_names) results.push_back(cg.slots[ex->SlotOf(n)]);
+    if (bound_outputs) {
+      for (size_t i = 0; i < results.size(); ++i) {
+        const at::Tensor& b = (*bound_outputs)[i].t;
+        if (b.defined() && results[i].t.defined() && b.data_ptr() != results[i].t.data_ptr()) {
+          const_cast<at::Tensor&>(b).copy_(results[i].t, true);
+          results[i].t = b;
+        }
+      }
+    }
+  } else if (bound_outputs) {
+    // run with caller-provided output buffers placed in their slots
+    std::vector<Value> slots = ex->NewSlots();
+    for (size_t i = 0; i < inputs.size(); ++i)
+      if (inputs[i].defined()) slots[ex->SlotOf(input_names_[i])] = inputs[i];
+    for (size_t i = 0; i < output_names.size(); ++i)
+      if ((*bound_outputs)[i].t.defined()) slots[ex->SlotOf(output_names[i])] = (*bound_outputs)[i];
+    ex->ExecuteSteps(ro, slots);
+    for (auto& n : output_names) results.push_back(slots[ex->SlotOf(n)]);
+  } else {
+    results = ex->Run(ro, inputs, nullptr, output_names);
+  }
+  if (profiler_.enabled()) {
+    if (device_.is_cuda()) cudaStreamSynchronize(at::cuda::getCurrentCUDAStream(device_.index()).stream());
+    profiler_.Record("Session", "model_run", t_run0, profiler_.NowUs() - t_run0);
+  }
+  return results;
+}
+
+std::vector<Value> InferenceSession::Run(const RunOptions& ro, const std::vector<std::string>& feed_names,
+                                         const std::vector<Value>& feeds, const std::vector<std::string>& output_names) {
+  return RunImpl(ro, feed_names, feeds, output_names, nullptr);
+}
+
+void InferenceSession::RunWithBinding(const RunOptions& ro, IOBinding& b) {
+  std::vector<std::string> names = b.out_names_;
+  std::vector<Value> res = RunImpl(ro, b.in_names_, b.in_values_, names, &b.out_values_);
+  b.results_.clear();
+  for (size_t i = 0; i < res.size(); ++i) {
+    Value v = res[i];
+    if (!b.out_values_[i].t.defined() && v.t.defined() && v.t.device() != b.out_devices_[i])
+      v.t = v.t.to(b.out_devices_[i]);
+    b.results_.push_back(v);
+  }
+}
+
+std::string InferenceSession::EndProfiling() { return profiler_.End(); }
+
+// ------------------------------------------------------------------ IOBinding
+void IOBinding::BindInput(const std::string& name, const at::Tensor& t) {
+  auto& names = session_->input_names_;
+  auto it = std::find(names.begin(), names.end(), name);
+  if (it == names.end()) ORTB_THROW(INVALID_ARGUMENT, "Failed to find input name in the model input def list: ", name);
+  // the copy to the device the consuming node is planned on happens here, once
+  const c10::Device want = session_->input_device_[static_cast<size_t>(it - names.begin())];
+  Value v;
+  v.t = t.device() == want ? t : t.to(want);
+  for (size_t i = 0; i < in_names_.size(); ++i)
+    if (in_names_[i] == name) {
+      in_values_[i] = v;
+      return;
+    }
+  in_names_.push_back(name);
+  in_values_.push_back(v);
+}
+
+void IOBinding::BindOutput(const std::string& name, const at::Tensor& t) {
+  auto& names = session_->output_names_;
+  if (std::find(names.begin(), names.end(), name) == names.end())
+    ORTB_THROW(INVALID_ARGUMENT, "Failed to find output name in the model output def list: ", name);
+  Value v;
+  v.t = t;
+  for (size_t i = 0; i < out_names_.size(); ++i)
+    if (out_names_[i] == name) {
+      out_values_[i] = v;
+      out_devices_[i] = t.device();
+      return;
+    }
+  out_names_.push_back(name);
+  out_values_.push_back(v);
+  out_devices_.push_back(t.device());
+}
+
+void IOBinding::BindOutputToDevice(const std::string& name, c10::Device device) {
+  auto& names = session_->output_names_;
+  if (std::find(names.begin(), names.end(), name) == names.end())
+    ORTB_THROW(INVALID_ARGUMENT, "Failed to find output name in the model output def list: ", name);
+  for (size_t i = 0; i < out_names_.size(); ++i)
+    if (out_names_[i] == name) {
+      out_values_[i] = Value();
+      out_devices_[i] = device;
+      return;
+    }
+  out_names_.push_back(name);
+  out_values_.emplace_back();
+  out_devices_.push_back(device);
+}
+
+void IOBinding::SynchronizeInputs() {
+  if (session_->device_.is_cuda())
+    cudaStreamSynchronize(at::cuda::getCurrentCUDAStream(session_->device_.index()).stream());
+}
+
+void IOBinding::SynchronizeOutputs() {
+  if (session_->device_.is_cuda()) {
+    cudaStreamSynchronize(at::cuda::getCurrentCUDAStream(session_->device_.index()).stream());
+    if (session_->config().Get("ortb200.check_status_every_run", "0") == "1") session_->CheckDeviceStatus();
+  }
+}
+
+}  // namespace ortb

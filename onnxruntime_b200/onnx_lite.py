@@ -1,0 +1,366 @@
+"""A small stand-alone ONNX protobuf writer/reader in pure Python.
+
+The ``onnx`` package is not required anywhere in this project: model builders,
+exporters and tests author graphs with the helpers below (``make_node``,
+``make_tensor``, ``make_graph``, ``make_model`` mirror ``onnx.helper``) and get
+``ModelProto`` bytes back.  The encoder is independent from the C++ parser in
+``csrc/core/onnx_pb.cc``, so round-trip tests check one against the other.
+
+Field numbers follow onnx.proto (ModelProto, GraphProto, NodeProto,
+AttributeProto, TensorProto, ValueInfoProto, TypeProto).
+"""
+from __future__ import annotations
+
+import struct
+from dataclasses import dataclass, field
+from typing import Any, Dict, Iterable, List, Optional, Sequence, Tuple, Union
+
+import numpy as np
+
+
+class TensorProto:
+    UNDEFINED, FLOAT, UINT8, INT8, UINT16, INT16, INT32, INT64, STRING, BOOL = range(10)
+    FLOAT16, DOUBLE, UINT32, UINT64, COMPLEX64, COMPLEX128, BFLOAT16 = range(10, 17)
+    FLOAT8E4M3FN, FLOAT8E4M3FNUZ, FLOAT8E5M2, FLOAT8E5M2FNUZ, UINT4, INT4, FLOAT4E2M1 = range(17, 24)
+
+
+_NP_TO_ONNX = {
+    np.dtype("float32"): TensorProto.FLOAT, np.dtype("uint8"): TensorProto.UINT8, np.dtype("int8"): TensorProto.INT8,
+    np.dtype("uint16"): TensorProto.UINT16, np.dtype("int16"): TensorProto.INT16, np.dtype("int32"): TensorProto.INT32,
+    np.dtype("int64"): TensorProto.INT64, np.dtype("bool"): TensorProto.BOOL, np.dtype("float16"): TensorProto.FLOAT16,
+    np.dtype("float64"): TensorProto.DOUBLE, np.dtype("uint32"): TensorProto.UINT32,
+    np.dtype("uint64"): TensorProto.UINT64,
+}
+_ONNX_TO_NP = {v: k for k, v in _NP_TO_ONNX.items()}
+
+ATTR_FLOAT, ATTR_INT, ATTR_STRING, ATTR_TENSOR, ATTR_GRAPH, ATTR_FLOATS, ATTR_INTS, ATTR_STRINGS = 1, 2, 3, 4, 5, 6, 7, 8
+
+
+# ------------------------------------------------------------------ wire writer
+def _varint(v: int) -> bytes:
+    if v < 0:
+        v += 1 << 64
+    out = bytearray()
+    while v >= 0x80:
+        out.append((v & 0x7F) | 0x80)
+        v >>= 7
+    out.append(v)
+    return bytes(out)
+
+
+def _key(field_no: int, wire: int) -> bytes:
+    return _varint((field_no << 3) | wire)
+
+
+def _f_varint(field_no: int, v: int) -> bytes:
+    return _key(field_no, 0) + _varint(int(v))
+
+
+def _f_bytes(field_no: int, b: Union[bytes, bytearray, memoryview]) -> bytes:
+    return _key(field_no, 2) + _varint(len(b)) + bytes(b)
+
+
+def _f_str(field_no: int, s: Union[str, bytes]) -> bytes:
+    return _f_bytes(field_no, s.encode("utf-8") if isinstance(s, str) else s)
+
+
+def _f_float(field_no: int, v: float) -> bytes:
+    return _key(field_no, 5) + struct.pack("<f", v)
+
+
+def _packed_varints(field_no: int, vals: Iterable[int]) -> bytes:
+    body = b"".join(_varint(int(v)) for v in vals)
+    return _f_bytes(field_no, body) if body else b""
+
+
+# ------------------------------------------------------------------ messages
+@dataclass
+class Tensor:
+    name: str
+    data_type: int
+    dims: Tuple[int, ...]
+    raw: bytes = b""
+    external: Optional[Dict[str, str]] = None  # location / offset / length
+
+    def serialize(self) -> bytes:
+        out = _packed_varints(1, self.dims)
+        out += _f_varint(2, self.data_type)
+        if self.name:
+            out += _f_str(8, self.name)
+        if self.external is not None:
+            for k, v in self.external.items():
+                out += _f_bytes(13, _f_str(1, k) + _f_str(2, str(v)))
+            out += _f_varint(14, 1)
+        else:
+            out += _f_bytes(9, self.raw)
+        return out
+
+
+@dataclass
+class ValueInfo:
+    name: str
+    elem_type: int = 0
+    shape: Optional[Sequence[Union[int, str, None]]] = None
+
+    def serialize(self) -> bytes:
+        out = _f_str(1, self.name)
+        if self.elem_type:
+            tt = _f_varint(1, self.elem_type)
+            if self.shape is not None:
+                dims = b""
+                for d in self.shape:
+                    if isinstance(d, (int, np.integer)):
+                        dims += _f_bytes(1, _f_varint(1, int(d)))
+                    elif isinstance(d, str):
+                        dims += _f_bytes(1, _f_str(2, d))
+                    else:
+                        dims += _f_bytes(1, b"")
+                tt += _f_bytes(2, dims)
+            out += _f_bytes(2, _f_bytes(1, tt))
+        return out
+
+
+@dataclass
+class Attribute:
+    name: str
+    type: int
+    value: Any
+
+    def serialize(self) -> bytes:
+        out = _f_str(1, self.name)
+        t, v = self.type, self.value
+        if t == ATTR_FLOAT:
+            out += _f_float(2, float(v))
+        elif t == ATTR_INT:
+            out += _f_varint(3, int(v))
+        elif t == ATTR_STRING:
+            out += _f_str(4, v)
+        elif t == ATTR_TENSOR:
+            out += _f_bytes(5, v.serialize())
+        elif t == ATTR_GRAPH:
+            out += _f_bytes(6, v.serialize())
+        elif t == ATTR_FLOATS:
+            if len(v):
+                out += _f_bytes(7, struct.pack(f"<{len(v)}f", *[float(x) for x in v]))
+        elif t == ATTR_INTS:
+            out += _packed_varints(8, v)
+        elif t == ATTR_STRINGS:
+            for s in v:
+                out += _f_str(9, s)
+        else:
+            raise ValueError(f"unsupported attribute type {t}")
+        out += _f_varint(20, t)
+        return out
+
+
+@dataclass
+class Node:
+    op_type: str
+    inputs: List[str]
+    outputs: List[str]
+    name: str = ""
+    domain: str = ""
+    attributes: List[Attribute] = field(default_factory=list)
+
+    def serialize(self) -> bytes:
+        out = b"".join(_f_str(1, i) for i in self.inputs)
+        out += b"".join(_f_str(2, o) for o in self.outputs)
+        if self.name:
+            out += _f_str(3, self.name)
+        out += _f_str(4, self.op_type)
+        out += b"".join(_f_bytes(5, a.serialize()) for a in self.attributes)
+        if self.domain:
+            out += _f_str(7, self.domain)
+        return out
+
+
+@dataclass
+class Graph:
+    nodes: List[Node]
+    name: str
+    inputs: List[ValueInfo]
+    outputs: List[ValueInfo]
+    initializers: List[Tensor] = field(default_factory=list)
+    value_info: List[ValueInfo] = field(default_factory=list)
+
+    def serialize(self) -> bytes:
+        out = b"".join(_f_bytes(1, n.serialize()) for n in self.nodes)
+        out += _f_str(2, self.name)
+        out += b"".join(_f_bytes(5, t.serialize()) for t in self.initializers)
+        out += b"".join(_f_bytes(11, v.serialize()) for v in self.inputs)
+        out += b"".join(_f_bytes(12, v.serialize()) for v in self.outputs)
+        out += b"".join(_f_bytes(13, v.serialize()) for v in self.value_info)
+        return out
+
+
+@dataclass
+class Model:
+    graph: Graph
+    opset_imports: Dict[str, int]
+    ir_version: int = 8
+    producer_name: str = "onnxruntime_b200"
+    metadata: Dict[str, str] = field(default_factory=dict)
+    doc_string: str = ""
+
+    def serialize(self) -> bytes:
+        out = _f_varint(1, self.ir_version)
+        out += _f_str(2, self.producer_name)
+        if self.doc_string:
+            out += _f_str(6, self.doc_string)
+        out += _f_bytes(7, self.graph.serialize())
+        for domain, version in self.opset_imports.items():
+            body = (_f_str(1, domain) if domain else b"") + _f_varint(2, version)
+            out += _f_bytes(8, body)
+        for k, v in self.metadata.items():
+            out += _f_bytes(14, _f_str(1, k) + _f_str(2, v))
+        return out
+
+    SerializeToString = serialize
+
+
+# ------------------------------------------------------------------ helpers
+def np_dtype_to_onnx(dt) -> int:
+    return _NP_TO_ONNX[np.dtype(dt)]
+
+
+def onnx_to_np_dtype(t: int):
+    return _ONNX_TO_NP[t]
+
+
+def make_tensor(name: str, array, data_type: Optional[int] = None) -> Tensor:
+    """Initializer from a numpy array or a torch tensor (bf16 / fp8 torch tensors keep their bits)."""
+    try:
+        import torch
+    except ImportError:  # pragma: no cover
+        torch = None
+    if torch is not None and isinstance(array, torch.Tensor):
+        t = array.detach().cpu().contiguous()
+        tmap = {torch.float32: TensorProto.FLOAT, torch.float16: TensorProto.FLOAT16, torch.bfloat16: TensorProto.BFLOAT16,
+                torch.int64: TensorProto.INT64, torch.int32: TensorProto.INT32, torch.int8: TensorProto.INT8,
+                torch.uint8: TensorProto.UINT8, torch.bool: TensorProto.BOOL, torch.float64: TensorProto.DOUBLE,
+                torch.int16: TensorProto.INT16, torch.float8_e4m3fn: TensorProto.FLOAT8E4M3FN,
+                torch.float8_e5m2: TensorProto.FLOAT8E5M2}
+        dt = data_type if data_type is not None else tmap[t.dtype]
+        raw = t.view(torch.uint8).numpy().tobytes() if t.numel() else b""
+        return Tensor(name, dt, tuple(t.shape), raw)
+    arr = np.ascontiguousarray(array)
+    dt = data_type if data_type is not None else np_dtype_to_onnx(arr.dtype)
+    return Tensor(name, dt, tuple(arr.shape), arr.tobytes())
+
+
+def make_external_tensor(name: str, data_type: int, dims: Sequence[int], location: str = "*session*",
+                         offset: Optional[int] = None, length: Optional[int] = None) -> Tensor:
+    """Initializer whose bytes live outside the model.
+
+    ``location="*session*"`` marks a tensor the caller hands to the session with
+    ``SessionOptions.add_external_initializers``; any other value is a file name
+    relative to the model's directory."""
+    ext = {"location": location}
+    if offset is not None:
+        ext["offset"] = str(offset)
+    if length is not None:
+        ext["length"] = str(length)
+    return Tensor(name, data_type, tuple(dims), b"", ext)
+
+
+def make_tensor_value_info(name: str, elem_type: int, shape: Optional[Sequence[Union[int, str, None]]]) -> ValueInfo:
+    return ValueInfo(name, elem_type, shape)
+
+
+def make_attribute(name: str, value: Any) -> Attribute:
+    if isinstance(value, bool):
+        return Attribute(name, ATTR_INT, int(value))
+    if isinstance(value, (int, np.integer)):
+        return Attribute(name, ATTR_INT, int(value))
+    if isinstance(value, (float, np.floating)):
+        return Attribute(name, ATTR_FLOAT, float(value))
+    if isinstance(value, (str, bytes)):
+        return Attribute(name, ATTR_STRING, value)
+    if isinstance(value, Tensor):
+        return Attribute(name, ATTR_TENSOR, value)
+    if isinstance(value, Graph):
+        return Attribute(name, ATTR_GRAPH, value)
+    if isinstance(value, np.ndarray):
+        return Attribute(name, ATTR_TENSOR, make_tensor("", value))
+    if isinstance(value, (list, tuple)):
+        if len(value) == 0:
+            return Attribute(name, ATTR_INTS, [])
+        if all(isinstance(v, (int, np.integer)) and not isinstance(v, bool) for v in value):
+            return Attribute(name, ATTR_INTS, list(value))
+        if all(isinstance(v, (int, float, np.floating, np.integer)) for v in value):
+            return Attribute(name, ATTR_FLOATS, list(value))
+        if all(isinstance(v, (str, bytes)) for v in value):
+            return Attribute(name, ATTR_STRINGS, list(value))
+    raise TypeError(f"cannot infer the attribute type of {name}={value!r}")
+
+
+def make_node(op_type: str, inputs: Sequence[str], outputs: Sequence[str], name: str = "", domain: str = "",
+              **attrs: Any) -> Node:
+    return Node(op_type, list(inputs), list(outputs), name, domain,
+                [make_attribute(k, v) for k, v in attrs.items() if v is not None])
+
+
+def make_graph(nodes: Sequence[Node], name: str, inputs: Sequence[ValueInfo], outputs: Sequence[ValueInfo],
+               initializer: Sequence[Tensor] = (), value_info: Sequence[ValueInfo] = ()) -> Graph:
+    return Graph(list(nodes), name, list(inputs), list(outputs), list(initializer), list(value_info))
+
+
+def make_model(graph: Graph, opset: int = 17, ms_opset: Optional[int] = 1, ir_version: int = 8,
+               producer_name: str = "onnxruntime_b200", metadata: Optional[Dict[str, str]] = None,
+               extra_opsets: Optional[Dict[str, int]] = None) -> Model:
+    opsets = {"": opset}
+    if ms_opset is not None:
+        opsets["com.microsoft"] = ms_opset
+    if extra_opsets:
+        opsets.update(extra_opsets)
+    return Model(graph, opsets, ir_version, producer_name, dict(metadata or {}))
+
+
+# ------------------------------------------------------------------ wire reader (for tests / tools)
+def parse_message(buf: bytes) -> List[Tuple[int, int, Any]]:
+    """Decode one protobuf message into (field, wire_type, value) triples; nested messages stay bytes."""
+    out = []
+    i, n = 0, len(buf)
+    while i < n:
+        key = 0
+        shift = 0
+        while True:
+            b = buf[i]
+            i += 1
+            key |= (b & 0x7F) << shift
+            shift += 7
+            if not b & 0x80:
+                break
+        field_no, wire = key >> 3, key & 7
+        if wire == 0:
+            v = 0
+            shift = 0
+            while True:
+                b = buf[i]
+                i += 1
+                v |= (b & 0x7F) << shift
+                shift += 7
+                if not b & 0x80:
+                    break
+            out.append((field_no, wire, v))
+        elif wire == 1:
+            out.append((field_no, wire, buf[i:i + 8]))
+            i += 8
+        elif wire == 2:
+            ln = 0
+            shift = 0
+            while True:
+                b = buf[i]
+                i += 1
+                ln |= (b & 0x7F) << shift
+                shift += 7
+                if not b & 0x80:
+                    break
+            out.append((field_no, wire, buf[i:i + ln]))
+            i += ln
+        elif wire == 5:
+            out.append((field_no, wire, buf[i:i + 4]))
+            i += 4
+        else:
+            raise ValueError(f"unsupported wire type {wire}")
+    return out
