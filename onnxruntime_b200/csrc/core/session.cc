@@ -264,6 +264,14 @@ at::Tensor& InferenceSession::GemmWorkspace(int64_t nbytes) {
   return gemm_ws_;
 }
 
+at::Tensor& InferenceSession::AttnWorkspace(int64_t nbytes) {
+  if (!attn_ws_.defined() || attn_ws_.numel() < nbytes) {
+    const int64_t sz = std::max<int64_t>(nbytes, 8 << 20);
+    attn_ws_ = at::zeros({sz}, at::TensorOptions().dtype(at::kByte).device(device_));
+  }
+  return attn_ws_;
+}
+
 at::Tensor& InferenceSession::StatusWord() {
   if (!status_word_.defined()) status_word_ = at::zeros({4}, at::TensorOptions().dtype(at::kInt).device(device_));
   return status_word_;

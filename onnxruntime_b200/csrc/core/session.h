@@ -137,6 +137,7 @@ class InferenceSession {
   void AddLaunches(int64_t n) { launch_count_ += n; }
   // device scratch shared by the GPU kernels (split-K partials, counters), zero-initialised
   at::Tensor& GemmWorkspace(int64_t nbytes);
+  at::Tensor& AttnWorkspace(int64_t nbytes);
   at::Tensor& StatusWord();
   // Check the device status word (bounded waits); throws EP_FAIL when a kernel reported a timeout.
   void CheckDeviceStatus();
@@ -168,7 +169,7 @@ class InferenceSession {
   Profiler profiler_;
   int64_t profiling_start_ns_ = 0;
   int64_t launch_count_ = 0;
-  at::Tensor gemm_ws_, status_word_;
+  at::Tensor gemm_ws_, attn_ws_, status_word_;
   std::mutex run_mu_;
 };
 

@@ -1,0 +1,393 @@
+// GroupQueryAttention for sm_100a: the fused "unpack packed QKV + rotary + KV
+// append" kernel and the split-KV decode attention kernel.
+//
+// Reference counterparts: UnpackRoPEAppend
+// (onnxruntime/contrib_ops/cuda/bert/group_query_attention_qkv.cuh:43), the XQA /
+// flash-decoding decode paths (bert/xqa/mha_impl.cuh, flash_api.cc:441
+// mha_fwd_kvcache) and PagedDecodeSplitKV + PagedDecodeReduce
+// (bert/paged_attention_impl.cu:719,963).
+//
+// Decode attention is bound by reading the KV cache once.  One CTA owns one
+// (batch, kv head, split) and serves all query heads of that kv head, so K and V
+// are streamed exactly once; 8 lanes share a key (32-byte vector loads, 3 shuffle
+// steps per dot product), the online-softmax state lives in registers, and the
+// CTA that arrives last on a per-(batch, kv head) counter merges the splits - no
+// second launch, grid size independent of the current sequence length so the
+// launch can be captured in a CUDA graph.
+#include <cuda_runtime.h>
+#include <math.h>
+#include "ortb200_kernels.h"
+#include "ptx_sm100.cuh"
+
+namespace ortb200 {
+
+// ------------------------------------------------------------------ prep
+template <typename T>
+__global__ void __launch_bounds__(256) gqa_prep_kernel(const ortb200_gqa_prep_args a) {
+  const int b = blockIdx.x / a.S, s = blockIdx.x % a.S;
+  const int H = a.H, halfH = H / 2;
+  const int rot = a.rot_dim > 0 ? a.rot_dim : H;
+  const int half = rot / 2;
+  const int heads = a.N + 2 * a.Nk;
+  pdl_wait_prior_grids();
+  const int past = a.first_prompt ? 0 : a.seqlens_k[b] + 1 - a.S;
+  const long long pos = a.position_ids ? a.position_ids[static_cast<long long>(b) * a.S + s] : past + s;
+  const int cache_pos = past + s;
+  const long long tok = static_cast<long long>(b) * a.S + s;
+  const T* cosr = a.do_rotary ? static_cast<const T*>(a.cos_cache) + pos * half : nullptr;
+  const T* sinr = a.do_rotary ? static_cast<const T*>(a.sin_cache) + pos * half : nullptr;
+  for (int idx = threadIdx.x; idx < heads * halfH; idx += blockDim.x) {
+    const int head = idx / halfH, i = idx % halfH;
+    const T* src;
+    if (a.k != nullptr) {
+      if (head < a.N) src = static_cast<const T*>(a.qkv) + tok * (a.N * H) + head * H;
+      else if (head < a.N + a.Nk) src = static_cast<const T*>(a.k) + tok * (a.Nk * H) + (head - a.N) * H;
+      else src = static_cast<const T*>(a.v) + tok * (a.Nk * H) + (head - a.N - a.Nk) * H;
+    } else {
+      src = static_cast<const T*>(a.qkv) + tok * (static_cast<long long>(heads) * H) + head * H;
+    }
+    T* dst;
+    if (head < a.N) {
+      dst = static_cast<T*>(a.q_out) + tok * (a.N * H) + head * H;
+    } else {
+      if (cache_pos < 0 || cache_pos >= a.Smax) continue;
+      const bool is_k = head < a.N + a.Nk;
+      const int kh = is_k ? head - a.N : head - a.N - a.Nk;
+      T* base = static_cast<T*>(is_k ? a.k_cache : a.v_cache);
+      dst = base + ((static_cast<long long>(b) * a.Nk + kh) * a.Smax + cache_pos) * H;
+    }
+    const bool rotate = a.do_rotary && head < a.N + a.Nk && i < half;
+    int e0, e1;
+    if (i < half) {
+      e0 = a.interleaved ? 2 * i : i;
+      e1 = a.interleaved ? 2 * i + 1 : i + half;
+    } else {
+      e0 = rot + 2 * (i - half);
+      e1 = e0 + 1;
+    }
+    if (!a.do_rotary || head >= a.N + a.Nk) {
+      e0 = 2 * i;
+      e1 = 2 * i + 1;
+    }
+    const float x0 = to_float<T>(src[e0]), x1 = to_float<T>(src[e1]);
+    if (rotate) {
+      const float c = to_float<T>(cosr[i]), sn = to_float<T>(sinr[i]);
+      dst[e0] = from_float<T>(x0 * c - x1 * sn);
+      dst[e1] = from_float<T>(x1 * c + x0 * sn);
+    } else {
+      dst[e0] = src[e0];
+      dst[e1] = src[e1];
+    }
+  }
+  pdl_launch_dependents();
+}
+
+// ---------------------------------------------------------------- decode
+struct DecodeParams {
+  const void* q;
+  const void* k_cache;
+  const void* v_cache;
+  const int* seqlens_k;
+  const void* head_sink;
+  void* out;
+  float* ws;
+  unsigned int* counters;
+  int B, N, Nk, Smax, splits, window, gparts;
+  float scale, softcap;
+};
+
+__device__ __forceinline__ float safe_exp_diff(float a, float b) {
+  // exp(a - b) with a = -inf treated as 0 even when b = -inf
+  return a == -INFINITY ? 0.f : __expf(a - b);
+}
+
+template <typename T, int H, int G>
+__global__ void __launch_bounds__(128) gqa_decode_kernel(const DecodeParams p) {
+  constexpr int DPL = H / 8;          // dims per lane (8 lanes share a key)
+  constexpr int VEC = DPL * sizeof(T) / 16;  // 16-byte loads per lane per row
+  static_assert(VEC >= 1, "head size too small");
+  const int split = blockIdx.x;
+  const int kvh = blockIdx.y / p.gparts, gp = blockIdx.y % p.gparts;
+  const int b = blockIdx.z;
+  const int group = p.N / p.Nk;
+  const int head0 = kvh * group + gp * G;       // first query head served here
+  const int n_heads = min(G, group - gp * G);   // query heads actually present
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int slot = lane >> 3, sub = lane & 7, d0 = sub * DPL;
+
+  __shared__ float sm_m[4][G], sm_l[4][G];
+  __shared__ float sm_acc[4][G][H];
+  __shared__ unsigned int sm_last;
+
+  pdl_wait_prior_grids();
+  const int total = p.seqlens_k[b] + 1;
+  const int start0 = p.window > 0 ? max(0, total - p.window) : 0;
+  const int len = max(total - start0, 0);
+  const int chunk = (len + p.splits - 1) / p.splits;
+  const int k_begin = start0 + split * chunk;
+  const int k_end = min(total, k_begin + chunk);
+
+  float qf[G][DPL];
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    const T* qp = static_cast<const T*>(p.q) + (static_cast<long long>(b) * p.N + head0 + (g < n_heads ? g : 0)) * H + d0;
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) qf[g][i] = to_float<T>(qp[i]) * p.scale;
+  }
+  float m[G], l[G], acc[G][DPL];
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    m[g] = -INFINITY;
+    l[g] = 0.f;
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) acc[g][i] = 0.f;
+  }
+
+  const T* kbase = static_cast<const T*>(p.k_cache) + (static_cast<long long>(b) * p.Nk + kvh) * p.Smax * H + d0;
+  const T* vbase = static_cast<const T*>(p.v_cache) + (static_cast<long long>(b) * p.Nk + kvh) * p.Smax * H + d0;
+
+  // Two keys per 8-lane group in flight.  The trip count is uniform across the warp (shuffles name all
+  // 32 lanes); keys past the end are masked out of the state update.
+  for (int base = k_begin + warp * 4; base < k_end; base += 32) {
+    const int keys[2] = {base + slot, base + slot + 16};
+    const bool valid[2] = {keys[0] < k_end, keys[1] < k_end};
+    uint4 kr[2][VEC], vr[2][VEC];
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+#pragma unroll
+      for (int v = 0; v < VEC; ++v) {
+        if (valid[u]) {
+          kr[u][v] = *reinterpret_cast<const uint4*>(kbase + static_cast<long long>(keys[u]) * H + v * (16 / sizeof(T)));
+          vr[u][v] = *reinterpret_cast<const uint4*>(vbase + static_cast<long long>(keys[u]) * H + v * (16 / sizeof(T)));
+        } else {
+          kr[u][v] = make_uint4(0, 0, 0, 0);
+          vr[u][v] = make_uint4(0, 0, 0, 0);
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      const T* kp = reinterpret_cast<const T*>(&kr[u][0]);
+      const T* vp = reinterpret_cast<const T*>(&vr[u][0]);
+      float kf[DPL], vf[DPL];
+#pragma unroll
+      for (int i = 0; i < DPL; ++i) {
+        kf[i] = to_float<T>(kp[i]);
+        vf[i] = to_float<T>(vp[i]);
+      }
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+        float s = 0.f;
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) s += qf[g][i] * kf[i];
+        s += __shfl_xor_sync(0xffffffffu, s, 1);
+        s += __shfl_xor_sync(0xffffffffu, s, 2);
+        s += __shfl_xor_sync(0xffffffffu, s, 4);
+        if (valid[u]) {
+          if (p.softcap > 0.f) s = p.softcap * tanhf(s / p.softcap);
+          const float m_new = fmaxf(m[g], s);
+          const float corr = safe_exp_diff(m[g], m_new);
+          const float pr = __expf(s - m_new);
+          l[g] = l[g] * corr + pr;
+#pragma unroll
+          for (int i = 0; i < DPL; ++i) acc[g][i] = acc[g][i] * corr + pr * vf[i];
+          m[g] = m_new;
+        }
+      }
+    }
+  }
+
+  // merge the 4 key slots of a warp (lanes differing in bits 3 and 4)
+#pragma unroll
+  for (int off = 8; off <= 16; off <<= 1) {
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      const float m_o = __shfl_xor_sync(0xffffffffu, m[g], off);
+      const float l_o = __shfl_xor_sync(0xffffffffu, l[g], off);
+      const float m_new = fmaxf(m[g], m_o);
+      const float c_s = safe_exp_diff(m[g], m_new), c_o = safe_exp_diff(m_o, m_new);
+      l[g] = l[g] * c_s + l_o * c_o;
+#pragma unroll
+      for (int i = 0; i < DPL; ++i) {
+        const float a_o = __shfl_xor_sync(0xffffffffu, acc[g][i], off);
+        acc[g][i] = acc[g][i] * c_s + a_o * c_o;
+      }
+      m[g] = m_new;
+    }
+  }
+  if (slot == 0) {
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      if (sub == 0) {
+        sm_m[warp][g] = m[g];
+        sm_l[warp][g] = l[g];
+      }
+#pragma unroll
+      for (int i = 0; i < DPL; ++i) sm_acc[warp][g][d0 + i] = acc[g][i];
+    }
+  }
+  __syncthreads();
+
+  // merge the 4 warps: thread t owns dim t (H <= 128 == blockDim)
+  const int tile = (b * p.Nk + kvh) * p.gparts + gp;
+  const bool owner = tid < H;
+  float fm[G], fl[G], fa[G];
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    float mm = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) mm = fmaxf(mm, sm_m[w][g]);
+    float ll = 0.f, aa = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float c = safe_exp_diff(sm_m[w][g], mm);
+      ll += sm_l[w][g] * c;
+      if (owner) aa += sm_acc[w][g][tid] * c;
+    }
+    fm[g] = mm;
+    fl[g] = ll;
+    fa[g] = aa;
+  }
+
+  bool finalize = true;
+  if (p.splits > 1) {
+    // publish partial state: ws[tile][split][g][H + 2]
+    float* my = p.ws + ((static_cast<size_t>(tile) * p.splits + split) * G) * (H + 2);
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      if (owner) my[g * (H + 2) + tid] = fa[g];
+      if (tid == 0) {
+        my[g * (H + 2) + H] = fm[g];
+        my[g * (H + 2) + H + 1] = fl[g];
+      }
+    }
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+      const unsigned int old = atomicAdd(&p.counters[tile], 1u);
+      const unsigned int last = old == static_cast<unsigned int>(p.splits - 1) ? 1u : 0u;
+      if (last) p.counters[tile] = 0;
+      sm_last = last;
+    }
+    __syncthreads();
+    finalize = sm_last != 0;
+    if (finalize) {
+      __threadfence();
+      const float* base = p.ws + (static_cast<size_t>(tile) * p.splits * G) * (H + 2);
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+        float mm = -INFINITY;
+        for (int s = 0; s < p.splits; ++s) mm = fmaxf(mm, __ldcg(&base[(s * G + g) * (H + 2) + H]));
+        float ll = 0.f, aa = 0.f;
+        for (int s = 0; s < p.splits; ++s) {
+          const float* ps = base + (s * G + g) * (H + 2);
+          const float c = safe_exp_diff(__ldcg(&ps[H]), mm);
+          ll += __ldcg(&ps[H + 1]) * c;
+          if (owner) aa += __ldcg(&ps[tid]) * c;
+        }
+        fm[g] = mm;
+        fl[g] = ll;
+        fa[g] = aa;
+      }
+    }
+  }
+  pdl_launch_dependents();
+  if (finalize && owner) {
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      if (g >= n_heads) break;
+      float ll = fl[g];
+      if (p.head_sink) {
+        const float sink = to_float<T>(static_cast<const T*>(p.head_sink)[head0 + g]);
+        const float mm = fmaxf(fm[g], sink);
+        const float c = safe_exp_diff(fm[g], mm);
+        ll = ll * c + __expf(sink - mm);
+        fa[g] *= c;
+      }
+      const float o = ll > 0.f ? fa[g] / ll : 0.f;
+      static_cast<T*>(p.out)[(static_cast<long long>(b) * p.N + head0 + g) * H + tid] = from_float<T>(o);
+    }
+  }
+}
+
+template <typename T, int H>
+static int launch_decode(const ortb200_gqa_decode_args* a, cudaStream_t stream) {
+  const int group = a->N / a->Nk;
+  const int G = group >= 4 ? 4 : (group >= 2 ? 2 : 1);
+  const int gparts = (group + G - 1) / G;
+  int splits = a->splits;
+  if (splits <= 0) {
+    const int ctas = a->B * a->Nk * gparts;
+    splits = (2 * 148 + ctas - 1) / ctas;
+    const int max_by_len = (a->Smax + 63) / 64;
+    if (splits > max_by_len) splits = max_by_len;
+    if (splits > 32) splits = 32;
+    if (splits < 1) splits = 1;
+  }
+  const int tiles = a->B * a->Nk * gparts;
+  const int64_t need = 65536 + static_cast<int64_t>(tiles) * splits * G * (H + 2) * 4;
+  if (splits > 1 && (!a->workspace || a->workspace_bytes < need || tiles > 16384)) splits = 1;
+  DecodeParams p;
+  p.q = a->q; p.k_cache = a->k_cache; p.v_cache = a->v_cache; p.seqlens_k = a->seqlens_k; p.head_sink = a->head_sink;
+  p.out = a->out;
+  p.counters = reinterpret_cast<unsigned int*>(a->workspace);
+  p.ws = a->workspace ? reinterpret_cast<float*>(static_cast<char*>(a->workspace) + 65536) : nullptr;
+  p.B = a->B; p.N = a->N; p.Nk = a->Nk; p.Smax = a->Smax; p.splits = splits; p.window = a->window; p.gparts = gparts;
+  p.scale = a->scale != 0.f ? a->scale : 1.0f / sqrtf(static_cast<float>(H));
+  p.softcap = a->softcap;
+  dim3 grid(splits, a->Nk * gparts, a->B);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(128, 1, 1);
+  cfg.stream = stream;
+  cudaLaunchAttribute attrs[1];
+  if (a->use_pdl) {
+    attrs[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attrs;
+    cfg.numAttrs = 1;
+  }
+  cudaError_t e;
+  if (G == 4) e = cudaLaunchKernelEx(&cfg, gqa_decode_kernel<T, H, 4>, p);
+  else if (G == 2) e = cudaLaunchKernelEx(&cfg, gqa_decode_kernel<T, H, 2>, p);
+  else e = cudaLaunchKernelEx(&cfg, gqa_decode_kernel<T, H, 1>, p);
+  return e == cudaSuccess ? 0 : -11;
+}
+
+}  // namespace ortb200
+
+using namespace ortb200;
+
+extern "C" int64_t ortb200_gqa_decode_workspace_bytes(int B, int N, int H) {
+  // tiles * G <= B * N ; at most 32 splits
+  return 65536 + static_cast<int64_t>(B) * N * 32 * (H + 2) * 4;
+}
+
+extern "C" int ortb200_gqa_decode(const ortb200_gqa_decode_args* a, ortb200_stream_t stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (!a || !a->q || !a->k_cache || !a->v_cache || !a->seqlens_k || !a->out) return -1;
+  if (a->B <= 0 || a->N <= 0 || a->Nk <= 0 || a->N % a->Nk != 0 || a->Smax <= 0) return -1;
+  if (a->H != 64 && a->H != 128) return -2;
+  if ((reinterpret_cast<uintptr_t>(a->k_cache) | reinterpret_cast<uintptr_t>(a->v_cache)) & 15) return -3;
+  if (a->dtype == ORTB200_BF16) {
+    return a->H == 128 ? launch_decode<__nv_bfloat16, 128>(a, stream) : launch_decode<__nv_bfloat16, 64>(a, stream);
+  } else if (a->dtype == ORTB200_F16) {
+    return a->H == 128 ? launch_decode<__half, 128>(a, stream) : launch_decode<__half, 64>(a, stream);
+  }
+  return -4;
+}
+
+extern "C" int ortb200_gqa_prep(const ortb200_gqa_prep_args* a, ortb200_stream_t stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (!a || !a->qkv || !a->q_out || !a->k_cache || !a->v_cache || !a->seqlens_k) return -1;
+  if (a->B <= 0 || a->S <= 0 || a->H % 2 != 0) return -1;
+  if (a->do_rotary && (!a->cos_cache || !a->sin_cache)) return -2;
+  if ((a->k != nullptr) != (a->v != nullptr)) return -2;
+  const int rot = a->rot_dim > 0 ? a->rot_dim : a->H;
+  if (rot > a->H || rot % 2 != 0) return -2;
+  dim3 grid(static_cast<unsigned>(a->B) * a->S);
+  if (a->dtype == ORTB200_BF16) gqa_prep_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(*a);
+  else if (a->dtype == ORTB200_F16) gqa_prep_kernel<__half><<<grid, 256, 0, stream>>>(*a);
+  else return -4;
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}

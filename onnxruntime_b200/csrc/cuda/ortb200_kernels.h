@@ -63,6 +63,120 @@ int64_t ortb200_gemm_workspace_bytes(int M, int N, int K, int act);
 // Number of kernels one ortb200_gemm call launches (always 1).
 int ortb200_gemm_last_config(int* bn, int* splits, int* stages);
 
+// ---------------------------------------------------------------------------
+// (Skip)LayerNorm / (Skip)SimplifiedLayerNorm.  out = norm(x + skip + bias) * gamma (+ beta);
+// sum_out (optional) receives x + skip + bias, the residual stream.  All pointers 16-byte aligned,
+// hidden * sizeof(T) a multiple of 16, hidden <= 16 * 256 * (16 / sizeof(T)).
+typedef struct {
+  const void* x;
+  const void* skip;   // optional
+  const void* bias;   // optional [hidden]
+  const void* gamma;  // [hidden]
+  const void* beta;   // optional [hidden]
+  void* out;
+  void* sum_out;      // optional
+  int64_t rows;
+  int hidden;
+  float epsilon;
+  int simplified;     // 1 = RMS form (no mean subtraction, no beta)
+  int dtype;
+} ortb200_norm_args;
+int ortb200_norm(const ortb200_norm_args* args, ortb200_stream_t stream);
+
+// ---------------------------------------------------------------------------
+// GroupQueryAttention, step 1: split packed QKV, apply rotary embedding to Q and K, append K/V to the cache.
+// Caches are [B, Nk, Smax, H].  Position of token s of batch b: position_ids[b, s] when given, else
+// past_len(b) + s with past_len(b) = first_prompt ? 0 : seqlens_k[b] + 1 - S.
+typedef struct {
+  const void* qkv;             // packed [B, S, (N + 2 Nk) H], or Q [B, S, N H] when k / v are given
+  const void* k;               // optional [B, S, Nk H]
+  const void* v;               // optional [B, S, Nk H]
+  void* q_out;                 // [B, S, N, H]
+  void* k_cache;
+  void* v_cache;
+  const int* seqlens_k;        // [B], total length - 1
+  const void* cos_cache;       // [max_pos, rot_dim / 2] (same dtype); null when do_rotary == 0
+  const void* sin_cache;
+  const int64_t* position_ids; // optional [B, S]
+  int B, S, N, Nk, H, Smax;
+  int rot_dim;                 // 0 = H
+  int interleaved;
+  int first_prompt;
+  int do_rotary;
+  int dtype;
+} ortb200_gqa_prep_args;
+int ortb200_gqa_prep(const ortb200_gqa_prep_args* args, ortb200_stream_t stream);
+
+// GroupQueryAttention, decode step (one query token per sequence): split-KV attention over the cache.
+// q [B, N, H]; attends to cache positions [max(0, total - window), total) with total = seqlens_k[b] + 1.
+// workspace: ortb200_gqa_decode_workspace_bytes(); its first 64 KiB (counters) must be zero before the first
+// launch and is left zero.  H must be 64 or 128.
+typedef struct {
+  const void* q;
+  const void* k_cache;
+  const void* v_cache;
+  const int* seqlens_k;
+  const void* head_sink;  // optional [N], same dtype
+  void* out;              // [B, N H]
+  void* workspace;
+  int64_t workspace_bytes;
+  int B, N, Nk, H, Smax;
+  int splits;             // 0 = heuristic
+  int window;             // <= 0: none
+  float scale;            // 0 = 1/sqrt(H)
+  float softcap;
+  int dtype;
+  int use_pdl;
+} ortb200_gqa_decode_args;
+int ortb200_gqa_decode(const ortb200_gqa_decode_args* args, ortb200_stream_t stream);
+int64_t ortb200_gqa_decode_workspace_bytes(int B, int N, int H);
+
+// Multi-token attention (prompt / chunked prefill, and encoder self-attention): flash-attention forward on
+// tcgen05 with S = Q K^T and O = P V accumulated in tensor memory.
+// q / out are [B, S, N, H] described by explicit strides; k / v are addressed as (batch, kv head, position, dim)
+// with explicit element strides, so both a [B, Nk, Smax, H] cache and a [B, S, Nk, H] activation work.
+// Query token s of batch b sits at absolute position past(b) + s, past(b) = first_prompt ? 0 : seqlens_k[b] + 1 - S,
+// and sees keys j < seqlens_k[b] + 1 with (causal ? j <= position : true) and (window > 0 ? j > position - window : true).
+// H must be 64 or 128; all strides multiples of 8 elements.
+typedef struct {
+  const void* q;
+  const void* k;
+  const void* v;
+  const int* seqlens_k;    // [B]; null = every sequence has kv_len keys
+  const void* head_sink;   // optional [N]
+  void* out;
+  int B, S, N, Nk, H;
+  int kv_len;              // extent of the position axis of k / v
+  int64_t q_strides[3];    // elements: batch, token, head
+  int64_t o_strides[3];
+  int64_t kv_strides[3];   // elements: batch, head, position
+  int first_prompt;
+  int causal;
+  int window;
+  float scale;             // 0 = 1/sqrt(H)
+  float softcap;
+  int dtype;
+  int* status;
+} ortb200_attn_prefill_args;
+int ortb200_attn_prefill(const ortb200_attn_prefill_args* args, ortb200_stream_t stream);
+
+// ---------------------------------------------------------------------------
+// Small utility kernels.
+// rows of `table` [vocab, hidden] selected by int64 ids -> out [n, hidden]
+int ortb200_gather_rows(const void* table, const int64_t* ids, void* out, int64_t n, int64_t vocab, int hidden,
+                        int elem_bytes, ortb200_stream_t stream);
+// argmax over the last dimension: x [rows, n] -> out int64 [rows] (first maximum wins)
+int ortb200_argmax(const void* x, int64_t* out, int64_t rows, int64_t n, int dtype, ortb200_stream_t stream);
+// y = act(x + bias[col]) elementwise; bias optional, cols = last dimension
+int ortb200_bias_act(const void* x, const void* bias, void* y, int64_t rows, int cols, int act, float alpha, int dtype,
+                     ortb200_stream_t stream);
+// y = silu(gate) * up for x = [rows, 2 * cols] split in halves (gate | up)
+int ortb200_swiglu(const void* x, void* y, int64_t rows, int cols, int dtype, ortb200_stream_t stream);
+// standalone rotary embedding on [B, S, N, H] (in -> out, may alias)
+int ortb200_rotary(const void* x, void* y, const int64_t* position_ids, int64_t position_offset, const void* cos_cache,
+                   const void* sin_cache, int B, int S, int N, int H, int rot_dim, int interleaved, int bnsh, int dtype,
+                   ortb200_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

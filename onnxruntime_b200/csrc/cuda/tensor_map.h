@@ -62,4 +62,24 @@ inline int make_tensor_map_3d(CUtensorMap* out, const void* base, CUtensorMapDat
   return r == CUDA_SUCCESS ? 0 : -4;
 }
 
+// 4-D variant: dims {d0 (contiguous), d1, d2, d3} with byte strides for d1..d3; box {box0, box1, 1, 1}.
+inline int make_tensor_map_4d(CUtensorMap* out, const void* base, CUtensorMapDataType dt, int elem_bytes,
+                              const int64_t dims_in[4], const int64_t strides_bytes[3], int box0, int box1,
+                              CUtensorMapSwizzle swz = CU_TENSOR_MAP_SWIZZLE_128B) {
+  PFN_encodeTiled fn = get_encode_fn();
+  if (!fn) return -1;
+  if (reinterpret_cast<uintptr_t>(base) & 15) return -2;
+  for (int i = 0; i < 3; ++i)
+    if (strides_bytes[i] & 15) return -2;
+  if (box1 > 256 || box0 * elem_bytes > 128) return -3;
+  cuuint64_t dims[4], strides[3];
+  for (int i = 0; i < 4; ++i) dims[i] = static_cast<cuuint64_t>(dims_in[i]);
+  for (int i = 0; i < 3; ++i) strides[i] = static_cast<cuuint64_t>(strides_bytes[i]);
+  cuuint32_t box[4] = {static_cast<cuuint32_t>(box0), static_cast<cuuint32_t>(box1), 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = fn(out, dt, 4, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -4;
+}
+
 }  // namespace ortb200

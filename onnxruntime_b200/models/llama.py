@@ -1,0 +1,212 @@
+"""Llama-family decoder as an ONNX graph (random-init exporter).
+
+Produces the graph shape the reference's LLM tooling produces after its fusion
+passes (onnxruntime/python/tools/transformers/models/llama/convert_to_onnx.py:
+``GroupQueryAttention`` with packed QKV and in-op rotary embedding,
+``SkipSimplifiedLayerNormalization`` carrying the residual stream, one
+``past_key_values.{i}.key/value`` -> ``present.{i}.key/value`` pair per layer
+bound to the same buffer) and, for tensor parallelism, one graph per rank with
+heads / FFN columns divided by the world size and ``com.microsoft.AllReduce``
+after the two row-parallel projections (the ``rank_{r}_*.onnx`` convention of
+that exporter).
+
+Weights are either embedded (tests) or declared as session-supplied external
+initializers and returned separately as torch tensors (large models).
+"""
+from __future__ import annotations
+
+import math
+import zlib
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Tuple
+
+import numpy as np
+import torch
+
+from .. import onnx_lite as ol
+
+T = ol.TensorProto
+
+
+@dataclass
+class LlamaConfig:
+    vocab_size: int = 128256
+    hidden_size: int = 4096
+    num_layers: int = 32
+    num_heads: int = 32
+    num_kv_heads: int = 8
+    head_dim: int = 128
+    ffn_size: int = 14336
+    rope_theta: float = 500000.0
+    max_seq_len: int = 2048
+    rms_eps: float = 1e-5
+    dtype: str = "bf16"  # bf16 | fp16 | fp32
+
+    @staticmethod
+    def llama3_8b(**kw) -> "LlamaConfig":
+        return LlamaConfig(**kw)
+
+    @staticmethod
+    def llama3_70b(**kw) -> "LlamaConfig":
+        return LlamaConfig(hidden_size=8192, num_layers=80, num_heads=64, num_kv_heads=8, ffn_size=28672, **kw)
+
+    @staticmethod
+    def tiny(**kw) -> "LlamaConfig":
+        base = dict(vocab_size=512, hidden_size=256, num_layers=2, num_heads=4, num_kv_heads=2, head_dim=64,
+                    ffn_size=512, max_seq_len=128)
+        base.update(kw)
+        return LlamaConfig(**base)
+
+
+_TORCH_DT = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}
+_ONNX_DT = {"bf16": T.BFLOAT16, "fp16": T.FLOAT16, "fp32": T.FLOAT}
+
+
+def rope_caches(cfg: LlamaConfig, device="cpu") -> Tuple[torch.Tensor, torch.Tensor]:
+    half = cfg.head_dim // 2
+    inv_freq = 1.0 / (cfg.rope_theta ** (torch.arange(0, half, dtype=torch.float64, device=device) / half))
+    t = torch.arange(cfg.max_seq_len, dtype=torch.float64, device=device)
+    freqs = torch.outer(t, inv_freq)
+    dt = _TORCH_DT[cfg.dtype]
+    return freqs.cos().to(dt), freqs.sin().to(dt)
+
+
+def build_llama(cfg: LlamaConfig, tp_rank: int = 0, tp_size: int = 1, external_weights: bool = False, seed: int = 0,
+                device: str = "cpu", with_argmax: bool = True, last_token_logits: bool = True,
+                weight_std: float = 0.02) -> Tuple[bytes, Dict[str, torch.Tensor]]:
+    """Returns (ModelProto bytes, weights).  With ``external_weights`` the dict holds every weight (on
+    ``device``) to pass to ``SessionOptions.add_external_initializers``; otherwise it is empty and the
+    weights are embedded in the model."""
+    assert cfg.num_heads % tp_size == 0 and cfg.num_kv_heads % tp_size == 0 and cfg.ffn_size % tp_size == 0
+    dt, odt = _TORCH_DT[cfg.dtype], _ONNX_DT[cfg.dtype]
+    N, Nk, H = cfg.num_heads // tp_size, cfg.num_kv_heads // tp_size, cfg.head_dim
+    hidden, ffn = cfg.hidden_size, cfg.ffn_size // tp_size
+    gen = torch.Generator(device=device)
+    weights: Dict[str, torch.Tensor] = {}
+    inits: List[ol.Tensor] = []
+    nodes: List[ol.Node] = []
+
+    def randn(name: str, shape, std: float = weight_std, shard: Optional[Tuple[int, int]] = None) -> str:
+        """Full-size tensor from a per-name seed, then the rank's shard (so ranks agree on the full model)."""
+        gen.manual_seed(seed * 1000003 + zlib.crc32(name.encode()))
+        full = tuple(shape)
+        if shard is not None:
+            axis, parts = shard
+            full = list(shape)
+            full[axis] *= parts
+        w = (torch.randn(full, generator=gen, device=device, dtype=torch.float32) * std).to(dt)
+        if shard is not None:
+            axis, parts = shard
+            w = w.chunk(parts, dim=axis)[tp_rank].contiguous()
+        add_weight(name, w)
+        return name
+
+    def add_weight(name: str, w: torch.Tensor) -> None:
+        if external_weights:
+            weights[name] = w
+            inits.append(ol.make_external_tensor(name, odt if w.dtype == dt else T.FLOAT, w.shape))
+        else:
+            inits.append(ol.make_tensor(name, w))
+
+    def ones(name: str, n: int) -> str:
+        add_weight(name, torch.ones(n, dtype=dt, device=device))
+        return name
+
+    cos, sin = rope_caches(cfg, device)
+    add_weight("cos_cache", cos)
+    add_weight("sin_cache", sin)
+
+    randn("model.embed_tokens.weight", (cfg.vocab_size, hidden))
+    nodes.append(ol.make_node("Gather", ["model.embed_tokens.weight", "input_ids"], ["hidden_0"], name="embed", axis=0))
+
+    residual = "hidden_0"   # running residual stream
+    pending = None          # output of the previous block still to be added to the residual
+    inputs = [
+        ol.make_tensor_value_info("input_ids", T.INT64, ["batch", "seq"]),
+        ol.make_tensor_value_info("seqlens_k", T.INT32, ["batch"]),
+        ol.make_tensor_value_info("total_sequence_length", T.INT32, []),
+    ]
+    outputs = []
+    for i in range(cfg.num_layers):
+        p = f"model.layers.{i}"
+        ln1 = ones(f"{p}.input_layernorm.weight", hidden)
+        if pending is None:
+            nodes.append(ol.make_node("SimplifiedLayerNormalization", [residual, ln1], [f"{p}.ln1_out"], name=f"{p}.ln1",
+                                      axis=-1, epsilon=cfg.rms_eps))
+        else:
+            nodes.append(ol.make_node("SkipSimplifiedLayerNormalization", [pending, residual, ln1],
+                                      [f"{p}.ln1_out", "", "", f"{p}.res1"], name=f"{p}.ln1", domain="com.microsoft",
+                                      epsilon=cfg.rms_eps))
+            residual = f"{p}.res1"
+        # packed QKV projection: column-parallel, columns ordered [q heads | k heads | v heads] of this rank
+        gen.manual_seed(seed * 1000003 + zlib.crc32(f"{p}.qkv".encode()))
+        full = (torch.randn((hidden, (cfg.num_heads + 2 * cfg.num_kv_heads) * H), generator=gen, device=device,
+                            dtype=torch.float32) * weight_std).to(dt)
+        q_full, k_full, v_full = full.split([cfg.num_heads * H, cfg.num_kv_heads * H, cfg.num_kv_heads * H], dim=1)
+        wqkv = torch.cat([q_full.chunk(tp_size, 1)[tp_rank], k_full.chunk(tp_size, 1)[tp_rank],
+                          v_full.chunk(tp_size, 1)[tp_rank]], dim=1).contiguous()
+        del full, q_full, k_full, v_full
+        add_weight(f"{p}.attn.qkv_proj.weight", wqkv)
+        nodes.append(ol.make_node("MatMul", [f"{p}.ln1_out", f"{p}.attn.qkv_proj.weight"], [f"{p}.qkv"], name=f"{p}.qkv_proj"))
+        inputs.append(ol.make_tensor_value_info(f"past_key_values.{i}.key", odt, ["batch", Nk, "past_seq", H]))
+        inputs.append(ol.make_tensor_value_info(f"past_key_values.{i}.value", odt, ["batch", Nk, "past_seq", H]))
+        outputs.append(ol.make_tensor_value_info(f"present.{i}.key", odt, ["batch", Nk, "present_seq", H]))
+        outputs.append(ol.make_tensor_value_info(f"present.{i}.value", odt, ["batch", Nk, "present_seq", H]))
+        nodes.append(ol.make_node(
+            "GroupQueryAttention",
+            [f"{p}.qkv", "", "", f"past_key_values.{i}.key", f"past_key_values.{i}.value", "seqlens_k",
+             "total_sequence_length", "cos_cache", "sin_cache"],
+            [f"{p}.attn_out", f"present.{i}.key", f"present.{i}.value"], name=f"{p}.attn", domain="com.microsoft",
+            num_heads=N, kv_num_heads=Nk, do_rotary=1, rotary_interleaved=0))
+        randn(f"{p}.attn.o_proj.weight", (N * H, hidden), shard=(0, tp_size))
+        nodes.append(ol.make_node("MatMul", [f"{p}.attn_out", f"{p}.attn.o_proj.weight"], [f"{p}.o_partial" if tp_size > 1 else f"{p}.o"],
+                                  name=f"{p}.o_proj"))
+        if tp_size > 1:
+            nodes.append(ol.make_node("AllReduce", [f"{p}.o_partial"], [f"{p}.o"], name=f"{p}.o_allreduce", domain="com.microsoft"))
+        ln2 = ones(f"{p}.post_attention_layernorm.weight", hidden)
+        nodes.append(ol.make_node("SkipSimplifiedLayerNormalization", [f"{p}.o", residual, ln2],
+                                  [f"{p}.ln2_out", "", "", f"{p}.res2"], name=f"{p}.ln2", domain="com.microsoft",
+                                  epsilon=cfg.rms_eps))
+        residual = f"{p}.res2"
+        randn(f"{p}.mlp.gate_proj.weight", (hidden, ffn), shard=(1, tp_size))
+        randn(f"{p}.mlp.up_proj.weight", (hidden, ffn), shard=(1, tp_size))
+        randn(f"{p}.mlp.down_proj.weight", (ffn, hidden), shard=(0, tp_size))
+        nodes += [
+            ol.make_node("MatMul", [f"{p}.ln2_out", f"{p}.mlp.gate_proj.weight"], [f"{p}.gate"], name=f"{p}.gate_proj"),
+            ol.make_node("MatMul", [f"{p}.ln2_out", f"{p}.mlp.up_proj.weight"], [f"{p}.up"], name=f"{p}.up_proj"),
+            ol.make_node("Sigmoid", [f"{p}.gate"], [f"{p}.gate_sig"], name=f"{p}.sigmoid"),
+            ol.make_node("Mul", [f"{p}.gate", f"{p}.gate_sig"], [f"{p}.gate_act"], name=f"{p}.silu"),
+            ol.make_node("Mul", [f"{p}.gate_act", f"{p}.up"], [f"{p}.mlp_h"], name=f"{p}.gate_mul"),
+            ol.make_node("MatMul", [f"{p}.mlp_h", f"{p}.mlp.down_proj.weight"],
+                         [f"{p}.down_partial" if tp_size > 1 else f"{p}.down"], name=f"{p}.down_proj"),
+        ]
+        if tp_size > 1:
+            nodes.append(ol.make_node("AllReduce", [f"{p}.down_partial"], [f"{p}.down"], name=f"{p}.down_allreduce",
+                                      domain="com.microsoft"))
+        pending = f"{p}.down"
+
+    lnf = ones("model.norm.weight", hidden)
+    nodes.append(ol.make_node("SkipSimplifiedLayerNormalization", [pending, residual, lnf], ["final_norm"],
+                              name="final_norm", domain="com.microsoft", epsilon=cfg.rms_eps))
+    head_in = "final_norm"
+    if last_token_logits:
+        inits.append(ol.make_tensor("last_index", np.array([-1], dtype=np.int64)))
+        nodes.append(ol.make_node("Gather", ["final_norm", "last_index"], ["final_last"], name="last_token", axis=1))
+        head_in = "final_last"
+    randn("lm_head.weight", (hidden, cfg.vocab_size))
+    nodes.append(ol.make_node("MatMul", [head_in, "lm_head.weight"], ["logits"], name="lm_head"))
+    outputs.insert(0, ol.make_tensor_value_info("logits", odt, ["batch", 1 if last_token_logits else "seq", cfg.vocab_size]))
+    if with_argmax:
+        nodes.append(ol.make_node("ArgMax", ["logits"], ["next_tokens"], name="greedy", axis=-1, keepdims=0))
+        outputs.insert(1, ol.make_tensor_value_info("next_tokens", T.INT64, ["batch", 1 if last_token_logits else "seq"]))
+    graph = ol.make_graph(nodes, "llama", inputs, outputs, inits)
+    meta = {"tp_rank": str(tp_rank), "tp_size": str(tp_size), "architecture": "llama"}
+    model = ol.make_model(graph, opset=17, metadata=meta)
+    return model.serialize(), weights
+
+
+def empty_kv_cache(cfg: LlamaConfig, batch: int, max_len: int, device, tp_size: int = 1) -> List[Tuple[torch.Tensor, torch.Tensor]]:
+    dt = _TORCH_DT[cfg.dtype]
+    nk = cfg.num_kv_heads // tp_size
+    return [(torch.zeros(batch, nk, max_len, cfg.head_dim, dtype=dt, device=device),
+             torch.zeros(batch, nk, max_len, cfg.head_dim, dtype=dt, device=device)) for _ in range(cfg.num_layers)]

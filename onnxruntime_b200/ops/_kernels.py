@@ -109,3 +109,122 @@ def gemm_last_config():
     bn, sp, st = ctypes.c_int(), ctypes.c_int(), ctypes.c_int()
     lib().ortb200_gemm_last_config(ctypes.byref(bn), ctypes.byref(sp), ctypes.byref(st))
     return bn.value, sp.value, st.value
+
+
+# ---------------------------------------------------------------------------- norm
+class NormArgs(ctypes.Structure):
+    _fields_ = [("x", ctypes.c_void_p), ("skip", ctypes.c_void_p), ("bias", ctypes.c_void_p), ("gamma", ctypes.c_void_p),
+                ("beta", ctypes.c_void_p), ("out", ctypes.c_void_p), ("sum_out", ctypes.c_void_p), ("rows", ctypes.c_int64),
+                ("hidden", ctypes.c_int), ("epsilon", ctypes.c_float), ("simplified", ctypes.c_int), ("dtype", ctypes.c_int)]
+
+
+def _check(rc: int, what: str) -> None:
+    if rc != 0:
+        raise RuntimeError(f"{what} rejected its arguments (code {rc})")
+
+
+def norm(x, gamma, beta=None, skip=None, bias=None, eps=1e-5, simplified=False, want_sum=False):
+    x = x.contiguous()
+    H = x.shape[-1]
+    out = torch.empty_like(x)
+    s = torch.empty_like(x) if want_sum else None
+    a = NormArgs(_ptr(x), _ptr(skip), _ptr(bias), _ptr(gamma), _ptr(beta), _ptr(out), _ptr(s), x.numel() // H, H, eps,
+                 1 if simplified else 0, dtype_code(x.dtype))
+    _check(lib().ortb200_norm(ctypes.byref(a), ctypes.c_void_p(stream_ptr())), "ortb200_norm")
+    return (out, s) if want_sum else out
+
+
+# ----------------------------------------------------------------------------- GQA
+class GqaPrepArgs(ctypes.Structure):
+    _fields_ = [("qkv", ctypes.c_void_p), ("k", ctypes.c_void_p), ("v", ctypes.c_void_p), ("q_out", ctypes.c_void_p),
+                ("k_cache", ctypes.c_void_p), ("v_cache", ctypes.c_void_p), ("seqlens_k", ctypes.c_void_p),
+                ("cos_cache", ctypes.c_void_p), ("sin_cache", ctypes.c_void_p), ("position_ids", ctypes.c_void_p),
+                ("B", ctypes.c_int), ("S", ctypes.c_int), ("N", ctypes.c_int), ("Nk", ctypes.c_int), ("H", ctypes.c_int),
+                ("Smax", ctypes.c_int), ("rot_dim", ctypes.c_int), ("interleaved", ctypes.c_int),
+                ("first_prompt", ctypes.c_int), ("do_rotary", ctypes.c_int), ("dtype", ctypes.c_int)]
+
+
+def gqa_prep(qkv, k_cache, v_cache, seqlens_k, cos, sin, N, Nk, H, first_prompt, interleaved=False, position_ids=None):
+    B, S = qkv.shape[0], qkv.shape[1]
+    q_out = torch.empty(B, S, N, H, dtype=qkv.dtype, device=qkv.device)
+    a = GqaPrepArgs(_ptr(qkv), None, None, _ptr(q_out), _ptr(k_cache), _ptr(v_cache), _ptr(seqlens_k), _ptr(cos), _ptr(sin),
+                    _ptr(position_ids), B, S, N, Nk, H, k_cache.shape[2], 0 if cos is None else cos.shape[1] * 2,
+                    1 if interleaved else 0, 1 if first_prompt else 0, 0 if cos is None else 1, dtype_code(qkv.dtype))
+    _check(lib().ortb200_gqa_prep(ctypes.byref(a), ctypes.c_void_p(stream_ptr())), "ortb200_gqa_prep")
+    return q_out
+
+
+class GqaDecodeArgs(ctypes.Structure):
+    _fields_ = [("q", ctypes.c_void_p), ("k_cache", ctypes.c_void_p), ("v_cache", ctypes.c_void_p),
+                ("seqlens_k", ctypes.c_void_p), ("head_sink", ctypes.c_void_p), ("out", ctypes.c_void_p),
+                ("workspace", ctypes.c_void_p), ("workspace_bytes", ctypes.c_int64), ("B", ctypes.c_int), ("N", ctypes.c_int),
+                ("Nk", ctypes.c_int), ("H", ctypes.c_int), ("Smax", ctypes.c_int), ("splits", ctypes.c_int),
+                ("window", ctypes.c_int), ("scale", ctypes.c_float), ("softcap", ctypes.c_float), ("dtype", ctypes.c_int),
+                ("use_pdl", ctypes.c_int)]
+
+
+_ATTN_WS = {}
+
+
+def gqa_decode(q, k_cache, v_cache, seqlens_k, splits=0, window=-1, scale=0.0, softcap=0.0, head_sink=None):
+    B, N, H = q.shape
+    Nk, Smax = k_cache.shape[1], k_cache.shape[2]
+    out = torch.empty(B, N * H, dtype=q.dtype, device=q.device)
+    lib().ortb200_gqa_decode_workspace_bytes.restype = ctypes.c_int64
+    need = lib().ortb200_gqa_decode_workspace_bytes(B, N, H)
+    key = q.device.index
+    ws = _ATTN_WS.get(key)
+    if ws is None or ws.numel() < need:
+        ws = torch.zeros(need, dtype=torch.uint8, device=q.device)
+        _ATTN_WS[key] = ws
+    a = GqaDecodeArgs(_ptr(q.contiguous()), _ptr(k_cache), _ptr(v_cache), _ptr(seqlens_k), _ptr(head_sink), _ptr(out), _ptr(ws),
+                      ws.numel(), B, N, Nk, H, Smax, splits, window, scale, softcap, dtype_code(q.dtype), 0)
+    _check(lib().ortb200_gqa_decode(ctypes.byref(a), ctypes.c_void_p(stream_ptr())), "ortb200_gqa_decode")
+    return out
+
+
+class AttnPrefillArgs(ctypes.Structure):
+    _fields_ = [("q", ctypes.c_void_p), ("k", ctypes.c_void_p), ("v", ctypes.c_void_p), ("seqlens_k", ctypes.c_void_p),
+                ("head_sink", ctypes.c_void_p), ("out", ctypes.c_void_p), ("B", ctypes.c_int), ("S", ctypes.c_int),
+                ("N", ctypes.c_int), ("Nk", ctypes.c_int), ("H", ctypes.c_int), ("kv_len", ctypes.c_int),
+                ("q_strides", ctypes.c_int64 * 3), ("o_strides", ctypes.c_int64 * 3), ("kv_strides", ctypes.c_int64 * 3),
+                ("first_prompt", ctypes.c_int), ("causal", ctypes.c_int), ("window", ctypes.c_int), ("scale", ctypes.c_float),
+                ("softcap", ctypes.c_float), ("dtype", ctypes.c_int), ("status", ctypes.c_void_p)]
+
+
+def attn_prefill(q, k, v, seqlens_k=None, first_prompt=True, causal=True, window=-1, scale=0.0, softcap=0.0,
+                 kv_layout="bnsh", status=None):
+    """q [B,S,N,H]; k/v [B,Nk,T,H] ("bnsh") or [B,T,Nk,H] ("bsnh").  Returns [B,S,N,H]."""
+    B, S, N, H = q.shape
+    if kv_layout == "bnsh":
+        Nk, T = k.shape[1], k.shape[2]
+        kvs = (k.stride(0), k.stride(1), k.stride(2))
+    else:
+        T, Nk = k.shape[1], k.shape[2]
+        kvs = (k.stride(0), k.stride(2), k.stride(1))
+    out = torch.empty_like(q)
+    a = AttnPrefillArgs(_ptr(q), _ptr(k), _ptr(v), _ptr(seqlens_k), None, _ptr(out), B, S, N, Nk, H, T,
+                        (ctypes.c_int64 * 3)(q.stride(0), q.stride(1), q.stride(2)),
+                        (ctypes.c_int64 * 3)(out.stride(0), out.stride(1), out.stride(2)), (ctypes.c_int64 * 3)(*kvs),
+                        1 if first_prompt else 0, 1 if causal else 0, window, scale, softcap, dtype_code(q.dtype), _ptr(status))
+    _check(lib().ortb200_attn_prefill(ctypes.byref(a), ctypes.c_void_p(stream_ptr())), "ortb200_attn_prefill")
+    return out
+
+
+# ---------------------------------------------------------------------------- misc
+def argmax(x):
+    x = x.contiguous()
+    rows, n = x.numel() // x.shape[-1], x.shape[-1]
+    out = torch.empty(x.shape[:-1], dtype=torch.int64, device=x.device)
+    _check(lib().ortb200_argmax(ctypes.c_void_p(_ptr(x)), ctypes.c_void_p(_ptr(out)), ctypes.c_int64(rows), ctypes.c_int64(n),
+                                dtype_code(x.dtype), ctypes.c_void_p(stream_ptr())), "ortb200_argmax")
+    return out
+
+
+def gather_rows(table, ids):
+    ids = ids.contiguous()
+    out = torch.empty(*ids.shape, table.shape[1], dtype=table.dtype, device=table.device)
+    _check(lib().ortb200_gather_rows(ctypes.c_void_p(_ptr(table)), ctypes.c_void_p(_ptr(ids)), ctypes.c_void_p(_ptr(out)),
+                                     ctypes.c_int64(ids.numel()), ctypes.c_int64(table.shape[0]), table.shape[1],
+                                     table.element_size(), ctypes.c_void_p(stream_ptr())), "ortb200_gather_rows")
+    return out

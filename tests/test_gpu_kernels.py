@@ -1,0 +1,200 @@
+"""Numerics of the hand-written sm_100a kernels against plain PyTorch fp32 references."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def K():
+    from onnxruntime_b200.ops import _kernels
+    _kernels.lib()  # fail loudly when the library is missing
+    return _kernels
+
+
+def _rel(a, b):
+    return (a.float() - b.float()).abs().max().item() / max(b.float().abs().max().item(), 1e-6)
+
+
+@pytest.mark.parametrize("M,N,Kd", [(8, 128, 64), (8, 4096, 4096), (1, 6144, 4096), (16, 1024, 14336), (32, 1024, 1024),
+                                    (64, 1024, 1024), (128, 1024, 1024), (200, 1000, 1024), (1024, 4096, 1024),
+                                    (8, 1000, 264)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_gemm(K, M, N, Kd, dtype):
+    torch.manual_seed(0)
+    x = (torch.randn(M, Kd, device="cuda") * 0.5).to(dtype)
+    w = (torch.randn(N, Kd, device="cuda") * 0.05).to(dtype)
+    y = K.gemm(x, w)
+    ref = x.float() @ w.float().T
+    assert _rel(y, ref) < 1e-2
+
+
+@pytest.mark.parametrize("splits", [1, 2, 4, 8])
+def test_gemm_split_k_epilogue(K, splits):
+    torch.manual_seed(1)
+    x = (torch.randn(8, 4096, device="cuda") * 0.5).bfloat16()
+    w = (torch.randn(2048, 4096, device="cuda") * 0.05).bfloat16()
+    b = torch.randn(2048, device="cuda").bfloat16()
+    r = torch.randn(8, 2048, device="cuda").bfloat16()
+    y = K.gemm(x, w, bias=b, residual=r, act="fastgelu", force_splits=splits)
+    ref = torch.nn.functional.gelu(x.float() @ w.float().T + b.float(), approximate="tanh") + r.float()
+    assert _rel(y, ref) < 1e-2
+
+
+@pytest.mark.parametrize("M", [8, 300])
+def test_gemm_swiglu(K, M):
+    torch.manual_seed(2)
+    I, H = 1536, 1024
+    x = (torch.randn(M, H, device="cuda") * 0.5).bfloat16()
+    w = (torch.randn(2 * I, H, device="cuda") * 0.05).bfloat16()
+    y = K.gemm(x, w, act="swiglu")
+    g, u = x.float() @ w[:I].float().T, x.float() @ w[I:].float().T
+    assert _rel(y, torch.nn.functional.silu(g) * u) < 1.5e-2
+
+
+def test_gemm_deterministic(K):
+    torch.manual_seed(3)
+    x = (torch.randn(8, 14336, device="cuda") * 0.5).bfloat16()
+    w = (torch.randn(4096, 14336, device="cuda") * 0.05).bfloat16()
+    a = K.gemm(x, w)
+    b = K.gemm(x, w)
+    assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("H", [128, 1024, 4096, 8192])
+@pytest.mark.parametrize("simplified", [True, False])
+def test_norm(K, dtype, H, simplified):
+    torch.manual_seed(0)
+    rows = 37
+    x = torch.randn(rows, H, device="cuda").to(dtype)
+    skip = torch.randn(rows, H, device="cuda").to(dtype)
+    bias = torch.randn(H, device="cuda").to(dtype)
+    gamma = torch.randn(H, device="cuda").to(dtype)
+    beta = None if simplified else torch.randn(H, device="cuda").to(dtype)
+    out, s = K.norm(x, gamma, beta=beta, skip=skip, bias=bias, eps=1e-5, simplified=simplified, want_sum=True)
+    sf = (x.float() + skip.float() + bias.float()).to(dtype).float()
+    if simplified:
+        ref = sf * torch.rsqrt(sf.pow(2).mean(-1, keepdim=True) + 1e-5) * gamma.float()
+    else:
+        ref = torch.nn.functional.layer_norm(sf, (H,), gamma.float(), beta.float(), 1e-5)
+    tol = 1e-5 if dtype == torch.float32 else 2e-2
+    assert _rel(out, ref) < tol
+    assert _rel(s, sf) < 1e-6
+
+
+def _ref_attention(q, k, v, causal_offset, scale, window=-1, lens=None):
+    # q [B,N,S,H], k/v [B,Nk,T,H] fp32; query s sits at position causal_offset[b] + s
+    B, N, S, H = q.shape
+    Nk, T = k.shape[1], k.shape[2]
+    g = N // Nk
+    kk, vv = k.repeat_interleave(g, 1), v.repeat_interleave(g, 1)
+    s = q @ kk.transpose(-1, -2) * scale
+    qpos = causal_offset.view(B, 1, 1, 1) + torch.arange(S, device=q.device).view(1, 1, S, 1)
+    kpos = torch.arange(T, device=q.device).view(1, 1, 1, T)
+    allowed = kpos <= qpos
+    if window > 0:
+        allowed = allowed & (kpos > qpos - window)
+    if lens is not None:
+        allowed = allowed & (kpos < lens.view(B, 1, 1, 1))
+    s = s.masked_fill(~allowed, float("-inf"))
+    return torch.softmax(s, -1) @ vv
+
+
+@pytest.mark.parametrize("H", [64, 128])
+@pytest.mark.parametrize("N,Nk", [(4, 4), (8, 2), (32, 8), (8, 1)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_gqa_decode(K, H, N, Nk, dtype):
+    torch.manual_seed(0)
+    B, Smax = 3, 700
+    lens = torch.tensor([1, 333, 700], dtype=torch.int32, device="cuda")
+    q = torch.randn(B, N, H, device="cuda").to(dtype)
+    kc = torch.randn(B, Nk, Smax, H, device="cuda").to(dtype)
+    vc = torch.randn(B, Nk, Smax, H, device="cuda").to(dtype)
+    out = K.gqa_decode(q, kc, vc, lens - 1)
+    ref = _ref_attention(q.float().unsqueeze(2), kc.float(), vc.float(), (lens - 1).long(), 1 / math.sqrt(H),
+                         lens=lens.long()).squeeze(2)
+    assert _rel(out.view(B, N, H), ref) < 2e-2
+
+
+def test_gqa_decode_window(K):
+    torch.manual_seed(0)
+    B, N, Nk, H, Smax = 2, 8, 2, 128, 512
+    lens = torch.tensor([100, 512], dtype=torch.int32, device="cuda")
+    q = torch.randn(B, N, H, device="cuda").bfloat16()
+    kc = torch.randn(B, Nk, Smax, H, device="cuda").bfloat16()
+    vc = torch.randn(B, Nk, Smax, H, device="cuda").bfloat16()
+    out = K.gqa_decode(q, kc, vc, lens - 1, window=64)
+    ref = _ref_attention(q.float().unsqueeze(2), kc.float(), vc.float(), (lens - 1).long(), 1 / math.sqrt(H), window=64,
+                         lens=lens.long()).squeeze(2)
+    assert _rel(out.view(B, N, H), ref) < 2e-2
+
+
+@pytest.mark.parametrize("H", [64, 128])
+@pytest.mark.parametrize("S,past", [(128, 0), (200, 0), (1024, 0), (77, 300)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_attn_prefill(K, H, S, past, dtype):
+    torch.manual_seed(0)
+    B, N, Nk = 2, 4, 2
+    T = past + S
+    q = torch.randn(B, S, N, H, device="cuda").to(dtype)
+    kc = torch.randn(B, Nk, T + 5, H, device="cuda").to(dtype)
+    vc = torch.randn(B, Nk, T + 5, H, device="cuda").to(dtype)
+    seqlens = torch.full((B,), T - 1, dtype=torch.int32, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    out = K.attn_prefill(q, kc, vc, seqlens, first_prompt=(past == 0), status=status)
+    assert status.item() == 0
+    ref = _ref_attention(q.float().transpose(1, 2), kc.float(), vc.float(),
+                         torch.full((B,), past, device="cuda"), 1 / math.sqrt(H),
+                         lens=torch.full((B,), T, device="cuda")).transpose(1, 2)
+    assert _rel(out, ref) < 2e-2
+
+
+def test_attn_prefill_noncausal_lengths(K):
+    torch.manual_seed(0)
+    B, S, N, H = 3, 384, 4, 64
+    q = torch.randn(B, S, N, H, device="cuda").half()
+    k = torch.randn(B, S, N, H, device="cuda").half()
+    v = torch.randn(B, S, N, H, device="cuda").half()
+    lens = torch.tensor([384, 100, 257], dtype=torch.int32, device="cuda")
+    out = K.attn_prefill(q, k, v, lens - 1, first_prompt=True, causal=False, kv_layout="bsnh")
+    s = torch.einsum("bsnh,btnh->bnst", q.float(), k.float()) / math.sqrt(H)
+    mask = torch.arange(S, device="cuda").view(1, 1, 1, S) < lens.view(B, 1, 1, 1)
+    ref = torch.einsum("bnst,btnh->bsnh", torch.softmax(s.masked_fill(~mask, float("-inf")), -1), v.float())
+    assert _rel(out, ref) < 2e-2
+
+
+def test_gqa_prep_rotary_append(K):
+    torch.manual_seed(0)
+    B, S, N, Nk, H, Smax = 2, 5, 4, 2, 64, 32
+    qkv = torch.randn(B, S, (N + 2 * Nk) * H, device="cuda").bfloat16()
+    half = H // 2
+    inv = 1.0 / (10000 ** (torch.arange(half, device="cuda").float() / half))
+    ang = torch.outer(torch.arange(Smax, device="cuda").float(), inv)
+    cos, sin = ang.cos().bfloat16(), ang.sin().bfloat16()
+    kc = torch.zeros(B, Nk, Smax, H, device="cuda").bfloat16()
+    vc = torch.zeros_like(kc)
+    seqlens = torch.tensor([7 + S - 1, 3 + S - 1], dtype=torch.int32, device="cuda")  # past lengths 7 and 3
+    q_rot = K.gqa_prep(qkv, kc, vc, seqlens, cos, sin, N, Nk, H, first_prompt=False)
+    qf = qkv.float().view(B, S, N + 2 * Nk, H)
+    for b, past in enumerate([7, 3]):
+        pos = torch.arange(past, past + S, device="cuda")
+        c, s_ = cos.float()[pos].unsqueeze(1), sin.float()[pos].unsqueeze(1)
+
+        def rot(x):
+            x1, x2 = x[..., :half], x[..., half:]
+            return torch.cat([x1 * c - x2 * s_, x2 * c + x1 * s_], -1)
+        assert _rel(q_rot[b], rot(qf[b, :, :N])) < 1e-2
+        assert _rel(kc[b, :, past:past + S].transpose(0, 1), rot(qf[b, :, N:N + Nk])) < 1e-2
+        assert torch.equal(vc[b, :, past:past + S].transpose(0, 1), qkv.view(B, S, N + 2 * Nk, H)[b, :, N + Nk:])
+
+
+def test_argmax_gather(K):
+    torch.manual_seed(0)
+    x = torch.randn(8, 128256, device="cuda").bfloat16()
+    assert torch.equal(K.argmax(x), x.float().argmax(-1))
+    table = torch.randn(1000, 256, device="cuda").bfloat16()
+    ids = torch.randint(0, 1000, (4, 7), device="cuda")
+    assert torch.equal(K.gather_rows(table, ids), table[ids])
