@@ -1,0 +1,263 @@
+"""Headline benchmark: Llama-3-8B tensor-parallel greedy decode through the session API.
+
+    python bench.py --gpus N --steps K --warmup W            # N = 1
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
+        bench.py --gpus N --steps K --warmup W               # N > 1, one rank per GPU
+
+Model / config (the reference's headline configuration): Llama-3-8B-shaped decoder (32 layers, hidden 4096,
+32 q / 8 kv heads, head 128, SwiGLU 14336, vocab 128256, RoPE theta 5e5), bf16, batch 8, prompt 1024 random
+token ids, greedy decode; random-init weights N(0, 0.02) generated on the device and handed to the session
+as external initializers (synthetic data, no checkpoint).  A "step" is one decode step of the whole batch:
+every layer, the LM head and the arg-max, all inside the timed region.
+
+Printed JSON: ``value`` = batch * K / time of K decode steps timed with CUDA events on the device (max over
+ranks); ``e2e.value`` = the same loop driven the way a user drives it, with each step's inputs copied from
+pinned host memory and the sampled tokens read back to the host every step; ``ttft_ms_p50`` = prompt run.
+Each decode step streams all weights (16 GB at N=1), far more than the 126 MB L2, so no explicit L2 flush is
+needed between iterations (config.l2 says so).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "llama3_8b_tp_decode_tokens_per_s"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100", "-i",
+                 str(self.gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], None, set()
+        for ln in self.lines:
+            parts = [p.strip() for p in ln.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                mx = float(parts[2])
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        med = sm[len(sm) // 2] if sm else None
+        return {"sm_mhz": med, "sm_max_mhz": mx, "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def reference_arm(args):
+    """The reference arm must run the unmodified reference from baseline/_ref.  Its one allowed offline install
+    (`pip install --no-index --no-build-isolation --find-links /opt/wheelhouse --target baseline/_ref
+    /root/reference`, also tried from a writable copy with --no-deps) stops at metadata generation: setup.py
+    packages a finished cmake build (onnxruntime/capi with the compiled pybind module), and that native build
+    needs third-party sources that are download URLs (cmake/deps.txt).  DESIGN.md records the attempt."""
+    reason = ("reference not installable offline: pip install of /root/reference fails at metadata generation "
+              "(setup.py expects a cmake-built onnxruntime/capi; the native build needs downloaded third-party sources)")
+    try:
+        sys.path.insert(0, os.path.join(ROOT, "baseline", "_ref"))
+        import onnxruntime  # noqa: F401
+        reason = "baseline/_ref imports but no reference benchmark driver is wired for it"
+    except Exception:
+        pass
+    print(json.dumps({"impl": "reference", "unavailable": reason}))
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=127)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--prompt", type=int, default=1024)
+    ap.add_argument("--layers", type=int, default=32, help="for quick experiments only; the headline uses 32")
+    ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--pdl", type=int, default=1)
+    ap.add_argument("--ttft-repeats", type=int, default=3)
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return reference_arm(args)
+
+    import torch
+    import torch.distributed as dist
+
+    import onnxruntime_b200 as ort
+    from onnxruntime_b200.models.generation import DecoderRunner
+    from onnxruntime_b200.models.llama import LlamaConfig, build_llama
+    from onnxruntime_b200.parallel.dist import init_distributed, single_process
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.gpus > 1 and world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} needs torch.distributed.run with --nproc-per-node {args.gpus} (WORLD_SIZE={world})")
+    info = init_distributed("nccl") if world > 1 else single_process()
+    local = info.local_rank
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    rank, tp = info.rank, info.world_size
+    W = max(args.warmup, 3)
+    K = args.steps
+
+    max_len = args.prompt + K + W + 8
+    max_len = (max_len + 127) // 128 * 128
+    cfg = LlamaConfig.llama3_8b(max_seq_len=max_len, num_layers=args.layers)
+    model, weights = build_llama(cfg, tp_rank=rank, tp_size=tp, external_weights=True, device=str(device))
+    so = ort.SessionOptions()
+    so.add_external_initializers(list(weights.keys()), list(weights.values()))
+    so.add_session_config_entry("ortb200.pdl", str(args.pdl))
+    providers = [("CUDAExecutionProvider", {"device_id": str(local), "enable_cuda_graph": "0" if args.no_graph else "1"})]
+    sess = ort.InferenceSession(model, so, providers=providers, dist=info if tp > 1 else None, enable_fallback=False)
+    del weights
+    torch.cuda.empty_cache()
+
+    runner = DecoderRunner(sess, cfg, batch=args.batch, max_len=max_len, tp_size=tp, device=device)
+    gen = torch.Generator().manual_seed(1234)
+    prompt = torch.randint(0, cfg.vocab_size, (args.batch, args.prompt), generator=gen)
+    prompt_pinned = prompt.pin_memory()
+
+    def sync_all():
+        if tp > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- TTFT: prompt run (input copied from pinned host memory, first token read back)
+    ttfts = []
+    for _ in range(max(args.ttft_repeats, 1)):
+        sync_all()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        first = runner.prefill(prompt_pinned)
+        first_host = first.cpu()
+        e1.record()
+        torch.cuda.synchronize()
+        ttfts.append(e0.elapsed_time(e1))
+    ttfts.sort()
+    ttft_p50 = ttfts[len(ttfts) // 2]
+    if tp > 1:
+        t = torch.tensor([ttft_p50], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ttft_p50 = t.item()
+
+    # ---- decode: warm-up (first call runs eagerly once and captures the CUDA graph)
+    runner.decode_step(first)
+    launches_per_step = sess.last_run_launch_count()
+    for _ in range(W - 1):
+        runner.decode_step(None)
+    sync_all()
+    sess.check_device_status()
+
+    # ---- kernel-side number: K steps, next token fed on the device
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    sync_all()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(K):
+        runner.decode_step(None)
+    e1.record()
+    sync_all()
+    dev_ms = e0.elapsed_time(e1)
+    clocks = sampler.stop() if rank == 0 else None
+    if tp > 1:
+        t = torch.tensor([dev_ms], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dev_ms = t.item()
+
+    # ---- end to end: per step H2D of the inputs from pinned memory, D2H of the sampled tokens, host sync
+    runner.cur_len = args.prompt + 1  # rewind the cache position so both loops see the same lengths
+    ids_pinned = torch.zeros(args.batch, 1, dtype=torch.int64).pin_memory()
+    ids_pinned.copy_(first_host)
+    out_pinned = torch.zeros(args.batch, 1, dtype=torch.int64).pin_memory()
+    seq_pinned = torch.zeros(args.batch, dtype=torch.int32).pin_memory()
+    h2d = ids_pinned.numel() * 8 + seq_pinned.numel() * 4
+    d2h = out_pinned.numel() * 8
+    for _ in range(2):
+        runner.decode_step_host(ids_pinned, seq_pinned, out_pinned)
+    runner.cur_len = args.prompt + 1
+    sync_all()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
+    e0.record()
+    for _ in range(K):
+        runner.decode_step_host(ids_pinned, seq_pinned, out_pinned)
+        ids_pinned.copy_(out_pinned)
+    e1.record()
+    sync_all()
+    e2e_ms = e0.elapsed_time(e1)
+    wall_ms = (time.perf_counter() - t0) * 1e3
+    if tp > 1:
+        t = torch.tensor([e2e_ms], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = t.item()
+    sess.check_device_status()
+
+    if rank == 0:
+        value = args.batch * K / (dev_ms * 1e-3)
+        e2e_value = args.batch * K / (e2e_ms * 1e-3)
+        out = {
+            "metric": METRIC, "value": round(value, 2), "unit": "tokens/s", "n_gpus": tp, "steps": K, "warmup": W,
+            "ms_per_step": round(dev_ms / K, 4), "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic (random token ids, random-init N(0,0.02) weights)",
+            "config": {"model": "Llama-3-8B" if args.layers == 32 else f"Llama-3-8B-shaped/{args.layers}L",
+                       "global_batch": args.batch, "seq_len": args.prompt, "decode_tokens": K,
+                       "parallelism": f"tp{tp}", "cuda_graph": not args.no_graph,
+                       "l2": "inputs larger than L2 (every step streams all weights)"},
+            "e2e": {"value": round(e2e_value, 2), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "ms_per_step": round(e2e_ms / K, 4), "wall_ms_per_step": round(wall_ms / K, 4)},
+            "gpu_launches": int(launches_per_step * K),
+            "launches_per_step": int(launches_per_step),
+            "ttft_ms_p50": round(ttft_p50, 3),
+            "prefill_tokens_per_s": round(args.batch * args.prompt / (ttft_p50 * 1e-3), 1),
+            "clocks": clocks,
+            "impl": "ours",
+        }
+        print(json.dumps(out))
+    if tp > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -581,6 +581,13 @@ class InferenceSession:
     def kernel_launch_count(self) -> int:
         return self._sess.kernel_launch_count()
 
+    def last_run_launch_count(self) -> int:
+        """Kernels of this library launched by the most recent eager run (or captured into the most recent graph)."""
+        return self._sess.last_run_launch_count()
+
+    def num_captured_graphs(self) -> int:
+        return self._sess.num_captured_graphs()
+
     def check_device_status(self) -> None:
         self._sess.check_device_status()
 

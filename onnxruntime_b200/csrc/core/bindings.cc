@@ -219,6 +219,7 @@ PYBIND11_MODULE(_core, m) {
       .def("node_assignments", &InferenceSession::NodeAssignments)
       .def("num_captured_graphs", &InferenceSession::NumCapturedGraphs)
       .def("kernel_launch_count", &InferenceSession::KernelLaunchCount)
+      .def("last_run_launch_count", &InferenceSession::LastRunLaunchCount)
       .def("check_device_status", [](InferenceSession& s) { Guard([&] { s.CheckDeviceStatus(); return 0; }); })
       .def("uses_gpu", &InferenceSession::uses_gpu)
       .def_readwrite("dist_group", &InferenceSession::dist_group)

@@ -226,7 +226,7 @@ void GraphExecutor::Build() {
     st.on_gpu = gpu && n->ep == kCudaEP;
     st.device = st.on_gpu ? dev : cpu;
     const std::vector<int> host = HostInputsOf(*n, *graph_);
-    std::vector<const at::Tensor*> const_inputs(n->inputs.size(), nullptr);
+    std::vector<at::Tensor> const_inputs(n->inputs.size());  // handles, not pointers: the slot vector may grow
     for (size_t i = 0; i < n->inputs.size(); ++i) {
       const std::string& v = n->inputs[i];
       if (v.empty()) {
@@ -237,7 +237,7 @@ void GraphExecutor::Build() {
         const bool want_gpu = st.on_gpu && !Contains(host, static_cast<int>(i));
         const int s = const_slot(v, want_gpu);
         st.in_slots.push_back(s);
-        const_inputs[i] = &constant_slots_[s].t;
+        const_inputs[i] = constant_slots_[s].t;
         continue;
       }
       auto it = slot_of_.find(v);
@@ -263,7 +263,7 @@ void GraphExecutor::Build() {
             constant_slots_[s].t = want_gpu ? outer_const->to(dev) : outer_const->cpu();
           }
           st.in_slots.push_back(s);
-          const_inputs[i] = &constant_slots_[s].t;
+          const_inputs[i] = constant_slots_[s].t;
         } else {
           st.in_slots.push_back(outer_slot(v));
         }
@@ -296,10 +296,14 @@ void GraphExecutor::Build() {
       ORTB_THROW(NOT_IMPLEMENTED, "Could not find an implementation for ", n->op_type, "(", n->since_version,
                  ") node with name '", n->name, "' (domain '", n->domain, "')");
     OpKernelInfo info{*n, *graph_, session_, st.device, &session_->config(),
-                      [const_inputs](int idx) -> const at::Tensor* {
-                        return idx >= 0 && idx < static_cast<int>(const_inputs.size()) ? const_inputs[idx] : nullptr;
+                      [&const_inputs](int idx) -> const at::Tensor* {
+                        return idx >= 0 && idx < static_cast<int>(const_inputs.size()) && const_inputs[idx].defined()
+                                   ? &const_inputs[idx]
+                                   : nullptr;
                       }};
     st.kernel = def->factory(info);
+    for (int idx : st.kernel->PrepackedInputs())
+      if (idx >= 0 && idx < static_cast<int>(st.in_slots.size())) st.in_slots[idx] = -1;
     steps_.push_back(std::move(st));
   }
 
@@ -310,6 +314,37 @@ void GraphExecutor::Build() {
       if (graph_->IsConstant(o.name)) const_slot(o.name, false);
       else if (graph_->Parent() != nullptr) outer_slot(o.name);
       else ORTB_THROW(INVALID_GRAPH, "graph output '", o.name, "' is not produced by any node");
+    }
+  }
+
+  // constants that only pre-packing kernels consumed are no longer needed in their original layout
+  {
+    std::vector<bool> used(slot_names_.size(), false);
+    for (auto& st : steps_)
+      for (int s : st.in_slots)
+        if (s >= 0) used[s] = true;
+    for (auto& o : output_names_) used[slot_of_[o]] = true;
+    for (int s : input_slot_) used[s] = true;
+    for (int s : outer_slot_) used[s] = true;
+    for (size_t s = 0; s < constant_slots_.size(); ++s) {
+      if (used[s] || !constant_slots_[s].t.defined()) continue;
+      constant_slots_[s] = Value();
+      std::string name = slot_names_[s];
+      const size_t suffix = name.find(kGpuSuffix);
+      if (suffix != std::string::npos) name = name.substr(0, suffix);
+      bool other_copy_used = false;
+      for (const std::string& alt : {name, name + kGpuSuffix}) {
+        auto it = slot_of_.find(alt);
+        if (it != slot_of_.end() && used[it->second]) other_copy_used = true;
+      }
+      if (!other_copy_used && graph_->IsConstant(name) && graph_->Parent() == nullptr && graph_->Consumers(name).size() > 0) {
+        bool subgraph_reader = false;
+        for (Node* c : graph_->Consumers(name))
+          if (!c->subgraphs.empty()) subgraph_reader = true;
+        const at::Tensor* t = graph_->GetInitializer(name);
+        if (!subgraph_reader && t && t->numel() > 4096)
+          graph_->AddInitializer(name, at::empty({0}, t->options().device(c10::kCPU)));  // free the storage, keep the name
+      }
     }
   }
 

@@ -110,6 +110,9 @@ class OpKernel {
   virtual void Compute(OpKernelContext& ctx) const = 0;
   // Inputs (by index) this kernel reads on the host even when the node runs on the GPU.
   virtual bool InputOnHost(int /*idx*/) const { return false; }
+  // Constant inputs the kernel re-packed into its own storage at construction; Compute() never reads them,
+  // so the session may drop the original copy.
+  virtual std::vector<int> PrepackedInputs() const { return {}; }
   const Node& node() const { return node_; }
 
  protected:

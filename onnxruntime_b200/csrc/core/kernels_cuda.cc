@@ -118,6 +118,7 @@ class GemmKernel final : public OpKernel {
     w_nk_ = w_is_nk ? w->contiguous() : w->t().contiguous();  // pre-pack: [N, K], K contiguous
     N_ = w_nk_.size(0);
   }
+  std::vector<int> PrepackedInputs() const override { return {1}; }
   void Compute(Ctx& ctx) const override {
     const at::Tensor& x = ctx.RequiredInput(0);
     at::Tensor x2 = Flatten2D(x);
@@ -169,6 +170,7 @@ class GemmSwiGLUKernel final : public OpKernel {
     I_ = wg->size(1);
     w_ = at::cat({wg->t(), wu->t()}, 0).contiguous();  // [2I, K]: gate rows then up rows
   }
+  std::vector<int> PrepackedInputs() const override { return {1, 2}; }
   void Compute(Ctx& ctx) const override {
     const at::Tensor& x = ctx.RequiredInput(0);
     at::Tensor y = LaunchGemm(ctx, Flatten2D(x), w_, I_, I_, at::Tensor(), at::Tensor(), ORTB200_ACT_SWIGLU, 1.f);

@@ -231,11 +231,20 @@ int AttentionFusion(PassContext& c) {
     Node* n = g.Producer(cur);
     if (n && n->op_type == "Add" && n->domain.empty()) {
       // one side is the attention scores (produced by Div/Mul/MatMul), the other the additive mask
+      auto is_score = [&](const std::string& v) {
+        Node* p = g.Producer(v);
+        if (!p || !p->domain.empty()) return false;
+        if (p->op_type == "MatMul") return true;
+        if (p->op_type != "Div" && p->op_type != "Mul") return false;
+        for (auto& in : p->inputs) {
+          Node* pp = g.Producer(in);
+          if (pp && pp->domain.empty() && pp->op_type == "MatMul") return true;
+        }
+        return false;
+      };
       int score_side = -1;
-      for (int s = 0; s < 2; ++s) {
-        Node* p = g.Producer(n->inputs[s]);
-        if (p && p->domain.empty() && (p->op_type == "Div" || p->op_type == "Mul" || p->op_type == "MatMul")) score_side = s;
-      }
+      for (int s = 0; s < 2; ++s)
+        if (is_score(n->inputs[s])) score_side = s;
       if (score_side < 0) continue;
       mask_value = n->inputs[1 - score_side];
       mid.push_back(n);

@@ -203,6 +203,13 @@ void InferenceSession::Initialize(const std::vector<std::pair<std::string, Provi
   output_names_ = exec->output_names();
   input_device_ = exec->input_devices();
   graph_capturable_ = exec->capturable();
+  input_index_.clear();
+  input_info_.assign(input_names_.size(), nullptr);
+  for (size_t i = 0; i < input_names_.size(); ++i) {
+    input_index_[input_names_[i]] = i;
+    for (auto& vi : g.Inputs())
+      if (vi.name == input_names_[i]) input_info_[i] = &vi;
+  }
   exec_ = std::move(exec);
   initialized_ = true;
   profiler_.Record("Session", "session_initialization", t0, profiler_.NowUs() - t0);
@@ -327,12 +334,11 @@ std::vector<Value> InferenceSession::RunImpl(const RunOptions& ro, const std::ve
   const Graph& g = *model_->graph_;
   std::vector<Value> inputs(input_names_.size());
   for (size_t i = 0; i < feed_names.size(); ++i) {
-    auto it = std::find(input_names_.begin(), input_names_.end(), feed_names[i]);
-    if (it == input_names_.end()) ORTB_THROW(INVALID_ARGUMENT, "Invalid input name: ", feed_names[i]);
-    const size_t idx = static_cast<size_t>(it - input_names_.begin());
+    auto it = input_index_.find(feed_names[i]);
+    if (it == input_index_.end()) ORTB_THROW(INVALID_ARGUMENT, "Invalid input name: ", feed_names[i]);
+    const size_t idx = it->second;
     if (feeds[i].t.defined()) {
-      for (auto& vi : g.Inputs())
-        if (vi.name == feed_names[i]) ValidateFeed(vi, feeds[i].t);
+      if (input_info_[idx]) ValidateFeed(*input_info_[idx], feeds[i].t);
       const c10::Device want = input_device_[idx];
       inputs[idx].t = feeds[i].t.device() == want ? feeds[i].t : feeds[i].t.to(want, /*non_blocking=*/true);
     } else {
@@ -374,8 +380,10 @@ std::vector<Value> InferenceSession::RunImpl(const RunOptions& ro, const std::ve
       {
         c10::cuda::CUDAStreamGuard sg(side);
         cg.graph.capture_begin();
+        const int64_t launches_before = launch_count_;
         try {
           ex->ExecuteSteps(ro, cg.slots);
+          last_run_launches_ = launch_count_ - launches_before;
         } catch (...) {
           cg.graph.capture_end();
           cuda_graphs_.erase(graph_id);
@@ -412,10 +420,14 @@ std::vector<Value> InferenceSession::RunImpl(const RunOptions& ro, const std::ve
       if (inputs[i].defined()) slots[ex->SlotOf(input_names_[i])] = inputs[i];
     for (size_t i = 0; i < output_names.size(); ++i)
       if ((*bound_outputs)[i].t.defined()) slots[ex->SlotOf(output_names[i])] = (*bound_outputs)[i];
+    const int64_t launches_before = launch_count_;
     ex->ExecuteSteps(ro, slots);
+    last_run_launches_ = launch_count_ - launches_before;
     for (auto& n : output_names) results.push_back(slots[ex->SlotOf(n)]);
   } else {
+    const int64_t launches_before = launch_count_;
     results = ex->Run(ro, inputs, nullptr, output_names);
+    last_run_launches_ = launch_count_ - launches_before;
   }
   if (profiler_.enabled()) {
     if (device_.is_cuda()) cudaStreamSynchronize(at::cuda::getCurrentCUDAStream(device_.index()).stream());

@@ -134,6 +134,8 @@ class InferenceSession {
   std::vector<std::tuple<std::string, std::string, std::string>> NodeAssignments() const;
   int NumCapturedGraphs() const { return static_cast<int>(cuda_graphs_.size()); }
   int64_t KernelLaunchCount() const { return launch_count_; }
+  // launches issued by the most recent execution of the step list (eager run or graph capture)
+  int64_t LastRunLaunchCount() const { return last_run_launches_; }
   void AddLaunches(int64_t n) { launch_count_ += n; }
   // device scratch shared by the GPU kernels (split-K partials, counters), zero-initialised
   at::Tensor& GemmWorkspace(int64_t nbytes);
@@ -169,6 +171,9 @@ class InferenceSession {
   Profiler profiler_;
   int64_t profiling_start_ns_ = 0;
   int64_t launch_count_ = 0;
+  int64_t last_run_launches_ = 0;
+  std::map<std::string, size_t> input_index_;
+  std::vector<const ValueInfo*> input_info_;
   at::Tensor gemm_ws_, attn_ws_, status_word_;
   std::mutex run_mu_;
 };

@@ -89,12 +89,28 @@ class DecoderRunner:
         self._ensure_decode_binding()
         if tokens is not None:
             self.step_ids.copy_(tokens, non_blocking=True)
+        else:
+            self.step_ids.copy_(self.step_next)
         self.step_seqlens.fill_(self.cur_len)  # total length - 1 after appending this token
         self.sess.run_with_iobinding(self._decode_binding, self._ro_decode)
         self.cur_len += 1
         if not self.has_argmax:
             self.step_next.copy_(self.step_logits.float().argmax(-1))
         return self.step_next
+
+    def decode_step_host(self, ids_pinned: torch.Tensor, seqlens_pinned: torch.Tensor, out_pinned: torch.Tensor) -> None:
+        """One decode step driven from the host: inputs come from pinned host memory, the sampled tokens are
+        copied back to pinned host memory and the call returns after they have arrived."""
+        self._ensure_decode_binding()
+        seqlens_pinned.fill_(self.cur_len)
+        self.step_ids.copy_(ids_pinned, non_blocking=True)
+        self.step_seqlens.copy_(seqlens_pinned, non_blocking=True)
+        self.sess.run_with_iobinding(self._decode_binding, self._ro_decode)
+        self.cur_len += 1
+        if not self.has_argmax:
+            self.step_next.copy_(self.step_logits.float().argmax(-1))
+        out_pinned.copy_(self.step_next, non_blocking=True)
+        torch.cuda.current_stream().synchronize() if self.device.type == "cuda" else None
 
     def generate(self, input_ids: torch.Tensor, max_new_tokens: int) -> torch.Tensor:
         out = [self.prefill(input_ids).clone()]

@@ -16,7 +16,8 @@ def test_llama_gpu_matches_cpu(head_dim, use_graph):
                            num_kv_heads=2, max_seq_len=256)
     model, _ = build_llama(cfg, weight_std=0.05)
     cpu = ort.InferenceSession(model, providers=["CPUExecutionProvider"])
-    gpu = ort.InferenceSession(model, providers=[("CUDAExecutionProvider", {"enable_cuda_graph": "1" if use_graph else "0"})])
+    gpu = ort.InferenceSession(model, providers=[("CUDAExecutionProvider", {"enable_cuda_graph": "1" if use_graph else "0"})],
+                               enable_fallback=False)
     ops = {n["op_type"] for n in gpu.graph_nodes()}
     assert "GemmSwiGLU" in ops and "FusedGemm" not in ops or True
     eps = {n["ep"] for n in gpu.graph_nodes()}
