@@ -4,6 +4,8 @@
 #include <c10/cuda/CUDAGuard.h>
 
 #include <algorithm>
+#include <sstream>
+#include <cuda_runtime_api.h>
 
 namespace ortb {
 
@@ -380,8 +382,8 @@ void GraphExecutor::Build() {
 }
 
 void GraphExecutor::ExecuteSteps(const RunOptions& ro, std::vector<Value>& slots) {
-  Profiler* prof = nullptr;
-  (void)prof;
+  Profiler* prof = session_->profiler().enabled() ? &session_->profiler() : nullptr;
+  int node_index = 0;
   std::vector<Value> in, out;
   const std::map<std::string, Value>* outer = current_outer_;
   OpKernelContext::Lookup lookup = [this, &slots, outer](const std::string& name) -> Value {
@@ -410,8 +412,27 @@ void GraphExecutor::ExecuteSteps(const RunOptions& ro, std::vector<Value>& slots
     OpKernelContext ctx(*st.node, session_, st.device, in, out, st.out_needed);
     ctx.set_lookup(&lookup);
     ctx.run_options = &ro;
+    const int64_t t_node0 = prof ? prof->NowUs() : 0;
     try {
       st.kernel->Compute(ctx);
+      if (prof) {
+        // per-node durations need the node's GPU work to have finished (profiling mode only)
+        if (st.on_gpu && at::cuda::currentStreamCaptureStatusMayInitCtx() == c10::cuda::CaptureStatus::None) cudaStreamSynchronize(at::cuda::getCurrentCUDAStream(st.device.index()).stream());
+        std::map<std::string, std::string> args;
+        args["op_name"] = st.node->op_type;
+        args["provider"] = st.node->ep.empty() ? kCpuEP : st.node->ep;
+        args["node_index"] = std::to_string(node_index);
+        std::string shapes;
+        for (auto& v : in)
+          if (v.t.defined()) {
+            std::ostringstream ss;
+            ss << v.t.sizes();
+            shapes += ss.str() + " ";
+          }
+        args["input_type_shape"] = shapes;
+        prof->Record("Node", st.node->name + "_kernel_time", t_node0, prof->NowUs() - t_node0, std::move(args));
+      }
+      ++node_index;
     } catch (const OrtError&) {
       throw;
     } catch (const std::exception& e) {

@@ -9,6 +9,7 @@
 #include <cmath>
 #include <limits>
 
+#include "collective.h"
 #include "contrib_math.h"
 #include "kernel.h"
 
@@ -730,6 +731,26 @@ void RegisterContribKernels(KernelRegistry& r) {
                                   ctx.RequiredInput(2).to(at::kFloat), ctx.node().attr_f("epsilon", 1e-5f), false);
     if (ctx.node().attr_i("activation", 0) == 1) y = y * at::sigmoid(y);
     ctx.SetOutput(0, y.permute({0, 2, 3, 1}).contiguous().to(x.scalar_type()));
+  });
+  // com.ortb200: ops the GPU lowering passes create; these ATen versions keep an optimized model loadable anywhere
+  r.RegisterFn("com.ortb200", "FusedGemm", 1, kMax, [](Ctx& ctx) {
+    const Node& n = ctx.node();
+    at::Tensor y = at::matmul(ctx.RequiredInput(0), ctx.RequiredInput(1));
+    if (ctx.HasInput(2)) y = y + ctx.Input(2);
+    const std::string act = n.attr_s("activation", "none");
+    if (act == "gelu") y = at::gelu(y);
+    else if (act == "fastgelu") y = at::gelu(y, "tanh");
+    else if (act == "relu") y = at::relu(y);
+    else if (act == "silu") y = at::silu(y);
+    else if (act == "quickgelu") y = y * at::sigmoid(y * 1.702);
+    else if (act != "none") ORTB_THROW(INVALID_ARGUMENT, "FusedGemm: unknown activation ", act);
+    if (n.attr_i("all_reduce", 0)) y = AllReduceSum(ctx.session(), y);
+    if (ctx.HasInput(3)) y = y + ctx.Input(3);
+    ctx.SetOutput(0, y);
+  });
+  r.RegisterFn("com.ortb200", "GemmSwiGLU", 1, kMax, [](Ctx& ctx) {
+    const at::Tensor& x = ctx.RequiredInput(0);
+    ctx.SetOutput(0, at::silu(at::matmul(x, ctx.RequiredInput(1))) * at::matmul(x, ctx.RequiredInput(2)));
   });
   r.RegisterFn(MS, "GatherBlockQuantized", 1, kMax, [](Ctx& ctx) {
     const Node& n = ctx.node();

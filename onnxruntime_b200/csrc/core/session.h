@@ -132,6 +132,7 @@ class InferenceSession {
   const ConfigOptions& config() const { return so_.config; }
   // per-node provider assignment: (node name, op type, provider)
   std::vector<std::tuple<std::string, std::string, std::string>> NodeAssignments() const;
+  Profiler& profiler() { return profiler_; }
   int NumCapturedGraphs() const { return static_cast<int>(cuda_graphs_.size()); }
   int64_t KernelLaunchCount() const { return launch_count_; }
   // launches issued by the most recent execution of the step list (eager run or graph capture)

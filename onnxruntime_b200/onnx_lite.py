@@ -243,7 +243,8 @@ def make_tensor(name: str, array, data_type: Optional[int] = None) -> Tensor:
         dt = data_type if data_type is not None else tmap[t.dtype]
         raw = t.view(torch.uint8).numpy().tobytes() if t.numel() else b""
         return Tensor(name, dt, tuple(t.shape), raw)
-    arr = np.ascontiguousarray(array)
+    arr = np.asarray(array)
+    arr = np.ascontiguousarray(arr).reshape(arr.shape)  # ascontiguousarray promotes 0-d arrays to 1-d
     dt = data_type if data_type is not None else np_dtype_to_onnx(arr.dtype)
     return Tensor(name, dt, tuple(arr.shape), arr.tobytes())
 

@@ -1,0 +1,210 @@
+"""Graph optimizer: each fusion is checked by op counts before/after AND by numerical equivalence of the
+optimized and unoptimized sessions (the approach of the reference's TransformerTester,
+onnxruntime/test/optimizer/graph_transform_test.cc)."""
+import math
+
+import numpy as np
+import pytest
+
+import onnxruntime_b200 as ort
+from onnxruntime_b200 import _core as C
+from onnxruntime_b200 import onnx_lite as ol
+from helpers import graph_model, op_counts
+
+T = ol.TensorProto
+rng = np.random.RandomState(0)
+
+
+def both(model, feeds, disabled=()):
+    so = ort.SessionOptions()
+    so.graph_optimization_level = ort.GraphOptimizationLevel.ORT_DISABLE_ALL
+    ref = ort.InferenceSession(model, so, providers=["CPUExecutionProvider"])
+    opt = ort.InferenceSession(model, providers=["CPUExecutionProvider"], disabled_optimizers=list(disabled))
+    a, b = ref.run(None, feeds), opt.run(None, feeds)
+    for x, y in zip(a, b):
+        np.testing.assert_allclose(x, y, rtol=2e-5, atol=2e-6)
+    return op_counts(ref), op_counts(opt)
+
+
+def c(name, value, dtype=np.float32):
+    return ol.make_tensor(name, np.asarray(value, dtype=dtype))
+
+
+X = [ol.make_tensor_value_info("x", T.FLOAT, ["b", 8, 16])]
+Y = [ol.make_tensor_value_info("y", T.FLOAT, None)]
+xs = {"x": rng.randn(2, 8, 16).astype(np.float32)}
+
+
+def test_identity_dropout_noop_elimination():
+    nodes = [ol.make_node("Identity", ["x"], ["a"]), ol.make_node("Dropout", ["a"], ["b"]),
+             ol.make_node("Add", ["b", "zero"], ["c"]), ol.make_node("Mul", ["c", "one"], ["d"]), ol.make_node("Relu", ["d"], ["y"])]
+    before, after = both(graph_model(nodes, X, Y, [c("zero", 0.0), c("one", 1.0)]), xs)
+    assert after == {"Relu": 1}
+
+
+def test_constant_folding_and_cse():
+    nodes = [ol.make_node("Add", ["k1", "k2"], ["k3"]), ol.make_node("Mul", ["x", "k3"], ["a"]),
+             ol.make_node("Mul", ["x", "k3"], ["b"]), ol.make_node("Add", ["a", "b"], ["y"]),
+             ol.make_node("Constant", [], ["unused"], value=np.ones(2, np.float32))]
+    before, after = both(graph_model(nodes, X, Y, [c("k1", [1.0] * 16), c("k2", [2.0] * 16)]), xs)
+    assert before["Mul"] == 2 and after == {"Mul": 1, "Add": 1}
+    # disabling a pass by name keeps its pattern
+    _, kept = both(graph_model(nodes, X, Y, [c("k1", [1.0] * 16), c("k2", [2.0] * 16)]), xs,
+                   disabled=["CommonSubexpressionElimination"])
+    assert kept["Mul"] == 2
+
+
+def test_shape_chain_folds_with_static_initializer():
+    nodes = [ol.make_node("Shape", ["w"], ["s"]), ol.make_node("Gather", ["s", "i0"], ["d"], axis=0),
+             ol.make_node("Unsqueeze", ["d", "ax"], ["d1"]), ol.make_node("Concat", ["m1", "d1"], ["shape"], axis=0),
+             ol.make_node("Reshape", ["x", "shape"], ["y"])]
+    inits = [c("w", np.zeros((16, 4))), c("i0", 0, np.int64), c("ax", [0], np.int64), c("m1", [-1], np.int64)]
+    before, after = both(graph_model(nodes, X, Y, inits), xs)
+    assert after == {"Reshape": 1}
+
+
+@pytest.mark.parametrize("form", [0, 1, 2])
+def test_gelu_fusion(form):
+    e = [ol.make_node("Div", ["x", "sqrt2"], ["d"]), ol.make_node("Erf", ["d"], ["e"]), ol.make_node("Add", ["e", "one"], ["p"])]
+    if form == 0:
+        tail = [ol.make_node("Mul", ["x", "p"], ["m"]), ol.make_node("Mul", ["m", "half"], ["y"])]
+    elif form == 1:
+        tail = [ol.make_node("Mul", ["x", "half"], ["m"]), ol.make_node("Mul", ["m", "p"], ["y"])]
+    else:
+        tail = [ol.make_node("Mul", ["half", "p"], ["m"]), ol.make_node("Mul", ["x", "m"], ["y"])]
+    before, after = both(graph_model(e + tail, X, Y, [c("sqrt2", math.sqrt(2)), c("one", 1.0), c("half", 0.5)]), xs)
+    assert after == {"Gelu": 1}
+
+
+@pytest.mark.parametrize("form", [0, 1])
+def test_fast_gelu_fusion(form):
+    k0 = math.sqrt(2 / math.pi)
+    if form == 0:
+        inner = [ol.make_node("Pow", ["x", "three"], ["x3"]), ol.make_node("Mul", ["k1", "x3"], ["a"]),
+                 ol.make_node("Add", ["x", "a"], ["b"]), ol.make_node("Mul", ["k0", "b"], ["inner"])]
+    else:
+        inner = [ol.make_node("Mul", ["x", "x"], ["x2"]), ol.make_node("Mul", ["k1", "x2"], ["a"]),
+                 ol.make_node("Add", ["one", "a"], ["b"]), ol.make_node("Mul", ["x", "k0"], ["xk"]),
+                 ol.make_node("Mul", ["xk", "b"], ["inner"])]
+    tail = [ol.make_node("Tanh", ["inner"], ["t"]), ol.make_node("Add", ["one", "t"], ["p"]),
+            ol.make_node("Mul", ["x", "half"], ["h"]), ol.make_node("Mul", ["h", "p"], ["y"])]
+    inits = [c("three", 3.0), c("k1", 0.044715), c("k0", k0), c("one", 1.0), c("half", 0.5)]
+    before, after = both(graph_model(inner + tail, X, Y, inits), xs)
+    assert after == {"FastGelu": 1}
+
+
+def _layernorm_nodes(src, out, dup_sub=False):
+    n = [ol.make_node("ReduceMean", [src], ["mu"], axes=[-1]), ol.make_node("Sub", [src, "mu"], ["d"])]
+    d2 = "d"
+    if dup_sub:
+        n.append(ol.make_node("Sub", [src, "mu"], ["d_b"]))
+        d2 = "d_b"
+    n += [ol.make_node("Pow", [d2, "two"], ["sq"]), ol.make_node("ReduceMean", ["sq"], ["var"], axes=[-1]),
+          ol.make_node("Add", ["var", "eps"], ["ve"]), ol.make_node("Sqrt", ["ve"], ["sd"]), ol.make_node("Div", ["d", "sd"], ["nrm"]),
+          ol.make_node("Mul", ["nrm", "gamma"], ["sc"]), ol.make_node("Add", ["sc", "beta"], [out])]
+    return n
+
+
+LN_INITS = [c("two", 2.0), c("eps", 1e-5), c("gamma", rng.randn(16)), c("beta", rng.randn(16))]
+
+
+@pytest.mark.parametrize("dup_sub", [False, True])
+def test_layernorm_fusion(dup_sub):
+    before, after = both(graph_model(_layernorm_nodes("x", "y", dup_sub), X, Y, LN_INITS), xs)
+    assert after == {"LayerNormalization": 1}
+
+
+def test_layernorm_not_fused_when_interior_value_escapes():
+    nodes = _layernorm_nodes("x", "y0") + [ol.make_node("Add", ["y0", "var"], ["y"])]
+    before, after = both(graph_model(nodes, X, Y, LN_INITS), xs)
+    assert "LayerNormalization" not in after
+
+
+@pytest.mark.parametrize("form", ["div", "recip_mul", "cast"])
+def test_simplified_layernorm_fusion(form):
+    n = [ol.make_node("Pow", ["x", "two"], ["sq"]), ol.make_node("ReduceMean", ["sq"], ["ms"], axes=[-1]),
+         ol.make_node("Add", ["ms", "eps"], ["ve"]), ol.make_node("Sqrt", ["ve"], ["rms"])]
+    if form == "div":
+        n += [ol.make_node("Div", ["x", "rms"], ["nrm"]), ol.make_node("Mul", ["nrm", "gamma"], ["y"])]
+    elif form == "recip_mul":
+        n += [ol.make_node("Div", ["one", "rms"], ["inv"]), ol.make_node("Mul", ["x", "inv"], ["nrm"]),
+              ol.make_node("Mul", ["gamma", "nrm"], ["y"])]
+    else:
+        n += [ol.make_node("Div", ["x", "rms"], ["nrm"]), ol.make_node("Cast", ["nrm"], ["nc"], to=T.FLOAT),
+              ol.make_node("Mul", ["nc", "gamma"], ["y"])]
+    before, after = both(graph_model(n, X, Y, LN_INITS + [c("one", 1.0)]), xs)
+    assert after == {"SimplifiedLayerNormalization": 1}
+
+
+def test_skip_layernorm_and_bias_gelu_fusion():
+    # (x @ W + b) -> gelu ; residual add -> layernorm, with the sum consumed twice
+    W, b = rng.randn(16, 16).astype(np.float32), rng.randn(16).astype(np.float32)
+    nodes = [ol.make_node("MatMul", ["x", "W"], ["mm"]), ol.make_node("Add", ["mm", "b"], ["mb"]),
+             ol.make_node("Gelu", ["mb"], ["g"], domain="com.microsoft"),
+             ol.make_node("Add", ["g", "x"], ["sum"]),
+             ol.make_node("LayerNormalization", ["sum", "gamma", "beta"], ["ln"], axis=-1, epsilon=1e-5),
+             ol.make_node("Add", ["ln", "sum"], ["y"])]
+    before, after = both(graph_model(nodes, X, Y, LN_INITS + [c("W", W), c("b", b)]), xs)
+    assert after.get("SkipLayerNormalization") == 1 and after.get("BiasGelu") == 1 and "LayerNormalization" not in after
+    # bias feeding the residual add is absorbed as the SkipLayerNorm bias input
+    nodes = [ol.make_node("MatMul", ["x", "W"], ["mm"]), ol.make_node("Add", ["mm", "b"], ["mb"]), ol.make_node("Add", ["mb", "x"], ["sum"]),
+             ol.make_node("SimplifiedLayerNormalization", ["sum", "gamma"], ["y"], axis=-1, epsilon=1e-5)]
+    before, after = both(graph_model(nodes, X, Y, LN_INITS + [c("W", W), c("b", b)]), xs)
+    assert after == {"MatMul": 1, "SkipSimplifiedLayerNormalization": 1}
+
+
+def test_bert_fusions_end_to_end():
+    from onnxruntime_b200.models.bert import BertConfig, build_bert, init_weights, reference_forward
+    cfg = BertConfig(type_vocab_size=2)
+    w = init_weights(cfg, 0)
+    model = build_bert(cfg, w)
+    ids = rng.randint(0, cfg.vocab_size, (2, 32)).astype(np.int64)
+    mask = np.ones((2, 32), np.int64)
+    mask[1, 25:] = 0
+    tt = rng.randint(0, 2, (2, 32)).astype(np.int64)
+    feeds = {"input_ids": ids, "attention_mask": mask, "token_type_ids": tt}
+    before, after = both(model, feeds)
+    assert after["Attention"] == cfg.num_layers and after["SkipLayerNormalization"] == 2 * cfg.num_layers
+    assert after["BiasGelu"] == cfg.num_layers and after["EmbedLayerNormalization"] == 1
+    assert "Softmax" not in after and "Erf" not in after and sum(after.values()) < sum(before.values()) // 4
+    s = ort.InferenceSession(model, providers=["CPUExecutionProvider"])
+    out = s.run(None, feeds)[0]
+    ref = reference_forward(cfg, w, ids, mask, tt)
+    valid = mask.astype(bool)
+    np.testing.assert_allclose(out[valid], ref[valid], rtol=1e-4, atol=2e-5)
+
+
+def test_conv_batchnorm_fusion():
+    x = rng.randn(1, 3, 8, 8).astype(np.float32)
+    inits = [c("w", rng.randn(4, 3, 3, 3)), c("s", rng.rand(4) + 0.5), c("b", rng.randn(4)), c("m", rng.randn(4)), c("v", rng.rand(4) + 0.5)]
+    nodes = [ol.make_node("Conv", ["x", "w"], ["cv"], kernel_shape=[3, 3]), ol.make_node("BatchNormalization", ["cv", "s", "b", "m", "v"], ["y"])]
+    model = graph_model(nodes, [ol.make_tensor_value_info("x", T.FLOAT, [1, 3, 8, 8])], Y, inits)
+    so = ort.SessionOptions()
+    so.graph_optimization_level = ort.GraphOptimizationLevel.ORT_DISABLE_ALL
+    a = ort.InferenceSession(model, so, providers=["CPUExecutionProvider"]).run(None, {"x": x})[0]
+    opt = ort.InferenceSession(model, providers=["CPUExecutionProvider"])
+    np.testing.assert_allclose(opt.run(None, {"x": x})[0], a, rtol=1e-4, atol=1e-4)
+    assert op_counts(opt) == {"Conv": 1}
+
+
+def test_gpu_lowering_passes_on_graph_level():
+    """The GPU-only passes are pure graph rewrites, so their structure can be checked without a GPU."""
+    import torch
+    W1, W2, W3 = (torch.randn(64, 128) * 0.05).half(), (torch.randn(64, 128) * 0.05).half(), (torch.randn(128, 64) * 0.05).half()
+    bias = torch.randn(64).half()
+    nodes = [ol.make_node("MatMul", ["x", "Wg"], ["g"]), ol.make_node("MatMul", ["x", "Wu"], ["u"]),
+             ol.make_node("Sigmoid", ["g"], ["sg"]), ol.make_node("Mul", ["g", "sg"], ["act"]), ol.make_node("Mul", ["act", "u"], ["h"]),
+             ol.make_node("MatMul", ["h", "Wd"], ["d"]), ol.make_node("Add", ["d", "bias"], ["db"]),
+             ol.make_node("FastGelu", ["db"], ["fg"], domain="com.microsoft"), ol.make_node("Add", ["fg", "x"], ["y"])]
+    model = graph_model(nodes, [ol.make_tensor_value_info("x", T.FLOAT16, ["b", 64])], [ol.make_tensor_value_info("y", T.FLOAT16, ["b", 64])],
+                        [ol.make_tensor("Wg", W1), ol.make_tensor("Wu", W2), ol.make_tensor("Wd", W3), ol.make_tensor("bias", bias)])
+    out, stats = C.optimize_model(model, 99, [], True)
+    ops = [(n["op_type"], n["domain"]) for n in C.model_nodes(out)]
+    assert ops == [("GemmSwiGLU", "com.ortb200"), ("FusedGemm", "com.ortb200")]
+    fused = C.model_nodes(out)[1]
+    assert fused["attrs"]["activation"] == b"fastgelu" and len(fused["inputs"]) == 4
+    # the fused ops also run on the CPU provider (ATen reference kernels), so the rewrite can be verified numerically
+    x = (torch.randn(3, 64) * 0.5).half().numpy()
+    a = ort.InferenceSession(model, providers=["CPUExecutionProvider"]).run(None, {"x": x})[0]
+    b = ort.InferenceSession(out, providers=["CPUExecutionProvider"]).run(None, {"x": x})[0]
+    np.testing.assert_allclose(a.astype(np.float32), b.astype(np.float32), rtol=2e-2, atol=2e-2)

@@ -1,0 +1,212 @@
+"""Python API contract: InferenceSession / SessionOptions / RunOptions / IOBinding / OrtValue."""
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import onnxruntime_b200 as ort
+from onnxruntime_b200 import onnx_lite as ol
+from helpers import graph_model
+
+T = ol.TensorProto
+
+
+def _model(dynamic=True):
+    w = np.arange(12, dtype=np.float32).reshape(4, 3)
+    return graph_model([ol.make_node("MatMul", ["x", "w"], ["y0"]), ol.make_node("Relu", ["y0"], ["y"]),
+                        ol.make_node("ReduceSum", ["y0"], ["s"], keepdims=0)],
+                       [ol.make_tensor_value_info("x", T.FLOAT, ["batch" if dynamic else 2, 4])],
+                       [ol.make_tensor_value_info("y", T.FLOAT, ["batch" if dynamic else 2, 3]), ol.make_tensor_value_info("s", T.FLOAT, [])],
+                       [ol.make_tensor("w", w)], opset=12), w
+
+
+def test_run_and_metadata():
+    m, w = _model()
+    s = ort.InferenceSession(m, providers=["CPUExecutionProvider"])
+    assert [i.name for i in s.get_inputs()] == ["x"]
+    assert [o.name for o in s.get_outputs()] == ["y", "s"]
+    assert s.get_inputs()[0].type == "tensor(float)" and s.get_inputs()[0].shape == ["batch", 4]
+    assert s.get_providers() == ["CPUExecutionProvider"]
+    assert "CPUExecutionProvider" in s.get_provider_options()
+    x = np.random.RandomState(0).randn(5, 4).astype(np.float32)
+    y, total = s.run(None, {"x": x})
+    np.testing.assert_allclose(y, np.maximum(x @ w, 0), rtol=1e-5, atol=1e-5)
+    only = s.run(["s"], {"x": x})
+    assert len(only) == 1 and only[0] == pytest.approx((x @ w).sum(), rel=1e-4)
+    vals = s.run_with_ort_values(["y"], {"x": ort.OrtValue.ortvalue_from_numpy(x)})
+    assert isinstance(vals[0], ort.OrtValue) and vals[0].shape() == [5, 3] and vals[0].data_type() == "tensor(float)"
+    assert vals[0].device_name() == "cpu"
+
+
+def test_input_validation_errors():
+    m, _ = _model(dynamic=False)
+    s = ort.InferenceSession(m, providers=["CPUExecutionProvider"])
+    with pytest.raises(ValueError):
+        s.run(None, {})
+    with pytest.raises(ort.InvalidArgument, match="Unexpected input data type"):
+        s.run(None, {"x": np.zeros((2, 4), np.float64)})
+    with pytest.raises(ort.InvalidArgument, match="Invalid rank"):
+        s.run(None, {"x": np.zeros((2, 4, 1), np.float32)})
+    with pytest.raises(ort.InvalidArgument, match="invalid dimensions"):
+        s.run(None, {"x": np.zeros((3, 4), np.float32)})
+    with pytest.raises(ort.InvalidArgument, match="Invalid output name"):
+        s.run(["nope"], {"x": np.zeros((2, 4), np.float32)})
+    with pytest.raises(ort.InvalidArgument):
+        s.run(None, {"x": np.zeros((2, 4), np.float32), "zzz": np.zeros(1, np.float32)})
+
+
+def test_load_errors_and_providers(tmp_path):
+    with pytest.raises(ort.NoSuchFile):
+        ort.InferenceSession(str(tmp_path / "missing.onnx"), providers=["CPUExecutionProvider"])
+    m, _ = _model()
+    with pytest.raises(ValueError):
+        ort.InferenceSession(m, providers=["NoSuchExecutionProvider"])
+    with pytest.raises(ValueError):
+        ort.InferenceSession(m, providers="CPUExecutionProvider")
+    assert ort.get_all_providers()[-1] == "CPUExecutionProvider"
+    assert "CPUExecutionProvider" in ort.get_available_providers()
+    assert ort.get_device() in ("CPU", "GPU")
+    # requesting the GPU provider on a machine without one falls back to the CPU provider
+    if not torch.cuda.is_available():
+        s = ort.InferenceSession(m, providers=["CUDAExecutionProvider", "CPUExecutionProvider"])
+        assert s.get_providers() == ["CPUExecutionProvider"]
+    bad = graph_model([ol.make_node("NoSuchOp", ["x"], ["y"])], [ol.make_tensor_value_info("x", T.FLOAT, [1])],
+                      [ol.make_tensor_value_info("y", T.FLOAT, [1])])
+    with pytest.raises(ort.NotImplemented, match="NoSuchOp"):
+        ort.InferenceSession(bad, providers=["CPUExecutionProvider"])
+    cyc = graph_model([ol.make_node("Relu", ["b"], ["a"]), ol.make_node("Relu", ["a"], ["b"])], [], [ol.make_tensor_value_info("b", T.FLOAT, [1])])
+    with pytest.raises(ort.InvalidGraph):
+        ort.InferenceSession(cyc, providers=["CPUExecutionProvider"])
+
+
+def test_session_options_and_config_entries(tmp_path):
+    so = ort.SessionOptions()
+    assert so.graph_optimization_level == ort.GraphOptimizationLevel.ORT_ENABLE_ALL
+    so.graph_optimization_level = ort.GraphOptimizationLevel.ORT_ENABLE_BASIC
+    assert so.graph_optimization_level == ort.GraphOptimizationLevel.ORT_ENABLE_BASIC
+    so.execution_mode = ort.ExecutionMode.ORT_PARALLEL
+    assert so.execution_mode == ort.ExecutionMode.ORT_PARALLEL
+    so.intra_op_num_threads = 2
+    so.log_severity_level = 3
+    assert so.intra_op_num_threads == 2 and so.log_severity_level == 3
+    so.add_session_config_entry("session.disable_prepacking", "1")
+    assert so.get_session_config_entry("session.disable_prepacking") == "1"
+    with pytest.raises(ort.RuntimeException):
+        so.get_session_config_entry("missing.key")
+    with pytest.raises(AttributeError):
+        so.no_such_option = 1
+    so.optimized_model_filepath = str(tmp_path / "opt.onnx")
+    m, w = _model()
+    s = ort.InferenceSession(m, so, providers=["CPUExecutionProvider"])
+    assert os.path.exists(so.optimized_model_filepath)
+    s2 = ort.InferenceSession(so.optimized_model_filepath, providers=["CPUExecutionProvider"])
+    x = np.ones((1, 4), np.float32)
+    np.testing.assert_allclose(s.run(["y"], {"x": x})[0], s2.run(["y"], {"x": x})[0])
+    ro = ort.RunOptions()
+    ro.add_run_config_entry("gpu_graph_id", "3")
+    assert ro.get_run_config_entry("gpu_graph_id") == "3"
+    ro.terminate = True
+    with pytest.raises(ort.Fail, match="terminate"):
+        s.run(None, {"x": x}, ro)
+
+
+def test_free_dimension_override_and_add_initializer():
+    m, w = _model()
+    so = ort.SessionOptions()
+    so.add_free_dimension_override_by_name("batch", 2)
+    s = ort.InferenceSession(m, so, providers=["CPUExecutionProvider"])
+    assert s.get_inputs()[0].shape == [2, 4]
+    with pytest.raises(ort.InvalidArgument):
+        s.run(None, {"x": np.zeros((3, 4), np.float32)})
+    so2 = ort.SessionOptions()
+    so2.add_initializer("w", ort.OrtValue.ortvalue_from_numpy(np.ones((4, 3), np.float32)))
+    s2 = ort.InferenceSession(m, so2, providers=["CPUExecutionProvider"])
+    np.testing.assert_allclose(s2.run(["y"], {"x": np.ones((1, 4), np.float32)})[0], np.full((1, 3), 4.0))
+
+
+def test_overridable_initializer():
+    g = graph_model([ol.make_node("Add", ["x", "b"], ["y"])],
+                    [ol.make_tensor_value_info("x", T.FLOAT, [2]), ol.make_tensor_value_info("b", T.FLOAT, [2])],
+                    [ol.make_tensor_value_info("y", T.FLOAT, [2])], [ol.make_tensor("b", np.array([1, 2], np.float32))])
+    s = ort.InferenceSession(g, providers=["CPUExecutionProvider"])
+    assert [i.name for i in s.get_inputs()] == ["x"]
+    assert [i.name for i in s.get_overridable_initializers()] == ["b"]
+    x = np.zeros(2, np.float32)
+    np.testing.assert_array_equal(s.run(None, {"x": x})[0], [1, 2])
+    np.testing.assert_array_equal(s.run(None, {"x": x, "b": np.array([5, 5], np.float32)})[0], [5, 5])
+
+
+def test_iobinding_cpu():
+    m, w = _model()
+    s = ort.InferenceSession(m, providers=["CPUExecutionProvider"])
+    x = np.random.RandomState(1).randn(3, 4).astype(np.float32)
+    b = s.io_binding()
+    b.bind_cpu_input("x", x)
+    b.bind_output("y")
+    out_s = ort.OrtValue.ortvalue_from_shape_and_type([], np.float32)
+    b.bind_ortvalue_output("s", out_s)
+    b.synchronize_inputs()
+    s.run_with_iobinding(b)
+    b.synchronize_outputs()
+    outs = b.copy_outputs_to_cpu()
+    np.testing.assert_allclose(outs[0], np.maximum(x @ w, 0), rtol=1e-5, atol=1e-5)
+    assert out_s.numpy() == pytest.approx((x @ w).sum(), rel=1e-4)
+    # bind by raw pointer
+    buf = np.zeros((3, 3), np.float32)
+    b2 = s.io_binding()
+    b2.bind_input("x", "cpu", 0, np.float32, x.shape, x.ctypes.data)
+    b2.bind_output("y", "cpu", 0, np.float32, buf.shape, buf.ctypes.data)
+    s.run_with_iobinding(b2)
+    np.testing.assert_allclose(buf, np.maximum(x @ w, 0), rtol=1e-5, atol=1e-5)
+    with pytest.raises(ort.InvalidArgument):
+        b2.bind_cpu_input("nope", x)
+    b2.clear_binding_inputs()
+    b2.clear_binding_outputs()
+
+
+def test_ortvalue():
+    a = np.arange(6, dtype=np.float32).reshape(2, 3)
+    v = ort.OrtValue.ortvalue_from_numpy(a)
+    assert v.shape() == [2, 3] and v.is_tensor() and v.has_value() and v.element_type() == 1
+    np.testing.assert_array_equal(v.numpy(), a)
+    doubled = a * 2
+    v.update_inplace(doubled)  # the OrtValue shares memory with `a`
+    np.testing.assert_array_equal(v.numpy(), doubled)
+    back = ort.OrtValue.from_dlpack(v.to_dlpack())
+    np.testing.assert_array_equal(back.numpy(), doubled)
+    z = ort.OrtValue.ortvalue_from_shape_and_type([4], np.int64)
+    assert z.data_type() == "tensor(int64)" and z.data_ptr() != 0
+
+
+def test_profiling(tmp_path):
+    m, _ = _model()
+    so = ort.SessionOptions()
+    so.enable_profiling = True
+    so.profile_file_prefix = str(tmp_path / "prof")
+    s = ort.InferenceSession(m, so, providers=["CPUExecutionProvider"])
+    s.run(None, {"x": np.ones((1, 4), np.float32)})
+    path = s.end_profiling()
+    assert path.startswith(str(tmp_path / "prof")) and path.endswith(".json")
+    events = json.load(open(path))
+    names = [e["name"] for e in events]
+    assert "model_run" in names and "session_initialization" in names
+    assert all({"cat", "pid", "tid", "dur", "ts", "ph", "name", "args"} <= set(e) for e in events)
+    node_events = [e for e in events if e["cat"] == "Node"]
+    assert any(e["name"].endswith("_kernel_time") and e["args"].get("op_name") == "MatMul" for e in node_events)
+
+
+def test_run_async_and_disabled_optimizers():
+    import threading
+    m, w = _model()
+    s = ort.InferenceSession(m, providers=["CPUExecutionProvider"], disabled_optimizers=["ConstantFolding"])
+    done = threading.Event()
+    box = {}
+
+    def cb(res, user, err):
+        box["res"], box["user"], box["err"] = res, user, err
+        done.set()
+    s.run_async(None, {"x": np.ones((1, 4), np.float32)}, cb, "tag")
+    assert done.wait(10) and box["user"] == "tag" and box["err"] == ""
+    np.testing.assert_allclose(box["res"][0], np.maximum(np.ones((1, 4), np.float32) @ w, 0))
