@@ -138,6 +138,8 @@ class EmbeddingGatherKernel final : public WithFallback {
 };
 
 class ArgMaxKernel final : public WithFallback {
+  mutable at::Tensor ws_;  // per-row merge slots + counters, kept zero between launches
+
  public:
   explicit ArgMaxKernel(const OpKernelInfo& info) : WithFallback(info) {}
   void Compute(Ctx& ctx) const override {
@@ -154,7 +156,11 @@ class ArgMaxKernel final : public WithFallback {
     if (node_.attr_i("keepdims", 1)) shape.back() = 1;
     else shape.pop_back();
     at::Tensor out = at::empty(shape, x.options().dtype(at::kLong));
-    CheckLaunch(ortb200_argmax(xc.data_ptr(), out.data_ptr<int64_t>(), xc.numel() / x.size(-1), x.size(-1), dt, ctx.cuda_stream()),
+    const int64_t rows = xc.numel() / x.size(-1);
+    if (!ws_.defined() || ws_.numel() < rows * 16 || ws_.device() != x.device())
+      ws_ = at::zeros({std::max<int64_t>(rows, 64) * 16}, x.options().dtype(at::kByte));
+    CheckLaunch(ortb200_argmax(xc.data_ptr(), out.data_ptr<int64_t>(), rows, x.size(-1), dt, ws_.data_ptr(), ws_.numel(),
+                               ctx.cuda_stream()),
                 "ortb200_argmax");
     ctx.session()->AddLaunches(1);
     ctx.SetOutput(0, out);
@@ -340,7 +346,8 @@ class GqaKernel final : public WithFallback {
       da.scale = scale_;
       da.softcap = softcap_;
       da.dtype = dt;
-      da.use_pdl = 0;
+      da.use_pdl = ctx.session()->config().Get("ortb200.pdl", "0") == "1" ? 1 : 0;
+      da.status = ctx.session()->StatusWord().data_ptr<int>();
       CheckLaunch(ortb200_gqa_decode(&da, ctx.cuda_stream()), "ortb200_gqa_decode");
       ctx.session()->AddLaunches(1);
     } else {

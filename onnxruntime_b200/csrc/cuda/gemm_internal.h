@@ -1,0 +1,27 @@
+// Internal interface between the GEMM dispatcher (gemm_tcgen05.cu) and the decode-shaped kernel (gemm_smallm.cu).
+#pragma once
+#include <cuda_runtime.h>
+#include "ortb200_kernels.h"
+
+namespace ortb200 {
+
+struct SmallGemmParams {
+  int M, N, K;
+  int num_kb;
+  int cluster;       // CTAs per cluster == split-K factor
+  int dual_offset;
+  int dtype;
+  int act;
+  float alpha;
+  void* out;
+  long long ldo;
+  const void* bias;
+  const void* residual;
+  long long ldr;
+  int* status;
+};
+
+// bn in {16, 32, 64}.  Returns 0 or a negative launch error; reports the cluster size and pipeline depth used.
+int launch_gemm_smallm(const ortb200_gemm_args* a, int bn, cudaStream_t stream, int* cluster_out, int* stages_out);
+
+}  // namespace ortb200

@@ -1,0 +1,349 @@
+// Decode-shaped GEMM (M <= 64 tokens) for sm_100a: the weight matrix is streamed
+// once at HBM speed through TMA into tcgen05.mma, and split-K partial tiles are
+// combined inside a thread-block cluster through distributed shared memory.
+//
+//   out[M, N] = act(alpha * X[M,K] * W[N,K]^T + bias) + residual
+//
+// A cluster of C CTAs (C = 1, 2, 4 or 8) owns one 128-row weight tile; CTA r
+// multiplies k-blocks [r * KB / C, (r + 1) * KB / C) into its own TMEM
+// accumulator, drops the fp32 partial tile into its shared memory, and after one
+// cluster barrier CTA r sums token columns [r * BN / C, (r + 1) * BN / C) of all
+// C partial tiles with ld.shared::cluster (fixed order, so the result does not
+// depend on timing) and runs the epilogue for them.  Nothing but the final
+// output touches global memory: no workspace, no atomics, no second launch.
+//
+// This is the path a decode step takes for every projection; it replaces the
+// skinny-GEMM special cases of the reference (SmallNGemvSplitKKernel,
+// onnxruntime/core/providers/cuda/math/matmul_small_n_gemv.cu:16-60, which keeps
+// an fp32 workspace plus an atomic tile counter) and cuBLAS for M <= 64.
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include "gemm_internal.h"
+#include "ortb200_kernels.h"
+#include "ptx_sm100.cuh"
+#include "tensor_map.h"
+
+namespace ortb200 {
+
+namespace {
+
+constexpr int kBM = 128;
+constexpr int kBK = 64;
+constexpr int kThreads = 192;
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release;\n\tbarrier.cluster.wait.acquire;" ::: "memory");
+}
+// address of the same shared-memory location in CTA `cta` of this cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t local_smem_addr, uint32_t cta) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_smem_addr), "r"(cta));
+  return r;
+}
+__device__ __forceinline__ float ld_dsmem(uint32_t addr) {
+  float v;
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
+  return v;
+}
+
+__device__ __forceinline__ float act_apply(int act, float v) {
+  switch (act) {
+    case ORTB200_ACT_GELU: return 0.5f * v * (1.0f + erff(v * 0.70710678118654752f));
+    case ORTB200_ACT_FASTGELU: return 0.5f * v * (1.0f + tanhf(0.7978845608028654f * v * (1.0f + 0.044715f * v * v)));
+    case ORTB200_ACT_RELU: return fmaxf(v, 0.0f);
+    case ORTB200_ACT_SILU: return v / (1.0f + __expf(-v));
+    case ORTB200_ACT_QUICKGELU: return v / (1.0f + __expf(-1.702f * v));
+    default: return v;
+  }
+}
+
+template <int BN, int STAGES, bool DUAL>
+struct SmallSmem {
+  static constexpr int kABytes = kBM * kBK * 2;
+  static constexpr int kBBytes = BN * kBK * 2;
+  static constexpr int kStageBytes = kABytes * (DUAL ? 2 : 1) + kBBytes;
+  static constexpr int kCols = (DUAL ? 2 : 1) * BN;
+  static constexpr int kPartOffset = 0;  // float part[kCols][128] re-uses the pipeline stages once the main loop is done
+  static constexpr int kPartBytes = kCols * kBM * 4;
+  static constexpr int kBarOffset = kStageBytes * STAGES;
+  static_assert(kPartBytes <= kStageBytes * STAGES, "partial tile must fit in the drained pipeline stages");
+  static constexpr int kTotal = kBarOffset + 8 * (2 * STAGES + 1) + 16 + 1024;
+  static constexpr int kTmemCols = kCols < 32 ? 32 : kCols;
+};
+
+template <int BN, int STAGES, bool DUAL>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
+                   const SmallGemmParams p) {
+  using S = SmallSmem<BN, STAGES, DUAL>;
+  static_assert((S::kTmemCols & (S::kTmemCols - 1)) == 0, "TMEM columns must be a power of two");
+  extern __shared__ uint8_t smem_raw[];
+  // every CTA of the cluster applies the same rounding, so shared-memory offsets agree across the cluster
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  float* part = reinterpret_cast<float*>(smem + S::kPartOffset);
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + S::kBarOffset);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* tmem_full_bar = empty_bar + STAGES;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_full_bar + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int C = p.cluster;
+  const int rank = C > 1 ? static_cast<int>(cluster_ctarank()) : 0;
+  const int n0 = (blockIdx.x / C) * kBM;
+  const int m0 = blockIdx.y * BN;
+  const int kb_begin = static_cast<int>(static_cast<long long>(rank) * p.num_kb / C);
+  const int kb_end = static_cast<int>(static_cast<long long>(rank + 1) * p.num_kb / C);
+  const int nkb = kb_end - kb_begin;  // >= 1 (the host keeps C <= num_kb)
+
+  if (threadIdx.x == 0) {
+    tma_prefetch_desc(&tmap_w);
+    tma_prefetch_desc(&tmap_x);
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    mbar_init(tmem_full_bar, 1);
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, S::kTmemCols);
+    tmem_relinquish();
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  pdl_launch_dependents();  // the next kernel may begin its prologue
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // Weights do not depend on the previous kernel: start streaming them before waiting for X's producer.
+      const uint64_t pol_w = policy_evict_first();
+      const int pre = nkb < STAGES ? nkb : STAGES;
+      for (int i = 0; i < pre; ++i) {
+        uint8_t* st = smem + i * S::kStageBytes;
+        mbar_expect_tx(&full_bar[i], S::kStageBytes);
+        tma_load_2d_hint(st, &tmap_w, &full_bar[i], (kb_begin + i) * kBK, n0, pol_w);
+        if (DUAL) tma_load_2d_hint(st + S::kABytes, &tmap_w, &full_bar[i], (kb_begin + i) * kBK, n0 + p.dual_offset, pol_w);
+      }
+      pdl_wait_prior_grids();
+      for (int i = 0; i < pre; ++i) {
+        uint8_t* st = smem + i * S::kStageBytes;
+        tma_load_2d(st + S::kABytes * (DUAL ? 2 : 1), &tmap_x, &full_bar[i], (kb_begin + i) * kBK, m0);
+      }
+      for (int i = pre; i < nkb; ++i) {
+        const int s = i % STAGES;
+        if (!mbar_wait(&empty_bar[s], ((i / STAGES) - 1) & 1)) {
+          if (p.status) atomicExch(p.status, kStatusTimeoutProducer);
+          break;
+        }
+        uint8_t* st = smem + s * S::kStageBytes;
+        mbar_expect_tx(&full_bar[s], S::kStageBytes);
+        tma_load_2d_hint(st, &tmap_w, &full_bar[s], (kb_begin + i) * kBK, n0, pol_w);
+        if (DUAL) tma_load_2d_hint(st + S::kABytes, &tmap_w, &full_bar[s], (kb_begin + i) * kBK, n0 + p.dual_offset, pol_w);
+        tma_load_2d(st + S::kABytes * (DUAL ? 2 : 1), &tmap_x, &full_bar[s], (kb_begin + i) * kBK, m0);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = umma_idesc_f16(p.dtype == ORTB200_BF16, kBM, BN);
+      for (int i = 0; i < nkb; ++i) {
+        const int s = i % STAGES;
+        if (!mbar_wait(&full_bar[s], (i / STAGES) & 1)) {
+          if (p.status) atomicExch(p.status, kStatusTimeoutMma);
+          break;
+        }
+        tcgen05_fence_after();
+        const uint32_t a_addr = smem_u32(smem + s * S::kStageBytes);
+        const uint32_t b_addr = a_addr + S::kABytes * (DUAL ? 2 : 1);
+        const uint64_t adesc = umma_desc_sw128(a_addr);
+        const uint64_t bdesc = umma_desc_sw128(b_addr);
+#pragma unroll
+        for (int k = 0; k < kBK / 16; ++k) umma_f16(tmem_base, adesc + 2 * k, bdesc + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+        if (DUAL) {
+          const uint64_t a2desc = umma_desc_sw128(a_addr + S::kABytes);
+#pragma unroll
+          for (int k = 0; k < kBK / 16; ++k) umma_f16(tmem_base + BN, a2desc + 2 * k, bdesc + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+        }
+        umma_commit(&empty_bar[s]);
+      }
+      umma_commit(tmem_full_bar);  // also on the failure path, so the epilogue never waits for nothing
+    }
+  } else {
+    // epilogue warps: TMEM -> registers -> this CTA's partial tile in shared memory
+    const int q = warp & 3;
+    const int r = q * 32 + lane;
+    const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+    if (!mbar_wait(tmem_full_bar, 0)) {
+      if (p.status) atomicExch(p.status, kStatusTimeoutEpilogue);
+    }
+    tcgen05_fence_after();
+    if (C > 1) {
+#pragma unroll 1
+      for (int c = 0; c < S::kCols; c += 16) {
+        float v[16];
+        tmem_ld_x16(t_lane + c, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 16; ++j) part[(c + j) * kBM + r] = v[j];
+      }
+    }
+  }
+
+  // every thread of every CTA in the cluster meets here: partial tiles are complete and visible
+  if (C > 1) cluster_sync_all();
+
+  if (warp >= 2) {
+    const int q = warp & 3;
+    const int r = q * 32 + lane;
+    const int n = n0 + r;
+    const bool n_ok = n < p.N;
+    const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+    pdl_wait_prior_grids();  // out / residual may still be in use by the previous kernel
+    const float bias_v = (p.bias != nullptr && n_ok)
+                             ? (p.dtype == ORTB200_BF16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.bias)[n])
+                                                        : __half2float(reinterpret_cast<const __half*>(p.bias)[n]))
+                             : 0.0f;
+    // token columns this CTA finishes
+    const int cols_per = BN / C;
+    const int j_begin = rank * cols_per;
+    const uint32_t part_addr = smem_u32(part);
+#pragma unroll 1
+    for (int jj = 0; jj < cols_per; ++jj) {
+      const int j = j_begin + jj;
+      float v = 0.f, u = 0.f;
+      if (C > 1) {
+        for (int c = 0; c < C; ++c) {
+          const uint32_t base = map_to_cta(part_addr, static_cast<uint32_t>(c));
+          v += ld_dsmem(base + static_cast<uint32_t>((j * kBM + r) * 4));
+          if (DUAL) u += ld_dsmem(base + static_cast<uint32_t>(((BN + j) * kBM + r) * 4));
+        }
+      } else {
+        float t1[8];
+        tmem_ld_x8(t_lane + (j & ~7), t1);
+        tmem_ld_wait();
+        v = t1[j & 7];
+        if (DUAL) {
+          tmem_ld_x8(t_lane + BN + (j & ~7), t1);
+          tmem_ld_wait();
+          u = t1[j & 7];
+        }
+      }
+      const int m = m0 + j;
+      if (n_ok && m < p.M) {
+        float y = v * p.alpha + bias_v;
+        if (DUAL) {
+          const float g = y / (1.0f + __expf(-y));
+          y = g * (u * p.alpha);
+        } else {
+          y = act_apply(p.act, y);
+        }
+        if (p.dtype == ORTB200_BF16) {
+          if (p.residual) y += __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.residual)[m * p.ldr + n]);
+          reinterpret_cast<__nv_bfloat16*>(p.out)[m * p.ldo + n] = __float2bfloat16_rn(y);
+        } else {
+          if (p.residual) y += __half2float(reinterpret_cast<const __half*>(p.residual)[m * p.ldr + n]);
+          reinterpret_cast<__half*>(p.out)[m * p.ldo + n] = __float2half_rn(y);
+        }
+      }
+    }
+  }
+
+  // nobody leaves while a peer may still read its partial tile
+  if (C > 1) cluster_sync_all();
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tcgen05_fence_after();
+    tmem_dealloc(tmem_base, S::kTmemCols);
+  }
+}
+
+template <int BN, int STAGES, bool DUAL>
+int launch_small(const CUtensorMap& tw, const CUtensorMap& tx, const SmallGemmParams& p, dim3 grid, cudaStream_t stream,
+                 bool use_pdl) {
+  using S = SmallSmem<BN, STAGES, DUAL>;
+  static_assert(S::kTotal <= 113 * 1024, "two CTAs per SM must fit");
+  auto kern = gemm_smallm_kernel<BN, STAGES, DUAL>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal) != cudaSuccess) return -10;
+    attr_set = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.dynamicSmemBytes = S::kTotal;
+  cfg.stream = stream;
+  cudaLaunchAttribute attrs[2];
+  int nattr = 0;
+  if (p.cluster > 1) {
+    attrs[nattr].id = cudaLaunchAttributeClusterDimension;
+    attrs[nattr].val.clusterDim.x = p.cluster;
+    attrs[nattr].val.clusterDim.y = 1;
+    attrs[nattr].val.clusterDim.z = 1;
+    ++nattr;
+  }
+  if (use_pdl) {
+    attrs[nattr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[nattr].val.programmaticStreamSerializationAllowed = 1;
+    ++nattr;
+  }
+  cfg.attrs = attrs;
+  cfg.numAttrs = nattr;
+  return cudaLaunchKernelEx(&cfg, kern, tw, tx, p) == cudaSuccess ? 0 : -11;
+}
+
+}  // namespace
+
+int pick_cluster(int tiles, int num_kb, int bn, int force) {
+  int c = 1;
+  if (force > 0) {
+    c = force >= 8 ? 8 : (force >= 4 ? 4 : (force >= 2 ? 2 : 1));
+  } else {
+    // aim for about two CTAs per SM; keep at least four k-blocks per CTA
+    const int want = (2 * 148) / (tiles > 0 ? tiles : 1);
+    while (c * 2 <= want && c < 8) c *= 2;
+  }
+  while (c > 1 && (num_kb / c < 4 || bn % c != 0)) c /= 2;
+  return c;
+}
+
+int launch_gemm_smallm(const ortb200_gemm_args* a, int bn, cudaStream_t stream, int* cluster_out, int* stages_out) {
+  const bool dual = a->act == ORTB200_ACT_SWIGLU;
+  const int num_kb = (a->K + kBK - 1) / kBK;
+  const int tiles_n = (a->N + kBM - 1) / kBM, tiles_m = (a->M + bn - 1) / bn;
+  const int cluster = pick_cluster(tiles_n * tiles_m, num_kb, bn, a->force_splits);
+  CUtensorMap tw, tx;
+  const CUtensorMapDataType dt = a->dtype == ORTB200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  if (make_tensor_map_2d(&tw, a->w, dt, 2, a->K, a->w_rows, static_cast<int64_t>(a->K) * 2, kBK, kBM) != 0) return -6;
+  if (make_tensor_map_2d(&tx, a->x, dt, 2, a->K, a->M, static_cast<int64_t>(a->K) * 2, kBK, bn) != 0) return -6;
+  SmallGemmParams p;
+  p.M = a->M; p.N = a->N; p.K = a->K; p.num_kb = num_kb; p.cluster = cluster; p.dual_offset = a->dual_offset;
+  p.dtype = a->dtype; p.act = a->act; p.alpha = a->alpha; p.out = a->out; p.ldo = a->ldo; p.bias = a->bias;
+  p.residual = a->residual; p.ldr = a->ldr; p.status = a->status;
+  dim3 grid(tiles_n * cluster, tiles_m, 1);
+  const bool pdl = a->use_pdl != 0;
+  *cluster_out = cluster;
+  switch (bn) {
+    case 16:
+      *stages_out = dual ? 3 : 5;
+      return dual ? launch_small<16, 3, true>(tw, tx, p, grid, stream, pdl) : launch_small<16, 5, false>(tw, tx, p, grid, stream, pdl);
+    case 32:
+      *stages_out = dual ? 2 : 4;
+      return dual ? launch_small<32, 2, true>(tw, tx, p, grid, stream, pdl) : launch_small<32, 4, false>(tw, tx, p, grid, stream, pdl);
+    case 64:
+      *stages_out = dual ? 2 : 3;
+      return dual ? launch_small<64, 2, true>(tw, tx, p, grid, stream, pdl) : launch_small<64, 3, false>(tw, tx, p, grid, stream, pdl);
+    default: return -8;
+  }
+}
+
+}  // namespace ortb200

@@ -7,11 +7,17 @@
 //
 // Orientation: the WEIGHT tile is the MMA's A operand (128 rows = 128 TMEM
 // lanes), the token tile is the B operand (BN = 16..256 columns).  A decode
-// step with 8 tokens therefore wastes no tensor-core rows on padding: one CTA
-// streams a 128 x K slab of W exactly once.  Split-K spreads narrow problems
-// over all SMs; partial tiles go to an fp32 workspace and the CTA that arrives
-// last on a per-tile counter reduces them in a fixed order (deterministic) and
-// runs the epilogue.  No host round trip, no second launch.
+// step with 8 tokens therefore wastes no tensor-core rows on padding and W is
+// streamed exactly once.
+//
+// The kernel is persistent: one CTA per SM walks a contiguous range of
+// (tile, k-block) work units, so the TMA pipeline never drains between tiles
+// and two TMEM accumulator buffers let the epilogue of one tile overlap the
+// main loop of the next.  With many tiles every CTA owns whole tiles; with few
+// (decode) the units are dealt out evenly (stream-K): a tile shared by several
+// CTAs is reduced through an fp32 workspace by the CTA that arrives last on a
+// per-tile counter, in a fixed order (deterministic).  No host round trip, no
+// second launch.
 //
 // Warp roles (192 threads): warp 0 = TMA producer, warp 1 = TMEM owner + MMA
 // issuer (one elected lane), warps 2..5 = epilogue (one TMEM lane quarter each).
@@ -20,6 +26,7 @@
 #include <mutex>
 #include <unordered_map>
 #include <stdio.h>
+#include "gemm_internal.h"
 #include "ortb200_kernels.h"
 #include "ptx_sm100.cuh"
 #include "tensor_map.h"
@@ -33,8 +40,10 @@ constexpr int kThreads = 192;
 struct GemmKernelParams {
   int M, N, K;
   int num_kb;         // ceil(K / 64)
-  int kb_per_split;
-  int splits;
+  int tiles;          // tiles_n * tiles_m
+  int tiles_m;        // tile index = tile_n * tiles_m + tile_m
+  int tile_aligned;   // 1: every CTA owns whole tiles; 0: stream-K over (tile, k-block) units
+  int max_contrib;    // workspace slots per tile in stream-K mode
   int dual_offset;
   int dtype;
   int act;
@@ -66,33 +75,54 @@ struct GemmSmem {
   static constexpr int kBBytes = BN * kBK * 2;
   static constexpr int kStageBytes = kABytes * (DUAL ? 2 : 1) + kBBytes;
   static constexpr int kBarOffset = kStageBytes * STAGES;
-  static constexpr int kTotal = kBarOffset + 8 * (2 * STAGES + 1) + 16 + 1024;  // + alignment slack
-  static constexpr int kTmemCols = (DUAL ? 2 : 1) * BN < 32 ? 32 : (DUAL ? 2 : 1) * BN;
+  static constexpr int kTotal = kBarOffset + 8 * (2 * STAGES + 4) + 16 + 1024;  // + alignment slack
+  static constexpr int kCols = (DUAL ? 2 : 1) * BN;                             // accumulator columns per buffer
+  static constexpr int kBufCols = kCols < 32 ? 32 : kCols;
+  static constexpr int kTmemCols = 2 * kBufCols;                                 // two accumulator buffers
 };
+
+// Work decomposition shared by the three warp roles.  Units are (tile, k-block) pairs numbered tile-major;
+// CTA c owns units [c * U / G, (c + 1) * U / G), or whole tiles when `tile_aligned`.
+struct WorkRange {
+  long long begin, end;
+};
+__device__ __forceinline__ WorkRange cta_range(const GemmKernelParams& p, int c) {
+  const long long G = gridDim.x;
+  WorkRange r;
+  if (p.tile_aligned) {
+    r.begin = (static_cast<long long>(c) * p.tiles / G) * p.num_kb;
+    r.end = (static_cast<long long>(c + 1) * p.tiles / G) * p.num_kb;
+  } else {
+    const long long U = static_cast<long long>(p.tiles) * p.num_kb;
+    r.begin = static_cast<long long>(c) * U / G;
+    r.end = static_cast<long long>(c + 1) * U / G;
+  }
+  return r;
+}
+// CTA that owns unit u in stream-K mode
+__device__ __forceinline__ int owner_of(const GemmKernelParams& p, long long u) {
+  const long long U = static_cast<long long>(p.tiles) * p.num_kb;
+  return static_cast<int>(((u + 1) * gridDim.x - 1) / U);
+}
 
 template <int BN, int STAGES, bool DUAL>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
                     const GemmKernelParams p) {
   using S = GemmSmem<BN, STAGES, DUAL>;
-  static_assert((S::kTmemCols & (S::kTmemCols - 1)) == 0, "TMEM columns must be a power of two");
+  static_assert((S::kTmemCols & (S::kTmemCols - 1)) == 0 && S::kTmemCols <= 512, "TMEM columns must be a power of two <= 512");
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + S::kBarOffset);
   uint64_t* empty_bar = full_bar + STAGES;
-  uint64_t* tmem_full_bar = empty_bar + STAGES;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_full_bar + 1);
+  uint64_t* tmem_full_bar = empty_bar + STAGES;   // [2]
+  uint64_t* tmem_empty_bar = tmem_full_bar + 2;    // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty_bar + 2);
   uint32_t* last_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int n0 = blockIdx.x * kBM;
-  const int m0 = blockIdx.y * BN;
-  const int split = blockIdx.z;
-  const int kb_begin = split * p.kb_per_split;
-  int kb_end = kb_begin + p.kb_per_split;
-  if (kb_end > p.num_kb) kb_end = p.num_kb;
-  const int nkb = kb_end - kb_begin;  // >= 1 by construction on the host
+  const WorkRange range = cta_range(p, blockIdx.x);
 
   if (threadIdx.x == 0) {
     tma_prefetch_desc(&tmap_w);
@@ -101,7 +131,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
     }
-    mbar_init(tmem_full_bar, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&tmem_full_bar[i], 1);
+      mbar_init(&tmem_empty_bar[i], 128);
+    }
     fence_mbar_init();
   }
   if (warp == 1) {
@@ -116,164 +149,208 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
   // Let the next kernel in the stream start its own prologue.
   pdl_launch_dependents();
 
-  bool failed = false;
-
   if (warp == 0) {
     if (lane == 0) {
-      // Weights do not depend on the previous kernel: fill the pipeline with W
-      // tiles first, then wait for the producer of X, then add the X tiles.
+      // Weights do not depend on the previous kernel: fill the pipeline with W tiles first, then wait for
+      // the producer of X, then add the X tiles.  `it` counts k-blocks across all segments of this CTA.
       const uint64_t pol_w = policy_evict_first();
-      const int pre = nkb < STAGES ? nkb : STAGES;
+      const long long total = range.end - range.begin;
+      const int pre = total < STAGES ? static_cast<int>(total) : STAGES;
+      auto coords = [&](long long u, int* kb, int* n0, int* m0) {
+        const int tile = static_cast<int>(u / p.num_kb);
+        *kb = static_cast<int>(u % p.num_kb);
+        *n0 = (tile / p.tiles_m) * kBM;
+        *m0 = (tile % p.tiles_m) * BN;
+      };
       for (int i = 0; i < pre; ++i) {
+        int kb, n0, m0;
+        coords(range.begin + i, &kb, &n0, &m0);
         uint8_t* st = smem + i * S::kStageBytes;
         mbar_expect_tx(&full_bar[i], S::kStageBytes);
-        tma_load_2d_hint(st, &tmap_w, &full_bar[i], (kb_begin + i) * kBK, n0, pol_w);
-        if (DUAL) tma_load_2d_hint(st + S::kABytes, &tmap_w, &full_bar[i], (kb_begin + i) * kBK, n0 + p.dual_offset, pol_w);
+        tma_load_2d_hint(st, &tmap_w, &full_bar[i], kb * kBK, n0, pol_w);
+        if (DUAL) tma_load_2d_hint(st + S::kABytes, &tmap_w, &full_bar[i], kb * kBK, n0 + p.dual_offset, pol_w);
       }
       pdl_wait_prior_grids();
       for (int i = 0; i < pre; ++i) {
+        int kb, n0, m0;
+        coords(range.begin + i, &kb, &n0, &m0);
         uint8_t* st = smem + i * S::kStageBytes;
-        tma_load_2d(st + S::kABytes * (DUAL ? 2 : 1), &tmap_x, &full_bar[i], (kb_begin + i) * kBK, m0);
+        tma_load_2d(st + S::kABytes * (DUAL ? 2 : 1), &tmap_x, &full_bar[i], kb * kBK, m0);
       }
-      for (int i = pre; i < nkb; ++i) {
-        const int s = i % STAGES;
-        const uint32_t parity = ((i / STAGES) - 1) & 1;
+      for (long long i = pre; i < total; ++i) {
+        const int s = static_cast<int>(i % STAGES);
+        const uint32_t parity = static_cast<uint32_t>((i / STAGES) - 1) & 1;
         if (!mbar_wait(&empty_bar[s], parity)) {
-          failed = true;
           if (p.status) atomicExch(p.status, kStatusTimeoutProducer);
           break;
         }
+        int kb, n0, m0;
+        coords(range.begin + i, &kb, &n0, &m0);
         uint8_t* st = smem + s * S::kStageBytes;
         mbar_expect_tx(&full_bar[s], S::kStageBytes);
-        tma_load_2d_hint(st, &tmap_w, &full_bar[s], (kb_begin + i) * kBK, n0, pol_w);
-        if (DUAL) tma_load_2d_hint(st + S::kABytes, &tmap_w, &full_bar[s], (kb_begin + i) * kBK, n0 + p.dual_offset, pol_w);
-        tma_load_2d(st + S::kABytes * (DUAL ? 2 : 1), &tmap_x, &full_bar[s], (kb_begin + i) * kBK, m0);
+        tma_load_2d_hint(st, &tmap_w, &full_bar[s], kb * kBK, n0, pol_w);
+        if (DUAL) tma_load_2d_hint(st + S::kABytes, &tmap_w, &full_bar[s], kb * kBK, n0 + p.dual_offset, pol_w);
+        tma_load_2d(st + S::kABytes * (DUAL ? 2 : 1), &tmap_x, &full_bar[s], kb * kBK, m0);
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
       const uint32_t idesc = umma_idesc_f16(p.dtype == ORTB200_BF16, kBM, BN);
-      for (int i = 0; i < nkb; ++i) {
-        const int s = i % STAGES;
-        const uint32_t parity = (i / STAGES) & 1;
-        if (!mbar_wait(&full_bar[s], parity)) {
-          failed = true;
-          if (p.status) atomicExch(p.status, kStatusTimeoutMma);
+      long long it = 0;
+      int seg = 0;
+      bool ok = true;
+      for (long long u = range.begin; u < range.end && ok; ++seg) {
+        const long long tile_end = (u / p.num_kb + 1) * p.num_kb;
+        const long long seg_end = tile_end < range.end ? tile_end : range.end;
+        const int buf = seg & 1;
+        const uint32_t tmem_d = tmem_base + buf * S::kBufCols;
+        if (seg >= 2 && !mbar_wait(&tmem_empty_bar[buf], ((seg >> 1) - 1) & 1)) {
+          ok = false;
           break;
         }
         tcgen05_fence_after();
-        const uint32_t a_addr = smem_u32(smem + s * S::kStageBytes);
-        const uint32_t b_addr = a_addr + S::kABytes * (DUAL ? 2 : 1);
-        const uint64_t adesc = umma_desc_sw128(a_addr);
-        const uint64_t bdesc = umma_desc_sw128(b_addr);
-#pragma unroll
-        for (int k = 0; k < kBK / 16; ++k) {
-          // 16 K-elements = 32 bytes: the start-address field advances by 2
-          umma_f16(tmem_base, adesc + 2 * k, bdesc + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
-        }
-        if (DUAL) {
-          const uint64_t a2desc = umma_desc_sw128(a_addr + S::kABytes);
+        bool first = true;
+        for (; u < seg_end; ++u, ++it) {
+          const int s = static_cast<int>(it % STAGES);
+          if (!mbar_wait(&full_bar[s], static_cast<uint32_t>(it / STAGES) & 1)) {
+            ok = false;
+            break;
+          }
+          tcgen05_fence_after();
+          const uint32_t a_addr = smem_u32(smem + s * S::kStageBytes);
+          const uint32_t b_addr = a_addr + S::kABytes * (DUAL ? 2 : 1);
+          const uint64_t adesc = umma_desc_sw128(a_addr);
+          const uint64_t bdesc = umma_desc_sw128(b_addr);
 #pragma unroll
           for (int k = 0; k < kBK / 16; ++k) {
-            umma_f16(tmem_base + BN, a2desc + 2 * k, bdesc + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+            // 16 K-elements = 32 bytes: the start-address field advances by 2
+            umma_f16(tmem_d, adesc + 2 * k, bdesc + 2 * k, idesc, (!first || k > 0) ? 1u : 0u);
           }
+          if (DUAL) {
+            const uint64_t a2desc = umma_desc_sw128(a_addr + S::kABytes);
+#pragma unroll
+            for (int k = 0; k < kBK / 16; ++k) {
+              umma_f16(tmem_d + BN, a2desc + 2 * k, bdesc + 2 * k, idesc, (!first || k > 0) ? 1u : 0u);
+            }
+          }
+          first = false;
+          umma_commit(&empty_bar[s]);  // stage is reusable once these MMAs have read it
         }
-        umma_commit(&empty_bar[s]);  // stage is reusable once these MMAs have read it
+        umma_commit(&tmem_full_bar[buf]);  // accumulator of this segment complete (also signalled on the failure path)
       }
-      umma_commit(tmem_full_bar);    // accumulator complete (also signalled on the failure path)
+      if (!ok && p.status) atomicExch(p.status, kStatusTimeoutMma);
     }
   } else {
     // ---------------------------------------------------------- epilogue
     const int q = warp & 3;                 // TMEM lane quarter this warp may read
     const int r = q * 32 + lane;            // lane within the tile == weight row
-    const int n = n0 + r;
-    const bool n_ok = n < p.N;
-    const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
-    const int tile_id = blockIdx.y * gridDim.x + blockIdx.x;
-
     pdl_wait_prior_grids();                 // out / residual / workspace may belong to the previous kernel
-    if (!mbar_wait(tmem_full_bar, 0)) {
-      failed = true;
-      if (p.status) atomicExch(p.status, kStatusTimeoutEpilogue);
-    }
-    tcgen05_fence_after();
-
-    bool do_output = !failed;
-    if (!failed && p.splits > 1) {
-      // 1) publish this split's partial tile
-      constexpr int kCols = (DUAL ? 2 : 1) * BN;
-      float* my_ws = p.ws + (static_cast<size_t>(tile_id) * p.splits + split) * (kCols * kBM);
-#pragma unroll 1
-      for (int c = 0; c < kCols; c += 16) {
-        float v[16];
-        tmem_ld_x16(t_lane + c, v);
-        tmem_ld_wait();
-#pragma unroll
-        for (int j = 0; j < 16; ++j) my_ws[(c + j) * kBM + r] = v[j];
+    int seg = 0;
+    bool ok = true;
+    for (long long u = range.begin; u < range.end && ok; ++seg) {
+      const int tile = static_cast<int>(u / p.num_kb);
+      const long long tile_begin = static_cast<long long>(tile) * p.num_kb;
+      const long long tile_end = tile_begin + p.num_kb;
+      const long long seg_end = tile_end < range.end ? tile_end : range.end;
+      const bool whole = (u == tile_begin) && (seg_end == tile_end);
+      const int buf = seg & 1;
+      const int n0 = (tile / p.tiles_m) * kBM, m0 = (tile % p.tiles_m) * BN;
+      const int n = n0 + r;
+      const bool n_ok = n < p.N;
+      const uint32_t t_lane = tmem_base + buf * S::kBufCols + (static_cast<uint32_t>(q * 32) << 16);
+      if (!mbar_wait(&tmem_full_bar[buf], (seg >> 1) & 1)) {
+        ok = false;
+        if (p.status) atomicExch(p.status, kStatusTimeoutEpilogue);
+        break;
       }
-      __threadfence();
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (threadIdx.x == 64) {
-        const unsigned int old = atomicAdd(&p.counters[tile_id], 1u);
-        const unsigned int last = (old == static_cast<unsigned int>(p.splits - 1)) ? 1u : 0u;
-        if (last) p.counters[tile_id] = 0;  // re-arm for the next launch (graph replay safe)
-        *last_flag = last;
-      }
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      do_output = (*last_flag != 0);
-      if (do_output) __threadfence();
-    }
+      tcgen05_fence_after();
 
-    if (do_output) {
-      const float bias_v = (p.bias != nullptr && n_ok)
-                               ? (p.dtype == ORTB200_BF16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.bias)[n])
-                                                          : __half2float(reinterpret_cast<const __half*>(p.bias)[n]))
-                               : 0.0f;
-      constexpr int kCols = (DUAL ? 2 : 1) * BN;
-      const float* tile_ws = p.splits > 1 ? p.ws + static_cast<size_t>(tile_id) * p.splits * (kCols * kBM) : nullptr;
+      bool do_output = true;
+      int n_contrib = 1, first_owner = 0;
+      if (!whole) {
+        // 1) publish this CTA's partial tile; slot = position of this CTA among the tile's contributors
+        first_owner = owner_of(p, tile_begin);
+        n_contrib = owner_of(p, tile_end - 1) - first_owner + 1;
+        const int slot = static_cast<int>(blockIdx.x) - first_owner;
+        float* my_ws = p.ws + (static_cast<size_t>(tile) * p.max_contrib + slot) * (S::kCols * kBM);
 #pragma unroll 1
-      for (int c = 0; c < BN; c += 16) {
-        float v[16];
-        float u[16];
-        if (p.splits == 1) {
+        for (int c = 0; c < S::kCols; c += 16) {
+          float v[16];
           tmem_ld_x16(t_lane + c, v);
-          if (DUAL) tmem_ld_x16(t_lane + BN + c, u);
           tmem_ld_wait();
-        } else {
 #pragma unroll
-          for (int j = 0; j < 16; ++j) { v[j] = 0.0f; u[j] = 0.0f; }
-          for (int s = 0; s < p.splits; ++s) {
-            const float* src = tile_ws + static_cast<size_t>(s) * (kCols * kBM);
+          for (int j = 0; j < 16; ++j) my_ws[(c + j) * kBM + r] = v[j];
+        }
+        tcgen05_fence_before();
+        mbar_arrive(&tmem_empty_bar[buf]);
+        __threadfence();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (threadIdx.x == 64) {
+          const unsigned int old = atomicAdd(&p.counters[tile], 1u);
+          const unsigned int last = (old == static_cast<unsigned int>(n_contrib - 1)) ? 1u : 0u;
+          if (last) p.counters[tile] = 0;  // re-arm for the next launch (graph replay safe)
+          *last_flag = last;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        do_output = (*last_flag != 0);
+        if (do_output) __threadfence();
+      }
+
+      if (do_output) {
+        const float bias_v = (p.bias != nullptr && n_ok)
+                                 ? (p.dtype == ORTB200_BF16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.bias)[n])
+                                                            : __half2float(reinterpret_cast<const __half*>(p.bias)[n]))
+                                 : 0.0f;
+        const float* tile_ws = whole ? nullptr : p.ws + static_cast<size_t>(tile) * p.max_contrib * (S::kCols * kBM);
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 16) {
+          float v[16];
+          float uu[16];
+          if (whole) {
+            tmem_ld_x16(t_lane + c, v);
+            if (DUAL) tmem_ld_x16(t_lane + BN + c, uu);
+            tmem_ld_wait();
+          } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) { v[j] = 0.0f; uu[j] = 0.0f; }
+            for (int s = 0; s < n_contrib; ++s) {
+              const float* src = tile_ws + static_cast<size_t>(s) * (S::kCols * kBM);
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                v[j] += __ldcg(&src[(c + j) * kBM + r]);
+                if (DUAL) uu[j] += __ldcg(&src[(BN + c + j) * kBM + r]);
+              }
+            }
+          }
+          if (n_ok) {
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
-              v[j] += __ldcg(&src[(c + j) * kBM + r]);
-              if (DUAL) u[j] += __ldcg(&src[(BN + c + j) * kBM + r]);
-            }
-          }
-        }
-        if (n_ok) {
-#pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const int m = m0 + c + j;
-            if (m < p.M) {
-              float y = v[j] * p.alpha + bias_v;
-              if (DUAL) {
-                const float g = y / (1.0f + __expf(-y));
-                y = g * (u[j] * p.alpha);
-              } else {
-                y = apply_act(p.act, y);
-              }
-              if (p.dtype == ORTB200_BF16) {
-                if (p.residual) y += __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.residual)[m * p.ldr + n]);
-                reinterpret_cast<__nv_bfloat16*>(p.out)[m * p.ldo + n] = __float2bfloat16_rn(y);
-              } else {
-                if (p.residual) y += __half2float(reinterpret_cast<const __half*>(p.residual)[m * p.ldr + n]);
-                reinterpret_cast<__half*>(p.out)[m * p.ldo + n] = __float2half_rn(y);
+              const int m = m0 + c + j;
+              if (m < p.M) {
+                float y = v[j] * p.alpha + bias_v;
+                if (DUAL) {
+                  const float g = y / (1.0f + __expf(-y));
+                  y = g * (uu[j] * p.alpha);
+                } else {
+                  y = apply_act(p.act, y);
+                }
+                if (p.dtype == ORTB200_BF16) {
+                  if (p.residual) y += __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.residual)[m * p.ldr + n]);
+                  reinterpret_cast<__nv_bfloat16*>(p.out)[m * p.ldo + n] = __float2bfloat16_rn(y);
+                } else {
+                  if (p.residual) y += __half2float(reinterpret_cast<const __half*>(p.residual)[m * p.ldr + n]);
+                  reinterpret_cast<__half*>(p.out)[m * p.ldo + n] = __float2half_rn(y);
+                }
               }
             }
           }
         }
       }
+      if (whole) {
+        tcgen05_fence_before();
+        mbar_arrive(&tmem_empty_bar[buf]);
+      }
+      u = seg_end;
     }
   }
 
@@ -283,7 +360,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
     tcgen05_fence_after();
     tmem_dealloc(tmem_base, S::kTmemCols);
   }
-  (void)failed;
 }
 
 // ------------------------------------------------------------------ host side
@@ -293,6 +369,16 @@ struct GemmConfig {
 };
 static thread_local GemmConfig g_last_config = {0, 0, 0};
 
+static int num_sms() {
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+  }
+  return sms;
+}
+
 static int pick_bn(int M) {
   if (M <= 16) return 16;
   if (M <= 32) return 32;
@@ -301,22 +387,11 @@ static int pick_bn(int M) {
   return 256;
 }
 
-static int pick_splits(int M, int N, int num_kb, int bn) {
-  const int tiles = ((N + kBM - 1) / kBM) * ((M + bn - 1) / bn);
-  const int kSMs = 148;
-  if (tiles >= kSMs || num_kb < 8) return 1;
-  int want = (2 * kSMs + tiles - 1) / tiles;
-  int max_by_k = num_kb / 4;  // keep at least 4 k-blocks per split
-  if (want > max_by_k) want = max_by_k;
-  if (want > 16) want = 16;
-  if (want < 1) want = 1;
-  return want;
-}
-
 template <int BN, int STAGES, bool DUAL>
-static int launch_gemm(const CUtensorMap& tw, const CUtensorMap& tx, const GemmKernelParams& p, dim3 grid,
+static int launch_gemm(const CUtensorMap& tw, const CUtensorMap& tx, const GemmKernelParams& p, int grid,
                        cudaStream_t stream, bool use_pdl) {
   using S = GemmSmem<BN, STAGES, DUAL>;
+  static_assert(S::kTotal <= 227 * 1024, "shared memory budget exceeded");
   auto kern = gemm_tcgen05_kernel<BN, STAGES, DUAL>;
   static bool attr_set = false;
   if (!attr_set) {
@@ -325,7 +400,7 @@ static int launch_gemm(const CUtensorMap& tw, const CUtensorMap& tx, const GemmK
     attr_set = true;
   }
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = grid;
+  cfg.gridDim = dim3(grid, 1, 1);
   cfg.blockDim = dim3(kThreads, 1, 1);
   cfg.dynamicSmemBytes = S::kTotal;
   cfg.stream = stream;
@@ -346,15 +421,64 @@ static int launch_gemm(const CUtensorMap& tw, const CUtensorMap& tx, const GemmK
 
 using namespace ortb200;
 
+namespace {
+struct GemmPlan {
+  int bn, num_kb, tiles_n, tiles_m, grid, max_contrib;
+  int64_t tiles, ws_need;
+  bool tile_aligned;
+};
+
+// Persistent grid: one CTA per SM.  With many tiles each CTA takes whole tiles; with few, the (tile, k-block)
+// units are dealt out evenly (stream-K) and tiles shared by several CTAs are reduced through the workspace.
+// ws_available < 0 means "unlimited" (used to size the workspace).
+int plan_gemm(int M, int N, int K, bool dual, int force_bn, int force_splits, int64_t ws_available, GemmPlan* pl) {
+  int bn = force_bn ? force_bn : pick_bn(M);
+  if (dual && bn > 128) bn = 128;     // two accumulators, double-buffered, must fit 512 TMEM columns
+  pl->bn = bn;
+  pl->num_kb = (K + kBK - 1) / kBK;
+  pl->tiles_n = (N + kBM - 1) / kBM;
+  pl->tiles_m = (M + bn - 1) / bn;
+  pl->tiles = static_cast<int64_t>(pl->tiles_n) * pl->tiles_m;
+  if (pl->tiles > 0x7fffffff / pl->num_kb) return -9;
+  const int sms = num_sms();
+  int grid = sms;
+  bool tile_aligned = pl->tiles >= 4LL * sms || force_splits == 1;
+  const int64_t units = pl->tiles * pl->num_kb;
+  int max_contrib = 1;
+  int64_t need = 0;
+  if (!tile_aligned) {
+    if (units < 2LL * grid) grid = static_cast<int>((units + 1) / 2);
+    if (force_splits > 1) {
+      int64_t g = pl->tiles * force_splits;
+      if (g > sms) g = sms;
+      if (g > units) g = units;
+      grid = static_cast<int>(g);
+    }
+    if (grid < 1) grid = 1;
+    const int64_t per_cta = units / grid;  // >= 1
+    max_contrib = static_cast<int>(pl->num_kb / (per_cta > 0 ? per_cta : 1)) + 2;
+    if (max_contrib > grid) max_contrib = grid;
+    need = 65536 + pl->tiles * max_contrib * (dual ? 2 : 1) * bn * kBM * 4;
+    if (pl->tiles > 16384 || (ws_available >= 0 && ws_available < need)) tile_aligned = true;
+  }
+  if (tile_aligned) {
+    max_contrib = 1;
+    need = 0;
+    if (grid > pl->tiles) grid = static_cast<int>(pl->tiles);
+    if (grid > sms) grid = sms;
+  }
+  pl->grid = grid;
+  pl->max_contrib = max_contrib;
+  pl->tile_aligned = tile_aligned;
+  pl->ws_need = need;
+  return 0;
+}
+}  // namespace
+
 extern "C" int64_t ortb200_gemm_workspace_bytes(int M, int N, int K, int act) {
-  const int bn = pick_bn(M);
-  const int num_kb = (K + kBK - 1) / kBK;
-  const int splits_max = 16;
-  const int64_t tiles = static_cast<int64_t>((N + kBM - 1) / kBM) * ((M + bn - 1) / bn);
-  const int64_t cols = (act == ORTB200_ACT_SWIGLU ? 2 : 1) * bn;
-  (void)num_kb;
-  // counters live in the first 64 KiB
-  return 65536 + tiles * splits_max * cols * kBM * 4;
+  GemmPlan pl;
+  if (M <= 0 || N <= 0 || K <= 0 || plan_gemm(M, N, K, act == ORTB200_ACT_SWIGLU, 0, 0, -1, &pl) != 0) return 65536;
+  return pl.ws_need > 65536 ? pl.ws_need : 65536;
 }
 
 extern "C" int ortb200_gemm_last_config(int* bn, int* splits, int* stages) {
@@ -375,29 +499,22 @@ extern "C" int ortb200_gemm(const ortb200_gemm_args* a, ortb200_stream_t stream_
   if (dual && (a->dual_offset <= 0 || a->w_rows < a->dual_offset + a->N)) return -5;
   if (!dual && a->w_rows < a->N) return -5;
 
-  int bn = a->force_bn ? a->force_bn : pick_bn(a->M);
-  if (dual && bn > 128) bn = 128;     // two accumulators must fit 512 TMEM columns with room to spare
-  const int num_kb = (a->K + kBK - 1) / kBK;
-  int splits = a->force_splits ? a->force_splits : pick_splits(a->M, a->N, num_kb, bn);
-  if (splits > num_kb) splits = num_kb;
-  int kb_per_split = (num_kb + splits - 1) / splits;
-  splits = (num_kb + kb_per_split - 1) / kb_per_split;  // no empty splits
-
-  const int tiles_n = (a->N + kBM - 1) / kBM;
-  const int tiles_m = (a->M + bn - 1) / bn;
-  const int64_t tiles = static_cast<int64_t>(tiles_n) * tiles_m;
-  float* ws = nullptr;
-  unsigned int* counters = nullptr;
-  if (splits > 1) {
-    const int64_t need = 65536 + tiles * splits * (dual ? 2 : 1) * bn * kBM * 4;
-    if (!a->workspace || a->workspace_bytes < need || tiles > 16384) {
-      splits = 1;
-      kb_per_split = num_kb;
-    } else {
-      counters = reinterpret_cast<unsigned int*>(a->workspace);
-      ws = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(a->workspace) + 65536);
+  {
+    // decode-shaped problems: non-persistent kernel with the split-K reduction inside a cluster
+    const int bn_small = a->force_bn ? a->force_bn : pick_bn(a->M);
+    if (bn_small <= 64) {
+      int cluster = 1, st = 0;
+      const int rc_small = launch_gemm_smallm(a, bn_small, stream, &cluster, &st);
+      g_last_config = {bn_small, cluster, st};
+      return rc_small;
     }
   }
+  GemmPlan pl;
+  const int prc = plan_gemm(a->M, a->N, a->K, dual, a->force_bn, a->force_splits, a->workspace ? a->workspace_bytes : 0, &pl);
+  if (prc != 0) return prc;
+  const int bn = pl.bn, num_kb = pl.num_kb, tiles_m = pl.tiles_m, grid = pl.grid, max_contrib = pl.max_contrib;
+  const int64_t tiles = pl.tiles;
+  const bool tile_aligned = pl.tile_aligned;
 
   CUtensorMap tw, tx;
   const CUtensorMapDataType dt = a->dtype == ORTB200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
@@ -406,33 +523,40 @@ extern "C" int ortb200_gemm(const ortb200_gemm_args* a, ortb200_stream_t stream_
 
   GemmKernelParams p;
   p.M = a->M; p.N = a->N; p.K = a->K;
-  p.num_kb = num_kb; p.kb_per_split = kb_per_split; p.splits = splits;
+  p.num_kb = num_kb; p.tiles = static_cast<int>(tiles); p.tiles_m = tiles_m;
+  p.tile_aligned = tile_aligned ? 1 : 0; p.max_contrib = max_contrib;
   p.dual_offset = a->dual_offset; p.dtype = a->dtype; p.act = a->act; p.alpha = a->alpha;
   p.out = a->out; p.ldo = a->ldo; p.bias = a->bias; p.residual = a->residual; p.ldr = a->ldr;
-  p.ws = ws; p.counters = counters; p.status = a->status;
+  p.counters = reinterpret_cast<unsigned int*>(a->workspace);
+  p.ws = a->workspace ? reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(a->workspace) + 65536) : nullptr;
+  p.status = a->status;
 
-  dim3 grid(tiles_n, tiles_m, splits);
   const bool pdl = a->use_pdl != 0;
   int stages = 0;
   int rc = -7;
-#define ORTB200_LAUNCH(BN_, ST_)                                                        \
-  do {                                                                                  \
-    stages = ST_;                                                                       \
-    rc = dual ? launch_gemm<BN_, (ST_ * (16384 * 2 + BN_ * 128) <= 200 * 1024 ? ST_ : ST_ / 2), true>(tw, tx, p, grid, stream, pdl) \
-              : launch_gemm<BN_, ST_, false>(tw, tx, p, grid, stream, pdl);             \
-  } while (0)
   switch (bn) {
-    case 16: ORTB200_LAUNCH(16, 6); break;
-    case 32: ORTB200_LAUNCH(32, 6); break;
-    case 64: ORTB200_LAUNCH(64, 6); break;
-    case 128: ORTB200_LAUNCH(128, 6); break;
+    case 16:
+      if (dual) { stages = 6; rc = launch_gemm<16, 6, true>(tw, tx, p, grid, stream, pdl); }
+      else { stages = 10; rc = launch_gemm<16, 10, false>(tw, tx, p, grid, stream, pdl); }
+      break;
+    case 32:
+      if (dual) { stages = 5; rc = launch_gemm<32, 5, true>(tw, tx, p, grid, stream, pdl); }
+      else { stages = 9; rc = launch_gemm<32, 9, false>(tw, tx, p, grid, stream, pdl); }
+      break;
+    case 64:
+      if (dual) { stages = 5; rc = launch_gemm<64, 5, true>(tw, tx, p, grid, stream, pdl); }
+      else { stages = 8; rc = launch_gemm<64, 8, false>(tw, tx, p, grid, stream, pdl); }
+      break;
+    case 128:
+      if (dual) { stages = 4; rc = launch_gemm<128, 4, true>(tw, tx, p, grid, stream, pdl); }
+      else { stages = 6; rc = launch_gemm<128, 6, false>(tw, tx, p, grid, stream, pdl); }
+      break;
     case 256:
       stages = 4;
       rc = launch_gemm<256, 4, false>(tw, tx, p, grid, stream, pdl);
       break;
     default: return -8;
   }
-#undef ORTB200_LAUNCH
-  g_last_config = {bn, splits, stages};
+  g_last_config = {bn, tile_aligned ? 1 : max_contrib, stages};
   return rc;
 }

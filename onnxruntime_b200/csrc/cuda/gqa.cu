@@ -36,7 +36,11 @@ __global__ void __launch_bounds__(256) gqa_prep_kernel(const ortb200_gqa_prep_ar
   const long long tok = static_cast<long long>(b) * a.S + s;
   const T* cosr = a.do_rotary ? static_cast<const T*>(a.cos_cache) + pos * half : nullptr;
   const T* sinr = a.do_rotary ? static_cast<const T*>(a.sin_cache) + pos * half : nullptr;
-  for (int idx = threadIdx.x; idx < heads * halfH; idx += blockDim.x) {
+  // blockIdx.y selects a group of heads so that few tokens still fill the machine
+  const int heads_per_block = (heads + gridDim.y - 1) / gridDim.y;
+  const int head_lo = blockIdx.y * heads_per_block;
+  const int head_hi = min(heads, head_lo + heads_per_block);
+  for (int idx = head_lo * halfH + threadIdx.x; idx < head_hi * halfH; idx += blockDim.x) {
     const int head = idx / halfH, i = idx % halfH;
     const T* src;
     if (a.k != nullptr) {
@@ -92,19 +96,26 @@ struct DecodeParams {
   void* out;
   float* ws;
   unsigned int* counters;
+  int* status;
   int B, N, Nk, Smax, splits, window, gparts;
   float scale, softcap;
 };
 
+// Running maxima start at a large negative finite value so that exp(m_old - m_new) never sees inf - inf.
+constexpr float kNegBig = -1.0e30f;
 __device__ __forceinline__ float safe_exp_diff(float a, float b) {
-  // exp(a - b) with a = -inf treated as 0 even when b = -inf
-  return a == -INFINITY ? 0.f : __expf(a - b);
+  return a <= kNegBig ? 0.f : __expf(a - b);
 }
+
+constexpr int kDecTile = 32;    // keys per pipeline stage
+constexpr int kDecStages = 4;
 
 template <typename T, int H, int G>
 __global__ void __launch_bounds__(128) gqa_decode_kernel(const DecodeParams p) {
   constexpr int DPL = H / 8;          // dims per lane (8 lanes share a key)
   constexpr int VEC = DPL * sizeof(T) / 16;  // 16-byte loads per lane per row
+  constexpr int kRowBytes = H * sizeof(T);
+  constexpr int kTileBytes = kDecTile * kRowBytes;
   static_assert(VEC >= 1, "head size too small");
   const int split = blockIdx.x;
   const int kvh = blockIdx.y / p.gparts, gp = blockIdx.y % p.gparts;
@@ -115,9 +126,20 @@ __global__ void __launch_bounds__(128) gqa_decode_kernel(const DecodeParams p) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int slot = lane >> 3, sub = lane & 7, d0 = sub * DPL;
 
-  __shared__ float sm_m[4][G], sm_l[4][G];
-  __shared__ float sm_acc[4][G][H];
+  // K/V tiles stream through shared memory with bulk asynchronous copies (kDecStages tiles in flight per CTA)
+  extern __shared__ __align__(128) uint8_t dec_smem[];
+  uint8_t* stage_base = dec_smem;                                             // [stages][K tile | V tile]
+  float* sm_acc = reinterpret_cast<float*>(dec_smem + kDecStages * 2 * kTileBytes);  // [4][G][H]
+  float* sm_m = sm_acc + 4 * G * H;                                            // [4][G]
+  float* sm_l = sm_m + 4 * G;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(sm_l + 4 * G);
   __shared__ unsigned int sm_last;
+
+  if (tid == 0) {
+    for (int i = 0; i < kDecStages; ++i) mbar_init(&full_bar[i], 1);
+    fence_mbar_init();
+  }
+  __syncthreads();
 
   pdl_wait_prior_grids();
   const int total = p.seqlens_k[b] + 1;
@@ -126,6 +148,25 @@ __global__ void __launch_bounds__(128) gqa_decode_kernel(const DecodeParams p) {
   const int chunk = (len + p.splits - 1) / p.splits;
   const int k_begin = start0 + split * chunk;
   const int k_end = min(total, k_begin + chunk);
+  const int n_tiles = k_end > k_begin ? (k_end - k_begin + kDecTile - 1) / kDecTile : 0;
+
+  const T* kbase = static_cast<const T*>(p.k_cache) + (static_cast<long long>(b) * p.Nk + kvh) * p.Smax * H;
+  const T* vbase = static_cast<const T*>(p.v_cache) + (static_cast<long long>(b) * p.Nk + kvh) * p.Smax * H;
+
+  auto issue_tile = [&](int t) {
+    const int s = t % kDecStages;
+    const int key0 = k_begin + t * kDecTile;
+    const int rows = min(kDecTile, k_end - key0);
+    const uint32_t bytes = static_cast<uint32_t>(rows) * kRowBytes;
+    uint8_t* dst = stage_base + s * 2 * kTileBytes;
+    mbar_expect_tx(&full_bar[s], 2 * bytes);
+    bulk_load(dst, kbase + static_cast<long long>(key0) * H, bytes, &full_bar[s]);
+    bulk_load(dst + kTileBytes, vbase + static_cast<long long>(key0) * H, bytes, &full_bar[s]);
+  };
+  if (tid == 0) {
+    const int pre = n_tiles < kDecStages ? n_tiles : kDecStages;
+    for (int t = 0; t < pre; ++t) issue_tile(t);
+  }
 
   float qf[G][DPL];
 #pragma unroll
@@ -137,65 +178,85 @@ __global__ void __launch_bounds__(128) gqa_decode_kernel(const DecodeParams p) {
   float m[G], l[G], acc[G][DPL];
 #pragma unroll
   for (int g = 0; g < G; ++g) {
-    m[g] = -INFINITY;
+    m[g] = kNegBig;
     l[g] = 0.f;
 #pragma unroll
     for (int i = 0; i < DPL; ++i) acc[g][i] = 0.f;
   }
 
-  const T* kbase = static_cast<const T*>(p.k_cache) + (static_cast<long long>(b) * p.Nk + kvh) * p.Smax * H + d0;
-  const T* vbase = static_cast<const T*>(p.v_cache) + (static_cast<long long>(b) * p.Nk + kvh) * p.Smax * H + d0;
-
-  // Two keys per 8-lane group in flight.  The trip count is uniform across the warp (shuffles name all
-  // 32 lanes); keys past the end are masked out of the state update.
-  for (int base = k_begin + warp * 4; base < k_end; base += 32) {
-    const int keys[2] = {base + slot, base + slot + 16};
-    const bool valid[2] = {keys[0] < k_end, keys[1] < k_end};
-    uint4 kr[2][VEC], vr[2][VEC];
+  bool ok = true;
+  for (int t = 0; t < n_tiles; ++t) {
+    const int s = t % kDecStages;
+    if (ok && !mbar_wait(&full_bar[s], (t / kDecStages) & 1)) ok = false;  // bounded; a failed wait skips the math below
+    const uint8_t* ktile = stage_base + s * 2 * kTileBytes;
+    const uint8_t* vtile = ktile + kTileBytes;
+    const int key0 = k_begin + t * kDecTile;
+    // 16 key slots per CTA (4 warps x 4 lane groups), two keys per slot per tile.  Everything below is
+    // branch-free so that the 2 x G dot-product / shuffle / exp chains overlap (the loop is latency-bound).
+    float kf[2][DPL], vf[2][DPL];
+    bool valid[2];
 #pragma unroll
     for (int u = 0; u < 2; ++u) {
+      const int row = u * 16 + warp * 4 + slot;
+      valid[u] = ok && (key0 + row) < k_end;
+      const int rr = valid[u] ? row : 0;  // row 0 of a started tile always holds data
 #pragma unroll
       for (int v = 0; v < VEC; ++v) {
-        if (valid[u]) {
-          kr[u][v] = *reinterpret_cast<const uint4*>(kbase + static_cast<long long>(keys[u]) * H + v * (16 / sizeof(T)));
-          vr[u][v] = *reinterpret_cast<const uint4*>(vbase + static_cast<long long>(keys[u]) * H + v * (16 / sizeof(T)));
-        } else {
-          kr[u][v] = make_uint4(0, 0, 0, 0);
-          vr[u][v] = make_uint4(0, 0, 0, 0);
+        const uint4 kq = *reinterpret_cast<const uint4*>(ktile + rr * kRowBytes + d0 * sizeof(T) + v * 16);
+        const uint4 vq = *reinterpret_cast<const uint4*>(vtile + rr * kRowBytes + d0 * sizeof(T) + v * 16);
+        const T* kp = reinterpret_cast<const T*>(&kq);
+        const T* vp = reinterpret_cast<const T*>(&vq);
+#pragma unroll
+        for (int i = 0; i < 16 / static_cast<int>(sizeof(T)); ++i) {
+          kf[u][v * (16 / sizeof(T)) + i] = to_float<T>(kp[i]);
+          vf[u][v * (16 / sizeof(T)) + i] = to_float<T>(vp[i]);
         }
       }
     }
+    float sc[2][G];
 #pragma unroll
     for (int u = 0; u < 2; ++u) {
-      const T* kp = reinterpret_cast<const T*>(&kr[u][0]);
-      const T* vp = reinterpret_cast<const T*>(&vr[u][0]);
-      float kf[DPL], vf[DPL];
-#pragma unroll
-      for (int i = 0; i < DPL; ++i) {
-        kf[i] = to_float<T>(kp[i]);
-        vf[i] = to_float<T>(vp[i]);
-      }
 #pragma unroll
       for (int g = 0; g < G; ++g) {
-        float s = 0.f;
+        float a0 = 0.f, a1 = 0.f;  // two partial sums halve the FMA dependency chain
 #pragma unroll
-        for (int i = 0; i < DPL; ++i) s += qf[g][i] * kf[i];
-        s += __shfl_xor_sync(0xffffffffu, s, 1);
-        s += __shfl_xor_sync(0xffffffffu, s, 2);
-        s += __shfl_xor_sync(0xffffffffu, s, 4);
-        if (valid[u]) {
-          if (p.softcap > 0.f) s = p.softcap * tanhf(s / p.softcap);
-          const float m_new = fmaxf(m[g], s);
-          const float corr = safe_exp_diff(m[g], m_new);
-          const float pr = __expf(s - m_new);
-          l[g] = l[g] * corr + pr;
-#pragma unroll
-          for (int i = 0; i < DPL; ++i) acc[g][i] = acc[g][i] * corr + pr * vf[i];
-          m[g] = m_new;
+        for (int i = 0; i < DPL; i += 2) {
+          a0 += qf[g][i] * kf[u][i];
+          a1 += qf[g][i + 1] * kf[u][i + 1];
         }
+        sc[u][g] = a0 + a1;
       }
     }
+#pragma unroll
+    for (int off = 1; off <= 4; off <<= 1) {
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+#pragma unroll
+        for (int g = 0; g < G; ++g) sc[u][g] += __shfl_xor_sync(0xffffffffu, sc[u][g], off);
+      }
+    }
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      float s0 = sc[0][g], s1 = sc[1][g];
+      if (p.softcap > 0.f) {
+        s0 = p.softcap * tanhf(s0 / p.softcap);
+        s1 = p.softcap * tanhf(s1 / p.softcap);
+      }
+      s0 = valid[0] ? s0 : kNegBig;
+      s1 = valid[1] ? s1 : kNegBig;
+      const float m_new = fmaxf(m[g], fmaxf(s0, s1));
+      const float corr = __expf(m[g] - m_new);
+      const float p0 = valid[0] ? __expf(s0 - m_new) : 0.f;
+      const float p1 = valid[1] ? __expf(s1 - m_new) : 0.f;
+      l[g] = l[g] * corr + p0 + p1;
+#pragma unroll
+      for (int i = 0; i < DPL; ++i) acc[g][i] = acc[g][i] * corr + p0 * vf[0][i] + p1 * vf[1][i];
+      m[g] = m_new;
+    }
+    __syncthreads();  // every warp is done with stage s
+    if (tid == 0 && ok && t + kDecStages < n_tiles) issue_tile(t + kDecStages);
   }
+  if (!ok && tid == 0 && p.status) atomicExch(p.status, kStatusTimeoutEpilogue);
 
   // merge the 4 key slots of a warp (lanes differing in bits 3 and 4)
 #pragma unroll
@@ -219,11 +280,11 @@ __global__ void __launch_bounds__(128) gqa_decode_kernel(const DecodeParams p) {
 #pragma unroll
     for (int g = 0; g < G; ++g) {
       if (sub == 0) {
-        sm_m[warp][g] = m[g];
-        sm_l[warp][g] = l[g];
+        sm_m[warp * G + g] = m[g];
+        sm_l[warp * G + g] = l[g];
       }
 #pragma unroll
-      for (int i = 0; i < DPL; ++i) sm_acc[warp][g][d0 + i] = acc[g][i];
+      for (int i = 0; i < DPL; ++i) sm_acc[(warp * G + g) * H + d0 + i] = acc[g][i];
     }
   }
   __syncthreads();
@@ -234,15 +295,15 @@ __global__ void __launch_bounds__(128) gqa_decode_kernel(const DecodeParams p) {
   float fm[G], fl[G], fa[G];
 #pragma unroll
   for (int g = 0; g < G; ++g) {
-    float mm = -INFINITY;
+    float mm = kNegBig;
 #pragma unroll
-    for (int w = 0; w < 4; ++w) mm = fmaxf(mm, sm_m[w][g]);
+    for (int w = 0; w < 4; ++w) mm = fmaxf(mm, sm_m[w * G + g]);
     float ll = 0.f, aa = 0.f;
 #pragma unroll
     for (int w = 0; w < 4; ++w) {
-      const float c = safe_exp_diff(sm_m[w][g], mm);
-      ll += sm_l[w][g] * c;
-      if (owner) aa += sm_acc[w][g][tid] * c;
+      const float c = safe_exp_diff(sm_m[w * G + g], mm);
+      ll += sm_l[w * G + g] * c;
+      if (owner) aa += sm_acc[(w * G + g) * H + tid] * c;
     }
     fm[g] = mm;
     fl[g] = ll;
@@ -276,7 +337,7 @@ __global__ void __launch_bounds__(128) gqa_decode_kernel(const DecodeParams p) {
       const float* base = p.ws + (static_cast<size_t>(tile) * p.splits * G) * (H + 2);
 #pragma unroll
       for (int g = 0; g < G; ++g) {
-        float mm = -INFINITY;
+        float mm = kNegBig;
         for (int s = 0; s < p.splits; ++s) mm = fmaxf(mm, __ldcg(&base[(s * G + g) * (H + 2) + H]));
         float ll = 0.f, aa = 0.f;
         for (int s = 0; s < p.splits; ++s) {
@@ -310,6 +371,30 @@ __global__ void __launch_bounds__(128) gqa_decode_kernel(const DecodeParams p) {
   }
 }
 
+template <typename T, int H, int G>
+static int launch_decode_g(const DecodeParams& p, dim3 grid, cudaStream_t stream, bool use_pdl) {
+  constexpr int kSmem = kDecStages * 2 * kDecTile * H * static_cast<int>(sizeof(T)) + (4 * G * H + 8 * G) * 4 + 8 * kDecStages;
+  auto kern = gqa_decode_kernel<T, H, G>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) != cudaSuccess) return -10;
+    attr_set = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(128, 1, 1);
+  cfg.dynamicSmemBytes = kSmem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attrs[1];
+  if (use_pdl) {
+    attrs[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attrs;
+    cfg.numAttrs = 1;
+  }
+  return cudaLaunchKernelEx(&cfg, kern, p) == cudaSuccess ? 0 : -11;
+}
+
 template <typename T, int H>
 static int launch_decode(const ortb200_gqa_decode_args* a, cudaStream_t stream) {
   const int group = a->N / a->Nk;
@@ -317,9 +402,10 @@ static int launch_decode(const ortb200_gqa_decode_args* a, cudaStream_t stream) 
   const int gparts = (group + G - 1) / G;
   int splits = a->splits;
   if (splits <= 0) {
+    // about three resident CTAs per SM, but at least two key tiles per CTA at full cache occupancy
     const int ctas = a->B * a->Nk * gparts;
-    splits = (2 * 148 + ctas - 1) / ctas;
-    const int max_by_len = (a->Smax + 63) / 64;
+    splits = (2 * 148) / ctas;  // one wave of (register-limited) two CTAs per SM
+    const int max_by_len = (a->Smax + 2 * kDecTile - 1) / (2 * kDecTile);
     if (splits > max_by_len) splits = max_by_len;
     if (splits > 32) splits = 32;
     if (splits < 1) splits = 1;
@@ -332,26 +418,14 @@ static int launch_decode(const ortb200_gqa_decode_args* a, cudaStream_t stream) 
   p.out = a->out;
   p.counters = reinterpret_cast<unsigned int*>(a->workspace);
   p.ws = a->workspace ? reinterpret_cast<float*>(static_cast<char*>(a->workspace) + 65536) : nullptr;
+  p.status = a->status;
   p.B = a->B; p.N = a->N; p.Nk = a->Nk; p.Smax = a->Smax; p.splits = splits; p.window = a->window; p.gparts = gparts;
   p.scale = a->scale != 0.f ? a->scale : 1.0f / sqrtf(static_cast<float>(H));
   p.softcap = a->softcap;
   dim3 grid(splits, a->Nk * gparts, a->B);
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = grid;
-  cfg.blockDim = dim3(128, 1, 1);
-  cfg.stream = stream;
-  cudaLaunchAttribute attrs[1];
-  if (a->use_pdl) {
-    attrs[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attrs[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attrs;
-    cfg.numAttrs = 1;
-  }
-  cudaError_t e;
-  if (G == 4) e = cudaLaunchKernelEx(&cfg, gqa_decode_kernel<T, H, 4>, p);
-  else if (G == 2) e = cudaLaunchKernelEx(&cfg, gqa_decode_kernel<T, H, 2>, p);
-  else e = cudaLaunchKernelEx(&cfg, gqa_decode_kernel<T, H, 1>, p);
-  return e == cudaSuccess ? 0 : -11;
+  if (G == 4) return launch_decode_g<T, H, 4>(p, grid, stream, a->use_pdl != 0);
+  if (G == 2) return launch_decode_g<T, H, 2>(p, grid, stream, a->use_pdl != 0);
+  return launch_decode_g<T, H, 1>(p, grid, stream, a->use_pdl != 0);
 }
 
 }  // namespace ortb200
@@ -385,9 +459,16 @@ extern "C" int ortb200_gqa_prep(const ortb200_gqa_prep_args* a, ortb200_stream_t
   if ((a->k != nullptr) != (a->v != nullptr)) return -2;
   const int rot = a->rot_dim > 0 ? a->rot_dim : a->H;
   if (rot > a->H || rot % 2 != 0) return -2;
-  dim3 grid(static_cast<unsigned>(a->B) * a->S);
-  if (a->dtype == ORTB200_BF16) gqa_prep_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(*a);
-  else if (a->dtype == ORTB200_F16) gqa_prep_kernel<__half><<<grid, 256, 0, stream>>>(*a);
+  const int tokens = a->B * a->S, heads = a->N + 2 * a->Nk;
+  int ygroups = 1;
+  if (tokens < 296) {
+    ygroups = (296 + tokens - 1) / tokens;
+    if (ygroups > heads) ygroups = heads;
+  }
+  dim3 grid(static_cast<unsigned>(tokens), static_cast<unsigned>(ygroups));
+  const int threads = ygroups > 1 ? 128 : 256;
+  if (a->dtype == ORTB200_BF16) gqa_prep_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(*a);
+  else if (a->dtype == ORTB200_F16) gqa_prep_kernel<__half><<<grid, threads, 0, stream>>>(*a);
   else return -4;
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }

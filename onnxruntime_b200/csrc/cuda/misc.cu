@@ -25,50 +25,51 @@ __global__ void gather_rows_kernel(const uint4* __restrict__ table, const int64_
   pdl_launch_dependents();
 }
 
+// Orderable 64-bit key: larger value wins, ties go to the smaller index.
+__device__ __forceinline__ unsigned long long argmax_key(float v, long long idx) {
+  unsigned int u = __float_as_uint(v);
+  u = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+  return (static_cast<unsigned long long>(u) << 32) | static_cast<unsigned long long>(0xFFFFFFFFu - static_cast<unsigned int>(idx));
+}
+
+// grid (chunks, rows).  Each CTA reduces its chunk, merges into ws[row] with a 64-bit atomicMax, and the CTA
+// that arrives last on counters[row] writes the index and leaves ws / counters zeroed for the next launch.
 template <typename T>
-__global__ void __launch_bounds__(1024) argmax_kernel(const T* __restrict__ x, int64_t* __restrict__ out, int64_t n) {
-  __shared__ float sv[32];
-  __shared__ int64_t si[32];
+__global__ void __launch_bounds__(256) argmax_kernel(const T* __restrict__ x, int64_t* __restrict__ out, int64_t n,
+                                                     unsigned long long* __restrict__ ws, unsigned int* __restrict__ counters) {
+  __shared__ unsigned long long sk[8];
   pdl_wait_prior_grids();
-  const T* row = x + static_cast<int64_t>(blockIdx.x) * n;
-  float best = -INFINITY;
-  int64_t best_i = 0x7fffffffffffffffLL;
-  for (int64_t i = threadIdx.x; i < n; i += blockDim.x) {
+  const int64_t rowi = blockIdx.y;
+  const T* row = x + rowi * n;
+  const int64_t per = (n + gridDim.x - 1) / gridDim.x;
+  const int64_t lo = blockIdx.x * per, hi = lo + per < n ? lo + per : n;
+  unsigned long long best = 0;
+  for (int64_t i = lo + threadIdx.x; i < hi; i += blockDim.x) {
     const float v = to_float<T>(row[i]);
-    if (v > best || (v == best && i < best_i)) {
-      best = v;
-      best_i = i;
+    if (v == v) {  // NaN never wins
+      const unsigned long long k = argmax_key(v, i);
+      best = k > best ? k : best;
     }
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
-    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-    const int64_t oi = __shfl_xor_sync(0xffffffffu, best_i, o);
-    if (ov > best || (ov == best && oi < best_i)) {
-      best = ov;
-      best_i = oi;
-    }
+    const unsigned long long ok = __shfl_xor_sync(0xffffffffu, best, o);
+    best = ok > best ? ok : best;
   }
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  if (lane == 0) {
-    sv[warp] = best;
-    si[warp] = best_i;
-  }
+  if (lane == 0) sk[warp] = best;
   __syncthreads();
-  if (warp == 0) {
-    const int nw = blockDim.x >> 5;
-    best = lane < nw ? sv[lane] : -INFINITY;
-    best_i = lane < nw ? si[lane] : 0x7fffffffffffffffLL;
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-      const int64_t oi = __shfl_xor_sync(0xffffffffu, best_i, o);
-      if (ov > best || (ov == best && oi < best_i)) {
-        best = ov;
-        best_i = oi;
-      }
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < (blockDim.x >> 5); ++w) best = sk[w] > best ? sk[w] : best;
+    atomicMax(&ws[rowi], best);
+    __threadfence();
+    const unsigned int old = atomicAdd(&counters[rowi], 1u);
+    if (old == gridDim.x - 1) {
+      __threadfence();
+      const unsigned long long k = atomicExch(&ws[rowi], 0ull);
+      counters[rowi] = 0;
+      out[rowi] = k == 0 ? 0 : static_cast<int64_t>(0xFFFFFFFFu - static_cast<unsigned int>(k & 0xFFFFFFFFull));
     }
-    if (lane == 0) out[blockIdx.x] = best_i == 0x7fffffffffffffffLL ? 0 : best_i;
   }
   pdl_launch_dependents();
 }
@@ -161,14 +162,24 @@ extern "C" int ortb200_gather_rows(const void* table, const int64_t* ids, void* 
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
-extern "C" int ortb200_argmax(const void* x, int64_t* out, int64_t rows, int64_t n, int dtype, ortb200_stream_t stream) {
-  if (!x || !out || rows < 0 || n <= 0) return -1;
+extern "C" int64_t ortb200_argmax_workspace_bytes(int64_t rows) { return rows * 16; }
+
+extern "C" int ortb200_argmax(const void* x, int64_t* out, int64_t rows, int64_t n, int dtype, void* workspace,
+                              int64_t workspace_bytes, ortb200_stream_t stream) {
+  if (!x || !out || rows < 0 || n <= 0 || n > 0xFFFFFFFFll) return -1;
   if (rows == 0) return 0;
+  if (!workspace || workspace_bytes < rows * 16 || (reinterpret_cast<uintptr_t>(workspace) & 7)) return -3;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const unsigned g = static_cast<unsigned>(rows);
-  if (dtype == ORTB200_BF16) argmax_kernel<__nv_bfloat16><<<g, 1024, 0, st>>>(static_cast<const __nv_bfloat16*>(x), out, n);
-  else if (dtype == ORTB200_F16) argmax_kernel<__half><<<g, 1024, 0, st>>>(static_cast<const __half*>(x), out, n);
-  else if (dtype == ORTB200_F32) argmax_kernel<float><<<g, 1024, 0, st>>>(static_cast<const float*>(x), out, n);
+  unsigned long long* ws = static_cast<unsigned long long*>(workspace);
+  unsigned int* counters = reinterpret_cast<unsigned int*>(ws + rows);
+  int chunks = static_cast<int>((n + 4095) / 4096);
+  const int64_t want = (2 * 148 + rows - 1) / rows;
+  if (chunks > want) chunks = static_cast<int>(want);
+  if (chunks < 1) chunks = 1;
+  dim3 g(static_cast<unsigned>(chunks), static_cast<unsigned>(rows));
+  if (dtype == ORTB200_BF16) argmax_kernel<__nv_bfloat16><<<g, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), out, n, ws, counters);
+  else if (dtype == ORTB200_F16) argmax_kernel<__half><<<g, 256, 0, st>>>(static_cast<const __half*>(x), out, n, ws, counters);
+  else if (dtype == ORTB200_F32) argmax_kernel<float><<<g, 256, 0, st>>>(static_cast<const float*>(x), out, n, ws, counters);
   else return -4;
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }

@@ -127,6 +127,7 @@ typedef struct {
   float softcap;
   int dtype;
   int use_pdl;
+  int* status;            // device int, may be null (bounded waits report here)
 } ortb200_gqa_decode_args;
 int ortb200_gqa_decode(const ortb200_gqa_decode_args* args, ortb200_stream_t stream);
 int64_t ortb200_gqa_decode_workspace_bytes(int B, int N, int H);
@@ -165,8 +166,11 @@ int ortb200_attn_prefill(const ortb200_attn_prefill_args* args, ortb200_stream_t
 // rows of `table` [vocab, hidden] selected by int64 ids -> out [n, hidden]
 int ortb200_gather_rows(const void* table, const int64_t* ids, void* out, int64_t n, int64_t vocab, int hidden,
                         int elem_bytes, ortb200_stream_t stream);
-// argmax over the last dimension: x [rows, n] -> out int64 [rows] (first maximum wins)
-int ortb200_argmax(const void* x, int64_t* out, int64_t rows, int64_t n, int dtype, ortb200_stream_t stream);
+// argmax over the last dimension: x [rows, n] -> out int64 [rows] (first maximum wins).  `workspace` holds
+// ortb200_argmax_workspace_bytes(rows) bytes, zero before the first launch; the kernel leaves it zero.
+int ortb200_argmax(const void* x, int64_t* out, int64_t rows, int64_t n, int dtype, void* workspace,
+                   int64_t workspace_bytes, ortb200_stream_t stream);
+int64_t ortb200_argmax_workspace_bytes(int64_t rows);
 // y = act(x + bias[col]) elementwise; bias optional, cols = last dimension
 int ortb200_bias_act(const void* x, const void* bias, void* y, int64_t rows, int cols, int act, float alpha, int dtype,
                      ortb200_stream_t stream);

@@ -160,7 +160,7 @@ class GqaDecodeArgs(ctypes.Structure):
                 ("workspace", ctypes.c_void_p), ("workspace_bytes", ctypes.c_int64), ("B", ctypes.c_int), ("N", ctypes.c_int),
                 ("Nk", ctypes.c_int), ("H", ctypes.c_int), ("Smax", ctypes.c_int), ("splits", ctypes.c_int),
                 ("window", ctypes.c_int), ("scale", ctypes.c_float), ("softcap", ctypes.c_float), ("dtype", ctypes.c_int),
-                ("use_pdl", ctypes.c_int)]
+                ("use_pdl", ctypes.c_int), ("status", ctypes.c_void_p)]
 
 
 _ATTN_WS = {}
@@ -178,7 +178,7 @@ def gqa_decode(q, k_cache, v_cache, seqlens_k, splits=0, window=-1, scale=0.0, s
         ws = torch.zeros(need, dtype=torch.uint8, device=q.device)
         _ATTN_WS[key] = ws
     a = GqaDecodeArgs(_ptr(q.contiguous()), _ptr(k_cache), _ptr(v_cache), _ptr(seqlens_k), _ptr(head_sink), _ptr(out), _ptr(ws),
-                      ws.numel(), B, N, Nk, H, Smax, splits, window, scale, softcap, dtype_code(q.dtype), 0)
+                      ws.numel(), B, N, Nk, H, Smax, splits, window, scale, softcap, dtype_code(q.dtype), 0, None)
     _check(lib().ortb200_gqa_decode(ctypes.byref(a), ctypes.c_void_p(stream_ptr())), "ortb200_gqa_decode")
     return out
 
@@ -216,8 +216,10 @@ def argmax(x):
     x = x.contiguous()
     rows, n = x.numel() // x.shape[-1], x.shape[-1]
     out = torch.empty(x.shape[:-1], dtype=torch.int64, device=x.device)
+    ws = torch.zeros(rows * 16, dtype=torch.uint8, device=x.device)
     _check(lib().ortb200_argmax(ctypes.c_void_p(_ptr(x)), ctypes.c_void_p(_ptr(out)), ctypes.c_int64(rows), ctypes.c_int64(n),
-                                dtype_code(x.dtype), ctypes.c_void_p(stream_ptr())), "ortb200_argmax")
+                                dtype_code(x.dtype), ctypes.c_void_p(_ptr(ws)), ctypes.c_int64(ws.numel()),
+                                ctypes.c_void_p(stream_ptr())), "ortb200_argmax")
     return out
 
 
