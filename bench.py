@@ -114,6 +114,7 @@ def main():
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--pdl", type=int, default=1)
     ap.add_argument("--ttft-repeats", type=int, default=3)
+    ap.add_argument("--fused-collectives", type=int, default=1, help="0: NCCL all-reduce after each row-parallel GEMM (baseline)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -148,6 +149,10 @@ def main():
     sess = ort.InferenceSession(model, so, providers=providers, dist=info if tp > 1 else None, enable_fallback=False)
     del weights
     torch.cuda.empty_cache()
+    if tp > 1 and args.fused_collectives:
+        # peer-mapped workspace: the row-parallel GEMMs of the decode step reduce across ranks inside the kernel
+        from onnxruntime_b200.parallel import symm
+        symm.attach(sess, symm.create_workspace())
 
     runner = DecoderRunner(sess, cfg, batch=args.batch, max_len=max_len, tp_size=tp, device=device)
     gen = torch.Generator().manual_seed(1234)
@@ -242,6 +247,7 @@ def main():
             "config": {"model": "Llama-3-8B" if args.layers == 32 else f"Llama-3-8B-shaped/{args.layers}L",
                        "global_batch": args.batch, "seq_len": args.prompt, "decode_tokens": K,
                        "parallelism": f"tp{tp}", "cuda_graph": not args.no_graph,
+                       "collectives": ("in-kernel peer-store all-reduce" if args.fused_collectives else "nccl") if tp > 1 else "none",
                        "l2": "inputs larger than L2 (every step streams all weights)"},
             "e2e": {"value": round(e2e_value, 2), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": round(e2e_ms / K, 4), "wall_ms_per_step": round(wall_ms / K, 4)},

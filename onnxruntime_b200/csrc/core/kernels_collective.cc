@@ -39,16 +39,17 @@ at::Tensor AllGatherAxis(InferenceSession* s, const at::Tensor& t, int64_t axis)
   if (!pg) return t;
   const int64_t w = pg->getSize();
   at::Tensor in = t.contiguous();
+  if (in.dim() == 0) in = in.reshape({1});
+  if (axis < 0) axis += in.dim();
+  // the flat form (leading dimension multiplied by the group size) is the one every backend accepts
+  std::vector<int64_t> flat = in.sizes().vec();
+  flat[0] *= w;
+  at::Tensor out = at::empty(flat, in.options());
+  pg->_allgather_base(out, in)->wait();
+  if (axis == 0) return out;
   std::vector<int64_t> shape = in.sizes().vec();
   shape.insert(shape.begin(), w);
-  at::Tensor out = at::empty(shape, in.options());
-  pg->_allgather_base(out, in)->wait();
-  if (axis < 0) axis += t.dim();
-  if (axis == 0) {
-    shape.erase(shape.begin());
-    shape[0] *= w;
-    return out.reshape(shape);
-  }
+  out = out.reshape(shape);
   // [w, d0, .., da, ..] -> [d0, .., w*da, ..]
   return out.movedim(0, axis).flatten(axis, axis + 1).contiguous();
 }

@@ -52,7 +52,7 @@ void CheckLaunch(int rc, const char* what) {
 
 // out[M,N] = act(x[M,K] @ w_nk[N,K]^T + bias) + residual on the tcgen05 GEMM.
 at::Tensor LaunchGemm(Ctx& ctx, const at::Tensor& x2d, const at::Tensor& w_nk, int64_t n_out, int64_t dual_offset,
-                      const at::Tensor& bias, const at::Tensor& residual2d, int act, float alpha) {
+                      const at::Tensor& bias, const at::Tensor& residual2d, int act, float alpha, bool fused_allreduce) {
   InferenceSession* s = ctx.session();
   const int64_t M = x2d.size(0), K = x2d.size(1);
   at::Tensor out = at::empty({M, n_out}, x2d.options());
@@ -79,9 +79,26 @@ at::Tensor LaunchGemm(Ctx& ctx, const at::Tensor& x2d, const at::Tensor& w_nk, i
   a.workspace_bytes = ws.numel();
   a.status = s->StatusWord().data_ptr<int>();
   a.use_pdl = s->config().Get("ortb200.pdl", "0") == "1" ? 1 : 0;
+  a.world = 1;
+  if (fused_allreduce) {
+    a.world = s->world_size;
+    a.rank = s->rank;
+    for (int i = 0; i < s->world_size && i < 8; ++i) a.peers[i] = s->symm_peers[i];
+    a.symm_bytes = s->symm_bytes;
+  }
   CheckLaunch(ortb200_gemm(&a, ctx.cuda_stream()), "ortb200_gemm");
   s->AddLaunches(1);
   return out;
+}
+
+bool CanFuseAllReduce(OpKernelContext& ctx, int64_t M, int64_t N) {
+  InferenceSession* s = ctx.session();
+  if (!s || s->world_size <= 1 || s->world_size > 8) return false;
+  if (static_cast<int>(s->symm_peers.size()) != s->world_size) return false;
+  if (s->config().Get("ortb200.fused_allreduce", "1") != "1") return false;
+  if (M > 64) return false;
+  const int64_t slot = (s->symm_bytes - 262144) / (2LL * s->world_size * 4);
+  return slot >= M * N && (N + 127) / 128 * 8 <= 4096;
 }
 
 namespace {
@@ -125,7 +142,13 @@ class GemmKernel final : public OpKernel {
     at::Tensor bias = bias_idx_ >= 0 && ctx.HasInput(bias_idx_) ? ctx.Input(bias_idx_) : at::Tensor();
     at::Tensor res = residual_idx_ >= 0 && ctx.HasInput(residual_idx_) ? Flatten2D(ctx.Input(residual_idx_)) : at::Tensor();
     if (all_reduce_ && ctx.session()->world_size > 1) {
-      // row-parallel: partial product, sum over ranks, then the residual
+      if (act_ == ORTB200_ACT_NONE && CanFuseAllReduce(ctx, x2.size(0), N_)) {
+        // one kernel: tcgen05 GEMM, partial tiles pushed to every peer over NVLink, summed in rank order, + residual
+        at::Tensor y = LaunchGemm(ctx, x2, w_nk_, N_, 0, bias, res, act_, alpha_, /*fused_allreduce=*/true);
+        ctx.SetOutput(0, y.reshape(OutShape(x, N_)));
+        return;
+      }
+      // baseline: partial product, library all-reduce over the process group, then the residual
       at::Tensor y = LaunchGemm(ctx, x2, w_nk_, N_, 0, bias, at::Tensor(), act_, alpha_);
       y = GemmAllReduce(ctx, y, res);
       ctx.SetOutput(0, y.reshape(OutShape(x, N_)));

@@ -144,6 +144,10 @@ class InferenceSession {
   at::Tensor& StatusWord();
   // Check the device status word (bounded waits); throws EP_FAIL when a kernel reported a timeout.
   void CheckDeviceStatus();
+  // Symmetric workspace for the fused compute+collective kernels: base address of every rank's buffer as mapped
+  // into this process (index = rank), and its size.  Empty = not available (collectives go through the process group).
+  std::vector<void*> symm_peers;
+  int64_t symm_bytes = 0;
   std::string dist_group;  // torch.distributed group name used by collective ops ("" = default)
   int rank = 0, world_size = 1;
 

@@ -51,6 +51,19 @@ __device__ __forceinline__ float ld_dsmem(uint32_t addr) {
   return v;
 }
 
+__device__ __forceinline__ void st_release_sys(unsigned int* p, unsigned int v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
+  unsigned int v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+constexpr long long kSymmFlagsOffset = 65536;
+constexpr int kSymmFlagsPerRank = 4096;
+// a second of polling at most; then the launch reports kStatusTimeoutPeer and finishes with what it has
+constexpr unsigned int kPeerSpinLimit = 1u << 22;
+
 __device__ __forceinline__ float act_apply(int act, float v) {
   switch (act) {
     case ORTB200_ACT_GELU: return 0.5f * v * (1.0f + erff(v * 0.70710678118654752f));
@@ -215,6 +228,14 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
     const int cols_per = BN / C;
     const int j_begin = rank * cols_per;
     const uint32_t part_addr = smem_u32(part);
+    const bool fused_ar = p.world > 1;
+    unsigned int epoch = 0;
+    float* stage_local = nullptr;
+    if (fused_ar) {
+      epoch = *reinterpret_cast<volatile unsigned int*>(p.epoch) + 1;  // stable: the previous fused launch has completed
+      stage_local = reinterpret_cast<float*>(static_cast<uint8_t*>(p.peers[p.rank]) + p.staging_offset) +
+                    static_cast<long long>(epoch & 1) * p.world * p.slot_elems;
+    }
 #pragma unroll 1
     for (int jj = 0; jj < cols_per; ++jj) {
       const int j = j_begin + jj;
@@ -237,6 +258,18 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
         }
       }
       const int m = m0 + j;
+      if (fused_ar) {
+        // push this rank's partial sum to every rank (its own copy included); 128 lanes write 512 contiguous bytes
+        if (n_ok && m < p.M) {
+          const long long off = static_cast<long long>(epoch & 1) * p.world * p.slot_elems +
+                                static_cast<long long>(p.rank) * p.slot_elems + static_cast<long long>(m) * p.ldo + n;
+          for (int d = 0; d < p.world; ++d) {
+            float* dst = reinterpret_cast<float*>(static_cast<uint8_t*>(p.peers[d]) + p.staging_offset) + off;
+            *dst = v * p.alpha;
+          }
+        }
+        continue;
+      }
       if (n_ok && m < p.M) {
         float y = v * p.alpha + bias_v;
         if (DUAL) {
@@ -251,6 +284,62 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
         } else {
           if (p.residual) y += __half2float(reinterpret_cast<const __half*>(p.residual)[m * p.ldr + n]);
           reinterpret_cast<__half*>(p.out)[m * p.ldo + n] = __float2half_rn(y);
+        }
+      }
+    }
+    if (fused_ar) {
+      // publish: all 128 epilogue threads have written; one thread raises this CTA's flag on every rank
+      const int flag_idx = static_cast<int>(blockIdx.y) * static_cast<int>(gridDim.x) + static_cast<int>(blockIdx.x);
+      __threadfence_system();
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (threadIdx.x == 64) {
+        for (int d = 0; d < p.world; ++d) {
+          unsigned int* f = reinterpret_cast<unsigned int*>(static_cast<uint8_t*>(p.peers[d]) + kSymmFlagsOffset) +
+                            p.rank * kSymmFlagsPerRank + flag_idx;
+          st_release_sys(f, epoch);
+        }
+      }
+      // wait for the same tile of every rank: lane s of the first epilogue warp polls rank s
+      if (threadIdx.x >= 64 && threadIdx.x < 64 + p.world) {
+        const int src = threadIdx.x - 64;
+        const unsigned int* f = reinterpret_cast<const unsigned int*>(static_cast<uint8_t*>(p.peers[p.rank]) + kSymmFlagsOffset) +
+                                src * kSymmFlagsPerRank + flag_idx;
+        unsigned int spins = 0;
+        // epochs only grow; compare with wrap-around in mind
+        while (static_cast<int>(ld_acquire_sys(f) - epoch) < 0) {
+          if (++spins > kPeerSpinLimit) {
+            if (p.status) atomicExch(p.status, kStatusTimeoutPeer);
+            break;
+          }
+          __nanosleep(64);
+        }
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      __threadfence_system();
+#pragma unroll 1
+      for (int jj = 0; jj < cols_per; ++jj) {
+        const int m = m0 + j_begin + jj;
+        if (!(n_ok && m < p.M)) continue;
+        float y = 0.f;
+        for (int s = 0; s < p.world; ++s)
+          y += __ldcg(stage_local + static_cast<long long>(s) * p.slot_elems + static_cast<long long>(m) * p.ldo + n);
+        y = act_apply(p.act, y + bias_v);
+        if (p.dtype == ORTB200_BF16) {
+          if (p.residual) y += __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.residual)[m * p.ldr + n]);
+          reinterpret_cast<__nv_bfloat16*>(p.out)[m * p.ldo + n] = __float2bfloat16_rn(y);
+        } else {
+          if (p.residual) y += __half2float(reinterpret_cast<const __half*>(p.residual)[m * p.ldr + n]);
+          reinterpret_cast<__half*>(p.out)[m * p.ldo + n] = __float2half_rn(y);
+        }
+      }
+      // the CTA that finishes last advances the epoch for the next fused launch
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (threadIdx.x == 64) {
+        const unsigned int total = gridDim.x * gridDim.y;
+        if (atomicAdd(p.done, 1u) == total - 1) {
+          *p.done = 0;
+          __threadfence();
+          *reinterpret_cast<volatile unsigned int*>(p.epoch) = epoch;
         }
       }
     }
@@ -329,6 +418,22 @@ int launch_gemm_smallm(const ortb200_gemm_args* a, int bn, cudaStream_t stream, 
   p.M = a->M; p.N = a->N; p.K = a->K; p.num_kb = num_kb; p.cluster = cluster; p.dual_offset = a->dual_offset;
   p.dtype = a->dtype; p.act = a->act; p.alpha = a->alpha; p.out = a->out; p.ldo = a->ldo; p.bias = a->bias;
   p.residual = a->residual; p.ldr = a->ldr; p.status = a->status;
+  p.world = 1; p.rank = 0; p.staging_offset = 0; p.slot_elems = 0; p.epoch = nullptr; p.done = nullptr;
+  for (int i = 0; i < 8; ++i) p.peers[i] = nullptr;
+  if (a->world > 1) {
+    if (a->world > 8 || a->rank < 0 || a->rank >= a->world || dual || a->ldo != a->N) return -12;
+    const long long staging_off = 262144;
+    const long long slot = (a->symm_bytes - staging_off) / (2LL * a->world * 4);
+    if (slot < static_cast<long long>(a->M) * a->ldo) return -13;
+    if (static_cast<long long>(tiles_n) * cluster * tiles_m > kSymmFlagsPerRank) return -13;
+    for (int i = 0; i < a->world; ++i) {
+      if (!a->peers[i]) return -12;
+      p.peers[i] = a->peers[i];
+    }
+    p.world = a->world; p.rank = a->rank; p.staging_offset = staging_off; p.slot_elems = slot;
+    p.epoch = reinterpret_cast<unsigned int*>(a->peers[a->rank]);
+    p.done = p.epoch + 1;
+  }
   dim3 grid(tiles_n * cluster, tiles_m, 1);
   const bool pdl = a->use_pdl != 0;
   *cluster_out = cluster;

@@ -509,6 +509,7 @@ extern "C" int ortb200_gemm(const ortb200_gemm_args* a, ortb200_stream_t stream_
       return rc_small;
     }
   }
+  if (a->world > 1) return -12;  // the fused all-reduce exists for decode-shaped problems only
   GemmPlan pl;
   const int prc = plan_gemm(a->M, a->N, a->K, dual, a->force_bn, a->force_splits, a->workspace ? a->workspace_bytes : 0, &pl);
   if (prc != 0) return prc;

@@ -56,6 +56,19 @@ typedef struct {
   int force_splits;     // 0 = heuristic
   int force_bn;         // 0 = heuristic; else 16/32/64/128/256
   int use_pdl;          // launch with programmatic stream serialization
+  // Fused all-reduce (row-parallel linear): when world > 1 the kernel sums the partial products of all ranks
+  // itself.  Every rank pushes its fp32 partial tile into each peer's symmetric workspace with plain peer stores,
+  // raises a per-tile flag there (release, system scope), waits (bounded) for the flags of all ranks in its own
+  // workspace and adds the partials in rank order, then bias / residual as usual.  Requires M <= 64.
+  // peers[i] is rank i's workspace base as mapped into this process; the layout is
+  //   [0, 64 KiB)                  epoch word (offset 0), done counter (offset 4), rest reserved
+  //   [64 KiB, 64 KiB + 8 * 16 KiB) flags[world<=8][4096] uint32
+  //   [256 KiB, ...)               staging[2][world][slot] fp32, slot = (bytes - 256 KiB) / (2 * world * 4) elements
+  // The workspace must be zero before the first launch.  All ranks must launch the same sequence of fused GEMMs.
+  int world;
+  int rank;
+  void* peers[8];
+  int64_t symm_bytes;
 } ortb200_gemm_args;
 
 int ortb200_gemm(const ortb200_gemm_args* args, ortb200_stream_t stream);

@@ -53,6 +53,7 @@ class GemmArgs(ctypes.Structure):
         ("dual_offset", ctypes.c_int), ("dtype", ctypes.c_int), ("act", ctypes.c_int), ("alpha", ctypes.c_float),
         ("workspace", ctypes.c_void_p), ("workspace_bytes", ctypes.c_int64), ("status", ctypes.c_void_p),
         ("force_splits", ctypes.c_int), ("force_bn", ctypes.c_int), ("use_pdl", ctypes.c_int),
+        ("world", ctypes.c_int), ("rank", ctypes.c_int), ("peers", ctypes.c_void_p * 8), ("symm_bytes", ctypes.c_int64),
     ]
 
 
@@ -81,7 +82,7 @@ def gemm(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
          residual: Optional[torch.Tensor] = None, act: str = "none", alpha: float = 1.0,
          out: Optional[torch.Tensor] = None, n: Optional[int] = None, dual_offset: int = 0,
          force_splits: int = 0, force_bn: int = 0, status: Optional[torch.Tensor] = None,
-         use_pdl: bool = False) -> torch.Tensor:
+         use_pdl: bool = False, peers=None, rank: int = 0, symm_bytes: int = 0) -> torch.Tensor:
     """out[M, N] = act(alpha * x[M, K] @ w[N, K].T + bias) + residual  (tcgen05 kernel)."""
     assert x.is_cuda and w.is_cuda and x.dtype == w.dtype and x.dim() == 2 and w.dim() == 2
     assert x.is_contiguous() and w.is_contiguous()
@@ -98,7 +99,9 @@ def gemm(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
     a = GemmArgs(_ptr(x), _ptr(w), _ptr(out), _ptr(bias), _ptr(residual), out.stride(0),
                  residual.stride(0) if residual is not None else 0, M, n, K, w_rows, dual_offset,
                  dtype_code(x.dtype), ACT[act], alpha, _ptr(ws), ws.numel(), _ptr(status), force_splits, force_bn,
-                 1 if use_pdl else 0)
+                 1 if use_pdl else 0, len(peers) if peers else 1, rank,
+                 (ctypes.c_void_p * 8)(*(list(peers) + [None] * (8 - len(peers)))) if peers else (ctypes.c_void_p * 8)(),
+                 symm_bytes)
     rc = lib().ortb200_gemm(ctypes.byref(a), ctypes.c_void_p(stream_ptr()))
     if rc != 0:
         raise RuntimeError(f"ortb200_gemm rejected its arguments (code {rc})")

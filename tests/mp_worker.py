@@ -1,0 +1,180 @@
+"""Worker launched by torch.distributed.run from the multi-process tests (one process per rank).
+
+usage: mp_worker.py <case> <device: cpu|cuda> <out_dir>
+Each case writes `<out_dir>/rank<r>.pt` with its results; the parent test compares them.
+"""
+import os
+import sys
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+import onnxruntime_b200 as ort  # noqa: E402
+from onnxruntime_b200 import onnx_lite as ol  # noqa: E402
+from onnxruntime_b200.parallel.dist import init_distributed  # noqa: E402
+
+T = ol.TensorProto
+
+
+def session(model, info, device, **kw):
+    providers = ["CPUExecutionProvider"] if device == "cpu" else [("CUDAExecutionProvider", {"device_id": str(info.local_rank)})]
+    return ort.InferenceSession(model, providers=providers, dist=info, enable_fallback=False, **kw)
+
+
+def case_collectives(info, device, out):
+    r, w = info.rank, info.world_size
+    x = np.arange(8, dtype=np.float32).reshape(4, 2) + 10 * r
+    res = {}
+    for op, attrs in (("AllReduce", {}), ("AllGather", {"axis": 0, "group_size": w}), ("AllGather", {"axis": 1, "group_size": w}),
+                      ("AllToAll", {"group_size": w})):
+        g = ol.make_graph([ol.make_node(op, ["x"], ["y"], domain="com.microsoft", **attrs)], "g",
+                          [ol.make_tensor_value_info("x", T.FLOAT, [4, 2])], [ol.make_tensor_value_info("y", T.FLOAT, None)])
+        s = session(ol.make_model(g).serialize(), info, device)
+        res[f"{op}{attrs.get('axis', '')}"] = torch.from_numpy(s.run(None, {"x": x})[0])
+    torch.save(res, os.path.join(out, f"rank{r}.pt"))
+
+
+def case_distributed_matmul(info, device, out):
+    r, w = info.rank, info.world_size
+    rng = np.random.RandomState(0)
+    A, B = rng.randn(4, 8).astype(np.float32), rng.randn(8, 6).astype(np.float32)
+    mesh = "[" + ",".join(str(i) for i in range(w)) + "]"
+
+    def run(a_spec, b_spec, y_spec, a, b):
+        g = ol.make_graph([ol.make_node("DistributedMatMul", ["a", "b"], ["y"], domain="com.microsoft",
+                                        input_device_mesh_elements=[mesh, mesh], input_device_mesh_shapes=[f"[{w}]", f"[{w}]"],
+                                        input_shard_specs=[a_spec, b_spec], output_device_mesh_elements=[mesh],
+                                        output_device_mesh_shapes=[f"[{w}]"], output_shard_specs=[y_spec])], "g",
+                          [ol.make_tensor_value_info("a", T.FLOAT, list(a.shape)), ol.make_tensor_value_info("b", T.FLOAT, list(b.shape))],
+                          [ol.make_tensor_value_info("y", T.FLOAT, None)])
+        return torch.from_numpy(session(ol.make_model(g).serialize(), info, device).run(None, {"a": a, "b": b})[0])
+    res = {
+        "col": run("RR", "RS[0]", "RS[0]", A, np.split(B, w, 1)[r].copy()),
+        "row": run("RS[0]", "S[0]R", "RR", np.split(A, w, 1)[r].copy(), np.split(B, w, 0)[r].copy()),
+        "reshard": run("S[0]R", "RS[0]", "RR", np.split(A, w, 0)[r].copy(), np.split(B, w, 1)[r].copy()),
+        "full": torch.from_numpy(A @ B),
+    }
+    torch.save(res, os.path.join(out, f"rank{r}.pt"))
+
+
+def case_sharded_moe(info, device, out):
+    r, w = info.rank, info.world_size
+    rng = np.random.RandomState(0)
+    Tn, H, I, E, k = 16, 32, 64, 4 * w, 2
+    x = rng.randn(Tn, H).astype(np.float32)
+    logits = rng.randn(Tn, E).astype(np.float32)
+    fc1, fc2, fc3 = rng.randn(E, H, I).astype(np.float32) * 0.1, rng.randn(E, I, H).astype(np.float32) * 0.1, rng.randn(E, H, I).astype(np.float32) * 0.1
+    el = E // w
+    sl = slice(r * el, (r + 1) * el)
+    g = ol.make_graph([ol.make_node("ShardedMoE", ["x", "p", "fc1", "", "fc2", "", "fc3"], ["y"], domain="com.microsoft", k=k,
+                                    activation_type="silu", normalize_routing_weights=1, local_experts_start_index=r * el)], "g",
+                      [ol.make_tensor_value_info("x", T.FLOAT, [Tn, H]), ol.make_tensor_value_info("p", T.FLOAT, [Tn, E])],
+                      [ol.make_tensor_value_info("y", T.FLOAT, None)],
+                      [ol.make_tensor("fc1", fc1[sl]), ol.make_tensor("fc2", fc2[sl]), ol.make_tensor("fc3", fc3[sl])])
+    y = session(ol.make_model(g).serialize(), info, device).run(None, {"x": x, "p": logits})[0]
+    # single-device MoE on the full expert set (new weight layout [E, I, H] / [E, H, I])
+    g2 = ol.make_graph([ol.make_node("MoE", ["x", "p", "fc1", "", "fc2", "", "fc3"], ["y"], domain="com.microsoft", k=k,
+                                     activation_type="silu", normalize_routing_weights=1)], "g",
+                       [ol.make_tensor_value_info("x", T.FLOAT, [Tn, H]), ol.make_tensor_value_info("p", T.FLOAT, [Tn, E])],
+                       [ol.make_tensor_value_info("y", T.FLOAT, None)],
+                       [ol.make_tensor("fc1", fc1.transpose(0, 2, 1).copy()), ol.make_tensor("fc2", fc2.transpose(0, 2, 1).copy()),
+                        ol.make_tensor("fc3", fc3.transpose(0, 2, 1).copy())])
+    ref = ort.InferenceSession(ol.make_model(g2).serialize(), providers=["CPUExecutionProvider"]).run(None, {"x": x, "p": logits})[0]
+    torch.save({"y": torch.from_numpy(y), "ref": torch.from_numpy(ref)}, os.path.join(out, f"rank{r}.pt"))
+
+
+def case_llama_tp(info, device, out):
+    from onnxruntime_b200.models.generation import DecoderRunner
+    from onnxruntime_b200.models.llama import LlamaConfig, build_llama
+    r, w = info.rank, info.world_size
+    dtype = "fp32" if device == "cpu" else "bf16"
+    cfg = LlamaConfig.tiny(dtype=dtype, head_dim=64, hidden_size=256, ffn_size=512, num_layers=2, num_heads=8, num_kv_heads=4,
+                           max_seq_len=128)
+    model, _ = build_llama(cfg, tp_rank=r, tp_size=w, weight_std=0.05)
+    opts = {}
+    if device == "cuda":
+        torch.cuda.set_device(info.local_rank)
+    providers = ["CPUExecutionProvider"] if device == "cpu" else [("CUDAExecutionProvider", {"device_id": str(info.local_rank), "enable_cuda_graph": "1"})]
+    sess = ort.InferenceSession(model, providers=providers, dist=info, enable_fallback=False, **opts)
+    fused = False
+    if device == "cuda" and os.environ.get("ORTB200_TEST_FUSED", "1") == "1":
+        from onnxruntime_b200.parallel import symm
+        ws = symm.create_workspace(16 << 20)
+        symm.attach(sess, ws)
+        fused = True
+    dev = torch.device("cpu") if device == "cpu" else torch.device("cuda", info.local_rank)
+    runner = DecoderRunner(sess, cfg, batch=2, max_len=96, tp_size=w, device=dev)
+    torch.manual_seed(0)
+    ids = torch.randint(0, cfg.vocab_size, (2, 40))
+    first = runner.prefill(ids)
+    logits = []
+    tok = first.clone()
+    for _ in range(6):
+        tok = runner.decode_step(tok).clone()
+        logits.append(runner.step_logits.float().cpu().clone())
+    if device == "cuda":
+        torch.cuda.synchronize()
+        sess.check_device_status()
+    ops = sorted({n["op_type"] for n in sess.graph_nodes()})
+    res = {"logits": torch.stack(logits), "ops": ops, "fused": fused}
+    if r == 0:
+        # single-rank run of the unsharded model for comparison
+        full, _ = build_llama(cfg, weight_std=0.05)
+        s1 = ort.InferenceSession(full, providers=["CPUExecutionProvider"] if device == "cpu" else [("CUDAExecutionProvider", {"device_id": str(info.local_rank)})],
+                                  enable_fallback=False)
+        r1 = DecoderRunner(s1, cfg, batch=2, max_len=96, device=dev)
+        t1 = r1.prefill(ids)
+        ref = []
+        tok = first.clone()
+        for _ in range(6):
+            r1.decode_step(tok)
+            ref.append(r1.step_logits.float().cpu().clone())
+            tok = torch.stack(logits)[len(ref) - 1].argmax(-1)  # follow the TP run's tokens so the caches stay comparable
+            tok = tok.to(dev)
+        res["ref"] = torch.stack(ref)
+        res["first_equal"] = bool(torch.equal(t1.cpu(), first.cpu()))
+    torch.save(res, os.path.join(out, f"rank{r}.pt"))
+
+
+def case_gemm_allreduce(info, device, out):
+    """The fused GEMM + all-reduce kernel against a process-group all-reduce of the per-rank products."""
+    from onnxruntime_b200.ops import _kernels as K
+    from onnxruntime_b200.parallel import symm
+    r, w = info.rank, info.world_size
+    torch.cuda.set_device(info.local_rank)
+    ws = symm.create_workspace(16 << 20)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    res = {}
+    for i, (M, N, Kd) in enumerate([(8, 4096, 512), (8, 1024, 1792), (16, 2048, 256), (1, 512, 128), (33, 768, 512)]):
+        g = torch.Generator(device="cuda").manual_seed(100 * i + r)
+        x = (torch.randn(M, Kd, device="cuda", generator=g) * 0.5).bfloat16()
+        wt = (torch.randn(N, Kd, device="cuda", generator=g) * 0.05).bfloat16()
+        resid = torch.randn(M, N, device="cuda", generator=torch.Generator(device="cuda").manual_seed(7 + i)).bfloat16()
+        outs = []
+        for rep in range(3):  # consecutive launches exercise the epoch / double-buffer protocol
+            outs.append(K.gemm(x, wt, residual=resid, status=status, peers=ws.peer_ptrs, rank=r, symm_bytes=ws.nbytes).clone())
+        ref = (x.float() @ wt.float().T)
+        dist.all_reduce(ref)
+        ref = ref + resid.float()
+        torch.cuda.synchronize()
+        res[f"case{i}"] = {"err": float((outs[-1].float() - ref).abs().max() / ref.abs().max()),
+                           "stable": bool(torch.equal(outs[0], outs[1]) and torch.equal(outs[1], outs[2])), "out": outs[-1].cpu()}
+    res["status"] = int(status.item())
+    torch.save(res, os.path.join(out, f"rank{r}.pt"))
+
+
+def main():
+    case, device, out = sys.argv[1], sys.argv[2], sys.argv[3]
+    info = init_distributed("gloo" if device == "cpu" else "nccl", timeout_s=120)
+    try:
+        globals()[f"case_{case}"](info, device, out)
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

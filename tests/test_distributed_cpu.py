@@ -1,0 +1,75 @@
+"""Collective / tensor-parallel host logic on CPU ranks (gloo, world size 2): real processes, no GPU."""
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def launch(case, device, nproc, tmp_path, extra_env=None, timeout=300):
+    import socket
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    env = dict(os.environ)
+    env.update({"OMP_NUM_THREADS": "1", "NCCL_NVLS_ENABLE": "0"})
+    env.update(extra_env or {})
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}", "--master-addr", "127.0.0.1",
+           "--master-port", str(port), os.path.join(HERE, "mp_worker.py"), case, device, str(tmp_path)]
+    res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=timeout)
+    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
+    return [torch.load(os.path.join(tmp_path, f"rank{r}.pt")) for r in range(nproc)]
+
+
+def test_collective_ops(tmp_path):
+    out = launch("collectives", "cpu", 2, tmp_path)
+    xs = [np.arange(8, dtype=np.float32).reshape(4, 2) + 10 * r for r in range(2)]
+    for r in range(2):
+        np.testing.assert_array_equal(out[r]["AllReduce"].numpy(), xs[0] + xs[1])
+        np.testing.assert_array_equal(out[r]["AllGather0"].numpy(), np.concatenate(xs, 0))
+        np.testing.assert_array_equal(out[r]["AllGather1"].numpy(), np.concatenate(xs, 1))
+        # all-to-all with equal splits along the flattened leading dimension
+        expect = np.concatenate([np.split(x, 2, 0)[r] for x in xs], 0)
+        np.testing.assert_array_equal(out[r]["AllToAll"].numpy(), expect)
+
+
+def test_distributed_matmul_specs(tmp_path):
+    out = launch("distributed_matmul", "cpu", 2, tmp_path)
+    full = out[0]["full"].numpy()
+    for r in range(2):
+        np.testing.assert_allclose(out[r]["col"].numpy(), np.split(full, 2, 1)[r], rtol=1e-5, atol=1e-5)
+        np.testing.assert_allclose(out[r]["row"].numpy(), full, rtol=1e-5, atol=1e-5)
+        np.testing.assert_allclose(out[r]["reshard"].numpy(), full, rtol=1e-5, atol=1e-5)
+
+
+def test_sharded_moe_matches_single_device_moe(tmp_path):
+    out = launch("sharded_moe", "cpu", 2, tmp_path)
+    for r in range(2):
+        np.testing.assert_allclose(out[r]["y"].numpy(), out[r]["ref"].numpy(), rtol=1e-4, atol=1e-5)
+
+
+def test_llama_tensor_parallel_matches_single_rank(tmp_path):
+    out = launch("llama_tp", "cpu", 2, tmp_path)
+    assert "AllReduce" in out[0]["ops"]
+    assert out[0]["first_equal"]
+    np.testing.assert_allclose(out[0]["logits"].numpy(), out[1]["logits"].numpy(), rtol=1e-5, atol=1e-5)
+    np.testing.assert_allclose(out[0]["logits"].numpy(), out[0]["ref"].numpy(), rtol=2e-3, atol=2e-3)
+
+
+def test_sharding_spec_algebra():
+    from onnxruntime_b200 import _core as C
+    d = C.parse_shard_spec("RS[0]", [0, 1, 2, 3], [4])
+    assert d == {"spec": "RS[0]", "sharded_axis": 1, "num_shards": 4}
+    assert C.shard_shape([8, 12], "RS[0]", [0, 1, 2, 3], [4]) == [8, 3]
+    assert C.shard_shape([8, 12], "S[0]R", [0, 1], [2]) == [4, 12]
+    assert C.parse_shard_spec("RRR", [0, 1], [2])["sharded_axis"] == -1
+    import onnxruntime_b200 as ort
+    with pytest.raises(ort.InvalidArgument):
+        C.parse_shard_spec("S[0]S[0]", [0, 1], [2])
+    with pytest.raises(ort.InvalidArgument):
+        C.shard_shape([7, 12], "S[0]R", [0, 1], [2])
