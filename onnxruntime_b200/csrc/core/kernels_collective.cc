@@ -22,6 +22,7 @@ namespace ortb {
 
 c10::intrusive_ptr<c10d::ProcessGroup> GroupOf(InferenceSession* s) {
   if (!s || s->world_size <= 1 || s->dist_group.empty()) return nullptr;
+  ++s->library_collective_calls;
   return c10d::resolve_process_group(s->dist_group);
 }
 

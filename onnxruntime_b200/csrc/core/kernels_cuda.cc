@@ -97,7 +97,7 @@ bool CanFuseAllReduce(OpKernelContext& ctx, int64_t M, int64_t N) {
   if (static_cast<int>(s->symm_peers.size()) != s->world_size) return false;
   if (s->config().Get("ortb200.fused_allreduce", "1") != "1") return false;
   if (M > 64) return false;
-  const int64_t slot = (s->symm_bytes - 262144) / (2LL * s->world_size * 4);
+  const int64_t slot = (s->symm_bytes - 262144) / (2LL * s->world_size * 8);
   return slot >= M * N && (N + 127) / 128 * 8 <= 4096;
 }
 

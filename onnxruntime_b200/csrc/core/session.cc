@@ -354,6 +354,21 @@ std::vector<Value> InferenceSession::RunImpl(const RunOptions& ro, const std::ve
   if (enable_cuda_graph_ && graph_capturable_) {
     const std::string id = ro.config.Get("gpu_graph_id", "0");
     graph_id = std::stoll(id);
+    if (uncapturable_graph_ids_.count(graph_id)) graph_id = -1;
+  }
+
+  if (graph_id >= 0 && !(cuda_graphs_.count(graph_id) && cuda_graphs_[graph_id]->captured)) {
+    // one eager run first (lazy initialisation, workspace allocation); it also shows whether the step calls a
+    // library collective, which is left out of graph capture (the process-group's own streams and watchdog do
+    // not belong inside a capture) - such a step keeps running eagerly
+    const int64_t lib_before = library_collective_calls;
+    results = ex->Run(ro, inputs, nullptr, output_names);
+    cudaStreamSynchronize(at::cuda::getCurrentCUDAStream(device_.index()).stream());
+    CheckDeviceStatus();
+    if (library_collective_calls != lib_before) {
+      uncapturable_graph_ids_.insert(graph_id);
+      graph_id = -1;
+    }
   }
 
   if (graph_id >= 0) {
@@ -361,10 +376,6 @@ std::vector<Value> InferenceSession::RunImpl(const RunOptions& ro, const std::ve
     if (!cg_ptr) cg_ptr = std::make_unique<CapturedGraph>();
     CapturedGraph& cg = *cg_ptr;
     if (!cg.captured) {
-      // one eager run first (lazy initialisation, workspace allocation), then capture
-      results = ex->Run(ro, inputs, nullptr, output_names);
-      cudaStreamSynchronize(at::cuda::getCurrentCUDAStream(device_.index()).stream());
-      CheckDeviceStatus();
       cg.static_in.clear();
       cg.in_shapes.clear();
       for (auto& v : inputs) {

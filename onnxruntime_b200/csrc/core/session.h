@@ -148,6 +148,8 @@ class InferenceSession {
   // into this process (index = rank), and its size.  Empty = not available (collectives go through the process group).
   std::vector<void*> symm_peers;
   int64_t symm_bytes = 0;
+  int64_t library_collective_calls = 0;  // process-group collectives issued so far (the in-kernel ones do not count)
+  std::set<int64_t> uncapturable_graph_ids_;
   std::string dist_group;  // torch.distributed group name used by collective ops ("" = default)
   int rank = 0, world_size = 1;
 

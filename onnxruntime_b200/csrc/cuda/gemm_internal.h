@@ -22,7 +22,7 @@ struct SmallGemmParams {
   // ---- fused all-reduce over peer memory (world > 1): see ortb200_symm_layout in ortb200_kernels.h
   int world, rank;
   void* peers[8];          // base of every rank's symmetric workspace (peers[rank] is the local one)
-  long long staging_offset;  // bytes from the workspace base to staging[2][world][slot_elems] (fp32)
+  long long staging_offset;  // bytes from the workspace base to staging[2][world][slot_elems] (64-bit words: value | epoch << 32)
   long long slot_elems;      // elements per (parity, source rank) slot, >= M * ldo
   unsigned int* epoch;       // local: number of completed fused launches
   unsigned int* done;        // local: CTAs finished in the current launch

@@ -51,17 +51,19 @@ __device__ __forceinline__ float ld_dsmem(uint32_t addr) {
   return v;
 }
 
-__device__ __forceinline__ void st_release_sys(unsigned int* p, unsigned int v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+// One 64-bit word carries a partial sum (low half) and the epoch of the launch that wrote it (high half).  A
+// naturally aligned 64-bit scalar access is single-copy atomic, so a reader that sees the expected epoch also sees
+// the value: no fence, no separate flag and no second NVLink round trip.
+__device__ __forceinline__ void st_packed_sys(unsigned long long* p, float v, unsigned int epoch) {
+  const unsigned long long w = (static_cast<unsigned long long>(epoch) << 32) | __float_as_uint(v);
+  asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(w) : "memory");
 }
-__device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
-  unsigned int v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
+__device__ __forceinline__ unsigned long long ld_packed_sys(const unsigned long long* p) {
+  unsigned long long w;
+  asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(w) : "l"(p) : "memory");
+  return w;
 }
-constexpr long long kSymmFlagsOffset = 65536;
-constexpr int kSymmFlagsPerRank = 4096;
-// a second of polling at most; then the launch reports kStatusTimeoutPeer and finishes with what it has
+// about a second of polling at most; then the launch reports kStatusTimeoutPeer and finishes with what it has
 constexpr unsigned int kPeerSpinLimit = 1u << 22;
 
 __device__ __forceinline__ float act_apply(int act, float v) {
@@ -230,11 +232,10 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
     const uint32_t part_addr = smem_u32(part);
     const bool fused_ar = p.world > 1;
     unsigned int epoch = 0;
-    float* stage_local = nullptr;
+    long long stage_base = 0;  // element offset of staging[epoch & 1][0][0]
     if (fused_ar) {
       epoch = *reinterpret_cast<volatile unsigned int*>(p.epoch) + 1;  // stable: the previous fused launch has completed
-      stage_local = reinterpret_cast<float*>(static_cast<uint8_t*>(p.peers[p.rank]) + p.staging_offset) +
-                    static_cast<long long>(epoch & 1) * p.world * p.slot_elems;
+      stage_base = static_cast<long long>(epoch & 1) * p.world * p.slot_elems;
     }
 #pragma unroll 1
     for (int jj = 0; jj < cols_per; ++jj) {
@@ -259,13 +260,13 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
       }
       const int m = m0 + j;
       if (fused_ar) {
-        // push this rank's partial sum to every rank (its own copy included); 128 lanes write 512 contiguous bytes
+        // push this rank's partial sum to every rank (its own copy included); 128 lanes write 1 KiB contiguous
         if (n_ok && m < p.M) {
-          const long long off = static_cast<long long>(epoch & 1) * p.world * p.slot_elems +
-                                static_cast<long long>(p.rank) * p.slot_elems + static_cast<long long>(m) * p.ldo + n;
+          const long long off = stage_base + static_cast<long long>(p.rank) * p.slot_elems + static_cast<long long>(m) * p.ldo + n;
           for (int d = 0; d < p.world; ++d) {
-            float* dst = reinterpret_cast<float*>(static_cast<uint8_t*>(p.peers[d]) + p.staging_offset) + off;
-            *dst = v * p.alpha;
+            const int dst_rank = (p.rank + d) % p.world;  // spread the first stores over the peers
+            st_packed_sys(reinterpret_cast<unsigned long long*>(static_cast<uint8_t*>(p.peers[dst_rank]) + p.staging_offset) + off,
+                          v * p.alpha, epoch);
           }
         }
         continue;
@@ -288,41 +289,30 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
       }
     }
     if (fused_ar) {
-      // publish: all 128 epilogue threads have written; one thread raises this CTA's flag on every rank
-      const int flag_idx = static_cast<int>(blockIdx.y) * static_cast<int>(gridDim.x) + static_cast<int>(blockIdx.x);
-      __threadfence_system();
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (threadIdx.x == 64) {
-        for (int d = 0; d < p.world; ++d) {
-          unsigned int* f = reinterpret_cast<unsigned int*>(static_cast<uint8_t*>(p.peers[d]) + kSymmFlagsOffset) +
-                            p.rank * kSymmFlagsPerRank + flag_idx;
-          st_release_sys(f, epoch);
-        }
-      }
-      // wait for the same tile of every rank: lane s of the first epilogue warp polls rank s
-      if (threadIdx.x >= 64 && threadIdx.x < 64 + p.world) {
-        const int src = threadIdx.x - 64;
-        const unsigned int* f = reinterpret_cast<const unsigned int*>(static_cast<uint8_t*>(p.peers[p.rank]) + kSymmFlagsOffset) +
-                                src * kSymmFlagsPerRank + flag_idx;
-        unsigned int spins = 0;
-        // epochs only grow; compare with wrap-around in mind
-        while (static_cast<int>(ld_acquire_sys(f) - epoch) < 0) {
-          if (++spins > kPeerSpinLimit) {
-            if (p.status) atomicExch(p.status, kStatusTimeoutPeer);
-            break;
-          }
-          __nanosleep(64);
-        }
-      }
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      __threadfence_system();
+      // gather: the thread that pushed element (m, n) also finishes it, so no CTA-wide barrier is needed; it polls the
+      // word of every source rank in its own copy of the staging area until the word carries this launch's epoch
+      const unsigned long long* stage_local =
+          reinterpret_cast<const unsigned long long*>(static_cast<const uint8_t*>(p.peers[p.rank]) + p.staging_offset) + stage_base;
+      bool timed_out = false;
 #pragma unroll 1
       for (int jj = 0; jj < cols_per; ++jj) {
         const int m = m0 + j_begin + jj;
         if (!(n_ok && m < p.M)) continue;
         float y = 0.f;
-        for (int s = 0; s < p.world; ++s)
-          y += __ldcg(stage_local + static_cast<long long>(s) * p.slot_elems + static_cast<long long>(m) * p.ldo + n);
+        for (int s = 0; s < p.world; ++s) {  // fixed order: every rank adds in the same order and gets the same bits
+          const unsigned long long* src = stage_local + static_cast<long long>(s) * p.slot_elems + static_cast<long long>(m) * p.ldo + n;
+          unsigned long long w = ld_packed_sys(src);
+          unsigned int spins = 0;
+          while (static_cast<unsigned int>(w >> 32) != epoch && !timed_out) {
+            if (++spins > kPeerSpinLimit) {
+              timed_out = true;
+              break;
+            }
+            __nanosleep(32);
+            w = ld_packed_sys(src);
+          }
+          y += __uint_as_float(static_cast<unsigned int>(w));
+        }
         y = act_apply(p.act, y + bias_v);
         if (p.dtype == ORTB200_BF16) {
           if (p.residual) y += __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.residual)[m * p.ldr + n]);
@@ -332,6 +322,7 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
           reinterpret_cast<__half*>(p.out)[m * p.ldo + n] = __float2half_rn(y);
         }
       }
+      if (timed_out && p.status) atomicExch(p.status, kStatusTimeoutPeer);
       // the CTA that finishes last advances the epoch for the next fused launch
       asm volatile("bar.sync 1, 128;" ::: "memory");
       if (threadIdx.x == 64) {
@@ -423,9 +414,8 @@ int launch_gemm_smallm(const ortb200_gemm_args* a, int bn, cudaStream_t stream, 
   if (a->world > 1) {
     if (a->world > 8 || a->rank < 0 || a->rank >= a->world || dual || a->ldo != a->N) return -12;
     const long long staging_off = 262144;
-    const long long slot = (a->symm_bytes - staging_off) / (2LL * a->world * 4);
+    const long long slot = (a->symm_bytes - staging_off) / (2LL * a->world * 8);
     if (slot < static_cast<long long>(a->M) * a->ldo) return -13;
-    if (static_cast<long long>(tiles_n) * cluster * tiles_m > kSymmFlagsPerRank) return -13;
     for (int i = 0; i < a->world; ++i) {
       if (!a->peers[i]) return -12;
       p.peers[i] = a->peers[i];

@@ -57,14 +57,17 @@ typedef struct {
   int force_bn;         // 0 = heuristic; else 16/32/64/128/256
   int use_pdl;          // launch with programmatic stream serialization
   // Fused all-reduce (row-parallel linear): when world > 1 the kernel sums the partial products of all ranks
-  // itself.  Every rank pushes its fp32 partial tile into each peer's symmetric workspace with plain peer stores,
-  // raises a per-tile flag there (release, system scope), waits (bounded) for the flags of all ranks in its own
-  // workspace and adds the partials in rank order, then bias / residual as usual.  Requires M <= 64.
+  // itself.  Each epilogue thread pushes its fp32 partial sums into every rank's symmetric workspace as 64-bit
+  // words (value in the low half, the launch's epoch in the high half) with plain peer stores, then polls (bounded)
+  // the words of all source ranks in its own workspace until they carry the epoch, adds them in rank order, and
+  // applies bias / residual as usual.  No fence, flag or barrier is involved: one NVLink store latency per GEMM.
+  // Requires M <= 64, ldo == N, no dual (SwiGLU) epilogue.
   // peers[i] is rank i's workspace base as mapped into this process; the layout is
-  //   [0, 64 KiB)                  epoch word (offset 0), done counter (offset 4), rest reserved
-  //   [64 KiB, 64 KiB + 8 * 16 KiB) flags[world<=8][4096] uint32
-  //   [256 KiB, ...)               staging[2][world][slot] fp32, slot = (bytes - 256 KiB) / (2 * world * 4) elements
-  // The workspace must be zero before the first launch.  All ranks must launch the same sequence of fused GEMMs.
+  //   [0, 256 KiB)    epoch word (offset 0), done counter (offset 4), rest reserved
+  //   [256 KiB, ...)  staging[2][world][slot] 64-bit words, slot = (bytes - 256 KiB) / (2 * world * 8) >= M * ldo
+  // Two staging halves alternate by epoch parity, so a rank that runs one launch ahead never overwrites words a
+  // slower rank still has to read.  The workspace must be zero before the first launch, and all ranks must launch
+  // the same sequence of fused GEMMs.
   int world;
   int rank;
   void* peers[8];

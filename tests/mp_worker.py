@@ -97,10 +97,13 @@ def case_llama_tp(info, device, out):
     opts = {}
     if device == "cuda":
         torch.cuda.set_device(info.local_rank)
-    providers = ["CPUExecutionProvider"] if device == "cpu" else [("CUDAExecutionProvider", {"device_id": str(info.local_rank), "enable_cuda_graph": "1"})]
+    want_fused = device == "cuda" and os.environ.get("ORTB200_TEST_FUSED", "1") == "1"
+    # graph capture only with the in-kernel reduction: the decode step then contains no library collective
+    providers = ["CPUExecutionProvider"] if device == "cpu" else [
+        ("CUDAExecutionProvider", {"device_id": str(info.local_rank), "enable_cuda_graph": "1" if want_fused else "0"})]
     sess = ort.InferenceSession(model, providers=providers, dist=info, enable_fallback=False, **opts)
     fused = False
-    if device == "cuda" and os.environ.get("ORTB200_TEST_FUSED", "1") == "1":
+    if want_fused:
         from onnxruntime_b200.parallel import symm
         ws = symm.create_workspace(16 << 20)
         symm.attach(sess, ws)
