@@ -21,5 +21,6 @@ bool CanFuseAllReduce(OpKernelContext& ctx, int64_t M, int64_t N);
 at::Tensor GemmAllReduce(OpKernelContext& ctx, const at::Tensor& partial, const at::Tensor& residual);
 
 void RegisterMoreCudaKernels(KernelRegistry& r);
+void RegisterCudaKernels3(KernelRegistry& r);
 
 }  // namespace ortb

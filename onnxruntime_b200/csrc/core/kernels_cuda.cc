@@ -226,6 +226,7 @@ void RegisterCudaKernels(KernelRegistry& r) {
   RegisterClass<GemmKernel>(r, kFusedDomain, "FusedGemm", GemmSupports);
   RegisterClass<GemmSwiGLUKernel>(r, kFusedDomain, "GemmSwiGLU");
   RegisterMoreCudaKernels(r);
+  RegisterCudaKernels3(r);
 }
 
 }  // namespace ortb

@@ -31,6 +31,7 @@ constexpr int kAttnThreads = 192;
 
 struct AttnParams {
   const int* seqlens_k;
+  const int* key_mask;
   const void* head_sink;
   void* out;
   int B, S, N, Nk, kv_len;
@@ -56,6 +57,14 @@ struct AttnSmem {
   static constexpr int kTotal = kOffBar + 128 + 1024;
   static constexpr int kTmemCols = 128 + (HD <= 64 ? 64 : 128) <= 128 ? 128 : 256;
 };
+
+// Bit j of the result = key (key0 + j) of batch b may be attended to.  Called by all 32 lanes of a warp.
+__device__ __forceinline__ unsigned key_keep_bits(const int* key_mask, int b, int kv_len, int key0, int lane) {
+  if (key_mask == nullptr) return 0xffffffffu;
+  const int key = key0 + lane;
+  const bool keep = key < kv_len && key_mask[static_cast<long long>(b) * kv_len + key] != 0;
+  return __ballot_sync(0xffffffffu, keep);
+}
 
 // barrier indices
 enum { BAR_Q = 0, BAR_KV_FULL0, BAR_KV_FULL1, BAR_KV_EMPTY0, BAR_KV_EMPTY1, BAR_S_FULL, BAR_P_READY, BAR_O_FULL, BAR_O_READ, BAR_COUNT };
@@ -207,10 +216,11 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         float v[32];
         tmem_ld_x32(tmem_s + lane_addr + c, v);
         tmem_ld_wait();
+        const unsigned keep = key_keep_bits(p.key_mask, b, p.kv_len, key0 + c, lane);
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
           const int key = key0 + c + j;
-          bool valid = key < total && key < p.kv_len;
+          bool valid = key < total && key < p.kv_len && ((keep >> j) & 1u);
           if (p.causal) valid = valid && key <= pos;
           if (p.window > 0) valid = valid && key > pos - p.window;
           float sc = v[j];
@@ -228,13 +238,14 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         tmem_ld_x32(tmem_s + lane_addr + c, v);
         tmem_ld_wait();
         uint32_t packed[16];
+        const unsigned keep = key_keep_bits(p.key_mask, b, p.kv_len, key0 + c, lane);
 #pragma unroll
         for (int j = 0; j < 32; j += 2) {
           float pr[2];
 #pragma unroll
           for (int u = 0; u < 2; ++u) {
             const int key = key0 + c + j + u;
-            bool valid = key < total && key < p.kv_len;
+            bool valid = key < total && key < p.kv_len && ((keep >> (j + u)) & 1u);
             if (p.causal) valid = valid && key <= pos;
             if (p.window > 0) valid = valid && key > pos - p.window;
             float sc = v[j + u];
@@ -342,6 +353,7 @@ static int launch_attn(const ortb200_attn_prefill_args* a, cudaStream_t stream) 
   }
   AttnParams p;
   p.seqlens_k = a->seqlens_k;
+  p.key_mask = a->key_mask;
   p.head_sink = a->head_sink;
   p.out = a->out;
   p.B = a->B; p.S = a->S; p.N = a->N; p.Nk = a->Nk; p.kv_len = a->kv_len;

@@ -86,6 +86,80 @@ __global__ void __launch_bounds__(256) gqa_prep_kernel(const ortb200_gqa_prep_ar
   pdl_launch_dependents();
 }
 
+// ------------------------------------------------------------ paged prep
+// One CTA per packed token: find its sequence, rotate Q and K at position past + offset, store Q and write K / V
+// into the cache slot named by slot_mapping (when given) or by the block table.
+template <typename T>
+__global__ void __launch_bounds__(256) paged_prep_kernel(const ortb200_paged_prep_args a) {
+  const int t = blockIdx.x;
+  const int H = a.H, halfH = H / 2;
+  const int rot = a.rot_dim > 0 ? a.rot_dim : H;
+  const int half = rot / 2;
+  const int heads = a.N + 2 * a.Nk;
+  pdl_wait_prior_grids();
+  // sequence of this token: last b with cu_seqlens[b] <= t
+  int lo = 0, hi = a.B;
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (a.cu_seqlens[mid] <= t) lo = mid; else hi = mid;
+  }
+  const int b = lo;
+  const int pos = a.past_seqlens[b] + (t - a.cu_seqlens[b]);
+  long long slot;
+  if (a.slot_mapping) {
+    slot = a.slot_mapping[t];
+  } else {
+    const int bi = pos / a.block_size;
+    slot = bi < a.max_blocks ? static_cast<long long>(a.block_table[static_cast<long long>(b) * a.max_blocks + bi]) * a.block_size + pos % a.block_size : -1;
+  }
+  const bool slot_ok = slot >= 0 && slot < static_cast<long long>(a.num_blocks) * a.block_size;
+  if (!a.slot_mapping && !slot_ok && threadIdx.x == 0 && a.status) atomicExch(a.status, kStatusBadArgument);
+  const T* cosr = a.do_rotary ? static_cast<const T*>(a.cos_cache) + static_cast<long long>(pos) * half : nullptr;
+  const T* sinr = a.do_rotary ? static_cast<const T*>(a.sin_cache) + static_cast<long long>(pos) * half : nullptr;
+  for (int idx = threadIdx.x; idx < heads * halfH; idx += blockDim.x) {
+    const int head = idx / halfH, i = idx % halfH;
+    const T* src;
+    if (a.k != nullptr) {
+      if (head < a.N) src = static_cast<const T*>(a.qkv) + static_cast<long long>(t) * (a.N * H) + head * H;
+      else if (head < a.N + a.Nk) src = static_cast<const T*>(a.k) + static_cast<long long>(t) * (a.Nk * H) + (head - a.N) * H;
+      else src = static_cast<const T*>(a.v) + static_cast<long long>(t) * (a.Nk * H) + (head - a.N - a.Nk) * H;
+    } else {
+      src = static_cast<const T*>(a.qkv) + static_cast<long long>(t) * (static_cast<long long>(heads) * H) + head * H;
+    }
+    T* dst;
+    if (head < a.N) {
+      dst = static_cast<T*>(a.q_out) + static_cast<long long>(t) * (a.N * H) + head * H;
+    } else {
+      if (!slot_ok) continue;  // slot_mapping -1: the token is not cached
+      const bool is_k = head < a.N + a.Nk;
+      const int kh = is_k ? head - a.N : head - a.N - a.Nk;
+      dst = static_cast<T*>(is_k ? a.k_cache : a.v_cache) + (slot * a.Nk + kh) * H;
+    }
+    const bool rotate = a.do_rotary && head < a.N + a.Nk && i < half;
+    int e0, e1;
+    if (rotate) {
+      e0 = a.interleaved ? 2 * i : i;
+      e1 = a.interleaved ? 2 * i + 1 : i + half;
+    } else if (a.do_rotary && head < a.N + a.Nk) {
+      e0 = rot + 2 * (i - half);
+      e1 = e0 + 1;
+    } else {
+      e0 = 2 * i;
+      e1 = 2 * i + 1;
+    }
+    const float x0 = to_float<T>(src[e0]), x1 = to_float<T>(src[e1]);
+    if (rotate) {
+      const float c = to_float<T>(cosr[i]), sn = to_float<T>(sinr[i]);
+      dst[e0] = from_float<T>(x0 * c - x1 * sn);
+      dst[e1] = from_float<T>(x1 * c + x0 * sn);
+    } else {
+      dst[e0] = src[e0];
+      dst[e1] = src[e1];
+    }
+  }
+  pdl_launch_dependents();
+}
+
 // ---------------------------------------------------------------- decode
 struct DecodeParams {
   const void* q;
@@ -99,6 +173,9 @@ struct DecodeParams {
   int* status;
   int B, N, Nk, Smax, splits, window, gparts;
   float scale, softcap;
+  // paged cache [num_blocks, block_size, Nk, H]: key j of sequence b lives in block block_table[b, j / block_size]
+  const int* block_table;
+  int block_size, max_blocks;
 };
 
 // Running maxima start at a large negative finite value so that exp(m_old - m_new) never sees inf - inf.
@@ -110,7 +187,7 @@ __device__ __forceinline__ float safe_exp_diff(float a, float b) {
 constexpr int kDecTile = 32;    // keys per pipeline stage
 constexpr int kDecStages = 4;
 
-template <typename T, int H, int G>
+template <typename T, int H, int G, bool PAGED>
 __global__ void __launch_bounds__(128) gqa_decode_kernel(const DecodeParams p) {
   constexpr int DPL = H / 8;          // dims per lane (8 lanes share a key)
   constexpr int VEC = DPL * sizeof(T) / 16;  // 16-byte loads per lane per row
@@ -163,7 +240,28 @@ __global__ void __launch_bounds__(128) gqa_decode_kernel(const DecodeParams p) {
     bulk_load(dst, kbase + static_cast<long long>(key0) * H, bytes, &full_bar[s]);
     bulk_load(dst + kTileBytes, vbase + static_cast<long long>(key0) * H, bytes, &full_bar[s]);
   };
-  if (tid == 0) {
+  // paged cache: the rows of a tile are scattered over blocks, so the 32 lanes of warp 0 fetch one row pair each
+  auto issue_tile_paged = [&](int t) {
+    const int s = t % kDecStages;
+    const int key0 = k_begin + t * kDecTile;
+    const int rows = min(kDecTile, k_end - key0);
+    uint8_t* dst = stage_base + s * 2 * kTileBytes;
+    if (lane == 0) mbar_expect_tx(&full_bar[s], 2u * static_cast<uint32_t>(rows) * kRowBytes);
+    __syncwarp();
+    if (lane < rows) {
+      const int key = key0 + lane;
+      const int blk = p.block_table[static_cast<long long>(b) * p.max_blocks + key / p.block_size];
+      const long long row = ((static_cast<long long>(blk) * p.block_size + key % p.block_size) * p.Nk + kvh) * H;
+      bulk_load(dst + lane * kRowBytes, static_cast<const T*>(p.k_cache) + row, kRowBytes, &full_bar[s]);
+      bulk_load(dst + kTileBytes + lane * kRowBytes, static_cast<const T*>(p.v_cache) + row, kRowBytes, &full_bar[s]);
+    }
+  };
+  if (PAGED) {
+    if (warp == 0) {
+      const int pre = n_tiles < kDecStages ? n_tiles : kDecStages;
+      for (int t = 0; t < pre; ++t) issue_tile_paged(t);
+    }
+  } else if (tid == 0) {
     const int pre = n_tiles < kDecStages ? n_tiles : kDecStages;
     for (int t = 0; t < pre; ++t) issue_tile(t);
   }
@@ -254,7 +352,11 @@ __global__ void __launch_bounds__(128) gqa_decode_kernel(const DecodeParams p) {
       m[g] = m_new;
     }
     __syncthreads();  // every warp is done with stage s
-    if (tid == 0 && ok && t + kDecStages < n_tiles) issue_tile(t + kDecStages);
+    if (PAGED) {
+      if (warp == 0 && ok && t + kDecStages < n_tiles) issue_tile_paged(t + kDecStages);
+    } else if (tid == 0 && ok && t + kDecStages < n_tiles) {
+      issue_tile(t + kDecStages);
+    }
   }
   if (!ok && tid == 0 && p.status) atomicExch(p.status, kStatusTimeoutEpilogue);
 
@@ -371,10 +473,10 @@ __global__ void __launch_bounds__(128) gqa_decode_kernel(const DecodeParams p) {
   }
 }
 
-template <typename T, int H, int G>
+template <typename T, int H, int G, bool PAGED>
 static int launch_decode_g(const DecodeParams& p, dim3 grid, cudaStream_t stream, bool use_pdl) {
   constexpr int kSmem = kDecStages * 2 * kDecTile * H * static_cast<int>(sizeof(T)) + (4 * G * H + 8 * G) * 4 + 8 * kDecStages;
-  auto kern = gqa_decode_kernel<T, H, G>;
+  auto kern = gqa_decode_kernel<T, H, G, PAGED>;
   static bool attr_set = false;
   if (!attr_set) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) != cudaSuccess) return -10;
@@ -422,10 +524,16 @@ static int launch_decode(const ortb200_gqa_decode_args* a, cudaStream_t stream) 
   p.B = a->B; p.N = a->N; p.Nk = a->Nk; p.Smax = a->Smax; p.splits = splits; p.window = a->window; p.gparts = gparts;
   p.scale = a->scale != 0.f ? a->scale : 1.0f / sqrtf(static_cast<float>(H));
   p.softcap = a->softcap;
+  p.block_table = a->block_table; p.block_size = a->block_size; p.max_blocks = a->max_blocks;
   dim3 grid(splits, a->Nk * gparts, a->B);
-  if (G == 4) return launch_decode_g<T, H, 4>(p, grid, stream, a->use_pdl != 0);
-  if (G == 2) return launch_decode_g<T, H, 2>(p, grid, stream, a->use_pdl != 0);
-  return launch_decode_g<T, H, 1>(p, grid, stream, a->use_pdl != 0);
+  if (a->block_table) {
+    if (G == 4) return launch_decode_g<T, H, 4, true>(p, grid, stream, a->use_pdl != 0);
+    if (G == 2) return launch_decode_g<T, H, 2, true>(p, grid, stream, a->use_pdl != 0);
+    return launch_decode_g<T, H, 1, true>(p, grid, stream, a->use_pdl != 0);
+  }
+  if (G == 4) return launch_decode_g<T, H, 4, false>(p, grid, stream, a->use_pdl != 0);
+  if (G == 2) return launch_decode_g<T, H, 2, false>(p, grid, stream, a->use_pdl != 0);
+  return launch_decode_g<T, H, 1, false>(p, grid, stream, a->use_pdl != 0);
 }
 
 }  // namespace ortb200
@@ -441,6 +549,7 @@ extern "C" int ortb200_gqa_decode(const ortb200_gqa_decode_args* a, ortb200_stre
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   if (!a || !a->q || !a->k_cache || !a->v_cache || !a->seqlens_k || !a->out) return -1;
   if (a->B <= 0 || a->N <= 0 || a->Nk <= 0 || a->N % a->Nk != 0 || a->Smax <= 0) return -1;
+  if (a->block_table && (a->block_size <= 0 || a->max_blocks <= 0)) return -1;
   if (a->H != 64 && a->H != 128) return -2;
   if ((reinterpret_cast<uintptr_t>(a->k_cache) | reinterpret_cast<uintptr_t>(a->v_cache)) & 15) return -3;
   if (a->dtype == ORTB200_BF16) {
@@ -449,6 +558,22 @@ extern "C" int ortb200_gqa_decode(const ortb200_gqa_decode_args* a, ortb200_stre
     return a->H == 128 ? launch_decode<__half, 128>(a, stream) : launch_decode<__half, 64>(a, stream);
   }
   return -4;
+}
+
+extern "C" int ortb200_paged_prep(const ortb200_paged_prep_args* a, ortb200_stream_t stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (!a || !a->qkv || !a->q_out || !a->k_cache || !a->v_cache || !a->cu_seqlens || !a->past_seqlens) return -1;
+  if (!a->slot_mapping && !a->block_table) return -1;
+  if (a->T < 0 || a->B <= 0 || a->H % 2 != 0 || a->block_size <= 0 || a->num_blocks <= 0) return -1;
+  if (a->do_rotary && (!a->cos_cache || !a->sin_cache)) return -2;
+  if ((a->k != nullptr) != (a->v != nullptr)) return -2;
+  const int rot = a->rot_dim > 0 ? a->rot_dim : a->H;
+  if (rot > a->H || rot % 2 != 0) return -2;
+  if (a->T == 0) return 0;
+  if (a->dtype == ORTB200_BF16) paged_prep_kernel<__nv_bfloat16><<<a->T, 256, 0, stream>>>(*a);
+  else if (a->dtype == ORTB200_F16) paged_prep_kernel<__half><<<a->T, 256, 0, stream>>>(*a);
+  else return -4;
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
 extern "C" int ortb200_gqa_prep(const ortb200_gqa_prep_args* a, ortb200_stream_t stream_) {

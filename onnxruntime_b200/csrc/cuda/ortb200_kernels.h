@@ -123,6 +123,30 @@ typedef struct {
 } ortb200_gqa_prep_args;
 int ortb200_gqa_prep(const ortb200_gqa_prep_args* args, ortb200_stream_t stream);
 
+// PagedAttention, step 1 (packed tokens [T, ...]): token t belongs to the sequence b with
+// cu_seqlens[b] <= t < cu_seqlens[b + 1] and sits at position past_seqlens[b] + t - cu_seqlens[b].  Q and K are rotated
+// at that position; K / V go to cache slot slot_mapping[t] (negative = skip) or, without a slot mapping, to
+// block_table[b, pos / block_size] * block_size + pos % block_size.  Caches are [num_blocks, block_size, Nk, H].
+typedef struct {
+  const void* qkv;             // packed [T, (N + 2 Nk) H], or Q [T, N H] when k / v are given
+  const void* k;
+  const void* v;
+  void* q_out;                 // [T, N, H]
+  void* k_cache;
+  void* v_cache;
+  const int* cu_seqlens;       // [B + 1]
+  const int* past_seqlens;     // [B]
+  const int* block_table;      // [B, max_blocks]
+  const int64_t* slot_mapping; // optional [T]
+  const void* cos_cache;
+  const void* sin_cache;
+  int T, B, N, Nk, H;
+  int block_size, max_blocks, num_blocks;
+  int rot_dim, interleaved, do_rotary, dtype;
+  int* status;                 // device int, may be null: a block index outside the table is reported here
+} ortb200_paged_prep_args;
+int ortb200_paged_prep(const ortb200_paged_prep_args* args, ortb200_stream_t stream);
+
 // GroupQueryAttention, decode step (one query token per sequence): split-KV attention over the cache.
 // q [B, N, H]; attends to cache positions [max(0, total - window), total) with total = seqlens_k[b] + 1.
 // workspace: ortb200_gqa_decode_workspace_bytes(); its first 64 KiB (counters) must be zero before the first
@@ -144,6 +168,12 @@ typedef struct {
   int dtype;
   int use_pdl;
   int* status;            // device int, may be null (bounded waits report here)
+  // Paged cache (PagedAttention): when block_table is given, k_cache / v_cache are [num_blocks, block_size, Nk, H]
+  // and key j of sequence b lives in block block_table[b * max_blocks + j / block_size]; Smax is then only the
+  // upper bound of the sequence length used to size the split-KV grid.
+  const int* block_table;
+  int block_size;
+  int max_blocks;
 } ortb200_gqa_decode_args;
 int ortb200_gqa_decode(const ortb200_gqa_decode_args* args, ortb200_stream_t stream);
 int64_t ortb200_gqa_decode_workspace_bytes(int B, int N, int H);
@@ -174,6 +204,7 @@ typedef struct {
   float softcap;
   int dtype;
   int* status;
+  const int* key_mask;     // optional [B, kv_len] int32, 0 = this key is padding for every query of the batch entry
 } ortb200_attn_prefill_args;
 int ortb200_attn_prefill(const ortb200_attn_prefill_args* args, ortb200_stream_t stream);
 
@@ -196,6 +227,13 @@ int ortb200_swiglu(const void* x, void* y, int64_t rows, int cols, int dtype, or
 int ortb200_rotary(const void* x, void* y, const int64_t* position_ids, int64_t position_offset, const void* cos_cache,
                    const void* sin_cache, int B, int S, int N, int H, int rot_dim, int interleaved, int bnsh, int dtype,
                    ortb200_stream_t stream);
+
+// MatMulNBits weights -> dense rows.  B uint8 [N, n_blocks, block_size * bits / 8] (low nibble = even k), scales
+// [N, n_blocks], zero_points packed uint8 [N, ceil(n_blocks * bits / 8)] (zp_is_packed = 1) or typed [N, n_blocks]
+// (zp_is_packed = 0) or null (2^(bits-1)); out [N, ldo] with out[n, k] = (q - zp) * scale.  bits = 4 or 8,
+// block_size a power of two >= 16, ldo a multiple of 8.
+int ortb200_nbits_dequant(const void* B, const void* scales, const void* zero_points, int zp_is_packed, void* out,
+                          int64_t N, int K, int bits, int block_size, int64_t ldo, int dtype, ortb200_stream_t stream);
 
 #ifdef __cplusplus
 }

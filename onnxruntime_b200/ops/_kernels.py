@@ -163,15 +163,22 @@ class GqaDecodeArgs(ctypes.Structure):
                 ("workspace", ctypes.c_void_p), ("workspace_bytes", ctypes.c_int64), ("B", ctypes.c_int), ("N", ctypes.c_int),
                 ("Nk", ctypes.c_int), ("H", ctypes.c_int), ("Smax", ctypes.c_int), ("splits", ctypes.c_int),
                 ("window", ctypes.c_int), ("scale", ctypes.c_float), ("softcap", ctypes.c_float), ("dtype", ctypes.c_int),
-                ("use_pdl", ctypes.c_int), ("status", ctypes.c_void_p)]
+                ("use_pdl", ctypes.c_int), ("status", ctypes.c_void_p), ("block_table", ctypes.c_void_p),
+                ("block_size", ctypes.c_int), ("max_blocks", ctypes.c_int)]
 
 
 _ATTN_WS = {}
 
 
-def gqa_decode(q, k_cache, v_cache, seqlens_k, splits=0, window=-1, scale=0.0, softcap=0.0, head_sink=None):
+def gqa_decode(q, k_cache, v_cache, seqlens_k, splits=0, window=-1, scale=0.0, softcap=0.0, head_sink=None, block_table=None):
+    """Dense cache [B,Nk,Smax,H]; or, with block_table [B,max_blocks] int32, a paged cache [num_blocks,block_size,Nk,H]."""
     B, N, H = q.shape
-    Nk, Smax = k_cache.shape[1], k_cache.shape[2]
+    if block_table is None:
+        Nk, Smax = k_cache.shape[1], k_cache.shape[2]
+        block_size = max_blocks = 0
+    else:
+        Nk, block_size, max_blocks = k_cache.shape[2], k_cache.shape[1], block_table.shape[1]
+        Smax = block_size * max_blocks
     out = torch.empty(B, N * H, dtype=q.dtype, device=q.device)
     lib().ortb200_gqa_decode_workspace_bytes.restype = ctypes.c_int64
     need = lib().ortb200_gqa_decode_workspace_bytes(B, N, H)
@@ -181,7 +188,8 @@ def gqa_decode(q, k_cache, v_cache, seqlens_k, splits=0, window=-1, scale=0.0, s
         ws = torch.zeros(need, dtype=torch.uint8, device=q.device)
         _ATTN_WS[key] = ws
     a = GqaDecodeArgs(_ptr(q.contiguous()), _ptr(k_cache), _ptr(v_cache), _ptr(seqlens_k), _ptr(head_sink), _ptr(out), _ptr(ws),
-                      ws.numel(), B, N, Nk, H, Smax, splits, window, scale, softcap, dtype_code(q.dtype), 0, None)
+                      ws.numel(), B, N, Nk, H, Smax, splits, window, scale, softcap, dtype_code(q.dtype), 0, None,
+                      _ptr(block_table), block_size, max_blocks)
     _check(lib().ortb200_gqa_decode(ctypes.byref(a), ctypes.c_void_p(stream_ptr())), "ortb200_gqa_decode")
     return out
 
@@ -192,12 +200,12 @@ class AttnPrefillArgs(ctypes.Structure):
                 ("N", ctypes.c_int), ("Nk", ctypes.c_int), ("H", ctypes.c_int), ("kv_len", ctypes.c_int),
                 ("q_strides", ctypes.c_int64 * 3), ("o_strides", ctypes.c_int64 * 3), ("kv_strides", ctypes.c_int64 * 3),
                 ("first_prompt", ctypes.c_int), ("causal", ctypes.c_int), ("window", ctypes.c_int), ("scale", ctypes.c_float),
-                ("softcap", ctypes.c_float), ("dtype", ctypes.c_int), ("status", ctypes.c_void_p)]
+                ("softcap", ctypes.c_float), ("dtype", ctypes.c_int), ("status", ctypes.c_void_p), ("key_mask", ctypes.c_void_p)]
 
 
 def attn_prefill(q, k, v, seqlens_k=None, first_prompt=True, causal=True, window=-1, scale=0.0, softcap=0.0,
-                 kv_layout="bnsh", status=None):
-    """q [B,S,N,H]; k/v [B,Nk,T,H] ("bnsh") or [B,T,Nk,H] ("bsnh").  Returns [B,S,N,H]."""
+                 kv_layout="bnsh", status=None, key_mask=None):
+    """q [B,S,N,H]; k/v [B,Nk,T,H] ("bnsh") or [B,T,Nk,H] ("bsnh"); key_mask int32 [B,T] (0 = padding).  Returns [B,S,N,H]."""
     B, S, N, H = q.shape
     if kv_layout == "bnsh":
         Nk, T = k.shape[1], k.shape[2]
@@ -209,8 +217,44 @@ def attn_prefill(q, k, v, seqlens_k=None, first_prompt=True, causal=True, window
     a = AttnPrefillArgs(_ptr(q), _ptr(k), _ptr(v), _ptr(seqlens_k), None, _ptr(out), B, S, N, Nk, H, T,
                         (ctypes.c_int64 * 3)(q.stride(0), q.stride(1), q.stride(2)),
                         (ctypes.c_int64 * 3)(out.stride(0), out.stride(1), out.stride(2)), (ctypes.c_int64 * 3)(*kvs),
-                        1 if first_prompt else 0, 1 if causal else 0, window, scale, softcap, dtype_code(q.dtype), _ptr(status))
+                        1 if first_prompt else 0, 1 if causal else 0, window, scale, softcap, dtype_code(q.dtype), _ptr(status),
+                        _ptr(key_mask))
     _check(lib().ortb200_attn_prefill(ctypes.byref(a), ctypes.c_void_p(stream_ptr())), "ortb200_attn_prefill")
+    return out
+
+
+class PagedPrepArgs(ctypes.Structure):
+    _fields_ = [("qkv", ctypes.c_void_p), ("k", ctypes.c_void_p), ("v", ctypes.c_void_p), ("q_out", ctypes.c_void_p),
+                ("k_cache", ctypes.c_void_p), ("v_cache", ctypes.c_void_p), ("cu_seqlens", ctypes.c_void_p),
+                ("past_seqlens", ctypes.c_void_p), ("block_table", ctypes.c_void_p), ("slot_mapping", ctypes.c_void_p),
+                ("cos_cache", ctypes.c_void_p), ("sin_cache", ctypes.c_void_p), ("T", ctypes.c_int), ("B", ctypes.c_int),
+                ("N", ctypes.c_int), ("Nk", ctypes.c_int), ("H", ctypes.c_int), ("block_size", ctypes.c_int),
+                ("max_blocks", ctypes.c_int), ("num_blocks", ctypes.c_int), ("rot_dim", ctypes.c_int), ("interleaved", ctypes.c_int),
+                ("do_rotary", ctypes.c_int), ("dtype", ctypes.c_int), ("status", ctypes.c_void_p)]
+
+
+def paged_prep(qkv, k_cache, v_cache, cu_seqlens, past_seqlens, block_table, N, Nk, cos=None, sin=None, interleaved=False,
+               slot_mapping=None, status=None):
+    """Packed qkv [T,(N+2Nk)H]; caches [num_blocks,block_size,Nk,H] updated in place.  Returns rotated q [T,N,H]."""
+    T = qkv.shape[0]
+    H = k_cache.shape[3]
+    q_out = torch.empty(T, N, H, dtype=qkv.dtype, device=qkv.device)
+    a = PagedPrepArgs(_ptr(qkv.contiguous()), None, None, _ptr(q_out), _ptr(k_cache), _ptr(v_cache), _ptr(cu_seqlens),
+                      _ptr(past_seqlens), _ptr(block_table), _ptr(slot_mapping), _ptr(cos), _ptr(sin), T, past_seqlens.numel(), N, Nk, H,
+                      k_cache.shape[1], block_table.shape[1], k_cache.shape[0], 0 if cos is None else cos.shape[1] * 2,
+                      1 if interleaved else 0, 0 if cos is None else 1, dtype_code(qkv.dtype), _ptr(status))
+    _check(lib().ortb200_paged_prep(ctypes.byref(a), ctypes.c_void_p(stream_ptr())), "ortb200_paged_prep")
+    return q_out
+
+
+def nbits_dequant(B, scales, zero_points, N, K, bits=4, block_size=32):
+    """MatMulNBits weights -> [N, K] rows of scales.dtype."""
+    out = torch.empty(N, K, dtype=scales.dtype, device=scales.device)
+    packed = zero_points is not None and zero_points.dtype == torch.uint8
+    _check(lib().ortb200_nbits_dequant(ctypes.c_void_p(_ptr(B.contiguous())), ctypes.c_void_p(_ptr(scales.contiguous())),
+                                       ctypes.c_void_p(_ptr(zero_points)), 1 if packed else 0, ctypes.c_void_p(_ptr(out)),
+                                       ctypes.c_int64(N), K, bits, block_size, ctypes.c_int64(K), dtype_code(scales.dtype),
+                                       ctypes.c_void_p(stream_ptr())), "ortb200_nbits_dequant")
     return out
 
 

@@ -1,0 +1,225 @@
+"""GPU kernels behind the quantised / paged / encoder-attention contrib ops: kernel-level numerics against PyTorch
+fp32 references, and session-level runs (GPU provider with fallback disabled) against the CPU provider."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def K():
+    from onnxruntime_b200.ops import _kernels
+    _kernels.lib()
+    return _kernels
+
+
+def _rel(a, b):
+    return (a.float() - b.float()).abs().max().item() / max(b.float().abs().max().item(), 1e-6)
+
+
+def _quantize(N, Kd, bits, bs, dtype, zp_mode, seed=0):
+    """Random block-quantised weights in the MatMulNBits layout plus their fp32 expansion."""
+    g = torch.Generator().manual_seed(seed)
+    nb = (Kd + bs - 1) // bs
+    q = torch.randint(0, 1 << bits, (N, nb, bs), generator=g)
+    scales = (torch.rand(N, nb, generator=g) * 0.02 + 0.005).to(dtype)
+    if zp_mode == "none":
+        zp_vals = torch.full((N, nb), 1 << (bits - 1))
+        zp = None
+    else:
+        zp_vals = torch.randint(0, 1 << bits, (N, nb), generator=g)
+        if zp_mode == "packed":
+            if bits == 4:
+                z = torch.nn.functional.pad(zp_vals, (0, nb % 2))
+                zp = (z[:, 0::2] | (z[:, 1::2] << 4)).to(torch.uint8)
+            else:
+                zp = zp_vals.to(torch.uint8)
+        else:
+            zp = zp_vals.to(dtype)
+    w = ((q - zp_vals.unsqueeze(-1)).float() * scales.float().unsqueeze(-1)).reshape(N, nb * bs)[:, :Kd]
+    if bits == 4:
+        B = (q[:, :, 0::2] | (q[:, :, 1::2] << 4)).to(torch.uint8)
+    else:
+        B = q.to(torch.uint8)
+    return B, scales, zp, w
+
+
+@pytest.mark.parametrize("bits,bs", [(4, 32), (4, 128), (8, 32), (4, 16)])
+@pytest.mark.parametrize("zp_mode", ["none", "packed", "typed"])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_nbits_dequant(K, bits, bs, zp_mode, dtype):
+    N, Kd = 300, 1000 if bs == 32 else 1024
+    B, scales, zp, w = _quantize(N, Kd, bits, bs, dtype, zp_mode)
+    out = K.nbits_dequant(B.cuda(), scales.cuda(), None if zp is None else zp.cuda(), N, Kd, bits, bs)
+    assert torch.equal(out.cpu(), w.to(dtype))
+
+
+@pytest.mark.parametrize("H,N,Nk", [(128, 8, 2), (64, 4, 4)])
+@pytest.mark.parametrize("block_size", [16, 64])
+def test_paged_decode_matches_dense(K, H, N, Nk, block_size):
+    torch.manual_seed(0)
+    B, max_len = 3, 500
+    max_blocks = (max_len + block_size - 1) // block_size
+    num_blocks = B * max_blocks + 5
+    past = torch.tensor([0, 137, 499], dtype=torch.int32, device="cuda")
+    perm = torch.randperm(num_blocks)[:B * max_blocks].reshape(B, max_blocks).to(torch.int32).cuda()
+    kc = torch.randn(num_blocks, block_size, Nk, H, device="cuda").bfloat16()
+    vc = torch.randn(num_blocks, block_size, Nk, H, device="cuda").bfloat16()
+    qkv = torch.randn(B, (N + 2 * Nk) * H, device="cuda").bfloat16()
+    half = H // 2
+    pos = torch.arange(1024, device="cuda").float().unsqueeze(1)
+    inv = 1.0 / (10000 ** (torch.arange(half, device="cuda").float() / half))
+    cos, sin = torch.cos(pos * inv).bfloat16(), torch.sin(pos * inv).bfloat16()
+    cu = torch.arange(B + 1, dtype=torch.int32, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    kc0, vc0 = kc.clone(), vc.clone()
+    q_rot = K.paged_prep(qkv, kc, vc, cu, past, perm, N, Nk, cos, sin, status=status)
+    out = K.gqa_decode(q_rot, kc, vc, past, block_table=perm)
+    torch.cuda.synchronize()
+    assert status.item() == 0
+
+    def rope(x, p):  # x [heads, H]
+        c, s = cos[p].float(), sin[p].float()
+        x1, x2 = x[:, :half].float(), x[:, half:].float()
+        return torch.cat([x1 * c - x2 * s, x2 * c + x1 * s], -1)
+
+    for b in range(B):
+        p = int(past[b])
+        q = rope(qkv[b, :N * H].view(N, H), p).bfloat16().float()
+        k_new = rope(qkv[b, N * H:(N + Nk) * H].view(Nk, H), p).bfloat16()
+        v_new = qkv[b, (N + Nk) * H:].view(Nk, H)
+        blk, off = int(perm[b, p // block_size]), p % block_size
+        assert torch.equal(kc[blk, off], k_new) and torch.equal(vc[blk, off], v_new)
+        L = p + 1
+        keys = torch.stack([kc[int(perm[b, j // block_size]), j % block_size] for j in range(L)]).float()   # L,Nk,H
+        vals = torch.stack([vc[int(perm[b, j // block_size]), j % block_size] for j in range(L)]).float()
+        keys = keys.repeat_interleave(N // Nk, 1)
+        vals = vals.repeat_interleave(N // Nk, 1)
+        s = torch.einsum("nh,lnh->nl", q, keys) / math.sqrt(H)
+        ref = torch.einsum("nl,lnh->nh", torch.softmax(s, -1), vals)
+        assert _rel(out[b].view(N, H), ref) < 2e-2, b
+    # nothing but the B new slots was written
+    changed = (kc != kc0).any(-1).any(-1).sum().item()
+    assert changed <= B
+
+
+def test_attn_prefill_key_mask(K):
+    torch.manual_seed(0)
+    B, S, N, H = 2, 300, 4, 64
+    q = torch.randn(B, S, N, H, device="cuda").half()
+    k = torch.randn(B, S, N, H, device="cuda").half()
+    v = torch.randn(B, S, N, H, device="cuda").half()
+    mask = (torch.rand(B, S, device="cuda") > 0.3).int()
+    mask[:, 0] = 1
+    out = K.attn_prefill(q, k, v, None, first_prompt=True, causal=False, kv_layout="bsnh", key_mask=mask)
+    s = torch.einsum("bsnh,btnh->bnst", q.float(), k.float()) / math.sqrt(H)
+    ref = torch.einsum("bnst,btnh->bsnh", torch.softmax(s.masked_fill(mask.view(B, 1, 1, S) == 0, float("-inf")), -1), v.float())
+    assert _rel(out, ref) < 2e-2
+
+
+# ------------------------------------------------------------------------------------------ session level
+def _both(op, inputs, initializers=(), n_outputs=1, **attrs):
+    """Run a one-node com.microsoft model on the CPU provider and on the GPU provider (fallback disabled)."""
+    import onnxruntime_b200 as ort
+    from onnxruntime_b200 import onnx_lite as ol
+    names = list(inputs)
+    node = ol.make_node(op, [n if inputs[n] is not None else "" for n in names], [f"o{i}" for i in range(n_outputs)],
+                        domain="com.microsoft", **attrs)
+    gin, inits = [], []
+    for n in names:
+        v = inputs[n]
+        if v is None:
+            continue
+        if n in initializers:
+            inits.append(ol.make_tensor(n, v))
+        else:
+            gin.append(ol.make_tensor_value_info(n, ol.np_dtype_to_onnx(v.dtype), list(v.shape)))
+    model = ol.make_model(ol.make_graph([node], "g", gin, [ol.make_tensor_value_info(f"o{i}", 0, None) for i in range(n_outputs)], inits)).serialize()
+    feeds = {n: inputs[n] for n in names if inputs[n] is not None and n not in initializers}
+    cpu = ort.InferenceSession(model, providers=["CPUExecutionProvider"])
+    gpu = ort.InferenceSession(model, providers=["CUDAExecutionProvider"], enable_fallback=False)
+    assert {n["ep"] for n in gpu.graph_nodes() if n["op_type"] == op} == {"CUDAExecutionProvider"}
+    before = gpu.kernel_launch_count()
+    rc = cpu.run(None, feeds)
+    rg = gpu.run(None, feeds)
+    gpu.check_device_status()
+    assert gpu.kernel_launch_count() > before, "the sm_100a kernel did not run"
+    return rc, rg
+
+
+def _np16(t):
+    return t.view(torch.int16).numpy().view(np.float16) if t.dtype == torch.float16 else t
+
+
+@pytest.mark.parametrize("M", [1, 8, 200])
+def test_session_matmul_nbits(M):
+    N, Kd, bs = 512, 1024, 32
+    B, scales, zp, w = _quantize(N, Kd, 4, bs, torch.float16, "packed", seed=3)
+    a = (torch.randn(2, M, Kd) * 0.5).half()
+    rc, rg = _both("MatMulNBits", {"a": a.numpy(), "B": B.numpy(), "scales": scales.numpy(), "zp": zp.numpy(), "g": None,
+                                   "bias": torch.randn(N).half().numpy()}, initializers=("B", "scales", "zp", "bias"),
+                   K=Kd, N=N, bits=4, block_size=bs)
+    ref = a.float() @ w.half().float().T
+    assert np.abs(rg[0].astype(np.float32) - rc[0].astype(np.float32)).max() / np.abs(rc[0].astype(np.float32)).max() < 1e-2
+    assert rg[0].shape == (2, M, N) and np.isfinite(rg[0].astype(np.float32)).all()
+    assert ref.shape == (2, M, N)
+
+
+@pytest.mark.parametrize("mask", ["none", "lengths", "raw"])
+def test_session_bert_attention(mask):
+    torch.manual_seed(0)
+    B, S, N, H = 2, 200, 4, 64
+    W = N * H
+    x = (torch.randn(B, S, W) * 0.5).half()
+    w = (torch.randn(W, 3 * W) * 0.05).half()
+    b = (torch.randn(3 * W) * 0.1).half()
+    m = None
+    if mask == "lengths":
+        m = np.array([200, 77], dtype=np.int32)
+    elif mask == "raw":
+        m = (np.random.RandomState(0).rand(B, S) > 0.3).astype(np.int32)
+        m[:, 0] = 1
+    rc, rg = _both("Attention", {"x": x.numpy(), "w": w.numpy(), "b": b.numpy(), "mask": m}, initializers=("w", "b"), num_heads=N)
+    c, g = rc[0].astype(np.float32), rg[0].astype(np.float32)
+    assert np.abs(c - g).max() / np.abs(c).max() < 2e-2
+
+
+def test_session_multihead_attention_packed_and_separate():
+    torch.manual_seed(0)
+    B, S, N, H = 2, 160, 4, 64
+    qkv = (torch.randn(B, S, N, 3, H) * 0.5).half()
+    rc, rg = _both("MultiHeadAttention", {"q": qkv.numpy()}, num_heads=N)
+    c, g = rc[0].astype(np.float32), rg[0].astype(np.float32)
+    assert np.abs(c - g).max() / np.abs(c).max() < 2e-2
+    q = (torch.randn(B, S, N * H) * 0.5).half()
+    k = (torch.randn(B, 96, N * H) * 0.5).half()
+    v = (torch.randn(B, 96, N * H) * 0.5).half()
+    rc, rg = _both("MultiHeadAttention", {"q": q.numpy(), "k": k.numpy(), "v": v.numpy()}, num_heads=N)
+    c, g = rc[0].astype(np.float32), rg[0].astype(np.float32)
+    assert np.abs(c - g).max() / np.abs(c).max() < 2e-2
+
+
+def test_session_paged_attention_decode():
+    import onnxruntime_b200 as ort
+    torch.manual_seed(0)
+    B, N, Nk, H, bsz, max_blocks = 3, 8, 2, 128, 16, 8
+    num_blocks = 40
+    qkv = (torch.randn(B, (N + 2 * Nk) * H) * 0.5).half()
+    kc = (torch.randn(num_blocks, bsz, Nk, H) * 0.5).half()
+    vc = (torch.randn(num_blocks, bsz, Nk, H) * 0.5).half()
+    table = torch.randperm(num_blocks)[:B * max_blocks].reshape(B, max_blocks).to(torch.int32)
+    past = torch.tensor([5, 100, 64], dtype=torch.int32)
+    cu = torch.arange(B + 1, dtype=torch.int32)
+    half = H // 2
+    pos = torch.arange(256).float().unsqueeze(1)
+    inv = 1.0 / (10000 ** (torch.arange(half).float() / half))
+    cos, sin = torch.cos(pos * inv).half(), torch.sin(pos * inv).half()
+    rc, rg = _both("PagedAttention", {"q": qkv.numpy(), "k": None, "v": None, "kc": kc.numpy(), "vc": vc.numpy(), "cu": cu.numpy(),
+                                      "past": past.numpy(), "table": table.numpy(), "cos": cos.numpy(), "sin": sin.numpy()},
+                   n_outputs=3, initializers=("cos", "sin"), num_heads=N, kv_num_heads=Nk, do_rotary=1)
+    for i in range(3):
+        c, g = rc[i].astype(np.float32), rg[i].astype(np.float32)
+        assert np.abs(c - g).max() / np.abs(c).max() < 2e-2, i
