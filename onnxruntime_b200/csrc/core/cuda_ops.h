@@ -11,9 +11,10 @@ void CheckLaunch(int rc, const char* what);
 // out[M,N] = act(alpha * x[M,K] @ w_nk[N,K]^T + bias) + residual on the tcgen05 GEMM kernel.
 // act == SWIGLU: w_nk holds gate rows then up rows, `dual_offset` rows apart.
 // fused_allreduce: the kernel also sums the result over all ranks through the session's symmetric workspace.
+// x2d / w_nk of type Float8_e4m3fn run the tensor cores in 8-bit mode; out_type (fp16 / bf16) is then required.
 at::Tensor LaunchGemm(OpKernelContext& ctx, const at::Tensor& x2d, const at::Tensor& w_nk, int64_t n_out,
                       int64_t dual_offset, const at::Tensor& bias, const at::Tensor& residual2d, int act, float alpha,
-                      bool fused_allreduce = false);
+                      bool fused_allreduce = false, at::ScalarType out_type = at::ScalarType::Undefined);
 // True when the fused GEMM + all-reduce kernel can take an [M, N] row-parallel product in this session.
 bool CanFuseAllReduce(OpKernelContext& ctx, int64_t M, int64_t N);
 

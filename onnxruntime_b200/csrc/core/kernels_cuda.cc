@@ -52,10 +52,13 @@ void CheckLaunch(int rc, const char* what) {
 
 // out[M,N] = act(x[M,K] @ w_nk[N,K]^T + bias) + residual on the tcgen05 GEMM.
 at::Tensor LaunchGemm(Ctx& ctx, const at::Tensor& x2d, const at::Tensor& w_nk, int64_t n_out, int64_t dual_offset,
-                      const at::Tensor& bias, const at::Tensor& residual2d, int act, float alpha, bool fused_allreduce) {
+                      const at::Tensor& bias, const at::Tensor& residual2d, int act, float alpha, bool fused_allreduce,
+                      at::ScalarType out_type) {
   InferenceSession* s = ctx.session();
   const int64_t M = x2d.size(0), K = x2d.size(1);
-  at::Tensor out = at::empty({M, n_out}, x2d.options());
+  const bool fp8 = x2d.scalar_type() == at::kFloat8_e4m3fn;
+  if (out_type == at::ScalarType::Undefined) out_type = x2d.scalar_type();
+  at::Tensor out = at::empty({M, n_out}, x2d.options().dtype(out_type));
   if (M == 0) return out;
   const int64_t ws_bytes = ortb200_gemm_workspace_bytes(static_cast<int>(M), static_cast<int>(n_out), static_cast<int>(K), act);
   at::Tensor& ws = s->GemmWorkspace(ws_bytes);
@@ -72,7 +75,8 @@ at::Tensor LaunchGemm(Ctx& ctx, const at::Tensor& x2d, const at::Tensor& w_nk, i
   a.K = static_cast<int>(K);
   a.w_rows = static_cast<int>(w_nk.size(0));
   a.dual_offset = static_cast<int>(dual_offset);
-  a.dtype = DtypeCode(x2d.scalar_type());
+  a.dtype = DtypeCode(out_type);
+  a.in_dtype = fp8 ? ORTB200_F8E4M3 : 0;
   a.act = act;
   a.alpha = alpha;
   a.workspace = ws.data_ptr();
@@ -97,7 +101,7 @@ bool CanFuseAllReduce(OpKernelContext& ctx, int64_t M, int64_t N) {
   if (static_cast<int>(s->symm_peers.size()) != s->world_size) return false;
   if (s->config().Get("ortb200.fused_allreduce", "1") != "1") return false;
   if (M > 64) return false;
-  const int64_t slot = (s->symm_bytes - 262144) / (2LL * s->world_size * 8);
+  const int64_t slot = (s->symm_bytes / 2 - 262144) / (2LL * s->world_size * 8);
   return slot >= M * N && (N + 127) / 128 * 8 <= 4096;
 }
 

@@ -5,8 +5,11 @@
 #include <ATen/ATen.h>
 #include <ATen/cuda/CUDAContext.h>
 
+#include <algorithm>
 #include <cmath>
 
+#include "collective.h"
+#include "contrib_math.h"
 #include "cuda_ops.h"
 #include "ortb200_kernels.h"
 #include "session.h"
@@ -342,6 +345,299 @@ class MultiHeadAttentionKernel final : public WithFallback {
   float scale_ = 0.f;
 };
 
+// ---------------------------------------------------------------------------------------------------------------
+// MoE / ShardedMoE on the GPU: routing + permutation kernels, two grouped tcgen05 GEMMs driven by a device-side
+// tile plan, weighted combine.  Seven launches, no host synchronisation.  With expert parallelism each rank serves its
+// own experts and the partial outputs are summed across ranks.
+class MoeKernel final : public WithFallback {
+ public:
+  explicit MoeKernel(const OpKernelInfo& info) : WithFallback(info) {
+    const Node& n = info.node;
+    sharded_ = n.op_type == "ShardedMoE";
+    attrs_ = contrib::ParseMoeAttrs(n);
+    start_ = sharded_ ? n.attr_i("local_experts_start_index", 0) : 0;
+    tensor_shards_ = sharded_ ? n.attr_i("tensor_shards", 1) : 1;
+    const at::Tensor* fc1 = info.constant_input(2);
+    const at::Tensor* fc2 = info.constant_input(4);
+    const at::Tensor* fc3 = info.node.inputs.size() > 6 && !info.node.inputs[6].empty() ? info.constant_input(6) : nullptr;
+    const bool has_fc3 = info.node.inputs.size() > 6 && !info.node.inputs[6].empty();
+    if (!fc1 || !fc2 || (has_fc3 && !fc3) || !HalfType(fc1->scalar_type()) || fc1->dim() != 3 || fc2->dim() != 3) return;
+    if (attrs_.activation == "swiglu" || tensor_shards_ > 1) return;
+    if (has_fc3 && attrs_.activation != "silu") return;
+    // to [E, out, in] with `in` contiguous; ShardedMoE stores [E, in, out]
+    at::Tensor w1 = sharded_ ? fc1->transpose(1, 2) : *fc1;
+    at::Tensor w2 = sharded_ ? fc2->transpose(1, 2) : *fc2;
+    E_local_ = w1.size(0);
+    I_ = w1.size(1);
+    H_ = w1.size(2);
+    if (w2.size(1) != H_ || w2.size(2) != I_ || H_ % 8 != 0 || I_ % 8 != 0) return;
+    if (has_fc3) {
+      at::Tensor w3 = sharded_ ? fc3->transpose(1, 2) : *fc3;
+      if (w3.sizes() != w1.sizes()) return;
+      w13_ = at::cat({w1, w3}, 1).contiguous();  // gate rows, then up rows
+      dual_ = true;
+    } else {
+      w13_ = w1.contiguous();
+    }
+    w2_ = w2.contiguous();
+    ok_ = true;
+  }
+  std::vector<int> PrepackedInputs() const override { return {}; }
+
+  void Compute(Ctx& ctx) const override {
+    const at::Tensor& x = ctx.RequiredInput(0);
+    const at::Tensor& logits_in = ctx.RequiredInput(1);
+    const int dt = DtypeCode(x.scalar_type());
+    const bool fc3_bias = ctx.HasInput(7);
+    if (!ok_ || dt < 0 || x.scalar_type() != w13_.scalar_type() || x.size(-1) != H_ || fc3_bias ||
+        attrs_.k > 8 || logits_in.size(-1) > 256) {
+      Fallback(ctx);
+      return;
+    }
+    at::Tensor x2 = x.reshape({-1, H_}).contiguous();
+    const int64_t T = x2.size(0), E = logits_in.size(-1), k = attrs_.k;
+    at::Tensor logits = logits_in.reshape({T, E}).contiguous();
+    int ldt = DtypeCode(logits.scalar_type());
+    if (logits.scalar_type() == at::kFloat) ldt = ORTB200_F32;
+    if (ldt < 0) {
+      Fallback(ctx);
+      return;
+    }
+    const int64_t R = T * k;
+    const int tile_rows = ortb200_moe_tile_rows(R, static_cast<int>(E_local_));
+    const int max_tiles = ortb200_moe_max_tiles(R, static_cast<int>(E_local_), tile_rows);
+    auto iopt = x.options().dtype(at::kInt);
+    at::Tensor topk_idx = at::empty({T, k}, iopt), row_of = at::empty({T, k}, iopt);
+    at::Tensor topk_w = at::empty({T, k}, x.options().dtype(at::kFloat));
+    at::Tensor ints = at::empty({3 * E_local_ + 2 + 4}, iopt);  // counts | offsets | cursors | num_tiles
+    at::Tensor tile_info = at::empty({max_tiles, 4}, iopt);
+    at::Tensor xp = at::zeros({R, H_}, x.options());
+    ortb200_moe_route_args ra{};
+    ra.logits = logits.data_ptr();
+    ra.x = x2.data_ptr();
+    ra.tokens = static_cast<int>(T); ra.E = static_cast<int>(E); ra.k = static_cast<int>(k); ra.H = static_cast<int>(H_);
+    ra.normalize = attrs_.normalize ? 1 : 0;
+    ra.expert_begin = static_cast<int>(start_);
+    ra.expert_end = static_cast<int>(start_ + E_local_);
+    ra.tile_rows = tile_rows; ra.max_tiles = max_tiles;
+    ra.dtype = ldt;
+    ra.topk_idx = topk_idx.data_ptr<int>();
+    ra.topk_w = topk_w.data_ptr<float>();
+    int* ip = ints.data_ptr<int>();
+    ra.counts = ip;
+    ra.offsets = ip + E_local_;
+    ra.cursors = ip + 2 * E_local_ + 1;
+    ra.num_tiles = ip + 3 * E_local_ + 1;
+    ra.tile_info = tile_info.data_ptr();
+    ra.xp = xp.data_ptr();
+    ra.row_of = row_of.data_ptr<int>();
+    if (ra.expert_end > ra.E) {
+      Fallback(ctx);
+      return;
+    }
+    CheckLaunch(ortb200_moe_route(&ra, ctx.cuda_stream()), "ortb200_moe_route");
+
+    at::Tensor fc1_bias = ctx.HasInput(3) ? ctx.Input(3).contiguous() : at::Tensor();
+    at::Tensor fc2_bias = ctx.HasInput(5) ? ctx.Input(5).contiguous() : at::Tensor();
+    if (fc2_bias.defined() && fc2_bias.size(0) != E_local_) fc2_bias = fc2_bias.narrow(0, start_, E_local_).contiguous();
+    at::Tensor h = at::empty({R, I_}, x.options());
+    ortb200_gemm_grouped_args g{};
+    g.x = xp.data_ptr(); g.w = w13_.data_ptr(); g.out = h.data_ptr();
+    g.bias = fc1_bias.defined() ? fc1_bias.data_ptr() : nullptr;
+    g.tile_info = tile_info.data_ptr(); g.num_tiles = ra.num_tiles;
+    g.rows = static_cast<int>(R); g.N = static_cast<int>(I_); g.K = static_cast<int>(H_);
+    g.num_experts = static_cast<int>(E_local_);
+    g.w_rows_per_expert = static_cast<int>(dual_ ? 2 * I_ : I_);
+    g.dual_offset = dual_ ? static_cast<int>(I_) : 0;
+    g.tile_rows = tile_rows; g.max_tiles = max_tiles;
+    g.dtype = dt;
+    g.act = dual_ ? ORTB200_ACT_SWIGLU : ActOf(attrs_.activation);
+    g.status = ctx.session()->StatusWord().data_ptr<int>();
+    CheckLaunch(ortb200_gemm_grouped(&g, ctx.cuda_stream()), "ortb200_gemm_grouped(fc1)");
+    at::Tensor y = at::empty({R, H_}, x.options());
+    g.x = h.data_ptr(); g.w = w2_.data_ptr(); g.out = y.data_ptr(); g.bias = nullptr;
+    g.N = static_cast<int>(H_); g.K = static_cast<int>(I_);
+    g.w_rows_per_expert = static_cast<int>(H_); g.dual_offset = 0; g.act = ORTB200_ACT_NONE;
+    CheckLaunch(ortb200_gemm_grouped(&g, ctx.cuda_stream()), "ortb200_gemm_grouped(fc2)");
+    at::Tensor out = at::empty({T, H_}, x.options());
+    CheckLaunch(ortb200_moe_combine(y.data_ptr(), fc2_bias.defined() ? fc2_bias.data_ptr() : nullptr, out.data_ptr(), static_cast<int>(T),
+                                    static_cast<int>(H_), static_cast<int>(k), static_cast<int>(start_), topk_idx.data_ptr<int>(),
+                                    topk_w.data_ptr<float>(), row_of.data_ptr<int>(), dt, ctx.cuda_stream()),
+                "ortb200_moe_combine");
+    ctx.session()->AddLaunches(6);
+    if (sharded_ && ctx.session()->world_size > 1) out = AllReduceSum(ctx.session(), out.to(at::kFloat)).to(x.scalar_type());
+    ctx.SetOutput(0, out.reshape(x.sizes()));
+  }
+
+ private:
+  static int ActOf(const std::string& a) {
+    if (a == "relu") return ORTB200_ACT_RELU;
+    if (a == "gelu") return ORTB200_ACT_GELU;
+    if (a == "silu") return ORTB200_ACT_SILU;
+    return ORTB200_ACT_NONE;
+  }
+  contrib::MoeAttrs attrs_;
+  bool sharded_ = false, ok_ = false, dual_ = false;
+  int64_t start_ = 0, tensor_shards_ = 1, E_local_ = 0, I_ = 0, H_ = 0;
+  at::Tensor w13_, w2_;
+};
+
+// ---------------------------------------------------------------------------------------------------------------
+// AllReduce / AllGather / AllToAll as one kernel over the session's peer-mapped workspace; messages that do not fit
+// (or sessions without a workspace) go through the process group instead.
+class SymmCollectiveKernel final : public WithFallback {
+ public:
+  explicit SymmCollectiveKernel(const OpKernelInfo& info) : WithFallback(info) {
+    const std::string& op = info.node.op_type;
+    op_ = op == "AllReduce" ? ORTB200_COLL_ALLREDUCE : (op == "AllGather" ? ORTB200_COLL_ALLGATHER : ORTB200_COLL_ALLTOALL);
+    axis_ = info.node.attr_i("axis", 0);
+  }
+  void Compute(Ctx& ctx) const override {
+    InferenceSession* s = ctx.session();
+    const int world = s->world_size;
+    if (world <= 1 || world > 8 || static_cast<int>(s->symm_peers.size()) != world ||
+        s->config().Get("ortb200.symm_collectives", "1") != "1") {
+      Fallback(ctx);
+      return;
+    }
+    const int n = op_ == ORTB200_COLL_ALLREDUCE ? std::min(ctx.InputCount(), ctx.OutputCount()) : 1;
+    // decide for the whole node first: either every tensor takes the kernel or the node falls back
+    for (int i = 0; i < n; ++i) {
+      if (!ctx.HasInput(i)) continue;
+      if (!Plan(ctx.Input(i), world, s->symm_bytes, nullptr)) {
+        Fallback(ctx);
+        return;
+      }
+    }
+    for (int i = 0; i < n; ++i) {
+      if (!ctx.HasInput(i)) continue;
+      at::Tensor in = ctx.Input(i).contiguous();
+      ortb200_symm_collective_args a{};
+      Plan(in, world, s->symm_bytes, &a);
+      std::vector<int64_t> shape = in.sizes().vec();
+      if (op_ == ORTB200_COLL_ALLGATHER) {
+        if (shape.empty()) shape = {1};
+        shape[Axis(in)] *= world;
+      }
+      at::Tensor out = at::empty(shape, in.options());
+      a.op = op_;
+      a.in = in.data_ptr();
+      a.out = out.data_ptr();
+      a.world = world;
+      a.rank = s->rank;
+      for (int r = 0; r < world; ++r) a.peers[r] = s->symm_peers[r];
+      a.symm_bytes = s->symm_bytes;
+      a.status = s->StatusWord().data_ptr<int>();
+      a.use_pdl = s->config().Get("ortb200.pdl", "0") == "1" ? 1 : 0;
+      CheckLaunch(ortb200_symm_collective(&a, ctx.cuda_stream()), "ortb200_symm_collective");
+      s->AddLaunches(1);
+      ctx.SetOutput(i, out);
+    }
+  }
+
+ private:
+  int64_t Axis(const at::Tensor& t) const {
+    const int64_t d = std::max<int64_t>(t.dim(), 1);
+    return axis_ < 0 ? axis_ + d : axis_;
+  }
+  // fills rows / row_bytes / dtype; false when the kernel cannot take this tensor
+  bool Plan(const at::Tensor& t, int world, int64_t symm_bytes, ortb200_symm_collective_args* a) const {
+    if (!t.defined() || !t.is_cuda() || t.numel() == 0) return false;
+    const int64_t esz = t.element_size();
+    const int64_t bytes = t.numel() * esz;
+    const int64_t limit = ortb200_symm_collective_max_bytes(op_, world, symm_bytes);
+    int64_t rows = 1, row_bytes = bytes;
+    int dt = 0;
+    if (op_ == ORTB200_COLL_ALLREDUCE) {
+      if (t.scalar_type() == at::kBFloat16) dt = ORTB200_BF16;
+      else if (t.scalar_type() == at::kHalf) dt = ORTB200_F16;
+      else if (t.scalar_type() == at::kFloat) dt = ORTB200_F32;
+      else return false;
+      if (bytes % 16 != 0 || bytes > limit) return false;
+    } else if (op_ == ORTB200_COLL_ALLGATHER) {
+      const int64_t ax = Axis(t);
+      if (ax < 0 || ax >= std::max<int64_t>(t.dim(), 1)) return false;
+      for (int64_t d = 0; d < ax; ++d) rows *= t.size(d);
+      row_bytes = bytes / rows;
+      if (row_bytes % 16 != 0 || bytes > limit) return false;
+    } else {
+      if (bytes % (16 * world) != 0 || bytes > limit) return false;
+      row_bytes = bytes / world;
+    }
+    if (a) {
+      a->rows = rows;
+      a->row_bytes = row_bytes;
+      a->dtype = dt;
+    }
+    return true;
+  }
+  int op_ = 0;
+  int64_t axis_ = 0;
+};
+
+// ---------------------------------------------------------------------------------------------------------------
+// GemmFloat8 with e4m3 operands: Y = act(alpha * scaleA * scaleB * A @ B^T + C) / scaleY on the 8-bit tensor-core path.
+class GemmFloat8Kernel final : public WithFallback {
+ public:
+  explicit GemmFloat8Kernel(const OpKernelInfo& info) : WithFallback(info) {
+    const Node& n = info.node;
+    trans_a_ = n.attr_i("transA", 0) != 0;
+    trans_b_ = n.attr_i("transB", 0) != 0;
+    alpha_ = n.attr_f("alpha", 1.f);
+    beta_ = n.attr_f("beta", 0.f);
+    act_name_ = n.attr_s("activation", "NONE");
+    out_dtype_ = n.attr_i("dtype", 1);
+    const at::Tensor* b = info.constant_input(1);
+    if (b && b->dim() == 2 && b->scalar_type() == at::kFloat8_e4m3fn && !trans_b_)
+      b_nk_ = b->view(at::kByte).t().contiguous().view(at::kFloat8_e4m3fn);  // pre-pack to [N, K]
+    for (int i = 3; i <= 5; ++i) {
+      const at::Tensor* sc = static_cast<int>(n.inputs.size()) > i && !n.inputs[i].empty() ? info.constant_input(i) : nullptr;
+      if (sc) const_scale_[i - 3] = sc->to(at::kCPU, at::kFloat).reshape({-1})[0].item<float>();
+    }
+  }
+  void Compute(Ctx& ctx) const override {
+    const at::Tensor& A = ctx.RequiredInput(0);
+    at::ScalarType out_t = out_dtype_ == 10 ? at::kHalf : (out_dtype_ == 16 ? at::kBFloat16 : at::ScalarType::Undefined);
+    const bool b_ok = b_nk_.defined() || (trans_b_ && ctx.RequiredInput(1).scalar_type() == at::kFloat8_e4m3fn);
+    int act = ORTB200_ACT_NONE;
+    bool act_ok = true;
+    if (act_name_ == "RELU") act = ORTB200_ACT_RELU;
+    else if (act_name_ == "GELU") act = ORTB200_ACT_GELU;
+    else if (act_name_ != "NONE") act_ok = false;
+    at::Tensor bias;
+    bool c_ok = true;
+    if (ctx.HasInput(2)) {
+      bias = ctx.Input(2);
+      c_ok = beta_ == 1.f && bias.dim() == 1 && bias.scalar_type() == out_t;
+    }
+    // scaleY divides after the activation; with an activation in between it cannot be folded into alpha
+    const bool has_sy = ctx.HasInput(5);
+    if (A.scalar_type() != at::kFloat8_e4m3fn || A.dim() != 2 || trans_a_ || !b_ok || out_t == at::ScalarType::Undefined || !act_ok ||
+        !c_ok || (has_sy && (act != ORTB200_ACT_NONE || bias.defined())) || A.size(1) % 16 != 0) {
+      Fallback(ctx);
+      return;
+    }
+    auto scale = [&](int i) -> float {
+      if (!ctx.HasInput(i)) return 1.f;
+      if (!std::isnan(const_scale_[i - 3])) return const_scale_[i - 3];
+      return ctx.Input(i).to(at::kCPU, at::kFloat).reshape({-1})[0].item<float>();  // runtime scale: one host read
+    };
+    float alpha = alpha_ * scale(3) * scale(4);
+    if (has_sy) alpha /= scale(5);
+    at::Tensor w = b_nk_.defined() ? b_nk_ : ctx.Input(1).contiguous();
+    at::Tensor y = LaunchGemm(ctx, A.contiguous(), w, w.size(0), 0, bias, at::Tensor(), act, alpha, false, out_t);
+    ctx.SetOutput(0, y);
+  }
+
+ private:
+  bool trans_a_ = false, trans_b_ = false;
+  float alpha_ = 1.f, beta_ = 0.f;
+  std::string act_name_;
+  int64_t out_dtype_ = 1;
+  at::Tensor b_nk_;
+  float const_scale_[3] = {NAN, NAN, NAN};
+};
+
 template <typename K>
 void Reg(KernelRegistry& r, const std::string& domain, const std::string& op, std::vector<int> host = {},
          std::function<bool(const Node&, const Graph&)> supports = nullptr) {
@@ -361,6 +657,12 @@ void RegisterCudaKernels3(KernelRegistry& r) {
   Reg<PagedAttentionKernel>(r, MS, "PagedAttention");
   Reg<BertAttentionKernel>(r, MS, "Attention");
   Reg<MultiHeadAttentionKernel>(r, MS, "MultiHeadAttention");
+  Reg<MoeKernel>(r, MS, "MoE");
+  Reg<MoeKernel>(r, MS, "ShardedMoE");
+  Reg<GemmFloat8Kernel>(r, MS, "GemmFloat8");
+  Reg<SymmCollectiveKernel>(r, MS, "AllReduce");
+  Reg<SymmCollectiveKernel>(r, MS, "AllGather");
+  Reg<SymmCollectiveKernel>(r, MS, "AllToAll");
 }
 
 }  // namespace ortb

@@ -26,7 +26,14 @@ struct SmallGemmParams {
   long long slot_elems;      // elements per (parity, source rank) slot, >= M * ldo
   unsigned int* epoch;       // local: number of completed fused launches
   unsigned int* done;        // local: CTAs finished in the current launch
+  // ---- grouped mode (mixture of experts): blockIdx.y indexes a device-side tile list instead of a row block
+  const int4* tile_info;     // {expert, first row, end row, unused}; null = ordinary GEMM
+  const int* num_tiles;      // device scalar: entries of tile_info in use
+  int w_rows_per_expert;     // rows of W (and entries of bias: N) that belong to one expert
 };
+
+// Grouped GEMM over a device-side tile list (see ortb200_gemm_grouped).
+int launch_gemm_grouped(const ortb200_gemm_grouped_args* a, cudaStream_t stream);
 
 // bn in {16, 32, 64}.  Returns 0 or a negative launch error; reports the cluster size and pipeline depth used.
 int launch_gemm_smallm(const ortb200_gemm_args* a, int bn, cudaStream_t stream, int* cluster_out, int* stages_out);

@@ -111,7 +111,20 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
   const int C = p.cluster;
   const int rank = C > 1 ? static_cast<int>(cluster_ctarank()) : 0;
   const int n0 = (blockIdx.x / C) * kBM;
-  const int m0 = blockIdx.y * BN;
+  int m0 = blockIdx.y * BN;
+  int m_end = p.M;
+  int w_row0 = 0;       // first W row of this tile's expert
+  int bias0 = 0;
+  if (p.tile_info != nullptr) {
+    // grouped mode: the tile list comes from the kernel before this one
+    pdl_wait_prior_grids();
+    if (static_cast<int>(blockIdx.y) >= *p.num_tiles) return;  // nothing allocated yet; the whole CTA leaves
+    const int4 ti = p.tile_info[blockIdx.y];
+    m0 = ti.y;
+    m_end = ti.z;
+    w_row0 = ti.x * p.w_rows_per_expert;
+    bias0 = ti.x * p.N;
+  }
   const int kb_begin = static_cast<int>(static_cast<long long>(rank) * p.num_kb / C);
   const int kb_end = static_cast<int>(static_cast<long long>(rank + 1) * p.num_kb / C);
   const int nkb = kb_end - kb_begin;  // >= 1 (the host keeps C <= num_kb)
@@ -145,8 +158,8 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
       for (int i = 0; i < pre; ++i) {
         uint8_t* st = smem + i * S::kStageBytes;
         mbar_expect_tx(&full_bar[i], S::kStageBytes);
-        tma_load_2d_hint(st, &tmap_w, &full_bar[i], (kb_begin + i) * kBK, n0, pol_w);
-        if (DUAL) tma_load_2d_hint(st + S::kABytes, &tmap_w, &full_bar[i], (kb_begin + i) * kBK, n0 + p.dual_offset, pol_w);
+        tma_load_2d_hint(st, &tmap_w, &full_bar[i], (kb_begin + i) * kBK, w_row0 + n0, pol_w);
+        if (DUAL) tma_load_2d_hint(st + S::kABytes, &tmap_w, &full_bar[i], (kb_begin + i) * kBK, w_row0 + n0 + p.dual_offset, pol_w);
       }
       pdl_wait_prior_grids();
       for (int i = 0; i < pre; ++i) {
@@ -161,8 +174,8 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
         }
         uint8_t* st = smem + s * S::kStageBytes;
         mbar_expect_tx(&full_bar[s], S::kStageBytes);
-        tma_load_2d_hint(st, &tmap_w, &full_bar[s], (kb_begin + i) * kBK, n0, pol_w);
-        if (DUAL) tma_load_2d_hint(st + S::kABytes, &tmap_w, &full_bar[s], (kb_begin + i) * kBK, n0 + p.dual_offset, pol_w);
+        tma_load_2d_hint(st, &tmap_w, &full_bar[s], (kb_begin + i) * kBK, w_row0 + n0, pol_w);
+        if (DUAL) tma_load_2d_hint(st + S::kABytes, &tmap_w, &full_bar[s], (kb_begin + i) * kBK, w_row0 + n0 + p.dual_offset, pol_w);
         tma_load_2d(st + S::kABytes * (DUAL ? 2 : 1), &tmap_x, &full_bar[s], (kb_begin + i) * kBK, m0);
       }
     }
@@ -223,8 +236,8 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
     const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
     pdl_wait_prior_grids();  // out / residual may still be in use by the previous kernel
     const float bias_v = (p.bias != nullptr && n_ok)
-                             ? (p.dtype == ORTB200_BF16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.bias)[n])
-                                                        : __half2float(reinterpret_cast<const __half*>(p.bias)[n]))
+                             ? (p.dtype == ORTB200_BF16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.bias)[bias0 + n])
+                                                        : __half2float(reinterpret_cast<const __half*>(p.bias)[bias0 + n]))
                              : 0.0f;
     // token columns this CTA finishes
     const int cols_per = BN / C;
@@ -261,7 +274,7 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
       const int m = m0 + j;
       if (fused_ar) {
         // push this rank's partial sum to every rank (its own copy included); 128 lanes write 1 KiB contiguous
-        if (n_ok && m < p.M) {
+        if (n_ok && m < m_end) {
           const long long off = stage_base + static_cast<long long>(p.rank) * p.slot_elems + static_cast<long long>(m) * p.ldo + n;
           for (int d = 0; d < p.world; ++d) {
             const int dst_rank = (p.rank + d) % p.world;  // spread the first stores over the peers
@@ -271,7 +284,7 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
         }
         continue;
       }
-      if (n_ok && m < p.M) {
+      if (n_ok && m < m_end) {
         float y = v * p.alpha + bias_v;
         if (DUAL) {
           const float g = y / (1.0f + __expf(-y));
@@ -297,7 +310,7 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
 #pragma unroll 1
       for (int jj = 0; jj < cols_per; ++jj) {
         const int m = m0 + j_begin + jj;
-        if (!(n_ok && m < p.M)) continue;
+        if (!(n_ok && m < m_end)) continue;
         float y = 0.f;
         for (int s = 0; s < p.world; ++s) {  // fixed order: every rank adds in the same order and gets the same bits
           const unsigned long long* src = stage_local + static_cast<long long>(s) * p.slot_elems + static_cast<long long>(m) * p.ldo + n;
@@ -410,11 +423,12 @@ int launch_gemm_smallm(const ortb200_gemm_args* a, int bn, cudaStream_t stream, 
   p.dtype = a->dtype; p.act = a->act; p.alpha = a->alpha; p.out = a->out; p.ldo = a->ldo; p.bias = a->bias;
   p.residual = a->residual; p.ldr = a->ldr; p.status = a->status;
   p.world = 1; p.rank = 0; p.staging_offset = 0; p.slot_elems = 0; p.epoch = nullptr; p.done = nullptr;
+  p.tile_info = nullptr; p.num_tiles = nullptr; p.w_rows_per_expert = 0;
   for (int i = 0; i < 8; ++i) p.peers[i] = nullptr;
   if (a->world > 1) {
     if (a->world > 8 || a->rank < 0 || a->rank >= a->world || dual || a->ldo != a->N) return -12;
     const long long staging_off = 262144;
-    const long long slot = (a->symm_bytes - staging_off) / (2LL * a->world * 8);
+    const long long slot = (a->symm_bytes / 2 - staging_off) / (2LL * a->world * 8);  // the upper half belongs to the collectives
     if (slot < static_cast<long long>(a->M) * a->ldo) return -13;
     for (int i = 0; i < a->world; ++i) {
       if (!a->peers[i]) return -12;
@@ -441,4 +455,42 @@ int launch_gemm_smallm(const ortb200_gemm_args* a, int bn, cudaStream_t stream, 
   }
 }
 
+int launch_gemm_grouped(const ortb200_gemm_grouped_args* a, cudaStream_t stream) {
+  const bool dual = a->act == ORTB200_ACT_SWIGLU;
+  const int bn = a->tile_rows;
+  if (bn != 16 && bn != 32 && bn != 64) return -8;
+  const int num_kb = (a->K + kBK - 1) / kBK;
+  const int tiles_n = (a->N + kBM - 1) / kBM;
+  CUtensorMap tw, tx;
+  const CUtensorMapDataType dt = a->dtype == ORTB200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  const int64_t w_rows = static_cast<int64_t>(a->num_experts) * a->w_rows_per_expert;
+  if (make_tensor_map_2d(&tw, a->w, dt, 2, a->K, w_rows, static_cast<int64_t>(a->K) * 2, kBK, kBM) != 0) return -6;
+  if (make_tensor_map_2d(&tx, a->x, dt, 2, a->K, a->rows, static_cast<int64_t>(a->K) * 2, kBK, bn) != 0) return -6;
+  SmallGemmParams p;
+  p.M = a->rows; p.N = a->N; p.K = a->K; p.num_kb = num_kb; p.cluster = 1; p.dual_offset = a->dual_offset;
+  p.dtype = a->dtype; p.act = a->act; p.alpha = 1.0f; p.out = a->out; p.ldo = a->N; p.bias = a->bias;
+  p.residual = nullptr; p.ldr = 0; p.status = a->status;
+  p.world = 1; p.rank = 0; p.staging_offset = 0; p.slot_elems = 0; p.epoch = nullptr; p.done = nullptr;
+  for (int i = 0; i < 8; ++i) p.peers[i] = nullptr;
+  p.tile_info = static_cast<const int4*>(a->tile_info);
+  p.num_tiles = a->num_tiles;
+  p.w_rows_per_expert = a->w_rows_per_expert;
+  dim3 grid(tiles_n, a->max_tiles, 1);
+  const bool pdl = a->use_pdl != 0;
+  switch (bn) {
+    case 16: return dual ? launch_small<16, 3, true>(tw, tx, p, grid, stream, pdl) : launch_small<16, 5, false>(tw, tx, p, grid, stream, pdl);
+    case 32: return dual ? launch_small<32, 2, true>(tw, tx, p, grid, stream, pdl) : launch_small<32, 4, false>(tw, tx, p, grid, stream, pdl);
+    default: return dual ? launch_small<64, 2, true>(tw, tx, p, grid, stream, pdl) : launch_small<64, 3, false>(tw, tx, p, grid, stream, pdl);
+  }
+}
+
 }  // namespace ortb200
+
+extern "C" int ortb200_gemm_grouped(const ortb200_gemm_grouped_args* a, ortb200_stream_t stream) {
+  if (!a || !a->x || !a->w || !a->out || !a->tile_info || !a->num_tiles) return -1;
+  if (a->rows <= 0 || a->N <= 0 || a->K <= 0 || a->K % 8 != 0 || a->num_experts <= 0 || a->max_tiles <= 0 || a->max_tiles > 65535) return -1;
+  if (a->dtype != ORTB200_BF16 && a->dtype != ORTB200_F16) return -4;
+  if (a->act == ORTB200_ACT_SWIGLU && a->dual_offset <= 0) return -2;
+  if ((reinterpret_cast<uintptr_t>(a->x) | reinterpret_cast<uintptr_t>(a->w) | reinterpret_cast<uintptr_t>(a->tile_info)) & 15) return -3;
+  return ortb200::launch_gemm_grouped(a, static_cast<cudaStream_t>(stream));
+}

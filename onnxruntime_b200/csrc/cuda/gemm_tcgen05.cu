@@ -46,6 +46,8 @@ struct GemmKernelParams {
   int max_contrib;    // workspace slots per tile in stream-K mode
   int dual_offset;
   int dtype;
+  int in_fp8;         // 1: x and w are e4m3 bytes (a stage then holds 128 K-elements instead of 64)
+  int k_per_block;    // K elements per pipeline stage: 64 (16-bit operands) or 128 (fp8)
   int act;
   float alpha;
   void* out;
@@ -167,15 +169,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
         coords(range.begin + i, &kb, &n0, &m0);
         uint8_t* st = smem + i * S::kStageBytes;
         mbar_expect_tx(&full_bar[i], S::kStageBytes);
-        tma_load_2d_hint(st, &tmap_w, &full_bar[i], kb * kBK, n0, pol_w);
-        if (DUAL) tma_load_2d_hint(st + S::kABytes, &tmap_w, &full_bar[i], kb * kBK, n0 + p.dual_offset, pol_w);
+        tma_load_2d_hint(st, &tmap_w, &full_bar[i], kb * p.k_per_block, n0, pol_w);
+        if (DUAL) tma_load_2d_hint(st + S::kABytes, &tmap_w, &full_bar[i], kb * p.k_per_block, n0 + p.dual_offset, pol_w);
       }
       pdl_wait_prior_grids();
       for (int i = 0; i < pre; ++i) {
         int kb, n0, m0;
         coords(range.begin + i, &kb, &n0, &m0);
         uint8_t* st = smem + i * S::kStageBytes;
-        tma_load_2d(st + S::kABytes * (DUAL ? 2 : 1), &tmap_x, &full_bar[i], kb * kBK, m0);
+        tma_load_2d(st + S::kABytes * (DUAL ? 2 : 1), &tmap_x, &full_bar[i], kb * p.k_per_block, m0);
       }
       for (long long i = pre; i < total; ++i) {
         const int s = static_cast<int>(i % STAGES);
@@ -188,14 +190,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
         coords(range.begin + i, &kb, &n0, &m0);
         uint8_t* st = smem + s * S::kStageBytes;
         mbar_expect_tx(&full_bar[s], S::kStageBytes);
-        tma_load_2d_hint(st, &tmap_w, &full_bar[s], kb * kBK, n0, pol_w);
-        if (DUAL) tma_load_2d_hint(st + S::kABytes, &tmap_w, &full_bar[s], kb * kBK, n0 + p.dual_offset, pol_w);
-        tma_load_2d(st + S::kABytes * (DUAL ? 2 : 1), &tmap_x, &full_bar[s], kb * kBK, m0);
+        tma_load_2d_hint(st, &tmap_w, &full_bar[s], kb * p.k_per_block, n0, pol_w);
+        if (DUAL) tma_load_2d_hint(st + S::kABytes, &tmap_w, &full_bar[s], kb * p.k_per_block, n0 + p.dual_offset, pol_w);
+        tma_load_2d(st + S::kABytes * (DUAL ? 2 : 1), &tmap_x, &full_bar[s], kb * p.k_per_block, m0);
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      const uint32_t idesc = umma_idesc_f16(p.dtype == ORTB200_BF16, kBM, BN);
+      const uint32_t idesc = p.in_fp8 ? umma_idesc_e4m3(kBM, BN) : umma_idesc_f16(p.dtype == ORTB200_BF16, kBM, BN);
       long long it = 0;
       int seg = 0;
       bool ok = true;
@@ -224,13 +226,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
 #pragma unroll
           for (int k = 0; k < kBK / 16; ++k) {
             // 16 K-elements = 32 bytes: the start-address field advances by 2
-            umma_f16(tmem_d, adesc + 2 * k, bdesc + 2 * k, idesc, (!first || k > 0) ? 1u : 0u);
+            // one instruction covers 32 bytes of K in either format: 16 half-precision or 32 fp8 elements
+            if (p.in_fp8) umma_f8(tmem_d, adesc + 2 * k, bdesc + 2 * k, idesc, (!first || k > 0) ? 1u : 0u);
+            else umma_f16(tmem_d, adesc + 2 * k, bdesc + 2 * k, idesc, (!first || k > 0) ? 1u : 0u);
           }
           if (DUAL) {
             const uint64_t a2desc = umma_desc_sw128(a_addr + S::kABytes);
 #pragma unroll
             for (int k = 0; k < kBK / 16; ++k) {
-              umma_f16(tmem_d + BN, a2desc + 2 * k, bdesc + 2 * k, idesc, (!first || k > 0) ? 1u : 0u);
+              if (p.in_fp8) umma_f8(tmem_d + BN, a2desc + 2 * k, bdesc + 2 * k, idesc, (!first || k > 0) ? 1u : 0u);
+              else umma_f16(tmem_d + BN, a2desc + 2 * k, bdesc + 2 * k, idesc, (!first || k > 0) ? 1u : 0u);
             }
           }
           first = false;
@@ -492,7 +497,9 @@ extern "C" int ortb200_gemm(const ortb200_gemm_args* a, ortb200_stream_t stream_
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   if (!a || !a->x || !a->w || !a->out) return -1;
   if (a->M <= 0 || a->N <= 0 || a->K <= 0) return -1;
-  if (a->K % 8 != 0) return -2;                                  // TMA row pitch must be a multiple of 16 bytes
+  const bool fp8 = a->in_dtype == ORTB200_F8E4M3;
+  if (a->in_dtype != 0 && !fp8 && a->in_dtype != a->dtype) return -4;
+  if (a->K % (fp8 ? 16 : 8) != 0) return -2;                     // TMA row pitch must be a multiple of 16 bytes
   if ((reinterpret_cast<uintptr_t>(a->x) & 15) || (reinterpret_cast<uintptr_t>(a->w) & 15)) return -3;
   if (a->dtype != ORTB200_F16 && a->dtype != ORTB200_BF16) return -4;
   const bool dual = a->act == ORTB200_ACT_SWIGLU;
@@ -502,7 +509,7 @@ extern "C" int ortb200_gemm(const ortb200_gemm_args* a, ortb200_stream_t stream_
   {
     // decode-shaped problems: non-persistent kernel with the split-K reduction inside a cluster
     const int bn_small = a->force_bn ? a->force_bn : pick_bn(a->M);
-    if (bn_small <= 64) {
+    if (bn_small <= 64 && !fp8) {
       int cluster = 1, st = 0;
       const int rc_small = launch_gemm_smallm(a, bn_small, stream, &cluster, &st);
       g_last_config = {bn_small, cluster, st};
@@ -511,18 +518,28 @@ extern "C" int ortb200_gemm(const ortb200_gemm_args* a, ortb200_stream_t stream_
   }
   if (a->world > 1) return -12;  // the fused all-reduce exists for decode-shaped problems only
   GemmPlan pl;
-  const int prc = plan_gemm(a->M, a->N, a->K, dual, a->force_bn, a->force_splits, a->workspace ? a->workspace_bytes : 0, &pl);
+  // fp8 operands: the planner counts 64-element k-blocks, and a stage holds 128 fp8 elements
+  const int k_planned = fp8 ? (a->K + 1) / 2 : a->K;
+  const int force_bn = fp8 && (a->force_bn == 0 || a->force_bn < 128) ? (a->M > 128 ? 256 : 128) : a->force_bn;
+  const int prc = plan_gemm(a->M, a->N, k_planned, dual, force_bn, a->force_splits, a->workspace ? a->workspace_bytes : 0, &pl);
   if (prc != 0) return prc;
   const int bn = pl.bn, num_kb = pl.num_kb, tiles_m = pl.tiles_m, grid = pl.grid, max_contrib = pl.max_contrib;
   const int64_t tiles = pl.tiles;
   const bool tile_aligned = pl.tile_aligned;
 
   CUtensorMap tw, tx;
-  const CUtensorMapDataType dt = a->dtype == ORTB200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-  if (make_tensor_map_2d(&tw, a->w, dt, 2, a->K, a->w_rows, static_cast<int64_t>(a->K) * 2, kBK, kBM) != 0) return -6;
-  if (make_tensor_map_2d(&tx, a->x, dt, 2, a->K, a->M, static_cast<int64_t>(a->K) * 2, kBK, bn) != 0) return -6;
+  if (fp8) {
+    if (make_tensor_map_2d(&tw, a->w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a->K, a->w_rows, a->K, 2 * kBK, kBM) != 0) return -6;
+    if (make_tensor_map_2d(&tx, a->x, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a->K, a->M, a->K, 2 * kBK, bn) != 0) return -6;
+  } else {
+    const CUtensorMapDataType dt = a->dtype == ORTB200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    if (make_tensor_map_2d(&tw, a->w, dt, 2, a->K, a->w_rows, static_cast<int64_t>(a->K) * 2, kBK, kBM) != 0) return -6;
+    if (make_tensor_map_2d(&tx, a->x, dt, 2, a->K, a->M, static_cast<int64_t>(a->K) * 2, kBK, bn) != 0) return -6;
+  }
 
   GemmKernelParams p;
+  p.in_fp8 = fp8 ? 1 : 0;
+  p.k_per_block = fp8 ? 2 * kBK : kBK;
   p.M = a->M; p.N = a->N; p.K = a->K;
   p.num_kb = num_kb; p.tiles = static_cast<int>(tiles); p.tiles_m = tiles_m;
   p.tile_aligned = tile_aligned ? 1 : 0; p.max_contrib = max_contrib;

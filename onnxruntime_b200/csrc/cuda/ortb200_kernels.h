@@ -17,7 +17,7 @@ extern "C" {
 
 typedef void* ortb200_stream_t;  // cudaStream_t
 
-enum ortb200_dtype { ORTB200_F16 = 0, ORTB200_BF16 = 1, ORTB200_F32 = 2 };
+enum ortb200_dtype { ORTB200_F16 = 0, ORTB200_BF16 = 1, ORTB200_F32 = 2, ORTB200_F8E4M3 = 3 };
 
 enum ortb200_act {
   ORTB200_ACT_NONE = 0,
@@ -64,7 +64,8 @@ typedef struct {
   // Requires M <= 64, ldo == N, no dual (SwiGLU) epilogue.
   // peers[i] is rank i's workspace base as mapped into this process; the layout is
   //   [0, 256 KiB)    epoch word (offset 0), done counter (offset 4), rest reserved
-  //   [256 KiB, ...)  staging[2][world][slot] 64-bit words, slot = (bytes - 256 KiB) / (2 * world * 8) >= M * ldo
+  //   [256 KiB, bytes / 2)  staging[2][world][slot] 64-bit words, slot = (bytes / 2 - 256 KiB) / (2 * world * 8) >= M * ldo
+  //   [bytes / 2, bytes)    used by ortb200_symm_collective
   // Two staging halves alternate by epoch parity, so a rank that runs one launch ahead never overwrites words a
   // slower rank still has to read.  The workspace must be zero before the first launch, and all ranks must launch
   // the same sequence of fused GEMMs.
@@ -72,9 +73,35 @@ typedef struct {
   int rank;
   void* peers[8];
   int64_t symm_bytes;
+  // Operand type when it differs from `dtype`: ORTB200_F8E4M3 = x and w hold e4m3 bytes (K a multiple of 16) and
+  // the tensor cores run in their 8-bit mode; out / bias / residual keep `dtype`, `alpha` carries the product of
+  // the per-tensor scales.  0 = operands are of `dtype`.
+  int in_dtype;
 } ortb200_gemm_args;
 
 int ortb200_gemm(const ortb200_gemm_args* args, ortb200_stream_t stream);
+
+// Grouped GEMM (mixture of experts): rows of x are sorted by expert; a device-side tile list says which expert's
+// weights multiply which row range, so no count ever travels to the host:
+//   out[r, :] = act(x[r, :] @ w[e]^T + bias[e]) for first_row <= r < end_row of every tile {e, first_row, end_row, -}.
+// Tiles cover at most tile_rows rows each (tile_rows in {16, 32, 64}); the grid has max_tiles rows of CTAs and the
+// CTAs beyond *num_tiles leave at once.  w is [num_experts * w_rows_per_expert, K]; with act == SWIGLU the gate rows
+// of expert e start at e * w_rows_per_expert and the up rows dual_offset rows later (N = rows of each half).
+typedef struct {
+  const void* x;          // [rows, K]
+  const void* w;
+  void* out;              // [rows, N]
+  const void* bias;       // optional [num_experts, N]
+  const void* tile_info;  // int4 per tile (16-byte aligned)
+  const int* num_tiles;   // device scalar
+  int rows, N, K;
+  int num_experts, w_rows_per_expert, dual_offset;
+  int tile_rows, max_tiles;
+  int dtype, act;
+  int* status;
+  int use_pdl;
+} ortb200_gemm_grouped_args;
+int ortb200_gemm_grouped(const ortb200_gemm_grouped_args* args, ortb200_stream_t stream);
 int64_t ortb200_gemm_workspace_bytes(int M, int N, int K, int act);
 // Number of kernels one ortb200_gemm call launches (always 1).
 int ortb200_gemm_last_config(int* bn, int* splits, int* stages);
@@ -227,6 +254,62 @@ int ortb200_swiglu(const void* x, void* y, int64_t rows, int cols, int dtype, or
 int ortb200_rotary(const void* x, void* y, const int64_t* position_ids, int64_t position_offset, const void* cos_cache,
                    const void* sin_cache, int B, int S, int N, int H, int rot_dim, int interleaved, int bnsh, int dtype,
                    ortb200_stream_t stream);
+
+// ---------------------------------------------------------------------------
+// Mixture of experts.  ortb200_moe_route runs: softmax + top-k routing (one warp per token), the per-expert histogram,
+// the tile plan of the grouped GEMM, and the permutation of the tokens into expert order.  Only the experts
+// [expert_begin, expert_end) are served (expert parallelism: the others belong to other ranks and get row_of = -1).
+// Afterwards:  ortb200_gemm_grouped(xp -> h), ortb200_gemm_grouped(h -> y), ortb200_moe_combine(y -> out).
+typedef struct {
+  const void* logits;   // [tokens, E], dtype
+  const void* x;        // [tokens, H], 16-bit dtype (bf16 / fp16)
+  int tokens, E, k, H;
+  int normalize;        // divide the k chosen probabilities by their sum
+  int expert_begin, expert_end;
+  int tile_rows, max_tiles;   // from ortb200_moe_tile_rows / ortb200_moe_max_tiles
+  int dtype;            // of logits
+  int* topk_idx;        // out [tokens, k]
+  float* topk_w;        // out [tokens, k]
+  int* counts;          // scratch [E_local]
+  int* offsets;         // out [E_local + 1]
+  int* cursors;         // scratch [E_local]
+  void* tile_info;      // out int4 [max_tiles]
+  int* num_tiles;       // out scalar
+  void* xp;             // out [tokens * k, H] rows in expert order (rows of other ranks' experts stay unwritten)
+  int* row_of;          // out [tokens, k]: row of (token, choice) in xp, or -1
+} ortb200_moe_route_args;
+int ortb200_moe_route(const ortb200_moe_route_args* args, ortb200_stream_t stream);
+int ortb200_moe_tile_rows(int64_t rows, int experts);
+int ortb200_moe_max_tiles(int64_t rows, int experts, int tile_rows);
+// out[t] = sum_j topk_w[t, j] * (y[row_of[t, j]] + bias[topk_idx[t, j] - expert_begin]); rows with row_of < 0 are skipped.
+int ortb200_moe_combine(const void* y, const void* bias, void* out, int tokens, int H, int k, int expert_begin,
+                        const int* topk_idx, const float* topk_w, const int* row_of, int dtype, ortb200_stream_t stream);
+
+// ---------------------------------------------------------------------------
+// Collectives as one kernel over the symmetric workspace (same workspace and peer table as the fused GEMM; this
+// file's kernels use its upper half).  All ranks must issue the same sequence of calls.
+//   ALLREDUCE: out = sum over ranks of in; row_bytes = bytes of the whole tensor (rows ignored).
+//   ALLGATHER: in is [rows, row_bytes]; out is [rows, world, row_bytes] (gathering along any axis is this with
+//              rows = product of the leading dimensions).
+//   ALLTOALL:  in is [world, row_bytes]; out[s] = chunk `rank` of rank s's input.
+// Sizes are multiples of 16 bytes, pointers 16-byte aligned; ortb200_symm_collective_max_bytes gives the largest
+// message (per-rank input bytes) the workspace can take - larger ones go through the library collective.
+enum { ORTB200_COLL_ALLREDUCE = 0, ORTB200_COLL_ALLGATHER = 1, ORTB200_COLL_ALLTOALL = 2 };
+typedef struct {
+  int op;
+  const void* in;
+  void* out;
+  int64_t rows;
+  int64_t row_bytes;
+  int dtype;       // all-reduce only
+  int world, rank;
+  void* peers[8];
+  int64_t symm_bytes;
+  int* status;
+  int use_pdl;
+} ortb200_symm_collective_args;
+int ortb200_symm_collective(const ortb200_symm_collective_args* args, ortb200_stream_t stream);
+int64_t ortb200_symm_collective_max_bytes(int op, int world, int64_t symm_bytes);
 
 // MatMulNBits weights -> dense rows.  B uint8 [N, n_blocks, block_size * bits / 8] (low nibble = even k), scales
 // [N, n_blocks], zero_points packed uint8 [N, ceil(n_blocks * bits / 8)] (zp_is_packed = 1) or typed [N, n_blocks]

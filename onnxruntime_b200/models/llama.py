@@ -73,7 +73,7 @@ def rope_caches(cfg: LlamaConfig, device="cpu") -> Tuple[torch.Tensor, torch.Ten
 
 def build_llama(cfg: LlamaConfig, tp_rank: int = 0, tp_size: int = 1, external_weights: bool = False, seed: int = 0,
                 device: str = "cpu", with_argmax: bool = True, last_token_logits: bool = True,
-                weight_std: float = 0.02) -> Tuple[bytes, Dict[str, torch.Tensor]]:
+                weight_std: float = 0.02, shard_lm_head: bool = True) -> Tuple[bytes, Dict[str, torch.Tensor]]:
     """Returns (ModelProto bytes, weights).  With ``external_weights`` the dict holds every weight (on
     ``device``) to pass to ``SessionOptions.add_external_initializers``; otherwise it is empty and the
     weights are embedded in the model."""
@@ -193,8 +193,16 @@ def build_llama(cfg: LlamaConfig, tp_rank: int = 0, tp_size: int = 1, external_w
         inits.append(ol.make_tensor("last_index", np.array([-1], dtype=np.int64)))
         nodes.append(ol.make_node("Gather", ["final_norm", "last_index"], ["final_last"], name="last_token", axis=1))
         head_in = "final_last"
-    randn("lm_head.weight", (hidden, cfg.vocab_size))
-    nodes.append(ol.make_node("MatMul", [head_in, "lm_head.weight"], ["logits"], name="lm_head"))
+    if tp_size > 1 and shard_lm_head and cfg.vocab_size % tp_size == 0:
+        # vocabulary-parallel head: every rank computes its slice of the logits, an all-gather along the last axis
+        # puts them together (the full-vocabulary product would otherwise be repeated on every rank)
+        randn("lm_head.weight", (hidden, cfg.vocab_size // tp_size), shard=(1, tp_size))
+        nodes.append(ol.make_node("MatMul", [head_in, "lm_head.weight"], ["logits_shard"], name="lm_head"))
+        nodes.append(ol.make_node("AllGather", ["logits_shard"], ["logits"], name="lm_head_allgather", domain="com.microsoft",
+                                  axis=2, group_size=tp_size))
+    else:
+        randn("lm_head.weight", (hidden, cfg.vocab_size))
+        nodes.append(ol.make_node("MatMul", [head_in, "lm_head.weight"], ["logits"], name="lm_head"))
     outputs.insert(0, ol.make_tensor_value_info("logits", odt, ["batch", 1 if last_token_logits else "seq", cfg.vocab_size]))
     if with_argmax:
         nodes.append(ol.make_node("ArgMax", ["logits"], ["next_tokens"], name="greedy", axis=-1, keepdims=0))

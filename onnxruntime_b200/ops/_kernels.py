@@ -54,6 +54,7 @@ class GemmArgs(ctypes.Structure):
         ("workspace", ctypes.c_void_p), ("workspace_bytes", ctypes.c_int64), ("status", ctypes.c_void_p),
         ("force_splits", ctypes.c_int), ("force_bn", ctypes.c_int), ("use_pdl", ctypes.c_int),
         ("world", ctypes.c_int), ("rank", ctypes.c_int), ("peers", ctypes.c_void_p * 8), ("symm_bytes", ctypes.c_int64),
+        ("in_dtype", ctypes.c_int),
     ]
 
 
@@ -82,8 +83,10 @@ def gemm(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
          residual: Optional[torch.Tensor] = None, act: str = "none", alpha: float = 1.0,
          out: Optional[torch.Tensor] = None, n: Optional[int] = None, dual_offset: int = 0,
          force_splits: int = 0, force_bn: int = 0, status: Optional[torch.Tensor] = None,
-         use_pdl: bool = False, peers=None, rank: int = 0, symm_bytes: int = 0) -> torch.Tensor:
-    """out[M, N] = act(alpha * x[M, K] @ w[N, K].T + bias) + residual  (tcgen05 kernel)."""
+         use_pdl: bool = False, peers=None, rank: int = 0, symm_bytes: int = 0,
+         out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """out[M, N] = act(alpha * x[M, K] @ w[N, K].T + bias) + residual  (tcgen05 kernel).
+    x / w of dtype float8_e4m3fn use the 8-bit tensor-core mode; out_dtype (fp16 / bf16) is then required."""
     assert x.is_cuda and w.is_cuda and x.dtype == w.dtype and x.dim() == 2 and w.dim() == 2
     assert x.is_contiguous() and w.is_contiguous()
     M, K = x.shape
@@ -92,16 +95,18 @@ def gemm(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
         n = w_rows // 2 if act == "swiglu" else w_rows
         if act == "swiglu" and dual_offset == 0:
             dual_offset = n
+    fp8 = x.dtype == torch.float8_e4m3fn
+    odt = out_dtype if out_dtype is not None else (out.dtype if out is not None else x.dtype)
     if out is None:
-        out = torch.empty((M, n), dtype=x.dtype, device=x.device)
+        out = torch.empty((M, n), dtype=odt, device=x.device)
     nbytes = lib().ortb200_gemm_workspace_bytes(M, n, K, ACT[act])
     ws = workspace(x.device, nbytes)
     a = GemmArgs(_ptr(x), _ptr(w), _ptr(out), _ptr(bias), _ptr(residual), out.stride(0),
                  residual.stride(0) if residual is not None else 0, M, n, K, w_rows, dual_offset,
-                 dtype_code(x.dtype), ACT[act], alpha, _ptr(ws), ws.numel(), _ptr(status), force_splits, force_bn,
+                 dtype_code(odt), ACT[act], alpha, _ptr(ws), ws.numel(), _ptr(status), force_splits, force_bn,
                  1 if use_pdl else 0, len(peers) if peers else 1, rank,
                  (ctypes.c_void_p * 8)(*(list(peers) + [None] * (8 - len(peers)))) if peers else (ctypes.c_void_p * 8)(),
-                 symm_bytes)
+                 symm_bytes, 3 if fp8 else 0)
     rc = lib().ortb200_gemm(ctypes.byref(a), ctypes.c_void_p(stream_ptr()))
     if rc != 0:
         raise RuntimeError(f"ortb200_gemm rejected its arguments (code {rc})")
@@ -255,6 +260,33 @@ def nbits_dequant(B, scales, zero_points, N, K, bits=4, block_size=32):
                                        ctypes.c_void_p(_ptr(zero_points)), 1 if packed else 0, ctypes.c_void_p(_ptr(out)),
                                        ctypes.c_int64(N), K, bits, block_size, ctypes.c_int64(K), dtype_code(scales.dtype),
                                        ctypes.c_void_p(stream_ptr())), "ortb200_nbits_dequant")
+    return out
+
+
+class SymmCollectiveArgs(ctypes.Structure):
+    _fields_ = [("op", ctypes.c_int), ("inp", ctypes.c_void_p), ("out", ctypes.c_void_p), ("rows", ctypes.c_int64),
+                ("row_bytes", ctypes.c_int64), ("dtype", ctypes.c_int), ("world", ctypes.c_int), ("rank", ctypes.c_int),
+                ("peers", ctypes.c_void_p * 8), ("symm_bytes", ctypes.c_int64), ("status", ctypes.c_void_p), ("use_pdl", ctypes.c_int)]
+
+
+def symm_collective(op, x, peers, rank, symm_bytes, axis=0, status=None):
+    """op in {"allreduce", "allgather", "alltoall"} over the peer-mapped workspace (parallel.symm); all ranks call it."""
+    world = len(peers)
+    x = x.contiguous()
+    code = {"allreduce": 0, "allgather": 1, "alltoall": 2}[op]
+    rows, row_bytes = 1, x.numel() * x.element_size()
+    shape = list(x.shape)
+    if op == "allgather":
+        for d in range(axis):
+            rows *= x.shape[d]
+        row_bytes //= rows
+        shape[axis] *= world
+    elif op == "alltoall":
+        row_bytes //= world
+    out = torch.empty(shape, dtype=x.dtype, device=x.device)
+    a = SymmCollectiveArgs(code, _ptr(x), _ptr(out), rows, row_bytes, dtype_code(x.dtype) if op == "allreduce" else 0, world, rank,
+                           (ctypes.c_void_p * 8)(*(list(peers) + [None] * (8 - world))), symm_bytes, _ptr(status), 0)
+    _check(lib().ortb200_symm_collective(ctypes.byref(a), ctypes.c_void_p(stream_ptr())), "ortb200_symm_collective")
     return out
 
 

@@ -169,6 +169,40 @@ def case_gemm_allreduce(info, device, out):
     torch.save(res, os.path.join(out, f"rank{r}.pt"))
 
 
+def case_symm_collectives(info, device, out):
+    """The one-kernel collectives over peer-mapped memory against the process group's results."""
+    from onnxruntime_b200.ops import _kernels as K
+    from onnxruntime_b200.parallel import symm
+    r, w = info.rank, info.world_size
+    torch.cuda.set_device(info.local_rank)
+    ws = symm.create_workspace(32 << 20)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    res = {}
+    g = torch.Generator(device="cuda").manual_seed(1000 + r)
+    for rep in range(3):  # repeated calls walk through both parities of the staging areas
+        for dtype in (torch.bfloat16, torch.float32):
+            for n in (8, 4096, 100000, 262144):
+                x = torch.randn(n, device="cuda", generator=g).to(dtype)
+                y = K.symm_collective("allreduce", x, ws.peer_ptrs, r, ws.nbytes, status=status)
+                ref = x.float().clone()
+                dist.all_reduce(ref)
+                res[f"ar_{rep}_{dtype}_{n}"] = float((y.float() - ref).abs().max() / ref.abs().max())
+        for shape, axis in (((8, 16032), 1), ((4, 3, 64), 0), ((2, 5, 128), 2), ((1, 8), 0)):
+            x = torch.randn(*shape, device="cuda", generator=g).bfloat16()
+            y = K.symm_collective("allgather", x, ws.peer_ptrs, r, ws.nbytes, axis=axis, status=status)
+            parts = [torch.empty_like(x) for _ in range(w)]
+            dist.all_gather(parts, x)
+            res[f"ag_{rep}_{shape}"] = bool(torch.equal(y, torch.cat(parts, axis)))
+        x = torch.randn(w * 3, 40, device="cuda", generator=g).half()
+        y = K.symm_collective("alltoall", x, ws.peer_ptrs, r, ws.nbytes, status=status)
+        ref = torch.empty_like(x)
+        dist.all_to_all_single(ref, x)
+        res[f"a2a_{rep}"] = bool(torch.equal(y, ref))
+    torch.cuda.synchronize()
+    res["status"] = int(status.item())
+    torch.save(res, os.path.join(out, f"rank{r}.pt"))
+
+
 def main():
     case, device, out = sys.argv[1], sys.argv[2], sys.argv[3]
     info = init_distributed("gloo" if device == "cpu" else "nccl", timeout_s=120)

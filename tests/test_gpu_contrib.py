@@ -223,3 +223,67 @@ def test_session_paged_attention_decode():
     for i in range(3):
         c, g = rc[i].astype(np.float32), rg[i].astype(np.float32)
         assert np.abs(c - g).max() / np.abs(c).max() < 2e-2, i
+
+
+@pytest.mark.parametrize("T,E,k,act,fc3,bias", [(1, 8, 2, "silu", True, False), (16, 8, 2, "silu", True, False),
+                                                (300, 8, 2, "silu", True, False), (64, 64, 4, "relu", False, True),
+                                                (40, 16, 1, "gelu", False, False), (2048, 8, 2, "silu", True, False),
+                                                (33, 6, 3, "identity", False, True)])
+def test_session_moe(T, E, k, act, fc3, bias):
+    torch.manual_seed(0)
+    H, I = 256, 512
+    x = (torch.randn(T, H) * 0.5).half()
+    # distinct values per row, so that the choice of experts does not hinge on how ties are broken
+    logits = (torch.argsort(torch.rand(T, E), dim=1).float() * 0.37 - 1.0).half()
+    fc1 = (torch.randn(E, I, H) * 0.05).half()
+    fc2 = (torch.randn(E, H, I) * 0.05).half()
+    inputs = {"x": x.numpy(), "router": logits.numpy(), "fc1": fc1.numpy(), "b1": (torch.randn(E, I) * 0.1).half().numpy() if bias else None,
+              "fc2": fc2.numpy(), "b2": (torch.randn(E, H) * 0.1).half().numpy() if bias else None}
+    inits = ["fc1", "fc2", "b1", "b2"]
+    if fc3:
+        inputs["fc3"] = (torch.randn(E, I, H) * 0.05).half().numpy()
+        inits.append("fc3")
+    rc, rg = _both("MoE", inputs, initializers=inits, k=k, activation_type=act, normalize_routing_weights=1)
+    c, g = rc[0].astype(np.float32), rg[0].astype(np.float32)
+    assert np.isfinite(g).all()
+    assert np.abs(c - g).max() / np.abs(c).max() < 2e-2
+
+
+@pytest.mark.parametrize("M,N,Kd", [(8, 256, 512), (200, 1024, 1024), (1024, 2048, 4096), (130, 384, 144)])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float16])
+def test_gemm_fp8_operands(K, M, N, Kd, out_dtype):
+    torch.manual_seed(0)
+    x = (torch.randn(M, Kd, device="cuda") * 0.5).to(torch.float8_e4m3fn)
+    w = (torch.randn(N, Kd, device="cuda") * 0.5).to(torch.float8_e4m3fn)
+    b = torch.randn(N, device="cuda").to(out_dtype)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    y = K.gemm(x, w, bias=b, alpha=0.125, out_dtype=out_dtype, status=status)
+    assert status.item() == 0
+    ref = 0.125 * (x.float() @ w.float().T) + b.float()
+    assert _rel(y, ref) < 1e-2
+
+
+def test_session_gemm_float8():
+    import onnxruntime_b200 as ort
+    from onnxruntime_b200 import onnx_lite as ol
+    T = ol.TensorProto
+    torch.manual_seed(0)
+    M, Kd, N = 64, 512, 384
+    a16 = (torch.randn(M, Kd) * 0.5).half()
+    w8 = (torch.randn(N, Kd) * 0.5).to(torch.float8_e4m3fn)
+    nodes = [ol.make_node("Cast", ["a"], ["a8"], to=T.FLOAT8E4M3FN, saturate=1),
+             ol.make_node("GemmFloat8", ["a8", "w", "", "sa", "sb"], ["y"], domain="com.microsoft", transB=1, dtype=T.FLOAT16, alpha=2.0)]
+    g = ol.make_graph(nodes, "g", [ol.make_tensor_value_info("a", T.FLOAT16, [M, Kd])], [ol.make_tensor_value_info("y", T.FLOAT16, None)],
+                      [ol.make_tensor("w", w8), ol.make_tensor("sa", np.array([0.5], np.float32)), ol.make_tensor("sb", np.array([0.25], np.float32))])
+    model = ol.make_model(g).serialize()
+    so = ort.SessionOptions()
+    so.graph_optimization_level = ort.GraphOptimizationLevel.ORT_DISABLE_ALL
+    cpu = ort.InferenceSession(model, so, providers=["CPUExecutionProvider"])
+    gpu = ort.InferenceSession(model, so, providers=["CUDAExecutionProvider"], enable_fallback=False)
+    before = gpu.kernel_launch_count()
+    c = cpu.run(None, {"a": a16.numpy()})[0].astype(np.float32)
+    gq = gpu.run(None, {"a": a16.numpy()})[0].astype(np.float32)
+    assert gpu.kernel_launch_count() > before
+    ref = 2.0 * 0.5 * 0.25 * (a16.to(torch.float8_e4m3fn).float() @ w8.float().T)
+    assert np.abs(gq - ref.numpy()).max() / np.abs(ref.numpy()).max() < 1e-2
+    assert np.abs(c - ref.numpy()).max() / np.abs(ref.numpy()).max() < 1e-2

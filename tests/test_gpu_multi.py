@@ -33,3 +33,15 @@ def test_llama_tp2_gpu(tmp_path, fused):
     a, b, ref = out[0]["logits"], out[1]["logits"], out[0]["ref"]
     assert (a - b).abs().max() / a.abs().max() < 1e-6
     assert (a - ref).abs().max() / ref.abs().max() < 0.06
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+def test_symmetric_memory_collectives(tmp_path):
+    out = launch("symm_collectives", "cuda", 2, tmp_path)
+    for r in range(2):
+        assert out[r]["status"] == 0
+        for k, v in out[r].items():
+            if k.startswith("ar_"):
+                assert v < 1e-2, (r, k, v)
+            elif k.startswith("ag_") or k.startswith("a2a_"):
+                assert v is True, (r, k)
