@@ -365,3 +365,235 @@ def parse_message(buf: bytes) -> List[Tuple[int, int, Any]]:
         else:
             raise ValueError(f"unsupported wire type {wire}")
     return out
+
+
+# ------------------------------------------------------------------ model reader (tools edit models through it)
+def _signed(v: int) -> int:
+    return v - (1 << 64) if v >= (1 << 63) else v
+
+
+def _unpack_varints(buf: bytes) -> List[int]:
+    out, i, n = [], 0, len(buf)
+    while i < n:
+        v = shift = 0
+        while True:
+            b = buf[i]
+            i += 1
+            v |= (b & 0x7F) << shift
+            shift += 7
+            if not b & 0x80:
+                break
+        out.append(_signed(v))
+    return out
+
+
+_TYPED_FIELD_DTYPES = {
+    # storage of the non-raw TensorProto fields: field number -> numpy dtype of the stored values
+    4: np.float32, 7: np.int64, 10: np.float64, 11: np.uint64,
+}
+
+
+def _tensor_from_fields(fields) -> Tensor:
+    name, dt, dims, raw, ext = "", 0, [], None, None
+    typed: Dict[int, List] = {}
+    for f, w, v in fields:
+        if f == 1:
+            dims += _unpack_varints(v) if w == 2 else [_signed(v)]
+        elif f == 2:
+            dt = v
+        elif f == 8:
+            name = bytes(v).decode()
+        elif f == 9:
+            raw = bytes(v)
+        elif f == 13:
+            kv = {ff: bytes(vv).decode() for ff, _, vv in parse_message(v)}
+            ext = ext or {}
+            ext[kv.get(1, "")] = kv.get(2, "")
+        elif f in (4, 10):  # float_data / double_data: packed fixed-width or single values
+            typed.setdefault(f, []).append(bytes(v))
+        elif f in (5, 7, 11):  # int32_data / int64_data / uint64_data: packed varints or single values
+            typed.setdefault(f, []).extend(_unpack_varints(v) if w == 2 else [_signed(v)])
+    if raw is None and ext is None:
+        if 4 in typed:
+            raw = b"".join(typed[4])
+        elif 10 in typed:
+            raw = b"".join(typed[10])
+        elif 7 in typed:
+            raw = np.asarray(typed[7], dtype=np.int64).tobytes()
+        elif 11 in typed:
+            raw = np.asarray(typed[11], dtype=np.uint64).tobytes()
+        elif 5 in typed:
+            vals = np.asarray(typed[5], dtype=np.int64)
+            if dt in (TensorProto.FLOAT16, TensorProto.BFLOAT16, TensorProto.UINT16):
+                raw = vals.astype(np.uint16).tobytes()
+            elif dt == TensorProto.INT16:
+                raw = vals.astype(np.int16).tobytes()
+            elif dt in (TensorProto.INT8,):
+                raw = vals.astype(np.int8).tobytes()
+            elif dt in (TensorProto.UINT8, TensorProto.BOOL, TensorProto.FLOAT8E4M3FN, TensorProto.FLOAT8E4M3FNUZ,
+                        TensorProto.FLOAT8E5M2, TensorProto.FLOAT8E5M2FNUZ, TensorProto.UINT4, TensorProto.INT4):
+                raw = vals.astype(np.uint8).tobytes()
+            else:
+                raw = vals.astype(np.int32).tobytes()
+        else:
+            raw = b""
+    return Tensor(name, dt, tuple(dims), raw or b"", ext)
+
+
+def _value_info_from_bytes(buf: bytes) -> ValueInfo:
+    name, elem, shape = "", 0, None
+    for f, _, v in parse_message(buf):
+        if f == 1:
+            name = bytes(v).decode()
+        elif f == 2:
+            for f2, _, v2 in parse_message(v):
+                if f2 != 1:
+                    continue  # only tensor types carry a shape here
+                for f3, _, v3 in parse_message(v2):
+                    if f3 == 1:
+                        elem = v3
+                    elif f3 == 2:
+                        shape = []
+                        for f4, _, v4 in parse_message(v3):
+                            if f4 != 1:
+                                continue
+                            d: Union[int, str, None] = None
+                            for f5, _, v5 in parse_message(v4):
+                                if f5 == 1:
+                                    d = _signed(v5)
+                                elif f5 == 2:
+                                    d = bytes(v5).decode()
+                            shape.append(d)
+    return ValueInfo(name, elem, shape)
+
+
+def _attribute_from_bytes(buf: bytes) -> Attribute:
+    name, atype = "", 0
+    f_val = i_val = s_val = t_val = g_val = None
+    floats: List[float] = []
+    ints: List[int] = []
+    strings: List[bytes] = []
+    for f, w, v in parse_message(buf):
+        if f == 1:
+            name = bytes(v).decode()
+        elif f == 2:
+            f_val = struct.unpack("<f", v)[0]
+        elif f == 3:
+            i_val = _signed(v)
+        elif f == 4:
+            s_val = bytes(v)
+        elif f == 5:
+            t_val = _tensor_from_fields(parse_message(v))
+        elif f == 6:
+            g_val = _graph_from_bytes(v)
+        elif f == 7:
+            floats += list(struct.unpack(f"<{len(v) // 4}f", v)) if w == 2 else [struct.unpack("<f", v)[0]]
+        elif f == 8:
+            ints += _unpack_varints(v) if w == 2 else [_signed(v)]
+        elif f == 9:
+            strings.append(bytes(v))
+        elif f == 20:
+            atype = v
+    if not atype:  # writers before IR 4 did not set the type
+        atype = (ATTR_FLOAT if f_val is not None else ATTR_INT if i_val is not None else ATTR_STRING if s_val is not None else
+                 ATTR_TENSOR if t_val is not None else ATTR_GRAPH if g_val is not None else ATTR_FLOATS if floats else
+                 ATTR_INTS if ints else ATTR_STRINGS)
+    value = {ATTR_FLOAT: f_val if f_val is not None else 0.0, ATTR_INT: i_val if i_val is not None else 0,
+             ATTR_STRING: s_val if s_val is not None else b"", ATTR_TENSOR: t_val, ATTR_GRAPH: g_val, ATTR_FLOATS: floats,
+             ATTR_INTS: ints, ATTR_STRINGS: strings}.get(atype)
+    return Attribute(name, atype, value)
+
+
+def _node_from_bytes(buf: bytes) -> Node:
+    n = Node("", [], [])
+    for f, _, v in parse_message(buf):
+        if f == 1:
+            n.inputs.append(bytes(v).decode())
+        elif f == 2:
+            n.outputs.append(bytes(v).decode())
+        elif f == 3:
+            n.name = bytes(v).decode()
+        elif f == 4:
+            n.op_type = bytes(v).decode()
+        elif f == 5:
+            n.attributes.append(_attribute_from_bytes(v))
+        elif f == 7:
+            n.domain = bytes(v).decode()
+    return n
+
+
+def _graph_from_bytes(buf: bytes) -> Graph:
+    g = Graph([], "", [], [])
+    for f, _, v in parse_message(buf):
+        if f == 1:
+            g.nodes.append(_node_from_bytes(v))
+        elif f == 2:
+            g.name = bytes(v).decode()
+        elif f == 5:
+            g.initializers.append(_tensor_from_fields(parse_message(v)))
+        elif f == 11:
+            g.inputs.append(_value_info_from_bytes(v))
+        elif f == 12:
+            g.outputs.append(_value_info_from_bytes(v))
+        elif f == 13:
+            g.value_info.append(_value_info_from_bytes(v))
+    return g
+
+
+def load_model(source: Union[str, bytes, bytearray, memoryview]) -> Model:
+    """ModelProto bytes (or a file path) -> editable ``Model``.  Functions, training info and sparse
+    initializers are not carried over; tools that need them should work on the bytes."""
+    if isinstance(source, str):
+        with open(source, "rb") as f:
+            source = f.read()
+    m = Model(Graph([], "", [], []), {})
+    for f, _, v in parse_message(bytes(source)):
+        if f == 1:
+            m.ir_version = v
+        elif f == 2:
+            m.producer_name = bytes(v).decode()
+        elif f == 6:
+            m.doc_string = bytes(v).decode()
+        elif f == 7:
+            m.graph = _graph_from_bytes(v)
+        elif f == 8:
+            domain, version = "", 0
+            for f2, _, v2 in parse_message(v):
+                if f2 == 1:
+                    domain = bytes(v2).decode()
+                elif f2 == 2:
+                    version = v2
+            m.opset_imports[domain] = version
+        elif f == 14:
+            kv = {ff: bytes(vv).decode() for ff, _, vv in parse_message(v)}
+            m.metadata[kv.get(1, "")] = kv.get(2, "")
+    return m
+
+
+def load_tensor(source: Union[str, bytes]) -> Tensor:
+    """A serialized TensorProto (the ``input_0.pb`` files of ONNX test data sets) -> ``Tensor``."""
+    if isinstance(source, str):
+        with open(source, "rb") as f:
+            source = f.read()
+    return _tensor_from_fields(parse_message(bytes(source)))
+
+
+def to_array(t: Tensor):
+    """Initializer -> numpy array; bf16 and fp8 tensors come back as torch tensors (numpy has no such types)."""
+    if t.external is not None:
+        raise ValueError(f"tensor {t.name!r} keeps its data outside the model")
+    shape = tuple(int(d) for d in t.dims)
+    if t.data_type in _ONNX_TO_NP:
+        return np.frombuffer(t.raw, dtype=_ONNX_TO_NP[t.data_type]).reshape(shape).copy()
+    import torch
+    tmap = {TensorProto.BFLOAT16: torch.bfloat16, TensorProto.FLOAT8E4M3FN: torch.float8_e4m3fn, TensorProto.FLOAT8E5M2: torch.float8_e5m2}
+    if t.data_type in tmap:
+        return torch.frombuffer(bytearray(t.raw), dtype=torch.uint8).view(tmap[t.data_type]).reshape(shape)
+    raise TypeError(f"no array type for ONNX data type {t.data_type}")
+
+
+def attr_value(node: Node, name: str, default: Any = None) -> Any:
+    for a in node.attributes:
+        if a.name == name:
+            return a.value
+    return default

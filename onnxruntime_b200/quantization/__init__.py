@@ -1,0 +1,2 @@
+"""Weight-only quantization tools (the counterpart of onnxruntime/python/tools/quantization)."""
+from .matmul_nbits_quantizer import MatMulNBitsQuantizer, quantize_blockwise, dequantize_blockwise  # noqa: F401

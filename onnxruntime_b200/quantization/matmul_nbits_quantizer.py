@@ -1,0 +1,132 @@
+"""Round-to-nearest block quantisation of MatMul weights into ``com.microsoft.MatMulNBits``.
+
+Mirrors what ``MatMulNBitsQuantizer`` with the default RTN algorithm does in the reference
+(onnxruntime/python/tools/quantization/matmul_nbits_quantizer.py: ``DefaultWeightOnlyQuantizer.quantize_matmul``
+and the native block quantiser behind ``quantize_matmul_4bits``): every ``MatMul`` whose second input is a constant
+2-D ``[K, N]`` weight becomes ``MatMulNBits(A, B_packed, scales[, zero_points])`` with
+
+* ``B_packed`` uint8 ``[N, n_blocks, block_size * bits / 8]`` (low nibble = even k),
+* ``scales`` ``[N, n_blocks]`` in the weight's float type,
+* ``zero_points`` packed uint8 ``[N, ceil(n_blocks * bits / 8)]`` when asymmetric (symmetric uses the implicit 2^(bits-1)).
+"""
+from __future__ import annotations
+
+from typing import Iterable, Optional, Tuple, Union
+
+import numpy as np
+
+from .. import onnx_lite as ol
+
+
+def quantize_blockwise(w_kn: np.ndarray, block_size: int = 32, bits: int = 4, symmetric: bool = True
+                       ) -> Tuple[np.ndarray, np.ndarray, Optional[np.ndarray]]:
+    """``w_kn`` float ``[K, N]`` -> (packed uint8 [N, n_blocks, blob], scales float32 [N, n_blocks], zero_points or None)."""
+    assert bits in (4, 8) and block_size >= 16 and block_size & (block_size - 1) == 0
+    K, N = w_kn.shape
+    nb = (K + block_size - 1) // block_size
+    w = np.zeros((N, nb * block_size), dtype=np.float32)
+    w[:, :K] = np.asarray(w_kn, dtype=np.float32).T
+    w = w.reshape(N, nb, block_size)
+    qmax = (1 << bits) - 1
+    mid = 1 << (bits - 1)
+    if symmetric:
+        # the value of largest magnitude maps to -mid (as in the reference's symmetric block quantiser)
+        idx = np.abs(w).argmax(-1)
+        vmax = np.take_along_axis(w, idx[..., None], -1)[..., 0]
+        scales = vmax / -float(mid)
+        inv = np.where(scales != 0, 1.0 / np.where(scales != 0, scales, 1.0), 0.0)
+        q = np.clip(np.rint(w * inv[..., None]) + mid, 0, qmax).astype(np.uint8)
+        zp = None
+    else:
+        lo = np.minimum(w.min(-1), 0.0)
+        hi = np.maximum(w.max(-1), 0.0)
+        scales = (hi - lo) / float(qmax)
+        inv = np.where(scales != 0, 1.0 / np.where(scales != 0, scales, 1.0), 0.0)
+        zp_vals = np.clip(np.rint(-lo * inv), 0, qmax).astype(np.uint8)
+        q = np.clip(np.rint(w * inv[..., None]) + zp_vals[..., None], 0, qmax).astype(np.uint8)
+        if bits == 4:
+            z = np.zeros((N, (nb + 1) // 2 * 2), dtype=np.uint8)
+            z[:, :nb] = zp_vals
+            zp = (z[:, 0::2] | (z[:, 1::2] << 4)).astype(np.uint8)
+        else:
+            zp = zp_vals
+    packed = (q[..., 0::2] | (q[..., 1::2] << 4)).astype(np.uint8) if bits == 4 else q
+    return packed, scales.astype(np.float32), zp
+
+
+def dequantize_blockwise(packed: np.ndarray, scales: np.ndarray, zero_points: Optional[np.ndarray], K: int, bits: int = 4,
+                         block_size: int = 32) -> np.ndarray:
+    """Inverse of :func:`quantize_blockwise`: float32 ``[N, K]``."""
+    N, nb = scales.shape
+    if bits == 4:
+        q = np.stack([packed & 0xF, packed >> 4], -1).reshape(N, nb, block_size).astype(np.float32)
+    else:
+        q = packed.reshape(N, nb, block_size).astype(np.float32)
+    if zero_points is None:
+        zp = np.full((N, nb), float(1 << (bits - 1)), dtype=np.float32)
+    elif bits == 4 and zero_points.dtype == np.uint8:
+        zp = np.stack([zero_points & 0xF, zero_points >> 4], -1).reshape(N, -1)[:, :nb].astype(np.float32)
+    else:
+        zp = zero_points.reshape(N, nb).astype(np.float32)
+    return ((q - zp[..., None]) * scales.astype(np.float32)[..., None]).reshape(N, nb * block_size)[:, :K]
+
+
+class MatMulNBitsQuantizer:
+    """``MatMulNBitsQuantizer(model, block_size=32, is_symmetric=True, bits=4).process()`` then ``.model`` /
+    ``.save(path)``.  ``model`` is ModelProto bytes, a path, or an ``onnx_lite.Model``."""
+
+    def __init__(self, model: Union[str, bytes, ol.Model], block_size: int = 32, is_symmetric: bool = True, bits: int = 4,
+                 nodes_to_exclude: Iterable[str] = (), nodes_to_include: Optional[Iterable[str]] = None, min_elements: int = 0):
+        self.model = model if isinstance(model, ol.Model) else ol.load_model(model)
+        self.block_size, self.symmetric, self.bits = block_size, is_symmetric, bits
+        self.exclude = set(nodes_to_exclude)
+        self.include = None if nodes_to_include is None else set(nodes_to_include)
+        self.min_elements = min_elements
+        self.quantized_nodes = []
+
+    def process(self) -> ol.Model:
+        g = self.model.graph
+        inits = {t.name: t for t in g.initializers}
+        uses = {}
+        for n in g.nodes:
+            for i in n.inputs:
+                uses[i] = uses.get(i, 0) + 1
+        new_nodes = []
+        for n in g.nodes:
+            w = inits.get(n.inputs[1]) if n.op_type == "MatMul" and n.domain in ("", "ai.onnx") and len(n.inputs) == 2 else None
+            ok = (w is not None and w.external is None and len(w.dims) == 2 and n.name not in self.exclude and
+                  (self.include is None or n.name in self.include) and
+                  w.data_type in (ol.TensorProto.FLOAT, ol.TensorProto.FLOAT16, ol.TensorProto.BFLOAT16) and
+                  int(np.prod(w.dims)) >= self.min_elements)
+            if not ok:
+                new_nodes.append(n)
+                continue
+            arr = ol.to_array(w)
+            is_torch = not isinstance(arr, np.ndarray)
+            w32 = arr.float().numpy() if is_torch else arr.astype(np.float32)
+            K, N = w32.shape
+            packed, scales, zp = quantize_blockwise(w32, self.block_size, self.bits, self.symmetric)
+            base = n.inputs[1]
+            if is_torch:
+                import torch
+                scales_t = ol.make_tensor(base + "_scales", torch.from_numpy(scales).to(arr.dtype))
+            else:
+                scales_t = ol.make_tensor(base + "_scales", scales.astype(arr.dtype))
+            g.initializers.append(ol.make_tensor(base + "_Q" + str(self.bits), packed))
+            g.initializers.append(scales_t)
+            ins = [n.inputs[0], base + "_Q" + str(self.bits), base + "_scales"]
+            if zp is not None:
+                g.initializers.append(ol.make_tensor(base + "_zero_points", zp))
+                ins.append(base + "_zero_points")
+            new_nodes.append(ol.make_node("MatMulNBits", ins, list(n.outputs), name=(n.name + "_Q" + str(self.bits)) if n.name else "",
+                                          domain="com.microsoft", K=K, N=N, bits=self.bits, block_size=self.block_size))
+            self.quantized_nodes.append(n.name or n.outputs[0])
+            uses[base] -= 1
+        g.nodes = new_nodes
+        g.initializers = [t for t in g.initializers if uses.get(t.name, 1) > 0 or t.name not in inits]
+        self.model.opset_imports.setdefault("com.microsoft", 1)
+        return self.model
+
+    def save(self, path: str) -> None:
+        with open(path, "wb") as f:
+            f.write(self.model.serialize())

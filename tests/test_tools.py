@@ -1,0 +1,124 @@
+"""Offline tools: model loader, MatMulNBits quantizer, float16 converter, optimizer front end, perf_test and
+onnx_test_runner command lines."""
+import json
+import os
+
+import numpy as np
+import pytest
+
+import onnxruntime_b200 as ort
+from onnxruntime_b200 import _core as C
+from onnxruntime_b200 import onnx_lite as ol
+
+T = ol.TensorProto
+
+
+def _mlp_model(K=64, N=48, dtype=np.float32):
+    rng = np.random.RandomState(0)
+    w1 = rng.randn(K, N).astype(dtype) * 0.2
+    w2 = rng.randn(N, K).astype(dtype) * 0.2
+    b = rng.randn(N).astype(dtype) * 0.1
+    nodes = [ol.make_node("MatMul", ["x", "w1"], ["h0"], name="fc1"), ol.make_node("Add", ["h0", "b"], ["h1"], name="bias"),
+             ol.make_node("Relu", ["h1"], ["h2"], name="act"), ol.make_node("MatMul", ["h2", "w2"], ["y"], name="fc2")]
+    et = ol.np_dtype_to_onnx(dtype)
+    g = ol.make_graph(nodes, "mlp", [ol.make_tensor_value_info("x", et, ["batch", K])], [ol.make_tensor_value_info("y", et, ["batch", K])],
+                      [ol.make_tensor("w1", w1), ol.make_tensor("w2", w2), ol.make_tensor("b", b)])
+    return ol.make_model(g).serialize(), (w1, w2, b)
+
+
+def test_load_model_round_trip_keeps_every_field():
+    mb, _ = _mlp_model()
+    m = ol.load_model(mb)
+    assert [n.op_type for n in m.graph.nodes] == ["MatMul", "Add", "Relu", "MatMul"]
+    assert m.graph.inputs[0].shape == ["batch", 64] and m.opset_imports[""] == 17
+    assert C.model_nodes(m.serialize()) == C.model_nodes(mb)
+    # typed (non-raw) tensor fields are read too: float_data / int64_data as another writer would emit them
+    raw = ol._packed_varints(1, [3]) + ol._f_varint(2, T.INT64) + ol._f_str(8, "v") + ol._packed_varints(7, [5, -2, 9])
+    t = ol.load_tensor(raw)
+    np.testing.assert_array_equal(ol.to_array(t), np.array([5, -2, 9], dtype=np.int64))
+
+
+@pytest.mark.parametrize("symmetric", [True, False])
+@pytest.mark.parametrize("bits", [4, 8])
+def test_matmul_nbits_quantizer(symmetric, bits):
+    from onnxruntime_b200.quantization import MatMulNBitsQuantizer, dequantize_blockwise, quantize_blockwise
+    mb, (w1, w2, b) = _mlp_model()
+    q = MatMulNBitsQuantizer(mb, block_size=16, is_symmetric=symmetric, bits=bits, nodes_to_exclude=["fc2"])
+    qm = q.process().serialize()
+    ops = [n["op_type"] for n in C.model_nodes(qm)]
+    assert ops == ["MatMulNBits", "Add", "Relu", "MatMul"] and q.quantized_nodes == ["fc1"]
+    packed, scales, zp = quantize_blockwise(w1, 16, bits, symmetric)
+    wq = dequantize_blockwise(packed, scales, zp, 64, bits, 16).T
+    step = np.abs(w1).max() / (7 if bits == 4 else 127)
+    assert np.abs(wq - w1).max() <= step * 0.75
+    x = np.random.RandomState(1).randn(5, 64).astype(np.float32)
+    y = ort.InferenceSession(qm, providers=["CPUExecutionProvider"]).run(None, {"x": x})[0]
+    ref = np.maximum(x @ wq + b, 0) @ w2
+    np.testing.assert_allclose(y, ref, rtol=1e-4, atol=1e-4)
+
+
+def test_float16_conversion_keep_io_types_and_block_list():
+    from onnxruntime_b200.transformers import convert_float_to_float16
+    mb, (w1, w2, b) = _mlp_model()
+    x = np.random.RandomState(1).randn(3, 64).astype(np.float32)
+    ref = ort.InferenceSession(mb, providers=["CPUExecutionProvider"]).run(None, {"x": x})[0]
+    m16 = convert_float_to_float16(mb, keep_io_types=True).serialize()
+    s = ort.InferenceSession(m16, providers=["CPUExecutionProvider"])
+    assert s.get_inputs()[0].type == "tensor(float)" and s.get_outputs()[0].type == "tensor(float)"
+    assert all(t.data_type == T.FLOAT16 for t in ol.load_model(m16).graph.initializers)
+    np.testing.assert_allclose(s.run(None, {"x": x})[0], ref, rtol=2e-2, atol=2e-2)
+    m16b = convert_float_to_float16(mb, keep_io_types=False).serialize()
+    s2 = ort.InferenceSession(m16b, providers=["CPUExecutionProvider"])
+    assert s2.get_inputs()[0].type == "tensor(float16)"
+    np.testing.assert_allclose(s2.run(None, {"x": x.astype(np.float16)})[0].astype(np.float32), ref, rtol=3e-2, atol=3e-2)
+    # a blocked op keeps float32 and is wrapped in casts
+    m16c = convert_float_to_float16(mb, keep_io_types=True, op_block_list=["Relu"]).serialize()
+    ops = [n["op_type"] for n in C.model_nodes(m16c)]
+    assert ops.count("Cast") >= 2
+    np.testing.assert_allclose(ort.InferenceSession(m16c, providers=["CPUExecutionProvider"]).run(None, {"x": x})[0], ref, rtol=2e-2, atol=2e-2)
+
+
+def test_optimizer_front_end_fuses_bert(tmp_path):
+    from onnxruntime_b200.models.bert import BertConfig, build_bert
+    from onnxruntime_b200.transformers import optimize_model
+    from onnxruntime_b200.transformers import optimizer as opt_cli
+    mb = build_bert(BertConfig.tiny())
+    m = optimize_model(mb, model_type="bert")
+    stats = m.get_fused_operator_statistics()
+    assert stats.get("Attention", 0) > 0 and stats.get("SkipLayerNormalization", 0) > 0 and m.is_fully_optimized()
+    src, dst = tmp_path / "bert.onnx", tmp_path / "bert_opt.onnx"
+    src.write_bytes(mb)
+    assert opt_cli.main(["--input", str(src), "--output", str(dst)]) == 0
+    assert "Attention" in {n["op_type"] for n in C.model_nodes(dst.read_bytes())}
+    none = optimize_model(mb, opt_level=0)
+    assert none.get_fused_operator_statistics().get("Attention", 0) == 0
+
+
+def test_perf_test_cli(tmp_path, capsys):
+    from onnxruntime_b200.tools import perf_test
+    mb, _ = _mlp_model()
+    path = tmp_path / "m.onnx"
+    path.write_bytes(mb)
+    out = tmp_path / "res.json"
+    assert perf_test.main(["-e", "cpu", "-m", "times", "-r", "20", "-c", "2", "-f", "batch:4", "-I", str(path), str(out)]) == 0
+    res = json.loads(out.read_text())
+    assert res["runs"] == 20 and res["p50_ms"] <= res["p99_ms"] <= res["max_ms"] and res["inferences_per_s"] > 0
+    text = capsys.readouterr().out
+    assert "P50 Latency" in text and "P999 Latency" in text
+    assert perf_test.main(["-m", "duration", "-t", "0.2", "-I", str(path)]) == 0
+
+
+def test_onnx_test_runner(tmp_path):
+    from onnxruntime_b200.tools import onnx_test_runner
+    mb, (w1, w2, b) = _mlp_model()
+    case = tmp_path / "test_mlp"
+    ds = case / "test_data_set_0"
+    os.makedirs(ds)
+    (case / "model.onnx").write_bytes(mb)
+    x = np.random.RandomState(2).randn(2, 64).astype(np.float32)
+    y = np.maximum(x @ w1 + b, 0) @ w2
+    (ds / "input_0.pb").write_bytes(ol.make_tensor("x", x).serialize())
+    (ds / "output_0.pb").write_bytes(ol.make_tensor("y", y).serialize())
+    assert onnx_test_runner.main([str(tmp_path)]) == 0
+    (ds / "output_0.pb").write_bytes(ol.make_tensor("y", y + 1).serialize())
+    assert onnx_test_runner.main([str(tmp_path)]) == 1
