@@ -22,6 +22,7 @@ import torch
 from . import _core as C
 
 __all__ = [
+    "AdapterFormat", "LoraAdapter", "register_custom_op",
     "InferenceSession", "SessionOptions", "RunOptions", "IOBinding", "OrtValue", "OrtDevice", "NodeArg",
     "ModelMetadata", "GraphOptimizationLevel", "ExecutionMode", "ExecutionOrder", "get_available_providers",
     "get_all_providers", "get_device", "set_default_logger_severity", "set_default_logger_verbosity",
@@ -371,13 +372,20 @@ class SessionOptions:
     def register_custom_ops_library(self, path: str) -> None:
         if not os.path.exists(path):
             raise NoSuchFile(f"custom op library {path} not found")
-        raise NotImplemented("custom op shared libraries (OrtCustomOp C ABI) are not supported; "  # noqa: F901
-                             "register Python custom ops with onnxruntime_b200.custom_ops instead")
+        # the library exports ortb200_register_custom_ops (csrc/core/custom_op_api.h); its operators join the
+        # kernel registry of the process, as the reference's RegisterCustomOps entry point does per session
+        C.load_custom_op_library(os.fspath(path))
 
 
 class RunOptions:
     def __init__(self):
         self._c = C.RunOptions()
+        self._adapters: List["LoraAdapter"] = []
+
+    def add_active_adapter(self, adapter: "LoraAdapter") -> None:
+        """The adapter's parameters are fed as extra inputs of every run made with these options (they override the
+        model's same-named optional inputs / overridable initializers)."""
+        self._adapters.append(adapter)
 
     log_severity_level = property(lambda s: s._c.log_severity_level, lambda s, v: setattr(s._c, "log_severity_level", v))
     log_verbosity_level = property(lambda s: s._c.log_verbosity_level, lambda s, v: setattr(s._c, "log_verbosity_level", v))
@@ -394,6 +402,97 @@ class RunOptions:
         if v is None:
             raise RuntimeException(f"Run config entry '{key}' was not found.")
         return v
+
+
+# --------------------------------------------------------------- LoRA adapters
+_ADAPTER_MAGIC = b"ORTB200ADAPTER\0\0"
+
+
+class AdapterFormat:
+    """Adapter file: named parameters plus an adapter version and the version of the model they belong to
+    (the role of onnxruntime.AdapterFormat, onnxruntime/python/onnxruntime_inference_collection.py:67; the
+    reference stores the same content in a flatbuffer).  Layout: 16-byte magic, three little-endian int32
+    (format version, adapter version, model version), uint32 count, then per parameter a uint32 length and a
+    serialized ONNX TensorProto."""
+
+    def __init__(self):
+        self._adapter_version = 1
+        self._model_version = 1
+        self._parameters: Dict[str, Any] = {}
+
+    def set_adapter_version(self, v: int) -> None:
+        self._adapter_version = int(v)
+
+    def get_adapter_version(self) -> int:
+        return self._adapter_version
+
+    def set_model_version(self, v: int) -> None:
+        self._model_version = int(v)
+
+    def get_model_version(self) -> int:
+        return self._model_version
+
+    def set_parameters(self, params: Dict[str, Any]) -> None:
+        self._parameters = dict(params)
+
+    def get_parameters(self) -> Dict[str, "OrtValue"]:
+        return {k: v if isinstance(v, OrtValue) else OrtValue(_to_torch(v)) for k, v in self._parameters.items()}
+
+    def export_adapter(self, file_path: str) -> None:
+        import struct
+        from . import onnx_lite as ol
+        out = bytearray(_ADAPTER_MAGIC)
+        out += struct.pack("<iiiI", 1, self._adapter_version, self._model_version, len(self._parameters))
+        for name, v in self._parameters.items():
+            t = ol.make_tensor(name, _to_torch(v)).serialize()
+            out += struct.pack("<I", len(t)) + t
+        with open(file_path, "wb") as f:
+            f.write(bytes(out))
+
+    @staticmethod
+    def read_adapter(file_path: str) -> "AdapterFormat":
+        import struct
+        with open(file_path, "rb") as f:
+            buf = f.read()
+        if buf[:16] != _ADAPTER_MAGIC:
+            raise InvalidArgument(f"{file_path} is not an adapter file")
+        fmt, av, mv, n = struct.unpack_from("<iiiI", buf, 16)
+        if fmt != 1:
+            raise InvalidArgument(f"unsupported adapter format version {fmt}")
+        a = AdapterFormat()
+        a._adapter_version, a._model_version = av, mv
+        off = 32
+        for _ in range(n):
+            (ln,) = struct.unpack_from("<I", buf, off)
+            off += 4
+            from . import onnx_lite as ol
+            blob = bytes(buf[off:off + ln])
+            off += ln
+            a._parameters[ol.load_tensor(blob).name] = C.tensor_from_proto(blob)
+        return a
+
+
+class LoraAdapter:
+    """Adapter parameters kept ready for ``RunOptions.add_active_adapter`` (onnxruntime.LoraAdapter)."""
+
+    def __init__(self):
+        self._params: Dict[str, torch.Tensor] = {}
+
+    def Load(self, file_path: str, device: Optional[str] = None) -> None:  # noqa: N802 (reference spelling)
+        fmt = AdapterFormat.read_adapter(file_path)
+        self._params = {k: (_to_torch(v).to(device) if device else _to_torch(v)) for k, v in fmt._parameters.items()}
+
+    def parameters(self) -> Dict[str, torch.Tensor]:
+        return self._params
+
+
+def register_custom_op(domain: str, op_type: str, fn) -> None:
+    """Register a Python callable as the kernel of ``domain::op_type``.
+
+    ``fn(*inputs, **attributes)`` receives torch tensors (``None`` for omitted optional inputs; on the device the
+    node runs on) and the node's attributes, and returns one tensor or a tuple of tensors.  The registration is
+    process-wide and must happen before the sessions that use the operator are created."""
+    C.register_python_op(domain, op_type, fn)
 
 
 # --------------------------------------------------------------- provider args
@@ -540,15 +639,28 @@ class InferenceSession:
             run_options: Optional[RunOptions] = None) -> List[Any]:
         self._validate_input(list(input_feed.keys()))
         ro = run_options._c if run_options is not None else C.RunOptions()
+        input_feed = self._with_adapters(input_feed, run_options)
         names = list(input_feed.keys())
         feeds = [_to_torch(v) for v in input_feed.values()]
         outs = self._sess.run(ro, names, feeds, list(output_names or []))
         return [_to_numpy(o) for o in outs]
 
+    def _with_adapters(self, input_feed: Dict[str, Any], run_options: Optional[RunOptions]) -> Dict[str, Any]:
+        if run_options is None or not run_options._adapters:
+            return input_feed
+        accepted = {a.name for a in self.get_inputs()} | {a.name for a in self.get_overridable_initializers()}
+        merged = dict(input_feed)
+        for adapter in run_options._adapters:
+            for name, value in adapter.parameters().items():
+                if name in accepted and name not in input_feed:
+                    merged[name] = value
+        return merged
+
     def run_with_ort_values(self, output_names: Optional[Sequence[str]], input_dict_ort_values: Dict[str, OrtValue],
                             run_options: Optional[RunOptions] = None) -> List[OrtValue]:
         self._validate_input(list(input_dict_ort_values.keys()))
         ro = run_options._c if run_options is not None else C.RunOptions()
+        input_dict_ort_values = self._with_adapters(input_dict_ort_values, run_options)
         names = list(input_dict_ort_values.keys())
         feeds = [_to_torch(v) for v in input_dict_ort_values.values()]
         outs = self._sess.run(ro, names, feeds, list(output_names or []))

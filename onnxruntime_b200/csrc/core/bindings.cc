@@ -13,6 +13,11 @@
 namespace py = pybind11;
 using namespace ortb;
 
+namespace ortb {
+void RegisterPythonOp(const std::string& domain, const std::string& op, pybind11::function fn);
+void LoadCustomOpLibrary(const std::string& path);
+}  // namespace ortb
+
 namespace {
 
 struct PyOrtError {
@@ -271,6 +276,10 @@ PYBIND11_MODULE(_core, m) {
       });
 
   // ---- model / graph utilities (used by the Python tools and tests)
+  m.def("register_python_op", [](const std::string& domain, const std::string& op, py::function fn) {
+    Guard([&] { RegisterPythonOp(domain, op, std::move(fn)); return 0; });
+  });
+  m.def("load_custom_op_library", [](const std::string& path) { Guard([&] { LoadCustomOpLibrary(path); return 0; }); });
   m.def("model_roundtrip", [](py::bytes b) {
     std::string bytes = b;
     return Guard([&] {
