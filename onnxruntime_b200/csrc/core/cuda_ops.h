@@ -14,7 +14,7 @@ void CheckLaunch(int rc, const char* what);
 // x2d / w_nk of type Float8_e4m3fn run the tensor cores in 8-bit mode; out_type (fp16 / bf16) is then required.
 at::Tensor LaunchGemm(OpKernelContext& ctx, const at::Tensor& x2d, const at::Tensor& w_nk, int64_t n_out,
                       int64_t dual_offset, const at::Tensor& bias, const at::Tensor& residual2d, int act, float alpha,
-                      bool fused_allreduce = false, at::ScalarType out_type = at::ScalarType::Undefined);
+                      bool fused_allreduce = false, at::ScalarType out_type = at::ScalarType::Undefined, float rms_eps = 0.f);
 // True when the fused GEMM + all-reduce kernel can take an [M, N] row-parallel product in this session.
 bool CanFuseAllReduce(OpKernelContext& ctx, int64_t M, int64_t N);
 

@@ -733,9 +733,18 @@ void RegisterContribKernels(KernelRegistry& r) {
     ctx.SetOutput(0, y.permute({0, 2, 3, 1}).contiguous().to(x.scalar_type()));
   });
   // com.ortb200: ops the GPU lowering passes create; these ATen versions keep an optimized model loadable anywhere
-  r.RegisterFn("com.ortb200", "FusedGemm", 1, kMax, [](Ctx& ctx) {
+  // an RMS normalisation folded into the GEMM in front of it: rms_eps attribute + gamma input
+  auto normed_input = [](Ctx& ctx, int gamma_index) {
+    const at::Tensor& x = ctx.RequiredInput(0);
+    const float eps = ctx.node().attr_f("rms_eps", 0.f);
+    if (eps <= 0.f) return x;
+    at::Tensor xf = x.to(at::kFloat);
+    at::Tensor y = xf * at::rsqrt(xf.pow(2).mean(-1, true) + eps);
+    return (y.to(x.scalar_type()) * ctx.RequiredInput(gamma_index)).to(x.scalar_type());
+  };
+  r.RegisterFn("com.ortb200", "FusedGemm", 1, kMax, [normed_input](Ctx& ctx) {
     const Node& n = ctx.node();
-    at::Tensor y = at::matmul(ctx.RequiredInput(0), ctx.RequiredInput(1));
+    at::Tensor y = at::matmul(normed_input(ctx, 4), ctx.RequiredInput(1));
     if (ctx.HasInput(2)) y = y + ctx.Input(2);
     const std::string act = n.attr_s("activation", "none");
     if (act == "gelu") y = at::gelu(y);
@@ -748,8 +757,8 @@ void RegisterContribKernels(KernelRegistry& r) {
     if (ctx.HasInput(3)) y = y + ctx.Input(3);
     ctx.SetOutput(0, y);
   });
-  r.RegisterFn("com.ortb200", "GemmSwiGLU", 1, kMax, [](Ctx& ctx) {
-    const at::Tensor& x = ctx.RequiredInput(0);
+  r.RegisterFn("com.ortb200", "GemmSwiGLU", 1, kMax, [normed_input](Ctx& ctx) {
+    at::Tensor x = normed_input(ctx, 3);
     ctx.SetOutput(0, at::silu(at::matmul(x, ctx.RequiredInput(1))) * at::matmul(x, ctx.RequiredInput(2)));
   });
   r.RegisterFn(MS, "GatherBlockQuantized", 1, kMax, [](Ctx& ctx) {

@@ -53,7 +53,7 @@ void CheckLaunch(int rc, const char* what) {
 // out[M,N] = act(x[M,K] @ w_nk[N,K]^T + bias) + residual on the tcgen05 GEMM.
 at::Tensor LaunchGemm(Ctx& ctx, const at::Tensor& x2d, const at::Tensor& w_nk, int64_t n_out, int64_t dual_offset,
                       const at::Tensor& bias, const at::Tensor& residual2d, int act, float alpha, bool fused_allreduce,
-                      at::ScalarType out_type) {
+                      at::ScalarType out_type, float rms_eps) {
   InferenceSession* s = ctx.session();
   const int64_t M = x2d.size(0), K = x2d.size(1);
   const bool fp8 = x2d.scalar_type() == at::kFloat8_e4m3fn;
@@ -77,6 +77,7 @@ at::Tensor LaunchGemm(Ctx& ctx, const at::Tensor& x2d, const at::Tensor& w_nk, i
   a.dual_offset = static_cast<int>(dual_offset);
   a.dtype = DtypeCode(out_type);
   a.in_dtype = fp8 ? ORTB200_F8E4M3 : 0;
+  a.rms_eps = rms_eps;
   a.act = act;
   a.alpha = alpha;
   a.workspace = ws.data_ptr();
@@ -93,6 +94,39 @@ at::Tensor LaunchGemm(Ctx& ctx, const at::Tensor& x2d, const at::Tensor& w_nk, i
   CheckLaunch(ortb200_gemm(&a, ctx.cuda_stream()), "ortb200_gemm");
   s->AddLaunches(1);
   return out;
+}
+
+// x / rms(x) row-wise (no gamma): the explicit form of the normalisation that decode-shaped GEMMs do in their epilogue.
+at::Tensor RmsNormalizeRows(Ctx& ctx, const at::Tensor& x2d, const at::Tensor& unit_gamma, float eps) {
+  at::Tensor out = at::empty_like(x2d);
+  ortb200_norm_args a{};
+  a.x = x2d.data_ptr();
+  a.gamma = unit_gamma.data_ptr();
+  a.out = out.data_ptr();
+  a.rows = x2d.size(0);
+  a.hidden = static_cast<int>(x2d.size(1));
+  a.epsilon = eps;
+  a.simplified = 1;
+  a.dtype = DtypeCode(x2d.scalar_type());
+  const int rc = ortb200_norm(&a, ctx.cuda_stream());
+  if (rc != 0) {
+    // shapes the norm kernel does not take: plain tensor math
+    at::Tensor xf = x2d.to(at::kFloat);
+    return (xf * at::rsqrt(xf.pow(2).mean(-1, true) + eps)).to(x2d.scalar_type());
+  }
+  ctx.session()->AddLaunches(1);
+  return out;
+}
+
+// Runs a GEMM whose weights carry the gamma of a preceding RMS normalisation (rms_eps > 0).
+at::Tensor LaunchNormedGemm(Ctx& ctx, const at::Tensor& x2d, const at::Tensor& w_nk, int64_t n_out, int64_t dual_offset,
+                            const at::Tensor& bias, const at::Tensor& residual2d, int act, float alpha, float rms_eps,
+                            const at::Tensor& unit_gamma) {
+  if (rms_eps > 0.f && x2d.size(0) > 64) {
+    at::Tensor xn = RmsNormalizeRows(ctx, x2d, unit_gamma, rms_eps);
+    return LaunchGemm(ctx, xn, w_nk, n_out, dual_offset, bias, residual2d, act, alpha);
+  }
+  return LaunchGemm(ctx, x2d, w_nk, n_out, dual_offset, bias, residual2d, act, alpha, false, at::ScalarType::Undefined, rms_eps);
 }
 
 bool CanFuseAllReduce(OpKernelContext& ctx, int64_t M, int64_t N) {
@@ -135,9 +169,17 @@ class GemmKernel final : public OpKernel {
       residual_idx_ = 3;
       act_ = ActCode(n.attr_s("activation", "none"));
       all_reduce_ = n.attr_i("all_reduce", 0) != 0;
+      rms_eps_ = n.attr_f("rms_eps", 0.f);
     }
     w_nk_ = w_is_nk ? w->contiguous() : w->t().contiguous();  // pre-pack: [N, K], K contiguous
     N_ = w_nk_.size(0);
+    if (rms_eps_ > 0.f) {
+      // the RMS norm in front of this GEMM was folded in: its gamma scales the K axis of the weights
+      const at::Tensor* gamma = info.constant_input(4);
+      ORTB_ENFORCE(gamma != nullptr && gamma->numel() == w_nk_.size(1), "FusedGemm with rms_eps needs a constant gamma of length K");
+      w_nk_ = (w_nk_.to(at::kFloat) * gamma->to(at::kFloat).reshape({1, -1})).to(w_nk_.scalar_type()).contiguous();
+      unit_gamma_ = at::ones({w_nk_.size(1)}, w_nk_.options());
+    }
   }
   std::vector<int> PrepackedInputs() const override { return {1}; }
   void Compute(Ctx& ctx) const override {
@@ -158,12 +200,13 @@ class GemmKernel final : public OpKernel {
       ctx.SetOutput(0, y.reshape(OutShape(x, N_)));
       return;
     }
-    at::Tensor y = LaunchGemm(ctx, x2, w_nk_, N_, 0, bias, res, act_, alpha_);
+    at::Tensor y = LaunchNormedGemm(ctx, x2, w_nk_, N_, 0, bias, res, act_, alpha_, rms_eps_, unit_gamma_);
     ctx.SetOutput(0, y.reshape(OutShape(x, N_)));
   }
 
  private:
-  at::Tensor w_nk_;
+  at::Tensor w_nk_, unit_gamma_;
+  float rms_eps_ = 0.f;
   int64_t N_ = 0;
   int bias_idx_ = -1, residual_idx_ = -1;
   int act_ = ORTB200_ACT_NONE;
@@ -196,16 +239,36 @@ class GemmSwiGLUKernel final : public OpKernel {
     ORTB_ENFORCE(wg && wu, "GemmSwiGLU needs constant weights");
     I_ = wg->size(1);
     w_ = at::cat({wg->t(), wu->t()}, 0).contiguous();  // [2I, K]: gate rows then up rows
+    rms_eps_ = info.node.attr_f("rms_eps", 0.f);
+    if (rms_eps_ > 0.f) {
+      const at::Tensor* gamma = info.constant_input(3);
+      ORTB_ENFORCE(gamma != nullptr && gamma->numel() == w_.size(1), "GemmSwiGLU with rms_eps needs a constant gamma of length K");
+      w_ = (w_.to(at::kFloat) * gamma->to(at::kFloat).reshape({1, -1})).to(w_.scalar_type()).contiguous();
+      unit_gamma_ = at::ones({w_.size(1)}, w_.options());
+    }
   }
   std::vector<int> PrepackedInputs() const override { return {1, 2}; }
   void Compute(Ctx& ctx) const override {
     const at::Tensor& x = ctx.RequiredInput(0);
-    at::Tensor y = LaunchGemm(ctx, Flatten2D(x), w_, I_, I_, at::Tensor(), at::Tensor(), ORTB200_ACT_SWIGLU, 1.f);
+    at::Tensor x2 = Flatten2D(x);
+    if (x2.size(0) > 128 && I_ % 8 == 0) {
+      // Large M: the two-accumulator kernel is limited to 128-token tiles (tensor memory), which costs more than it
+      // saves; one plain GEMM over the stacked gate | up rows at 256-token tiles plus a streaming SwiGLU is faster.
+      at::Tensor gu = LaunchNormedGemm(ctx, x2, w_, 2 * I_, 0, at::Tensor(), at::Tensor(), ORTB200_ACT_NONE, 1.f, rms_eps_, unit_gamma_);
+      at::Tensor y = at::empty({x2.size(0), I_}, x2.options());
+      CheckLaunch(ortb200_swiglu(gu.data_ptr(), y.data_ptr(), x2.size(0), static_cast<int>(I_), DtypeCode(x2.scalar_type()), ctx.cuda_stream()),
+                  "ortb200_swiglu");
+      ctx.session()->AddLaunches(1);
+      ctx.SetOutput(0, y.reshape(OutShape(x, I_)));
+      return;
+    }
+    at::Tensor y = LaunchNormedGemm(ctx, x2, w_, I_, I_, at::Tensor(), at::Tensor(), ORTB200_ACT_SWIGLU, 1.f, rms_eps_, unit_gamma_);
     ctx.SetOutput(0, y.reshape(OutShape(x, I_)));
   }
 
  private:
-  at::Tensor w_;
+  at::Tensor w_, unit_gamma_;
+  float rms_eps_ = 0.f;
   int64_t I_ = 0;
 };
 

@@ -200,7 +200,7 @@ int AllReduceResidualFusion(PassContext& c) {
     if (!add || add->op_type != "Add" || !add->domain.empty()) continue;
     for (int s = 0; s < 2; ++s) {
       if (add->inputs[1 - s] == f->outputs[0] && !g.GetConstant(add->inputs[s]) && add->inputs[s] != f->outputs[0]) {
-        f->inputs.resize(4);
+        if (f->inputs.size() < 4) f->inputs.resize(4);
         f->inputs[3] = add->inputs[s];
         f->outputs[0] = add->outputs[0];
         g.RemoveNode(add);
@@ -213,6 +213,86 @@ int AllReduceResidualFusion(PassContext& c) {
   return count;
 }
 
+// RMS normalisation folded into the GEMMs around it:
+//   G1 = GEMM(a, W1);  (h, sum) = SkipSimplifiedLayerNormalization(G1, residual, gamma);  G2 = GEMM(h, W2)
+//     -> sum = FusedGemm(a, W1, residual);  G2 = GEMM(sum, W2 * gamma){rms_eps}
+//   h = SimplifiedLayerNormalization(x, gamma);  G2 = GEMM(h, W2)  ->  G2 = GEMM(x, W2 * gamma){rms_eps}
+// The residual add rides in the epilogue of the first GEMM; 1 / rms(x) is a per-token factor that commutes with
+// the second GEMM, whose kernel computes it while the weights stream.  Two launches per decoder layer disappear.
+int RmsNormGemmFusion(PassContext& c) {
+  Graph& g = c.g;
+  int count = 0;
+  for (Node* norm : g.Nodes()) {
+    const bool skip = norm->domain == kMSDomain && norm->op_type == "SkipSimplifiedLayerNormalization";
+    const bool plain = norm->domain.empty() && (norm->op_type == "SimplifiedLayerNormalization" || norm->op_type == "RMSNormalization");
+    if (!skip && !plain) continue;
+    if (plain && norm->attr_i("axis", -1) != -1) continue;
+    if (skip && norm->has_input(3)) continue;
+    const std::string gamma = norm->input(skip ? 2 : 1);
+    int64_t K = 0;
+    if (!IsConst1D(g, gamma, &K)) continue;
+    const at::ScalarType gt = g.GetConstant(gamma)->scalar_type();
+    if (gt != at::kHalf && gt != at::kBFloat16) continue;
+    bool extra_used = false;
+    for (size_t o = 1; o < norm->outputs.size(); ++o) {
+      if (skip && o == 3) continue;
+      if (norm->has_output(o) && (g.NumConsumers(norm->outputs[o]) > 0 || g.IsGraphOutput(norm->outputs[o]))) extra_used = true;
+    }
+    if (extra_used) continue;
+    const std::string ln_out = norm->outputs[0];
+    Node* cons = SoleConsumer(g, ln_out);
+    if (!cons || cons->inputs.empty() || cons->inputs[0] != ln_out) continue;
+    int kind = 0;  // 1 MatMul, 2 FusedGemm, 3 GemmSwiGLU
+    if (cons->domain.empty() && cons->op_type == "MatMul" && IsHalfWeight2D(g, cons->inputs[1]) &&
+        g.GetConstant(cons->inputs[1])->size(0) == K && g.GetConstant(cons->inputs[1])->scalar_type() == gt)
+      kind = 1;
+    else if (cons->domain == kFusedDomain && cons->op_type == "FusedGemm" && cons->attr_i("all_reduce", 0) == 0 &&
+             cons->attr_f("rms_eps", 0.f) == 0.f && g.GetConstant(cons->inputs[1]) && g.GetConstant(cons->inputs[1])->size(0) == K)
+      kind = 2;
+    else if (cons->domain == kFusedDomain && cons->op_type == "GemmSwiGLU" && cons->attr_f("rms_eps", 0.f) == 0.f &&
+             g.GetConstant(cons->inputs[1]) && g.GetConstant(cons->inputs[1])->size(0) == K)
+      kind = 3;
+    if (!kind) continue;
+    std::string x_new = norm->inputs[0];
+    if (skip) {
+      Node* prod = g.Producer(norm->inputs[0]);
+      if (!prod || g.NumConsumers(prod->outputs[0]) != 1 || g.IsGraphOutput(prod->outputs[0])) continue;
+      const bool p_mm = prod->domain.empty() && prod->op_type == "MatMul" && IsHalfWeight2D(g, prod->inputs[1]) && !g.GetConstant(prod->inputs[0]);
+      const bool p_fg = prod->domain == kFusedDomain && prod->op_type == "FusedGemm" && !prod->has_input(3);
+      if (!p_mm && !p_fg) continue;
+      const std::string sum = norm->has_output(3) ? norm->outputs[3] : g.UniqueName(ln_out + "_sum");
+      if (p_mm) {
+        Node* f = g.AddNode("FusedGemm", {prod->inputs[0], prod->inputs[1], "", norm->inputs[1]}, {sum}, kFusedDomain,
+                            g.UniqueName("FusedGemm"));
+        f->set_attr_s("activation", "none");
+        g.RemoveNode(prod);
+      } else {
+        if (prod->inputs.size() < 4) prod->inputs.resize(4);
+        prod->inputs[3] = norm->inputs[1];
+        prod->outputs[0] = sum;
+      }
+      x_new = sum;
+    }
+    const float eps = norm->attr_f("epsilon", 1e-5f);
+    if (kind == 1) {
+      Node* f = g.AddNode("FusedGemm", {x_new, cons->inputs[1], "", "", gamma}, cons->outputs, kFusedDomain, g.UniqueName("FusedGemm"));
+      f->set_attr_s("activation", "none");
+      f->set_attr_f("rms_eps", eps);
+      g.RemoveNode(cons);
+    } else {
+      const size_t gi = kind == 2 ? 4 : 3;
+      if (cons->inputs.size() < gi + 1) cons->inputs.resize(gi + 1);
+      cons->inputs[0] = x_new;
+      cons->inputs[gi] = gamma;
+      cons->set_attr_f("rms_eps", eps);
+    }
+    g.RemoveNode(norm);
+    g.Invalidate();
+    ++count;
+  }
+  return count;
+}
+
 }  // namespace
 
 void AddGpuPasses(std::vector<Pass>& v) {
@@ -220,6 +300,7 @@ void AddGpuPasses(std::vector<Pass>& v) {
   v.push_back({"MatMulAllReduceFusion", 2, true, MatMulAllReduceFusion});
   v.push_back({"AllReduceResidualFusion", 2, true, AllReduceResidualFusion});
   v.push_back({"GemmEpilogueFusion", 2, true, GemmEpilogueFusion});
+  v.push_back({"RmsNormGemmFusion", 2, true, RmsNormGemmFusion});
 }
 
 }  // namespace opt

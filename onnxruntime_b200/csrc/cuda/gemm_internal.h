@@ -30,6 +30,9 @@ struct SmallGemmParams {
   const int4* tile_info;     // {expert, first row, end row, unused}; null = ordinary GEMM
   const int* num_tiles;      // device scalar: entries of tile_info in use
   int w_rows_per_expert;     // rows of W (and entries of bias: N) that belong to one expert
+  // ---- fused RMS normalisation of the activations (rms_eps > 0): out = (W x) / rms(x) with gamma folded into W
+  float rms_eps;
+  const void* x_rows;        // the activation matrix [M, K] itself (read with plain loads for the row statistics)
 };
 
 // Grouped GEMM over a device-side tile list (see ortb200_gemm_grouped).

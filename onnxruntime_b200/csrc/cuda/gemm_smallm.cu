@@ -87,7 +87,8 @@ struct SmallSmem {
   static constexpr int kPartBytes = kCols * kBM * 4;
   static constexpr int kBarOffset = kStageBytes * STAGES;
   static_assert(kPartBytes <= kStageBytes * STAGES, "partial tile must fit in the drained pipeline stages");
-  static constexpr int kTotal = kBarOffset + 8 * (2 * STAGES + 1) + 16 + 1024;
+  static constexpr int kRstdOffset = kBarOffset + 8 * (2 * STAGES + 1) + 16;  // float rstd[64] (fused RMS norm)
+  static constexpr int kTotal = kRstdOffset + 64 * 4 + 1024;
   static constexpr int kTmemCols = kCols < 32 ? 32 : kCols;
 };
 
@@ -105,6 +106,7 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
   uint64_t* empty_bar = full_bar + STAGES;
   uint64_t* tmem_full_bar = empty_bar + STAGES;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_full_bar + 1);
+  float* s_rstd = reinterpret_cast<float*>(smem + S::kRstdOffset);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -209,6 +211,40 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
     const int q = warp & 3;
     const int r = q * 32 + lane;
     const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+    if (p.rms_eps > 0.f) {
+      // Fused RMS normalisation: the weights carry gamma, so only 1 / rms(x[m, :]) is missing, and it is a per-token
+      // factor that commutes with the GEMM.  These warps are idle while the weights stream, so they read the token
+      // rows (a few KiB, L2 resident) and leave the factors in shared memory for the epilogue.
+      pdl_wait_prior_grids();
+      const int vecs = p.K / 8;
+      for (int j = q; j < BN; j += 4) {
+        const int m = m0 + j;
+        float ss = 0.f;
+        if (m < m_end) {
+          const uint4* row = reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(p.x_rows) + static_cast<long long>(m) * p.K * 2);
+          for (int v = lane; v < vecs; v += 32) {
+            const uint4 u4 = __ldg(row + v);
+            const uint32_t w4[4] = {u4.x, u4.y, u4.z, u4.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              float lo, hi;
+              if (p.dtype == ORTB200_BF16) {
+                lo = __uint_as_float(w4[e] << 16);
+                hi = __uint_as_float(w4[e] & 0xffff0000u);
+              } else {
+                const __half2 h2 = *reinterpret_cast<const __half2*>(&w4[e]);
+                lo = __low2float(h2);
+                hi = __high2float(h2);
+              }
+              ss += lo * lo + hi * hi;
+            }
+          }
+        }
+        ss = warp_sum(ss);
+        if (lane == 0) s_rstd[j] = rsqrtf(ss / static_cast<float>(p.K) + p.rms_eps);
+      }
+      asm volatile("bar.sync 2, 128;" ::: "memory");  // the four epilogue warps only
+    }
     if (!mbar_wait(tmem_full_bar, 0)) {
       if (p.status) atomicExch(p.status, kStatusTimeoutEpilogue);
     }
@@ -285,10 +321,11 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
         continue;
       }
       if (n_ok && m < m_end) {
-        float y = v * p.alpha + bias_v;
+        const float row_scale = p.rms_eps > 0.f ? s_rstd[j] * p.alpha : p.alpha;
+        float y = v * row_scale + bias_v;
         if (DUAL) {
           const float g = y / (1.0f + __expf(-y));
-          y = g * (u * p.alpha);
+          y = g * (u * row_scale);
         } else {
           y = act_apply(p.act, y);
         }
@@ -424,6 +461,8 @@ int launch_gemm_smallm(const ortb200_gemm_args* a, int bn, cudaStream_t stream, 
   p.residual = a->residual; p.ldr = a->ldr; p.status = a->status;
   p.world = 1; p.rank = 0; p.staging_offset = 0; p.slot_elems = 0; p.epoch = nullptr; p.done = nullptr;
   p.tile_info = nullptr; p.num_tiles = nullptr; p.w_rows_per_expert = 0;
+  p.rms_eps = a->rms_eps; p.x_rows = a->x;
+  if (a->rms_eps > 0.f && a->world > 1) return -12;
   for (int i = 0; i < 8; ++i) p.peers[i] = nullptr;
   if (a->world > 1) {
     if (a->world > 8 || a->rank < 0 || a->rank >= a->world || dual || a->ldo != a->N) return -12;
@@ -472,6 +511,7 @@ int launch_gemm_grouped(const ortb200_gemm_grouped_args* a, cudaStream_t stream)
   p.residual = nullptr; p.ldr = 0; p.status = a->status;
   p.world = 1; p.rank = 0; p.staging_offset = 0; p.slot_elems = 0; p.epoch = nullptr; p.done = nullptr;
   for (int i = 0; i < 8; ++i) p.peers[i] = nullptr;
+  p.rms_eps = 0.f; p.x_rows = nullptr;
   p.tile_info = static_cast<const int4*>(a->tile_info);
   p.num_tiles = a->num_tiles;
   p.w_rows_per_expert = a->w_rows_per_expert;

@@ -71,16 +71,29 @@ __device__ __forceinline__ float apply_act(int act, float v) {
   }
 }
 
-template <int BN, int STAGES, bool DUAL>
+// DUAL: two weight tiles (gate rows, up rows) share the activation tile and are combined by the SwiGLU epilogue.
+// TWOM: two vertically adjacent weight tiles share the activation tile, i.e. the CTA tile is 256 weight rows x BN
+// tokens.  Per k-block the CTA then loads 32 KiB of W and 2 * BN * 64 bytes of X for twice the math, which is what
+// keeps a large GEMM from being bound by L2 -> SM bandwidth (131 instead of 85 FLOP per loaded byte at BN = 256).
+template <int BN, int STAGES, bool DUAL, bool TWOM = false>
 struct GemmSmem {
+  static constexpr bool kTwoA = DUAL || TWOM;
   static constexpr int kABytes = kBM * kBK * 2;
   static constexpr int kBBytes = BN * kBK * 2;
-  static constexpr int kStageBytes = kABytes * (DUAL ? 2 : 1) + kBBytes;
+  static constexpr int kStageBytes = kABytes * (kTwoA ? 2 : 1) + kBBytes;
   static constexpr int kBarOffset = kStageBytes * STAGES;
-  static constexpr int kTotal = kBarOffset + 8 * (2 * STAGES + 4) + 16 + 1024;  // + alignment slack
-  static constexpr int kCols = (DUAL ? 2 : 1) * BN;                             // accumulator columns per buffer
+  // epilogue staging: up to 128 token columns x 128 weight rows of 16-bit results, so that global memory is written
+  // (and the residual read) with 16-byte accesses along the output rows
+  static constexpr int kPassCols = BN < 128 ? BN : 128;
+  static constexpr int kStagingOffset = kBarOffset + 256;
+  static constexpr int kStagingBytes = kPassCols * kBM * 2;
+  static constexpr int kTotal = kStagingOffset + kStagingBytes + 1024;          // + alignment slack
+  static_assert(8 * (2 * STAGES + 4) + 16 <= 256, "barrier area");
+  static constexpr int kCols = (kTwoA ? 2 : 1) * BN;                            // accumulator columns per buffer
   static constexpr int kBufCols = kCols < 32 ? 32 : kCols;
-  static constexpr int kTmemCols = 2 * kBufCols;                                 // two accumulator buffers
+  static constexpr int kNumBufs = 2 * kBufCols <= 512 ? 2 : 1;                   // accumulator buffers that fit in TMEM
+  static constexpr int kTmemCols = kNumBufs * kBufCols;
+  static constexpr int kTileRows = TWOM ? 2 * kBM : kBM;                         // weight rows per CTA tile
 };
 
 // Work decomposition shared by the three warp roles.  Units are (tile, k-block) pairs numbered tile-major;
@@ -107,11 +120,14 @@ __device__ __forceinline__ int owner_of(const GemmKernelParams& p, long long u) 
   return static_cast<int>(((u + 1) * gridDim.x - 1) / U);
 }
 
-template <int BN, int STAGES, bool DUAL>
+template <int BN, int STAGES, bool DUAL, bool TWOM = false>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
                     const GemmKernelParams p) {
-  using S = GemmSmem<BN, STAGES, DUAL>;
+  using S = GemmSmem<BN, STAGES, DUAL, TWOM>;
+  constexpr bool TWO_A = S::kTwoA;
+  constexpr int NBUF = S::kNumBufs;
+  const int second_a_rows = DUAL ? p.dual_offset : kBM;  // row distance between the two weight tiles of a stage
   static_assert((S::kTmemCols & (S::kTmemCols - 1)) == 0 && S::kTmemCols <= 512, "TMEM columns must be a power of two <= 512");
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -161,7 +177,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
       auto coords = [&](long long u, int* kb, int* n0, int* m0) {
         const int tile = static_cast<int>(u / p.num_kb);
         *kb = static_cast<int>(u % p.num_kb);
-        *n0 = (tile / p.tiles_m) * kBM;
+        *n0 = (tile / p.tiles_m) * S::kTileRows;
         *m0 = (tile % p.tiles_m) * BN;
       };
       for (int i = 0; i < pre; ++i) {
@@ -170,14 +186,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
         uint8_t* st = smem + i * S::kStageBytes;
         mbar_expect_tx(&full_bar[i], S::kStageBytes);
         tma_load_2d_hint(st, &tmap_w, &full_bar[i], kb * p.k_per_block, n0, pol_w);
-        if (DUAL) tma_load_2d_hint(st + S::kABytes, &tmap_w, &full_bar[i], kb * p.k_per_block, n0 + p.dual_offset, pol_w);
+        if (TWO_A) tma_load_2d_hint(st + S::kABytes, &tmap_w, &full_bar[i], kb * p.k_per_block, n0 + second_a_rows, pol_w);
       }
       pdl_wait_prior_grids();
       for (int i = 0; i < pre; ++i) {
         int kb, n0, m0;
         coords(range.begin + i, &kb, &n0, &m0);
         uint8_t* st = smem + i * S::kStageBytes;
-        tma_load_2d(st + S::kABytes * (DUAL ? 2 : 1), &tmap_x, &full_bar[i], kb * p.k_per_block, m0);
+        tma_load_2d(st + S::kABytes * (TWO_A ? 2 : 1), &tmap_x, &full_bar[i], kb * p.k_per_block, m0);
       }
       for (long long i = pre; i < total; ++i) {
         const int s = static_cast<int>(i % STAGES);
@@ -191,8 +207,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
         uint8_t* st = smem + s * S::kStageBytes;
         mbar_expect_tx(&full_bar[s], S::kStageBytes);
         tma_load_2d_hint(st, &tmap_w, &full_bar[s], kb * p.k_per_block, n0, pol_w);
-        if (DUAL) tma_load_2d_hint(st + S::kABytes, &tmap_w, &full_bar[s], kb * p.k_per_block, n0 + p.dual_offset, pol_w);
-        tma_load_2d(st + S::kABytes * (DUAL ? 2 : 1), &tmap_x, &full_bar[s], kb * p.k_per_block, m0);
+        if (TWO_A) tma_load_2d_hint(st + S::kABytes, &tmap_w, &full_bar[s], kb * p.k_per_block, n0 + second_a_rows, pol_w);
+        tma_load_2d(st + S::kABytes * (TWO_A ? 2 : 1), &tmap_x, &full_bar[s], kb * p.k_per_block, m0);
       }
     }
   } else if (warp == 1) {
@@ -204,9 +220,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
       for (long long u = range.begin; u < range.end && ok; ++seg) {
         const long long tile_end = (u / p.num_kb + 1) * p.num_kb;
         const long long seg_end = tile_end < range.end ? tile_end : range.end;
-        const int buf = seg & 1;
+        const int buf = seg % NBUF;
         const uint32_t tmem_d = tmem_base + buf * S::kBufCols;
-        if (seg >= 2 && !mbar_wait(&tmem_empty_bar[buf], ((seg >> 1) - 1) & 1)) {
+        if (seg >= NBUF && !mbar_wait(&tmem_empty_bar[buf], ((seg / NBUF) - 1) & 1)) {
           ok = false;
           break;
         }
@@ -220,7 +236,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
           }
           tcgen05_fence_after();
           const uint32_t a_addr = smem_u32(smem + s * S::kStageBytes);
-          const uint32_t b_addr = a_addr + S::kABytes * (DUAL ? 2 : 1);
+          const uint32_t b_addr = a_addr + S::kABytes * (TWO_A ? 2 : 1);
           const uint64_t adesc = umma_desc_sw128(a_addr);
           const uint64_t bdesc = umma_desc_sw128(b_addr);
 #pragma unroll
@@ -230,7 +246,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
             if (p.in_fp8) umma_f8(tmem_d, adesc + 2 * k, bdesc + 2 * k, idesc, (!first || k > 0) ? 1u : 0u);
             else umma_f16(tmem_d, adesc + 2 * k, bdesc + 2 * k, idesc, (!first || k > 0) ? 1u : 0u);
           }
-          if (DUAL) {
+          if (TWO_A) {
             const uint64_t a2desc = umma_desc_sw128(a_addr + S::kABytes);
 #pragma unroll
             for (int k = 0; k < kBK / 16; ++k) {
@@ -258,12 +274,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
       const long long tile_end = tile_begin + p.num_kb;
       const long long seg_end = tile_end < range.end ? tile_end : range.end;
       const bool whole = (u == tile_begin) && (seg_end == tile_end);
-      const int buf = seg & 1;
-      const int n0 = (tile / p.tiles_m) * kBM, m0 = (tile % p.tiles_m) * BN;
-      const int n = n0 + r;
-      const bool n_ok = n < p.N;
+      const int buf = seg % NBUF;
+      const int n0 = (tile / p.tiles_m) * S::kTileRows, m0 = (tile % p.tiles_m) * BN;
       const uint32_t t_lane = tmem_base + buf * S::kBufCols + (static_cast<uint32_t>(q * 32) << 16);
-      if (!mbar_wait(&tmem_full_bar[buf], (seg >> 1) & 1)) {
+      if (!mbar_wait(&tmem_full_bar[buf], (seg / NBUF) & 1)) {
         ok = false;
         if (p.status) atomicExch(p.status, kStatusTimeoutEpilogue);
         break;
@@ -301,37 +315,40 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
         if (do_output) __threadfence();
       }
 
-      if (do_output) {
-        const float bias_v = (p.bias != nullptr && n_ok)
-                                 ? (p.dtype == ORTB200_BF16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.bias)[n])
-                                                            : __half2float(reinterpret_cast<const __half*>(p.bias)[n]))
-                                 : 0.0f;
-        const float* tile_ws = whole ? nullptr : p.ws + static_cast<size_t>(tile) * p.max_contrib * (S::kCols * kBM);
+      if (whole) {
+        // ---- whole tile: accumulator -> (bias, activation) -> 16-bit staging tile in shared memory -> coalesced
+        // 16-byte global writes with the residual added on the way out
+        constexpr int PASS = S::kPassCols;
+        constexpr int LD = PASS >= 32 ? 32 : 16;
+        uint16_t* stg = reinterpret_cast<uint16_t*>(smem + S::kStagingOffset);
+        const int et = static_cast<int>(threadIdx.x) - 64;  // 0..127 among the epilogue threads
+        const bool bf16 = p.dtype == ORTB200_BF16;
+        const bool vec_ok = (p.ldo % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0) &&
+                            (p.residual == nullptr || ((p.ldr % 8 == 0) && (reinterpret_cast<uintptr_t>(p.residual) & 15) == 0));
 #pragma unroll 1
-        for (int c = 0; c < BN; c += 16) {
-          float v[16];
-          float uu[16];
-          if (whole) {
-            tmem_ld_x16(t_lane + c, v);
-            if (DUAL) tmem_ld_x16(t_lane + BN + c, uu);
-            tmem_ld_wait();
-          } else {
-#pragma unroll
-            for (int j = 0; j < 16; ++j) { v[j] = 0.0f; uu[j] = 0.0f; }
-            for (int s = 0; s < n_contrib; ++s) {
-              const float* src = tile_ws + static_cast<size_t>(s) * (S::kCols * kBM);
-#pragma unroll
-              for (int j = 0; j < 16; ++j) {
-                v[j] += __ldcg(&src[(c + j) * kBM + r]);
-                if (DUAL) uu[j] += __ldcg(&src[(BN + c + j) * kBM + r]);
+        for (int half = 0; half < (TWOM ? 2 : 1); ++half) {
+          const int nrow0 = n0 + half * kBM;
+          const int n = nrow0 + r;
+          const float bias_v = (p.bias != nullptr && n < p.N)
+                                   ? (bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.bias)[n])
+                                           : __half2float(reinterpret_cast<const __half*>(p.bias)[n]))
+                                   : 0.0f;
+#pragma unroll 1
+          for (int pc = 0; pc < BN; pc += PASS) {
+#pragma unroll 1
+            for (int c = 0; c < PASS; c += LD) {
+              float v[LD];
+              float uu[LD];
+              if (LD == 32) {
+                tmem_ld_x32(t_lane + half * BN + pc + c, v);
+                if (DUAL) tmem_ld_x32(t_lane + BN + pc + c, uu);
+              } else {
+                tmem_ld_x16(t_lane + half * BN + pc + c, v);
+                if (DUAL) tmem_ld_x16(t_lane + BN + pc + c, uu);
               }
-            }
-          }
-          if (n_ok) {
+              tmem_ld_wait();
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              const int m = m0 + c + j;
-              if (m < p.M) {
+              for (int j = 0; j < LD; ++j) {
                 float y = v[j] * p.alpha + bias_v;
                 if (DUAL) {
                   const float g = y / (1.0f + __expf(-y));
@@ -339,21 +356,142 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
                 } else {
                   y = apply_act(p.act, y);
                 }
-                if (p.dtype == ORTB200_BF16) {
-                  if (p.residual) y += __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.residual)[m * p.ldr + n]);
-                  reinterpret_cast<__nv_bfloat16*>(p.out)[m * p.ldo + n] = __float2bfloat16_rn(y);
+                uint16_t bits;
+                if (bf16) {
+                  const __nv_bfloat16 h = __float2bfloat16_rn(y);
+                  bits = *reinterpret_cast<const uint16_t*>(&h);
                 } else {
-                  if (p.residual) y += __half2float(reinterpret_cast<const __half*>(p.residual)[m * p.ldr + n]);
-                  reinterpret_cast<__half*>(p.out)[m * p.ldo + n] = __float2half_rn(y);
+                  const __half h = __float2half_rn(y);
+                  bits = *reinterpret_cast<const uint16_t*>(&h);
+                }
+                stg[(c + j) * kBM + r] = bits;
+              }
+            }
+            if (half == (TWOM ? 1 : 0) && pc + PASS >= BN) {
+              // the accumulator has been read completely: the MMA warp may reuse this buffer
+              tcgen05_fence_before();
+              mbar_arrive(&tmem_empty_bar[buf]);
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            for (int idx = et; idx < PASS * 16; idx += 128) {
+              const int row = idx >> 4, ch = idx & 15;
+              const int m = m0 + pc + row;
+              const int nn = nrow0 + ch * 8;
+              if (m >= p.M || nn >= p.N) continue;
+              const uint4 val = *reinterpret_cast<const uint4*>(stg + row * kBM + ch * 8);
+              const long long o = static_cast<long long>(m) * p.ldo + nn;
+              if (vec_ok && nn + 8 <= p.N) {
+                uint4 res = val;
+                if (p.residual != nullptr) {
+                  const uint4 rr = __ldg(reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(p.residual) + static_cast<long long>(m) * p.ldr + nn));
+                  const uint32_t a4[4] = {val.x, val.y, val.z, val.w};
+                  const uint32_t b4[4] = {rr.x, rr.y, rr.z, rr.w};
+                  uint32_t o4[4];
+#pragma unroll
+                  for (int e = 0; e < 4; ++e) {
+                    if (bf16) {
+                      const float lo = __uint_as_float(a4[e] << 16) + __uint_as_float(b4[e] << 16);
+                      const float hi = __uint_as_float(a4[e] & 0xffff0000u) + __uint_as_float(b4[e] & 0xffff0000u);
+                      const __nv_bfloat162 h2 = __floats2bfloat162_rn(lo, hi);
+                      o4[e] = *reinterpret_cast<const uint32_t*>(&h2);
+                    } else {
+                      const float2 fa = __half22float2(*reinterpret_cast<const __half2*>(&a4[e]));
+                      const float2 fb = __half22float2(*reinterpret_cast<const __half2*>(&b4[e]));
+                      const __half2 h2 = __floats2half2_rn(fa.x + fb.x, fa.y + fb.y);
+                      o4[e] = *reinterpret_cast<const uint32_t*>(&h2);
+                    }
+                  }
+                  res = make_uint4(o4[0], o4[1], o4[2], o4[3]);
+                }
+                *reinterpret_cast<uint4*>(static_cast<uint16_t*>(p.out) + o) = res;
+              } else {
+                const uint16_t* sv = stg + row * kBM + ch * 8;
+                for (int e = 0; e < 8 && nn + e < p.N; ++e) {
+                  float y = bf16 ? __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(sv + e)) : __half2float(*reinterpret_cast<const __half*>(sv + e));
+                  if (p.residual != nullptr) {
+                    const long long ri = static_cast<long long>(m) * p.ldr + nn + e;
+                    y += bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.residual)[ri]) : __half2float(reinterpret_cast<const __half*>(p.residual)[ri]);
+                  }
+                  if (bf16) reinterpret_cast<__nv_bfloat16*>(p.out)[o + e] = __float2bfloat16_rn(y);
+                  else reinterpret_cast<__half*>(p.out)[o + e] = __float2half_rn(y);
+                }
+              }
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");  // staging is free again
+          }
+        }
+        u = seg_end;
+        continue;
+      }
+
+      if (do_output) {
+        const float* tile_ws = whole ? nullptr : p.ws + static_cast<size_t>(tile) * p.max_contrib * (S::kCols * kBM);
+#pragma unroll 1
+        for (int half = 0; half < (TWOM ? 2 : 1); ++half) {
+          const int n = n0 + half * kBM + r;  // weight row == output column of this lane
+          const bool n_ok = n < p.N;
+          const int c_off = half * BN;        // accumulator columns of this half
+          const float bias_v = (p.bias != nullptr && n_ok)
+                                   ? (p.dtype == ORTB200_BF16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.bias)[n])
+                                                              : __half2float(reinterpret_cast<const __half*>(p.bias)[n]))
+                                   : 0.0f;
+#pragma unroll 1
+          for (int c = 0; c < BN; c += 16) {
+            // residual values first: 16 independent loads in flight while the accumulator is fetched (issued one by
+            // one between the stores they would otherwise be serialised, since `out` may alias `residual`)
+            float rv[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) rv[j] = 0.0f;
+            if (p.residual != nullptr && n_ok) {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                const int m = m0 + c + j;
+                if (m < p.M) {
+                  const long long idx = static_cast<long long>(m) * p.ldr + n;
+                  rv[j] = p.dtype == ORTB200_BF16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.residual)[idx])
+                                                  : __half2float(reinterpret_cast<const __half*>(p.residual)[idx]);
+                }
+              }
+            }
+            float v[16];
+            float uu[16];
+            if (whole) {
+              tmem_ld_x16(t_lane + c_off + c, v);
+              if (DUAL) tmem_ld_x16(t_lane + BN + c, uu);
+              tmem_ld_wait();
+            } else {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) { v[j] = 0.0f; uu[j] = 0.0f; }
+              for (int s = 0; s < n_contrib; ++s) {
+                const float* src = tile_ws + static_cast<size_t>(s) * (S::kCols * kBM);
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                  v[j] += __ldcg(&src[(c_off + c + j) * kBM + r]);
+                  if (DUAL) uu[j] += __ldcg(&src[(BN + c + j) * kBM + r]);
+                }
+              }
+            }
+            if (n_ok) {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                const int m = m0 + c + j;
+                if (m < p.M) {
+                  float y = v[j] * p.alpha + bias_v;
+                  if (DUAL) {
+                    const float g = y / (1.0f + __expf(-y));
+                    y = g * (uu[j] * p.alpha);
+                  } else {
+                    y = apply_act(p.act, y);
+                  }
+                  y += rv[j];
+                  const long long o = static_cast<long long>(m) * p.ldo + n;
+                  if (p.dtype == ORTB200_BF16) reinterpret_cast<__nv_bfloat16*>(p.out)[o] = __float2bfloat16_rn(y);
+                  else reinterpret_cast<__half*>(p.out)[o] = __float2half_rn(y);
                 }
               }
             }
           }
         }
-      }
-      if (whole) {
-        tcgen05_fence_before();
-        mbar_arrive(&tmem_empty_bar[buf]);
       }
       u = seg_end;
     }
@@ -392,12 +530,12 @@ static int pick_bn(int M) {
   return 256;
 }
 
-template <int BN, int STAGES, bool DUAL>
+template <int BN, int STAGES, bool DUAL, bool TWOM = false>
 static int launch_gemm(const CUtensorMap& tw, const CUtensorMap& tx, const GemmKernelParams& p, int grid,
                        cudaStream_t stream, bool use_pdl) {
-  using S = GemmSmem<BN, STAGES, DUAL>;
+  using S = GemmSmem<BN, STAGES, DUAL, TWOM>;
   static_assert(S::kTotal <= 227 * 1024, "shared memory budget exceeded");
-  auto kern = gemm_tcgen05_kernel<BN, STAGES, DUAL>;
+  auto kern = gemm_tcgen05_kernel<BN, STAGES, DUAL, TWOM>;
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal);
@@ -431,17 +569,24 @@ struct GemmPlan {
   int bn, num_kb, tiles_n, tiles_m, grid, max_contrib;
   int64_t tiles, ws_need;
   bool tile_aligned;
+  bool twom;  // CTA tiles of 256 weight rows (two stacked 128-row MMA tiles)
 };
 
 // Persistent grid: one CTA per SM.  With many tiles each CTA takes whole tiles; with few, the (tile, k-block)
 // units are dealt out evenly (stream-K) and tiles shared by several CTAs are reduced through the workspace.
 // ws_available < 0 means "unlimited" (used to size the workspace).
-int plan_gemm(int M, int N, int K, bool dual, int force_bn, int force_splits, int64_t ws_available, GemmPlan* pl) {
+int plan_gemm(int M, int N, int K, bool dual, int force_bn, int force_splits, int64_t ws_available, GemmPlan* pl,
+              int force_tile_rows = 0) {
   int bn = force_bn ? force_bn : pick_bn(M);
   if (dual && bn > 128) bn = 128;     // two accumulators, double-buffered, must fit 512 TMEM columns
   pl->bn = bn;
   pl->num_kb = (K + kBK - 1) / kBK;
-  pl->tiles_n = (N + kBM - 1) / kBM;
+  // 256 x 256 CTA tiles (two stacked weight tiles sharing the activation tile) halve the X traffic from L2, but the
+  // second MMA re-reads the X tile from shared memory and the 512-column accumulator cannot be double-buffered;
+  // measured slower than 128 x 256 tiles on B200 (8192 x 6144 x 4096: 575 vs 429 us), so only on request
+  pl->twom = !dual && bn == 256 && N >= 256 && force_tile_rows == 256;
+  const int tile_rows = pl->twom ? 2 * kBM : kBM;
+  pl->tiles_n = (N + tile_rows - 1) / tile_rows;
   pl->tiles_m = (M + bn - 1) / bn;
   pl->tiles = static_cast<int64_t>(pl->tiles_n) * pl->tiles_m;
   if (pl->tiles > 0x7fffffff / pl->num_kb) return -9;
@@ -463,7 +608,7 @@ int plan_gemm(int M, int N, int K, bool dual, int force_bn, int force_splits, in
     const int64_t per_cta = units / grid;  // >= 1
     max_contrib = static_cast<int>(pl->num_kb / (per_cta > 0 ? per_cta : 1)) + 2;
     if (max_contrib > grid) max_contrib = grid;
-    need = 65536 + pl->tiles * max_contrib * (dual ? 2 : 1) * bn * kBM * 4;
+    need = 65536 + pl->tiles * max_contrib * ((dual || pl->twom) ? 2 : 1) * bn * kBM * 4;
     if (pl->tiles > 16384 || (ws_available >= 0 && ws_available < need)) tile_aligned = true;
   }
   if (tile_aligned) {
@@ -481,9 +626,11 @@ int plan_gemm(int M, int N, int K, bool dual, int force_bn, int force_splits, in
 }  // namespace
 
 extern "C" int64_t ortb200_gemm_workspace_bytes(int M, int N, int K, int act) {
-  GemmPlan pl;
+  GemmPlan pl, pl128;
   if (M <= 0 || N <= 0 || K <= 0 || plan_gemm(M, N, K, act == ORTB200_ACT_SWIGLU, 0, 0, -1, &pl) != 0) return 65536;
-  return pl.ws_need > 65536 ? pl.ws_need : 65536;
+  int64_t need = pl.ws_need;
+  if (plan_gemm(M, N, K, act == ORTB200_ACT_SWIGLU, 0, 0, -1, &pl128, 128) == 0 && pl128.ws_need > need) need = pl128.ws_need;
+  return need > 65536 ? need : 65536;
 }
 
 extern "C" int ortb200_gemm_last_config(int* bn, int* splits, int* stages) {
@@ -517,11 +664,13 @@ extern "C" int ortb200_gemm(const ortb200_gemm_args* a, ortb200_stream_t stream_
     }
   }
   if (a->world > 1) return -12;  // the fused all-reduce exists for decode-shaped problems only
+  if (a->rms_eps > 0.f) return -14;  // so does the fused RMS normalisation
   GemmPlan pl;
   // fp8 operands: the planner counts 64-element k-blocks, and a stage holds 128 fp8 elements
   const int k_planned = fp8 ? (a->K + 1) / 2 : a->K;
   const int force_bn = fp8 && (a->force_bn == 0 || a->force_bn < 128) ? (a->M > 128 ? 256 : 128) : a->force_bn;
-  const int prc = plan_gemm(a->M, a->N, k_planned, dual, force_bn, a->force_splits, a->workspace ? a->workspace_bytes : 0, &pl);
+  const int prc = plan_gemm(a->M, a->N, k_planned, dual, force_bn, a->force_splits, a->workspace ? a->workspace_bytes : 0, &pl,
+                            a->force_tile_rows);
   if (prc != 0) return prc;
   const int bn = pl.bn, num_kb = pl.num_kb, tiles_m = pl.tiles_m, grid = pl.grid, max_contrib = pl.max_contrib;
   const int64_t tiles = pl.tiles;
@@ -570,8 +719,8 @@ extern "C" int ortb200_gemm(const ortb200_gemm_args* a, ortb200_stream_t stream_
       else { stages = 6; rc = launch_gemm<128, 6, false>(tw, tx, p, grid, stream, pdl); }
       break;
     case 256:
-      stages = 4;
-      rc = launch_gemm<256, 4, false>(tw, tx, p, grid, stream, pdl);
+      if (pl.twom) { stages = 3; rc = launch_gemm<256, 3, false, true>(tw, tx, p, grid, stream, pdl); }
+      else { stages = 4; rc = launch_gemm<256, 4, false>(tw, tx, p, grid, stream, pdl); }
       break;
     default: return -8;
   }

@@ -473,6 +473,7 @@ __global__ void __launch_bounds__(128) gqa_decode_kernel(const DecodeParams p) {
   }
 }
 
+
 template <typename T, int H, int G, bool PAGED>
 static int launch_decode_g(const DecodeParams& p, dim3 grid, cudaStream_t stream, bool use_pdl) {
   constexpr int kSmem = kDecStages * 2 * kDecTile * H * static_cast<int>(sizeof(T)) + (4 * G * H + 8 * G) * 4 + 8 * kDecStages;
@@ -513,7 +514,7 @@ static int launch_decode(const ortb200_gqa_decode_args* a, cudaStream_t stream) 
     if (splits < 1) splits = 1;
   }
   const int tiles = a->B * a->Nk * gparts;
-  const int64_t need = 65536 + static_cast<int64_t>(tiles) * splits * G * (H + 2) * 4;
+  const int64_t need = 65536 + static_cast<int64_t>(tiles) * splits * G * (H + 4) * 4;
   if (splits > 1 && (!a->workspace || a->workspace_bytes < need || tiles > 16384)) splits = 1;
   DecodeParams p;
   p.q = a->q; p.k_cache = a->k_cache; p.v_cache = a->v_cache; p.seqlens_k = a->seqlens_k; p.head_sink = a->head_sink;
@@ -542,7 +543,7 @@ using namespace ortb200;
 
 extern "C" int64_t ortb200_gqa_decode_workspace_bytes(int B, int N, int H) {
   // tiles * G <= B * N ; at most 32 splits
-  return 65536 + static_cast<int64_t>(B) * N * 32 * (H + 2) * 4;
+  return 65536 + static_cast<int64_t>(B) * N * 32 * (H + 4) * 4;
 }
 
 extern "C" int ortb200_gqa_decode(const ortb200_gqa_decode_args* a, ortb200_stream_t stream_) {

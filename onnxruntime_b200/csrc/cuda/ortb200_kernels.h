@@ -77,6 +77,11 @@ typedef struct {
   // the tensor cores run in their 8-bit mode; out / bias / residual keep `dtype`, `alpha` carries the product of
   // the per-tensor scales.  0 = operands are of `dtype`.
   int in_dtype;
+  // Fused RMS normalisation of x (decode-shaped problems, M <= 64, only): when rms_eps > 0 the kernel computes
+  // out = act(alpha * (x @ w^T) / rms(x) + bias) + residual with rms(x)[m] = sqrt(mean_k x[m, k]^2 + rms_eps);
+  // the caller folds the norm's gamma into w (w[n, k] *= gamma[k]).  Larger M returns -14: normalise first.
+  float rms_eps;
+  int force_tile_rows;  // 0 / 128 = 128-weight-row CTA tiles; 256 = 256-row tiles in the large-M kernel (M > 128)
 } ortb200_gemm_args;
 
 int ortb200_gemm(const ortb200_gemm_args* args, ortb200_stream_t stream);

@@ -54,7 +54,7 @@ class GemmArgs(ctypes.Structure):
         ("workspace", ctypes.c_void_p), ("workspace_bytes", ctypes.c_int64), ("status", ctypes.c_void_p),
         ("force_splits", ctypes.c_int), ("force_bn", ctypes.c_int), ("use_pdl", ctypes.c_int),
         ("world", ctypes.c_int), ("rank", ctypes.c_int), ("peers", ctypes.c_void_p * 8), ("symm_bytes", ctypes.c_int64),
-        ("in_dtype", ctypes.c_int),
+        ("in_dtype", ctypes.c_int), ("rms_eps", ctypes.c_float), ("force_tile_rows", ctypes.c_int),
     ]
 
 
@@ -84,7 +84,7 @@ def gemm(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
          out: Optional[torch.Tensor] = None, n: Optional[int] = None, dual_offset: int = 0,
          force_splits: int = 0, force_bn: int = 0, status: Optional[torch.Tensor] = None,
          use_pdl: bool = False, peers=None, rank: int = 0, symm_bytes: int = 0,
-         out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+         out_dtype: Optional[torch.dtype] = None, rms_eps: float = 0.0, force_tile_rows: int = 0) -> torch.Tensor:
     """out[M, N] = act(alpha * x[M, K] @ w[N, K].T + bias) + residual  (tcgen05 kernel).
     x / w of dtype float8_e4m3fn use the 8-bit tensor-core mode; out_dtype (fp16 / bf16) is then required."""
     assert x.is_cuda and w.is_cuda and x.dtype == w.dtype and x.dim() == 2 and w.dim() == 2
@@ -106,7 +106,7 @@ def gemm(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
                  dtype_code(odt), ACT[act], alpha, _ptr(ws), ws.numel(), _ptr(status), force_splits, force_bn,
                  1 if use_pdl else 0, len(peers) if peers else 1, rank,
                  (ctypes.c_void_p * 8)(*(list(peers) + [None] * (8 - len(peers)))) if peers else (ctypes.c_void_p * 8)(),
-                 symm_bytes, 3 if fp8 else 0)
+                 symm_bytes, 3 if fp8 else 0, rms_eps, force_tile_rows)
     rc = lib().ortb200_gemm(ctypes.byref(a), ctypes.c_void_p(stream_ptr()))
     if rc != 0:
         raise RuntimeError(f"ortb200_gemm rejected its arguments (code {rc})")

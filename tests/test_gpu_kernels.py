@@ -198,3 +198,40 @@ def test_argmax_gather(K):
     table = torch.randn(1000, 256, device="cuda").bfloat16()
     ids = torch.randint(0, 1000, (4, 7), device="cuda")
     assert torch.equal(K.gather_rows(table, ids), table[ids])
+
+
+@pytest.mark.parametrize("M,N,Kd,act", [(8, 1024, 4096, "none"), (1, 512, 512, "none"), (16, 2048, 1024, "swiglu"), (33, 768, 2048, "none"),
+                                        (8, 4096, 14336, "none")])
+def test_gemm_fused_rms_norm(K, M, N, Kd, act):
+    """out = act((x / rms(x)) @ (W * gamma)^T): gamma is folded into the weights by the caller, 1 / rms in the epilogue."""
+    torch.manual_seed(0)
+    x = (torch.randn(M, Kd, device="cuda") * 2.0).bfloat16()
+    rows = N * (2 if act == "swiglu" else 1)
+    w = (torch.randn(rows, Kd, device="cuda") * 0.05).bfloat16()
+    res = torch.randn(M, N, device="cuda").bfloat16() if act == "none" else None
+    y = K.gemm(x, w, act=act, residual=res, rms_eps=1e-5)
+    xn = x.float() * torch.rsqrt(x.float().pow(2).mean(-1, keepdim=True) + 1e-5)
+    if act == "swiglu":
+        ref = torch.nn.functional.silu(xn @ w[:N].float().T) * (xn @ w[N:].float().T)
+    else:
+        ref = xn @ w.float().T + res.float()
+    assert _rel(y, ref) < 1e-2
+
+
+@pytest.mark.parametrize("splits", [1, 3, 8])
+@pytest.mark.parametrize("H", [64, 128])
+def test_gqa_decode_split_counts_agree(K, H, splits):
+    """Every split count gives the fp32 reference's answer, also with a head sink and a soft cap in play."""
+    torch.manual_seed(1)
+    B, N, Nk, Smax = 4, 16, 2, 1100
+    lens = torch.tensor([1, 31, 640, 1100], dtype=torch.int32, device="cuda")
+    q = torch.randn(B, N, H, device="cuda").bfloat16()
+    kc = torch.randn(B, Nk, Smax, H, device="cuda").bfloat16()
+    vc = torch.randn(B, Nk, Smax, H, device="cuda").bfloat16()
+    a = K.gqa_decode(q, kc, vc, lens - 1, splits=splits)
+    ref = _ref_attention(q.float().unsqueeze(2), kc.float(), vc.float(), (lens - 1).long(), 1 / math.sqrt(H), lens=lens.long()).squeeze(2)
+    assert _rel(a.view(B, N, H), ref) < 2e-2
+    sink = torch.randn(N, device="cuda").bfloat16()
+    a2 = K.gqa_decode(q, kc, vc, lens - 1, splits=splits, head_sink=sink, softcap=30.0)
+    b2 = K.gqa_decode(q, kc, vc, lens - 1, splits=1, head_sink=sink, softcap=30.0)
+    assert _rel(a2, b2) < 1e-2

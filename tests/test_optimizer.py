@@ -208,3 +208,40 @@ def test_gpu_lowering_passes_on_graph_level():
     a = ort.InferenceSession(model, providers=["CPUExecutionProvider"]).run(None, {"x": x})[0]
     b = ort.InferenceSession(out, providers=["CPUExecutionProvider"]).run(None, {"x": x})[0]
     np.testing.assert_allclose(a.astype(np.float32), b.astype(np.float32), rtol=2e-2, atol=2e-2)
+
+
+def test_rms_norm_folds_into_the_surrounding_gemms():
+    """x -> GEMM -> (+residual, RMS norm) -> GEMM / SwiGLU pair: the add moves into the first GEMM's epilogue and the
+    norm into the second GEMM (gamma into its weights, 1/rms as an epilogue factor)."""
+    import torch
+    torch.manual_seed(0)
+    H, F = 64, 128
+    W1, Wq = (torch.randn(H, H) * 0.1).half(), (torch.randn(H, 96) * 0.1).half()
+    Wg, Wu, Wd = (torch.randn(H, F) * 0.1).half(), (torch.randn(H, F) * 0.1).half(), (torch.randn(F, H) * 0.1).half()
+    g0, g1, g2 = (torch.rand(H) + 0.5).half(), (torch.rand(H) + 0.5).half(), (torch.rand(H) + 0.5).half()
+    nodes = [ol.make_node("SimplifiedLayerNormalization", ["x", "g0"], ["n0"], axis=-1, epsilon=1e-5),
+             ol.make_node("MatMul", ["n0", "W1"], ["o"]),
+             ol.make_node("SkipSimplifiedLayerNormalization", ["o", "x", "g1"], ["n1", "", "", "res1"], domain="com.microsoft", epsilon=1e-5),
+             ol.make_node("MatMul", ["n1", "Wg"], ["g"]), ol.make_node("MatMul", ["n1", "Wu"], ["u"]),
+             ol.make_node("Sigmoid", ["g"], ["sg"]), ol.make_node("Mul", ["g", "sg"], ["act"]), ol.make_node("Mul", ["act", "u"], ["h"]),
+             ol.make_node("MatMul", ["h", "Wd"], ["d"]),
+             ol.make_node("SkipSimplifiedLayerNormalization", ["d", "res1", "g2"], ["n2", "", "", "res2"], domain="com.microsoft", epsilon=1e-5),
+             ol.make_node("MatMul", ["n2", "Wq"], ["q"]), ol.make_node("Identity", ["res2"], ["stream"])]
+    model = graph_model(nodes, [ol.make_tensor_value_info("x", T.FLOAT16, ["b", H])],
+                        [ol.make_tensor_value_info("q", T.FLOAT16, None), ol.make_tensor_value_info("stream", T.FLOAT16, None)],
+                        [ol.make_tensor(n, v) for n, v in (("W1", W1), ("Wq", Wq), ("Wg", Wg), ("Wu", Wu), ("Wd", Wd), ("g0", g0), ("g1", g1), ("g2", g2))])
+    out, stats = C.optimize_model(model, 99, [], True)
+    assert stats["RmsNormGemmFusion"] == 3
+    nodes_out = C.model_nodes(out)
+    ops = [n["op_type"] for n in nodes_out]
+    assert "SkipSimplifiedLayerNormalization" not in ops and "SimplifiedLayerNormalization" not in ops
+    assert ops.count("FusedGemm") == 3 and ops.count("GemmSwiGLU") == 1
+    assert sum(1 for n in nodes_out if "rms_eps" in n["attrs"]) == 3
+    x = (torch.randn(5, H) * 0.7).half().numpy()
+    a = ort.InferenceSession(model, providers=["CPUExecutionProvider"]).run(None, {"x": x})
+    b = ort.InferenceSession(out, providers=["CPUExecutionProvider"]).run(None, {"x": x})
+    for u, v in zip(a, b):
+        np.testing.assert_allclose(u.astype(np.float32), v.astype(np.float32), rtol=2e-2, atol=2e-2)
+    # without the GPU passes the norms stay
+    plain, _ = C.optimize_model(model, 99, [], False)
+    assert "SkipSimplifiedLayerNormalization" in [n["op_type"] for n in C.model_nodes(plain)]
