@@ -404,7 +404,10 @@ class MoeKernel final : public WithFallback {
       return;
     }
     const int64_t R = T * k;
-    const int tile_rows = ortb200_moe_tile_rows(R, static_cast<int>(E_local_));
+    int tile_rows = ortb200_moe_tile_rows(R, static_cast<int>(E_local_));
+    // the gated (two-accumulator) kernel stops at 128-token tiles; without a bias the 256-token path runs the gate
+    // and up projections as one plain GEMM followed by a streaming SwiGLU
+    if (dual_ && tile_rows == 256 && ctx.HasInput(3)) tile_rows = 128;
     const int max_tiles = ortb200_moe_max_tiles(R, static_cast<int>(E_local_), tile_rows);
     auto iopt = x.options().dtype(at::kInt);
     at::Tensor topk_idx = at::empty({T, k}, iopt), row_of = at::empty({T, k}, iopt);
@@ -453,7 +456,18 @@ class MoeKernel final : public WithFallback {
     g.dtype = dt;
     g.act = dual_ ? ORTB200_ACT_SWIGLU : ActOf(attrs_.activation);
     g.status = ctx.session()->StatusWord().data_ptr<int>();
-    CheckLaunch(ortb200_gemm_grouped(&g, ctx.cuda_stream()), "ortb200_gemm_grouped(fc1)");
+    if (dual_ && tile_rows == 256) {
+      at::Tensor gu = at::empty({R, 2 * I_}, x.options());
+      g.out = gu.data_ptr();
+      g.N = static_cast<int>(2 * I_);
+      g.dual_offset = 0;
+      g.act = ORTB200_ACT_NONE;
+      CheckLaunch(ortb200_gemm_grouped(&g, ctx.cuda_stream()), "ortb200_gemm_grouped(fc1|fc3)");
+      CheckLaunch(ortb200_swiglu(gu.data_ptr(), h.data_ptr(), R, static_cast<int>(I_), dt, ctx.cuda_stream()), "ortb200_swiglu");
+      ctx.session()->AddLaunches(1);
+    } else {
+      CheckLaunch(ortb200_gemm_grouped(&g, ctx.cuda_stream()), "ortb200_gemm_grouped(fc1)");
+    }
     at::Tensor y = at::empty({R, H_}, x.options());
     g.x = h.data_ptr(); g.w = w2_.data_ptr(); g.out = y.data_ptr(); g.bias = nullptr;
     g.N = static_cast<int>(H_); g.K = static_cast<int>(I_);

@@ -303,14 +303,21 @@ int LayerNormFusion(PassContext& c) {
   Pat d = Op("Sub", {V("x"), ReduceMeanOf(V("x"), "rm1")}, "d");
   Pat var = ReduceMeanOf(Op("Pow", {d, C(2.0)}), "rm2");
   Pat norm = Op("Div", {d, Op("Sqrt", {Op("Add", {var, K("eps")})})});
+  // the same without "+ eps": a half-precision export whose epsilon rounded to zero loses the Add to no-op elimination
+  Pat norm0 = Op("Div", {d, Op("Sqrt", {var})});
   Pat with_affine = Op("Add", {Op("Mul", {norm, K("gamma")}), K("beta")});
   Pat scale_only = Op("Mul", {norm, K("gamma")});
+  Pat with_affine0 = Op("Add", {Op("Mul", {norm0, K("gamma")}), K("beta")});
+  Pat scale_only0 = Op("Mul", {norm0, K("gamma")});
   for (Node* n : g.Nodes()) {
     if (!n->domain.empty() || (n->op_type != "Add" && n->op_type != "Mul")) continue;
-    for (int variant = 0; variant < 2; ++variant) {
+    for (int v4 = 0; v4 < 4; ++v4) {
+      const int variant = v4 & 1;
+      const bool no_eps = v4 >= 2;
       if ((variant == 0) != (n->op_type == "Add")) continue;
       Match m;
-      if (!MatchExpr(g, n->outputs[0], variant == 0 ? with_affine : scale_only, &m, /*through_casts=*/true)) continue;
+      const Pat& pat = variant == 0 ? (no_eps ? with_affine0 : with_affine) : (no_eps ? scale_only0 : scale_only);
+      if (!MatchExpr(g, n->outputs[0], pat, &m, /*through_casts=*/true)) continue;
       if (variant == 1 && g.NumConsumers(n->outputs[0]) == 1) {
         // leave "(..) * gamma" alone when an Add(beta) follows: the Add-rooted match will take it
         Node* cons = g.Consumers(n->outputs[0]).empty() ? nullptr : g.Consumers(n->outputs[0])[0];
@@ -321,8 +328,8 @@ int LayerNormFusion(PassContext& c) {
       }
       if (!IsClosed(g, m, n)) continue;
       if (!LastAxisOnly(g, m.nodes["rm1"], m.values["x"]) || !LastAxisOnly(g, m.nodes["rm2"], m.values["x"])) continue;
-      double eps;
-      if (!ScalarConst(g, m.values["eps"], &eps)) continue;
+      double eps = 0.0;
+      if (!no_eps && !ScalarConst(g, m.values["eps"], &eps)) continue;
       if (!IsConst1D(g, m.values["gamma"])) continue;
       std::vector<std::string> ins = {m.values["x"], m.values["gamma"]};
       if (variant == 0) {

@@ -37,6 +37,8 @@ struct SmallGemmParams {
 
 // Grouped GEMM over a device-side tile list (see ortb200_gemm_grouped).
 int launch_gemm_grouped(const ortb200_gemm_grouped_args* a, cudaStream_t stream);
+// The same on the persistent large-tile kernel (tile_rows 128 or 256).
+int launch_gemm_grouped_large(const ortb200_gemm_grouped_args* a, cudaStream_t stream);
 
 // bn in {16, 32, 64}.  Returns 0 or a negative launch error; reports the cluster size and pipeline depth used.
 int launch_gemm_smallm(const ortb200_gemm_args* a, int bn, cudaStream_t stream, int* cluster_out, int* stages_out);

@@ -58,6 +58,11 @@ struct GemmKernelParams {
   float* ws;
   unsigned int* counters;
   int* status;
+  // grouped mode (mixture of experts): the token tiles come from a device-side list built by the routing kernels
+  const int4* tile_info;   // {expert, first row, end row, -}; null = ordinary GEMM
+  const int* num_tiles;    // device scalar: token tiles in use
+  int tiles_n;             // weight-row tiles per expert
+  int w_rows_per_expert;
 };
 
 __device__ __forceinline__ float apply_act(int act, float v) {
@@ -101,12 +106,12 @@ struct GemmSmem {
 struct WorkRange {
   long long begin, end;
 };
-__device__ __forceinline__ WorkRange cta_range(const GemmKernelParams& p, int c) {
+__device__ __forceinline__ WorkRange cta_range(const GemmKernelParams& p, int c, long long tiles) {
   const long long G = gridDim.x;
   WorkRange r;
   if (p.tile_aligned) {
-    r.begin = (static_cast<long long>(c) * p.tiles / G) * p.num_kb;
-    r.end = (static_cast<long long>(c + 1) * p.tiles / G) * p.num_kb;
+    r.begin = (static_cast<long long>(c) * tiles / G) * p.num_kb;
+    r.end = (static_cast<long long>(c + 1) * tiles / G) * p.num_kb;
   } else {
     const long long U = static_cast<long long>(p.tiles) * p.num_kb;
     r.begin = static_cast<long long>(c) * U / G;
@@ -140,7 +145,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const WorkRange range = cta_range(p, blockIdx.x);
+  // grouped mode: the number of token tiles is only known on the device (and only after the routing kernels ran)
+  const bool grouped = p.tile_info != nullptr;
+  int tiles_m = p.tiles_m;
+  long long tiles_total = p.tiles;
+  if (grouped) {
+    pdl_wait_prior_grids();
+    tiles_m = *p.num_tiles;
+    tiles_total = static_cast<long long>(p.tiles_n) * tiles_m;
+  }
+  const WorkRange range = cta_range(p, blockIdx.x, tiles_total);
 
   if (threadIdx.x == 0) {
     tma_prefetch_desc(&tmap_w);
@@ -177,8 +191,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
       auto coords = [&](long long u, int* kb, int* n0, int* m0) {
         const int tile = static_cast<int>(u / p.num_kb);
         *kb = static_cast<int>(u % p.num_kb);
-        *n0 = (tile / p.tiles_m) * S::kTileRows;
-        *m0 = (tile % p.tiles_m) * BN;
+        *n0 = (tile / tiles_m) * S::kTileRows;
+        *m0 = (tile % tiles_m) * BN;
+        if (grouped) {
+          const int4 ti = p.tile_info[tile % tiles_m];
+          *n0 += ti.x * p.w_rows_per_expert;  // this expert's rows of the stacked weight matrix
+          *m0 = ti.y;
+        }
       };
       for (int i = 0; i < pre; ++i) {
         int kb, n0, m0;
@@ -275,7 +294,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
       const long long seg_end = tile_end < range.end ? tile_end : range.end;
       const bool whole = (u == tile_begin) && (seg_end == tile_end);
       const int buf = seg % NBUF;
-      const int n0 = (tile / p.tiles_m) * S::kTileRows, m0 = (tile % p.tiles_m) * BN;
+      int n0 = (tile / tiles_m) * S::kTileRows, m0 = (tile % tiles_m) * BN;
+      int m_end = p.M, bias0 = 0;
+      if (grouped) {
+        const int4 ti = p.tile_info[tile % tiles_m];
+        m0 = ti.y;
+        m_end = ti.z;
+        bias0 = ti.x * p.N;
+      }
       const uint32_t t_lane = tmem_base + buf * S::kBufCols + (static_cast<uint32_t>(q * 32) << 16);
       if (!mbar_wait(&tmem_full_bar[buf], (seg / NBUF) & 1)) {
         ok = false;
@@ -330,31 +356,37 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
           const int nrow0 = n0 + half * kBM;
           const int n = nrow0 + r;
           const float bias_v = (p.bias != nullptr && n < p.N)
-                                   ? (bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.bias)[n])
-                                           : __half2float(reinterpret_cast<const __half*>(p.bias)[n]))
+                                   ? (bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.bias)[bias0 + n])
+                                           : __half2float(reinterpret_cast<const __half*>(p.bias)[bias0 + n]))
                                    : 0.0f;
 #pragma unroll 1
           for (int pc = 0; pc < BN; pc += PASS) {
+            // A tensor-memory load issued while the MMAs of the next tile run takes on the order of a microsecond, so
+            // the loads of a whole group of columns go out back to back and are waited for once.
+            constexpr int GC = (DUAL ? 64 : 128) < PASS ? (DUAL ? 64 : 128) : PASS;
 #pragma unroll 1
-            for (int c = 0; c < PASS; c += LD) {
-              float v[LD];
-              float uu[LD];
-              if (LD == 32) {
-                tmem_ld_x32(t_lane + half * BN + pc + c, v);
-                if (DUAL) tmem_ld_x32(t_lane + BN + pc + c, uu);
-              } else {
-                tmem_ld_x16(t_lane + half * BN + pc + c, v);
-                if (DUAL) tmem_ld_x16(t_lane + BN + pc + c, uu);
+            for (int c = 0; c < PASS; c += GC) {
+              float v[GC];
+              float uu[DUAL ? GC : 1];
+#pragma unroll
+              for (int g4 = 0; g4 < GC / LD; ++g4) {
+                if (LD == 32) {
+                  tmem_ld_x32(t_lane + half * BN + pc + c + g4 * LD, v + g4 * LD);
+                  if (DUAL) tmem_ld_x32(t_lane + BN + pc + c + g4 * LD, uu + g4 * LD);
+                } else {
+                  tmem_ld_x16(t_lane + half * BN + pc + c + g4 * LD, v + g4 * LD);
+                  if (DUAL) tmem_ld_x16(t_lane + BN + pc + c + g4 * LD, uu + g4 * LD);
+                }
               }
               tmem_ld_wait();
 #pragma unroll
-              for (int j = 0; j < LD; ++j) {
+              for (int j = 0; j < GC; ++j) {
+                // no activation switch in this fully unrolled loop (it would be copied GC times): activations other
+                // than the gated one are applied on the way out, on the 16-bit value, as a separate op would
                 float y = v[j] * p.alpha + bias_v;
                 if (DUAL) {
                   const float g = y / (1.0f + __expf(-y));
                   y = g * (uu[j] * p.alpha);
-                } else {
-                  y = apply_act(p.act, y);
                 }
                 uint16_t bits;
                 if (bf16) {
@@ -377,27 +409,41 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
               const int row = idx >> 4, ch = idx & 15;
               const int m = m0 + pc + row;
               const int nn = nrow0 + ch * 8;
-              if (m >= p.M || nn >= p.N) continue;
+              if (m >= m_end || nn >= p.N) continue;
               const uint4 val = *reinterpret_cast<const uint4*>(stg + row * kBM + ch * 8);
               const long long o = static_cast<long long>(m) * p.ldo + nn;
+              const bool post_act = !DUAL && p.act != ORTB200_ACT_NONE;
               if (vec_ok && nn + 8 <= p.N) {
                 uint4 res = val;
-                if (p.residual != nullptr) {
-                  const uint4 rr = __ldg(reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(p.residual) + static_cast<long long>(m) * p.ldr + nn));
+                if (p.residual != nullptr || post_act) {
+                  uint4 rr = make_uint4(0u, 0u, 0u, 0u);
+                  if (p.residual != nullptr)
+                    rr = __ldg(reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(p.residual) + static_cast<long long>(m) * p.ldr + nn));
                   const uint32_t a4[4] = {val.x, val.y, val.z, val.w};
                   const uint32_t b4[4] = {rr.x, rr.y, rr.z, rr.w};
                   uint32_t o4[4];
 #pragma unroll
                   for (int e = 0; e < 4; ++e) {
+                    float lo, hi, rlo, rhi;
                     if (bf16) {
-                      const float lo = __uint_as_float(a4[e] << 16) + __uint_as_float(b4[e] << 16);
-                      const float hi = __uint_as_float(a4[e] & 0xffff0000u) + __uint_as_float(b4[e] & 0xffff0000u);
-                      const __nv_bfloat162 h2 = __floats2bfloat162_rn(lo, hi);
-                      o4[e] = *reinterpret_cast<const uint32_t*>(&h2);
+                      lo = __uint_as_float(a4[e] << 16); hi = __uint_as_float(a4[e] & 0xffff0000u);
+                      rlo = __uint_as_float(b4[e] << 16); rhi = __uint_as_float(b4[e] & 0xffff0000u);
                     } else {
                       const float2 fa = __half22float2(*reinterpret_cast<const __half2*>(&a4[e]));
                       const float2 fb = __half22float2(*reinterpret_cast<const __half2*>(&b4[e]));
-                      const __half2 h2 = __floats2half2_rn(fa.x + fb.x, fa.y + fb.y);
+                      lo = fa.x; hi = fa.y; rlo = fb.x; rhi = fb.y;
+                    }
+                    if (post_act) {
+                      lo = apply_act(p.act, lo);
+                      hi = apply_act(p.act, hi);
+                    }
+                    lo += rlo;
+                    hi += rhi;
+                    if (bf16) {
+                      const __nv_bfloat162 h2 = __floats2bfloat162_rn(lo, hi);
+                      o4[e] = *reinterpret_cast<const uint32_t*>(&h2);
+                    } else {
+                      const __half2 h2 = __floats2half2_rn(lo, hi);
                       o4[e] = *reinterpret_cast<const uint32_t*>(&h2);
                     }
                   }
@@ -408,6 +454,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
                 const uint16_t* sv = stg + row * kBM + ch * 8;
                 for (int e = 0; e < 8 && nn + e < p.N; ++e) {
                   float y = bf16 ? __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(sv + e)) : __half2float(*reinterpret_cast<const __half*>(sv + e));
+                  if (post_act) y = apply_act(p.act, y);
                   if (p.residual != nullptr) {
                     const long long ri = static_cast<long long>(m) * p.ldr + nn + e;
                     y += bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.residual)[ri]) : __half2float(reinterpret_cast<const __half*>(p.residual)[ri]);
@@ -691,6 +738,7 @@ extern "C" int ortb200_gemm(const ortb200_gemm_args* a, ortb200_stream_t stream_
   p.k_per_block = fp8 ? 2 * kBK : kBK;
   p.M = a->M; p.N = a->N; p.K = a->K;
   p.num_kb = num_kb; p.tiles = static_cast<int>(tiles); p.tiles_m = tiles_m;
+  p.tile_info = nullptr; p.num_tiles = nullptr; p.tiles_n = 0; p.w_rows_per_expert = 0;
   p.tile_aligned = tile_aligned ? 1 : 0; p.max_contrib = max_contrib;
   p.dual_offset = a->dual_offset; p.dtype = a->dtype; p.act = a->act; p.alpha = a->alpha;
   p.out = a->out; p.ldo = a->ldo; p.bias = a->bias; p.residual = a->residual; p.ldr = a->ldr;
@@ -727,3 +775,36 @@ extern "C" int ortb200_gemm(const ortb200_gemm_args* a, ortb200_stream_t stream_
   g_last_config = {bn, tile_aligned ? 1 : max_contrib, stages};
   return rc;
 }
+
+// Grouped GEMM on the persistent kernel: token tiles of 128 or 256 rows taken from the device-side tile list.
+namespace ortb200 {
+int launch_gemm_grouped_large(const ortb200_gemm_grouped_args* a, cudaStream_t stream) {
+  const bool dual = a->act == ORTB200_ACT_SWIGLU;
+  const int bn = a->tile_rows;
+  if ((bn != 128 && bn != 256) || (dual && bn != 128)) return -8;
+  const int num_kb = (a->K + kBK - 1) / kBK;
+  const int tiles_n = (a->N + kBM - 1) / kBM;
+  CUtensorMap tw, tx;
+  const CUtensorMapDataType dt = a->dtype == ORTB200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  const int64_t w_rows = static_cast<int64_t>(a->num_experts) * a->w_rows_per_expert;
+  if (make_tensor_map_2d(&tw, a->w, dt, 2, a->K, w_rows, static_cast<int64_t>(a->K) * 2, kBK, kBM) != 0) return -6;
+  if (make_tensor_map_2d(&tx, a->x, dt, 2, a->K, a->rows, static_cast<int64_t>(a->K) * 2, kBK, bn) != 0) return -6;
+  GemmKernelParams p;
+  p.M = a->rows; p.N = a->N; p.K = a->K;
+  p.num_kb = num_kb; p.tiles = 0; p.tiles_m = 0;
+  p.tile_aligned = 1; p.max_contrib = 1;
+  p.dual_offset = a->dual_offset; p.dtype = a->dtype; p.in_fp8 = 0; p.k_per_block = kBK; p.act = a->act; p.alpha = 1.0f;
+  p.out = a->out; p.ldo = a->N; p.bias = a->bias; p.residual = nullptr; p.ldr = 0;
+  p.counters = nullptr; p.ws = nullptr; p.status = a->status;
+  p.tile_info = static_cast<const int4*>(a->tile_info);
+  p.num_tiles = a->num_tiles;
+  p.tiles_n = tiles_n;
+  p.w_rows_per_expert = a->w_rows_per_expert;
+  const int grid = num_sms();
+  const bool pdl = a->use_pdl != 0;
+  if (dual) return launch_gemm<128, 4, true>(tw, tx, p, grid, stream, pdl);
+  if (bn == 128) return launch_gemm<128, 6, false>(tw, tx, p, grid, stream, pdl);
+  return launch_gemm<256, 4, false>(tw, tx, p, grid, stream, pdl);
+}
+}  // namespace ortb200
+

@@ -163,7 +163,10 @@ using namespace ortb200;
 
 extern "C" int ortb200_moe_tile_rows(int64_t rows, int experts) {
   const int64_t per = experts > 0 ? rows / experts : rows;
-  return per <= 16 ? 16 : (per <= 32 ? 32 : 64);
+  if (per <= 16) return 16;
+  if (per <= 32) return 32;
+  if (per <= 96) return 64;
+  return per <= 512 ? 128 : 256;  // prompt-sized batches: the large-tile persistent kernel
 }
 
 extern "C" int ortb200_moe_max_tiles(int64_t rows, int experts, int tile_rows) {
@@ -178,7 +181,7 @@ extern "C" int ortb200_moe_route(const ortb200_moe_route_args* a, ortb200_stream
   if (a->tokens <= 0 || a->E <= 0 || a->E > kMaxExperts || a->k <= 0 || a->k > kMaxTopK || a->k > a->E) return -2;
   if (a->expert_begin < 0 || a->expert_end > a->E || a->expert_end <= a->expert_begin) return -2;
   if ((a->H * 2) % 16 != 0 || ((reinterpret_cast<uintptr_t>(a->x) | reinterpret_cast<uintptr_t>(a->xp)) & 15)) return -3;
-  if (a->tile_rows != 16 && a->tile_rows != 32 && a->tile_rows != 64) return -2;
+  if (a->tile_rows != 16 && a->tile_rows != 32 && a->tile_rows != 64 && a->tile_rows != 128 && a->tile_rows != 256) return -2;
   const int E_local = a->expert_end - a->expert_begin;
   if (cudaMemsetAsync(a->counts, 0, sizeof(int) * E_local, stream) != cudaSuccess) return -11;
   const unsigned gblocks = static_cast<unsigned>((a->tokens + 3) / 4);

@@ -89,8 +89,9 @@ int ortb200_gemm(const ortb200_gemm_args* args, ortb200_stream_t stream);
 // Grouped GEMM (mixture of experts): rows of x are sorted by expert; a device-side tile list says which expert's
 // weights multiply which row range, so no count ever travels to the host:
 //   out[r, :] = act(x[r, :] @ w[e]^T + bias[e]) for first_row <= r < end_row of every tile {e, first_row, end_row, -}.
-// Tiles cover at most tile_rows rows each (tile_rows in {16, 32, 64}); the grid has max_tiles rows of CTAs and the
-// CTAs beyond *num_tiles leave at once.  w is [num_experts * w_rows_per_expert, K]; with act == SWIGLU the gate rows
+// Tiles cover at most tile_rows rows each.  tile_rows in {16, 32, 64}: one CTA per (weight tile, token tile), the
+// grid has max_tiles rows of CTAs and the CTAs beyond *num_tiles leave at once.  tile_rows in {128, 256}: the
+// persistent large-tile kernel walks the list (SWIGLU needs 128).  w is [num_experts * w_rows_per_expert, K]; with act == SWIGLU the gate rows
 // of expert e start at e * w_rows_per_expert and the up rows dual_offset rows later (N = rows of each half).
 typedef struct {
   const void* x;          // [rows, K]
