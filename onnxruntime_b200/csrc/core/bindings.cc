@@ -8,6 +8,7 @@
 #include "graph.h"
 #include "kernel.h"
 #include "session.h"
+#include "cuda_ops.h"
 #include "sharding_spec.h"
 
 namespace py = pybind11;
@@ -280,6 +281,9 @@ PYBIND11_MODULE(_core, m) {
     Guard([&] { RegisterPythonOp(domain, op, std::move(fn)); return 0; });
   });
   m.def("load_custom_op_library", [](const std::string& path) { Guard([&] { LoadCustomOpLibrary(path); return 0; }); });
+  m.def("nbits_build_blobs", [](const at::Tensor& B, const at::Tensor& scales, py::object zp, int64_t N, int64_t K, int64_t block) {
+    return Guard([&] { return NbitsBuildBlobs(B, scales, zp.is_none() ? at::Tensor() : zp.cast<at::Tensor>(), N, K, block); });
+  });
   m.def("model_roundtrip", [](py::bytes b) {
     std::string bytes = b;
     return Guard([&] {

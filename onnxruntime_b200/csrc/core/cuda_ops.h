@@ -15,6 +15,11 @@ void CheckLaunch(int rc, const char* what);
 at::Tensor LaunchGemm(OpKernelContext& ctx, const at::Tensor& x2d, const at::Tensor& w_nk, int64_t n_out,
                       int64_t dual_offset, const at::Tensor& bias, const at::Tensor& residual2d, int act, float alpha,
                       bool fused_allreduce = false, at::ScalarType out_type = at::ScalarType::Undefined, float rms_eps = 0.f);
+// MatMulNBits (4-bit) weights as the tile-blob array the decode GEMM expands in shared memory, and that GEMM (M <= 64).
+at::Tensor NbitsBuildBlobs(const at::Tensor& B, const at::Tensor& scales, const at::Tensor& zp_bytes, int64_t N, int64_t K,
+                           int64_t block);
+at::Tensor LaunchGemmQ4(OpKernelContext& ctx, const at::Tensor& x2d, const at::Tensor& blobs, int64_t n_out, const at::Tensor& bias,
+                        const at::Tensor& residual2d, bool fused_allreduce = false);
 // True when the fused GEMM + all-reduce kernel can take an [M, N] row-parallel product in this session.
 bool CanFuseAllReduce(OpKernelContext& ctx, int64_t M, int64_t N);
 

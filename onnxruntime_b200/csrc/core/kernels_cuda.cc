@@ -129,6 +129,70 @@ at::Tensor LaunchNormedGemm(Ctx& ctx, const at::Tensor& x2d, const at::Tensor& w
   return LaunchGemm(ctx, x2d, w_nk, n_out, dual_offset, bias, residual2d, act, alpha, false, at::ScalarType::Undefined, rms_eps);
 }
 
+// MatMulNBits weights -> the tile-blob array of the in-kernel expansion (layout: ortb200_gemm_args, in_dtype Q4).
+// B uint8 [N, n_blocks, block / 2] (4-bit, low nibble = even k), scales [N, n_blocks], zp_bytes uint8 [N, n_blocks]
+// (one byte per block) or undefined for the implicit 8.  All on the GPU.
+at::Tensor NbitsBuildBlobs(const at::Tensor& B, const at::Tensor& scales, const at::Tensor& zp_bytes, int64_t N, int64_t K,
+                           int64_t block) {
+  ORTB_ENFORCE_ARG(B.is_cuda() && K % 64 == 0 && block >= 32 && (block & (block - 1)) == 0, "NbitsBuildBlobs: unsupported layout");
+  const int64_t num_kb = K / 64, Np = (N + 127) / 128 * 128, nb = (K + block - 1) / block;
+  at::Tensor src = B.contiguous().reshape({N, K / 2});
+  at::Tensor nib = at::empty_like(src);
+  CheckLaunch(ortb200_nbits_prepack(src.data_ptr(), nib.data_ptr(), N * (K / 2), at::cuda::getCurrentCUDAStream().stream()),
+              "ortb200_nbits_prepack");
+  auto pad_rows = [&](const at::Tensor& t) {
+    if (Np == N) return t;
+    std::vector<int64_t> shape = t.sizes().vec();
+    shape[0] = Np - N;
+    return at::cat({t, at::zeros(shape, t.options())}, 0);
+  };
+  // nibbles: [Np, num_kb, 32] -> [tiles, num_kb, 128, 32]
+  at::Tensor w = pad_rows(nib).reshape({Np / 128, 128, num_kb, 32}).permute({0, 2, 1, 3}).reshape({Np / 128, num_kb, 4096});
+  // scales and zero points at 32-element granularity (two per k-block), whatever the block size
+  const int64_t rep = block / 32;
+  at::Tensor s32 = scales.reshape({N, nb}).repeat_interleave(rep, 1).narrow(1, 0, K / 32).contiguous();
+  at::Tensor sb = pad_rows(s32).reshape({Np / 128, 128, num_kb, 2}).permute({0, 2, 1, 3}).contiguous().view(at::kByte).reshape({Np / 128, num_kb, 512});
+  at::Tensor z32 = zp_bytes.defined() ? zp_bytes.reshape({N, nb}).repeat_interleave(rep, 1).narrow(1, 0, K / 32).contiguous()
+                                      : at::full({N, K / 32}, 8, B.options());
+  at::Tensor zb = pad_rows(z32).reshape({Np / 128, 128, num_kb, 2}).permute({0, 2, 1, 3}).reshape({Np / 128, num_kb, 256});
+  return at::cat({w, sb, zb}, 2).contiguous();
+}
+
+// out[M, N] = x[M, K] @ dequant(blobs)[N, K]^T + bias with the 4-bit weights expanded inside the kernel (M <= 64).
+at::Tensor LaunchGemmQ4(Ctx& ctx, const at::Tensor& x2d, const at::Tensor& blobs, int64_t n_out, const at::Tensor& bias,
+                        const at::Tensor& residual2d, bool fused_allreduce) {
+  InferenceSession* s = ctx.session();
+  const int64_t M = x2d.size(0), K = x2d.size(1);
+  at::Tensor out = at::empty({M, n_out}, x2d.options());
+  if (M == 0) return out;
+  ortb200_gemm_args a{};
+  a.x = x2d.data_ptr();
+  a.w = blobs.data_ptr();
+  a.out = out.data_ptr();
+  a.bias = bias.defined() ? bias.data_ptr() : nullptr;
+  a.residual = residual2d.defined() ? residual2d.data_ptr() : nullptr;
+  a.ldo = n_out;
+  a.ldr = residual2d.defined() ? residual2d.stride(0) : 0;
+  a.M = static_cast<int>(M); a.N = static_cast<int>(n_out); a.K = static_cast<int>(K);
+  a.w_rows = static_cast<int>(blobs.size(0) * 128);
+  a.dtype = DtypeCode(x2d.scalar_type());
+  a.in_dtype = ORTB200_Q4;
+  a.act = ORTB200_ACT_NONE;
+  a.alpha = 1.f;
+  a.status = s->StatusWord().data_ptr<int>();
+  a.use_pdl = s->config().Get("ortb200.pdl", "0") == "1" ? 1 : 0;
+  a.world = 1;
+  if (fused_allreduce) {
+    a.world = s->world_size;
+    a.rank = s->rank;
+    for (int i = 0; i < s->world_size && i < 8; ++i) a.peers[i] = s->symm_peers[i];
+    a.symm_bytes = s->symm_bytes;
+  }
+  CheckLaunch(ortb200_gemm(&a, ctx.cuda_stream()), "ortb200_gemm(q4)");
+  s->AddLaunches(1);
+  return out;
+}
+
 bool CanFuseAllReduce(OpKernelContext& ctx, int64_t M, int64_t N) {
   InferenceSession* s = ctx.session();
   if (!s || s->world_size <= 1 || s->world_size > 8) return false;

@@ -53,9 +53,38 @@ class MatMulNBitsKernel final : public WithFallback {
     N_ = n.attr_i("N", 0);
     bits_ = n.attr_i("bits", 4);
     block_ = n.attr_i("block_size", 32);
+    // decode path: re-arrange the nibbles once for the in-kernel expansion (4-bit, block >= 32, K % 64 == 0,
+    // constant weights, integer zero points)
+    const at::Tensor* B = info.constant_input(1);
+    const at::Tensor* sc = info.constant_input(2);
+    const bool has_zp = n.inputs.size() > 3 && !n.inputs[3].empty();
+    const at::Tensor* zp = has_zp ? info.constant_input(3) : nullptr;
+    if (B && sc && B->is_cuda() && bits_ == 4 && block_ >= 32 && (block_ & (block_ - 1)) == 0 && K_ % 64 == 0 &&
+        HalfType(sc->scalar_type()) && (!has_zp || (zp && zp->scalar_type() == at::kByte)) &&
+        !(n.inputs.size() > 4 && !n.inputs[4].empty())) {
+      at::Tensor zp_bytes;
+      if (zp) {
+        // packed nibbles [N, ceil(nb / 2)] -> one byte per block
+        const int64_t nb = (K_ + block_ - 1) / block_;
+        at::Tensor z = zp->reshape({N_, -1}).to(at::kInt);
+        zp_bytes = at::stack({at::bitwise_and(z, 0xF), at::bitwise_and(at::bitwise_right_shift(z, 4), 0xF)}, -1)
+                       .reshape({N_, -1}).narrow(1, 0, nb).to(at::kByte).contiguous();
+      }
+      packed_ = NbitsBuildBlobs(*B, *sc, zp_bytes, N_, K_, block_);
+      scales_ = *sc;
+    }
   }
   void Compute(Ctx& ctx) const override {
     const at::Tensor& a = ctx.RequiredInput(0);
+    if (packed_.defined() && a.scalar_type() == scales_.scalar_type() && a.numel() / K_ <= 64) {
+      at::Tensor x2 = a.reshape({-1, K_}).contiguous();
+      at::Tensor bias = ctx.HasInput(5) ? ctx.Input(5) : at::Tensor();
+      at::Tensor y = LaunchGemmQ4(ctx, x2, packed_, N_, bias, at::Tensor());
+      std::vector<int64_t> shape = a.sizes().vec();
+      shape.back() = N_;
+      ctx.SetOutput(0, y.reshape(shape));
+      return;
+    }
     const at::Tensor& B = ctx.RequiredInput(1);
     const at::Tensor& scales = ctx.RequiredInput(2);
     at::Tensor zp = ctx.HasInput(3) ? ctx.Input(3) : at::Tensor();
@@ -85,6 +114,7 @@ class MatMulNBitsKernel final : public WithFallback {
 
  private:
   int64_t K_ = 0, N_ = 0, bits_ = 4, block_ = 32;
+  at::Tensor packed_, scales_;
 };
 
 // ---------------------------------------------------------------------------------------------------------------

@@ -33,6 +33,8 @@ struct SmallGemmParams {
   // ---- fused RMS normalisation of the activations (rms_eps > 0): out = (W x) / rms(x) with gamma folded into W
   float rms_eps;
   const void* x_rows;        // the activation matrix [M, K] itself (read with plain loads for the row statistics)
+  // ---- packed 4-bit weights (NBITS kernels): per (weight tile, k-block) one contiguous 4864-byte blob
+  const void* nbits_blob;
 };
 
 // Grouped GEMM over a device-side tile list (see ortb200_gemm_grouped).

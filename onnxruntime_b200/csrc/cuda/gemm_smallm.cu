@@ -77,26 +77,73 @@ __device__ __forceinline__ float act_apply(int act, float v) {
   }
 }
 
-template <int BN, int STAGES, bool DUAL>
+// NBITS: the weight tile arrives as packed 4-bit values (32 bytes per row and k-block, nibbles pre-arranged by
+// ortb200_nbits_prepack) and the four epilogue warps expand it to a swizzled 16-bit MMA operand in one of two
+// dequantisation buffers while the next stages are in flight.
+template <int BN, int STAGES, bool DUAL, bool NBITS = false>
 struct SmallSmem {
-  static constexpr int kABytes = kBM * kBK * 2;
+  // NBITS: one tile blob per k-block = 4096 bytes of nibbles + 128 x 2 scales + 128 x 2 zero points (4864 bytes,
+  // laid out contiguously in global memory by the prepack step), padded to 5 KiB so the X tile stays 1 KiB aligned
+  static constexpr int kBlobBytes = 4096 + 512 + 256;
+  static constexpr int kABytes = NBITS ? 5120 : kBM * kBK * 2;
   static constexpr int kBBytes = BN * kBK * 2;
   static constexpr int kStageBytes = kABytes * (DUAL ? 2 : 1) + kBBytes;
   static constexpr int kCols = (DUAL ? 2 : 1) * BN;
   static constexpr int kPartOffset = 0;  // float part[kCols][128] re-uses the pipeline stages once the main loop is done
   static constexpr int kPartBytes = kCols * kBM * 4;
-  static constexpr int kBarOffset = kStageBytes * STAGES;
+  static constexpr int kDqOffset = kStageBytes * STAGES;
+  static constexpr int kDqTileBytes = kBM * kBK * 2;
+  static constexpr int kNumDq = 4;  // expansion buffers: the expansion runs up to four k-blocks ahead of the MMA
+  static constexpr int kDqBytes = NBITS ? kNumDq * kDqTileBytes : 0;
+  static constexpr int kBarOffset = kDqOffset + kDqBytes;
   static_assert(kPartBytes <= kStageBytes * STAGES, "partial tile must fit in the drained pipeline stages");
-  static constexpr int kRstdOffset = kBarOffset + 8 * (2 * STAGES + 1) + 16;  // float rstd[64] (fused RMS norm)
+  static_assert(!NBITS || (kDqOffset % 1024 == 0 && kStageBytes % 1024 == 0), "swizzled tiles need 1 KiB alignment");
+  static_assert(!(NBITS && DUAL), "the gated epilogue is not combined with packed weights");
+  static constexpr int kRstdOffset = kBarOffset + 8 * (2 * STAGES + 1 + 8) + 16;  // float rstd[64] (fused RMS norm)
   static constexpr int kTotal = kRstdOffset + 64 * 4 + 1024;
   static constexpr int kTmemCols = kCols < 32 ? 32 : kCols;
 };
 
-template <int BN, int STAGES, bool DUAL>
+// ---- 4-bit expansion helpers.  A prepacked 32-bit word holds 8 weights: bits [4i, 4i+4) = weight 2i, bits
+// [16+4i, 16+4i+4) = weight 2i+1, so (w >> 4i) & 0x000F000F is the pair (2i, 2i+1) in the two halves of a register.
+// OR-ing the exponent pattern of 128 (bf16) / 1024 (fp16) turns the pair into exact small numbers without a convert.
+template <typename T2>
+struct Nib {};
+template <>
+struct Nib<__nv_bfloat162> {
+  static constexpr uint32_t kMagic = 0x43004300u;  // 128.0 | 128.0
+  static constexpr float kBase = 128.0f;
+  __device__ static __nv_bfloat162 bcast(float v) { return __float2bfloat162_rn(v); }
+};
+template <>
+struct Nib<__half2> {
+  static constexpr uint32_t kMagic = 0x64006400u;  // 1024.0 | 1024.0
+  static constexpr float kBase = 1024.0f;
+  __device__ static __half2 bcast(float v) { return __float2half2_rn(v); }
+};
+
+// 32 packed weights (four prepacked words) of one quantisation block -> four 16-byte chunks of 8 values each
+template <typename T2>
+__device__ __forceinline__ void expand_words(const uint32_t w[4], T2 offset, T2 scale, uint4 out[4]) {
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    uint32_t r[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint32_t bits = ((w[j] >> (4 * i)) & 0x000F000Fu) | Nib<T2>::kMagic;
+      T2 v = *reinterpret_cast<const T2*>(&bits);
+      v = __hmul2(__hsub2(v, offset), scale);  // (q - zp) exactly, then one rounding in the product
+      r[i] = *reinterpret_cast<const uint32_t*>(&v);
+    }
+    out[j] = make_uint4(r[0], r[1], r[2], r[3]);
+  }
+}
+
+template <int BN, int STAGES, bool DUAL, bool NBITS = false>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
                    const SmallGemmParams p) {
-  using S = SmallSmem<BN, STAGES, DUAL>;
+  using S = SmallSmem<BN, STAGES, DUAL, NBITS>;
   static_assert((S::kTmemCols & (S::kTmemCols - 1)) == 0, "TMEM columns must be a power of two");
   extern __shared__ uint8_t smem_raw[];
   // every CTA of the cluster applies the same rounding, so shared-memory offsets agree across the cluster
@@ -105,7 +152,10 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + S::kBarOffset);
   uint64_t* empty_bar = full_bar + STAGES;
   uint64_t* tmem_full_bar = empty_bar + STAGES;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_full_bar + 1);
+  constexpr int NDQ = S::kNumDq;
+  uint64_t* dq_full_bar = tmem_full_bar + 1;     // [NDQ] dequantised tile ready (128 arrivals)
+  uint64_t* dq_empty_bar = dq_full_bar + NDQ;    // [NDQ] MMAs reading the tile have finished
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(dq_empty_bar + NDQ);
   float* s_rstd = reinterpret_cast<float*>(smem + S::kRstdOffset);
 
   const int warp = threadIdx.x >> 5;
@@ -139,6 +189,10 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
       mbar_init(&empty_bar[s], 1);
     }
     mbar_init(tmem_full_bar, 1);
+    for (int d = 0; d < NDQ; ++d) {
+      mbar_init(&dq_full_bar[d], 128);
+      mbar_init(&dq_empty_bar[d], 1);
+    }
     fence_mbar_init();
   }
   if (warp == 1) {
@@ -159,8 +213,9 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
       const int pre = nkb < STAGES ? nkb : STAGES;
       for (int i = 0; i < pre; ++i) {
         uint8_t* st = smem + i * S::kStageBytes;
-        mbar_expect_tx(&full_bar[i], S::kStageBytes);
-        tma_load_2d_hint(st, &tmap_w, &full_bar[i], (kb_begin + i) * kBK, w_row0 + n0, pol_w);
+        mbar_expect_tx(&full_bar[i], NBITS ? S::kBlobBytes + S::kBBytes : S::kStageBytes);
+        if (NBITS) bulk_load(st, static_cast<const uint8_t*>(p.nbits_blob) + (static_cast<long long>(blockIdx.x / C) * p.num_kb + kb_begin + i) * S::kBlobBytes, S::kBlobBytes, &full_bar[i]);
+        else tma_load_2d_hint(st, &tmap_w, &full_bar[i], (kb_begin + i) * kBK, w_row0 + n0, pol_w);
         if (DUAL) tma_load_2d_hint(st + S::kABytes, &tmap_w, &full_bar[i], (kb_begin + i) * kBK, w_row0 + n0 + p.dual_offset, pol_w);
       }
       pdl_wait_prior_grids();
@@ -175,8 +230,9 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
           break;
         }
         uint8_t* st = smem + s * S::kStageBytes;
-        mbar_expect_tx(&full_bar[s], S::kStageBytes);
-        tma_load_2d_hint(st, &tmap_w, &full_bar[s], (kb_begin + i) * kBK, w_row0 + n0, pol_w);
+        mbar_expect_tx(&full_bar[s], NBITS ? S::kBlobBytes + S::kBBytes : S::kStageBytes);
+        if (NBITS) bulk_load(st, static_cast<const uint8_t*>(p.nbits_blob) + (static_cast<long long>(blockIdx.x / C) * p.num_kb + kb_begin + i) * S::kBlobBytes, S::kBlobBytes, &full_bar[s]);
+        else tma_load_2d_hint(st, &tmap_w, &full_bar[s], (kb_begin + i) * kBK, w_row0 + n0, pol_w);
         if (DUAL) tma_load_2d_hint(st + S::kABytes, &tmap_w, &full_bar[s], (kb_begin + i) * kBK, w_row0 + n0 + p.dual_offset, pol_w);
         tma_load_2d(st + S::kABytes * (DUAL ? 2 : 1), &tmap_x, &full_bar[s], (kb_begin + i) * kBK, m0);
       }
@@ -190,9 +246,14 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
           if (p.status) atomicExch(p.status, kStatusTimeoutMma);
           break;
         }
+        if (NBITS && !mbar_wait(&dq_full_bar[i % NDQ], (i / NDQ) & 1)) {
+          if (p.status) atomicExch(p.status, kStatusTimeoutMma);
+          break;
+        }
         tcgen05_fence_after();
-        const uint32_t a_addr = smem_u32(smem + s * S::kStageBytes);
-        const uint32_t b_addr = a_addr + S::kABytes * (DUAL ? 2 : 1);
+        const uint32_t stage_addr = smem_u32(smem + s * S::kStageBytes);
+        const uint32_t a_addr = NBITS ? smem_u32(smem + S::kDqOffset + (i % NDQ) * S::kDqTileBytes) : stage_addr;
+        const uint32_t b_addr = stage_addr + S::kABytes * (DUAL ? 2 : 1);
         const uint64_t adesc = umma_desc_sw128(a_addr);
         const uint64_t bdesc = umma_desc_sw128(b_addr);
 #pragma unroll
@@ -203,6 +264,7 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
           for (int k = 0; k < kBK / 16; ++k) umma_f16(tmem_base + BN, a2desc + 2 * k, bdesc + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
         }
         umma_commit(&empty_bar[s]);
+        if (NBITS) umma_commit(&dq_empty_bar[i % NDQ]);
       }
       umma_commit(tmem_full_bar);  // also on the failure path, so the epilogue never waits for nothing
     }
@@ -211,6 +273,58 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
     const int q = warp & 3;
     const int r = q * 32 + lane;
     const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+    if (NBITS) {
+      // ---- weight expansion: thread r owns weight row r of the tile.  Per k-block it reads 32 packed bytes, two
+      // scales and two zero points, and writes one 128-byte row of the swizzled MMA operand.
+      bool dq_ok = true;
+      // one k-block: wait for the packed tile and a free expansion buffer, expand row r, publish
+      auto expand_kblock = [&](int i) {
+        const int s = i % STAGES, d = i % NDQ;
+        if (dq_ok && !mbar_wait(&full_bar[s], (i / STAGES) & 1)) dq_ok = false;
+        if (dq_ok && i >= NDQ && !mbar_wait(&dq_empty_bar[d], ((i / NDQ) - 1) & 1)) dq_ok = false;
+        if (dq_ok) {
+          const uint8_t* blob = smem + s * S::kStageBytes;
+          const uint4* src = reinterpret_cast<const uint4*>(blob + r * 32);
+          const uint4 p0 = src[0], p1 = src[1];
+          // the row's two scales and two zero points travel in the same blob as its nibbles
+          const uint32_t sw = *reinterpret_cast<const uint32_t*>(blob + 4096 + r * 4);
+          const uint32_t zw = *reinterpret_cast<const uint16_t*>(blob + 4608 + r * 2);
+          float s0, s1;
+          if (p.dtype == ORTB200_BF16) {
+            s0 = __uint_as_float(sw << 16);
+            s1 = __uint_as_float(sw & 0xffff0000u);
+          } else {
+            s0 = __half2float(__ushort_as_half(static_cast<unsigned short>(sw & 0xffffu)));
+            s1 = __half2float(__ushort_as_half(static_cast<unsigned short>(sw >> 16)));
+          }
+          const float z0 = static_cast<float>(zw & 0xffu), z1 = static_cast<float>(zw >> 8);
+          const uint32_t w0[4] = {p0.x, p0.y, p0.z, p0.w};
+          const uint32_t w1[4] = {p1.x, p1.y, p1.z, p1.w};
+          uint4 o0[4], o1[4];
+          if (p.dtype == ORTB200_BF16) {
+            using T2 = __nv_bfloat162;
+            expand_words<T2>(w0, Nib<T2>::bcast(Nib<T2>::kBase + z0), Nib<T2>::bcast(s0), o0);
+            expand_words<T2>(w1, Nib<T2>::bcast(Nib<T2>::kBase + z1), Nib<T2>::bcast(s1), o1);
+          } else {
+            using T2 = __half2;
+            expand_words<T2>(w0, Nib<T2>::bcast(Nib<T2>::kBase + z0), Nib<T2>::bcast(s0), o0);
+            expand_words<T2>(w1, Nib<T2>::bcast(Nib<T2>::kBase + z1), Nib<T2>::bcast(s1), o1);
+          }
+          // 128-byte swizzle: 16-byte chunk c of row r lives at chunk position c ^ (r & 7)
+          uint8_t* dst = smem + S::kDqOffset + d * S::kDqTileBytes + r * 128;
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            *reinterpret_cast<uint4*>(dst + ((c ^ (r & 7)) << 4)) = o0[c];
+            *reinterpret_cast<uint4*>(dst + (((4 + c) ^ (r & 7)) << 4)) = o1[c];
+          }
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy stores -> visible to the MMA
+        }
+        mbar_arrive(&dq_full_bar[d]);  // also on the failure path: the MMA warp must not wait for nothing
+      };
+#pragma unroll 1
+      for (int i = 0; i < nkb; ++i) expand_kblock(i);
+      if (!dq_ok && p.status) atomicExch(p.status, kStatusTimeoutEpilogue);
+    }
     if (p.rms_eps > 0.f) {
       // Fused RMS normalisation: the weights carry gamma, so only 1 / rms(x[m, :]) is missing, and it is a per-token
       // factor that commutes with the GEMM.  These warps are idle while the weights stream, so they read the token
@@ -344,32 +458,62 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
       const unsigned long long* stage_local =
           reinterpret_cast<const unsigned long long*>(static_cast<const uint8_t*>(p.peers[p.rank]) + p.staging_offset) + stage_base;
       bool timed_out = false;
+      // Two token columns per round: the loads of all source ranks go out together, so a round costs about one
+      // memory round trip instead of one per (column, rank); words that have not arrived yet are re-read together.
+      constexpr int CB = 2;
 #pragma unroll 1
-      for (int jj = 0; jj < cols_per; ++jj) {
-        const int m = m0 + j_begin + jj;
-        if (!(n_ok && m < m_end)) continue;
-        float y = 0.f;
-        for (int s = 0; s < p.world; ++s) {  // fixed order: every rank adds in the same order and gets the same bits
-          const unsigned long long* src = stage_local + static_cast<long long>(s) * p.slot_elems + static_cast<long long>(m) * p.ldo + n;
-          unsigned long long w = ld_packed_sys(src);
-          unsigned int spins = 0;
-          while (static_cast<unsigned int>(w >> 32) != epoch && !timed_out) {
-            if (++spins > kPeerSpinLimit) {
-              timed_out = true;
-              break;
-            }
-            __nanosleep(32);
-            w = ld_packed_sys(src);
+      for (int jj0 = 0; jj0 < cols_per; jj0 += CB) {
+        unsigned long long w[CB][8];
+        const unsigned long long* src[CB];
+        bool need[CB];
+        float resv[CB];
+#pragma unroll
+        for (int cb = 0; cb < CB; ++cb) {
+          const int m = m0 + j_begin + jj0 + cb;
+          need[cb] = (jj0 + cb < cols_per) && n_ok && m < m_end;
+          src[cb] = stage_local + static_cast<long long>(m) * p.ldo + n;
+          resv[cb] = 0.f;
+#pragma unroll
+          for (int sr = 0; sr < 8; ++sr)
+            w[cb][sr] = (need[cb] && sr < p.world) ? ld_packed_sys(src[cb] + static_cast<long long>(sr) * p.slot_elems)
+                                                   : (static_cast<unsigned long long>(epoch) << 32);
+          if (need[cb] && p.residual) {
+            const long long ri = static_cast<long long>(m) * p.ldr + n;
+            resv[cb] = p.dtype == ORTB200_BF16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.residual)[ri])
+                                               : __half2float(reinterpret_cast<const __half*>(p.residual)[ri]);
           }
-          y += __uint_as_float(static_cast<unsigned int>(w));
         }
-        y = act_apply(p.act, y + bias_v);
-        if (p.dtype == ORTB200_BF16) {
-          if (p.residual) y += __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.residual)[m * p.ldr + n]);
-          reinterpret_cast<__nv_bfloat16*>(p.out)[m * p.ldo + n] = __float2bfloat16_rn(y);
-        } else {
-          if (p.residual) y += __half2float(reinterpret_cast<const __half*>(p.residual)[m * p.ldr + n]);
-          reinterpret_cast<__half*>(p.out)[m * p.ldo + n] = __float2half_rn(y);
+        unsigned int spins = 0;
+        while (!timed_out) {
+          bool all = true;
+#pragma unroll
+          for (int cb = 0; cb < CB; ++cb)
+#pragma unroll
+            for (int sr = 0; sr < 8; ++sr) all = all && (static_cast<unsigned int>(w[cb][sr] >> 32) == epoch);
+          if (all) break;
+          if (++spins > kPeerSpinLimit) {
+            timed_out = true;
+            break;
+          }
+          __nanosleep(32);
+#pragma unroll
+          for (int cb = 0; cb < CB; ++cb)
+#pragma unroll
+            for (int sr = 0; sr < 8; ++sr)
+              if (static_cast<unsigned int>(w[cb][sr] >> 32) != epoch)
+                w[cb][sr] = ld_packed_sys(src[cb] + static_cast<long long>(sr) * p.slot_elems);
+        }
+#pragma unroll
+        for (int cb = 0; cb < CB; ++cb) {
+          if (!need[cb]) continue;
+          const int m = m0 + j_begin + jj0 + cb;
+          float y = 0.f;
+#pragma unroll
+          for (int sr = 0; sr < 8; ++sr)  // fixed order: every rank adds in the same order and gets the same bits
+            if (sr < p.world) y += __uint_as_float(static_cast<unsigned int>(w[cb][sr]));
+          y = act_apply(p.act, y + bias_v) + resv[cb];
+          if (p.dtype == ORTB200_BF16) reinterpret_cast<__nv_bfloat16*>(p.out)[m * p.ldo + n] = __float2bfloat16_rn(y);
+          else reinterpret_cast<__half*>(p.out)[m * p.ldo + n] = __float2half_rn(y);
         }
       }
       if (timed_out && p.status) atomicExch(p.status, kStatusTimeoutPeer);
@@ -396,12 +540,12 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
   }
 }
 
-template <int BN, int STAGES, bool DUAL>
+template <int BN, int STAGES, bool DUAL, bool NBITS = false>
 int launch_small(const CUtensorMap& tw, const CUtensorMap& tx, const SmallGemmParams& p, dim3 grid, cudaStream_t stream,
                  bool use_pdl) {
-  using S = SmallSmem<BN, STAGES, DUAL>;
+  using S = SmallSmem<BN, STAGES, DUAL, NBITS>;
   static_assert(S::kTotal <= 113 * 1024, "two CTAs per SM must fit");
-  auto kern = gemm_smallm_kernel<BN, STAGES, DUAL>;
+  auto kern = gemm_smallm_kernel<BN, STAGES, DUAL, NBITS>;
   static bool attr_set = false;
   if (!attr_set) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal) != cudaSuccess) return -10;
@@ -453,9 +597,17 @@ int launch_gemm_smallm(const ortb200_gemm_args* a, int bn, cudaStream_t stream, 
   const int cluster = pick_cluster(tiles_n * tiles_m, num_kb, bn, a->force_splits);
   CUtensorMap tw, tx;
   const CUtensorMapDataType dt = a->dtype == ORTB200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-  if (make_tensor_map_2d(&tw, a->w, dt, 2, a->K, a->w_rows, static_cast<int64_t>(a->K) * 2, kBK, kBM) != 0) return -6;
+  const bool nbits = a->in_dtype == ORTB200_Q4;
+  if (nbits) {
+    // a->w is the tile-blob array of ortb200_nbits_blob_bytes(N, K) bytes: no tensor map, plain bulk copies
+    if (dual || a->K % 64 != 0 || a->rms_eps > 0.f) return -15;
+    tw = CUtensorMap{};
+  } else if (make_tensor_map_2d(&tw, a->w, dt, 2, a->K, a->w_rows, static_cast<int64_t>(a->K) * 2, kBK, kBM) != 0) {
+    return -6;
+  }
   if (make_tensor_map_2d(&tx, a->x, dt, 2, a->K, a->M, static_cast<int64_t>(a->K) * 2, kBK, bn) != 0) return -6;
   SmallGemmParams p;
+  p.nbits_blob = nbits ? a->w : nullptr;
   p.M = a->M; p.N = a->N; p.K = a->K; p.num_kb = num_kb; p.cluster = cluster; p.dual_offset = a->dual_offset;
   p.dtype = a->dtype; p.act = a->act; p.alpha = a->alpha; p.out = a->out; p.ldo = a->ldo; p.bias = a->bias;
   p.residual = a->residual; p.ldr = a->ldr; p.status = a->status;
@@ -480,6 +632,14 @@ int launch_gemm_smallm(const ortb200_gemm_args* a, int bn, cudaStream_t stream, 
   dim3 grid(tiles_n * cluster, tiles_m, 1);
   const bool pdl = a->use_pdl != 0;
   *cluster_out = cluster;
+  if (nbits) {
+    switch (bn) {
+      case 16: *stages_out = 6; return launch_small<16, 6, false, true>(tw, tx, p, grid, stream, pdl);
+      case 32: *stages_out = 4; return launch_small<32, 4, false, true>(tw, tx, p, grid, stream, pdl);
+      case 64: *stages_out = 3; return launch_small<64, 3, false, true>(tw, tx, p, grid, stream, pdl);
+      default: return -8;
+    }
+  }
   switch (bn) {
     case 16:
       *stages_out = dual ? 3 : 5;
@@ -512,6 +672,7 @@ int launch_gemm_grouped(const ortb200_gemm_grouped_args* a, cudaStream_t stream)
   p.world = 1; p.rank = 0; p.staging_offset = 0; p.slot_elems = 0; p.epoch = nullptr; p.done = nullptr;
   for (int i = 0; i < 8; ++i) p.peers[i] = nullptr;
   p.rms_eps = 0.f; p.x_rows = nullptr;
+  p.nbits_blob = nullptr;
   p.tile_info = static_cast<const int4*>(a->tile_info);
   p.num_tiles = a->num_tiles;
   p.w_rows_per_expert = a->w_rows_per_expert;

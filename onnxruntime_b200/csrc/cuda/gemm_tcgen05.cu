@@ -692,13 +692,15 @@ extern "C" int ortb200_gemm(const ortb200_gemm_args* a, ortb200_stream_t stream_
   if (!a || !a->x || !a->w || !a->out) return -1;
   if (a->M <= 0 || a->N <= 0 || a->K <= 0) return -1;
   const bool fp8 = a->in_dtype == ORTB200_F8E4M3;
-  if (a->in_dtype != 0 && !fp8 && a->in_dtype != a->dtype) return -4;
+  const bool q4 = a->in_dtype == ORTB200_Q4;
+  if (a->in_dtype != 0 && !fp8 && !q4 && a->in_dtype != a->dtype) return -4;
   if (a->K % (fp8 ? 16 : 8) != 0) return -2;                     // TMA row pitch must be a multiple of 16 bytes
   if ((reinterpret_cast<uintptr_t>(a->x) & 15) || (reinterpret_cast<uintptr_t>(a->w) & 15)) return -3;
   if (a->dtype != ORTB200_F16 && a->dtype != ORTB200_BF16) return -4;
   const bool dual = a->act == ORTB200_ACT_SWIGLU;
   if (dual && (a->dual_offset <= 0 || a->w_rows < a->dual_offset + a->N)) return -5;
   if (!dual && a->w_rows < a->N) return -5;
+  if (q4 && (a->force_bn ? a->force_bn : pick_bn(a->M)) > 64) return -15;  // packed weights: decode-shaped problems only
 
   {
     // decode-shaped problems: non-persistent kernel with the split-K reduction inside a cluster

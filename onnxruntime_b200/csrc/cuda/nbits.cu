@@ -73,10 +73,35 @@ __global__ void __launch_bounds__(256) nbits_dequant_kernel(const uint8_t* __res
   pdl_launch_dependents();
 }
 
+__global__ void __launch_bounds__(256) nbits_prepack_kernel(const uint32_t* __restrict__ in, uint32_t* __restrict__ out, int64_t words) {
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < words; i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const uint32_t w = in[i];
+    uint32_t o = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      o |= ((w >> (8 * j)) & 0xFu) << (4 * j);             // weight 2j   (low nibble of byte j)
+      o |= ((w >> (8 * j + 4)) & 0xFu) << (16 + 4 * j);    // weight 2j+1 (high nibble of byte j)
+    }
+    out[i] = o;
+  }
+}
+
 }  // namespace
 }  // namespace ortb200
 
 using namespace ortb200;
+
+extern "C" int ortb200_nbits_prepack(const void* B, void* out, int64_t bytes, ortb200_stream_t stream_) {
+  if (!B || !out || bytes < 0 || bytes % 4 != 0 || B == out) return -1;
+  if ((reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(out)) & 3) return -3;
+  if (bytes == 0) return 0;
+  const int64_t words = bytes / 4;
+  int64_t blocks = (words + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  nbits_prepack_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream_)>>>(
+      static_cast<const uint32_t*>(B), static_cast<uint32_t*>(out), words);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
 
 extern "C" int ortb200_nbits_dequant(const void* B, const void* scales, const void* zero_points, int zp_is_packed, void* out,
                                      int64_t N, int K, int bits, int block_size, int64_t ldo, int dtype,

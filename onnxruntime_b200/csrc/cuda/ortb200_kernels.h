@@ -17,7 +17,7 @@ extern "C" {
 
 typedef void* ortb200_stream_t;  // cudaStream_t
 
-enum ortb200_dtype { ORTB200_F16 = 0, ORTB200_BF16 = 1, ORTB200_F32 = 2, ORTB200_F8E4M3 = 3 };
+enum ortb200_dtype { ORTB200_F16 = 0, ORTB200_BF16 = 1, ORTB200_F32 = 2, ORTB200_F8E4M3 = 3, ORTB200_Q4 = 4 };
 
 enum ortb200_act {
   ORTB200_ACT_NONE = 0,
@@ -81,6 +81,15 @@ typedef struct {
   // out = act(alpha * (x @ w^T) / rms(x) + bias) + residual with rms(x)[m] = sqrt(mean_k x[m, k]^2 + rms_eps);
   // the caller folds the norm's gamma into w (w[n, k] *= gamma[k]).  Larger M returns -14: normalise first.
   float rms_eps;
+  // in_dtype == ORTB200_Q4 (decode-shaped problems, M <= 64): w is the tile-blob array that the caller builds once
+  // from MatMulNBits weights (layout below); the kernel fetches one contiguous blob per (weight tile, k-block) and
+  // expands the nibbles to `dtype` in shared memory on their way to the tensor cores.  K a multiple of 64.
+  //   blob(tile t, k-block kb) at byte ((t * K / 64) + kb) * 4864:
+  //     [0, 4096)    row r (weight row 128 t + r) at r * 32: the 64 nibbles of the k-block, re-arranged per 32-bit word
+  //                  by ortb200_nbits_prepack
+  //     [4096, 4608) row r at r * 4: the scales of elements [0, 32) and [32, 64) of the k-block, in `dtype`
+  //     [4608, 4864) row r at r * 2: their zero points, one byte each (8 when the model has none)
+  //   rows beyond N are zero.  W[n, k] = (q - zp) * scale.
   int force_tile_rows;  // 0 / 128 = 128-weight-row CTA tiles; 256 = 256-row tiles in the large-M kernel (M > 128)
 } ortb200_gemm_args;
 
@@ -316,6 +325,11 @@ typedef struct {
 } ortb200_symm_collective_args;
 int ortb200_symm_collective(const ortb200_symm_collective_args* args, ortb200_stream_t stream);
 int64_t ortb200_symm_collective_max_bytes(int op, int world, int64_t symm_bytes);
+
+// Re-arranges MatMulNBits 4-bit weights for the in-kernel expansion: within every 32-bit word (8 weights, low nibble
+// = even k) weight 2i moves to bits [4i, 4i+4) and weight 2i+1 to bits [16+4i, 16+4i+4).  B and out are N * K / 2
+// bytes; they may not alias.
+int ortb200_nbits_prepack(const void* B, void* out, int64_t bytes, ortb200_stream_t stream);
 
 // MatMulNBits weights -> dense rows.  B uint8 [N, n_blocks, block_size * bits / 8] (low nibble = even k), scales
 // [N, n_blocks], zero_points packed uint8 [N, ceil(n_blocks * bits / 8)] (zp_is_packed = 1) or typed [N, n_blocks]

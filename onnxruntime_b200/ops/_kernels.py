@@ -84,10 +84,14 @@ def gemm(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
          out: Optional[torch.Tensor] = None, n: Optional[int] = None, dual_offset: int = 0,
          force_splits: int = 0, force_bn: int = 0, status: Optional[torch.Tensor] = None,
          use_pdl: bool = False, peers=None, rank: int = 0, symm_bytes: int = 0,
-         out_dtype: Optional[torch.dtype] = None, rms_eps: float = 0.0, force_tile_rows: int = 0) -> torch.Tensor:
+         out_dtype: Optional[torch.dtype] = None, rms_eps: float = 0.0, force_tile_rows: int = 0,
+         q4: bool = False) -> torch.Tensor:
     """out[M, N] = act(alpha * x[M, K] @ w[N, K].T + bias) + residual  (tcgen05 kernel).
     x / w of dtype float8_e4m3fn use the 8-bit tensor-core mode; out_dtype (fp16 / bf16) is then required."""
-    assert x.is_cuda and w.is_cuda and x.dtype == w.dtype and x.dim() == 2 and w.dim() == 2
+    assert x.is_cuda and w.is_cuda and (x.dtype == w.dtype or q4) and x.dim() == 2
+    if q4:  # w is the tile-blob array from nbits_build_blobs: [tiles, K / 64, 4864] bytes; n must be given
+        assert n is not None
+        w = w.reshape(w.shape[0] * 128, -1)
     assert x.is_contiguous() and w.is_contiguous()
     M, K = x.shape
     w_rows = w.shape[0]
@@ -106,7 +110,7 @@ def gemm(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
                  dtype_code(odt), ACT[act], alpha, _ptr(ws), ws.numel(), _ptr(status), force_splits, force_bn,
                  1 if use_pdl else 0, len(peers) if peers else 1, rank,
                  (ctypes.c_void_p * 8)(*(list(peers) + [None] * (8 - len(peers)))) if peers else (ctypes.c_void_p * 8)(),
-                 symm_bytes, 3 if fp8 else 0, rms_eps, force_tile_rows)
+                 symm_bytes, 4 if q4 else (3 if fp8 else 0), rms_eps, force_tile_rows)
     rc = lib().ortb200_gemm(ctypes.byref(a), ctypes.c_void_p(stream_ptr()))
     if rc != 0:
         raise RuntimeError(f"ortb200_gemm rejected its arguments (code {rc})")
@@ -250,6 +254,21 @@ def paged_prep(qkv, k_cache, v_cache, cu_seqlens, past_seqlens, block_table, N, 
                       1 if interleaved else 0, 0 if cos is None else 1, dtype_code(qkv.dtype), _ptr(status))
     _check(lib().ortb200_paged_prep(ctypes.byref(a), ctypes.c_void_p(stream_ptr())), "ortb200_paged_prep")
     return q_out
+
+
+def nbits_prepack(B):
+    """MatMulNBits 4-bit weights [N, n_blocks, block/2] -> [N, K/2] bytes in the nibble order the GEMM expands."""
+    B = B.contiguous()
+    out = torch.empty(B.shape[0], B.numel() // B.shape[0], dtype=torch.uint8, device=B.device)
+    _check(lib().ortb200_nbits_prepack(ctypes.c_void_p(_ptr(B)), ctypes.c_void_p(_ptr(out)), ctypes.c_int64(B.numel()),
+                                       ctypes.c_void_p(stream_ptr())), "ortb200_nbits_prepack")
+    return out
+
+
+def nbits_build_blobs(B, scales, zp_bytes, N, K, block_size=32):
+    """MatMulNBits 4-bit weights -> the [tiles, K / 64, 4864] byte array ``gemm(..., q4=True)`` consumes."""
+    from .. import _core
+    return _core.nbits_build_blobs(B, scales, zp_bytes, N, K, block_size)
 
 
 def nbits_dequant(B, scales, zero_points, N, K, bits=4, block_size=32):

@@ -287,3 +287,27 @@ def test_session_gemm_float8():
     ref = 2.0 * 0.5 * 0.25 * (a16.to(torch.float8_e4m3fn).float() @ w8.float().T)
     assert np.abs(gq - ref.numpy()).max() / np.abs(ref.numpy()).max() < 1e-2
     assert np.abs(c - ref.numpy()).max() / np.abs(ref.numpy()).max() < 1e-2
+
+
+@pytest.mark.parametrize("M,N,Kd,bs", [(1, 512, 1024, 32), (8, 1280, 8192, 32), (33, 384, 2048, 64), (64, 1000, 1024, 128), (8, 4096, 4096, 32)])
+@pytest.mark.parametrize("zp_mode", ["none", "packed"])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_gemm_q4_in_kernel_expansion(K, M, N, Kd, bs, zp_mode, dtype):
+    """Decode GEMM on 4-bit block-quantised weights: the kernel expands the nibbles in shared memory.  The result
+    must match the GEMM on the explicitly dequantised weights (same rounding of the weights to 16 bits)."""
+    B, scales, zp, w = _quantize(N, Kd, 4, bs, dtype, zp_mode, seed=5)
+    zp_bytes = None
+    if zp is not None:
+        z = zp.to(torch.int32)
+        zp_bytes = torch.stack([z & 0xF, (z >> 4) & 0xF], -1).reshape(N, -1)[:, :(Kd + bs - 1) // bs].to(torch.uint8).contiguous().cuda()
+    blobs = K.nbits_build_blobs(B.cuda(), scales.cuda(), zp_bytes, N, Kd, bs)
+    assert blobs.shape == ((N + 127) // 128, Kd // 64, 4864) and blobs.dtype == torch.uint8
+    x = (torch.randn(M, Kd, device="cuda") * 0.5).to(dtype)
+    bias = torch.randn(N, device="cuda").to(dtype)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    y = K.gemm(x, blobs, bias=bias, n=N, q4=True, status=status)
+    assert status.item() == 0
+    ref = x.float() @ w.to(dtype).float().cuda().T + bias.float()
+    assert _rel(y, ref) < 1e-2
+    dense = K.gemm(x, K.nbits_dequant(B.cuda(), scales.cuda(), None if zp is None else zp.cuda(), N, Kd, 4, bs), bias=bias)
+    assert _rel(y, dense) < 4e-3
