@@ -300,31 +300,36 @@ class GqaKernel final : public WithFallback {
     at::Tensor pos_ids;
     if (ctx.HasInput(9)) pos_ids = ctx.Input(9).to(query.device(), at::kLong).contiguous();
 
-    ortb200_gqa_prep_args pa{};
-    pa.qkv = qc.data_ptr();
-    at::Tensor kin, vin;
-    if (!packed) {
-      kin = ctx.Input(1).contiguous();
-      vin = ctx.RequiredInput(2).contiguous();
-      pa.k = kin.data_ptr();
-      pa.v = vin.data_ptr();
+    // one-token steps: the attention kernel unpacks, rotates and appends by itself (no separate launch, no q buffer)
+    const bool fuse_prep = S == 1 && !first_prompt && packed && !pos_ids.defined() &&
+                           (!do_rotary_ || ctx.Input(7).size(1) * 2 == H) && ctx.session()->config().Get("ortb200.fused_gqa_prep", "1") == "1";
+    if (!fuse_prep) {
+      ortb200_gqa_prep_args pa{};
+      pa.qkv = qc.data_ptr();
+      at::Tensor kin, vin;
+      if (!packed) {
+        kin = ctx.Input(1).contiguous();
+        vin = ctx.RequiredInput(2).contiguous();
+        pa.k = kin.data_ptr();
+        pa.v = vin.data_ptr();
+      }
+      pa.q_out = q_rot.data_ptr();
+      pa.k_cache = kc.data_ptr();
+      pa.v_cache = vc.data_ptr();
+      pa.seqlens_k = sl.data_ptr<int>();
+      pa.cos_cache = do_rotary_ ? ctx.Input(7).data_ptr() : nullptr;
+      pa.sin_cache = do_rotary_ ? ctx.RequiredInput(8).data_ptr() : nullptr;
+      pa.position_ids = pos_ids.defined() ? pos_ids.data_ptr<int64_t>() : nullptr;
+      pa.B = static_cast<int>(B); pa.S = static_cast<int>(S); pa.N = static_cast<int>(N_); pa.Nk = static_cast<int>(Nk_);
+      pa.H = static_cast<int>(H); pa.Smax = static_cast<int>(Smax);
+      pa.rot_dim = do_rotary_ ? static_cast<int>(ctx.Input(7).size(1) * 2) : 0;
+      pa.interleaved = interleaved_ ? 1 : 0;
+      pa.first_prompt = first_prompt ? 1 : 0;
+      pa.do_rotary = do_rotary_ ? 1 : 0;
+      pa.dtype = dt;
+      CheckLaunch(ortb200_gqa_prep(&pa, ctx.cuda_stream()), "ortb200_gqa_prep");
+      ctx.session()->AddLaunches(1);
     }
-    pa.q_out = q_rot.data_ptr();
-    pa.k_cache = kc.data_ptr();
-    pa.v_cache = vc.data_ptr();
-    pa.seqlens_k = sl.data_ptr<int>();
-    pa.cos_cache = do_rotary_ ? ctx.Input(7).data_ptr() : nullptr;
-    pa.sin_cache = do_rotary_ ? ctx.RequiredInput(8).data_ptr() : nullptr;
-    pa.position_ids = pos_ids.defined() ? pos_ids.data_ptr<int64_t>() : nullptr;
-    pa.B = static_cast<int>(B); pa.S = static_cast<int>(S); pa.N = static_cast<int>(N_); pa.Nk = static_cast<int>(Nk_);
-    pa.H = static_cast<int>(H); pa.Smax = static_cast<int>(Smax);
-    pa.rot_dim = do_rotary_ ? static_cast<int>(ctx.Input(7).size(1) * 2) : 0;
-    pa.interleaved = interleaved_ ? 1 : 0;
-    pa.first_prompt = first_prompt ? 1 : 0;
-    pa.do_rotary = do_rotary_ ? 1 : 0;
-    pa.dtype = dt;
-    CheckLaunch(ortb200_gqa_prep(&pa, ctx.cuda_stream()), "ortb200_gqa_prep");
-    ctx.session()->AddLaunches(1);
 
     at::Tensor out;
     if (S == 1) {
@@ -332,6 +337,13 @@ class GqaKernel final : public WithFallback {
       at::Tensor& ws = ctx.session()->AttnWorkspace(ortb200_gqa_decode_workspace_bytes(static_cast<int>(B), static_cast<int>(N_), static_cast<int>(H)));
       ortb200_gqa_decode_args da{};
       da.q = q_rot.data_ptr();
+      if (fuse_prep) {
+        da.qkv = qc.data_ptr();
+        da.cos_cache = do_rotary_ ? ctx.Input(7).data_ptr() : nullptr;
+        da.sin_cache = do_rotary_ ? ctx.RequiredInput(8).data_ptr() : nullptr;
+        da.do_rotary = do_rotary_ ? 1 : 0;
+        da.rotary_interleaved = interleaved_ ? 1 : 0;
+      }
       da.k_cache = kc.data_ptr();
       da.v_cache = vc.data_ptr();
       da.seqlens_k = sl.data_ptr<int>();

@@ -176,6 +176,13 @@ struct DecodeParams {
   // paged cache [num_blocks, block_size, Nk, H]: key j of sequence b lives in block block_table[b, j / block_size]
   const int* block_table;
   int block_size, max_blocks;
+  // fused "unpack + rotary + append" (one new token per sequence): q, k and v are read from the packed projection
+  // output qkv [B, (N + 2 Nk) H]; the CTA whose key range ends at the new position rotates the new key, writes
+  // key and value into the cache and attends to them from registers
+  const void* qkv;
+  const void* cos_cache;
+  const void* sin_cache;
+  int do_rotary, interleaved;
 };
 
 // Running maxima start at a large negative finite value so that exp(m_old - m_new) never sees inf - inf.
@@ -224,7 +231,10 @@ __global__ void __launch_bounds__(128) gqa_decode_kernel(const DecodeParams p) {
   const int len = max(total - start0, 0);
   const int chunk = (len + p.splits - 1) / p.splits;
   const int k_begin = start0 + split * chunk;
-  const int k_end = min(total, k_begin + chunk);
+  const int k_end_all = min(total, k_begin + chunk);
+  // fused prep: the newest key is not in the cache yet; the CTA whose range reaches it handles it from registers
+  const bool owns_new = (p.qkv != nullptr) && k_end_all == total && k_begin < total;
+  const int k_end = owns_new ? k_end_all - 1 : k_end_all;
   const int n_tiles = k_end > k_begin ? (k_end - k_begin + kDecTile - 1) / kDecTile : 0;
 
   const T* kbase = static_cast<const T*>(p.k_cache) + (static_cast<long long>(b) * p.Nk + kvh) * p.Smax * H;
@@ -266,12 +276,52 @@ __global__ void __launch_bounds__(128) gqa_decode_kernel(const DecodeParams p) {
     for (int t = 0; t < pre; ++t) issue_tile(t);
   }
 
+  const bool fused = p.qkv != nullptr;
+  // rotary factors of the new position for this lane's dims (non-interleaved: dim i pairs with i +- H/2, held by the
+  // lane 4 further on; interleaved: neighbouring dims, held by this lane)
+  float rc[DPL], rs[DPL];
+  if (fused && p.do_rotary) {
+    const T* cosr = static_cast<const T*>(p.cos_cache) + static_cast<long long>(total - 1) * (H / 2);
+    const T* sinr = static_cast<const T*>(p.sin_cache) + static_cast<long long>(total - 1) * (H / 2);
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) {
+      const int d = d0 + i;
+      const int fi = p.interleaved ? (d >> 1) : (d % (H / 2));
+      rc[i] = to_float<T>(cosr[fi]);
+      rs[i] = to_float<T>(sinr[fi]);
+    }
+  }
+  // x[DPL] holds this lane's dims of one head vector; returns it rotated
+  auto rope = [&](float* x) {
+    if (p.interleaved) {
+#pragma unroll
+      for (int i = 0; i < DPL; i += 2) {
+        const float a = x[i], bb = x[i + 1];
+        x[i] = a * rc[i] - bb * rs[i];
+        x[i + 1] = bb * rc[i + 1] + a * rs[i + 1];
+      }
+    } else {
+      const bool upper = sub >= 4;  // dims [H/2, H)
+#pragma unroll
+      for (int i = 0; i < DPL; ++i) {
+        const float other = __shfl_xor_sync(0xffffffffu, x[i], 4);
+        x[i] = upper ? x[i] * rc[i] + other * rs[i] : x[i] * rc[i] - other * rs[i];
+      }
+    }
+  };
+  const long long qkv_row = static_cast<long long>(b) * (p.N + 2 * p.Nk) * H;
   float qf[G][DPL];
 #pragma unroll
   for (int g = 0; g < G; ++g) {
-    const T* qp = static_cast<const T*>(p.q) + (static_cast<long long>(b) * p.N + head0 + (g < n_heads ? g : 0)) * H + d0;
+    const int hd = head0 + (g < n_heads ? g : 0);
+    const T* qp = fused ? static_cast<const T*>(p.qkv) + qkv_row + static_cast<long long>(hd) * H + d0
+                        : static_cast<const T*>(p.q) + (static_cast<long long>(b) * p.N + hd) * H + d0;
+    float x[DPL];
 #pragma unroll
-    for (int i = 0; i < DPL; ++i) qf[g][i] = to_float<T>(qp[i]) * p.scale;
+    for (int i = 0; i < DPL; ++i) x[i] = to_float<T>(qp[i]);
+    if (fused && p.do_rotary) rope(x);
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) qf[g][i] = x[i] * p.scale;
   }
   float m[G], l[G], acc[G][DPL];
 #pragma unroll
@@ -359,6 +409,57 @@ __global__ void __launch_bounds__(128) gqa_decode_kernel(const DecodeParams p) {
     }
   }
   if (!ok && tid == 0 && p.status) atomicExch(p.status, kStatusTimeoutEpilogue);
+
+  if (owns_new) {
+    // the new token: rotate its key, store key and value at cache position total - 1, attend to them.  All lanes run
+    // the shuffles; only lane group 0 of warp 0 stores and accumulates.
+    const T* kp = static_cast<const T*>(p.qkv) + qkv_row + static_cast<long long>(p.N + kvh) * H + d0;
+    const T* vp = static_cast<const T*>(p.qkv) + qkv_row + static_cast<long long>(p.N + p.Nk + kvh) * H + d0;
+    float kx[DPL], vx[DPL];
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) {
+      kx[i] = to_float<T>(kp[i]);
+      vx[i] = to_float<T>(vp[i]);
+    }
+    if (p.do_rotary) rope(kx);
+    const bool mine = warp == 0 && slot == 0;
+    if (mine) {
+      long long row;
+      if (PAGED) {
+        const int key = total - 1;
+        const int blk = p.block_table[static_cast<long long>(b) * p.max_blocks + key / p.block_size];
+        row = ((static_cast<long long>(blk) * p.block_size + key % p.block_size) * p.Nk + kvh) * H;
+      } else {
+        row = ((static_cast<long long>(b) * p.Nk + kvh) * p.Smax + (total - 1)) * H;
+      }
+      T* kd = static_cast<T*>(const_cast<void*>(p.k_cache)) + row + d0;
+      T* vd = static_cast<T*>(const_cast<void*>(p.v_cache)) + row + d0;
+#pragma unroll
+      for (int i = 0; i < DPL; ++i) {
+        kd[i] = from_float<T>(kx[i]);
+        vd[i] = vp[i];
+        kx[i] = to_float<T>(kd[i]);  // attend to the stored (rounded) key, as later steps will
+      }
+    }
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      float a0 = 0.f;
+#pragma unroll
+      for (int i = 0; i < DPL; ++i) a0 += qf[g][i] * kx[i];
+#pragma unroll
+      for (int off = 1; off <= 4; off <<= 1) a0 += __shfl_xor_sync(0xffffffffu, a0, off);
+      if (p.softcap > 0.f) a0 = p.softcap * tanhf(a0 / p.softcap);
+      if (mine) {
+        const float m_new = fmaxf(m[g], a0);
+        const float corr = __expf(m[g] - m_new);
+        const float pr = __expf(a0 - m_new);
+        l[g] = l[g] * corr + pr;
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) acc[g][i] = acc[g][i] * corr + pr * vx[i];
+        m[g] = m_new;
+      }
+    }
+  }
 
   // merge the 4 key slots of a warp (lanes differing in bits 3 and 4)
 #pragma unroll
@@ -526,6 +627,8 @@ static int launch_decode(const ortb200_gqa_decode_args* a, cudaStream_t stream) 
   p.scale = a->scale != 0.f ? a->scale : 1.0f / sqrtf(static_cast<float>(H));
   p.softcap = a->softcap;
   p.block_table = a->block_table; p.block_size = a->block_size; p.max_blocks = a->max_blocks;
+  p.qkv = a->qkv; p.cos_cache = a->cos_cache; p.sin_cache = a->sin_cache;
+  p.do_rotary = a->do_rotary; p.interleaved = a->rotary_interleaved;
   dim3 grid(splits, a->Nk * gparts, a->B);
   if (a->block_table) {
     if (G == 4) return launch_decode_g<T, H, 4, true>(p, grid, stream, a->use_pdl != 0);
@@ -548,7 +651,8 @@ extern "C" int64_t ortb200_gqa_decode_workspace_bytes(int B, int N, int H) {
 
 extern "C" int ortb200_gqa_decode(const ortb200_gqa_decode_args* a, ortb200_stream_t stream_) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-  if (!a || !a->q || !a->k_cache || !a->v_cache || !a->seqlens_k || !a->out) return -1;
+  if (!a || (!a->q && !a->qkv) || !a->k_cache || !a->v_cache || !a->seqlens_k || !a->out) return -1;
+  if (a->qkv && a->do_rotary && (!a->cos_cache || !a->sin_cache)) return -2;
   if (a->B <= 0 || a->N <= 0 || a->Nk <= 0 || a->N % a->Nk != 0 || a->Smax <= 0) return -1;
   if (a->block_table && (a->block_size <= 0 || a->max_blocks <= 0)) return -1;
   if (a->H != 64 && a->H != 128) return -2;

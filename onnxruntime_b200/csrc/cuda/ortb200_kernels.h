@@ -216,6 +216,15 @@ typedef struct {
   const int* block_table;
   int block_size;
   int max_blocks;
+  // Fused step 1 (replaces ortb200_gqa_prep for one-token steps): when qkv is given, q is ignored; query, key and
+  // value of the new token are read from the packed projection output qkv [B, (N + 2 Nk) H], rotated at position
+  // seqlens_k[b] (cos / sin caches [max_pos, H / 2], full-width rotary) and the new key / value are written to cache
+  // position seqlens_k[b] by the kernel itself.
+  const void* qkv;
+  const void* cos_cache;
+  const void* sin_cache;
+  int do_rotary;
+  int rotary_interleaved;
 } ortb200_gqa_decode_args;
 int ortb200_gqa_decode(const ortb200_gqa_decode_args* args, ortb200_stream_t stream);
 int64_t ortb200_gqa_decode_workspace_bytes(int B, int N, int H);

@@ -173,15 +173,23 @@ class GqaDecodeArgs(ctypes.Structure):
                 ("Nk", ctypes.c_int), ("H", ctypes.c_int), ("Smax", ctypes.c_int), ("splits", ctypes.c_int),
                 ("window", ctypes.c_int), ("scale", ctypes.c_float), ("softcap", ctypes.c_float), ("dtype", ctypes.c_int),
                 ("use_pdl", ctypes.c_int), ("status", ctypes.c_void_p), ("block_table", ctypes.c_void_p),
-                ("block_size", ctypes.c_int), ("max_blocks", ctypes.c_int)]
+                ("block_size", ctypes.c_int), ("max_blocks", ctypes.c_int), ("qkv", ctypes.c_void_p), ("cos_cache", ctypes.c_void_p),
+                ("sin_cache", ctypes.c_void_p), ("do_rotary", ctypes.c_int), ("rotary_interleaved", ctypes.c_int)]
 
 
 _ATTN_WS = {}
 
 
-def gqa_decode(q, k_cache, v_cache, seqlens_k, splits=0, window=-1, scale=0.0, softcap=0.0, head_sink=None, block_table=None):
-    """Dense cache [B,Nk,Smax,H]; or, with block_table [B,max_blocks] int32, a paged cache [num_blocks,block_size,Nk,H]."""
-    B, N, H = q.shape
+def gqa_decode(q, k_cache, v_cache, seqlens_k, splits=0, window=-1, scale=0.0, softcap=0.0, head_sink=None, block_table=None,
+               qkv=None, num_heads=0, cos=None, sin=None, interleaved=False):
+    """Dense cache [B,Nk,Smax,H]; or, with block_table [B,max_blocks] int32, a paged cache [num_blocks,block_size,Nk,H].
+    With ``qkv`` (packed [B,(N+2Nk)H], ``num_heads`` = N) the kernel also rotates q / k and appends k / v itself."""
+    if qkv is not None:
+        H = k_cache.shape[3]
+        B, N = qkv.shape[0], num_heads
+        q = qkv
+    else:
+        B, N, H = q.shape
     if block_table is None:
         Nk, Smax = k_cache.shape[1], k_cache.shape[2]
         block_size = max_blocks = 0
@@ -196,9 +204,10 @@ def gqa_decode(q, k_cache, v_cache, seqlens_k, splits=0, window=-1, scale=0.0, s
     if ws is None or ws.numel() < need:
         ws = torch.zeros(need, dtype=torch.uint8, device=q.device)
         _ATTN_WS[key] = ws
-    a = GqaDecodeArgs(_ptr(q.contiguous()), _ptr(k_cache), _ptr(v_cache), _ptr(seqlens_k), _ptr(head_sink), _ptr(out), _ptr(ws),
+    a = GqaDecodeArgs(None if qkv is not None else _ptr(q.contiguous()), _ptr(k_cache), _ptr(v_cache), _ptr(seqlens_k), _ptr(head_sink), _ptr(out), _ptr(ws),
                       ws.numel(), B, N, Nk, H, Smax, splits, window, scale, softcap, dtype_code(q.dtype), 0, None,
-                      _ptr(block_table), block_size, max_blocks)
+                      _ptr(block_table), block_size, max_blocks, _ptr(qkv), _ptr(cos), _ptr(sin), 0 if cos is None else 1,
+                      1 if interleaved else 0)
     _check(lib().ortb200_gqa_decode(ctypes.byref(a), ctypes.c_void_p(stream_ptr())), "ortb200_gqa_decode")
     return out
 

@@ -235,3 +235,29 @@ def test_gqa_decode_split_counts_agree(K, H, splits):
     a2 = K.gqa_decode(q, kc, vc, lens - 1, splits=splits, head_sink=sink, softcap=30.0)
     b2 = K.gqa_decode(q, kc, vc, lens - 1, splits=1, head_sink=sink, softcap=30.0)
     assert _rel(a2, b2) < 1e-2
+
+
+@pytest.mark.parametrize("H,N,Nk", [(128, 32, 8), (64, 8, 2), (128, 4, 4), (128, 8, 1)])
+@pytest.mark.parametrize("interleaved", [False, True])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_gqa_decode_with_fused_rotary_and_append(K, H, N, Nk, interleaved, dtype):
+    """One-token step with the unpack + rotary + KV append done inside the attention kernel equals the two-kernel
+    sequence (prep kernel, then attention), output and cache contents alike."""
+    torch.manual_seed(0)
+    B, Smax = 4, 600
+    lens = torch.tensor([1, 2, 300, 600], dtype=torch.int32, device="cuda")   # length including the new token
+    qkv = torch.randn(B, 1, (N + 2 * Nk) * H, device="cuda").to(dtype)
+    kc = torch.randn(B, Nk, Smax, H, device="cuda").to(dtype)
+    vc = torch.randn(B, Nk, Smax, H, device="cuda").to(dtype)
+    half = H // 2
+    pos = torch.arange(1024, device="cuda").float().unsqueeze(1)
+    inv = 1.0 / (10000 ** (torch.arange(half, device="cuda").float() / half))
+    cos, sin = torch.cos(pos * inv).to(dtype), torch.sin(pos * inv).to(dtype)
+    k1, v1 = kc.clone(), vc.clone()
+    q_rot = K.gqa_prep(qkv, k1, v1, lens - 1, cos, sin, N, Nk, H, first_prompt=False, interleaved=interleaved)
+    want = K.gqa_decode(q_rot.view(B, N, H), k1, v1, lens - 1)
+    k2, v2 = kc.clone(), vc.clone()
+    got = K.gqa_decode(None, k2, v2, lens - 1, qkv=qkv.view(B, -1), num_heads=N, cos=cos, sin=sin, interleaved=interleaved)
+    torch.cuda.synchronize()
+    assert torch.equal(k1, k2) and torch.equal(v1, v2)
+    assert _rel(got, want) < 1e-2
