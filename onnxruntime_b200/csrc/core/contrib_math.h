@@ -34,6 +34,8 @@ at::Tensor MoeForward(const at::Tensor& x, const at::Tensor& logits, const at::T
 at::Tensor DequantizeNBits(const at::Tensor& B, const at::Tensor& scales, const at::Tensor& zero_points, int64_t N,
                            int64_t K, int64_t bits, int64_t block_size, at::ScalarType out_type);
 
+at::Tensor DequantizeQMoeWeights(const at::Tensor& w, const at::Tensor& scales, int64_t bits, int64_t block);
+
 at::Tensor RotaryBSNH(const at::Tensor& x, const at::Tensor& pos, const at::Tensor& cos_cache,
                       const at::Tensor& sin_cache, bool interleaved, int64_t rot_dim, float scale);
 

@@ -528,6 +528,31 @@ void MoeImpl(Ctx& ctx) {
   ctx.SetOutput(0, y.reshape(x.sizes()));
 }
 
+}  // namespace
+
+namespace contrib {
+// QMoE expert weights [E, rows, K * bits / 8] with symmetric scales per output row ([E, rows]) or per block along K
+// ([E, rows, K / block]) -> float [E, rows, K]
+at::Tensor DequantizeQMoeWeights(const at::Tensor& w, const at::Tensor& scales, int64_t bits, int64_t block) {
+  if (!w.defined()) return at::Tensor();
+  const int64_t E = w.size(0), rows = w.size(1);
+  const int64_t K = bits == 4 ? w.size(2) * 2 : w.size(2);
+  at::Tensor q;
+  if (bits == 4) {
+    at::Tensor b = w.to(at::kInt);
+    q = at::stack({at::bitwise_and(b, 0xF), at::bitwise_and(at::bitwise_right_shift(b, 4), 0xF)}, -1).reshape({E, rows, K}).to(at::kFloat) - 8.0;
+  } else {
+    q = w.to(at::kFloat) - 128.0;
+  }
+  at::Tensor s = scales.to(at::kFloat);
+  if (s.dim() == 2) s = s.unsqueeze(-1);                       // per output row
+  else if (block > 0) s = s.repeat_interleave(block, 2).narrow(2, 0, K);  // per block along K
+  return q * s;
+}
+}  // namespace contrib
+
+namespace {
+
 // QMoE: block- or column-quantised expert weights; dequantise, then run the dense MoE.
 void QMoeImpl(Ctx& ctx) {
   const Node& n = ctx.node();
@@ -538,22 +563,7 @@ void QMoeImpl(Ctx& ctx) {
   at::Tensor x2 = x.reshape({-1, x.size(-1)});
   auto opt = [&](int i) { return ctx.HasInput(i) ? ctx.Input(i) : at::Tensor(); };
   // inputs: 0 input, 1 router_probs, 2 fc1_w, 3 fc1_scales, 4 fc1_bias, 5 fc2_w, 6 fc2_scales, 7 fc2_bias, 8 fc3_w, 9 fc3_scales, 10 fc3_bias
-  auto dequant = [&](const at::Tensor& w, const at::Tensor& scales) {
-    if (!w.defined()) return at::Tensor();
-    const int64_t E = w.size(0), rows = w.size(1);
-    const int64_t K = bits == 4 ? w.size(2) * 2 : w.size(2);
-    at::Tensor q;
-    if (bits == 4) {
-      at::Tensor b = w.to(at::kInt);
-      q = at::stack({at::bitwise_and(b, 0xF), at::bitwise_and(at::bitwise_right_shift(b, 4), 0xF)}, -1).reshape({E, rows, K}).to(at::kFloat) - 8.0;
-    } else {
-      q = w.to(at::kFloat) - 128.0;
-    }
-    at::Tensor s = scales.to(at::kFloat);
-    if (s.dim() == 2) s = s.unsqueeze(-1);                       // per output row
-    else if (block > 0) s = s.repeat_interleave(block, 2).narrow(2, 0, K);  // per block along K
-    return q * s;
-  };
+  auto dequant = [&](const at::Tensor& w, const at::Tensor& scales) { return contrib::DequantizeQMoeWeights(w, scales, bits, block); };
   at::Tensor fc1 = dequant(ctx.RequiredInput(2), ctx.RequiredInput(3));
   at::Tensor fc2 = dequant(ctx.RequiredInput(5), ctx.RequiredInput(6));
   at::Tensor fc3 = dequant(opt(8), opt(9));

@@ -384,13 +384,36 @@ class MoeKernel final : public WithFallback {
   explicit MoeKernel(const OpKernelInfo& info) : WithFallback(info) {
     const Node& n = info.node;
     sharded_ = n.op_type == "ShardedMoE";
+    const bool quantised = n.op_type == "QMoE";
     attrs_ = contrib::ParseMoeAttrs(n);
     start_ = sharded_ ? n.attr_i("local_experts_start_index", 0) : 0;
     tensor_shards_ = sharded_ ? n.attr_i("tensor_shards", 1) : 1;
-    const at::Tensor* fc1 = info.constant_input(2);
-    const at::Tensor* fc2 = info.constant_input(4);
-    const at::Tensor* fc3 = info.node.inputs.size() > 6 && !info.node.inputs[6].empty() ? info.constant_input(6) : nullptr;
-    const bool has_fc3 = info.node.inputs.size() > 6 && !info.node.inputs[6].empty();
+    // input slots: MoE (x, router, fc1, b1, fc2, b2, fc3, b3); QMoE adds a scales input behind every weight
+    const int i1 = 2, i2 = quantised ? 5 : 4, i3 = quantised ? 8 : 6;
+    b1_ = quantised ? 4 : 3;
+    b2_ = quantised ? 7 : 5;
+    b3_ = quantised ? 10 : 7;
+    auto has = [&](int i) { return static_cast<int>(n.inputs.size()) > i && !n.inputs[i].empty(); };
+    const at::Tensor* fc1 = info.constant_input(i1);
+    const at::Tensor* fc2 = info.constant_input(i2);
+    const bool has_fc3 = has(i3);
+    const at::Tensor* fc3 = has_fc3 ? info.constant_input(i3) : nullptr;
+    at::Tensor dq1, dq2, dq3;
+    if (quantised) {
+      // expert weights are expanded once, at session creation, to the scales' 16-bit type: the grouped GEMMs then run
+      // as for MoE (memory for speed; the packed form stays the model's storage format)
+      const at::Tensor* s1 = info.constant_input(3);
+      const at::Tensor* s2 = info.constant_input(6);
+      const at::Tensor* s3 = has_fc3 ? info.constant_input(9) : nullptr;
+      if (!fc1 || !fc2 || !s1 || !s2 || (has_fc3 && (!fc3 || !s3)) || !HalfType(s1->scalar_type())) return;
+      const int64_t bits = n.attr_i("expert_weight_bits", 4), block = n.attr_i("block_size", 0);
+      dq1 = contrib::DequantizeQMoeWeights(*fc1, *s1, bits, block).to(s1->scalar_type());
+      dq2 = contrib::DequantizeQMoeWeights(*fc2, *s2, bits, block).to(s1->scalar_type());
+      if (has_fc3) dq3 = contrib::DequantizeQMoeWeights(*fc3, *s3, bits, block).to(s1->scalar_type());
+      fc1 = &dq1;
+      fc2 = &dq2;
+      if (has_fc3) fc3 = &dq3;
+    }
     if (!fc1 || !fc2 || (has_fc3 && !fc3) || !HalfType(fc1->scalar_type()) || fc1->dim() != 3 || fc2->dim() != 3) return;
     if (attrs_.activation == "swiglu" || tensor_shards_ > 1) return;
     if (has_fc3 && attrs_.activation != "silu") return;
@@ -418,7 +441,7 @@ class MoeKernel final : public WithFallback {
     const at::Tensor& x = ctx.RequiredInput(0);
     const at::Tensor& logits_in = ctx.RequiredInput(1);
     const int dt = DtypeCode(x.scalar_type());
-    const bool fc3_bias = ctx.HasInput(7);
+    const bool fc3_bias = ctx.HasInput(b3_);
     if (!ok_ || dt < 0 || x.scalar_type() != w13_.scalar_type() || x.size(-1) != H_ || fc3_bias ||
         attrs_.k > 8 || logits_in.size(-1) > 256) {
       Fallback(ctx);
@@ -437,7 +460,7 @@ class MoeKernel final : public WithFallback {
     int tile_rows = ortb200_moe_tile_rows(R, static_cast<int>(E_local_));
     // the gated (two-accumulator) kernel stops at 128-token tiles; without a bias the 256-token path runs the gate
     // and up projections as one plain GEMM followed by a streaming SwiGLU
-    if (dual_ && tile_rows == 256 && ctx.HasInput(3)) tile_rows = 128;
+    if (dual_ && tile_rows == 256 && ctx.HasInput(b1_)) tile_rows = 128;
     const int max_tiles = ortb200_moe_max_tiles(R, static_cast<int>(E_local_), tile_rows);
     auto iopt = x.options().dtype(at::kInt);
     at::Tensor topk_idx = at::empty({T, k}, iopt), row_of = at::empty({T, k}, iopt);
@@ -470,8 +493,8 @@ class MoeKernel final : public WithFallback {
     }
     CheckLaunch(ortb200_moe_route(&ra, ctx.cuda_stream()), "ortb200_moe_route");
 
-    at::Tensor fc1_bias = ctx.HasInput(3) ? ctx.Input(3).contiguous() : at::Tensor();
-    at::Tensor fc2_bias = ctx.HasInput(5) ? ctx.Input(5).contiguous() : at::Tensor();
+    at::Tensor fc1_bias = ctx.HasInput(b1_) ? ctx.Input(b1_).contiguous() : at::Tensor();
+    at::Tensor fc2_bias = ctx.HasInput(b2_) ? ctx.Input(b2_).contiguous() : at::Tensor();
     if (fc2_bias.defined() && fc2_bias.size(0) != E_local_) fc2_bias = fc2_bias.narrow(0, start_, E_local_).contiguous();
     at::Tensor h = at::empty({R, I_}, x.options());
     ortb200_gemm_grouped_args g{};
@@ -522,6 +545,7 @@ class MoeKernel final : public WithFallback {
   }
   contrib::MoeAttrs attrs_;
   bool sharded_ = false, ok_ = false, dual_ = false;
+  int b1_ = 3, b2_ = 5, b3_ = 7;
   int64_t start_ = 0, tensor_shards_ = 1, E_local_ = 0, I_ = 0, H_ = 0;
   at::Tensor w13_, w2_;
 };
@@ -703,6 +727,7 @@ void RegisterCudaKernels3(KernelRegistry& r) {
   Reg<MultiHeadAttentionKernel>(r, MS, "MultiHeadAttention");
   Reg<MoeKernel>(r, MS, "MoE");
   Reg<MoeKernel>(r, MS, "ShardedMoE");
+  Reg<MoeKernel>(r, MS, "QMoE");
   Reg<GemmFloat8Kernel>(r, MS, "GemmFloat8");
   Reg<SymmCollectiveKernel>(r, MS, "AllReduce");
   Reg<SymmCollectiveKernel>(r, MS, "AllGather");

@@ -311,3 +311,17 @@ def test_gemm_q4_in_kernel_expansion(K, M, N, Kd, bs, zp_mode, dtype):
     assert _rel(y, ref) < 1e-2
     dense = K.gemm(x, K.nbits_dequant(B.cuda(), scales.cuda(), None if zp is None else zp.cuda(), N, Kd, 4, bs), bias=bias)
     assert _rel(y, dense) < 4e-3
+
+
+@pytest.mark.parametrize("bits,block", [(4, 0), (4, 32)])
+def test_session_qmoe(bits, block):
+    """QMoE on the GPU provider (weights expanded once at session creation, then the grouped-GEMM MoE path)."""
+    import sys
+    sys.path.insert(0, __import__("os").path.dirname(__file__))
+    from test_ops_cpu import _qmoe_case
+    x, logits, (p1, s1, _), (p2, s2, _), (p3, s3, _) = _qmoe_case(bits, block, E=8, H=256, I=512, T=40, dtype=np.float16)
+    rc, rg = _both("QMoE", {"x": x, "r": logits, "w1": p1, "s1": s1, "b1": None, "w2": p2, "s2": s2, "b2": None, "w3": p3, "s3": s3},
+                   initializers=("w1", "s1", "w2", "s2", "w3", "s3"), k=2, activation_type="silu", normalize_routing_weights=1,
+                   expert_weight_bits=bits, block_size=block)
+    c, g = rc[0].astype(np.float32), rg[0].astype(np.float32)
+    assert np.abs(c - g).max() / np.abs(c).max() < 2e-2

@@ -281,3 +281,39 @@ def test_control_flow_if_loop_scan():
     sf, ys = s.run(None, {"s0": np.zeros(3, np.float32), "xs": xs})
     np.testing.assert_allclose(ys, np.cumsum(xs, 0), rtol=1e-5, atol=1e-6)
     np.testing.assert_allclose(sf, xs.sum(0), rtol=1e-5, atol=1e-6)
+
+
+def _qmoe_case(bits=4, block=0, E=4, H=32, I=64, T=6, k=2, dtype=np.float32, seed=0):
+    """Quantised expert weights for QMoE plus their dequantised form (what MoE must reproduce)."""
+    rng = np.random.RandomState(seed)
+    qmax, mid = (15, 8) if bits == 4 else (255, 128)
+
+    def quant(w):  # w [E, rows, K] -> packed, scales, dequantised
+        Ee, rows, K = w.shape
+        if block:
+            wb = w.reshape(Ee, rows, K // block, block)
+            s = np.abs(wb).max(-1) / (mid - 1) + 1e-8
+            q = np.clip(np.rint(wb / s[..., None]) + mid, 0, qmax).astype(np.uint8).reshape(Ee, rows, K)
+            deq = ((q.reshape(Ee, rows, K // block, block).astype(np.float32) - mid) * s[..., None]).reshape(Ee, rows, K)
+        else:
+            s = np.abs(w).max(-1) / (mid - 1) + 1e-8
+            q = np.clip(np.rint(w / s[..., None]) + mid, 0, qmax).astype(np.uint8)
+            deq = (q.astype(np.float32) - mid) * s[..., None]
+        packed = (q[..., 0::2] | (q[..., 1::2] << 4)).astype(np.uint8) if bits == 4 else q
+        return packed, s.astype(dtype), deq.astype(dtype)
+    fc1 = rng.randn(E, I, H).astype(np.float32) * 0.2
+    fc2 = rng.randn(E, H, I).astype(np.float32) * 0.2
+    fc3 = rng.randn(E, I, H).astype(np.float32) * 0.2
+    x = rng.randn(T, H).astype(dtype)
+    logits = (np.argsort(rng.rand(T, E), axis=1) * 0.37 - 1.0).astype(dtype)
+    return x, logits, quant(fc1), quant(fc2), quant(fc3)
+
+
+@pytest.mark.parametrize("bits,block", [(4, 0), (8, 0), (4, 16)])
+def test_qmoe_matches_moe_on_dequantised_weights(bits, block):
+    x, logits, (p1, s1, d1), (p2, s2, d2), (p3, s3, d3) = _qmoe_case(bits, block)
+    attrs = dict(k=2, activation_type="silu", normalize_routing_weights=1)
+    q = run_node("QMoE", {"x": x, "r": logits, "w1": p1, "s1": s1, "b1": None, "w2": p2, "s2": s2, "b2": None, "w3": p3, "s3": s3},
+                 domain="com.microsoft", expert_weight_bits=bits, block_size=block, **attrs)[0]
+    m = run_node("MoE", {"x": x, "r": logits, "w1": d1, "b1": None, "w2": d2, "b2": None, "w3": d3}, domain="com.microsoft", **attrs)[0]
+    np.testing.assert_allclose(q, m, rtol=1e-4, atol=1e-5)
