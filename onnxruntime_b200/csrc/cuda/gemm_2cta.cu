@@ -1,0 +1,398 @@
+// Large-M GEMM on pairs of SMs (tcgen05 cta_group::2) for sm_100a.
+//
+//   out[M, N] = act(alpha * X[M,K] * W[N,K]^T + bias) + residual        (bf16 / fp16, fp32 accumulation)
+//
+// A cluster of two CTAs computes one 256 (weight rows) x 256 (tokens) tile.  Each CTA stages its own 128 weight
+// rows (A operand) and 128 of the 256 token rows (its half of the B operand) with TMA; ONE thread of the leader CTA
+// issues tcgen05.mma.cta_group::2, which reads A and B from the shared memory of both CTAs and accumulates each
+// CTA's 128 x 256 half of the tile in that CTA's tensor memory.  Per 128 x 256 x 64 unit of math a CTA therefore
+// moves 32 KB through its shared memory (TMA in) + 32 KB (operand reads) instead of 48 + 48 KB for a lone CTA, which
+// is what bounds the single-CTA kernel in gemm_tcgen05.cu.
+//
+// Synchronisation (all mbarriers live at the same shared-memory offset in both CTAs):
+//   full[s]        leader only   both producers' TMA bytes land on the LEADER's barrier (.cta_group::2 loads)
+//   empty[s]       per CTA       tcgen05.commit multicast to both CTAs once the MMAs reading stage s are done
+//   tmem_full[b]   per CTA       multicast commit: accumulator buffer b complete
+//   tmem_empty[b]  leader only   256 arrivals: the epilogue threads of both CTAs (the peer arrives remotely)
+// Every wait is bounded; a timeout sets the status word and the kernel drains and returns.
+//
+// Reference counterpart: cublasGemmEx behind onnxruntime/core/providers/cuda/math/matmul.cc.
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include "gemm_internal.h"
+#include "ortb200_kernels.h"
+#include "ptx_sm100.cuh"
+#include "tensor_map.h"
+
+namespace ortb200 {
+namespace {
+
+constexpr int kBM = 128;        // weight rows per CTA (256 per pair)
+constexpr int kBNHalf = 128;    // token rows each CTA stages (256 per pair)
+constexpr int kBN = 256;        // tokens per tile = accumulator columns
+constexpr int kBK = 64;
+constexpr int kStages = 5;
+constexpr int kThreads = 192;
+
+struct Gemm2Params {
+  int M, N, K, num_kb;
+  int tiles_m, tiles;  // tiles of 256 x 256; tile = tile_n * tiles_m + tile_m
+  int dtype, act;
+  float alpha;
+  void* out;
+  long long ldo;
+  const void* bias;
+  const void* residual;
+  long long ldr;
+  int* status;
+};
+
+struct Smem2 {
+  static constexpr int kABytes = kBM * kBK * 2;
+  static constexpr int kBBytes = kBNHalf * kBK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kBarOffset = kStageBytes * kStages;
+  static constexpr int kStagingOffset = kBarOffset + 256;
+  static constexpr int kStagingBytes = 128 * kBM * 2;
+  static constexpr int kTotal = kStagingOffset + kStagingBytes + 1024;
+  static constexpr int kTmemCols = 512;  // two accumulator buffers of 256 columns
+};
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release;\n\tbarrier.cluster.wait.acquire;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t map_to_rank(uint32_t local_smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_smem_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void tmem_alloc2(uint32_t* smem_result, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_result)), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish2() { asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_dealloc2(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+// TMA load whose completion bytes are counted on a barrier given as a shared::cluster address (the leader's)
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const void* tmap, uint32_t bar_cluster_addr, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(tmap), "r"(bar_cluster_addr), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void umma2_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// arrive (once the MMAs issued so far are done) on the barrier at this offset in BOTH CTAs of the pair
+__device__ __forceinline__ void umma2_commit_both(uint64_t* bar) {
+  const uint16_t mask = 0x3;
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(smem_u32(bar)), "h"(mask)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster_addr) : "memory");
+}
+
+__device__ __forceinline__ float act2(int act, float v) {
+  switch (act) {
+    case ORTB200_ACT_GELU: return 0.5f * v * (1.0f + erff(v * 0.70710678118654752f));
+    case ORTB200_ACT_FASTGELU: return 0.5f * v * (1.0f + tanhf(0.7978845608028654f * v * (1.0f + 0.044715f * v * v)));
+    case ORTB200_ACT_RELU: return fmaxf(v, 0.0f);
+    case ORTB200_ACT_SILU: return v / (1.0f + __expf(-v));
+    case ORTB200_ACT_QUICKGELU: return v / (1.0f + __expf(-1.702f * v));
+    default: return v;
+  }
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x, const Gemm2Params p) {
+  using S = Smem2;
+  extern __shared__ uint8_t smem_raw[];
+  // the same rounding in both CTAs (the dynamic shared-memory window starts at the same offset in every CTA)
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + S::kBarOffset);
+  uint64_t* empty_bar = full_bar + kStages;
+  uint64_t* tmem_full_bar = empty_bar + kStages;   // [2]
+  uint64_t* tmem_empty_bar = tmem_full_bar + 2;    // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty_bar + 2);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_rank();         // 0 = leader
+  const bool leader = rank == 0;
+  const int pair = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    tma_prefetch_desc(&tmap_w);
+    tma_prefetch_desc(&tmap_x);
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&tmem_full_bar[i], 1);
+      mbar_init(&tmem_empty_bar[i], 256);
+    }
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc2(tmem_slot, S::kTmemCols);
+    tmem_relinquish2();
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  cluster_sync();  // barriers of both CTAs initialised before anyone signals across
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  pdl_wait_prior_grids();
+
+  int my_tiles = 0;
+  for (int t = pair; t < p.tiles; t += num_pairs) ++my_tiles;
+  const long long total_kb = static_cast<long long>(my_tiles) * p.num_kb;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // producer of this CTA: its 128 weight rows and its 128 token rows of every k-block; bytes are counted on the
+      // leader's full barrier
+      long long it = 0;
+      bool ok = true;
+      for (int t = pair; t < p.tiles && ok; t += num_pairs) {
+        const int n0 = (t / p.tiles_m) * (2 * kBM) + static_cast<int>(rank) * kBM;
+        const int m0 = (t % p.tiles_m) * kBN + static_cast<int>(rank) * kBNHalf;
+        for (int kb = 0; kb < p.num_kb; ++kb, ++it) {
+          const int s = static_cast<int>(it % kStages);
+          if (it >= kStages && !mbar_wait(&empty_bar[s], static_cast<uint32_t>((it / kStages) - 1) & 1)) {
+            ok = false;
+            break;
+          }
+          uint8_t* st = smem + s * S::kStageBytes;
+          const uint32_t bar = map_to_rank(smem_u32(&full_bar[s]), 0);
+          if (leader) mbar_expect_tx(&full_bar[s], 2 * S::kStageBytes);
+          tma_load_2d_pair(st, &tmap_w, bar, kb * kBK, n0);
+          tma_load_2d_pair(st + S::kABytes, &tmap_x, bar, kb * kBK, m0);
+        }
+      }
+      if (!ok && p.status) atomicExch(p.status, kStatusTimeoutProducer);
+    }
+  } else if (warp == 1) {
+    if (leader && lane == 0) {
+      const uint32_t idesc = umma_idesc_f16(p.dtype == ORTB200_BF16, 2 * kBM, kBN);
+      long long it = 0;
+      int seg = 0;
+      bool ok = true;
+      for (int t = pair; t < p.tiles && ok; t += num_pairs, ++seg) {
+        const int buf = seg & 1;
+        const uint32_t tmem_d = tmem_base + buf * kBN;
+        if (seg >= 2 && !mbar_wait(&tmem_empty_bar[buf], ((seg >> 1) - 1) & 1)) {
+          ok = false;
+          break;
+        }
+        tcgen05_fence_after();
+        for (int kb = 0; kb < p.num_kb; ++kb, ++it) {
+          const int s = static_cast<int>(it % kStages);
+          if (!mbar_wait(&full_bar[s], static_cast<uint32_t>(it / kStages) & 1)) {
+            ok = false;
+            break;
+          }
+          tcgen05_fence_after();
+          const uint32_t a_addr = smem_u32(smem + s * S::kStageBytes);
+          const uint64_t adesc = umma_desc_sw128(a_addr);
+          const uint64_t bdesc = umma_desc_sw128(a_addr + S::kABytes);
+#pragma unroll
+          for (int k = 0; k < kBK / 16; ++k) umma2_f16(tmem_d, adesc + 2 * k, bdesc + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          umma2_commit_both(&empty_bar[s]);
+        }
+        umma2_commit_both(&tmem_full_bar[buf]);  // also after a failed wait, so the epilogues do not wait for nothing
+      }
+      if (!ok && p.status) atomicExch(p.status, kStatusTimeoutMma);
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue: this CTA's 128 weight rows x 256 tokens
+    const int q = warp & 3;
+    const int r = q * 32 + lane;
+    const int et = static_cast<int>(threadIdx.x) - 64;
+    uint16_t* stg = reinterpret_cast<uint16_t*>(smem + S::kStagingOffset);
+    const bool bf16 = p.dtype == ORTB200_BF16;
+    const bool vec_ok = (p.ldo % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0) &&
+                        (p.residual == nullptr || ((p.ldr % 8 == 0) && (reinterpret_cast<uintptr_t>(p.residual) & 15) == 0));
+    const uint32_t empty_remote0 = map_to_rank(smem_u32(&tmem_empty_bar[0]), 0);
+    const uint32_t empty_remote1 = map_to_rank(smem_u32(&tmem_empty_bar[1]), 0);
+    int seg = 0;
+    bool ok = true;
+    for (int t = pair; t < p.tiles && ok; t += num_pairs, ++seg) {
+      const int buf = seg & 1;
+      const int nrow0 = (t / p.tiles_m) * (2 * kBM) + static_cast<int>(rank) * kBM;
+      const int m0 = (t % p.tiles_m) * kBN;
+      const int n = nrow0 + r;
+      const uint32_t t_lane = tmem_base + buf * kBN + (static_cast<uint32_t>(q * 32) << 16);
+      if (!mbar_wait(&tmem_full_bar[buf], (seg >> 1) & 1)) {
+        ok = false;
+        if (p.status) atomicExch(p.status, kStatusTimeoutEpilogue);
+        break;
+      }
+      tcgen05_fence_after();
+      const float bias_v = (p.bias != nullptr && n < p.N)
+                               ? (bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.bias)[n])
+                                       : __half2float(reinterpret_cast<const __half*>(p.bias)[n]))
+                               : 0.0f;
+#pragma unroll 1
+      for (int pc = 0; pc < kBN; pc += 128) {
+        float v[128];
+#pragma unroll
+        for (int g4 = 0; g4 < 4; ++g4) tmem_ld_x32(t_lane + pc + g4 * 32, v + g4 * 32);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 128; ++j) {
+          const float y = v[j] * p.alpha + bias_v;
+          uint16_t bits;
+          if (bf16) {
+            const __nv_bfloat16 h = __float2bfloat16_rn(y);
+            bits = *reinterpret_cast<const uint16_t*>(&h);
+          } else {
+            const __half h = __float2half_rn(y);
+            bits = *reinterpret_cast<const uint16_t*>(&h);
+          }
+          stg[j * kBM + r] = bits;
+        }
+        if (pc + 128 >= kBN) {
+          // accumulator read completely: tell the leader's MMA warp (it counts the threads of both CTAs)
+          tcgen05_fence_before();
+          mbar_arrive_cluster(buf == 0 ? empty_remote0 : empty_remote1);
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        const bool post_act = p.act != ORTB200_ACT_NONE;
+        for (int idx = et; idx < 128 * 16; idx += 128) {
+          const int row = idx >> 4, ch = idx & 15;
+          const int m = m0 + pc + row;
+          const int nn = nrow0 + ch * 8;
+          if (m >= p.M || nn >= p.N) continue;
+          const uint4 val = *reinterpret_cast<const uint4*>(stg + row * kBM + ch * 8);
+          const long long o = static_cast<long long>(m) * p.ldo + nn;
+          if (vec_ok && nn + 8 <= p.N) {
+            uint4 res = val;
+            if (p.residual != nullptr || post_act) {
+              uint4 rr = make_uint4(0u, 0u, 0u, 0u);
+              if (p.residual != nullptr)
+                rr = __ldg(reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(p.residual) + static_cast<long long>(m) * p.ldr + nn));
+              const uint32_t a4[4] = {val.x, val.y, val.z, val.w};
+              const uint32_t b4[4] = {rr.x, rr.y, rr.z, rr.w};
+              uint32_t o4[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                float lo, hi, rlo, rhi;
+                if (bf16) {
+                  lo = __uint_as_float(a4[e] << 16); hi = __uint_as_float(a4[e] & 0xffff0000u);
+                  rlo = __uint_as_float(b4[e] << 16); rhi = __uint_as_float(b4[e] & 0xffff0000u);
+                } else {
+                  const float2 fa = __half22float2(*reinterpret_cast<const __half2*>(&a4[e]));
+                  const float2 fb = __half22float2(*reinterpret_cast<const __half2*>(&b4[e]));
+                  lo = fa.x; hi = fa.y; rlo = fb.x; rhi = fb.y;
+                }
+                if (post_act) {
+                  lo = act2(p.act, lo);
+                  hi = act2(p.act, hi);
+                }
+                lo += rlo;
+                hi += rhi;
+                if (bf16) {
+                  const __nv_bfloat162 h2 = __floats2bfloat162_rn(lo, hi);
+                  o4[e] = *reinterpret_cast<const uint32_t*>(&h2);
+                } else {
+                  const __half2 h2 = __floats2half2_rn(lo, hi);
+                  o4[e] = *reinterpret_cast<const uint32_t*>(&h2);
+                }
+              }
+              res = make_uint4(o4[0], o4[1], o4[2], o4[3]);
+            }
+            *reinterpret_cast<uint4*>(static_cast<uint16_t*>(p.out) + o) = res;
+          } else {
+            const uint16_t* sv = stg + row * kBM + ch * 8;
+            for (int e = 0; e < 8 && nn + e < p.N; ++e) {
+              float y = bf16 ? __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(sv + e)) : __half2float(*reinterpret_cast<const __half*>(sv + e));
+              if (post_act) y = act2(p.act, y);
+              if (p.residual != nullptr) {
+                const long long ri = static_cast<long long>(m) * p.ldr + nn + e;
+                y += bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.residual)[ri]) : __half2float(reinterpret_cast<const __half*>(p.residual)[ri]);
+              }
+              if (bf16) reinterpret_cast<__nv_bfloat16*>(p.out)[o + e] = __float2bfloat16_rn(y);
+              else reinterpret_cast<__half*>(p.out)[o + e] = __float2half_rn(y);
+            }
+          }
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+      }
+    }
+  }
+  (void)total_kb;
+
+  // nobody leaves (or frees tensor memory) while the peer may still be reading this CTA's shared memory
+  tcgen05_fence_before();
+  __syncthreads();
+  cluster_sync();
+  if (warp == 1) {
+    tcgen05_fence_after();
+    tmem_dealloc2(tmem_base, S::kTmemCols);
+  }
+}
+
+}  // namespace
+
+int launch_gemm_2cta(const ortb200_gemm_args* a, cudaStream_t stream) {
+  if (a->act == ORTB200_ACT_SWIGLU || a->in_dtype != 0 || a->world > 1 || a->rms_eps > 0.f) return -16;
+  CUtensorMap tw, tx;
+  const CUtensorMapDataType dt = a->dtype == ORTB200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  if (make_tensor_map_2d(&tw, a->w, dt, 2, a->K, a->w_rows, static_cast<int64_t>(a->K) * 2, kBK, kBM) != 0) return -6;
+  if (make_tensor_map_2d(&tx, a->x, dt, 2, a->K, a->M, static_cast<int64_t>(a->K) * 2, kBK, kBNHalf) != 0) return -6;
+  Gemm2Params p;
+  p.M = a->M; p.N = a->N; p.K = a->K; p.num_kb = (a->K + kBK - 1) / kBK;
+  const int tiles_n = (a->N + 2 * kBM - 1) / (2 * kBM);
+  p.tiles_m = (a->M + kBN - 1) / kBN;
+  p.tiles = tiles_n * p.tiles_m;
+  p.dtype = a->dtype; p.act = a->act; p.alpha = a->alpha; p.out = a->out; p.ldo = a->ldo; p.bias = a->bias;
+  p.residual = a->residual; p.ldr = a->ldr; p.status = a->status;
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  int pairs = sms / 2;
+  if (pairs > p.tiles) pairs = p.tiles;
+  if (pairs < 1) return -1;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(gemm_2cta_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem2::kTotal) != cudaSuccess) return -10;
+    attr_set = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * pairs, 1, 1);
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.dynamicSmemBytes = Smem2::kTotal;
+  cfg.stream = stream;
+  cudaLaunchAttribute attrs[2];
+  attrs[0].id = cudaLaunchAttributeClusterDimension;
+  attrs[0].val.clusterDim.x = 2;
+  attrs[0].val.clusterDim.y = 1;
+  attrs[0].val.clusterDim.z = 1;
+  int nattr = 1;
+  if (a->use_pdl) {
+    attrs[nattr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[nattr].val.programmaticStreamSerializationAllowed = 1;
+    ++nattr;
+  }
+  cfg.attrs = attrs;
+  cfg.numAttrs = nattr;
+  return cudaLaunchKernelEx(&cfg, gemm_2cta_kernel, tw, tx, p) == cudaSuccess ? 0 : -11;
+}
+
+}  // namespace ortb200

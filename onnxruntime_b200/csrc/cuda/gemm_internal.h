@@ -42,6 +42,9 @@ int launch_gemm_grouped(const ortb200_gemm_grouped_args* a, cudaStream_t stream)
 // The same on the persistent large-tile kernel (tile_rows 128 or 256).
 int launch_gemm_grouped_large(const ortb200_gemm_grouped_args* a, cudaStream_t stream);
 
+// Large-M GEMM on CTA pairs (gemm_2cta.cu): 256 x 256 tiles, tcgen05 cta_group::2.
+int launch_gemm_2cta(const ortb200_gemm_args* a, cudaStream_t stream);
+
 // bn in {16, 32, 64}.  Returns 0 or a negative launch error; reports the cluster size and pipeline depth used.
 int launch_gemm_smallm(const ortb200_gemm_args* a, int bn, cudaStream_t stream, int* cluster_out, int* stages_out);
 

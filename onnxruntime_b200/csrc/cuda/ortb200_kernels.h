@@ -90,7 +90,8 @@ typedef struct {
   //     [4096, 4608) row r at r * 4: the scales of elements [0, 32) and [32, 64) of the k-block, in `dtype`
   //     [4608, 4864) row r at r * 2: their zero points, one byte each (8 when the model has none)
   //   rows beyond N are zero.  W[n, k] = (q - zp) * scale.
-  int force_tile_rows;  // 0 / 128 = 128-weight-row CTA tiles; 256 = 256-row tiles in the large-M kernel (M > 128)
+  int force_tile_rows;  // 0 / 128 = 128-weight-row CTA tiles; 256 = 256-row tiles in the large-M kernel (M > 128);
+                        // 512 = pairs of CTAs on 256 x 256 tiles (cta_group::2 kernel)
 } ortb200_gemm_args;
 
 int ortb200_gemm(const ortb200_gemm_args* args, ortb200_stream_t stream);
