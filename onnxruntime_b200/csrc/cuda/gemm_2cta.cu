@@ -45,6 +45,11 @@ struct Gemm2Params {
   const void* residual;
   long long ldr;
   int* status;
+  // grouped mode (mixture of experts): token tiles of up to 256 rows from a device-side list
+  const int4* tile_info;   // {expert, first row, end row, -}; null = ordinary GEMM
+  const int* num_tiles;
+  int tiles_n;             // 256-row weight tiles per expert
+  int w_rows_per_expert;
 };
 
 struct Smem2 {
@@ -159,9 +164,10 @@ gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
 
   pdl_wait_prior_grids();
 
-  int my_tiles = 0;
-  for (int t = pair; t < p.tiles; t += num_pairs) ++my_tiles;
-  const long long total_kb = static_cast<long long>(my_tiles) * p.num_kb;
+  // grouped mode: the number of token tiles is a device-side value written by the routing kernels
+  const bool grouped = p.tile_info != nullptr;
+  const int tiles_m = grouped ? *p.num_tiles : p.tiles_m;
+  const int tiles = grouped ? p.tiles_n * tiles_m : p.tiles;
 
   if (warp == 0) {
     if (lane == 0) {
@@ -169,9 +175,14 @@ gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
       // leader's full barrier
       long long it = 0;
       bool ok = true;
-      for (int t = pair; t < p.tiles && ok; t += num_pairs) {
-        const int n0 = (t / p.tiles_m) * (2 * kBM) + static_cast<int>(rank) * kBM;
-        const int m0 = (t % p.tiles_m) * kBN + static_cast<int>(rank) * kBNHalf;
+      for (int t = pair; t < tiles && ok; t += num_pairs) {
+        int n0 = (t / tiles_m) * (2 * kBM) + static_cast<int>(rank) * kBM;
+        int m0 = (t % tiles_m) * kBN + static_cast<int>(rank) * kBNHalf;
+        if (grouped) {
+          const int4 ti = p.tile_info[t % tiles_m];
+          n0 += ti.x * p.w_rows_per_expert;
+          m0 = ti.y + static_cast<int>(rank) * kBNHalf;
+        }
         for (int kb = 0; kb < p.num_kb; ++kb, ++it) {
           const int s = static_cast<int>(it % kStages);
           if (it >= kStages && !mbar_wait(&empty_bar[s], static_cast<uint32_t>((it / kStages) - 1) & 1)) {
@@ -193,7 +204,7 @@ gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
       long long it = 0;
       int seg = 0;
       bool ok = true;
-      for (int t = pair; t < p.tiles && ok; t += num_pairs, ++seg) {
+      for (int t = pair; t < tiles && ok; t += num_pairs, ++seg) {
         const int buf = seg & 1;
         const uint32_t tmem_d = tmem_base + buf * kBN;
         if (seg >= 2 && !mbar_wait(&tmem_empty_bar[buf], ((seg >> 1) - 1) & 1)) {
@@ -232,10 +243,16 @@ gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
     const uint32_t empty_remote1 = map_to_rank(smem_u32(&tmem_empty_bar[1]), 0);
     int seg = 0;
     bool ok = true;
-    for (int t = pair; t < p.tiles && ok; t += num_pairs, ++seg) {
+    for (int t = pair; t < tiles && ok; t += num_pairs, ++seg) {
       const int buf = seg & 1;
-      const int nrow0 = (t / p.tiles_m) * (2 * kBM) + static_cast<int>(rank) * kBM;
-      const int m0 = (t % p.tiles_m) * kBN;
+      const int nrow0 = (t / tiles_m) * (2 * kBM) + static_cast<int>(rank) * kBM;
+      int m0 = (t % tiles_m) * kBN, m_end = p.M, bias0 = 0;
+      if (grouped) {
+        const int4 ti = p.tile_info[t % tiles_m];
+        m0 = ti.y;
+        m_end = ti.z;
+        bias0 = ti.x * p.N;
+      }
       const int n = nrow0 + r;
       const uint32_t t_lane = tmem_base + buf * kBN + (static_cast<uint32_t>(q * 32) << 16);
       if (!mbar_wait(&tmem_full_bar[buf], (seg >> 1) & 1)) {
@@ -245,8 +262,8 @@ gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
       }
       tcgen05_fence_after();
       const float bias_v = (p.bias != nullptr && n < p.N)
-                               ? (bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.bias)[n])
-                                       : __half2float(reinterpret_cast<const __half*>(p.bias)[n]))
+                               ? (bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.bias)[bias0 + n])
+                                       : __half2float(reinterpret_cast<const __half*>(p.bias)[bias0 + n]))
                                : 0.0f;
 #pragma unroll 1
       for (int pc = 0; pc < kBN; pc += 128) {
@@ -278,7 +295,7 @@ gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
           const int row = idx >> 4, ch = idx & 15;
           const int m = m0 + pc + row;
           const int nn = nrow0 + ch * 8;
-          if (m >= p.M || nn >= p.N) continue;
+          if (m >= m_end || nn >= p.N) continue;
           const uint4 val = *reinterpret_cast<const uint4*>(stg + row * kBM + ch * 8);
           const long long o = static_cast<long long>(m) * p.ldo + nn;
           if (vec_ok && nn + 8 <= p.N) {
@@ -336,7 +353,6 @@ gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
       }
     }
   }
-  (void)total_kb;
 
   // nobody leaves (or frees tensor memory) while the peer may still be reading this CTA's shared memory
   tcgen05_fence_before();
@@ -363,6 +379,7 @@ int launch_gemm_2cta(const ortb200_gemm_args* a, cudaStream_t stream) {
   p.tiles = tiles_n * p.tiles_m;
   p.dtype = a->dtype; p.act = a->act; p.alpha = a->alpha; p.out = a->out; p.ldo = a->ldo; p.bias = a->bias;
   p.residual = a->residual; p.ldr = a->ldr; p.status = a->status;
+  p.tile_info = nullptr; p.num_tiles = nullptr; p.tiles_n = 0; p.w_rows_per_expert = 0;
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
@@ -392,6 +409,47 @@ int launch_gemm_2cta(const ortb200_gemm_args* a, cudaStream_t stream) {
   }
   cfg.attrs = attrs;
   cfg.numAttrs = nattr;
+  return cudaLaunchKernelEx(&cfg, gemm_2cta_kernel, tw, tx, p) == cudaSuccess ? 0 : -11;
+}
+
+// Grouped GEMM (mixture of experts) on CTA pairs: 256-token tiles from the device-side tile list.
+int launch_gemm_grouped_2cta(const ortb200_gemm_grouped_args* a, cudaStream_t stream) {
+  if (a->act == ORTB200_ACT_SWIGLU || a->tile_rows != 256) return -16;
+  CUtensorMap tw, tx;
+  const CUtensorMapDataType dt = a->dtype == ORTB200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  const int64_t w_rows = static_cast<int64_t>(a->num_experts) * a->w_rows_per_expert;
+  if (make_tensor_map_2d(&tw, a->w, dt, 2, a->K, w_rows, static_cast<int64_t>(a->K) * 2, kBK, kBM) != 0) return -6;
+  if (make_tensor_map_2d(&tx, a->x, dt, 2, a->K, a->rows, static_cast<int64_t>(a->K) * 2, kBK, kBNHalf) != 0) return -6;
+  Gemm2Params p;
+  p.M = a->rows; p.N = a->N; p.K = a->K; p.num_kb = (a->K + kBK - 1) / kBK;
+  p.tiles_m = 0; p.tiles = 0;
+  p.dtype = a->dtype; p.act = a->act; p.alpha = 1.0f; p.out = a->out; p.ldo = a->N; p.bias = a->bias;
+  p.residual = nullptr; p.ldr = 0; p.status = a->status;
+  p.tile_info = static_cast<const int4*>(a->tile_info);
+  p.num_tiles = a->num_tiles;
+  p.tiles_n = (a->N + 2 * kBM - 1) / (2 * kBM);
+  p.w_rows_per_expert = a->w_rows_per_expert;
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int pairs = sms / 2;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(gemm_2cta_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem2::kTotal) != cudaSuccess) return -10;
+    attr_set = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * pairs, 1, 1);
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.dynamicSmemBytes = Smem2::kTotal;
+  cfg.stream = stream;
+  cudaLaunchAttribute attrs[1];
+  attrs[0].id = cudaLaunchAttributeClusterDimension;
+  attrs[0].val.clusterDim.x = 2;
+  attrs[0].val.clusterDim.y = 1;
+  attrs[0].val.clusterDim.z = 1;
+  cfg.attrs = attrs;
+  cfg.numAttrs = 1;
   return cudaLaunchKernelEx(&cfg, gemm_2cta_kernel, tw, tx, p) == cudaSuccess ? 0 : -11;
 }
 

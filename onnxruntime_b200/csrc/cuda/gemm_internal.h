@@ -44,6 +44,7 @@ int launch_gemm_grouped_large(const ortb200_gemm_grouped_args* a, cudaStream_t s
 
 // Large-M GEMM on CTA pairs (gemm_2cta.cu): 256 x 256 tiles, tcgen05 cta_group::2.
 int launch_gemm_2cta(const ortb200_gemm_args* a, cudaStream_t stream);
+int launch_gemm_grouped_2cta(const ortb200_gemm_grouped_args* a, cudaStream_t stream);
 
 // bn in {16, 32, 64}.  Returns 0 or a negative launch error; reports the cluster size and pipeline depth used.
 int launch_gemm_smallm(const ortb200_gemm_args* a, int bn, cudaStream_t stream, int* cluster_out, int* stages_out);

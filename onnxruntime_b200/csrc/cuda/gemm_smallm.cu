@@ -693,6 +693,7 @@ extern "C" int ortb200_gemm_grouped(const ortb200_gemm_grouped_args* a, ortb200_
   if (a->dtype != ORTB200_BF16 && a->dtype != ORTB200_F16) return -4;
   if (a->act == ORTB200_ACT_SWIGLU && a->dual_offset <= 0) return -2;
   if ((reinterpret_cast<uintptr_t>(a->x) | reinterpret_cast<uintptr_t>(a->w) | reinterpret_cast<uintptr_t>(a->tile_info)) & 15) return -3;
+  if (a->tile_rows == 256 && a->act != ORTB200_ACT_SWIGLU) return ortb200::launch_gemm_grouped_2cta(a, static_cast<cudaStream_t>(stream));
   if (a->tile_rows >= 128) return ortb200::launch_gemm_grouped_large(a, static_cast<cudaStream_t>(stream));
   return ortb200::launch_gemm_grouped(a, static_cast<cudaStream_t>(stream));
 }
