@@ -209,69 +209,89 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       }
       tcgen05_fence_after();
       const int key0 = kv_begin + t * kKT;
-      // pass 1: masked scores, row maximum
-      float m_new = m;
-#pragma unroll 1
-      for (int c = 0; c < kKT; c += 32) {
-        float v[32];
-        tmem_ld_x32(tmem_s + lane_addr + c, v);
-        tmem_ld_wait();
-        const unsigned keep = key_keep_bits(p.key_mask, b, p.kv_len, key0 + c, lane);
+      // Interior tiles (every key visible to every row of this query tile) skip the per-element mask logic.
+      const bool need_mask = (key0 + kKT > total) || (key0 + kKT > p.kv_len) || (p.key_mask != nullptr) || (p.window > 0) ||
+                             (p.causal && key0 + kKT - 1 > past + q0) || (p.softcap > 0.f);
+      // Scores of GL columns are fetched with back-to-back tensor-memory loads and one wait, then turned into
+      // base-2 logits in place (-inf where masked).  With a 64-wide head all 128 columns of the tile stay in
+      // registers between the maximum and the exponentials; with a 128-wide head two groups of 64 are read twice.
+      constexpr int GL = HD == 64 ? 128 : 64;
+      float sv[GL];
+      auto load_group = [&](int c0) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const int key = key0 + c + j;
-          bool valid = key < total && key < p.kv_len && ((keep >> j) & 1u);
-          if (p.causal) valid = valid && key <= pos;
-          if (p.window > 0) valid = valid && key > pos - p.window;
-          float sc = v[j];
-          if (p.softcap > 0.f) sc = p.softcap * tanhf(sc * p.scale / p.softcap) * 1.4426950408889634f;
-          else sc *= p.scale_log2;
-          if (valid) m_new = fmaxf(m_new, sc);
+        for (int g4 = 0; g4 < GL / 32; ++g4) tmem_ld_x32(tmem_s + lane_addr + c0 + g4 * 32, sv + g4 * 32);
+        tmem_ld_wait();
+        if (!need_mask) {
+#pragma unroll
+          for (int j = 0; j < GL; ++j) sv[j] *= p.scale_log2;
+        } else {
+#pragma unroll
+          for (int g4 = 0; g4 < GL / 32; ++g4) {
+            const unsigned keep = key_keep_bits(p.key_mask, b, p.kv_len, key0 + c0 + g4 * 32, lane);
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const int key = key0 + c0 + g4 * 32 + j;
+              bool valid = key < total && key < p.kv_len && ((keep >> j) & 1u);
+              if (p.causal) valid = valid && key <= pos;
+              if (p.window > 0) valid = valid && key > pos - p.window;
+              float sc = sv[g4 * 32 + j];
+              if (p.softcap > 0.f) sc = p.softcap * tanhf(sc * p.scale / p.softcap) * 1.4426950408889634f;
+              else sc *= p.scale_log2;
+              sv[g4 * 32 + j] = valid ? sc : -INFINITY;
+            }
+          }
+        }
+      };
+      auto store_probs = [&](int c0, float m_ref, float& row_sum) {
+#pragma unroll
+        for (int c = 0; c < GL; c += 32) {
+          uint32_t packed[16];
+#pragma unroll
+          for (int j = 0; j < 32; j += 2) {
+            const float p0 = m_ref == -INFINITY ? 0.f : exp2f(sv[c + j] - m_ref);
+            const float p1 = m_ref == -INFINITY ? 0.f : exp2f(sv[c + j + 1] - m_ref);
+            if (p.bf16) {
+              __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+              packed[j / 2] = *reinterpret_cast<uint32_t*>(&h);
+              row_sum += __bfloat162float(h.x) + __bfloat162float(h.y);
+            } else {
+              __half2 h = __floats2half2_rn(p0, p1);
+              packed[j / 2] = *reinterpret_cast<uint32_t*>(&h);
+              row_sum += __half2float(h.x) + __half2float(h.y);
+            }
+          }
+          // 32 keys = 4 chunks of 16 bytes; column cc lives in box cc / 64
+          const int cc = c0 + c;
+          const int box = cc / 64;
+#pragma unroll
+          for (int ch = 0; ch < 4; ++ch) {
+            const int chunk = ((cc % 64) * 2) / 16 + ch;
+            uint8_t* dst = p_smem + box * L::kBoxBytes + r * 128 + ((chunk ^ (r & 7)) << 4);
+            *reinterpret_cast<uint4*>(dst) = make_uint4(packed[ch * 4], packed[ch * 4 + 1], packed[ch * 4 + 2], packed[ch * 4 + 3]);
+          }
+        }
+      };
+      float m_new = m;
+      float row_sum = 0.f;
+      if (GL == kKT) {
+        load_group(0);
+#pragma unroll
+        for (int j = 0; j < GL; ++j) m_new = fmaxf(m_new, sv[j]);
+        store_probs(0, m_new, row_sum);
+      } else {
+#pragma unroll 1
+        for (int c0 = 0; c0 < kKT; c0 += GL) {
+          load_group(c0);
+#pragma unroll
+          for (int j = 0; j < GL; ++j) m_new = fmaxf(m_new, sv[j]);
+        }
+#pragma unroll 1
+        for (int c0 = 0; c0 < kKT; c0 += GL) {
+          load_group(c0);
+          store_probs(c0, m_new, row_sum);
         }
       }
       const float corr = m == -INFINITY ? 0.f : exp2f(m - m_new);
-      // pass 2: probabilities -> shared memory (bf16 / fp16), row sum
-      float row_sum = 0.f;
-#pragma unroll 1
-      for (int c = 0; c < kKT; c += 32) {
-        float v[32];
-        tmem_ld_x32(tmem_s + lane_addr + c, v);
-        tmem_ld_wait();
-        uint32_t packed[16];
-        const unsigned keep = key_keep_bits(p.key_mask, b, p.kv_len, key0 + c, lane);
-#pragma unroll
-        for (int j = 0; j < 32; j += 2) {
-          float pr[2];
-#pragma unroll
-          for (int u = 0; u < 2; ++u) {
-            const int key = key0 + c + j + u;
-            bool valid = key < total && key < p.kv_len && ((keep >> (j + u)) & 1u);
-            if (p.causal) valid = valid && key <= pos;
-            if (p.window > 0) valid = valid && key > pos - p.window;
-            float sc = v[j + u];
-            if (p.softcap > 0.f) sc = p.softcap * tanhf(sc * p.scale / p.softcap) * 1.4426950408889634f;
-            else sc *= p.scale_log2;
-            pr[u] = (valid && m_new != -INFINITY) ? exp2f(sc - m_new) : 0.f;
-          }
-          if (p.bf16) {
-            __nv_bfloat162 h = __floats2bfloat162_rn(pr[0], pr[1]);
-            packed[j / 2] = *reinterpret_cast<uint32_t*>(&h);
-            row_sum += __bfloat162float(h.x) + __bfloat162float(h.y);
-          } else {
-            __half2 h = __floats2half2_rn(pr[0], pr[1]);
-            packed[j / 2] = *reinterpret_cast<uint32_t*>(&h);
-            row_sum += __half2float(h.x) + __half2float(h.y);
-          }
-        }
-        // 32 keys = 4 chunks of 16 bytes; column c lives in box c / 64
-        const int box = c / 64;
-#pragma unroll
-        for (int ch = 0; ch < 4; ++ch) {
-          const int chunk = ((c % 64) * 2) / 16 + ch;
-          uint8_t* dst = p_smem + box * L::kBoxBytes + r * 128 + ((chunk ^ (r & 7)) << 4);
-          *reinterpret_cast<uint4*>(dst) = make_uint4(packed[ch * 4], packed[ch * 4 + 1], packed[ch * 4 + 2], packed[ch * 4 + 3]);
-        }
-      }
       l = l * corr + row_sum;
       m = m_new;
       // make the generic-proxy writes of P visible to the tensor core, then publish

@@ -73,10 +73,27 @@ def rope_caches(cfg: LlamaConfig, device="cpu") -> Tuple[torch.Tensor, torch.Ten
 
 def build_llama(cfg: LlamaConfig, tp_rank: int = 0, tp_size: int = 1, external_weights: bool = False, seed: int = 0,
                 device: str = "cpu", with_argmax: bool = True, last_token_logits: bool = True,
-                weight_std: float = 0.02, shard_lm_head: bool = True) -> Tuple[bytes, Dict[str, torch.Tensor]]:
+                weight_std: float = 0.02, shard_lm_head: bool = True, quant_bits: int = 0,
+                quant_block: int = 32, paged: bool = False) -> Tuple[bytes, Dict[str, torch.Tensor]]:
     """Returns (ModelProto bytes, weights).  With ``external_weights`` the dict holds every weight (on
     ``device``) to pass to ``SessionOptions.add_external_initializers``; otherwise it is empty and the
-    weights are embedded in the model."""
+    weights are embedded in the model.
+
+    ``quant_bits=4`` emits the seven projections of every layer as ``com.microsoft.MatMulNBits`` (symmetric
+    blocks of ``quant_block`` weights along K, packed two per byte, one scale per block: the layout of
+    onnxruntime/contrib_ops/cpu/quantization/matmul_nbits.cc) the way the reference's 4-bit exporters do;
+    the embedding and the LM head stay in the compute type.
+
+    ``paged=True`` builds the serving form: tokens of all sequences packed along one axis (``input_ids``
+    [tokens]), ``com.microsoft.PagedAttention`` over block caches ``key_cache.{i}`` / ``value_cache.{i}``
+    [num_blocks, block_size, kv_heads, head_dim] shared by all sequences through ``block_table``, with
+    ``cumulative_sequence_length`` and ``past_seqlens`` describing the packing (input order of
+    onnxruntime/core/graph/contrib_ops/bert_defs.cc, PagedAttention); ``logits_indices`` [rows] picks the
+    packed positions whose logits are wanted (the last token of every sequence), so the LM head runs on those
+    rows only."""
+    if paged:
+        last_token_logits = False
+    assert quant_bits in (0, 4)
     assert cfg.num_heads % tp_size == 0 and cfg.num_kv_heads % tp_size == 0 and cfg.ffn_size % tp_size == 0
     dt, odt = _TORCH_DT[cfg.dtype], _ONNX_DT[cfg.dtype]
     N, Nk, H = cfg.num_heads // tp_size, cfg.num_kv_heads // tp_size, cfg.head_dim
@@ -104,9 +121,45 @@ def build_llama(cfg: LlamaConfig, tp_rank: int = 0, tp_size: int = 1, external_w
     def add_weight(name: str, w: torch.Tensor) -> None:
         if external_weights:
             weights[name] = w
-            inits.append(ol.make_external_tensor(name, odt if w.dtype == dt else T.FLOAT, w.shape))
+            onnx_type = odt if w.dtype == dt else (T.UINT8 if w.dtype == torch.uint8 else T.FLOAT)
+            inits.append(ol.make_external_tensor(name, onnx_type, w.shape))
         else:
             inits.append(ol.make_tensor(name, w))
+
+    def linear(x: str, weight: str, k: int, n: int, out: str, node_name: str, shard: Optional[Tuple[int, int]] = None,
+               dense: Optional[torch.Tensor] = None, full_n: Optional[int] = None,
+               columns: Optional[torch.Tensor] = None) -> None:
+        """out = x @ W with W [k, n] (this rank's shard; ``shard`` = (axis, parts) of the full matrix, or the
+        already sharded ``dense`` matrix, which is columns ``columns`` of a ``full_n`` wide one), as MatMul or as
+        MatMulNBits over randomly drawn 4-bit blocks."""
+        if not quant_bits:
+            if dense is not None:
+                add_weight(weight, dense)
+            else:
+                randn(weight, (k, n), shard=shard)
+            nodes.append(ol.make_node("MatMul", [x, weight], [out], name=node_name))
+            return
+        assert k % quant_block == 0
+        gen.manual_seed(seed * 1000003 + zlib.crc32(weight.encode()))
+        full_n, full_k = full_n or n, k
+        if shard is not None:
+            full_k, full_n = (k * shard[1], n) if shard[0] == 0 else (k, n * shard[1])
+        # packed [N, K/block, block/2] bytes and [N, K/block] scales; scale so that a dequantised weight has
+        # about the standard deviation of the dense initialisation (a uniform nibble minus 8 has sigma 4.6)
+        packed = torch.randint(0, 256, (full_n, full_k // quant_block, quant_block // 2), generator=gen, device=device,
+                               dtype=torch.uint8)
+        scales = ((torch.rand((full_n, full_k // quant_block), generator=gen, device=device) * 0.5 + 0.75)
+                  * (weight_std / 4.6)).to(dt)
+        if shard is not None:
+            axis = 1 if shard[0] == 0 else 0          # K shards are block ranges, N shards are row ranges
+            packed = packed.chunk(shard[1], dim=axis)[tp_rank].contiguous()
+            scales = scales.chunk(shard[1], dim=axis)[tp_rank].contiguous()
+        if columns is not None:
+            packed, scales = packed[columns].contiguous(), scales[columns].contiguous()
+        add_weight(weight + ".q4", packed)
+        add_weight(weight + ".scales", scales)
+        nodes.append(ol.make_node("MatMulNBits", [x, weight + ".q4", weight + ".scales"], [out], name=node_name,
+                                  domain="com.microsoft", K=k, N=n, bits=quant_bits, block_size=quant_block))
 
     def ones(name: str, n: int) -> str:
         add_weight(name, torch.ones(n, dtype=dt, device=device))
@@ -121,11 +174,20 @@ def build_llama(cfg: LlamaConfig, tp_rank: int = 0, tp_size: int = 1, external_w
 
     residual = "hidden_0"   # running residual stream
     pending = None          # output of the previous block still to be added to the residual
-    inputs = [
-        ol.make_tensor_value_info("input_ids", T.INT64, ["batch", "seq"]),
-        ol.make_tensor_value_info("seqlens_k", T.INT32, ["batch"]),
-        ol.make_tensor_value_info("total_sequence_length", T.INT32, []),
-    ]
+    if paged:
+        inputs = [
+            ol.make_tensor_value_info("input_ids", T.INT64, ["tokens"]),
+            ol.make_tensor_value_info("cumulative_sequence_length", T.INT32, ["batch_plus_1"]),
+            ol.make_tensor_value_info("past_seqlens", T.INT32, ["batch"]),
+            ol.make_tensor_value_info("block_table", T.INT32, ["batch", "max_blocks"]),
+            ol.make_tensor_value_info("logits_indices", T.INT64, ["rows"]),
+        ]
+    else:
+        inputs = [
+            ol.make_tensor_value_info("input_ids", T.INT64, ["batch", "seq"]),
+            ol.make_tensor_value_info("seqlens_k", T.INT32, ["batch"]),
+            ol.make_tensor_value_info("total_sequence_length", T.INT32, []),
+        ]
     outputs = []
     for i in range(cfg.num_layers):
         p = f"model.layers.{i}"
@@ -146,21 +208,35 @@ def build_llama(cfg: LlamaConfig, tp_rank: int = 0, tp_size: int = 1, external_w
         wqkv = torch.cat([q_full.chunk(tp_size, 1)[tp_rank], k_full.chunk(tp_size, 1)[tp_rank],
                           v_full.chunk(tp_size, 1)[tp_rank]], dim=1).contiguous()
         del full, q_full, k_full, v_full
-        add_weight(f"{p}.attn.qkv_proj.weight", wqkv)
-        nodes.append(ol.make_node("MatMul", [f"{p}.ln1_out", f"{p}.attn.qkv_proj.weight"], [f"{p}.qkv"], name=f"{p}.qkv_proj"))
-        inputs.append(ol.make_tensor_value_info(f"past_key_values.{i}.key", odt, ["batch", Nk, "past_seq", H]))
-        inputs.append(ol.make_tensor_value_info(f"past_key_values.{i}.value", odt, ["batch", Nk, "past_seq", H]))
-        outputs.append(ol.make_tensor_value_info(f"present.{i}.key", odt, ["batch", Nk, "present_seq", H]))
-        outputs.append(ol.make_tensor_value_info(f"present.{i}.value", odt, ["batch", Nk, "present_seq", H]))
-        nodes.append(ol.make_node(
-            "GroupQueryAttention",
-            [f"{p}.qkv", "", "", f"past_key_values.{i}.key", f"past_key_values.{i}.value", "seqlens_k",
-             "total_sequence_length", "cos_cache", "sin_cache"],
-            [f"{p}.attn_out", f"present.{i}.key", f"present.{i}.value"], name=f"{p}.attn", domain="com.microsoft",
-            num_heads=N, kv_num_heads=Nk, do_rotary=1, rotary_interleaved=0))
-        randn(f"{p}.attn.o_proj.weight", (N * H, hidden), shard=(0, tp_size))
-        nodes.append(ol.make_node("MatMul", [f"{p}.attn_out", f"{p}.attn.o_proj.weight"], [f"{p}.o_partial" if tp_size > 1 else f"{p}.o"],
-                                  name=f"{p}.o_proj"))
+        nq, nkv = cfg.num_heads * H, cfg.num_kv_heads * H
+        cols = torch.cat([torch.arange(nq, device=device).chunk(tp_size)[tp_rank],
+                          nq + torch.arange(nkv, device=device).chunk(tp_size)[tp_rank],
+                          nq + nkv + torch.arange(nkv, device=device).chunk(tp_size)[tp_rank]])
+        linear(f"{p}.ln1_out", f"{p}.attn.qkv_proj.weight", hidden, wqkv.shape[1], f"{p}.qkv", f"{p}.qkv_proj", dense=wqkv,
+               full_n=nq + 2 * nkv, columns=cols)
+        if paged:
+            for kv in ("key", "value"):
+                inputs.append(ol.make_tensor_value_info(f"{kv}_cache.{i}", odt, ["num_blocks", "block_size", Nk, H]))
+                outputs.append(ol.make_tensor_value_info(f"{kv}_cache_out.{i}", odt, ["num_blocks", "block_size", Nk, H]))
+            nodes.append(ol.make_node(
+                "PagedAttention",
+                [f"{p}.qkv", "", "", f"key_cache.{i}", f"value_cache.{i}", "cumulative_sequence_length", "past_seqlens",
+                 "block_table", "cos_cache", "sin_cache"],
+                [f"{p}.attn_out", f"key_cache_out.{i}", f"value_cache_out.{i}"], name=f"{p}.attn", domain="com.microsoft",
+                num_heads=N, kv_num_heads=Nk, do_rotary=1, rotary_interleaved=0))
+        else:
+            inputs.append(ol.make_tensor_value_info(f"past_key_values.{i}.key", odt, ["batch", Nk, "past_seq", H]))
+            inputs.append(ol.make_tensor_value_info(f"past_key_values.{i}.value", odt, ["batch", Nk, "past_seq", H]))
+            outputs.append(ol.make_tensor_value_info(f"present.{i}.key", odt, ["batch", Nk, "present_seq", H]))
+            outputs.append(ol.make_tensor_value_info(f"present.{i}.value", odt, ["batch", Nk, "present_seq", H]))
+            nodes.append(ol.make_node(
+                "GroupQueryAttention",
+                [f"{p}.qkv", "", "", f"past_key_values.{i}.key", f"past_key_values.{i}.value", "seqlens_k",
+                 "total_sequence_length", "cos_cache", "sin_cache"],
+                [f"{p}.attn_out", f"present.{i}.key", f"present.{i}.value"], name=f"{p}.attn", domain="com.microsoft",
+                num_heads=N, kv_num_heads=Nk, do_rotary=1, rotary_interleaved=0))
+        linear(f"{p}.attn_out", f"{p}.attn.o_proj.weight", N * H, hidden, f"{p}.o_partial" if tp_size > 1 else f"{p}.o",
+               f"{p}.o_proj", shard=(0, tp_size))
         if tp_size > 1:
             nodes.append(ol.make_node("AllReduce", [f"{p}.o_partial"], [f"{p}.o"], name=f"{p}.o_allreduce", domain="com.microsoft"))
         ln2 = ones(f"{p}.post_attention_layernorm.weight", hidden)
@@ -168,18 +244,15 @@ def build_llama(cfg: LlamaConfig, tp_rank: int = 0, tp_size: int = 1, external_w
                                   [f"{p}.ln2_out", "", "", f"{p}.res2"], name=f"{p}.ln2", domain="com.microsoft",
                                   epsilon=cfg.rms_eps))
         residual = f"{p}.res2"
-        randn(f"{p}.mlp.gate_proj.weight", (hidden, ffn), shard=(1, tp_size))
-        randn(f"{p}.mlp.up_proj.weight", (hidden, ffn), shard=(1, tp_size))
-        randn(f"{p}.mlp.down_proj.weight", (ffn, hidden), shard=(0, tp_size))
+        linear(f"{p}.ln2_out", f"{p}.mlp.gate_proj.weight", hidden, ffn, f"{p}.gate", f"{p}.gate_proj", shard=(1, tp_size))
+        linear(f"{p}.ln2_out", f"{p}.mlp.up_proj.weight", hidden, ffn, f"{p}.up", f"{p}.up_proj", shard=(1, tp_size))
         nodes += [
-            ol.make_node("MatMul", [f"{p}.ln2_out", f"{p}.mlp.gate_proj.weight"], [f"{p}.gate"], name=f"{p}.gate_proj"),
-            ol.make_node("MatMul", [f"{p}.ln2_out", f"{p}.mlp.up_proj.weight"], [f"{p}.up"], name=f"{p}.up_proj"),
             ol.make_node("Sigmoid", [f"{p}.gate"], [f"{p}.gate_sig"], name=f"{p}.sigmoid"),
             ol.make_node("Mul", [f"{p}.gate", f"{p}.gate_sig"], [f"{p}.gate_act"], name=f"{p}.silu"),
             ol.make_node("Mul", [f"{p}.gate_act", f"{p}.up"], [f"{p}.mlp_h"], name=f"{p}.gate_mul"),
-            ol.make_node("MatMul", [f"{p}.mlp_h", f"{p}.mlp.down_proj.weight"],
-                         [f"{p}.down_partial" if tp_size > 1 else f"{p}.down"], name=f"{p}.down_proj"),
         ]
+        linear(f"{p}.mlp_h", f"{p}.mlp.down_proj.weight", ffn, hidden, f"{p}.down_partial" if tp_size > 1 else f"{p}.down",
+               f"{p}.down_proj", shard=(0, tp_size))
         if tp_size > 1:
             nodes.append(ol.make_node("AllReduce", [f"{p}.down_partial"], [f"{p}.down"], name=f"{p}.down_allreduce",
                                       domain="com.microsoft"))
@@ -193,24 +266,37 @@ def build_llama(cfg: LlamaConfig, tp_rank: int = 0, tp_size: int = 1, external_w
         inits.append(ol.make_tensor("last_index", np.array([-1], dtype=np.int64)))
         nodes.append(ol.make_node("Gather", ["final_norm", "last_index"], ["final_last"], name="last_token", axis=1))
         head_in = "final_last"
+    if paged:
+        nodes.append(ol.make_node("Gather", ["final_norm", "logits_indices"], ["final_rows"], name="logit_rows", axis=0))
+        head_in = "final_rows"
     if tp_size > 1 and shard_lm_head and cfg.vocab_size % tp_size == 0:
         # vocabulary-parallel head: every rank computes its slice of the logits, an all-gather along the last axis
         # puts them together (the full-vocabulary product would otherwise be repeated on every rank)
         randn("lm_head.weight", (hidden, cfg.vocab_size // tp_size), shard=(1, tp_size))
         nodes.append(ol.make_node("MatMul", [head_in, "lm_head.weight"], ["logits_shard"], name="lm_head"))
         nodes.append(ol.make_node("AllGather", ["logits_shard"], ["logits"], name="lm_head_allgather", domain="com.microsoft",
-                                  axis=2, group_size=tp_size))
+                                  axis=1 if paged else 2, group_size=tp_size))
     else:
         randn("lm_head.weight", (hidden, cfg.vocab_size))
         nodes.append(ol.make_node("MatMul", [head_in, "lm_head.weight"], ["logits"], name="lm_head"))
-    outputs.insert(0, ol.make_tensor_value_info("logits", odt, ["batch", 1 if last_token_logits else "seq", cfg.vocab_size]))
+    logits_shape = ["rows"] if paged else ["batch", 1 if last_token_logits else "seq"]
+    outputs.insert(0, ol.make_tensor_value_info("logits", odt, logits_shape + [cfg.vocab_size]))
     if with_argmax:
         nodes.append(ol.make_node("ArgMax", ["logits"], ["next_tokens"], name="greedy", axis=-1, keepdims=0))
-        outputs.insert(1, ol.make_tensor_value_info("next_tokens", T.INT64, ["batch", 1 if last_token_logits else "seq"]))
+        outputs.insert(1, ol.make_tensor_value_info("next_tokens", T.INT64, logits_shape))
     graph = ol.make_graph(nodes, "llama", inputs, outputs, inits)
     meta = {"tp_rank": str(tp_rank), "tp_size": str(tp_size), "architecture": "llama"}
     model = ol.make_model(graph, opset=17, metadata=meta)
     return model.serialize(), weights
+
+
+def empty_paged_cache(cfg: LlamaConfig, num_blocks: int, block_size: int, device,
+                      tp_size: int = 1) -> List[Tuple[torch.Tensor, torch.Tensor]]:
+    """Per layer (key_cache, value_cache) of shape [num_blocks, block_size, kv_heads / tp, head_dim]."""
+    dt = _TORCH_DT[cfg.dtype]
+    nk = cfg.num_kv_heads // tp_size
+    return [(torch.zeros(num_blocks, block_size, nk, cfg.head_dim, dtype=dt, device=device),
+             torch.zeros(num_blocks, block_size, nk, cfg.head_dim, dtype=dt, device=device)) for _ in range(cfg.num_layers)]
 
 
 def empty_kv_cache(cfg: LlamaConfig, batch: int, max_len: int, device, tp_size: int = 1) -> List[Tuple[torch.Tensor, torch.Tensor]]:

@@ -93,7 +93,8 @@ def case_llama_tp(info, device, out):
     dtype = "fp32" if device == "cpu" else "bf16"
     cfg = LlamaConfig.tiny(dtype=dtype, head_dim=64, hidden_size=256, ffn_size=512, num_layers=2, num_heads=8, num_kv_heads=4,
                            max_seq_len=128)
-    model, _ = build_llama(cfg, tp_rank=r, tp_size=w, weight_std=0.05)
+    quant = int(os.environ.get("ORTB200_TEST_QUANT", "0"))
+    model, _ = build_llama(cfg, tp_rank=r, tp_size=w, weight_std=0.05, quant_bits=quant)
     opts = {}
     if device == "cuda":
         torch.cuda.set_device(info.local_rank)
@@ -125,7 +126,7 @@ def case_llama_tp(info, device, out):
     res = {"logits": torch.stack(logits), "ops": ops, "fused": fused}
     if r == 0:
         # single-rank run of the unsharded model for comparison
-        full, _ = build_llama(cfg, weight_std=0.05)
+        full, _ = build_llama(cfg, weight_std=0.05, quant_bits=quant)
         s1 = ort.InferenceSession(full, providers=["CPUExecutionProvider"] if device == "cpu" else [("CUDAExecutionProvider", {"device_id": str(info.local_rank)})],
                                   enable_fallback=False)
         r1 = DecoderRunner(s1, cfg, batch=2, max_len=96, device=dev)

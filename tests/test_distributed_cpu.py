@@ -61,6 +61,15 @@ def test_llama_tensor_parallel_matches_single_rank(tmp_path):
     np.testing.assert_allclose(out[0]["logits"].numpy(), out[0]["ref"].numpy(), rtol=2e-3, atol=2e-3)
 
 
+def test_int4_llama_tensor_parallel_matches_single_rank(tmp_path, monkeypatch):
+    """The 4-bit model shards its packed blocks (rows for column-parallel, block ranges for row-parallel
+    projections); two ranks must reproduce the single-rank logits."""
+    monkeypatch.setenv("ORTB200_TEST_QUANT", "4")
+    out = launch("llama_tp", "cpu", 2, tmp_path)
+    assert "MatMulNBits" in out[0]["ops"] and "AllReduce" in out[0]["ops"]
+    np.testing.assert_allclose(out[0]["logits"].numpy(), out[0]["ref"].numpy(), rtol=2e-3, atol=2e-3)
+
+
 def test_sharding_spec_algebra():
     from onnxruntime_b200 import _core as C
     d = C.parse_shard_spec("RS[0]", [0, 1, 2, 3], [4])
