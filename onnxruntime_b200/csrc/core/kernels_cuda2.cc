@@ -329,6 +329,7 @@ class GqaKernel final : public WithFallback {
       pa.first_prompt = first_prompt ? 1 : 0;
       pa.do_rotary = do_rotary_ ? 1 : 0;
       pa.dtype = dt;
+      pa.use_pdl = ctx.session()->config().Get("ortb200.pdl", "0") == "1" ? 1 : 0;
       CheckLaunch(ortb200_gqa_prep(&pa, ctx.cuda_stream()), "ortb200_gqa_prep");
       ctx.session()->AddLaunches(1);
     }
@@ -362,6 +363,8 @@ class GqaKernel final : public WithFallback {
       da.dtype = dt;
       da.use_pdl = ctx.session()->config().Get("ortb200.pdl", "0") == "1" ? 1 : 0;
       da.status = ctx.session()->StatusWord().data_ptr<int>();
+      // "0" picks (the tcgen05 kernel where it applies), "1" forces the CUDA-core split-KV kernel
+      da.algo = ctx.session()->config().Get("ortb200.decode_attention_algo", "0") == "1" ? 1 : 0;
       CheckLaunch(ortb200_gqa_decode(&da, ctx.cuda_stream()), "ortb200_gqa_decode");
       ctx.session()->AddLaunches(1);
     } else {

@@ -202,6 +202,7 @@ class PagedAttentionKernel final : public WithFallback {
     da.block_table = tb.data_ptr<int>();
     da.block_size = static_cast<int>(block_size);
     da.max_blocks = static_cast<int>(tb.size(1));
+    da.num_blocks = static_cast<int>(num_blocks);
     CheckLaunch(ortb200_gqa_decode(&da, ctx.cuda_stream()), "ortb200_gqa_decode(paged)");
     ctx.session()->AddLaunches(2);
     ctx.SetOutput(0, out);

@@ -18,6 +18,7 @@
 #include <math.h>
 #include "ortb200_kernels.h"
 #include "ptx_sm100.cuh"
+#include "gqa_internal.h"
 
 namespace ortb200 {
 
@@ -29,6 +30,7 @@ __global__ void __launch_bounds__(256) gqa_prep_kernel(const ortb200_gqa_prep_ar
   const int rot = a.rot_dim > 0 ? a.rot_dim : H;
   const int half = rot / 2;
   const int heads = a.N + 2 * a.Nk;
+  pdl_launch_dependents();  // the attention kernel may set up; it waits for this grid before reading q or the caches
   pdl_wait_prior_grids();
   const int past = a.first_prompt ? 0 : a.seqlens_k[b] + 1 - a.S;
   const long long pos = a.position_ids ? a.position_ids[static_cast<long long>(b) * a.S + s] : past + s;
@@ -83,7 +85,6 @@ __global__ void __launch_bounds__(256) gqa_prep_kernel(const ortb200_gqa_prep_ar
       dst[e1] = src[e1];
     }
   }
-  pdl_launch_dependents();
 }
 
 // ------------------------------------------------------------ paged prep
@@ -161,36 +162,6 @@ __global__ void __launch_bounds__(256) paged_prep_kernel(const ortb200_paged_pre
 }
 
 // ---------------------------------------------------------------- decode
-struct DecodeParams {
-  const void* q;
-  const void* k_cache;
-  const void* v_cache;
-  const int* seqlens_k;
-  const void* head_sink;
-  void* out;
-  float* ws;
-  unsigned int* counters;
-  int* status;
-  int B, N, Nk, Smax, splits, window, gparts;
-  float scale, softcap;
-  // paged cache [num_blocks, block_size, Nk, H]: key j of sequence b lives in block block_table[b, j / block_size]
-  const int* block_table;
-  int block_size, max_blocks;
-  // fused "unpack + rotary + append" (one new token per sequence): q, k and v are read from the packed projection
-  // output qkv [B, (N + 2 Nk) H]; the CTA whose key range ends at the new position rotates the new key, writes
-  // key and value into the cache and attends to them from registers
-  const void* qkv;
-  const void* cos_cache;
-  const void* sin_cache;
-  int do_rotary, interleaved;
-};
-
-// Running maxima start at a large negative finite value so that exp(m_old - m_new) never sees inf - inf.
-constexpr float kNegBig = -1.0e30f;
-__device__ __forceinline__ float safe_exp_diff(float a, float b) {
-  return a <= kNegBig ? 0.f : __expf(a - b);
-}
-
 constexpr int kDecTile = 32;    // keys per pipeline stage
 constexpr int kDecStages = 4;
 
@@ -513,65 +484,7 @@ __global__ void __launch_bounds__(128) gqa_decode_kernel(const DecodeParams p) {
     fa[g] = aa;
   }
 
-  bool finalize = true;
-  if (p.splits > 1) {
-    // publish partial state: ws[tile][split][g][H + 2]
-    float* my = p.ws + ((static_cast<size_t>(tile) * p.splits + split) * G) * (H + 2);
-#pragma unroll
-    for (int g = 0; g < G; ++g) {
-      if (owner) my[g * (H + 2) + tid] = fa[g];
-      if (tid == 0) {
-        my[g * (H + 2) + H] = fm[g];
-        my[g * (H + 2) + H + 1] = fl[g];
-      }
-    }
-    __threadfence();
-    __syncthreads();
-    if (tid == 0) {
-      const unsigned int old = atomicAdd(&p.counters[tile], 1u);
-      const unsigned int last = old == static_cast<unsigned int>(p.splits - 1) ? 1u : 0u;
-      if (last) p.counters[tile] = 0;
-      sm_last = last;
-    }
-    __syncthreads();
-    finalize = sm_last != 0;
-    if (finalize) {
-      __threadfence();
-      const float* base = p.ws + (static_cast<size_t>(tile) * p.splits * G) * (H + 2);
-#pragma unroll
-      for (int g = 0; g < G; ++g) {
-        float mm = kNegBig;
-        for (int s = 0; s < p.splits; ++s) mm = fmaxf(mm, __ldcg(&base[(s * G + g) * (H + 2) + H]));
-        float ll = 0.f, aa = 0.f;
-        for (int s = 0; s < p.splits; ++s) {
-          const float* ps = base + (s * G + g) * (H + 2);
-          const float c = safe_exp_diff(__ldcg(&ps[H]), mm);
-          ll += __ldcg(&ps[H + 1]) * c;
-          if (owner) aa += __ldcg(&ps[tid]) * c;
-        }
-        fm[g] = mm;
-        fl[g] = ll;
-        fa[g] = aa;
-      }
-    }
-  }
-  pdl_launch_dependents();
-  if (finalize && owner) {
-#pragma unroll
-    for (int g = 0; g < G; ++g) {
-      if (g >= n_heads) break;
-      float ll = fl[g];
-      if (p.head_sink) {
-        const float sink = to_float<T>(static_cast<const T*>(p.head_sink)[head0 + g]);
-        const float mm = fmaxf(fm[g], sink);
-        const float c = safe_exp_diff(fm[g], mm);
-        ll = ll * c + __expf(sink - mm);
-        fa[g] *= c;
-      }
-      const float o = ll > 0.f ? fa[g] / ll : 0.f;
-      static_cast<T*>(p.out)[(static_cast<long long>(b) * p.N + head0 + g) * H + tid] = from_float<T>(o);
-    }
-  }
+  decode_finish<T, H, G>(p, tile, split, b, head0, n_heads, tid, fm, fl, fa, &sm_last);
 }
 
 
@@ -657,6 +570,8 @@ extern "C" int ortb200_gqa_decode(const ortb200_gqa_decode_args* a, ortb200_stre
   if (a->block_table && (a->block_size <= 0 || a->max_blocks <= 0)) return -1;
   if (a->H != 64 && a->H != 128) return -2;
   if ((reinterpret_cast<uintptr_t>(a->k_cache) | reinterpret_cast<uintptr_t>(a->v_cache)) & 15) return -3;
+  if (a->algo == 2 && !gqa_decode_tc_supported(a)) return -6;
+  if (a->algo != 1 && gqa_decode_tc_supported(a)) return launch_gqa_decode_tc(a, stream);
   if (a->dtype == ORTB200_BF16) {
     return a->H == 128 ? launch_decode<__nv_bfloat16, 128>(a, stream) : launch_decode<__nv_bfloat16, 64>(a, stream);
   } else if (a->dtype == ORTB200_F16) {
@@ -697,8 +612,20 @@ extern "C" int ortb200_gqa_prep(const ortb200_gqa_prep_args* a, ortb200_stream_t
   }
   dim3 grid(static_cast<unsigned>(tokens), static_cast<unsigned>(ygroups));
   const int threads = ygroups > 1 ? 128 : 256;
-  if (a->dtype == ORTB200_BF16) gqa_prep_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(*a);
-  else if (a->dtype == ORTB200_F16) gqa_prep_kernel<__half><<<grid, threads, 0, stream>>>(*a);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(threads, 1, 1);
+  cfg.stream = stream;
+  cudaLaunchAttribute attrs[1];
+  if (a->use_pdl) {
+    attrs[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attrs;
+    cfg.numAttrs = 1;
+  }
+  cudaError_t e;
+  if (a->dtype == ORTB200_BF16) e = cudaLaunchKernelEx(&cfg, gqa_prep_kernel<__nv_bfloat16>, *a);
+  else if (a->dtype == ORTB200_F16) e = cudaLaunchKernelEx(&cfg, gqa_prep_kernel<__half>, *a);
   else return -4;
-  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+  return e == cudaSuccess ? 0 : -11;
 }

@@ -163,6 +163,7 @@ typedef struct {
   int first_prompt;
   int do_rotary;
   int dtype;
+  int use_pdl;                 // launch with programmatic stream serialization (overlaps the previous kernel's tail)
 } ortb200_gqa_prep_args;
 int ortb200_gqa_prep(const ortb200_gqa_prep_args* args, ortb200_stream_t stream);
 
@@ -226,6 +227,8 @@ typedef struct {
   const void* sin_cache;
   int do_rotary;
   int rotary_interleaved;
+  int num_blocks;         // paged cache: blocks in the pool (needed by the tensor-core kernel; 0 = unknown)
+  int algo;               // 0 = pick, 1 = CUDA-core split-KV kernel, 2 = tcgen05 kernel (error if unsupported)
 } ortb200_gqa_decode_args;
 int ortb200_gqa_decode(const ortb200_gqa_decode_args* args, ortb200_stream_t stream);
 int64_t ortb200_gqa_decode_workspace_bytes(int B, int N, int H);

@@ -48,7 +48,9 @@ class LlamaConfig:
 
     @staticmethod
     def llama3_70b(**kw) -> "LlamaConfig":
-        return LlamaConfig(hidden_size=8192, num_layers=80, num_heads=64, num_kv_heads=8, ffn_size=28672, **kw)
+        base = dict(hidden_size=8192, num_layers=80, num_heads=64, num_kv_heads=8, ffn_size=28672)
+        base.update(kw)
+        return LlamaConfig(**base)
 
     @staticmethod
     def tiny(**kw) -> "LlamaConfig":

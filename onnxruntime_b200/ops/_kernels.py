@@ -153,7 +153,7 @@ class GqaPrepArgs(ctypes.Structure):
                 ("cos_cache", ctypes.c_void_p), ("sin_cache", ctypes.c_void_p), ("position_ids", ctypes.c_void_p),
                 ("B", ctypes.c_int), ("S", ctypes.c_int), ("N", ctypes.c_int), ("Nk", ctypes.c_int), ("H", ctypes.c_int),
                 ("Smax", ctypes.c_int), ("rot_dim", ctypes.c_int), ("interleaved", ctypes.c_int),
-                ("first_prompt", ctypes.c_int), ("do_rotary", ctypes.c_int), ("dtype", ctypes.c_int)]
+                ("first_prompt", ctypes.c_int), ("do_rotary", ctypes.c_int), ("dtype", ctypes.c_int), ("use_pdl", ctypes.c_int)]
 
 
 def gqa_prep(qkv, k_cache, v_cache, seqlens_k, cos, sin, N, Nk, H, first_prompt, interleaved=False, position_ids=None):
@@ -174,16 +174,18 @@ class GqaDecodeArgs(ctypes.Structure):
                 ("window", ctypes.c_int), ("scale", ctypes.c_float), ("softcap", ctypes.c_float), ("dtype", ctypes.c_int),
                 ("use_pdl", ctypes.c_int), ("status", ctypes.c_void_p), ("block_table", ctypes.c_void_p),
                 ("block_size", ctypes.c_int), ("max_blocks", ctypes.c_int), ("qkv", ctypes.c_void_p), ("cos_cache", ctypes.c_void_p),
-                ("sin_cache", ctypes.c_void_p), ("do_rotary", ctypes.c_int), ("rotary_interleaved", ctypes.c_int)]
+                ("sin_cache", ctypes.c_void_p), ("do_rotary", ctypes.c_int), ("rotary_interleaved", ctypes.c_int),
+                ("num_blocks", ctypes.c_int), ("algo", ctypes.c_int)]
 
 
 _ATTN_WS = {}
 
 
 def gqa_decode(q, k_cache, v_cache, seqlens_k, splits=0, window=-1, scale=0.0, softcap=0.0, head_sink=None, block_table=None,
-               qkv=None, num_heads=0, cos=None, sin=None, interleaved=False):
+               qkv=None, num_heads=0, cos=None, sin=None, interleaved=False, algo=0):
     """Dense cache [B,Nk,Smax,H]; or, with block_table [B,max_blocks] int32, a paged cache [num_blocks,block_size,Nk,H].
-    With ``qkv`` (packed [B,(N+2Nk)H], ``num_heads`` = N) the kernel also rotates q / k and appends k / v itself."""
+    With ``qkv`` (packed [B,(N+2Nk)H], ``num_heads`` = N) the kernel also rotates q / k and appends k / v itself.
+    ``algo``: 0 = pick, 1 = CUDA-core split-KV kernel, 2 = tcgen05 kernel (head size 128, 16-bit types)."""
     if qkv is not None:
         H = k_cache.shape[3]
         B, N = qkv.shape[0], num_heads
@@ -192,8 +194,9 @@ def gqa_decode(q, k_cache, v_cache, seqlens_k, splits=0, window=-1, scale=0.0, s
         B, N, H = q.shape
     if block_table is None:
         Nk, Smax = k_cache.shape[1], k_cache.shape[2]
-        block_size = max_blocks = 0
+        block_size = max_blocks = num_blocks = 0
     else:
+        num_blocks = k_cache.shape[0]
         Nk, block_size, max_blocks = k_cache.shape[2], k_cache.shape[1], block_table.shape[1]
         Smax = block_size * max_blocks
     out = torch.empty(B, N * H, dtype=q.dtype, device=q.device)
@@ -207,7 +210,7 @@ def gqa_decode(q, k_cache, v_cache, seqlens_k, splits=0, window=-1, scale=0.0, s
     a = GqaDecodeArgs(None if qkv is not None else _ptr(q.contiguous()), _ptr(k_cache), _ptr(v_cache), _ptr(seqlens_k), _ptr(head_sink), _ptr(out), _ptr(ws),
                       ws.numel(), B, N, Nk, H, Smax, splits, window, scale, softcap, dtype_code(q.dtype), 0, None,
                       _ptr(block_table), block_size, max_blocks, _ptr(qkv), _ptr(cos), _ptr(sin), 0 if cos is None else 1,
-                      1 if interleaved else 0)
+                      1 if interleaved else 0, num_blocks, algo)
     _check(lib().ortb200_gqa_decode(ctypes.byref(a), ctypes.c_void_p(stream_ptr())), "ortb200_gqa_decode")
     return out
 

@@ -261,3 +261,64 @@ def test_gqa_decode_with_fused_rotary_and_append(K, H, N, Nk, interleaved, dtype
     torch.cuda.synchronize()
     assert torch.equal(k1, k2) and torch.equal(v1, v2)
     assert _rel(got, want) < 1e-2
+
+
+# ---------------------------------------------------------------- tcgen05 decode attention (head size 128)
+@pytest.mark.parametrize("N,Nk", [(32, 8), (16, 2), (4, 4), (16, 1), (6, 2)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_gqa_decode_tensor_core_kernel(K, N, Nk, dtype):
+    """The tensor-core kernel against the fp32 reference: lengths that end inside a tile, the cache beyond each
+    length poisoned with NaN (a masked key must not leak through 0 * NaN), and scores that keep growing along the
+    sequence so the reference maximum is raised (and O^T rescaled) several times."""
+    torch.manual_seed(0)
+    B, H, Smax = 4, 128, 1152
+    lens = torch.tensor([1, 130, 1024, 1152], dtype=torch.int32, device="cuda")
+    q = torch.randn(B, N, H, device="cuda").to(dtype)
+    ramp = torch.linspace(0.2, 3.0, Smax, device="cuda").view(1, 1, Smax, 1)
+    kc = (torch.randn(B, Nk, Smax, H, device="cuda") * ramp).to(dtype)
+    vc = torch.randn(B, Nk, Smax, H, device="cuda").to(dtype)
+    ref = _ref_attention(q.float().unsqueeze(2), kc.float(), vc.float(), (lens - 1).long(), 1 / math.sqrt(H),
+                         lens=lens.long()).squeeze(2)
+    for b in range(B):
+        kc[b, :, int(lens[b]):] = float("nan")
+        vc[b, :, int(lens[b]):] = float("nan")
+    for splits in (0, 1, 3):
+        out = K.gqa_decode(q, kc, vc, lens - 1, splits=splits, algo=2)
+        assert torch.isfinite(out.float()).all()
+        assert _rel(out.view(B, N, H), ref) < 2e-2, splits
+    old = K.gqa_decode(q, kc, vc, lens - 1, algo=1)
+    assert _rel(old.view(B, N, H), ref) < 2e-2
+
+
+@pytest.mark.parametrize("block_size", [16, 128, 256])
+def test_gqa_decode_tensor_core_kernel_paged(K, block_size):
+    torch.manual_seed(1)
+    B, N, Nk, H = 3, 8, 2, 128
+    max_len = 768
+    per_seq = max_len // block_size
+    lens = torch.tensor([5, 300, 768], dtype=torch.int32, device="cuda")
+    num_blocks = B * per_seq + 3
+    perm = torch.randperm(num_blocks, device="cuda")[:B * per_seq].view(B, per_seq).int()
+    k = torch.randn(B, Nk, max_len, H, device="cuda").bfloat16()
+    v = torch.randn(B, Nk, max_len, H, device="cuda").bfloat16()
+    kc = torch.full((num_blocks, block_size, Nk, H), float("nan"), device="cuda", dtype=torch.bfloat16)
+    vc = torch.full((num_blocks, block_size, Nk, H), float("nan"), device="cuda", dtype=torch.bfloat16)
+    for b in range(B):
+        for j in range(per_seq):
+            lo, hi = j * block_size, min((j + 1) * block_size, int(lens[b]))
+            if hi > lo:
+                kc[perm[b, j], :hi - lo] = k[b, :, lo:hi].transpose(0, 1)
+                vc[perm[b, j], :hi - lo] = v[b, :, lo:hi].transpose(0, 1)
+    # table entries past a sequence's last block are unset
+    table = perm.clone()
+    for b in range(B):
+        used = (int(lens[b]) + block_size - 1) // block_size
+        table[b, used:] = -1
+    q = torch.randn(B, N, H, device="cuda").bfloat16()
+    ref = _ref_attention(q.float().unsqueeze(2), k.float(), v.float(), (lens - 1).long(), 1 / math.sqrt(H),
+                         lens=lens.long()).squeeze(2)
+    for algo in (1, 2):
+        tb = table if algo == 2 else perm   # the CUDA-core kernel is given a fully populated table
+        out = K.gqa_decode(q, kc, vc, lens - 1, block_table=tb, algo=algo)
+        assert torch.isfinite(out.float()).all(), algo
+        assert _rel(out.view(B, N, H), ref) < 2e-2, algo
