@@ -55,7 +55,7 @@ struct AttnSmem {
   static constexpr int kOffP = kOffKV + 2 * kStageBytes;
   static constexpr int kOffBar = kOffP + kPBytes;
   static constexpr int kTotal = kOffBar + 128 + 1024;
-  static constexpr int kTmemCols = 128 + (HD <= 64 ? 64 : 128) <= 128 ? 128 : 256;
+  static constexpr int kTmemCols = 512;                // two score buffers (2 x 128 columns) + O (HD columns)
 };
 
 // Bit j of the result = key (key0 + j) of batch b may be attended to.  Called by all 32 lanes of a warp.
@@ -66,8 +66,19 @@ __device__ __forceinline__ unsigned key_keep_bits(const int* key_mask, int b, in
   return __ballot_sync(0xffffffffu, keep);
 }
 
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
+__device__ __forceinline__ float ex2_approx(float x) {
+  float r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+  return r;
+}
+
 // barrier indices
-enum { BAR_Q = 0, BAR_KV_FULL0, BAR_KV_FULL1, BAR_KV_EMPTY0, BAR_KV_EMPTY1, BAR_S_FULL, BAR_P_READY, BAR_O_FULL, BAR_O_READ, BAR_COUNT };
+enum { BAR_Q = 0, BAR_KV_FULL0, BAR_KV_FULL1, BAR_KV_EMPTY0, BAR_KV_EMPTY1, BAR_S_FULL0, BAR_S_FULL1, BAR_P_READY, BAR_O_FULL, BAR_COUNT };
 
 template <int HD>
 __global__ void __launch_bounds__(kAttnThreads, 1)
@@ -88,7 +99,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     tma_prefetch_desc(&tm_q);
     tma_prefetch_desc(&tm_k);
     tma_prefetch_desc(&tm_v);
-    for (int i = 0; i < BAR_COUNT; ++i) mbar_init(&bars[i], (i == BAR_P_READY || i == BAR_O_READ) ? 128 : 1);
+    for (int i = 0; i < BAR_COUNT; ++i) mbar_init(&bars[i], i == BAR_P_READY ? 128 : 1);
     fence_mbar_init();
   }
   if (warp == 1) {
@@ -99,8 +110,8 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   __syncthreads();
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tmem_s = tmem_base;          // S: columns [0, 128)
-  const uint32_t tmem_o = tmem_base + 128;    // O tile: columns [128, 128 + HD)
+  const uint32_t tmem_s = tmem_base;          // S: two buffers, columns [0, 128) and [128, 256)
+  const uint32_t tmem_o = tmem_base + 256;    // O: columns [256, 256 + HD), accumulated over all key tiles
 
   pdl_wait_prior_grids();
   const int total = p.seqlens_k ? p.seqlens_k[b] + 1 : p.kv_len;
@@ -142,95 +153,91 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       const uint32_t q_addr = smem_u32(smem + L::kOffQ);
       const uint32_t p_addr = smem_u32(smem + L::kOffP);
       bool ok = mbar_wait(&bars[BAR_Q], 0);
-      if (!ok && p.status) atomicExch(p.status, kStatusTimeoutMma);
       auto issue_s = [&](int t) {
         const int s = t & 1;
         const uint32_t k_addr = smem_u32(smem + L::kOffKV + s * L::kStageBytes);
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk) {
           const uint32_t off = (kk / 4) * L::kBoxBytes + (kk % 4) * 32;
-          umma_f16(tmem_s, umma_desc_sw128(q_addr + off), umma_desc_sw128(k_addr + off), idesc_s, kk > 0 ? 1u : 0u);
+          umma_f16(tmem_s + s * kKT, umma_desc_sw128(q_addr + off), umma_desc_sw128(k_addr + off), idesc_s, kk > 0 ? 1u : 0u);
         }
-        umma_commit(&bars[BAR_S_FULL]);
+        umma_commit(&bars[BAR_S_FULL0 + s]);
       };
-      if (ok) {
-        if (!mbar_wait(&bars[BAR_KV_FULL0], 0)) {
-          ok = false;
-          if (p.status) atomicExch(p.status, kStatusTimeoutMma);
-        }
-      }
+      if (ok && !mbar_wait(&bars[BAR_KV_FULL0], 0)) ok = false;
       if (ok) {
         tcgen05_fence_after();
         issue_s(0);
       }
       for (int t = 0; t < n_tiles && ok; ++t) {
         const int s = t & 1;
-        // P of tile t published (and S consumed)
+        if (t + 1 < n_tiles) {
+          // S of the next tile goes to the other score buffer while the softmax threads work on this one; that
+          // buffer was consumed before P of tile t - 1 was published, which this thread has waited for
+          if (!mbar_wait(&bars[BAR_KV_FULL0 + (s ^ 1)], ((t + 1) >> 1) & 1)) { ok = false; break; }
+          tcgen05_fence_after();
+          issue_s(t + 1);
+        }
+        // P of tile t published (O rescaled if the row maxima moved)
         if (!mbar_wait(&bars[BAR_P_READY], t & 1)) { ok = false; break; }
-        // O tile of the previous iteration has been folded into registers
-        if (t > 0 && !mbar_wait(&bars[BAR_O_READ], (t - 1) & 1)) { ok = false; break; }
         tcgen05_fence_after();
         const uint32_t v_addr = smem_u32(smem + L::kOffKV + s * L::kStageBytes + L::kKVBytes);
 #pragma unroll
         for (int kk = 0; kk < kKT / 16; ++kk) {
           const uint64_t pdesc = umma_desc_sw128(p_addr + (kk / 4) * L::kBoxBytes + (kk % 4) * 32);
           const uint64_t vdesc = umma_desc_mn_sw128(v_addr + kk * 2048, L::kBoxBytes, 1024);
-          umma_f16(tmem_o, pdesc, vdesc, idesc_o, kk > 0 ? 1u : 0u);
+          umma_f16(tmem_o, pdesc, vdesc, idesc_o, (t > 0 || kk > 0) ? 1u : 0u);
         }
         umma_commit(&bars[BAR_O_FULL]);
         umma_commit(&bars[BAR_KV_EMPTY0 + s]);
-        if (t + 1 < n_tiles) {
-          const int s2 = (t + 1) & 1;
-          if (!mbar_wait(&bars[BAR_KV_FULL0 + s2], ((t + 1) >> 1) & 1)) { ok = false; break; }
-          tcgen05_fence_after();
-          issue_s(t + 1);
-        }
       }
       if (!ok && p.status) atomicExch(p.status, kStatusTimeoutMma);
     }
   } else {
-    // ------------------------------------------------ softmax + accumulate (one thread per query row)
+    // ------------------------------------------------ softmax (one thread per query row); O accumulates in TMEM
     const int qw = warp & 3;
     const int r = qw * 32 + lane;
     const int s_idx = q0 + r;
     const int pos = past + s_idx;
     const uint32_t lane_addr = static_cast<uint32_t>(qw * 32) << 16;
-    float acc[HD];
-#pragma unroll
-    for (int i = 0; i < HD; ++i) acc[i] = 0.f;
+    // The reference maximum of a row is raised only when a tile exceeds it by 2^8 (probabilities stay below 256),
+    // so the accumulator in tensor memory is rescaled a few times per row instead of once per tile.
+    constexpr float kRaise = 8.f;
     float m = -INFINITY, l = 0.f;
     uint8_t* p_smem = smem + L::kOffP;
     bool ok = true;
-    for (int t = 0; t < n_tiles && ok; ++t) {
-      if (!mbar_wait(&bars[BAR_S_FULL], t & 1)) {
-        ok = false;
-        if (p.status) atomicExch(p.status, kStatusTimeoutEpilogue);
-        break;
-      }
+    for (int t = 0; t < n_tiles; ++t) {
+      if (ok && !mbar_wait(&bars[BAR_S_FULL0 + (t & 1)], (t >> 1) & 1)) ok = false;
       tcgen05_fence_after();
       const int key0 = kv_begin + t * kKT;
       // Interior tiles (every key visible to every row of this query tile) skip the per-element mask logic.
       const bool need_mask = (key0 + kKT > total) || (key0 + kKT > p.kv_len) || (p.key_mask != nullptr) || (p.window > 0) ||
                              (p.causal && key0 + kKT - 1 > past + q0) || (p.softcap > 0.f);
-      // Scores of GL columns are fetched with back-to-back tensor-memory loads and one wait, then turned into
-      // base-2 logits in place (-inf where masked).  With a 64-wide head all 128 columns of the tile stay in
-      // registers between the maximum and the exponentials; with a 128-wide head two groups of 64 are read twice.
-      constexpr int GL = HD == 64 ? 128 : 64;
-      float sv[GL];
-      auto load_group = [&](int c0) {
+      // The whole row of scores is fetched with back-to-back tensor-memory loads and one wait, then turned into
+      // base-2 logits in place (-inf where masked).
+      float sv[kKT];
+      const uint32_t s_addr = tmem_s + (t & 1) * kKT + lane_addr;
 #pragma unroll
-        for (int g4 = 0; g4 < GL / 32; ++g4) tmem_ld_x32(tmem_s + lane_addr + c0 + g4 * 32, sv + g4 * 32);
-        tmem_ld_wait();
-        if (!need_mask) {
+      for (int g4 = 0; g4 < kKT / 32; ++g4) tmem_ld_x32(s_addr + g4 * 32, sv + g4 * 32);
+      tmem_ld_wait();
+      // Scores stay unscaled in registers: the scale is folded into the exponent's multiply-add.  Plain length /
+      // causal masking is one compare and select per element against a per-row limit; key masks, sliding windows
+      // and soft-capping take the general path, which leaves final base-2 logits (scale 1).
+      float fs = p.scale_log2;
+      if (need_mask) {
+        if (p.key_mask == nullptr && p.window <= 0 && p.softcap <= 0.f) {
+          int hi = min(total, p.kv_len);
+          if (p.causal) hi = min(hi, pos + 1);
+          hi -= key0;
 #pragma unroll
-          for (int j = 0; j < GL; ++j) sv[j] *= p.scale_log2;
+          for (int j = 0; j < kKT; ++j) sv[j] = j < hi ? sv[j] : -INFINITY;
         } else {
+          fs = 1.f;
 #pragma unroll
-          for (int g4 = 0; g4 < GL / 32; ++g4) {
-            const unsigned keep = key_keep_bits(p.key_mask, b, p.kv_len, key0 + c0 + g4 * 32, lane);
+          for (int g4 = 0; g4 < kKT / 32; ++g4) {
+            const unsigned keep = key_keep_bits(p.key_mask, b, p.kv_len, key0 + g4 * 32, lane);
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
-              const int key = key0 + c0 + g4 * 32 + j;
+              const int key = key0 + g4 * 32 + j;
               bool valid = key < total && key < p.kv_len && ((keep >> j) & 1u);
               if (p.causal) valid = valid && key <= pos;
               if (p.window > 0) valid = valid && key > pos - p.window;
@@ -241,108 +248,109 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
             }
           }
         }
-      };
-      auto store_probs = [&](int c0, float m_ref, float& row_sum) {
+      }
+      float m_raw = -INFINITY;
 #pragma unroll
-        for (int c = 0; c < GL; c += 32) {
-          uint32_t packed[16];
+      for (int j = 0; j < kKT; j += 2) m_raw = fmax3(m_raw, sv[j], sv[j + 1]);
+      const float m_tile = m_raw * fs;   // fs > 0: -inf stays -inf
+      // the previous PV product reads P and writes O: it must have finished before either is touched
+      if (t > 0 && ok && !mbar_wait(&bars[BAR_O_FULL], (t - 1) & 1)) ok = false;
+      tcgen05_fence_after();
+      const bool raise = m_tile > m + kRaise;   // also the first finite maximum of a row (m = -inf)
+      if (__any_sync(0xffffffffu, raise)) {
+        // tensor-memory loads and stores are warp-wide: every lane takes part, rows that keep their maximum scale by 1
+        const float corr = raise ? (m == -INFINITY ? 0.f : exp2f(m - m_tile)) : 1.f;
+        if (t > 0) {
+#pragma unroll 1
+          for (int c = 0; c < HD; c += 32) {
+            float v[32];
+            tmem_ld_x32(tmem_o + lane_addr + c, v);
+            tmem_ld_wait();
 #pragma unroll
-          for (int j = 0; j < 32; j += 2) {
-            const float p0 = m_ref == -INFINITY ? 0.f : exp2f(sv[c + j] - m_ref);
-            const float p1 = m_ref == -INFINITY ? 0.f : exp2f(sv[c + j + 1] - m_ref);
-            if (p.bf16) {
-              __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
-              packed[j / 2] = *reinterpret_cast<uint32_t*>(&h);
-              row_sum += __bfloat162float(h.x) + __bfloat162float(h.y);
-            } else {
-              __half2 h = __floats2half2_rn(p0, p1);
-              packed[j / 2] = *reinterpret_cast<uint32_t*>(&h);
-              row_sum += __half2float(h.x) + __half2float(h.y);
-            }
+            for (int j = 0; j < 32; ++j) v[j] *= corr;
+            tmem_st_x32(tmem_o + lane_addr + c, v);
           }
-          // 32 keys = 4 chunks of 16 bytes; column cc lives in box cc / 64
-          const int cc = c0 + c;
-          const int box = cc / 64;
+          tmem_st_wait();
+        }
+        l *= corr;
+        if (raise) m = m_tile;
+      }
+      // masked scores are -inf and give 0; a row with no visible key so far (m = -inf) uses 0 as its reference
+      const float neg_m = m == -INFINITY ? 0.f : -m;
+      float row_sum = 0.f, row_sum1 = 0.f;
 #pragma unroll
-          for (int ch = 0; ch < 4; ++ch) {
-            const int chunk = ((cc % 64) * 2) / 16 + ch;
-            uint8_t* dst = p_smem + box * L::kBoxBytes + r * 128 + ((chunk ^ (r & 7)) << 4);
-            *reinterpret_cast<uint4*>(dst) = make_uint4(packed[ch * 4], packed[ch * 4 + 1], packed[ch * 4 + 2], packed[ch * 4 + 3]);
+      for (int c = 0; c < kKT; c += 32) {
+        uint32_t packed[16];
+#pragma unroll
+        for (int j = 0; j < 32; j += 2) {
+          const float p0 = ex2_approx(fmaf(sv[c + j], fs, neg_m));
+          const float p1 = ex2_approx(fmaf(sv[c + j + 1], fs, neg_m));
+          row_sum += p0;
+          row_sum1 += p1;
+          if (p.bf16) {
+            __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+            packed[j / 2] = *reinterpret_cast<uint32_t*>(&h);
+          } else {
+            __half2 h = __floats2half2_rn(p0, p1);
+            packed[j / 2] = *reinterpret_cast<uint32_t*>(&h);
           }
         }
-      };
-      float m_new = m;
-      float row_sum = 0.f;
-      if (GL == kKT) {
-        load_group(0);
+        // 32 keys = 4 chunks of 16 bytes; column c lives in box c / 64
+        const int box = c / 64;
 #pragma unroll
-        for (int j = 0; j < GL; ++j) m_new = fmaxf(m_new, sv[j]);
-        store_probs(0, m_new, row_sum);
-      } else {
-#pragma unroll 1
-        for (int c0 = 0; c0 < kKT; c0 += GL) {
-          load_group(c0);
-#pragma unroll
-          for (int j = 0; j < GL; ++j) m_new = fmaxf(m_new, sv[j]);
-        }
-#pragma unroll 1
-        for (int c0 = 0; c0 < kKT; c0 += GL) {
-          load_group(c0);
-          store_probs(c0, m_new, row_sum);
+        for (int ch = 0; ch < 4; ++ch) {
+          const int chunk = ((c % 64) * 2) / 16 + ch;
+          uint8_t* dst = p_smem + box * L::kBoxBytes + r * 128 + ((chunk ^ (r & 7)) << 4);
+          *reinterpret_cast<uint4*>(dst) = make_uint4(packed[ch * 4], packed[ch * 4 + 1], packed[ch * 4 + 2], packed[ch * 4 + 3]);
         }
       }
-      const float corr = m == -INFINITY ? 0.f : exp2f(m - m_new);
-      l = l * corr + row_sum;
-      m = m_new;
+      l += row_sum + row_sum1;
       // make the generic-proxy writes of P visible to the tensor core, then publish
       fence_proxy_async();
       tcgen05_fence_before();
       mbar_arrive(&bars[BAR_P_READY]);
-      // fold the PV product of this tile into the accumulator
-      if (!mbar_wait(&bars[BAR_O_FULL], t & 1)) {
-        ok = false;
-        if (p.status) atomicExch(p.status, kStatusTimeoutEpilogue);
-        break;
-      }
-      tcgen05_fence_after();
-#pragma unroll
-      for (int c = 0; c < HD; c += 32) {
-        float v[32];
-        tmem_ld_x32(tmem_o + lane_addr + c, v);
-        tmem_ld_wait();
-#pragma unroll
-        for (int j = 0; j < 32; ++j) acc[c + j] = acc[c + j] * corr + v[j];
-      }
-      tcgen05_fence_before();
-      mbar_arrive(&bars[BAR_O_READ]);
     }
+    if (n_tiles > 0 && ok && !mbar_wait(&bars[BAR_O_FULL], (n_tiles - 1) & 1)) ok = false;
+    tcgen05_fence_after();
+    if (!ok && p.status) atomicExch(p.status, kStatusTimeoutEpilogue);
     pdl_launch_dependents();
-    if (ok && s_idx < p.S) {
-      float denom = l;
-      float rescale = 1.f;
-      if (p.head_sink) {
-        const float sink = (p.bf16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(p.head_sink)[head])
-                                   : __half2float(static_cast<const __half*>(p.head_sink)[head])) * 1.4426950408889634f;
-        const float mm = fmaxf(m, sink);
-        rescale = m == -INFINITY ? 0.f : exp2f(m - mm);
-        denom = l * rescale + exp2f(sink - mm);
+    float denom = l;
+    float rescale = 1.f;
+    if (p.head_sink) {
+      const float sink = (p.bf16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(p.head_sink)[head])
+                                 : __half2float(static_cast<const __half*>(p.head_sink)[head])) * 1.4426950408889634f;
+      const float mm = fmaxf(m, sink);
+      rescale = m == -INFINITY ? 0.f : exp2f(m - mm);
+      denom = l * rescale + exp2f(sink - mm);
+    }
+    const float inv = (denom > 0.f && n_tiles > 0) ? rescale / denom : 0.f;
+    uint8_t* orow = static_cast<uint8_t*>(p.out) + 2 * (b * p.o_strides[0] + s_idx * p.o_strides[1] + head * p.o_strides[2]);
+#pragma unroll 1
+    for (int c0 = 0; c0 < HD; c0 += 32) {
+      float v[32];
+      if (n_tiles > 0) {   // uniform over the CTA
+        tmem_ld_x32(tmem_o + lane_addr + c0, v);
+        tmem_ld_wait();
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = 0.f;
       }
-      const float inv = denom > 0.f ? rescale / denom : 0.f;
-      uint8_t* orow = static_cast<uint8_t*>(p.out) + 2 * (b * p.o_strides[0] + s_idx * p.o_strides[1] + head * p.o_strides[2]);
+      if (ok && s_idx < p.S) {
 #pragma unroll
-      for (int c = 0; c < HD; c += 8) {
-        uint32_t w[4];
+        for (int c = 0; c < 32; c += 8) {
+          uint32_t w[4];
 #pragma unroll
-        for (int j = 0; j < 8; j += 2) {
-          if (p.bf16) {
-            __nv_bfloat162 h = __floats2bfloat162_rn(acc[c + j] * inv, acc[c + j + 1] * inv);
-            w[j / 2] = *reinterpret_cast<uint32_t*>(&h);
-          } else {
-            __half2 h = __floats2half2_rn(acc[c + j] * inv, acc[c + j + 1] * inv);
-            w[j / 2] = *reinterpret_cast<uint32_t*>(&h);
+          for (int j = 0; j < 8; j += 2) {
+            if (p.bf16) {
+              __nv_bfloat162 h = __floats2bfloat162_rn(v[c + j] * inv, v[c + j + 1] * inv);
+              w[j / 2] = *reinterpret_cast<uint32_t*>(&h);
+            } else {
+              __half2 h = __floats2half2_rn(v[c + j] * inv, v[c + j + 1] * inv);
+              w[j / 2] = *reinterpret_cast<uint32_t*>(&h);
+            }
           }
+          *reinterpret_cast<uint4*>(orow + (c0 + c) * 2) = make_uint4(w[0], w[1], w[2], w[3]);
         }
-        *reinterpret_cast<uint4*>(orow + c * 2) = make_uint4(w[0], w[1], w[2], w[3]);
       }
     }
   }

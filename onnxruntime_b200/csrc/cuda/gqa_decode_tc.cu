@@ -64,7 +64,6 @@ __device__ __forceinline__ void tmem_st_x8(uint32_t taddr, const float* v) {
                "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7]))
                : "memory");
 }
-__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // G query heads live in columns [0, G) of S^T and O^T; columns are read eight at a time
 template <int G>
