@@ -152,6 +152,7 @@ void RegisterElementwiseKernels(KernelRegistry& r);
 void RegisterTensorKernels(KernelRegistry& r);
 void RegisterNnKernels(KernelRegistry& r);
 void RegisterContribKernels(KernelRegistry& r);
+void RegisterContribKernels2(KernelRegistry& r);
 void RegisterControlFlowKernels(KernelRegistry& r);
 void RegisterCollectiveKernels(KernelRegistry& r);
 void RegisterCudaKernels(KernelRegistry& r);

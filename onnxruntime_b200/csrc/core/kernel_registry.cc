@@ -71,6 +71,7 @@ void EnsureKernelsRegistered() {
     RegisterTensorKernels(g);
     RegisterNnKernels(g);
     RegisterContribKernels(g);
+    RegisterContribKernels2(g);
     RegisterControlFlowKernels(g);
     RegisterCollectiveKernels(g);
     RegisterCudaKernels(KernelRegistry::Cuda());
