@@ -25,7 +25,7 @@ __all__ = [
     "AdapterFormat", "LoraAdapter", "register_custom_op",
     "InferenceSession", "SessionOptions", "RunOptions", "IOBinding", "OrtValue", "OrtDevice", "NodeArg",
     "ModelMetadata", "GraphOptimizationLevel", "ExecutionMode", "ExecutionOrder", "get_available_providers",
-    "get_all_providers", "get_device", "set_default_logger_severity", "set_default_logger_verbosity",
+    "get_all_providers", "get_device", "set_default_logger_severity", "set_default_logger_verbosity", "set_log_sink",
 ]
 
 
@@ -113,11 +113,18 @@ def set_default_logger_severity(severity: int) -> None:
     if not 0 <= severity <= 4:
         raise InvalidArgument("severity must be in [0, 4]")
     _default_logger_severity = severity
+    C.set_default_logger_severity(severity)
 
 
 def set_default_logger_verbosity(verbosity: int) -> None:
     global _default_logger_verbosity
     _default_logger_verbosity = verbosity
+    C.set_default_logger_verbosity(verbosity)
+
+
+def set_log_sink(sink) -> None:
+    """Route log lines to ``sink(severity, logger_id, line)`` instead of stderr; ``None`` restores stderr."""
+    C.set_log_sink(sink)
 
 
 # ------------------------------------------------------------------ type names
@@ -318,7 +325,6 @@ class SessionOptions:
         object.__setattr__(self, "_c", C.SessionOptions())
         object.__setattr__(self, "_custom_op_libraries", [])
         object.__setattr__(self, "_keepalive", [])
-        self._c.log_severity_level = _default_logger_severity
 
     def __getattr__(self, name):
         if name in SessionOptions._FIELDS:

@@ -4,6 +4,7 @@
 #include <pybind11/stl.h>
 #include <torch/extension.h>
 
+#include "logging.h"
 #include "executor.h"
 #include "graph.h"
 #include "kernel.h"
@@ -103,6 +104,25 @@ auto Guard(F&& f) -> decltype(f()) {
 PYBIND11_MODULE(_core, m) {
   m.doc() = "onnxruntime_b200 native runtime";
   m.def("set_error_factory", [](py::object f) { g_error_factory = f; });
+  m.def("set_default_logger_severity", [](int s) { logging::Manager::Get().set_default_severity(s); });
+  m.def("set_default_logger_verbosity", [](int v) { logging::Manager::Get().set_default_verbosity(v); });
+  // sink(severity, logger_id, formatted_line); None restores stderr
+  m.def("set_log_sink", [](py::object fn) {
+    if (fn.is_none()) {
+      logging::Manager::Get().SetSink(nullptr);
+      return;
+    }
+    auto holder = std::make_shared<py::object>(fn);
+    logging::Manager::Get().SetSink([holder](const logging::Record& r) {
+      py::gil_scoped_acquire gil;
+      (*holder)(static_cast<int>(r.severity), r.logger_id, logging::Manager::Format(r));
+    });
+  });
+  m.def("log_message", [](int severity, const std::string& id, const std::string& msg) {
+    logging::Logger lg(id, -1, -1);
+    if (lg.Enabled(static_cast<logging::Severity>(severity)))
+      logging::Manager::Get().Emit({static_cast<logging::Severity>(severity), id, "python", "", msg, 0});
+  });
   m.def("registered_ops", [](const std::string& which) {
     EnsureKernelsRegistered();
     return which == "cuda" ? KernelRegistry::Cuda().ListOps() : KernelRegistry::Generic().ListOps();

@@ -85,7 +85,8 @@ struct InferenceSession::CapturedGraph {
   int warm_runs = 0;
 };
 
-InferenceSession::InferenceSession(const SessionOptions& so) : so_(so) {
+InferenceSession::InferenceSession(const SessionOptions& so)
+    : so_(so), logger_(so.logid, so.log_severity_level, so.log_verbosity_level) {
   EnsureKernelsRegistered();
   if (so_.enable_profiling) {
     profiler_.Start(so_.profile_file_prefix);
@@ -193,7 +194,10 @@ void InferenceSession::Initialize(const std::vector<std::pair<std::string, Provi
     std::string tok;
     while (std::getline(ss, tok, ',')) if (!tok.empty()) disabled.insert(tok);
   }
+  const size_t nodes_before = g.Nodes().size();
   OptimizeGraph(g, so_.graph_optimization_level, disabled, device_.is_cuda(), so_.config, world_size);
+  ORTB_LOG(logger_, kInfo) << "graph optimization level " << so_.graph_optimization_level << ": " << nodes_before << " -> "
+                           << g.Nodes().size() << " nodes";
 
   if (!so_.optimized_model_filepath.empty()) model_->Save(so_.optimized_model_filepath);
 
@@ -212,6 +216,22 @@ void InferenceSession::Initialize(const std::vector<std::pair<std::string, Provi
   }
   exec_ = std::move(exec);
   initialized_ = true;
+  {
+    // nodes that could not be placed on the first provider are worth a warning (they force device <-> host copies)
+    size_t on_cpu = 0, total = 0;
+    std::string example;
+    for (auto& t : NodeAssignments()) {
+      ++total;
+      if (std::get<2>(t) == kCpuEP) {
+        ++on_cpu;
+        if (example.empty()) example = std::get<1>(t) + " (" + std::get<0>(t) + ")";
+      }
+    }
+    ORTB_LOG(logger_, kInfo) << "session initialized: " << total << " nodes, providers " << providers_.front()
+                             << (providers_.size() > 1 ? " + " + providers_.back() : std::string()) << ", device " << device_.str();
+    if (device_.is_cuda() && on_cpu > 0)
+      ORTB_LOG(logger_, kWarning) << on_cpu << " of " << total << " nodes run on the CPU provider, e.g. " << example;
+  }
   profiler_.Record("Session", "session_initialization", t0, profiler_.NowUs() - t0);
 }
 
@@ -322,6 +342,10 @@ std::vector<Value> InferenceSession::RunImpl(const RunOptions& ro, const std::ve
   std::lock_guard<std::mutex> run_lock(run_mu_);
   GraphExecutor* ex = exec_.get();
   const int64_t t_run0 = profiler_.NowUs();
+  // a run may carry its own id and threshold (RunOptions.logid / log_severity_level)
+  logging::Logger run_logger(ro.logid.empty() ? logger_.id() : ro.logid, ro.log_severity_level >= 0 ? ro.log_severity_level : logger_.threshold(),
+                             ro.log_verbosity_level > 0 ? ro.log_verbosity_level : logger_.verbosity());
+  ORTB_VLOG(run_logger, 1) << "run: " << feed_names.size() << " feeds, " << output_names_in.size() << " requested outputs";
   c10::cuda::OptionalCUDAGuard guard;
   if (device_.is_cuda()) guard.set_device(device_);
 

@@ -16,6 +16,7 @@
 #include <string>
 #include <vector>
 
+#include "logging.h"
 #include "graph.h"
 #include "kernel.h"
 
@@ -29,7 +30,7 @@ struct SessionOptions {
   std::string profile_file_prefix = "onnxruntime_profile_";
   std::string optimized_model_filepath;
   std::string logid;
-  int log_severity_level = 2;
+  int log_severity_level = -1;      // -1: the process default (logging::Manager)
   int log_verbosity_level = 0;
   int intra_op_num_threads = 0;
   int inter_op_num_threads = 0;
@@ -133,6 +134,7 @@ class InferenceSession {
   // per-node provider assignment: (node name, op type, provider)
   std::vector<std::tuple<std::string, std::string, std::string>> NodeAssignments() const;
   Profiler& profiler() { return profiler_; }
+  const logging::Logger& logger() const { return logger_; }
   int NumCapturedGraphs() const { return static_cast<int>(cuda_graphs_.size()); }
   int64_t KernelLaunchCount() const { return launch_count_; }
   // launches issued by the most recent execution of the step list (eager run or graph capture)
@@ -176,6 +178,7 @@ class InferenceSession {
 
   std::map<int64_t, std::unique_ptr<CapturedGraph>> cuda_graphs_;
   Profiler profiler_;
+  logging::Logger logger_;
   int64_t profiling_start_ns_ = 0;
   int64_t launch_count_ = 0;
   int64_t last_run_launches_ = 0;

@@ -210,3 +210,44 @@ def test_run_async_and_disabled_optimizers():
     s.run_async(None, {"x": np.ones((1, 4), np.float32)}, cb, "tag")
     assert done.wait(10) and box["user"] == "tag" and box["err"] == ""
     np.testing.assert_allclose(box["res"][0], np.maximum(np.ones((1, 4), np.float32) @ w, 0))
+
+
+def test_logging_severity_sink_and_session_ids(capfd):
+    """Per-session logger id and threshold, process default, replaceable sink (the reference's LoggingManager:
+    onnxruntime/core/common/logging/logging.h; python: set_default_logger_severity, SessionOptions.logid)."""
+    import numpy as np
+    import onnxruntime_b200 as ort
+    from onnxruntime_b200 import onnx_lite as ol
+    T = ol.TensorProto
+    g = ol.make_graph([ol.make_node("Relu", ["x"], ["y"])], "g", [ol.make_tensor_value_info("x", T.FLOAT, [2])],
+                      [ol.make_tensor_value_info("y", T.FLOAT, [2])])
+    model = ol.make_model(g, opset=17).serialize()
+    lines = []
+    ort.set_log_sink(lambda sev, logid, line: lines.append((sev, logid, line)))
+    try:
+        so = ort.SessionOptions()
+        so.logid = "quiet"
+        ort.InferenceSession(model, so, providers=["CPUExecutionProvider"])
+        assert lines == []                      # default threshold is WARNING
+        so = ort.SessionOptions()
+        so.logid = "chatty"
+        so.log_severity_level = 1
+        sess = ort.InferenceSession(model, so, providers=["CPUExecutionProvider"])
+        assert any(sev == 1 and logid == "chatty" and "session initialized" in line for sev, logid, line in lines)
+        assert all(logid == "chatty" for _, logid, _ in lines)
+        n = len(lines)
+        ro = ort.RunOptions()
+        ro.logid = "run7"
+        ro.log_severity_level = 0
+        ro.log_verbosity_level = 1
+        sess.run(None, {"x": np.zeros(2, np.float32)}, ro)
+        assert any(sev == 0 and logid == "run7" for sev, logid, _ in lines[n:])
+    finally:
+        ort.set_log_sink(None)
+    # without a sink lines go to stderr in the "[I:ortb200:<id>, file:line function] message" form
+    so = ort.SessionOptions()
+    so.logid = "stderr-session"
+    so.log_severity_level = 1
+    ort.InferenceSession(model, so, providers=["CPUExecutionProvider"])
+    err = capfd.readouterr().err
+    assert "[I:ortb200:stderr-session, session.cc:" in err
