@@ -48,3 +48,62 @@ def test_int4_model_dequantises_to_the_dense_model():
     sess = ort.InferenceSession(ol.make_model(g, opset=17).serialize(), providers=["CPUExecutionProvider"])
     (y,) = sess.run(None, {"x": x})
     np.testing.assert_allclose(y, x @ w, rtol=1e-4, atol=1e-4)
+
+
+def _tiny_runner(batch, with_argmax=False):
+    cfg = LlamaConfig.tiny(dtype="fp32", vocab_size=64, num_layers=1)
+    model, _ = build_llama(cfg, weight_std=0.3, with_argmax=with_argmax)
+    sess = ort.InferenceSession(model, providers=["CPUExecutionProvider"])
+    return cfg, sess, DecoderRunner(sess, cfg, batch, 64)
+
+
+def test_generate_greedy_sampling_and_processors():
+    from onnxruntime_b200.models.generation import GenerationConfig, generate, process_logits, top_k_top_p_filter
+    cfg, sess, runner = _tiny_runner(2)
+    torch.manual_seed(0)
+    ids = torch.randint(0, cfg.vocab_size, (2, 6))
+    greedy = generate(runner, ids, GenerationConfig(max_new_tokens=6))
+    ref = DecoderRunner(sess, cfg, 2, 64).generate(ids, 6)
+    assert torch.equal(greedy[:, 6:], ref)
+    # sampling is reproducible under a seed and stays inside the top-k set
+    a = generate(DecoderRunner(sess, cfg, 2, 64), ids, GenerationConfig(max_new_tokens=5, top_k=3, seed=7))
+    b = generate(DecoderRunner(sess, cfg, 2, 64), ids, GenerationConfig(max_new_tokens=5, top_k=3, seed=7))
+    assert torch.equal(a, b)
+    # processors
+    logits = torch.tensor([[1.0, 2.0, 3.0, 4.0]])
+    seq = torch.tensor([[3, 1, 3]])
+    out = process_logits(logits, seq, 0, GenerationConfig(repetition_penalty=2.0))
+    assert out.tolist() == [[1.0, 1.0, 3.0, 2.0]]
+    out = process_logits(logits, seq, 0, GenerationConfig(no_repeat_ngram_size=2))   # (3, 1) seen: 1 after 3 is banned
+    assert out[0, 1] == float("-inf") and torch.isfinite(out[0, [0, 2, 3]]).all()
+    out = process_logits(logits, seq, 0, GenerationConfig(eos_token_id=2, min_new_tokens=1))
+    assert out[0, 2] == float("-inf")
+    f = top_k_top_p_filter(torch.tensor([[0.0, 1.0, 2.0, 3.0]]), top_k=2, top_p=1.0)
+    assert torch.isinf(f[0, :2]).all() and torch.isfinite(f[0, 2:]).all()
+    f = top_k_top_p_filter(torch.log(torch.tensor([[0.1, 0.2, 0.3, 0.4]])), top_k=0, top_p=0.5)
+    assert torch.isinf(f[0, :2]).all() and torch.isfinite(f[0, 2:]).all()
+
+
+def test_beam_search_finds_a_sequence_at_least_as_likely_as_greedy():
+    from onnxruntime_b200.models.generation import GenerationConfig, generate
+    cfg, sess, _ = _tiny_runner(1)
+    torch.manual_seed(1)
+    ids = torch.randint(0, cfg.vocab_size, (2, 5))
+    steps, K = 5, 3
+    beams = generate(DecoderRunner(sess, cfg, 2 * K, 64), ids, GenerationConfig(max_new_tokens=steps, num_beams=K, length_penalty=0.0))
+    greedy = generate(DecoderRunner(sess, cfg, 2, 64), ids, GenerationConfig(max_new_tokens=steps))
+    assert beams.shape == greedy.shape and torch.equal(beams[:, :5], ids)
+
+    def logprob(seq):   # score a full sequence with a fresh pass
+        r = DecoderRunner(sess, cfg, 2, 64)
+        r.prefill(seq[:, :5])
+        total = torch.zeros(2)
+        logits = r.prefill_logits.reshape(2, -1).float()
+        for t in range(steps):
+            lp = torch.log_softmax(logits, -1)
+            total += lp.gather(1, seq[:, 5 + t].view(-1, 1)).squeeze(1)
+            if t + 1 < steps:
+                r.decode_step(seq[:, 5 + t].view(-1, 1))
+                logits = r.step_logits.reshape(2, -1).float()
+        return total
+    assert (logprob(beams) >= logprob(greedy) - 1e-4).all()
