@@ -153,6 +153,7 @@ void RegisterTensorKernels(KernelRegistry& r);
 void RegisterNnKernels(KernelRegistry& r);
 void RegisterContribKernels(KernelRegistry& r);
 void RegisterContribKernels2(KernelRegistry& r);
+void RegisterOnnxExtraKernels(KernelRegistry& r);
 void RegisterControlFlowKernels(KernelRegistry& r);
 void RegisterCollectiveKernels(KernelRegistry& r);
 void RegisterCudaKernels(KernelRegistry& r);

@@ -72,6 +72,7 @@ void EnsureKernelsRegistered() {
     RegisterNnKernels(g);
     RegisterContribKernels(g);
     RegisterContribKernels2(g);
+    RegisterOnnxExtraKernels(g);
     RegisterControlFlowKernels(g);
     RegisterCollectiveKernels(g);
     RegisterCudaKernels(KernelRegistry::Cuda());

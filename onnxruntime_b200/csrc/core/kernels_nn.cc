@@ -127,6 +127,48 @@ void ConvImpl(Ctx& ctx) {
   ctx.SetOutput(0, at::convolution(x, w, bias, a.strides, pad, a.dilations, false, std::vector<int64_t>(pad.size(), 0), a.group));
 }
 
+// float convolution of already dequantised operands with the node's attributes
+at::Tensor ConvFloat(const Node& node, at::Tensor x, const at::Tensor& w, const c10::optional<at::Tensor>& bias) {
+  ConvAttrs a = ParseConv(node, x, w.sizes().slice(2), false);
+  std::vector<int64_t> pad = a.pads_begin;
+  if (!Symmetric(a)) {
+    x = PadSpatial(x, a, 0.0);
+    pad.assign(pad.size(), 0);
+  }
+  return at::convolution(x, w, bias, a.strides, pad, a.dilations, false, std::vector<int64_t>(pad.size(), 0), a.group);
+}
+
+// QLinearConv: x, x_scale, x_zp, w, w_scale (scalar or per output channel), w_zp, y_scale, y_zp, bias (int32, scale
+// x_scale * w_scale).  ConvInteger: x, w, x_zp?, w_zp? -> int32.
+void QLinearConvImpl(Ctx& ctx) {
+  at::Tensor xf = (ctx.RequiredInput(0).to(at::kFloat) - ctx.RequiredInput(2).to(at::kFloat)) * ctx.RequiredInput(1).to(at::kFloat);
+  const at::Tensor& w = ctx.RequiredInput(3);
+  at::Tensor ws = ctx.RequiredInput(4).to(at::kFloat), wz = ctx.RequiredInput(5).to(at::kFloat);
+  std::vector<int64_t> per_channel(w.dim(), 1);
+  per_channel[0] = -1;
+  if (ws.numel() > 1) ws = ws.reshape(per_channel);
+  if (wz.numel() > 1) wz = wz.reshape(per_channel);
+  at::Tensor wf = (w.to(at::kFloat) - wz) * ws;
+  c10::optional<at::Tensor> bias;
+  if (ctx.HasInput(8)) bias = ctx.Input(8).to(at::kFloat) * (ctx.RequiredInput(1).to(at::kFloat) * ctx.RequiredInput(4).to(at::kFloat).reshape({-1}));
+  at::Tensor y = ConvFloat(ctx.node(), xf, wf, bias);
+  const at::Tensor& yz = ctx.RequiredInput(7);
+  const double lo = yz.scalar_type() == at::kChar ? -128 : 0, hi = yz.scalar_type() == at::kChar ? 127 : 255;
+  ctx.SetOutput(0, at::clamp(at::round(y / ctx.RequiredInput(6).to(at::kFloat)) + yz.to(at::kFloat), lo, hi).to(yz.scalar_type()));
+}
+
+void ConvIntegerImpl(Ctx& ctx) {
+  at::Tensor xf = ctx.RequiredInput(0).to(at::kFloat), wf = ctx.RequiredInput(1).to(at::kFloat);
+  if (ctx.HasInput(2)) xf = xf - ctx.Input(2).to(at::kFloat);
+  if (ctx.HasInput(3)) {
+    at::Tensor wz = ctx.Input(3).to(at::kFloat);
+    std::vector<int64_t> per_channel(wf.dim(), 1);
+    per_channel[0] = -1;
+    wf = wf - (wz.numel() > 1 ? wz.reshape(per_channel) : wz);
+  }
+  ctx.SetOutput(0, at::round(ConvFloat(ctx.node(), xf, wf, c10::nullopt)).to(at::kInt));
+}
+
 void ConvTransposeImpl(Ctx& ctx) {
   const at::Tensor& x = ctx.RequiredInput(0);
   const at::Tensor& w = ctx.RequiredInput(1);
@@ -450,6 +492,8 @@ void RegisterNnKernels(KernelRegistry& r) {
   });
   r.RegisterFn("", "Conv", 1, kMax, ConvImpl);
   r.RegisterFn("", "ConvTranspose", 1, kMax, ConvTransposeImpl);
+  r.RegisterFn("", "QLinearConv", 10, kMax, QLinearConvImpl);
+  r.RegisterFn("", "ConvInteger", 10, kMax, ConvIntegerImpl);
   r.RegisterFn("", "MaxPool", 1, kMax, [](Ctx& ctx) { PoolImpl(ctx, true); });
   r.RegisterFn("", "AveragePool", 1, kMax, [](Ctx& ctx) { PoolImpl(ctx, false); });
   r.RegisterFn("", "GlobalAveragePool", 1, kMax, [](Ctx& ctx) {
