@@ -3,6 +3,8 @@
 // Reference counterparts: onnxruntime/contrib_ops/cuda/quantization/matmul_nbits.cc,
 // contrib_ops/cuda/bert/paged_attention.cc, bert/attention.cc and bert/multihead_attention.cc.
 #include <ATen/ATen.h>
+
+#include <mutex>
 #include <ATen/cuda/CUDAContext.h>
 
 #include <algorithm>
@@ -721,6 +723,47 @@ void Reg(KernelRegistry& r, const std::string& domain, const std::string& op, st
 
 }  // namespace
 
+// MatMulBlockQuantizedFp8Weight: the fp8 weight with its per-block scales is expanded to the activation type once (at
+// the first call; constant weights only) and the product runs on the tcgen05 GEMM.  Weight-only block scaling cannot
+// ride the 8-bit tensor-core mode, whose accumulation would need one scale per output instead of one per K block.
+class BlockFp8WeightMatMulKernel final : public WithFallback {
+ public:
+  explicit BlockFp8WeightMatMulKernel(const OpKernelInfo& info) : WithFallback(info) {
+    block_ = info.node.attr_i("block_size", 128);
+    const_weight_ = info.constant_input(1) != nullptr && info.constant_input(2) != nullptr;
+  }
+  void Compute(Ctx& ctx) const override {
+    const at::Tensor& a = ctx.RequiredInput(0);
+    const at::Tensor& b = ctx.RequiredInput(1);
+    const int dt = DtypeCode(a.scalar_type());
+    if (!const_weight_ || ctx.HasInput(3) || dt < 0 || !a.is_cuda() || b.dim() != 2 || b.scalar_type() != at::kFloat8_e4m3fn ||
+        b.size(1) % 8 != 0 || (ctx.HasInput(4) && ctx.Input(4).scalar_type() != a.scalar_type())) {
+      Fallback(ctx);
+      return;
+    }
+    {
+      std::lock_guard<std::mutex> lock(mu_);
+      if (!w_.defined() || w_.scalar_type() != a.scalar_type()) {
+        at::Tensor s = ctx.RequiredInput(2).to(at::kFloat).repeat_interleave(block_, 1).narrow(1, 0, b.size(1));
+        w_ = (b.to(at::kFloat) * s).to(a.scalar_type()).contiguous();
+      }
+    }
+    const int64_t K = b.size(1), N = b.size(0);
+    at::Tensor x2 = a.reshape({-1, K}).contiguous();
+    at::Tensor bias = ctx.HasInput(4) ? ctx.Input(4) : at::Tensor();
+    at::Tensor y = LaunchGemm(ctx, x2, w_, N, 0, bias, at::Tensor(), ORTB200_ACT_NONE, 1.f);
+    std::vector<int64_t> shape(a.sizes().begin(), a.sizes().end());
+    shape.back() = N;
+    ctx.SetOutput(0, y.reshape(shape));
+  }
+
+ private:
+  int64_t block_ = 128;
+  bool const_weight_ = false;
+  mutable std::mutex mu_;
+  mutable at::Tensor w_;
+};
+
 void RegisterCudaKernels3(KernelRegistry& r) {
   Reg<MatMulNBitsKernel>(r, MS, "MatMulNBits");
   Reg<PagedAttentionKernel>(r, MS, "PagedAttention");
@@ -730,6 +773,7 @@ void RegisterCudaKernels3(KernelRegistry& r) {
   Reg<MoeKernel>(r, MS, "ShardedMoE");
   Reg<MoeKernel>(r, MS, "QMoE");
   Reg<GemmFloat8Kernel>(r, MS, "GemmFloat8");
+  Reg<BlockFp8WeightMatMulKernel>(r, MS, "MatMulBlockQuantizedFp8Weight");
   Reg<SymmCollectiveKernel>(r, MS, "AllReduce");
   Reg<SymmCollectiveKernel>(r, MS, "AllGather");
   Reg<SymmCollectiveKernel>(r, MS, "AllToAll");

@@ -325,3 +325,28 @@ def test_session_qmoe(bits, block):
                    expert_weight_bits=bits, block_size=block)
     c, g = rc[0].astype(np.float32), rg[0].astype(np.float32)
     assert np.abs(c - g).max() / np.abs(c).max() < 2e-2
+
+
+def test_block_scaled_fp8_weight_matmul_on_gpu():
+    """MatMulBlockQuantizedFp8Weight: the weight is expanded once and the product runs on the tcgen05 GEMM."""
+    import onnxruntime_b200 as ort
+    from onnxruntime_b200 import onnx_lite as ol
+    T = ol.TensorProto
+    torch.manual_seed(0)
+    N, K, bs = 512, 1024, 128
+    w8 = (torch.randn(N, K) * 2).to(torch.float8_e4m3fn)
+    scale = (torch.rand(N, K // bs) + 0.5).float() * 0.02
+    bias = torch.randn(N).to(torch.bfloat16)
+    node = ol.make_node("MatMulBlockQuantizedFp8Weight", ["a", "b", "s", "", "bias"], ["y"], domain="com.microsoft", block_size=bs)
+    g = ol.make_graph([node], "g", [ol.make_tensor_value_info("a", T.BFLOAT16, ["m", K])], [ol.make_tensor_value_info("y", T.BFLOAT16, ["m", N])],
+                      [ol.make_tensor("b", w8), ol.make_tensor("s", scale), ol.make_tensor("bias", bias)])
+    sess = ort.InferenceSession(ol.make_model(g, opset=17).serialize(), providers=["CUDAExecutionProvider"], enable_fallback=False)
+    w = (w8.float() * scale.repeat_interleave(bs, 1)).to(torch.bfloat16).float()
+    for m in (8, 300):
+        a = torch.randn(m, K).to(torch.bfloat16)
+        before = sess.kernel_launch_count()
+        (y,) = sess.run(None, {"a": a})
+        assert sess.kernel_launch_count() > before
+        ref = a.float() @ w.T + bias.float()
+        y = torch.as_tensor(y).float().cpu() if not isinstance(y, torch.Tensor) else y.float().cpu()
+        assert (y - ref).abs().max() / ref.abs().max() < 2e-2
