@@ -300,11 +300,14 @@ class GqaKernel final : public WithFallback {
     at::Tensor pos_ids;
     if (ctx.HasInput(9)) pos_ids = ctx.Input(9).to(query.device(), at::kLong).contiguous();
 
-    // one-token steps: on request (session config ortb200.fused_gqa_prep=1) the attention kernel unpacks, rotates and
-    // appends by itself.  One launch fewer, but every split re-rotates q and the split that owns the new key gains a
-    // serial tail; measured 0.19 ms per step slower on Llama-3-8B at batch 8, so the separate kernel stays the default.
+    // one-token steps: the tcgen05 decode kernel (head size 128) unpacks, rotates and appends by itself - one launch
+    // fewer and no round trip of the rotated query (3.63 -> 3.56 ms per step on Llama-3-8B at batch 8).  The CUDA-core
+    // kernel (head size 64) can do the same but was measured slower that way, so there it needs ortb200.fused_gqa_prep=1;
+    // "0" switches the fusion off everywhere.
+    const std::string fuse_cfg = ctx.session()->config().Get("ortb200.fused_gqa_prep", "auto");
+    const bool tc_kernel = H == 128 && ctx.session()->config().Get("ortb200.decode_attention_algo", "0") != "1";
     const bool fuse_prep = S == 1 && !first_prompt && packed && !pos_ids.defined() &&
-                           (!do_rotary_ || ctx.Input(7).size(1) * 2 == H) && ctx.session()->config().Get("ortb200.fused_gqa_prep", "0") == "1";
+                           (!do_rotary_ || ctx.Input(7).size(1) * 2 == H) && (fuse_cfg == "1" || (fuse_cfg != "0" && tc_kernel));
     if (!fuse_prep) {
       ortb200_gqa_prep_args pa{};
       pa.qkv = qc.data_ptr();

@@ -43,7 +43,9 @@ constexpr int kOffQ = kStages * kStageBytes;
 constexpr int kOffP = kOffQ + 2 * kQBox;
 constexpr int kOffMax = kOffP + 2 * 2 * kPBox;      // float [2][4][16]
 constexpr int kOffSum = kOffMax + 2 * 4 * 16 * 4;   // float [4][16]
-constexpr int kOffBar = kOffSum + 4 * 16 * 4;
+constexpr int kOffXch = kOffSum + 4 * 16 * 4;        // float [17][128]: q heads and the new key, for the rotary partner
+constexpr int kOffNew = kOffXch + 17 * 128 * 4;      // float [16]: scores of the new key
+constexpr int kOffBar = kOffNew + 16 * 4;
 constexpr int kSmemBytes = kOffBar + 256 + 1024;
 constexpr int kThreads = 160;              // 4 softmax warps + 1 TMA / MMA warp
 constexpr int kTmemCols = 64;              // S^T buffers at columns 0 and 16, O^T at 32
@@ -86,7 +88,13 @@ gqa_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + BAR_COUNT);
   float* sm_max = reinterpret_cast<float*>(smem + kOffMax);
   float* sm_sum = reinterpret_cast<float*>(smem + kOffSum);
+  float* sm_xch = reinterpret_cast<float*>(smem + kOffXch);
+  float* sm_new = reinterpret_cast<float*>(smem + kOffNew);
   __shared__ unsigned int sm_last;
+  // Fused step 1 (one new token per sequence): q, k and v come from the packed projection output; this kernel
+  // rotates q and k, writes the query tile itself, appends k / v to the cache and attends to the new key from
+  // registers, so no separate prep launch and no round trip of the rotated query through global memory.
+  const bool fused = p.qkv != nullptr;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
@@ -98,7 +106,7 @@ gqa_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     tma_prefetch_desc(&tm_q);
     tma_prefetch_desc(&tm_k);
     tma_prefetch_desc(&tm_v);
-    for (int i = 0; i < BAR_COUNT; ++i) mbar_init(&bars[i], (i == BAR_P0 || i == BAR_P1) ? 128 : 1);
+    for (int i = 0; i < BAR_COUNT; ++i) mbar_init(&bars[i], (i == BAR_P0 || i == BAR_P1 || (i == BAR_Q && fused)) ? 128 : 1);
     fence_mbar_init();
   }
   if (warp == 4) {
@@ -118,7 +126,9 @@ gqa_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   int chunk = (len + p.splits - 1) / p.splits;
   if (PAGED) chunk = (chunk + kTile - 1) / kTile * kTile;   // tiles start on piece boundaries (start0 is 0 when paged)
   const int k_begin = start0 + split * chunk;
-  const int k_end = min(total, k_begin + chunk);
+  // fused: the newest key (position total - 1) is not in the cache yet; the CTA whose range reaches it takes it
+  const bool owns_new = fused && k_begin < total && k_begin + chunk >= total;
+  const int k_end = owns_new ? total - 1 : min(total, k_begin + chunk);
   const int n_tiles = k_end > k_begin ? (k_end - k_begin + kTile - 1) / kTile : 0;
 
   if (warp == 4) {
@@ -175,7 +185,7 @@ gqa_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     };
     bool ok = true;
     if (n_tiles > 0) {
-      if (lane == 0) {
+      if (lane == 0 && !fused) {
         mbar_expect_tx(&bars[BAR_Q], 2 * kQBox);
         tma_load_2d(smem + kOffQ, &tm_q, &bars[BAR_Q], 0, b * p.N + head0);
         tma_load_2d(smem + kOffQ + kQBox, &tm_q, &bars[BAR_Q], 64, b * p.N + head0);
@@ -229,6 +239,81 @@ gqa_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   }
   bool ok = true;
   const float scale_log2 = p.scale * 1.4426950408889634f;
+  float v_new = 0.f;   // fused: this thread's dim of the new value row
+  if (warp < 4 && fused) {
+    // thread t holds dim t of every query head of the group, of the new key and of the new value
+    const int t = tid;
+    const T* row = static_cast<const T*>(p.qkv) + static_cast<long long>(b) * (p.N + 2 * p.Nk) * H;
+    float c = 1.f, sn = 0.f;
+    if (p.do_rotary) {
+      const int fi = p.interleaved ? (t >> 1) : (t & (H / 2 - 1));
+      c = to_float<T>(static_cast<const T*>(p.cos_cache)[static_cast<long long>(total - 1) * (H / 2) + fi]);
+      sn = to_float<T>(static_cast<const T*>(p.sin_cache)[static_cast<long long>(total - 1) * (H / 2) + fi]);
+    }
+    float qx[G];
+#pragma unroll
+    for (int g = 0; g < G; ++g) qx[g] = g < n_heads ? to_float<T>(row[static_cast<long long>(head0 + g) * H + t]) : 0.f;
+    float kx = to_float<T>(row[static_cast<long long>(p.N + kvh) * H + t]);
+    const T v_raw = row[static_cast<long long>(p.N + p.Nk + kvh) * H + t];
+    v_new = to_float<T>(v_raw);
+    if (p.do_rotary) {
+#pragma unroll
+      for (int g = 0; g < G; ++g) sm_xch[g * 128 + t] = qx[g];
+      sm_xch[16 * 128 + t] = kx;
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      const int partner = p.interleaved ? (t ^ 1) : (t ^ (H / 2));
+      const bool second = p.interleaved ? (t & 1) : (t >= H / 2);   // holds the "imaginary" half of its pair
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+        const float o = sm_xch[g * 128 + partner];
+        qx[g] = second ? qx[g] * c + o * sn : qx[g] * c - o * sn;
+      }
+      const float ok_ = sm_xch[16 * 128 + partner];
+      kx = second ? kx * c + ok_ * sn : kx * c - ok_ * sn;
+    }
+    // the query tile in the layout MMA 1 reads (128-byte swizzle, K-major); rows past the group stay zero
+    const T k_t = from_float<T>(kx);
+    float part[G];
+    {
+      uint8_t* qb = smem + kOffQ + (t >> 6) * kQBox;
+      const int col = t & 63;
+#pragma unroll
+      for (int g = 0; g < 16; ++g) {
+        T qt = from_float<T>(0.f);
+        if (g < G) {
+          qt = from_float<T>(qx[g < G ? g : 0]);
+          part[g < G ? g : 0] = to_float<T>(qt) * to_float<T>(k_t);
+        }
+        *reinterpret_cast<T*>(qb + g * 128 + (((col >> 3) ^ (g & 7)) << 4) + (col & 7) * 2) = qt;
+      }
+    }
+    fence_proxy_async();
+    mbar_arrive(&bars[BAR_Q]);
+    // score of the new key for every head: a 128-thread dot product
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      const float ws = warp_sum(part[g]);
+      if (lane == 0) sm_sum[warp * 16 + g] = ws;
+    }
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    if (t < G) sm_new[t] = sm_sum[t] + sm_sum[16 + t] + sm_sum[32 + t] + sm_sum[48 + t];
+    if (owns_new) {
+      long long crow;
+      if (PAGED) {
+        const int key = total - 1;
+        const int bi = key / p.block_size;
+        const int blk = bi < p.max_blocks ? p.block_table[static_cast<long long>(b) * p.max_blocks + bi] : -1;
+        crow = blk >= 0 ? ((static_cast<long long>(blk) * p.block_size + key % p.block_size) * p.Nk + kvh) * H : -1;
+      } else {
+        crow = ((static_cast<long long>(b) * p.Nk + kvh) * p.Smax + (total - 1)) * H;
+      }
+      if (crow >= 0 && total - 1 < p.Smax) {
+        static_cast<T*>(const_cast<void*>(p.k_cache))[crow + t] = k_t;
+        static_cast<T*>(const_cast<void*>(p.v_cache))[crow + t] = v_raw;
+      }
+    }
+    asm volatile("bar.sync 1, 128;" ::: "memory");   // sm_sum is reused at the end; sm_new is complete
+  }
   if (warp < 4) {
     const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
     // A wait that gives up clears `ok`; the loop still runs to its end (without further waits) so that every
@@ -349,6 +434,20 @@ gqa_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     tcgen05_fence_after();
     tmem_dealloc(tmem_base, kTmemCols);
   }
+  if (owns_new) {
+    // fold the new key, held in registers, into the state of this CTA's key range
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      float sc = sm_new[g] * p.scale;
+      if (p.softcap > 0.f) sc = p.softcap * tanhf(sc / p.softcap);
+      const float m_new = fmaxf(fm[g], sc);
+      const float c_old = safe_exp_diff(fm[g], m_new);
+      const float pn = __expf(sc - m_new);
+      fl[g] = fl[g] * c_old + pn;
+      fa[g] = fa[g] * c_old + pn * v_new;
+      fm[g] = m_new;
+    }
+  }
   const int tile = b * p.Nk + kvh;
   decode_finish<T, H, G>(p, tile, split, b, head0, n_heads, tid, fm, fl, fa, &sm_last);
 }
@@ -389,10 +488,11 @@ int launch_tc_g(int group, const CUtensorMap& tq, const CUtensorMap& tk, const C
 
 bool gqa_decode_tc_supported(const ortb200_gqa_decode_args* a) {
   if (a->H != 128 || (a->dtype != ORTB200_BF16 && a->dtype != ORTB200_F16)) return false;
-  if (a->qkv != nullptr || a->q == nullptr) return false;
+  if (a->qkv == nullptr && a->q == nullptr) return false;
+  if (a->qkv != nullptr && (reinterpret_cast<uintptr_t>(a->qkv) & 15)) return false;
   const int group = a->N / a->Nk;
   if (group > 16 || !a->workspace) return false;
-  if (reinterpret_cast<uintptr_t>(a->q) & 15) return false;
+  if (a->qkv == nullptr && (reinterpret_cast<uintptr_t>(a->q) & 15)) return false;
   if (a->block_table) {
     const int bs = a->block_size;
     if (bs < 8 || (bs & (bs - 1)) != 0 || a->window > 0 || a->num_blocks <= 0) return false;
@@ -426,7 +526,9 @@ int launch_gqa_decode_tc(const ortb200_gqa_decode_args* a, cudaStream_t stream) 
 
   const CUtensorMapDataType dt = a->dtype == ORTB200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
   CUtensorMap tq, tk, tv;
-  if (make_tensor_map_2d(&tq, a->q, dt, 2, H, static_cast<int64_t>(a->B) * a->N, H * 2, 64, 16) != 0) return -5;
+  // fused launches build the query tile themselves; the map then only has to be a valid one
+  const void* q_base = a->qkv != nullptr ? a->k_cache : a->q;
+  if (make_tensor_map_2d(&tq, q_base, dt, 2, H, static_cast<int64_t>(a->B) * a->N, H * 2, 64, 16) != 0) return -5;
   int piece_rows = kTile;
   if (a->block_table) {
     piece_rows = a->block_size < kTile ? a->block_size : kTile;
@@ -451,6 +553,8 @@ int launch_gqa_decode_tc(const ortb200_gqa_decode_args* a, cudaStream_t stream) 
   p.scale = a->scale != 0.f ? a->scale : 1.0f / sqrtf(static_cast<float>(H));
   p.softcap = a->softcap;
   p.block_table = a->block_table; p.block_size = a->block_size; p.max_blocks = a->max_blocks;
+  p.qkv = a->qkv; p.cos_cache = a->cos_cache; p.sin_cache = a->sin_cache;
+  p.do_rotary = a->do_rotary; p.interleaved = a->rotary_interleaved;
   dim3 grid(splits, a->Nk, a->B);
   const bool pdl = a->use_pdl != 0;
   if (a->dtype == ORTB200_BF16) {
