@@ -53,10 +53,10 @@ def main(argv=None) -> int:
     runner = PagedDecoderRunner(sess, cfg, batch=a.batch, max_len=max_len, block_size=a.block_size, tp_size=world, device=device)
     runner.assume_context(a.context)
     tokens = torch.randint(0, cfg.vocab_size, (a.batch,), device=device)
-    runner.decode_step(tokens)
     before = sess.kernel_launch_count()
-    runner.decode_step()
+    runner.decode_step(tokens)     # the first step runs eagerly (the session captures its graph afterwards): count it
     launches = sess.kernel_launch_count() - before
+    runner.decode_step()
     ms = timed_ms(lambda: runner.decode_step(), a.steps, a.warmup, world, device)
     sess.check_device_status()
     report(rank, metric="llama3_70b_int4_paged_decode_tokens_per_s" if a.model == "70b" and not a.dense else "paged_decode_tokens_per_s",

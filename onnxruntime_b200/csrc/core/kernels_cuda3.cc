@@ -156,6 +156,10 @@ class PagedAttentionKernel final : public WithFallback {
     at::Tensor qc = query.contiguous();
     at::Tensor q_rot = at::empty({T, N_, H}, query.options());
     at::Tensor tb = table.contiguous();
+    // head size 128: the tcgen05 decode kernel rotates, appends and attends in one launch
+    const bool fuse = packed && H == 128 && window_ <= 0 && (block_size & (block_size - 1)) == 0 && block_size >= 8 &&
+                      (!do_rotary_ || ctx.Input(8).size(1) * 2 == H) && ctx.session()->config().Get("ortb200.fused_gqa_prep", "auto") != "0" &&
+                      ctx.session()->config().Get("ortb200.decode_attention_algo", "0") != "1";
     ortb200_paged_prep_args pa{};
     pa.qkv = qc.data_ptr();
     at::Tensor kin, vin;
@@ -181,7 +185,7 @@ class PagedAttentionKernel final : public WithFallback {
     pa.do_rotary = do_rotary_ ? 1 : 0;
     pa.dtype = dt;
     pa.status = ctx.session()->StatusWord().data_ptr<int>();
-    CheckLaunch(ortb200_paged_prep(&pa, ctx.cuda_stream()), "ortb200_paged_prep");
+    if (!fuse) CheckLaunch(ortb200_paged_prep(&pa, ctx.cuda_stream()), "ortb200_paged_prep");
 
     at::Tensor out = at::empty({T, N_ * H}, query.options());
     at::Tensor& ws = ctx.session()->AttnWorkspace(ortb200_gqa_decode_workspace_bytes(static_cast<int>(B), static_cast<int>(N_), static_cast<int>(H)));
@@ -205,8 +209,16 @@ class PagedAttentionKernel final : public WithFallback {
     da.block_size = static_cast<int>(block_size);
     da.max_blocks = static_cast<int>(tb.size(1));
     da.num_blocks = static_cast<int>(num_blocks);
+    if (fuse) {
+      da.qkv = qc.data_ptr();
+      da.cos_cache = pa.cos_cache;
+      da.sin_cache = pa.sin_cache;
+      da.do_rotary = pa.do_rotary;
+      da.rotary_interleaved = pa.interleaved;
+      da.algo = 2;
+    }
     CheckLaunch(ortb200_gqa_decode(&da, ctx.cuda_stream()), "ortb200_gqa_decode(paged)");
-    ctx.session()->AddLaunches(2);
+    ctx.session()->AddLaunches(fuse ? 1 : 2);
     ctx.SetOutput(0, out);
     if (ctx.OutputCount() > 1) ctx.SetOutput(1, kc);
     if (ctx.OutputCount() > 2) ctx.SetOutput(2, vc);

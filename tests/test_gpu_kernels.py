@@ -322,3 +322,30 @@ def test_gqa_decode_tensor_core_kernel_paged(K, block_size):
         out = K.gqa_decode(q, kc, vc, lens - 1, block_table=tb, algo=algo)
         assert torch.isfinite(out.float()).all(), algo
         assert _rel(out.view(B, N, H), ref) < 2e-2, algo
+
+
+@pytest.mark.parametrize("interleaved", [False, True])
+def test_gqa_decode_tensor_core_kernel_paged_fused_append(K, interleaved):
+    """Paged cache + fused step 1 in the tcgen05 kernel: same result as rotating / appending first and attending after,
+    and the new key / value land in the right slot of the block pool."""
+    torch.manual_seed(2)
+    B, N, Nk, H, bs = 3, 8, 2, 128, 16
+    max_len = 256
+    per_seq = max_len // bs
+    lens = torch.tensor([1, 100, 256], dtype=torch.int32, device="cuda")     # totals including the new token
+    num_blocks = B * per_seq
+    table = torch.randperm(num_blocks, device="cuda").view(B, per_seq).int()
+    kc = torch.randn(num_blocks, bs, Nk, H, device="cuda").bfloat16()
+    vc = torch.randn(num_blocks, bs, Nk, H, device="cuda").bfloat16()
+    qkv = torch.randn(B, (N + 2 * Nk) * H, device="cuda").bfloat16()
+    pos = torch.arange(max_len, device="cuda").float()
+    inv = 1.0 / (10000 ** (torch.arange(0, H // 2, device="cuda").float() / (H // 2)))
+    cos, sin = torch.outer(pos, inv).cos().bfloat16(), torch.outer(pos, inv).sin().bfloat16()
+    k1, v1 = kc.clone(), vc.clone()
+    cu = torch.arange(B + 1, dtype=torch.int32, device="cuda")
+    q_rot = K.paged_prep(qkv, k1, v1, cu, lens - 1, table, N, Nk, cos=cos, sin=sin, interleaved=interleaved)
+    want = K.gqa_decode(q_rot.view(B, N, H), k1, v1, lens - 1, block_table=table, algo=2)
+    k2, v2 = kc.clone(), vc.clone()
+    got = K.gqa_decode(None, k2, v2, lens - 1, block_table=table, qkv=qkv, num_heads=N, cos=cos, sin=sin, interleaved=interleaved, algo=2)
+    assert _rel(got, want) < 1e-2
+    assert torch.equal(k1, k2) and torch.equal(v1, v2)
