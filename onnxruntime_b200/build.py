@@ -103,6 +103,19 @@ def write_ninja(kernels_only: bool = False) -> str:
         core_so = os.path.join(HERE, core_ext_name())
         lines.append(f"build {core_so}: cxxlink " + " ".join(cobjs) + f" | {kern_so}")
         defaults.append(core_so)
+        # the same runtime without the Python bindings, behind the C API (ortb200_c_api.h)
+        lines += [
+            "rule cxxlink_c",
+            f"  command = $cxx -shared -o $out $in -L{torch_lib} -L{LIBDIR} -L{cuda}/lib64 "
+            "-lc10 -ltorch_cpu -ltorch -lc10_cuda -ltorch_cuda -lcudart -lortb200_kernels "
+            f"-Wl,-rpath,{torch_lib} -Wl,-rpath,'$$ORIGIN' -Wl,-rpath,{cuda}/lib64",
+            "  description = LINK $out",
+        ]
+        python_only = ("core_bindings.o", "core_python_ops.o")
+        c_objs = [o for o in cobjs if os.path.basename(o) not in python_only]
+        c_so = os.path.join(LIBDIR, "libortb200.so")
+        lines.append(f"build {c_so}: cxxlink_c " + " ".join(c_objs) + f" | {kern_so}")
+        defaults.append(c_so)
     lines.append("default " + " ".join(defaults))
     path = os.path.join(BUILD, "build.ninja")
     with open(path, "w") as f:
