@@ -1,0 +1,170 @@
+"""8-bit quantisation of ONNX models: dynamic (weights offline, activations at run time) and static (QDQ format
+from calibration data).
+
+Counterparts in the reference: ``quantize_dynamic`` / ``quantize_static`` / ``MinMaxCalibrater``
+(onnxruntime/python/tools/quantization/quantize.py, onnx_quantizer.py, qdq_quantizer.py, calibrate.py).
+
+* ``quantize_dynamic``: every ``MatMul`` with a constant 2-D weight becomes ``com.microsoft.DynamicQuantizeMatMul``
+  (the activation is quantised to uint8 per call, the weight is stored as int8 / uint8 with a per-tensor or
+  per-column scale).
+* ``quantize_static``: activations of ``MatMul`` / ``Gemm`` / ``Conv`` are observed on calibration feeds (min / max),
+  then ``QuantizeLinear -> DequantizeLinear`` pairs are inserted on their inputs and the constant weights are stored
+  quantised behind a ``DequantizeLinear`` (QDQ format); the engine's optimizer or any QDQ-aware runtime can fuse them.
+"""
+from __future__ import annotations
+
+from typing import Dict, Iterable, List, Optional, Sequence, Union
+
+import numpy as np
+
+from .. import onnx_lite as ol
+
+T = ol.TensorProto
+
+
+def _load(model: Union[str, bytes, ol.Model]) -> ol.Model:
+    return model if isinstance(model, ol.Model) else ol.load_model(model)
+
+
+def _save(model: ol.Model, path: Optional[str]) -> ol.Model:
+    if path:
+        with open(path, "wb") as f:
+            f.write(model.serialize())
+    return model
+
+
+def quantize_weight(w: np.ndarray, signed: bool = True, per_channel: bool = False, axis: int = -1, symmetric: bool = True):
+    """float weight -> (q, scale, zero_point).  Per-channel scales run along ``axis``."""
+    w = np.asarray(w, dtype=np.float32)
+    qmin, qmax = (-127, 127) if signed else (0, 255)
+    if per_channel:
+        red = tuple(i for i in range(w.ndim) if i != axis % w.ndim)
+        lo, hi = w.min(axis=red), w.max(axis=red)
+        shape = [1] * w.ndim
+        shape[axis % w.ndim] = -1
+    else:
+        lo, hi = np.float32(w.min()), np.float32(w.max())
+        shape = []
+    lo, hi = np.minimum(lo, 0), np.maximum(hi, 0)
+    if symmetric and signed:
+        scale = np.maximum(np.abs(lo), np.abs(hi)) / 127.0
+        zp = np.zeros_like(scale)
+    else:
+        scale = (hi - lo) / float(qmax - qmin)
+        zp = None
+    scale = np.where(scale == 0, 1.0, scale).astype(np.float32)
+    if zp is None:
+        zp = np.clip(np.rint(qmin - lo / scale), qmin, qmax)
+    s, z = (scale.reshape(shape), zp.reshape(shape)) if per_channel else (scale, zp)
+    q = np.clip(np.rint(w / s) + z, qmin, qmax).astype(np.int8 if signed else np.uint8)
+    return q, scale.astype(np.float32), zp.astype(np.int8 if signed else np.uint8)
+
+
+def quantize_dynamic(model_input, model_output: Optional[str] = None, per_channel: bool = False, weight_signed: bool = True,
+                     nodes_to_exclude: Iterable[str] = ()) -> ol.Model:
+    model = _load(model_input)
+    g = model.graph
+    inits = {t.name: t for t in g.initializers}
+    exclude = set(nodes_to_exclude)
+    new_nodes: List[ol.Node] = []
+    for n in g.nodes:
+        w_t = inits.get(n.inputs[1]) if n.op_type == "MatMul" and n.domain == "" and len(n.inputs) == 2 else None
+        if w_t is None or n.name in exclude or len(w_t.dims) != 2:
+            new_nodes.append(n)
+            continue
+        w = ol.to_array(w_t)
+        if w.dtype not in (np.float32, np.float16):
+            new_nodes.append(n)
+            continue
+        q, scale, zp = quantize_weight(w, signed=weight_signed, per_channel=per_channel, axis=1)
+        base = n.inputs[1]
+        g.initializers += [ol.make_tensor(base + "_quantized", q), ol.make_tensor(base + "_scale", scale),
+                           ol.make_tensor(base + "_zero_point", zp)]
+        new_nodes.append(ol.make_node("DynamicQuantizeMatMul", [n.inputs[0], base + "_quantized", base + "_scale", base + "_zero_point"],
+                                      list(n.outputs), name=(n.name + "_quant") if n.name else "", domain="com.microsoft"))
+    g.nodes = new_nodes
+    used = {i for n in g.nodes for i in n.inputs} | {o.name for o in g.outputs}
+    g.initializers = [t for t in g.initializers if t.name in used]
+    model.opset_imports.setdefault("com.microsoft", 1)
+    return _save(model, model_output)
+
+
+class MinMaxCalibrator:
+    """Runs the float model on calibration feeds with the chosen tensors exposed as outputs and keeps their ranges."""
+
+    def __init__(self, model: ol.Model, tensors: Sequence[str]):
+        import copy
+
+        import onnxruntime_b200 as ort
+        m = copy.deepcopy(model)
+        have = {o.name for o in m.graph.outputs}
+        self.tensors = [t for t in dict.fromkeys(tensors)]
+        for t in self.tensors:
+            if t not in have:
+                m.graph.outputs.append(ol.make_tensor_value_info(t, 0, None))
+        so = ort.SessionOptions()
+        so.graph_optimization_level = ort.GraphOptimizationLevel.ORT_DISABLE_ALL
+        self.sess = ort.InferenceSession(m.serialize(), so, providers=["CPUExecutionProvider"])
+        self.ranges: Dict[str, List[float]] = {}
+
+    def collect(self, feeds: Dict[str, np.ndarray]) -> None:
+        graph_inputs = {i.name for i in self.sess.get_inputs()}
+        outs = self.sess.run(self.tensors, {k: v for k, v in feeds.items() if k in graph_inputs})
+        for name, v in zip(self.tensors, outs):
+            v = np.asarray(v, dtype=np.float32)
+            lo, hi = float(v.min()), float(v.max())
+            r = self.ranges.setdefault(name, [lo, hi])
+            r[0], r[1] = min(r[0], lo), max(r[1], hi)
+
+
+def quantize_static(model_input, calibration_feeds: Iterable[Dict[str, np.ndarray]], model_output: Optional[str] = None,
+                    op_types: Sequence[str] = ("MatMul", "Gemm", "Conv"), per_channel: bool = False) -> ol.Model:
+    """QDQ format: uint8 asymmetric activations, int8 symmetric weights (per tensor, or per output channel)."""
+    model = _load(model_input)
+    g = model.graph
+    inits = {t.name: t for t in g.initializers}
+    targets = [n for n in g.nodes if n.op_type in op_types and n.domain == ""]
+    acts = [n.inputs[0] for n in targets if n.inputs[0] not in inits]
+    calib = MinMaxCalibrator(model, acts)
+    for feeds in calibration_feeds:
+        calib.collect(feeds)
+    new_nodes: List[ol.Node] = []
+    qdq_of: Dict[str, str] = {}
+    for n in g.nodes:
+        if n not in targets:
+            new_nodes.append(n)
+            continue
+        ins = list(n.inputs)
+        a = ins[0]
+        if a in calib.ranges:
+            if a not in qdq_of:
+                lo, hi = min(calib.ranges[a][0], 0.0), max(calib.ranges[a][1], 0.0)
+                scale = np.float32((hi - lo) / 255.0) if hi > lo else np.float32(1.0)
+                zp = np.uint8(np.clip(np.rint(-lo / scale), 0, 255))
+                g.initializers += [ol.make_tensor(a + "_scale", np.array(scale, np.float32)), ol.make_tensor(a + "_zero_point", np.array(zp, np.uint8))]
+                new_nodes.append(ol.make_node("QuantizeLinear", [a, a + "_scale", a + "_zero_point"], [a + "_quantized"], name=a + "_QuantizeLinear"))
+                new_nodes.append(ol.make_node("DequantizeLinear", [a + "_quantized", a + "_scale", a + "_zero_point"], [a + "_dequantized"],
+                                              name=a + "_DequantizeLinear"))
+                qdq_of[a] = a + "_dequantized"
+            ins[0] = qdq_of[a]
+        w_t = inits.get(ins[1]) if len(ins) > 1 else None
+        if w_t is not None and ol.to_array(w_t).dtype == np.float32:
+            w = ol.to_array(w_t)
+            # output channels: rows of a Conv weight / transposed Gemm weight, columns of a MatMul weight
+            trans_b = n.op_type == "Gemm" and any(a_.name == "transB" and ol.attr_value(a_) == 1 for a_ in n.attributes)
+            axis = 0 if (n.op_type == "Conv" or trans_b) else w.ndim - 1
+            q, scale, zp = quantize_weight(w, signed=True, per_channel=per_channel, axis=axis)
+            base = ins[1]
+            g.initializers += [ol.make_tensor(base + "_quantized", q), ol.make_tensor(base + "_scale", scale), ol.make_tensor(base + "_zero_point", zp)]
+            dq = ol.make_node("DequantizeLinear", [base + "_quantized", base + "_scale", base + "_zero_point"], [base + "_dequantized"],
+                              name=base + "_DequantizeLinear", **({"axis": axis} if per_channel else {}))
+            new_nodes.append(dq)
+            ins[1] = base + "_dequantized"
+        n.inputs = ins
+        new_nodes.append(n)
+    g.nodes = new_nodes
+    used = {i for n in g.nodes for i in n.inputs} | {o.name for o in g.outputs}
+    g.initializers = [t for t in g.initializers if t.name in used]
+    if per_channel and model.opset_imports.get("", 0) < 13:
+        model.opset_imports[""] = 13
+    return _save(model, model_output)

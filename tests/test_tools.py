@@ -122,3 +122,43 @@ def test_onnx_test_runner(tmp_path):
     assert onnx_test_runner.main([str(tmp_path)]) == 0
     (ds / "output_0.pb").write_bytes(ol.make_tensor("y", y + 1).serialize())
     assert onnx_test_runner.main([str(tmp_path)]) == 1
+
+
+def _two_layer_mlp():
+    import numpy as np
+    from onnxruntime_b200 import onnx_lite as ol
+    T = ol.TensorProto
+    rng = np.random.default_rng(0)
+    w1, w2 = rng.standard_normal((16, 32)).astype(np.float32) * 0.3, rng.standard_normal((32, 8)).astype(np.float32) * 0.3
+    g = ol.make_graph([ol.make_node("MatMul", ["x", "w1"], ["h"], name="fc1"), ol.make_node("Relu", ["h"], ["r"]),
+                       ol.make_node("MatMul", ["r", "w2"], ["y"], name="fc2")], "mlp",
+                      [ol.make_tensor_value_info("x", T.FLOAT, ["n", 16])], [ol.make_tensor_value_info("y", T.FLOAT, ["n", 8])],
+                      [ol.make_tensor("w1", w1), ol.make_tensor("w2", w2)])
+    return ol.make_model(g, opset=17).serialize(), rng
+
+
+def test_quantize_dynamic_and_static_keep_the_model_close_to_float():
+    """quantize_dynamic -> DynamicQuantizeMatMul; quantize_static -> QDQ pairs from calibrated ranges
+    (reference: onnxruntime/python/tools/quantization/quantize.py)."""
+    import numpy as np
+    import onnxruntime_b200 as ort
+    from onnxruntime_b200 import onnx_lite as ol
+    from onnxruntime_b200.quantization import quantize_dynamic, quantize_static
+    model, rng = _two_layer_mlp()
+    x = rng.standard_normal((12, 16)).astype(np.float32)
+    (ref,) = ort.InferenceSession(model, providers=["CPUExecutionProvider"]).run(None, {"x": x})
+    for per_channel in (False, True):
+        qd = quantize_dynamic(model, per_channel=per_channel, nodes_to_exclude=["fc2"])
+        ops = [n.op_type for n in qd.graph.nodes]
+        assert ops == ["DynamicQuantizeMatMul", "Relu", "MatMul"]
+        qd = quantize_dynamic(model, per_channel=per_channel)
+        assert [n.op_type for n in qd.graph.nodes] == ["DynamicQuantizeMatMul", "Relu", "DynamicQuantizeMatMul"]
+        assert all(ol.to_array(t).dtype == np.int8 for t in qd.graph.initializers if t.name.endswith("_quantized"))
+        (y,) = ort.InferenceSession(qd.serialize(), providers=["CPUExecutionProvider"]).run(None, {"x": x})
+        assert np.abs(y - ref).max() < 0.05 * np.abs(ref).max()
+        calib = [{"x": rng.standard_normal((12, 16)).astype(np.float32)} for _ in range(4)] + [{"x": x}]
+        qs = quantize_static(model, calib, per_channel=per_channel)
+        ops = [n.op_type for n in qs.graph.nodes]
+        assert ops.count("QuantizeLinear") == 2 and ops.count("DequantizeLinear") == 4 and ops.count("MatMul") == 2
+        (y,) = ort.InferenceSession(qs.serialize(), providers=["CPUExecutionProvider"]).run(None, {"x": x})
+        assert np.abs(y - ref).max() < 0.05 * np.abs(ref).max()
