@@ -162,3 +162,31 @@ def test_quantize_dynamic_and_static_keep_the_model_close_to_float():
         assert ops.count("QuantizeLinear") == 2 and ops.count("DequantizeLinear") == 4 and ops.count("MatMul") == 2
         (y,) = ort.InferenceSession(qs.serialize(), providers=["CPUExecutionProvider"]).run(None, {"x": x})
         assert np.abs(y - ref).max() < 0.05 * np.abs(ref).max()
+
+
+def test_shape_inference_by_tracing_names_symbolic_dimensions():
+    import numpy as np
+    from onnxruntime_b200 import onnx_lite as ol
+    from onnxruntime_b200.tools.shape_inference import infer_shapes
+    T = ol.TensorProto
+    w = np.zeros((16, 4), np.float32)
+    nodes = [ol.make_node("MatMul", ["x", "w"], ["h"]),                      # [batch, seq, 4]
+             ol.make_node("Shape", ["h"], ["shp"]),                           # [3]
+             ol.make_node("Transpose", ["h"], ["t"], perm=[0, 2, 1]),         # [batch, 4, seq]
+             ol.make_node("ReduceSum", ["t"], ["r"], keepdims=0),             # scalar (all axes)
+             ol.make_node("Concat", ["h", "h"], ["c"], axis=1)]               # [batch, 2 * seq, 4]: a new symbol
+    g = ol.make_graph(nodes, "g", [ol.make_tensor_value_info("x", T.FLOAT, ["batch", "seq", 16])],
+                      [ol.make_tensor_value_info("c", T.FLOAT, None), ol.make_tensor_value_info("r", T.FLOAT, None)],
+                      [ol.make_tensor("w", w)])
+    m = infer_shapes(ol.make_model(g, opset=17).serialize())
+    info = {v.name: (v.elem_type, list(v.shape)) for v in m.graph.value_info}
+    assert info["h"] == (T.FLOAT, ["batch", "seq", 4])
+    assert info["shp"] == (T.INT64, [3])
+    assert info["t"] == (T.FLOAT, ["batch", 4, "seq"])
+    out = {v.name: v for v in m.graph.outputs}
+    assert list(out["r"].shape) == [] and out["c"].shape[0] == "batch" and out["c"].shape[2] == 4
+    assert isinstance(out["c"].shape[1], str) and out["c"].shape[1].startswith("unk__")
+    # the annotated model still loads and runs
+    import onnxruntime_b200 as ort
+    sess = ort.InferenceSession(m.serialize(), providers=["CPUExecutionProvider"])
+    assert sess.run(None, {"x": np.ones((2, 3, 16), np.float32)})[0].shape == (2, 6, 4)
