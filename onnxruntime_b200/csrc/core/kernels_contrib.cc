@@ -487,7 +487,47 @@ void GqaImpl(Ctx& ctx) {
   if (ctx.HasInput(9)) in.position_ids = ctx.Input(9);
   if (ctx.HasInput(10)) in.attention_bias = ctx.Input(10);
   if (ctx.HasInput(11)) in.head_sink = ctx.Input(11);
-  ORTB_ENFORCE_ARG(!ctx.HasInput(12) && !ctx.HasInput(13), "quantized KV cache is not supported by this kernel");
+  // Per-head RMS norm of Q and K before the rotary embedding (q_norm_weight / k_norm_weight, Qwen3-style models):
+  // a packed QKV input is split so that the normalised parts travel as separate query / key / value.
+  if (ctx.HasInput(14) || ctx.HasInput(15)) {
+    ORTB_ENFORCE_ARG(ctx.HasInput(14) && ctx.HasInput(15), "q_norm_weight and k_norm_weight must be given together");
+    const int64_t N = n.attr_i("num_heads", 0), Nk = n.attr_i("kv_num_heads", 0);
+    const float eps = n.attr_f("qk_norm_epsilon", 1e-6f);
+    const int64_t B = in.query.size(0), S = in.query.size(1);
+    if (!in.key.defined()) {
+      const int64_t H = in.query.size(2) / (N + 2 * Nk);
+      at::Tensor packed = in.query;
+      in.query = packed.narrow(2, 0, N * H);
+      in.key = packed.narrow(2, N * H, Nk * H);
+      in.value = packed.narrow(2, (N + Nk) * H, Nk * H);
+    }
+    auto head_norm = [&](const at::Tensor& x, int64_t heads, const at::Tensor& w) {
+      at::Tensor xf = x.reshape({B, S, heads, -1}).to(at::kFloat);
+      at::Tensor y = xf * at::rsqrt(xf.pow(2).mean(-1, true) + eps) * w.to(at::kFloat);
+      return y.reshape({B, S, -1}).to(x.scalar_type());
+    };
+    in.query = head_norm(in.query, N, ctx.Input(14));
+    in.key = head_norm(in.key, Nk, ctx.Input(15));
+  }
+  // Quantised KV cache (k_scale / v_scale; int8 or float8 e4m3 caches, per tensor or per channel): the past is
+  // expanded to the compute type, attention runs as usual, and the present is quantised back - into the past
+  // buffer itself when it has room, as the float path does.
+  const bool quant_cache = ctx.HasInput(12) || ctx.HasInput(13);
+  at::Tensor q_past_k, q_past_v, k_scale, v_scale;
+  if (quant_cache) {
+    ORTB_ENFORCE_ARG(ctx.HasInput(12) && ctx.HasInput(13), "k_scale and v_scale must be given together");
+    ORTB_ENFORCE_ARG(n.attr_i("kv_cache_bit_width", 8) == 8, "4-bit KV caches are not supported by this kernel");
+    k_scale = ctx.Input(12).to(at::kFloat);
+    v_scale = ctx.Input(13).to(at::kFloat);
+    q_past_k = in.past_key;
+    q_past_v = in.past_value;
+    if (q_past_k.defined()) {
+      const at::ScalarType ct = q_past_k.scalar_type();
+      ORTB_ENFORCE_ARG(ct == at::kChar || ct == at::kFloat8_e4m3fn, "quantised KV cache must be int8 or float8e4m3fn");
+      in.past_key = (q_past_k.to(at::kFloat) * k_scale).to(in.query.scalar_type());
+      in.past_value = (q_past_v.to(at::kFloat) * v_scale).to(in.query.scalar_type());
+    }
+  }
   // A past buffer with room for the new tokens is updated in place and returned as present
   // (the reference's past_present_share_buffer mode); otherwise present is a new tensor.
   in.share_buffer = in.past_key.defined() && in.past_key.size(2) >= in.total_sequence_length;
@@ -502,6 +542,22 @@ void GqaImpl(Ctx& ctx) {
   a.smooth_softmax = n.attr_i("smooth_softmax", 0) != 0;
   GqaResult r = GqaForward(in, a);
   ctx.SetOutput(0, r.output);
+  if (quant_cache) {
+    const at::ScalarType ct = q_past_k.defined() ? q_past_k.scalar_type()
+                                                 : (n.attr_s("k_quant_type", "PER_TENSOR") == "NONE" ? in.query.scalar_type() : at::kChar);
+    auto quantise = [&](const at::Tensor& x, const at::Tensor& scale, const at::Tensor& into) {
+      at::Tensor y = x.to(at::kFloat) / scale;
+      at::Tensor q = ct == at::kChar ? at::clamp(at::round(y), -128, 127).to(at::kChar) : at::clamp(y, -448.f, 448.f).to(ct);
+      if (into.defined() && into.sizes() == q.sizes()) {
+        into.copy_(q);
+        return into;
+      }
+      return q;
+    };
+    if (ctx.OutputCount() > 1) ctx.SetOutput(1, quantise(r.present_key, k_scale, q_past_k));
+    if (ctx.OutputCount() > 2) ctx.SetOutput(2, quantise(r.present_value, v_scale, q_past_v));
+    return;
+  }
   if (ctx.OutputCount() > 1) ctx.SetOutput(1, r.present_key);
   if (ctx.OutputCount() > 2) ctx.SetOutput(2, r.present_value);
 }

@@ -209,3 +209,43 @@ def test_legacy_image_ops():
     np.testing.assert_allclose(p, 1.5 * np.log1p(np.exp(0.5 * x)), rtol=1e-5, atol=1e-6)
     (d,) = run_node("DynamicSlice", {"x": x, "s": np.array([1, 2], np.int64), "e": np.array([4, 6], np.int64), "ax": np.array([2, 3], np.int64)})
     np.testing.assert_array_equal(d, x[:, :, 1:4, 2:6])
+
+
+def _gqa(inputs, n_outputs=3, **attrs):
+    return run_node("GroupQueryAttention", inputs, n_outputs=n_outputs, domain=MS, num_heads=4, kv_num_heads=2, **attrs)
+
+
+def test_gqa_quantised_kv_cache_and_qk_norm():
+    """int8 KV cache with per-tensor scales: prompt then one decode step track the float-cache run within the
+    quantisation error, and the cache comes back as int8 in the shared buffer; q / k norm weights equal to an explicit
+    per-head RMS norm applied before the operator."""
+    B, S, N, Nk, H, cap = 2, 5, 4, 2, 8, 16
+    qkv = rng.standard_normal((B, S, (N + 2 * Nk) * H)).astype(np.float32)
+    step = rng.standard_normal((B, 1, (N + 2 * Nk) * H)).astype(np.float32)
+    sl0, tot0 = np.full(B, S - 1, np.int32), np.array(S, np.int32)
+    sl1, tot1 = np.full(B, S, np.int32), np.array(S + 1, np.int32)
+    zeros_f = np.zeros((B, Nk, cap, H), np.float32)
+    base = {"q": qkv, "k": None, "v": None, "pk": zeros_f, "pv": zeros_f.copy(), "sl": sl0, "tot": tot0}
+    y0, pk, pv = _gqa(base)
+    y1, _, _ = _gqa({**base, "q": step, "pk": pk, "pv": pv, "sl": sl1, "tot": tot1})
+    ks, vs = np.array([0.03], np.float32), np.array([0.03], np.float32)
+    zeros_q = np.zeros((B, Nk, cap, H), np.int8)
+    qbase = {"q": qkv, "k": None, "v": None, "pk": zeros_q, "pv": zeros_q.copy(), "sl": sl0, "tot": tot0, "cos": None, "sin": None,
+             "pos": None, "bias": None, "sink": None, "ks": ks, "vs": vs}
+    q0, qk, qv = _gqa(qbase, k_quant_type="PER_TENSOR", v_quant_type="PER_TENSOR", kv_cache_bit_width=8)
+    assert qk.dtype == np.int8 and qk.shape == (B, Nk, cap, H)
+    np.testing.assert_allclose(qk[:, :, :S].astype(np.float32) * 0.03, pk[:, :, :S], atol=0.016)
+    np.testing.assert_allclose(q0, y0, atol=1e-5)     # the prompt attends to its own unquantised keys
+    q1, qk1, _ = _gqa({**qbase, "q": step, "pk": qk, "pv": qv, "sl": sl1, "tot": tot1},
+                      k_quant_type="PER_TENSOR", v_quant_type="PER_TENSOR", kv_cache_bit_width=8)
+    assert np.abs(q1 - y1).max() < 0.05 and qk1.dtype == np.int8
+    # q / k norm
+    wq, wk = rng.standard_normal(H).astype(np.float32), rng.standard_normal(H).astype(np.float32)
+    def norm(x, heads, w):
+        x = x.reshape(B, S, heads, H)
+        return (x / np.sqrt((x ** 2).mean(-1, keepdims=True) + 1e-6) * w).reshape(B, S, heads * H)
+    qn = np.concatenate([norm(qkv[..., :N * H], N, wq), norm(qkv[..., N * H:(N + Nk) * H], Nk, wk), qkv[..., (N + Nk) * H:]], -1)
+    want, _, _ = _gqa({**base, "q": qn.astype(np.float32)})
+    got, _, _ = _gqa({**base, "cos": None, "sin": None, "pos": None, "bias": None, "sink": None, "ks": None, "vs": None, "qn": wq, "kn": wk},
+                     qk_norm_epsilon=1e-6)
+    np.testing.assert_allclose(got, want, rtol=1e-4, atol=1e-5)
