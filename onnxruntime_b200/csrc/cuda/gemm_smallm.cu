@@ -68,7 +68,7 @@ constexpr unsigned int kPeerSpinLimit = 1u << 22;
 
 __device__ __forceinline__ float act_apply(int act, float v) {
   switch (act) {
-    case ORTB200_ACT_GELU: return 0.5f * v * (1.0f + erff(v * 0.70710678118654752f));
+    case ORTB200_ACT_GELU: return gelu_erf_fast(v);
     case ORTB200_ACT_FASTGELU: return 0.5f * v * (1.0f + tanhf(0.7978845608028654f * v * (1.0f + 0.044715f * v * v)));
     case ORTB200_ACT_RELU: return fmaxf(v, 0.0f);
     case ORTB200_ACT_SILU: return v / (1.0f + __expf(-v));
