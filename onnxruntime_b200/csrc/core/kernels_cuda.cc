@@ -244,6 +244,8 @@ class GemmKernel final : public OpKernel {
       w_nk_ = (w_nk_.to(at::kFloat) * gamma->to(at::kFloat).reshape({1, -1})).to(w_nk_.scalar_type()).contiguous();
       unit_gamma_ = at::ones({w_nk_.size(1)}, w_nk_.options());
     }
+    if (info.session != nullptr && w_nk_.defined() && w_nk_.is_cuda())
+      info.session->RegisterWeightHint(info.node.name, w_nk_.data_ptr(), static_cast<int64_t>(w_nk_.numel()) * w_nk_.element_size());
   }
   std::vector<int> PrepackedInputs() const override { return {1}; }
   void Compute(Ctx& ctx) const override {

@@ -140,6 +140,13 @@ class InferenceSession {
   // launches issued by the most recent execution of the step list (eager run or graph capture)
   int64_t LastRunLaunchCount() const { return last_run_launches_; }
   void AddLaunches(int64_t n) { launch_count_ += n; }
+  // Device memory a kernel streams on every run (its pre-packed weights), by node name.  A kernel that leaves the
+  // memory system idle (decode attention) asks the L2 for the next node's weights while it runs.
+  void RegisterWeightHint(const std::string& node_name, const void* ptr, int64_t bytes) { weight_hints_[node_name] = {ptr, bytes}; }
+  std::pair<const void*, int64_t> FindWeightHint(const std::string& node_name) const {
+    auto it = weight_hints_.find(node_name);
+    return it == weight_hints_.end() ? std::pair<const void*, int64_t>{nullptr, 0} : it->second;
+  }
   // device scratch shared by the GPU kernels (split-K partials, counters), zero-initialised
   at::Tensor& GemmWorkspace(int64_t nbytes);
   at::Tensor& AttnWorkspace(int64_t nbytes);
@@ -177,6 +184,7 @@ class InferenceSession {
   bool graph_capturable_ = false;
 
   std::map<int64_t, std::unique_ptr<CapturedGraph>> cuda_graphs_;
+  std::map<std::string, std::pair<const void*, int64_t>> weight_hints_;
   Profiler profiler_;
   logging::Logger logger_;
   int64_t profiling_start_ns_ = 0;

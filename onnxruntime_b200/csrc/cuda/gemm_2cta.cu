@@ -112,91 +112,6 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster_addr) {
 }
 
 
-template <int ACT>
-__device__ __forceinline__ float act_const(float v) {
-  if (ACT == ORTB200_ACT_GELU) return gelu_erf_fast(v);
-  if (ACT == ORTB200_ACT_FASTGELU) return 0.5f * v * (1.0f + tanhf(0.7978845608028654f * v * (1.0f + 0.044715f * v * v)));
-  if (ACT == ORTB200_ACT_RELU) return fmaxf(v, 0.0f);
-  if (ACT == ORTB200_ACT_SILU) return v / (1.0f + __expf(-v));
-  if (ACT == ORTB200_ACT_QUICKGELU) return v / (1.0f + __expf(-1.702f * v));
-  return v;
-}
-
-// One 128-row pass of the staged 16-bit tile -> global memory: 16-byte rows chunks, activation, residual.
-// stg[row][128] holds rows m_base .. m_base + 127 (tokens) by 128 output features starting at nrow0.
-template <bool BF16, int ACT>
-__device__ __forceinline__ void store_pass(const Gemm2Params& p, const uint16_t* stg, int et, int m_base, int m_end, int nrow0,
-                                           bool vec_ok) {
-  const bool has_res = p.residual != nullptr;
-  for (int idx = et; idx < 128 * 16; idx += kStoreThreads) {
-    const int row = idx >> 4, ch = idx & 15;
-    const int m = m_base + row;
-    const int nn = nrow0 + ch * 8;
-    if (m >= m_end || nn >= p.N) continue;
-    const uint4 val = *reinterpret_cast<const uint4*>(stg + row * kBM + ch * 8);
-    const long long o = static_cast<long long>(m) * p.ldo + nn;
-    if (vec_ok && nn + 8 <= p.N) {
-      uint4 res = val;
-      if (has_res || ACT != ORTB200_ACT_NONE) {
-        uint4 rr = make_uint4(0u, 0u, 0u, 0u);
-        if (has_res)
-          rr = __ldg(reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(p.residual) + static_cast<long long>(m) * p.ldr + nn));
-        const uint32_t a4[4] = {val.x, val.y, val.z, val.w};
-        const uint32_t b4[4] = {rr.x, rr.y, rr.z, rr.w};
-        uint32_t o4[4];
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          float lo, hi, rlo, rhi;
-          if (BF16) {
-            lo = __uint_as_float(a4[e] << 16); hi = __uint_as_float(a4[e] & 0xffff0000u);
-            rlo = __uint_as_float(b4[e] << 16); rhi = __uint_as_float(b4[e] & 0xffff0000u);
-          } else {
-            const float2 fa = __half22float2(*reinterpret_cast<const __half2*>(&a4[e]));
-            const float2 fb = __half22float2(*reinterpret_cast<const __half2*>(&b4[e]));
-            lo = fa.x; hi = fa.y; rlo = fb.x; rhi = fb.y;
-          }
-          lo = act_const<ACT>(lo) + rlo;
-          hi = act_const<ACT>(hi) + rhi;
-          if (BF16) {
-            const __nv_bfloat162 h2 = __floats2bfloat162_rn(lo, hi);
-            o4[e] = *reinterpret_cast<const uint32_t*>(&h2);
-          } else {
-            const __half2 h2 = __floats2half2_rn(lo, hi);
-            o4[e] = *reinterpret_cast<const uint32_t*>(&h2);
-          }
-        }
-        res = make_uint4(o4[0], o4[1], o4[2], o4[3]);
-      }
-      *reinterpret_cast<uint4*>(static_cast<uint16_t*>(p.out) + o) = res;
-    } else {
-      const uint16_t* sv = stg + row * kBM + ch * 8;
-      for (int e = 0; e < 8 && nn + e < p.N; ++e) {
-        float y = BF16 ? __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(sv + e)) : __half2float(*reinterpret_cast<const __half*>(sv + e));
-        y = act_const<ACT>(y);
-        if (has_res) {
-          const long long ri = static_cast<long long>(m) * p.ldr + nn + e;
-          y += BF16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.residual)[ri]) : __half2float(reinterpret_cast<const __half*>(p.residual)[ri]);
-        }
-        if (BF16) reinterpret_cast<__nv_bfloat16*>(p.out)[o + e] = __float2bfloat16_rn(y);
-        else reinterpret_cast<__half*>(p.out)[o + e] = __float2half_rn(y);
-      }
-    }
-  }
-}
-
-template <bool BF16>
-__device__ __noinline__ void store_pass_act(const Gemm2Params& p, const uint16_t* stg, int et, int m_base, int m_end, int nrow0,
-                                            bool vec_ok) {
-  switch (p.act) {
-    case ORTB200_ACT_GELU: store_pass<BF16, ORTB200_ACT_GELU>(p, stg, et, m_base, m_end, nrow0, vec_ok); break;
-    case ORTB200_ACT_FASTGELU: store_pass<BF16, ORTB200_ACT_FASTGELU>(p, stg, et, m_base, m_end, nrow0, vec_ok); break;
-    case ORTB200_ACT_RELU: store_pass<BF16, ORTB200_ACT_RELU>(p, stg, et, m_base, m_end, nrow0, vec_ok); break;
-    case ORTB200_ACT_SILU: store_pass<BF16, ORTB200_ACT_SILU>(p, stg, et, m_base, m_end, nrow0, vec_ok); break;
-    case ORTB200_ACT_QUICKGELU: store_pass<BF16, ORTB200_ACT_QUICKGELU>(p, stg, et, m_base, m_end, nrow0, vec_ok); break;
-    default: store_pass<BF16, ORTB200_ACT_NONE>(p, stg, et, m_base, m_end, nrow0, vec_ok); break;
-  }
-}
-
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x, const Gemm2Params p) {
   using S = Smem2;
@@ -315,6 +230,7 @@ gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
     const bool bf16 = p.dtype == ORTB200_BF16;
     const bool vec_ok = (p.ldo % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0) &&
                         (p.residual == nullptr || ((p.ldr % 8 == 0) && (reinterpret_cast<uintptr_t>(p.residual) & 15) == 0));
+    const StoreArgs sa{p.out, p.residual, p.ldo, p.ldr, p.N};
     for (int t = pair; t < tiles; t += num_pairs) {
       const int nrow0 = (t / tiles_m) * (2 * kBM) + static_cast<int>(rank) * kBM;
       int m0 = (t % tiles_m) * kBN, m_end = p.M;
@@ -327,12 +243,12 @@ gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
       for (int pc = 0; pc < kBN; pc += 128) {
         asm volatile("bar.sync 1, 256;" ::: "memory");   // the pass is staged
         if (p.act == ORTB200_ACT_NONE) {
-          if (bf16) store_pass<true, ORTB200_ACT_NONE>(p, stg, et, m0 + pc, m_end, nrow0, vec_ok);
-          else store_pass<false, ORTB200_ACT_NONE>(p, stg, et, m0 + pc, m_end, nrow0, vec_ok);
+          if (bf16) store_pass<true, ORTB200_ACT_NONE, kStoreThreads>(sa, stg, 128, et, m0 + pc, m_end, nrow0, vec_ok);
+          else store_pass<false, ORTB200_ACT_NONE, kStoreThreads>(sa, stg, 128, et, m0 + pc, m_end, nrow0, vec_ok);
         } else if (bf16) {
-          store_pass_act<true>(p, stg, et, m0 + pc, m_end, nrow0, vec_ok);
+          store_pass_act<true, kStoreThreads>(sa, p.act, stg, 128, et, m0 + pc, m_end, nrow0, vec_ok);
         } else {
-          store_pass_act<false>(p, stg, et, m0 + pc, m_end, nrow0, vec_ok);
+          store_pass_act<false, kStoreThreads>(sa, p.act, stg, 128, et, m0 + pc, m_end, nrow0, vec_ok);
         }
         asm volatile("bar.sync 1, 256;" ::: "memory");   // the staging tile may be overwritten
       }
@@ -346,6 +262,7 @@ gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
     const bool bf16 = p.dtype == ORTB200_BF16;
     const bool vec_ok = (p.ldo % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0) &&
                         (p.residual == nullptr || ((p.ldr % 8 == 0) && (reinterpret_cast<uintptr_t>(p.residual) & 15) == 0));
+    const StoreArgs sa{p.out, p.residual, p.ldo, p.ldr, p.N};
     const uint32_t empty_remote0 = map_to_rank(smem_u32(&tmem_empty_bar[0]), 0);
     const uint32_t empty_remote1 = map_to_rank(smem_u32(&tmem_empty_bar[1]), 0);
     int seg = 0;
@@ -402,12 +319,12 @@ gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         // instruction count: 11 M -> 27 M warp instructions for a plain ReLU on 8192 x 4096 x 1024)
         // (the plain path stays inline: an out-of-line call cost it a quarter of its speed)
         if (p.act == ORTB200_ACT_NONE) {
-          if (bf16) store_pass<true, ORTB200_ACT_NONE>(p, stg, et, m0 + pc, m_end, nrow0, vec_ok);
-          else store_pass<false, ORTB200_ACT_NONE>(p, stg, et, m0 + pc, m_end, nrow0, vec_ok);
+          if (bf16) store_pass<true, ORTB200_ACT_NONE, kStoreThreads>(sa, stg, 128, et, m0 + pc, m_end, nrow0, vec_ok);
+          else store_pass<false, ORTB200_ACT_NONE, kStoreThreads>(sa, stg, 128, et, m0 + pc, m_end, nrow0, vec_ok);
         } else if (bf16) {
-          store_pass_act<true>(p, stg, et, m0 + pc, m_end, nrow0, vec_ok);
+          store_pass_act<true, kStoreThreads>(sa, p.act, stg, 128, et, m0 + pc, m_end, nrow0, vec_ok);
         } else {
-          store_pass_act<false>(p, stg, et, m0 + pc, m_end, nrow0, vec_ok);
+          store_pass_act<false, kStoreThreads>(sa, p.act, stg, 128, et, m0 + pc, m_end, nrow0, vec_ok);
         }
         asm volatile("bar.sync 1, 256;" ::: "memory");
       }

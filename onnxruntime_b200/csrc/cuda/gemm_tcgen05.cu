@@ -405,63 +405,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
               mbar_arrive(&tmem_empty_bar[buf]);
             }
             asm volatile("bar.sync 1, 128;" ::: "memory");
-            for (int idx = et; idx < PASS * 16; idx += 128) {
-              const int row = idx >> 4, ch = idx & 15;
-              const int m = m0 + pc + row;
-              const int nn = nrow0 + ch * 8;
-              if (m >= m_end || nn >= p.N) continue;
-              const uint4 val = *reinterpret_cast<const uint4*>(stg + row * kBM + ch * 8);
-              const long long o = static_cast<long long>(m) * p.ldo + nn;
-              const bool post_act = !DUAL && p.act != ORTB200_ACT_NONE;
-              if (vec_ok && nn + 8 <= p.N) {
-                uint4 res = val;
-                if (p.residual != nullptr || post_act) {
-                  uint4 rr = make_uint4(0u, 0u, 0u, 0u);
-                  if (p.residual != nullptr)
-                    rr = __ldg(reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(p.residual) + static_cast<long long>(m) * p.ldr + nn));
-                  const uint32_t a4[4] = {val.x, val.y, val.z, val.w};
-                  const uint32_t b4[4] = {rr.x, rr.y, rr.z, rr.w};
-                  uint32_t o4[4];
-#pragma unroll
-                  for (int e = 0; e < 4; ++e) {
-                    float lo, hi, rlo, rhi;
-                    if (bf16) {
-                      lo = __uint_as_float(a4[e] << 16); hi = __uint_as_float(a4[e] & 0xffff0000u);
-                      rlo = __uint_as_float(b4[e] << 16); rhi = __uint_as_float(b4[e] & 0xffff0000u);
-                    } else {
-                      const float2 fa = __half22float2(*reinterpret_cast<const __half2*>(&a4[e]));
-                      const float2 fb = __half22float2(*reinterpret_cast<const __half2*>(&b4[e]));
-                      lo = fa.x; hi = fa.y; rlo = fb.x; rhi = fb.y;
-                    }
-                    if (post_act) {
-                      lo = apply_act(p.act, lo);
-                      hi = apply_act(p.act, hi);
-                    }
-                    lo += rlo;
-                    hi += rhi;
-                    if (bf16) {
-                      const __nv_bfloat162 h2 = __floats2bfloat162_rn(lo, hi);
-                      o4[e] = *reinterpret_cast<const uint32_t*>(&h2);
-                    } else {
-                      const __half2 h2 = __floats2half2_rn(lo, hi);
-                      o4[e] = *reinterpret_cast<const uint32_t*>(&h2);
-                    }
-                  }
-                  res = make_uint4(o4[0], o4[1], o4[2], o4[3]);
-                }
-                *reinterpret_cast<uint4*>(static_cast<uint16_t*>(p.out) + o) = res;
+            {
+              // activation and type are compile-time constants inside the store loop (shared with the CTA-pair kernel)
+              const StoreArgs sa{p.out, p.residual, p.ldo, p.ldr, p.N};
+              const int act = DUAL ? ORTB200_ACT_NONE : p.act;
+              if (act == ORTB200_ACT_NONE) {
+                if (bf16) store_pass<true, ORTB200_ACT_NONE, 128>(sa, stg, PASS, et, m0 + pc, m_end, nrow0, vec_ok);
+                else store_pass<false, ORTB200_ACT_NONE, 128>(sa, stg, PASS, et, m0 + pc, m_end, nrow0, vec_ok);
+              } else if (bf16) {
+                store_pass_act<true, 128>(sa, act, stg, PASS, et, m0 + pc, m_end, nrow0, vec_ok);
               } else {
-                const uint16_t* sv = stg + row * kBM + ch * 8;
-                for (int e = 0; e < 8 && nn + e < p.N; ++e) {
-                  float y = bf16 ? __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(sv + e)) : __half2float(*reinterpret_cast<const __half*>(sv + e));
-                  if (post_act) y = apply_act(p.act, y);
-                  if (p.residual != nullptr) {
-                    const long long ri = static_cast<long long>(m) * p.ldr + nn + e;
-                    y += bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.residual)[ri]) : __half2float(reinterpret_cast<const __half*>(p.residual)[ri]);
-                  }
-                  if (bf16) reinterpret_cast<__nv_bfloat16*>(p.out)[o + e] = __float2bfloat16_rn(y);
-                  else reinterpret_cast<__half*>(p.out)[o + e] = __float2half_rn(y);
-                }
+                store_pass_act<false, 128>(sa, act, stg, PASS, et, m0 + pc, m_end, nrow0, vec_ok);
               }
             }
             asm volatile("bar.sync 1, 128;" ::: "memory");  // staging is free again

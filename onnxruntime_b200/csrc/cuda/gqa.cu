@@ -541,6 +541,7 @@ static int launch_decode(const ortb200_gqa_decode_args* a, cudaStream_t stream) 
   p.softcap = a->softcap;
   p.block_table = a->block_table; p.block_size = a->block_size; p.max_blocks = a->max_blocks;
   p.qkv = a->qkv; p.cos_cache = a->cos_cache; p.sin_cache = a->sin_cache;
+  p.prefetch = nullptr; p.prefetch_bytes = 0; p.prefetch_per_cta = 0;
   p.do_rotary = a->do_rotary; p.interleaved = a->rotary_interleaved;
   dim3 grid(splits, a->Nk * gparts, a->B);
   if (a->block_table) {

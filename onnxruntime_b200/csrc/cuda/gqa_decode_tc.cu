@@ -131,6 +131,17 @@ gqa_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   const int k_end = owns_new ? total - 1 : min(total, k_begin + chunk);
   const int n_tiles = k_end > k_begin ? (k_end - k_begin + kTile - 1) / kTile : 0;
 
+  if (warp == 4 && p.prefetch != nullptr) {
+    // This grid moves a few tens of MB and leaves most of the memory bandwidth idle: ask the L2 for this CTA's slice
+    // of the next kernel's weights now, so that kernel finds them on chip.
+    const long long cta = (static_cast<long long>(blockIdx.z) * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
+    const long long lo = cta * p.prefetch_per_cta;
+    const long long hi = lo + p.prefetch_per_cta < p.prefetch_bytes ? lo + p.prefetch_per_cta : p.prefetch_bytes;
+    for (long long off = lo + static_cast<long long>(lane) * 16384; off < hi; off += 32 * 16384) {
+      const long long nbytes = hi - off < 16384 ? hi - off : 16384;
+      bulk_prefetch_l2(p.prefetch + off, static_cast<uint32_t>(nbytes));
+    }
+  }
   if (warp == 4) {
     // ------------------------------------------------------------ TMA producer + MMA issuer (lane 0 issues; with a
     // paged cache lane i fetches piece i of a tile)
@@ -556,6 +567,14 @@ int launch_gqa_decode_tc(const ortb200_gqa_decode_args* a, cudaStream_t stream) 
   p.qkv = a->qkv; p.cos_cache = a->cos_cache; p.sin_cache = a->sin_cache;
   p.do_rotary = a->do_rotary; p.interleaved = a->rotary_interleaved;
   dim3 grid(splits, a->Nk, a->B);
+  p.prefetch = nullptr; p.prefetch_bytes = 0; p.prefetch_per_cta = 0;
+  if (a->prefetch != nullptr && a->prefetch_bytes >= 16 && (reinterpret_cast<uintptr_t>(a->prefetch) & 15) == 0) {
+    const long long bytes = (a->prefetch_bytes < (48LL << 20) ? a->prefetch_bytes : (48LL << 20)) & ~15LL;
+    const long long ctas = static_cast<long long>(grid.x) * grid.y * grid.z;
+    p.prefetch = static_cast<const unsigned char*>(a->prefetch);
+    p.prefetch_bytes = bytes;
+    p.prefetch_per_cta = static_cast<int>(((bytes + ctas - 1) / ctas + 15) & ~15LL);
+  }
   const bool pdl = a->use_pdl != 0;
   if (a->dtype == ORTB200_BF16) {
     return a->block_table ? launch_tc_g<__nv_bfloat16, true>(group, tq, tk, tv, p, piece_rows, grid, stream, pdl)

@@ -29,6 +29,10 @@ struct DecodeParams {
   const void* cos_cache;
   const void* sin_cache;
   int do_rotary, interleaved;
+  // L2 prefetch of the next kernel's weights: CTA i asks for bytes [i, i + 1) * prefetch_per_cta of the range
+  const unsigned char* prefetch;
+  long long prefetch_bytes;
+  int prefetch_per_cta;
 };
 
 // Running maxima start at a large negative finite value so that exp(m_old - m_new) never sees inf - inf.

@@ -229,6 +229,10 @@ typedef struct {
   int rotary_interleaved;
   int num_blocks;         // paged cache: blocks in the pool (needed by the tensor-core kernel; 0 = unknown)
   int algo;               // 0 = pick, 1 = CUDA-core split-KV kernel, 2 = tcgen05 kernel (error if unsupported)
+  // Optional hint (tcgen05 kernel): device memory the next kernel will stream (the output projection's weights).  The
+  // step leaves most of the memory bandwidth idle, so the CTAs ask the L2 for it while they work (at most 48 MiB).
+  const void* prefetch;
+  int64_t prefetch_bytes;
 } ortb200_gqa_decode_args;
 int ortb200_gqa_decode(const ortb200_gqa_decode_args* args, ortb200_stream_t stream);
 int64_t ortb200_gqa_decode_workspace_bytes(int B, int N, int H);

@@ -137,6 +137,11 @@ __device__ __forceinline__ void bulk_load(void* smem_dst, const void* gmem_src, 
       : "memory");
 }
 
+// Ask the L2 to fetch [gmem, gmem + bytes) (16-byte aligned address, size a multiple of 16); nothing is waited for.
+__device__ __forceinline__ void bulk_prefetch_l2(const void* gmem, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(gmem), "r"(bytes) : "memory");
+}
+
 __device__ __forceinline__ void tma_prefetch_desc(const void* tmap) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
 }

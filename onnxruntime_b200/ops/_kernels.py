@@ -175,14 +175,14 @@ class GqaDecodeArgs(ctypes.Structure):
                 ("use_pdl", ctypes.c_int), ("status", ctypes.c_void_p), ("block_table", ctypes.c_void_p),
                 ("block_size", ctypes.c_int), ("max_blocks", ctypes.c_int), ("qkv", ctypes.c_void_p), ("cos_cache", ctypes.c_void_p),
                 ("sin_cache", ctypes.c_void_p), ("do_rotary", ctypes.c_int), ("rotary_interleaved", ctypes.c_int),
-                ("num_blocks", ctypes.c_int), ("algo", ctypes.c_int)]
+                ("num_blocks", ctypes.c_int), ("algo", ctypes.c_int), ("prefetch", ctypes.c_void_p), ("prefetch_bytes", ctypes.c_int64)]
 
 
 _ATTN_WS = {}
 
 
 def gqa_decode(q, k_cache, v_cache, seqlens_k, splits=0, window=-1, scale=0.0, softcap=0.0, head_sink=None, block_table=None,
-               qkv=None, num_heads=0, cos=None, sin=None, interleaved=False, algo=0):
+               qkv=None, num_heads=0, cos=None, sin=None, interleaved=False, algo=0, prefetch=None):
     """Dense cache [B,Nk,Smax,H]; or, with block_table [B,max_blocks] int32, a paged cache [num_blocks,block_size,Nk,H].
     With ``qkv`` (packed [B,(N+2Nk)H], ``num_heads`` = N) the kernel also rotates q / k and appends k / v itself.
     ``algo``: 0 = pick, 1 = CUDA-core split-KV kernel, 2 = tcgen05 kernel (head size 128, 16-bit types)."""
@@ -210,7 +210,8 @@ def gqa_decode(q, k_cache, v_cache, seqlens_k, splits=0, window=-1, scale=0.0, s
     a = GqaDecodeArgs(None if qkv is not None else _ptr(q.contiguous()), _ptr(k_cache), _ptr(v_cache), _ptr(seqlens_k), _ptr(head_sink), _ptr(out), _ptr(ws),
                       ws.numel(), B, N, Nk, H, Smax, splits, window, scale, softcap, dtype_code(q.dtype), 0, None,
                       _ptr(block_table), block_size, max_blocks, _ptr(qkv), _ptr(cos), _ptr(sin), 0 if cos is None else 1,
-                      1 if interleaved else 0, num_blocks, algo)
+                      1 if interleaved else 0, num_blocks, algo, _ptr(prefetch),
+                      prefetch.numel() * prefetch.element_size() if prefetch is not None else 0)
     _check(lib().ortb200_gqa_decode(ctypes.byref(a), ctypes.c_void_p(stream_ptr())), "ortb200_gqa_decode")
     return out
 
