@@ -395,9 +395,14 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
     const uint32_t part_addr = smem_u32(part);
     const bool fused_ar = p.world > 1;
     unsigned int epoch = 0;
+    unsigned int spin_limit = kPeerSpinLimit;
     long long stage_base = 0;  // element offset of staging[epoch & 1][0][0]
     if (fused_ar) {
       epoch = *reinterpret_cast<volatile unsigned int*>(p.epoch) + 1;  // stable: the previous fused launch has completed
+      // word 2 of the workspace header overrides the polling budget (0 = default); failure-detection tests set a small
+      // one so that a peer that never answers costs milliseconds
+      const unsigned int lim = reinterpret_cast<volatile unsigned int*>(p.epoch)[2];
+      if (lim != 0) spin_limit = lim;
       stage_base = static_cast<long long>(epoch & 1) * p.world * p.slot_elems;
     }
 #pragma unroll 1
@@ -491,7 +496,7 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
 #pragma unroll
             for (int sr = 0; sr < 8; ++sr) all = all && (static_cast<unsigned int>(w[cb][sr] >> 32) == epoch);
           if (all) break;
-          if (++spins > kPeerSpinLimit) {
+          if (++spins > spin_limit) {
             timed_out = true;
             break;
           }

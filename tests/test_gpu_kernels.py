@@ -349,3 +349,31 @@ def test_gqa_decode_tensor_core_kernel_paged_fused_append(K, interleaved):
     got = K.gqa_decode(None, k2, v2, lens - 1, block_table=table, qkv=qkv, num_heads=N, cos=cos, sin=sin, interleaved=interleaved, algo=2)
     assert _rel(got, want) < 1e-2
     assert torch.equal(k1, k2) and torch.equal(v1, v2)
+
+
+def test_fused_allreduce_gives_up_on_a_silent_peer(K):
+    """Failure detection without a fault: rank 0 of a two-rank fused GEMM + all-reduce whose peer never writes (its
+    'workspace' is a second local buffer that nothing fills).  The kernel's polling budget (header word 2, set small
+    here) runs out, the status word reports the peer timeout, the kernel returns normally and the context stays
+    usable - the next GEMM is correct."""
+    torch.manual_seed(0)
+    nbytes = 4 << 20
+    ws = torch.zeros(nbytes, dtype=torch.uint8, device="cuda")
+    silent_peer = torch.zeros(nbytes, dtype=torch.uint8, device="cuda")
+    ws.view(torch.int32)[2] = 2000            # polling rounds before giving up (default: 4 M)
+    x = torch.randn(8, 256, device="cuda").bfloat16()
+    w = (torch.randn(128, 256, device="cuda") * 0.1).bfloat16()
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    t0 = torch.cuda.Event(enable_timing=True)
+    t1 = torch.cuda.Event(enable_timing=True)
+    t0.record()
+    K.gemm(x, w, peers=[ws.data_ptr(), silent_peer.data_ptr()], rank=0, symm_bytes=nbytes, status=status)
+    t1.record()
+    torch.cuda.synchronize()
+    assert status.item() == 4                  # kStatusTimeoutPeer
+    assert t0.elapsed_time(t1) < 1000.0        # milliseconds: bounded, nowhere near a hang
+    status.zero_()
+    y = K.gemm(x, w, status=status)
+    torch.cuda.synchronize()
+    assert status.item() == 0
+    assert _rel(y, x.float() @ w.float().T) < 2e-2
