@@ -224,27 +224,27 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       // and soft-capping take the general path, which leaves final base-2 logits (scale 1).
       float fs = p.scale_log2;
       if (need_mask) {
-        if (p.key_mask == nullptr && p.window <= 0 && p.softcap <= 0.f) {
-          int hi = min(total, p.kv_len);
-          if (p.causal) hi = min(hi, pos + 1);
-          hi -= key0;
-#pragma unroll
-          for (int j = 0; j < kKT; ++j) sv[j] = j < hi ? sv[j] : -INFINITY;
-        } else {
+        if (p.softcap > 0.f) {   // soft-capped logits are final base-2 logits: the exponent then uses scale 1
           fs = 1.f;
+#pragma unroll
+          for (int j = 0; j < kKT; ++j) sv[j] = p.softcap * tanhf(sv[j] * p.scale / p.softcap) * 1.4426950408889634f;
+        }
+        // visible keys of this row within the tile: [lo, hi) and the tile's key-mask bits (one ballot per 32 keys)
+        int hi = min(total, p.kv_len);
+        if (p.causal) hi = min(hi, pos + 1);
+        hi -= key0;
+        const int lo = p.window > 0 ? pos - p.window + 1 - key0 : -kKT;
+        if (p.key_mask == nullptr) {
+#pragma unroll
+          for (int j = 0; j < kKT; ++j) sv[j] = (j < hi && j >= lo) ? sv[j] : -INFINITY;
+        } else {
 #pragma unroll
           for (int g4 = 0; g4 < kKT / 32; ++g4) {
             const unsigned keep = key_keep_bits(p.key_mask, b, p.kv_len, key0 + g4 * 32, lane);
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
-              const int key = key0 + g4 * 32 + j;
-              bool valid = key < total && key < p.kv_len && ((keep >> j) & 1u);
-              if (p.causal) valid = valid && key <= pos;
-              if (p.window > 0) valid = valid && key > pos - p.window;
-              float sc = sv[g4 * 32 + j];
-              if (p.softcap > 0.f) sc = p.softcap * tanhf(sc * p.scale / p.softcap) * 1.4426950408889634f;
-              else sc *= p.scale_log2;
-              sv[g4 * 32 + j] = valid ? sc : -INFINITY;
+              const int jj = g4 * 32 + j;
+              sv[jj] = (jj < hi && jj >= lo && ((keep >> j) & 1u)) ? sv[jj] : -INFINITY;
             }
           }
         }
