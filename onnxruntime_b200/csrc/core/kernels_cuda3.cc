@@ -735,6 +735,73 @@ void Reg(KernelRegistry& r, const std::string& domain, const std::string& op, st
 
 }  // namespace
 
+// EmbedLayerNormalization: gather of the three embedding rows + LayerNorm in one kernel.
+class EmbedLayerNormKernel final : public WithFallback {
+ public:
+  explicit EmbedLayerNormKernel(const OpKernelInfo& info) : WithFallback(info) { eps_ = info.node.attr_f("epsilon", 1e-12f); }
+  void Compute(Ctx& ctx) const override {
+    const at::Tensor& ids = ctx.RequiredInput(0);
+    const at::Tensor& word = ctx.RequiredInput(2);
+    const at::Tensor& pos = ctx.RequiredInput(3);
+    const int dt = word.scalar_type() == at::kFloat ? static_cast<int>(ORTB200_F32) : DtypeCode(word.scalar_type());
+    const bool has_seg = ctx.HasInput(1) && ctx.HasInput(4);
+    auto id_ok = [&](const at::Tensor& t) {
+      return t.is_cuda() && t.is_contiguous() && (t.scalar_type() == at::kInt || t.scalar_type() == at::kLong) &&
+             t.scalar_type() == ids.scalar_type();
+    };
+    const int64_t H = word.size(1);
+    bool ok = dt >= 0 && ids.dim() == 2 && id_ok(ids) && word.is_cuda() && word.is_contiguous() && pos.is_contiguous() &&
+              pos.scalar_type() == word.scalar_type() && (H * word.element_size()) % 16 == 0 && H * word.element_size() <= 8192 &&
+              ctx.RequiredInput(5).scalar_type() == word.scalar_type() && ctx.RequiredInput(6).scalar_type() == word.scalar_type();
+    if (ok && has_seg) ok = id_ok(ctx.Input(1)) && ctx.Input(4).is_contiguous() && ctx.Input(4).scalar_type() == word.scalar_type();
+    at::Tensor pos_ids;
+    if (ok && ctx.HasInput(8)) {
+      pos_ids = ctx.Input(8);
+      ok = id_ok(pos_ids) && pos_ids.dim() == 2 && pos_ids.size(1) == ids.size(1) && (pos_ids.size(0) == ids.size(0) || pos_ids.size(0) == 1);
+    }
+    if (!ok) {
+      Fallback(ctx);
+      return;
+    }
+    const int64_t B = ids.size(0), S = ids.size(1);
+    at::Tensor out = at::empty({B, S, H}, word.options());
+    at::Tensor sum_out;
+    const bool want_sum = ctx.OutputCount() > 2 && ctx.OutputNeeded(2);
+    if (want_sum) sum_out = at::empty({B, S, H}, word.options());
+    at::Tensor gamma = ctx.RequiredInput(5).contiguous(), beta = ctx.RequiredInput(6).contiguous();
+    ortb200_embed_layernorm_args a{};
+    a.input_ids = ids.data_ptr();
+    a.segment_ids = has_seg ? ctx.Input(1).data_ptr() : nullptr;
+    a.position_ids = pos_ids.defined() ? pos_ids.data_ptr() : nullptr;
+    a.word_emb = word.data_ptr();
+    a.pos_emb = pos.data_ptr();
+    a.segment_emb = has_seg ? ctx.Input(4).data_ptr() : nullptr;
+    a.gamma = gamma.data_ptr();
+    a.beta = beta.data_ptr();
+    a.out = out.data_ptr();
+    a.sum_out = want_sum ? sum_out.data_ptr() : nullptr;
+    a.B = static_cast<int>(B); a.S = static_cast<int>(S); a.hidden = static_cast<int>(H);
+    a.word_rows = static_cast<int>(word.size(0)); a.pos_rows = static_cast<int>(pos.size(0));
+    a.seg_rows = has_seg ? static_cast<int>(ctx.Input(4).size(0)) : 0;
+    a.id_bytes = ids.scalar_type() == at::kLong ? 8 : 4;
+    a.position_broadcast = pos_ids.defined() && pos_ids.size(0) == 1 && B > 1 ? 1 : 0;
+    a.epsilon = eps_;
+    a.dtype = dt;
+    a.status = ctx.session()->StatusWord().data_ptr<int>();
+    CheckLaunch(ortb200_embed_layernorm(&a, ctx.cuda_stream()), "ortb200_embed_layernorm");
+    ctx.session()->AddLaunches(1);
+    ctx.SetOutput(0, out);
+    if (ctx.OutputCount() > 1 && ctx.OutputNeeded(1)) {
+      if (ctx.HasInput(7)) ctx.SetOutput(1, ctx.Input(7).to(at::kInt).sum(-1).to(at::kInt));
+      else ctx.SetOutput(1, at::zeros({B}, at::TensorOptions().dtype(at::kInt).device(word.device())));
+    }
+    if (want_sum) ctx.SetOutput(2, sum_out);
+  }
+
+ private:
+  float eps_ = 1e-12f;
+};
+
 // MatMulBlockQuantizedFp8Weight: the fp8 weight with its per-block scales is expanded to the activation type once (at
 // the first call; constant weights only) and the product runs on the tcgen05 GEMM.  Weight-only block scaling cannot
 // ride the 8-bit tensor-core mode, whose accumulation would need one scale per output instead of one per K block.
@@ -786,6 +853,7 @@ void RegisterCudaKernels3(KernelRegistry& r) {
   Reg<MoeKernel>(r, MS, "QMoE");
   Reg<GemmFloat8Kernel>(r, MS, "GemmFloat8");
   Reg<BlockFp8WeightMatMulKernel>(r, MS, "MatMulBlockQuantizedFp8Weight");
+  Reg<EmbedLayerNormKernel>(r, MS, "EmbedLayerNormalization");
   Reg<SymmCollectiveKernel>(r, MS, "AllReduce");
   Reg<SymmCollectiveKernel>(r, MS, "AllGather");
   Reg<SymmCollectiveKernel>(r, MS, "AllToAll");

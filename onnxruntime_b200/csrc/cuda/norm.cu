@@ -174,3 +174,123 @@ extern "C" int ortb200_norm(const ortb200_norm_args* a, ortb200_stream_t stream_
     default: return -4;
   }
 }
+
+// ---------------------------------------------------------------------------------------------------------------
+// EmbedLayerNormalization: out[b, s, :] = LayerNorm(word[ids[b, s]] + pos[position] + seg[segment_ids[b, s]]).
+// One block per token; the three rows are gathered with 16-byte loads, summed in registers, normalised with fp32
+// statistics and written once (reference: EmbedLayerNormKernel, contrib_ops/cuda/bert/embed_layer_norm_impl.cu:123).
+namespace ortb200 {
+
+template <typename T, int VPT>
+__global__ void __launch_bounds__(128) embed_layernorm_kernel(const ortb200_embed_layernorm_args a) {
+  constexpr int E = Vec16<T>::kElems;
+  __shared__ float red[32];
+  const int64_t tok = blockIdx.x;
+  const int H = a.hidden;
+  const int s = static_cast<int>(tok % a.S);
+  auto id_at = [&](const void* p, int64_t i) -> int64_t {
+    return a.id_bytes == 8 ? static_cast<const int64_t*>(p)[i] : static_cast<int64_t>(static_cast<const int32_t*>(p)[i]);
+  };
+  int64_t wid = id_at(a.input_ids, tok);
+  int64_t pid = a.position_ids ? id_at(a.position_ids, a.position_broadcast ? s : tok) : s;
+  int64_t sid = (a.segment_ids && a.segment_emb) ? id_at(a.segment_ids, tok) : -1;
+  // ids outside the tables read row 0 and flag the launch (the reference fails the run on such ids)
+  if (wid < 0 || wid >= a.word_rows || pid < 0 || pid >= a.pos_rows || (sid >= a.seg_rows)) {
+    if (a.status && threadIdx.x == 0) atomicExch(a.status, kStatusBadArgument);
+    wid = wid < 0 || wid >= a.word_rows ? 0 : wid;
+    pid = pid < 0 || pid >= a.pos_rows ? 0 : pid;
+    sid = sid >= a.seg_rows ? 0 : sid;
+  }
+  const T* wr = static_cast<const T*>(a.word_emb) + wid * H;
+  const T* pr = static_cast<const T*>(a.pos_emb) + pid * H;
+  const T* sr = sid >= 0 ? static_cast<const T*>(a.segment_emb) + sid * H : nullptr;
+  float vals[VPT][E];
+  float s1 = 0.f;
+#pragma unroll
+  for (int v = 0; v < VPT; ++v) {
+    const int col = (v * blockDim.x + threadIdx.x) * E;
+    if (col < H) {
+      Vec16<T> w, p, g;
+      w.raw = *reinterpret_cast<const uint4*>(wr + col);
+      p.raw = *reinterpret_cast<const uint4*>(pr + col);
+      if (sr) g.raw = *reinterpret_cast<const uint4*>(sr + col);
+#pragma unroll
+      for (int i = 0; i < E; ++i) {
+        // the sum is rounded to T first, as the reference does before normalising (and as embedding_sum stores it)
+        const float e = to_float<T>(from_float<T>(w.get(i) + p.get(i) + (sr ? g.get(i) : 0.f)));
+        vals[v][i] = e;
+        s1 += e;
+      }
+      if (a.sum_out) {
+        Vec16<T> o;
+#pragma unroll
+        for (int i = 0; i < E; ++i) o.set(i, vals[v][i]);
+        *reinterpret_cast<uint4*>(static_cast<T*>(a.sum_out) + tok * H + col) = o.raw;
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < E; ++i) vals[v][i] = 0.f;
+    }
+  }
+  const float mean = block_sum(s1, red) / static_cast<float>(H);
+  float s2 = 0.f;
+#pragma unroll
+  for (int v = 0; v < VPT; ++v) {
+    const int col = (v * blockDim.x + threadIdx.x) * E;
+    if (col < H) {
+#pragma unroll
+      for (int i = 0; i < E; ++i) {
+        const float c = vals[v][i] - mean;
+        s2 += c * c;
+      }
+    }
+  }
+  const float rstd = rsqrtf(block_sum(s2, red) / static_cast<float>(H) + a.epsilon);
+#pragma unroll
+  for (int v = 0; v < VPT; ++v) {
+    const int col = (v * blockDim.x + threadIdx.x) * E;
+    if (col < H) {
+      Vec16<T> g, bt, o;
+      g.raw = *reinterpret_cast<const uint4*>(static_cast<const T*>(a.gamma) + col);
+      bt.raw = *reinterpret_cast<const uint4*>(static_cast<const T*>(a.beta) + col);
+#pragma unroll
+      for (int i = 0; i < E; ++i) o.set(i, (vals[v][i] - mean) * rstd * g.get(i) + bt.get(i));
+      *reinterpret_cast<uint4*>(static_cast<T*>(a.out) + tok * H + col) = o.raw;
+    }
+  }
+}
+
+template <typename T>
+int launch_embed_ln(const ortb200_embed_layernorm_args* a, cudaStream_t stream) {
+  constexpr int E = Vec16<T>::kElems;
+  if (a->hidden % E != 0) return -3;
+  const int per_pass = 128 * E;
+  const int vpt = (a->hidden + per_pass - 1) / per_pass;
+  const dim3 grid(static_cast<unsigned>(a->B) * static_cast<unsigned>(a->S));
+  switch (vpt) {
+    case 1: embed_layernorm_kernel<T, 1><<<grid, 128, 0, stream>>>(*a); break;
+    case 2: embed_layernorm_kernel<T, 2><<<grid, 128, 0, stream>>>(*a); break;
+    case 3: case 4: embed_layernorm_kernel<T, 4><<<grid, 128, 0, stream>>>(*a); break;
+    default: return -2;   // hidden sizes above 4096 (fp16) take the generic path
+  }
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+}  // namespace ortb200
+
+extern "C" int ortb200_embed_layernorm(const ortb200_embed_layernorm_args* a, ortb200_stream_t stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (!a || !a->input_ids || !a->word_emb || !a->pos_emb || !a->gamma || !a->beta || !a->out) return -1;
+  if (a->B <= 0 || a->S <= 0 || a->hidden <= 0 || (a->id_bytes != 4 && a->id_bytes != 8)) return -1;
+  const uintptr_t align = reinterpret_cast<uintptr_t>(a->word_emb) | reinterpret_cast<uintptr_t>(a->pos_emb) |
+                          reinterpret_cast<uintptr_t>(a->segment_emb) | reinterpret_cast<uintptr_t>(a->gamma) |
+                          reinterpret_cast<uintptr_t>(a->beta) | reinterpret_cast<uintptr_t>(a->out) |
+                          reinterpret_cast<uintptr_t>(a->sum_out);
+  if (align & 15) return -3;
+  switch (a->dtype) {
+    case ORTB200_F16: return ortb200::launch_embed_ln<__half>(a, stream);
+    case ORTB200_BF16: return ortb200::launch_embed_ln<__nv_bfloat16>(a, stream);
+    case ORTB200_F32: return ortb200::launch_embed_ln<float>(a, stream);
+    default: return -4;
+  }
+}

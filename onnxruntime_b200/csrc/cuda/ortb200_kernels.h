@@ -143,6 +143,30 @@ typedef struct {
 } ortb200_norm_args;
 int ortb200_norm(const ortb200_norm_args* args, ortb200_stream_t stream);
 
+// EmbedLayerNormalization: out[b, s, :] = LayerNorm(word[ids] + pos[position] + seg[segment]) * gamma + beta.
+// ids are int32 or int64 (id_bytes 4 / 8); position_ids optional ([B, S], or [1, S] with position_broadcast = 1;
+// absent = 0 .. S - 1); segment ids / table optional.  hidden * element size must be a multiple of 16, at most 4096
+// elements of 16 bits (2048 of 32).  An id outside its table sets *status to the bad-argument code and reads row 0.
+typedef struct {
+  const void* input_ids;
+  const void* segment_ids;
+  const void* position_ids;
+  const void* word_emb;
+  const void* pos_emb;
+  const void* segment_emb;
+  const void* gamma;
+  const void* beta;
+  void* out;           // [B, S, hidden]
+  void* sum_out;       // optional [B, S, hidden]: the embedding sum before normalisation
+  int B, S, hidden;
+  int word_rows, pos_rows, seg_rows;
+  int id_bytes, position_broadcast;
+  float epsilon;
+  int dtype;
+  int* status;         // optional device int
+} ortb200_embed_layernorm_args;
+int ortb200_embed_layernorm(const ortb200_embed_layernorm_args* args, ortb200_stream_t stream);
+
 // ---------------------------------------------------------------------------
 // GroupQueryAttention, step 1: split packed QKV, apply rotary embedding to Q and K, append K/V to the cache.
 // Caches are [B, Nk, Smax, H].  Position of token s of batch b: position_ids[b, s] when given, else

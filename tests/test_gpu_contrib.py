@@ -350,3 +350,24 @@ def test_block_scaled_fp8_weight_matmul_on_gpu():
         ref = a.float() @ w.T + bias.float()
         y = torch.as_tensor(y).float().cpu() if not isinstance(y, torch.Tensor) else y.float().cpu()
         assert (y - ref).abs().max() / ref.abs().max() < 2e-2
+
+
+@pytest.mark.parametrize("dtype", [np.float16, np.float32])
+@pytest.mark.parametrize("with_segment", [True, False])
+def test_embed_layer_normalization_kernel(dtype, with_segment):
+    rng = np.random.default_rng(3)
+    B, S, H, V = 3, 7, 256, 50
+    ids = rng.integers(0, V, (B, S)).astype(np.int32)
+    seg = rng.integers(0, 2, (B, S)).astype(np.int32)
+    word = rng.standard_normal((V, H)).astype(dtype)
+    pos = rng.standard_normal((16, H)).astype(dtype)
+    segt = rng.standard_normal((2, H)).astype(dtype)
+    gamma, beta = rng.standard_normal(H).astype(dtype), rng.standard_normal(H).astype(dtype)
+    mask = (np.arange(S)[None, :] < np.array([7, 3, 5])[:, None]).astype(np.int32)
+    inputs = {"ids": ids, "seg": seg if with_segment else None, "word": word, "pos": pos, "segt": segt if with_segment else None,
+              "gamma": gamma, "beta": beta, "mask": mask}
+    rc, rg = _both("EmbedLayerNormalization", inputs, initializers=("word", "pos", "segt", "gamma", "beta"), n_outputs=3, epsilon=1e-5)
+    tol = 2e-2 if dtype == np.float16 else 1e-4
+    np.testing.assert_allclose(np.asarray(rg[0], dtype=np.float32), np.asarray(rc[0], dtype=np.float32), rtol=tol, atol=tol)
+    np.testing.assert_array_equal(rg[1], [7, 3, 5])
+    np.testing.assert_allclose(np.asarray(rg[2], dtype=np.float32), np.asarray(rc[2], dtype=np.float32), rtol=tol, atol=tol)
