@@ -85,12 +85,12 @@ class ClockSampler:
 
 
 def reference_arm(args):
-    """The reference arm must run the unmodified reference from baseline/_ref.  Its one allowed offline install
-    (`pip install --no-index --no-build-isolation --find-links /opt/wheelhouse --target baseline/_ref
-    /root/reference`, also tried from a writable copy with --no-deps) stops at metadata generation: setup.py
-    packages a finished cmake build (onnxruntime/capi with the compiled pybind module), and that native build
-    needs third-party sources that are download URLs (cmake/deps.txt).  DESIGN.md records the attempt."""
-    reason = ("reference not installable offline: pip install of /root/reference fails at metadata generation "
+    """The reference arm runs the unmodified reference from baseline/_ref when it is installed there.  The offline
+    install of the reference's source tree (pip, no index, no build isolation; also tried from a writable copy with
+    --no-deps) stops at metadata generation: its setup.py packages a finished cmake build (onnxruntime/capi with the
+    compiled pybind module), and that native build needs third-party sources that are download URLs
+    (cmake/deps.txt).  Without the package this arm reports itself unavailable."""
+    reason = ("reference not installable offline: pip install of the reference source tree fails at metadata generation "
               "(setup.py expects a cmake-built onnxruntime/capi; the native build needs downloaded third-party sources)")
     try:
         sys.path.insert(0, os.path.join(ROOT, "baseline", "_ref"))
