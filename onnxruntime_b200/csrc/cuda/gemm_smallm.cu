@@ -399,7 +399,7 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
     long long stage_base = 0;  // element offset of staging[epoch & 1][0][0]
     if (fused_ar) {
       epoch = *reinterpret_cast<volatile unsigned int*>(p.epoch) + 1;  // stable: the previous fused launch has completed
-      // word 2 of the workspace header overrides the polling budget (0 = default); failure-detection tests set a small
+      // word 2 of the workspace header overrides the polling limit (0 = default); failure-detection tests set a small
       // one so that a peer that never answers costs milliseconds
       const unsigned int lim = reinterpret_cast<volatile unsigned int*>(p.epoch)[2];
       if (lim != 0) spin_limit = lim;

@@ -63,7 +63,7 @@ typedef struct {
   // applies bias / residual as usual.  No fence, flag or barrier is involved: one NVLink store latency per GEMM.
   // Requires M <= 64, ldo == N, no dual (SwiGLU) epilogue.
   // peers[i] is rank i's workspace base as mapped into this process; the layout is
-  //   [0, 256 KiB)    epoch word (offset 0), done counter (offset 4), polling budget override (offset 8, 0 = default),
+  //   [0, 256 KiB)    epoch word (offset 0), done counter (offset 4), polling limit override (offset 8, 0 = default),
   //                   rest reserved
   //   [256 KiB, bytes / 2)  staging[2][world][slot] 64-bit words, slot = (bytes / 2 - 256 KiB) / (2 * world * 8) >= M * ldo
   //   [bytes / 2, bytes)    used by ortb200_symm_collective

@@ -353,7 +353,7 @@ def test_gqa_decode_tensor_core_kernel_paged_fused_append(K, interleaved):
 
 def test_fused_allreduce_gives_up_on_a_silent_peer(K):
     """Failure detection without a fault: rank 0 of a two-rank fused GEMM + all-reduce whose peer never writes (its
-    'workspace' is a second local buffer that nothing fills).  The kernel's polling budget (header word 2, set small
+    'workspace' is a second local buffer that nothing fills).  The kernel's polling limit (header word 2, set small
     here) runs out, the status word reports the peer timeout, the kernel returns normally and the context stays
     usable - the next GEMM is correct."""
     torch.manual_seed(0)
