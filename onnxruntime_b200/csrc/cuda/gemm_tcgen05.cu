@@ -535,7 +535,7 @@ template <int BN, int STAGES, bool DUAL, bool TWOM = false>
 static int launch_gemm(const CUtensorMap& tw, const CUtensorMap& tx, const GemmKernelParams& p, int grid,
                        cudaStream_t stream, bool use_pdl) {
   using S = GemmSmem<BN, STAGES, DUAL, TWOM>;
-  static_assert(S::kTotal <= 227 * 1024, "shared memory budget exceeded");
+  static_assert(S::kTotal <= 227 * 1024, "shared memory limit exceeded");
   auto kern = gemm_tcgen05_kernel<BN, STAGES, DUAL, TWOM>;
   static bool attr_set = false;
   if (!attr_set) {

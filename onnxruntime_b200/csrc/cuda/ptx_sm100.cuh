@@ -25,7 +25,7 @@ enum KernelStatus : int {
   kStatusBadArgument = 6,
 };
 
-// Spin budgets.  A try_wait that fails suspends for a hardware-defined time
+// Spin limits.  A try_wait that fails suspends for a hardware-defined time
 // slice, so these iteration counts correspond to roughly a second.
 #ifndef ORTB200_SPIN_LIMIT
 #define ORTB200_SPIN_LIMIT (1u << 20)
@@ -85,7 +85,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Bounded wait.  Returns false when the budget ran out.
+// Bounded wait.  Returns false when the limit was reached.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
   for (uint32_t i = 0; i < ORTB200_SPIN_LIMIT; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
