@@ -455,9 +455,17 @@ Node* Graph::AddNode(const std::string& op_type, const std::vector<std::string>&
 void Graph::RemoveNode(Node* n) {
   if (!n) return;
   ORTB_ENFORCE(n->id >= 0 && n->id < static_cast<int>(nodes_.size()) && nodes_[n->id].get() == n, "foreign node");
-  nodes_[n->id].reset();
+  // Tombstone: a pass may still hold this pointer in a snapshot of the node list, so the object stays alive (with an
+  // operator type nothing matches) until PurgeRemoved() runs between passes.
+  n->removed = true;
+  n->op_type = "<removed>";
+  n->inputs.clear();
+  n->outputs.clear();
+  graveyard_.push_back(std::move(nodes_[n->id]));
   dirty_ = true;
 }
+
+void Graph::PurgeRemoved() { graveyard_.clear(); }
 
 std::vector<Node*> Graph::Nodes() const {
   std::vector<Node*> out;
@@ -685,7 +693,7 @@ int Graph::RemoveDeadNodes() {
         }
       }
       if (!used) {
-        n.reset();
+        RemoveNode(n.get());
         ++removed;
         changed = true;
         dirty_ = true;

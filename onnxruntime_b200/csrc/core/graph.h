@@ -47,6 +47,7 @@ struct Node {
   std::map<std::string, std::shared_ptr<Graph>> subgraphs;  // attribute name -> body
   std::string ep;  // execution provider assigned by the partitioner
   int since_version = 0;
+  bool removed = false;  // set by Graph::RemoveNode; the object lives on until Graph::PurgeRemoved()
 
   bool has_attr(const std::string& n) const { return attrs.count(n) != 0; }
   int64_t attr_i(const std::string& n, int64_t dflt) const;
@@ -83,7 +84,10 @@ class Graph {
   Node* AddNode(const std::string& op_type, const std::vector<std::string>& inputs,
                 const std::vector<std::string>& outputs, const std::string& domain = "",
                 const std::string& name = "");
+  // Unlinks `n` from the graph.  The object itself is only marked (`removed`, operator type "<removed>") and is
+  // released by PurgeRemoved(), so loops over a snapshot of Nodes() may still read it.
   void RemoveNode(Node* n);
+  void PurgeRemoved();
   std::vector<Node*> Nodes() const;             // live nodes, insertion order
   std::vector<Node*> TopologicalOrder() const;  // Kahn's algorithm, stable; throws INVALID_GRAPH on a cycle
   size_t NumNodes() const;
@@ -135,6 +139,7 @@ class Graph {
 
   std::string name_;
   std::vector<std::unique_ptr<Node>> nodes_;
+  std::vector<std::unique_ptr<Node>> graveyard_;  // removed nodes awaiting PurgeRemoved()
   std::map<std::string, at::Tensor> initializers_;
   std::set<std::string> pending_external_;
   std::vector<ValueInfo> inputs_, outputs_;

@@ -252,7 +252,30 @@ class GemmKernel final : public OpKernel {
     const at::Tensor& x = ctx.RequiredInput(0);
     at::Tensor x2 = Flatten2D(x);
     at::Tensor bias = bias_idx_ >= 0 && ctx.HasInput(bias_idx_) ? ctx.Input(bias_idx_) : at::Tensor();
-    at::Tensor res = residual_idx_ >= 0 && ctx.HasInput(residual_idx_) ? Flatten2D(ctx.Input(residual_idx_)) : at::Tensor();
+    at::Tensor res = residual_idx_ >= 0 && ctx.HasInput(residual_idx_) ? ctx.Input(residual_idx_) : at::Tensor();
+    at::Tensor late_res;  // a residual the kernels cannot index row by row: added afterwards with broadcasting
+    if (res.defined()) {
+      // The epilogues read residual[m * ld + n] for every m < M, so the operand must be exactly the output's shape
+      // and type.  Anything else (a [B, 1, N] or [N] term that the original Add would have broadcast, or a larger
+      // operand that broadcasts the product up) takes the plain Add after the GEMM.
+      if (res.sizes().vec() == OutShape(x, N_) && res.scalar_type() == x.scalar_type()) {
+        res = Flatten2D(res);
+      } else {
+        late_res = res;
+        res = at::Tensor();
+      }
+    }
+    if (late_res.defined()) {
+      at::Tensor y;
+      if (all_reduce_ && ctx.session()->world_size > 1) {
+        y = LaunchGemm(ctx, x2, w_nk_, N_, 0, bias, at::Tensor(), act_, alpha_);
+        y = GemmAllReduce(ctx, y, at::Tensor());
+      } else {
+        y = LaunchNormedGemm(ctx, x2, w_nk_, N_, 0, bias, at::Tensor(), act_, alpha_, rms_eps_, unit_gamma_);
+      }
+      ctx.SetOutput(0, at::add(y.reshape(OutShape(x, N_)), late_res));
+      return;
+    }
     if (all_reduce_ && ctx.session()->world_size > 1) {
       if (act_ == ORTB200_ACT_NONE && CanFuseAllReduce(ctx, x2.size(0), N_)) {
         // one kernel: tcgen05 GEMM, partial tiles pushed to every peer over NVLink, summed in rank order, + residual

@@ -338,6 +338,7 @@ class GqaKernel final : public WithFallback {
       pa.B = static_cast<int>(B); pa.S = static_cast<int>(S); pa.N = static_cast<int>(N_); pa.Nk = static_cast<int>(Nk_);
       pa.H = static_cast<int>(H); pa.Smax = static_cast<int>(Smax);
       pa.rot_dim = do_rotary_ ? static_cast<int>(ctx.Input(7).size(1) * 2) : 0;
+      pa.cos_rows = do_rotary_ ? static_cast<int>(ctx.Input(7).size(0)) : 0;
       pa.interleaved = interleaved_ ? 1 : 0;
       pa.first_prompt = first_prompt ? 1 : 0;
       pa.do_rotary = do_rotary_ ? 1 : 0;
@@ -359,6 +360,7 @@ class GqaKernel final : public WithFallback {
         da.sin_cache = do_rotary_ ? ctx.RequiredInput(8).data_ptr() : nullptr;
         da.do_rotary = do_rotary_ ? 1 : 0;
         da.rotary_interleaved = interleaved_ ? 1 : 0;
+        da.cos_rows = do_rotary_ ? static_cast<int>(ctx.Input(7).size(0)) : 0;
       }
       da.k_cache = kc.data_ptr();
       da.v_cache = vc.data_ptr();

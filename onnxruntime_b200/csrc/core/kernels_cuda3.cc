@@ -176,6 +176,7 @@ class PagedAttentionKernel final : public WithFallback {
     pa.past_seqlens = past.data_ptr<int>();
     pa.block_table = tb.data_ptr<int>();
     pa.cos_cache = do_rotary_ ? ctx.Input(8).data_ptr() : nullptr;
+    pa.cos_rows = do_rotary_ ? static_cast<int>(ctx.Input(8).size(0)) : 0;
     pa.sin_cache = do_rotary_ ? ctx.RequiredInput(9).data_ptr() : nullptr;
     pa.T = static_cast<int>(T); pa.B = static_cast<int>(B); pa.N = static_cast<int>(N_); pa.Nk = static_cast<int>(Nk_);
     pa.H = static_cast<int>(H);
@@ -212,6 +213,7 @@ class PagedAttentionKernel final : public WithFallback {
     if (fuse) {
       da.qkv = qc.data_ptr();
       da.cos_cache = pa.cos_cache;
+      da.cos_rows = pa.cos_rows;
       da.sin_cache = pa.sin_cache;
       da.do_rotary = pa.do_rotary;
       da.rotary_interleaved = pa.interleaved;

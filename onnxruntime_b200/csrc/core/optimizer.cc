@@ -220,6 +220,7 @@ OptimizerStats OptimizeGraph(Graph& g, int level, const std::set<std::string>& d
       if (p.gpu_only && !gpu) continue;
       if (disabled.count(p.name)) continue;
       const int n = p.run(ctx);
+      g.PurgeRemoved();  // no pass keeps node pointers beyond its own run
       if (n > 0) {
         stats.applied[p.name] += n;
         changed += n;
@@ -229,6 +230,7 @@ OptimizerStats OptimizeGraph(Graph& g, int level, const std::set<std::string>& d
     if (!changed) break;
   }
   g.RemoveDeadNodes();
+  g.PurgeRemoved();
   // recurse into control-flow bodies with the basic passes
   for (Node* n : g.Nodes())
     for (auto& kv : n->subgraphs) {

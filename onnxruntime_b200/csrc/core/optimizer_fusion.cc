@@ -308,27 +308,53 @@ int AttentionFusion(PassContext& c) {
     m.matched.insert(m.matched.begin(), out_reshape);
     if (!IsClosed(g, m, out_reshape)) continue;
 
-    // mask: accept the raw [B,S] attention mask behind the usual (1 - mask) * -10000 expansion
+    // mask: only the exact expansion of a 2-D keep-mask is understood,
+    //   Mul(Sub(1, Cast?(Unsqueeze(Unsqueeze(mask)))), negative constant)      (Cast may sit on either side of the
+    // Unsqueezes; one Unsqueeze with two axes counts as two).  Anything else added to the scores (an additive float
+    // mask, a bias, a differently built expansion) leaves the block unfused: turning it into mask_index would change
+    // the result.
     std::string mask_index;
     if (!mask_value.empty()) {
-      // walk up: Mul(Sub(1, Cast(Unsqueeze(Unsqueeze(mask)))), -10000)
-      std::string mv = mask_value;
-      Node* p = g.Producer(mv);
-      std::vector<std::string> chain_ops;
-      int guard = 0;
-      while (p && guard++ < 8 && p->domain.empty() &&
-             (p->op_type == "Mul" || p->op_type == "Sub" || p->op_type == "Cast" || p->op_type == "Unsqueeze" || p->op_type == "Reshape")) {
-        std::string next;
-        for (auto& in : p->inputs) {
-          double dummy;
-          if (in.empty() || ScalarConst(g, in, &dummy) || g.GetConstant(in)) continue;
-          next = in;
+      Node* mul = g.Producer(mask_value);
+      if (!mul || !mul->domain.empty() || mul->op_type != "Mul" || mul->inputs.size() != 2) continue;
+      double neg = 0;
+      int cs = -1;
+      for (int s2 = 0; s2 < 2; ++s2)
+        if (ScalarConst(g, mul->inputs[s2], &neg)) cs = s2;
+      if (cs < 0 || !(neg < -1.0)) continue;
+      Node* sub = g.Producer(mul->inputs[1 - cs]);
+      double one = 0;
+      if (!sub || !sub->domain.empty() || sub->op_type != "Sub" || sub->inputs.size() != 2 ||
+          !ScalarConst(g, sub->inputs[0], &one) || std::abs(one - 1.0) > 1e-6)
+        continue;
+      std::string mv = sub->inputs[1];
+      int unsqueezed = 0, guard = 0;
+      bool ok = true;
+      for (Node* p = g.Producer(mv); p && guard++ < 6; p = g.Producer(mv)) {
+        if (!p->domain.empty()) break;
+        if (p->op_type == "Cast") {
+          mv = p->inputs[0];
+        } else if (p->op_type == "Unsqueeze") {
+          std::vector<int64_t> axes = p->attr_ints("axes");
+          if (axes.empty() && p->has_input(1)) {
+            const at::Tensor* ax = g.GetConstant(p->inputs[1]);
+            if (!ax) { ok = false; break; }
+            at::Tensor axc = ax->to(at::kCPU, at::kLong).reshape({-1});
+            for (int64_t i = 0; i < axc.numel(); ++i) axes.push_back(axc[i].item<int64_t>());
+          }
+          for (int64_t a : axes)
+            if (a != 1 && a != 2) ok = false;  // [B, S] -> [B, 1, 1, S]
+          unsqueezed += static_cast<int>(axes.size());
+          mv = p->inputs[0];
+        } else {
+          break;
         }
-        if (next.empty()) break;
-        mv = next;
-        p = g.Producer(mv);
       }
-      if (!g.IsGraphInput(mv) && !(p && p->op_type == "Cast")) continue;  // unknown mask construction: leave the block alone
+      if (!ok || unsqueezed != 2) continue;
+      // a declared rank other than 2 rules the pattern out
+      for (auto& vi : g.Inputs())
+        if (vi.name == mv && vi.type.which == 1 && vi.type.has_shape && vi.type.dims.size() != 2) ok = false;
+      if (!ok) continue;
       mask_index = mv;
     }
 
@@ -347,7 +373,9 @@ int AttentionFusion(PassContext& c) {
     }
     Node* f = g.AddNode("Attention", ins, {out_reshape->outputs[0]}, kMSDomain, g.UniqueName("Attention"));
     f->set_attr_i("num_heads", num_heads);
-    if (have_scale) f->set_attr_f("scale", static_cast<float>(scale));
+    // always explicit: the operator's default is 1 / sqrt(head size), which is wrong for a block that scales elsewhere
+    // (folded into the weights) or not at all
+    f->set_attr_f("scale", have_scale ? static_cast<float>(scale) : 1.0f);
     RemoveMatched(g, m);
     ++count;
   }

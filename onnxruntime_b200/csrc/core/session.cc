@@ -82,6 +82,7 @@ struct InferenceSession::CapturedGraph {
   std::vector<at::Tensor> static_in;   // per runtime input: tensor whose storage the graph reads
   std::vector<std::vector<int64_t>> in_shapes;
   bool captured = false;
+  bool bound_at_capture = false;       // inputs were IOBinding buffers, used in place
   int warm_runs = 0;
 };
 
@@ -333,6 +334,14 @@ static void ValidateFeed(const ValueInfo& vi, const at::Tensor& t) {
   }
 }
 
+namespace {
+bool AliasesAny(const at::Tensor& t, const std::vector<at::Tensor>& pool) {
+  for (auto& p : pool)
+    if (p.defined() && p.is_alias_of(t)) return true;
+  return false;
+}
+}  // namespace
+
 std::vector<Value> InferenceSession::RunImpl(const RunOptions& ro, const std::vector<std::string>& feed_names,
                                              const std::vector<Value>& feeds,
                                              const std::vector<std::string>& output_names_in,
@@ -402,14 +411,22 @@ std::vector<Value> InferenceSession::RunImpl(const RunOptions& ro, const std::ve
     if (!cg.captured) {
       cg.static_in.clear();
       cg.in_shapes.clear();
+      // Addresses are frozen into the graph.  Buffers bound through IOBinding are used in place (the caller fixed their
+      // addresses on purpose: a KV cache is updated where it lies), as the reference requires for graph replay.
+      // Tensors handed to a plain run() are copied into buffers the session owns, so that a later run with other
+      // tensors never writes into the first call's arguments.
+      cg.bound_at_capture = bound_outputs != nullptr;
       for (auto& v : inputs) {
-        cg.static_in.push_back(v.t);
-        cg.in_shapes.push_back(v.t.defined() ? v.t.sizes().vec() : std::vector<int64_t>{});
+        at::Tensor t = v.t;
+        if (t.defined() && !cg.bound_at_capture) t = t.clone();
+        cg.static_in.push_back(t);
+        cg.in_shapes.push_back(t.defined() ? t.sizes().vec() : std::vector<int64_t>{});
       }
       cg.slots = ex->NewSlots();
       for (size_t i = 0; i < inputs.size(); ++i) {
         const int s = ex->SlotOf(input_names_[i]);
-        if (inputs[i].defined()) cg.slots[s] = inputs[i];
+        if (inputs[i].t.defined()) cg.slots[s].t = cg.static_in[i];
+        else if (inputs[i].defined()) cg.slots[s] = inputs[i];
       }
       c10::cuda::CUDAStream side = c10::cuda::getStreamFromPool(false, device_.index());
       {
@@ -431,21 +448,26 @@ std::vector<Value> InferenceSession::RunImpl(const RunOptions& ro, const std::ve
     } else {
       for (size_t i = 0; i < inputs.size(); ++i) {
         if (!inputs[i].t.defined()) continue;
-        ORTB_ENFORCE_ARG(inputs[i].t.sizes().vec() == cg.in_shapes[i], "input '", input_names_[i],
+        ORTB_ENFORCE_ARG(cg.static_in[i].defined() && inputs[i].t.sizes().vec() == cg.in_shapes[i], "input '", input_names_[i],
                          "' changed shape after CUDA graph capture; use a different gpu_graph_id per shape");
+        ORTB_ENFORCE_ARG(inputs[i].t.scalar_type() == cg.static_in[i].scalar_type() && inputs[i].t.device() == cg.static_in[i].device(),
+                         "input '", input_names_[i], "' changed type or device after CUDA graph capture");
         if (inputs[i].t.data_ptr() != cg.static_in[i].data_ptr()) cg.static_in[i].copy_(inputs[i].t, true);
       }
       cg.graph.replay();
     }
     results.clear();
     for (auto& n : output_names) results.push_back(cg.slots[ex->SlotOf(n)]);
-    if (bound_outputs) {
-      for (size_t i = 0; i < results.size(); ++i) {
-        const at::Tensor& b = (*bound_outputs)[i].t;
-        if (b.defined() && results[i].t.defined() && b.data_ptr() != results[i].t.data_ptr()) {
-          const_cast<at::Tensor&>(b).copy_(results[i].t, true);
-          results[i].t = b;
-        }
+    for (size_t i = 0; i < results.size(); ++i) {
+      if (!results[i].t.defined()) continue;
+      const at::Tensor b = bound_outputs ? (*bound_outputs)[i].t : at::Tensor();
+      if (b.defined()) {
+        if (b.data_ptr() != results[i].t.data_ptr()) const_cast<at::Tensor&>(b).copy_(results[i].t, true);
+        results[i].t = b;
+      } else if (!bound_outputs || !AliasesAny(results[i].t, cg.static_in)) {
+        // the graph's own output buffer is overwritten by the next replay: hand out a copy (an output that is one of
+        // the bound input buffers, such as an in-place KV cache, is returned as it is)
+        results[i].t = results[i].t.clone();
       }
     }
   } else if (bound_outputs) {

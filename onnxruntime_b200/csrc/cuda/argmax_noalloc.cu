@@ -23,7 +23,7 @@ void* g_scratch_addr[kMaxDevices] = {};
 // value in the high half (made orderable as an unsigned integer), inverted index in the low half:
 // the larger value wins and, between equal values, the smaller index
 __device__ __forceinline__ unsigned long long make_key(float v, long long idx) {
-  unsigned int u = __float_as_uint(v);
+  unsigned int u = __float_as_uint(v + 0.0f);  // -0.0 + 0.0 = +0.0: the two zeros compare equal, the first index wins
   u = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
   return (static_cast<unsigned long long>(u) << 32) | static_cast<unsigned long long>(0xFFFFFFFFu - static_cast<unsigned int>(idx));
 }

@@ -33,7 +33,8 @@ __global__ void __launch_bounds__(256) gqa_prep_kernel(const ortb200_gqa_prep_ar
   pdl_launch_dependents();  // the attention kernel may set up; it waits for this grid before reading q or the caches
   pdl_wait_prior_grids();
   const int past = a.first_prompt ? 0 : a.seqlens_k[b] + 1 - a.S;
-  const long long pos = a.position_ids ? a.position_ids[static_cast<long long>(b) * a.S + s] : past + s;
+  long long pos = a.position_ids ? a.position_ids[static_cast<long long>(b) * a.S + s] : past + s;
+  if (a.cos_rows > 0) pos = pos < 0 ? 0 : (pos >= a.cos_rows ? a.cos_rows - 1 : pos);  // never read past the rotary tables
   const int cache_pos = past + s;
   const long long tok = static_cast<long long>(b) * a.S + s;
   const T* cosr = a.do_rotary ? static_cast<const T*>(a.cos_cache) + pos * half : nullptr;
@@ -115,8 +116,9 @@ __global__ void __launch_bounds__(256) paged_prep_kernel(const ortb200_paged_pre
   }
   const bool slot_ok = slot >= 0 && slot < static_cast<long long>(a.num_blocks) * a.block_size;
   if (!a.slot_mapping && !slot_ok && threadIdx.x == 0 && a.status) atomicExch(a.status, kStatusBadArgument);
-  const T* cosr = a.do_rotary ? static_cast<const T*>(a.cos_cache) + static_cast<long long>(pos) * half : nullptr;
-  const T* sinr = a.do_rotary ? static_cast<const T*>(a.sin_cache) + static_cast<long long>(pos) * half : nullptr;
+  const int rpos = a.cos_rows > 0 ? (pos < 0 ? 0 : (pos >= a.cos_rows ? a.cos_rows - 1 : pos)) : pos;  // never read past the rotary tables
+  const T* cosr = a.do_rotary ? static_cast<const T*>(a.cos_cache) + static_cast<long long>(rpos) * half : nullptr;
+  const T* sinr = a.do_rotary ? static_cast<const T*>(a.sin_cache) + static_cast<long long>(rpos) * half : nullptr;
   for (int idx = threadIdx.x; idx < heads * halfH; idx += blockDim.x) {
     const int head = idx / halfH, i = idx % halfH;
     const T* src;
@@ -197,7 +199,12 @@ __global__ void __launch_bounds__(128) gqa_decode_kernel(const DecodeParams p) {
   __syncthreads();
 
   pdl_wait_prior_grids();
-  const int total = p.seqlens_k[b] + 1;
+  int total = p.seqlens_k[b] + 1;
+  if (total > p.Smax || total < 0) {
+    // a length beyond the cache capacity would read past the buffer: attend to what the cache holds and report it
+    if (tid == 0 && p.status) atomicExch(p.status, kStatusBadLength);
+    total = total < 0 ? 0 : p.Smax;
+  }
   const int start0 = p.window > 0 ? max(0, total - p.window) : 0;
   const int len = max(total - start0, 0);
   const int chunk = (len + p.splits - 1) / p.splits;
@@ -252,8 +259,9 @@ __global__ void __launch_bounds__(128) gqa_decode_kernel(const DecodeParams p) {
   // lane 4 further on; interleaved: neighbouring dims, held by this lane)
   float rc[DPL], rs[DPL];
   if (fused && p.do_rotary) {
-    const T* cosr = static_cast<const T*>(p.cos_cache) + static_cast<long long>(total - 1) * (H / 2);
-    const T* sinr = static_cast<const T*>(p.sin_cache) + static_cast<long long>(total - 1) * (H / 2);
+    const int rpos = p.cos_rows > 0 && total - 1 >= p.cos_rows ? p.cos_rows - 1 : (total > 0 ? total - 1 : 0);
+    const T* cosr = static_cast<const T*>(p.cos_cache) + static_cast<long long>(rpos) * (H / 2);
+    const T* sinr = static_cast<const T*>(p.sin_cache) + static_cast<long long>(rpos) * (H / 2);
 #pragma unroll
     for (int i = 0; i < DPL; ++i) {
       const int d = d0 + i;
@@ -540,7 +548,7 @@ static int launch_decode(const ortb200_gqa_decode_args* a, cudaStream_t stream) 
   p.scale = a->scale != 0.f ? a->scale : 1.0f / sqrtf(static_cast<float>(H));
   p.softcap = a->softcap;
   p.block_table = a->block_table; p.block_size = a->block_size; p.max_blocks = a->max_blocks;
-  p.qkv = a->qkv; p.cos_cache = a->cos_cache; p.sin_cache = a->sin_cache;
+  p.qkv = a->qkv; p.cos_cache = a->cos_cache; p.sin_cache = a->sin_cache; p.cos_rows = a->cos_rows;
   p.prefetch = nullptr; p.prefetch_bytes = 0; p.prefetch_per_cta = 0;
   p.do_rotary = a->do_rotary; p.interleaved = a->rotary_interleaved;
   dim3 grid(splits, a->Nk * gparts, a->B);

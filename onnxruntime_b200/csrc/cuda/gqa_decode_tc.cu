@@ -120,7 +120,12 @@ gqa_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   const uint32_t tmem_o = tmem_base + 32;
 
   pdl_wait_prior_grids();
-  const int total = p.seqlens_k[b] + 1;
+  int total = p.seqlens_k[b] + 1;
+  if (total > p.Smax || total < 0) {
+    // a length beyond the cache capacity would read past the buffer: attend to what the cache holds and report it
+    if (threadIdx.x == 0 && p.status) atomicExch(p.status, kStatusBadLength);
+    total = total < 0 ? 0 : p.Smax;
+  }
   const int start0 = p.window > 0 ? max(0, total - p.window) : 0;
   const int len = max(total - start0, 0);
   int chunk = (len + p.splits - 1) / p.splits;
@@ -258,8 +263,9 @@ gqa_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     float c = 1.f, sn = 0.f;
     if (p.do_rotary) {
       const int fi = p.interleaved ? (t >> 1) : (t & (H / 2 - 1));
-      c = to_float<T>(static_cast<const T*>(p.cos_cache)[static_cast<long long>(total - 1) * (H / 2) + fi]);
-      sn = to_float<T>(static_cast<const T*>(p.sin_cache)[static_cast<long long>(total - 1) * (H / 2) + fi]);
+      const int rpos = p.cos_rows > 0 && total - 1 >= p.cos_rows ? p.cos_rows - 1 : (total > 0 ? total - 1 : 0);  // stay inside the tables
+      c = to_float<T>(static_cast<const T*>(p.cos_cache)[static_cast<long long>(rpos) * (H / 2) + fi]);
+      sn = to_float<T>(static_cast<const T*>(p.sin_cache)[static_cast<long long>(rpos) * (H / 2) + fi]);
     }
     float qx[G];
 #pragma unroll
@@ -564,7 +570,7 @@ int launch_gqa_decode_tc(const ortb200_gqa_decode_args* a, cudaStream_t stream) 
   p.scale = a->scale != 0.f ? a->scale : 1.0f / sqrtf(static_cast<float>(H));
   p.softcap = a->softcap;
   p.block_table = a->block_table; p.block_size = a->block_size; p.max_blocks = a->max_blocks;
-  p.qkv = a->qkv; p.cos_cache = a->cos_cache; p.sin_cache = a->sin_cache;
+  p.qkv = a->qkv; p.cos_cache = a->cos_cache; p.sin_cache = a->sin_cache; p.cos_rows = a->cos_rows;
   p.do_rotary = a->do_rotary; p.interleaved = a->rotary_interleaved;
   dim3 grid(splits, a->Nk, a->B);
   p.prefetch = nullptr; p.prefetch_bytes = 0; p.prefetch_per_cta = 0;

@@ -26,6 +26,7 @@ struct DecodeParams {
   // output qkv [B, (N + 2 Nk) H]; the CTA whose key range ends at the new position rotates the new key, writes
   // key and value into the cache and attends to them from registers
   const void* qkv;
+  int cos_rows;
   const void* cos_cache;
   const void* sin_cache;
   int do_rotary, interleaved;

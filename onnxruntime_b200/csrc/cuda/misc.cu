@@ -27,7 +27,7 @@ __global__ void gather_rows_kernel(const uint4* __restrict__ table, const int64_
 
 // Orderable 64-bit key: larger value wins, ties go to the smaller index.
 __device__ __forceinline__ unsigned long long argmax_key(float v, long long idx) {
-  unsigned int u = __float_as_uint(v);
+  unsigned int u = __float_as_uint(v + 0.0f);  // -0.0 + 0.0 = +0.0: the two zeros compare equal, the first index wins
   u = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
   return (static_cast<unsigned long long>(u) << 32) | static_cast<unsigned long long>(0xFFFFFFFFu - static_cast<unsigned int>(idx));
 }

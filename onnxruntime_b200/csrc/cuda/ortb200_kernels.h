@@ -189,6 +189,7 @@ typedef struct {
   int do_rotary;
   int dtype;
   int use_pdl;                 // launch with programmatic stream serialization (overlaps the previous kernel's tail)
+  int cos_rows;                // rows of cos_cache / sin_cache; positions are clamped to it (0 = not checked)
 } ortb200_gqa_prep_args;
 int ortb200_gqa_prep(const ortb200_gqa_prep_args* args, ortb200_stream_t stream);
 
@@ -213,6 +214,7 @@ typedef struct {
   int block_size, max_blocks, num_blocks;
   int rot_dim, interleaved, do_rotary, dtype;
   int* status;                 // device int, may be null: a block index outside the table is reported here
+  int cos_rows;                // rows of cos_cache / sin_cache; positions are clamped to it (0 = not checked)
 } ortb200_paged_prep_args;
 int ortb200_paged_prep(const ortb200_paged_prep_args* args, ortb200_stream_t stream);
 
@@ -258,6 +260,7 @@ typedef struct {
   // step leaves most of the memory bandwidth idle, so the CTAs ask the L2 for it while they work (at most 48 MiB).
   const void* prefetch;
   int64_t prefetch_bytes;
+  int cos_rows;           // rows of cos_cache / sin_cache; the rotary position is clamped to it (0 = not checked)
 } ortb200_gqa_decode_args;
 int ortb200_gqa_decode(const ortb200_gqa_decode_args* args, ortb200_stream_t stream);
 int64_t ortb200_gqa_decode_workspace_bytes(int B, int N, int H);

@@ -23,6 +23,7 @@ enum KernelStatus : int {
   kStatusTimeoutPeer = 4,       // gave up waiting on a flag owned by another rank
   kStatusTimeoutSplitK = 5,     // gave up waiting for the partial tiles of a split
   kStatusBadArgument = 6,
+  kStatusBadLength = 7,         // a sequence length beyond the cache capacity was clamped
 };
 
 // Spin limits.  A try_wait that fails suspends for a hardware-defined time

@@ -245,3 +245,57 @@ def test_rms_norm_folds_into_the_surrounding_gemms():
     # without the GPU passes the norms stay
     plain, _ = C.optimize_model(model, 99, [], False)
     assert "SkipSimplifiedLayerNormalization" in [n["op_type"] for n in C.model_nodes(plain)]
+
+
+def _attention_block(scale_node: bool, mask_kind: str):
+    """One self-attention block on x [b, 8, 16] with 2 heads, built node by node.  mask_kind: "none", "keep" (the
+    (1 - mask) * -10000 expansion of a 2-D keep-mask) or "additive" (a float [b, 1, 1, 8] term added to the scores)."""
+    Hd, heads, hs = 16, 2, 8
+    inits = [c("shape4", [0, 0, heads, hs], np.int64), c("shape3", [0, 0, Hd], np.int64)]
+    nodes = []
+    for nm in "qkv":
+        inits += [c("W" + nm, rng.randn(Hd, Hd) * 0.3), c("B" + nm, rng.randn(Hd) * 0.1)]
+        nodes += [ol.make_node("MatMul", ["x", "W" + nm], [nm + "_mm"]), ol.make_node("Add", [nm + "_mm", "B" + nm], [nm + "_b"]),
+                  ol.make_node("Reshape", [nm + "_b", "shape4"], [nm + "_r"]),
+                  ol.make_node("Transpose", [nm + "_r"], [nm + "_t"], perm=[0, 2, 3, 1] if nm == "k" else [0, 2, 1, 3])]
+    nodes.append(ol.make_node("MatMul", ["q_t", "k_t"], ["qk"]))
+    scores = "qk"
+    if scale_node:
+        inits.append(c("sqrt_hs", math.sqrt(hs)))
+        nodes.append(ol.make_node("Div", ["qk", "sqrt_hs"], ["qk_s"]))
+        scores = "qk_s"
+    ins = list(X)
+    if mask_kind == "keep":
+        ins.append(ol.make_tensor_value_info("mask", T.INT64, ["b", 8]))
+        inits += [c("ax1", [1], np.int64), c("ax2", [2], np.int64), c("one", 1.0), c("neg", -10000.0)]
+        nodes += [ol.make_node("Unsqueeze", ["mask", "ax1"], ["m1"]), ol.make_node("Unsqueeze", ["m1", "ax2"], ["m2"]),
+                  ol.make_node("Cast", ["m2"], ["mf"], to=T.FLOAT), ol.make_node("Sub", ["one", "mf"], ["inv"]),
+                  ol.make_node("Mul", ["inv", "neg"], ["addm"]), ol.make_node("Add", [scores, "addm"], ["masked"])]
+        scores = "masked"
+    elif mask_kind == "additive":
+        ins.append(ol.make_tensor_value_info("bias4", T.FLOAT, ["b", 1, 1, 8]))
+        nodes.append(ol.make_node("Add", [scores, "bias4"], ["masked"]))
+        scores = "masked"
+    nodes += [ol.make_node("Softmax", [scores], ["p"], axis=-1), ol.make_node("MatMul", ["p", "v_t"], ["ctx"]),
+              ol.make_node("Transpose", ["ctx"], ["ctx_t"], perm=[0, 2, 1, 3]), ol.make_node("Reshape", ["ctx_t", "shape3"], ["y"])]
+    return graph_model(nodes, ins, Y, inits)
+
+
+@pytest.mark.parametrize("scale_node", [True, False])
+def test_attention_fusion_keeps_the_blocks_own_scaling(scale_node):
+    """A block without a Div / Mul on the scores (scale folded into the weights, or none) must not pick up the fused
+    operator's default 1 / sqrt(head size)."""
+    before, after = both(_attention_block(scale_node, "none"), xs)
+    assert after.get("Attention") == 1 and "Softmax" not in after
+
+
+def test_attention_fusion_understands_only_the_keep_mask_expansion():
+    keep = np.ones((2, 8), np.int64)
+    keep[1, 5:] = 0
+    before, after = both(_attention_block(True, "keep"), dict(xs, mask=keep))
+    assert after.get("Attention") == 1
+    # an additive float term is not a keep-mask: the block stays as it is and the numbers stay right
+    bias4 = np.zeros((2, 1, 1, 8), np.float32)
+    bias4[0, ..., 6:] = -10000.0
+    before, after = both(_attention_block(True, "additive"), dict(xs, bias4=bias4))
+    assert "Attention" not in after and after.get("Softmax") == 1
