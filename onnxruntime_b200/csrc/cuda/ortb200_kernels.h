@@ -119,6 +119,47 @@ typedef struct {
   int use_pdl;
 } ortb200_gemm_grouped_args;
 int ortb200_gemm_grouped(const ortb200_gemm_grouped_args* args, ortb200_stream_t stream);
+
+// ---------------------------------------------------------------------------
+// A chain of decode-shaped GEMMs (M <= 16 token rows) in one persistent launch: stage s computes
+//   y_s[M, N_s] = act_s((x_s[M, K_s] @ W_s[N_s, K_s]^T) / rms(x_s) + bias_s) + residual_s      with x_0 = x, x_{s+1} = y_s
+// so K_{s+1} must equal N_s.  One CTA per SM walks all stages; the weight stream of stage s + 1 runs while stage s
+// drains, which is what a sequence of separate launches cannot do (gemm_chain.cu).  K_s must be a multiple of 64.
+#define ORTB200_CHAIN_MAX_STAGES 4
+typedef struct {
+  const void* w;         // [w_rows, K], K contiguous; with rms_eps > 0 the caller has folded the norm's gamma into it
+  void* out;             // [M, N] contiguous (also the next stage's input)
+  const void* bias;      // [N] or null
+  const void* residual;  // [M, ldr] or null; ignored when residual_stage >= 0
+  int64_t ldr;
+  int N, K, w_rows;
+  int dual_offset;       // act == SWIGLU: up rows start dual_offset rows after the gate rows
+  int act;               // ortb200_act
+  float rms_eps;         // > 0: divide by rms of the stage's input rows (not for stage 0, not with all_reduce)
+  int residual_stage;    // >= 0: the residual is the output of that earlier stage of this chain; -1 = use `residual`
+  int all_reduce;        // world > 1: sum the products of all ranks before bias / activation / residual
+} ortb200_chain_stage;
+
+typedef struct {
+  const void* x;         // [M, K_0]
+  int M;                 // 1..16
+  int num_stages;        // 1..ORTB200_CHAIN_MAX_STAGES
+  int dtype;             // F16 or BF16 (everything: x, weights, outputs, bias, residual)
+  ortb200_chain_stage stage[ORTB200_CHAIN_MAX_STAGES];
+  void* workspace;       // ortb200_gemm_chain_workspace_bytes() bytes, zero before the first launch, left zero
+  int64_t workspace_bytes;
+  int* status;           // device int, may be null
+  int use_pdl;
+  int prefetch_items;    // how many (tile, k-block) items beyond its shared-memory ring a CTA asks the L2 for (0 = none)
+  int max_ctas;          // 0 = one CTA per SM
+  // tensor parallelism, as in ortb200_gemm_args (same symmetric workspace layout and epoch counter)
+  int world, rank;
+  void* peers[8];
+  int64_t symm_bytes;
+  void* trace;           // optional device buffer of gridDim x 32 uint64: %globaltimer stamps of the launch's phases (profiling)
+} ortb200_gemm_chain_args;
+int64_t ortb200_gemm_chain_workspace_bytes(void);
+int ortb200_gemm_chain(const ortb200_gemm_chain_args* args, ortb200_stream_t stream);
 int64_t ortb200_gemm_workspace_bytes(int M, int N, int K, int act);
 // Number of kernels one ortb200_gemm call launches (always 1).
 int ortb200_gemm_last_config(int* bn, int* splits, int* stages);

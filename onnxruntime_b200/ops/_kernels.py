@@ -117,6 +117,73 @@ def gemm(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
     return out
 
 
+class ChainStage(ctypes.Structure):
+    _fields_ = [("w", ctypes.c_void_p), ("out", ctypes.c_void_p), ("bias", ctypes.c_void_p), ("residual", ctypes.c_void_p),
+                ("ldr", ctypes.c_int64), ("N", ctypes.c_int), ("K", ctypes.c_int), ("w_rows", ctypes.c_int),
+                ("dual_offset", ctypes.c_int), ("act", ctypes.c_int), ("rms_eps", ctypes.c_float),
+                ("residual_stage", ctypes.c_int), ("all_reduce", ctypes.c_int)]
+
+
+class GemmChainArgs(ctypes.Structure):
+    _fields_ = [("x", ctypes.c_void_p), ("M", ctypes.c_int), ("num_stages", ctypes.c_int), ("dtype", ctypes.c_int),
+                ("stage", ChainStage * 4), ("workspace", ctypes.c_void_p), ("workspace_bytes", ctypes.c_int64),
+                ("status", ctypes.c_void_p), ("use_pdl", ctypes.c_int), ("prefetch_items", ctypes.c_int),
+                ("max_ctas", ctypes.c_int), ("world", ctypes.c_int), ("rank", ctypes.c_int), ("peers", ctypes.c_void_p * 8),
+                ("symm_bytes", ctypes.c_int64), ("trace", ctypes.c_void_p)]
+
+
+_CHAIN_WS = {}
+
+
+def gemm_chain(x: torch.Tensor, stages, status: Optional[torch.Tensor] = None, use_pdl: bool = False, prefetch_items: int = 0,
+               max_ctas: int = 0, peers=None, rank: int = 0, symm_bytes: int = 0, trace: Optional[torch.Tensor] = None):
+    """Runs up to four dependent decode-shaped GEMMs (x: [M <= 16, K0]) as one persistent launch.
+
+    ``stages`` is a list of dicts: ``w`` [rows, K] (for ``act="swiglu"`` the gate rows followed by the up rows), optional
+    ``bias`` [N], ``residual`` ([M, N] tensor, or an int = index of an earlier stage whose output is added), ``act``,
+    ``rms_eps`` (the caller has folded gamma into ``w``), ``all_reduce``.  Returns the list of stage outputs."""
+    assert x.is_cuda and x.dim() == 2 and x.is_contiguous() and 1 <= len(stages) <= 4
+    M = x.shape[0]
+    lib().ortb200_gemm_chain_workspace_bytes.restype = ctypes.c_int64
+    need = lib().ortb200_gemm_chain_workspace_bytes()
+    key = x.device.index if x.device.index is not None else torch.cuda.current_device()
+    ws = _CHAIN_WS.get(key)
+    if ws is None or ws.numel() < need:
+        ws = torch.zeros(need, dtype=torch.uint8, device=x.device)
+        _CHAIN_WS[key] = ws
+    a = GemmChainArgs()
+    a.x, a.M, a.num_stages, a.dtype = _ptr(x), M, len(stages), dtype_code(x.dtype)
+    outs, keep = [], []
+    for i, st in enumerate(stages):
+        w = st["w"]
+        assert w.is_contiguous() and w.dtype == x.dtype
+        act = st.get("act", "none")
+        n = st.get("n", w.shape[0] // 2 if act == "swiglu" else w.shape[0])
+        out = torch.empty((M, n), dtype=x.dtype, device=x.device)
+        outs.append(out)
+        res = st.get("residual")
+        c = a.stage[i]
+        c.w, c.out, c.bias = _ptr(w), _ptr(out), _ptr(st.get("bias"))
+        c.N, c.K, c.w_rows = n, w.shape[1], w.shape[0]
+        c.dual_offset = st.get("dual_offset", n) if act == "swiglu" else 0
+        c.act, c.rms_eps = ACT[act], float(st.get("rms_eps", 0.0))
+        c.all_reduce = 1 if st.get("all_reduce") else 0
+        if isinstance(res, int):
+            c.residual_stage, c.residual, c.ldr = res, None, 0
+        else:
+            c.residual_stage, c.residual, c.ldr = -1, _ptr(res), (res.stride(0) if res is not None else 0)
+            keep.append(res)
+    a.workspace, a.workspace_bytes, a.status = _ptr(ws), ws.numel(), _ptr(status)
+    a.use_pdl, a.prefetch_items, a.max_ctas = (1 if use_pdl else 0), prefetch_items, max_ctas
+    a.world, a.rank, a.symm_bytes = (len(peers) if peers else 1), rank, symm_bytes
+    a.trace = _ptr(trace)
+    if peers:
+        for i, pp in enumerate(peers):
+            a.peers[i] = pp
+    _check(lib().ortb200_gemm_chain(ctypes.byref(a), ctypes.c_void_p(stream_ptr())), "ortb200_gemm_chain")
+    return outs
+
+
 def gemm_last_config():
     bn, sp, st = ctypes.c_int(), ctypes.c_int(), ctypes.c_int()
     lib().ortb200_gemm_last_config(ctypes.byref(bn), ctypes.byref(sp), ctypes.byref(st))
@@ -153,7 +220,8 @@ class GqaPrepArgs(ctypes.Structure):
                 ("cos_cache", ctypes.c_void_p), ("sin_cache", ctypes.c_void_p), ("position_ids", ctypes.c_void_p),
                 ("B", ctypes.c_int), ("S", ctypes.c_int), ("N", ctypes.c_int), ("Nk", ctypes.c_int), ("H", ctypes.c_int),
                 ("Smax", ctypes.c_int), ("rot_dim", ctypes.c_int), ("interleaved", ctypes.c_int),
-                ("first_prompt", ctypes.c_int), ("do_rotary", ctypes.c_int), ("dtype", ctypes.c_int), ("use_pdl", ctypes.c_int)]
+                ("first_prompt", ctypes.c_int), ("do_rotary", ctypes.c_int), ("dtype", ctypes.c_int), ("use_pdl", ctypes.c_int),
+                ("cos_rows", ctypes.c_int)]
 
 
 def gqa_prep(qkv, k_cache, v_cache, seqlens_k, cos, sin, N, Nk, H, first_prompt, interleaved=False, position_ids=None):
@@ -161,7 +229,8 @@ def gqa_prep(qkv, k_cache, v_cache, seqlens_k, cos, sin, N, Nk, H, first_prompt,
     q_out = torch.empty(B, S, N, H, dtype=qkv.dtype, device=qkv.device)
     a = GqaPrepArgs(_ptr(qkv), None, None, _ptr(q_out), _ptr(k_cache), _ptr(v_cache), _ptr(seqlens_k), _ptr(cos), _ptr(sin),
                     _ptr(position_ids), B, S, N, Nk, H, k_cache.shape[2], 0 if cos is None else cos.shape[1] * 2,
-                    1 if interleaved else 0, 1 if first_prompt else 0, 0 if cos is None else 1, dtype_code(qkv.dtype))
+                    1 if interleaved else 0, 1 if first_prompt else 0, 0 if cos is None else 1, dtype_code(qkv.dtype), 0,
+                    0 if cos is None else cos.shape[0])
     _check(lib().ortb200_gqa_prep(ctypes.byref(a), ctypes.c_void_p(stream_ptr())), "ortb200_gqa_prep")
     return q_out
 
@@ -175,7 +244,8 @@ class GqaDecodeArgs(ctypes.Structure):
                 ("use_pdl", ctypes.c_int), ("status", ctypes.c_void_p), ("block_table", ctypes.c_void_p),
                 ("block_size", ctypes.c_int), ("max_blocks", ctypes.c_int), ("qkv", ctypes.c_void_p), ("cos_cache", ctypes.c_void_p),
                 ("sin_cache", ctypes.c_void_p), ("do_rotary", ctypes.c_int), ("rotary_interleaved", ctypes.c_int),
-                ("num_blocks", ctypes.c_int), ("algo", ctypes.c_int), ("prefetch", ctypes.c_void_p), ("prefetch_bytes", ctypes.c_int64)]
+                ("num_blocks", ctypes.c_int), ("algo", ctypes.c_int), ("prefetch", ctypes.c_void_p), ("prefetch_bytes", ctypes.c_int64),
+                ("cos_rows", ctypes.c_int)]
 
 
 _ATTN_WS = {}
@@ -211,7 +281,8 @@ def gqa_decode(q, k_cache, v_cache, seqlens_k, splits=0, window=-1, scale=0.0, s
                       ws.numel(), B, N, Nk, H, Smax, splits, window, scale, softcap, dtype_code(q.dtype), 0, None,
                       _ptr(block_table), block_size, max_blocks, _ptr(qkv), _ptr(cos), _ptr(sin), 0 if cos is None else 1,
                       1 if interleaved else 0, num_blocks, algo, _ptr(prefetch),
-                      prefetch.numel() * prefetch.element_size() if prefetch is not None else 0)
+                      prefetch.numel() * prefetch.element_size() if prefetch is not None else 0,
+                      0 if cos is None else cos.shape[0])
     _check(lib().ortb200_gqa_decode(ctypes.byref(a), ctypes.c_void_p(stream_ptr())), "ortb200_gqa_decode")
     return out
 
@@ -252,7 +323,7 @@ class PagedPrepArgs(ctypes.Structure):
                 ("cos_cache", ctypes.c_void_p), ("sin_cache", ctypes.c_void_p), ("T", ctypes.c_int), ("B", ctypes.c_int),
                 ("N", ctypes.c_int), ("Nk", ctypes.c_int), ("H", ctypes.c_int), ("block_size", ctypes.c_int),
                 ("max_blocks", ctypes.c_int), ("num_blocks", ctypes.c_int), ("rot_dim", ctypes.c_int), ("interleaved", ctypes.c_int),
-                ("do_rotary", ctypes.c_int), ("dtype", ctypes.c_int), ("status", ctypes.c_void_p)]
+                ("do_rotary", ctypes.c_int), ("dtype", ctypes.c_int), ("status", ctypes.c_void_p), ("cos_rows", ctypes.c_int)]
 
 
 def paged_prep(qkv, k_cache, v_cache, cu_seqlens, past_seqlens, block_table, N, Nk, cos=None, sin=None, interleaved=False,
@@ -264,7 +335,8 @@ def paged_prep(qkv, k_cache, v_cache, cu_seqlens, past_seqlens, block_table, N, 
     a = PagedPrepArgs(_ptr(qkv.contiguous()), None, None, _ptr(q_out), _ptr(k_cache), _ptr(v_cache), _ptr(cu_seqlens),
                       _ptr(past_seqlens), _ptr(block_table), _ptr(slot_mapping), _ptr(cos), _ptr(sin), T, past_seqlens.numel(), N, Nk, H,
                       k_cache.shape[1], block_table.shape[1], k_cache.shape[0], 0 if cos is None else cos.shape[1] * 2,
-                      1 if interleaved else 0, 0 if cos is None else 1, dtype_code(qkv.dtype), _ptr(status))
+                      1 if interleaved else 0, 0 if cos is None else 1, dtype_code(qkv.dtype), _ptr(status),
+                      0 if cos is None else cos.shape[0])
     _check(lib().ortb200_paged_prep(ctypes.byref(a), ctypes.c_void_p(stream_ptr())), "ortb200_paged_prep")
     return q_out
 
