@@ -14,7 +14,13 @@ Printed JSON: ``value`` = batch * K / time of K decode steps timed with CUDA eve
 ranks); ``e2e.value`` = the same loop driven the way a user drives it, with each step's inputs copied from
 pinned host memory and the sampled tokens read back to the host every step; ``ttft_ms_p50`` = prompt run.
 Each decode step streams all weights (16 GB at N=1), far more than the 126 MB L2, so no explicit L2 flush is
-needed between iterations (config.l2 says so).
+needed between iterations (config.l2 says so).  The K-step loop is timed ``--repeats`` times over the same cache
+positions; ``value`` is the median repeat and ``repeats`` carries min / median / max.
+
+``--impl library`` runs the same model, loop and timing on library kernels only (cuBLAS GEMMs, FlashAttention-2 or
+PyTorch SDPA, separate norm / activation kernels, ncclAllReduce; benchmarks/library_llama.py) and prints the same line
+with ``"impl": "library"``: the decomposition the reference executes, as a same-box comparison.  ``--impl reference``
+is the unmodified reference when it is installed.
 """
 from __future__ import annotations
 
@@ -107,7 +113,10 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=127)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "library"],
+                    help="ours: this package; reference: the unmodified reference (when installed); library: the same model on cuBLAS / "
+                         "FlashAttention / NCCL library kernels under PyTorch (the decomposition the reference executes)")
+    ap.add_argument("--repeats", type=int, default=5, help="the timed K-step loop is run this many times; value = median")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--prompt", type=int, default=1024)
     ap.add_argument("--layers", type=int, default=32, help="for quick experiments only; the headline uses 32")
@@ -141,26 +150,31 @@ def main():
     W = max(args.warmup, 3)
     K = args.steps
 
-    max_len = args.prompt + K + W + 8
+    R = max(args.repeats, 1)
+    max_len = args.prompt + K + W + 16
     max_len = (max_len + 127) // 128 * 128
     cfg = LlamaConfig.llama3_8b(max_seq_len=max_len, num_layers=args.layers)
-    model, weights = build_llama(cfg, tp_rank=rank, tp_size=tp, external_weights=True, device=str(device))
-    so = ort.SessionOptions()
-    so.add_external_initializers(list(weights.keys()), list(weights.values()))
-    so.add_session_config_entry("ortb200.pdl", str(args.pdl))
-    so.add_session_config_entry("ortb200.decode_attention_algo", str(args.attn_algo))
-    so.add_session_config_entry("ortb200.fused_gqa_prep", str(args.fused_prep))
-    so.add_session_config_entry("ortb200.attention_prefetch", str(args.attn_prefetch))
-    providers = [("CUDAExecutionProvider", {"device_id": str(local), "enable_cuda_graph": "0" if args.no_graph else "1"})]
-    sess = ort.InferenceSession(model, so, providers=providers, dist=info if tp > 1 else None, enable_fallback=False)
-    del weights
-    torch.cuda.empty_cache()
-    if tp > 1 and args.fused_collectives:
-        # peer-mapped workspace: the row-parallel GEMMs of the decode step reduce across ranks inside the kernel
-        from onnxruntime_b200.parallel import symm
-        symm.attach(sess, symm.create_workspace())
-
-    runner = DecoderRunner(sess, cfg, batch=args.batch, max_len=max_len, tp_size=tp, device=device)
+    sess = None
+    if args.impl == "library":
+        from onnxruntime_b200.benchmarks.library_llama import LibraryLlama, count_kernels_of_one_step
+        runner = LibraryLlama(cfg, args.batch, max_len, rank=rank, tp=tp, device=device, use_graph=not args.no_graph)
+    else:
+        model, weights = build_llama(cfg, tp_rank=rank, tp_size=tp, external_weights=True, device=str(device))
+        so = ort.SessionOptions()
+        so.add_external_initializers(list(weights.keys()), list(weights.values()))
+        so.add_session_config_entry("ortb200.pdl", str(args.pdl))
+        so.add_session_config_entry("ortb200.decode_attention_algo", str(args.attn_algo))
+        so.add_session_config_entry("ortb200.fused_gqa_prep", str(args.fused_prep))
+        so.add_session_config_entry("ortb200.attention_prefetch", str(args.attn_prefetch))
+        providers = [("CUDAExecutionProvider", {"device_id": str(local), "enable_cuda_graph": "0" if args.no_graph else "1"})]
+        sess = ort.InferenceSession(model, so, providers=providers, dist=info if tp > 1 else None, enable_fallback=False)
+        del weights
+        torch.cuda.empty_cache()
+        if tp > 1 and args.fused_collectives:
+            # peer-mapped workspace: the row-parallel GEMMs of the decode step reduce across ranks inside the kernel
+            from onnxruntime_b200.parallel import symm
+            symm.attach(sess, symm.create_workspace())
+        runner = DecoderRunner(sess, cfg, batch=args.batch, max_len=max_len, tp_size=tp, device=device)
     gen = torch.Generator().manual_seed(1234)
     prompt = torch.randint(0, cfg.vocab_size, (args.batch, args.prompt), generator=gen)
     prompt_pinned = prompt.pin_memory()
@@ -189,34 +203,49 @@ def main():
         ttft_p50 = t.item()
 
     # ---- decode: warm-up (first call runs eagerly once and captures the CUDA graph)
+    def check():
+        if sess is not None:
+            sess.check_device_status()
+
+    def max_over_ranks(ms: float) -> float:
+        if tp > 1:
+            t = torch.tensor([ms], device=device)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            return t.item()
+        return ms
+
     runner.decode_step(first)
-    launches_per_step = sess.last_run_launch_count()
+    if sess is not None:
+        launches_per_step = sess.last_run_launch_count()
+    else:
+        launches_per_step = count_kernels_of_one_step(runner)
     for _ in range(W - 1):
         runner.decode_step(None)
     sync_all()
-    sess.check_device_status()
+    check()
 
-    # ---- kernel-side number: K steps, next token fed on the device
+    # ---- kernel-side number: R repeats of exactly K steps each, next token fed on the device; value = median repeat
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
         time.sleep(0.3)
-    sync_all()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(K):
-        runner.decode_step(None)
-    e1.record()
-    sync_all()
-    dev_ms = e0.elapsed_time(e1)
+    dev_runs = []
+    start_len = runner.cur_len
+    for _ in range(R):
+        runner.cur_len = start_len  # every repeat decodes the same positions (context prompt + W ... prompt + W + K)
+        sync_all()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(K):
+            runner.decode_step(None)
+        e1.record()
+        sync_all()
+        dev_runs.append(max_over_ranks(e0.elapsed_time(e1)))
     clocks = sampler.stop() if rank == 0 else None
-    if tp > 1:
-        t = torch.tensor([dev_ms], device=device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        dev_ms = t.item()
+    dev_sorted = sorted(dev_runs)
+    dev_ms = dev_sorted[len(dev_sorted) // 2]
 
     # ---- end to end: per step H2D of the inputs from pinned memory, D2H of the sampled tokens, host sync
-    runner.cur_len = args.prompt + 1  # rewind the cache position so both loops see the same lengths
     ids_pinned = torch.zeros(args.batch, 1, dtype=torch.int64).pin_memory()
     ids_pinned.copy_(first_host)
     out_pinned = torch.zeros(args.batch, 1, dtype=torch.int64).pin_memory()
@@ -225,23 +254,25 @@ def main():
     d2h = out_pinned.numel() * 8
     for _ in range(2):
         runner.decode_step_host(ids_pinned, seq_pinned, out_pinned)
-    runner.cur_len = args.prompt + 1
     sync_all()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    t0 = time.perf_counter()
-    e0.record()
-    for _ in range(K):
-        runner.decode_step_host(ids_pinned, seq_pinned, out_pinned)
-        ids_pinned.copy_(out_pinned)
-    e1.record()
-    sync_all()
-    e2e_ms = e0.elapsed_time(e1)
-    wall_ms = (time.perf_counter() - t0) * 1e3
-    if tp > 1:
-        t = torch.tensor([e2e_ms], device=device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_ms = t.item()
-    sess.check_device_status()
+    e2e_runs, wall_runs = [], []
+    for _ in range(min(R, 3)):
+        runner.cur_len = args.prompt + 1  # every repeat sees the same cache lengths as the first device-timed repeat
+        sync_all()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0 = time.perf_counter()
+        e0.record()
+        for _ in range(K):
+            runner.decode_step_host(ids_pinned, seq_pinned, out_pinned)
+            torch.cuda.current_stream().synchronize()  # the tokens have arrived on the host
+            ids_pinned.copy_(out_pinned)
+        e1.record()
+        sync_all()
+        e2e_runs.append(max_over_ranks(e0.elapsed_time(e1)))
+        wall_runs.append((time.perf_counter() - t0) * 1e3)
+    e2e_ms = sorted(e2e_runs)[len(e2e_runs) // 2]
+    wall_ms = sorted(wall_runs)[len(wall_runs) // 2]
+    check()
 
     if rank == 0:
         value = args.batch * K / (dev_ms * 1e-3)
@@ -253,7 +284,7 @@ def main():
             "config": {"model": "Llama-3-8B" if args.layers == 32 else f"Llama-3-8B-shaped/{args.layers}L",
                        "global_batch": args.batch, "seq_len": args.prompt, "decode_tokens": K,
                        "parallelism": f"tp{tp}", "cuda_graph": not args.no_graph,
-                       "collectives": ("in-kernel peer-store all-reduce" if args.fused_collectives else "nccl") if tp > 1 else "none",
+                       "collectives": ("nccl" if (args.impl == "library" or not args.fused_collectives) else "in-kernel peer-store all-reduce") if tp > 1 else "none",
                        "l2": "inputs larger than L2 (every step streams all weights)"},
             "e2e": {"value": round(e2e_value, 2), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": round(e2e_ms / K, 4), "wall_ms_per_step": round(wall_ms / K, 4)},
@@ -262,7 +293,11 @@ def main():
             "ttft_ms_p50": round(ttft_p50, 3),
             "prefill_tokens_per_s": round(args.batch * args.prompt / (ttft_p50 * 1e-3), 1),
             "clocks": clocks,
-            "impl": "ours",
+            "repeats": {"n": R, "ms_per_step_min": round(dev_sorted[0] / K, 4), "ms_per_step_median": round(dev_ms / K, 4),
+                        "ms_per_step_max": round(dev_sorted[-1] / K, 4)},
+            "impl": args.impl,
+            "library_kernels": ({"gemm": "cuBLAS (torch.matmul)", "attention": "flash_attn_with_kvcache" if runner.use_fa else "torch SDPA",
+                                 "all_reduce": "ncclAllReduce"} if args.impl == "library" else None),
         }
         print(json.dumps(out))
     if tp > 1:
