@@ -24,6 +24,9 @@ def main(argv=None) -> int:
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--baseline", default="", choices=["", "torch"])
+    ap.add_argument("--combine", default="fused", choices=["fused", "allreduce"],
+                    help="N > 1: fused = one kernel un-permutes, scales, sums across ranks over peer memory and replicates; "
+                         "allreduce = local combine, then a library all-reduce of the whole output (baseline)")
     a = ap.parse_args(argv)
     rank, world, device, info = setup()
     import onnxruntime_b200 as ort
@@ -88,6 +91,10 @@ def main(argv=None) -> int:
         sess = ort.InferenceSession(ol.make_model(graph).serialize(), so, providers=[("CUDAExecutionProvider", {"device_id": str(device.index)})],
                                     dist=info, enable_fallback=False)
         del fc1, fc2, fc3
+        if world > 1 and a.combine == "fused":
+            from onnxruntime_b200.parallel import symm
+            need = 8 * a.tokens * H * 2 * max(1, (k + world - 1) // world + 1)   # scatter and result areas, two parities
+            symm.attach(sess, symm.create_workspace(max(64 << 20, (need + (1 << 20)) // 256 * 256)))
         out = torch.empty(a.tokens, H, dtype=torch.bfloat16, device=device)
         b = sess.io_binding()
         b.bind_torch_input("x", x)
@@ -99,7 +106,8 @@ def main(argv=None) -> int:
     flops = a.tokens * k * 6 * H * I  # three GEMMs per routed token
     report(rank, metric="mixtral_moe_prefill_tokens_per_s", value=round(a.tokens / (ms * 1e-3), 1), unit="tokens/s", n_gpus=world,
            ms_per_step=round(ms, 3), tflops_total=round(flops / (ms * 1e-3) / 1e12, 1), dtype="bf16", impl=a.baseline or "ours",
-           config={"tokens": a.tokens, "hidden": H, "intermediate": I, "experts": E, "top_k": k, "parallelism": f"ep{world}"},
+           config={"tokens": a.tokens, "hidden": H, "intermediate": I, "experts": E, "top_k": k, "parallelism": f"ep{world}",
+                   "combine": (a.combine if world > 1 and not a.baseline else None)},
            launches_per_step=launches, data="synthetic")
     finish(world)
     return 0

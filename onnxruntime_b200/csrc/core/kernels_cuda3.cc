@@ -544,6 +544,29 @@ class MoeKernel final : public WithFallback {
     g.w_rows_per_expert = static_cast<int>(H_); g.dual_offset = 0; g.act = ORTB200_ACT_NONE;
     CheckLaunch(ortb200_gemm_grouped(&g, ctx.cuda_stream()), "ortb200_gemm_grouped(fc2)");
     at::Tensor out = at::empty({T, H_}, x.options());
+    InferenceSession* sess = ctx.session();
+    if (sharded_ && sess->world_size > 1 && static_cast<int>(sess->symm_peers.size()) == sess->world_size &&
+        sess->config().Get("ortb200.fused_moe_combine", "1") == "1" && E == E_local_ * sess->world_size &&
+        start_ == sess->rank * E_local_ &&
+        T <= ortb200_moe_combine_symm_max_tokens(sess->world_size, static_cast<int>(k), static_cast<int>(H_), sess->symm_bytes)) {
+      // expert parallelism: un-permute, scale, sum across ranks and replicate in one kernel over peer memory
+      ortb200_moe_combine_symm_args ca{};
+      ca.y = y.data_ptr();
+      ca.bias = fc2_bias.defined() ? fc2_bias.data_ptr() : nullptr;
+      ca.out = out.data_ptr();
+      ca.topk_idx = topk_idx.data_ptr<int>(); ca.topk_w = topk_w.data_ptr<float>(); ca.row_of = row_of.data_ptr<int>();
+      ca.T = static_cast<int>(T); ca.H = static_cast<int>(H_); ca.k = static_cast<int>(k);
+      ca.E_local = static_cast<int>(E_local_); ca.expert_begin = static_cast<int>(start_);
+      ca.dtype = dt;
+      ca.world = sess->world_size; ca.rank = sess->rank;
+      for (int i = 0; i < sess->world_size && i < 8; ++i) ca.peers[i] = sess->symm_peers[i];
+      ca.symm_bytes = sess->symm_bytes;
+      ca.status = sess->StatusWord().data_ptr<int>();
+      CheckLaunch(ortb200_moe_combine_symm(&ca, ctx.cuda_stream()), "ortb200_moe_combine_symm");
+      sess->AddLaunches(6);
+      ctx.SetOutput(0, out.reshape(x.sizes()));
+      return;
+    }
     CheckLaunch(ortb200_moe_combine(y.data_ptr(), fc2_bias.defined() ? fc2_bias.data_ptr() : nullptr, out.data_ptr(), static_cast<int>(T),
                                     static_cast<int>(H_), static_cast<int>(k), static_cast<int>(start_), topk_idx.data_ptr<int>(),
                                     topk_w.data_ptr<float>(), row_of.data_ptr<int>(), dt, ctx.cuda_stream()),

@@ -185,10 +185,185 @@ __global__ void __launch_bounds__(256) symm_collective_kernel(const CollParams p
   }
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// Expert-parallel mixture of experts: un-permute + routing-weight scale + cross-rank sum + replication in one kernel.
+//
+// Every rank has run its local experts on the (replicated) tokens routed to them; y holds those expert outputs in
+// permuted order.  Token t is owned by rank t / T_own.  Step 1: each rank adds up ITS experts' weighted rows of token t
+// and stores that one row straight into the owner's scatter area (slot = position of the rank's first expert in the
+// token's top-k list, so no two ranks share a slot and nobody needs a count).  Step 2: the owner adds the slots of the
+// token in top-k order and stores the finished row into every rank's result area.  Step 3: copy out.  CTA b handles
+// the tokens t = b (mod grid) on every rank, so the two flag exchanges between namesake CTAs are the only
+// synchronisation.  Per GPU this moves (routed rows / world) * 7/8 rows out in step 1 and its token shard to 7 peers in
+// step 2, against a broadcast of every permuted row in the reference
+// (onnxruntime/contrib_ops/cuda/collective/sharded_moe.cc:159-176).
+struct MoeCombineParams {
+  CollParams c;             // world, rank, peers, half_bytes, region_offset, status (op / in / out unused)
+  const void* y;            // [rows, H] expert outputs of this rank, permuted order
+  const void* bias;         // optional [E_local, H]
+  void* out;                // [T, H]
+  const int* topk_idx;      // [T, k] global expert ids
+  const float* topk_w;      // [T, k]
+  const int* row_of;        // [T, k] row of y, or -1 when the expert lives on another rank
+  int T, H, k, E_local, expert_begin, T_own;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256) moe_combine_symm_kernel(const MoeCombineParams p) {
+  pdl_wait_prior_grids();
+  const CollParams& c = p.c;
+  unsigned int* hdr = reinterpret_cast<unsigned int*>(static_cast<uint8_t*>(c.peers[c.rank]) + 64);
+  const unsigned int epoch = *reinterpret_cast<volatile unsigned int*>(hdr) + 1;
+  const long long half_off = c.region_offset + static_cast<long long>(epoch & 1) * c.half_bytes;
+  const long long scatter_vecs = c.half_bytes / 32;
+  auto scatter_of = [&](int r) { return reinterpret_cast<uint4*>(static_cast<uint8_t*>(c.peers[r]) + half_off); };
+  auto result_of = [&](int r) { return scatter_of(r) + scatter_vecs; };
+  constexpr int EPV = 16 / static_cast<int>(sizeof(T));  // elements per 16-byte vector
+  const int hvecs = p.H / EPV;
+  const T* y = static_cast<const T*>(p.y);
+  const T* bias = static_cast<const T*>(p.bias);
+
+  // ---- step 1: this rank's share of every token of this CTA, pushed to the token's owner
+  for (int t = blockIdx.x; t < p.T; t += gridDim.x) {
+    int slot = -1;
+    for (int j = 0; j < p.k; ++j)
+      if (p.row_of[t * p.k + j] >= 0) {
+        slot = j;
+        break;
+      }
+    if (slot < 0) continue;  // none of this token's experts live here
+    const int owner = t / p.T_own, tl = t - owner * p.T_own;
+    uint4* dst = scatter_of(owner) + (static_cast<long long>(tl) * p.k + slot) * hvecs;
+    for (int hv = threadIdx.x; hv < hvecs; hv += blockDim.x) {
+      float acc[EPV];
+#pragma unroll
+      for (int e = 0; e < EPV; ++e) acc[e] = 0.f;
+      for (int j = slot; j < p.k; ++j) {
+        const int row = p.row_of[t * p.k + j];
+        if (row < 0) continue;
+        const float w = p.topk_w[t * p.k + j];
+        const uint4 v = __ldg(reinterpret_cast<const uint4*>(y + static_cast<long long>(row) * p.H) + hv);
+        const T* ve = reinterpret_cast<const T*>(&v);
+        if (bias) {
+          const uint4 bv = __ldg(reinterpret_cast<const uint4*>(bias + static_cast<long long>(p.topk_idx[t * p.k + j] - p.expert_begin) * p.H) + hv);
+          const T* be = reinterpret_cast<const T*>(&bv);
+#pragma unroll
+          for (int e = 0; e < EPV; ++e) acc[e] += w * (to_float<T>(ve[e]) + to_float<T>(be[e]));
+        } else {
+#pragma unroll
+          for (int e = 0; e < EPV; ++e) acc[e] += w * to_float<T>(ve[e]);
+        }
+      }
+      uint4 o;
+      T* oe = reinterpret_cast<T*>(&o);
+#pragma unroll
+      for (int e = 0; e < EPV; ++e) oe[e] = from_float<T>(acc[e]);
+      dst[hv] = o;
+    }
+  }
+  bool ok = cta_exchange_flags(c, 2 * epoch + 1);
+
+  // ---- step 2: the owner adds the slots of its tokens in top-k order and replicates the row
+  for (int t = blockIdx.x; t < p.T; t += gridDim.x) {
+    if (t / p.T_own != c.rank) continue;
+    const int tl = t - c.rank * p.T_own;
+    const uint4* src = scatter_of(c.rank) + static_cast<long long>(tl) * p.k * hvecs;
+    // slot j carries data when expert j's rank does not already appear earlier in the list
+    unsigned int use = 0;
+    for (int j = 0; j < p.k; ++j) {
+      const int rj = p.topk_idx[t * p.k + j] / p.E_local;
+      bool first = true;
+      for (int i = 0; i < j; ++i) first = first && (p.topk_idx[t * p.k + i] / p.E_local != rj);
+      if (first) use |= 1u << j;
+    }
+    for (int hv = threadIdx.x; hv < hvecs; hv += blockDim.x) {
+      float acc[EPV];
+#pragma unroll
+      for (int e = 0; e < EPV; ++e) acc[e] = 0.f;
+      for (int j = 0; j < p.k; ++j) {
+        if (!((use >> j) & 1u)) continue;
+        const uint4 v = __ldcg(src + static_cast<long long>(j) * hvecs + hv);
+        const T* ve = reinterpret_cast<const T*>(&v);
+#pragma unroll
+        for (int e = 0; e < EPV; ++e) acc[e] += to_float<T>(ve[e]);
+      }
+      uint4 o;
+      T* oe = reinterpret_cast<T*>(&o);
+#pragma unroll
+      for (int e = 0; e < EPV; ++e) oe[e] = from_float<T>(acc[e]);
+      const long long idx = static_cast<long long>(t) * hvecs + hv;
+      for (int d = 0; d < c.world; ++d) result_of((c.rank + d) % c.world)[idx] = o;
+    }
+  }
+  ok = cta_exchange_flags(c, 2 * epoch + 2) && ok;
+
+  // ---- step 3: copy this CTA's tokens out of the local result area
+  const uint4* res = result_of(c.rank);
+  uint4* out = static_cast<uint4*>(p.out);
+  for (int t = blockIdx.x; t < p.T; t += gridDim.x)
+    for (int hv = threadIdx.x; hv < hvecs; hv += blockDim.x) out[static_cast<long long>(t) * hvecs + hv] = __ldcg(res + static_cast<long long>(t) * hvecs + hv);
+  (void)ok;
+  pdl_launch_dependents();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    if (atomicAdd(hdr + 1, 1u) == gridDim.x - 1) {
+      hdr[1] = 0;
+      __threadfence();
+      *reinterpret_cast<volatile unsigned int*>(hdr) = epoch;
+    }
+  }
+}
+
 }  // namespace
 }  // namespace ortb200
 
 using namespace ortb200;
+
+extern "C" int ortb200_moe_combine_symm(const ortb200_moe_combine_symm_args* a, ortb200_stream_t stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (!a || !a->y || !a->out || !a->topk_idx || !a->topk_w || !a->row_of) return -1;
+  if (a->world < 2 || a->world > 8 || a->rank < 0 || a->rank >= a->world || a->T <= 0 || a->H <= 0 || a->k <= 0 || a->k > 8 || a->E_local <= 0) return -1;
+  if (a->dtype != ORTB200_BF16 && a->dtype != ORTB200_F16) return -4;
+  if (a->H % 8 != 0) return -3;
+  if ((reinterpret_cast<uintptr_t>(a->y) | reinterpret_cast<uintptr_t>(a->out) | reinterpret_cast<uintptr_t>(a->bias)) & 15) return -3;
+  if (a->symm_bytes < (1 << 20) || (a->symm_bytes % 256) != 0) return -3;
+  for (int i = 0; i < a->world; ++i)
+    if (!a->peers[i]) return -1;
+  MoeCombineParams p{};
+  p.c.world = a->world; p.c.rank = a->rank;
+  for (int i = 0; i < 8; ++i) p.c.peers[i] = i < a->world ? a->peers[i] : nullptr;
+  p.c.region_offset = a->symm_bytes / 2;
+  p.c.half_bytes = a->symm_bytes / 4;
+  p.c.status = a->status;
+  p.y = a->y; p.bias = a->bias; p.out = a->out; p.topk_idx = a->topk_idx; p.topk_w = a->topk_w; p.row_of = a->row_of;
+  p.T = a->T; p.H = a->H; p.k = a->k; p.E_local = a->E_local; p.expert_begin = a->expert_begin;
+  p.T_own = (a->T + a->world - 1) / a->world;
+  const long long area = p.c.half_bytes / 2;  // scatter area == result area
+  if (static_cast<long long>(p.T_own) * a->k * a->H * 2 > area || static_cast<long long>(a->T) * a->H * 2 > area) return -13;
+  int ctas = a->T < 2 * 148 ? a->T : 2 * 148;  // all CTAs resident at once: a CTA waits for its namesakes on the other ranks
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(ctas));
+  cfg.blockDim = dim3(256);
+  cfg.stream = stream;
+  cudaLaunchAttribute attrs[1];
+  if (a->use_pdl) {
+    attrs[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attrs;
+    cfg.numAttrs = 1;
+  }
+  cudaError_t e;
+  if (a->dtype == ORTB200_BF16) e = cudaLaunchKernelEx(&cfg, moe_combine_symm_kernel<__nv_bfloat16>, p);
+  else e = cudaLaunchKernelEx(&cfg, moe_combine_symm_kernel<__half>, p);
+  return e == cudaSuccess ? 0 : -11;
+}
+
+extern "C" int64_t ortb200_moe_combine_symm_max_tokens(int world, int k, int H, int64_t symm_bytes) {
+  const int64_t area = symm_bytes / 8;
+  const int64_t by_result = area / (static_cast<int64_t>(H) * 2);
+  const int64_t by_scatter = area / (static_cast<int64_t>(H) * 2 * k) * world - world;  // T_own is rounded up
+  return by_result < by_scatter ? by_result : by_scatter;
+}
 
 extern "C" int64_t ortb200_symm_collective_max_bytes(int op, int world, int64_t symm_bytes) {
   // one parity half = symm_bytes / 4; its scatter and result areas are half of that each

@@ -412,6 +412,29 @@ typedef struct {
 int ortb200_symm_collective(const ortb200_symm_collective_args* args, ortb200_stream_t stream);
 int64_t ortb200_symm_collective_max_bytes(int op, int world, int64_t symm_bytes);
 
+// Expert-parallel MoE, last step, as one kernel over the symmetric workspace (same layout and epoch word as
+// ortb200_symm_collective): out[t] = sum over the token's top-k experts of topk_w * (expert output + bias), where every
+// rank holds only the outputs of its own experts (row_of < 0 elsewhere).  Each rank pushes one pre-summed row per token
+// to the token's owner rank, the owner adds them in top-k order and stores the finished row into every rank's copy,
+// so all ranks end with the full [T, H] result.  Experts are dealt to ranks in equal blocks of E_local.
+typedef struct {
+  const void* y;          // [rows, H] outputs of this rank's experts (permuted order)
+  const void* bias;       // optional [E_local, H]
+  void* out;              // [T, H]
+  const int* topk_idx;    // [T, k] global expert ids (identical on every rank)
+  const float* topk_w;    // [T, k]
+  const int* row_of;      // [T, k] row of y, -1 when the expert is not local
+  int T, H, k, E_local, expert_begin;
+  int dtype;              // F16 or BF16
+  int world, rank;
+  void* peers[8];
+  int64_t symm_bytes;
+  int* status;
+  int use_pdl;
+} ortb200_moe_combine_symm_args;
+int ortb200_moe_combine_symm(const ortb200_moe_combine_symm_args* args, ortb200_stream_t stream);
+int64_t ortb200_moe_combine_symm_max_tokens(int world, int k, int H, int64_t symm_bytes);
+
 // Re-arranges MatMulNBits 4-bit weights for the in-kernel expansion: within every 32-bit word (8 weights, low nibble
 // = even k) weight 2i moves to bits [4i, 4i+4) and weight 2i+1 to bits [16+4i, 16+4i+4).  B and out are N * K / 2
 // bytes; they may not alias.

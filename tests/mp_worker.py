@@ -86,13 +86,54 @@ def case_sharded_moe(info, device, out):
     torch.save({"y": torch.from_numpy(y), "ref": torch.from_numpy(ref)}, os.path.join(out, f"rank{r}.pt"))
 
 
+def case_sharded_moe_gpu(info, device, out):
+    """ShardedMoE in fp16 on GPUs, with the fused cross-rank combine (symmetric workspace) and with the library all-reduce,
+    against the single-device MoE on the full expert set (the design of the reference's own parity test,
+    onnxruntime/test/python/transformers/sharded_moe/test_sharded_moe.py:221-336)."""
+    from onnxruntime_b200.parallel import symm
+    r, w = info.rank, info.world_size
+    rng = np.random.RandomState(0)
+    res = {}
+    ws = symm.create_workspace(64 << 20)
+    for case, (Tn, H, I, E, k) in enumerate([(64, 128, 512, 4 * w, 2), (1024, 1024, 512, 8 * w, 2), (37, 256, 256, 2 * w, 3)]):
+        x = (rng.randn(Tn, H) * 0.5).astype(np.float16)
+        # every row a permutation of distinct values: no ties, so the top-k choice cannot depend on a tie rule
+        logits = np.stack([rng.permutation(np.linspace(-2.0, 2.0, E)) for _ in range(Tn)]).astype(np.float16)
+        fc1, fc2, fc3 = [(rng.randn(*s) * 0.05).astype(np.float16) for s in ((E, H, I), (E, I, H), (E, H, I))]
+        el = E // w
+        sl = slice(r * el, (r + 1) * el)
+        g = ol.make_graph([ol.make_node("ShardedMoE", ["x", "p", "fc1", "", "fc2", "", "fc3"], ["y"], domain="com.microsoft", k=k,
+                                        activation_type="silu", normalize_routing_weights=1, local_experts_start_index=r * el)], "g",
+                          [ol.make_tensor_value_info("x", T.FLOAT16, [Tn, H]), ol.make_tensor_value_info("p", T.FLOAT16, [Tn, E])],
+                          [ol.make_tensor_value_info("y", T.FLOAT16, None)],
+                          [ol.make_tensor("fc1", fc1[sl]), ol.make_tensor("fc2", fc2[sl]), ol.make_tensor("fc3", fc3[sl])])
+        model = ol.make_model(g).serialize()
+        fused = session(model, info, device)
+        symm.attach(fused, ws)
+        ys = [fused.run(None, {"x": x, "p": logits})[0] for _ in range(3)]  # both parities of the staging areas
+        fused.check_device_status()
+        plain = session(model, info, device)
+        yp = plain.run(None, {"x": x, "p": logits})[0]
+        g2 = ol.make_graph([ol.make_node("MoE", ["x", "p", "fc1", "", "fc2", "", "fc3"], ["y"], domain="com.microsoft", k=k,
+                                         activation_type="silu", normalize_routing_weights=1)], "g",
+                           [ol.make_tensor_value_info("x", T.FLOAT, [Tn, H]), ol.make_tensor_value_info("p", T.FLOAT, [Tn, E])],
+                           [ol.make_tensor_value_info("y", T.FLOAT, None)],
+                           [ol.make_tensor("fc1", fc1.transpose(0, 2, 1).astype(np.float32)), ol.make_tensor("fc2", fc2.transpose(0, 2, 1).astype(np.float32)),
+                            ol.make_tensor("fc3", fc3.transpose(0, 2, 1).astype(np.float32))])
+        ref = ort.InferenceSession(ol.make_model(g2).serialize(), providers=["CPUExecutionProvider"]).run(
+            None, {"x": x.astype(np.float32), "p": logits.astype(np.float32)})[0]
+        res[f"case{case}"] = {"fused": torch.from_numpy(ys[-1].astype(np.float32)), "plain": torch.from_numpy(yp.astype(np.float32)),
+                              "ref": torch.from_numpy(ref), "stable": all(np.array_equal(ys[0], y) for y in ys[1:])}
+    torch.save(res, os.path.join(out, f"rank{r}.pt"))
+
+
 def case_llama_tp(info, device, out):
     from onnxruntime_b200.models.generation import DecoderRunner
     from onnxruntime_b200.models.llama import LlamaConfig, build_llama
     r, w = info.rank, info.world_size
     dtype = "fp32" if device == "cpu" else "bf16"
-    cfg = LlamaConfig.tiny(dtype=dtype, head_dim=64, hidden_size=256, ffn_size=512, num_layers=2, num_heads=8, num_kv_heads=4,
-                           max_seq_len=128)
+    cfg = LlamaConfig.tiny(dtype=dtype, head_dim=64, hidden_size=256, ffn_size=512, num_layers=2, num_heads=max(8, w),
+                           num_kv_heads=max(4, w), max_seq_len=128)
     quant = int(os.environ.get("ORTB200_TEST_QUANT", "0"))
     model, _ = build_llama(cfg, tp_rank=r, tp_size=w, weight_std=0.05, quant_bits=quant)
     opts = {}

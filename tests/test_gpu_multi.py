@@ -11,9 +11,17 @@ def _ngpu():
     return torch.cuda.device_count() if torch.cuda.is_available() else 0
 
 
-@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
-def test_fused_gemm_allreduce_kernel(tmp_path):
-    n = 2
+WORLDS = [2, 4, 8]
+
+
+def _need(n):
+    if _ngpu() < n:
+        pytest.skip(f"needs {n} GPUs")
+
+
+@pytest.mark.parametrize("n", WORLDS)
+def test_fused_gemm_allreduce_kernel(tmp_path, n):
+    _need(n)
     out = launch("gemm_allreduce", "cuda", n, tmp_path)
     for r in range(n):
         assert out[r]["status"] == 0
@@ -22,26 +30,45 @@ def test_fused_gemm_allreduce_kernel(tmp_path):
                 assert v["err"] < 1e-2 and v["stable"], (r, k, v["err"], v["stable"])
     for k in out[0]:
         if k.startswith("case"):
-            assert torch.equal(out[0][k]["out"], out[1][k]["out"])  # every rank holds the same reduced result
+            for r in range(1, n):
+                assert torch.equal(out[0][k]["out"], out[r][k]["out"])  # every rank holds the same reduced result
 
 
-@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+@pytest.mark.parametrize("n", WORLDS)
 @pytest.mark.parametrize("fused", ["1", "0"])
-def test_llama_tp2_gpu(tmp_path, fused):
-    out = launch("llama_tp", "cuda", 2, tmp_path, extra_env={"ORTB200_TEST_FUSED": fused})
+def test_llama_tp_gpu(tmp_path, fused, n):
+    _need(n)
+    out = launch("llama_tp", "cuda", n, tmp_path, extra_env={"ORTB200_TEST_FUSED": fused})
     assert out[0]["fused"] == (fused == "1")
-    a, b, ref = out[0]["logits"], out[1]["logits"], out[0]["ref"]
-    assert (a - b).abs().max() / a.abs().max() < 1e-6
+    a, ref = out[0]["logits"], out[0]["ref"]
+    for r in range(1, n):
+        assert (a - out[r]["logits"]).abs().max() / a.abs().max() < 1e-6
     assert (a - ref).abs().max() / ref.abs().max() < 0.06
 
 
-@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
-def test_symmetric_memory_collectives(tmp_path):
-    out = launch("symm_collectives", "cuda", 2, tmp_path)
-    for r in range(2):
+@pytest.mark.parametrize("n", WORLDS)
+def test_symmetric_memory_collectives(tmp_path, n):
+    _need(n)
+    out = launch("symm_collectives", "cuda", n, tmp_path)
+    for r in range(n):
         assert out[r]["status"] == 0
         for k, v in out[r].items():
             if k.startswith("ar_"):
                 assert v < 1e-2, (r, k, v)
             elif k.startswith("ag_") or k.startswith("a2a_"):
                 assert v is True, (r, k)
+
+
+@pytest.mark.parametrize("n", WORLDS)
+def test_sharded_moe_fused_combine(tmp_path, n):
+    """Expert parallelism with the one-kernel cross-rank combine: every rank ends with the single-device MoE result."""
+    _need(n)
+    out = launch("sharded_moe_gpu", "cuda", n, tmp_path)
+    for k in out[0]:
+        ref = out[0][k]["ref"]
+        scale = ref.abs().max()
+        for r in range(n):
+            assert out[r][k]["stable"]
+            assert (out[r][k]["fused"] - ref).abs().max() / scale < 3e-2, (r, k)
+            assert (out[r][k]["plain"] - ref).abs().max() / scale < 3e-2, (r, k)
+            assert torch.equal(out[r][k]["fused"], out[0][k]["fused"])  # replicated bit for bit
