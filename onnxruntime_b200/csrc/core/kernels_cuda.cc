@@ -92,7 +92,7 @@ at::Tensor LaunchGemm(Ctx& ctx, const at::Tensor& x2d, const at::Tensor& w_nk, i
     a.symm_bytes = s->symm_bytes;
   }
   CheckLaunch(ortb200_gemm(&a, ctx.cuda_stream()), "ortb200_gemm");
-  s->AddLaunches(1);
+  s->AddLaunches(fused_allreduce && M > 64 ? 2 : 1);
   return out;
 }
 
@@ -198,7 +198,10 @@ bool CanFuseAllReduce(OpKernelContext& ctx, int64_t M, int64_t N) {
   if (!s || s->world_size <= 1 || s->world_size > 8) return false;
   if (static_cast<int>(s->symm_peers.size()) != s->world_size) return false;
   if (s->config().Get("ortb200.fused_allreduce", "1") != "1") return false;
-  if (M > 64) return false;
+  if (M > 64) {
+    // prompt-sized: the CTA-pair GEMM pushes its product into the all-reduce scatter areas, a reduction kernel follows
+    return N % 8 == 0 && M * N * 2 <= ortb200_symm_collective_max_bytes(ORTB200_COLL_ALLREDUCE, s->world_size, s->symm_bytes);
+  }
   const int64_t slot = (s->symm_bytes / 2 - 262144) / (2LL * s->world_size * 8);
   return slot >= M * N && (N + 127) / 128 * 8 <= 4096;
 }

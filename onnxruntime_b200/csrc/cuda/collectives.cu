@@ -15,6 +15,7 @@
 //   [64 KiB, 256 KiB)      flags[src rank < 8][CTA < 4096] uint32
 //   [bytes / 2, bytes)     two halves used alternately by epoch parity; each half = [scatter area | result area]
 #include <cuda_runtime.h>
+#include "gemm_internal.h"
 #include "ortb200_kernels.h"
 #include "ptx_sm100.cuh"
 
@@ -48,6 +49,12 @@ struct CollParams {
   long long total_vecs;   // all-reduce: vectors in the whole tensor
   int dtype;
   int* status;
+  // all-reduce that finishes a tensor-parallel GEMM: the scatter areas were filled by the GEMM's epilogue
+  // (prescattered), and residual [M, N] (row pitch ldr elements, N = row_elems) is added to the sums
+  int prescattered;
+  const void* residual;
+  long long ldr;
+  int row_elems;
 };
 
 // CTA-wide: tell every rank that this CTA's stores for `value` are done, then wait for the same CTA of every rank.
@@ -87,11 +94,12 @@ __device__ __forceinline__ void add_vec(float* acc, const uint4& v) {
   for (int i = 0; i < 16 / static_cast<int>(sizeof(T)); ++i) acc[i] += to_float<T>(e[i]);
 }
 template <typename T>
-__device__ __forceinline__ uint4 sum_vecs(const uint4* const* src, int world, long long idx) {
+__device__ __forceinline__ uint4 sum_vecs(const uint4* const* src, int world, long long idx, const uint4* residual = nullptr) {
   float acc[16 / sizeof(T)];
 #pragma unroll
   for (int i = 0; i < 16 / static_cast<int>(sizeof(T)); ++i) acc[i] = 0.f;
   for (int s = 0; s < world; ++s) add_vec<T>(acc, __ldcg(src[s] + idx));  // rank order: same bits on every rank
+  if (residual) add_vec<T>(acc, __ldg(residual));
   uint4 r;
   T* e = reinterpret_cast<T*>(&r);
 #pragma unroll
@@ -146,12 +154,14 @@ __global__ void __launch_bounds__(256) symm_collective_kernel(const CollParams p
   } else {
     // all-reduce in two steps: slice d of every rank's input is pushed to rank d (scatter[src rank][row_vecs]),
     // rank d adds the slices in rank order and pushes the sums to everyone's result area, everyone copies out
-    for (long long i = t0; i < p.row_vecs; i += stride)
-      for (int d = 0; d < p.world; ++d) {
-        const int dst = (p.rank + d) % p.world;
-        const long long g = static_cast<long long>(dst) * p.row_vecs + i;
-        if (g < p.total_vecs) scatter_of(dst)[static_cast<long long>(p.rank) * p.row_vecs + i] = p.in[g];
-      }
+    if (!p.prescattered) {
+      for (long long i = t0; i < p.row_vecs; i += stride)
+        for (int d = 0; d < p.world; ++d) {
+          const int dst = (p.rank + d) % p.world;
+          const long long g = static_cast<long long>(dst) * p.row_vecs + i;
+          if (g < p.total_vecs) scatter_of(dst)[static_cast<long long>(p.rank) * p.row_vecs + i] = p.in[g];
+        }
+    }
     ok = cta_exchange_flags(p, 2 * epoch + 1);
     const uint4* src[8];
     for (int s = 0; s < p.world; ++s) src[s] = scatter_of(p.rank) + static_cast<long long>(s) * p.row_vecs;
@@ -159,8 +169,14 @@ __global__ void __launch_bounds__(256) symm_collective_kernel(const CollParams p
       const long long g = static_cast<long long>(p.rank) * p.row_vecs + i;
       if (g >= p.total_vecs) continue;
       uint4 r;
-      if (p.dtype == ORTB200_BF16) r = sum_vecs<__nv_bfloat16>(src, p.world, i);
-      else if (p.dtype == ORTB200_F16) r = sum_vecs<__half>(src, p.world, i);
+      const uint4* res_vec = nullptr;
+      if (p.residual) {
+        const long long el = g * 8;  // 16-bit types only
+        const long long m = el / p.row_elems, n = el - m * p.row_elems;
+        res_vec = reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(p.residual) + m * p.ldr + n);
+      }
+      if (p.dtype == ORTB200_BF16) r = sum_vecs<__nv_bfloat16>(src, p.world, i, res_vec);
+      else if (p.dtype == ORTB200_F16) r = sum_vecs<__half>(src, p.world, i, res_vec);
       else r = sum_vecs<float>(src, p.world, i);
       for (int d = 0; d < p.world; ++d) result_of((p.rank + d) % p.world)[g] = r;
     }
@@ -319,6 +335,35 @@ __global__ void __launch_bounds__(256) moe_combine_symm_kernel(const MoeCombineP
 
 using namespace ortb200;
 
+namespace ortb200 {
+int launch_allreduce_prescattered(const ortb200_gemm_args* a, cudaStream_t stream) {
+  if (a->world < 2 || a->world > 8 || !a->out || a->ldo != a->N || a->N % 8 != 0) return -12;
+  if (a->residual && ((a->ldr % 8) != 0 || (reinterpret_cast<uintptr_t>(a->residual) & 15))) return -3;
+  if (reinterpret_cast<uintptr_t>(a->out) & 15) return -3;
+  CollParams p;
+  p.op = ORTB200_COLL_ALLREDUCE; p.world = a->world; p.rank = a->rank;
+  for (int i = 0; i < 8; ++i) p.peers[i] = i < a->world ? a->peers[i] : nullptr;
+  p.region_offset = a->symm_bytes / 2;
+  p.half_bytes = a->symm_bytes / 4;
+  p.in = nullptr;
+  p.out = static_cast<uint4*>(a->out);
+  p.dtype = a->dtype;
+  p.status = a->status;
+  p.rows = 1;
+  p.total_vecs = static_cast<long long>(a->M) * a->N / 8;
+  p.row_vecs = (p.total_vecs + a->world - 1) / a->world;
+  p.prescattered = 1; p.residual = a->residual; p.ldr = a->ldr; p.row_elems = a->N;
+  long long ctas = (p.row_vecs + 255) / 256;
+  if (ctas > 2 * 148) ctas = 2 * 148;
+  if (ctas < 1) ctas = 1;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(ctas));
+  cfg.blockDim = dim3(256);
+  cfg.stream = stream;
+  return cudaLaunchKernelEx(&cfg, symm_collective_kernel, p) == cudaSuccess ? 0 : -11;
+}
+}  // namespace ortb200
+
 extern "C" int ortb200_moe_combine_symm(const ortb200_moe_combine_symm_args* a, ortb200_stream_t stream_) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   if (!a || !a->y || !a->out || !a->topk_idx || !a->topk_w || !a->row_of) return -1;
@@ -390,6 +435,7 @@ extern "C" int ortb200_symm_collective(const ortb200_symm_collective_args* a, or
   p.dtype = a->dtype;
   p.status = a->status;
   p.rows = 1; p.row_vecs = 0; p.total_vecs = 0;
+  p.prescattered = 0; p.residual = nullptr; p.ldr = 0; p.row_elems = 0;
   const int64_t limit = ortb200_symm_collective_max_bytes(a->op, a->world, a->symm_bytes);
   long long work_vecs = 0;
   if (a->op == ORTB200_COLL_ALLGATHER) {

@@ -51,6 +51,12 @@ struct Gemm2Params {
   const int* num_tiles;
   int tiles_n;             // 256-row weight tiles per expert
   int w_rows_per_expert;
+  // tensor parallelism (world > 1): the epilogue pushes the product into the all-reduce scatter areas of the symmetric
+  // workspace instead of `out` (see scatter_pass); the reduction kernel that follows finishes the sum
+  int world, rank;
+  void* peers[8];
+  long long region_offset, half_bytes;
+  unsigned int row_vecs;
 };
 
 struct Smem2 {
@@ -111,6 +117,21 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster_addr) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster_addr) : "memory");
 }
 
+
+// Where this launch's products go when the GEMM feeds an all-reduce: the scatter area of the parity that the reduction
+// kernel launched right after this one will use (it reads the same epoch word; the previous reduction has completed).
+__device__ __forceinline__ ScatterArgs make_scatter_args(const Gemm2Params& p) {
+  ScatterArgs sc{};
+  if (p.world > 1) {
+    const unsigned int epoch = *reinterpret_cast<volatile unsigned int*>(static_cast<uint8_t*>(p.peers[p.rank]) + 64) + 1;
+    for (int i = 0; i < 8; ++i) sc.peers[i] = p.peers[i];
+    sc.area_offset = p.region_offset + static_cast<long long>(epoch & 1) * p.half_bytes;
+    sc.row_vecs = p.row_vecs;
+    sc.rank = p.rank;
+    sc.N = p.N;
+  }
+  return sc;
+}
 
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x, const Gemm2Params p) {
@@ -231,6 +252,7 @@ gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
     const bool vec_ok = (p.ldo % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0) &&
                         (p.residual == nullptr || ((p.ldr % 8 == 0) && (reinterpret_cast<uintptr_t>(p.residual) & 15) == 0));
     const StoreArgs sa{p.out, p.residual, p.ldo, p.ldr, p.N};
+    const ScatterArgs sc = make_scatter_args(p);
     for (int t = pair; t < tiles; t += num_pairs) {
       const int nrow0 = (t / tiles_m) * (2 * kBM) + static_cast<int>(rank) * kBM;
       int m0 = (t % tiles_m) * kBN, m_end = p.M;
@@ -242,7 +264,9 @@ gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
 #pragma unroll 1
       for (int pc = 0; pc < kBN; pc += 128) {
         asm volatile("bar.sync 1, 256;" ::: "memory");   // the pass is staged
-        if (p.act == ORTB200_ACT_NONE) {
+        if (p.world > 1) {
+          scatter_pass<kStoreThreads>(sc, stg, 128, et, m0 + pc, m_end, nrow0);
+        } else if (p.act == ORTB200_ACT_NONE) {
           if (bf16) store_pass<true, ORTB200_ACT_NONE, kStoreThreads>(sa, stg, 128, et, m0 + pc, m_end, nrow0, vec_ok);
           else store_pass<false, ORTB200_ACT_NONE, kStoreThreads>(sa, stg, 128, et, m0 + pc, m_end, nrow0, vec_ok);
         } else if (bf16) {
@@ -263,6 +287,7 @@ gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
     const bool vec_ok = (p.ldo % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0) &&
                         (p.residual == nullptr || ((p.ldr % 8 == 0) && (reinterpret_cast<uintptr_t>(p.residual) & 15) == 0));
     const StoreArgs sa{p.out, p.residual, p.ldo, p.ldr, p.N};
+    const ScatterArgs sc = make_scatter_args(p);
     const uint32_t empty_remote0 = map_to_rank(smem_u32(&tmem_empty_bar[0]), 0);
     const uint32_t empty_remote1 = map_to_rank(smem_u32(&tmem_empty_bar[1]), 0);
     int seg = 0;
@@ -318,7 +343,9 @@ gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         // activation and type are compile-time constants inside the loop (a runtime switch per element tripled its
         // instruction count: 11 M -> 27 M warp instructions for a plain ReLU on 8192 x 4096 x 1024)
         // (the plain path stays inline: an out-of-line call cost it a quarter of its speed)
-        if (p.act == ORTB200_ACT_NONE) {
+        if (p.world > 1) {
+          scatter_pass<kStoreThreads>(sc, stg, 128, et, m0 + pc, m_end, nrow0);
+        } else if (p.act == ORTB200_ACT_NONE) {
           if (bf16) store_pass<true, ORTB200_ACT_NONE, kStoreThreads>(sa, stg, 128, et, m0 + pc, m_end, nrow0, vec_ok);
           else store_pass<false, ORTB200_ACT_NONE, kStoreThreads>(sa, stg, 128, et, m0 + pc, m_end, nrow0, vec_ok);
         } else if (bf16) {
@@ -344,7 +371,8 @@ gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
 }  // namespace
 
 int launch_gemm_2cta(const ortb200_gemm_args* a, cudaStream_t stream) {
-  if (a->act == ORTB200_ACT_SWIGLU || a->in_dtype != 0 || a->world > 1 || a->rms_eps > 0.f) return -16;
+  if (a->act == ORTB200_ACT_SWIGLU || a->in_dtype != 0 || a->rms_eps > 0.f) return -16;
+  if (a->world > 1 && (a->act != ORTB200_ACT_NONE || a->ldo != a->N || a->N % 8 != 0 || a->world > 8)) return -12;
   CUtensorMap tw, tx;
   const CUtensorMapDataType dt = a->dtype == ORTB200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
   if (make_tensor_map_2d(&tw, a->w, dt, 2, a->K, a->w_rows, static_cast<int64_t>(a->K) * 2, kBK, kBM) != 0) return -6;
@@ -357,6 +385,22 @@ int launch_gemm_2cta(const ortb200_gemm_args* a, cudaStream_t stream) {
   p.dtype = a->dtype; p.act = a->act; p.alpha = a->alpha; p.out = a->out; p.ldo = a->ldo; p.bias = a->bias;
   p.residual = a->residual; p.ldr = a->ldr; p.status = a->status;
   p.tile_info = nullptr; p.num_tiles = nullptr; p.tiles_n = 0; p.w_rows_per_expert = 0;
+  p.world = 1; p.rank = 0; p.region_offset = 0; p.half_bytes = 0; p.row_vecs = 1;
+  for (int i = 0; i < 8; ++i) p.peers[i] = nullptr;
+  if (a->world > 1) {
+    const long long total_vecs = static_cast<long long>(a->M) * a->N / 8;
+    if (static_cast<long long>(a->M) * a->N * 2 > ortb200_symm_collective_max_bytes(ORTB200_COLL_ALLREDUCE, a->world, a->symm_bytes)) return -13;
+    p.world = a->world; p.rank = a->rank;
+    for (int i = 0; i < a->world; ++i) {
+      if (!a->peers[i]) return -12;
+      p.peers[i] = a->peers[i];
+    }
+    p.region_offset = a->symm_bytes / 2;
+    p.half_bytes = a->symm_bytes / 4;
+    p.row_vecs = static_cast<unsigned int>((total_vecs + a->world - 1) / a->world);
+    p.out = nullptr; p.residual = nullptr;     // the reduction kernel applies the residual and writes `out`
+    if (a->rank != 0) p.bias = nullptr;        // the bias enters the sum once
+  }
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
@@ -386,7 +430,8 @@ int launch_gemm_2cta(const ortb200_gemm_args* a, cudaStream_t stream) {
   }
   cfg.attrs = attrs;
   cfg.numAttrs = nattr;
-  return cudaLaunchKernelEx(&cfg, gemm_2cta_kernel, tw, tx, p) == cudaSuccess ? 0 : -11;
+  if (cudaLaunchKernelEx(&cfg, gemm_2cta_kernel, tw, tx, p) != cudaSuccess) return -11;
+  return a->world > 1 ? launch_allreduce_prescattered(a, stream) : 0;
 }
 
 // Grouped GEMM (mixture of experts) on CTA pairs: 256-token tiles from the device-side tile list.
@@ -406,6 +451,8 @@ int launch_gemm_grouped_2cta(const ortb200_gemm_grouped_args* a, cudaStream_t st
   p.num_tiles = a->num_tiles;
   p.tiles_n = (a->N + 2 * kBM - 1) / (2 * kBM);
   p.w_rows_per_expert = a->w_rows_per_expert;
+  p.world = 1; p.rank = 0; p.region_offset = 0; p.half_bytes = 0; p.row_vecs = 1;
+  for (int i = 0; i < 8; ++i) p.peers[i] = nullptr;
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);

@@ -44,6 +44,10 @@ int launch_gemm_grouped_large(const ortb200_gemm_grouped_args* a, cudaStream_t s
 
 // Large-M GEMM on CTA pairs (gemm_2cta.cu): 256 x 256 tiles, tcgen05 cta_group::2.
 int launch_gemm_2cta(const ortb200_gemm_args* a, cudaStream_t stream);
+// Second half of the prefill-sized fused GEMM + all-reduce (collectives.cu): the products already sit in the scatter
+// areas of the symmetric workspace (the GEMM epilogue pushed them there); adds them in rank order, adds the residual,
+// replicates the sums and copies them to `out` [M, N].
+int launch_allreduce_prescattered(const ortb200_gemm_args* a, cudaStream_t stream);
 int launch_gemm_grouped_2cta(const ortb200_gemm_grouped_args* a, cudaStream_t stream);
 
 // bn in {16, 32, 64}.  Returns 0 or a negative launch error; reports the cluster size and pipeline depth used.
@@ -131,6 +135,31 @@ __device__ __forceinline__ void store_pass(const StoreArgs& p, const uint16_t* s
         else reinterpret_cast<__half*>(p.out)[o + e] = __float2half_rn(y);
       }
     }
+  }
+}
+
+// Tensor-parallel variant of the store pass: instead of `out`, every 16-byte chunk of the staged tile goes straight to
+// the rank that will reduce it - slice `g / row_vecs` of the flattened [M, N] product, at scatter[this rank][g % row_vecs]
+// in that rank's symmetric workspace (the layout ortb200_symm_collective's all-reduce sums from).  Needs N % 8 == 0.
+struct ScatterArgs {
+  void* peers[8];
+  long long area_offset;   // byte offset of the scatter area of this launch's parity within every workspace
+  unsigned int row_vecs;   // 16-byte vectors per slice
+  int rank, N;
+};
+
+template <int STRIDE>
+__device__ __forceinline__ void scatter_pass(const ScatterArgs& p, const uint16_t* stg, int rows, int et, int m_base, int m_end, int nrow0) {
+  for (int idx = et; idx < rows * 16; idx += STRIDE) {
+    const int row = idx >> 4, ch = idx & 15;
+    const int m = m_base + row;
+    const int nn = nrow0 + ch * 8;
+    if (m >= m_end || nn >= p.N) continue;
+    const uint4 val = *reinterpret_cast<const uint4*>(stg + row * 128 + ch * 8);
+    const unsigned int g = static_cast<unsigned int>((static_cast<long long>(m) * p.N + nn) >> 3);
+    const unsigned int dst = g / p.row_vecs, i = g - dst * p.row_vecs;
+    uint4* d = reinterpret_cast<uint4*>(static_cast<uint8_t*>(p.peers[dst]) + p.area_offset) + static_cast<long long>(p.rank) * p.row_vecs + i;
+    *d = val;
   }
 }
 

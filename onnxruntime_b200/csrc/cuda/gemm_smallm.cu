@@ -240,6 +240,10 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
   } else if (warp == 1) {
     if (lane == 0) {
       const uint32_t idesc = umma_idesc_f16(p.dtype == ORTB200_BF16, kBM, BN);
+      // Every bounded wait below depends on the activations, which the producer only requests once the previous grid
+      // has finished.  Waiting for that grid here (an unbounded hardware wait that costs nothing once it is satisfied)
+      // keeps a slow predecessor - a fused all-reduce waiting for a late rank - from running out this kernel's limits.
+      pdl_wait_prior_grids();
       for (int i = 0; i < nkb; ++i) {
         const int s = i % STAGES;
         if (!mbar_wait(&full_bar[s], (i / STAGES) & 1)) {
@@ -273,6 +277,7 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
     const int q = warp & 3;
     const int r = q * 32 + lane;
     const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+    pdl_wait_prior_grids();  // same reason as in the MMA warp: no bounded wait may span the previous grid's run time
     if (NBITS) {
       // ---- weight expansion: thread r owns weight row r of the tile.  Per k-block it reads 32 packed bytes, two
       // scales and two zero points, and writes one 128-byte row of the swizzled MMA operand.

@@ -236,6 +236,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
       long long it = 0;
       int seg = 0;
       bool ok = true;
+      pdl_wait_prior_grids();  // the bounded waits below must not span the previous grid's run time
       for (long long u = range.begin; u < range.end && ok; ++seg) {
         const long long tile_end = (u / p.num_kb + 1) * p.num_kb;
         const long long seg_end = tile_end < range.end ? tile_end : range.end;
@@ -669,14 +670,16 @@ extern "C" int ortb200_gemm(const ortb200_gemm_args* a, ortb200_stream_t stream_
   // Large problems run on CTA pairs (256 x 256 tiles, cta_group::2): measured 1.3 PFLOP/s against 0.98 for the
   // single-CTA kernel on 8192 x 6144 x 4096.  Needs at least most of a wave of 74 pairs to pay off.
   const long long tiles256 = static_cast<long long>((a->M + 255) / 256) * ((a->N + 255) / 256);
-  const bool pair_ok = !dual && !fp8 && !q4 && a->world <= 1 && a->rms_eps <= 0.f;
-  if (a->force_tile_rows == 512 || (a->force_tile_rows == 0 && a->force_bn == 0 && a->force_splits == 0 && pair_ok && a->M >= 512 &&
-                                    tiles256 >= 60)) {
+  const bool pair_ok = !dual && !fp8 && !q4 && a->rms_eps <= 0.f;
+  // world > 1 (row-parallel linear at prompt size): only the CTA-pair kernel has the epilogue that pushes the product
+  // into the all-reduce scatter areas; the reduction kernel is launched right behind it
+  if (a->force_tile_rows == 512 || (a->world > 1 && pair_ok) ||
+      (a->force_tile_rows == 0 && a->force_bn == 0 && a->force_splits == 0 && pair_ok && a->M >= 512 && tiles256 >= 60)) {
     const int rc2 = launch_gemm_2cta(a, stream);
     g_last_config = {256, 2, 5};
     return rc2;
   }
-  if (a->world > 1) return -12;  // the fused all-reduce exists for decode-shaped problems only
+  if (a->world > 1) return -12;  // no fused all-reduce for this combination
   if (a->rms_eps > 0.f) return -14;  // so does the fused RMS normalisation
   GemmPlan pl;
   // fp8 operands: the planner counts 64-element k-blocks, and a stage holds 128 fp8 elements

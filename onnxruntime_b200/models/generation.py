@@ -22,7 +22,9 @@ class DecoderRunner:
     """Owns the KV cache and the bindings of one (session, batch size, cache capacity)."""
 
     def __init__(self, session: InferenceSession, cfg: LlamaConfig, batch: int, max_len: int, tp_size: int = 1,
-                 device: Optional[torch.device] = None):
+                 device: Optional[torch.device] = None, prefill_graph: bool = False):
+        """``prefill_graph``: also capture the prompt run in a CUDA graph (one graph per prompt shape; worthwhile when the
+        same prompt shape recurs, e.g. fixed-size prefill chunks).  Needs a session created with ``enable_cuda_graph``."""
         self.sess = session
         self.cfg = cfg
         self.batch = batch
@@ -43,6 +45,8 @@ class DecoderRunner:
         self._ro_decode.add_run_config_entry("gpu_graph_id", "1")
         self._ro_prefill = RunOptions()
         self._ro_prefill.add_run_config_entry("gpu_graph_id", "-1")
+        self._prefill_graph = prefill_graph
+        self._prefill_graph_ids: Dict[Tuple[int, int], int] = {}
 
     def _bind_common(self, binding, ids: torch.Tensor, seqlens: torch.Tensor, total: torch.Tensor, logits, next_tokens) -> None:
         binding.bind_torch_input("input_ids", ids)
@@ -68,7 +72,19 @@ class DecoderRunner:
         nxt = torch.empty(B, 1, dtype=torch.int64, device=self.device)
         binding = self.sess.io_binding()
         self._bind_common(binding, ids, seqlens, total, logits, nxt)
-        self.sess.run_with_iobinding(binding, self._ro_prefill)
+        ro = self._ro_prefill
+        if self._prefill_graph:
+            gid = self._prefill_graph_ids.setdefault((B, S), 2 + len(self._prefill_graph_ids))
+            ro = RunOptions()
+            ro.add_run_config_entry("gpu_graph_id", str(gid))
+        try:
+            self.sess.run_with_iobinding(binding, ro)
+        except Exception:
+            if ro is self._ro_prefill:
+                raise
+            # the prompt graph holds something that cannot be captured: run it eagerly from now on
+            self._prefill_graph = False
+            self.sess.run_with_iobinding(binding, self._ro_prefill)
         self.cur_len = S
         self.prefill_logits = logits
         if not self.has_argmax:

@@ -190,10 +190,13 @@ def case_gemm_allreduce(info, device, out):
     from onnxruntime_b200.parallel import symm
     r, w = info.rank, info.world_size
     torch.cuda.set_device(info.local_rank)
-    ws = symm.create_workspace(16 << 20)
+    ws = symm.create_workspace(64 << 20)
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
     res = {}
-    for i, (M, N, Kd) in enumerate([(8, 4096, 512), (8, 1024, 1792), (16, 2048, 256), (1, 512, 128), (33, 768, 512)]):
+    # decode-sized problems reduce inside the GEMM kernel; the prompt-sized ones (M > 64) push their product into the
+    # all-reduce scatter areas from the CTA-pair kernel's epilogue and a reduction kernel finishes them
+    for i, (M, N, Kd) in enumerate([(8, 4096, 512), (8, 1024, 1792), (16, 2048, 256), (1, 512, 128), (33, 768, 512),
+                                    (1024, 2048, 512), (700, 1000, 256), (2048, 512, 1024)]):
         g = torch.Generator(device="cuda").manual_seed(100 * i + r)
         x = (torch.randn(M, Kd, device="cuda", generator=g) * 0.5).bfloat16()
         wt = (torch.randn(N, Kd, device="cuda", generator=g) * 0.05).bfloat16()
