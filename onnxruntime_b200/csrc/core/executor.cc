@@ -4,10 +4,30 @@
 #include <c10/cuda/CUDAGuard.h>
 
 #include <algorithm>
+#include <atomic>
+#include <mutex>
+#include <set>
 #include <sstream>
 #include <cuda_runtime_api.h>
+#include <nvtx3/nvToolsExt.h>
+
+#include "threadpool.h"
 
 namespace ortb {
+
+namespace {
+// NVTX range around one node (reference: onnxruntime/core/providers/cuda/nvtx_profile.h:100-139, used at
+// sequential_executor.cc:413,517).  Without a profiler attached the calls are a few nanoseconds.
+struct NvtxRange {
+  explicit NvtxRange(const char* name) : on_(name != nullptr) {
+    if (on_) nvtxRangePushA(name);
+  }
+  ~NvtxRange() {
+    if (on_) nvtxRangePop();
+  }
+  bool on_;
+};
+}  // namespace
 
 namespace {
 bool IsShapeOnlyOp(const Node& n) { return n.domain.empty() && (n.op_type == "Shape" || n.op_type == "Size"); }
@@ -379,12 +399,64 @@ void GraphExecutor::Build() {
     if (!st.on_gpu && !IsShapeOnlyOp(*st.node)) capturable_ = false;
     if (st.node->op_type == "MemcpyToHost") capturable_ = false;
   }
+  BuildStepGraph();
+  nvtx_ = session_->config().Get("ortb200.nvtx", "1") == "1";
+}
+
+// One node: gather its inputs from the slots, run the kernel, put the outputs back.
+void GraphExecutor::RunStep(const RunOptions& ro, const Step& st, std::vector<Value>& slots, OpKernelContext::Lookup* lookup, int node_index) {
+  Profiler* prof = session_->profiler().enabled() ? &session_->profiler() : nullptr;
+  std::vector<Value> in(st.in_slots.size()), out(st.out_slots.size());
+  for (size_t i = 0; i < st.in_slots.size(); ++i)
+    if (st.in_slots[i] >= 0) in[i] = slots[st.in_slots[i]];
+  for (size_t i = 0; i < st.out_slots.size(); ++i)
+    if (st.out_slots[i] >= 0) out[i] = slots[st.out_slots[i]];  // caller-bound output buffer, if any
+  OpKernelContext ctx(*st.node, session_, st.device, in, out, st.out_needed);
+  ctx.set_lookup(lookup);
+  ctx.run_options = &ro;
+  const int64_t t_node0 = prof ? prof->NowUs() : 0;
+  NvtxRange range(nvtx_ ? st.node->name.c_str() : nullptr);  // one range per node: profiler timelines carry node names
+  try {
+    st.kernel->Compute(ctx);
+    if (prof) {
+      // per-node durations need the node's GPU work to have finished (profiling mode only)
+      if (st.on_gpu && at::cuda::currentStreamCaptureStatusMayInitCtx() == c10::cuda::CaptureStatus::None) cudaStreamSynchronize(at::cuda::getCurrentCUDAStream(st.device.index()).stream());
+      std::map<std::string, std::string> args;
+      args["op_name"] = st.node->op_type;
+      args["provider"] = st.node->ep.empty() ? kCpuEP : st.node->ep;
+      args["node_index"] = std::to_string(node_index);
+      std::string shapes;
+      for (auto& v : in)
+        if (v.t.defined()) {
+          std::ostringstream ss;
+          ss << v.t.sizes();
+          shapes += ss.str() + " ";
+        }
+      args["input_type_shape"] = shapes;
+      prof->Record("Node", st.node->name + "_kernel_time", t_node0, prof->NowUs() - t_node0, std::move(args));
+    }
+  } catch (const OrtError&) {
+    throw;
+  } catch (const std::exception& e) {
+    ORTB_THROW(RUNTIME_EXCEPTION, "Non-zero status code returned while running ", st.node->op_type, " node. Name:'",
+               st.node->name, "' Status Message: ", e.what());
+  }
+  for (size_t i = 0; i < st.out_slots.size(); ++i) {
+    const int s = st.out_slots[i];
+    if (s < 0) continue;
+    Value& bound = slots[s];
+    if (bound.t.defined() && out[i].t.defined() && !bound.t.is_same(out[i].t) &&
+        bound.t.data_ptr() != out[i].t.data_ptr()) {
+      ORTB_ENFORCE_ARG(bound.t.sizes() == out[i].t.sizes(), "bound output '", slot_names_[s], "' has shape ",
+                       bound.t.sizes(), " but the model produced ", out[i].t.sizes());
+      bound.t.copy_(out[i].t, /*non_blocking=*/true);
+    } else {
+      slots[s] = std::move(out[i]);
+    }
+  }
 }
 
 void GraphExecutor::ExecuteSteps(const RunOptions& ro, std::vector<Value>& slots) {
-  Profiler* prof = session_->profiler().enabled() ? &session_->profiler() : nullptr;
-  int node_index = 0;
-  std::vector<Value> in, out;
   const std::map<std::string, Value>* outer = current_outer_;
   OpKernelContext::Lookup lookup = [this, &slots, outer](const std::string& name) -> Value {
     auto it = slot_of_.find(name);
@@ -400,59 +472,85 @@ void GraphExecutor::ExecuteSteps(const RunOptions& ro, std::vector<Value>& slots
     }
     ORTB_THROW(FAIL, "value '", name, "' is not available in the enclosing scope");
   };
+  ThreadPool* pool = session_->InterOpPool();
+  if (pool != nullptr && pool->NumThreads() > 0 && parallel_ok_ && steps_.size() > 1) {
+    ExecuteStepsParallel(ro, slots, &lookup, pool);
+    return;
+  }
+  int node_index = 0;
   for (auto& st : steps_) {
     if (ro.terminate && ro.terminate->load(std::memory_order_relaxed))
       ORTB_THROW(FAIL, "Exiting due to terminate flag being set to true.");
-    in.assign(st.in_slots.size(), Value());
-    out.assign(st.out_slots.size(), Value());
-    for (size_t i = 0; i < st.in_slots.size(); ++i)
-      if (st.in_slots[i] >= 0) in[i] = slots[st.in_slots[i]];
-    for (size_t i = 0; i < st.out_slots.size(); ++i)
-      if (st.out_slots[i] >= 0) out[i] = slots[st.out_slots[i]];  // caller-bound output buffer, if any
-    OpKernelContext ctx(*st.node, session_, st.device, in, out, st.out_needed);
-    ctx.set_lookup(&lookup);
-    ctx.run_options = &ro;
-    const int64_t t_node0 = prof ? prof->NowUs() : 0;
-    try {
-      st.kernel->Compute(ctx);
-      if (prof) {
-        // per-node durations need the node's GPU work to have finished (profiling mode only)
-        if (st.on_gpu && at::cuda::currentStreamCaptureStatusMayInitCtx() == c10::cuda::CaptureStatus::None) cudaStreamSynchronize(at::cuda::getCurrentCUDAStream(st.device.index()).stream());
-        std::map<std::string, std::string> args;
-        args["op_name"] = st.node->op_type;
-        args["provider"] = st.node->ep.empty() ? kCpuEP : st.node->ep;
-        args["node_index"] = std::to_string(node_index);
-        std::string shapes;
-        for (auto& v : in)
-          if (v.t.defined()) {
-            std::ostringstream ss;
-            ss << v.t.sizes();
-            shapes += ss.str() + " ";
-          }
-        args["input_type_shape"] = shapes;
-        prof->Record("Node", st.node->name + "_kernel_time", t_node0, prof->NowUs() - t_node0, std::move(args));
-      }
-      ++node_index;
-    } catch (const OrtError&) {
-      throw;
-    } catch (const std::exception& e) {
-      ORTB_THROW(RUNTIME_EXCEPTION, "Non-zero status code returned while running ", st.node->op_type, " node. Name:'",
-                 st.node->name, "' Status Message: ", e.what());
-    }
-    for (size_t i = 0; i < st.out_slots.size(); ++i) {
-      const int s = st.out_slots[i];
-      if (s < 0) continue;
-      Value& bound = slots[s];
-      if (bound.t.defined() && out[i].t.defined() && !bound.t.is_same(out[i].t) &&
-          bound.t.data_ptr() != out[i].t.data_ptr()) {
-        ORTB_ENFORCE_ARG(bound.t.sizes() == out[i].t.sizes(), "bound output '", slot_names_[s], "' has shape ",
-                         bound.t.sizes(), " but the model produced ", out[i].t.sizes());
-        bound.t.copy_(out[i].t, /*non_blocking=*/true);
-      } else {
-        slots[s] = std::move(out[i]);
-      }
-    }
+    RunStep(ro, st, slots, &lookup, node_index++);
     for (int s : st.release) slots[s] = Value();
+  }
+}
+
+// ExecutionMode::ORT_PARALLEL (host graphs): a node is queued on the inter-op pool as soon as the nodes that produce
+// its inputs have finished; the calling thread helps until the graph is done.  Nodes with control-flow bodies read
+// values by name, so they wait for everything before them and everything after them waits for them.  Values are
+// released when the run ends (a release list assumes program order).  The reference's counterpart is the parallel
+// branch of onnxruntime/core/framework/sequential_executor.cc:526-771 (one task per logic stream).
+void GraphExecutor::ExecuteStepsParallel(const RunOptions& ro, std::vector<Value>& slots, OpKernelContext::Lookup* lookup, ThreadPool* pool) {
+  const size_t n = steps_.size();
+  std::vector<std::atomic<int>> pending(n);
+  for (size_t i = 0; i < n; ++i) pending[i].store(static_cast<int>(step_deps_[i].size()), std::memory_order_relaxed);
+  std::atomic<size_t> finished{0};
+  std::atomic<bool> failed{false};
+  std::exception_ptr first_error;
+  std::mutex err_mu;
+  std::function<void(size_t)> run = [&](size_t i) {
+    if (!failed.load(std::memory_order_acquire) && !(ro.terminate && ro.terminate->load(std::memory_order_relaxed))) {
+      try {
+        RunStep(ro, steps_[i], slots, lookup, static_cast<int>(i));
+      } catch (...) {
+        std::lock_guard<std::mutex> lk(err_mu);
+        if (!first_error) first_error = std::current_exception();
+        failed.store(true, std::memory_order_release);
+      }
+    }
+    for (int succ : step_succ_[i])
+      if (pending[static_cast<size_t>(succ)].fetch_sub(1, std::memory_order_acq_rel) == 1) pool->Schedule([&run, succ] { run(static_cast<size_t>(succ)); });
+    finished.fetch_add(1, std::memory_order_acq_rel);
+  };
+  for (size_t i = 0; i < n; ++i)
+    if (step_deps_[i].empty()) pool->Schedule([&run, i] { run(i); });
+  pool->HelpUntil([&] { return finished.load(std::memory_order_acquire) == n; });
+  if (first_error) std::rethrow_exception(first_error);
+  if (ro.terminate && ro.terminate->load(std::memory_order_relaxed)) ORTB_THROW(FAIL, "Exiting due to terminate flag being set to true.");
+}
+
+// Dependencies between steps, from the slots they read and write.
+void GraphExecutor::BuildStepGraph() {
+  const size_t n = steps_.size();
+  step_deps_.assign(n, {});
+  step_succ_.assign(n, {});
+  std::map<int, int> producer;  // slot -> step
+  int last_barrier = -1;
+  parallel_ok_ = true;
+  for (size_t i = 0; i < n; ++i) {
+    const Step& st = steps_[i];
+    std::set<int> deps;
+    const bool barrier = !st.node->subgraphs.empty();
+    if (barrier) {
+      for (size_t j = 0; j < i; ++j) deps.insert(static_cast<int>(j));
+    } else {
+      if (last_barrier >= 0) deps.insert(last_barrier);
+      for (int s : st.in_slots) {
+        auto it = s >= 0 ? producer.find(s) : producer.end();
+        if (it != producer.end()) deps.insert(it->second);
+      }
+    }
+    for (int s : st.out_slots) {
+      if (s < 0) continue;
+      auto it = producer.find(s);
+      if (it != producer.end()) deps.insert(it->second);  // two writers of one slot keep their order
+      producer[s] = static_cast<int>(i);
+    }
+    if (barrier) last_barrier = static_cast<int>(i);
+    if (st.on_gpu) parallel_ok_ = false;  // device work is ordered by its stream: nothing to gain, a lot to break
+    step_deps_[i].assign(deps.begin(), deps.end());
+    for (int d : deps) step_succ_[static_cast<size_t>(d)].push_back(static_cast<int>(i));
   }
 }
 

@@ -40,12 +40,17 @@ class GraphExecutor {
   Graph* graph() const { return graph_; }
   // Run only the step loop over a prepared slot vector (used inside CUDA-graph capture).
   void ExecuteSteps(const RunOptions& ro, std::vector<Value>& slots);
+  // true when ExecutionMode::ORT_PARALLEL can apply: every step runs on the host
+  bool parallel_ok() const { return parallel_ok_; }
   std::vector<Value> NewSlots() const { return constant_slots_; }
   int SlotOf(const std::string& name) const;
 
  private:
   void Partition();
   void InsertCopies();
+  void BuildStepGraph();
+  void RunStep(const RunOptions& ro, const Step& st, std::vector<Value>& slots, OpKernelContext::Lookup* lookup, int node_index);
+  void ExecuteStepsParallel(const RunOptions& ro, std::vector<Value>& slots, OpKernelContext::Lookup* lookup, class ThreadPool* pool);
   int NewSlot(const std::string& name);
 
   InferenceSession* session_;
@@ -60,6 +65,8 @@ class GraphExecutor {
   std::vector<int> input_slot_, outer_slot_;
   std::vector<c10::Device> input_device_;
   bool capturable_ = false;
+  bool parallel_ok_ = false, nvtx_ = true;
+  std::vector<std::vector<int>> step_deps_, step_succ_;  // step index -> steps it waits for / steps waiting for it
   const std::map<std::string, Value>* current_outer_ = nullptr;
 };
 

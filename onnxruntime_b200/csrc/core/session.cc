@@ -2,7 +2,9 @@
 
 #include <ATen/cuda/CUDAContext.h>
 #include <ATen/cuda/CUDAGraph.h>
+#include <ATen/Parallel.h>
 #include <c10/cuda/CUDAGuard.h>
+#include <c10/cuda/CUDACachingAllocator.h>
 #include <c10/cuda/CUDAStream.h>
 #include <cuda_runtime_api.h>
 #include <unistd.h>
@@ -10,9 +12,12 @@
 #include <ctime>
 #include <fstream>
 #include <iomanip>
+#include <set>
 #include <sstream>
+#include <thread>
 
 #include "executor.h"
+#include "threadpool.h"
 
 namespace ortb {
 
@@ -202,6 +207,7 @@ void InferenceSession::Initialize(const std::vector<std::pair<std::string, Provi
 
   if (!so_.optimized_model_filepath.empty()) model_->Save(so_.optimized_model_filepath);
 
+  ApplyThreadingAndWarnings();
   auto exec = std::make_unique<GraphExecutor>(this, &g, nullptr);
   exec->Build();
   input_names_ = exec->input_names();
@@ -230,10 +236,84 @@ void InferenceSession::Initialize(const std::vector<std::pair<std::string, Provi
     }
     ORTB_LOG(logger_, kInfo) << "session initialized: " << total << " nodes, providers " << providers_.front()
                              << (providers_.size() > 1 ? " + " + providers_.back() : std::string()) << ", device " << device_.str();
-    if (device_.is_cuda() && on_cpu > 0)
+    if (device_.is_cuda() && on_cpu > 0) {
       ORTB_LOG(logger_, kWarning) << on_cpu << " of " << total << " nodes run on the CPU provider, e.g. " << example;
+      if (so_.config.Get("session.disable_cpu_ep_fallback", "0") == "1") {
+        initialized_ = false;
+        ORTB_THROW(FAIL, "session.disable_cpu_ep_fallback is set and ", on_cpu, " nodes were placed on the CPU provider, e.g. ", example);
+      }
+    }
   }
   profiler_.Record("Session", "session_initialization", t0, profiler_.NowUs() - t0);
+}
+
+// Options of the reference that map onto something here are applied; the rest is accepted (scripts written for the
+// reference keep working) but reported, so that nobody tunes a knob that does nothing.
+void InferenceSession::ApplyThreadingAndWarnings() {
+  // intra-op parallelism of the host kernels is ATen's pool (process-wide, like the reference's global thread pools)
+  if (so_.intra_op_num_threads > 0) {
+    at::set_num_threads(so_.intra_op_num_threads);
+    ORTB_LOG(logger_, kInfo) << "intra_op_num_threads=" << so_.intra_op_num_threads << " applied to the host math pool (process-wide)";
+  }
+  if (so_.execution_mode == 1) {
+    int n = so_.inter_op_num_threads > 0 ? so_.inter_op_num_threads : static_cast<int>(std::thread::hardware_concurrency());
+    if (n < 1) n = 1;
+    if (device_.is_cuda()) {
+      ORTB_LOG(logger_, kWarning) << "execution_mode=ORT_PARALLEL has no effect on a GPU session: device work is ordered by one stream";
+    } else {
+      inter_op_pool_ = std::make_shared<ThreadPool>(n - 1, "inter-op");  // the calling thread is the n-th lane
+    }
+  } else if (so_.inter_op_num_threads > 1) {
+    ORTB_LOG(logger_, kWarning) << "inter_op_num_threads is only used with execution_mode=ORT_PARALLEL";
+  }
+  if (!so_.enable_mem_pattern || !so_.enable_mem_reuse || !so_.enable_cpu_mem_arena)
+    ORTB_LOG(logger_, kWarning) << "enable_mem_pattern / enable_mem_reuse / enable_cpu_mem_arena have no effect: tensors come from "
+                                   "PyTorch's caching allocators (see memory.enable_memory_arena_shrinkage to give memory back)";
+  if (so_.use_deterministic_compute) {
+    // every kernel of this library sums in a fixed order; ATen needs to be told
+    at::globalContext().setDeterministicAlgorithms(true, /*warn_only=*/true);
+  }
+  if (so_.execution_order != 0)
+    ORTB_LOG(logger_, kWarning) << "execution_order is ignored: nodes run in a stable topological order";
+  // session configuration keys: known ones are honoured where they apply, unknown ones are reported once
+  static const std::set<std::string> known = {
+      "session.graph_optimizations_loop_level", "optimization.disable_specified_optimizers", "session.disable_cpu_ep_fallback",
+      "session.disable_prepacking", "session.use_device_allocator_for_initializers", "session.use_env_allocators",
+      "session.set_denormal_as_zero", "session.intra_op.allow_spinning", "session.inter_op.allow_spinning",
+      "session.record_ep_graph_assignment_info", "session.load_model_format", "session.save_model_format",
+      "optimization.enable_gelu_approximation", "optimization.minimal_build_optimizations", "ep.context_enable",
+      "ep.context_file_path", "ep.context_embed_mode", "session.use_ort_model_bytes_directly", "session.strict_shape_type_inference",
+      "session.qdqisint8allowed", "session.enable_dq_matmulnbits_fusion", "session.qdq_matmulnbits_accuracy_level",
+      "session.dynamic_block_base", "session.force_spinning_stop", "session.collect_node_memory_stats_to_file"};
+  for (auto& kv : so_.config.entries) {
+    if (kv.first.rfind("ortb200.", 0) == 0 || kv.first.rfind("ep.cuda.", 0) == 0) continue;
+    if (!known.count(kv.first)) ORTB_LOG(logger_, kWarning) << "session config entry '" << kv.first << "' is not known to this runtime and is ignored";
+  }
+  if (so_.config.Get("session.set_denormal_as_zero", "0") == "1") at::globalContext().setFlushDenormal(true);
+  static const std::set<std::string> cuda_known = {"device_id", "enable_cuda_graph", "gpu_mem_limit", "arena_extend_strategy",
+      "cudnn_conv_algo_search", "do_copy_in_default_stream", "user_compute_stream", "tunable_op_enable", "tunable_op_tuning_enable",
+      "tunable_op_max_tuning_duration_ms", "prefer_nhwc", "use_ep_level_unified_stream", "use_tf32", "fuse_conv_bias", "sdpa_kernel",
+      "cudnn_conv_use_max_workspace", "cudnn_conv1d_pad_to_nc1d", "enable_cudnn", "enable_skip_layer_norm_strict_mode", "has_user_compute_stream",
+      "gpu_external_alloc", "gpu_external_free", "gpu_external_empty_cache"};
+  auto po = provider_options_.find(kCudaEP);
+  if (po != provider_options_.end()) {
+    for (auto& kv : po->second) {
+      if (!cuda_known.count(kv.first)) {
+        ORTB_LOG(logger_, kWarning) << "CUDA provider option '" << kv.first << "' is not known and is ignored";
+      } else if (kv.first == "use_tf32") {
+        at::globalContext().setAllowTF32CuBLAS(kv.second == "1");
+      } else if (kv.first == "gpu_mem_limit" && device_.is_cuda()) {
+        // a byte budget becomes a fraction of the device for the caching allocator
+        const double limit = std::stod(kv.second);
+        size_t free_b = 0, total_b = 0;
+        if (limit > 0 && cudaMemGetInfo(&free_b, &total_b) == cudaSuccess && total_b > 0 && limit < static_cast<double>(total_b))
+          c10::cuda::CUDACachingAllocator::setMemoryFraction(limit / static_cast<double>(total_b), device_.index());
+      } else if (kv.first != "device_id" && kv.first != "enable_cuda_graph") {
+        ORTB_LOG(logger_, kInfo) << "CUDA provider option '" << kv.first << "' is accepted; it selects between library code paths the "
+                                    "reference has and this runtime does not";
+      }
+    }
+  }
 }
 
 std::vector<std::string> InferenceSession::Providers() const { return providers_; }
@@ -489,6 +569,12 @@ std::vector<Value> InferenceSession::RunImpl(const RunOptions& ro, const std::ve
   if (profiler_.enabled()) {
     if (device_.is_cuda()) cudaStreamSynchronize(at::cuda::getCurrentCUDAStream(device_.index()).stream());
     profiler_.Record("Session", "model_run", t_run0, profiler_.NowUs() - t_run0);
+  }
+  // run option memory.enable_memory_arena_shrinkage ("cpu:0;gpu:0"): hand cached device memory back after this run
+  // (reference: onnxruntime/core/session/inference_session.cc:4147 ShrinkMemoryArenas)
+  if (device_.is_cuda() && ro.config.Get("memory.enable_memory_arena_shrinkage").find("gpu") != std::string::npos) {
+    cudaStreamSynchronize(at::cuda::getCurrentCUDAStream(device_.index()).stream());
+    c10::cuda::CUDACachingAllocator::emptyCache();
   }
   return results;
 }

@@ -131,6 +131,8 @@ class InferenceSession {
   bool uses_gpu() const { return device_.is_cuda(); }
   const SessionOptions& options() const { return so_; }
   const ConfigOptions& config() const { return so_.config; }
+  // inter-op pool: present when execution_mode is parallel (ExecutionMode::ORT_PARALLEL), null otherwise
+  class ThreadPool* InterOpPool() const { return inter_op_pool_.get(); }
   // per-node provider assignment: (node name, op type, provider)
   std::vector<std::tuple<std::string, std::string, std::string>> NodeAssignments() const;
   Profiler& profiler() { return profiler_; }
@@ -169,6 +171,8 @@ class InferenceSession {
                              const std::vector<Value>* bound_outputs);
 
   struct CapturedGraph;
+  void ApplyThreadingAndWarnings();
+  std::shared_ptr<class ThreadPool> inter_op_pool_;
   SessionOptions so_;
   std::shared_ptr<Model> model_;
   bool initialized_ = false;

@@ -251,3 +251,72 @@ def test_logging_severity_sink_and_session_ids(capfd):
     ort.InferenceSession(model, so, providers=["CPUExecutionProvider"])
     err = capfd.readouterr().err
     assert "[I:ortb200:stderr-session, session.cc:" in err
+
+
+def _wide_model(branches=6, depth=4, n=64):
+    """`branches` independent chains of MatMul + Tanh over one input, summed at the end: work an inter-op pool can spread."""
+    import numpy as np
+    from onnxruntime_b200 import onnx_lite as ol
+    T = ol.TensorProto
+    rng = np.random.RandomState(3)
+    nodes, inits, tails = [], [], []
+    for b in range(branches):
+        cur = "x"
+        for d in range(depth):
+            w = f"w{b}_{d}"
+            inits.append(ol.make_tensor(w, (rng.randn(n, n) * 0.2).astype(np.float32)))
+            nodes += [ol.make_node("MatMul", [cur, w], [f"m{b}_{d}"]), ol.make_node("Tanh", [f"m{b}_{d}"], [f"t{b}_{d}"])]
+            cur = f"t{b}_{d}"
+        tails.append(cur)
+    nodes.append(ol.make_node("Sum", tails, ["y"]))
+    g = ol.make_graph(nodes, "wide", [ol.make_tensor_value_info("x", T.FLOAT, ["b", n])], [ol.make_tensor_value_info("y", T.FLOAT, None)], inits)
+    return ol.make_model(g, opset=17).serialize()
+
+
+def test_parallel_execution_mode_matches_sequential():
+    """ExecutionMode.ORT_PARALLEL runs independent nodes on the inter-op pool; results equal the sequential run, errors
+    surface as the usual exception, control-flow nodes keep their place."""
+    import numpy as np
+    import onnxruntime_b200 as ort
+    model = _wide_model()
+    x = np.random.RandomState(0).randn(5, 64).astype(np.float32)
+    so0 = ort.SessionOptions()
+    so0.graph_optimization_level = ort.GraphOptimizationLevel.ORT_DISABLE_ALL
+    ref = ort.InferenceSession(model, so0, providers=["CPUExecutionProvider"]).run(None, {"x": x})[0]
+    so = ort.SessionOptions()
+    so.graph_optimization_level = ort.GraphOptimizationLevel.ORT_DISABLE_ALL
+    so.execution_mode = ort.ExecutionMode.ORT_PARALLEL
+    so.inter_op_num_threads = 4
+    so.intra_op_num_threads = 1
+    sess = ort.InferenceSession(model, so, providers=["CPUExecutionProvider"])
+    for _ in range(5):
+        np.testing.assert_array_equal(sess.run(None, {"x": x})[0], ref)
+    # a failing node surfaces as the same kind of exception as in the sequential executor
+    with pytest.raises(ort.capi.OrtException):
+        sess.run(None, {"x": np.zeros((5, 63), np.float32)})
+    np.testing.assert_array_equal(sess.run(None, {"x": x})[0], ref)   # and the session stays usable
+
+
+def test_ignored_options_are_reported_and_mapped_ones_applied():
+    import numpy as np
+    import torch
+    import onnxruntime_b200 as ort
+    model = _wide_model(2, 1, 8)
+    lines = []
+    ort.set_log_sink(lambda sev, logid, line: lines.append((sev, line)))
+    before = torch.get_num_threads()
+    try:
+        so = ort.SessionOptions()
+        so.enable_mem_pattern = False
+        so.inter_op_num_threads = 3
+        so.intra_op_num_threads = 2
+        so.add_session_config_entry("session.no_such_key", "1")
+        so.add_session_config_entry("session.disable_prepacking", "1")
+        ort.InferenceSession(model, so, providers=["CPUExecutionProvider"])
+        text = "\\n".join(l for _, l in lines)
+        assert "enable_mem_pattern" in text and "inter_op_num_threads is only used" in text
+        assert "session.no_such_key" in text and "session.disable_prepacking" not in text
+        assert torch.get_num_threads() == 2
+    finally:
+        ort.set_log_sink(None)
+        torch.set_num_threads(before)
