@@ -9,6 +9,7 @@
 #include "graph.h"
 #include "kernel.h"
 #include "session.h"
+#include "shape_inference.h"
 #include "cuda_ops.h"
 #include "sharding_spec.h"
 
@@ -321,6 +322,31 @@ PYBIND11_MODULE(_core, m) {
       OptimizerStats st = OptimizeGraph(model->MainGraph(), level, dis, gpu, cfg, 1);
       return py::make_tuple(py::bytes(model->Serialize()), st.applied);
     });
+  });
+  m.def("infer_shapes", [](py::bytes b, bool strict) {
+    std::string bytes = b;
+    return Guard([&] {
+      auto model = Model::LoadFromBytes(std::make_shared<std::string>(bytes), "");
+      InferenceReport rep = InferShapes(model->MainGraph(), strict);
+      py::dict d;
+      d["nodes"] = rep.nodes;
+      d["inferred"] = rep.inferred;
+      d["problems"] = rep.problems;
+      return py::make_tuple(py::bytes(model->Serialize()), d);
+    });
+  }, py::arg("model"), py::arg("strict") = false);
+  m.def("op_schemas", [] {
+    py::list out;
+    for (const OpSchema* s : AllSchemas()) {
+      py::dict d;
+      d["domain"] = s->domain;
+      d["op_type"] = s->op_type;
+      d["min_inputs"] = s->min_inputs;
+      d["max_inputs"] = s->max_inputs;
+      d["has_shape_function"] = static_cast<bool>(s->infer);
+      out.append(d);
+    }
+    return out;
   });
   m.def("model_nodes", [](py::bytes b) {
     std::string bytes = b;

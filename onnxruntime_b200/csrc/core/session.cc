@@ -17,6 +17,7 @@
 #include <thread>
 
 #include "executor.h"
+#include "shape_inference.h"
 #include "threadpool.h"
 
 namespace ortb {
@@ -205,6 +206,14 @@ void InferenceSession::Initialize(const std::vector<std::pair<std::string, Provi
   ORTB_LOG(logger_, kInfo) << "graph optimization level " << so_.graph_optimization_level << ": " << nodes_before << " -> "
                            << g.Nodes().size() << " nodes";
 
+  {
+    // static type / shape inference over the optimized graph: gives get_outputs() its shapes when the file declares none
+    // and fills value_info for tools; schema violations are worth a warning (strict mode makes them errors)
+    const bool strict = so_.config.Get("session.strict_shape_type_inference", "0") == "1";
+    InferenceReport rep = InferShapes(g, strict);
+    for (auto& p : rep.problems) ORTB_LOG(logger_, kWarning) << "shape inference: " << p;
+    ORTB_LOG(logger_, kInfo) << "shape inference: " << rep.inferred << " of " << rep.nodes << " nodes fully resolved";
+  }
   if (!so_.optimized_model_filepath.empty()) model_->Save(so_.optimized_model_filepath);
 
   ApplyThreadingAndWarnings();

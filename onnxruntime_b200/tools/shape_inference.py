@@ -109,6 +109,24 @@ def infer_shapes(model: Union[str, bytes, ol.Model], dim_values: Optional[Dict[s
     return model
 
 
+def infer_shapes_static(model: Union[str, bytes, ol.Model], strict: bool = False) -> ol.Model:
+    """The same result without running anything: the runtime's per-operator shape functions (C++,
+    ``csrc/core/shape_inference*.cc``) walk the graph symbolically.  Dimensions they cannot resolve get ``unk__N``
+    names; operators without a shape function leave their outputs without a shape."""
+    from .. import _core
+    if isinstance(model, ol.Model):
+        data = model.serialize()
+    elif isinstance(model, (bytes, bytearray)):
+        data = bytes(model)
+    else:
+        with open(model, "rb") as f:
+            data = f.read()
+    out, report = _core.infer_shapes(data, strict)
+    m = ol.load_model(out)
+    m.shape_inference_report = report
+    return m
+
+
 def _torch_type(t) -> int:
     import torch
     return {torch.bfloat16: 16, torch.float16: 10, torch.float32: 1, torch.float64: 11, torch.int64: 7, torch.int32: 6,
@@ -120,9 +138,10 @@ def main(argv=None) -> int:
     ap.add_argument("input")
     ap.add_argument("output")
     ap.add_argument("--dim", action="append", default=[], help="name=value for a symbolic input dimension")
+    ap.add_argument("--static", action="store_true", help="use the per-operator shape functions instead of tracing two runs")
     a = ap.parse_args(argv)
     dims = {k: int(v) for k, v in (d.split("=") for d in a.dim)}
-    m = infer_shapes(a.input, dims)
+    m = infer_shapes_static(a.input) if a.static else infer_shapes(a.input, dims)
     with open(a.output, "wb") as f:
         f.write(m.serialize())
     print(f"{len(m.graph.value_info)} value_info entries")
