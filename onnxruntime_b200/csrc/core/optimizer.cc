@@ -1,4 +1,5 @@
 #include "optimizer.h"
+#include "shape_inference.h"
 
 #include <cmath>
 
@@ -168,6 +169,7 @@ const std::vector<Pass>& AllPasses() {
     std::vector<Pass> v;
     AddBasicPasses(v);
     AddFusionPasses(v);
+    AddMorePasses(v);  // after the transformer fusions: those match the un-simplified MatMul / Add / Softmax forms
     AddGpuPasses(v);
     return v;
   }();
@@ -209,6 +211,8 @@ OptimizerStats OptimizeGraph(Graph& g, int level, const std::set<std::string>& d
                              const ConfigOptions& config, int world_size) {
   OptimizerStats stats;
   if (level <= 0) return stats;
+  // several rules ask for ranks and element types: resolve what can be resolved statically first
+  InferShapes(g, false);
   opt::PassContext ctx{g, gpu, config, world_size};
   int loops = 1;
   const std::string loop_cfg = config.Get("session.graph_optimizations_loop_level", "1");

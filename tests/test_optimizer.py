@@ -298,4 +298,74 @@ def test_attention_fusion_understands_only_the_keep_mask_expansion():
     bias4 = np.zeros((2, 1, 1, 8), np.float32)
     bias4[0, ..., 6:] = -10000.0
     before, after = both(_attention_block(True, "additive"), dict(xs, bias4=bias4))
-    assert "Attention" not in after and after.get("Softmax") == 1
+    assert "Attention" not in after and after.get("Softmax", 0) + after.get("BiasSoftmax", 0) == 1
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# smaller rewrite rules (matmul_add_fusion, reshape_fusion, constant_sharing, bias_softmax_fusion, cast_elimination, ...)
+X2 = [ol.make_tensor_value_info("x", T.FLOAT, ["b", 16])]
+x2 = {"x": rng.randn(3, 16).astype(np.float32)}
+
+
+def test_matmul_add_becomes_gemm_for_2d_inputs_only():
+    inits = [c("W", rng.randn(16, 8)), c("bias", rng.randn(8))]
+    nodes = [ol.make_node("MatMul", ["x", "W"], ["m"]), ol.make_node("Add", ["m", "bias"], ["y"])]
+    before, after = both(graph_model(nodes, X2, Y, inits), x2)
+    assert after == {"Gemm": 1}
+    before, after = both(graph_model(nodes, X, Y, inits), xs)   # 3-D input: left alone
+    assert "Gemm" not in after
+
+
+def test_reshape_fusion_replaces_the_shape_gather_concat_target():
+    inits = [c("i0", 0, np.int64), c("i1", 1, np.int64), c("ax", [0], np.int64), c("hh", [4, 4], np.int64)]
+    nodes = [ol.make_node("Shape", ["x"], ["s"]), ol.make_node("Gather", ["s", "i0"], ["b"], axis=0), ol.make_node("Gather", ["s", "i1"], ["q"], axis=0),
+             ol.make_node("Unsqueeze", ["b", "ax"], ["b1"]), ol.make_node("Unsqueeze", ["q", "ax"], ["q1"]),
+             ol.make_node("Concat", ["b1", "q1", "hh"], ["target"], axis=0), ol.make_node("Reshape", ["x", "target"], ["y"])]
+    before, after = both(graph_model(nodes, X, Y, inits), xs)
+    assert after == {"Reshape": 1}
+
+
+def test_constant_sharing_cast_and_trivial_node_elimination():
+    inits = [c("e1", 1e-5), c("e2", 1e-5), c("st", [0], np.int64), c("en", [2 ** 31 - 1], np.int64), c("ax", [1], np.int64)]
+    nodes = [ol.make_node("Cast", ["x"], ["xc"], to=T.FLOAT), ol.make_node("Add", ["xc", "e1"], ["a"]), ol.make_node("Add", ["a", "e2"], ["b"]),
+             ol.make_node("Slice", ["b", "st", "en", "ax"], ["sl"]), ol.make_node("Relu", ["sl"], ["y"])]
+    model = graph_model(nodes, X, Y, inits)
+    before, after = both(model, xs)
+    assert after == {"Add": 2, "Relu": 1}
+    out, stats = C.optimize_model(model, 1, [], False)
+    assert stats.get("ConstantSharing") == 1 and stats.get("CastElimination") == 1 and stats.get("TrivialNodeElimination") == 1
+
+
+def test_bias_softmax_div_mul_not_where_relu_clip():
+    inits = [c("bias", rng.randn(8, 16)), c("one", 1.0), c("lo", -1.0), c("hi", 2.0)]
+    nodes = [ol.make_node("Add", ["x", "bias"], ["xb"]), ol.make_node("Softmax", ["xb"], ["p"], axis=-1),
+             ol.make_node("Div", ["one", "p"], ["inv"]), ol.make_node("Mul", ["inv", "x"], ["q"]),
+             ol.make_node("Greater", ["q", "one"], ["g"]), ol.make_node("Not", ["g"], ["ng"]), ol.make_node("Where", ["ng", "x", "q"], ["w"]),
+             ol.make_node("Relu", ["w"], ["r"]), ol.make_node("Clip", ["r", "lo", "hi"], ["y"])]
+    before, after = both(graph_model(nodes, X, Y, inits), xs)
+    assert after.get("BiasSoftmax") == 1 and "Softmax" not in after
+    assert after.get("Div") == 1 and "Mul" not in after
+    assert "Not" not in after and "Relu" not in after and after.get("Clip") == 1
+
+
+def test_transpose_pairs_and_gemm_transposes():
+    inits = [c("W", rng.randn(8, 16))]
+    nodes = [ol.make_node("Transpose", ["x"], ["t1"], perm=[0, 2, 1]), ol.make_node("Transpose", ["t1"], ["t2"], perm=[0, 2, 1]),
+             ol.make_node("Transpose", ["t2"], ["t3"], perm=[1, 0, 2]), ol.make_node("Transpose", ["t3"], ["t4"], perm=[0, 2, 1]),
+             ol.make_node("Relu", ["t4"], ["y"])]
+    before, after = both(graph_model(nodes, X, Y, []), xs)
+    assert after == {"Transpose": 1, "Relu": 1}
+    nodes = [ol.make_node("Transpose", ["W"], ["wt"], perm=[1, 0]), ol.make_node("Transpose", ["x"], ["xt"], perm=[1, 0]),
+             ol.make_node("Transpose", ["xt"], ["xtt"], perm=[1, 0]), ol.make_node("Gemm", ["xtt", "wt"], ["y"])]
+    # W is a graph input here so that constant folding does not remove the Transpose first
+    ins = X2 + [ol.make_tensor_value_info("W", T.FLOAT, [8, 16])]
+    before, after = both(graph_model(nodes, ins, Y, []), dict(x2, W=rng.randn(8, 16).astype(np.float32)))
+    assert after == {"Gemm": 1}
+
+
+def test_double_qdq_pair_removed():
+    inits = [c("s", 0.02), ol.make_tensor("z", np.array(128, np.uint8))]
+    nodes = [ol.make_node("QuantizeLinear", ["x", "s", "z"], ["q1"]), ol.make_node("DequantizeLinear", ["q1", "s", "z"], ["d1"]),
+             ol.make_node("QuantizeLinear", ["d1", "s", "z"], ["q2"]), ol.make_node("DequantizeLinear", ["q2", "s", "z"], ["y"])]
+    before, after = both(graph_model(nodes, X, Y, inits), xs)
+    assert after == {"QuantizeLinear": 1, "DequantizeLinear": 1}
