@@ -11,7 +11,7 @@
 // (collective/custom_reduce_impl.cu).
 //
 // Workspace layout (bytes from the base of each rank's buffer; see also ortb200_gemm_args):
-//   64, 68                 epoch / done words of this file's kernels
+//   64, 68, 72             epoch / done words of this file's kernels; polling-limit override (0 = default)
 //   [64 KiB, 256 KiB)      flags[src rank < 8][CTA < 4096] uint32
 //   [bytes / 2, bytes)     two halves used alternately by epoch parity; each half = [scatter area | result area]
 #include <cuda_runtime.h>
@@ -72,9 +72,13 @@ __device__ __forceinline__ bool cta_exchange_flags(const CollParams& p, unsigned
   if (threadIdx.x < p.world) {
     const unsigned int* f = reinterpret_cast<const unsigned int*>(static_cast<const uint8_t*>(p.peers[p.rank]) + kFlagsOffset) +
                             threadIdx.x * kFlagsPerRank + blockIdx.x;
+    // word 2 of this file's header (byte 72 of the local workspace) overrides the polling limit (0 = default);
+    // failure-detection tests set a small one so that a rank that never answers costs milliseconds
+    const unsigned int lim_override = *reinterpret_cast<const volatile unsigned int*>(static_cast<const uint8_t*>(p.peers[p.rank]) + 72);
+    const unsigned int limit = lim_override != 0 ? lim_override : kSpinLimit;
     unsigned int spins = 0;
     while (static_cast<int>(ld_acquire_sys(f) - value) < 0) {
-      if (++spins > kSpinLimit) {
+      if (++spins > limit) {
         s_ok = 0;
         if (p.status) atomicExch(p.status, kStatusTimeoutPeer);
         break;

@@ -55,3 +55,59 @@ def init_distributed(backend: Optional[str] = None, timeout_s: int = 600) -> Dis
 
 def single_process() -> DistInfo:
     return DistInfo("", 0, 1, 0)
+
+
+class RankLeft(RuntimeError):
+    """A peer announced that it is leaving (or stopped refreshing its heartbeat): no further collective may start."""
+
+
+class RankMonitor:
+    """Host-side failure detection between steps, over a key-value store every rank can reach.
+
+    The reference has nothing of the kind: its custom all-reduce barriers spin for ever
+    (onnxruntime/contrib_ops/cuda/collective/custom_reduce_impl.cu:113-135), so a dead peer hangs the GPU.  Here the
+    device-side waits are bounded, and this class keeps a rank from launching into a group that is no longer complete:
+    a rank calls ``leave()`` between steps (never with kernels or collectives in flight), and every rank calls
+    ``check()`` before its next launch.  ``beat()`` / ``max_silence_s`` add a heartbeat for ranks that die without
+    saying so.  The store is the one torch.distributed was initialised with, or any ``torch.distributed.Store``.
+    """
+
+    def __init__(self, rank: int, world_size: int, store=None, max_silence_s: float = 0.0, prefix: str = "ortb200/monitor"):
+        import time
+        self.rank, self.world, self.prefix, self.max_silence_s = rank, world_size, prefix, max_silence_s
+        if store is None:
+            store = dist.distributed_c10d._get_default_store()
+        self.store = store
+        self._time = time
+        self.beat()
+
+    def _key(self, kind: str, r: int) -> str:
+        return f"{self.prefix}/{kind}/{r}"
+
+    def beat(self) -> None:
+        self.store.set(self._key("beat", self.rank), repr(self._time.time()))
+
+    def leave(self, reason: str = "") -> None:
+        """Announce an orderly exit.  Call it between steps, after the device is idle."""
+        self.store.set(self._key("left", self.rank), reason or "left")
+
+    def departed(self):
+        """Ranks that left or have been silent for longer than ``max_silence_s`` (0 = heartbeats are not checked)."""
+        gone = []
+        now = self._time.time()
+        for r in range(self.world):
+            if r == self.rank:
+                continue
+            if self.store.check([self._key("left", r)]):
+                gone.append((r, self.store.get(self._key("left", r)).decode()))
+            elif self.max_silence_s > 0 and self.store.check([self._key("beat", r)]):
+                last = float(self.store.get(self._key("beat", r)).decode())
+                if now - last > self.max_silence_s:
+                    gone.append((r, f"silent for {now - last:.1f} s"))
+        return gone
+
+    def check(self) -> None:
+        self.beat()
+        gone = self.departed()
+        if gone:
+            raise RankLeft("; ".join(f"rank {r}: {why}" for r, why in gone))

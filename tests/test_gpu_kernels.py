@@ -377,3 +377,28 @@ def test_fused_allreduce_gives_up_on_a_silent_peer(K):
     torch.cuda.synchronize()
     assert status.item() == 0
     assert _rel(y, x.float() @ w.float().T) < 2e-2
+
+
+def test_symmetric_collective_gives_up_on_a_silent_peer(K):
+    """The same for the one-kernel collectives: rank 0 of a two-rank all-reduce whose peer never raises its flags (the
+    peer 'workspace' is a second local buffer).  The polling limit (header word at byte 72, set small here) runs out,
+    the status word reports the peer, the kernel returns, and a later single-GPU kernel is correct."""
+    nbytes = 8 << 20
+    ws = torch.zeros(nbytes, dtype=torch.uint8, device="cuda")
+    silent_peer = torch.zeros(nbytes, dtype=torch.uint8, device="cuda")
+    ws.view(torch.int32)[18] = 2000
+    x = torch.randn(4096, device="cuda").bfloat16()
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    K.symm_collective("allreduce", x, [ws.data_ptr(), silent_peer.data_ptr()], 0, nbytes, status=status)
+    t1.record()
+    torch.cuda.synchronize()
+    assert status.item() == 4
+    assert t0.elapsed_time(t1) < 1000.0
+    status.zero_()
+    a = torch.randn(8, 256, device="cuda").bfloat16()
+    w = (torch.randn(128, 256, device="cuda") * 0.1).bfloat16()
+    y = K.gemm(a, w, status=status)
+    torch.cuda.synchronize()
+    assert status.item() == 0 and _rel(y, a.float() @ w.float().T) < 2e-2
