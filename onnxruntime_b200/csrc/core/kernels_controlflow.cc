@@ -4,6 +4,10 @@
 // which create a sub-SessionState per body).
 #include <ATen/ATen.h>
 
+#include <ATen/CPUGeneratorImpl.h>
+
+#include <algorithm>
+#include <cmath>
 #include <mutex>
 
 #include "executor.h"
@@ -200,6 +204,237 @@ class ScanKernel final : public ControlFlowBase {
   mutable Body body_;
 };
 
+// ---------------------------------------------------------------------------------------------------------------
+// Generation as operators: com.microsoft GreedySearch / Sampling / BeamSearch drive a decoder body graph token by token
+// (reference: onnxruntime/contrib_ops/cpu/transformers/greedy_search.cc, sampling.cc, beam_search.cc, beam_search_scorer.cc,
+// logits_processor.h; device kernels contrib_ops/cuda/transformers/generation_cuda_impl.cu).  Supported here: the GPT
+// form (model_type 0).  The `decoder` body takes input_ids [R, S] int32, position_ids [R, S] int32, attention_mask
+// [R, total] int32 and one past state per layer [2, R, heads, past, head]; it returns logits [R, S, vocab] and the present
+// states, which the loop feeds back (beam search re-orders their rows).  All tensor work is ATen on the body's device.
+class GenerationKernel final : public ControlFlowBase {
+ public:
+  explicit GenerationKernel(const OpKernelInfo& info) : ControlFlowBase(info) {
+    const Node& n = info.node;
+    kind_ = n.op_type;
+    ORTB_ENFORCE_ARG(n.attr_i("model_type", 0) == 0, kind_, ": only the GPT form (model_type 0) is implemented");
+    decoder_ = MakeBody("decoder");
+    eos_ = n.attr_i("eos_token_id", -1);
+    pad_ = n.attr_i("pad_token_id", 0);
+    no_repeat_ngram_ = n.attr_i("no_repeat_ngram_size", 0);
+    early_stopping_ = n.attr_i("early_stopping", 0) != 0;
+    temperature_ = n.attr_f("temperature", 1.f);
+    top_p_ = n.attr_f("top_p", 0.f);
+    filter_value_ = n.attr_f("filter_value", -1e20f);
+    min_tokens_to_keep_ = n.attr_i("min_tokens_to_keep", 1);
+    presence_penalty_ = n.attr_f("presence_penalty", 0.f);
+    seed_ = n.attr_i("seed", 0);
+    const auto& ins = decoder_.graph->Inputs();
+    ORTB_ENFORCE_ARG(ins.size() >= 3, kind_, ": the decoder body needs input_ids, position_ids, attention_mask and past states");
+    layers_ = static_cast<int>(ins.size()) - 3;
+    if (layers_ > 0) {
+      const auto& d = ins[3].type.dims;
+      ORTB_ENFORCE_ARG(d.size() == 5 && d[2].has_value && d[4].has_value, kind_, ": past states must be [2, batch, heads, past, head] with static heads and head size");
+      heads_ = d[2].value;
+      head_size_ = d[4].value;
+      past_type_ = ToTorchType(ins[3].type.elem_type);
+    }
+  }
+
+  void Compute(Ctx& ctx) const override {
+    std::lock_guard<std::mutex> lk(mu_);
+    const bool beam = kind_ == "BeamSearch";
+    at::Tensor ids = ctx.RequiredInput(0).to(at::kLong);
+    ORTB_ENFORCE_ARG(ids.dim() == 2, kind_, ": input_ids must be [batch, sequence]");
+    auto scalar_i = [&](int i, int64_t dflt) { return ctx.HasInput(i) ? ctx.Input(i).cpu().reshape({-1})[0].item<int64_t>() : dflt; };
+    auto scalar_f = [&](int i, double dflt) { return ctx.HasInput(i) ? ctx.Input(i).cpu().to(at::kDouble).reshape({-1})[0].item<double>() : dflt; };
+    const int64_t B = ids.size(0), S0 = ids.size(1);
+    const int64_t max_length = scalar_i(1, S0 + 1), min_length = scalar_i(2, 0);
+    // input layout: BeamSearch (ids, max, min, num_beams, num_return_sequences, length_penalty, repetition_penalty, vocab_mask,
+    // prefix_vocab_mask, attention_mask); GreedySearch / Sampling (ids, max, min, repetition_penalty, vocab_mask, prefix_vocab_mask, attention_mask)
+    const int64_t K = beam ? scalar_i(3, 1) : 1, nrs = beam ? scalar_i(4, 1) : 1;
+    const double length_penalty = beam ? scalar_f(5, 1.0) : 1.0;
+    const double rep_penalty = scalar_f(beam ? 6 : 3, 1.0);
+    const int vm = beam ? 7 : 4, am = beam ? 9 : 6;
+    ORTB_ENFORCE_ARG(K >= 1 && nrs >= 1 && nrs <= K && max_length > S0, kind_, ": invalid num_beams / num_return_sequences / max_length");
+    at::Device dev = ids.device();
+    at::Tensor vocab_mask = ctx.HasInput(vm) ? ctx.Input(vm).to(dev) : at::Tensor();
+    at::Tensor mask = ctx.HasInput(am) ? ctx.Input(am).to(dev, at::kInt) : at::ones({B, S0}, at::TensorOptions().dtype(at::kInt).device(dev));
+    const int64_t R = B * K;
+    at::Tensor seqs = ids.repeat_interleave(K, 0);
+    mask = mask.repeat_interleave(K, 0);
+    // positions count the attended tokens (left padding keeps position 0 for the first real token)
+    at::Tensor pos = (mask.to(at::kLong).cumsum(1) - 1).clamp_min(0);
+    std::vector<at::Tensor> past(static_cast<size_t>(layers_));
+    for (auto& p : past) p = at::zeros({2, R, heads_, 0, head_size_}, at::TensorOptions().dtype(past_type_).device(dev));
+    at::Tensor step_ids = seqs, step_pos = pos;
+    at::Tensor beam_scores = at::zeros({B, K}, at::TensorOptions().dtype(at::kFloat).device(dev));
+    if (K > 1) beam_scores.narrow(1, 1, K - 1).fill_(-1e9f);
+    at::Tensor done = at::zeros({R}, at::TensorOptions().dtype(at::kBool).device(dev));
+    std::vector<std::vector<std::pair<double, at::Tensor>>> finished(static_cast<size_t>(B));
+    std::vector<bool> batch_done(static_cast<size_t>(B), false);
+    at::Generator gen = at::detail::createCPUGenerator(static_cast<uint64_t>(seed_));
+    int64_t V = 0;
+
+    for (int64_t step = 0; seqs.size(1) < max_length; ++step) {
+      std::vector<Value> in(static_cast<size_t>(3 + layers_));
+      in[0].t = step_ids.to(at::kInt);
+      in[1].t = step_pos.to(at::kInt);
+      in[2].t = mask;
+      for (int l = 0; l < layers_; ++l) in[static_cast<size_t>(3 + l)].t = past[static_cast<size_t>(l)];
+      std::vector<Value> out = RunBody(decoder_, ctx, in);
+      ORTB_ENFORCE(static_cast<int>(out.size()) >= 1 + layers_, kind_, ": the decoder body returned too few outputs");
+      at::Tensor logits = out[0].t;
+      logits = logits.select(1, logits.size(1) - 1).to(at::kFloat).clone();   // [R, V]
+      V = logits.size(1);
+      for (int l = 0; l < layers_; ++l) past[static_cast<size_t>(l)] = out[static_cast<size_t>(1 + l)].t;
+      // ---- logits processors, in the reference's order
+      const int64_t cur_len = seqs.size(1);
+      if (eos_ >= 0 && cur_len < min_length) logits.select(1, eos_).fill_(-INFINITY);
+      if (rep_penalty != 1.0) {
+        at::Tensor seen = logits.gather(1, seqs);
+        seen = at::where(seen < 0, seen * rep_penalty, seen / rep_penalty);
+        logits.scatter_(1, seqs, seen);
+      }
+      if (presence_penalty_ != 0.f) {
+        at::Tensor seen = at::zeros_like(logits).scatter_(1, seqs, 1.0);
+        logits = logits - seen * presence_penalty_;
+      }
+      if (no_repeat_ngram_ > 0 && cur_len + 1 >= no_repeat_ngram_) BanRepeatedNgrams(logits, seqs, no_repeat_ngram_);
+      if (vocab_mask.defined()) logits.masked_fill_(vocab_mask.reshape({1, -1}) == 0, -INFINITY);
+      if (ctx.HasInput(vm + 1) && step == 0) logits.masked_fill_(ctx.Input(vm + 1).to(dev).repeat_interleave(K, 0) == 0, -INFINITY);
+
+      at::Tensor next_tok, rows;
+      if (!beam) {
+        if (kind_ == "Sampling") {
+          at::Tensor sc = temperature_ > 0.f && temperature_ != 1.f ? logits / temperature_ : logits;
+          if (top_p_ > 0.f && top_p_ < 1.f) sc = TopPFilter(sc);
+          at::Tensor probs = at::softmax(sc, -1).cpu();
+          next_tok = at::multinomial(probs, 1, false, gen).reshape({-1}).to(dev);
+        } else {
+          next_tok = logits.argmax(-1);
+        }
+        next_tok = at::where(done, at::full_like(next_tok, pad_), next_tok);
+        if (eos_ >= 0) done = done | (next_tok == eos_);
+      } else {
+        // ---- beam scorer: 2K candidates per batch entry so that finished beams can be replaced
+        at::Tensor logp = at::log_softmax(logits, -1);
+        at::Tensor cand = (beam_scores.reshape({R, 1}) + logp).reshape({B, K * V});
+        auto top = at::topk(cand, 2 * K, 1);
+        at::Tensor ts = std::get<0>(top).cpu(), ti = std::get<1>(top).cpu();
+        at::Tensor new_scores = at::full({B, K}, -1e9f), new_src = at::zeros({B, K}, at::kLong), new_tok = at::full({B, K}, pad_, at::kLong);
+        auto tsa = ts.accessor<float, 2>();
+        auto tia = ti.accessor<int64_t, 2>();
+        const int64_t gen_len = cur_len + 1 - S0;
+        for (int64_t b = 0; b < B; ++b) {
+          if (batch_done[static_cast<size_t>(b)]) continue;
+          int64_t filled = 0;
+          for (int64_t rank = 0; rank < 2 * K && filled < K; ++rank) {
+            const int64_t src = tia[b][rank] / V, tok = tia[b][rank] % V;
+            if (eos_ >= 0 && tok == eos_) {
+              if (rank < K) {
+                at::Tensor hyp = at::cat({seqs[b * K + src], at::full({1}, eos_, seqs.options())});
+                finished[static_cast<size_t>(b)].emplace_back(tsa[b][rank] / std::pow(static_cast<double>(gen_len), length_penalty), hyp);
+              }
+              continue;
+            }
+            new_scores[b][filled] = tsa[b][rank];
+            new_src[b][filled] = src;
+            new_tok[b][filled] = tok;
+            ++filled;
+          }
+          auto& fin = finished[static_cast<size_t>(b)];
+          if (static_cast<int64_t>(fin.size()) >= K) {
+            std::vector<double> sc;
+            for (auto& f : fin) sc.push_back(f.first);
+            std::sort(sc.begin(), sc.end());
+            const double worst_kept = sc[sc.size() - static_cast<size_t>(K)];
+            const double best_open = new_scores[b].max().item<float>() / std::pow(static_cast<double>(gen_len), length_penalty);
+            if (early_stopping_ || worst_kept >= best_open) batch_done[static_cast<size_t>(b)] = true;
+          }
+        }
+        rows = (at::arange(B, at::kLong).unsqueeze(1) * K + new_src).reshape({-1}).to(dev);
+        seqs = seqs.index_select(0, rows);
+        mask = mask.index_select(0, rows);
+        pos = pos.index_select(0, rows);
+        for (auto& p : past) p = p.index_select(1, rows);
+        beam_scores = new_scores.to(dev);
+        next_tok = new_tok.reshape({-1}).to(dev);
+      }
+      seqs = at::cat({seqs, next_tok.unsqueeze(1)}, 1);
+      mask = at::cat({mask, at::ones({R, 1}, mask.options())}, 1);
+      step_pos = pos.select(1, pos.size(1) - 1).unsqueeze(1) + 1;
+      pos = at::cat({pos, step_pos}, 1);
+      step_ids = next_tok.unsqueeze(1);
+      if (!beam && eos_ >= 0 && done.all().item<bool>()) break;
+      if (beam && std::all_of(batch_done.begin(), batch_done.end(), [](bool d) { return d; })) break;
+    }
+
+    auto iopt = at::TensorOptions().dtype(at::kInt).device(dev);
+    if (!beam) {
+      at::Tensor outseq = at::full({B, max_length}, pad_, iopt);
+      outseq.narrow(1, 0, seqs.size(1)).copy_(seqs.to(at::kInt));
+      ctx.SetOutput(0, outseq);
+      return;
+    }
+    const int64_t gen_len = std::max<int64_t>(seqs.size(1) - S0, 1);
+    at::Tensor outseq = at::full({B, nrs, max_length}, pad_, iopt);
+    at::Tensor outscore = at::zeros({B, nrs}, at::TensorOptions().dtype(at::kFloat));
+    at::Tensor bs_cpu = beam_scores.cpu();
+    for (int64_t b = 0; b < B; ++b) {
+      auto hyps = finished[static_cast<size_t>(b)];
+      for (int64_t k = 0; k < K; ++k)  // open beams count as hypotheses of the current length
+        hyps.emplace_back(bs_cpu[b][k].item<float>() / std::pow(static_cast<double>(gen_len), length_penalty), seqs[b * K + k]);
+      std::stable_sort(hyps.begin(), hyps.end(), [](const auto& x, const auto& y) { return x.first > y.first; });
+      for (int64_t j = 0; j < nrs; ++j) {
+        const at::Tensor& h = hyps[static_cast<size_t>(j)].second;
+        const int64_t len = std::min<int64_t>(h.size(0), max_length);
+        outseq[b][j].narrow(0, 0, len).copy_(h.narrow(0, 0, len).to(at::kInt));
+        outscore[b][j] = hyps[static_cast<size_t>(j)].first;
+      }
+    }
+    ctx.SetOutput(0, outseq);
+    if (ctx.OutputCount() > 1) ctx.SetOutput(1, outscore.to(dev));
+  }
+
+ private:
+  // tokens that would complete an n-gram already present in the row are banned
+  static void BanRepeatedNgrams(at::Tensor& logits, const at::Tensor& seqs, int64_t n) {
+    const int64_t L = seqs.size(1);
+    if (n == 1) {
+      logits.scatter_(1, seqs, -INFINITY);
+      return;
+    }
+    at::Tensor grams = seqs.unfold(1, n, 1);                                   // [R, L - n + 1, n]
+    at::Tensor tail = seqs.narrow(1, L - (n - 1), n - 1).unsqueeze(1);          // [R, 1, n - 1]
+    at::Tensor hit = (grams.narrow(2, 0, n - 1) == tail).all(-1);              // [R, L - n + 1]
+    at::Tensor last = grams.select(2, n - 1);
+    at::Tensor ban = at::zeros_like(logits, at::kBool);
+    ban.scatter_(1, at::where(hit, last, at::zeros_like(last)), hit);
+    // position 0 of `ban` may have been written with false by the masked-out entries: restore real hits on token 0
+    at::Tensor zero_hit = (hit & (last == 0)).any(1);
+    ban.select(1, 0).copy_(zero_hit);
+    logits.masked_fill_(ban, -INFINITY);
+  }
+
+  at::Tensor TopPFilter(const at::Tensor& logits) const {
+    auto sorted = at::sort(logits, -1, /*descending=*/true);
+    at::Tensor sl = std::get<0>(sorted), idx = std::get<1>(sorted);
+    at::Tensor probs = at::softmax(sl, -1);
+    at::Tensor drop = (probs.cumsum(-1) - probs) > top_p_;   // the token that crosses the threshold stays
+    if (min_tokens_to_keep_ > 0) drop.narrow(1, 0, std::min<int64_t>(min_tokens_to_keep_, drop.size(1))).fill_(false);
+    sl = sl.masked_fill(drop, filter_value_);
+    return at::full_like(logits, filter_value_).scatter(1, idx, sl);
+  }
+
+  std::string kind_;
+  mutable Body decoder_;
+  int64_t eos_ = -1, pad_ = 0, no_repeat_ngram_ = 0, min_tokens_to_keep_ = 1, seed_ = 0, heads_ = 0, head_size_ = 0;
+  bool early_stopping_ = false;
+  float temperature_ = 1.f, top_p_ = 0.f, filter_value_ = -1e20f, presence_penalty_ = 0.f;
+  int layers_ = 0;
+  at::ScalarType past_type_ = at::kFloat;
+};
+
 template <typename K>
 void RegisterClass(KernelRegistry& r, const std::string& op, int since, std::vector<int> host) {
   KernelDef d;
@@ -218,6 +453,15 @@ void RegisterControlFlowKernels(KernelRegistry& r) {
   RegisterClass<IfKernel>(r, "If", 1, {0});
   RegisterClass<LoopKernel>(r, "Loop", 1, {0, 1});
   RegisterClass<ScanKernel>(r, "Scan", 9, {});
+  for (const char* op : {"GreedySearch", "Sampling", "BeamSearch"}) {
+    KernelDef d;
+    d.domain = kMSDomain;
+    d.op_type = op;
+    d.since_min = 1;
+    d.since_max = kMax;
+    d.factory = [](const OpKernelInfo& info) { return std::make_unique<GenerationKernel>(info); };
+    r.Register(std::move(d));
+  }
 }
 
 }  // namespace ortb

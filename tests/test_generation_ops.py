@@ -1,0 +1,138 @@
+"""com.microsoft GreedySearch / Sampling / BeamSearch over a decoder body graph, against a numpy restatement that
+recomputes the toy model from scratch at every step (so cache handling and beam re-ordering are really checked)."""
+import numpy as np
+import pytest
+
+import onnxruntime_b200 as ort
+from onnxruntime_b200 import onnx_lite as ol
+
+T = ol.TensorProto
+V, D, N, HD, MAXPOS = 23, 16, 2, 8, 64
+rng = np.random.RandomState(7)
+W = {"E": rng.randn(V, D).astype(np.float32), "P": (rng.randn(MAXPOS, D) * 0.3).astype(np.float32),
+     "Wv": (rng.randn(D, D) * 0.4).astype(np.float32), "Wo": (rng.randn(D, V) * 0.8).astype(np.float32)}
+
+
+def decoder_body():
+    i = lambda name, v: ol.make_tensor(name, np.asarray(v, np.int64))
+    inits = [ol.make_tensor(k, v) for k, v in W.items()] + [i("kv_shape", [0, 0, N, HD]), i("ax0", [0]), i("one", 1), i("axm1", [-1]), i("ax1", [1]),
+                                                             i("ctx_shape", [0, 0, D])]
+    n = ol.make_node
+    nodes = [n("Gather", ["E", "input_ids"], ["emb"]), n("Gather", ["P", "position_ids"], ["pe"]), n("Add", ["emb", "pe"], ["h"]),
+             n("MatMul", ["h", "Wv"], ["v"]), n("Reshape", ["v", "kv_shape"], ["v4"]), n("Transpose", ["v4"], ["vt"], perm=[0, 2, 1, 3]),
+             n("Unsqueeze", ["vt", "ax0"], ["vu"]), n("Concat", ["vu", "vu"], ["kv"], axis=0), n("Concat", ["past_0", "kv"], ["present_0"], axis=3),
+             n("Gather", ["present_0", "one"], ["vals"], axis=0), n("Transpose", ["vals"], ["vals_t"], perm=[0, 2, 1, 3]),
+             n("Reshape", ["vals_t", "ctx_shape"], ["vals2"]), n("Cast", ["attention_mask"], ["mf"], to=T.FLOAT), n("Unsqueeze", ["mf", "axm1"], ["m3"]),
+             n("Mul", ["vals2", "m3"], ["masked"]), n("ReduceSum", ["masked", "ax1"], ["num"], keepdims=1), n("ReduceSum", ["m3", "ax1"], ["den"], keepdims=1),
+             n("Div", ["num", "den"], ["ctx"]), n("Add", ["h", "ctx"], ["hc"]), n("Tanh", ["hc"], ["act"]), n("MatMul", ["act", "Wo"], ["logits"])]
+    ins = [ol.make_tensor_value_info("input_ids", T.INT32, ["r", "s"]), ol.make_tensor_value_info("position_ids", T.INT32, ["r", "s"]),
+           ol.make_tensor_value_info("attention_mask", T.INT32, ["r", "t"]), ol.make_tensor_value_info("past_0", T.FLOAT, [2, "r", N, "p", HD])]
+    outs = [ol.make_tensor_value_info("logits", T.FLOAT, ["r", "s", V]), ol.make_tensor_value_info("present_0", T.FLOAT, [2, "r", N, "t", HD])]
+    return ol.make_graph(nodes, "decoder", ins, outs, inits)
+
+
+def ref_logits(seq):
+    """last-position logits of the toy model for one full sequence (no cache)."""
+    seq = np.asarray(seq)
+    h = W["E"][seq] + W["P"][np.arange(len(seq))]
+    ctx = (h @ W["Wv"]).mean(0)
+    return np.tanh(h[-1] + ctx) @ W["Wo"]
+
+
+def session(op, inputs, outputs, **attrs):
+    node = ol.make_node(op, inputs, outputs, domain="com.microsoft", decoder=decoder_body(), model_type=0, **attrs)
+    gi = [ol.make_tensor_value_info("input_ids", T.INT32, ["b", "s"]), ol.make_tensor_value_info("max_length", T.INT32, [1])]
+    extra = {"min_length": (T.INT32, [1]), "num_beams": (T.INT32, [1]), "num_return_sequences": (T.INT32, [1]), "length_penalty": (T.FLOAT, [1]),
+             "repetition_penalty": (T.FLOAT, [1])}
+    for name in inputs[2:]:
+        if name:
+            gi.append(ol.make_tensor_value_info(name, *extra[name]))
+    g = ol.make_graph([node], "g", gi, [ol.make_tensor_value_info(o, 0, None) for o in outputs])
+    so = ort.SessionOptions()
+    return ort.InferenceSession(ol.make_model(g).serialize(), so, providers=["CPUExecutionProvider"])
+
+
+def test_greedy_search_matches_recomputation_with_eos_and_penalty():
+    eos, pad = 5, 0
+    sess = session("GreedySearch", ["input_ids", "max_length", "min_length", "repetition_penalty"], ["sequences"], eos_token_id=eos, pad_token_id=pad)
+    ids = np.array([[3, 9, 1, 4], [7, 7, 2, 11]], np.int32)
+    got = sess.run(None, {"input_ids": ids, "max_length": np.array([12], np.int32), "min_length": np.array([6], np.int32),
+                          "repetition_penalty": np.array([1.3], np.float32)})[0]
+    assert got.shape == (2, 12) and got.dtype == np.int32
+    for b in range(2):
+        seq, finished = list(ids[b]), False
+        while len(seq) < 12:
+            if finished:
+                seq.append(pad)
+                continue
+            lg = ref_logits(seq).astype(np.float64)
+            if len(seq) < 6:
+                lg[eos] = -np.inf
+            for t in set(seq):
+                lg[t] = lg[t] * 1.3 if lg[t] < 0 else lg[t] / 1.3
+            tok = int(np.argmax(lg))
+            seq.append(tok)
+            finished = tok == eos
+        np.testing.assert_array_equal(got[b], np.array(seq, np.int32))
+
+
+def test_sampling_is_seeded_and_respects_top_p():
+    sess = session("Sampling", ["input_ids", "max_length"], ["sequences"], eos_token_id=-1, pad_token_id=0, top_p=0.05, temperature=0.7, seed=11)
+    ids = np.array([[3, 9, 1, 4]], np.int32)
+    feeds = {"input_ids": ids, "max_length": np.array([10], np.int32)}
+    a, b = sess.run(None, feeds)[0], sess.run(None, feeds)[0]
+    np.testing.assert_array_equal(a, b)            # same seed, same draw
+    # with a nucleus this small only the most likely token survives: sampling degenerates to greedy
+    seq = list(ids[0])
+    while len(seq) < 10:
+        seq.append(int(np.argmax(ref_logits(seq))))
+    np.testing.assert_array_equal(a[0], np.array(seq, np.int32))
+
+
+def _ref_beam(ids, K, max_length, eos, length_penalty, nrs):
+    beams = [(0.0, list(ids))] + [(-1e9, list(ids))] * (K - 1)
+    finished, S0 = [], len(ids)
+    while len(beams[0][1]) < max_length:
+        cands = []
+        for bi, (sc, seq) in enumerate(beams):
+            lg = ref_logits(seq).astype(np.float64)
+            logp = lg - (np.log(np.exp(lg - lg.max()).sum()) + lg.max())
+            cands += [(sc + lp, bi, t) for t, lp in enumerate(logp)]
+        cands.sort(key=lambda c: -c[0])
+        gen_len = len(beams[0][1]) + 1 - S0
+        nxt = []
+        for rank, (sc, bi, t) in enumerate(cands[: 2 * K]):
+            if t == eos:
+                if rank < K:
+                    finished.append((sc / gen_len ** length_penalty, beams[bi][1] + [t]))
+                continue
+            nxt.append((sc, beams[bi][1] + [t]))
+            if len(nxt) == K:
+                break
+        beams = nxt
+        if len(finished) >= K:
+            worst = sorted(f[0] for f in finished)[-K]
+            if worst >= max(b[0] for b in beams) / gen_len ** length_penalty:
+                break
+    gen_len = max(len(beams[0][1]) - S0, 1)
+    hyps = finished + [(sc / gen_len ** length_penalty, seq) for sc, seq in beams]
+    hyps.sort(key=lambda h: -h[0])
+    return hyps[:nrs]
+
+
+def test_beam_search_matches_a_plain_python_beam_search():
+    eos = 5
+    sess = session("BeamSearch", ["input_ids", "max_length", "min_length", "num_beams", "num_return_sequences", "length_penalty"],
+                   ["sequences", "sequences_scores"], eos_token_id=eos, pad_token_id=0)
+    ids = np.array([[3, 9, 1], [12, 2, 8]], np.int32)
+    out = sess.run(None, {"input_ids": ids, "max_length": np.array([9], np.int32), "min_length": np.array([0], np.int32),
+                          "num_beams": np.array([3], np.int32), "num_return_sequences": np.array([2], np.int32),
+                          "length_penalty": np.array([1.0], np.float32)})
+    seqs, scores = out
+    assert seqs.shape == (2, 2, 9)
+    for b in range(2):
+        want = _ref_beam(ids[b], 3, 9, eos, 1.0, 2)
+        for j, (sc, seq) in enumerate(want):
+            padded = np.array(seq + [0] * (9 - len(seq)), np.int32)
+            np.testing.assert_array_equal(seqs[b, j], padded)
+            assert abs(scores[b, j] - sc) < 1e-3 * max(1.0, abs(sc))
