@@ -76,7 +76,8 @@ def rope_caches(cfg: LlamaConfig, device="cpu") -> Tuple[torch.Tensor, torch.Ten
 def build_llama(cfg: LlamaConfig, tp_rank: int = 0, tp_size: int = 1, external_weights: bool = False, seed: int = 0,
                 device: str = "cpu", with_argmax: bool = True, last_token_logits: bool = True,
                 weight_std: float = 0.02, shard_lm_head: bool = True, quant_bits: int = 0,
-                quant_block: int = 32, paged: bool = False) -> Tuple[bytes, Dict[str, torch.Tensor]]:
+                quant_block: int = 32, paged: bool = False, moe_experts: int = 0, moe_top_k: int = 2, ep_rank: int = 0,
+                ep_size: int = 1) -> Tuple[bytes, Dict[str, torch.Tensor]]:
     """Returns (ModelProto bytes, weights).  With ``external_weights`` the dict holds every weight (on
     ``device``) to pass to ``SessionOptions.add_external_initializers``; otherwise it is empty and the
     weights are embedded in the model.
@@ -92,7 +93,15 @@ def build_llama(cfg: LlamaConfig, tp_rank: int = 0, tp_size: int = 1, external_w
     ``cumulative_sequence_length`` and ``past_seqlens`` describing the packing (input order of
     onnxruntime/core/graph/contrib_ops/bert_defs.cc, PagedAttention); ``logits_indices`` [rows] picks the
     packed positions whose logits are wanted (the last token of every sequence), so the LM head runs on those
-    rows only."""
+    rows only.
+
+    ``moe_experts > 0`` replaces the dense SwiGLU block of every layer by a top-``moe_top_k`` softmax-routed mixture of
+    that many SwiGLU experts (the Mixtral shape): ``com.microsoft.MoE`` on one device, or ``com.microsoft.ShardedMoE``
+    holding experts ``[ep_rank * E / ep_size, (ep_rank + 1) * E / ep_size)`` when ``ep_size > 1`` (expert parallelism:
+    attention and router weights are replicated, every rank sees all tokens, as the operator's contract has it,
+    onnxruntime/contrib_ops/cuda/collective/sharded_moe.cc:54-189)."""
+    assert not (moe_experts and (tp_size > 1 or quant_bits)), "the mixture-of-experts form is dense and expert-parallel only"
+    assert moe_experts % max(ep_size, 1) == 0
     if paged:
         last_token_logits = False
     assert quant_bits in (0, 4)
@@ -246,18 +255,38 @@ def build_llama(cfg: LlamaConfig, tp_rank: int = 0, tp_size: int = 1, external_w
                                   [f"{p}.ln2_out", "", "", f"{p}.res2"], name=f"{p}.ln2", domain="com.microsoft",
                                   epsilon=cfg.rms_eps))
         residual = f"{p}.res2"
-        linear(f"{p}.ln2_out", f"{p}.mlp.gate_proj.weight", hidden, ffn, f"{p}.gate", f"{p}.gate_proj", shard=(1, tp_size))
-        linear(f"{p}.ln2_out", f"{p}.mlp.up_proj.weight", hidden, ffn, f"{p}.up", f"{p}.up_proj", shard=(1, tp_size))
-        nodes += [
-            ol.make_node("Sigmoid", [f"{p}.gate"], [f"{p}.gate_sig"], name=f"{p}.sigmoid"),
-            ol.make_node("Mul", [f"{p}.gate", f"{p}.gate_sig"], [f"{p}.gate_act"], name=f"{p}.silu"),
-            ol.make_node("Mul", [f"{p}.gate_act", f"{p}.up"], [f"{p}.mlp_h"], name=f"{p}.gate_mul"),
-        ]
-        linear(f"{p}.mlp_h", f"{p}.mlp.down_proj.weight", ffn, hidden, f"{p}.down_partial" if tp_size > 1 else f"{p}.down",
-               f"{p}.down_proj", shard=(0, tp_size))
-        if tp_size > 1:
-            nodes.append(ol.make_node("AllReduce", [f"{p}.down_partial"], [f"{p}.down"], name=f"{p}.down_allreduce",
-                                      domain="com.microsoft"))
+        if moe_experts:
+            el = moe_experts // ep_size
+            randn(f"{p}.moe.router.weight", (hidden, moe_experts))
+            nodes.append(ol.make_node("MatMul", [f"{p}.ln2_out", f"{p}.moe.router.weight"], [f"{p}.router_logits"], name=f"{p}.router"))
+            names = []
+            for nm, shape in (("fc1", (ffn, hidden)), ("fc2", (hidden, ffn)), ("fc3", (ffn, hidden))):
+                per_expert = []
+                for e in range(ep_rank * el, (ep_rank + 1) * el):
+                    gen.manual_seed(seed * 1000003 + zlib.crc32(f"{p}.moe.{nm}.{e}".encode()))
+                    w = (torch.randn(shape, generator=gen, device=device, dtype=torch.float32) * weight_std).to(dt)
+                    # MoE stores [out, in] per expert, ShardedMoE the older [in, out]
+                    per_expert.append(w if ep_size == 1 else w.t().contiguous())
+                add_weight(f"{p}.moe.{nm}", torch.stack(per_expert))
+                names.append(f"{p}.moe.{nm}")
+            attrs = dict(k=moe_top_k, activation_type="silu", normalize_routing_weights=1)
+            if ep_size > 1:
+                attrs["local_experts_start_index"] = ep_rank * el
+            nodes.append(ol.make_node("MoE" if ep_size == 1 else "ShardedMoE", [f"{p}.ln2_out", f"{p}.router_logits", names[0], "", names[1], "", names[2]],
+                                      [f"{p}.down"], name=f"{p}.moe", domain="com.microsoft", **attrs))
+        else:
+            linear(f"{p}.ln2_out", f"{p}.mlp.gate_proj.weight", hidden, ffn, f"{p}.gate", f"{p}.gate_proj", shard=(1, tp_size))
+            linear(f"{p}.ln2_out", f"{p}.mlp.up_proj.weight", hidden, ffn, f"{p}.up", f"{p}.up_proj", shard=(1, tp_size))
+            nodes += [
+                ol.make_node("Sigmoid", [f"{p}.gate"], [f"{p}.gate_sig"], name=f"{p}.sigmoid"),
+                ol.make_node("Mul", [f"{p}.gate", f"{p}.gate_sig"], [f"{p}.gate_act"], name=f"{p}.silu"),
+                ol.make_node("Mul", [f"{p}.gate_act", f"{p}.up"], [f"{p}.mlp_h"], name=f"{p}.gate_mul"),
+            ]
+            linear(f"{p}.mlp_h", f"{p}.mlp.down_proj.weight", ffn, hidden, f"{p}.down_partial" if tp_size > 1 else f"{p}.down",
+                   f"{p}.down_proj", shard=(0, tp_size))
+            if tp_size > 1:
+                nodes.append(ol.make_node("AllReduce", [f"{p}.down_partial"], [f"{p}.down"], name=f"{p}.down_allreduce",
+                                          domain="com.microsoft"))
         pending = f"{p}.down"
 
     lnf = ones("model.norm.weight", hidden)
@@ -287,7 +316,7 @@ def build_llama(cfg: LlamaConfig, tp_rank: int = 0, tp_size: int = 1, external_w
         nodes.append(ol.make_node("ArgMax", ["logits"], ["next_tokens"], name="greedy", axis=-1, keepdims=0))
         outputs.insert(1, ol.make_tensor_value_info("next_tokens", T.INT64, logits_shape))
     graph = ol.make_graph(nodes, "llama", inputs, outputs, inits)
-    meta = {"tp_rank": str(tp_rank), "tp_size": str(tp_size), "architecture": "llama"}
+    meta = {"tp_rank": str(tp_rank), "tp_size": str(tp_size), "architecture": "mixtral" if moe_experts else "llama"}
     model = ol.make_model(graph, opset=17, metadata=meta)
     return model.serialize(), weights
 

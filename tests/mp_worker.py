@@ -127,6 +127,34 @@ def case_sharded_moe_gpu(info, device, out):
     torch.save(res, os.path.join(out, f"rank{r}.pt"))
 
 
+def case_mixtral_ep(info, device, out):
+    """Mixtral-shaped decoder with expert parallelism (ShardedMoE per layer) against the single-rank MoE form."""
+    from onnxruntime_b200.models.generation import DecoderRunner
+    from onnxruntime_b200.models.llama import LlamaConfig, build_llama
+    r, w = info.rank, info.world_size
+    cfg = LlamaConfig.tiny(dtype="fp32" if device == "cpu" else "bf16", head_dim=64, hidden_size=128, ffn_size=256, num_layers=2, num_heads=4,
+                           num_kv_heads=2, max_seq_len=64)
+    dev = torch.device("cpu") if device == "cpu" else torch.device("cuda", info.local_rank)
+    if device == "cuda":
+        torch.cuda.set_device(info.local_rank)
+    model, _ = build_llama(cfg, weight_std=0.05, moe_experts=2 * w, ep_rank=r, ep_size=w)
+    sess = session(model, info, device)
+    if device == "cuda":
+        from onnxruntime_b200.parallel import symm
+        symm.attach(sess, symm.create_workspace(16 << 20))
+    ids = torch.randint(0, cfg.vocab_size, (2, 17), generator=torch.Generator().manual_seed(5))
+    run = DecoderRunner(sess, cfg, batch=2, max_len=64, device=dev)
+    run.prefill(ids)
+    res = {"logits": run.prefill_logits.float().cpu().clone(), "ops": sorted({n["op_type"] for n in sess.graph_nodes()})}
+    if r == 0:
+        full, _ = build_llama(cfg, weight_std=0.05, moe_experts=2 * w)
+        s1 = ort.InferenceSession(full, providers=["CPUExecutionProvider"] if device == "cpu" else [("CUDAExecutionProvider", {"device_id": str(info.local_rank)})])
+        r1 = DecoderRunner(s1, cfg, batch=2, max_len=64, device=dev)
+        r1.prefill(ids)
+        res["ref"] = r1.prefill_logits.float().cpu().clone()
+    torch.save(res, os.path.join(out, f"rank{r}.pt"))
+
+
 def case_llama_tp(info, device, out):
     from onnxruntime_b200.models.generation import DecoderRunner
     from onnxruntime_b200.models.llama import LlamaConfig, build_llama

@@ -82,3 +82,12 @@ def test_sharding_spec_algebra():
         C.parse_shard_spec("S[0]S[0]", [0, 1], [2])
     with pytest.raises(ort.InvalidArgument):
         C.shard_shape([7, 12], "S[0]R", [0, 1], [2])
+
+
+def test_mixtral_shaped_decoder_with_expert_parallelism(tmp_path):
+    """Two gloo ranks, two local experts each: the expert-parallel decoder reproduces the single-rank mixture."""
+    out = launch("mixtral_ep", "cpu", 2, tmp_path)
+    assert "ShardedMoE" in out[0]["ops"]
+    a, b, ref = out[0]["logits"], out[1]["logits"], out[0]["ref"]
+    assert (a - b).abs().max() == 0
+    assert (a - ref).abs().max() / ref.abs().max() < 1e-4

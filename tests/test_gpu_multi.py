@@ -72,3 +72,13 @@ def test_sharded_moe_fused_combine(tmp_path, n):
             assert (out[r][k]["fused"] - ref).abs().max() / scale < 3e-2, (r, k)
             assert (out[r][k]["plain"] - ref).abs().max() / scale < 3e-2, (r, k)
             assert torch.equal(out[r][k]["fused"], out[0][k]["fused"])  # replicated bit for bit
+
+
+@pytest.mark.parametrize("n", WORLDS)
+def test_mixtral_shaped_decoder_expert_parallel_gpu(tmp_path, n):
+    _need(n)
+    out = launch("mixtral_ep", "cuda", n, tmp_path)
+    ref = out[0]["ref"]
+    for r in range(n):
+        assert torch.equal(out[r]["logits"], out[0]["logits"])
+        assert (out[r]["logits"] - ref).abs().max() / ref.abs().max() < 5e-2
