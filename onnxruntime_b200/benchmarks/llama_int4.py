@@ -21,7 +21,7 @@ from .common import finish, report, setup, timed_ms
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--layers", type=int, default=80)
-    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--batch", default="8", help="decode batch size, or a comma-separated list measured on one loaded model")
     ap.add_argument("--context", type=int, default=1024)
     ap.add_argument("--block-size", type=int, default=256)
     ap.add_argument("--steps", type=int, default=32)
@@ -35,6 +35,7 @@ def main(argv=None) -> int:
     from onnxruntime_b200.models.generation import PagedDecoderRunner
     from onnxruntime_b200.models.llama import LlamaConfig, build_llama
 
+    batches = [int(b) for b in str(a.batch).split(",")]
     max_len = (a.context + a.steps + max(a.warmup, 3) + 8 + a.block_size - 1) // a.block_size * a.block_size
     make = LlamaConfig.llama3_70b if a.model == "70b" else LlamaConfig.llama3_8b
     cfg = make(max_seq_len=max_len, num_layers=a.layers)
@@ -49,23 +50,27 @@ def main(argv=None) -> int:
     torch.cuda.empty_cache()
     if world > 1:
         from onnxruntime_b200.parallel import symm
-        symm.attach(sess, symm.create_workspace())
-    runner = PagedDecoderRunner(sess, cfg, batch=a.batch, max_len=max_len, block_size=a.block_size, tp_size=world, device=device)
-    runner.assume_context(a.context)
-    tokens = torch.randint(0, cfg.vocab_size, (a.batch,), device=device)
-    before = sess.kernel_launch_count()
-    runner.decode_step(tokens)     # the first step runs eagerly (the session captures its graph afterwards): count it
-    launches = sess.kernel_launch_count() - before
-    runner.decode_step()
-    ms = timed_ms(lambda: runner.decode_step(), a.steps, a.warmup, world, device)
-    sess.check_device_status()
-    report(rank, metric="llama3_70b_int4_paged_decode_tokens_per_s" if a.model == "70b" and not a.dense else "paged_decode_tokens_per_s",
-           value=round(a.batch / ms * 1e3, 1), unit="tokens/s", n_gpus=world, ms_per_step=round(ms, 4),
-           weight_gb_per_rank=round(weight_bytes / 1e9, 2), weight_stream_gbs=round(weight_bytes / ms / 1e6, 1),
-           launches_per_step=launches, dtype="int4 weights (block 32, bf16 scales), bf16 activations" if not a.dense else "bf16",
-           impl="ours", data="synthetic",
-           config={"model": f"Llama-3-{a.model.upper()}", "layers": a.layers, "batch": a.batch, "context": a.context,
-                   "kv_block_size": a.block_size, "parallelism": f"tp{world}", "cuda_graph": not a.no_graph})
+        symm.attach(sess, symm.create_workspace(256 << 20))
+    for gi, batch in enumerate(batches):
+        runner = PagedDecoderRunner(sess, cfg, batch=batch, max_len=max_len, block_size=a.block_size, tp_size=world, device=device,
+                                    graph_id=1 + gi)
+        runner.assume_context(a.context)
+        tokens = torch.randint(0, cfg.vocab_size, (batch,), device=device)
+        before = sess.kernel_launch_count()
+        runner.decode_step(tokens)     # the first step runs eagerly (the session captures its graph afterwards): count it
+        launches = sess.kernel_launch_count() - before
+        runner.decode_step()
+        ms = timed_ms(lambda: runner.decode_step(), a.steps, a.warmup, world, device)
+        sess.check_device_status()
+        report(rank, metric="llama3_70b_int4_paged_decode_tokens_per_s" if a.model == "70b" and not a.dense else "paged_decode_tokens_per_s",
+               value=round(batch / ms * 1e3, 1), unit="tokens/s", n_gpus=world, ms_per_step=round(ms, 4),
+               weight_gb_per_rank=round(weight_bytes / 1e9, 2), weight_stream_gbs=round(weight_bytes / ms / 1e6, 1),
+               launches_per_step=launches, dtype="int4 weights (block 32, bf16 scales), bf16 activations" if not a.dense else "bf16",
+               impl="ours", data="synthetic",
+               config={"model": f"Llama-3-{a.model.upper()}", "layers": a.layers, "batch": batch, "context": a.context,
+                       "kv_block_size": a.block_size, "parallelism": f"tp{world}", "cuda_graph": not a.no_graph})
+        del runner
+        torch.cuda.empty_cache()
     finish(world)
     return 0
 

@@ -571,6 +571,9 @@ void MatMulNBitsImpl(Ctx& ctx) {
   at::Tensor w = DequantizeNBits(ctx.RequiredInput(1), ctx.RequiredInput(2), zp, N, K, bits, bs, at::kFloat);
   at::Tensor y = at::matmul(a.to(at::kFloat), w.t());
   if (ctx.HasInput(5)) y = y + ctx.Input(5).to(at::kFloat);
+  // extensions written by the GPU lowering passes: sum over the ranks first, then a residual (input 6)
+  if (n.attr_i("all_reduce", 0)) y = AllReduceSum(ctx.session(), y);
+  if (ctx.HasInput(6)) y = y + ctx.Input(6).to(at::kFloat);
   ctx.SetOutput(0, y.to(a.scalar_type()));
 }
 
@@ -822,6 +825,12 @@ void RegisterContribKernels(KernelRegistry& r) {
     if (n.attr_i("all_reduce", 0)) y = AllReduceSum(ctx.session(), y);
     if (ctx.HasInput(3)) y = y + ctx.Input(3);
     ctx.SetOutput(0, y);
+  });
+  r.RegisterFn("com.ortb200", "SwiGLU", 1, kMax, [](Ctx& ctx) {
+    // [..., 2 I] -> silu(x[..., :I]) * x[..., I:]
+    const at::Tensor& x = ctx.RequiredInput(0);
+    const int64_t I = x.size(-1) / 2;
+    ctx.SetOutput(0, at::silu(x.narrow(-1, 0, I)) * x.narrow(-1, I, I));
   });
   r.RegisterFn("com.ortb200", "GemmSwiGLU", 1, kMax, [normed_input](Ctx& ctx) {
     at::Tensor x = normed_input(ctx, 3);

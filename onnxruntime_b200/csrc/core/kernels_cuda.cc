@@ -364,6 +364,29 @@ class GemmSwiGLUKernel final : public OpKernel {
   int64_t I_ = 0;
 };
 
+// com.ortb200.SwiGLU: [..., 2 I] -> silu(x[..., :I]) * x[..., I:], one streaming kernel (behind the stacked gate | up
+// projection of 4-bit models).
+class SwiGLUKernel final : public OpKernel {
+ public:
+  explicit SwiGLUKernel(const OpKernelInfo& info) : OpKernel(info) {}
+  void Compute(Ctx& ctx) const override {
+    const at::Tensor& x = ctx.RequiredInput(0);
+    const int64_t I = x.size(-1) / 2;
+    at::Tensor x2 = x.reshape({-1, 2 * I}).contiguous();
+    std::vector<int64_t> shape = x.sizes().vec();
+    shape.back() = I;
+    if (!HalfType(x.scalar_type()) || I % 8 != 0 || x2.size(0) == 0) {
+      ctx.SetOutput(0, (at::silu(x2.narrow(1, 0, I)) * x2.narrow(1, I, I)).reshape(shape));
+      return;
+    }
+    at::Tensor y = at::empty({x2.size(0), I}, x.options());
+    CheckLaunch(ortb200_swiglu(x2.data_ptr(), y.data_ptr(), x2.size(0), static_cast<int>(I), DtypeCode(x.scalar_type()), ctx.cuda_stream()),
+                "ortb200_swiglu");
+    ctx.session()->AddLaunches(1);
+    ctx.SetOutput(0, y.reshape(shape));
+  }
+};
+
 template <typename K>
 void RegisterClass(KernelRegistry& r, const std::string& domain, const std::string& op,
                    std::function<bool(const Node&, const Graph&)> supports = nullptr, std::vector<int> host = {}) {
@@ -384,6 +407,7 @@ void RegisterCudaKernels(KernelRegistry& r) {
   RegisterClass<GemmKernel>(r, MS, "FusedMatMul", GemmSupports);
   RegisterClass<GemmKernel>(r, kFusedDomain, "FusedGemm", GemmSupports);
   RegisterClass<GemmSwiGLUKernel>(r, kFusedDomain, "GemmSwiGLU");
+  RegisterClass<SwiGLUKernel>(r, kFusedDomain, "SwiGLU");
   RegisterMoreCudaKernels(r);
   RegisterCudaKernels3(r);
 }

@@ -55,6 +55,7 @@ class MatMulNBitsKernel final : public WithFallback {
     N_ = n.attr_i("N", 0);
     bits_ = n.attr_i("bits", 4);
     block_ = n.attr_i("block_size", 32);
+    all_reduce_ = n.attr_i("all_reduce", 0) != 0;
     // decode path: re-arrange the nibbles once for the in-kernel expansion (4-bit, block >= 32, K % 64 == 0,
     // constant weights, integer zero points)
     const at::Tensor* B = info.constant_input(1);
@@ -78,13 +79,31 @@ class MatMulNBitsKernel final : public WithFallback {
   }
   void Compute(Ctx& ctx) const override {
     const at::Tensor& a = ctx.RequiredInput(0);
+    const bool reduce = all_reduce_ && ctx.session()->world_size > 1;
+    std::vector<int64_t> out_shape = a.sizes().vec();
+    out_shape.back() = N_;
+    at::Tensor res = ctx.HasInput(6) ? ctx.Input(6) : at::Tensor();
+    if (res.defined() && (res.sizes().vec() != out_shape || res.scalar_type() != a.scalar_type())) {
+      Fallback(ctx);  // a residual that needs broadcasting: the generic path adds it
+      return;
+    }
     if (packed_.defined() && a.scalar_type() == scales_.scalar_type() && a.numel() / K_ <= 64) {
       at::Tensor x2 = a.reshape({-1, K_}).contiguous();
       at::Tensor bias = ctx.HasInput(5) ? ctx.Input(5) : at::Tensor();
-      at::Tensor y = LaunchGemmQ4(ctx, x2, packed_, N_, bias, at::Tensor());
-      std::vector<int64_t> shape = a.sizes().vec();
-      shape.back() = N_;
-      ctx.SetOutput(0, y.reshape(shape));
+      at::Tensor res2 = res.defined() ? res.reshape({-1, N_}).contiguous() : at::Tensor();
+      at::Tensor y;
+      if (reduce && CanFuseAllReduce(ctx, x2.size(0), N_)) {
+        y = LaunchGemmQ4(ctx, x2, packed_, N_, bias, res2, /*fused_allreduce=*/true);
+      } else if (reduce) {
+        y = GemmAllReduce(ctx, LaunchGemmQ4(ctx, x2, packed_, N_, bias, at::Tensor()), res2);
+      } else {
+        y = LaunchGemmQ4(ctx, x2, packed_, N_, bias, res2);
+      }
+      ctx.SetOutput(0, y.reshape(out_shape));
+      return;
+    }
+    if (reduce || res.defined()) {
+      Fallback(ctx);
       return;
     }
     const at::Tensor& B = ctx.RequiredInput(1);
@@ -116,6 +135,7 @@ class MatMulNBitsKernel final : public WithFallback {
 
  private:
   int64_t K_ = 0, N_ = 0, bits_ = 4, block_ = 32;
+  bool all_reduce_ = false;
   at::Tensor packed_, scales_;
 };
 

@@ -293,9 +293,92 @@ int RmsNormGemmFusion(PassContext& c) {
   return count;
 }
 
+// ---- 4-bit weights (com.microsoft.MatMulNBits) in the GPU lowering.
+// (a) AllReduce(MatMulNBits(x, ...)) [+ residual Add]  ->  the MatMulNBits node carries all_reduce = 1 (and the residual
+//     as input 6): the decode kernel finishes the row-parallel sum over NVLink itself, so a tensor-parallel decode step
+//     holds no library collective and can be captured in a CUDA graph.
+// (b) Mul(silu(MatMulNBits(x, Wg)), MatMulNBits(x, Wu))  ->  one MatMulNBits over the stacked gate | up rows followed by
+//     com.ortb200.SwiGLU (a streaming kernel): two weight passes and three element-wise launches become two launches.
+int NBitsAllReduceFusion(PassContext& c) {
+  Graph& g = c.g;
+  int count = 0;
+  if (c.world_size <= 1) return 0;
+  for (Node* ar : g.Nodes()) {
+    if (ar->op_type != "AllReduce" || ar->domain != kMSDomain || ar->inputs.size() != 1) continue;
+    Node* p = g.Producer(ar->inputs[0]);
+    if (!p || p->op_type != "MatMulNBits" || p->domain != kMSDomain || g.NumConsumers(p->outputs[0]) != 1 || p->has_input(5)) continue;
+    std::string out = ar->outputs[0], residual;
+    Node* add = SoleConsumer(g, out);
+    if (add && add->op_type == "Add" && add->domain.empty() && add->inputs.size() == 2) {
+      for (int s = 0; s < 2; ++s)
+        if (add->inputs[1 - s] == out && !g.GetConstant(add->inputs[s]) && add->inputs[s] != out) residual = add->inputs[s];
+    }
+    p->set_attr_i("all_reduce", 1);
+    if (!residual.empty()) {
+      p->inputs.resize(7);
+      p->inputs[6] = residual;
+      p->outputs[0] = add->outputs[0];
+      g.RemoveNode(add);
+    } else {
+      p->outputs[0] = out;
+    }
+    g.RemoveNode(ar);
+    g.Invalidate();
+    ++count;
+  }
+  return count;
+}
+
+int NBitsSwiGLUFusion(PassContext& c) {
+  Graph& g = c.g;
+  int count = 0;
+  for (Node* top : g.Nodes()) {
+    if (top->op_type != "Mul" || !top->domain.empty() || top->inputs.size() != 2) continue;
+    for (int s = 0; s < 2; ++s) {
+      Node* silu = g.Producer(top->inputs[s]);
+      Node* up = g.Producer(top->inputs[1 - s]);
+      if (!silu || !up) continue;
+      std::string gate_out;
+      Node* sig = nullptr;
+      if (!MatchSilu(g, silu, &gate_out, &sig)) continue;
+      Node* gate = g.Producer(gate_out);
+      auto is_q = [&](Node* n) { return n && n->op_type == "MatMulNBits" && n->domain == kMSDomain && n->inputs.size() >= 3 && !n->has_input(3) && !n->has_input(4) && !n->has_input(5); };
+      if (!is_q(gate) || !is_q(up) || gate->inputs[0] != up->inputs[0]) continue;
+      if (gate->attr_i("K", 0) != up->attr_i("K", 0) || gate->attr_i("N", 0) != up->attr_i("N", 0) || gate->attr_i("bits", 4) != up->attr_i("bits", 4) ||
+          gate->attr_i("block_size", 32) != up->attr_i("block_size", 32))
+        continue;
+      const at::Tensor *bg = g.GetConstant(gate->inputs[1]), *bu = g.GetConstant(up->inputs[1]);
+      const at::Tensor *sg = g.GetConstant(gate->inputs[2]), *su = g.GetConstant(up->inputs[2]);
+      if (!bg || !bu || !sg || !su || bg->sizes() != bu->sizes() || sg->sizes() != su->sizes()) continue;
+      if (g.NumConsumers(gate_out) != 2 || g.NumConsumers(up->outputs[0]) != 1 || g.NumConsumers(silu->outputs[0]) != 1) continue;
+      const int64_t I = gate->attr_i("N", 0);
+      const std::string bn = g.UniqueName(gate->inputs[1] + "_gate_up"), sn = g.UniqueName(gate->inputs[2] + "_gate_up");
+      g.AddInitializer(bn, at::cat({*bg, *bu}, 0).contiguous());
+      g.AddInitializer(sn, at::cat({sg->reshape({I, -1}), su->reshape({I, -1})}, 0).contiguous());
+      const std::string gu = g.UniqueName(top->outputs[0] + "_gate_up");
+      Node* mm = g.AddNode("MatMulNBits", {gate->inputs[0], bn, sn}, {gu}, kMSDomain, g.UniqueName("MatMulNBits_gate_up"));
+      mm->set_attr_i("K", gate->attr_i("K", 0));
+      mm->set_attr_i("N", 2 * I);
+      mm->set_attr_i("bits", gate->attr_i("bits", 4));
+      mm->set_attr_i("block_size", gate->attr_i("block_size", 32));
+      g.AddNode("SwiGLU", {gu}, {top->outputs[0]}, kFusedDomain, g.UniqueName("SwiGLU"));
+      g.RemoveNode(top);
+      g.RemoveNode(silu);
+      g.RemoveNode(sig);
+      g.RemoveNode(gate);
+      g.RemoveNode(up);
+      ++count;
+      break;
+    }
+  }
+  return count;
+}
+
 }  // namespace
 
 void AddGpuPasses(std::vector<Pass>& v) {
+  v.push_back({"NBitsSwiGLUFusion", 2, true, NBitsSwiGLUFusion});
+  v.push_back({"NBitsAllReduceFusion", 2, true, NBitsAllReduceFusion});
   v.push_back({"SwiGLUFusion", 2, true, SwiGLUFusion});
   v.push_back({"MatMulAllReduceFusion", 2, true, MatMulAllReduceFusion});
   v.push_back({"AllReduceResidualFusion", 2, true, AllReduceResidualFusion});

@@ -605,7 +605,7 @@ void RegisterBuiltinSchemas(std::map<std::string, OpSchema>& t) {
     if (!c.node.has_input(1) && out[1].has_value && N > 0) out[1] = Known(out[1].value / (N + 2 * Nk) * N);
     c.SetOutput(0, c.ElemType(0), out);
   });
-  Reg(t, MS, "MatMulNBits", 3, 6, MatMulNBits);
+  Reg(t, MS, "MatMulNBits", 3, 7, MatMulNBits);  // input 6: residual added by this runtime's GPU lowering
   Reg(t, MS, "FusedMatMul", 2, 2, FusedMatMul);
   Reg(t, MS, "TransposeMatMul", 2, 2, FusedMatMul);
   Reg(t, MS, "GemmFloat8", 2, 6, GemmFloat8);
@@ -630,6 +630,12 @@ void RegisterBuiltinSchemas(std::map<std::string, OpSchema>& t) {
   // ---- this runtime's fused operators
   Reg(t, FUSED, "FusedGemm", 2, 5, FusedGemm);
   Reg(t, FUSED, "GemmSwiGLU", 3, 4, FusedGemm);
+  Reg(t, FUSED, "SwiGLU", 1, 1, [](Ctx& c) {
+    if (!c.HasShape(0) || c.Rank(0) < 1) return;
+    Dims out = c.Dims(0);
+    out.back() = out.back().has_value ? Known(out.back().value / 2) : c.FreshDim();
+    c.SetOutput(0, c.ElemType(0), out);
+  });
 }
 
 }  // namespace ortb

@@ -153,7 +153,7 @@ class PagedDecoderRunner:
     shapes and addresses and is captured as one CUDA graph."""
 
     def __init__(self, session: InferenceSession, cfg: LlamaConfig, batch: int, max_len: int, block_size: int = 256,
-                 tp_size: int = 1, device: Optional[torch.device] = None):
+                 tp_size: int = 1, device: Optional[torch.device] = None, graph_id: int = 1):
         self.sess, self.cfg, self.batch, self.max_len, self.block_size = session, cfg, batch, max_len, block_size
         self.device = device if device is not None else (
             torch.device("cuda", torch.cuda.current_device()) if "CUDAExecutionProvider" in session.get_providers() else torch.device("cpu"))
@@ -170,7 +170,7 @@ class PagedDecoderRunner:
         self.has_argmax = "next_tokens" in [o.name for o in session.get_outputs()]
         self._decode_binding = None
         self._ro_decode = RunOptions()
-        self._ro_decode.add_run_config_entry("gpu_graph_id", "1")
+        self._ro_decode.add_run_config_entry("gpu_graph_id", str(graph_id))  # one captured graph per (session, shape)
         self._ro_prefill = RunOptions()
         self._ro_prefill.add_run_config_entry("gpu_graph_id", "-1")
         self.cur_len = 0

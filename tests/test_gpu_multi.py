@@ -82,3 +82,16 @@ def test_mixtral_shaped_decoder_expert_parallel_gpu(tmp_path, n):
     for r in range(n):
         assert torch.equal(out[r]["logits"], out[0]["logits"])
         assert (out[r]["logits"] - ref).abs().max() / ref.abs().max() < 5e-2
+
+
+@pytest.mark.parametrize("n", WORLDS)
+def test_llama_tp_int4_reduces_in_kernel_and_is_captured(tmp_path, n):
+    """4-bit weights under tensor parallelism: the row-parallel MatMulNBits nodes carry the all-reduce themselves, so the
+    decode step holds no library collective (no AllReduce node is left) and runs as a captured graph."""
+    _need(n)
+    out = launch("llama_tp", "cuda", n, tmp_path, extra_env={"ORTB200_TEST_FUSED": "1", "ORTB200_TEST_QUANT": "4"})
+    assert "AllReduce" not in out[0]["ops"] and "MatMulNBits" in out[0]["ops"] and "SwiGLU" in out[0]["ops"]
+    a, ref = out[0]["logits"], out[0]["ref"]
+    for r in range(1, n):
+        assert (a - out[r]["logits"]).abs().max() / a.abs().max() < 1e-6
+    assert (a - ref).abs().max() / ref.abs().max() < 0.06

@@ -369,3 +369,26 @@ def test_double_qdq_pair_removed():
              ol.make_node("QuantizeLinear", ["d1", "s", "z"], ["q2"]), ol.make_node("DequantizeLinear", ["q2", "s", "z"], ["y"])]
     before, after = both(graph_model(nodes, X, Y, inits), xs)
     assert after == {"QuantizeLinear": 1, "DequantizeLinear": 1}
+
+
+def test_nbits_gate_up_merge_and_swiglu_on_graph_level():
+    """4-bit gate / up projections sharing an input become one MatMulNBits over the stacked rows plus a streaming SwiGLU."""
+    import torch
+    torch.manual_seed(0)
+    K, I = 64, 96
+    def q4(seed):
+        g = torch.Generator().manual_seed(seed)
+        return (torch.randint(0, 256, (I, K // 32, 16), generator=g, dtype=torch.uint8), (torch.rand(I, K // 32, generator=g) * 0.02 + 0.01).half())
+    (bg, sg), (bu, su) = q4(1), q4(2)
+    nodes = [ol.make_node("MatMulNBits", ["x", "Bg", "Sg"], ["g"], domain="com.microsoft", K=K, N=I, bits=4, block_size=32),
+             ol.make_node("MatMulNBits", ["x", "Bu", "Su"], ["u"], domain="com.microsoft", K=K, N=I, bits=4, block_size=32),
+             ol.make_node("Sigmoid", ["g"], ["sg"]), ol.make_node("Mul", ["g", "sg"], ["act"]), ol.make_node("Mul", ["act", "u"], ["y"])]
+    model = graph_model(nodes, [ol.make_tensor_value_info("x", T.FLOAT16, ["b", K])], [ol.make_tensor_value_info("y", T.FLOAT16, None)],
+                        [ol.make_tensor("Bg", bg), ol.make_tensor("Sg", sg), ol.make_tensor("Bu", bu), ol.make_tensor("Su", su)])
+    out, stats = C.optimize_model(model, 99, [], True)
+    ops = [(n["op_type"], n["domain"]) for n in C.model_nodes(out)]
+    assert stats.get("NBitsSwiGLUFusion") == 1 and ops == [("MatMulNBits", "com.microsoft"), ("SwiGLU", "com.ortb200")]
+    x = (torch.randn(5, K) * 0.5).half().numpy()
+    a = ort.InferenceSession(model, providers=["CPUExecutionProvider"]).run(None, {"x": x})[0]
+    b = ort.InferenceSession(out, providers=["CPUExecutionProvider"]).run(None, {"x": x})[0]
+    np.testing.assert_allclose(a.astype(np.float32), b.astype(np.float32), rtol=2e-2, atol=2e-3)
