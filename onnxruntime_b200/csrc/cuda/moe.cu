@@ -136,6 +136,7 @@ __global__ void __launch_bounds__(128) moe_permute_kernel(const uint4* __restric
 }
 
 // One CTA per token: out[t] = sum_j w[t, j] * (y[row_of[t, j]] + bias[expert(t, j)]) in the order j = 0 .. k-1.
+// Rows move as 16-byte vectors (H is a multiple of 8), all k rows of a vector in flight before the first add.
 template <typename T>
 __global__ void __launch_bounds__(256) moe_combine_kernel(const T* __restrict__ y, const T* __restrict__ bias, int H, int k,
                                                           int expert_begin, const int* __restrict__ topk_idx,
@@ -143,16 +144,41 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const T* __restrict__ 
                                                           T* __restrict__ out) {
   pdl_wait_prior_grids();
   const int t = blockIdx.x;
-  for (int h = threadIdx.x; h < H; h += blockDim.x) {
-    float acc = 0.f;
-    for (int j = 0; j < k; ++j) {
-      const int row = row_of[t * k + j];
-      if (row < 0) continue;
-      float v = to_float<T>(y[static_cast<long long>(row) * H + h]);
-      if (bias) v += to_float<T>(bias[static_cast<long long>(topk_idx[t * k + j] - expert_begin) * H + h]);
-      acc += topk_w[t * k + j] * v;
+  constexpr int EPV = 16 / static_cast<int>(sizeof(T));
+  const int hvecs = H / EPV;
+  int rows[kMaxTopK];
+  float ws[kMaxTopK];
+  int experts[kMaxTopK];
+#pragma unroll
+  for (int j = 0; j < kMaxTopK; ++j) {
+    rows[j] = j < k ? row_of[t * k + j] : -1;
+    ws[j] = j < k ? topk_w[t * k + j] : 0.f;
+    experts[j] = j < k ? topk_idx[t * k + j] - expert_begin : 0;
+  }
+  for (int hv = threadIdx.x; hv < hvecs; hv += blockDim.x) {
+    uint4 v[kMaxTopK], b[kMaxTopK];
+#pragma unroll
+    for (int j = 0; j < kMaxTopK; ++j) {
+      v[j] = rows[j] >= 0 ? __ldg(reinterpret_cast<const uint4*>(y + static_cast<long long>(rows[j]) * H) + hv) : make_uint4(0u, 0u, 0u, 0u);
+      b[j] = (bias != nullptr && rows[j] >= 0) ? __ldg(reinterpret_cast<const uint4*>(bias + static_cast<long long>(experts[j]) * H) + hv)
+                                                : make_uint4(0u, 0u, 0u, 0u);
     }
-    out[static_cast<long long>(t) * H + h] = from_float<T>(acc);
+    float acc[EPV];
+#pragma unroll
+    for (int e = 0; e < EPV; ++e) acc[e] = 0.f;
+#pragma unroll
+    for (int j = 0; j < kMaxTopK; ++j) {
+      if (rows[j] < 0) continue;
+      const T* ve = reinterpret_cast<const T*>(&v[j]);
+      const T* be = reinterpret_cast<const T*>(&b[j]);
+#pragma unroll
+      for (int e = 0; e < EPV; ++e) acc[e] += ws[j] * (to_float<T>(ve[e]) + to_float<T>(be[e]));
+    }
+    uint4 o;
+    T* oe = reinterpret_cast<T*>(&o);
+#pragma unroll
+    for (int e = 0; e < EPV; ++e) oe[e] = from_float<T>(acc[e]);
+    reinterpret_cast<uint4*>(out + static_cast<long long>(t) * H)[hv] = o;
   }
 }
 
@@ -207,7 +233,8 @@ extern "C" int ortb200_moe_route(const ortb200_moe_route_args* a, ortb200_stream
 extern "C" int ortb200_moe_combine(const void* y, const void* bias, void* out, int tokens, int H, int k, int expert_begin,
                                    const int* topk_idx, const float* topk_w, const int* row_of, int dtype, ortb200_stream_t stream_) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-  if (!y || !out || !topk_idx || !topk_w || !row_of || tokens <= 0 || H <= 0 || k <= 0) return -1;
+  if (!y || !out || !topk_idx || !topk_w || !row_of || tokens <= 0 || H <= 0 || k <= 0 || k > kMaxTopK) return -1;
+  if (H % 8 != 0 || ((reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(bias)) & 15)) return -3;
   if (dtype == ORTB200_BF16)
     moe_combine_kernel<__nv_bfloat16><<<tokens, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(y), static_cast<const __nv_bfloat16*>(bias), H, k,
                                                                   expert_begin, topk_idx, topk_w, row_of, static_cast<__nv_bfloat16*>(out));
