@@ -30,6 +30,9 @@ namespace {
 constexpr int kBM = 128;
 constexpr int kBK = 64;
 constexpr int kThreads = 192;
+// Packed 4-bit weights: four more warps share the expansion (they take the odd k-blocks), and two CTAs per SM keep
+// four expansion warps on every SM sub-partition, so one warp's barrier waits and stores hide behind another's ALU work.
+constexpr int kThreadsNBits = 320;
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
@@ -78,8 +81,11 @@ __device__ __forceinline__ float act_apply(int act, float v) {
 }
 
 // NBITS: the weight tile arrives as packed 4-bit values (32 bytes per row and k-block, nibbles pre-arranged by
-// ortb200_nbits_prepack) and the four epilogue warps expand it to a swizzled 16-bit MMA operand in one of two
-// dequantisation buffers while the next stages are in flight.
+// ortb200_nbits_prepack).  Eight warps expand it to 16-bit values and store them straight into tensor memory
+// (thread r = weight row r = TMEM lane r, 32 columns of packed pairs per k-block); the MMA takes its A operand from
+// there.  Shared memory only carries the packed bytes and the token tile: an expanded copy in shared memory would be
+// written once and read once per k-block (32 KiB against 7 KiB of input), and that traffic, not the ALU work, was
+// the bound of the first version of this kernel.
 template <int BN, int STAGES, bool DUAL, bool NBITS = false>
 struct SmallSmem {
   // NBITS: one tile blob per k-block = 4096 bytes of nibbles + 128 x 2 scales + 128 x 2 zero points (4864 bytes,
@@ -92,16 +98,18 @@ struct SmallSmem {
   static constexpr int kPartOffset = 0;  // float part[kCols][128] re-uses the pipeline stages once the main loop is done
   static constexpr int kPartBytes = kCols * kBM * 4;
   static constexpr int kDqOffset = kStageBytes * STAGES;
-  static constexpr int kDqTileBytes = kBM * kBK * 2;
-  static constexpr int kNumDq = 4;  // expansion buffers: the expansion runs up to four k-blocks ahead of the MMA
-  static constexpr int kDqBytes = NBITS ? kNumDq * kDqTileBytes : 0;
+  static constexpr int kNumDq = 2;    // expansion buffers in tensor memory, one per set of expansion warps (four measured the same)
+  static constexpr int kDqCol0 = 64;  // first TMEM column of the buffers (the accumulator uses at most 64 columns)
+  static constexpr int kDqCols = kBK / 2;
+  static constexpr int kDqBytes = 0;
   static constexpr int kBarOffset = kDqOffset + kDqBytes;
   static_assert(kPartBytes <= kStageBytes * STAGES, "partial tile must fit in the drained pipeline stages");
-  static_assert(!NBITS || (kDqOffset % 1024 == 0 && kStageBytes % 1024 == 0), "swizzled tiles need 1 KiB alignment");
+  static_assert(!NBITS || kStageBytes % 1024 == 0, "swizzled tiles need 1 KiB alignment");
+  static_assert(!NBITS || kCols <= kDqCol0, "accumulator and expansion buffers overlap in tensor memory");
   static_assert(!(NBITS && DUAL), "the gated epilogue is not combined with packed weights");
   static constexpr int kRstdOffset = kBarOffset + 8 * (2 * STAGES + 1 + 8) + 16;  // float rstd[64] (fused RMS norm)
   static constexpr int kTotal = kRstdOffset + 64 * 4 + 1024;
-  static constexpr int kTmemCols = kCols < 32 ? 32 : kCols;
+  static constexpr int kTmemCols = NBITS ? 128 : (kCols < 32 ? 32 : kCols);
 };
 
 // ---- 4-bit expansion helpers.  A prepacked 32-bit word holds 8 weights: bits [4i, 4i+4) = weight 2i, bits
@@ -122,25 +130,42 @@ struct Nib<__half2> {
   __device__ static __half2 bcast(float v) { return __float2half2_rn(v); }
 };
 
-// 32 packed weights (four prepacked words) of one quantisation block -> four 16-byte chunks of 8 values each
+// 32 packed weights (four prepacked words) of one quantisation block -> four 16-byte chunks of 8 values each.
+// Per pair of weights: one shift, one three-input logic op ((w >> 4i) & 0x000F000F | magic), an exact subtraction of
+// (base + zero point) and the multiplication by the scale.  (Folding the last two into one fused multiply-add would
+// round -(base + zero point) * scale to the 16-bit type first: an error of up to half a quantisation step.)
+__device__ __forceinline__ uint32_t nib_pair(uint32_t w, int shift, uint32_t magic) {
+  uint32_t r;
+  asm("lop3.b32 %0, %1, 0x000F000F, %2, 0xEA;" : "=r"(r) : "r"(w >> shift), "r"(magic));  // (a & b) | c
+  return r;
+}
 template <typename T2>
-__device__ __forceinline__ void expand_words(const uint32_t w[4], T2 offset, T2 scale, uint4 out[4]) {
+__device__ __forceinline__ void expand_words(const uint32_t w[4], T2 zero, T2 scale, uint32_t out[16]) {
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
-    uint32_t r[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      const uint32_t bits = ((w[j] >> (4 * i)) & 0x000F000Fu) | Nib<T2>::kMagic;
+      const uint32_t bits = nib_pair(w[j], 4 * i, Nib<T2>::kMagic);
       T2 v = *reinterpret_cast<const T2*>(&bits);
-      v = __hmul2(__hsub2(v, offset), scale);  // (q - zp) exactly, then one rounding in the product
-      r[i] = *reinterpret_cast<const uint32_t*>(&v);
+      v = __hmul2(__hsub2(v, zero), scale);
+      out[4 * j + i] = *reinterpret_cast<const uint32_t*>(&v);
     }
-    out[j] = make_uint4(r[0], r[1], r[2], r[3]);
   }
 }
 
+#ifdef ORTB200_NBITS_TRACE
+__device__ unsigned long long g_nbits_trace[16];
+#define NB_T(i) do { if (tr) { long long c_ = clock64(); tacc[i] += c_ - tlast; tlast = c_; } } while (0)
+#define NB_DECL(cond) const bool tr = (cond); long long tacc[6] = {0, 0, 0, 0, 0, 0}; long long tlast = clock64()
+#define NB_DUMP(base, n) do { if (tr) for (int t_ = 0; t_ < (n); ++t_) g_nbits_trace[(base) + t_] = tacc[t_]; } while (0)
+#else
+#define NB_T(i) do {} while (0)
+#define NB_DECL(cond) do {} while (0)
+#define NB_DUMP(base, n) do {} while (0)
+#endif
+
 template <int BN, int STAGES, bool DUAL, bool NBITS = false>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(NBITS ? kThreadsNBits : kThreads, NBITS ? 2 : 1)
 gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
                    const SmallGemmParams p) {
   using S = SmallSmem<BN, STAGES, DUAL, NBITS>;
@@ -154,8 +179,7 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
   uint64_t* tmem_full_bar = empty_bar + STAGES;
   constexpr int NDQ = S::kNumDq;
   uint64_t* dq_full_bar = tmem_full_bar + 1;     // [NDQ] dequantised tile ready (128 arrivals)
-  uint64_t* dq_empty_bar = dq_full_bar + NDQ;    // [NDQ] MMAs reading the tile have finished
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(dq_empty_bar + NDQ);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(dq_full_bar + NDQ);
   float* s_rstd = reinterpret_cast<float*>(smem + S::kRstdOffset);
 
   const int warp = threadIdx.x >> 5;
@@ -191,7 +215,6 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
     mbar_init(tmem_full_bar, 1);
     for (int d = 0; d < NDQ; ++d) {
       mbar_init(&dq_full_bar[d], 128);
-      mbar_init(&dq_empty_bar[d], 1);
     }
     fence_mbar_init();
   }
@@ -223,19 +246,23 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
         uint8_t* st = smem + i * S::kStageBytes;
         tma_load_2d(st + S::kABytes * (DUAL ? 2 : 1), &tmap_x, &full_bar[i], (kb_begin + i) * kBK, m0);
       }
+      NB_DECL(NBITS && blockIdx.x == 5);
       for (int i = pre; i < nkb; ++i) {
         const int s = i % STAGES;
         if (!mbar_wait(&empty_bar[s], ((i / STAGES) - 1) & 1)) {
           if (p.status) atomicExch(p.status, kStatusTimeoutProducer);
           break;
         }
+        NB_T(0);
         uint8_t* st = smem + s * S::kStageBytes;
         mbar_expect_tx(&full_bar[s], NBITS ? S::kBlobBytes + S::kBBytes : S::kStageBytes);
         if (NBITS) bulk_load(st, static_cast<const uint8_t*>(p.nbits_blob) + (static_cast<long long>(blockIdx.x / C) * p.num_kb + kb_begin + i) * S::kBlobBytes, S::kBlobBytes, &full_bar[s]);
         else tma_load_2d_hint(st, &tmap_w, &full_bar[s], (kb_begin + i) * kBK, w_row0 + n0, pol_w);
         if (DUAL) tma_load_2d_hint(st + S::kABytes, &tmap_w, &full_bar[s], (kb_begin + i) * kBK, w_row0 + n0 + p.dual_offset, pol_w);
         tma_load_2d(st + S::kABytes * (DUAL ? 2 : 1), &tmap_x, &full_bar[s], (kb_begin + i) * kBK, m0);
+        NB_T(1);
       }
+      NB_DUMP(11, 2);
     }
   } else if (warp == 1) {
     if (lane == 0) {
@@ -244,19 +271,43 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
       // has finished.  Waiting for that grid here (an unbounded hardware wait that costs nothing once it is satisfied)
       // keeps a slow predecessor - a fused all-reduce waiting for a late rank - from running out this kernel's limits.
       pdl_wait_prior_grids();
+      NB_DECL(NBITS && blockIdx.x == 5);
+      if (NBITS) {
+        // Every k-block of the CTA passes through this one thread, which shares its scheduler with expansion warps:
+        // the loop keeps running counters instead of divisions and builds the descriptor once.  The expansion warps
+        // waited for the stage before they published the expanded tile, so the token tile that arrived on the same
+        // barrier is complete as well and is not waited for again.
+        const uint64_t bdesc0 = umma_desc_sw128(smem_u32(smem) + S::kABytes);
+        int s = 0, d = 0;
+        uint32_t dq_parity = 0, acc = 0;
+        for (int i = 0; i < nkb; ++i) {
+          if (!mbar_wait(&dq_full_bar[d], dq_parity)) {
+            if (p.status) atomicExch(p.status, kStatusTimeoutMma);
+            break;
+          }
+          NB_T(1);
+          tcgen05_fence_after();
+          const uint64_t bdesc = bdesc0 + static_cast<uint64_t>(s * (S::kStageBytes >> 4));
+          const uint32_t a_tmem = tmem_base + S::kDqCol0 + d * S::kDqCols;
+          umma_f16_ts(tmem_base, a_tmem, bdesc, idesc, acc);
+          acc = 1u;
+#pragma unroll
+          for (int k = 1; k < kBK / 16; ++k) umma_f16_ts(tmem_base, a_tmem + 8 * k, bdesc + 2 * k, idesc, 1u);
+          umma_commit(&empty_bar[s]);  // frees the stage and tells the expansion warps that the TMEM buffer is free
+          NB_T(2);
+          if (++s == STAGES) s = 0;
+          if (++d == NDQ) { d = 0; dq_parity ^= 1u; }
+        }
+      } else
       for (int i = 0; i < nkb; ++i) {
         const int s = i % STAGES;
         if (!mbar_wait(&full_bar[s], (i / STAGES) & 1)) {
           if (p.status) atomicExch(p.status, kStatusTimeoutMma);
           break;
         }
-        if (NBITS && !mbar_wait(&dq_full_bar[i % NDQ], (i / NDQ) & 1)) {
-          if (p.status) atomicExch(p.status, kStatusTimeoutMma);
-          break;
-        }
         tcgen05_fence_after();
         const uint32_t stage_addr = smem_u32(smem + s * S::kStageBytes);
-        const uint32_t a_addr = NBITS ? smem_u32(smem + S::kDqOffset + (i % NDQ) * S::kDqTileBytes) : stage_addr;
+        const uint32_t a_addr = stage_addr;
         const uint32_t b_addr = stage_addr + S::kABytes * (DUAL ? 2 : 1);
         const uint64_t adesc = umma_desc_sw128(a_addr);
         const uint64_t bdesc = umma_desc_sw128(b_addr);
@@ -268,8 +319,8 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
           for (int k = 0; k < kBK / 16; ++k) umma_f16(tmem_base + BN, a2desc + 2 * k, bdesc + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
         }
         umma_commit(&empty_bar[s]);
-        if (NBITS) umma_commit(&dq_empty_bar[i % NDQ]);
       }
+      NB_DUMP(8, 3);
       umma_commit(tmem_full_bar);  // also on the failure path, so the epilogue never waits for nothing
     }
   } else {
@@ -277,16 +328,20 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
     const int q = warp & 3;
     const int r = q * 32 + lane;
     const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+    const bool extra = warp >= 6;  // NBITS only: the second set of expansion warps, no part in the epilogue
     pdl_wait_prior_grids();  // same reason as in the MMA warp: no bounded wait may span the previous grid's run time
     if (NBITS) {
       // ---- weight expansion: thread r owns weight row r of the tile.  Per k-block it reads 32 packed bytes, two
       // scales and two zero points, and writes one 128-byte row of the swizzled MMA operand.
       bool dq_ok = true;
-      // one k-block: wait for the packed tile and a free expansion buffer, expand row r, publish
+      NB_DECL(blockIdx.x == 5 && r == 0 && !extra);
+      // one k-block: wait for the packed tile, expand row r in registers, wait for the buffer, store, publish
       auto expand_kblock = [&](int i) {
         const int s = i % STAGES, d = i % NDQ;
         if (dq_ok && !mbar_wait(&full_bar[s], (i / STAGES) & 1)) dq_ok = false;
-        if (dq_ok && i >= NDQ && !mbar_wait(&dq_empty_bar[d], ((i / NDQ) - 1) & 1)) dq_ok = false;
+        dq_ok = __all_sync(0xffffffffu, dq_ok);
+        NB_T(0);
+        uint32_t o[32];
         if (dq_ok) {
           const uint8_t* blob = smem + s * S::kStageBytes;
           const uint4* src = reinterpret_cast<const uint4*>(blob + r * 32);
@@ -305,32 +360,43 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
           const float z0 = static_cast<float>(zw & 0xffu), z1 = static_cast<float>(zw >> 8);
           const uint32_t w0[4] = {p0.x, p0.y, p0.z, p0.w};
           const uint32_t w1[4] = {p1.x, p1.y, p1.z, p1.w};
-          uint4 o0[4], o1[4];
           if (p.dtype == ORTB200_BF16) {
             using T2 = __nv_bfloat162;
-            expand_words<T2>(w0, Nib<T2>::bcast(Nib<T2>::kBase + z0), Nib<T2>::bcast(s0), o0);
-            expand_words<T2>(w1, Nib<T2>::bcast(Nib<T2>::kBase + z1), Nib<T2>::bcast(s1), o1);
+            expand_words<T2>(w0, Nib<T2>::bcast(Nib<T2>::kBase + z0), Nib<T2>::bcast(s0), o);
+            expand_words<T2>(w1, Nib<T2>::bcast(Nib<T2>::kBase + z1), Nib<T2>::bcast(s1), o + 16);
           } else {
             using T2 = __half2;
-            expand_words<T2>(w0, Nib<T2>::bcast(Nib<T2>::kBase + z0), Nib<T2>::bcast(s0), o0);
-            expand_words<T2>(w1, Nib<T2>::bcast(Nib<T2>::kBase + z1), Nib<T2>::bcast(s1), o1);
+            expand_words<T2>(w0, Nib<T2>::bcast(Nib<T2>::kBase + z0), Nib<T2>::bcast(s0), o);
+            expand_words<T2>(w1, Nib<T2>::bcast(Nib<T2>::kBase + z1), Nib<T2>::bcast(s1), o + 16);
           }
-          // 128-byte swizzle: 16-byte chunk c of row r lives at chunk position c ^ (r & 7)
-          uint8_t* dst = smem + S::kDqOffset + d * S::kDqTileBytes + r * 128;
-#pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            *reinterpret_cast<uint4*>(dst + ((c ^ (r & 7)) << 4)) = o0[c];
-            *reinterpret_cast<uint4*>(dst + (((4 + c) ^ (r & 7)) << 4)) = o1[c];
-          }
-          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy stores -> visible to the MMA
+        }
+        NB_T(2);
+        // The MMAs that read this buffer two k-blocks ago must have finished: their commit completed a phase of that
+        // k-block's stage barrier, and the phase after it cannot complete before this k-block has been expanded.
+        if (dq_ok && i >= NDQ && !mbar_wait(&empty_bar[(i - NDQ) % STAGES], ((i - NDQ) / STAGES) & 1)) dq_ok = false;
+        dq_ok = __all_sync(0xffffffffu, dq_ok);
+        NB_T(1);
+        if (dq_ok) {
+          tcgen05_fence_after();
+          const uint32_t t_a = t_lane + S::kDqCol0 + d * S::kDqCols;
+          tmem_st_x16_u32(t_a, o);
+          tmem_st_x16_u32(t_a + 16, o + 16);
+          tmem_st_wait();
+          tcgen05_fence_before();  // orders the stores before the arrival the MMA thread waits for
+          NB_T(3);
         }
         mbar_arrive(&dq_full_bar[d]);  // also on the failure path: the MMA warp must not wait for nothing
+        NB_T(5);
       };
 #pragma unroll 1
-      for (int i = 0; i < nkb; ++i) expand_kblock(i);
+      for (int i = extra ? 1 : 0; i < nkb; i += 2) expand_kblock(i);
       if (!dq_ok && p.status) atomicExch(p.status, kStatusTimeoutEpilogue);
+      NB_DUMP(0, 6);
+#ifdef ORTB200_NBITS_TRACE
+      if (tr) { g_nbits_trace[6] = (nkb + 1) / 2; g_nbits_trace[7] = nkb; }
+#endif
     }
-    if (p.rms_eps > 0.f) {
+    if (!extra && p.rms_eps > 0.f) {
       // Fused RMS normalisation: the weights carry gamma, so only 1 / rms(x[m, :]) is missing, and it is a per-token
       // factor that commutes with the GEMM.  These warps are idle while the weights stream, so they read the token
       // rows (a few KiB, L2 resident) and leave the factors in shared memory for the epilogue.
@@ -364,11 +430,11 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
       }
       asm volatile("bar.sync 2, 128;" ::: "memory");  // the four epilogue warps only
     }
-    if (!mbar_wait(tmem_full_bar, 0)) {
+    if (!extra && !mbar_wait(tmem_full_bar, 0)) {
       if (p.status) atomicExch(p.status, kStatusTimeoutEpilogue);
     }
     tcgen05_fence_after();
-    if (C > 1) {
+    if (!extra && C > 1) {
 #pragma unroll 1
       for (int c = 0; c < S::kCols; c += 16) {
         float v[16];
@@ -383,7 +449,7 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
   // every thread of every CTA in the cluster meets here: partial tiles are complete and visible
   if (C > 1) cluster_sync_all();
 
-  if (warp >= 2) {
+  if (warp >= 2 && warp < 6) {
     const int q = warp & 3;
     const int r = q * 32 + lane;
     const int n = n0 + r;
@@ -563,7 +629,7 @@ int launch_small(const CUtensorMap& tw, const CUtensorMap& tx, const SmallGemmPa
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
-  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.blockDim = dim3(NBITS ? kThreadsNBits : kThreads, 1, 1);
   cfg.dynamicSmemBytes = S::kTotal;
   cfg.stream = stream;
   cudaLaunchAttribute attrs[2];
@@ -644,9 +710,9 @@ int launch_gemm_smallm(const ortb200_gemm_args* a, int bn, cudaStream_t stream, 
   *cluster_out = cluster;
   if (nbits) {
     switch (bn) {
-      case 16: *stages_out = 6; return launch_small<16, 6, false, true>(tw, tx, p, grid, stream, pdl);
-      case 32: *stages_out = 4; return launch_small<32, 4, false, true>(tw, tx, p, grid, stream, pdl);
-      case 64: *stages_out = 3; return launch_small<64, 3, false, true>(tw, tx, p, grid, stream, pdl);
+      case 16: *stages_out = 12; return launch_small<16, 12, false, true>(tw, tx, p, grid, stream, pdl);
+      case 32: *stages_out = 10; return launch_small<32, 10, false, true>(tw, tx, p, grid, stream, pdl);
+      case 64: *stages_out = 8; return launch_small<64, 8, false, true>(tw, tx, p, grid, stream, pdl);
       default: return -8;
     }
   }
@@ -707,3 +773,9 @@ extern "C" int ortb200_gemm_grouped(const ortb200_gemm_grouped_args* a, ortb200_
   if (a->tile_rows >= 128) return ortb200::launch_gemm_grouped_large(a, static_cast<cudaStream_t>(stream));
   return ortb200::launch_gemm_grouped(a, static_cast<cudaStream_t>(stream));
 }
+
+#ifdef ORTB200_NBITS_TRACE
+extern "C" int ortb200_debug_nbits_trace(unsigned long long* out) {
+  return static_cast<int>(cudaMemcpyFromSymbol(out, ortb200::g_nbits_trace, sizeof(ortb200::g_nbits_trace)));
+}
+#endif
