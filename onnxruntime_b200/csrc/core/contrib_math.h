@@ -39,6 +39,10 @@ at::Tensor DequantizeQMoeWeights(const at::Tensor& w, const at::Tensor& scales, 
 at::Tensor RotaryBSNH(const at::Tensor& x, const at::Tensor& pos, const at::Tensor& cos_cache,
                       const at::Tensor& sin_cache, bool interleaved, int64_t rot_dim, float scale);
 
+// additive mask [B, 1, 1 or S, T] from the mask_index forms of the BERT Attention operator (lengths, end / start
+// positions, 2-D / 3-D / 4-D 0-1 masks); masked positions get `filter`
+at::Tensor AttentionMaskBias(const at::Tensor& mask_index, int64_t B, int64_t S, int64_t T, float filter, at::Device dev);
+
 struct GqaInputs {
   at::Tensor query, key, value, past_key, past_value, seqlens_k, cos_cache, sin_cache, position_ids, attention_bias,
       head_sink;

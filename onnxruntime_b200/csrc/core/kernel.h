@@ -153,6 +153,13 @@ void RegisterTensorKernels(KernelRegistry& r);
 void RegisterNnKernels(KernelRegistry& r);
 void RegisterContribKernels(KernelRegistry& r);
 void RegisterContribKernels2(KernelRegistry& r);
+void RegisterContribKernels3(KernelRegistry& r);
+void RegisterContribKernels4(KernelRegistry& r);
+// convolution / pooling with the attributes of `node` (kernels_nn.cc)
+at::Tensor ConvWithNodeAttrs(const Node& node, const at::Tensor& x, const at::Tensor& w, const c10::optional<at::Tensor>& bias);
+at::Tensor ConvTransposeWithNodeAttrs(const Node& node, const at::Tensor& x, const at::Tensor& w,
+                                      const c10::optional<at::Tensor>& bias, const std::vector<int64_t>* pads_override = nullptr);
+at::Tensor PoolWithNodeAttrs(const Node& node, at::Tensor x, bool is_max);
 void RegisterOnnxExtraKernels(KernelRegistry& r);
 void RegisterControlFlowKernels(KernelRegistry& r);
 void RegisterCollectiveKernels(KernelRegistry& r);

@@ -72,6 +72,8 @@ void EnsureKernelsRegistered() {
     RegisterNnKernels(g);
     RegisterContribKernels(g);
     RegisterContribKernels2(g);
+    RegisterContribKernels3(g);
+    RegisterContribKernels4(g);
     RegisterOnnxExtraKernels(g);
     RegisterControlFlowKernels(g);
     RegisterCollectiveKernels(g);

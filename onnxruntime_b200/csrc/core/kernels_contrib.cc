@@ -590,6 +590,10 @@ void MoeImpl(Ctx& ctx) {
 }  // namespace
 
 namespace contrib {
+at::Tensor AttentionMaskBias(const at::Tensor& mask_index, int64_t B, int64_t S, int64_t T, float filter, at::Device dev) {
+  return BertMask(mask_index, B, S, T, filter, dev);
+}
+
 // QMoE expert weights [E, rows, K * bits / 8] with symmetric scales per output row ([E, rows]) or per block along K
 // ([E, rows, K / block]) -> float [E, rows, K]
 at::Tensor DequantizeQMoeWeights(const at::Tensor& w, const at::Tensor& scales, int64_t bits, int64_t block) {

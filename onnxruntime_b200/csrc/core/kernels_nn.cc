@@ -443,6 +443,58 @@ void Attention23(Ctx& ctx) {
 
 }  // namespace
 
+// Shared with the contrib operators that wrap a convolution or a pooling (FusedConv, NhwcConv, QLinearAveragePool ...)
+at::Tensor ConvWithNodeAttrs(const Node& node, const at::Tensor& x, const at::Tensor& w, const c10::optional<at::Tensor>& bias) {
+  return ConvFloat(node, x, w, bias);
+}
+
+at::Tensor ConvTransposeWithNodeAttrs(const Node& node, const at::Tensor& x, const at::Tensor& w,
+                                      const c10::optional<at::Tensor>& bias, const std::vector<int64_t>* pads_override) {
+  std::vector<int64_t> kernel(w.sizes().slice(2).begin(), w.sizes().slice(2).end());
+  ConvAttrs a = ParseConv(node, x, kernel, true);
+  const int64_t nd = x.dim() - 2;
+  if (pads_override != nullptr) {
+    ORTB_ENFORCE_ARG(static_cast<int64_t>(pads_override->size()) == 2 * nd, "pads must have 2 * spatial rank entries");
+    for (int64_t i = 0; i < nd; ++i) {
+      a.pads_begin[i] = (*pads_override)[i];
+      a.pads_end[i] = (*pads_override)[i + nd];
+    }
+  }
+  // run without padding and crop: handles asymmetric pads uniformly
+  at::Tensor y = at::convolution(x, w, bias, a.strides, std::vector<int64_t>(nd, 0), a.dilations, true, a.output_padding, a.group);
+  for (int64_t i = 0; i < nd; ++i) {
+    const int64_t len = y.size(2 + i) - a.pads_begin[i] - a.pads_end[i];
+    ORTB_ENFORCE_ARG(len > 0, "ConvTranspose: pads remove the whole output");
+    y = y.narrow(2 + i, a.pads_begin[i], len);
+  }
+  return y.contiguous();
+}
+
+at::Tensor PoolWithNodeAttrs(const Node& n, at::Tensor x, bool is_max) {
+  std::vector<int64_t> kernel = n.attr_ints("kernel_shape");
+  const int64_t nd = x.dim() - 2;
+  ORTB_ENFORCE_ARG(static_cast<int64_t>(kernel.size()) == nd, "kernel_shape rank mismatch");
+  ConvAttrs a = ParseConv(n, x, kernel, false);
+  const bool ceil_mode = n.attr_i("ceil_mode", 0) != 0;
+  const bool include_pad = n.attr_i("count_include_pad", 0) != 0;
+  std::vector<int64_t> pad = a.pads_begin;
+  if (!Symmetric(a)) {
+    ORTB_ENFORCE_ARG(is_max || include_pad, "average pooling with asymmetric pads requires count_include_pad=1");
+    x = PadSpatial(x, a, is_max ? -std::numeric_limits<double>::infinity() : 0.0);
+    pad.assign(nd, 0);
+  }
+  if (is_max) {
+    if (nd == 1) return std::get<0>(at::max_pool1d_with_indices(x, kernel, a.strides, pad, a.dilations, ceil_mode));
+    if (nd == 2) return std::get<0>(at::max_pool2d_with_indices(x, kernel, a.strides, pad, a.dilations, ceil_mode));
+    if (nd == 3) return std::get<0>(at::max_pool3d_with_indices(x, kernel, a.strides, pad, a.dilations, ceil_mode));
+  } else {
+    if (nd == 1) return at::avg_pool1d(x, kernel, a.strides, pad, ceil_mode, include_pad);
+    if (nd == 2) return at::avg_pool2d(x, kernel, a.strides, pad, ceil_mode, include_pad);
+    if (nd == 3) return at::avg_pool3d(x, kernel, a.strides, pad, ceil_mode, include_pad);
+  }
+  ORTB_NOT_IMPLEMENTED("pooling with ", nd, " spatial dims");
+}
+
 void RegisterNnKernels(KernelRegistry& r) {
   r.RegisterFn("", "LayerNormalization", 1, kMax, [](Ctx& ctx) { LayerNormImpl(ctx, false); });
   r.RegisterFn("", "SimplifiedLayerNormalization", 1, kMax, [](Ctx& ctx) { LayerNormImpl(ctx, true); });

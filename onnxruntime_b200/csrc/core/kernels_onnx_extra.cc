@@ -131,10 +131,10 @@ void FinishRnn(Ctx& ctx, const RnnCommon& c, const std::vector<at::Tensor>& ys, 
   }
 }
 
-void LstmImpl(Ctx& ctx) {
+// W [D, 4H, I] (gate order i o f c), R [D, 4H, H]
+void LstmWithWeights(Ctx& ctx, const at::Tensor& W, const at::Tensor& R) {
   RnnCommon c = ParseRnn(ctx, 4, {"Sigmoid", "Tanh", "Tanh"});
-  const at::Tensor& W = ctx.RequiredInput(1);   // [D, 4H, I]  gate order i o f c
-  const at::Tensor& R = ctx.RequiredInput(2);   // [D, 4H, H]
+  c.H = R.size(2);
   const std::string dir = ctx.node().attr_s("direction", "forward");
   std::vector<at::Tensor> ys;
   std::vector<std::vector<at::Tensor>> finals;
@@ -165,6 +165,23 @@ void LstmImpl(Ctx& ctx) {
     finals.push_back(st);
   }
   FinishRnn(ctx, c, ys, finals);
+}
+
+void LstmImpl(Ctx& ctx) { LstmWithWeights(ctx, ctx.RequiredInput(1), ctx.RequiredInput(2)); }
+
+// DynamicQuantizeLSTM (contrib_ops/cpu/quantization/dynamic_quantize_lstm.cc): an LSTM whose W [D, I, 4H] and
+// R [D, H, 4H] arrive as 8-bit integers with per-direction or per-column scales / zero points (inputs 8 - 11).
+void DynamicQuantizeLstmImpl(Ctx& ctx) {
+  auto dequant = [&](int wi, int si, int zi) {
+    at::Tensor q = ctx.RequiredInput(wi).to(at::kFloat);            // [D, in, 4H]
+    at::Tensor scale = ctx.RequiredInput(si).to(at::kFloat);
+    at::Tensor zp = ctx.HasInput(zi) ? ctx.Input(zi).to(at::kFloat) : at::zeros_like(scale);
+    auto shape_for = [&](const at::Tensor& t) {
+      return t.dim() == 2 ? t.reshape({t.size(0), 1, t.size(1)}) : t.reshape({-1, 1, 1});
+    };
+    return ((q - shape_for(zp)) * shape_for(scale)).transpose(1, 2).contiguous();  // [D, 4H, in]
+  };
+  LstmWithWeights(ctx, dequant(1, 8, 9), dequant(2, 10, 11));
 }
 
 void GruImpl(Ctx& ctx) {
@@ -422,6 +439,7 @@ void RegisterOnnxExtraKernels(KernelRegistry& r) {
 
   // ---- recurrent layers
   r.RegisterFn("", "LSTM", 7, kMax, LstmImpl);
+  r.RegisterFn(kMSDomain, "DynamicQuantizeLSTM", 1, kMax, DynamicQuantizeLstmImpl);
   r.RegisterFn("", "GRU", 7, kMax, GruImpl);
   r.RegisterFn("", "RNN", 7, kMax, RnnImpl);
 

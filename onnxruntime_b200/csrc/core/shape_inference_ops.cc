@@ -626,6 +626,46 @@ void RegisterBuiltinSchemas(std::map<std::string, OpSchema>& t) {
   Reg(t, MS, "GreedySearch", 2, 7);
   Reg(t, MS, "Sampling", 2, 9);
   Reg(t, MS, "DecoderMaskedMultiHeadAttention", 1, 14, [](Ctx& c) { c.PassThrough(0, 0); });
+  // third / fourth batch of contrib operators: arity checks for all, shape functions where the output follows an input
+  Reg(t, MS, "DecoderMaskedSelfAttention", 3, 10, [](Ctx& c) { c.PassThrough(0, 0); });
+  Reg(t, MS, "LongformerAttention", 7, 7, [](Ctx& c) { c.PassThrough(0, 0); });
+  Reg(t, MS, "SparseAttention", 9, 11, [](Ctx& c) { c.PassThrough(0, 0); });
+  Reg(t, MS, "MRotaryEmbedding", 4, 4, Same);
+  Reg(t, MS, "LinearAttentionGate", 3, 4, Same);
+  Reg(t, MS, "CausalConvWithState", 2, 4, [](Ctx& c) { c.PassThrough(0, 0); });
+  Reg(t, MS, "LinearAttention", 3, 6);
+  Reg(t, MS, "GatedRelativePositionBias", 6, 7);
+  Reg(t, MS, "FusedConv", 2, 4, [](Ctx& c) { ConvLike(c, true); });
+  Reg(t, MS, "NhwcConv", 2, 3);
+  Reg(t, MS, "NhwcFusedConv", 2, 4);
+  Reg(t, MS, "NhwcMaxPool", 1, 1);
+  Reg(t, MS, "ConvTransposeWithDynamicPads", 2, 4);
+  Reg(t, MS, "FusedMatMulActivation", 2, 2, FusedMatMul);
+  Reg(t, MS, "GemmFastGelu", 2, 3, MatMul);
+  Reg(t, MS, "MaxpoolWithMask", 2, 2);
+  Reg(t, MS, "ExpandDims", 2, 2);
+  Reg(t, MS, "IsAllFinite", 1, 1 << 20);
+  Reg(t, MS, "CDist", 2, 2);
+  Reg(t, MS, "MurmurHash3", 1, 1);
+  Reg(t, MS, "CropAndResize", 4, 4);
+  Reg(t, MS, "SampleOp", 1, 1, Same);
+  Reg(t, MS, "ShrunkenGather", 2, 2, Gather);
+  Reg(t, MS, "TorchEmbedding", 2, 4);
+  Reg(t, MS, "BitmaskBiasDropout", 2, 5, [](Ctx& c) { c.PassThrough(0, 0); });
+  Reg(t, MS, "QLinearAveragePool", 4, 5);
+  Reg(t, MS, "QLinearGlobalAveragePool", 4, 5);
+  Reg(t, MS, "QLinearConcat", 5, 1 << 20);
+  Reg(t, MS, "QLinearSoftmax", 4, 5, [](Ctx& c) { c.PassThrough(0, 0); });
+  Reg(t, MS, "QLinearConvTranspose", 8, 9);
+  Reg(t, MS, "QLinearReduceMean", 4, 5);
+  Reg(t, MS, "QLinearWhere", 9, 9);
+  Reg(t, MS, "MulInteger", 3, 4);
+  Reg(t, MS, "ReduceSumInteger", 1, 1);
+  Reg(t, MS, "MatMulInteger16", 2, 2);
+  Reg(t, MS, "QAttention", 5, 9);
+  Reg(t, MS, "QEmbedLayerNormalization", 13, 18);
+  Reg(t, MS, "MatMulBlockQuantizedFp4Weight", 4, 6);
+  Reg(t, MS, "DynamicQuantizeLSTM", 12, 12);
 
   // ---- this runtime's fused operators
   Reg(t, FUSED, "FusedGemm", 2, 5, FusedGemm);

@@ -1,0 +1,238 @@
+"""com.microsoft contrib operators of the fourth batch (decoder-masked attentions, LongformerAttention,
+SparseAttention, GatedRelativePositionBias, MRotaryEmbedding, linear-attention family, QAttention) against numpy
+restatements of the definitions in docs/ContribOperators.md of the reference."""
+import numpy as np
+import pytest
+
+from helpers import run_node
+
+MS = "com.microsoft"
+rng = np.random.default_rng(4)
+
+
+def _softmax(x, axis=-1):
+    e = np.exp(x - x.max(axis, keepdims=True))
+    return e / e.sum(axis, keepdims=True)
+
+
+def test_decoder_masked_mha_self_attention_with_shared_cache_and_beams():
+    batch, beam, N, H, cap, past = 2, 2, 2, 4, 8, 3
+    B = batch * beam
+    q = rng.standard_normal((B, 1, N * H)).astype(np.float32)
+    k = rng.standard_normal((B, 1, N * H)).astype(np.float32)
+    v = rng.standard_normal((B, 1, N * H)).astype(np.float32)
+    pk = rng.standard_normal((B, N, cap, H)).astype(np.float32)
+    pv = rng.standard_normal((B, N, cap, H)).astype(np.float32)
+    ind = rng.integers(0, beam, (batch, beam, cap)).astype(np.int32)
+    mask = np.ones((B, past + 1), np.int32)
+    mask[1, 0] = 0
+    out, nk, nv = run_node("DecoderMaskedMultiHeadAttention",
+                           {"q": q, "k": k, "v": v, "mask": mask, "ab": None, "pk": pk, "pv": pv, "pl": np.array([past], np.int32),
+                            "bw": np.array([beam], np.int32), "ci": ind}, n_outputs=3, domain=MS, num_heads=N, past_present_share_buffer=1)
+    want = np.zeros((B, 1, N * H), np.float32)
+    for r in range(B):
+        b, j = divmod(r, beam)
+        for h in range(N):
+            keys = np.stack([pk[b * beam + ind[b, j, t], h, t] for t in range(past)] + [k[r, 0, h * H:(h + 1) * H]])
+            vals = np.stack([pv[b * beam + ind[b, j, t], h, t] for t in range(past)] + [v[r, 0, h * H:(h + 1) * H]])
+            s = keys @ q[r, 0, h * H:(h + 1) * H] / np.sqrt(H) + np.where(mask[r] != 0, 0.0, -10000.0)
+            want[r, 0, h * H:(h + 1) * H] = _softmax(s) @ vals
+    np.testing.assert_allclose(out, want, rtol=1e-4, atol=1e-5)
+    np.testing.assert_allclose(nk[:, :, past], k.reshape(B, N, H), rtol=0, atol=0)
+    np.testing.assert_array_equal(nk[:, :, :past], pk[:, :, :past])
+    np.testing.assert_allclose(nv[:, :, past], v.reshape(B, N, H), rtol=0, atol=0)
+
+
+def test_decoder_masked_mha_cross_attention_and_qk_output():
+    B, N, H, L = 2, 2, 4, 5
+    q = rng.standard_normal((B, 1, N * H)).astype(np.float32)
+    k = rng.standard_normal((B, N, L, H)).astype(np.float32)
+    v = rng.standard_normal((B, N, L, H)).astype(np.float32)
+    out, _, _, qk = run_node("DecoderMaskedMultiHeadAttention", {"q": q, "k": k, "v": v}, n_outputs=4, domain=MS, num_heads=N, output_qk=1)
+    s = np.einsum("bnh,bnlh->bnl", q.reshape(B, N, H), k) / np.sqrt(H)
+    np.testing.assert_allclose(qk.reshape(B, N, L), s, rtol=1e-4, atol=1e-5)
+    want = np.einsum("bnl,bnlh->bnh", _softmax(s), v).reshape(B, 1, N * H)
+    np.testing.assert_allclose(out, want, rtol=1e-4, atol=1e-5)
+
+
+def test_decoder_masked_self_attention_matches_attention_with_past():
+    B, N, H, past = 2, 2, 4, 3
+    hidden = N * H
+    x = rng.standard_normal((B, 1, hidden)).astype(np.float32)
+    w = (rng.standard_normal((hidden, 3 * hidden)) * 0.3).astype(np.float32)
+    b = rng.standard_normal(3 * hidden).astype(np.float32)
+    pst = rng.standard_normal((2, B, N, past, H)).astype(np.float32)
+    out, present = run_node("DecoderMaskedSelfAttention", {"x": x, "w": w, "b": b, "m": None, "past": pst}, n_outputs=2, domain=MS, num_heads=N)
+    ref, ref_present = run_node("Attention", {"x": x, "w": w, "b": b, "m": None, "past": pst}, n_outputs=2, domain=MS, num_heads=N, unidirectional=1)
+    np.testing.assert_allclose(out, ref, rtol=1e-4, atol=1e-5)
+    np.testing.assert_allclose(present, ref_present, rtol=1e-5, atol=1e-6)
+
+
+def test_longformer_attention_dense_restatement():
+    B, S, N, H, w = 1, 12, 2, 4, 2
+    hidden = N * H
+    x = rng.standard_normal((B, S, hidden)).astype(np.float32)
+    W = (rng.standard_normal((hidden, 3 * hidden)) * 0.3).astype(np.float32)
+    bias = rng.standard_normal(3 * hidden).astype(np.float32)
+    GW = (rng.standard_normal((hidden, 3 * hidden)) * 0.3).astype(np.float32)
+    gb = rng.standard_normal(3 * hidden).astype(np.float32)
+    mask = np.zeros((B, S), np.float32)
+    mask[0, -2:] = -10000.0
+    glob = np.zeros((B, S), np.int32)
+    glob[0, 0] = 1
+    (out,) = run_node("LongformerAttention", {"x": x, "w": W, "b": bias, "m": mask, "gw": GW, "gb": gb, "g": glob}, domain=MS, num_heads=N, window=w)
+    qkv, gqkv = x @ W + bias, x @ GW + gb
+    want = np.zeros((B, S, hidden), np.float32)
+    for h in range(N):
+        sl = lambda t, part: t[0, :, part * hidden + h * H: part * hidden + (h + 1) * H]
+        for i in range(S):
+            if glob[0, i]:
+                s = sl(gqkv, 1) @ sl(gqkv, 0)[i] / np.sqrt(H) + mask[0]
+                want[0, i, h * H:(h + 1) * H] = _softmax(s) @ sl(gqkv, 2)
+            else:
+                allowed = (np.abs(np.arange(S) - i) <= w) | (glob[0] != 0)
+                s = np.where(allowed, sl(qkv, 1) @ sl(qkv, 0)[i] / np.sqrt(H) + mask[0], -np.inf)
+                want[0, i, h * H:(h + 1) * H] = _softmax(s) @ sl(qkv, 2)
+    np.testing.assert_allclose(out, want, rtol=1e-4, atol=1e-5)
+
+
+def test_gated_relative_position_bias():
+    B, S, N, H, D = 2, 5, 3, 4, 8
+    q = rng.standard_normal((B, S, N * H)).astype(np.float32)
+    qb = rng.standard_normal(N * H).astype(np.float32)
+    rel = rng.standard_normal((1, N, S, S)).astype(np.float32)
+    w = rng.standard_normal((H, D)).astype(np.float32)
+    b = rng.standard_normal(D).astype(np.float32)
+    eco = rng.standard_normal((1, N, 1, 1)).astype(np.float32)
+    (out,) = run_node("GatedRelativePositionBias", {"q": q, "qb": qb, "rel": rel, "w": w, "b": b, "eco": eco}, domain=MS, num_heads=N)
+    ql = (q + qb).reshape(B, S, N, H).transpose(0, 2, 1, 3)
+    g = 1 / (1 + np.exp(-((ql @ w + b).reshape(B, N, S, 2, D // 2).sum(-1))))
+    gate = g[..., 0] * (g[..., 1] * eco.reshape(1, N, 1) - 1.0) + 2.0
+    np.testing.assert_allclose(out, gate[..., None] * rel, rtol=1e-4, atol=1e-5)
+
+
+@pytest.mark.parametrize("layout", [0, 1])
+def test_mrotary_embedding_sections(layout):
+    B, S, N, H = 1, 6, 2, 8
+    half, sec = H // 2, [2, 1, 1]
+    x = rng.standard_normal((B, S, N * H)).astype(np.float32)
+    pos = rng.integers(0, 16, (3, B, S)).astype(np.int64)
+    ang = np.arange(16)[:, None] * (1.0 / 10000 ** (np.arange(half) / half))[None, :]
+    cos, sin = np.cos(ang).astype(np.float32), np.sin(ang).astype(np.float32)
+    (out,) = run_node("MRotaryEmbedding", {"x": x, "p": pos, "c": cos, "s": sin}, domain=MS, mrope_section=sec, mrope_layout=layout, num_heads=N)
+    if layout == 0:
+        stream = [0] * sec[0] + [1] * sec[1] + [2] * sec[2]
+    else:
+        stream = [0] * half
+        for d in range(1, min(half, sec[1] * 3), 3):
+            stream[d] = 1
+        for d in range(2, min(half, sec[2] * 3), 3):
+            stream[d] = 2
+    want = np.zeros((B, S, N, H), np.float32)
+    xs = x.reshape(B, S, N, H)
+    for s in range(S):
+        c = np.array([cos[pos[stream[d], 0, s], d] for d in range(half)])
+        sn = np.array([sin[pos[stream[d], 0, s], d] for d in range(half)])
+        a, b = xs[0, s, :, :half], xs[0, s, :, half:]
+        want[0, s] = np.concatenate([a * c - b * sn, b * c + a * sn], -1)
+    np.testing.assert_allclose(out, want.reshape(B, S, N * H), rtol=1e-5, atol=1e-5)
+
+
+def test_causal_conv_with_state_chunked_equals_whole():
+    B, C, L, k = 2, 3, 7, 4
+    x = rng.standard_normal((B, C, L)).astype(np.float32)
+    w = rng.standard_normal((C, 1, k)).astype(np.float32)
+    b = rng.standard_normal(C).astype(np.float32)
+    y, st = run_node("CausalConvWithState", {"x": x, "w": w, "b": b}, n_outputs=2, domain=MS, activation="silu")
+    xp = np.concatenate([np.zeros((B, C, k - 1), np.float32), x], 2)
+    pre = np.stack([(xp[:, :, t:t + k] * w[None, :, 0]).sum(-1) + b for t in range(L)], -1)
+    np.testing.assert_allclose(y, pre / (1 + np.exp(-pre)), rtol=1e-4, atol=1e-5)
+    np.testing.assert_array_equal(st, xp[:, :, -(k - 1):])
+    y1, s1 = run_node("CausalConvWithState", {"x": x[:, :, :4].copy(), "w": w, "b": b}, n_outputs=2, domain=MS, activation="silu")
+    y2, s2 = run_node("CausalConvWithState", {"x": x[:, :, 4:].copy(), "w": w, "b": b, "p": s1}, n_outputs=2, domain=MS, activation="silu")
+    np.testing.assert_allclose(np.concatenate([y1, y2], 2), y, rtol=1e-4, atol=1e-5)
+    np.testing.assert_allclose(s2, st, rtol=0, atol=0)
+    _, sw = run_node("CausalConvWithState", {"x": x, "w": w, "b": b}, n_outputs=2, domain=MS, state_window=2)
+    assert sw.shape == (2, B, C, k - 1)
+    np.testing.assert_array_equal(sw[1], st)
+    np.testing.assert_array_equal(sw[0], xp[:, :, L - 2 + 1: L - 2 + k])
+
+
+@pytest.mark.parametrize("rule", ["linear", "gated", "delta", "gated_delta"])
+def test_linear_attention_recurrence(rule):
+    B, T, Hq, Hkv, dk, dv = 2, 5, 4, 2, 3, 4
+    q = rng.standard_normal((B, T, Hq * dk)).astype(np.float32)
+    k = rng.standard_normal((B, T, Hkv * dk)).astype(np.float32)
+    k /= np.linalg.norm(k.reshape(B, T, Hkv, dk), axis=-1, keepdims=True).repeat(dk, -1).reshape(B, T, Hkv * dk)
+    v = rng.standard_normal((B, T, Hkv * dv)).astype(np.float32)
+    past = rng.standard_normal((B, Hkv, dk, dv)).astype(np.float32)
+    decay = -np.abs(rng.standard_normal((B, T, Hkv))).astype(np.float32)
+    beta = rng.uniform(0, 1, (B, T, Hkv)).astype(np.float32)
+    feeds = {"q": q, "k": k, "v": v, "past": past,
+             "decay": decay if "gated" in rule else None, "beta": beta if "delta" in rule else None}
+    out, state = run_node("LinearAttention", feeds, n_outputs=2, domain=MS, q_num_heads=Hq, kv_num_heads=Hkv, update_rule=rule)
+    S = past.astype(np.float64).copy()
+    want = np.zeros((B, T, Hq, dv))
+    for t in range(T):
+        kt, vt = k[:, t].reshape(B, Hkv, dk), v[:, t].reshape(B, Hkv, dv)
+        if "gated" in rule:
+            S = S * np.exp(decay[:, t])[:, :, None, None]
+        if "delta" in rule:
+            pred = np.einsum("bhkv,bhk->bhv", S, kt)
+            S = S + beta[:, t][:, :, None, None] * kt[..., None] * (vt - pred)[:, :, None, :]
+        else:
+            S = S + kt[..., None] * vt[:, :, None, :]
+        qt = q[:, t].reshape(B, Hq, dk)
+        want[:, t] = np.einsum("bhk,bhkv->bhv", qt, np.repeat(S, Hq // Hkv, 1)) / np.sqrt(dk)
+    np.testing.assert_allclose(out, want.reshape(B, T, Hq * dv), rtol=1e-4, atol=1e-4)
+    np.testing.assert_allclose(state, S, rtol=1e-4, atol=1e-4)
+
+
+def test_linear_attention_gate():
+    a = rng.standard_normal((2, 3, 4)).astype(np.float16)
+    b = rng.standard_normal((2, 3, 4)).astype(np.float16)
+    dt = rng.standard_normal(4).astype(np.float32)
+    sc = -np.exp(rng.standard_normal(4)).astype(np.float32)
+    decay, beta = run_node("LinearAttentionGate", {"a": a, "dt": dt, "sc": sc, "b": b}, n_outputs=2, domain=MS)
+    z = a.astype(np.float32) + dt
+    np.testing.assert_allclose(decay.astype(np.float32), sc * np.log1p(np.exp(z)), rtol=2e-3, atol=2e-3)
+    np.testing.assert_allclose(beta.astype(np.float32), 1 / (1 + np.exp(-b.astype(np.float32))), rtol=2e-3, atol=2e-3)
+
+
+def test_sparse_attention_block_layout():
+    B, S, N, Nk, H, bs, blocks = 1, 8, 2, 1, 4, 2, 4
+    q = rng.standard_normal((B, S, N * H)).astype(np.float32)
+    k = rng.standard_normal((B, S, Nk * H)).astype(np.float32)
+    v = rng.standard_normal((B, S, Nk * H)).astype(np.float32)
+    cache = np.zeros((B, Nk, blocks * bs, H), np.float32)
+    layout = np.array([[[1, 0, 0, 0], [1, 1, 0, 0], [0, 1, 1, 0], [0, 1, 1, 1]],
+                       [[1, 0, 0, 0], [1, 1, 0, 0], [1, 1, 1, 0], [1, 0, 1, 1]]], bool)
+    rows = np.array([[0, 1, 3, 5, 8], [0, 1, 3, 6, 9]], np.int32)
+    cols = np.array([[0, 0, 1, 1, 2, 1, 2, 3, -1], [0, 0, 1, 0, 1, 2, 0, 2, 3]], np.int32)
+    out, pk, pv = run_node("SparseAttention", {"q": q, "k": k, "v": v, "pk": cache, "pv": cache.copy(), "r": rows, "c": cols,
+                                                "t": np.array([S], np.int32), "kl": np.array([S], np.int32)},
+                           n_outputs=3, domain=MS, num_heads=N, kv_num_heads=Nk, sparse_block_size=bs)
+    want = np.zeros((B, S, N, H), np.float32)
+    for h in range(N):
+        for i in range(S):
+            ok = np.array([j <= i and layout[h % 2, i // bs, j // bs] for j in range(S)])
+            s = np.where(ok, k[0].reshape(S, H) @ q[0, i, h * H:(h + 1) * H] / np.sqrt(H), -np.inf)
+            want[0, i, h] = _softmax(s) @ v[0].reshape(S, H)
+    np.testing.assert_allclose(out, want.reshape(B, S, N * H), rtol=1e-4, atol=1e-5)
+    np.testing.assert_allclose(pk[0, 0, :S], k[0], rtol=0, atol=0)
+
+
+def test_qattention_matches_float_attention_on_dequantised_operands():
+    B, S, N, H = 2, 4, 2, 4
+    hidden = N * H
+    xs, ws = np.float32(0.05), np.float32(0.02)
+    xq = rng.integers(0, 255, (B, S, hidden)).astype(np.uint8)
+    wq = rng.integers(-127, 127, (hidden, 3 * hidden)).astype(np.int8)
+    bias = rng.standard_normal(3 * hidden).astype(np.float32)
+    mask = np.array([4, 2], np.int32)
+    (out,) = run_node("QAttention", {"x": xq, "w": wq, "b": bias, "xs": xs, "ws": ws, "m": mask, "xz": np.uint8(128), "wz": np.int8(0)},
+                      domain=MS, num_heads=N)
+    x = (xq.astype(np.float32) - 128) * xs
+    w = wq.astype(np.float32) * ws
+    (ref,) = run_node("Attention", {"x": x, "w": w, "b": bias, "m": mask}, domain=MS, num_heads=N)
+    np.testing.assert_allclose(out, ref, rtol=1e-3, atol=1e-3)
