@@ -74,6 +74,7 @@ void EnsureKernelsRegistered() {
     RegisterContribKernels2(g);
     RegisterContribKernels3(g);
     RegisterContribKernels4(g);
+    RegisterContribKernels5(g);
     RegisterOnnxExtraKernels(g);
     RegisterControlFlowKernels(g);
     RegisterCollectiveKernels(g);

@@ -666,6 +666,10 @@ void RegisterBuiltinSchemas(std::map<std::string, OpSchema>& t) {
   Reg(t, MS, "QEmbedLayerNormalization", 13, 18);
   Reg(t, MS, "MatMulBlockQuantizedFp4Weight", 4, 6);
   Reg(t, MS, "DynamicQuantizeLSTM", 12, 12);
+  Reg(t, MS, "MatMulNBitsMlp", 8, 9);
+  Reg(t, MS, "MatMulNBitsQkv", 11, 12);
+  Reg(t, MS, "DecoderAttention", 12, 12, [](Ctx& c) { c.PassThrough(0, 0); });
+  Reg(t, MS, "BifurcationDetector", 3, 4);
 
   // ---- this runtime's fused operators
   Reg(t, FUSED, "FusedGemm", 2, 5, FusedGemm);

@@ -236,3 +236,90 @@ def test_qattention_matches_float_attention_on_dequantised_operands():
     w = wq.astype(np.float32) * ws
     (ref,) = run_node("Attention", {"x": x, "w": w, "b": bias, "m": mask}, domain=MS, num_heads=N)
     np.testing.assert_allclose(out, ref, rtol=1e-3, atol=1e-3)
+
+
+def _quant4(w, block=32):
+    """Symmetric-zero-point (8) 4-bit block quantisation in the MatMulNBits layout: B [N, blocks, block / 2], scales [N, blocks]."""
+    N, K = w.shape
+    blocks = K // block
+    wb = w.reshape(N, blocks, block)
+    scales = (np.abs(wb).max(-1) / 7.0).astype(np.float32)
+    q = np.clip(np.rint(wb / scales[..., None]) + 8, 0, 15).astype(np.uint8)
+    packed = (q[..., 0::2] | (q[..., 1::2] << 4)).astype(np.uint8)
+    deq = (q.astype(np.float32) - 8) * scales[..., None]
+    return packed, scales, deq.reshape(N, K)
+
+
+def test_matmul_nbits_mlp_and_qkv_with_rms_norm():
+    T, K, N = 3, 64, 32
+    a = rng.standard_normal((T, K)).astype(np.float32)
+    skip = rng.standard_normal((T, K)).astype(np.float32)
+    gamma = rng.standard_normal(K).astype(np.float32)
+    gB, gs, gw = _quant4(rng.standard_normal((N, K)).astype(np.float32))
+    uB, us, uw = _quant4(rng.standard_normal((N, K)).astype(np.float32))
+    gb = rng.standard_normal(N).astype(np.float32)
+    y, ssum = run_node("MatMulNBitsMlp", {"a": a, "skip": skip, "g": gamma, "gB": gB, "gs": gs, "gb": gb, "uB": uB, "us": us, "ub": None},
+                       n_outputs=2, domain=MS, K=K, N=N, bits=4, block_size=32, activation="silu", epsilon=1e-5)
+    x = a + skip
+    xn = x / np.sqrt((x ** 2).mean(-1, keepdims=True) + 1e-5) * gamma
+    gate = xn @ gw.T + gb
+    np.testing.assert_allclose(y, gate / (1 + np.exp(-gate)) * (xn @ uw.T), rtol=1e-4, atol=1e-4)
+    np.testing.assert_allclose(ssum, x, rtol=1e-6, atol=1e-6)
+    Nq, Nkv = 32, 16
+    qB, qs, qw = _quant4(rng.standard_normal((Nq, K)).astype(np.float32))
+    kB, ks, kw = _quant4(rng.standard_normal((Nkv, K)).astype(np.float32))
+    vB, vs, vw = _quant4(rng.standard_normal((Nkv, K)).astype(np.float32))
+    q, k, v = run_node("MatMulNBitsQkv", {"a": a, "skip": None, "g": gamma, "qB": qB, "qs": qs, "qb": None, "kB": kB, "ks": ks, "kb": None,
+                                          "vB": vB, "vs": vs, "vb": None}, n_outputs=3, domain=MS, K=K, Nq=Nq, Nkv=Nkv, bits=4, block_size=32)
+    an = a / np.sqrt((a ** 2).mean(-1, keepdims=True) + 1e-5) * gamma
+    np.testing.assert_allclose(q, an @ qw.T, rtol=1e-4, atol=1e-4)
+    np.testing.assert_allclose(k, an @ kw.T, rtol=1e-4, atol=1e-4)
+    np.testing.assert_allclose(v, an @ vw.T, rtol=1e-4, atol=1e-4)
+
+
+def test_decoder_attention_self_then_cached_step():
+    S, B, N, H = 3, 2, 2, 4
+    hidden = N * H
+    x = rng.standard_normal((S, B, hidden)).astype(np.float32)
+    qw = (rng.standard_normal((hidden, hidden)) * 0.3).astype(np.float32)
+    kvw = (rng.standard_normal((hidden, 2 * hidden)) * 0.3).astype(np.float32)
+    bias = rng.standard_normal(3 * hidden).astype(np.float32)
+    f, t = np.array(False), np.array(True)
+    out, kc, vc = run_node("DecoderAttention", {"q": x, "k": x, "qw": qw, "kvw": kvw, "b": bias, "m": None, "kc": None, "vc": None,
+                                                "static_kv": f, "use_past": f, "has_layer_state": f, "has_mask": f}, n_outputs=3, domain=MS, num_heads=N)
+
+    def heads(z):
+        return z.reshape(z.shape[0], B, N, H).transpose(1, 2, 0, 3)
+    q = heads(x @ qw + bias[:hidden])
+    kv = x @ kvw + bias[hidden:]
+    k, v = heads(kv[..., :hidden]), heads(kv[..., hidden:])
+    want = (_softmax(q @ k.transpose(0, 1, 3, 2) / np.sqrt(H)) @ v).transpose(2, 0, 1, 3).reshape(S, B, hidden)
+    np.testing.assert_allclose(out, want, rtol=1e-4, atol=1e-5)
+    np.testing.assert_allclose(kc, k, rtol=1e-5, atol=1e-6)
+    x1 = rng.standard_normal((1, B, hidden)).astype(np.float32)
+    out1, kc1, _ = run_node("DecoderAttention", {"q": x1, "k": x1, "qw": qw, "kvw": kvw, "b": bias, "m": None, "kc": kc, "vc": vc,
+                                                 "static_kv": f, "use_past": t, "has_layer_state": t, "has_mask": f}, n_outputs=3, domain=MS, num_heads=N)
+    assert kc1.shape == (B, N, S + 1, H)
+    q1 = heads(x1 @ qw + bias[:hidden])
+    kv1 = x1 @ kvw + bias[hidden:]
+    k1 = np.concatenate([k, heads(kv1[..., :hidden])], 2)
+    v1 = np.concatenate([v, heads(kv1[..., hidden:])], 2)
+    want1 = (_softmax(q1 @ k1.transpose(0, 1, 3, 2) / np.sqrt(H)) @ v1).transpose(2, 0, 1, 3).reshape(1, B, hidden)
+    np.testing.assert_allclose(out1, want1, rtol=1e-4, atol=1e-5)
+
+
+def test_bifurcation_detector():
+    src = np.array([10, 11, 12, 13, 14, 15, 11, 20], np.int64)
+    cur = np.array([1, 2], np.int64)
+    pred = np.array([12, 13, 99, 15, 11, 20, 7], np.int64)     # leaves the source at index 2 (prev = 2)
+    tokens, idx = run_node("BifurcationDetector", {"s": src, "c": cur, "p": np.array([2], np.int64), "pred": pred},
+                           n_outputs=2, domain=MS, min_ngram_size=1, max_ngram_size=3)
+    np.testing.assert_array_equal(tokens, [1, 2, 12, 13, 99])
+    assert int(idx[0]) == -1                                    # 99 does not occur in the source
+    tokens, idx = run_node("BifurcationDetector", {"s": src, "c": np.array([5, 13, 14], np.int64), "p": np.array([0], np.int64)},
+                           n_outputs=2, domain=MS, min_ngram_size=1, max_ngram_size=3)
+    np.testing.assert_array_equal(tokens, [5, 13, 14])
+    assert int(idx[0]) == 5                                     # "13 14" is unique in the source and ends before index 5
+    _, idx = run_node("BifurcationDetector", {"s": src, "c": np.array([11], np.int64), "p": np.array([0], np.int64)},
+                      n_outputs=2, domain=MS, min_ngram_size=1, max_ngram_size=3)
+    assert int(idx[0]) == -1                                    # 11 occurs twice
