@@ -162,6 +162,7 @@ at::Tensor ConvTransposeWithNodeAttrs(const Node& node, const at::Tensor& x, con
                                       const c10::optional<at::Tensor>& bias, const std::vector<int64_t>* pads_override = nullptr);
 at::Tensor PoolWithNodeAttrs(const Node& node, at::Tensor x, bool is_max);
 void RegisterOnnxExtraKernels(KernelRegistry& r);
+void RegisterOnnxExtraKernels2(KernelRegistry& r);
 void RegisterControlFlowKernels(KernelRegistry& r);
 void RegisterCollectiveKernels(KernelRegistry& r);
 void RegisterCudaKernels(KernelRegistry& r);

@@ -76,6 +76,7 @@ void EnsureKernelsRegistered() {
     RegisterContribKernels4(g);
     RegisterContribKernels5(g);
     RegisterOnnxExtraKernels(g);
+    RegisterOnnxExtraKernels2(g);
     RegisterControlFlowKernels(g);
     RegisterCollectiveKernels(g);
     RegisterCudaKernels(KernelRegistry::Cuda());

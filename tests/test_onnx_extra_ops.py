@@ -156,3 +156,106 @@ def test_quantised_convolutions():
     (ci,) = run_node("ConvInteger", {"x": x, "w": w, "xz": xz, "wz": wz})
     ref = torch.nn.functional.conv2d(torch.from_numpy(x.astype(np.float64) - 128), torch.from_numpy(w.astype(np.float64) - 127)).numpy()
     np.testing.assert_array_equal(ci, ref.astype(np.int32))
+
+
+def _bilinear_roialign(img, y, x):
+    """One RoiAlign sample on img [C, H, W] following the operator's definition."""
+    C, H, W = img.shape
+    if y < -1.0 or y > H or x < -1.0 or x > W:
+        return np.zeros(C, np.float32), [np.zeros(C, np.float32)] * 4
+    y, x = max(y, 0.0), max(x, 0.0)
+    y0, x0 = int(y), int(x)
+    if y0 >= H - 1:
+        y0 = y1 = H - 1
+        y = float(y0)
+    else:
+        y1 = y0 + 1
+    if x0 >= W - 1:
+        x0 = x1 = W - 1
+        x = float(x0)
+    else:
+        x1 = x0 + 1
+    ly, lx = y - y0, x - x0
+    parts = [img[:, y0, x0] * (1 - ly) * (1 - lx), img[:, y0, x1] * (1 - ly) * lx, img[:, y1, x0] * ly * (1 - lx), img[:, y1, x1] * ly * lx]
+    return sum(parts), parts
+
+
+@pytest.mark.parametrize("mode", ["avg", "max"])
+@pytest.mark.parametrize("sampling_ratio", [2, 0])
+def test_roi_align(mode, sampling_ratio):
+    rng = np.random.default_rng(11)
+    x = rng.standard_normal((2, 3, 10, 12)).astype(np.float32)
+    rois = np.array([[1.0, 1.5, 9.0, 8.0], [0.0, 0.0, 23.0, 19.0], [4.2, 3.1, 6.9, 5.5]], np.float32)
+    bidx = np.array([0, 1, 1], np.int64)
+    oh, ow, scale = 3, 4, 0.5
+    (y,) = run_node("RoiAlign", {"x": x, "r": rois, "b": bidx}, opset=16, mode=mode, output_height=oh, output_width=ow,
+                    sampling_ratio=sampling_ratio, spatial_scale=scale)
+    want = np.zeros((3, 3, oh, ow), np.float32)
+    for r in range(3):
+        x1, y1, x2, y2 = rois[r] * scale - 0.5
+        rw, rh = x2 - x1, y2 - y1
+        bh, bw = rh / oh, rw / ow
+        gh = sampling_ratio if sampling_ratio > 0 else int(np.ceil(rh / oh))
+        gw = sampling_ratio if sampling_ratio > 0 else int(np.ceil(rw / ow))
+        gh, gw = max(gh, 1), max(gw, 1)
+        for p in range(oh):
+            for q in range(ow):
+                vals = []
+                for i in range(gh):
+                    for j in range(gw):
+                        s, parts = _bilinear_roialign(x[bidx[r]], y1 + p * bh + (i + 0.5) * bh / gh, x1 + q * bw + (j + 0.5) * bw / gw)
+                        vals.append(np.max(parts, 0) if mode == "max" else s)
+                want[r, :, p, q] = np.max(vals, 0) if mode == "max" else np.mean(vals, 0)
+    np.testing.assert_allclose(y, want, rtol=1e-4, atol=1e-5)
+
+
+def test_deform_conv_zero_offsets_is_conv_and_random_offsets_match_naive():
+    import torch
+    rng = np.random.default_rng(12)
+    N, C, H, W, M, kh, kw = 1, 4, 6, 7, 6, 3, 3
+    x = rng.standard_normal((N, C, H, W)).astype(np.float32)
+    w = rng.standard_normal((M, C // 2, kh, kw)).astype(np.float32)
+    b = rng.standard_normal(M).astype(np.float32)
+    oH, oW = H, W
+    off = np.zeros((N, 2 * kh * kw * 2, oH, oW), np.float32)
+    (y,) = run_node("DeformConv", {"x": x, "w": w, "o": off, "b": b}, opset=19, group=2, offset_group=2, pads=[1, 1, 1, 1], kernel_shape=[kh, kw])
+    want = torch.nn.functional.conv2d(torch.tensor(x), torch.tensor(w), torch.tensor(b), padding=1, groups=2).numpy()
+    np.testing.assert_allclose(y, want, rtol=1e-4, atol=1e-4)
+    off = rng.uniform(-1.5, 1.5, off.shape).astype(np.float32)
+    mask = rng.uniform(0, 1, (N, 2 * kh * kw, oH, oW)).astype(np.float32)
+    (y,) = run_node("DeformConv", {"x": x, "w": w, "o": off, "b": b, "m": mask}, opset=19, group=2, offset_group=2, pads=[1, 1, 1, 1], kernel_shape=[kh, kw])
+
+    def sample(img, py, px):   # img [H, W], zero outside, bilinear
+        y0, x0 = int(np.floor(py)), int(np.floor(px))
+        v = 0.0
+        for yy, wy in ((y0, 1 - (py - y0)), (y0 + 1, py - y0)):
+            for xx, wx in ((x0, 1 - (px - x0)), (x0 + 1, px - x0)):
+                if 0 <= yy < H and 0 <= xx < W:
+                    v += img[yy, xx] * wy * wx
+        return v
+    want = np.zeros((N, M, oH, oW), np.float32)
+    cg = C // 2
+    for m in range(M):
+        g = m // (M // 2)
+        for oy in range(oH):
+            for ox in range(oW):
+                acc = b[m]
+                for c in range(C // 2):
+                    ch = g * (C // 2) + c
+                    ogi = ch // cg
+                    for k in range(kh * kw):
+                        ky, kx = divmod(k, kw)
+                        py = oy - 1 + ky + off[0, (ogi * kh * kw + k) * 2, oy, ox]
+                        px = ox - 1 + kx + off[0, (ogi * kh * kw + k) * 2 + 1, oy, ox]
+                        acc += w[m, c, ky, kx] * sample(x[0, ch], py, px) * mask[0, ogi * kh * kw + k, oy, ox]
+                want[0, m, oy, ox] = acc
+    np.testing.assert_allclose(y, want, rtol=1e-3, atol=1e-4)
+
+
+def test_label_encoder_numeric():
+    x = np.array([[3, 7, 5], [9, 3, 1]], np.int64)
+    (y,) = run_node("LabelEncoder", {"x": x}, domain="ai.onnx.ml", keys_int64s=[7, 3, 9], values_floats=[0.7, 0.3, 0.9], default_float=-1.0)
+    np.testing.assert_allclose(y, [[0.3, 0.7, -1.0], [0.9, 0.3, -1.0]], rtol=1e-6)
+    xf = np.array([0.5, 2.0, 1.5], np.float32)
+    (z,) = run_node("LabelEncoder", {"x": xf}, domain="ai.onnx.ml", keys_floats=[1.5, 0.5], values_int64s=[15, 5], default_int64=-7)
+    np.testing.assert_array_equal(z, [5, -7, 15])
