@@ -86,3 +86,143 @@ def test_c_program_runs_a_model(tmp_path):
     assert lines[1] == "out 1 2 2 2: " + " ".join(f"{v:g}" for v in want.reshape(-1))
     assert lines[2].startswith("bad 1 ") and "nope" in lines[2]
     assert lines[3] == "missing 1"
+
+
+C_SOURCE_WIDE = r"""
+#include <stdio.h>
+#include <string.h>
+#include "ortb200_c_api.h"
+
+#define CHECK(x) do { int rc_ = (x); if (rc_ != 0) { printf("ERR %d %s\n", rc_, ortb200_last_error()); return 1; } } while (0)
+
+int main(int argc, char** argv) {
+  ortb200_session_options* so = NULL;
+  CHECK(ortb200_create_session_options(&so));
+  CHECK(ortb200_session_options_set_graph_optimization_level(so, 1));
+  CHECK(ortb200_session_options_set_intra_op_num_threads(so, 2));
+  CHECK(ortb200_session_options_set_execution_mode(so, 0));
+  CHECK(ortb200_session_options_set_log_id(so, "wide"));
+  CHECK(ortb200_session_options_add_config_entry(so, "session.disable_prepacking", "1"));
+  CHECK(ortb200_session_options_add_free_dimension_override_by_name(so, "batch", 2));
+  CHECK(ortb200_session_options_append_execution_provider(so, "CPUExecutionProvider", NULL, NULL, 0));
+  printf("badlevel %d\n", ortb200_session_options_set_graph_optimization_level(so, 7) != 0);
+  ortb200_session* s = NULL;
+  CHECK(ortb200_create_session_from_options(argv[1], NULL, 0, so, &s));
+  ortb200_release_session_options(so);
+
+  ortb200_type_info ti;
+  CHECK(ortb200_session_input_type_info(s, 0, &ti));
+  printf("in %d %d %d %lld %lld [%s]\n", ti.elem_type, ti.has_shape, ti.ndim, (long long)ti.dims[0], (long long)ti.dims[1], ti.dim_params[0]);
+  CHECK(ortb200_session_output_type_info(s, 0, &ti));
+  printf("out %d %d\n", ti.elem_type, ti.ndim);
+  ortb200_model_metadata md;
+  CHECK(ortb200_session_model_metadata(s, &md));
+  const char* val = NULL;
+  CHECK(ortb200_session_lookup_custom_metadata(s, "author", &val));
+  const char* missing = "x";
+  CHECK(ortb200_session_lookup_custom_metadata(s, "nope", &missing));
+  const char* key0 = NULL;
+  CHECK(ortb200_session_custom_metadata_key(s, 0, &key0));
+  printf("meta %s %s %zu %s %s %d\n", md.producer_name, md.graph_name, md.num_custom_keys, key0, val, missing == NULL);
+  size_t np_ = 0; const char* p0 = NULL;
+  CHECK(ortb200_session_provider_count(s, &np_));
+  CHECK(ortb200_session_provider_name(s, 0, &p0));
+  printf("providers %zu %s\n", np_, p0);
+
+  /* run with run options */
+  float x[6] = {-1.f, 2.f, -3.f, 4.f, -5.f, 6.f};
+  ortb200_tensor_view v; memset(&v, 0, sizeof(v));
+  v.data = x; v.elem_type = 1; v.ndim = 2; v.dims[0] = 2; v.dims[1] = 3;
+  const char* names[] = {"x"};
+  ortb200_run_options* ro = NULL;
+  CHECK(ortb200_create_run_options(&ro));
+  CHECK(ortb200_run_options_set_tag(ro, "run-1"));
+  ortb200_value* out = NULL;
+  CHECK(ortb200_run_with_options(s, ro, names, &v, 1, NULL, 1, &out));
+  float y[4]; size_t nbytes = 0;
+  CHECK(ortb200_value_byte_size(out, &nbytes));
+  CHECK(ortb200_value_copy_to_host(out, y, sizeof(y)));
+  printf("run %zu %g %g %g %g\n", nbytes, y[0], y[1], y[2], y[3]);
+  ortb200_release_value(out);
+  CHECK(ortb200_run_options_set_terminate(ro, 1));
+  printf("terminated %d\n", ortb200_run_with_options(s, ro, names, &v, 1, NULL, 1, &out) != 0);
+  ortb200_release_run_options(ro);
+
+  /* I/O binding with a runtime-owned input and a caller-owned output buffer */
+  int64_t dims[2] = {2, 3};
+  ortb200_value* xin = NULL;
+  CHECK(ortb200_create_tensor(1, dims, 2, 0, 0, &xin));
+  CHECK(ortb200_value_copy_from_host(xin, x, sizeof(x)));
+  ortb200_tensor_view xv;
+  CHECK(ortb200_value_tensor(xin, 0, &xv));
+  float ybuf[4] = {0, 0, 0, 0};
+  ortb200_tensor_view yv; memset(&yv, 0, sizeof(yv));
+  yv.data = ybuf; yv.elem_type = 1; yv.ndim = 2; yv.dims[0] = 2; yv.dims[1] = 2;
+  ortb200_io_binding* b = NULL;
+  CHECK(ortb200_create_io_binding(s, &b));
+  CHECK(ortb200_io_binding_bind_input(b, "x", &xv));
+  CHECK(ortb200_io_binding_bind_output(b, "y", &yv));
+  CHECK(ortb200_run_with_binding(s, NULL, b));
+  CHECK(ortb200_io_binding_synchronize_outputs(b));
+  size_t nout = 0; const char* oname = NULL;
+  CHECK(ortb200_io_binding_output_count(b, &nout));
+  CHECK(ortb200_io_binding_output_name(b, 0, &oname));
+  printf("bound %zu %s %g %g %g %g\n", nout, oname, ybuf[0], ybuf[1], ybuf[2], ybuf[3]);
+  CHECK(ortb200_io_binding_clear_outputs(b));
+  CHECK(ortb200_io_binding_bind_output_to_device(b, "y", 0, 0));
+  CHECK(ortb200_run_with_binding(s, NULL, b));
+  ortb200_value* bound = NULL;
+  CHECK(ortb200_io_binding_output_value(b, 0, &bound));
+  ortb200_tensor_view bv;
+  CHECK(ortb200_value_tensor(bound, 1, &bv));
+  printf("bound2 %lld %lld %g\n", (long long)bv.dims[0], (long long)bv.dims[1], ((float*)bv.data)[3]);
+  ortb200_release_value(bound);
+  ortb200_release_io_binding(b);
+  ortb200_release_value(xin);
+
+  size_t navail = 0; const char* last = NULL;
+  CHECK(ortb200_available_provider_count(&navail));
+  CHECK(ortb200_available_provider_name(navail - 1, &last));
+  printf("avail %d %s\n", navail >= 1, last);
+  CHECK(ortb200_set_default_logger_severity(3));
+  CHECK(ortb200_session_check_device_status(s));
+  ortb200_release_session(s);
+  return 0;
+}
+"""
+
+
+@pytest.mark.skipif(not os.path.exists(os.path.join(LIB, "libortb200.so")), reason="libortb200.so not built")
+def test_c_program_uses_options_metadata_and_io_binding(tmp_path):
+    T = ol.TensorProto
+    w = np.array([[1.0, 0.0], [0.0, 1.0], [1.0, 1.0]], np.float32)
+    g = ol.make_graph([ol.make_node("Relu", ["x"], ["r"]), ol.make_node("MatMul", ["r", "w"], ["y"])], "wide_graph",
+                      [ol.make_tensor_value_info("x", T.FLOAT, ["batch", 3])], [ol.make_tensor_value_info("y", T.FLOAT, ["batch", 2])],
+                      [ol.make_tensor("w", w)])
+    m = ol.make_model(g, opset=17, producer_name="unit-test", metadata={"author": "someone"})
+    model = tmp_path / "m.onnx"
+    model.write_bytes(m.serialize())
+    src = tmp_path / "wide.c"
+    src.write_text(C_SOURCE_WIDE)
+    exe = tmp_path / "wide"
+    import torch
+    torch_lib = os.path.join(os.path.dirname(torch.__file__), "lib")
+    cmd = ["gcc", "-std=c99", "-o", str(exe), str(src), f"-I{INC}", f"-L{LIB}", "-lortb200", f"-Wl,-rpath,{LIB}",
+           f"-Wl,-rpath,{torch_lib}", f"-Wl,-rpath-link,{torch_lib}", f"-Wl,-rpath-link,{LIB}"]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    assert res.returncode == 0, res.stderr[-3000:]
+    env = dict(os.environ)
+    env.pop("PYTHONPATH", None)
+    run = subprocess.run([str(exe), str(model)], capture_output=True, text=True, env=env, timeout=300)
+    assert run.returncode == 0, run.stdout[-2000:] + run.stderr[-2000:]
+    lines = run.stdout.strip().splitlines()
+    assert lines[0] == "badlevel 1"
+    assert lines[1] == "in 1 1 2 2 3 []" or lines[1] == "in 1 1 2 -1 3 [batch]"   # the override pins the symbol
+    assert lines[2] == "out 1 2"
+    assert lines[3] == "meta unit-test wide_graph 1 author someone 1"
+    assert lines[4] == "providers 1 CPUExecutionProvider"
+    assert lines[5] == "run 16 0 2 10 6"
+    assert lines[6] == "terminated 1"
+    assert lines[7] == "bound 1 y 0 2 10 6"
+    assert lines[8] == "bound2 2 2 6"
+    assert lines[9] == "avail 1 CPUExecutionProvider"
