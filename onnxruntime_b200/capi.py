@@ -709,6 +709,18 @@ class InferenceSession:
     def check_device_status(self) -> None:
         self._sess.check_device_status()
 
+    def get_memory_plans(self):
+        """One entry per input-shape pattern run so far (``SessionOptions.enable_mem_pattern``): the arena size that
+        would serve the pattern with buffer reuse (``*_peak_bytes``), the sum of all requests (``*_total_bytes``), the
+        lower bound (``*_live_peak_bytes``) and per value ``(name, bytes, first_step, last_step, on_gpu, offset)``.
+        The reference keeps the same information in its memory-pattern planner
+        (onnxruntime/core/framework/mem_pattern_planner.h)."""
+        return self._sess.memory_plans()
+
+    def get_memory_stats(self) -> dict:
+        """Statistics of the device arena (the torch caching allocator) for a GPU session; empty for CPU sessions."""
+        return self._sess.memory_stats()
+
 
 # --------------------------------------------------------------------- IOBinding
 class IOBinding:

@@ -8,6 +8,8 @@
 #include "executor.h"
 #include "graph.h"
 #include "kernel.h"
+#include <c10/cuda/CUDACachingAllocator.h>
+
 #include "session.h"
 #include "shape_inference.h"
 #include "cuda_ops.h"
@@ -246,6 +248,44 @@ PYBIND11_MODULE(_core, m) {
       .def("node_assignments", &InferenceSession::NodeAssignments)
       .def("num_captured_graphs", &InferenceSession::NumCapturedGraphs)
       .def("kernel_launch_count", &InferenceSession::KernelLaunchCount)
+      .def("memory_plans", [](InferenceSession& s) {
+        py::list out;
+        for (auto& kv : s.MemoryPlans()) {
+          const MemoryPlan& p = kv.second;
+          py::dict d;
+          d["pattern"] = p.pattern;
+          d["host_peak_bytes"] = p.peak_bytes[0];
+          d["host_total_bytes"] = p.total_bytes[0];
+          d["host_live_peak_bytes"] = p.live_peak_bytes[0];
+          d["host_values_reusing_memory"] = p.num_reused[0];
+          d["device_peak_bytes"] = p.peak_bytes[1];
+          d["device_total_bytes"] = p.total_bytes[1];
+          d["device_live_peak_bytes"] = p.live_peak_bytes[1];
+          d["device_values_reusing_memory"] = p.num_reused[1];
+          std::string why;
+          d["valid"] = PlanIsValid(p, &why);
+          py::list bufs;
+          for (auto& b : p.buffers) bufs.append(py::make_tuple(b.name, b.bytes, b.first_step, b.last_step, b.on_gpu, b.offset));
+          d["buffers"] = bufs;
+          out.append(d);
+        }
+        return out;
+      })
+      .def("memory_stats", [](InferenceSession& s) {
+        // arena statistics of the device allocator (the counterpart of the reference's BFCArena::GetStats)
+        py::dict d;
+        if (s.uses_gpu()) {
+          const auto st = c10::cuda::CUDACachingAllocator::getDeviceStats(s.device().index());
+          d["allocated_bytes"] = st.allocated_bytes[0].current;
+          d["allocated_bytes_peak"] = st.allocated_bytes[0].peak;
+          d["reserved_bytes"] = st.reserved_bytes[0].current;
+          d["reserved_bytes_peak"] = st.reserved_bytes[0].peak;
+          d["num_driver_allocations"] = st.segment[0].allocated;
+          d["num_alloc_retries"] = st.num_alloc_retries;
+          d["num_ooms"] = st.num_ooms;
+        }
+        return d;
+      })
       .def("last_run_launch_count", &InferenceSession::LastRunLaunchCount)
       .def("check_device_status", [](InferenceSession& s) { Guard([&] { s.CheckDeviceStatus(); return 0; }); })
       .def("uses_gpu", &InferenceSession::uses_gpu)

@@ -453,7 +453,44 @@ void GraphExecutor::RunStep(const RunOptions& ro, const Step& st, std::vector<Va
     } else {
       slots[s] = std::move(out[i]);
     }
+    if (tracing_ && slots[s].t.defined()) {
+      const at::Tensor& t = slots[s].t;
+      // a view of an input (Reshape, Squeeze, Identity ...) allocates nothing
+      bool alias = false;
+      for (auto& v : in)
+        if (v.t.defined() && v.t.has_storage() && t.has_storage() && v.t.storage().data() == t.storage().data()) alias = true;
+      SlotTrace& tr = trace_[static_cast<size_t>(s)];
+      tr.bytes = alias || !t.has_storage() ? 0 : static_cast<int64_t>(t.storage().nbytes());
+      tr.step = node_index;
+      tr.on_gpu = t.is_cuda();
+    }
   }
+}
+
+void GraphExecutor::BeginMemoryTrace() {
+  trace_.assign(slot_names_.size(), SlotTrace());
+  tracing_ = true;
+}
+
+std::vector<PlannedBuffer> GraphExecutor::EndMemoryTrace() {
+  tracing_ = false;
+  const int n = static_cast<int>(steps_.size());
+  std::vector<int> last(slot_names_.size(), n - 1);  // values nobody releases (graph outputs) live to the end
+  for (int i = 0; i < n; ++i)
+    for (int s : steps_[static_cast<size_t>(i)].release) last[static_cast<size_t>(s)] = i;
+  std::vector<PlannedBuffer> out;
+  for (size_t s = 0; s < trace_.size(); ++s) {
+    if (trace_[s].bytes < 0) continue;
+    PlannedBuffer b;
+    b.name = slot_names_[s];
+    b.bytes = trace_[s].bytes;
+    b.first_step = trace_[s].step;
+    b.last_step = std::max(last[s], trace_[s].step);
+    b.on_gpu = trace_[s].on_gpu;
+    out.push_back(std::move(b));
+  }
+  trace_.clear();
+  return out;
 }
 
 void GraphExecutor::ExecuteSteps(const RunOptions& ro, std::vector<Value>& slots) {

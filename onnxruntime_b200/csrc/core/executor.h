@@ -16,6 +16,7 @@
 #include <string>
 #include <vector>
 
+#include "allocation_planner.h"
 #include "session.h"
 
 namespace ortb {
@@ -44,6 +45,9 @@ class GraphExecutor {
   bool parallel_ok() const { return parallel_ok_; }
   std::vector<Value> NewSlots() const { return constant_slots_; }
   int SlotOf(const std::string& name) const;
+  // Memory-pattern tracing: between the two calls every step records what its outputs allocated.
+  void BeginMemoryTrace();
+  std::vector<PlannedBuffer> EndMemoryTrace();
 
  private:
   void Partition();
@@ -68,6 +72,13 @@ class GraphExecutor {
   bool parallel_ok_ = false, nvtx_ = true;
   std::vector<std::vector<int>> step_deps_, step_succ_;  // step index -> steps it waits for / steps waiting for it
   const std::map<std::string, Value>* current_outer_ = nullptr;
+  struct SlotTrace {
+    int64_t bytes = -1;  // -1: not produced by a step during the trace
+    int step = -1;
+    bool on_gpu = false;
+  };
+  std::vector<SlotTrace> trace_;
+  bool tracing_ = false;
 };
 
 }  // namespace ortb

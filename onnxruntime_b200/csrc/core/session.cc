@@ -1,4 +1,5 @@
 #include "session.h"
+#include "allocation_planner.h"
 
 #include <ATen/cuda/CUDAContext.h>
 #include <ATen/cuda/CUDAGraph.h>
@@ -473,6 +474,34 @@ std::vector<Value> InferenceSession::RunImpl(const RunOptions& ro, const std::ve
 
   std::vector<Value> results;
   int64_t graph_id = -1;
+  // memory pattern of this set of input shapes: traced on its first eager run, planned afterwards
+  std::string pattern;
+  bool trace_memory = false;
+  if (so_.enable_mem_pattern) {
+    std::ostringstream key;
+    for (size_t i = 0; i < inputs.size(); ++i)
+      if (inputs[i].t.defined()) key << input_names_[i] << inputs[i].t.sizes() << ";";
+    pattern = key.str();
+    trace_memory = memory_plans_.count(pattern) == 0 && memory_plans_.size() < 16;
+  }
+  auto run_eager = [&]() {
+    if (trace_memory) ex->BeginMemoryTrace();
+    std::vector<Value> r;
+    try {
+      r = ex->Run(ro, inputs, nullptr, output_names);
+    } catch (...) {
+      if (trace_memory) ex->EndMemoryTrace();
+      throw;
+    }
+    if (trace_memory) {
+      memory_plans_[pattern] = PlanBuffers(ex->EndMemoryTrace(), pattern);
+      trace_memory = false;
+      const MemoryPlan& mp = memory_plans_[pattern];
+      ORTB_VLOG(run_logger, 1) << "memory pattern " << pattern << ": host " << mp.peak_bytes[0] << " of " << mp.total_bytes[0]
+                               << " bytes, device " << mp.peak_bytes[1] << " of " << mp.total_bytes[1] << " bytes";
+    }
+    return r;
+  };
   if (enable_cuda_graph_ && graph_capturable_) {
     const std::string id = ro.config.Get("gpu_graph_id", "0");
     graph_id = std::stoll(id);
@@ -484,7 +513,7 @@ std::vector<Value> InferenceSession::RunImpl(const RunOptions& ro, const std::ve
     // library collective, which is left out of graph capture (the process-group's own streams and watchdog do
     // not belong inside a capture) - such a step keeps running eagerly
     const int64_t lib_before = library_collective_calls;
-    results = ex->Run(ro, inputs, nullptr, output_names);
+    results = run_eager();
     cudaStreamSynchronize(at::cuda::getCurrentCUDAStream(device_.index()).stream());
     CheckDeviceStatus();
     if (library_collective_calls != lib_before) {
@@ -572,7 +601,7 @@ std::vector<Value> InferenceSession::RunImpl(const RunOptions& ro, const std::ve
     for (auto& n : output_names) results.push_back(slots[ex->SlotOf(n)]);
   } else {
     const int64_t launches_before = launch_count_;
-    results = ex->Run(ro, inputs, nullptr, output_names);
+    results = run_eager();
     last_run_launches_ = launch_count_ - launches_before;
   }
   if (profiler_.enabled()) {

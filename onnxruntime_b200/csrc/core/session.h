@@ -16,6 +16,7 @@
 #include <string>
 #include <vector>
 
+#include "allocation_planner.h"
 #include "logging.h"
 #include "graph.h"
 #include "kernel.h"
@@ -139,6 +140,8 @@ class InferenceSession {
   const logging::Logger& logger() const { return logger_; }
   int NumCapturedGraphs() const { return static_cast<int>(cuda_graphs_.size()); }
   int64_t KernelLaunchCount() const { return launch_count_; }
+  // one plan per input-shape pattern seen so far (SessionOptions.enable_mem_pattern)
+  const std::map<std::string, MemoryPlan>& MemoryPlans() const { return memory_plans_; }
   // launches issued by the most recent execution of the step list (eager run or graph capture)
   int64_t LastRunLaunchCount() const { return last_run_launches_; }
   void AddLaunches(int64_t n) { launch_count_ += n; }
@@ -194,6 +197,7 @@ class InferenceSession {
   int64_t profiling_start_ns_ = 0;
   int64_t launch_count_ = 0;
   int64_t last_run_launches_ = 0;
+  std::map<std::string, MemoryPlan> memory_plans_;
   std::map<std::string, size_t> input_index_;
   std::vector<const ValueInfo*> input_info_;
   at::Tensor gemm_ws_, attn_ws_, status_word_;

@@ -320,3 +320,36 @@ def test_ignored_options_are_reported_and_mapped_ones_applied():
     finally:
         ort.set_log_sink(None)
         torch.set_num_threads(before)
+
+
+def test_memory_plan_reuses_buffers_of_dead_values():
+    """A chain of elementwise nodes needs two live buffers at a time, not one per node: the plan traced on the first
+    run packs the values accordingly and never lets two live values overlap."""
+    import onnxruntime_b200 as ort
+    from onnxruntime_b200 import onnx_lite as ol
+    T = ol.TensorProto
+    nodes, prev = [], "x"
+    for i in range(8):
+        nodes.append(ol.make_node("Relu" if i % 2 else "Neg", [prev], [f"v{i}"]))
+        prev = f"v{i}"
+    nodes.append(ol.make_node("Reshape", [prev, "shape"], ["flat"]))       # a view: allocates nothing
+    nodes.append(ol.make_node("Add", ["flat", "flat"], ["y"]))
+    g = ol.make_graph(nodes, "chain", [ol.make_tensor_value_info("x", T.FLOAT, ["n", 256])], [ol.make_tensor_value_info("y", T.FLOAT, None)],
+                      [ol.make_tensor("shape", np.array([-1], np.int64))])
+    so = ort.SessionOptions()
+    so.graph_optimization_level = ort.GraphOptimizationLevel.ORT_DISABLE_ALL
+    sess = ort.InferenceSession(ol.make_model(g, opset=17).serialize(), so, providers=["CPUExecutionProvider"])
+    assert sess.get_memory_plans() == []
+    sess.run(None, {"x": np.ones((4, 256), np.float32)})
+    sess.run(None, {"x": np.ones((4, 256), np.float32)})          # same pattern: no second plan
+    sess.run(None, {"x": np.ones((8, 256), np.float32)})
+    plans = sess.get_memory_plans()
+    assert len(plans) == 2 and all(p["valid"] for p in plans)
+    p = next(p for p in plans if "[4, 256]" in p["pattern"])
+    one = 4 * 256 * 4
+    assert p["host_total_bytes"] == 9 * one                        # 8 chain values + y; the reshape is a view
+    assert p["host_live_peak_bytes"] == 2 * one
+    assert p["host_peak_bytes"] <= 3 * one and p["host_values_reusing_memory"] >= 6
+    by_name = {b[0]: b for b in p["buffers"]}
+    assert by_name["flat"][1] == 0 and by_name["flat"][5] == -1
+    assert sess.get_memory_stats() == {}
