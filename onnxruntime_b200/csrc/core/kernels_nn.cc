@@ -314,7 +314,8 @@ std::pair<double, double> QRange(at::ScalarType t) {
 void QuantizeLinearImpl(Ctx& ctx) {
   const at::Tensor& x = ctx.RequiredInput(0);
   const Node& n = ctx.node();
-  const int64_t axis = NormAxis(n.attr_i("axis", 1), std::max<int64_t>(x.dim(), 1));
+  // the axis only matters for per-axis parameters (a 1-D tensor quantised per tensor keeps the default axis 1)
+  const int64_t axis = ctx.RequiredInput(1).numel() == 1 ? 0 : NormAxis(n.attr_i("axis", 1), std::max<int64_t>(x.dim(), 1));
   at::Tensor scale = BroadcastAlongAxis(ctx.RequiredInput(1).to(at::kFloat), axis, x.dim());
   at::ScalarType out_t = at::kByte;
   at::Tensor zp;
@@ -339,7 +340,7 @@ void DequantizeLinearImpl(Ctx& ctx) {
   const at::Tensor& x = ctx.RequiredInput(0);
   const Node& n = ctx.node();
   const at::Tensor& scale_in = ctx.RequiredInput(1);
-  const int64_t axis = NormAxis(n.attr_i("axis", 1), std::max<int64_t>(x.dim(), 1));
+  const int64_t axis = scale_in.numel() == 1 ? 0 : NormAxis(n.attr_i("axis", 1), std::max<int64_t>(x.dim(), 1));
   const int64_t block = n.attr_i("block_size", 0);
   at::Tensor xf = x.to(at::kFloat);
   at::Tensor scale = scale_in.to(at::kFloat);

@@ -169,7 +169,8 @@ const std::vector<Pass>& AllPasses() {
     std::vector<Pass> v;
     AddBasicPasses(v);
     AddFusionPasses(v);
-    AddMorePasses(v);  // after the transformer fusions: those match the un-simplified MatMul / Add / Softmax forms
+    AddMorePasses(v);
+    AddQdqPasses(v);  // after the transformer fusions: those match the un-simplified MatMul / Add / Softmax forms
     AddGpuPasses(v);
     return v;
   }();

@@ -391,6 +391,79 @@ int DoubleQDQPairsRemover(PassContext& c) {
   return count;
 }
 
+// GroupQueryAttentionFusion (onnxruntime/core/optimizer/group_query_attention_fusion.cc): a GroupQueryAttention whose
+// query and key come from two RotaryEmbedding nodes over the same caches and positions does the rotation itself
+// (do_rotary = 1, position_ids passed through as input 9), and three MatMul projections of one activation with
+// constant weights become one MatMul feeding the operator's packed-QKV form.
+int GroupQueryAttentionFusion(PassContext& c) {
+  Graph& g = c.g;
+  int count = 0;
+  for (Node* a : g.Nodes()) {
+    if (a->removed || a->op_type != "GroupQueryAttention" || a->domain != kMSDomain) continue;
+    bool changed = false;
+    // ---- rotary embedding into the attention
+    if (a->attr_i("do_rotary", 0) == 0 && !a->has_input(7) && !a->has_input(8) && a->has_input(1) && a->has_input(2)) {
+      Node* rq = g.Producer(a->input(0));
+      Node* rk = g.Producer(a->input(1));
+      auto is_rotary = [&](Node* r) {
+        return r && r->op_type == "RotaryEmbedding" && r->domain == kMSDomain && r->inputs.size() >= 4 && SoleUser(g, r->outputs[0]) == a &&
+               r->attr_i("rotary_embedding_dim", 0) == 0 && r->attr_f("scale", 1.0f) == 1.0f && !r->attr_i("is_packed_batching", 0);
+      };
+      if (is_rotary(rq) && is_rotary(rk) && rq != rk && rq->input(1) == rk->input(1) && rq->input(2) == rk->input(2) &&
+          rq->input(3) == rk->input(3) && rq->attr_i("interleaved", 0) == rk->attr_i("interleaved", 0) &&
+          RankOf(g, rq->input(0)) != 4) {  // the operator takes [batch, sequence, hidden] projections
+        const std::string pos = rq->input(1), cosv = rq->input(2), sinv = rq->input(3);
+        const int64_t inter = rq->attr_i("interleaved", 0);
+        a->inputs[0] = rq->input(0);
+        a->inputs[1] = rk->input(0);
+        while (a->inputs.size() < 10) a->inputs.push_back("");
+        a->inputs[7] = cosv;
+        a->inputs[8] = sinv;
+        a->inputs[9] = pos;
+        a->set_attr_i("do_rotary", 1);
+        a->set_attr_i("rotary_interleaved", inter);
+        g.RemoveNode(rq);
+        g.RemoveNode(rk);
+        changed = true;
+      }
+    }
+    // ---- three projections of one activation into one packed projection
+    if (a->has_input(1) && a->has_input(2)) {
+      Node* mq = g.Producer(a->input(0));
+      Node* mk = g.Producer(a->input(1));
+      Node* mv = g.Producer(a->input(2));
+      auto is_proj = [&](Node* m) {
+        if (!m || m->op_type != "MatMul" || !m->domain.empty() || SoleUser(g, m->outputs[0]) != a) return false;
+        const at::Tensor* w = g.GetConstant(m->input(1));
+        return w != nullptr && w->dim() == 2;
+      };
+      if (is_proj(mq) && is_proj(mk) && is_proj(mv) && mq != mk && mk != mv && mq != mv && mq->input(0) == mk->input(0) &&
+          mq->input(0) == mv->input(0)) {
+        const at::Tensor* wq = g.GetConstant(mq->input(1));
+        const at::Tensor* wk = g.GetConstant(mk->input(1));
+        const at::Tensor* wv = g.GetConstant(mv->input(1));
+        if (wq->size(0) == wk->size(0) && wq->size(0) == wv->size(0) && wq->scalar_type() == wk->scalar_type() &&
+            wq->scalar_type() == wv->scalar_type() && wk->size(1) == wv->size(1)) {
+          const std::string wname = g.UniqueName(mq->input(1) + "_qkv");
+          g.AddInitializer(wname, at::cat({*wq, *wk, *wv}, 1).contiguous());
+          const std::string packed = g.UniqueName(a->name + "_packed_qkv");
+          Node* m = g.AddNode("MatMul", {mq->input(0), wname}, {packed}, "", g.UniqueName(mq->name + "_qkv"));
+          (void)m;
+          a->inputs[0] = packed;
+          a->inputs[1] = "";
+          a->inputs[2] = "";
+          g.RemoveNode(mq);
+          g.RemoveNode(mk);
+          g.RemoveNode(mv);
+          changed = true;
+        }
+      }
+    }
+    if (changed) ++count;
+  }
+  return count;
+}
+
 }  // namespace
 
 void AddMorePasses(std::vector<Pass>& v) {
@@ -406,6 +479,7 @@ void AddMorePasses(std::vector<Pass>& v) {
   v.push_back({"MatMulAddFusion", 1, false, MatMulAddFusion});
   v.push_back({"GemmTransposeFusion", 1, false, GemmTransposeFusion});
   v.push_back({"BiasSoftmaxFusion", 2, false, BiasSoftmaxFusion});
+  v.push_back({"GroupQueryAttentionFusion", 2, false, GroupQueryAttentionFusion});
 }
 
 }  // namespace opt

@@ -392,3 +392,92 @@ def test_nbits_gate_up_merge_and_swiglu_on_graph_level():
     a = ort.InferenceSession(model, providers=["CPUExecutionProvider"]).run(None, {"x": x})[0]
     b = ort.InferenceSession(out, providers=["CPUExecutionProvider"]).run(None, {"x": x})[0]
     np.testing.assert_allclose(a.astype(np.float32), b.astype(np.float32), rtol=2e-2, atol=2e-3)
+
+
+def test_qdq_fusion_turns_node_groups_into_quantised_operators():
+    """DequantizeLinear -> op -> QuantizeLinear groups become QLinear* operators; results stay the same because the
+    quantised kernels compute dequantise / float operator / requantise."""
+    T = ol.TensorProto
+    rng = np.random.default_rng(21)
+
+    def qparams(name, scale, zp, dtype=np.uint8):
+        return [ol.make_tensor(name + "_s", np.array(scale, np.float32)), ol.make_tensor(name + "_z", np.array(zp, dtype))]
+    inits = []
+    inits += qparams("x", 0.02, 128) + qparams("w", 0.01, 0, np.int8) + qparams("c", 0.05, 120) + qparams("p", 0.05, 120)
+    inits += qparams("m", 0.1, 100) + qparams("a", 0.08, 110) + qparams("sm", 1 / 256, 0)
+    wq = rng.integers(-100, 100, (4, 3, 3, 3)).astype(np.int8)
+    bq = rng.integers(-500, 500, (4,)).astype(np.int32)
+    w2q = rng.integers(-100, 100, (16, 8)).astype(np.int8)
+    inits += [ol.make_tensor("wq", wq), ol.make_tensor("bq", bq), ol.make_tensor("b_s", np.array(0.02 * 0.01, np.float32)),
+              ol.make_tensor("w2q", w2q), ol.make_tensor("shape", np.array([2, 16], np.int64))]
+    nodes = [
+        ol.make_node("QuantizeLinear", ["x", "x_s", "x_z"], ["xq"]),
+        ol.make_node("DequantizeLinear", ["xq", "x_s", "x_z"], ["xd"]),
+        ol.make_node("DequantizeLinear", ["wq", "w_s", "w_z"], ["wd"]),
+        ol.make_node("DequantizeLinear", ["bq", "b_s"], ["bd"]),
+        ol.make_node("Conv", ["xd", "wd", "bd"], ["conv"], pads=[1, 1, 1, 1], name="conv0"),
+        ol.make_node("QuantizeLinear", ["conv", "c_s", "c_z"], ["convq"]),
+        ol.make_node("DequantizeLinear", ["convq", "c_s", "c_z"], ["convd"]),
+        ol.make_node("MaxPool", ["convd"], ["pool"], kernel_shape=[2, 2], strides=[2, 2], name="pool0"),
+        ol.make_node("QuantizeLinear", ["pool", "p_s", "p_z"], ["poolq"]),
+        ol.make_node("Reshape", ["poolq", "shape"], ["flatq"]),
+        ol.make_node("DequantizeLinear", ["flatq", "p_s", "p_z"], ["flatd"]),
+        ol.make_node("DequantizeLinear", ["w2q", "w_s", "w_z"], ["w2d"]),
+        ol.make_node("MatMul", ["flatd", "w2d"], ["mm"], name="mm0"),
+        ol.make_node("QuantizeLinear", ["mm", "m_s", "m_z"], ["mmq"]),
+        ol.make_node("DequantizeLinear", ["mmq", "m_s", "m_z"], ["mmd1"]),
+        ol.make_node("DequantizeLinear", ["mmq", "m_s", "m_z"], ["mmd2"]),
+        ol.make_node("Add", ["mmd1", "mmd2"], ["sum"], name="add0"),
+        ol.make_node("QuantizeLinear", ["sum", "a_s", "a_z"], ["sumq"]),
+        ol.make_node("DequantizeLinear", ["sumq", "a_s", "a_z"], ["sumd"]),
+        ol.make_node("Softmax", ["sumd"], ["soft"], axis=-1, name="soft0"),
+        ol.make_node("QuantizeLinear", ["soft", "sm_s", "sm_z"], ["softq"]),
+        ol.make_node("DequantizeLinear", ["softq", "sm_s", "sm_z"], ["y"]),
+    ]
+    g = ol.make_graph(nodes, "qdq", [ol.make_tensor_value_info("x", T.FLOAT, [2, 3, 4, 4])], [ol.make_tensor_value_info("y", T.FLOAT, [2, 8])], inits)
+    model = ol.make_model(g, opset=17).serialize()
+    x = rng.uniform(-2, 2, (2, 3, 4, 4)).astype(np.float32)
+    so0 = ort.SessionOptions()
+    so0.graph_optimization_level = ort.GraphOptimizationLevel.ORT_DISABLE_ALL
+    plain = ort.InferenceSession(model, so0, providers=["CPUExecutionProvider"])
+    fused = ort.InferenceSession(model, providers=["CPUExecutionProvider"])
+    counts = op_counts(fused)
+    assert counts.get("QLinearConv") == 1 and counts.get("QLinearMatMul") == 1 and counts.get("QLinearAdd") == 1
+    assert counts.get("QLinearSoftmax") == 1 and counts.get("MaxPool") == 1
+    assert counts.get("Conv", 0) == 0 and counts.get("MatMul", 0) == 0 and counts.get("Softmax", 0) == 0
+    assert counts.get("DequantizeLinear", 0) == 1 and counts.get("QuantizeLinear", 0) == 1   # only the model's two ends remain
+    want = plain.run(None, {"x": x})[0]
+    got = fused.run(None, {"x": x})[0]
+    assert np.abs(got - want).max() <= 1 / 256 + 1e-6     # at most one quantisation step of the last stage
+    so = ort.SessionOptions()
+    so.add_session_config_entry("session.disable_quant_qdq", "1")
+    off = ort.InferenceSession(model, so, providers=["CPUExecutionProvider"])
+    assert "QLinearConv" not in op_counts(off)
+
+
+def test_group_query_attention_fusion_takes_rotary_and_packs_qkv():
+    B, S, N, Nk, H, maxpos = 2, 4, 2, 1, 8, 16
+    hidden = N * H
+    r = np.random.RandomState(5)
+    ang = np.arange(maxpos)[:, None] * (1.0 / 10000 ** (np.arange(H // 2) / (H // 2)))[None, :]
+    inits = [c("wq", r.randn(hidden, N * H) * 0.3), c("wk", r.randn(hidden, Nk * H) * 0.3), c("wv", r.randn(hidden, Nk * H) * 0.3),
+             c("cos", np.cos(ang)), c("sin", np.sin(ang)),
+             c("seqlens", np.full((B,), S - 1), np.int32), c("total", np.array(S), np.int32)]
+    nodes = [
+        ol.make_node("MatMul", ["x", "wq"], ["q"], name="q_proj"),
+        ol.make_node("MatMul", ["x", "wk"], ["k"], name="k_proj"),
+        ol.make_node("MatMul", ["x", "wv"], ["v"], name="v_proj"),
+        ol.make_node("RotaryEmbedding", ["q", "pos", "cos", "sin"], ["qr"], domain="com.microsoft", num_heads=N),
+        ol.make_node("RotaryEmbedding", ["k", "pos", "cos", "sin"], ["kr"], domain="com.microsoft", num_heads=Nk),
+        ol.make_node("GroupQueryAttention", ["qr", "kr", "v", "pk", "pv", "seqlens", "total"], ["y", "nk", "nv"], domain="com.microsoft",
+                     num_heads=N, kv_num_heads=Nk, name="gqa"),
+    ]
+    g = ol.make_graph(nodes, "g", [ol.make_tensor_value_info("x", T.FLOAT, [B, S, hidden]), ol.make_tensor_value_info("pos", T.INT64, [B, S]),
+                                   ol.make_tensor_value_info("pk", T.FLOAT, [B, Nk, 0, H]), ol.make_tensor_value_info("pv", T.FLOAT, [B, Nk, 0, H])],
+                      [ol.make_tensor_value_info("y", T.FLOAT, None), ol.make_tensor_value_info("nk", T.FLOAT, None)], inits)
+    model = ol.make_model(g, opset=17).serialize()
+    feeds = {"x": r.randn(B, S, hidden).astype(np.float32), "pos": np.tile(np.arange(S, dtype=np.int64), (B, 1)),
+             "pk": np.zeros((B, Nk, 0, H), np.float32), "pv": np.zeros((B, Nk, 0, H), np.float32)}
+    before, after = both(model, feeds)
+    assert before["RotaryEmbedding"] == 2 and before["MatMul"] == 3
+    assert after.get("RotaryEmbedding", 0) == 0 and after["MatMul"] == 1 and after["GroupQueryAttention"] == 1
