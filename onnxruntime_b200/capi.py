@@ -26,6 +26,7 @@ __all__ = [
     "InferenceSession", "SessionOptions", "RunOptions", "IOBinding", "OrtValue", "OrtDevice", "NodeArg",
     "ModelMetadata", "GraphOptimizationLevel", "ExecutionMode", "ExecutionOrder", "get_available_providers",
     "get_all_providers", "get_device", "set_default_logger_severity", "set_default_logger_verbosity", "set_log_sink",
+    "ModelCompiler",
 ]
 
 
@@ -720,6 +721,54 @@ class InferenceSession:
     def get_memory_stats(self) -> dict:
         """Statistics of the device arena (the torch caching allocator) for a GPU session; empty for CPU sessions."""
         return self._sess.memory_stats()
+
+
+# --------------------------------------------------------------------- compile API
+class ModelCompiler:
+    """Ahead-of-time preparation of a model: the graph is optimized, fused and lowered for the providers given in the
+    session options, and stored as a model with one ``com.microsoft.EPContext`` node whose payload is that graph; a
+    session created from the result skips the preparation.  Mirrors the reference's ``onnxruntime.ModelCompiler``
+    (onnxruntime/python/onnxruntime_inference_collection.py; C side onnxruntime/core/session/compile_api.cc) and the
+    ``ep.context_*`` session configuration keys.
+
+    ``input_model`` is a path or the model's bytes.  ``embed_compiled_data_into_model`` = False puts the payload
+    into a side file beside the output model (``compile_to_file`` only)."""
+
+    def __init__(self, sess_options: Optional["SessionOptions"], input_model, embed_compiled_data_into_model: bool = False,
+                 providers=None, provider_options=None, **kwargs):
+        self._so = sess_options
+        self._input = input_model
+        self._embed = bool(embed_compiled_data_into_model)
+        self._providers = providers
+        self._provider_options = provider_options
+        self._kwargs = kwargs
+
+    def _options(self, out_path: str, embed: bool) -> "SessionOptions":
+        so = SessionOptions()
+        if self._so is not None:
+            for f in SessionOptions._FIELDS:
+                setattr(so, f, getattr(self._so, f))
+            so.graph_optimization_level = self._so.graph_optimization_level
+            so.execution_mode = self._so.execution_mode
+            for k, v in self._so._c.config_entries().items():
+                so.add_session_config_entry(k, v)
+        so.add_session_config_entry("ep.context_enable", "1")
+        so.add_session_config_entry("ep.context_file_path", out_path)
+        so.add_session_config_entry("ep.context_embed_mode", "1" if embed else "0")
+        return so
+
+    def compile_to_file(self, output_model_path: str) -> None:
+        InferenceSession(self._input, self._options(os.fspath(output_model_path), self._embed), providers=self._providers,
+                         provider_options=self._provider_options, **self._kwargs)
+
+    def compile_to_bytes(self) -> bytes:
+        import tempfile
+        with tempfile.TemporaryDirectory() as d:
+            out = os.path.join(d, "compiled.onnx")
+            InferenceSession(self._input, self._options(out, True), providers=self._providers,
+                             provider_options=self._provider_options, **self._kwargs)
+            with open(out, "rb") as f:
+                return f.read()
 
 
 # --------------------------------------------------------------------- IOBinding

@@ -17,6 +17,7 @@
 #include <sstream>
 #include <thread>
 
+#include "ep_context.h"
 #include "executor.h"
 #include "shape_inference.h"
 #include "threadpool.h"
@@ -112,6 +113,8 @@ void InferenceSession::Load(const std::string& path) {
   if (model_) ORTB_THROW(MODEL_LOADED, "This session already contains a loaded model.");
   const int64_t t0 = profiler_.NowUs();
   model_ = Model::Load(path);
+  model_path_ = path;
+  loaded_from_context_ = ExpandContextModel(model_, model_->model_dir);
   profiler_.Record("Session", "model_loading_uri", t0, profiler_.NowUs() - t0);
 }
 
@@ -119,7 +122,35 @@ void InferenceSession::LoadFromBytes(const std::string& bytes) {
   if (model_) ORTB_THROW(MODEL_LOADED, "This session already contains a loaded model.");
   const int64_t t0 = profiler_.NowUs();
   model_ = Model::LoadFromBytes(std::make_shared<std::string>(bytes), "");
+  loaded_from_context_ = ExpandContextModel(model_, "");
   profiler_.Record("Session", "model_loading_array", t0, profiler_.NowUs() - t0);
+}
+
+// ep.context_enable: store the prepared graph as a one-node EPContext model (ep_context.h)
+void InferenceSession::WriteContextModel() {
+  std::string out = so_.config.Get("ep.context_file_path");
+  if (out.empty()) {
+    ORTB_ENFORCE_ARG(!model_path_.empty(), "ep.context_file_path is required when the model was loaded from memory");
+    const size_t dot = model_path_.rfind(".onnx");
+    out = (dot == std::string::npos ? model_path_ : model_path_.substr(0, dot)) + "_ctx.onnx";
+  }
+  const bool embed = so_.config.Get("ep.context_embed_mode", "1") != "0";
+  const size_t slash = out.find_last_of('/');
+  const std::string dir = slash == std::string::npos ? "." : out.substr(0, slash);
+  std::string base = slash == std::string::npos ? out : out.substr(slash + 1);
+  const size_t dot = base.rfind(".onnx");
+  const std::string side_name = (dot == std::string::npos ? base : base.substr(0, dot)) + "_ortb200.bin";
+  std::string side;
+  const std::string bytes = MakeContextModel(*model_, embed, side_name, &side);
+  std::ofstream f(out, std::ios::binary);
+  if (!f) ORTB_THROW(FAIL, "cannot open ", out, " for writing");
+  f.write(bytes.data(), static_cast<std::streamsize>(bytes.size()));
+  if (!embed) {
+    std::ofstream sf(dir + "/" + side_name, std::ios::binary);
+    if (!sf) ORTB_THROW(FAIL, "cannot open ", dir + "/" + side_name, " for writing");
+    sf.write(side.data(), static_cast<std::streamsize>(side.size()));
+  }
+  ORTB_LOG(logger_, kInfo) << "compiled model written to " << out << (embed ? " (payload embedded)" : " (payload in " + side_name + ")");
 }
 
 static void ApplyFreeDimOverrides(Graph& g, const SessionOptions& so) {
@@ -203,7 +234,8 @@ void InferenceSession::Initialize(const std::vector<std::pair<std::string, Provi
     while (std::getline(ss, tok, ',')) if (!tok.empty()) disabled.insert(tok);
   }
   const size_t nodes_before = g.Nodes().size();
-  OptimizeGraph(g, so_.graph_optimization_level, disabled, device_.is_cuda(), so_.config, world_size);
+  // a compiled (EP context) model holds the graph as an earlier session prepared it: nothing left to optimize
+  OptimizeGraph(g, loaded_from_context_ ? 0 : so_.graph_optimization_level, disabled, device_.is_cuda(), so_.config, world_size);
   ORTB_LOG(logger_, kInfo) << "graph optimization level " << so_.graph_optimization_level << ": " << nodes_before << " -> "
                            << g.Nodes().size() << " nodes";
 
@@ -216,6 +248,7 @@ void InferenceSession::Initialize(const std::vector<std::pair<std::string, Provi
     ORTB_LOG(logger_, kInfo) << "shape inference: " << rep.inferred << " of " << rep.nodes << " nodes fully resolved";
   }
   if (!so_.optimized_model_filepath.empty()) model_->Save(so_.optimized_model_filepath);
+  if (so_.config.Get("ep.context_enable", "0") == "1" && !loaded_from_context_) WriteContextModel();
 
   ApplyThreadingAndWarnings();
   auto exec = std::make_unique<GraphExecutor>(this, &g, nullptr);
@@ -276,9 +309,10 @@ void InferenceSession::ApplyThreadingAndWarnings() {
   } else if (so_.inter_op_num_threads > 1) {
     ORTB_LOG(logger_, kWarning) << "inter_op_num_threads is only used with execution_mode=ORT_PARALLEL";
   }
-  if (!so_.enable_mem_pattern || !so_.enable_mem_reuse || !so_.enable_cpu_mem_arena)
-    ORTB_LOG(logger_, kWarning) << "enable_mem_pattern / enable_mem_reuse / enable_cpu_mem_arena have no effect: tensors come from "
-                                   "PyTorch's caching allocators (see memory.enable_memory_arena_shrinkage to give memory back)";
+  if (!so_.enable_mem_reuse || !so_.enable_cpu_mem_arena)
+    ORTB_LOG(logger_, kWarning) << "enable_mem_reuse / enable_cpu_mem_arena have no effect: tensors come from PyTorch's caching "
+                                   "allocators (see memory.enable_memory_arena_shrinkage to give memory back); enable_mem_pattern "
+                                   "controls the tracing of memory patterns (get_memory_plans)";
   if (so_.use_deterministic_compute) {
     // every kernel of this library sums in a fixed order; ATen needs to be told
     at::globalContext().setDeterministicAlgorithms(true, /*warn_only=*/true);
@@ -294,7 +328,8 @@ void InferenceSession::ApplyThreadingAndWarnings() {
       "optimization.enable_gelu_approximation", "optimization.minimal_build_optimizations", "ep.context_enable",
       "ep.context_file_path", "ep.context_embed_mode", "session.use_ort_model_bytes_directly", "session.strict_shape_type_inference",
       "session.qdqisint8allowed", "session.enable_dq_matmulnbits_fusion", "session.qdq_matmulnbits_accuracy_level",
-      "session.dynamic_block_base", "session.force_spinning_stop", "session.collect_node_memory_stats_to_file"};
+      "session.dynamic_block_base", "session.force_spinning_stop", "session.collect_node_memory_stats_to_file",
+      "session.disable_quant_qdq", "ep.context_node_name_prefix"};
   for (auto& kv : so_.config.entries) {
     if (kv.first.rfind("ortb200.", 0) == 0 || kv.first.rfind("ep.cuda.", 0) == 0) continue;
     if (!known.count(kv.first)) ORTB_LOG(logger_, kWarning) << "session config entry '" << kv.first << "' is not known to this runtime and is ignored";

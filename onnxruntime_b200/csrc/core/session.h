@@ -175,6 +175,9 @@ class InferenceSession {
 
   struct CapturedGraph;
   void ApplyThreadingAndWarnings();
+  void WriteContextModel();
+  std::string model_path_;
+  bool loaded_from_context_ = false;
   std::shared_ptr<class ThreadPool> inter_op_pool_;
   SessionOptions so_;
   std::shared_ptr<Model> model_;

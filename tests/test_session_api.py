@@ -307,14 +307,14 @@ def test_ignored_options_are_reported_and_mapped_ones_applied():
     before = torch.get_num_threads()
     try:
         so = ort.SessionOptions()
-        so.enable_mem_pattern = False
+        so.enable_mem_reuse = False
         so.inter_op_num_threads = 3
         so.intra_op_num_threads = 2
         so.add_session_config_entry("session.no_such_key", "1")
         so.add_session_config_entry("session.disable_prepacking", "1")
         ort.InferenceSession(model, so, providers=["CPUExecutionProvider"])
         text = "\\n".join(l for _, l in lines)
-        assert "enable_mem_pattern" in text and "inter_op_num_threads is only used" in text
+        assert "enable_mem_reuse" in text and "inter_op_num_threads is only used" in text
         assert "session.no_such_key" in text and "session.disable_prepacking" not in text
         assert torch.get_num_threads() == 2
     finally:
@@ -353,3 +353,43 @@ def test_memory_plan_reuses_buffers_of_dead_values():
     by_name = {b[0]: b for b in p["buffers"]}
     assert by_name["flat"][1] == 0 and by_name["flat"][5] == -1
     assert sess.get_memory_stats() == {}
+
+
+def test_compiled_model_round_trip_through_an_ep_context_node(tmp_path):
+    """ModelCompiler / ep.context_enable store the prepared graph in one EPContext node; loading that model gives the
+    same results and runs no optimizer pass again."""
+    import numpy as np
+    import onnxruntime_b200 as ort
+    from onnxruntime_b200 import onnx_lite as ol
+    from helpers import op_counts
+    T = ol.TensorProto
+    rs = np.random.RandomState(3)
+    nodes = [ol.make_node("MatMul", ["x", "w"], ["m"]), ol.make_node("Add", ["m", "b"], ["a"]),
+             ol.make_node("Mul", ["a", "half"], ["h"]), ol.make_node("Div", ["a", "sqrt2"], ["d"]), ol.make_node("Erf", ["d"], ["e"]),
+             ol.make_node("Add", ["e", "one"], ["p"]), ol.make_node("Mul", ["h", "p"], ["y"])]
+    inits = [ol.make_tensor("w", rs.randn(8, 8).astype(np.float32)), ol.make_tensor("b", rs.randn(8).astype(np.float32)),
+             ol.make_tensor("half", np.array(0.5, np.float32)), ol.make_tensor("sqrt2", np.array(np.sqrt(2.0), np.float32)),
+             ol.make_tensor("one", np.array(1.0, np.float32))]
+    g = ol.make_graph(nodes, "gelu_mlp", [ol.make_tensor_value_info("x", T.FLOAT, ["n", 8])], [ol.make_tensor_value_info("y", T.FLOAT, ["n", 8])], inits)
+    src = tmp_path / "model.onnx"
+    src.write_bytes(ol.make_model(g, opset=17, metadata={"k": "v"}).serialize())
+    x = rs.randn(3, 8).astype(np.float32)
+    want = ort.InferenceSession(str(src), providers=["CPUExecutionProvider"]).run(None, {"x": x})[0]
+
+    embedded = tmp_path / "embedded_ctx.onnx"
+    ort.ModelCompiler(None, str(src), embed_compiled_data_into_model=True, providers=["CPUExecutionProvider"]).compile_to_file(str(embedded))
+    side = tmp_path / "side_ctx.onnx"
+    ort.ModelCompiler(None, str(src), embed_compiled_data_into_model=False, providers=["CPUExecutionProvider"]).compile_to_file(str(side))
+    assert (tmp_path / "side_ctx_ortb200.bin").exists() and side.stat().st_size < embedded.stat().st_size
+    for path in (embedded, side):
+        outer = ol.load(str(path)) if hasattr(ol, "load") else None
+        so = ort.SessionOptions()
+        so.graph_optimization_level = ort.GraphOptimizationLevel.ORT_DISABLE_ALL    # the payload is already optimized
+        sess = ort.InferenceSession(str(path), so, providers=["CPUExecutionProvider"])
+        counts = op_counts(sess)
+        assert "EPContext" not in counts and "Erf" not in counts and counts.get("Gelu", 0) + counts.get("BiasGelu", 0) == 1
+        np.testing.assert_allclose(sess.run(None, {"x": x})[0], want, rtol=1e-6, atol=1e-6)
+        assert sess.get_modelmeta().custom_metadata_map == {"k": "v"}
+        assert [i.name for i in sess.get_inputs()] == ["x"] and sess.get_inputs()[0].shape == ["n", 8]
+    blob = ort.ModelCompiler(None, src.read_bytes(), providers=["CPUExecutionProvider"]).compile_to_bytes()
+    np.testing.assert_allclose(ort.InferenceSession(blob, providers=["CPUExecutionProvider"]).run(None, {"x": x})[0], want, rtol=1e-6, atol=1e-6)
