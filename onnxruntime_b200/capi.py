@@ -413,14 +413,17 @@ class RunOptions:
 
 # --------------------------------------------------------------- LoRA adapters
 _ADAPTER_MAGIC = b"ORTB200ADAPTER\0\0"
+_TORCH_TO_ONNX_ELEM = {torch.float32: 1, torch.uint8: 2, torch.int8: 3, torch.int16: 5, torch.int32: 6, torch.int64: 7,
+                       torch.bool: 9, torch.float16: 10, torch.float64: 11, torch.bfloat16: 16,
+                       torch.float8_e4m3fn: 17, torch.float8_e5m2: 19}
 
 
 class AdapterFormat:
     """Adapter file: named parameters plus an adapter version and the version of the model they belong to
-    (the role of onnxruntime.AdapterFormat, onnxruntime/python/onnxruntime_inference_collection.py:67; the
-    reference stores the same content in a flatbuffer).  Layout: 16-byte magic, three little-endian int32
-    (format version, adapter version, model version), uint32 count, then per parameter a uint32 length and a
-    serialized ONNX TensorProto."""
+    (onnxruntime.AdapterFormat, onnxruntime/python/onnxruntime_inference_collection.py:67).  Files are written in the
+    reference's own format - a FlatBuffer with file identifier ``TORT`` (``flatbuf_lite.py``) - so adapters travel in
+    both directions; ``read_adapter`` also accepts the length-prefixed TensorProto container earlier versions of this
+    package wrote (16-byte magic ``ORTB200ADAPTER``)."""
 
     def __init__(self):
         self._adapter_version = 1
@@ -446,33 +449,52 @@ class AdapterFormat:
         return {k: v if isinstance(v, OrtValue) else OrtValue(_to_torch(v)) for k, v in self._parameters.items()}
 
     def export_adapter(self, file_path: str) -> None:
-        import struct
-        from . import onnx_lite as ol
-        out = bytearray(_ADAPTER_MAGIC)
-        out += struct.pack("<iiiI", 1, self._adapter_version, self._model_version, len(self._parameters))
+        from . import flatbuf_lite as fb
+        params = []
         for name, v in self._parameters.items():
-            t = ol.make_tensor(name, _to_torch(v)).serialize()
-            out += struct.pack("<I", len(t)) + t
+            t = _to_torch(v).detach().cpu().contiguous()
+            et = _TORCH_TO_ONNX_ELEM.get(t.dtype)
+            if et is None:
+                raise InvalidArgument(f"adapter parameter '{name}' has unsupported type {t.dtype}")
+            raw = t.reshape(-1).view(torch.uint8).numpy().tobytes() if t.numel() else b""
+            params.append((name, list(t.shape), et, raw))
         with open(file_path, "wb") as f:
-            f.write(bytes(out))
+            f.write(fb.write_adapter(self._adapter_version, self._model_version, params))
 
     @staticmethod
     def read_adapter(file_path: str) -> "AdapterFormat":
         import struct
+        from . import flatbuf_lite as fb
         with open(file_path, "rb") as f:
             buf = f.read()
+        a = AdapterFormat()
+        if fb.is_adapter_flatbuffer(buf):
+            try:
+                fmt, av, mv, params = fb.read_adapter(buf)
+            except (ValueError, struct.error) as e:
+                raise InvalidArgument(f"{file_path}: malformed adapter file ({e})") from None
+            if fmt != fb.ADAPTER_FORMAT_VERSION:
+                raise InvalidArgument(f"unsupported adapter format version {fmt}")
+            a._adapter_version, a._model_version = av, mv
+            onnx_to_torch = {v: k for k, v in _TORCH_TO_ONNX_ELEM.items()}
+            for name, dims, et, raw in params:
+                dt = onnx_to_torch.get(et)
+                if dt is None:
+                    raise InvalidArgument(f"adapter parameter '{name}' has unsupported element type {et}")
+                t = torch.frombuffer(bytearray(raw), dtype=torch.uint8).view(dt) if raw else torch.empty(0, dtype=dt)
+                a._parameters[name] = t.reshape(dims).clone()
+            return a
         if buf[:16] != _ADAPTER_MAGIC:
             raise InvalidArgument(f"{file_path} is not an adapter file")
         fmt, av, mv, n = struct.unpack_from("<iiiI", buf, 16)
         if fmt != 1:
             raise InvalidArgument(f"unsupported adapter format version {fmt}")
-        a = AdapterFormat()
         a._adapter_version, a._model_version = av, mv
         off = 32
+        from . import onnx_lite as ol
         for _ in range(n):
             (ln,) = struct.unpack_from("<I", buf, off)
             off += 4
-            from . import onnx_lite as ol
             blob = bytes(buf[off:off + ln])
             off += ln
             a._parameters[ol.load_tensor(blob).name] = C.tensor_from_proto(blob)

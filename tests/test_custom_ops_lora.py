@@ -121,3 +121,54 @@ def test_lora_adapter_round_trip_and_activation(tmp_path):
     ro.add_active_adapter(adapter)
     np.testing.assert_allclose(sess.run(None, {"x": x}, ro)[0], x @ (W + A @ B), rtol=1e-4, atol=1e-5)
     np.testing.assert_allclose(sess.run(None, {"x": x})[0], x @ W, rtol=1e-5)  # without the options the base model runs
+
+
+def test_adapter_files_use_the_flatbuffer_layout_of_the_reference(tmp_path):
+    """export_adapter writes a FlatBuffer with identifier TORT (Adapter{format_version, adapter_version, model_version,
+    parameters[name, dims, data_type, raw_data aligned to 8]}); a hand-assembled buffer in that layout reads back."""
+    import struct
+    import torch
+    import onnxruntime_b200 as ort
+    from onnxruntime_b200 import flatbuf_lite as fb
+    a = ort.AdapterFormat()
+    a.set_adapter_version(7)
+    a.set_model_version(3)
+    a.set_parameters({"lora_a": np.arange(8, dtype=np.float32).reshape(4, 2), "lora_b": torch.arange(6).reshape(2, 3).to(torch.bfloat16),
+                      "steps": np.array([5], np.int64)})
+    path = tmp_path / "a.onnx_adapter"
+    a.export_adapter(str(path))
+    buf = path.read_bytes()
+    assert buf[4:8] == b"TORT"
+    fmt, av, mv, params = fb.read_adapter(buf)
+    assert (fmt, av, mv) == (1, 7, 3) and [p[0] for p in params] == ["lora_a", "lora_b", "steps"]
+    assert params[0][1:3] == ([4, 2], 1) and params[1][1:3] == ([2, 3], 16) and params[2][1:3] == ([1], 7)
+    for name, dims, et, raw in params:
+        assert buf.find(raw) % 8 == 0                       # raw_data: force_align 8
+    b = ort.AdapterFormat.read_adapter(str(path))
+    assert b.get_adapter_version() == 7 and b.get_model_version() == 3
+    got = b.get_parameters()
+    np.testing.assert_array_equal(got["lora_a"].numpy(), np.arange(8, dtype=np.float32).reshape(4, 2))
+    assert got["lora_b"]._tensor.dtype == torch.bfloat16 and got["lora_b"]._tensor.float().tolist() == [[0, 1, 2], [3, 4, 5]]
+    # a buffer laid out by hand, fields in another order and one field absent (default 0), as another writer might do
+    raw = struct.pack("<2f", 1.5, -2.0)
+    out = bytearray(b"\0\0\0\0TORT")
+    vt = len(out); out += struct.pack("<HHHHHH", 12, 12, 0, 4, 0, 8)          # format_version, model_version absent
+    tab = len(out); out += struct.pack("<iiI", tab - vt, 9, 0)
+    struct.pack_into("<I", out, 0, tab)
+    vec = len(out); struct.pack_into("<I", out, tab + 8, vec - (tab + 8)); out += struct.pack("<II", 1, 0)
+    pvt = len(out); out += struct.pack("<HHHHHH", 12, 20, 16, 12, 4, 8)       # name at 16, dims at 12, type at 4, data at 8
+    while len(out) % 4:
+        out.append(0)
+    pt = len(out); out += struct.pack("<iiIII", pt - pvt, 1, 0, 0, 0)
+    struct.pack_into("<I", out, vec + 4, pt - (vec + 4))
+    while (len(out) + 4) % 8:
+        out.append(0)
+    struct.pack_into("<I", out, pt + 8, len(out) - (pt + 8)); out += struct.pack("<I", len(raw)) + raw
+    struct.pack_into("<I", out, pt + 12, len(out) - (pt + 12)); out += struct.pack("<Iq", 1, 2)
+    struct.pack_into("<I", out, pt + 16, len(out) - (pt + 16)); out += struct.pack("<I", 1) + b"w\0"
+    fmt, av, mv, params = fb.read_adapter(bytes(out))
+    assert (fmt, av, mv) == (0, 9, 0) and params == [("w", [2], 1, raw)]
+    bad = tmp_path / "bad.onnx_adapter"
+    bad.write_bytes(bytes(out[:40]))
+    with pytest.raises(Exception):
+        ort.AdapterFormat.read_adapter(str(bad))
