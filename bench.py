@@ -127,6 +127,7 @@ def main():
     ap.add_argument("--fused-prep", default="auto", help="auto / 1: decode attention unpacks, rotates and appends the new token itself; 0: separate kernel")
     ap.add_argument("--attn-prefetch", type=int, default=0, help="decode attention asks the L2 for the output projection's weights")
     ap.add_argument("--attn-algo", type=int, default=0, help="decode attention: 0 = tcgen05 kernel, 1 = CUDA-core split-KV kernel")
+    ap.add_argument("--tunable", type=int, default=0, help="1: TunableOp picks the GEMM launch configurations on the first (eager) step")
     ap.add_argument("--fused-collectives", type=int, default=1, help="0: NCCL all-reduce after each row-parallel GEMM (baseline)")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -170,7 +171,10 @@ def main():
         so.add_session_config_entry("ortb200.decode_attention_algo", str(args.attn_algo))
         so.add_session_config_entry("ortb200.fused_gqa_prep", str(args.fused_prep))
         so.add_session_config_entry("ortb200.attention_prefetch", str(args.attn_prefetch))
-        providers = [("CUDAExecutionProvider", {"device_id": str(local), "enable_cuda_graph": "0" if args.no_graph else "1"})]
+        popts = {"device_id": str(local), "enable_cuda_graph": "0" if args.no_graph else "1"}
+        if args.tunable:
+            popts.update({"tunable_op_enable": "1", "tunable_op_tuning_enable": "1"})
+        providers = [("CUDAExecutionProvider", popts)]
         sess = ort.InferenceSession(model, so, providers=providers, dist=info if tp > 1 else None, enable_fallback=False)
         del weights
         torch.cuda.empty_cache()

@@ -740,6 +740,32 @@ class InferenceSession:
         (onnxruntime/core/framework/mem_pattern_planner.h)."""
         return self._sess.memory_plans()
 
+    _TUNING_VALIDATORS = {"ORTB200_VERSION": "0.1.0", "DEVICE_ARCH": "sm_100a"}
+
+    def get_tuning_results(self) -> List[dict]:
+        """TunableOp results in the reference's shape (``InferenceSession.get_tuning_results``): one entry per
+        provider with ``results[op][signature] = configuration`` and the validators that must match on import."""
+        res = self._sess.tuning_results()
+        if not res:
+            return []
+        gemm = {k: f"splits={v[0]},bn={v[1]},tile_rows={v[2]}" for k, v in res.items()}
+        return [{"ep": "CUDAExecutionProvider", "results": {"Gemm": gemm}, "validators": dict(self._TUNING_VALIDATORS)}]
+
+    def set_tuning_results(self, results: List[dict], *, error_on_invalid: bool = False) -> None:
+        for entry in results or []:
+            ok = entry.get("ep") == "CUDAExecutionProvider" and entry.get("validators") == self._TUNING_VALIDATORS
+            if not ok:
+                if error_on_invalid:
+                    raise InvalidArgument("tuning results were recorded by another provider, version or device architecture")
+                continue
+            for sig, cfg in entry.get("results", {}).get("Gemm", {}).items():
+                try:
+                    kv = dict(item.split("=") for item in cfg.split(","))
+                    self._sess.set_tuning_result(sig, int(kv["splits"]), int(kv["bn"]), int(kv["tile_rows"]))
+                except (KeyError, ValueError):
+                    if error_on_invalid:
+                        raise InvalidArgument(f"malformed tuning result for {sig}: {cfg!r}") from None
+
     def get_memory_stats(self) -> dict:
         """Statistics of the device arena (the torch caching allocator) for a GPU session; empty for CPU sessions."""
         return self._sess.memory_stats()

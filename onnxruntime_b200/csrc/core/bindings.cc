@@ -271,6 +271,19 @@ PYBIND11_MODULE(_core, m) {
         }
         return out;
       })
+      .def("tuning_results", [](InferenceSession& s) {
+        py::dict d;
+        for (auto& kv : s.tuning_results)
+          d[py::str(kv.first)] = py::make_tuple(kv.second.force_splits, kv.second.force_bn, kv.second.force_tile_rows, kv.second.microseconds);
+        return d;
+      })
+      .def("set_tuning_result", [](InferenceSession& s, const std::string& key, int splits, int bn, int rows) {
+        InferenceSession::TunedGemm t;
+        t.force_splits = splits;
+        t.force_bn = bn;
+        t.force_tile_rows = rows;
+        s.tuning_results[key] = t;
+      })
       .def("memory_stats", [](InferenceSession& s) {
         // arena statistics of the device allocator (the counterpart of the reference's BFCArena::GetStats)
         py::dict d;

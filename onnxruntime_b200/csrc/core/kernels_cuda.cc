@@ -8,6 +8,8 @@
 // onnxruntime/contrib_ops/cuda/bert/{skip_layer_norm.cc,rotary_embedding.cc,
 // group_query_attention.cc,fast_gelu.cc}, quantization/matmul_nbits.cc, moe/moe.cc.
 #include <ATen/ATen.h>
+#include <sstream>
+#include <chrono>
 #include <ATen/cuda/CUDAContext.h>
 
 #include "cuda_ops.h"
@@ -48,6 +50,80 @@ bool HalfType(at::ScalarType t) { return t == at::kHalf || t == at::kBFloat16; }
 
 void CheckLaunch(int rc, const char* what) {
   if (rc != 0) ORTB_THROW(EP_FAIL, what, " rejected its arguments (code ", rc, ")");
+}
+
+// TunableOp for the GEMM: the first time a signature is seen (and tuning is enabled, and the stream is not being
+// captured) every candidate launch configuration runs a few times with the L2 flushed in between; the fastest one is
+// remembered in the session.  Candidates are the forced forms of the kernels' own heuristics: token-tile width and
+// split-K cluster size for decode-shaped problems, tile family for large ones.
+void ApplyTunedConfig(Ctx& ctx, ortb200_gemm_args* a, at::ScalarType out_type) {
+  InferenceSession* s = ctx.session();
+  std::ostringstream key;
+  key << "Gemm_" << c10::toString(out_type) << "_in" << a->in_dtype << "_" << a->M << "_" << a->N << "_" << a->K << "_act" << a->act
+      << (a->rms_eps > 0.f ? "_rms" : "") << (a->bias ? "_b" : "") << (a->residual ? "_r" : "");
+  auto it = s->tuning_results.find(key.str());
+  cudaStream_t stream = static_cast<cudaStream_t>(ctx.cuda_stream());
+  if (it == s->tuning_results.end()) {
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    cudaStreamIsCapturing(stream, &cap);
+    if (!s->tunable_op_tuning_enable || cap != cudaStreamCaptureStatusNone) return;
+    struct Cand { int splits, bn, rows; };
+    std::vector<Cand> cands = {{0, 0, 0}};
+    if (a->M <= 64 && a->in_dtype != ORTB200_F8E4M3) {
+      for (int bn : {16, 32, 64}) {
+        if (bn < a->M && bn != 64) continue;  // one token tile per weight tile: the weights stream once
+        for (int splits : {1, 2, 4, 8}) cands.push_back({splits, bn, 0});
+      }
+    } else if (a->M > 128 && a->in_dtype == 0 && a->act != ORTB200_ACT_SWIGLU) {
+      cands.push_back({0, 0, 128});
+      cands.push_back({0, 0, 512});
+    }
+    static at::Tensor flush;  // larger than the L2: every timed launch starts cold, as in a model step
+    if (!flush.defined() || flush.device() != ctx.device()) flush = at::empty({256LL << 20}, at::TensorOptions().dtype(at::kByte).device(ctx.device()));
+    cudaEvent_t e0, e1;
+    cudaEventCreate(&e0);
+    cudaEventCreate(&e1);
+    const auto t_begin = std::chrono::steady_clock::now();
+    InferenceSession::TunedGemm best;
+    float best_us = 0.f;
+    for (const Cand& c : cands) {
+      ortb200_gemm_args t = *a;
+      t.force_splits = c.splits;
+      t.force_bn = c.bn;
+      t.force_tile_rows = c.rows;
+      if (ortb200_gemm(&t, stream) != 0) continue;  // a configuration the kernels do not offer for this shape
+      float sum = 0.f;
+      const int iters = 3;
+      for (int i = 0; i < iters; ++i) {
+        flush.zero_();
+        cudaEventRecord(e0, stream);
+        ortb200_gemm(&t, stream);
+        cudaEventRecord(e1, stream);
+        cudaEventSynchronize(e1);
+        float ms = 0.f;
+        cudaEventElapsedTime(&ms, e0, e1);
+        sum += ms;
+      }
+      const float us = sum / iters * 1e3f;
+      if (best_us == 0.f || us < best_us) {
+        best_us = us;
+        best.force_splits = c.splits;
+        best.force_bn = c.bn;
+        best.force_tile_rows = c.rows;
+      }
+      const auto elapsed = std::chrono::duration_cast<std::chrono::milliseconds>(std::chrono::steady_clock::now() - t_begin).count();
+      if (elapsed > s->tunable_op_max_tuning_duration_ms) break;
+    }
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    best.microseconds = best_us;
+    it = s->tuning_results.emplace(key.str(), best).first;
+    ORTB_VLOG(s->logger(), 1) << "tuned " << key.str() << ": splits " << best.force_splits << ", bn " << best.force_bn << ", tile rows "
+                              << best.force_tile_rows << " (" << best_us << " us)";
+  }
+  a->force_splits = it->second.force_splits;
+  a->force_bn = it->second.force_bn;
+  a->force_tile_rows = it->second.force_tile_rows;
 }
 
 // out[M,N] = act(x[M,K] @ w_nk[N,K]^T + bias) + residual on the tcgen05 GEMM.
@@ -91,6 +167,7 @@ at::Tensor LaunchGemm(Ctx& ctx, const at::Tensor& x2d, const at::Tensor& w_nk, i
     for (int i = 0; i < s->world_size && i < 8; ++i) a.peers[i] = s->symm_peers[i];
     a.symm_bytes = s->symm_bytes;
   }
+  if (s->tunable_op_enable && !fused_allreduce) ApplyTunedConfig(ctx, &a, out_type);
   CheckLaunch(ortb200_gemm(&a, ctx.cuda_stream()), "ortb200_gemm");
   s->AddLaunches(fused_allreduce && M > 64 ? 2 : 1);
   return out;

@@ -345,6 +345,13 @@ void InferenceSession::ApplyThreadingAndWarnings() {
     for (auto& kv : po->second) {
       if (!cuda_known.count(kv.first)) {
         ORTB_LOG(logger_, kWarning) << "CUDA provider option '" << kv.first << "' is not known and is ignored";
+      } else if (kv.first == "tunable_op_enable") {
+        tunable_op_enable = kv.second == "1" || kv.second == "true" || kv.second == "True";
+      } else if (kv.first == "tunable_op_tuning_enable") {
+        tunable_op_tuning_enable = kv.second == "1" || kv.second == "true" || kv.second == "True";
+      } else if (kv.first == "tunable_op_max_tuning_duration_ms") {
+        const int ms = std::stoi(kv.second);
+        if (ms > 0) tunable_op_max_tuning_duration_ms = ms;
       } else if (kv.first == "use_tf32") {
         at::globalContext().setAllowTF32CuBLAS(kv.second == "1");
       } else if (kv.first == "gpu_mem_limit" && device_.is_cuda()) {

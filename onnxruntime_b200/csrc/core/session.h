@@ -160,6 +160,18 @@ class InferenceSession {
   void CheckDeviceStatus();
   // Symmetric workspace for the fused compute+collective kernels: base address of every rank's buffer as mapped
   // into this process (index = rank), and its size.  Empty = not available (collectives go through the process group).
+  // TunableOp (CUDA provider options tunable_op_enable / tunable_op_tuning_enable / tunable_op_max_tuning_duration_ms;
+  // reference: onnxruntime/core/framework/tunable.h, core/providers/cuda/tunable/cuda_tuning_context.cc): per GEMM
+  // signature the launch configuration that measured fastest on this device.  Results can be exported and loaded
+  // again (get_tuning_results / set_tuning_results), so a deployment tunes once.
+  struct TunedGemm {
+    int force_splits = 0, force_bn = 0, force_tile_rows = 0;
+    float microseconds = 0.f;  // 0 when the entry was loaded, not measured
+  };
+  std::map<std::string, TunedGemm> tuning_results;
+  bool tunable_op_enable = false, tunable_op_tuning_enable = false;
+  int tunable_op_max_tuning_duration_ms = 200;  // per signature
+
   std::vector<void*> symm_peers;
   int64_t symm_bytes = 0;
   int64_t library_collective_calls = 0;  // process-group collectives issued so far (the in-kernel ones do not count)

@@ -69,3 +69,37 @@ def test_argmax_treats_the_two_zeros_as_equal():
     x[2, 7] = 0.5
     got = K.argmax(x).cpu()
     assert got.tolist() == torch.argmax(x, dim=-1).cpu().tolist() == [10, 10, 7]
+
+
+def test_tunable_gemm_picks_a_configuration_and_results_travel():
+    """tunable_op_enable + tunable_op_tuning_enable: the first run of a GEMM signature times the candidate launch
+    configurations and keeps the fastest; results export / import in the reference's get / set_tuning_results shape and
+    the tuned session computes the same product."""
+    torch.manual_seed(1)
+    K, N = 1024, 2048
+    W = (torch.randn(K, N) * 0.05).to(torch.bfloat16)
+    model = graph_model([ol.make_node("MatMul", ["x", "W"], ["y"])], [ol.make_tensor_value_info("x", T.BFLOAT16, ["m", K])],
+                        [ol.make_tensor_value_info("y", T.BFLOAT16, None)], [ol.make_tensor("W", W)])
+    opts = {"tunable_op_enable": "1", "tunable_op_tuning_enable": "1", "tunable_op_max_tuning_duration_ms": "100"}
+    sess = ort.InferenceSession(model, providers=[("CUDAExecutionProvider", opts)], enable_fallback=False)
+    assert sess.get_tuning_results() == []
+    for m in (8, 300):
+        x = (torch.randn(m, K) * 0.5).to(torch.bfloat16).cuda()
+        y = sess.run(None, {"x": x})[0]
+        ref = x.float() @ W.float().cuda()
+        assert (torch.as_tensor(y).float().cuda() - ref).abs().max() / ref.abs().max() < 2e-2
+    sess.check_device_status()
+    res = sess.get_tuning_results()
+    assert len(res) == 1 and res[0]["ep"] == "CUDAExecutionProvider"
+    gemm = res[0]["results"]["Gemm"]
+    assert len(gemm) == 2 and all(k.startswith("Gemm_") and "splits=" in v for k, v in gemm.items())
+    # a second session takes the results without tuning
+    sess2 = ort.InferenceSession(model, providers=[("CUDAExecutionProvider", {"tunable_op_enable": "1"})], enable_fallback=False)
+    sess2.set_tuning_results(res)
+    assert sess2.get_tuning_results()[0]["results"] == res[0]["results"]
+    x = (torch.randn(8, K) * 0.5).to(torch.bfloat16).cuda()
+    np.testing.assert_array_equal(torch.as_tensor(sess2.run(None, {"x": x})[0]).float().cpu().numpy(),
+                                  torch.as_tensor(sess.run(None, {"x": x})[0]).float().cpu().numpy())
+    bad = [dict(res[0], validators={"ORTB200_VERSION": "other"})]
+    with pytest.raises(Exception):
+        sess2.set_tuning_results(bad, error_on_invalid=True)

@@ -393,3 +393,17 @@ def test_compiled_model_round_trip_through_an_ep_context_node(tmp_path):
         assert [i.name for i in sess.get_inputs()] == ["x"] and sess.get_inputs()[0].shape == ["n", 8]
     blob = ort.ModelCompiler(None, src.read_bytes(), providers=["CPUExecutionProvider"]).compile_to_bytes()
     np.testing.assert_allclose(ort.InferenceSession(blob, providers=["CPUExecutionProvider"]).run(None, {"x": x})[0], want, rtol=1e-6, atol=1e-6)
+
+
+def test_tuning_results_are_empty_on_cpu_and_imports_are_validated():
+    import onnxruntime_b200 as ort
+    sess = ort.InferenceSession(_wide_model(2, 1, 8), providers=["CPUExecutionProvider"])
+    assert sess.get_tuning_results() == []
+    good = [{"ep": "CUDAExecutionProvider", "validators": {"ORTB200_VERSION": "0.1.0", "DEVICE_ARCH": "sm_100a"},
+             "results": {"Gemm": {"Gemm_BFloat16_in0_8_64_64_act0": "splits=2,bn=16,tile_rows=0"}}}]
+    sess.set_tuning_results(good)
+    assert sess.get_tuning_results()[0]["results"]["Gemm"] == good[0]["results"]["Gemm"]
+    sess.set_tuning_results([{"ep": "ROCMExecutionProvider", "validators": {}, "results": {}}])      # skipped silently
+    import pytest
+    with pytest.raises(ort.capi.InvalidArgument):
+        sess.set_tuning_results([{"ep": "ROCMExecutionProvider", "validators": {}, "results": {}}], error_on_invalid=True)
