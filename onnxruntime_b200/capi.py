@@ -13,6 +13,7 @@ from __future__ import annotations
 
 import os
 import threading
+from struct import error as struct_error
 from enum import IntEnum
 from typing import Any, Dict, List, Optional, Sequence, Tuple, Union
 
@@ -141,6 +142,10 @@ _ONNX_ELEM_TO_TORCH = {
     9: torch.bool, 10: torch.float16, 11: torch.float64, 12: torch.uint32, 13: torch.uint64, 16: torch.bfloat16,
     17: torch.float8_e4m3fn, 19: torch.float8_e5m2,
 }
+
+
+def _is_ort_format(buf: bytes) -> bool:
+    return len(buf) >= 8 and bytes(buf[4:8]) == b"ORTM"
 
 
 def _to_torch(value: Any) -> torch.Tensor:
@@ -605,6 +610,18 @@ class InferenceSession:
             pairs = [(n, o) for n, o in zip(names, opts) if n != "CUDAExecutionProvider"]
             names, opts = [p[0] for p in pairs] or ["CPUExecutionProvider"], [p[1] for p in pairs] or [{}]
         sess = C.InferenceSession(self._sess_options._c)
+        cfg = self._sess_options._c.config_entries()
+        load_format = cfg.get("session.load_model_format", "").upper()
+        if self._model_path is not None and (load_format == "ORT" or (load_format == "" and self._model_path.lower().endswith(".ort"))):
+            with open(self._model_path, "rb") as f:
+                self._model_bytes, self._model_path = f.read(), None
+        if self._model_bytes is not None and (load_format == "ORT" or (load_format == "" and _is_ort_format(self._model_bytes))):
+            # ORT-format (FlatBuffers) model: converted to the ONNX form the core loads (ort_format.py)
+            from . import ort_format
+            try:
+                self._model_bytes = ort_format.ort_to_onnx(self._model_bytes).serialize()
+            except (ValueError, struct_error) as e:
+                raise InvalidProtobuf(f"cannot read the ORT-format model: {e}") from None
         if self._model_path is not None:
             sess.load(self._model_path)
         else:
@@ -616,6 +633,15 @@ class InferenceSession:
             sess.world_size = dist.world_size
         sess.initialize(list(zip(names, opts)), disabled)
         self._sess = sess
+        out_path = self._sess_options.optimized_model_filepath
+        save_format = cfg.get("session.save_model_format", "").upper()
+        if out_path and (save_format == "ORT" or (save_format == "" and out_path.lower().endswith(".ort"))):
+            # the core wrote the optimized model as ONNX; rewrite it in the ORT format
+            from . import onnx_lite as ol, ort_format
+            with open(out_path, "rb") as f:
+                optimized = ol.load_model(f.read())
+            with open(out_path, "wb") as f:
+                f.write(ort_format.onnx_to_ort(optimized))
         self._providers = sess.providers()
         self._provider_options = sess.provider_options()
         self._inputs_meta = [NodeArg(m) for m in sess.inputs_meta()]

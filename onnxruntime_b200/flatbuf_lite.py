@@ -151,3 +151,146 @@ def write_adapter(adapter_version: int, model_version: int, params: List[Paramet
         buf += struct.pack("<I", len(raw)) + bytes(raw)
     align(8)
     return bytes(buf)
+
+
+# ------------------------------------------------------------------------------------------------------------------
+# Generic helpers used by the ORT-format reader / writer (ort_format.py)
+class Table(_Table):
+    """Read access to one FlatBuffers table by field index."""
+
+    def table(self, field: int):
+        p = self._indirect(field)
+        return Table(self.buf, p) if p else None
+
+    def tables(self, field: int) -> List["Table"]:
+        first, n = self.vector(field, 4)
+        out = []
+        for i in range(n):
+            slot = first + 4 * i
+            (rel,) = struct.unpack_from("<I", self.buf, slot)
+            out.append(Table(self.buf, slot + rel))
+        return out
+
+    def strings(self, field: int) -> List[str]:
+        first, n = self.vector(field, 4)
+        out = []
+        for i in range(n):
+            slot = first + 4 * i
+            (rel,) = struct.unpack_from("<I", self.buf, slot)
+            p = slot + rel
+            (ln,) = struct.unpack_from("<I", self.buf, p)
+            if p + 4 + ln > len(self.buf):
+                raise ValueError("string outside the buffer")
+            out.append(bytes(self.buf[p + 4:p + 4 + ln]).decode("utf-8"))
+        return out
+
+    def scalars(self, field: int, fmt: str) -> list:
+        size = struct.calcsize("<" + fmt)
+        first, n = self.vector(field, size)
+        return list(struct.unpack_from("<%d%s" % (n, fmt), self.buf, first)) if n else []
+
+    def bytes_(self, field: int) -> bytes:
+        first, n = self.vector(field, 1)
+        return bytes(self.buf[first:first + n])
+
+
+def root_table(buf: bytes, identifier: bytes) -> Table:
+    if len(buf) < 8 or bytes(buf[4:8]) != identifier:
+        raise ValueError("file identifier %r missing" % identifier)
+    (root,) = struct.unpack_from("<I", buf, 0)
+    return Table(buf, root)
+
+
+_SCALAR = {"i8": "b", "u8": "B", "bool": "?", "i32": "i", "u32": "I", "i64": "q", "u64": "Q", "f32": "f"}
+
+
+class Builder:
+    """Forward-writing FlatBuffers builder: a table is described as a list ``[(kind, value) or None, ...]`` indexed by
+    field id.  Kinds: the scalar names of ``_SCALAR``; ``str``; ``table`` (a nested description); ``vec_table``;
+    ``vec_str``; ``vec_<scalar>`` (``vec_u8`` takes bytes).  Every referenced object is written behind the table that
+    refers to it, so all offsets point forward as the format requires."""
+
+    def __init__(self, identifier: bytes):
+        self.buf = bytearray(b"\0\0\0\0" + identifier)
+
+    def _align(self, n: int, bias: int = 0) -> None:
+        while (len(self.buf) + bias) % n:
+            self.buf.append(0)
+
+    def _patch(self, slot: int, target: int) -> None:
+        struct.pack_into("<I", self.buf, slot, target - slot)
+
+    def finish(self, root_fields) -> bytes:
+        pos = self._table(root_fields)
+        struct.pack_into("<I", self.buf, 0, pos)
+        self._align(8)
+        return bytes(self.buf)
+
+    def _table(self, fields) -> int:
+        # inline layout: 4-byte vtable offset, then the present fields in order with natural alignment
+        layout, off, big = [], 4, 4
+        for f in fields:
+            if f is None:
+                layout.append(0)
+                continue
+            kind = f[0]
+            size = struct.calcsize("<" + _SCALAR[kind]) if kind in _SCALAR else 4
+            off = (off + size - 1) // size * size
+            layout.append(off)
+            off += size
+            big = max(big, size)
+        inline = (off + 3) // 4 * 4
+        self._align(2)
+        vt_size = 4 + 2 * len(fields)
+        # the table must start on a `big` boundary: pad in front of the vtable
+        self._align(big, bias=vt_size + (-vt_size % 4))
+        vt = len(self.buf)
+        self.buf += struct.pack("<HH", vt_size, inline) + b"".join(struct.pack("<H", o) for o in layout)
+        self._align(4)
+        tab = len(self.buf)
+        assert tab % big == 0
+        self.buf += struct.pack("<i", tab - vt) + b"\0" * (inline - 4)
+        pending = []
+        for f, o in zip(fields, layout):
+            if f is None:
+                continue
+            kind, value = f
+            if kind in _SCALAR:
+                struct.pack_into("<" + _SCALAR[kind], self.buf, tab + o, value)
+            else:
+                pending.append((tab + o, kind, value))
+        for slot, kind, value in pending:
+            self._patch(slot, self._object(kind, value))
+        return tab
+
+    def _string(self, s: str) -> int:
+        self._align(4)
+        pos = len(self.buf)
+        b = s.encode("utf-8")
+        self.buf += struct.pack("<I", len(b)) + b + b"\0"
+        return pos
+
+    def _object(self, kind: str, value) -> int:
+        if kind == "str":
+            return self._string(value)
+        if kind == "table":
+            return self._table(value)
+        if kind in ("vec_table", "vec_str"):
+            self._align(4)
+            pos = len(self.buf)
+            self.buf += struct.pack("<I", len(value)) + b"\0" * (4 * len(value))
+            for i, v in enumerate(value):
+                target = self._table(v) if kind == "vec_table" else self._string(v)
+                self._patch(pos + 4 + 4 * i, target)
+            return pos
+        if kind.startswith("vec_"):
+            fmt = _SCALAR[kind[4:]]
+            size = struct.calcsize("<" + fmt)
+            self._align(max(size, 8) if kind == "vec_u8" else max(size, 4), bias=4)
+            pos = len(self.buf)
+            if kind == "vec_u8":
+                self.buf += struct.pack("<I", len(value)) + bytes(value)
+            else:
+                self.buf += struct.pack("<I", len(value)) + struct.pack("<%d%s" % (len(value), fmt), *value)
+            return pos
+        raise ValueError("unknown kind " + kind)

@@ -190,3 +190,49 @@ def test_shape_inference_by_tracing_names_symbolic_dimensions():
     import onnxruntime_b200 as ort
     sess = ort.InferenceSession(m.serialize(), providers=["CPUExecutionProvider"])
     assert sess.run(None, {"x": np.ones((2, 3, 16), np.float32)})[0].shape == (2, 6, 4)
+
+
+def test_ort_format_round_trip_and_conversion_tool(tmp_path):
+    """ONNX -> ORT format (FlatBuffers, identifier ORTM) -> session: same results, also for control flow bodies;
+    session.save_model_format / load_model_format and the conversion tool go through the same writer / reader."""
+    import onnxruntime_b200 as ort
+    from onnxruntime_b200 import onnx_lite as ol, ort_format
+    from onnxruntime_b200.tools import convert_onnx_models_to_ort as tool
+    T = ol.TensorProto
+    rs = np.random.RandomState(9)
+    then_g = ol.make_graph([ol.make_node("Mul", ["h", "two"], ["t_out"])], "then", [], [ol.make_tensor_value_info("t_out", T.FLOAT, None)],
+                           [ol.make_tensor("two", np.array(2.0, np.float32))])
+    else_g = ol.make_graph([ol.make_node("Neg", ["h"], ["e_out"])], "else", [], [ol.make_tensor_value_info("e_out", T.FLOAT, None)])
+    nodes = [ol.make_node("Gemm", ["x", "w", "b"], ["h"], alpha=0.5, transB=1, name="gemm0"),
+             ol.make_node("If", ["flag"], ["branch"], then_branch=then_g, else_branch=else_g),
+             ol.make_node("Concat", ["h", "branch"], ["c"], axis=1),
+             ol.make_node("Transpose", ["c"], ["y"], perm=[1, 0])]
+    g = ol.make_graph(nodes, "g", [ol.make_tensor_value_info("x", T.FLOAT, ["n", 4]), ol.make_tensor_value_info("flag", T.BOOL, [])],
+                      [ol.make_tensor_value_info("y", T.FLOAT, [6, "n"])],
+                      [ol.make_tensor("w", rs.randn(3, 4).astype(np.float32)), ol.make_tensor("b", rs.randn(3).astype(np.float32))])
+    model = ol.make_model(g, opset=17, metadata={"origin": "unit test"})
+    onnx_path = tmp_path / "m.onnx"
+    onnx_path.write_bytes(model.serialize())
+    buf = ort_format.onnx_to_ort(model)
+    assert buf[4:8] == b"ORTM" and ort_format.is_ort_format(buf)
+    back = ort_format.ort_to_onnx(buf)
+    assert [n.op_type for n in back.graph.nodes] == ["Gemm", "If", "Concat", "Transpose"]
+    assert back.opset_imports[""] == 17 and back.metadata == {"origin": "unit test"}
+    assert [(v.name, v.elem_type, list(v.shape)) for v in back.graph.inputs] == [("x", T.FLOAT, ["n", 4]), ("flag", T.BOOL, [])]
+    x = rs.randn(5, 4).astype(np.float32)
+    ref = ort.InferenceSession(str(onnx_path), providers=["CPUExecutionProvider"])
+    ort_path = tmp_path / "m.ort"
+    ort_path.write_bytes(buf)
+    for source in (str(ort_path), buf):
+        sess = ort.InferenceSession(source, providers=["CPUExecutionProvider"])
+        for flag in (True, False):
+            feeds = {"x": x, "flag": np.array(flag)}
+            np.testing.assert_allclose(sess.run(None, feeds)[0], ref.run(None, feeds)[0], rtol=1e-6, atol=1e-6)
+        assert sess.get_modelmeta().custom_metadata_map == {"origin": "unit test"}
+    out_dir = tmp_path / "converted"
+    assert tool.main([str(onnx_path), "--output_dir", str(out_dir), "--optimization_level", "basic"]) == 0
+    conv = ort.InferenceSession(str(out_dir / "m.ort"), providers=["CPUExecutionProvider"])
+    feeds = {"x": x, "flag": np.array(True)}
+    np.testing.assert_allclose(conv.run(None, feeds)[0], ref.run(None, feeds)[0], rtol=1e-6, atol=1e-6)
+    with pytest.raises(Exception):
+        ort.InferenceSession(buf[:60], providers=["CPUExecutionProvider"])
