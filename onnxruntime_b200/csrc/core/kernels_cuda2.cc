@@ -279,6 +279,10 @@ class GqaKernel final : public WithFallback {
     const int64_t B = query.size(0), S = query.size(1);
     const int64_t H = packed ? query.size(2) / (N_ + 2 * Nk_) : query.size(2) / N_;
     const int dt = DtypeCode(query.scalar_type());
+    if (S > 1 && ctx.session()->config().Get("ortb200.math_attention", "0") == "1") {
+      Fallback(ctx);  // fused attention kernels switched off (sdpa_kernel = MATH / ORT_DISABLE_FLASH_ATTENTION)
+      return;
+    }
     const at::Tensor& seqlens = ctx.RequiredInput(5);
     const int64_t total = ctx.RequiredInput(6).cpu().to(at::kLong).reshape({-1})[0].item<int64_t>();
     const bool has_past = ctx.HasInput(3) && ctx.HasInput(4);

@@ -339,7 +339,8 @@ class BertAttentionKernel final : public WithFallback {
     const bool equal_sizes = sizes_.empty() || (sizes_.size() == 3 && sizes_[0] == sizes_[1] && sizes_[1] == sizes_[2]);
     const int64_t H = W3 > 0 ? W3 / 3 / N_ : 0;
     at::Tensor lengths, key_mask;
-    if (dt < 0 || !w_nk_.defined() || w_nk_.scalar_type() != x.scalar_type() || !equal_sizes || (H != 64 && H != 128) ||
+    if (ctx.session()->config().Get("ortb200.math_attention", "0") == "1" ||
+        dt < 0 || !w_nk_.defined() || w_nk_.scalar_type() != x.scalar_type() || !equal_sizes || (H != 64 && H != 128) ||
         ctx.HasInput(4) || ctx.HasInput(5) || (ctx.OutputCount() > 1 && ctx.OutputNeeded(1)) ||
         (ctx.HasInput(3) && !DecodeMask(ctx.Input(3), B, S, &lengths, &key_mask))) {
       Fallback(ctx);
@@ -372,7 +373,7 @@ class MultiHeadAttentionKernel final : public WithFallback {
     const int dt = DtypeCode(q_in.scalar_type());
     const bool extra = ctx.HasInput(3) || ctx.HasInput(5) || ctx.HasInput(6) || ctx.HasInput(7) ||
                        (ctx.OutputCount() > 1 && ctx.OutputNeeded(1)) || (ctx.OutputCount() > 2 && ctx.OutputNeeded(2));
-    if (dt < 0 || extra) {
+    if (dt < 0 || extra || ctx.session()->config().Get("ortb200.math_attention", "0") == "1") {
       Fallback(ctx);
       return;
     }

@@ -10,6 +10,7 @@
 #include <cuda_runtime_api.h>
 #include <unistd.h>
 
+#include <cstdlib>
 #include <ctime>
 #include <fstream>
 #include <iomanip>
@@ -335,6 +336,34 @@ void InferenceSession::ApplyThreadingAndWarnings() {
     if (!known.count(kv.first)) ORTB_LOG(logger_, kWarning) << "session config entry '" << kv.first << "' is not known to this runtime and is ignored";
   }
   if (so_.config.Get("session.set_denormal_as_zero", "0") == "1") at::globalContext().setFlushDenormal(true);
+  // Attention kernel selection of the reference (contrib_ops/cpu/bert/attention_common.h: ORT_DISABLE_FLASH_ATTENTION ...,
+  // provider option sdpa_kernel with bit 16 = MATH): with the fused families switched off, prompt-sized attention runs on
+  // the unfused ATen path and decode attention on the CUDA-core split-KV kernel instead of the tcgen05 kernels.
+  {
+    auto env_is_one = [](const char* name) {
+      const char* v = std::getenv(name);
+      return v != nullptr && std::string(v) == "1";
+    };
+    bool math_only = env_is_one("ORT_DISABLE_FLASH_ATTENTION");
+    auto cuda_opts = provider_options_.find(kCudaEP);
+    if (cuda_opts != provider_options_.end()) {
+      auto sd = cuda_opts->second.find("sdpa_kernel");
+      if (sd != cuda_opts->second.end()) {
+        int bits = 0;
+        try {
+          bits = std::stoi(sd->second);
+        } catch (const std::exception&) {
+          ORTB_LOG(logger_, kWarning) << "sdpa_kernel must be an integer bit mask; got '" << sd->second << "'";
+        }
+        if (bits != 0 && (bits & ~16) == 0) math_only = true;
+      }
+    }
+    if (math_only) {
+      so_.config.entries.emplace("ortb200.math_attention", "1");
+      so_.config.entries.emplace("ortb200.decode_attention_algo", "1");
+      ORTB_LOG(logger_, kInfo) << "fused attention kernels are switched off for this session";
+    }
+  }
   static const std::set<std::string> cuda_known = {"device_id", "enable_cuda_graph", "gpu_mem_limit", "arena_extend_strategy",
       "cudnn_conv_algo_search", "do_copy_in_default_stream", "user_compute_stream", "tunable_op_enable", "tunable_op_tuning_enable",
       "tunable_op_max_tuning_duration_ms", "prefer_nhwc", "use_ep_level_unified_stream", "use_tf32", "fuse_conv_bias", "sdpa_kernel",

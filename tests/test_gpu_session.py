@@ -103,3 +103,21 @@ def test_tunable_gemm_picks_a_configuration_and_results_travel():
     bad = [dict(res[0], validators={"ORTB200_VERSION": "other"})]
     with pytest.raises(Exception):
         sess2.set_tuning_results(bad, error_on_invalid=True)
+
+
+def test_sdpa_kernel_math_switches_the_fused_attention_kernels_off():
+    """Provider option sdpa_kernel = 16 (MATH) and ORT_DISABLE_FLASH_ATTENTION: MultiHeadAttention runs unfused on
+    ATen instead of the tcgen05 kernel, with the same result."""
+    torch.manual_seed(2)
+    B, S, N, H = 2, 96, 4, 64
+    model = graph_model([ol.make_node("MultiHeadAttention", ["q", "k", "v"], ["y"], domain="com.microsoft", num_heads=N)],
+                        [ol.make_tensor_value_info(n, T.FLOAT16, [B, S, N * H]) for n in ("q", "k", "v")],
+                        [ol.make_tensor_value_info("y", T.FLOAT16, None)], [])
+    feeds = {n: (torch.randn(B, S, N * H) * 0.5).half().numpy() for n in ("q", "k", "v")}
+    fused = ort.InferenceSession(model, providers=["CUDAExecutionProvider"], enable_fallback=False)
+    math = ort.InferenceSession(model, providers=[("CUDAExecutionProvider", {"sdpa_kernel": "16"})], enable_fallback=False)
+    y0 = fused.run(None, feeds)[0].astype(np.float32)
+    n_fused = fused.kernel_launch_count()
+    y1 = math.run(None, feeds)[0].astype(np.float32)
+    assert n_fused >= 1 and math.kernel_launch_count() == 0          # none of this library's kernels ran
+    np.testing.assert_allclose(y0, y1, rtol=2e-2, atol=2e-3)
