@@ -302,11 +302,12 @@ PYBIND11_MODULE(_core, m) {
       .def("last_run_launch_count", &InferenceSession::LastRunLaunchCount)
       .def("check_device_status", [](InferenceSession& s) { Guard([&] { s.CheckDeviceStatus(); return 0; }); })
       .def("uses_gpu", &InferenceSession::uses_gpu)
-      .def("set_symmetric_workspace", [](InferenceSession& s, const std::vector<int64_t>& ptrs, int64_t bytes) {
+      .def("set_symmetric_workspace", [](InferenceSession& s, const std::vector<int64_t>& ptrs, int64_t bytes, int64_t multicast_ptr) {
         s.symm_peers.clear();
         for (auto p : ptrs) s.symm_peers.push_back(reinterpret_cast<void*>(static_cast<uintptr_t>(p)));
         s.symm_bytes = bytes;
-      })
+        s.symm_multicast = reinterpret_cast<void*>(static_cast<uintptr_t>(multicast_ptr));
+      }, py::arg("ptrs"), py::arg("bytes"), py::arg("multicast_ptr") = 0)
       .def_readwrite("dist_group", &InferenceSession::dist_group)
       .def_readwrite("rank", &InferenceSession::rank)
       .def_readwrite("world_size", &InferenceSession::world_size)

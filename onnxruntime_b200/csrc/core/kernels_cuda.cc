@@ -166,6 +166,7 @@ at::Tensor LaunchGemm(Ctx& ctx, const at::Tensor& x2d, const at::Tensor& w_nk, i
     a.rank = s->rank;
     for (int i = 0; i < s->world_size && i < 8; ++i) a.peers[i] = s->symm_peers[i];
     a.symm_bytes = s->symm_bytes;
+    a.mc_ptr = s->NvlsPointer();  // prompt-sized problems reduce through the switch when the workspace is multicast-mapped
   }
   if (s->tunable_op_enable && !fused_allreduce) ApplyTunedConfig(ctx, &a, out_type);
   CheckLaunch(ortb200_gemm(&a, ctx.cuda_stream()), "ortb200_gemm");

@@ -656,6 +656,7 @@ class SymmCollectiveKernel final : public WithFallback {
       a.rank = s->rank;
       for (int r = 0; r < world; ++r) a.peers[r] = s->symm_peers[r];
       a.symm_bytes = s->symm_bytes;
+      a.mc_ptr = s->NvlsPointer();
       a.status = s->StatusWord().data_ptr<int>();
       a.use_pdl = s->config().Get("ortb200.pdl", "0") == "1" ? 1 : 0;
       CheckLaunch(ortb200_symm_collective(&a, ctx.cuda_stream()), "ortb200_symm_collective");

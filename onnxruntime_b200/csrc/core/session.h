@@ -174,6 +174,9 @@ class InferenceSession {
 
   std::vector<void*> symm_peers;
   int64_t symm_bytes = 0;
+  void* symm_multicast = nullptr;  // NVLS multicast address of the workspace (0: none)
+  // the multicast address to hand to a kernel, honouring ortb200.nvls = "0"
+  void* NvlsPointer() const { return so_.config.Get("ortb200.nvls", "1") == "0" ? nullptr : symm_multicast; }
   int64_t library_collective_calls = 0;  // process-group collectives issued so far (the in-kernel ones do not count)
   std::set<int64_t> uncapturable_graph_ids_;
   std::string dist_group;  // torch.distributed group name used by collective ops ("" = default)

@@ -55,7 +55,32 @@ struct CollParams {
   const void* residual;
   long long ldr;
   int row_elems;
+  // NVLS: multicast address of the workspace (every rank's buffer behind one address).  When set, the all-reduce lets
+  // the switch do the work: a rank's slice is summed by one multimem.ld_reduce per 16 bytes (the switch reads the
+  // slice from all ranks and adds in flight) and replicated by one multimem.st, so a GPU moves 2 / world of the
+  // tensor over its links instead of 2 (world - 1) / world.  16-bit and 32-bit float types.
+  void* mc;
 };
+
+// 16 bytes summed over all ranks by the switch (fp32 accumulation for the 16-bit types)
+__device__ __forceinline__ uint4 multimem_ld_reduce(const void* mc_addr, int dtype) {
+  uint4 v;
+  if (dtype == ORTB200_BF16)
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc_addr) : "memory");
+  else if (dtype == ORTB200_F16)
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc_addr) : "memory");
+  else
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc_addr) : "memory");
+  return v;
+}
+// 16 bytes stored into every rank's copy
+__device__ __forceinline__ void multimem_st(void* mc_addr, const uint4& v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc_addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+               : "memory");
+}
 
 // CTA-wide: tell every rank that this CTA's stores for `value` are done, then wait for the same CTA of every rank.
 __device__ __forceinline__ bool cta_exchange_flags(const CollParams& p, unsigned int value) {
@@ -155,6 +180,59 @@ __global__ void __launch_bounds__(256) symm_collective_kernel(const CollParams p
     const uint4* res = result_of(p.rank);
     for (long long i = t0; i < p.row_vecs; i += stride)
       for (int s = 0; s < p.world; ++s) p.out[static_cast<long long>(s) * p.row_vecs + i] = __ldcg(res + static_cast<long long>(s) * p.row_vecs + i);
+  } else if (p.mc != nullptr) {
+    // all-reduce through the switch: every rank leaves its whole input in its OWN scatter area (the GEMM epilogue has
+    // done that already when prescattered), then reduces its slice with multimem.ld_reduce and replicates the sums
+    // with multimem.st into every rank's result area
+    uint4* mine = scatter_of(p.rank);
+    if (!p.prescattered) {
+      for (long long i = t0; i < p.row_vecs; i += stride)
+        for (int d = 0; d < p.world; ++d) {
+          const long long g = static_cast<long long>(d) * p.row_vecs + i;
+          if (g < p.total_vecs) mine[g] = p.in[g];
+        }
+    }
+    ok = cta_exchange_flags(p, 2 * epoch + 1);
+    uint8_t* mc_scatter = static_cast<uint8_t*>(p.mc) + half_off;
+    uint8_t* mc_result = mc_scatter + scatter_vecs * 16;
+    for (long long i = t0; i < p.row_vecs; i += stride) {
+      const long long g = static_cast<long long>(p.rank) * p.row_vecs + i;
+      if (g >= p.total_vecs) continue;
+      uint4 r = multimem_ld_reduce(mc_scatter + g * 16, p.dtype);
+      if (p.residual) {
+        const long long el = g * 8;  // 16-bit types only
+        const long long m = el / p.row_elems, n = el - m * p.row_elems;
+        const uint4 rv = __ldg(reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(p.residual) + m * p.ldr + n));
+        const uint4* none[1] = {nullptr};
+        (void)none;
+        float acc[8];
+        if (p.dtype == ORTB200_BF16) {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+          add_vec<__nv_bfloat16>(acc, r);
+          add_vec<__nv_bfloat16>(acc, rv);
+          __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(&r);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) o[e] = __float2bfloat16_rn(acc[e]);
+        } else {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+          add_vec<__half>(acc, r);
+          add_vec<__half>(acc, rv);
+          __half* o = reinterpret_cast<__half*>(&r);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) o[e] = __float2half_rn(acc[e]);
+        }
+      }
+      multimem_st(mc_result + g * 16, r);
+    }
+    ok = cta_exchange_flags(p, 2 * epoch + 2) && ok;
+    const uint4* res = result_of(p.rank);
+    for (long long i = t0; i < p.row_vecs; i += stride)
+      for (int s = 0; s < p.world; ++s) {
+        const long long g = static_cast<long long>(s) * p.row_vecs + i;
+        if (g < p.total_vecs) p.out[g] = __ldcg(res + g);
+      }
   } else {
     // all-reduce in two steps: slice d of every rank's input is pushed to rank d (scatter[src rank][row_vecs]),
     // rank d adds the slices in rank order and pushes the sums to everyone's result area, everyone copies out
@@ -357,6 +435,7 @@ int launch_allreduce_prescattered(const ortb200_gemm_args* a, cudaStream_t strea
   p.total_vecs = static_cast<long long>(a->M) * a->N / 8;
   p.row_vecs = (p.total_vecs + a->world - 1) / a->world;
   p.prescattered = 1; p.residual = a->residual; p.ldr = a->ldr; p.row_elems = a->N;
+  p.mc = a->mc_ptr;
   long long ctas = (p.row_vecs + 255) / 256;
   if (ctas > 2 * 148) ctas = 2 * 148;
   if (ctas < 1) ctas = 1;
@@ -440,6 +519,7 @@ extern "C" int ortb200_symm_collective(const ortb200_symm_collective_args* a, or
   p.status = a->status;
   p.rows = 1; p.row_vecs = 0; p.total_vecs = 0;
   p.prescattered = 0; p.residual = nullptr; p.ldr = 0; p.row_elems = 0;
+  p.mc = a->op == ORTB200_COLL_ALLREDUCE ? a->mc_ptr : nullptr;
   const int64_t limit = ortb200_symm_collective_max_bytes(a->op, a->world, a->symm_bytes);
   long long work_vecs = 0;
   if (a->op == ORTB200_COLL_ALLGATHER) {

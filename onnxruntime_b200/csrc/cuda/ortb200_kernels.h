@@ -93,6 +93,10 @@ typedef struct {
   //   rows beyond N are zero.  W[n, k] = (q - zp) * scale.
   int force_tile_rows;  // 0 / 128 = 128-weight-row CTA tiles; 256 = 256-row tiles in the large-M kernel (M > 128);
                         // 512 = pairs of CTAs on 256 x 256 tiles (cta_group::2 kernel)
+  // Prompt-sized fused all-reduce (world > 1, M > 64) with NVLS: the multicast address of the symmetric workspace.  The
+  // epilogue then keeps the partial product in this rank's own scatter area and the reduction kernel sums and
+  // replicates through the switch (multimem.ld_reduce / multimem.st).  Null: peer stores + local sums.
+  void* mc_ptr;
 } ortb200_gemm_args;
 
 int ortb200_gemm(const ortb200_gemm_args* args, ortb200_stream_t stream);
@@ -408,6 +412,7 @@ typedef struct {
   int64_t symm_bytes;
   int* status;
   int use_pdl;
+  void* mc_ptr;    // all-reduce: NVLS multicast address of the workspace, or null (peer loads and stores only)
 } ortb200_symm_collective_args;
 int ortb200_symm_collective(const ortb200_symm_collective_args* args, ortb200_stream_t stream);
 int64_t ortb200_symm_collective_max_bytes(int op, int world, int64_t symm_bytes);

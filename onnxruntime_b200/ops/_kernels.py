@@ -54,7 +54,7 @@ class GemmArgs(ctypes.Structure):
         ("workspace", ctypes.c_void_p), ("workspace_bytes", ctypes.c_int64), ("status", ctypes.c_void_p),
         ("force_splits", ctypes.c_int), ("force_bn", ctypes.c_int), ("use_pdl", ctypes.c_int),
         ("world", ctypes.c_int), ("rank", ctypes.c_int), ("peers", ctypes.c_void_p * 8), ("symm_bytes", ctypes.c_int64),
-        ("in_dtype", ctypes.c_int), ("rms_eps", ctypes.c_float), ("force_tile_rows", ctypes.c_int),
+        ("in_dtype", ctypes.c_int), ("rms_eps", ctypes.c_float), ("force_tile_rows", ctypes.c_int), ("mc_ptr", ctypes.c_void_p),
     ]
 
 
@@ -85,7 +85,7 @@ def gemm(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
          force_splits: int = 0, force_bn: int = 0, status: Optional[torch.Tensor] = None,
          use_pdl: bool = False, peers=None, rank: int = 0, symm_bytes: int = 0,
          out_dtype: Optional[torch.dtype] = None, rms_eps: float = 0.0, force_tile_rows: int = 0,
-         q4: bool = False) -> torch.Tensor:
+         q4: bool = False, mc_ptr: int = 0) -> torch.Tensor:
     """out[M, N] = act(alpha * x[M, K] @ w[N, K].T + bias) + residual  (tcgen05 kernel).
     x / w of dtype float8_e4m3fn use the 8-bit tensor-core mode; out_dtype (fp16 / bf16) is then required."""
     assert x.is_cuda and w.is_cuda and (x.dtype == w.dtype or q4) and x.dim() == 2
@@ -110,7 +110,7 @@ def gemm(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
                  dtype_code(odt), ACT[act], alpha, _ptr(ws), ws.numel(), _ptr(status), force_splits, force_bn,
                  1 if use_pdl else 0, len(peers) if peers else 1, rank,
                  (ctypes.c_void_p * 8)(*(list(peers) + [None] * (8 - len(peers)))) if peers else (ctypes.c_void_p * 8)(),
-                 symm_bytes, 4 if q4 else (3 if fp8 else 0), rms_eps, force_tile_rows)
+                 symm_bytes, 4 if q4 else (3 if fp8 else 0), rms_eps, force_tile_rows, mc_ptr or None)
     rc = lib().ortb200_gemm(ctypes.byref(a), ctypes.c_void_p(stream_ptr()))
     if rc != 0:
         raise RuntimeError(f"ortb200_gemm rejected its arguments (code {rc})")
@@ -370,10 +370,11 @@ def nbits_dequant(B, scales, zero_points, N, K, bits=4, block_size=32):
 class SymmCollectiveArgs(ctypes.Structure):
     _fields_ = [("op", ctypes.c_int), ("inp", ctypes.c_void_p), ("out", ctypes.c_void_p), ("rows", ctypes.c_int64),
                 ("row_bytes", ctypes.c_int64), ("dtype", ctypes.c_int), ("world", ctypes.c_int), ("rank", ctypes.c_int),
-                ("peers", ctypes.c_void_p * 8), ("symm_bytes", ctypes.c_int64), ("status", ctypes.c_void_p), ("use_pdl", ctypes.c_int)]
+                ("peers", ctypes.c_void_p * 8), ("symm_bytes", ctypes.c_int64), ("status", ctypes.c_void_p), ("use_pdl", ctypes.c_int),
+                ("mc_ptr", ctypes.c_void_p)]
 
 
-def symm_collective(op, x, peers, rank, symm_bytes, axis=0, status=None):
+def symm_collective(op, x, peers, rank, symm_bytes, axis=0, status=None, mc_ptr=0):
     """op in {"allreduce", "allgather", "alltoall"} over the peer-mapped workspace (parallel.symm); all ranks call it."""
     world = len(peers)
     x = x.contiguous()
@@ -389,7 +390,7 @@ def symm_collective(op, x, peers, rank, symm_bytes, axis=0, status=None):
         row_bytes //= world
     out = torch.empty(shape, dtype=x.dtype, device=x.device)
     a = SymmCollectiveArgs(code, _ptr(x), _ptr(out), rows, row_bytes, dtype_code(x.dtype) if op == "allreduce" else 0, world, rank,
-                           (ctypes.c_void_p * 8)(*(list(peers) + [None] * (8 - world))), symm_bytes, _ptr(status), 0)
+                           (ctypes.c_void_p * 8)(*(list(peers) + [None] * (8 - world))), symm_bytes, _ptr(status), 0, mc_ptr or None)
     _check(lib().ortb200_symm_collective(ctypes.byref(a), ctypes.c_void_p(stream_ptr())), "ortb200_symm_collective")
     return out
 

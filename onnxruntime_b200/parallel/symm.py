@@ -49,6 +49,8 @@ def create_workspace(nbytes: int = DEFAULT_BYTES, group: Optional[dist.ProcessGr
 
 
 def attach(session, ws: SymmetricWorkspace) -> None:
-    """Give a session the peer addresses; its row-parallel GEMMs then reduce across ranks inside the kernel."""
-    session._sess.set_symmetric_workspace(ws.peer_ptrs, ws.nbytes)
+    """Give a session the peer addresses; its row-parallel GEMMs then reduce across ranks inside the kernel.  With an
+    NVLS multicast address the prompt-sized all-reduces are summed and replicated by the switch (session config
+    ``ortb200.nvls`` = "0" keeps them on peer loads and stores)."""
+    session._sess.set_symmetric_workspace(ws.peer_ptrs, ws.nbytes, ws.multicast_ptr)
     session._symm_ws = ws  # keep the mapping alive as long as the session

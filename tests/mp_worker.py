@@ -238,6 +238,14 @@ def case_gemm_allreduce(info, device, out):
         torch.cuda.synchronize()
         res[f"case{i}"] = {"err": float((outs[-1].float() - ref).abs().max() / ref.abs().max()),
                            "stable": bool(torch.equal(outs[0], outs[1]) and torch.equal(outs[1], outs[2])), "out": outs[-1].cpu()}
+        if M > 64 and ws.multicast_ptr:
+            # the same problem reduced through the switch (multimem.ld_reduce / multimem.st)
+            outs = [K.gemm(x, wt, residual=resid, status=status, peers=ws.peer_ptrs, rank=r, symm_bytes=ws.nbytes,
+                           mc_ptr=ws.multicast_ptr).clone() for _ in range(3)]
+            torch.cuda.synchronize()
+            res[f"case{i}_nvls"] = {"err": float((outs[-1].float() - ref).abs().max() / ref.abs().max()),
+                                    "stable": bool(torch.equal(outs[0], outs[1]) and torch.equal(outs[1], outs[2])), "out": outs[-1].cpu()}
+    res["nvls"] = bool(ws.multicast_ptr)
     res["status"] = int(status.item())
     torch.save(res, os.path.join(out, f"rank{r}.pt"))
 
@@ -260,6 +268,9 @@ def case_symm_collectives(info, device, out):
                 ref = x.float().clone()
                 dist.all_reduce(ref)
                 res[f"ar_{rep}_{dtype}_{n}"] = float((y.float() - ref).abs().max() / ref.abs().max())
+                if ws.multicast_ptr:
+                    y = K.symm_collective("allreduce", x, ws.peer_ptrs, r, ws.nbytes, status=status, mc_ptr=ws.multicast_ptr)
+                    res[f"ar_nvls_{rep}_{dtype}_{n}"] = float((y.float() - ref).abs().max() / ref.abs().max())
         for shape, axis in (((8, 16032), 1), ((4, 3, 64), 0), ((2, 5, 128), 2), ((1, 8), 0)):
             x = torch.randn(*shape, device="cuda", generator=g).bfloat16()
             y = K.symm_collective("allgather", x, ws.peer_ptrs, r, ws.nbytes, axis=axis, status=status)
