@@ -127,9 +127,11 @@ def main():
     ap.add_argument("--fused-prep", default="auto", help="auto / 1: decode attention unpacks, rotates and appends the new token itself; 0: separate kernel")
     ap.add_argument("--attn-prefetch", type=int, default=0, help="decode attention asks the L2 for the output projection's weights")
     ap.add_argument("--attn-algo", type=int, default=0, help="decode attention: 0 = tcgen05 kernel, 1 = CUDA-core split-KV kernel")
+    ap.add_argument("--nvls", type=int, default=1, help="prompt-sized all-reduces sum and replicate in the NVSwitch (multimem) when the workspace has a multicast mapping")
     ap.add_argument("--tunable", type=int, default=0, help="1: TunableOp picks the GEMM launch configurations on the first (eager) step")
     ap.add_argument("--fused-collectives", type=int, default=1, help="0: NCCL all-reduce after each row-parallel GEMM (baseline)")
     args = ap.parse_args()
+    nvls_active = False
     if args.impl == "reference":
         return reference_arm(args)
 
@@ -171,6 +173,7 @@ def main():
         so.add_session_config_entry("ortb200.decode_attention_algo", str(args.attn_algo))
         so.add_session_config_entry("ortb200.fused_gqa_prep", str(args.fused_prep))
         so.add_session_config_entry("ortb200.attention_prefetch", str(args.attn_prefetch))
+        so.add_session_config_entry("ortb200.nvls", str(args.nvls))
         popts = {"device_id": str(local), "enable_cuda_graph": "0" if args.no_graph else "1"}
         if args.tunable:
             popts.update({"tunable_op_enable": "1", "tunable_op_tuning_enable": "1"})
@@ -183,7 +186,9 @@ def main():
             from onnxruntime_b200.parallel import symm
             # sized for the prompt-sized all-reduce too: its scatter and result areas hold batch x prompt x hidden elements
             need = 16 * args.batch * args.prompt * cfg.hidden_size * 2
-            symm.attach(sess, symm.create_workspace(max(64 << 20, need)))
+            ws = symm.create_workspace(max(64 << 20, need))
+            symm.attach(sess, ws)
+            nvls_active = bool(ws.multicast_ptr) and bool(args.nvls)
         runner = DecoderRunner(sess, cfg, batch=args.batch, max_len=max_len, tp_size=tp, device=device,
                                prefill_graph=bool(args.prefill_graph) and not args.no_graph)
     gen = torch.Generator().manual_seed(1234)
@@ -298,7 +303,7 @@ def main():
             "config": {"model": "Llama-3-8B" if args.layers == 32 else f"Llama-3-8B-shaped/{args.layers}L",
                        "global_batch": args.batch, "seq_len": args.prompt, "decode_tokens": K,
                        "parallelism": f"tp{tp}", "cuda_graph": (not args.no_graph) and (args.impl != "library" or tp == 1),
-                       "collectives": ("nccl" if (args.impl == "library" or not args.fused_collectives) else "in-kernel peer-store all-reduce") if tp > 1 else "none",
+                       "collectives": ("nccl" if (args.impl == "library" or not args.fused_collectives) else "in-kernel peer-store all-reduce" + ("; prompt-sized all-reduce in the NVSwitch (multimem)" if nvls_active else "")) if tp > 1 else "none",
                        "l2": "inputs larger than L2 (every step streams all weights)"},
             "e2e": {"value": round(e2e_value, 2), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": round(e2e_ms / K, 4), "wall_ms_per_step": round(wall_ms / K, 4)},

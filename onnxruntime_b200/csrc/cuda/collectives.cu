@@ -55,10 +55,13 @@ struct CollParams {
   const void* residual;
   long long ldr;
   int row_elems;
-  // NVLS: multicast address of the workspace (every rank's buffer behind one address).  When set, the all-reduce lets
-  // the switch do the work: a rank's slice is summed by one multimem.ld_reduce per 16 bytes (the switch reads the
-  // slice from all ranks and adds in flight) and replicated by one multimem.st, so a GPU moves 2 / world of the
-  // tensor over its links instead of 2 (world - 1) / world.  16-bit and 32-bit float types.
+  // NVLS: multicast address of the workspace (every rank's buffer behind one address).  With it the sums are
+  // replicated by one multimem.st per 16 bytes (the switch copies them to every rank: 1 / world of the tensor leaves
+  // the GPU instead of (world - 1) / world).  A stand-alone all-reduce also lets the switch add: the inputs stay at
+  // home and one multimem.ld_reduce per 16 bytes of the rank's slice returns the sum.  The all-reduce that finishes a
+  // GEMM keeps its peer-store scatter, because those stores overlap the GEMM's remaining tiles while a reduction in
+  // the switch can only start after the GEMM (measured on 4 GPUs: 42.1 ms time to first token with ld_reduce
+  // against 39.6 ms with the overlapped scatter).  16-bit and 32-bit float types.
   void* mc;
 };
 
@@ -180,51 +183,61 @@ __global__ void __launch_bounds__(256) symm_collective_kernel(const CollParams p
     const uint4* res = result_of(p.rank);
     for (long long i = t0; i < p.row_vecs; i += stride)
       for (int s = 0; s < p.world; ++s) p.out[static_cast<long long>(s) * p.row_vecs + i] = __ldcg(res + static_cast<long long>(s) * p.row_vecs + i);
-  } else if (p.mc != nullptr) {
-    // all-reduce through the switch: every rank leaves its whole input in its OWN scatter area (the GEMM epilogue has
-    // done that already when prescattered), then reduces its slice with multimem.ld_reduce and replicates the sums
-    // with multimem.st into every rank's result area
+  } else if (p.mc != nullptr && !p.prescattered) {
+    // stand-alone all-reduce through the switch: every rank leaves its whole input in its OWN scatter area, then
+    // reduces its slice with multimem.ld_reduce and replicates the sums with multimem.st into every rank's result area
     uint4* mine = scatter_of(p.rank);
-    if (!p.prescattered) {
-      for (long long i = t0; i < p.row_vecs; i += stride)
-        for (int d = 0; d < p.world; ++d) {
-          const long long g = static_cast<long long>(d) * p.row_vecs + i;
-          if (g < p.total_vecs) mine[g] = p.in[g];
-        }
-    }
+    for (long long i = t0; i < p.row_vecs; i += stride)
+      for (int d = 0; d < p.world; ++d) {
+        const long long g = static_cast<long long>(d) * p.row_vecs + i;
+        if (g < p.total_vecs) mine[g] = p.in[g];
+      }
     ok = cta_exchange_flags(p, 2 * epoch + 1);
     uint8_t* mc_scatter = static_cast<uint8_t*>(p.mc) + half_off;
     uint8_t* mc_result = mc_scatter + scatter_vecs * 16;
-    for (long long i = t0; i < p.row_vecs; i += stride) {
-      const long long g = static_cast<long long>(p.rank) * p.row_vecs + i;
-      if (g >= p.total_vecs) continue;
-      uint4 r = multimem_ld_reduce(mc_scatter + g * 16, p.dtype);
-      if (p.residual) {
-        const long long el = g * 8;  // 16-bit types only
-        const long long m = el / p.row_elems, n = el - m * p.row_elems;
-        const uint4 rv = __ldg(reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(p.residual) + m * p.ldr + n));
-        const uint4* none[1] = {nullptr};
-        (void)none;
-        float acc[8];
-        if (p.dtype == ORTB200_BF16) {
+    // four reductions in flight per thread: one switch round trip costs microseconds, so the loop is unrolled with
+    // all loads (and residual loads) issued before the first result is touched
+    constexpr int kUnroll = 4;
+    for (long long i0 = t0; i0 < p.row_vecs; i0 += kUnroll * stride) {
+      uint4 r[kUnroll], rv[kUnroll];
+      long long gs[kUnroll];
 #pragma unroll
-          for (int e = 0; e < 8; ++e) acc[e] = 0.f;
-          add_vec<__nv_bfloat16>(acc, r);
-          add_vec<__nv_bfloat16>(acc, rv);
-          __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(&r);
-#pragma unroll
-          for (int e = 0; e < 8; ++e) o[e] = __float2bfloat16_rn(acc[e]);
-        } else {
-#pragma unroll
-          for (int e = 0; e < 8; ++e) acc[e] = 0.f;
-          add_vec<__half>(acc, r);
-          add_vec<__half>(acc, rv);
-          __half* o = reinterpret_cast<__half*>(&r);
-#pragma unroll
-          for (int e = 0; e < 8; ++e) o[e] = __float2half_rn(acc[e]);
+      for (int u = 0; u < kUnroll; ++u) {
+        const long long i = i0 + u * stride;
+        const long long g = static_cast<long long>(p.rank) * p.row_vecs + i;
+        gs[u] = (i < p.row_vecs && g < p.total_vecs) ? g : -1;
+        if (gs[u] >= 0) {
+          r[u] = multimem_ld_reduce(mc_scatter + g * 16, p.dtype);
+          if (p.residual) {
+            const long long el = g * 8;  // 16-bit types only
+            const long long m = el / p.row_elems, n = el - m * p.row_elems;
+            rv[u] = __ldg(reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(p.residual) + m * p.ldr + n));
+          }
         }
       }
-      multimem_st(mc_result + g * 16, r);
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+        if (gs[u] < 0) continue;
+        if (p.residual) {
+          float acc[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+          if (p.dtype == ORTB200_BF16) {
+            add_vec<__nv_bfloat16>(acc, r[u]);
+            add_vec<__nv_bfloat16>(acc, rv[u]);
+            __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(&r[u]);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) o[e] = __float2bfloat16_rn(acc[e]);
+          } else {
+            add_vec<__half>(acc, r[u]);
+            add_vec<__half>(acc, rv[u]);
+            __half* o = reinterpret_cast<__half*>(&r[u]);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) o[e] = __float2half_rn(acc[e]);
+          }
+        }
+        multimem_st(mc_result + gs[u] * 16, r[u]);
+      }
     }
     ok = cta_exchange_flags(p, 2 * epoch + 2) && ok;
     const uint4* res = result_of(p.rank);
@@ -260,7 +273,12 @@ __global__ void __launch_bounds__(256) symm_collective_kernel(const CollParams p
       if (p.dtype == ORTB200_BF16) r = sum_vecs<__nv_bfloat16>(src, p.world, i, res_vec);
       else if (p.dtype == ORTB200_F16) r = sum_vecs<__half>(src, p.world, i, res_vec);
       else r = sum_vecs<float>(src, p.world, i);
-      for (int d = 0; d < p.world; ++d) result_of((p.rank + d) % p.world)[g] = r;
+      if (p.mc != nullptr) {
+        // one store, replicated by the switch into every rank's result area
+        multimem_st(static_cast<uint8_t*>(p.mc) + half_off + (scatter_vecs + g) * 16, r);
+      } else {
+        for (int d = 0; d < p.world; ++d) result_of((p.rank + d) % p.world)[g] = r;
+      }
     }
     ok = cta_exchange_flags(p, 2 * epoch + 2) && ok;
     const uint4* res = result_of(p.rank);

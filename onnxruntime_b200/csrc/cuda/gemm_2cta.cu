@@ -398,12 +398,6 @@ int launch_gemm_2cta(const ortb200_gemm_args* a, cudaStream_t stream) {
     p.region_offset = a->symm_bytes / 2;
     p.half_bytes = a->symm_bytes / 4;
     p.row_vecs = static_cast<unsigned int>((total_vecs + a->world - 1) / a->world);
-    if (a->mc_ptr != nullptr) {
-      // NVLS: the partial product stays at home, laid out as the whole tensor.  The epilogue computes
-      // peers[slice] + area + (rank * row_vecs + i) * 16; with these bases that is own base + area + (slice * row_vecs + i) * 16.
-      for (int i = 0; i < a->world; ++i)
-        p.peers[i] = static_cast<uint8_t*>(a->peers[a->rank]) + (static_cast<long long>(i) - a->rank) * static_cast<long long>(p.row_vecs) * 16;
-    }
     p.out = nullptr; p.residual = nullptr;     // the reduction kernel applies the residual and writes `out`
     if (a->rank != 0) p.bias = nullptr;        // the bias enters the sum once
   }

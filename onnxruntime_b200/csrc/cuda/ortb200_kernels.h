@@ -94,8 +94,8 @@ typedef struct {
   int force_tile_rows;  // 0 / 128 = 128-weight-row CTA tiles; 256 = 256-row tiles in the large-M kernel (M > 128);
                         // 512 = pairs of CTAs on 256 x 256 tiles (cta_group::2 kernel)
   // Prompt-sized fused all-reduce (world > 1, M > 64) with NVLS: the multicast address of the symmetric workspace.  The
-  // epilogue then keeps the partial product in this rank's own scatter area and the reduction kernel sums and
-  // replicates through the switch (multimem.ld_reduce / multimem.st).  Null: peer stores + local sums.
+  // reduction kernel then replicates the sums with one multimem.st per 16 bytes instead of a store to every peer.
+  // Null: peer stores only.
   void* mc_ptr;
 } ortb200_gemm_args;
 

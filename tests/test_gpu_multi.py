@@ -32,6 +32,9 @@ def test_fused_gemm_allreduce_kernel(tmp_path, n):
         if k.startswith("case"):
             for r in range(1, n):
                 assert torch.equal(out[0][k]["out"], out[r][k]["out"])  # every rank holds the same reduced result
+    if out[0]["nvls"]:  # the workspace has a multicast mapping: the prompt-sized cases also ran through the switch
+        assert any(k.endswith("_nvls") for k in out[0])
+    print("NVLS multicast mapping:", out[0]["nvls"])
 
 
 @pytest.mark.parametrize("n", WORLDS)
