@@ -207,16 +207,24 @@ class ScanKernel final : public ControlFlowBase {
 // ---------------------------------------------------------------------------------------------------------------
 // Generation as operators: com.microsoft GreedySearch / Sampling / BeamSearch drive a decoder body graph token by token
 // (reference: onnxruntime/contrib_ops/cpu/transformers/greedy_search.cc, sampling.cc, beam_search.cc, beam_search_scorer.cc,
-// logits_processor.h; device kernels contrib_ops/cuda/transformers/generation_cuda_impl.cu).  Supported here: the GPT
-// form (model_type 0).  The `decoder` body takes input_ids [R, S] int32, position_ids [R, S] int32, attention_mask
-// [R, total] int32 and one past state per layer [2, R, heads, past, head]; it returns logits [R, S, vocab] and the present
-// states, which the loop feeds back (beam search re-orders their rows).  All tensor work is ATen on the body's device.
+// logits_processor.h; device kernels contrib_ops/cuda/transformers/generation_cuda_impl.cu).
+//   model_type 0 (GPT): the `decoder` body takes input_ids [R, S] int32, position_ids [R, S] int32, attention_mask
+//     [R, total] int32 and one past state per layer [2, R, heads, past, head]; it returns logits [R, S, vocab] and the
+//     present states, which the loop feeds back (beam search re-orders their rows).
+//   model_type 1 (T5) and 2 (Whisper; also the WhisperBeamSearch operator): the `encoder` body runs once on the
+//     encoder input (token ids, or audio features for Whisper), the encoder attention mask (T5 only) and the first
+//     decoder tokens; it returns logits, encoder_hidden_states and per layer key / value of the decoder's self attention
+//     and of the cross attention.  The `decoder` body then takes input_ids [R, 1], the encoder attention mask (T5 only),
+//     encoder_hidden_states when it declares that input, the self-attention states of all layers and then the
+//     cross-attention states of all layers; it returns logits and the new self-attention states.
+// All tensor work is ATen on the body's device.
 class GenerationKernel final : public ControlFlowBase {
  public:
   explicit GenerationKernel(const OpKernelInfo& info) : ControlFlowBase(info) {
     const Node& n = info.node;
     kind_ = n.op_type;
-    ORTB_ENFORCE_ARG(n.attr_i("model_type", 0) == 0, kind_, ": only the GPT form (model_type 0) is implemented");
+    model_type_ = n.attr_i("model_type", kind_ == "WhisperBeamSearch" ? 2 : 0);
+    ORTB_ENFORCE_ARG(model_type_ >= 0 && model_type_ <= 2, kind_, ": model_type must be 0 (GPT), 1 (T5) or 2 (Whisper)");
     decoder_ = MakeBody("decoder");
     eos_ = n.attr_i("eos_token_id", -1);
     pad_ = n.attr_i("pad_token_id", 0);
@@ -229,6 +237,22 @@ class GenerationKernel final : public ControlFlowBase {
     presence_penalty_ = n.attr_f("presence_penalty", 0.f);
     seed_ = n.attr_i("seed", 0);
     const auto& ins = decoder_.graph->Inputs();
+    if (model_type_ != 0) {
+      ORTB_ENFORCE_ARG(kind_ == "BeamSearch" || kind_ == "WhisperBeamSearch" || kind_ == "GreedySearch", kind_,
+                       ": encoder-decoder models are driven by BeamSearch, WhisperBeamSearch or GreedySearch");
+      encoder_ = MakeBody("encoder");
+      start_token_ = n.attr_i("decoder_start_token_id", 0);
+      const int n_enc_out = static_cast<int>(encoder_.graph->Outputs().size());
+      ORTB_ENFORCE_ARG(n_enc_out > 2 && (n_enc_out - 2) % 4 == 0, kind_,
+                       ": the encoder body must return logits, encoder_hidden_states and four states per layer");
+      layers_ = (n_enc_out - 2) / 4;
+      const int fixed = static_cast<int>(ins.size()) - 4 * layers_;
+      dec_has_mask_ = model_type_ == 1;
+      const int base = dec_has_mask_ ? 2 : 1;
+      ORTB_ENFORCE_ARG(fixed == base || fixed == base + 1, kind_, ": the decoder body's inputs do not match ", layers_, " layers");
+      dec_has_hidden_ = fixed == base + 1;
+      return;
+    }
     ORTB_ENFORCE_ARG(ins.size() >= 3, kind_, ": the decoder body needs input_ids, position_ids, attention_mask and past states");
     layers_ = static_cast<int>(ins.size()) - 3;
     if (layers_ > 0) {
@@ -242,8 +266,17 @@ class GenerationKernel final : public ControlFlowBase {
 
   void Compute(Ctx& ctx) const override {
     std::lock_guard<std::mutex> lk(mu_);
-    const bool beam = kind_ == "BeamSearch";
-    at::Tensor ids = ctx.RequiredInput(0).to(at::kLong);
+    const bool beam = kind_ == "BeamSearch" || kind_ == "WhisperBeamSearch";
+    const bool encdec = model_type_ != 0;
+    const at::Tensor& enc_input = ctx.RequiredInput(0);
+    at::Tensor ids;
+    if (!encdec) {
+      ids = enc_input.to(at::kLong);
+    } else if (kind_ == "WhisperBeamSearch" && ctx.HasInput(10)) {
+      ids = ctx.Input(10).to(enc_input.device(), at::kLong);   // forced decoder prompt
+    } else {
+      ids = at::full({enc_input.size(0), 1}, start_token_, at::TensorOptions().dtype(at::kLong).device(enc_input.device()));
+    }
     ORTB_ENFORCE_ARG(ids.dim() == 2, kind_, ": input_ids must be [batch, sequence]");
     auto scalar_i = [&](int i, int64_t dflt) { return ctx.HasInput(i) ? ctx.Input(i).cpu().reshape({-1})[0].item<int64_t>() : dflt; };
     auto scalar_f = [&](int i, double dflt) { return ctx.HasInput(i) ? ctx.Input(i).cpu().to(at::kDouble).reshape({-1})[0].item<double>() : dflt; };
@@ -258,14 +291,25 @@ class GenerationKernel final : public ControlFlowBase {
     ORTB_ENFORCE_ARG(K >= 1 && nrs >= 1 && nrs <= K && max_length > S0, kind_, ": invalid num_beams / num_return_sequences / max_length");
     at::Device dev = ids.device();
     at::Tensor vocab_mask = ctx.HasInput(vm) ? ctx.Input(vm).to(dev) : at::Tensor();
-    at::Tensor mask = ctx.HasInput(am) ? ctx.Input(am).to(dev, at::kInt) : at::ones({B, S0}, at::TensorOptions().dtype(at::kInt).device(dev));
+    at::Tensor mask, enc_mask;
+    if (encdec) {
+      // the attention_mask input belongs to the encoder; the decoder side attends to everything generated so far
+      mask = at::ones({B, S0}, at::TensorOptions().dtype(at::kInt).device(dev));
+      if (model_type_ == 1)
+        enc_mask = ctx.HasInput(am) ? ctx.Input(am).to(dev, at::kInt) : at::ones({B, enc_input.size(1)}, at::TensorOptions().dtype(at::kInt).device(dev));
+    } else {
+      mask = ctx.HasInput(am) ? ctx.Input(am).to(dev, at::kInt) : at::ones({B, S0}, at::TensorOptions().dtype(at::kInt).device(dev));
+    }
     const int64_t R = B * K;
     at::Tensor seqs = ids.repeat_interleave(K, 0);
     mask = mask.repeat_interleave(K, 0);
     // positions count the attended tokens (left padding keeps position 0 for the first real token)
     at::Tensor pos = (mask.to(at::kLong).cumsum(1) - 1).clamp_min(0);
     std::vector<at::Tensor> past(static_cast<size_t>(layers_));
-    for (auto& p : past) p = at::zeros({2, R, heads_, 0, head_size_}, at::TensorOptions().dtype(past_type_).device(dev));
+    if (!encdec)
+      for (auto& p : past) p = at::zeros({2, R, heads_, 0, head_size_}, at::TensorOptions().dtype(past_type_).device(dev));
+    at::Tensor enc_hidden, enc_mask_rows;
+    const int64_t reorder_dim = encdec ? 0 : 1;
     at::Tensor step_ids = seqs, step_pos = pos;
     at::Tensor beam_scores = at::zeros({B, K}, at::TensorOptions().dtype(at::kFloat).device(dev));
     if (K > 1) beam_scores.narrow(1, 1, K - 1).fill_(-1e9f);
@@ -276,17 +320,59 @@ class GenerationKernel final : public ControlFlowBase {
     int64_t V = 0;
 
     for (int64_t step = 0; seqs.size(1) < max_length; ++step) {
-      std::vector<Value> in(static_cast<size_t>(3 + layers_));
-      in[0].t = step_ids.to(at::kInt);
-      in[1].t = step_pos.to(at::kInt);
-      in[2].t = mask;
-      for (int l = 0; l < layers_; ++l) in[static_cast<size_t>(3 + l)].t = past[static_cast<size_t>(l)];
-      std::vector<Value> out = RunBody(decoder_, ctx, in);
-      ORTB_ENFORCE(static_cast<int>(out.size()) >= 1 + layers_, kind_, ": the decoder body returned too few outputs");
-      at::Tensor logits = out[0].t;
-      logits = logits.select(1, logits.size(1) - 1).to(at::kFloat).clone();   // [R, V]
+      at::Tensor logits;
+      if (!encdec) {
+        std::vector<Value> in(static_cast<size_t>(3 + layers_));
+        in[0].t = step_ids.to(at::kInt);
+        in[1].t = step_pos.to(at::kInt);
+        in[2].t = mask;
+        for (int l = 0; l < layers_; ++l) in[static_cast<size_t>(3 + l)].t = past[static_cast<size_t>(l)];
+        std::vector<Value> out = RunBody(decoder_, ctx, in);
+        ORTB_ENFORCE(static_cast<int>(out.size()) >= 1 + layers_, kind_, ": the decoder body returned too few outputs");
+        logits = out[0].t;
+        logits = logits.select(1, logits.size(1) - 1).to(at::kFloat).clone();   // [R, V]
+        for (int l = 0; l < layers_; ++l) past[static_cast<size_t>(l)] = out[static_cast<size_t>(1 + l)].t;
+      } else if (step == 0) {
+        // encoder pass: also yields the logits of the first decoder position(s) and every layer's states
+        std::vector<Value> in;
+        in.emplace_back();
+        in.back().t = enc_input;
+        if (model_type_ == 1) {
+          in.emplace_back();
+          in.back().t = enc_mask;
+        }
+        in.emplace_back();
+        in.back().t = ids.to(at::kInt);
+        std::vector<Value> out = RunBody(encoder_, ctx, in);
+        ORTB_ENFORCE(static_cast<int>(out.size()) >= 2 + 4 * layers_, kind_, ": the encoder body returned too few outputs");
+        logits = out[0].t;
+        logits = logits.select(1, logits.size(1) - 1).to(at::kFloat).repeat_interleave(K, 0);
+        enc_hidden = out[1].t.repeat_interleave(K, 0);
+        if (enc_mask.defined()) enc_mask_rows = enc_mask.repeat_interleave(K, 0);
+        past.assign(static_cast<size_t>(4 * layers_), at::Tensor());
+        for (int l = 0; l < layers_; ++l) {   // stored as the decoder wants them: all self states, then all cross states
+          past[static_cast<size_t>(2 * l)] = out[static_cast<size_t>(2 + 4 * l)].t.repeat_interleave(K, 0);
+          past[static_cast<size_t>(2 * l + 1)] = out[static_cast<size_t>(3 + 4 * l)].t.repeat_interleave(K, 0);
+          past[static_cast<size_t>(2 * layers_ + 2 * l)] = out[static_cast<size_t>(4 + 4 * l)].t.repeat_interleave(K, 0);
+          past[static_cast<size_t>(2 * layers_ + 2 * l + 1)] = out[static_cast<size_t>(5 + 4 * l)].t.repeat_interleave(K, 0);
+        }
+      } else {
+        std::vector<Value> in;
+        auto push = [&](const at::Tensor& t) {
+          in.emplace_back();
+          in.back().t = t;
+        };
+        push(step_ids.to(at::kInt));
+        if (dec_has_mask_) push(enc_mask_rows);
+        if (dec_has_hidden_) push(enc_hidden);
+        for (auto& p : past) push(p);
+        std::vector<Value> out = RunBody(decoder_, ctx, in);
+        ORTB_ENFORCE(static_cast<int>(out.size()) >= 1 + 2 * layers_, kind_, ": the decoder body returned too few outputs");
+        logits = out[0].t;
+        logits = logits.select(1, logits.size(1) - 1).to(at::kFloat).clone();
+        for (int i = 0; i < 2 * layers_; ++i) past[static_cast<size_t>(i)] = out[static_cast<size_t>(1 + i)].t;
+      }
       V = logits.size(1);
-      for (int l = 0; l < layers_; ++l) past[static_cast<size_t>(l)] = out[static_cast<size_t>(1 + l)].t;
       // ---- logits processors, in the reference's order
       const int64_t cur_len = seqs.size(1);
       if (eos_ >= 0 && cur_len < min_length) logits.select(1, eos_).fill_(-INFINITY);
@@ -356,7 +442,7 @@ class GenerationKernel final : public ControlFlowBase {
         seqs = seqs.index_select(0, rows);
         mask = mask.index_select(0, rows);
         pos = pos.index_select(0, rows);
-        for (auto& p : past) p = p.index_select(1, rows);
+        for (auto& p : past) p = p.index_select(reorder_dim, rows);
         beam_scores = new_scores.to(dev);
         next_tok = new_tok.reshape({-1}).to(dev);
       }
@@ -427,7 +513,9 @@ class GenerationKernel final : public ControlFlowBase {
   }
 
   std::string kind_;
-  mutable Body decoder_;
+  mutable Body decoder_, encoder_;
+  int64_t model_type_ = 0, start_token_ = 0;
+  bool dec_has_mask_ = false, dec_has_hidden_ = false;
   int64_t eos_ = -1, pad_ = 0, no_repeat_ngram_ = 0, min_tokens_to_keep_ = 1, seed_ = 0, heads_ = 0, head_size_ = 0;
   bool early_stopping_ = false;
   float temperature_ = 1.f, top_p_ = 0.f, filter_value_ = -1e20f, presence_penalty_ = 0.f;
@@ -453,7 +541,7 @@ void RegisterControlFlowKernels(KernelRegistry& r) {
   RegisterClass<IfKernel>(r, "If", 1, {0});
   RegisterClass<LoopKernel>(r, "Loop", 1, {0, 1});
   RegisterClass<ScanKernel>(r, "Scan", 9, {});
-  for (const char* op : {"GreedySearch", "Sampling", "BeamSearch"}) {
+  for (const char* op : {"GreedySearch", "Sampling", "BeamSearch", "WhisperBeamSearch"}) {
     KernelDef d;
     d.domain = kMSDomain;
     d.op_type = op;

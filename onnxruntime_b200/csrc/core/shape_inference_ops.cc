@@ -625,6 +625,7 @@ void RegisterBuiltinSchemas(std::map<std::string, OpSchema>& t) {
   Reg(t, MS, "BeamSearch", 5, 12);
   Reg(t, MS, "GreedySearch", 2, 7);
   Reg(t, MS, "Sampling", 2, 9);
+  Reg(t, MS, "WhisperBeamSearch", 5, 15);
   Reg(t, MS, "DecoderMaskedMultiHeadAttention", 1, 14, [](Ctx& c) { c.PassThrough(0, 0); });
   // third / fourth batch of contrib operators: arity checks for all, shape functions where the output follows an input
   Reg(t, MS, "DecoderMaskedSelfAttention", 3, 10, [](Ctx& c) { c.PassThrough(0, 0); });
