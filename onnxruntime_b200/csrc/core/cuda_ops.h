@@ -19,7 +19,10 @@ at::Tensor LaunchGemm(OpKernelContext& ctx, const at::Tensor& x2d, const at::Ten
 at::Tensor NbitsBuildBlobs(const at::Tensor& B, const at::Tensor& scales, const at::Tensor& zp_bytes, int64_t N, int64_t K,
                            int64_t block);
 at::Tensor LaunchGemmQ4(OpKernelContext& ctx, const at::Tensor& x2d, const at::Tensor& blobs, int64_t n_out, const at::Tensor& bias,
-                        const at::Tensor& residual2d, bool fused_allreduce = false);
+                        const at::Tensor& residual2d, bool fused_allreduce = false, int in_dtype = 4 /* ORTB200_Q4 */);
+// Weight-only fp8 (e4m3 [N, K] + fp32 scales [N, K / block]) as the tile-blob array of the decode GEMM's fp8 mode
+// (layout: ortb200_gemm_args, in_dtype F8W).  K and block must be multiples of 64.
+at::Tensor Fp8WeightBuildBlobs(const at::Tensor& B, const at::Tensor& scales, int64_t block);
 // True when the fused GEMM + all-reduce kernel can take an [M, N] row-parallel product in this session.
 bool CanFuseAllReduce(OpKernelContext& ctx, int64_t M, int64_t N);
 

@@ -237,8 +237,23 @@ at::Tensor NbitsBuildBlobs(const at::Tensor& B, const at::Tensor& scales, const 
 }
 
 // out[M, N] = x[M, K] @ dequant(blobs)[N, K]^T + bias with the 4-bit weights expanded inside the kernel (M <= 64).
+at::Tensor Fp8WeightBuildBlobs(const at::Tensor& B, const at::Tensor& scales, int64_t block) {
+  const int64_t N = B.size(0), K = B.size(1);
+  ORTB_ENFORCE_ARG(K % 64 == 0 && block % 64 == 0 && block > 0, "fp8 weight blobs need K and block_size to be multiples of 64");
+  const int64_t tiles = (N + 127) / 128, kbs = K / 64, rows = tiles * 128;
+  at::Tensor bytes = B.contiguous().view(at::kByte);
+  at::Tensor sc = scales.to(at::kFloat).repeat_interleave(block / 64, 1).narrow(1, 0, kbs).contiguous();   // [N, K / 64]
+  if (rows != N) {  // rows beyond N: zero weights, zero scales
+    bytes = at::cat({bytes, at::zeros({rows - N, K}, bytes.options())}, 0);
+    sc = at::cat({sc, at::zeros({rows - N, kbs}, sc.options())}, 0);
+  }
+  at::Tensor w = bytes.reshape({tiles, 128, kbs, 64}).permute({0, 2, 1, 3}).reshape({tiles, kbs, 128 * 64});
+  at::Tensor s4 = sc.reshape({tiles, 128, kbs}).permute({0, 2, 1}).contiguous().view(at::kByte).reshape({tiles, kbs, 128 * 4});
+  return at::cat({w, s4}, 2).contiguous();   // [tiles, K / 64, 8704]
+}
+
 at::Tensor LaunchGemmQ4(Ctx& ctx, const at::Tensor& x2d, const at::Tensor& blobs, int64_t n_out, const at::Tensor& bias,
-                        const at::Tensor& residual2d, bool fused_allreduce) {
+                        const at::Tensor& residual2d, bool fused_allreduce, int in_dtype) {
   InferenceSession* s = ctx.session();
   const int64_t M = x2d.size(0), K = x2d.size(1);
   at::Tensor out = at::empty({M, n_out}, x2d.options());
@@ -254,7 +269,7 @@ at::Tensor LaunchGemmQ4(Ctx& ctx, const at::Tensor& x2d, const at::Tensor& blobs
   a.M = static_cast<int>(M); a.N = static_cast<int>(n_out); a.K = static_cast<int>(K);
   a.w_rows = static_cast<int>(blobs.size(0) * 128);
   a.dtype = DtypeCode(x2d.scalar_type());
-  a.in_dtype = ORTB200_Q4;
+  a.in_dtype = in_dtype;
   a.act = ORTB200_ACT_NONE;
   a.alpha = 1.f;
   a.status = s->StatusWord().data_ptr<int>();

@@ -867,17 +867,30 @@ class BlockFp8WeightMatMulKernel final : public WithFallback {
       Fallback(ctx);
       return;
     }
-    {
-      std::lock_guard<std::mutex> lock(mu_);
-      if (!w_.defined() || w_.scalar_type() != a.scalar_type()) {
-        at::Tensor s = ctx.RequiredInput(2).to(at::kFloat).repeat_interleave(block_, 1).narrow(1, 0, b.size(1));
-        w_ = (b.to(at::kFloat) * s).to(a.scalar_type()).contiguous();
-      }
-    }
     const int64_t K = b.size(1), N = b.size(0);
     at::Tensor x2 = a.reshape({-1, K}).contiguous();
     at::Tensor bias = ctx.HasInput(4) ? ctx.Input(4) : at::Tensor();
-    at::Tensor y = LaunchGemm(ctx, x2, w_, N, 0, bias, at::Tensor(), ORTB200_ACT_NONE, 1.f);
+    at::Tensor y;
+    // decode-shaped calls keep the weights in fp8: the kernel expands them on their way to the tensor cores (half the
+    // bytes of the 16-bit copy); larger ones use a 16-bit copy that is made when the first such call arrives
+    const bool in_kernel = x2.size(0) <= 64 && K % 64 == 0 && block_ % 64 == 0 &&
+                           ctx.session()->config().Get("ortb200.fp8_weight_in_kernel", "1") != "0";
+    if (in_kernel) {
+      {
+        std::lock_guard<std::mutex> lock(mu_);
+        if (!blobs_.defined()) blobs_ = Fp8WeightBuildBlobs(b, ctx.RequiredInput(2), block_);
+      }
+      y = LaunchGemmQ4(ctx, x2, blobs_, N, bias, at::Tensor(), false, ORTB200_F8W);
+    } else {
+      {
+        std::lock_guard<std::mutex> lock(mu_);
+        if (!w_.defined() || w_.scalar_type() != a.scalar_type()) {
+          at::Tensor s = ctx.RequiredInput(2).to(at::kFloat).repeat_interleave(block_, 1).narrow(1, 0, b.size(1));
+          w_ = (b.to(at::kFloat) * s).to(a.scalar_type()).contiguous();
+        }
+      }
+      y = LaunchGemm(ctx, x2, w_, N, 0, bias, at::Tensor(), ORTB200_ACT_NONE, 1.f);
+    }
     std::vector<int64_t> shape(a.sizes().begin(), a.sizes().end());
     shape.back() = N;
     ctx.SetOutput(0, y.reshape(shape));
@@ -887,7 +900,7 @@ class BlockFp8WeightMatMulKernel final : public WithFallback {
   int64_t block_ = 128;
   bool const_weight_ = false;
   mutable std::mutex mu_;
-  mutable at::Tensor w_;
+  mutable at::Tensor w_, blobs_;
 };
 
 void RegisterCudaKernels3(KernelRegistry& r) {

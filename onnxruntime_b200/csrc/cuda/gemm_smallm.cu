@@ -86,12 +86,13 @@ __device__ __forceinline__ float act_apply(int act, float v) {
 // there.  Shared memory only carries the packed bytes and the token tile: an expanded copy in shared memory would be
 // written once and read once per k-block (32 KiB against 7 KiB of input), and that traffic, not the ALU work, was
 // the bound of the first version of this kernel.
-template <int BN, int STAGES, bool DUAL, bool NBITS = false>
+template <int BN, int STAGES, bool DUAL, int NBITS = 0>
 struct SmallSmem {
   // NBITS: one tile blob per k-block = 4096 bytes of nibbles + 128 x 2 scales + 128 x 2 zero points (4864 bytes,
   // laid out contiguously in global memory by the prepack step), padded to 5 KiB so the X tile stays 1 KiB aligned
-  static constexpr int kBlobBytes = 4096 + 512 + 256;
-  static constexpr int kABytes = NBITS ? 5120 : kBM * kBK * 2;
+  // NBITS == 2 (fp8 weights, weight-only): 128 rows x 64 e4m3 bytes + 128 fp32 scales = 8704 bytes, padded to 9 KiB
+  static constexpr int kBlobBytes = NBITS == 2 ? 8192 + 512 : 4096 + 512 + 256;
+  static constexpr int kABytes = NBITS == 2 ? 9216 : (NBITS ? 5120 : kBM * kBK * 2);
   static constexpr int kBBytes = BN * kBK * 2;
   static constexpr int kStageBytes = kABytes * (DUAL ? 2 : 1) + kBBytes;
   static constexpr int kCols = (DUAL ? 2 : 1) * BN;
@@ -153,6 +154,46 @@ __device__ __forceinline__ void expand_words(const uint32_t w[4], T2 zero, T2 sc
   }
 }
 
+// ---- fp8 (e4m3) weight expansion.  An e4m3 byte moved to bits [4, 12) of a bf16 (sign to bit 15) is the same number
+// scaled by 2^-120 (exponent bias 7 against 127; subnormals line up as well), so one multiplication by
+// 2^120 * block scale yields the dequantised weight.  For fp16 the hardware conversion is used.
+__device__ __forceinline__ uint32_t e4m3_pair_to_bf16_bits(uint32_t w, uint32_t selector) {
+  uint32_t t;
+  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(t) : "r"(w), "r"(0u), "r"(selector));   // bytes -> high halves of the two lanes
+  uint32_t r;
+  asm("lop3.b32 %0, %1, 0x80008000, %2, 0xEA;" : "=r"(r) : "r"(t), "r"((t >> 4) & 0x07F007F0u));  // (t & sign) | magnitude
+  return r;
+}
+__device__ __forceinline__ void expand_fp8_row(const uint4 (&src)[4], float scale, bool bf16, uint32_t out[32]) {
+  const uint32_t w[16] = {src[0].x, src[0].y, src[0].z, src[0].w, src[1].x, src[1].y, src[1].z, src[1].w,
+                          src[2].x, src[2].y, src[2].z, src[2].w, src[3].x, src[3].y, src[3].z, src[3].w};
+  if (bf16) {
+    const __nv_bfloat162 m = __float2bfloat162_rn(scale * 1.329227995784916e36f);   // 2^120 * scale
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const uint32_t lo = e4m3_pair_to_bf16_bits(w[i], 0x1404u), hi = e4m3_pair_to_bf16_bits(w[i], 0x3424u);
+      __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&lo), b = *reinterpret_cast<const __nv_bfloat162*>(&hi);
+      a = __hmul2(a, m);
+      b = __hmul2(b, m);
+      out[2 * i] = *reinterpret_cast<const uint32_t*>(&a);
+      out[2 * i + 1] = *reinterpret_cast<const uint32_t*>(&b);
+    }
+  } else {
+    const __half2 m = __float2half2_rn(scale);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      uint32_t lo, hi;
+      asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(lo) : "h"(static_cast<unsigned short>(w[i] & 0xffffu)));
+      asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(hi) : "h"(static_cast<unsigned short>(w[i] >> 16)));
+      __half2 a = *reinterpret_cast<const __half2*>(&lo), b = *reinterpret_cast<const __half2*>(&hi);
+      a = __hmul2(a, m);
+      b = __hmul2(b, m);
+      out[2 * i] = *reinterpret_cast<const uint32_t*>(&a);
+      out[2 * i + 1] = *reinterpret_cast<const uint32_t*>(&b);
+    }
+  }
+}
+
 #ifdef ORTB200_NBITS_TRACE
 __device__ unsigned long long g_nbits_trace[16];
 #define NB_T(i) do { if (tr) { long long c_ = clock64(); tacc[i] += c_ - tlast; tlast = c_; } } while (0)
@@ -164,7 +205,7 @@ __device__ unsigned long long g_nbits_trace[16];
 #define NB_DUMP(base, n) do {} while (0)
 #endif
 
-template <int BN, int STAGES, bool DUAL, bool NBITS = false>
+template <int BN, int STAGES, bool DUAL, int NBITS = 0>
 __global__ void __launch_bounds__(NBITS ? kThreadsNBits : kThreads, NBITS ? 2 : 1)
 gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
                    const SmallGemmParams p) {
@@ -342,7 +383,14 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
         dq_ok = __all_sync(0xffffffffu, dq_ok);
         NB_T(0);
         uint32_t o[32];
-        if (dq_ok) {
+        if (dq_ok && NBITS == 2) {
+          // fp8 weights: the 64 bytes of row r
+          const uint8_t* blob = smem + s * S::kStageBytes;
+          const uint4* src = reinterpret_cast<const uint4*>(blob + r * 64);
+          const uint4 chunk[4] = {src[0], src[1], src[2], src[3]};
+          const float sc = *reinterpret_cast<const float*>(blob + 8192 + r * 4);
+          expand_fp8_row(chunk, sc, p.dtype == ORTB200_BF16, o);
+        } else if (dq_ok) {
           const uint8_t* blob = smem + s * S::kStageBytes;
           const uint4* src = reinterpret_cast<const uint4*>(blob + r * 32);
           const uint4 p0 = src[0], p1 = src[1];
@@ -616,7 +664,7 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
   }
 }
 
-template <int BN, int STAGES, bool DUAL, bool NBITS = false>
+template <int BN, int STAGES, bool DUAL, int NBITS = 0>
 int launch_small(const CUtensorMap& tw, const CUtensorMap& tx, const SmallGemmParams& p, dim3 grid, cudaStream_t stream,
                  bool use_pdl) {
   using S = SmallSmem<BN, STAGES, DUAL, NBITS>;
@@ -673,7 +721,8 @@ int launch_gemm_smallm(const ortb200_gemm_args* a, int bn, cudaStream_t stream, 
   const int cluster = pick_cluster(tiles_n * tiles_m, num_kb, bn, a->force_splits);
   CUtensorMap tw, tx;
   const CUtensorMapDataType dt = a->dtype == ORTB200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-  const bool nbits = a->in_dtype == ORTB200_Q4;
+  const bool f8w = a->in_dtype == ORTB200_F8W;
+  const bool nbits = a->in_dtype == ORTB200_Q4 || f8w;
   if (nbits) {
     // a->w is the tile-blob array of ortb200_nbits_blob_bytes(N, K) bytes: no tensor map, plain bulk copies
     if (dual || a->K % 64 != 0 || a->rms_eps > 0.f) return -15;
@@ -708,11 +757,19 @@ int launch_gemm_smallm(const ortb200_gemm_args* a, int bn, cudaStream_t stream, 
   dim3 grid(tiles_n * cluster, tiles_m, 1);
   const bool pdl = a->use_pdl != 0;
   *cluster_out = cluster;
+  if (f8w) {
+    switch (bn) {
+      case 16: *stages_out = 9; return launch_small<16, 9, false, 2>(tw, tx, p, grid, stream, pdl);
+      case 32: *stages_out = 8; return launch_small<32, 8, false, 2>(tw, tx, p, grid, stream, pdl);
+      case 64: *stages_out = 6; return launch_small<64, 6, false, 2>(tw, tx, p, grid, stream, pdl);
+      default: return -8;
+    }
+  }
   if (nbits) {
     switch (bn) {
-      case 16: *stages_out = 12; return launch_small<16, 12, false, true>(tw, tx, p, grid, stream, pdl);
-      case 32: *stages_out = 10; return launch_small<32, 10, false, true>(tw, tx, p, grid, stream, pdl);
-      case 64: *stages_out = 8; return launch_small<64, 8, false, true>(tw, tx, p, grid, stream, pdl);
+      case 16: *stages_out = 12; return launch_small<16, 12, false, 1>(tw, tx, p, grid, stream, pdl);
+      case 32: *stages_out = 10; return launch_small<32, 10, false, 1>(tw, tx, p, grid, stream, pdl);
+      case 64: *stages_out = 8; return launch_small<64, 8, false, 1>(tw, tx, p, grid, stream, pdl);
       default: return -8;
     }
   }

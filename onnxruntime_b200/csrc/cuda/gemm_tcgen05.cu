@@ -647,7 +647,7 @@ extern "C" int ortb200_gemm(const ortb200_gemm_args* a, ortb200_stream_t stream_
   if (!a || !a->x || !a->w || !a->out) return -1;
   if (a->M <= 0 || a->N <= 0 || a->K <= 0) return -1;
   const bool fp8 = a->in_dtype == ORTB200_F8E4M3;
-  const bool q4 = a->in_dtype == ORTB200_Q4;
+  const bool q4 = a->in_dtype == ORTB200_Q4 || a->in_dtype == ORTB200_F8W;  // tile-blob weights expanded inside the decode kernel
   if (a->in_dtype != 0 && !fp8 && !q4 && a->in_dtype != a->dtype) return -4;
   if (a->K % (fp8 ? 16 : 8) != 0) return -2;                     // TMA row pitch must be a multiple of 16 bytes
   if ((reinterpret_cast<uintptr_t>(a->x) & 15) || (reinterpret_cast<uintptr_t>(a->w) & 15)) return -3;

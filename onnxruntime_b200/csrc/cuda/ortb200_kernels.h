@@ -17,7 +17,7 @@ extern "C" {
 
 typedef void* ortb200_stream_t;  // cudaStream_t
 
-enum ortb200_dtype { ORTB200_F16 = 0, ORTB200_BF16 = 1, ORTB200_F32 = 2, ORTB200_F8E4M3 = 3, ORTB200_Q4 = 4 };
+enum ortb200_dtype { ORTB200_F16 = 0, ORTB200_BF16 = 1, ORTB200_F32 = 2, ORTB200_F8E4M3 = 3, ORTB200_Q4 = 4, ORTB200_F8W = 5 };
 
 enum ortb200_act {
   ORTB200_ACT_NONE = 0,
@@ -91,6 +91,10 @@ typedef struct {
   //     [4096, 4608) row r at r * 4: the scales of elements [0, 32) and [32, 64) of the k-block, in `dtype`
   //     [4608, 4864) row r at r * 2: their zero points, one byte each (8 when the model has none)
   //   rows beyond N are zero.  W[n, k] = (q - zp) * scale.
+  // in_dtype == ORTB200_F8W (decode-shaped problems, M <= 64): weight-only fp8.  w is a tile-blob array like the 4-bit
+  // one: blob(tile t, k-block kb) at byte ((t * K / 64) + kb) * 8704 holds [0, 8192) row r at r * 64: the 64 e4m3 bytes
+  // W[128 t + r, 64 kb ... 64 kb + 63], and [8192, 8704) row r at r * 4: the fp32 scale of that row and k-block.
+  // W[n, k] = e4m3(byte) * scale.  The kernel expands to `dtype` on the way to the tensor cores.  K a multiple of 64.
   int force_tile_rows;  // 0 / 128 = 128-weight-row CTA tiles; 256 = 256-row tiles in the large-M kernel (M > 128);
                         // 512 = pairs of CTAs on 256 x 256 tiles (cta_group::2 kernel)
   // Prompt-sized fused all-reduce (world > 1, M > 64) with NVLS: the multicast address of the symmetric workspace.  The

@@ -327,29 +327,41 @@ def test_session_qmoe(bits, block):
     assert np.abs(c - g).max() / np.abs(c).max() < 2e-2
 
 
-def test_block_scaled_fp8_weight_matmul_on_gpu():
-    """MatMulBlockQuantizedFp8Weight: the weight is expanded once and the product runs on the tcgen05 GEMM."""
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("N", [512, 500])
+def test_block_scaled_fp8_weight_matmul_on_gpu(dtype, N):
+    """MatMulBlockQuantizedFp8Weight: decode-shaped calls keep the weight in fp8 and expand it inside the tcgen05 decode
+    GEMM (tensor-memory operand); larger ones use a 16-bit copy made once.  Both against the dequantised product."""
     import onnxruntime_b200 as ort
     from onnxruntime_b200 import onnx_lite as ol
     T = ol.TensorProto
     torch.manual_seed(0)
-    N, K, bs = 512, 1024, 128
+    K, bs = 1024, 128
     w8 = (torch.randn(N, K) * 2).to(torch.float8_e4m3fn)
+    w8.view(torch.uint8)[:, :16] = torch.arange(16, dtype=torch.uint8)      # zero, the seven subnormals and small normals
+    w8.view(torch.uint8)[:, 16:32] = torch.arange(16, dtype=torch.uint8) + 0x80
     scale = (torch.rand(N, K // bs) + 0.5).float() * 0.02
-    bias = torch.randn(N).to(torch.bfloat16)
+    bias = torch.randn(N).to(dtype)
+    et = T.BFLOAT16 if dtype == torch.bfloat16 else T.FLOAT16
     node = ol.make_node("MatMulBlockQuantizedFp8Weight", ["a", "b", "s", "", "bias"], ["y"], domain="com.microsoft", block_size=bs)
-    g = ol.make_graph([node], "g", [ol.make_tensor_value_info("a", T.BFLOAT16, ["m", K])], [ol.make_tensor_value_info("y", T.BFLOAT16, ["m", N])],
+    g = ol.make_graph([node], "g", [ol.make_tensor_value_info("a", et, ["m", K])], [ol.make_tensor_value_info("y", et, ["m", N])],
                       [ol.make_tensor("b", w8), ol.make_tensor("s", scale), ol.make_tensor("bias", bias)])
-    sess = ort.InferenceSession(ol.make_model(g, opset=17).serialize(), providers=["CUDAExecutionProvider"], enable_fallback=False)
-    w = (w8.float() * scale.repeat_interleave(bs, 1)).to(torch.bfloat16).float()
-    for m in (8, 300):
-        a = torch.randn(m, K).to(torch.bfloat16)
+    model = ol.make_model(g, opset=17).serialize()
+    sess = ort.InferenceSession(model, providers=["CUDAExecutionProvider"], enable_fallback=False)
+    so = ort.SessionOptions()
+    so.add_session_config_entry("ortb200.fp8_weight_in_kernel", "0")
+    copy16 = ort.InferenceSession(model, so, providers=["CUDAExecutionProvider"], enable_fallback=False)
+    w = (w8.float() * scale.repeat_interleave(bs, 1)).to(dtype).float()
+    for m in (1, 8, 40, 300):
+        a = torch.randn(m, K).to(dtype)
         before = sess.kernel_launch_count()
-        (y,) = sess.run(None, {"a": a})
-        assert sess.kernel_launch_count() > before
+        y = torch.as_tensor(sess.run(None, {"a": a.cuda()})[0]).float().cpu()
+        assert sess.kernel_launch_count() == before + 1
         ref = a.float() @ w.T + bias.float()
-        y = torch.as_tensor(y).float().cpu() if not isinstance(y, torch.Tensor) else y.float().cpu()
-        assert (y - ref).abs().max() / ref.abs().max() < 2e-2
+        assert (y - ref).abs().max() / ref.abs().max() < 1e-2, m
+        y16 = torch.as_tensor(copy16.run(None, {"a": a.cuda()})[0]).float().cpu()
+        assert (y - y16).abs().max() / ref.abs().max() < 1e-2, m
+    sess.check_device_status()
 
 
 @pytest.mark.parametrize("dtype", [np.float16, np.float32])
