@@ -441,6 +441,7 @@ void GraphExecutor::RunStep(const RunOptions& ro, const Step& st, std::vector<Va
     ORTB_THROW(RUNTIME_EXCEPTION, "Non-zero status code returned while running ", st.node->op_type, " node. Name:'",
                st.node->name, "' Status Message: ", e.what());
   }
+  if (dump_.any) DumpNodeIO(dump_, *st.node, in, out);
   for (size_t i = 0; i < st.out_slots.size(); ++i) {
     const int s = st.out_slots[i];
     if (s < 0) continue;

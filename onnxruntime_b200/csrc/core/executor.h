@@ -17,6 +17,7 @@
 #include <vector>
 
 #include "allocation_planner.h"
+#include "debug_node_io.h"
 #include "session.h"
 
 namespace ortb {
@@ -79,6 +80,7 @@ class GraphExecutor {
   };
   std::vector<SlotTrace> trace_;
   bool tracing_ = false;
+  NodeDumpOptions dump_ = NodeDumpOptions::FromEnvironment();
 };
 
 }  // namespace ortb

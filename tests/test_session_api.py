@@ -407,3 +407,34 @@ def test_tuning_results_are_empty_on_cpu_and_imports_are_validated():
     import pytest
     with pytest.raises(ort.capi.InvalidArgument):
         sess.set_tuning_results([{"ep": "ROCMExecutionProvider", "validators": {}, "results": {}}], error_on_invalid=True)
+
+
+def test_debug_node_io_environment_variables(tmp_path):
+    """ORT_DEBUG_NODE_IO_*: shapes, placement, statistics and output snippets of the selected nodes, to stdout or files."""
+    import subprocess
+    import sys
+    script = r'''
+import numpy as np, onnxruntime_b200 as ort
+from onnxruntime_b200 import onnx_lite as ol
+T = ol.TensorProto
+g = ol.make_graph([ol.make_node("Relu", ["x"], ["r"], name="relu0"), ol.make_node("Log", ["r"], ["y"], name="log0")], "g",
+                  [ol.make_tensor_value_info("x", T.FLOAT, [2, 3])], [ol.make_tensor_value_info("y", T.FLOAT, [2, 3])])
+so = ort.SessionOptions(); so.graph_optimization_level = ort.GraphOptimizationLevel.ORT_DISABLE_ALL
+s = ort.InferenceSession(ol.make_model(g, opset=17).serialize(), so, providers=["CPUExecutionProvider"])
+s.run(None, {"x": np.array([[-1, 2, 3], [4, -5, 6]], np.float32)})
+'''
+    env = dict(os.environ, ORT_DEBUG_NODE_IO_DUMP_SHAPE_DATA="1", ORT_DEBUG_NODE_IO_DUMP_NODE_PLACEMENT="1",
+               ORT_DEBUG_NODE_IO_DUMP_STATISTICS_DATA="1", ORT_DEBUG_NODE_IO_DUMP_OUTPUT_DATA="1", ORT_DEBUG_NODE_IO_OP_TYPE_FILTER="Log",
+               ORT_DEBUG_NODE_IO_SNIPPET_EDGE_ITEMS="2")
+    env["PYTHONPATH"] = os.pathsep.join([os.path.dirname(os.path.dirname(os.path.abspath(__file__))), env.get("PYTHONPATH", "")])
+    out = subprocess.run([sys.executable, "-c", script], capture_output=True, text=True, env=env, timeout=300)
+    assert out.returncode == 0, out.stderr[-2000:]
+    text = out.stdout
+    assert "node 'log0' (Log) on CPUExecutionProvider" in text and "relu0" not in text
+    assert "input 'r' Float [2, 3]" in text and "output 'y' Float [2, 3]" in text
+    assert "inf 2" in text and "count 6" in text                 # log(0) twice
+    assert "data: [-inf 0.693147 ... -inf 1.79176]" in text
+    env.update(ORT_DEBUG_NODE_IO_DUMP_DATA_DESTINATION="files", ORT_DEBUG_NODE_IO_OUTPUT_DIR=str(tmp_path), ORT_DEBUG_NODE_IO_OP_TYPE_FILTER="Relu")
+    out = subprocess.run([sys.executable, "-c", script], capture_output=True, text=True, env=env, timeout=300)
+    assert out.returncode == 0 and "node '" not in out.stdout
+    assert "output 'r' Float [2, 3]" in (tmp_path / "relu0.txt").read_text()
