@@ -288,3 +288,22 @@ def test_whisper_beam_search_with_forced_decoder_prompt():
             return np.tanh(W2["Ed"][seq[-1]] + (W2["Ed"][seq] @ W2["Wv2"]).mean(0) + hidden.mean(0) + 0.1 * hidden.mean(0)) @ W2["Wo2"]
         (score, seq), = _ref_beam(list(prompt[b]), K, max_len, eos, 1.0, 1, logits_fn=fn)
         np.testing.assert_array_equal(got[b, 0, :len(seq)], np.array(seq, np.int32))
+
+
+def test_convert_generation_tool_wraps_a_decoder_file(tmp_path):
+    """transformers.convert_generation: decoder.onnx -> a model with one BeamSearch node, same result as the hand-built one."""
+    from onnxruntime_b200.transformers import convert_generation as cg
+    dec_path, out_path = tmp_path / "decoder.onnx", tmp_path / "beam.onnx"
+    dec_path.write_bytes(ol.make_model(decoder_body()).serialize())
+    assert cg.main(["--decoder_onnx", str(dec_path), "--output", str(out_path), "--num_beams_op", "beam", "--eos_token_id", "5"]) == 0
+    sess = ort.InferenceSession(str(out_path), providers=["CPUExecutionProvider"])
+    assert [i.name for i in sess.get_inputs()] == ["input_ids", "max_length", "min_length", "num_beams", "num_return_sequences", "length_penalty",
+                                                   "repetition_penalty", "attention_mask"]
+    ids = np.array([[3, 9, 1, 4]], np.int32)
+    seqs, scores = sess.run(None, {"input_ids": ids, "max_length": np.array([10], np.int32), "min_length": np.array([0], np.int32),
+                                   "num_beams": np.array([3], np.int32), "num_return_sequences": np.array([1], np.int32),
+                                   "length_penalty": np.array([1.0], np.float32), "repetition_penalty": np.array([1.0], np.float32),
+                                   "attention_mask": np.ones((1, 4), np.int32)})
+    (score, seq), = _ref_beam(list(ids[0]), 3, 10, 5, 1.0, 1)
+    np.testing.assert_array_equal(seqs[0, 0, :len(seq)], np.array(seq, np.int32))
+    assert abs(scores[0, 0] - score) < 1e-3
