@@ -171,6 +171,7 @@ const std::vector<Pass>& AllPasses() {
     AddFusionPasses(v);
     AddMorePasses(v);
     AddQdqPasses(v);  // after the transformer fusions: those match the un-simplified MatMul / Add / Softmax forms
+    AddMorePasses2(v);  // MatMul scale / transpose folding and the conv fusions come last for the same reason
     AddGpuPasses(v);
     return v;
   }();

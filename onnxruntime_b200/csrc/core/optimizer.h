@@ -73,6 +73,7 @@ void AddFusionPasses(std::vector<Pass>& v);
 void AddGpuPasses(std::vector<Pass>& v);
 void AddMorePasses(std::vector<Pass>& v);
 void AddQdqPasses(std::vector<Pass>& v);
+void AddMorePasses2(std::vector<Pass>& v);
 
 // Replace the nodes of `m` by `fused` (already added to the graph); rewires nothing else.
 void RemoveMatched(Graph& g, const Match& m);

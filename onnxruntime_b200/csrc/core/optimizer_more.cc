@@ -422,6 +422,7 @@ int GroupQueryAttentionFusion(PassContext& c) {
         a->inputs[9] = pos;
         a->set_attr_i("do_rotary", 1);
         a->set_attr_i("rotary_interleaved", inter);
+        g.Invalidate();
         g.RemoveNode(rq);
         g.RemoveNode(rk);
         changed = true;
@@ -452,6 +453,7 @@ int GroupQueryAttentionFusion(PassContext& c) {
           a->inputs[0] = packed;
           a->inputs[1] = "";
           a->inputs[2] = "";
+          g.Invalidate();
           g.RemoveNode(mq);
           g.RemoveNode(mk);
           g.RemoveNode(mv);

@@ -481,3 +481,65 @@ def test_group_query_attention_fusion_takes_rotary_and_packs_qkv():
     before, after = both(model, feeds)
     assert before["RotaryEmbedding"] == 2 and before["MatMul"] == 3
     assert after.get("RotaryEmbedding", 0) == 0 and after["MatMul"] == 1 and after["GroupQueryAttention"] == 1
+
+
+def test_slice_expand_conv_gemm_rewrites():
+    r = np.random.RandomState(11)
+    x4 = [ol.make_tensor_value_info("x", T.FLOAT, [2, 3, 6, 6])]
+    inits = [c("w", r.randn(4, 3, 3, 3) * 0.3), c("b", r.randn(4)), c("addk", r.randn(1, 4, 1, 1)), c("mulk", r.randn(4, 1, 1)),
+             c("starts", [0, 0], np.int64), c("ends", [2**31 - 1, 6], np.int64), c("axes", [1, 3], np.int64), c("shape", [1, 1, 4, 4], np.int64)]
+    nodes = [ol.make_node("Slice", ["x", "starts", "ends", "axes"], ["xs"]),
+             ol.make_node("Conv", ["xs", "w", "b"], ["cv"], name="conv0"),
+             ol.make_node("Mul", ["cv", "mulk"], ["cm"]), ol.make_node("Add", ["addk", "cm"], ["ca"]),
+             ol.make_node("Expand", ["ca", "shape"], ["ce"]), ol.make_node("Relu", ["ce"], ["y"])]
+    model = graph_model(nodes, x4, Y, inits)
+    before, after = both(model, {"x": r.randn(2, 3, 6, 6).astype(np.float32)})
+    assert before["Slice"] == 1 and before["Expand"] == 1
+    assert after == {"FusedConv": 1}                                  # slice and expand gone, Mul / Add folded, Relu fused
+    # Gemm + Sum
+    g_in = [ol.make_tensor_value_info("a", T.FLOAT, [5, 8]), ol.make_tensor_value_info("cc", T.FLOAT, [1, 7])]
+    model = graph_model([ol.make_node("Gemm", ["a", "w2"], ["gm"]), ol.make_node("Sum", ["cc", "gm"], ["y"])], g_in, Y, [c("w2", r.randn(8, 7))])
+    before, after = both(model, {"a": r.randn(5, 8).astype(np.float32), "cc": r.randn(1, 7).astype(np.float32)})
+    assert after == {"Gemm": 1}
+
+
+def test_matmul_scale_and_transpose_become_fused_matmul():
+    r = np.random.RandomState(12)
+    ins = [ol.make_tensor_value_info("a", T.FLOAT, [2, 4, 5]), ol.make_tensor_value_info("b", T.FLOAT, [2, 6, 5])]
+    nodes = [ol.make_node("Mul", ["a", "two"], ["a2"]), ol.make_node("Transpose", ["b"], ["bt"], perm=[0, 2, 1]),
+             ol.make_node("MatMul", ["a2", "bt"], ["mm"]), ol.make_node("Div", ["mm", "four"], ["y"])]
+    model = graph_model(nodes, ins, Y, [c("two", 2.0), c("four", 4.0)])
+    before, after = both(model, {"a": r.randn(2, 4, 5).astype(np.float32), "b": r.randn(2, 6, 5).astype(np.float32)})
+    assert after == {"FusedMatMul": 1}
+
+
+def test_integer_matmul_chain_becomes_dynamic_quantize_matmul():
+    r = np.random.RandomState(13)
+    wq = r.randint(-100, 100, (8, 6)).astype(np.int8)
+    nodes = [ol.make_node("DynamicQuantizeLinear", ["x"], ["xq", "xs", "xz"]),
+             ol.make_node("MatMulInteger", ["xq", "wq", "xz", "wz"], ["acc"]), ol.make_node("Cast", ["acc"], ["accf"], to=T.FLOAT),
+             ol.make_node("Mul", ["xs", "ws"], ["s"]), ol.make_node("Mul", ["accf", "s"], ["scaled"]), ol.make_node("Add", ["scaled", "bias"], ["y"])]
+    inits = [ol.make_tensor("wq", wq), c("wz", 0, np.int8), c("ws", [0.02]), c("bias", r.randn(6))]
+    model = graph_model(nodes, [ol.make_tensor_value_info("x", T.FLOAT, [3, 8])], Y, inits)
+    before, after = both(model, {"x": r.randn(3, 8).astype(np.float32)})
+    assert before["MatMulInteger"] == 1 and after == {"DynamicQuantizeMatMul": 1}
+
+
+def test_bias_skip_layer_norm_and_gelu_approximation():
+    r = np.random.RandomState(14)
+    nodes = [ol.make_node("Add", ["x", "bias"], ["xb"]),
+             ol.make_node("SkipLayerNormalization", ["xb", "skip", "gamma", "beta"], ["n"], domain="com.microsoft", epsilon=1e-5),
+             ol.make_node("Gelu", ["n"], ["y"], domain="com.microsoft")]
+    inits = [c("bias", r.randn(16)), c("gamma", r.randn(16)), c("beta", r.randn(16))]
+    model = graph_model(nodes, X + [ol.make_tensor_value_info("skip", T.FLOAT, ["b", 8, 16])], Y, inits)
+    feeds = {"x": xs["x"], "skip": r.randn(2, 8, 16).astype(np.float32)}
+    before, after = both(model, feeds)
+    assert after == {"SkipLayerNormalization": 1, "Gelu": 1}
+    so = ort.SessionOptions()
+    so.add_session_config_entry("optimization.enable_gelu_approximation", "1")
+    approx = ort.InferenceSession(model, so, providers=["CPUExecutionProvider"])
+    assert op_counts(approx) == {"SkipLayerNormalization": 1, "FastGelu": 1}
+    so0 = ort.SessionOptions()
+    so0.graph_optimization_level = ort.GraphOptimizationLevel.ORT_DISABLE_ALL
+    exact = ort.InferenceSession(model, so0, providers=["CPUExecutionProvider"]).run(None, feeds)[0]
+    np.testing.assert_allclose(approx.run(None, feeds)[0], exact, rtol=0, atol=2e-3)     # tanh form: close, not equal
