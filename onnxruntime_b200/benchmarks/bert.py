@@ -1,6 +1,6 @@
 """BERT-large encoder throughput, data parallel: every rank runs batch x seq tokens through the same model.
 
-    python -m onnxruntime_b200.benchmarks.bert [--batch 64 --seq 384 --layers 24 --steps 10 --baseline torch]
+    python -m onnxruntime_b200.benchmarks.bert [--batch 64 --seq 384 --layers 24 --steps 10 --baseline torch --dtype fp8]
 
 The session path loads the exporter-style (unfused) graph and lets the optimizer find Attention,
 SkipLayerNormalization, EmbedLayerNormalization and the GEMM epilogues; inputs are bound on the device."""
@@ -44,11 +44,12 @@ def main(argv=None) -> int:
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--baseline", default="", choices=["", "torch"])
+    ap.add_argument("--dtype", default="fp16", choices=["fp16", "fp8"], help="fp8: dense layers as GemmFloat8 (e4m3 weights and activations)")
     a = ap.parse_args(argv)
     rank, world, device, info = setup()
 
     import onnxruntime_b200 as ort
-    from onnxruntime_b200.models.bert import BertConfig, build_bert, init_weights
+    from onnxruntime_b200.models.bert import BertConfig, build_bert, build_bert_fp8, init_weights
     cfg = BertConfig.bert_large(num_layers=a.layers, max_position=max(512, a.seq))
     weights = init_weights(cfg)
     rng = np.random.RandomState(rank)
@@ -63,7 +64,7 @@ def main(argv=None) -> int:
         launches = None
         fused = {}
     else:
-        model = build_bert(cfg, weights)
+        model = build_bert_fp8(cfg, weights) if a.dtype == "fp8" else build_bert(cfg, weights)
         sess = ort.InferenceSession(model, providers=[("CUDAExecutionProvider", {"device_id": str(device.index)})], enable_fallback=False)
         out_name = sess.get_outputs()[0].name
         out = torch.empty(a.batch, a.seq, cfg.hidden_size, dtype=torch.float16, device=device)
@@ -75,14 +76,14 @@ def main(argv=None) -> int:
         launches = sess.last_run_launch_count()
         fused = {}
         for n in sess.graph_nodes():
-            if n["op_type"] in ("Attention", "SkipLayerNormalization", "EmbedLayerNormalization", "FusedGemm", "BiasGelu"):
+            if n["op_type"] in ("Attention", "MultiHeadAttention", "SkipLayerNormalization", "EmbedLayerNormalization", "FusedGemm", "BiasGelu", "GemmFloat8"):
                 fused[n["op_type"]] = fused.get(n["op_type"], 0) + 1
         sess.check_device_status()
     tokens = a.batch * a.seq * world
     flops = a.layers * (8 * cfg.hidden_size ** 2 + 4 * cfg.hidden_size * cfg.ffn_size + 4 * a.seq * cfg.hidden_size) * a.batch * a.seq
     report(rank, metric="bert_large_sequences_per_s", value=round(a.batch * world / (ms * 1e-3), 2), unit="sequences/s", n_gpus=world,
            ms_per_step=round(ms, 3), tokens_per_s=round(tokens / (ms * 1e-3), 1), tflops_per_gpu=round(flops / (ms * 1e-3) / 1e12, 1),
-           dtype="fp16", impl=a.baseline or "ours", config={"batch_per_gpu": a.batch, "seq_len": a.seq, "layers": a.layers,
+           dtype=a.dtype, impl=a.baseline or "ours", config={"batch_per_gpu": a.batch, "seq_len": a.seq, "layers": a.layers,
                                                             "parallelism": f"dp{world}"},
            launches_per_step=launches, fused_ops=fused, data="synthetic (random ids, right-padded to random lengths)")
     finish(world)

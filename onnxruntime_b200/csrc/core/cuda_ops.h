@@ -14,7 +14,8 @@ void CheckLaunch(int rc, const char* what);
 // x2d / w_nk of type Float8_e4m3fn run the tensor cores in 8-bit mode; out_type (fp16 / bf16) is then required.
 at::Tensor LaunchGemm(OpKernelContext& ctx, const at::Tensor& x2d, const at::Tensor& w_nk, int64_t n_out,
                       int64_t dual_offset, const at::Tensor& bias, const at::Tensor& residual2d, int act, float alpha,
-                      bool fused_allreduce = false, at::ScalarType out_type = at::ScalarType::Undefined, float rms_eps = 0.f);
+                      bool fused_allreduce = false, at::ScalarType out_type = at::ScalarType::Undefined, float rms_eps = 0.f,
+                      const at::Tensor& alpha_dev = at::Tensor());
 // MatMulNBits (4-bit) weights as the tile-blob array the decode GEMM expands in shared memory, and that GEMM (M <= 64).
 at::Tensor NbitsBuildBlobs(const at::Tensor& B, const at::Tensor& scales, const at::Tensor& zp_bytes, int64_t N, int64_t K,
                            int64_t block);

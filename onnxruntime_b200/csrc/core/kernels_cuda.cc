@@ -129,7 +129,7 @@ void ApplyTunedConfig(Ctx& ctx, ortb200_gemm_args* a, at::ScalarType out_type) {
 // out[M,N] = act(x[M,K] @ w_nk[N,K]^T + bias) + residual on the tcgen05 GEMM.
 at::Tensor LaunchGemm(Ctx& ctx, const at::Tensor& x2d, const at::Tensor& w_nk, int64_t n_out, int64_t dual_offset,
                       const at::Tensor& bias, const at::Tensor& residual2d, int act, float alpha, bool fused_allreduce,
-                      at::ScalarType out_type, float rms_eps) {
+                      at::ScalarType out_type, float rms_eps, const at::Tensor& alpha_dev) {
   InferenceSession* s = ctx.session();
   const int64_t M = x2d.size(0), K = x2d.size(1);
   const bool fp8 = x2d.scalar_type() == at::kFloat8_e4m3fn;
@@ -156,6 +156,7 @@ at::Tensor LaunchGemm(Ctx& ctx, const at::Tensor& x2d, const at::Tensor& w_nk, i
   a.rms_eps = rms_eps;
   a.act = act;
   a.alpha = alpha;
+  a.alpha_dev = alpha_dev.defined() ? alpha_dev.data_ptr<float>() : nullptr;
   a.workspace = ws.data_ptr();
   a.workspace_bytes = ws.numel();
   a.status = s->StatusWord().data_ptr<int>();

@@ -747,15 +747,26 @@ class GemmFloat8Kernel final : public WithFallback {
       Fallback(ctx);
       return;
     }
-    auto scale = [&](int i) -> float {
-      if (!ctx.HasInput(i)) return 1.f;
-      if (!std::isnan(const_scale_[i - 3])) return const_scale_[i - 3];
-      return ctx.Input(i).to(at::kCPU, at::kFloat).reshape({-1})[0].item<float>();  // runtime scale: one host read
+    // constant scales fold into alpha on the host; scales that are computed at run time stay on the device and the
+    // kernel multiplies their product in (no host read, so the node can sit inside a captured graph)
+    float alpha = alpha_;
+    at::Tensor alpha_dev;
+    auto fold = [&](int i, bool divide) {
+      if (!ctx.HasInput(i)) return;
+      if (!std::isnan(const_scale_[i - 3])) {
+        alpha = divide ? alpha / const_scale_[i - 3] : alpha * const_scale_[i - 3];
+        return;
+      }
+      at::Tensor s = ctx.Input(i).to(A.device(), at::kFloat).reshape({1});
+      if (divide) s = s.reciprocal();
+      alpha_dev = alpha_dev.defined() ? alpha_dev * s : s;
     };
-    float alpha = alpha_ * scale(3) * scale(4);
-    if (has_sy) alpha /= scale(5);
+    fold(3, false);
+    fold(4, false);
+    if (has_sy) fold(5, true);
+    if (alpha_dev.defined()) alpha_dev = alpha_dev.contiguous();
     at::Tensor w = b_nk_.defined() ? b_nk_ : ctx.Input(1).contiguous();
-    at::Tensor y = LaunchGemm(ctx, A.contiguous(), w, w.size(0), 0, bias, at::Tensor(), act, alpha, false, out_t);
+    at::Tensor y = LaunchGemm(ctx, A.contiguous(), w, w.size(0), 0, bias, at::Tensor(), act, alpha, false, out_t, 0.f, alpha_dev);
     ctx.SetOutput(0, y);
   }
 

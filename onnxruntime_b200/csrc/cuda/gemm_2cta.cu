@@ -40,6 +40,9 @@ struct Gemm2Params {
   int tiles_m, tiles;  // tiles of 256 x 256; tile = tile_n * tiles_m + tile_m
   int dtype, act;
   float alpha;
+  const float* alpha_dev;  // optional device scalar multiplied into alpha (fp8 operands with run-time scales)
+  int in_fp8;              // 1: x and w hold e4m3 bytes; a stage then carries 128 K-elements and the MMAs run as kind::f8f6f4
+  int k_per_block;         // K elements per pipeline stage: 64 (16-bit operands) or 128 (fp8)
   void* out;
   long long ldo;
   const void* bias;
@@ -103,6 +106,14 @@ __device__ __forceinline__ void umma2_f16(uint32_t tmem_d, uint64_t adesc, uint6
       "{\n\t.reg .pred p;\n\t"
       "setp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma2_f8(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
       ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
@@ -204,15 +215,15 @@ gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
           uint8_t* st = smem + s * S::kStageBytes;
           const uint32_t bar = map_to_rank(smem_u32(&full_bar[s]), 0);
           if (leader) mbar_expect_tx(&full_bar[s], 2 * S::kStageBytes);
-          tma_load_2d_pair(st, &tmap_w, bar, kb * kBK, n0);
-          tma_load_2d_pair(st + S::kABytes, &tmap_x, bar, kb * kBK, m0);
+          tma_load_2d_pair(st, &tmap_w, bar, kb * p.k_per_block, n0);
+          tma_load_2d_pair(st + S::kABytes, &tmap_x, bar, kb * p.k_per_block, m0);
         }
       }
       if (!ok && p.status) atomicExch(p.status, kStatusTimeoutProducer);
     }
   } else if (warp == 1) {
     if (leader && lane == 0) {
-      const uint32_t idesc = umma_idesc_f16(p.dtype == ORTB200_BF16, 2 * kBM, kBN);
+      const uint32_t idesc = p.in_fp8 ? umma_idesc_e4m3(2 * kBM, kBN) : umma_idesc_f16(p.dtype == ORTB200_BF16, 2 * kBM, kBN);
       long long it = 0;
       int seg = 0;
       bool ok = true;
@@ -235,7 +246,10 @@ gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
           const uint64_t adesc = umma_desc_sw128(a_addr);
           const uint64_t bdesc = umma_desc_sw128(a_addr + S::kABytes);
 #pragma unroll
-          for (int k = 0; k < kBK / 16; ++k) umma2_f16(tmem_d, adesc + 2 * k, bdesc + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          for (int k = 0; k < kBK / 16; ++k) {  // 32 bytes of K per instruction: 16 16-bit or 32 8-bit elements
+            if (p.in_fp8) umma2_f8(tmem_d, adesc + 2 * k, bdesc + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            else umma2_f16(tmem_d, adesc + 2 * k, bdesc + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
           umma2_commit_both(&empty_bar[s]);
         }
         umma2_commit_both(&tmem_full_bar[buf]);  // also after a failed wait, so the epilogues do not wait for nothing
@@ -292,6 +306,7 @@ gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
     const uint32_t empty_remote1 = map_to_rank(smem_u32(&tmem_empty_bar[1]), 0);
     int seg = 0;
     bool ok = true;
+    const float alpha_v = p.alpha_dev ? p.alpha * __ldg(p.alpha_dev) : p.alpha;
     // a wait that gives up clears `ok`; the loop still runs to its end so that the store helpers, which count the same
     // barriers, never wait for nothing
     for (int t = pair; t < tiles; t += num_pairs, ++seg) {
@@ -323,7 +338,7 @@ gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         tmem_ld_wait();
 #pragma unroll
         for (int j = 0; j < 128; ++j) {
-          const float y = v[j] * p.alpha + bias_v;
+          const float y = v[j] * alpha_v + bias_v;
           uint16_t bits;
           if (bf16) {
             const __nv_bfloat16 h = __float2bfloat16_rn(y);
@@ -371,14 +386,24 @@ gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
 }  // namespace
 
 int launch_gemm_2cta(const ortb200_gemm_args* a, cudaStream_t stream) {
-  if (a->act == ORTB200_ACT_SWIGLU || a->in_dtype != 0 || a->rms_eps > 0.f) return -16;
+  const bool fp8 = a->in_dtype == ORTB200_F8E4M3;
+  if (a->act == ORTB200_ACT_SWIGLU || (a->in_dtype != 0 && !fp8) || a->rms_eps > 0.f) return -16;
+  if (fp8 && (a->world > 1 || a->K % 16 != 0)) return -16;
+  if (a->alpha_dev != nullptr && !fp8) return -16;
   if (a->world > 1 && (a->act != ORTB200_ACT_NONE || a->ldo != a->N || a->N % 8 != 0 || a->world > 8)) return -12;
   CUtensorMap tw, tx;
-  const CUtensorMapDataType dt = a->dtype == ORTB200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-  if (make_tensor_map_2d(&tw, a->w, dt, 2, a->K, a->w_rows, static_cast<int64_t>(a->K) * 2, kBK, kBM) != 0) return -6;
-  if (make_tensor_map_2d(&tx, a->x, dt, 2, a->K, a->M, static_cast<int64_t>(a->K) * 2, kBK, kBNHalf) != 0) return -6;
+  const int k_per_block = fp8 ? 2 * kBK : kBK;   // a stage row is 128 bytes either way
+  if (fp8) {
+    if (make_tensor_map_2d(&tw, a->w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a->K, a->w_rows, a->K, k_per_block, kBM) != 0) return -6;
+    if (make_tensor_map_2d(&tx, a->x, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a->K, a->M, a->K, k_per_block, kBNHalf) != 0) return -6;
+  } else {
+    const CUtensorMapDataType dt = a->dtype == ORTB200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    if (make_tensor_map_2d(&tw, a->w, dt, 2, a->K, a->w_rows, static_cast<int64_t>(a->K) * 2, kBK, kBM) != 0) return -6;
+    if (make_tensor_map_2d(&tx, a->x, dt, 2, a->K, a->M, static_cast<int64_t>(a->K) * 2, kBK, kBNHalf) != 0) return -6;
+  }
   Gemm2Params p;
-  p.M = a->M; p.N = a->N; p.K = a->K; p.num_kb = (a->K + kBK - 1) / kBK;
+  p.M = a->M; p.N = a->N; p.K = a->K; p.num_kb = (a->K + k_per_block - 1) / k_per_block;
+  p.in_fp8 = fp8 ? 1 : 0; p.k_per_block = k_per_block; p.alpha_dev = a->alpha_dev;
   const int tiles_n = (a->N + 2 * kBM - 1) / (2 * kBM);
   p.tiles_m = (a->M + kBN - 1) / kBN;
   p.tiles = tiles_n * p.tiles_m;
@@ -444,6 +469,7 @@ int launch_gemm_grouped_2cta(const ortb200_gemm_grouped_args* a, cudaStream_t st
   if (make_tensor_map_2d(&tx, a->x, dt, 2, a->K, a->rows, static_cast<int64_t>(a->K) * 2, kBK, kBNHalf) != 0) return -6;
   Gemm2Params p;
   p.M = a->rows; p.N = a->N; p.K = a->K; p.num_kb = (a->K + kBK - 1) / kBK;
+  p.in_fp8 = 0; p.k_per_block = kBK; p.alpha_dev = nullptr;
   p.tiles_m = 0; p.tiles = 0;
   p.dtype = a->dtype; p.act = a->act; p.alpha = 1.0f; p.out = a->out; p.ldo = a->N; p.bias = a->bias;
   p.residual = nullptr; p.ldr = 0; p.status = a->status;

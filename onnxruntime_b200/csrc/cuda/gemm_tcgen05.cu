@@ -50,6 +50,7 @@ struct GemmKernelParams {
   int k_per_block;    // K elements per pipeline stage: 64 (16-bit operands) or 128 (fp8)
   int act;
   float alpha;
+  const float* alpha_dev;  // optional device scalar multiplied into alpha (runtime scales: no host read)
   void* out;
   long long ldo;
   const void* bias;
@@ -356,6 +357,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
         for (int half = 0; half < (TWOM ? 2 : 1); ++half) {
           const int nrow0 = n0 + half * kBM;
           const int n = nrow0 + r;
+          const float alpha_v = p.alpha_dev ? p.alpha * __ldg(p.alpha_dev) : p.alpha;
           const float bias_v = (p.bias != nullptr && n < p.N)
                                    ? (bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.bias)[bias0 + n])
                                            : __half2float(reinterpret_cast<const __half*>(p.bias)[bias0 + n]))
@@ -384,10 +386,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
               for (int j = 0; j < GC; ++j) {
                 // no activation switch in this fully unrolled loop (it would be copied GC times): activations other
                 // than the gated one are applied on the way out, on the 16-bit value, as a separate op would
-                float y = v[j] * p.alpha + bias_v;
+                float y = v[j] * alpha_v + bias_v;
                 if (DUAL) {
                   const float g = y / (1.0f + __expf(-y));
-                  y = g * (uu[j] * p.alpha);
+                  y = g * (uu[j] * alpha_v);
                 }
                 uint16_t bits;
                 if (bf16) {
@@ -433,6 +435,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
           const int n = n0 + half * kBM + r;  // weight row == output column of this lane
           const bool n_ok = n < p.N;
           const int c_off = half * BN;        // accumulator columns of this half
+          const float alpha_v = p.alpha_dev ? p.alpha * __ldg(p.alpha_dev) : p.alpha;
           const float bias_v = (p.bias != nullptr && n_ok)
                                    ? (p.dtype == ORTB200_BF16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.bias)[n])
                                                               : __half2float(reinterpret_cast<const __half*>(p.bias)[n]))
@@ -478,10 +481,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
               for (int j = 0; j < 16; ++j) {
                 const int m = m0 + c + j;
                 if (m < p.M) {
-                  float y = v[j] * p.alpha + bias_v;
+                  float y = v[j] * alpha_v + bias_v;
                   if (DUAL) {
                     const float g = y / (1.0f + __expf(-y));
-                    y = g * (uu[j] * p.alpha);
+                    y = g * (uu[j] * alpha_v);
                   } else {
                     y = apply_act(p.act, y);
                   }
@@ -670,7 +673,8 @@ extern "C" int ortb200_gemm(const ortb200_gemm_args* a, ortb200_stream_t stream_
   // Large problems run on CTA pairs (256 x 256 tiles, cta_group::2): measured 1.3 PFLOP/s against 0.98 for the
   // single-CTA kernel on 8192 x 6144 x 4096.  Needs at least most of a wave of 74 pairs to pay off.
   const long long tiles256 = static_cast<long long>((a->M + 255) / 256) * ((a->N + 255) / 256);
-  const bool pair_ok = !dual && !fp8 && !q4 && a->rms_eps <= 0.f;
+  if (a->alpha_dev != nullptr && !fp8) return -16;  // the device-side alpha factor exists in the fp8 kernel only
+  const bool pair_ok = !dual && !q4 && a->rms_eps <= 0.f && !(fp8 && a->world > 1);  // fp8 operands run on the pair kernel too
   // world > 1 (row-parallel linear at prompt size): only the CTA-pair kernel has the epilogue that pushes the product
   // into the all-reduce scatter areas; the reduction kernel is launched right behind it
   if (a->force_tile_rows == 512 || (a->world > 1 && pair_ok) ||
@@ -709,7 +713,7 @@ extern "C" int ortb200_gemm(const ortb200_gemm_args* a, ortb200_stream_t stream_
   p.num_kb = num_kb; p.tiles = static_cast<int>(tiles); p.tiles_m = tiles_m;
   p.tile_info = nullptr; p.num_tiles = nullptr; p.tiles_n = 0; p.w_rows_per_expert = 0;
   p.tile_aligned = tile_aligned ? 1 : 0; p.max_contrib = max_contrib;
-  p.dual_offset = a->dual_offset; p.dtype = a->dtype; p.act = a->act; p.alpha = a->alpha;
+  p.dual_offset = a->dual_offset; p.dtype = a->dtype; p.act = a->act; p.alpha = a->alpha; p.alpha_dev = a->alpha_dev;
   p.out = a->out; p.ldo = a->ldo; p.bias = a->bias; p.residual = a->residual; p.ldr = a->ldr;
   p.counters = reinterpret_cast<unsigned int*>(a->workspace);
   p.ws = a->workspace ? reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(a->workspace) + 65536) : nullptr;
@@ -762,7 +766,7 @@ int launch_gemm_grouped_large(const ortb200_gemm_grouped_args* a, cudaStream_t s
   p.M = a->rows; p.N = a->N; p.K = a->K;
   p.num_kb = num_kb; p.tiles = 0; p.tiles_m = 0;
   p.tile_aligned = 1; p.max_contrib = 1;
-  p.dual_offset = a->dual_offset; p.dtype = a->dtype; p.in_fp8 = 0; p.k_per_block = kBK; p.act = a->act; p.alpha = 1.0f;
+  p.dual_offset = a->dual_offset; p.dtype = a->dtype; p.in_fp8 = 0; p.k_per_block = kBK; p.act = a->act; p.alpha = 1.0f; p.alpha_dev = nullptr;
   p.out = a->out; p.ldo = a->N; p.bias = a->bias; p.residual = nullptr; p.ldr = 0;
   p.counters = nullptr; p.ws = nullptr; p.status = a->status;
   p.tile_info = static_cast<const int4*>(a->tile_info);

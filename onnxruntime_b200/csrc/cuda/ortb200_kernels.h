@@ -101,6 +101,9 @@ typedef struct {
   // reduction kernel then replicates the sums with one multimem.st per 16 bytes instead of a store to every peer.
   // Null: peer stores only.
   void* mc_ptr;
+  // Optional device scalar (fp32) multiplied into alpha by the kernel: scales that only exist on the device (GemmFloat8 with
+  // runtime scale inputs) need no host read.  fp8 operand mode only; null otherwise.
+  const float* alpha_dev;
 } ortb200_gemm_args;
 
 int ortb200_gemm(const ortb200_gemm_args* args, ortb200_stream_t stream);

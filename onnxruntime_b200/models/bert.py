@@ -172,6 +172,73 @@ def build_bert(cfg: BertConfig, weights: Dict[str, np.ndarray] = None, seed: int
     return ol.make_model(graph, opset=opset).serialize()
 
 
+def build_bert_fp8(cfg: BertConfig, weights: Dict[str, np.ndarray] = None, seed: int = 0, opset: int = 17) -> bytes:
+    """The same encoder as a quantisation tool would emit it for fp8 serving (the reference serves fp8 through
+    com.microsoft GemmFloat8, onnxruntime/contrib_ops/cuda/math/gemm_float8.cc): every dense layer is
+    ``GemmFloat8(Cast_e4m3(activation), W_e4m3, bias, scaleA = 1, scaleB)`` with a per-tensor weight scale, the merged QKV
+    projection feeds ``MultiHeadAttention`` in its packed form, residual + LayerNorm are ``SkipLayerNormalization`` and
+    the GELU rides in the first FFN GEMM.  Activations (LayerNorm / GELU outputs, O(1) magnitudes) are cast to e4m3
+    directly, so scaleA is 1.  Hidden states stay fp16."""
+    import torch
+    assert cfg.dtype == "fp16", "the fp8 graph keeps fp16 hidden states"
+    w = weights if weights is not None else init_weights(cfg, seed)
+    b = _Builder(np.float16)
+    H, N, F = cfg.hidden_size, cfg.num_heads, cfg.ffn_size
+    hd = H // N
+
+    def add(name, arr):
+        b.inits.append(ol.make_tensor(name, arr))
+        return name
+
+    def fp8_weight(name: str, mat: np.ndarray):
+        """[K, N] fp16 -> e4m3 initializer + fp32 scale (amax mapped to 448)"""
+        m = torch.from_numpy(mat.astype(np.float32))
+        scale = float(m.abs().max()) / 448.0 or 1.0
+        add(name, (m / scale).to(torch.float8_e4m3fn))
+        add(name + ".scale", np.array([scale], np.float32))
+        return name, name + ".scale"
+
+    for k in ("embeddings.word", "embeddings.position", "embeddings.ln.gamma", "embeddings.ln.beta"):
+        add(k, w[k])
+    one = add("unit_scale", np.array([1.0], np.float32))
+    inputs = [ol.make_tensor_value_info("input_ids", T.INT64, ["batch", "seq"]), ol.make_tensor_value_info("attention_mask", T.INT64, ["batch", "seq"])]
+    mask32 = b.op("Cast", ["attention_mask"], to=T.INT32)
+    x3 = b.op("EmbedLayerNormalization", ["input_ids", "", "embeddings.word", "embeddings.position", "", "embeddings.ln.gamma", "embeddings.ln.beta"],
+              n_out=2, domain="com.microsoft", epsilon=cfg.layer_norm_eps)[0]
+    flat = b.const([-1, H], np.int64)
+    x = b.op("Reshape", [x3, flat])                                     # [T, H] from here on
+    shape_in = b.op("Shape", ["input_ids"])
+    packed_shape = b.op("Concat", [shape_in, b.const([N, 3, hd], np.int64)], axis=0)
+
+    def gemm8(src: str, wname: str, sname: str, bias: str, act: str = "NONE") -> str:
+        q = b.op("Cast", [src], to=T.FLOAT8E4M3FN, saturate=1)
+        return b.op("GemmFloat8", [q, wname, bias, one, sname], domain="com.microsoft", dtype=T.FLOAT16, beta=1.0, activation=act)
+
+    for i in range(cfg.num_layers):
+        p = f"layer.{i}"
+        # merged QKV with columns ordered [head, (q, k, v), head_dim]: the product is MultiHeadAttention's packed input
+        cols = np.stack([w[f"{p}.attn.{nm}.weight"].reshape(H, N, hd) for nm in ("q", "k", "v")], 2).reshape(H, 3 * H)
+        bias = np.stack([w[f"{p}.attn.{nm}.bias"].reshape(N, hd) for nm in ("q", "k", "v")], 1).reshape(3 * H)
+        wq, sq = fp8_weight(f"{p}.attn.qkv.weight", cols)
+        qkv = gemm8(x, wq, sq, add(f"{p}.attn.qkv.bias", bias.astype(np.float16)))
+        packed = b.op("Reshape", [qkv, packed_shape])
+        ctx = b.op("MultiHeadAttention", [packed, "", "", "", mask32], domain="com.microsoft", num_heads=N)
+        wo, so = fp8_weight(f"{p}.attn.o.weight", w[f"{p}.attn.o.weight"])
+        attn_out = gemm8(b.op("Reshape", [ctx, flat]), wo, so, add(f"{p}.attn.o.bias", w[f"{p}.attn.o.bias"]))
+        x = b.op("SkipLayerNormalization", [attn_out, x, add(f"{p}.attn.ln.gamma", w[f"{p}.attn.ln.gamma"]), add(f"{p}.attn.ln.beta", w[f"{p}.attn.ln.beta"])],
+                 domain="com.microsoft", epsilon=cfg.layer_norm_eps)
+        w1, s1 = fp8_weight(f"{p}.ffn.fc1.weight", w[f"{p}.ffn.fc1.weight"])
+        h = gemm8(x, w1, s1, add(f"{p}.ffn.fc1.bias", w[f"{p}.ffn.fc1.bias"]), act="GELU")
+        w2, s2 = fp8_weight(f"{p}.ffn.fc2.weight", w[f"{p}.ffn.fc2.weight"])
+        ffn_out = gemm8(h, w2, s2, add(f"{p}.ffn.fc2.bias", w[f"{p}.ffn.fc2.bias"]))
+        x = b.op("SkipLayerNormalization", [ffn_out, x, add(f"{p}.ffn.ln.gamma", w[f"{p}.ffn.ln.gamma"]), add(f"{p}.ffn.ln.beta", w[f"{p}.ffn.ln.beta"])],
+                 domain="com.microsoft", epsilon=cfg.layer_norm_eps)
+    out_shape = b.op("Concat", [shape_in, b.const([H], np.int64)], axis=0)
+    b.nodes.append(ol.make_node("Reshape", [x, out_shape], ["last_hidden_state"], name="output"))
+    graph = ol.make_graph(b.nodes, "bert_fp8", inputs, [ol.make_tensor_value_info("last_hidden_state", T.FLOAT16, ["batch", "seq", H])], b.inits)
+    return ol.make_model(graph, opset=opset).serialize()
+
+
 def reference_forward(cfg: BertConfig, w: Dict[str, np.ndarray], input_ids: np.ndarray, attention_mask: np.ndarray,
                       token_type_ids: np.ndarray = None) -> np.ndarray:
     """Plain numpy fp32 restatement of the encoder math (the oracle for the session's output)."""

@@ -55,6 +55,7 @@ class GemmArgs(ctypes.Structure):
         ("force_splits", ctypes.c_int), ("force_bn", ctypes.c_int), ("use_pdl", ctypes.c_int),
         ("world", ctypes.c_int), ("rank", ctypes.c_int), ("peers", ctypes.c_void_p * 8), ("symm_bytes", ctypes.c_int64),
         ("in_dtype", ctypes.c_int), ("rms_eps", ctypes.c_float), ("force_tile_rows", ctypes.c_int), ("mc_ptr", ctypes.c_void_p),
+        ("alpha_dev", ctypes.c_void_p),
     ]
 
 
@@ -110,7 +111,7 @@ def gemm(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
                  dtype_code(odt), ACT[act], alpha, _ptr(ws), ws.numel(), _ptr(status), force_splits, force_bn,
                  1 if use_pdl else 0, len(peers) if peers else 1, rank,
                  (ctypes.c_void_p * 8)(*(list(peers) + [None] * (8 - len(peers)))) if peers else (ctypes.c_void_p * 8)(),
-                 symm_bytes, 4 if q4 else (3 if fp8 else 0), rms_eps, force_tile_rows, mc_ptr or None)
+                 symm_bytes, 4 if q4 else (3 if fp8 else 0), rms_eps, force_tile_rows, mc_ptr or None, None)
     rc = lib().ortb200_gemm(ctypes.byref(a), ctypes.c_void_p(stream_ptr()))
     if rc != 0:
         raise RuntimeError(f"ortb200_gemm rejected its arguments (code {rc})")

@@ -249,7 +249,8 @@ def test_session_moe(T, E, k, act, fc3, bias):
     assert np.abs(c - g).max() / np.abs(c).max() < 2e-2
 
 
-@pytest.mark.parametrize("M,N,Kd", [(8, 256, 512), (200, 1024, 1024), (1024, 2048, 4096), (130, 384, 144)])
+@pytest.mark.parametrize("M,N,Kd", [(8, 256, 512), (200, 1024, 1024), (1024, 2048, 4096), (130, 384, 144),
+                                    (4096, 4096, 512), (2500, 3000, 1040)])   # the last two run on CTA pairs (kind::f8f6f4, cta_group::2)
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float16])
 def test_gemm_fp8_operands(K, M, N, Kd, out_dtype):
     torch.manual_seed(0)
@@ -383,3 +384,25 @@ def test_embed_layer_normalization_kernel(dtype, with_segment):
     np.testing.assert_allclose(np.asarray(rg[0], dtype=np.float32), np.asarray(rc[0], dtype=np.float32), rtol=tol, atol=tol)
     np.testing.assert_array_equal(rg[1], [7, 3, 5])
     np.testing.assert_allclose(np.asarray(rg[2], dtype=np.float32), np.asarray(rc[2], dtype=np.float32), rtol=tol, atol=tol)
+
+
+def test_session_gemm_float8_with_runtime_scales_needs_no_host_read():
+    """Scales that arrive as run-time inputs stay on the device: the kernel multiplies their product into alpha."""
+    import onnxruntime_b200 as ort
+    from onnxruntime_b200 import onnx_lite as ol
+    T = ol.TensorProto
+    torch.manual_seed(0)
+    M, Kd, N = 256, 512, 384
+    a8 = (torch.randn(M, Kd) * 0.5).to(torch.float8_e4m3fn)
+    w8 = (torch.randn(N, Kd) * 0.5).to(torch.float8_e4m3fn)
+    node = ol.make_node("GemmFloat8", ["a", "w", "", "sa", "sb"], ["y"], domain="com.microsoft", transB=1, dtype=T.BFLOAT16, alpha=2.0)
+    g = ol.make_graph([node], "g", [ol.make_tensor_value_info("a", T.FLOAT8E4M3FN, [M, Kd]), ol.make_tensor_value_info("sa", T.FLOAT, [1]),
+                                    ol.make_tensor_value_info("sb", T.FLOAT, [1])], [ol.make_tensor_value_info("y", T.BFLOAT16, None)],
+                      [ol.make_tensor("w", w8)])
+    sess = ort.InferenceSession(ol.make_model(g).serialize(), providers=["CUDAExecutionProvider"], enable_fallback=False)
+    for sa, sb in ((0.5, 0.25), (1.5, 0.125)):
+        before = sess.kernel_launch_count()
+        y = sess.run(None, {"a": a8.cuda(), "sa": torch.tensor([sa]).cuda(), "sb": torch.tensor([sb]).cuda()})[0]
+        assert sess.kernel_launch_count() == before + 1
+        ref = 2.0 * sa * sb * (a8.float() @ w8.float().T)
+        assert (torch.as_tensor(y).float().cpu() - ref).abs().max() / ref.abs().max() < 1e-2

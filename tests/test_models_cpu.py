@@ -107,3 +107,26 @@ def test_beam_search_finds_a_sequence_at_least_as_likely_as_greedy():
                 logits = r.step_logits.reshape(2, -1).float()
         return total
     assert (logprob(beams) >= logprob(greedy) - 1e-4).all()
+
+
+def test_fp8_bert_graph_tracks_the_fp16_graph():
+    """build_bert_fp8 (GemmFloat8 dense layers, packed MultiHeadAttention, SkipLayerNormalization) against the exporter-style
+    fp16 graph on the same weights: fp8 rounding only."""
+    import onnxruntime_b200 as ort
+    from onnxruntime_b200.models.bert import BertConfig, build_bert, build_bert_fp8, init_weights
+    cfg = BertConfig(vocab_size=100, hidden_size=64, num_layers=2, num_heads=2, ffn_size=128, max_position=32, dtype="fp16")
+    w = init_weights(cfg)
+    for k in w:
+        if k.endswith("weight"):
+            w[k] = (w[k].astype(np.float32) * 5).astype(np.float16)
+    ids = np.random.RandomState(0).randint(0, 100, (2, 16))
+    mask = np.ones((2, 16), np.int64)
+    mask[1, 10:] = 0
+    feeds = {"input_ids": ids, "attention_mask": mask}
+    a = ort.InferenceSession(build_bert(cfg, w), providers=["CPUExecutionProvider"]).run(None, feeds)[0].astype(np.float32)
+    sess = ort.InferenceSession(build_bert_fp8(cfg, w), providers=["CPUExecutionProvider"])
+    b = sess.run(None, feeds)[0].astype(np.float32)
+    valid = mask.astype(bool)
+    assert np.abs(a - b)[valid].max() < 0.3 and np.abs(a - b)[valid].mean() < 0.05
+    from helpers import op_counts
+    assert op_counts(sess)["GemmFloat8"] == 8
