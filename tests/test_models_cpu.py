@@ -112,6 +112,7 @@ def test_beam_search_finds_a_sequence_at_least_as_likely_as_greedy():
 def test_fp8_bert_graph_tracks_the_fp16_graph():
     """build_bert_fp8 (GemmFloat8 dense layers, packed MultiHeadAttention, SkipLayerNormalization) against the exporter-style
     fp16 graph on the same weights: fp8 rounding only."""
+    import numpy as np
     import onnxruntime_b200 as ort
     from onnxruntime_b200.models.bert import BertConfig, build_bert, build_bert_fp8, init_weights
     cfg = BertConfig(vocab_size=100, hidden_size=64, num_layers=2, num_heads=2, ffn_size=128, max_position=32, dtype="fp16")
