@@ -163,6 +163,8 @@ at::Tensor ConvTransposeWithNodeAttrs(const Node& node, const at::Tensor& x, con
 at::Tensor PoolWithNodeAttrs(const Node& node, at::Tensor x, bool is_max);
 void RegisterOnnxExtraKernels(KernelRegistry& r);
 void RegisterOnnxExtraKernels2(KernelRegistry& r);
+void RegisterOnnxExtraKernels3(KernelRegistry& r);
+void RegisterMlKernels(KernelRegistry& r);
 void RegisterControlFlowKernels(KernelRegistry& r);
 void RegisterCollectiveKernels(KernelRegistry& r);
 void RegisterCudaKernels(KernelRegistry& r);

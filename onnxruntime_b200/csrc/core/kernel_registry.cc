@@ -77,6 +77,8 @@ void EnsureKernelsRegistered() {
     RegisterContribKernels5(g);
     RegisterOnnxExtraKernels(g);
     RegisterOnnxExtraKernels2(g);
+    RegisterOnnxExtraKernels3(g);
+    RegisterMlKernels(g);
     RegisterControlFlowKernels(g);
     RegisterCollectiveKernels(g);
     RegisterCudaKernels(KernelRegistry::Cuda());

@@ -840,39 +840,6 @@ void RegisterContribKernels(KernelRegistry& r) {
     at::Tensor x = normed_input(ctx, 3);
     ctx.SetOutput(0, at::silu(at::matmul(x, ctx.RequiredInput(1))) * at::matmul(x, ctx.RequiredInput(2)));
   });
-  r.RegisterFn(MS, "GatherBlockQuantized", 1, kMax, [](Ctx& ctx) {
-    const Node& n = ctx.node();
-    const at::Tensor& data = ctx.RequiredInput(0);  // uint8 packed 4-bit (two per byte along last dim) or int8-ish
-    at::Tensor idx = ctx.RequiredInput(1).to(at::kLong);
-    const at::Tensor& scales = ctx.RequiredInput(2);
-    const int64_t block = n.attr_i("block_size", 128);
-    const int64_t bits = n.attr_i("bits", 4);
-    ORTB_ENFORCE_ARG(n.attr_i("gather_axis", 0) == 0, "GatherBlockQuantized supports gather_axis 0");
-    at::Tensor rows = data.index_select(0, idx.reshape({-1}).to(data.device()));
-    at::Tensor q;
-    if (bits == 4) {
-      at::Tensor b = rows.to(at::kInt);
-      q = at::stack({at::bitwise_and(b, 0xF), at::bitwise_and(at::bitwise_right_shift(b, 4), 0xF)}, -1).flatten(-2).to(at::kFloat);
-    } else {
-      q = rows.to(at::kFloat);
-    }
-    at::Tensor s = scales.index_select(0, idx.reshape({-1}).to(scales.device())).to(at::kFloat).repeat_interleave(block, -1).narrow(-1, 0, q.size(-1));
-    at::Tensor zp;
-    if (ctx.HasInput(3)) {
-      at::Tensor z = ctx.Input(3).index_select(0, idx.reshape({-1}).to(data.device()));
-      if (bits == 4 && z.scalar_type() == at::kByte) {
-        at::Tensor zi = z.to(at::kInt);
-        z = at::stack({at::bitwise_and(zi, 0xF), at::bitwise_and(at::bitwise_right_shift(zi, 4), 0xF)}, -1).flatten(-2);
-      }
-      zp = z.to(at::kFloat).repeat_interleave(block, -1).narrow(-1, 0, q.size(-1));
-    } else {
-      zp = at::full({1}, static_cast<double>(1 << (bits - 1)), q.options());
-    }
-    at::Tensor y = ((q - zp) * s).to(scales.scalar_type());
-    std::vector<int64_t> shape(idx.sizes().begin(), idx.sizes().end());
-    shape.push_back(y.size(-1));
-    ctx.SetOutput(0, y.reshape(shape));
-  });
 }
 
 }  // namespace ortb

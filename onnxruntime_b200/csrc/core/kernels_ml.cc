@@ -1,0 +1,421 @@
+// ai.onnx.ml operators (numeric forms): tree ensembles, linear models, SVM regression, feature transforms.
+// Reference kernels: onnxruntime/core/providers/cpu/ml/ (tree_ensemble_*.cc, linearclassifier.cc, linearregressor.cc,
+// svmregressor.cc, scaler.cc, normalizer.cc, binarizer.cc, imputer.cc, onehotencoder.cc, array_feature_extractor.cc,
+// feature_vectorizer.cc; score post-processing: ml_common.h).  These models are small and branchy: they run on the host
+// in double precision, whatever device the session uses.  String labels / map types are not tensor types here.
+#include <ATen/ATen.h>
+
+#include <algorithm>
+#include <cmath>
+#include <limits>
+#include <map>
+
+#include "kernel.h"
+
+namespace ortb {
+
+namespace {
+
+using Ctx = OpKernelContext;
+constexpr int kMax = 1 << 30;
+constexpr const char* ML = "ai.onnx.ml";
+
+enum class Post { NONE, SOFTMAX, LOGISTIC, SOFTMAX_ZERO, PROBIT };
+
+Post ParsePost(const std::string& s) {
+  if (s == "SOFTMAX") return Post::SOFTMAX;
+  if (s == "LOGISTIC") return Post::LOGISTIC;
+  if (s == "SOFTMAX_ZERO") return Post::SOFTMAX_ZERO;
+  if (s == "PROBIT") return Post::PROBIT;
+  ORTB_ENFORCE_ARG(s.empty() || s == "NONE", "unknown post_transform '", s, "'");
+  return Post::NONE;
+}
+
+double Logistic(double x) { return 1.0 / (1.0 + std::exp(-x)); }
+
+// inverse of the standard normal CDF (Winitzki's approximation of erfinv, the form the reference uses)
+double Probit(double p) {
+  const double x = 2.0 * p - 1.0, sgn = x < 0 ? -1.0 : 1.0;
+  const double ln = std::log((1.0 - x) * (1.0 + x));
+  const double a = 0.147, t = 2.0 / (M_PI * a) + 0.5 * ln;
+  return 1.41421356 * sgn * std::sqrt(std::sqrt(t * t - ln / a) - t);
+}
+
+// scores of one sample -> transformed scores (ml_common.h write_scores).  add_second_class: -1 none; 0 / 1 = a single
+// score from all-positive weights becomes [1 - s, s]; 2 / 3 = from mixed weights becomes [-s, s].
+std::vector<double> PostProcess(std::vector<double> s, Post post, int add_second_class) {
+  if (s.size() >= 2) {
+    switch (post) {
+      case Post::PROBIT:
+        for (auto& v : s) v = Probit(v);
+        break;
+      case Post::LOGISTIC:
+        for (auto& v : s) v = Logistic(v);
+        break;
+      case Post::SOFTMAX:
+      case Post::SOFTMAX_ZERO: {
+        double mx = -std::numeric_limits<double>::infinity();
+        for (double v : s) mx = std::max(mx, v);
+        double sum = 0;
+        for (auto& v : s) {
+          if (post == Post::SOFTMAX_ZERO && v == 0.0) continue;  // zeros stay zero
+          v = std::exp(v - mx);
+          sum += v;
+        }
+        for (auto& v : s)
+          if (!(post == Post::SOFTMAX_ZERO && v == 0.0)) v /= sum;
+        break;
+      }
+      case Post::NONE:
+        break;
+    }
+    return s;
+  }
+  if (s.size() == 1) {
+    if (post == Post::PROBIT) return {Probit(s[0])};
+    if (add_second_class >= 0) {
+      const double v = s[0];
+      if (post == Post::LOGISTIC) return {Logistic(-v), Logistic(v)};
+      if (add_second_class <= 1) return {1.0 - v, v};
+      return {-v, v};
+    }
+  }
+  return s;
+}
+
+at::Tensor HostDouble(const at::Tensor& t) { return t.to(at::kCPU, at::kDouble).contiguous(); }
+
+std::vector<double> AttrDoubles(const Node& n, const std::string& name) {
+  std::vector<float> f = n.attr_floats(name);
+  return std::vector<double>(f.begin(), f.end());
+}
+
+// ------------------------------------------------------------------------------------------------ tree ensembles
+struct TreeEnsemble {
+  struct TreeNode {
+    int mode = 0;  // 0 leaf, 1 <=, 2 <, 3 >=, 4 >, 5 ==, 6 !=
+    int64_t feature = 0;
+    double value = 0;
+    int64_t yes = -1, no = -1;  // indices into `nodes`
+    bool missing_true = false;
+    std::vector<std::pair<int64_t, double>> weights;  // leaf: (target or class index, weight)
+  };
+  std::vector<TreeNode> nodes;
+  std::vector<int64_t> roots;
+  int64_t n_outputs = 1;
+  int aggregate = 0;  // 0 SUM, 1 AVERAGE, 2 MIN, 3 MAX
+  Post post = Post::NONE;
+  std::vector<double> base;
+  bool weights_all_positive = true;
+
+  void Build(const Node& n, bool classifier) {
+    const char* prefix = classifier ? "class" : "target";
+    const std::vector<int64_t> tree_ids = n.attr_ints("nodes_treeids"), node_ids = n.attr_ints("nodes_nodeids"),
+                               features = n.attr_ints("nodes_featureids"), yes = n.attr_ints("nodes_truenodeids"),
+                               no = n.attr_ints("nodes_falsenodeids"), miss = n.attr_ints("nodes_missing_value_tracks_true");
+    const std::vector<double> values = AttrDoubles(n, "nodes_values");
+    const std::vector<std::string> modes = n.attr_strings("nodes_modes");
+    const size_t N = tree_ids.size();
+    ORTB_ENFORCE_ARG(node_ids.size() == N && features.size() == N && yes.size() == N && no.size() == N && values.size() == N && modes.size() == N,
+                     "tree ensemble: the nodes_* attributes differ in length");
+    static const std::map<std::string, int> mode_of = {{"LEAF", 0}, {"BRANCH_LEQ", 1}, {"BRANCH_LT", 2}, {"BRANCH_GTE", 3},
+                                                        {"BRANCH_GT", 4}, {"BRANCH_EQ", 5}, {"BRANCH_NEQ", 6}};
+    std::map<std::pair<int64_t, int64_t>, int64_t> index;
+    nodes.resize(N);
+    for (size_t i = 0; i < N; ++i) index[{tree_ids[i], node_ids[i]}] = static_cast<int64_t>(i);
+    std::vector<bool> is_child(N, false);
+    for (size_t i = 0; i < N; ++i) {
+      auto m = mode_of.find(modes[i]);
+      ORTB_ENFORCE_ARG(m != mode_of.end(), "tree ensemble: unknown node mode '", modes[i], "'");
+      TreeNode& t = nodes[i];
+      t.mode = m->second;
+      t.feature = features[i];
+      t.value = values[i];
+      t.missing_true = i < miss.size() && miss[i] != 0;
+      if (t.mode != 0) {
+        auto y = index.find({tree_ids[i], yes[i]}), f = index.find({tree_ids[i], no[i]});
+        ORTB_ENFORCE_ARG(y != index.end() && f != index.end(), "tree ensemble: a branch points to a node that does not exist");
+        t.yes = y->second;
+        t.no = f->second;
+        is_child[static_cast<size_t>(t.yes)] = is_child[static_cast<size_t>(t.no)] = true;
+      }
+    }
+    for (size_t i = 0; i < N; ++i)
+      if (!is_child[i]) roots.push_back(static_cast<int64_t>(i));
+    const std::vector<int64_t> w_tree = n.attr_ints(std::string(prefix) + "_treeids"), w_node = n.attr_ints(std::string(prefix) + "_nodeids"),
+                               w_id = n.attr_ints(std::string(prefix) + "_ids");
+    const std::vector<double> w = AttrDoubles(n, std::string(prefix) + "_weights");
+    ORTB_ENFORCE_ARG(w_tree.size() == w.size() && w_node.size() == w.size() && w_id.size() == w.size(), "tree ensemble: the leaf weight attributes differ in length");
+    for (size_t i = 0; i < w.size(); ++i) {
+      auto it = index.find({w_tree[i], w_node[i]});
+      ORTB_ENFORCE_ARG(it != index.end(), "tree ensemble: a weight belongs to a node that does not exist");
+      nodes[static_cast<size_t>(it->second)].weights.emplace_back(w_id[i], w[i]);
+      if (w[i] < 0) weights_all_positive = false;
+    }
+    const std::string agg = n.attr_s("aggregate_function", "SUM");
+    aggregate = agg == "AVERAGE" ? 1 : (agg == "MIN" ? 2 : (agg == "MAX" ? 3 : 0));
+    post = ParsePost(n.attr_s("post_transform", "NONE"));
+    base = AttrDoubles(n, "base_values");
+  }
+
+  // per-output aggregated scores of one sample (without base values)
+  void Evaluate(const double* x, int64_t n_features, std::vector<double>* out) const {
+    std::vector<bool> seen(static_cast<size_t>(n_outputs), false);
+    out->assign(static_cast<size_t>(n_outputs), 0.0);
+    for (int64_t root : roots) {
+      int64_t i = root;
+      while (nodes[static_cast<size_t>(i)].mode != 0) {
+        const TreeNode& t = nodes[static_cast<size_t>(i)];
+        ORTB_ENFORCE_ARG(t.feature >= 0 && t.feature < n_features, "tree ensemble: feature index ", t.feature, " out of range");
+        const double v = x[t.feature];
+        bool go;
+        if (std::isnan(v)) {
+          go = t.missing_true;
+        } else {
+          switch (t.mode) {
+            case 1: go = v <= t.value; break;
+            case 2: go = v < t.value; break;
+            case 3: go = v >= t.value; break;
+            case 4: go = v > t.value; break;
+            case 5: go = v == t.value; break;
+            default: go = v != t.value; break;
+          }
+        }
+        i = go ? t.yes : t.no;
+      }
+      for (auto& kv : nodes[static_cast<size_t>(i)].weights) {
+        ORTB_ENFORCE_ARG(kv.first >= 0 && kv.first < n_outputs, "tree ensemble: target / class index out of range");
+        double& acc = (*out)[static_cast<size_t>(kv.first)];
+        const bool first = !seen[static_cast<size_t>(kv.first)];
+        seen[static_cast<size_t>(kv.first)] = true;
+        if (aggregate == 2) acc = first ? kv.second : std::min(acc, kv.second);
+        else if (aggregate == 3) acc = first ? kv.second : std::max(acc, kv.second);
+        else acc += kv.second;
+      }
+    }
+    if (aggregate == 1 && !roots.empty())
+      for (auto& v : *out) v /= static_cast<double>(roots.size());
+  }
+};
+
+class TreeEnsembleKernel final : public OpKernel {
+ public:
+  TreeEnsembleKernel(const OpKernelInfo& info, bool classifier) : OpKernel(info), classifier_(classifier) {
+    const Node& n = info.node;
+    if (classifier) {
+      ORTB_ENFORCE(!n.has_attr("classlabels_strings") || n.attr_strings("classlabels_strings").empty(),
+                   "TreeEnsembleClassifier: string class labels are not supported");
+      labels_ = n.attr_ints("classlabels_int64s");
+      // weights may name fewer classes than there are labels (binary models carry the positive class only)
+      std::vector<int64_t> ids = n.attr_ints("class_ids");
+      int64_t distinct = 0;
+      for (int64_t id : ids) distinct = std::max(distinct, id + 1);
+      std::sort(ids.begin(), ids.end());
+      ids.erase(std::unique(ids.begin(), ids.end()), ids.end());
+      binary_ = labels_.size() == 2 && ids.size() == 1;
+      trees_.n_outputs = binary_ ? 1 : std::max<int64_t>(static_cast<int64_t>(labels_.size()), distinct);
+      single_id_ = ids.empty() ? 0 : ids[0];
+    } else {
+      trees_.n_outputs = n.attr_i("n_targets", 1);
+    }
+    trees_.Build(n, classifier);
+    if (binary_)  // all weights sit on one class id: fold it to output 0
+      for (auto& t : trees_.nodes)
+        for (auto& kv : t.weights) kv.first = 0;
+  }
+
+  void Compute(Ctx& ctx) const override {
+    const at::Tensor& x_in = ctx.RequiredInput(0);
+    at::Tensor x = HostDouble(x_in.dim() == 1 ? x_in.unsqueeze(0) : x_in);
+    ORTB_ENFORCE_ARG(x.dim() == 2, "tree ensemble: input must be [N, features]");
+    const int64_t N = x.size(0), F = x.size(1);
+    const int64_t n_out = classifier_ ? (binary_ ? 2 : trees_.n_outputs) : trees_.n_outputs;
+    at::Tensor scores = at::empty({N, n_out}, at::kFloat);
+    at::Tensor labels = classifier_ ? at::empty({N}, at::kLong) : at::Tensor();
+    std::vector<double> s;
+    for (int64_t i = 0; i < N; ++i) {
+      trees_.Evaluate(x.data_ptr<double>() + i * F, F, &s);
+      for (size_t k = 0; k < s.size() && k < trees_.base.size(); ++k) s[k] += trees_.base[k];
+      int add_second = -1;
+      if (classifier_) {
+        int64_t label;
+        if (binary_) {
+          const bool positive = trees_.weights_all_positive ? s[0] > 0.5 : s[0] > 0.0;
+          add_second = trees_.weights_all_positive ? (positive ? 0 : 1) : (positive ? 2 : 3);
+          label = positive ? labels_[1] : labels_[0];
+        } else {
+          const size_t best = static_cast<size_t>(std::max_element(s.begin(), s.end()) - s.begin());
+          label = best < labels_.size() ? labels_[best] : static_cast<int64_t>(best);
+        }
+        labels.data_ptr<int64_t>()[i] = label;
+      }
+      std::vector<double> z = PostProcess(s, trees_.post, add_second);
+      for (int64_t k = 0; k < n_out; ++k) scores.data_ptr<float>()[i * n_out + k] = static_cast<float>(k < static_cast<int64_t>(z.size()) ? z[static_cast<size_t>(k)] : 0.0);
+    }
+    if (classifier_) {
+      ctx.SetOutput(0, labels.to(x_in.device()));
+      if (ctx.OutputCount() > 1) ctx.SetOutput(1, scores.to(x_in.device()));
+    } else {
+      ctx.SetOutput(0, scores.to(x_in.device()));
+    }
+  }
+
+ private:
+  bool classifier_, binary_ = false;
+  TreeEnsemble trees_;
+  std::vector<int64_t> labels_;
+  int64_t single_id_ = 0;
+};
+
+// ------------------------------------------------------------------------------------------------ linear models
+void LinearImpl(Ctx& ctx, bool classifier) {
+  const Node& n = ctx.node();
+  const at::Tensor& x_in = ctx.RequiredInput(0);
+  at::Tensor x = HostDouble(x_in.dim() == 1 ? x_in.unsqueeze(0) : x_in);
+  const int64_t N = x.size(0), F = x.size(1);
+  const std::vector<double> coef = AttrDoubles(n, "coefficients"), icpt = AttrDoubles(n, "intercepts");
+  ORTB_ENFORCE_ARG(F > 0 && coef.size() % static_cast<size_t>(F) == 0, "linear model: coefficients do not match ", F, " features");
+  const int64_t rows = static_cast<int64_t>(coef.size()) / F;
+  at::Tensor W = at::tensor(coef, at::kDouble).reshape({rows, F});
+  at::Tensor s = at::matmul(x, W.t());
+  if (!icpt.empty()) s = s + at::tensor(icpt, at::kDouble).reshape({1, -1});
+  const Post post = ParsePost(n.attr_s("post_transform", "NONE"));
+  std::vector<int64_t> labels = classifier ? n.attr_ints("classlabels_ints") : std::vector<int64_t>();
+  ORTB_ENFORCE(!classifier || !n.has_attr("classlabels_strings") || n.attr_strings("classlabels_strings").empty(),
+               "LinearClassifier: string class labels are not supported");
+  const bool binary = classifier && rows == 1 && labels.size() == 2;
+  const int64_t n_out = binary ? 2 : rows;
+  at::Tensor scores = at::empty({N, n_out}, at::kFloat);
+  at::Tensor lab = classifier ? at::empty({N}, at::kLong) : at::Tensor();
+  for (int64_t i = 0; i < N; ++i) {
+    std::vector<double> row(s.data_ptr<double>() + i * rows, s.data_ptr<double>() + (i + 1) * rows);
+    int add_second = -1;
+    if (classifier) {
+      if (binary) {
+        const bool positive = row[0] > 0;
+        add_second = positive ? 2 : 3;
+        lab.data_ptr<int64_t>()[i] = positive ? labels[1] : labels[0];
+      } else {
+        const size_t best = static_cast<size_t>(std::max_element(row.begin(), row.end()) - row.begin());
+        lab.data_ptr<int64_t>()[i] = best < labels.size() ? labels[best] : static_cast<int64_t>(best);
+      }
+    }
+    std::vector<double> z = PostProcess(row, post, add_second);
+    for (int64_t k = 0; k < n_out; ++k) scores.data_ptr<float>()[i * n_out + k] = static_cast<float>(z[static_cast<size_t>(k)]);
+  }
+  if (classifier) {
+    ctx.SetOutput(0, lab.to(x_in.device()));
+    if (ctx.OutputCount() > 1) ctx.SetOutput(1, scores.to(x_in.device()));
+  } else {
+    ctx.SetOutput(0, scores.to(x_in.device()));
+  }
+}
+
+// SVMRegressor: sum_i coef_i K(sv_i, x) + rho (support-vector form) or w . x + rho (n_supports = 0, linear kernel)
+void SvmRegressorImpl(Ctx& ctx) {
+  const Node& n = ctx.node();
+  const at::Tensor& x_in = ctx.RequiredInput(0);
+  at::Tensor x = HostDouble(x_in.dim() == 1 ? x_in.unsqueeze(0) : x_in);
+  const int64_t F = x.size(1), nsv = n.attr_i("n_supports", 0);
+  const std::vector<double> coef = AttrDoubles(n, "coefficients"), rho = AttrDoubles(n, "rho"), kp = AttrDoubles(n, "kernel_params");
+  const std::string kernel = n.attr_s("kernel_type", "LINEAR");
+  const double gamma = kp.size() > 0 ? kp[0] : 0.0, coef0 = kp.size() > 1 ? kp[1] : 0.0, degree = kp.size() > 2 ? kp[2] : 0.0;
+  auto K = [&](const at::Tensor& a, const at::Tensor& b) {  // [N, F] x [S, F] -> [N, S]
+    if (kernel == "RBF") return at::exp(-gamma * at::cdist(a, b, 2.0, 2).pow(2));
+    at::Tensor dot = at::matmul(a, b.t());
+    if (kernel == "POLY") return (gamma * dot + coef0).pow(degree);
+    if (kernel == "SIGMOID") return at::tanh(gamma * dot + coef0);
+    ORTB_ENFORCE_ARG(kernel == "LINEAR", "SVMRegressor: unknown kernel_type '", kernel, "'");
+    return dot;
+  };
+  at::Tensor y;
+  if (nsv > 0) {
+    at::Tensor sv = at::tensor(AttrDoubles(n, "support_vectors"), at::kDouble).reshape({nsv, F});
+    y = at::matmul(K(x, sv), at::tensor(coef, at::kDouble).reshape({nsv, 1}));
+  } else {
+    y = K(x, at::tensor(coef, at::kDouble).reshape({1, F}));
+  }
+  if (!rho.empty()) y = y + rho[0];
+  if (n.attr_i("one_class", 0)) y = at::where(y > 0, at::ones_like(y), -at::ones_like(y));
+  ctx.SetOutput(0, y.to(at::kFloat).to(x_in.device()));
+}
+
+at::Tensor PerFeature(const std::vector<float>& v, const at::Tensor& like) {
+  at::Tensor t = at::tensor(v, at::kFloat).to(like.device());
+  return t.numel() == 1 ? t.reshape({}) : t;
+}
+
+}  // namespace
+
+void RegisterMlKernels(KernelRegistry& r) {
+  for (bool classifier : {false, true}) {
+    KernelDef d;
+    d.domain = ML;
+    d.op_type = classifier ? "TreeEnsembleClassifier" : "TreeEnsembleRegressor";
+    d.since_min = 1;
+    d.since_max = kMax;
+    d.factory = [classifier](const OpKernelInfo& info) { return std::make_unique<TreeEnsembleKernel>(info, classifier); };
+    r.Register(std::move(d));
+  }
+  r.RegisterFn(ML, "LinearRegressor", 1, kMax, [](Ctx& ctx) { LinearImpl(ctx, false); });
+  r.RegisterFn(ML, "LinearClassifier", 1, kMax, [](Ctx& ctx) { LinearImpl(ctx, true); });
+  r.RegisterFn(ML, "SVMRegressor", 1, kMax, SvmRegressorImpl);
+  r.RegisterFn(ML, "Scaler", 1, kMax, [](Ctx& ctx) {
+    at::Tensor x = ctx.RequiredInput(0).to(at::kFloat);
+    ctx.SetOutput(0, (x - PerFeature(ctx.node().attr_floats("offset"), x)) * PerFeature(ctx.node().attr_floats("scale"), x));
+  });
+  r.RegisterFn(ML, "Normalizer", 1, kMax, [](Ctx& ctx) {
+    at::Tensor x = ctx.RequiredInput(0).to(at::kFloat);
+    const std::string norm = ctx.node().attr_s("norm", "MAX");
+    at::Tensor d = norm == "L1" ? x.abs().sum(-1, true) : (norm == "L2" ? x.pow(2).sum(-1, true).sqrt() : x.abs().amax(-1, true));
+    ctx.SetOutput(0, at::where(d == 0, x, x / d));
+  });
+  r.RegisterFn(ML, "Binarizer", 1, kMax, [](Ctx& ctx) {
+    const at::Tensor& x = ctx.RequiredInput(0);
+    ctx.SetOutput(0, (x > ctx.node().attr_f("threshold", 0.f)).to(x.scalar_type()));
+  });
+  r.RegisterFn(ML, "Imputer", 1, kMax, [](Ctx& ctx) {
+    const Node& n = ctx.node();
+    const at::Tensor& x = ctx.RequiredInput(0);
+    if (x.is_floating_point()) {
+      const float replaced = n.attr_f("replaced_value_float", 0.f);
+      at::Tensor fill = PerFeature(n.attr_floats("imputed_value_floats"), x).to(x.scalar_type());
+      at::Tensor hit = std::isnan(replaced) ? at::isnan(x) : (x == replaced);
+      ctx.SetOutput(0, at::where(hit, fill.expand_as(x), x));
+    } else {
+      std::vector<int64_t> v = n.attr_ints("imputed_value_int64s");
+      at::Tensor fill = at::tensor(v, at::kLong).to(x.device());
+      if (fill.numel() == 1) fill = fill.reshape({});
+      ctx.SetOutput(0, at::where(x == n.attr_i("replaced_value_int64", 0), fill.expand_as(x), x));
+    }
+  });
+  r.RegisterFn(ML, "OneHotEncoder", 1, kMax, [](Ctx& ctx) {
+    const Node& n = ctx.node();
+    ORTB_ENFORCE(!n.has_attr("cats_strings") || n.attr_strings("cats_strings").empty(), "OneHotEncoder: string categories are not supported");
+    const at::Tensor& x = ctx.RequiredInput(0);
+    at::Tensor cats = at::tensor(n.attr_ints("cats_int64s"), at::kLong).to(x.device());
+    at::Tensor hot = x.to(at::kLong).unsqueeze(-1) == cats;
+    if (n.attr_i("zeros", 1) == 0) ORTB_ENFORCE_ARG(hot.any(-1).all().item<bool>(), "OneHotEncoder: a value is not among the categories (zeros = 0)");
+    ctx.SetOutput(0, hot.to(at::kFloat));
+  });
+  r.RegisterFn(ML, "ArrayFeatureExtractor", 1, kMax, [](Ctx& ctx) {
+    const at::Tensor& x = ctx.RequiredInput(0);
+    at::Tensor idx = ctx.RequiredInput(1).to(x.device(), at::kLong).reshape({-1});
+    at::Tensor y = x.index_select(x.dim() - 1, idx);
+    ctx.SetOutput(0, x.dim() == 1 ? y.unsqueeze(0) : y);
+  });
+  r.RegisterFn(ML, "FeatureVectorizer", 1, kMax, [](Ctx& ctx) {
+    std::vector<at::Tensor> parts;
+    const std::vector<int64_t> dims = ctx.node().attr_ints("inputdimensions");
+    for (int i = 0; i < ctx.InputCount(); ++i) {
+      if (!ctx.HasInput(i)) continue;
+      at::Tensor t = ctx.Input(i).to(at::kFloat);
+      const int64_t width = i < static_cast<int>(dims.size()) ? dims[static_cast<size_t>(i)] : (t.dim() > 1 ? t.size(-1) : t.numel());
+      t = t.dim() <= 1 ? t.reshape({1, -1}) : t.reshape({t.size(0), -1});
+      parts.push_back(t.narrow(1, 0, std::min<int64_t>(width, t.size(1))));
+    }
+    ctx.SetOutput(0, at::cat(parts, 1));
+  });
+}
+
+}  // namespace ortb
