@@ -366,17 +366,17 @@ PYBIND11_MODULE(_core, m) {
       return py::bytes(model->Serialize());
     });
   });
-  m.def("optimize_model", [](py::bytes b, int level, const std::vector<std::string>& disabled, bool gpu) {
+  m.def("optimize_model", [](py::bytes b, int level, const std::vector<std::string>& disabled, bool gpu, int world_size) {
     std::string bytes = b;
     return Guard([&] {
       EnsureKernelsRegistered();
       auto model = Model::LoadFromBytes(std::make_shared<std::string>(bytes), "");
       std::set<std::string> dis(disabled.begin(), disabled.end());
       ConfigOptions cfg;
-      OptimizerStats st = OptimizeGraph(model->MainGraph(), level, dis, gpu, cfg, 1);
+      OptimizerStats st = OptimizeGraph(model->MainGraph(), level, dis, gpu, cfg, world_size);
       return py::make_tuple(py::bytes(model->Serialize()), st.applied);
     });
-  });
+  }, py::arg("model"), py::arg("level"), py::arg("disabled"), py::arg("gpu"), py::arg("world_size") = 1);
   m.def("infer_shapes", [](py::bytes b, bool strict) {
     std::string bytes = b;
     return Guard([&] {

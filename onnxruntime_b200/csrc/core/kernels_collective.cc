@@ -227,6 +227,11 @@ void RegisterCollectiveKernels(KernelRegistry& r) {
   r.RegisterFn(MS, "AllGather", 1, kMax, [](Ctx& ctx) {
     ctx.SetOutput(0, AllGatherAxis(ctx.session(), ctx.RequiredInput(0), ctx.node().attr_i("axis", 0)));
   });
+  // all-gather along axis 0, then MatMul (+ bias): the generic form of the fused GPU kernel
+  r.RegisterFn("com.ortb200", "AllGatherMatMul", 1, kMax, [](Ctx& ctx) {
+    at::Tensor y = at::matmul(AllGatherAxis(ctx.session(), ctx.RequiredInput(0), 0), ctx.RequiredInput(1));
+    ctx.SetOutput(0, ctx.HasInput(2) ? y + ctx.Input(2) : y);
+  });
   r.RegisterFn(MS, "AllToAll", 1, kMax, [](Ctx& ctx) { ctx.SetOutput(0, AllToAllEqual(ctx.session(), ctx.RequiredInput(0))); });
   {
     KernelDef d;

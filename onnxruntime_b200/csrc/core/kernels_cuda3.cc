@@ -914,6 +914,60 @@ class BlockFp8WeightMatMulKernel final : public WithFallback {
   mutable at::Tensor w_, blobs_;
 };
 
+// ---------------------------------------------------------------------------------------------------------------
+// com.ortb200.AllGatherMatMul: Y = concat over ranks of X_local (axis 0) @ W (+ bias) as one kernel over the session's
+// peer-mapped workspace.  Shapes the kernel does not take (or sessions without a workspace) run the generic form:
+// the process group's all-gather, then a matmul.
+class AllGatherMatMulKernel final : public WithFallback {
+ public:
+  explicit AllGatherMatMulKernel(const OpKernelInfo& info) : WithFallback(info) {
+    const at::Tensor* w = info.constant_input(1);
+    if (w && w->dim() == 2 && (w->scalar_type() == at::kHalf || w->scalar_type() == at::kBFloat16)) w_nk_ = w->t().contiguous();
+  }
+  void Compute(Ctx& ctx) const override {
+    InferenceSession* s = ctx.session();
+    const at::Tensor& x = ctx.RequiredInput(0);
+    const int world = s->world_size;
+    const bool ok = w_nk_.defined() && x.is_cuda() && x.dim() >= 2 && x.scalar_type() == w_nk_.scalar_type() && x.size(-1) == w_nk_.size(1) &&
+                    world > 1 && world <= 8 && static_cast<int>(s->symm_peers.size()) == world && x.numel() > 0 && x.size(-1) % 8 == 0 &&
+                    s->config().Get("ortb200.symm_collectives", "1") == "1" &&
+                    x.numel() / x.size(-1) <= ortb200_allgather_gemm_max_rows(world, static_cast<int>(x.size(-1)), s->symm_bytes) &&
+                    (!ctx.HasInput(2) || (ctx.Input(2).dim() == 1 && ctx.Input(2).scalar_type() == x.scalar_type()));
+    if (!ok) {
+      Fallback(ctx);
+      return;
+    }
+    at::Tensor x2 = x.reshape({-1, x.size(-1)}).contiguous();
+    std::vector<int64_t> shape = x.sizes().vec();
+    shape[0] *= world;
+    shape.back() = w_nk_.size(0);
+    at::Tensor out = at::empty({x2.size(0) * world, w_nk_.size(0)}, x.options());
+    at::Tensor bias = ctx.HasInput(2) ? ctx.Input(2).contiguous() : at::Tensor();
+    ortb200_allgather_gemm_args a{};
+    a.x_local = x2.data_ptr();
+    a.w = w_nk_.data_ptr();
+    a.bias = bias.defined() ? bias.data_ptr() : nullptr;
+    a.out = out.data_ptr();
+    a.rows_local = static_cast<int>(x2.size(0));
+    a.N = static_cast<int>(w_nk_.size(0));
+    a.K = static_cast<int>(x2.size(1));
+    a.dtype = x.scalar_type() == at::kBFloat16 ? ORTB200_BF16 : ORTB200_F16;
+    a.act = ORTB200_ACT_NONE;
+    a.world = world;
+    a.rank = s->rank;
+    for (int r = 0; r < world; ++r) a.peers[r] = s->symm_peers[r];
+    a.symm_bytes = s->symm_bytes;
+    a.status = s->StatusWord().data_ptr<int>();
+    a.use_pdl = s->config().Get("ortb200.pdl", "0") == "1" ? 1 : 0;
+    CheckLaunch(ortb200_allgather_gemm(&a, ctx.cuda_stream()), "ortb200_allgather_gemm");
+    s->AddLaunches(1);
+    ctx.SetOutput(0, out.reshape(shape));
+  }
+
+ private:
+  at::Tensor w_nk_;
+};
+
 void RegisterCudaKernels3(KernelRegistry& r) {
   Reg<MatMulNBitsKernel>(r, MS, "MatMulNBits");
   Reg<PagedAttentionKernel>(r, MS, "PagedAttention");
@@ -928,6 +982,7 @@ void RegisterCudaKernels3(KernelRegistry& r) {
   Reg<SymmCollectiveKernel>(r, MS, "AllReduce");
   Reg<SymmCollectiveKernel>(r, MS, "AllGather");
   Reg<SymmCollectiveKernel>(r, MS, "AllToAll");
+  Reg<AllGatherMatMulKernel>(r, "com.ortb200", "AllGatherMatMul");
 }
 
 }  // namespace ortb

@@ -190,6 +190,25 @@ int MatMulAllReduceFusion(PassContext& c) {
   return count;
 }
 
+// AllGather(axis 0) -> MatMul with a constant 16-bit weight  ->  com.ortb200.AllGatherMatMul, which the GPU registry runs
+// as one kernel (the shard is pushed to the peers by spare warps while the tensor cores start on the local rows).
+int AllGatherMatMulFusion(PassContext& c) {
+  Graph& g = c.g;
+  int count = 0;
+  if (c.world_size <= 1) return 0;
+  for (Node* ag : g.Nodes()) {
+    if (ag->op_type != "AllGather" || ag->domain != kMSDomain || ag->inputs.size() != 1 || ag->attr_i("axis", 0) != 0) continue;
+    Node* mm = SoleConsumer(g, ag->outputs[0]);
+    if (!mm || !mm->domain.empty() || mm->op_type != "MatMul" || mm->inputs[0] != ag->outputs[0] || !IsHalfWeight2D(g, mm->inputs[1])) continue;
+    if (g.IsGraphOutput(ag->outputs[0])) continue;
+    g.AddNode("AllGatherMatMul", {ag->inputs[0], mm->inputs[1]}, {mm->outputs[0]}, kFusedDomain, g.UniqueName("AllGatherMatMul"));
+    g.RemoveNode(mm);
+    g.RemoveNode(ag);
+    ++count;
+  }
+  return count;
+}
+
 // After MatMulAllReduceFusion: a residual Add directly behind an all-reducing GEMM is applied after the sum.
 int AllReduceResidualFusion(PassContext& c) {
   Graph& g = c.g;
@@ -380,6 +399,7 @@ void AddGpuPasses(std::vector<Pass>& v) {
   v.push_back({"NBitsSwiGLUFusion", 2, true, NBitsSwiGLUFusion});
   v.push_back({"NBitsAllReduceFusion", 2, true, NBitsAllReduceFusion});
   v.push_back({"SwiGLUFusion", 2, true, SwiGLUFusion});
+  v.push_back({"AllGatherMatMulFusion", 2, true, AllGatherMatMulFusion});
   v.push_back({"MatMulAllReduceFusion", 2, true, MatMulAllReduceFusion});
   v.push_back({"AllReduceResidualFusion", 2, true, AllReduceResidualFusion});
   v.push_back({"GemmEpilogueFusion", 2, true, GemmEpilogueFusion});

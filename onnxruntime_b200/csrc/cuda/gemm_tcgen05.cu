@@ -64,7 +64,21 @@ struct GemmKernelParams {
   const int* num_tiles;    // device scalar: token tiles in use
   int tiles_n;             // weight-row tiles per expert
   int w_rows_per_expert;
+  // all-gather fused into the GEMM (gather kernels only; see ortb200_allgather_gemm): x is sharded by rows over the
+  // ranks, every rank pushes its shard into the peers' gather areas while its own tiles already run
+  int gather_world, gather_rank;
+  int gather_rows;                 // rows of x per rank
+  int gather_tiles_per_shard;      // token tiles per shard (ceil(gather_rows / BN))
+  void* gather_peers[8];           // bases of the symmetric workspaces
+  long long gather_area_offset;    // bytes from a workspace base to its gather area of parity 0
+  long long gather_half_bytes;     // distance between the areas of the two parities
+  const void* gather_x_local;      // this rank's shard [gather_rows, K]
 };
+
+constexpr long long kGatherFlagsOffset = 65536;   // flags[src rank < 8][4096] uint32 of the symmetric workspace header
+constexpr int kGatherFlagSlot = 4095;             // the slot of a source rank that the gather kernels use
+constexpr unsigned int kGatherSpinLimit = 1u << 19;
+constexpr int kGatherThreads = 320;               // the six warps of the plain kernel + four that push the local shard
 
 __device__ __forceinline__ float apply_act(int act, float v) {
   switch (act) {
@@ -126,10 +140,36 @@ __device__ __forceinline__ int owner_of(const GemmKernelParams& p, long long u) 
   return static_cast<int>(((u + 1) * gridDim.x - 1) / U);
 }
 
-template <int BN, int STAGES, bool DUAL, bool TWOM = false>
-__global__ void __launch_bounds__(kThreads, 1)
-gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
-                    const GemmKernelParams p) {
+// Gather kernels: the t-th tile of CTA c is physical tile c + t * gridDim.x, and the physical tiles are numbered
+// token-tile-major starting with the rank's own shard, so every CTA begins with rows that are already here while
+// the other shards are still crossing NVLink.
+struct GatherTile {
+  int n0, m0, m_end, src, local;
+};
+template <int BN, int TILE_ROWS>
+__device__ __forceinline__ GatherTile gather_tile(const GemmKernelParams& p, long long vtile) {
+  const long long phys = blockIdx.x + vtile * gridDim.x;
+  const int tile_n = static_cast<int>(phys % p.tiles_n), j = static_cast<int>(phys / p.tiles_n);
+  GatherTile t;
+  t.src = (p.gather_rank + j / p.gather_tiles_per_shard) % p.gather_world;
+  t.local = (j % p.gather_tiles_per_shard) * BN;
+  t.n0 = tile_n * TILE_ROWS;
+  t.m0 = t.src * p.gather_rows + t.local;
+  t.m_end = (t.src + 1) * p.gather_rows;
+  return t;
+}
+__device__ __forceinline__ unsigned int gather_ld_acquire_sys(const unsigned int* q) {
+  unsigned int v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(q) : "memory");
+  return v;
+}
+__device__ __forceinline__ void gather_st_release_sys(unsigned int* q, unsigned int v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(q), "r"(v) : "memory");
+}
+
+template <int BN, int STAGES, bool DUAL, bool TWOM, bool GATHER>
+__device__ __forceinline__ void gemm_tcgen05_body(const CUtensorMap* tmap_w, const CUtensorMap* tmap_x, const CUtensorMap* tmap_g,
+                                                  const GemmKernelParams& p) {
   using S = GemmSmem<BN, STAGES, DUAL, TWOM>;
   constexpr bool TWO_A = S::kTwoA;
   constexpr int NBUF = S::kNumBufs;
@@ -155,11 +195,20 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
     tiles_m = *p.num_tiles;
     tiles_total = static_cast<long long>(p.tiles_n) * tiles_m;
   }
-  const WorkRange range = cta_range(p, blockIdx.x, tiles_total);
+  WorkRange range = cta_range(p, blockIdx.x, tiles_total);
+  if (GATHER) {
+    const long long mine = static_cast<long long>(blockIdx.x) < tiles_total ? (tiles_total - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    range.begin = 0;
+    range.end = mine * p.num_kb;
+  }
+  // gather kernels: header of the local symmetric workspace (word 16: epoch of the collectives, 17: CTAs done,
+  // 18: polling limit override, 20 .. 26: CTAs done with the copy to the d-th destination)
+  unsigned int* const ghdr = GATHER ? reinterpret_cast<unsigned int*>(static_cast<uint8_t*>(p.gather_peers[p.gather_rank]) + 64) : nullptr;
 
   if (threadIdx.x == 0) {
-    tma_prefetch_desc(&tmap_w);
-    tma_prefetch_desc(&tmap_x);
+    tma_prefetch_desc(tmap_w);
+    tma_prefetch_desc(tmap_x);
+    if (GATHER) tma_prefetch_desc(tmap_g);
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
@@ -189,7 +238,20 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
       const uint64_t pol_w = policy_evict_first();
       const long long total = range.end - range.begin;
       const int pre = total < STAGES ? static_cast<int>(total) : STAGES;
+      long long total_limit = total;  // 0 once a wait for another rank has run out
+      // gather kernels: where the token rows of a tile come from (own shard: the input itself; others: the gather area)
+      int x_src = 0, x_local = 0;
+      unsigned int ready = GATHER ? (1u << p.gather_rank) : 0u, g_epoch = 0;
       auto coords = [&](long long u, int* kb, int* n0, int* m0) {
+        if (GATHER) {
+          const GatherTile t = gather_tile<BN, S::kTileRows>(p, u / p.num_kb);
+          *kb = static_cast<int>(u % p.num_kb);
+          *n0 = t.n0;
+          *m0 = t.m0;
+          x_src = t.src;
+          x_local = t.local;
+          return;
+        }
         const int tile = static_cast<int>(u / p.num_kb);
         *kb = static_cast<int>(u % p.num_kb);
         *n0 = (tile / tiles_m) * S::kTileRows;
@@ -200,22 +262,56 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
           *m0 = ti.y;
         }
       };
+      // X tile of the current coords() into `dst`.  Rows of another rank are first waited for (once per source: that
+      // rank's push raises one flag here when all of its shard has arrived), with a bounded wait.
+      auto load_x = [&](uint8_t* dst, uint64_t* bar, int kb, int m0) -> bool {
+        if (!GATHER) {
+          tma_load_2d(dst, tmap_x, bar, kb * p.k_per_block, m0);
+          return true;
+        }
+        if (x_src == p.gather_rank) {
+          tma_load_2d(dst, tmap_x, bar, kb * p.k_per_block, x_local);
+          return true;
+        }
+        if (!((ready >> x_src) & 1u)) {
+          const unsigned int* f = reinterpret_cast<const unsigned int*>(static_cast<const uint8_t*>(p.gather_peers[p.gather_rank]) + kGatherFlagsOffset) +
+                                  x_src * 4096 + kGatherFlagSlot;
+          const unsigned int lim_override = *reinterpret_cast<const volatile unsigned int*>(ghdr + 2);
+          const unsigned int limit = lim_override != 0 ? lim_override : kGatherSpinLimit;
+          const unsigned int want = 2 * g_epoch + 1;
+          unsigned int spins = 0;
+          while (static_cast<int>(gather_ld_acquire_sys(f) - want) < 0) {
+            if (++spins > limit) {
+              if (p.status) atomicExch(p.status, kStatusTimeoutPeer);
+              return false;
+            }
+            __nanosleep(128);
+          }
+          fence_proxy_async();  // the rows were written with generic stores (by the peer); the copy engine reads them
+          ready |= 1u << x_src;
+        }
+        tma_load_3d(dst, tmap_g, bar, kb * p.k_per_block, m0, static_cast<int>(g_epoch & 1u));
+        return true;
+      };
       for (int i = 0; i < pre; ++i) {
         int kb, n0, m0;
         coords(range.begin + i, &kb, &n0, &m0);
         uint8_t* st = smem + i * S::kStageBytes;
         mbar_expect_tx(&full_bar[i], S::kStageBytes);
-        tma_load_2d_hint(st, &tmap_w, &full_bar[i], kb * p.k_per_block, n0, pol_w);
-        if (TWO_A) tma_load_2d_hint(st + S::kABytes, &tmap_w, &full_bar[i], kb * p.k_per_block, n0 + second_a_rows, pol_w);
+        tma_load_2d_hint(st, tmap_w, &full_bar[i], kb * p.k_per_block, n0, pol_w);
+        if (TWO_A) tma_load_2d_hint(st + S::kABytes, tmap_w, &full_bar[i], kb * p.k_per_block, n0 + second_a_rows, pol_w);
       }
       pdl_wait_prior_grids();
-      for (int i = 0; i < pre; ++i) {
+      if (GATHER) g_epoch = *reinterpret_cast<const volatile unsigned int*>(ghdr) + 1;
+      bool x_ok = true;
+      for (int i = 0; i < pre && x_ok; ++i) {
         int kb, n0, m0;
         coords(range.begin + i, &kb, &n0, &m0);
         uint8_t* st = smem + i * S::kStageBytes;
-        tma_load_2d(st + S::kABytes * (TWO_A ? 2 : 1), &tmap_x, &full_bar[i], kb * p.k_per_block, m0);
+        x_ok = load_x(st + S::kABytes * (TWO_A ? 2 : 1), &full_bar[i], kb, m0);
       }
-      for (long long i = pre; i < total; ++i) {
+      if (!x_ok) total_limit = 0;
+      for (long long i = pre; i < total_limit; ++i) {
         const int s = static_cast<int>(i % STAGES);
         const uint32_t parity = static_cast<uint32_t>((i / STAGES) - 1) & 1;
         if (!mbar_wait(&empty_bar[s], parity)) {
@@ -226,9 +322,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
         coords(range.begin + i, &kb, &n0, &m0);
         uint8_t* st = smem + s * S::kStageBytes;
         mbar_expect_tx(&full_bar[s], S::kStageBytes);
-        tma_load_2d_hint(st, &tmap_w, &full_bar[s], kb * p.k_per_block, n0, pol_w);
-        if (TWO_A) tma_load_2d_hint(st + S::kABytes, &tmap_w, &full_bar[s], kb * p.k_per_block, n0 + second_a_rows, pol_w);
-        tma_load_2d(st + S::kABytes * (TWO_A ? 2 : 1), &tmap_x, &full_bar[s], kb * p.k_per_block, m0);
+        tma_load_2d_hint(st, tmap_w, &full_bar[s], kb * p.k_per_block, n0, pol_w);
+        if (TWO_A) tma_load_2d_hint(st + S::kABytes, tmap_w, &full_bar[s], kb * p.k_per_block, n0 + second_a_rows, pol_w);
+        if (!load_x(st + S::kABytes * (TWO_A ? 2 : 1), &full_bar[s], kb, m0)) break;
       }
     }
   } else if (warp == 1) {
@@ -282,7 +378,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
       }
       if (!ok && p.status) atomicExch(p.status, kStatusTimeoutMma);
     }
-  } else {
+  } else if (warp < 6) {
     // ---------------------------------------------------------- epilogue
     const int q = warp & 3;                 // TMEM lane quarter this warp may read
     const int r = q * 32 + lane;            // lane within the tile == weight row
@@ -303,6 +399,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
         m0 = ti.y;
         m_end = ti.z;
         bias0 = ti.x * p.N;
+      }
+      if (GATHER) {
+        const GatherTile t = gather_tile<BN, S::kTileRows>(p, tile);
+        n0 = t.n0;
+        m0 = t.m0;
+        m_end = t.m_end;
       }
       const uint32_t t_lane = tmem_base + buf * S::kBufCols + (static_cast<uint32_t>(q * 32) << 16);
       if (!mbar_wait(&tmem_full_bar[buf], (seg / NBUF) & 1)) {
@@ -500,6 +602,47 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
       }
       u = seg_end;
     }
+  } else if (GATHER) {
+    // ---------------------------------------------------------- push (gather kernels: warps 6..9)
+    // This rank's shard goes into every other rank's gather area with 16-byte peer stores, one grid-strided share per
+    // CTA, while the other warps already work on the shard.  Rank r reaches the shard of rank r + d as its d-th, so
+    // the copies go out nearest consumer first (to rank - 1, then rank - 2, ...) and each destination gets its flag
+    // as soon as its copy is complete: stores, system-wide fence, a local counter per destination; the CTA that
+    // completes a copy fences again and releases this rank's flag on that destination.
+    pdl_wait_prior_grids();
+    const unsigned int epoch = *reinterpret_cast<const volatile unsigned int*>(ghdr) + 1;
+    const int pt = static_cast<int>(threadIdx.x) - 192;
+    const long long shard_bytes = static_cast<long long>(p.gather_rows) * p.K * 2;
+    const long long vecs = shard_bytes / 16;
+    const long long area = p.gather_area_offset + static_cast<long long>(epoch & 1u) * p.gather_half_bytes + p.gather_rank * shard_bytes;
+    const uint4* src = static_cast<const uint4*>(p.gather_x_local);
+    for (int d = 1; d < p.gather_world; ++d) {
+      const int dst = (p.gather_rank - d + p.gather_world) % p.gather_world;
+      uint4* to = reinterpret_cast<uint4*>(static_cast<uint8_t*>(p.gather_peers[dst]) + area);
+      // four loads in flight per thread: with one, the copy runs at a fraction of the link's rate
+      const long long step = static_cast<long long>(gridDim.x) * 128;
+      for (long long i = static_cast<long long>(blockIdx.x) * 128 + pt; i < vecs; i += 4 * step) {
+        uint4 v[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          if (i + k * step < vecs) v[k] = __ldg(src + i + k * step);
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          if (i + k * step < vecs) to[i + k * step] = v[k];
+      }
+      __threadfence_system();
+      asm volatile("bar.sync 2, 128;" ::: "memory");
+      if (pt == 0) {
+        unsigned int* counter = ghdr + 3 + d;   // words 20 .. 26 of the workspace header: CTAs done with copy d
+        if (atomicAdd(counter, 1u) == gridDim.x - 1) {
+          *counter = 0;
+          __threadfence_system();
+          unsigned int* f = reinterpret_cast<unsigned int*>(static_cast<uint8_t*>(p.gather_peers[dst]) + kGatherFlagsOffset) +
+                            p.gather_rank * 4096 + kGatherFlagSlot;
+          gather_st_release_sys(f, 2 * epoch + 1);
+        }
+      }
+    }
   }
 
   tcgen05_fence_before();
@@ -508,6 +651,31 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
     tcgen05_fence_after();
     tmem_dealloc(tmem_base, S::kTmemCols);
   }
+  if (GATHER && threadIdx.x == 0) {
+    // the CTA that finishes last closes the epoch (every CTA has read it by then)
+    const unsigned int epoch = *reinterpret_cast<const volatile unsigned int*>(ghdr) + 1;
+    if (atomicAdd(ghdr + 1, 1u) == gridDim.x - 1) {
+      ghdr[1] = 0;
+      __threadfence();
+      *reinterpret_cast<volatile unsigned int*>(ghdr) = epoch;
+    }
+  }
+}
+
+template <int BN, int STAGES, bool DUAL, bool TWOM = false>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
+                    const GemmKernelParams p) {
+  gemm_tcgen05_body<BN, STAGES, DUAL, TWOM, false>(&tmap_w, &tmap_x, nullptr, p);
+}
+
+// All-gather fused into the GEMM: tmap_x covers this rank's shard of x, tmap_g the gather areas of the local symmetric
+// workspace ([K, world * rows, 2 parities]) that the other ranks' push warps fill.
+template <int BN, int STAGES, bool TWOM>
+__global__ void __launch_bounds__(kGatherThreads, 1)
+gemm_allgather_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
+                      const __grid_constant__ CUtensorMap tmap_g, const GemmKernelParams p) {
+  gemm_tcgen05_body<BN, STAGES, false, TWOM, true>(&tmap_w, &tmap_x, &tmap_g, p);
 }
 
 // ------------------------------------------------------------------ host side
@@ -563,6 +731,34 @@ static int launch_gemm(const CUtensorMap& tw, const CUtensorMap& tx, const GemmK
   cfg.numAttrs = nattr;
   cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tw, tx, p);
   return e == cudaSuccess ? 0 : -11;
+}
+
+template <int BN, int STAGES, bool TWOM>
+static int launch_gemm_allgather(const CUtensorMap& tw, const CUtensorMap& tx, const CUtensorMap& tg, const GemmKernelParams& p, int grid,
+                                 cudaStream_t stream, bool use_pdl) {
+  using S = GemmSmem<BN, STAGES, false, TWOM>;
+  static_assert(S::kTotal <= 227 * 1024, "shared memory limit exceeded");
+  auto kern = gemm_allgather_kernel<BN, STAGES, TWOM>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal) != cudaSuccess) return -10;
+    attr_set = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid, 1, 1);
+  cfg.blockDim = dim3(kGatherThreads, 1, 1);
+  cfg.dynamicSmemBytes = S::kTotal;
+  cfg.stream = stream;
+  cudaLaunchAttribute attrs[1];
+  int nattr = 0;
+  if (use_pdl) {
+    attrs[nattr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[nattr].val.programmaticStreamSerializationAllowed = 1;
+    ++nattr;
+  }
+  cfg.attrs = attrs;
+  cfg.numAttrs = nattr;
+  return cudaLaunchKernelEx(&cfg, kern, tw, tx, tg, p) == cudaSuccess ? 0 : -11;
 }
 
 }  // namespace ortb200
@@ -629,6 +825,59 @@ int plan_gemm(int M, int N, int K, bool dual, int force_bn, int force_splits, in
   return 0;
 }
 }  // namespace
+
+extern "C" int64_t ortb200_allgather_gemm_area_offset(int64_t symm_bytes, int parity) {
+  return symm_bytes / 2 + (parity & 1) * (symm_bytes / 4) + symm_bytes / 8;
+}
+extern "C" int64_t ortb200_allgather_gemm_flag_offset(int src) {
+  return kGatherFlagsOffset + (static_cast<int64_t>(src) * 4096 + kGatherFlagSlot) * 4;
+}
+extern "C" int64_t ortb200_allgather_gemm_max_rows(int world, int K, int64_t symm_bytes) {
+  if (world < 1 || K <= 0) return 0;
+  return (symm_bytes / 8) / (static_cast<int64_t>(world) * K * 2);
+}
+
+extern "C" int ortb200_allgather_gemm(const ortb200_allgather_gemm_args* a, ortb200_stream_t stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (!a || !a->x_local || !a->w || !a->out) return -1;
+  if (a->dtype != ORTB200_BF16 && a->dtype != ORTB200_F16) return -2;
+  if (a->world < 1 || a->world > 8 || a->rank < 0 || a->rank >= a->world) return -12;
+  if (a->rows_local <= 0 || a->N <= 0 || a->K <= 0 || a->K % 8 != 0) return -3;
+  if (a->act == ORTB200_ACT_SWIGLU) return -8;
+  if ((reinterpret_cast<uintptr_t>(a->x_local) | reinterpret_cast<uintptr_t>(a->w)) & 15) return -3;
+  if (a->rows_local > ortb200_allgather_gemm_max_rows(a->world, a->K, a->symm_bytes)) return -13;
+  for (int i = 0; i < a->world; ++i)
+    if (!a->peers[i]) return -12;
+  const int bn = a->rows_local >= 256 ? 256 : 128;
+  const CUtensorMapDataType dt = a->dtype == ORTB200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  const int64_t pitch = static_cast<int64_t>(a->K) * 2;
+  CUtensorMap tw, tx, tg;
+  if (make_tensor_map_2d(&tw, a->w, dt, 2, a->K, a->N, pitch, kBK, kBM) != 0) return -6;
+  if (make_tensor_map_2d(&tx, a->x_local, dt, 2, a->K, a->rows_local, pitch, kBK, bn) != 0) return -6;
+  const uint8_t* area0 = static_cast<const uint8_t*>(a->peers[a->rank]) + ortb200_allgather_gemm_area_offset(a->symm_bytes, 0);
+  if (make_tensor_map_3d(&tg, area0, dt, 2, a->K, static_cast<int64_t>(a->world) * a->rows_local, 2, pitch, a->symm_bytes / 4, kBK, bn) != 0)
+    return -6;
+  GemmKernelParams p = {};
+  p.M = a->world * a->rows_local; p.N = a->N; p.K = a->K;
+  p.num_kb = (a->K + kBK - 1) / kBK;
+  const bool twom = bn == 256 && a->N >= 2 * kBM;   // 256 weight rows x 256 tokens per CTA tile
+  p.tiles_n = twom ? (a->N + 2 * kBM - 1) / (2 * kBM) : (a->N + kBM - 1) / kBM;
+  p.gather_tiles_per_shard = (a->rows_local + bn - 1) / bn;
+  p.tiles_m = a->world * p.gather_tiles_per_shard;
+  p.tiles = p.tiles_n * p.tiles_m;
+  p.tile_aligned = 1; p.max_contrib = 1;
+  p.dtype = a->dtype; p.in_fp8 = 0; p.k_per_block = kBK; p.act = a->act; p.alpha = 1.0f; p.alpha_dev = nullptr;
+  p.out = a->out; p.ldo = a->N; p.bias = a->bias; p.residual = nullptr; p.ldr = 0;
+  p.status = a->status;
+  p.gather_world = a->world; p.gather_rank = a->rank; p.gather_rows = a->rows_local;
+  for (int i = 0; i < 8; ++i) p.gather_peers[i] = i < a->world ? a->peers[i] : nullptr;
+  p.gather_area_offset = ortb200_allgather_gemm_area_offset(a->symm_bytes, 0);
+  p.gather_half_bytes = a->symm_bytes / 4;
+  p.gather_x_local = a->x_local;
+  if (twom) return launch_gemm_allgather<256, 3, true>(tw, tx, tg, p, num_sms(), stream, a->use_pdl != 0);
+  return bn == 256 ? launch_gemm_allgather<256, 4, false>(tw, tx, tg, p, num_sms(), stream, a->use_pdl != 0)
+                   : launch_gemm_allgather<128, 6, false>(tw, tx, tg, p, num_sms(), stream, a->use_pdl != 0);
+}
 
 extern "C" int64_t ortb200_gemm_workspace_bytes(int M, int N, int K, int act) {
   GemmPlan pl, pl128;

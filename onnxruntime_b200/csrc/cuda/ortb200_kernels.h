@@ -172,6 +172,34 @@ typedef struct {
 int64_t ortb200_gemm_chain_workspace_bytes(void);
 int ortb200_gemm_chain(const ortb200_gemm_chain_args* args, ortb200_stream_t stream);
 int64_t ortb200_gemm_workspace_bytes(int M, int N, int K, int act);
+
+// All-gather -> GEMM as one kernel: x is sharded by rows over the ranks (this rank holds x_local [rows_local, K]) and
+// out [world * rows_local, N] = act(concat over ranks of x_local @ w^T + bias) for this rank's w [N, K].  Four extra
+// warps of every CTA push the shard into the other ranks' symmetric workspaces with peer stores while the tensor-core
+// warps start on the rank's own rows; the tiles of another rank's rows wait (bounded, status word) for that rank's one
+// flag and are read from local memory by TMA, so every remote row crosses NVLink once.  The call counts as one step
+// of the collectives' epoch (all ranks must issue the same sequence of collective calls); the gather areas are the
+// result areas of ortb200_symm_collective's workspace halves, so world * rows_local * K * 2 bytes must fit in
+// symm_bytes / 8 (ortb200_allgather_gemm_max_rows).  K a multiple of 8, 16-bit types, pointers 16-byte aligned.
+typedef struct {
+  const void* x_local;
+  const void* w;
+  const void* bias;      // optional [N]
+  void* out;
+  int rows_local, N, K;
+  int dtype, act;        // act: NONE / GELU / FASTGELU / RELU / SILU / QUICKGELU
+  int world, rank;
+  void* peers[8];
+  int64_t symm_bytes;
+  int* status;
+  int use_pdl;
+} ortb200_allgather_gemm_args;
+int ortb200_allgather_gemm(const ortb200_allgather_gemm_args* args, ortb200_stream_t stream);
+int64_t ortb200_allgather_gemm_max_rows(int world, int K, int64_t symm_bytes);
+// Byte offsets inside a symmetric workspace that the kernel above uses (for tests that stand in for a peer):
+// the gather area of `parity`, and the flag word that source rank `src` raises.
+int64_t ortb200_allgather_gemm_area_offset(int64_t symm_bytes, int parity);
+int64_t ortb200_allgather_gemm_flag_offset(int src);
 // Number of kernels one ortb200_gemm call launches (always 1).
 int ortb200_gemm_last_config(int* bn, int* splits, int* stages);
 

@@ -396,6 +396,39 @@ def symm_collective(op, x, peers, rank, symm_bytes, axis=0, status=None, mc_ptr=
     return out
 
 
+class AllGatherGemmArgs(ctypes.Structure):
+    _fields_ = [("x_local", ctypes.c_void_p), ("w", ctypes.c_void_p), ("bias", ctypes.c_void_p), ("out", ctypes.c_void_p),
+                ("rows_local", ctypes.c_int), ("N", ctypes.c_int), ("K", ctypes.c_int), ("dtype", ctypes.c_int), ("act", ctypes.c_int),
+                ("world", ctypes.c_int), ("rank", ctypes.c_int), ("peers", ctypes.c_void_p * 8), ("symm_bytes", ctypes.c_int64),
+                ("status", ctypes.c_void_p), ("use_pdl", ctypes.c_int)]
+
+
+def allgather_gemm_max_rows(world, K, symm_bytes):
+    fn = lib().ortb200_allgather_gemm_max_rows
+    fn.restype = ctypes.c_int64
+    return int(fn(world, K, ctypes.c_int64(symm_bytes)))
+
+
+def allgather_gemm_offsets(symm_bytes, parity, src):
+    """(byte offset of the gather area of `parity`, byte offset of source rank `src`'s flag word) in a workspace."""
+    area, flag = lib().ortb200_allgather_gemm_area_offset, lib().ortb200_allgather_gemm_flag_offset
+    area.restype = flag.restype = ctypes.c_int64
+    return int(area(ctypes.c_int64(symm_bytes), parity)), int(flag(src))
+
+
+def allgather_gemm(x_local, w, peers, rank, symm_bytes, bias=None, act="none", status=None):
+    """concat over ranks of x_local [rows, K], times w^T ([N, K]) -> [world * rows, N], as one kernel: the shard is
+    pushed to the peers' workspaces by spare warps while the tensor-core warps start on the local rows.  All ranks call it."""
+    world = len(peers)
+    x_local, w = x_local.contiguous(), w.contiguous()
+    rows, K = x_local.shape
+    out = torch.empty(world * rows, w.shape[0], dtype=x_local.dtype, device=x_local.device)
+    a = AllGatherGemmArgs(_ptr(x_local), _ptr(w), _ptr(bias), _ptr(out), rows, w.shape[0], K, dtype_code(x_local.dtype), ACT[act], world, rank,
+                          (ctypes.c_void_p * 8)(*(list(peers) + [None] * (8 - world))), symm_bytes, _ptr(status), 0)
+    _check(lib().ortb200_allgather_gemm(ctypes.byref(a), ctypes.c_void_p(stream_ptr())), "ortb200_allgather_gemm")
+    return out
+
+
 # ---------------------------------------------------------------------------- misc
 def argmax(x):
     x = x.contiguous()

@@ -34,6 +34,13 @@ def case_collectives(info, device, out):
                           [ol.make_tensor_value_info("x", T.FLOAT, [4, 2])], [ol.make_tensor_value_info("y", T.FLOAT, None)])
         s = session(ol.make_model(g).serialize(), info, device)
         res[f"{op}{attrs.get('axis', '')}"] = torch.from_numpy(s.run(None, {"x": x})[0])
+    # the fused node's generic form: all-gather along axis 0, then MatMul + bias
+    wt = (np.arange(6, dtype=np.float32).reshape(2, 3) - 2) * 0.5
+    g = ol.make_graph([ol.make_node("AllGatherMatMul", ["x", "w", "b"], ["y"], domain="com.ortb200")], "g",
+                      [ol.make_tensor_value_info("x", T.FLOAT, [4, 2])], [ol.make_tensor_value_info("y", T.FLOAT, None)],
+                      [ol.make_tensor("w", wt), ol.make_tensor("b", np.array([1, 2, 3], np.float32))])
+    s = session(ol.make_model(g).serialize(), info, device)
+    res["AllGatherMatMul"] = torch.from_numpy(s.run(None, {"x": x})[0])
     torch.save(res, os.path.join(out, f"rank{r}.pt"))
 
 
@@ -282,6 +289,69 @@ def case_symm_collectives(info, device, out):
         ref = torch.empty_like(x)
         dist.all_to_all_single(ref, x)
         res[f"a2a_{rep}"] = bool(torch.equal(y, ref))
+    torch.cuda.synchronize()
+    res["status"] = int(status.item())
+    torch.save(res, os.path.join(out, f"rank{r}.pt"))
+
+
+def case_allgather_gemm(info, device, out):
+    """All-gather -> GEMM as one kernel against the process group's all-gather followed by a matmul, with device times
+    of both (CUDA events, max over ranks is taken by the caller)."""
+    from onnxruntime_b200.ops import _kernels as K
+    from onnxruntime_b200.parallel import symm
+    r, w = info.rank, info.world_size
+    torch.cuda.set_device(info.local_rank)
+    ws = symm.create_workspace(1 << 30)   # gather areas are an eighth of it: 8192 x 8192 bf16 rows fit
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    res = {}
+    g = torch.Generator(device="cuda").manual_seed(7 + r)
+    gw = torch.Generator(device="cuda").manual_seed(99 + r)
+    for rep in range(2):   # both parities of the gather areas
+        for rows, N, Kd, act in ((96, 384, 512, "none"), (320, 256, 1024, "gelu"), (1024, 2048, 4096, "none")):
+            x = (torch.randn(rows, Kd, device="cuda", generator=g) * 0.5).bfloat16()
+            wt = (torch.randn(N, Kd, device="cuda", generator=gw) * 0.05).bfloat16()
+            bias = torch.randn(N, device="cuda", generator=gw).bfloat16()
+            y = K.allgather_gemm(x, wt, ws.peer_ptrs, r, ws.nbytes, bias=bias, act=act, status=status)
+            parts = [torch.empty_like(x) for _ in range(w)]
+            dist.all_gather(parts, x)
+            ref = torch.cat(parts).float() @ wt.float().t() + bias.float()
+            if act == "gelu":
+                ref = torch.nn.functional.gelu(ref)
+            res[f"agg_{rep}_{rows}_{N}_{Kd}"] = float((y.float() - ref).abs().max() / ref.abs().max())
+    # timing: the shape of a sequence-parallel projection (8192 tokens in all, hidden 8192, this rank's 4096 output features)
+    rows, N, Kd = 8192 // w, 4096, 8192
+    x = (torch.randn(rows, Kd, device="cuda", generator=g) * 0.5).bfloat16()
+    wt = (torch.randn(N, Kd, device="cuda", generator=gw) * 0.05).bfloat16()
+    full = torch.empty(w * rows, Kd, dtype=torch.bfloat16, device="cuda")
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+
+    def timed(fn, iters=10):
+        for _ in range(3):
+            fn()
+        total = 0.0
+        for _ in range(iters):
+            flush.zero_()
+            dist.barrier()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            total += e0.elapsed_time(e1)
+        return total / iters
+
+    def fused():
+        return K.allgather_gemm(x, wt, ws.peer_ptrs, r, ws.nbytes, status=status)
+
+    def library():
+        dist.all_gather_into_tensor(full, x)
+        return K.gemm(full, wt)
+
+    res["ms_fused"] = timed(fused)
+    res["ms_library"] = timed(library)
+    res["ms_gemm_only"] = timed(lambda: K.gemm(full, wt))
+    res["same"] = float((fused().float() - library().float()).abs().max())
     torch.cuda.synchronize()
     res["status"] = int(status.item())
     torch.save(res, os.path.join(out, f"rank{r}.pt"))

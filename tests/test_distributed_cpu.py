@@ -36,6 +36,8 @@ def test_collective_ops(tmp_path):
         # all-to-all with equal splits along the flattened leading dimension
         expect = np.concatenate([np.split(x, 2, 0)[r] for x in xs], 0)
         np.testing.assert_array_equal(out[r]["AllToAll"].numpy(), expect)
+        wt = (np.arange(6, dtype=np.float32).reshape(2, 3) - 2) * 0.5
+        np.testing.assert_allclose(out[r]["AllGatherMatMul"].numpy(), np.concatenate(xs, 0) @ wt + np.array([1, 2, 3], np.float32), rtol=1e-6)
 
 
 def test_distributed_matmul_specs(tmp_path):

@@ -98,3 +98,17 @@ def test_llama_tp_int4_reduces_in_kernel_and_is_captured(tmp_path, n):
     for r in range(1, n):
         assert (a - out[r]["logits"]).abs().max() / a.abs().max() < 1e-6
     assert (a - ref).abs().max() / ref.abs().max() < 0.06
+
+
+@pytest.mark.parametrize("n", WORLDS)
+def test_allgather_gemm_one_kernel(tmp_path, n):
+    _need(n)
+    out = launch("allgather_gemm", "cuda", n, tmp_path)
+    for r in range(n):
+        assert out[r]["status"] == 0
+        for k, v in out[r].items():
+            if k.startswith("agg_"):
+                assert v < 2e-2, (r, k, v)
+        assert out[r]["same"] < 0.25, out[r]["same"]
+    fused, library, gemm = (max(out[r][k] for r in range(n)) for k in ("ms_fused", "ms_library", "ms_gemm_only"))
+    print(f"allgather_gemm world={n} 8192x4096x8192: fused {fused:.3f} ms, all-gather + GEMM {library:.3f} ms, GEMM alone {gemm:.3f} ms")

@@ -543,3 +543,20 @@ def test_bias_skip_layer_norm_and_gelu_approximation():
     so0.graph_optimization_level = ort.GraphOptimizationLevel.ORT_DISABLE_ALL
     exact = ort.InferenceSession(model, so0, providers=["CPUExecutionProvider"]).run(None, feeds)[0]
     np.testing.assert_allclose(approx.run(None, feeds)[0], exact, rtol=0, atol=2e-3)     # tanh form: close, not equal
+
+
+def test_allgather_matmul_fusion_on_graph_level():
+    """AllGather (axis 0) feeding a MatMul with a constant 16-bit weight becomes one node when the job has several ranks."""
+    w = (np.arange(32 * 16).reshape(32, 16) % 7 - 3).astype(np.float16)
+    nodes = [ol.make_node("AllGather", ["x"], ["g"], domain="com.microsoft", axis=0, group_size=2), ol.make_node("MatMul", ["g", "w"], ["y"])]
+    model = graph_model(nodes, [ol.make_tensor_value_info("x", T.FLOAT16, ["b", 32])], [ol.make_tensor_value_info("y", T.FLOAT16, None)],
+                        [ol.make_tensor("w", w)])
+    out, stats = C.optimize_model(model, 99, [], True, 2)
+    assert stats.get("AllGatherMatMulFusion") == 1
+    assert [(n["op_type"], n["domain"]) for n in C.model_nodes(out)] == [("AllGatherMatMul", "com.ortb200")]
+    out1, stats1 = C.optimize_model(model, 99, [], True, 1)        # a single rank keeps the pair
+    assert not stats1.get("AllGatherMatMulFusion")
+    nodes[0] = ol.make_node("AllGather", ["x"], ["g"], domain="com.microsoft", axis=1, group_size=2)   # another axis: no fusion
+    model = graph_model(nodes, [ol.make_tensor_value_info("x", T.FLOAT16, ["b", 16])], [ol.make_tensor_value_info("y", T.FLOAT16, None)],
+                        [ol.make_tensor("w", w)])
+    assert not C.optimize_model(model, 99, [], True, 2)[1].get("AllGatherMatMulFusion")
