@@ -144,8 +144,12 @@ __device__ __forceinline__ ScatterArgs make_scatter_args(const Gemm2Params& p) {
   return sc;
 }
 
+// FP8 is a compile-time switch: as a run-time branch inside the MMA loop it cost the 16-bit path a quarter of its
+// speed (8192 x 6144 x 4096 bf16: 410 us against 312 us).
+template <bool FP8>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x, const Gemm2Params p) {
+  constexpr int kKPerBlock = FP8 ? 2 * kBK : kBK;  // K elements per pipeline stage (a stage row is 128 bytes)
   using S = Smem2;
   extern __shared__ uint8_t smem_raw[];
   // the same rounding in both CTAs (the dynamic shared-memory window starts at the same offset in every CTA)
@@ -215,15 +219,15 @@ gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
           uint8_t* st = smem + s * S::kStageBytes;
           const uint32_t bar = map_to_rank(smem_u32(&full_bar[s]), 0);
           if (leader) mbar_expect_tx(&full_bar[s], 2 * S::kStageBytes);
-          tma_load_2d_pair(st, &tmap_w, bar, kb * p.k_per_block, n0);
-          tma_load_2d_pair(st + S::kABytes, &tmap_x, bar, kb * p.k_per_block, m0);
+          tma_load_2d_pair(st, &tmap_w, bar, kb * kKPerBlock, n0);
+          tma_load_2d_pair(st + S::kABytes, &tmap_x, bar, kb * kKPerBlock, m0);
         }
       }
       if (!ok && p.status) atomicExch(p.status, kStatusTimeoutProducer);
     }
   } else if (warp == 1) {
     if (leader && lane == 0) {
-      const uint32_t idesc = p.in_fp8 ? umma_idesc_e4m3(2 * kBM, kBN) : umma_idesc_f16(p.dtype == ORTB200_BF16, 2 * kBM, kBN);
+      const uint32_t idesc = FP8 ? umma_idesc_e4m3(2 * kBM, kBN) : umma_idesc_f16(p.dtype == ORTB200_BF16, 2 * kBM, kBN);
       long long it = 0;
       int seg = 0;
       bool ok = true;
@@ -247,7 +251,7 @@ gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
           const uint64_t bdesc = umma_desc_sw128(a_addr + S::kABytes);
 #pragma unroll
           for (int k = 0; k < kBK / 16; ++k) {  // 32 bytes of K per instruction: 16 16-bit or 32 8-bit elements
-            if (p.in_fp8) umma2_f8(tmem_d, adesc + 2 * k, bdesc + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            if (FP8) umma2_f8(tmem_d, adesc + 2 * k, bdesc + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
             else umma2_f16(tmem_d, adesc + 2 * k, bdesc + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
           }
           umma2_commit_both(&empty_bar[s]);
@@ -434,7 +438,8 @@ int launch_gemm_2cta(const ortb200_gemm_args* a, cudaStream_t stream) {
   if (pairs < 1) return -1;
   static bool attr_set = false;
   if (!attr_set) {
-    if (cudaFuncSetAttribute(gemm_2cta_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem2::kTotal) != cudaSuccess) return -10;
+    if (cudaFuncSetAttribute(gemm_2cta_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem2::kTotal) != cudaSuccess) return -10;
+    if (cudaFuncSetAttribute(gemm_2cta_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem2::kTotal) != cudaSuccess) return -10;
     attr_set = true;
   }
   cudaLaunchConfig_t cfg = {};
@@ -455,7 +460,7 @@ int launch_gemm_2cta(const ortb200_gemm_args* a, cudaStream_t stream) {
   }
   cfg.attrs = attrs;
   cfg.numAttrs = nattr;
-  if (cudaLaunchKernelEx(&cfg, gemm_2cta_kernel, tw, tx, p) != cudaSuccess) return -11;
+  if (cudaLaunchKernelEx(&cfg, fp8 ? gemm_2cta_kernel<true> : gemm_2cta_kernel<false>, tw, tx, p) != cudaSuccess) return -11;
   return a->world > 1 ? launch_allreduce_prescattered(a, stream) : 0;
 }
 
@@ -485,7 +490,8 @@ int launch_gemm_grouped_2cta(const ortb200_gemm_grouped_args* a, cudaStream_t st
   const int pairs = sms / 2;
   static bool attr_set = false;
   if (!attr_set) {
-    if (cudaFuncSetAttribute(gemm_2cta_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem2::kTotal) != cudaSuccess) return -10;
+    if (cudaFuncSetAttribute(gemm_2cta_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem2::kTotal) != cudaSuccess) return -10;
+    if (cudaFuncSetAttribute(gemm_2cta_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem2::kTotal) != cudaSuccess) return -10;
     attr_set = true;
   }
   cudaLaunchConfig_t cfg = {};
@@ -500,7 +506,7 @@ int launch_gemm_grouped_2cta(const ortb200_gemm_grouped_args* a, cudaStream_t st
   attrs[0].val.clusterDim.z = 1;
   cfg.attrs = attrs;
   cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, gemm_2cta_kernel, tw, tx, p) == cudaSuccess ? 0 : -11;
+  return cudaLaunchKernelEx(&cfg, gemm_2cta_kernel<false>, tw, tx, p) == cudaSuccess ? 0 : -11;
 }
 
 }  // namespace ortb200

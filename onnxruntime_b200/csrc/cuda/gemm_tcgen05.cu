@@ -329,7 +329,8 @@ __device__ __forceinline__ void gemm_tcgen05_body(const CUtensorMap* tmap_w, con
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      const uint32_t idesc = p.in_fp8 ? umma_idesc_e4m3(kBM, BN) : umma_idesc_f16(p.dtype == ORTB200_BF16, kBM, BN);
+      // the gather kernels are 16-bit only: no run-time format branch in their MMA loop
+      const uint32_t idesc = (!GATHER && p.in_fp8) ? umma_idesc_e4m3(kBM, BN) : umma_idesc_f16(p.dtype == ORTB200_BF16, kBM, BN);
       long long it = 0;
       int seg = 0;
       bool ok = true;
@@ -360,14 +361,14 @@ __device__ __forceinline__ void gemm_tcgen05_body(const CUtensorMap* tmap_w, con
           for (int k = 0; k < kBK / 16; ++k) {
             // 16 K-elements = 32 bytes: the start-address field advances by 2
             // one instruction covers 32 bytes of K in either format: 16 half-precision or 32 fp8 elements
-            if (p.in_fp8) umma_f8(tmem_d, adesc + 2 * k, bdesc + 2 * k, idesc, (!first || k > 0) ? 1u : 0u);
+            if (!GATHER && p.in_fp8) umma_f8(tmem_d, adesc + 2 * k, bdesc + 2 * k, idesc, (!first || k > 0) ? 1u : 0u);
             else umma_f16(tmem_d, adesc + 2 * k, bdesc + 2 * k, idesc, (!first || k > 0) ? 1u : 0u);
           }
           if (TWO_A) {
             const uint64_t a2desc = umma_desc_sw128(a_addr + S::kABytes);
 #pragma unroll
             for (int k = 0; k < kBK / 16; ++k) {
-              if (p.in_fp8) umma_f8(tmem_d + BN, a2desc + 2 * k, bdesc + 2 * k, idesc, (!first || k > 0) ? 1u : 0u);
+              if (!GATHER && p.in_fp8) umma_f8(tmem_d + BN, a2desc + 2 * k, bdesc + 2 * k, idesc, (!first || k > 0) ? 1u : 0u);
               else umma_f16(tmem_d + BN, a2desc + 2 * k, bdesc + 2 * k, idesc, (!first || k > 0) ? 1u : 0u);
             }
           }
