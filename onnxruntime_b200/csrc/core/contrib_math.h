@@ -43,6 +43,9 @@ at::Tensor RotaryBSNH(const at::Tensor& x, const at::Tensor& pos, const at::Tens
 // positions, 2-D / 3-D / 4-D 0-1 masks); masked positions get `filter`
 at::Tensor AttentionMaskBias(const at::Tensor& mask_index, int64_t B, int64_t S, int64_t T, float filter, at::Device dev);
 
+// LongformerAttention on projected inputs (kernels_contrib4.cc): qkv / gqkv [B, S, 3 * hidden] float -> [B, S, hidden]
+at::Tensor LongformerCore(const at::Tensor& qkv, const at::Tensor& gqkv, const at::Tensor& mask, const at::Tensor& global, int64_t N, int64_t w);
+
 struct GqaInputs {
   at::Tensor query, key, value, past_key, past_value, seqlens_k, cos_cache, sin_cache, position_ids, attention_bias,
       head_sink;

@@ -165,6 +165,7 @@ void RegisterOnnxExtraKernels(KernelRegistry& r);
 void RegisterOnnxExtraKernels2(KernelRegistry& r);
 void RegisterOnnxExtraKernels3(KernelRegistry& r);
 void RegisterMlKernels(KernelRegistry& r);
+void RegisterQOrderedKernels(KernelRegistry& r);
 void RegisterControlFlowKernels(KernelRegistry& r);
 void RegisterCollectiveKernels(KernelRegistry& r);
 void RegisterCudaKernels(KernelRegistry& r);

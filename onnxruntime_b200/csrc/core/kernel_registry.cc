@@ -79,6 +79,7 @@ void EnsureKernelsRegistered() {
     RegisterOnnxExtraKernels2(g);
     RegisterOnnxExtraKernels3(g);
     RegisterMlKernels(g);
+    RegisterQOrderedKernels(g);
     RegisterControlFlowKernels(g);
     RegisterCollectiveKernels(g);
     RegisterCudaKernels(KernelRegistry::Cuda());

@@ -220,21 +220,31 @@ void DecoderMaskedSelfImpl(Ctx& ctx) {
 void LongformerImpl(Ctx& ctx) {
   const Node& n = ctx.node();
   const at::Tensor& x = ctx.RequiredInput(0);
-  const int64_t B = x.size(0), S = x.size(1), N = n.attr_i("num_heads", 1), w = n.attr_i("window", 1);
   auto project = [&](int wi, int bi) {
     at::Tensor p = at::matmul(x, ctx.RequiredInput(wi));
     if (ctx.HasInput(bi)) p = p + ctx.Input(bi);
     return p.to(at::kFloat);
   };
-  at::Tensor qkv = project(1, 2), gqkv = project(4, 5);
+  at::Tensor y = contrib::LongformerCore(project(1, 2), project(4, 5), ctx.RequiredInput(3), ctx.RequiredInput(6), n.attr_i("num_heads", 1),
+                                         n.attr_i("window", 1));
+  ctx.SetOutput(0, y.to(x.scalar_type()).contiguous());
+}
+
+}  // namespace
+
+namespace contrib {
+// Sliding-window attention with global tokens on projected inputs: qkv / gqkv are [B, S, 3 * hidden] (float), mask is the
+// additive key mask [B, S], global marks the tokens that attend to (and are attended by) everything.  Returns [B, S, hidden].
+at::Tensor LongformerCore(const at::Tensor& qkv, const at::Tensor& gqkv, const at::Tensor& mask, const at::Tensor& global, int64_t N, int64_t w) {
+  const int64_t B = qkv.size(0), S = qkv.size(1);
   const int64_t hidden = qkv.size(2) / 3, H = hidden / N;
   auto heads = [&](const at::Tensor& t, int64_t part) {
     return t.narrow(2, part * hidden, hidden).reshape({B, S, N, H}).transpose(1, 2);  // [B, N, S, H]
   };
   const double scale = 1.0 / std::sqrt(static_cast<double>(H));
-  at::Tensor key_mask = ctx.RequiredInput(3).to(at::kFloat).reshape({B, 1, 1, S});
-  at::Tensor is_global = ctx.RequiredInput(6).to(x.device()).ne(0);                  // [B, S]
-  auto lopt = at::TensorOptions().dtype(at::kLong).device(x.device());
+  at::Tensor key_mask = mask.to(qkv.device(), at::kFloat).reshape({B, 1, 1, S});
+  at::Tensor is_global = global.to(qkv.device()).ne(0);                                // [B, S]
+  auto lopt = at::TensorOptions().dtype(at::kLong).device(qkv.device());
   at::Tensor pos = at::arange(S, lopt);
   at::Tensor in_window = (pos.unsqueeze(0) - pos.unsqueeze(1)).abs().le(w);          // [S, S]
   at::Tensor allowed = in_window.reshape({1, 1, S, S}).logical_or(is_global.reshape({B, 1, 1, S}));
@@ -245,8 +255,11 @@ void LongformerImpl(Ctx& ctx) {
   at::Tensor s_glob = at::matmul(heads(gqkv, 0) * scale, heads(gqkv, 1).transpose(-1, -2)) + key_mask;
   at::Tensor y_glob = at::matmul(at::softmax(s_glob, -1), heads(gqkv, 2));
   at::Tensor y = at::where(is_global.reshape({B, 1, S, 1}), y_glob, y_local);
-  ctx.SetOutput(0, y.transpose(1, 2).reshape({B, S, hidden}).to(x.scalar_type()).contiguous());
+  return y.transpose(1, 2).reshape({B, S, hidden});
 }
+}  // namespace contrib
+
+namespace {
 
 // GatedRelativePositionBias (contrib_ops/cuda/bert/gated_relative_position_bias.cc; WavLM): per query a pair of gates
 // from a small linear layer scales the shared relative position bias.
