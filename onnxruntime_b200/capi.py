@@ -148,11 +148,37 @@ def _is_ort_format(buf: bytes) -> bool:
     return len(buf) >= 8 and bytes(buf[4:8]) == b"ORTM"
 
 
+class _StringTensor:
+    """A tensor of strings on its way into or out of the runtime (which carries ids of its string table)."""
+
+    def __init__(self, strings: List[str], shape: Sequence[int]):
+        self.strings, self.shape = list(strings), tuple(int(d) for d in shape)
+
+    def numpy(self) -> np.ndarray:
+        out = np.empty(len(self.strings), dtype=object)
+        out[:] = self.strings
+        return out.reshape(self.shape)
+
+
+def _is_string_array(value: Any) -> bool:
+    if isinstance(value, np.ndarray):
+        if value.dtype.kind in "US":
+            return True
+        return value.dtype.kind == "O" and value.size > 0 and isinstance(value.reshape(-1)[0], (str, bytes))
+    if isinstance(value, (str, bytes)):
+        return True
+    return isinstance(value, (list, tuple)) and len(value) > 0 and isinstance(np.asarray(value, dtype=object).reshape(-1)[0], (str, bytes))
+
+
 def _to_torch(value: Any) -> torch.Tensor:
     if isinstance(value, OrtValue):
         return value._tensor
     if isinstance(value, torch.Tensor):
         return value
+    if _is_string_array(value):
+        arr = np.asarray(value, dtype=object)
+        flat = [s.decode("utf-8") if isinstance(s, bytes) else str(s) for s in arr.reshape(-1)]
+        return _StringTensor(flat, arr.shape)
     if isinstance(value, np.ndarray):
         if not value.flags.c_contiguous:
             value = np.ascontiguousarray(value)
@@ -169,6 +195,8 @@ def _to_numpy(t: Any) -> Any:
         return None
     if isinstance(t, list):
         return [_to_numpy(x) for x in t]
+    if isinstance(t, tuple) and len(t) == 3 and t[0] == "__strings__":
+        return _StringTensor(t[1], t[2]).numpy()
     t = t.detach()
     if t.is_cuda:
         t = t.cpu()

@@ -4,6 +4,7 @@
 #include <pybind11/stl.h>
 #include <torch/extension.h>
 
+#include "string_table.h"
 #include "logging.h"
 #include "executor.h"
 #include "graph.h"
@@ -47,6 +48,10 @@ std::vector<Value> ToValues(const std::vector<py::object>& objs) {
   for (auto& o : objs) {
     Value v;
     if (o.is_none()) {
+    } else if (py::hasattr(o, "strings") && py::hasattr(o, "shape") && !py::hasattr(o, "dtype")) {
+      // capi._StringTensor: strings + shape -> ids of the string table
+      v.t = InternStrings(o.attr("strings").cast<std::vector<std::string>>(), o.attr("shape").cast<std::vector<int64_t>>());
+      v.is_string = true;
     } else if (py::isinstance<py::list>(o) || py::isinstance<py::tuple>(o)) {
       v.seq = std::make_shared<std::vector<at::Tensor>>(o.cast<std::vector<at::Tensor>>());
     } else {
@@ -59,6 +64,7 @@ std::vector<Value> ToValues(const std::vector<py::object>& objs) {
 
 py::object FromValue(const Value& v) {
   if (v.seq) return py::cast(*v.seq);
+  if (v.t.defined() && v.is_string) return py::make_tuple(py::str("__strings__"), StringsOfTensor(v.t), v.t.sizes().vec());
   if (v.t.defined()) return py::cast(v.t);
   return py::none();
 }

@@ -211,6 +211,7 @@ void GraphExecutor::Build() {
     if (is_init) {
       const at::Tensor* t = graph_->GetInitializer(v.name);
       constant_slots_[s].t = g ? t->to(dev) : *t;
+      constant_slots_[s].is_string = graph_->IsStringValue(v.name);
     }
   }
 
@@ -238,6 +239,7 @@ void GraphExecutor::Build() {
                  "' is marked as supplied by the session but no value was given (add_external_initializers)");
     if (want_gpu) constant_slots_[s].t = t->is_cuda() ? *t : t->to(dev);
     else constant_slots_[s].t = t->is_cuda() ? t->cpu() : *t;
+    constant_slots_[s].is_string = graph_->IsStringValue(name);
     return s;
   };
 
@@ -403,6 +405,16 @@ void GraphExecutor::Build() {
   nvtx_ = session_->config().Get("ortb200.nvtx", "1") == "1";
 }
 
+namespace {
+bool MovesElementsOnly(const Node& n) {
+  static const std::set<std::string> ops = {"Identity", "Reshape", "Squeeze", "Unsqueeze", "Flatten", "Transpose", "Gather", "GatherElements",
+                                            "GatherND", "Concat", "Slice", "Split", "Expand", "Tile", "Where", "Compress", "Pad",
+                                            "DepthToSpace", "SpaceToDepth", "ReverseSequence", "ScatterElements", "ScatterND", "Unique",
+                                            "MemcpyToHost", "MemcpyFromHost", "Optional", "OptionalGetElement"};
+  return n.domain.empty() && ops.count(n.op_type) != 0;
+}
+}  // namespace
+
 // One node: gather its inputs from the slots, run the kernel, put the outputs back.
 void GraphExecutor::RunStep(const RunOptions& ro, const Step& st, std::vector<Value>& slots, OpKernelContext::Lookup* lookup, int node_index) {
   Profiler* prof = session_->profiler().enabled() ? &session_->profiler() : nullptr;
@@ -440,6 +452,15 @@ void GraphExecutor::RunStep(const RunOptions& ro, const Step& st, std::vector<Va
   } catch (const std::exception& e) {
     ORTB_THROW(RUNTIME_EXCEPTION, "Non-zero status code returned while running ", st.node->op_type, " node. Name:'",
                st.node->name, "' Status Message: ", e.what());
+  }
+  // operators that only move elements hand the string-ness of their data input on to their outputs
+  if (!in.empty() && MovesElementsOnly(*st.node)) {
+    bool strings = in[0].is_string;
+    if (st.node->op_type == "Where" && in.size() > 1) strings = in[1].is_string;
+    if (st.node->op_type == "Concat")
+      for (auto& v : in) strings = strings || v.is_string;
+    if (strings)
+      for (auto& v : out) v.is_string = v.t.defined();
   }
   if (dump_.any) DumpNodeIO(dump_, *st.node, in, out);
   for (size_t i = 0; i < st.out_slots.size(); ++i) {
@@ -502,6 +523,7 @@ void GraphExecutor::ExecuteSteps(const RunOptions& ro, std::vector<Value>& slots
     if (graph_->IsInitializer(name)) {
       Value v;
       v.t = *graph_->GetInitializer(name);
+      v.is_string = graph_->IsStringValue(name);
       return v;
     }
     if (outer) {

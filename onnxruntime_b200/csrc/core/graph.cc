@@ -1,4 +1,5 @@
 #include "graph.h"
+#include "string_table.h"
 
 #include <fcntl.h>
 #include <sys/mman.h>
@@ -135,7 +136,7 @@ int64_t NumElements(const std::vector<int64_t>& dims) {
 }  // namespace
 
 at::Tensor TensorFromProto(const pb::TensorProto& t, const std::string& model_dir) {
-  ORTB_ENFORCE_ARG(t.data_type != pb::STRING, "string tensors are not supported (tensor '", t.name, "')");
+  if (t.data_type == pb::STRING) return InternStrings(t.string_data, t.dims);  // ids; the caller marks the value as strings
   const at::ScalarType st = ToTorchType(t.data_type);
   const bool sub_byte = (t.data_type == pb::UINT4 || t.data_type == pb::INT4 || t.data_type == pb::FLOAT4E2M1);
   std::vector<int64_t> dims = t.dims;
@@ -288,6 +289,11 @@ std::vector<std::string> Node::attr_strings(const std::string& n) const {
   auto* a = FindAttr(*this, n);
   return a ? a->strings : std::vector<std::string>{};
 }
+bool ConstantHoldsStrings(const Node& n) {
+  if (n.has_attr("value_string") || n.has_attr("value_strings")) return true;
+  auto* a = FindAttr(n, "value");
+  return a && a->t && a->t->data_type == pb::STRING;
+}
 at::Tensor Node::attr_tensor(const std::string& n) const {
   auto* a = FindAttr(*this, n);
   if (!a || !a->t) return at::Tensor();
@@ -350,6 +356,7 @@ std::shared_ptr<Graph> Graph::FromProto(const pb::GraphProto& g, const std::map<
       out->value_info_[t.name] = vi;
     } else {
       out->initializers_[t.name] = TensorFromProto(t, model_dir);
+      if (t.data_type == pb::STRING) out->string_values_.insert(t.name);
       if (t.data_type == pb::UINT4 || t.data_type == pb::INT4 || t.data_type == pb::FLOAT4E2M1) {
         ValueInfo vi;
         vi.name = t.name;
@@ -413,6 +420,15 @@ pb::GraphProto Graph::ToProto() const {
   }
   for (auto& kv : initializers_) {
     if (pending_external_.count(kv.first) && kv.second.numel() == 0) continue;
+    if (string_values_.count(kv.first)) {
+      pb::TensorProto p;
+      p.name = kv.first;
+      p.data_type = pb::STRING;
+      p.dims = kv.second.sizes().vec();
+      p.string_data = StringsOfTensor(kv.second);
+      g.initializer.push_back(std::move(p));
+      continue;
+    }
     g.initializer.push_back(TensorToProto(kv.second, kv.first));
   }
   for (auto& v : inputs_) {
@@ -606,7 +622,7 @@ const at::Tensor* Graph::GetInitializer(const std::string& name) const {
 }
 
 const at::Tensor* Graph::GetConstant(const std::string& name) const {
-  if (name.empty() || !IsConstant(name) || pending_external_.count(name)) return nullptr;
+  if (name.empty() || !IsConstant(name) || pending_external_.count(name) || string_values_.count(name)) return nullptr;
   return GetInitializer(name);
 }
 

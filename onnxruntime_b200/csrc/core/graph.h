@@ -73,6 +73,9 @@ struct Node {
   bool has_output(size_t i) const { return i < outputs.size() && !outputs[i].empty(); }
 };
 
+// a Constant node whose value is a tensor of strings (value_string / value_strings, or a STRING tensor in `value`)
+bool ConstantHoldsStrings(const Node& n);
+
 class Graph {
  public:
   Graph() = default;
@@ -103,6 +106,9 @@ class Graph {
   void AddInitializer(const std::string& name, const at::Tensor& t);
   void RemoveInitializer(const std::string& name);
   const std::map<std::string, at::Tensor>& Initializers() const { return initializers_; }
+  // initializers that hold strings (ids of the string table); GetConstant() hides them from the graph rewrites
+  bool IsStringValue(const std::string& name) const { return string_values_.count(name) != 0; }
+  void MarkStringValue(const std::string& name) { string_values_.insert(name); }
   // names of initializers whose data is supplied by the session (external initializers)
   std::set<std::string>& PendingExternal() { return pending_external_; }
 
@@ -141,6 +147,7 @@ class Graph {
   std::vector<std::unique_ptr<Node>> nodes_;
   std::vector<std::unique_ptr<Node>> graveyard_;  // removed nodes awaiting PurgeRemoved()
   std::map<std::string, at::Tensor> initializers_;
+  std::set<std::string> string_values_;
   std::set<std::string> pending_external_;
   std::vector<ValueInfo> inputs_, outputs_;
   std::map<std::string, ValueInfo> value_info_;

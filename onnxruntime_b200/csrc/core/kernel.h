@@ -32,6 +32,7 @@ using RunOptionsRef = RunOptions;
 struct Value {
   at::Tensor t;
   std::shared_ptr<std::vector<at::Tensor>> seq;
+  bool is_string = false;  // t holds ids of the string table (string_table.h): a tensor of strings
   bool defined() const { return t.defined() || seq != nullptr; }
 };
 
@@ -74,6 +75,14 @@ class OpKernelContext {
     return in_[i].t;
   }
   const Value& InputValue(int i) const { return in_[i]; }
+  bool InputIsString(int i) const { return i < static_cast<int>(in_.size()) && in_[i].is_string; }
+  // output i is a tensor of strings: `ids` index the string table
+  void SetOutputStrings(int i, at::Tensor ids) {
+    if (i < static_cast<int>(out_.size())) {
+      out_[i].t = std::move(ids);
+      out_[i].is_string = true;
+    }
+  }
   bool OutputNeeded(int i) const { return i < static_cast<int>(out_needed_.size()) && out_needed_[i]; }
   void SetOutput(int i, at::Tensor t) {
     if (i < static_cast<int>(out_.size())) out_[i].t = std::move(t);
@@ -166,6 +175,9 @@ void RegisterOnnxExtraKernels2(KernelRegistry& r);
 void RegisterOnnxExtraKernels3(KernelRegistry& r);
 void RegisterMlKernels(KernelRegistry& r);
 void RegisterQOrderedKernels(KernelRegistry& r);
+void RegisterStringKernels(KernelRegistry& r);
+// Cast with a string on either side (kernels_string.cc); false when neither side is a string
+bool CastWithStrings(OpKernelContext& ctx, int32_t to);
 void RegisterControlFlowKernels(KernelRegistry& r);
 void RegisterCollectiveKernels(KernelRegistry& r);
 void RegisterCudaKernels(KernelRegistry& r);

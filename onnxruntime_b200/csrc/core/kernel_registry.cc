@@ -80,6 +80,7 @@ void EnsureKernelsRegistered() {
     RegisterOnnxExtraKernels3(g);
     RegisterMlKernels(g);
     RegisterQOrderedKernels(g);
+    RegisterStringKernels(g);
     RegisterControlFlowKernels(g);
     RegisterCollectiveKernels(g);
     RegisterCudaKernels(KernelRegistry::Cuda());

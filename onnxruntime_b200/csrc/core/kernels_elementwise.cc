@@ -143,10 +143,14 @@ void RegisterElementwiseKernels(KernelRegistry& r) {
     ctx.SetOutput(0, x);
   });
   r.RegisterFn("", "Cast", 1, kMax, [](Ctx& ctx) {
-    ctx.SetOutput(0, CastTo(ctx.RequiredInput(0), static_cast<int32_t>(ctx.node().attr_i("to", 1))));
+    const int32_t to = static_cast<int32_t>(ctx.node().attr_i("to", 1));
+    if (CastWithStrings(ctx, to)) return;
+    ctx.SetOutput(0, CastTo(ctx.RequiredInput(0), to));
   });
   r.RegisterFn("", "CastLike", 15, kMax, [](Ctx& ctx) {
-    ctx.SetOutput(0, CastTo(ctx.RequiredInput(0), ToOnnxType(ctx.RequiredInput(1).scalar_type())));
+    const int32_t to = ctx.InputIsString(1) ? static_cast<int32_t>(pb::STRING) : ToOnnxType(ctx.RequiredInput(1).scalar_type());
+    if (CastWithStrings(ctx, to)) return;
+    ctx.SetOutput(0, CastTo(ctx.RequiredInput(0), to));
   });
   r.RegisterFn("", "Dropout", 1, kMax, [](Ctx& ctx) {
     // inference: identity, mask of ones

@@ -11,6 +11,7 @@
 #include <map>
 
 #include "kernel.h"
+#include "string_table.h"
 
 namespace ortb {
 
@@ -391,9 +392,13 @@ void RegisterMlKernels(KernelRegistry& r) {
   });
   r.RegisterFn(ML, "OneHotEncoder", 1, kMax, [](Ctx& ctx) {
     const Node& n = ctx.node();
-    ORTB_ENFORCE(!n.has_attr("cats_strings") || n.attr_strings("cats_strings").empty(), "OneHotEncoder: string categories are not supported");
     const at::Tensor& x = ctx.RequiredInput(0);
-    at::Tensor cats = at::tensor(n.attr_ints("cats_int64s"), at::kLong).to(x.device());
+    std::vector<int64_t> cat_ids = n.attr_ints("cats_int64s");
+    if (ctx.InputIsString(0)) {  // strings are ids of the string table: compare ids
+      cat_ids.clear();
+      for (auto& s : n.attr_strings("cats_strings")) cat_ids.push_back(InternString(s));
+    }
+    at::Tensor cats = at::tensor(cat_ids, at::kLong).to(x.device());
     at::Tensor hot = x.to(at::kLong).unsqueeze(-1) == cats;
     if (n.attr_i("zeros", 1) == 0) ORTB_ENFORCE_ARG(hot.any(-1).all().item<bool>(), "OneHotEncoder: a value is not among the categories (zeros = 0)");
     ctx.SetOutput(0, hot.to(at::kFloat));

@@ -7,6 +7,7 @@
 #include <cmath>
 #include <limits>
 
+#include "string_table.h"
 #include "kernel.h"
 
 namespace ortb {
@@ -141,17 +142,31 @@ void DeformConvImpl(Ctx& ctx) {
   ctx.SetOutput(0, y.to(x_in.scalar_type()));
 }
 
-// LabelEncoder, numeric forms (int64 / float keys and values).  String tensors are not a tensor type of this runtime.
+// LabelEncoder: int64 / float / string keys and values (strings travel as ids of the string table).
 void LabelEncoderImpl(Ctx& ctx) {
   const Node& n = ctx.node();
-  ORTB_ENFORCE(!n.has_attr("keys_strings") && !n.has_attr("values_strings"), "LabelEncoder: string keys / values are not supported");
+  // strings are ids of the string table (one id per distinct string), so string keys / values are integer keys / values
+  const bool str_keys = n.has_attr("keys_strings") || n.has_attr("classes_strings"), str_vals = n.has_attr("values_strings");
+  ORTB_ENFORCE(str_keys == ctx.InputIsString(0), "LabelEncoder: string keys need a string input (and only then)");
   const at::Tensor& x = ctx.RequiredInput(0);
-  const bool int_keys = n.has_attr("keys_int64s"), int_vals = n.has_attr("values_int64s");
+  const bool int_keys = n.has_attr("keys_int64s") || str_keys, int_vals = n.has_attr("values_int64s") || str_vals || n.has_attr("classes_strings");
+  auto intern_all = [](const std::vector<std::string>& v) {
+    std::vector<int64_t> ids;
+    for (auto& s : v) ids.push_back(InternString(s));
+    return ids;
+  };
   at::Tensor keys, vals;
-  if (int_keys) keys = at::tensor(n.attr_ints("keys_int64s"), at::TensorOptions().dtype(at::kLong));
-  else keys = at::tensor(n.attr_floats("keys_floats"), at::TensorOptions().dtype(at::kFloat));
-  if (int_vals) vals = at::tensor(n.attr_ints("values_int64s"), at::TensorOptions().dtype(at::kLong));
-  else vals = at::tensor(n.attr_floats("values_floats"), at::TensorOptions().dtype(at::kFloat));
+  if (n.has_attr("classes_strings")) {  // opset 1 form: string -> its position in classes_strings
+    keys = at::tensor(intern_all(n.attr_strings("classes_strings")), at::TensorOptions().dtype(at::kLong));
+    vals = at::arange(keys.numel(), at::TensorOptions().dtype(at::kLong));
+  } else {
+    if (str_keys) keys = at::tensor(intern_all(n.attr_strings("keys_strings")), at::TensorOptions().dtype(at::kLong));
+    else if (int_keys) keys = at::tensor(n.attr_ints("keys_int64s"), at::TensorOptions().dtype(at::kLong));
+    else keys = at::tensor(n.attr_floats("keys_floats"), at::TensorOptions().dtype(at::kFloat));
+    if (str_vals) vals = at::tensor(intern_all(n.attr_strings("values_strings")), at::TensorOptions().dtype(at::kLong));
+    else if (int_vals) vals = at::tensor(n.attr_ints("values_int64s"), at::TensorOptions().dtype(at::kLong));
+    else vals = at::tensor(n.attr_floats("values_floats"), at::TensorOptions().dtype(at::kFloat));
+  }
   ORTB_ENFORCE_ARG(keys.numel() == vals.numel() && keys.numel() > 0, "LabelEncoder: keys and values must have the same, non-zero length");
   at::Tensor order = at::argsort(keys);
   keys = keys.index_select(0, order).to(x.device());
@@ -159,9 +174,12 @@ void LabelEncoderImpl(Ctx& ctx) {
   at::Tensor xq = x.to(keys.scalar_type()).reshape({-1});
   at::Tensor pos = at::searchsorted(keys, xq).clamp_max(keys.numel() - 1);
   at::Tensor hit = keys.index_select(0, pos).eq(xq);
-  at::Tensor dflt = int_vals ? at::full({1}, n.attr_i("default_int64", -1), vals.options())
-                             : at::full({1}, static_cast<double>(n.attr_f("default_float", -0.0f)), vals.options());
-  ctx.SetOutput(0, at::where(hit, vals.index_select(0, pos), dflt).reshape(x.sizes()));
+  at::Tensor dflt = str_vals ? at::full({1}, InternString(n.attr_s("default_string", "_Unused")), vals.options())
+                    : int_vals ? at::full({1}, n.attr_i("default_int64", -1), vals.options())
+                               : at::full({1}, static_cast<double>(n.attr_f("default_float", -0.0f)), vals.options());
+  at::Tensor y = at::where(hit, vals.index_select(0, pos), dflt).reshape(x.sizes());
+  if (str_vals) ctx.SetOutputStrings(0, y);
+  else ctx.SetOutput(0, y);
 }
 
 }  // namespace

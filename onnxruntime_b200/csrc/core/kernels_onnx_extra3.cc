@@ -10,6 +10,7 @@
 #include <map>
 
 #include "kernel.h"
+#include "string_table.h"
 
 namespace ortb {
 
@@ -21,14 +22,18 @@ constexpr int kMax = 1 << 30;
 // ------------------------------------------------------------------------------------------------ TfIdfVectorizer
 void TfIdfImpl(Ctx& ctx) {
   const Node& n = ctx.node();
-  ORTB_ENFORCE(!n.has_attr("pool_strings") || n.attr_strings("pool_strings").empty(), "TfIdfVectorizer: string pools are not supported");
   const at::Tensor& x_in = ctx.RequiredInput(0);
   at::Tensor x = x_in.to(at::kCPU, at::kLong).contiguous();
   ORTB_ENFORCE_ARG(x.dim() == 1 || x.dim() == 2, "TfIdfVectorizer: input must have rank 1 or 2");
   const int64_t rows = x.dim() == 2 ? x.size(0) : 1, C = x.dim() == 2 ? x.size(1) : x.size(0);
   const int64_t min_n = n.attr_i("min_gram_length", 1), max_n = n.attr_i("max_gram_length", 1), max_skip = n.attr_i("max_skip_count", 0);
   const std::string mode = n.attr_s("mode", "TF");
-  const std::vector<int64_t> starts = n.attr_ints("ngram_counts"), out_index = n.attr_ints("ngram_indexes"), pool = n.attr_ints("pool_int64s");
+  const std::vector<int64_t> starts = n.attr_ints("ngram_counts"), out_index = n.attr_ints("ngram_indexes");
+  std::vector<int64_t> pool = n.attr_ints("pool_int64s");
+  if (ctx.InputIsString(0)) {  // string tokens are ids of the string table: the pool becomes ids as well
+    pool.clear();
+    for (auto& s : n.attr_strings("pool_strings")) pool.push_back(InternString(s));
+  }
   const std::vector<float> weights = n.attr_floats("weights");
   ORTB_ENFORCE_ARG(min_n >= 1 && max_n >= min_n, "TfIdfVectorizer: bad gram lengths");
   // pool n-grams of each length -> id (position among all n-grams, the index into ngram_indexes / weights)

@@ -7,6 +7,7 @@
 #include <algorithm>
 #include <numeric>
 
+#include "string_table.h"
 #include "kernel.h"
 
 namespace ortb {
@@ -201,7 +202,12 @@ at::Tensor ScatterND(const at::Tensor& data, const at::Tensor& indices_in, const
 }
 
 at::Tensor ConstantValue(const Node& n) {
-  if (n.has_attr("value")) return n.attr_tensor("value");
+  if (n.has_attr("value")) return n.attr_tensor("value");  // a string tensor comes back as ids of the string table
+  if (n.has_attr("value_string")) return InternStrings({n.attr_s("value_string")}, {});
+  if (n.has_attr("value_strings")) {
+    const std::vector<std::string> v = n.attr_strings("value_strings");
+    return InternStrings(v, {static_cast<int64_t>(v.size())});
+  }
   if (n.has_attr("value_float")) return at::scalar_tensor(n.attr_f("value_float", 0.f), at::kFloat);
   if (n.has_attr("value_int")) return at::scalar_tensor(n.attr_i("value_int", 0), at::kLong);
   if (n.has_attr("value_floats")) return at::tensor(n.attr_floats("value_floats"), at::kFloat);
@@ -211,11 +217,18 @@ at::Tensor ConstantValue(const Node& n) {
 
 class ConstantKernel final : public OpKernel {
  public:
-  explicit ConstantKernel(const OpKernelInfo& info) : OpKernel(info) { value_ = ConstantValue(info.node).to(info.device); }
-  void Compute(Ctx& ctx) const override { ctx.SetOutput(0, value_); }
+  explicit ConstantKernel(const OpKernelInfo& info) : OpKernel(info) {
+    value_ = ConstantValue(info.node).to(info.device);
+    strings_ = ConstantHoldsStrings(info.node);
+  }
+  void Compute(Ctx& ctx) const override {
+    if (strings_) ctx.SetOutputStrings(0, value_);
+    else ctx.SetOutput(0, value_);
+  }
 
  private:
   at::Tensor value_;
+  bool strings_ = false;
 };
 
 }  // namespace

@@ -89,6 +89,7 @@ bool Foldable(const Node& n) {
   if (never.count(n.op_type)) return false;
   if (n.op_type.rfind("Distributed", 0) == 0) return false;
   if (!n.subgraphs.empty()) return false;
+  if (n.op_type == "Constant" && ConstantHoldsStrings(n)) return false;  // an initializer would lose the string flag
   return true;
 }
 

@@ -475,9 +475,13 @@ void InferenceSession::CheckDeviceStatus() {
   }
 }
 
-static void ValidateFeed(const ValueInfo& vi, const at::Tensor& t) {
+static void ValidateFeed(const ValueInfo& vi, const at::Tensor& t, bool is_string) {
   if (vi.type.which != 1) return;
-  if (vi.type.elem_type != 0) {
+  if (is_string || vi.type.elem_type == pb::STRING) {
+    if (!is_string || (vi.type.elem_type != 0 && vi.type.elem_type != pb::STRING))
+      ORTB_THROW(INVALID_ARGUMENT, "Unexpected input data type. Actual: (tensor(", is_string ? "string" : pb::DataTypeName(ToOnnxType(t.scalar_type())),
+                 ")) , expected: (tensor(", pb::DataTypeName(vi.type.elem_type), ")) for input '", vi.name, "'");
+  } else if (vi.type.elem_type != 0) {
     at::ScalarType want = ToTorchType(vi.type.elem_type);
     if (want != t.scalar_type())
       ORTB_THROW(INVALID_ARGUMENT, "Unexpected input data type. Actual: (tensor(", pb::DataTypeName(ToOnnxType(t.scalar_type())),
@@ -532,9 +536,10 @@ std::vector<Value> InferenceSession::RunImpl(const RunOptions& ro, const std::ve
     if (it == input_index_.end()) ORTB_THROW(INVALID_ARGUMENT, "Invalid input name: ", feed_names[i]);
     const size_t idx = it->second;
     if (feeds[i].t.defined()) {
-      if (input_info_[idx]) ValidateFeed(*input_info_[idx], feeds[i].t);
+      if (input_info_[idx]) ValidateFeed(*input_info_[idx], feeds[i].t, feeds[i].is_string);
       const c10::Device want = input_device_[idx];
       inputs[idx].t = feeds[i].t.device() == want ? feeds[i].t : feeds[i].t.to(want, /*non_blocking=*/true);
+      inputs[idx].is_string = feeds[i].is_string;
     } else {
       inputs[idx] = feeds[i];
     }

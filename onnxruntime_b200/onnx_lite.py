@@ -81,13 +81,17 @@ class Tensor:
     dims: Tuple[int, ...]
     raw: bytes = b""
     external: Optional[Dict[str, str]] = None  # location / offset / length
+    strings: Optional[List[bytes]] = None      # string tensors (data_type STRING): one entry per element
 
     def serialize(self) -> bytes:
         out = _packed_varints(1, self.dims)
         out += _f_varint(2, self.data_type)
         if self.name:
             out += _f_str(8, self.name)
-        if self.external is not None:
+        if self.strings is not None:
+            for s in self.strings:
+                out += _f_bytes(6, s)
+        elif self.external is not None:
             for k, v in self.external.items():
                 out += _f_bytes(13, _f_str(1, k) + _f_str(2, str(v)))
             out += _f_varint(14, 1)
@@ -220,7 +224,10 @@ class Model:
 
 # ------------------------------------------------------------------ helpers
 def np_dtype_to_onnx(dt) -> int:
-    return _NP_TO_ONNX[np.dtype(dt)]
+    dt = np.dtype(dt)
+    if dt.kind in "OUS":   # object / unicode / bytes arrays hold strings
+        return TensorProto.STRING
+    return _NP_TO_ONNX[dt]
 
 
 def onnx_to_np_dtype(t: int):
@@ -244,6 +251,9 @@ def make_tensor(name: str, array, data_type: Optional[int] = None) -> Tensor:
         raw = t.view(torch.uint8).numpy().tobytes() if t.numel() else b""
         return Tensor(name, dt, tuple(t.shape), raw)
     arr = np.asarray(array)
+    if arr.dtype.kind in "USO":   # strings
+        flat = [s if isinstance(s, bytes) else str(s).encode("utf-8") for s in arr.reshape(-1)]
+        return Tensor(name, TensorProto.STRING, tuple(arr.shape), b"", None, flat)
     arr = np.ascontiguousarray(arr).reshape(arr.shape)  # ascontiguousarray promotes 0-d arrays to 1-d
     dt = data_type if data_type is not None else np_dtype_to_onnx(arr.dtype)
     return Tensor(name, dt, tuple(arr.shape), arr.tobytes())
@@ -396,8 +406,11 @@ _TYPED_FIELD_DTYPES = {
 def _tensor_from_fields(fields) -> Tensor:
     name, dt, dims, raw, ext = "", 0, [], None, None
     typed: Dict[int, List] = {}
+    strings: List[bytes] = []
     for f, w, v in fields:
-        if f == 1:
+        if f == 6:
+            strings.append(bytes(v))
+        elif f == 1:
             dims += _unpack_varints(v) if w == 2 else [_signed(v)]
         elif f == 2:
             dt = v
@@ -437,7 +450,7 @@ def _tensor_from_fields(fields) -> Tensor:
                 raw = vals.astype(np.int32).tobytes()
         else:
             raw = b""
-    return Tensor(name, dt, tuple(dims), raw or b"", ext)
+    return Tensor(name, dt, tuple(dims), raw or b"", ext, strings if dt == TensorProto.STRING else None)
 
 
 def _value_info_from_bytes(buf: bytes) -> ValueInfo:

@@ -39,8 +39,10 @@ def is_ort_format(buf) -> bool:
 
 # ------------------------------------------------------------------------------------------------------- reading
 def _tensor(t: fb.Table) -> ol.Tensor:
-    if t.strings(_T_STRINGS):
-        raise ValueError(f"initializer '{t.string(_T_NAME)}' holds strings, which this runtime has no tensor type for")
+    strings = t.strings(_T_STRINGS)
+    if strings:
+        return ol.Tensor(t.string(_T_NAME), ol.TensorProto.STRING, tuple(t.scalars(_T_DIMS, "q")), b"", None,
+                         [s.encode("utf-8") if isinstance(s, str) else bytes(s) for s in strings])
     if t.scalar(_T_EXT_OFFSET, "q", -1) != -1:
         raise ValueError(f"initializer '{t.string(_T_NAME)}' lives in an external file, which is not supported for ORT-format models")
     return ol.Tensor(t.string(_T_NAME), t.scalar(_T_TYPE, "i"), tuple(t.scalars(_T_DIMS, "q")), t.bytes_(_T_RAW))
@@ -121,6 +123,9 @@ def ort_to_onnx(buf) -> ol.Model:
 def _w_tensor(t: ol.Tensor):
     if t.external is not None:
         raise ValueError(f"initializer '{t.name}' uses external data; load it before converting")
+    if t.strings is not None:
+        return [("str", t.name), None, ("vec_i64", [int(d) for d in t.dims]), ("i32", int(t.data_type)), None,
+                ("vec_str", [s.decode("utf-8") if isinstance(s, (bytes, bytearray)) else str(s) for s in t.strings])]
     return [("str", t.name), None, ("vec_i64", [int(d) for d in t.dims]), ("i32", int(t.data_type)), ("vec_u8", bytes(t.raw))]
 
 
