@@ -204,9 +204,12 @@ class TreeEnsembleKernel final : public OpKernel {
   TreeEnsembleKernel(const OpKernelInfo& info, bool classifier) : OpKernel(info), classifier_(classifier) {
     const Node& n = info.node;
     if (classifier) {
-      ORTB_ENFORCE(!n.has_attr("classlabels_strings") || n.attr_strings("classlabels_strings").empty(),
-                   "TreeEnsembleClassifier: string class labels are not supported");
       labels_ = n.attr_ints("classlabels_int64s");
+      if (n.has_attr("classlabels_strings") && !n.attr_strings("classlabels_strings").empty()) {
+        string_labels_ = true;  // labels travel as ids of the string table
+        labels_.clear();
+        for (auto& s : n.attr_strings("classlabels_strings")) labels_.push_back(InternString(s));
+      }
       // weights may name fewer classes than there are labels (binary models carry the positive class only)
       std::vector<int64_t> ids = n.attr_ints("class_ids");
       int64_t distinct = 0;
@@ -254,7 +257,8 @@ class TreeEnsembleKernel final : public OpKernel {
       for (int64_t k = 0; k < n_out; ++k) scores.data_ptr<float>()[i * n_out + k] = static_cast<float>(k < static_cast<int64_t>(z.size()) ? z[static_cast<size_t>(k)] : 0.0);
     }
     if (classifier_) {
-      ctx.SetOutput(0, labels.to(x_in.device()));
+      if (string_labels_) ctx.SetOutputStrings(0, labels);
+      else ctx.SetOutput(0, labels.to(x_in.device()));
       if (ctx.OutputCount() > 1) ctx.SetOutput(1, scores.to(x_in.device()));
     } else {
       ctx.SetOutput(0, scores.to(x_in.device()));
@@ -262,7 +266,7 @@ class TreeEnsembleKernel final : public OpKernel {
   }
 
  private:
-  bool classifier_, binary_ = false;
+  bool classifier_, binary_ = false, string_labels_ = false;
   TreeEnsemble trees_;
   std::vector<int64_t> labels_;
   int64_t single_id_ = 0;
@@ -282,8 +286,11 @@ void LinearImpl(Ctx& ctx, bool classifier) {
   if (!icpt.empty()) s = s + at::tensor(icpt, at::kDouble).reshape({1, -1});
   const Post post = ParsePost(n.attr_s("post_transform", "NONE"));
   std::vector<int64_t> labels = classifier ? n.attr_ints("classlabels_ints") : std::vector<int64_t>();
-  ORTB_ENFORCE(!classifier || !n.has_attr("classlabels_strings") || n.attr_strings("classlabels_strings").empty(),
-               "LinearClassifier: string class labels are not supported");
+  const bool string_labels = classifier && n.has_attr("classlabels_strings") && !n.attr_strings("classlabels_strings").empty();
+  if (string_labels) {
+    labels.clear();
+    for (auto& s : n.attr_strings("classlabels_strings")) labels.push_back(InternString(s));
+  }
   const bool binary = classifier && rows == 1 && labels.size() == 2;
   const int64_t n_out = binary ? 2 : rows;
   at::Tensor scores = at::empty({N, n_out}, at::kFloat);
@@ -305,7 +312,8 @@ void LinearImpl(Ctx& ctx, bool classifier) {
     for (int64_t k = 0; k < n_out; ++k) scores.data_ptr<float>()[i * n_out + k] = static_cast<float>(z[static_cast<size_t>(k)]);
   }
   if (classifier) {
-    ctx.SetOutput(0, lab.to(x_in.device()));
+    if (string_labels) ctx.SetOutputStrings(0, lab);
+    else ctx.SetOutput(0, lab.to(x_in.device()));
     if (ctx.OutputCount() > 1) ctx.SetOutput(1, scores.to(x_in.device()));
   } else {
     ctx.SetOutput(0, scores.to(x_in.device()));
@@ -341,6 +349,155 @@ void SvmRegressorImpl(Ctx& ctx) {
   ctx.SetOutput(0, y.to(at::kFloat).to(x_in.device()));
 }
 
+// [N, F] x [S, F] -> [N, S] kernel matrix (kernel_params: gamma, coef0, degree)
+at::Tensor SvmKernel(const std::string& kernel, const std::vector<double>& kp, const at::Tensor& a, const at::Tensor& b) {
+  const double gamma = kp.size() > 0 ? kp[0] : 0.0, coef0 = kp.size() > 1 ? kp[1] : 0.0, degree = kp.size() > 2 ? kp[2] : 0.0;
+  if (kernel == "RBF") return at::exp(-gamma * at::cdist(a, b, 2.0, 2).pow(2));
+  at::Tensor dot = at::matmul(a, b.t());
+  if (kernel == "POLY") return (gamma * dot + coef0).pow(degree);
+  if (kernel == "SIGMOID") return at::tanh(gamma * dot + coef0);
+  ORTB_ENFORCE_ARG(kernel == "LINEAR", "SVM: unknown kernel_type '", kernel, "'");
+  return dot;
+}
+
+// Class probabilities from pairwise probabilities r[i][j] = P(class i | class i or j): the second method of Wu, Lin and
+// Weng, "Probability estimates for multi-class classification by pairwise coupling" (2004), as in libsvm.
+std::vector<double> CouplePairwise(int64_t k, const std::vector<double>& r) {
+  std::vector<double> p(static_cast<size_t>(k), 1.0 / static_cast<double>(k)), Q(static_cast<size_t>(k * k), 0.0), Qp(static_cast<size_t>(k), 0.0);
+  auto at = [k](int64_t i, int64_t j) { return static_cast<size_t>(i * k + j); };
+  for (int64_t t = 0; t < k; ++t)
+    for (int64_t j = 0; j < k; ++j) {
+      if (j == t) continue;
+      Q[at(t, t)] += r[at(j, t)] * r[at(j, t)];
+      Q[at(t, j)] = -r[at(j, t)] * r[at(t, j)];
+    }
+  const double eps = 0.005 / static_cast<double>(k);
+  for (int iter = 0; iter < 100; ++iter) {
+    double pQp = 0;
+    for (int64_t t = 0; t < k; ++t) {
+      Qp[static_cast<size_t>(t)] = 0;
+      for (int64_t j = 0; j < k; ++j) Qp[static_cast<size_t>(t)] += Q[at(t, j)] * p[static_cast<size_t>(j)];
+      pQp += p[static_cast<size_t>(t)] * Qp[static_cast<size_t>(t)];
+    }
+    double worst = 0;
+    for (int64_t t = 0; t < k; ++t) worst = std::max(worst, std::fabs(Qp[static_cast<size_t>(t)] - pQp));
+    if (worst < eps) break;
+    for (int64_t t = 0; t < k; ++t) {
+      const double diff = (-Qp[static_cast<size_t>(t)] + pQp) / Q[at(t, t)];
+      p[static_cast<size_t>(t)] += diff;
+      pQp = (pQp + diff * (diff * Q[at(t, t)] + 2 * Qp[static_cast<size_t>(t)])) / ((1 + diff) * (1 + diff));
+      for (int64_t j = 0; j < k; ++j) {
+        Qp[static_cast<size_t>(j)] = (Qp[static_cast<size_t>(j)] + diff * Q[at(t, j)]) / (1 + diff);
+        p[static_cast<size_t>(j)] /= (1 + diff);
+      }
+    }
+  }
+  return p;
+}
+
+// SVMClassifier.  With support vectors: one-vs-one decisions d(i, j) = sum over the support vectors of class i of
+// coef[j - 1][v] K(x, v) + sum over those of class j of coef[i][v] K(x, v) + rho(i, j); d > 0 votes for i.  Scores are
+// the decisions (more than two classes), [-d, d] (two classes; logistic of both with post_transform LOGISTIC) or, with
+// prob_a / prob_b, the coupled class probabilities.  Without support vectors: one linear (kernelised) score per class.
+void SvmClassifierImpl(Ctx& ctx) {
+  const Node& n = ctx.node();
+  const at::Tensor& x_in = ctx.RequiredInput(0);
+  at::Tensor x = HostDouble(x_in.dim() == 1 ? x_in.unsqueeze(0) : x_in);
+  const int64_t N = x.size(0), F = x.size(1);
+  const std::vector<double> coef = AttrDoubles(n, "coefficients"), rho = AttrDoubles(n, "rho"), kp = AttrDoubles(n, "kernel_params"),
+                            sv = AttrDoubles(n, "support_vectors"), prob_a = AttrDoubles(n, "prob_a"), prob_b = AttrDoubles(n, "prob_b");
+  const std::vector<int64_t> per_class = n.attr_ints("vectors_per_class");
+  const std::string kernel = n.attr_s("kernel_type", "LINEAR");
+  const Post post = ParsePost(n.attr_s("post_transform", "NONE"));
+  const bool string_labels = n.has_attr("classlabels_strings") && !n.attr_strings("classlabels_strings").empty();
+  std::vector<int64_t> labels = n.attr_ints("classlabels_ints");
+  if (string_labels) {
+    labels.clear();
+    for (auto& s : n.attr_strings("classlabels_strings")) labels.push_back(InternString(s));
+  }
+  const bool all_positive = std::all_of(coef.begin(), coef.end(), [](double v) { return v >= 0; });
+  const bool svc = !sv.empty();
+  const int64_t classes = svc ? static_cast<int64_t>(per_class.size()) : std::max<int64_t>(static_cast<int64_t>(labels.size()), 1);
+  ORTB_ENFORCE_ARG(classes >= 1 && !rho.empty(), "SVMClassifier: needs classes and rho");
+  at::Tensor lab = at::empty({N}, at::kLong);
+  at::Tensor scores;
+  auto pick = [&](size_t best, double max_weight, bool have_proba) -> int64_t {
+    if (labels.size() == 2 && classes <= 2) {
+      if (!have_proba && ((all_positive && max_weight >= 0.5) || (max_weight > 0 && !all_positive))) return labels[1];
+      return labels[best];
+    }
+    if (classes <= 2) return max_weight > 0 ? (string_labels ? InternString("1") : 1) : (string_labels ? InternString("0") : 0);
+    return best < labels.size() ? labels[best] : static_cast<int64_t>(best);
+  };
+  if (!svc) {
+    ORTB_ENFORCE_ARG(static_cast<int64_t>(coef.size()) >= classes * F, "SVMClassifier: coefficients do not cover classes x features");
+    at::Tensor W = at::tensor(coef, at::kDouble).narrow(0, 0, classes * F).reshape({classes, F});
+    at::Tensor s = SvmKernel(kernel, kp, x, W) + rho[0];
+    scores = at::empty({N, classes}, at::kFloat);
+    for (int64_t i = 0; i < N; ++i) {
+      std::vector<double> row(s.data_ptr<double>() + i * classes, s.data_ptr<double>() + (i + 1) * classes);
+      const size_t best = static_cast<size_t>(std::max_element(row.begin(), row.end()) - row.begin());
+      lab.data_ptr<int64_t>()[i] = classes == 2 ? pick(best, row[best], false) : (best < labels.size() ? labels[best] : static_cast<int64_t>(best));
+      std::vector<double> z = PostProcess(row, post, -1);
+      for (int64_t c = 0; c < classes; ++c) scores.data_ptr<float>()[i * classes + c] = static_cast<float>(z[static_cast<size_t>(c)]);
+    }
+  } else {
+    int64_t V = 0;
+    std::vector<int64_t> first;
+    for (int64_t c : per_class) {
+      first.push_back(V);
+      V += c;
+    }
+    const int64_t pairs = classes * (classes - 1) / 2;
+    ORTB_ENFORCE_ARG(static_cast<int64_t>(sv.size()) == V * F && static_cast<int64_t>(coef.size()) >= (classes - 1) * V &&
+                         static_cast<int64_t>(rho.size()) >= pairs,
+                     "SVMClassifier: support_vectors / coefficients / rho do not match vectors_per_class");
+    const bool have_proba = !prob_a.empty();
+    ORTB_ENFORCE_ARG(!have_proba || (static_cast<int64_t>(prob_a.size()) >= pairs && static_cast<int64_t>(prob_b.size()) >= pairs),
+                     "SVMClassifier: prob_a / prob_b need one entry per pair of classes");
+    at::Tensor Kx = SvmKernel(kernel, kp, x, at::tensor(sv, at::kDouble).reshape({V, F})).contiguous();  // [N, V]
+    const int64_t width = have_proba ? classes : (classes > 2 ? pairs : 2);
+    scores = at::empty({N, width}, at::kFloat);
+    std::vector<double> dec(static_cast<size_t>(pairs));
+    for (int64_t i = 0; i < N; ++i) {
+      const double* k = Kx.data_ptr<double>() + i * V;
+      std::vector<int64_t> votes(static_cast<size_t>(classes), 0);
+      int64_t pidx = 0;
+      for (int64_t a = 0; a < classes - 1; ++a)
+        for (int64_t b = a + 1; b < classes; ++b, ++pidx) {
+          double sum = rho[static_cast<size_t>(pidx)];
+          for (int64_t m = 0; m < per_class[static_cast<size_t>(a)]; ++m) sum += coef[static_cast<size_t>((b - 1) * V + first[static_cast<size_t>(a)] + m)] * k[first[static_cast<size_t>(a)] + m];
+          for (int64_t m = 0; m < per_class[static_cast<size_t>(b)]; ++m) sum += coef[static_cast<size_t>(a * V + first[static_cast<size_t>(b)] + m)] * k[first[static_cast<size_t>(b)] + m];
+          dec[static_cast<size_t>(pidx)] = sum;
+          ++votes[static_cast<size_t>(sum > 0 ? a : b)];
+        }
+      const size_t best = static_cast<size_t>(std::max_element(votes.begin(), votes.end()) - votes.begin());
+      lab.data_ptr<int64_t>()[i] = pairs == 1 ? pick(best, 0.0, have_proba) : (best < labels.size() ? labels[best] : static_cast<int64_t>(best));
+      std::vector<double> z;
+      if (have_proba) {
+        std::vector<double> r(static_cast<size_t>(classes * classes), 0.0);
+        pidx = 0;
+        for (int64_t a = 0; a < classes - 1; ++a)
+          for (int64_t b = a + 1; b < classes; ++b, ++pidx) {
+            const double v = dec[static_cast<size_t>(pidx)] * prob_a[static_cast<size_t>(pidx)] + prob_b[static_cast<size_t>(pidx)];
+            const double pr = std::min(std::max(1.0 / (1.0 + std::exp(v)), 1e-7), 1.0 - 1e-7);
+            r[static_cast<size_t>(a * classes + b)] = pr;
+            r[static_cast<size_t>(b * classes + a)] = 1.0 - pr;
+          }
+        z = PostProcess(CouplePairwise(classes, r), post, -1);
+      } else if (classes > 2) {
+        z = PostProcess(dec, post, -1);
+      } else {
+        z = PostProcess({dec[0]}, post, post == Post::NONE ? 2 : 0);
+      }
+      for (int64_t c = 0; c < width; ++c) scores.data_ptr<float>()[i * width + c] = static_cast<float>(c < static_cast<int64_t>(z.size()) ? z[static_cast<size_t>(c)] : 0.0);
+    }
+  }
+  if (string_labels) ctx.SetOutputStrings(0, lab);
+  else ctx.SetOutput(0, lab.to(x_in.device()));
+  if (ctx.OutputCount() > 1) ctx.SetOutput(1, scores.to(x_in.device()));
+}
+
 at::Tensor PerFeature(const std::vector<float>& v, const at::Tensor& like) {
   at::Tensor t = at::tensor(v, at::kFloat).to(like.device());
   return t.numel() == 1 ? t.reshape({}) : t;
@@ -361,6 +518,7 @@ void RegisterMlKernels(KernelRegistry& r) {
   r.RegisterFn(ML, "LinearRegressor", 1, kMax, [](Ctx& ctx) { LinearImpl(ctx, false); });
   r.RegisterFn(ML, "LinearClassifier", 1, kMax, [](Ctx& ctx) { LinearImpl(ctx, true); });
   r.RegisterFn(ML, "SVMRegressor", 1, kMax, SvmRegressorImpl);
+  r.RegisterFn(ML, "SVMClassifier", 1, kMax, SvmClassifierImpl);
   r.RegisterFn(ML, "Scaler", 1, kMax, [](Ctx& ctx) {
     at::Tensor x = ctx.RequiredInput(0).to(at::kFloat);
     ctx.SetOutput(0, (x - PerFeature(ctx.node().attr_floats("offset"), x)) * PerFeature(ctx.node().attr_floats("scale"), x));

@@ -243,3 +243,57 @@ def test_gather_block_quantized(bits):
                     bits=bits, block_size=block)
     deq = (q.astype(np.float32) - (1 << (bits - 1))) * np.repeat(scales, block, 1)
     np.testing.assert_allclose(y, deq[idx], rtol=1e-6)
+
+
+def _svc_attrs(m, negate):
+    sign = -1.0 if negate else 1.0     # scikit-learn flips the sign of a two-class model; the operator wants libsvm's
+    return dict(kernel_type=m.kernel.upper(), kernel_params=[float(m._gamma), float(m.coef0), float(m.degree)],
+                support_vectors=m.support_vectors_.ravel().tolist(), vectors_per_class=[int(v) for v in m.n_support_],
+                coefficients=(sign * m.dual_coef_).ravel().tolist(), rho=(sign * m.intercept_).tolist())
+
+
+@pytest.mark.parametrize("kernel", ["rbf", "linear", "poly"])
+def test_svm_classifier_multiclass_matches_sklearn(kernel):
+    from sklearn.svm import SVC
+    X = rng.standard_normal((150, 4))
+    y = (X[:, 0] > 0.3).astype(int) + (X[:, 1] + X[:, 2] > 0.5).astype(int) * 2
+    m = SVC(kernel=kernel, gamma=0.3, coef0=0.5, degree=2, decision_function_shape="ovo").fit(X, y)
+    labels, scores = run_node("SVMClassifier", {"X": X.astype(np.float32)}, n_outputs=2, domain=ML,
+                              classlabels_ints=[int(c) for c in m.classes_], **_svc_attrs(m, False))
+    dec = m.decision_function(X.astype(np.float32).astype(np.float64))
+    np.testing.assert_allclose(scores, dec, rtol=2e-3, atol=2e-3)
+    clear = np.abs(dec).min(1) > 1e-3
+    np.testing.assert_array_equal(labels[clear], m.predict(X.astype(np.float32).astype(np.float64))[clear])
+
+
+def test_svm_classifier_binary_probabilities_and_string_labels():
+    from sklearn.svm import SVC
+    X = rng.standard_normal((120, 3))
+    y2 = (X[:, 0] + 0.5 * X[:, 1] > 0).astype(int)
+    m = SVC(kernel="rbf", gamma=0.5).fit(X, y2)
+    Xf = X.astype(np.float32)
+    labels, scores = run_node("SVMClassifier", {"X": Xf}, n_outputs=2, domain=ML, classlabels_strings=["neg", "pos"], **_svc_attrs(m, True))
+    dec = m.decision_function(Xf.astype(np.float64))
+    np.testing.assert_allclose(scores, np.stack([dec, -dec], 1), rtol=2e-3, atol=2e-3)      # [-d, d] with d = libsvm's decision
+    clear = np.abs(dec) > 1e-3
+    assert labels.dtype == object
+    np.testing.assert_array_equal(labels[clear], np.where(m.predict(Xf.astype(np.float64)) == 1, "pos", "neg")[clear])
+    # three classes with Platt scaling: pairwise probabilities coupled into class probabilities
+    y3 = (X[:, 0] > 0.3).astype(int) + (X[:, 1] > 0.2).astype(int)
+    mp = SVC(kernel="rbf", gamma=0.5, probability=True, random_state=0).fit(X, y3)
+    labels, scores = run_node("SVMClassifier", {"X": Xf}, n_outputs=2, domain=ML, classlabels_ints=[0, 1, 2],
+                              prob_a=mp.probA_.tolist(), prob_b=mp.probB_.tolist(), **_svc_attrs(mp, False))
+    np.testing.assert_allclose(scores, mp.predict_proba(Xf.astype(np.float64)), rtol=5e-3, atol=5e-3)
+
+
+def test_linear_and_tree_classifiers_with_string_labels():
+    X = rng.standard_normal((6, 3)).astype(np.float32)
+    W = rng.standard_normal((3, 3)).astype(np.float32)
+    labels, _ = run_node("LinearClassifier", {"X": X}, n_outputs=2, domain=ML, coefficients=W.ravel().tolist(), intercepts=[0.0, 0.0, 0.0],
+                         classlabels_strings=["a", "b", "c"])
+    assert labels.tolist() == [["a", "b", "c"][i] for i in (X @ W.T).argmax(1)]
+    attrs = dict(nodes_treeids=[0, 0, 0], nodes_nodeids=[0, 1, 2], nodes_featureids=[0, 0, 0], nodes_values=[0.0, 0.0, 0.0],
+                 nodes_modes=["BRANCH_LEQ", "LEAF", "LEAF"], nodes_truenodeids=[1, 0, 0], nodes_falsenodeids=[2, 0, 0],
+                 class_treeids=[0, 0], class_nodeids=[1, 2], class_ids=[0, 1], class_weights=[1.0, 1.0])
+    labels, scores = run_node("TreeEnsembleClassifier", {"X": X}, n_outputs=2, domain=ML, classlabels_strings=["low", "high"], **attrs)
+    assert labels.tolist() == ["low" if v <= 0 else "high" for v in X[:, 0]]
