@@ -193,6 +193,8 @@ def _to_torch(value: Any) -> torch.Tensor:
 def _to_numpy(t: Any) -> Any:
     if t is None:
         return None
+    if isinstance(t, dict):        # a row of a ZipMap output
+        return t
     if isinstance(t, list):
         return [_to_numpy(x) for x in t]
     if isinstance(t, tuple) and len(t) == 3 and t[0] == "__strings__":

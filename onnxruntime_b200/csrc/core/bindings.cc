@@ -64,6 +64,24 @@ std::vector<Value> ToValues(const std::vector<py::object>& objs) {
 
 py::object FromValue(const Value& v) {
   if (v.seq) return py::cast(*v.seq);
+  if (v.maps) {
+    // a list of dicts, one per row
+    at::Tensor vals = v.maps->values.to(at::kCPU, at::kFloat).contiguous();
+    at::Tensor keys = v.maps->keys.to(at::kCPU, at::kLong).contiguous();
+    const int64_t N = vals.size(0), C = vals.size(1);
+    std::vector<py::object> names;
+    for (int64_t c = 0; c < C; ++c) {
+      const int64_t k = keys.data_ptr<int64_t>()[c];
+      names.push_back(v.maps->string_keys ? py::object(py::str(StringOfId(k))) : py::object(py::int_(k)));
+    }
+    py::list rows;
+    for (int64_t i = 0; i < N; ++i) {
+      py::dict d;
+      for (int64_t c = 0; c < C; ++c) d[names[static_cast<size_t>(c)]] = py::float_(vals.data_ptr<float>()[i * C + c]);
+      rows.append(d);
+    }
+    return rows;
+  }
   if (v.t.defined() && v.is_string) return py::make_tuple(py::str("__strings__"), StringsOfTensor(v.t), v.t.sizes().vec());
   if (v.t.defined()) return py::cast(v.t);
   return py::none();

@@ -29,11 +29,19 @@ struct RunOptions;
 using RunOptionsRef = RunOptions;
 
 // A run-time value: a tensor, or a sequence of tensors (ONNX sequence type), or absent.
+// A sequence of maps that share one key set (what ai.onnx.ml ZipMap produces): row i maps keys[c] -> values[i, c].
+struct MapRows {
+  at::Tensor keys;           // [C] int64 (ids of the string table when string_keys)
+  bool string_keys = false;
+  at::Tensor values;         // [N, C] float
+};
+
 struct Value {
   at::Tensor t;
   std::shared_ptr<std::vector<at::Tensor>> seq;
+  std::shared_ptr<MapRows> maps;
   bool is_string = false;  // t holds ids of the string table (string_table.h): a tensor of strings
-  bool defined() const { return t.defined() || seq != nullptr; }
+  bool defined() const { return t.defined() || seq != nullptr || maps != nullptr; }
 };
 
 struct ConfigOptions {
@@ -86,6 +94,9 @@ class OpKernelContext {
   bool OutputNeeded(int i) const { return i < static_cast<int>(out_needed_.size()) && out_needed_[i]; }
   void SetOutput(int i, at::Tensor t) {
     if (i < static_cast<int>(out_.size())) out_[i].t = std::move(t);
+  }
+  void SetOutputMaps(int i, MapRows m) {
+    if (i < static_cast<int>(out_.size())) out_[i].maps = std::make_shared<MapRows>(std::move(m));
   }
   void SetOutputSeq(int i, std::vector<at::Tensor> s) {
     if (i < static_cast<int>(out_.size())) out_[i].seq = std::make_shared<std::vector<at::Tensor>>(std::move(s));

@@ -519,6 +519,24 @@ void RegisterMlKernels(KernelRegistry& r) {
   r.RegisterFn(ML, "LinearClassifier", 1, kMax, [](Ctx& ctx) { LinearImpl(ctx, true); });
   r.RegisterFn(ML, "SVMRegressor", 1, kMax, SvmRegressorImpl);
   r.RegisterFn(ML, "SVMClassifier", 1, kMax, SvmClassifierImpl);
+  // ZipMap: the rows of [N, C] scores become N maps from class label to score
+  r.RegisterFn(ML, "ZipMap", 1, kMax, [](Ctx& ctx) {
+    const Node& n = ctx.node();
+    at::Tensor x = ctx.RequiredInput(0).to(at::kCPU, at::kFloat);
+    if (x.dim() == 1) x = x.unsqueeze(0);
+    ORTB_ENFORCE_ARG(x.dim() == 2, "ZipMap: input must be [C] or [N, C]");
+    MapRows m;
+    m.string_keys = n.has_attr("classlabels_strings") && !n.attr_strings("classlabels_strings").empty();
+    std::vector<int64_t> keys = n.attr_ints("classlabels_int64s");
+    if (m.string_keys) {
+      keys.clear();
+      for (auto& s : n.attr_strings("classlabels_strings")) keys.push_back(InternString(s));
+    }
+    ORTB_ENFORCE_ARG(static_cast<int64_t>(keys.size()) == x.size(1), "ZipMap: ", keys.size(), " class labels for ", x.size(1), " columns");
+    m.keys = at::tensor(keys, at::kLong);
+    m.values = x.contiguous();
+    ctx.SetOutputMaps(0, std::move(m));
+  });
   r.RegisterFn(ML, "Scaler", 1, kMax, [](Ctx& ctx) {
     at::Tensor x = ctx.RequiredInput(0).to(at::kFloat);
     ctx.SetOutput(0, (x - PerFeature(ctx.node().attr_floats("offset"), x)) * PerFeature(ctx.node().attr_floats("scale"), x));

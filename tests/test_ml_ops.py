@@ -297,3 +297,24 @@ def test_linear_and_tree_classifiers_with_string_labels():
                  class_treeids=[0, 0], class_nodeids=[1, 2], class_ids=[0, 1], class_weights=[1.0, 1.0])
     labels, scores = run_node("TreeEnsembleClassifier", {"X": X}, n_outputs=2, domain=ML, classlabels_strings=["low", "high"], **attrs)
     assert labels.tolist() == ["low" if v <= 0 else "high" for v in X[:, 0]]
+
+
+def test_zipmap_returns_a_list_of_dicts():
+    X = np.array([[0.1, 0.9], [0.75, 0.25]], np.float32)
+    (rows,) = run_node("ZipMap", {"X": X}, domain=ML, classlabels_int64s=[10, 20])
+    assert isinstance(rows, list) and len(rows) == 2 and set(rows[0]) == {10, 20}
+    assert rows[1][10] == pytest.approx(0.75) and rows[0][20] == pytest.approx(0.9)
+    (rows,) = run_node("ZipMap", {"X": X[0]}, domain=ML, classlabels_strings=["no", "yes"])
+    assert rows == [{"no": pytest.approx(0.1), "yes": pytest.approx(0.9)}]
+    # the usual tail of a converted scikit-learn classifier: classifier -> ZipMap on the probabilities
+    import onnxruntime_b200 as ort
+    from onnxruntime_b200 import onnx_lite as ol
+    from helpers import graph_model
+    W = np.array([[1.0, -1.0], [-1.0, 1.0]], np.float32)
+    nodes = [ol.make_node("LinearClassifier", ["X"], ["label", "proba"], domain=ML, coefficients=W.ravel().tolist(), intercepts=[0.0, 0.0],
+                          classlabels_strings=["a", "b"], post_transform="SOFTMAX"),
+             ol.make_node("ZipMap", ["proba"], ["probs"], domain=ML, classlabels_strings=["a", "b"])]
+    model = graph_model(nodes, [ol.make_tensor_value_info("X", ol.TensorProto.FLOAT, ["n", 2])],
+                        [ol.make_tensor_value_info("label", ol.TensorProto.STRING, None), ol.make_tensor_value_info("probs", 0, None)])
+    label, probs = ort.InferenceSession(model, providers=["CPUExecutionProvider"]).run(None, {"X": np.array([[2.0, 0.0], [0.0, 3.0]], np.float32)})
+    assert label.tolist() == ["a", "b"] and probs[0]["a"] > 0.9 and probs[1]["b"] > 0.9
