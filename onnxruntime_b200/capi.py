@@ -27,7 +27,9 @@ __all__ = [
     "InferenceSession", "SessionOptions", "RunOptions", "IOBinding", "OrtValue", "OrtDevice", "NodeArg",
     "ModelMetadata", "GraphOptimizationLevel", "ExecutionMode", "ExecutionOrder", "get_available_providers",
     "get_all_providers", "get_device", "set_default_logger_severity", "set_default_logger_verbosity", "set_log_sink",
-    "ModelCompiler",
+    "ModelCompiler", "OrtValueVector", "SparseTensor", "OrtEpDevice", "OrtExecutionProviderDevicePolicy", "get_ep_devices",
+    "get_version_string", "get_build_info", "has_collective_ops", "set_seed", "enable_telemetry_events", "disable_telemetry_events",
+    "ModelLoadCanceled", "ModelRequiresCompilation", "NotFound",
 ]
 
 
@@ -83,6 +85,16 @@ class ExecutionMode(IntEnum):
     ORT_PARALLEL = 1
 
 
+class OrtExecutionProviderDevicePolicy(IntEnum):
+    DEFAULT = 0
+    PREFER_CPU = 1
+    PREFER_NPU = 2
+    PREFER_GPU = 3
+    MAX_PERFORMANCE = 4
+    MAX_EFFICIENCY = 5
+    MIN_OVERALL_POWER = 6
+
+
 class ExecutionOrder(IntEnum):
     DEFAULT = 0
     PRIORITY_BASED = 1
@@ -108,6 +120,57 @@ def get_available_providers() -> List[str]:
 
 def get_device() -> str:
     return "GPU" if torch.cuda.is_available() else "CPU"
+
+
+def get_version_string() -> str:
+    from . import __version__
+    return __version__
+
+
+def get_build_info() -> str:
+    return (f"onnxruntime_b200 {get_version_string()}, sm_100a kernels, torch {torch.__version__}, "
+            f"cuda {torch.version.cuda or 'none'}")
+
+
+def has_collective_ops() -> bool:
+    """AllReduce / AllGather / AllToAll / ShardedMoE / Distributed* are always part of the build."""
+    return True
+
+
+def set_seed(seed: int) -> None:
+    """Seed of the random operators (RandomNormal, Multinomial, Dropout in training mode, Sampling ...)."""
+    torch.manual_seed(int(seed))
+
+
+def enable_telemetry_events() -> None:
+    """Kept for API parity: this runtime collects no telemetry."""
+
+
+def disable_telemetry_events() -> None:
+    """Kept for API parity: this runtime collects no telemetry."""
+
+
+class OrtEpDevice:
+    """One (execution provider, hardware device) pair, as ``get_ep_devices`` lists them."""
+
+    def __init__(self, ep_name: str, device_type: str, device_id: int, vendor: str, metadata: Dict[str, str]):
+        self.ep_name, self.ep_vendor = ep_name, "onnxruntime_b200"
+        self.device = OrtDevice(device_type, device_id)
+        self.ep_metadata, self.ep_options = dict(metadata), {}
+        self.device_vendor = vendor
+
+    def __repr__(self) -> str:
+        return f"OrtEpDevice({self.ep_name}, {self.device.device_type()}:{self.device.device_id()})"
+
+
+def get_ep_devices() -> List["OrtEpDevice"]:
+    out = [OrtEpDevice("CPUExecutionProvider", "cpu", 0, "host", {})]
+    if torch.cuda.is_available():
+        for i in range(torch.cuda.device_count()):
+            p = torch.cuda.get_device_properties(i)
+            out.append(OrtEpDevice("CUDAExecutionProvider", "cuda", i, "NVIDIA",
+                                   {"name": p.name, "compute_capability": f"{p.major}.{p.minor}", "memory_bytes": str(p.total_memory)}))
+    return out
 
 
 def set_default_logger_severity(severity: int) -> None:
@@ -171,10 +234,12 @@ def _is_string_array(value: Any) -> bool:
 
 
 def _to_torch(value: Any) -> torch.Tensor:
+    if isinstance(value, SparseTensor):
+        return value._t.to_dense()
     if isinstance(value, OrtValue):
-        return value._tensor
+        value = value._tensor
     if isinstance(value, torch.Tensor):
-        return value
+        return value.to_dense() if value.layout != torch.strided else value
     if _is_string_array(value):
         arr = np.asarray(value, dtype=object)
         flat = [s.decode("utf-8") if isinstance(s, bytes) else str(s) for s in arr.reshape(-1)]
@@ -311,7 +376,16 @@ class OrtValue:
         return True
 
     def is_sparse_tensor(self) -> bool:
-        return False
+        return bool(getattr(self._tensor, "is_sparse", False) or getattr(self._tensor, "is_sparse_csr", False))
+
+    @staticmethod
+    def ort_value_from_sparse_tensor(sparse_tensor: "SparseTensor") -> "OrtValue":
+        return OrtValue(sparse_tensor._t)
+
+    def as_sparse_tensor(self) -> "SparseTensor":
+        if not self.is_sparse_tensor():
+            raise InvalidArgument("this OrtValue does not hold a sparse tensor")
+        return SparseTensor(self._tensor)
 
     def is_tensor_sequence(self) -> bool:
         return False
@@ -321,6 +395,122 @@ class OrtValue:
 
     def update_inplace(self, np_arr: np.ndarray) -> None:
         self._tensor.copy_(_to_torch(np_arr))
+
+
+class OrtValueVector:
+    """A growable list of OrtValues (the reference's ``OrtValueVector``)."""
+
+    def __init__(self, values: Optional[Sequence["OrtValue"]] = None):
+        self._v: List[OrtValue] = list(values or [])
+
+    def push_back(self, value) -> None:
+        self._v.append(value if isinstance(value, OrtValue) else OrtValue(_to_torch(value)))
+
+    def push_back_batch(self, tensors: Sequence[Any], *_ignored) -> None:
+        for t in tensors:
+            self.push_back(t)
+
+    def reserve(self, n: int) -> None:
+        pass
+
+    def shrink_to_fit(self) -> None:
+        pass
+
+    def clear(self) -> None:
+        self._v.clear()
+
+    def __len__(self) -> int:
+        return len(self._v)
+
+    def __getitem__(self, i) -> "OrtValue":
+        return self._v[i]
+
+    def __iter__(self):
+        return iter(self._v)
+
+    def dlpack_at(self, i: int):
+        return self._v[i].to_dlpack()
+
+    def to_dlpacks(self, to_tensor=None) -> List[Any]:
+        caps = [v.to_dlpack() for v in self._v]
+        return caps if to_tensor is None else [to_tensor(c) for c in caps]
+
+    def bool_tensor_indices(self) -> List[int]:
+        return [i for i, v in enumerate(self._v) if v._tensor.dtype == torch.bool]
+
+    def element_type_at(self, i: int) -> int:
+        return self._v[i].element_type()
+
+
+class _SparseView:
+    def __init__(self, **parts):
+        self._parts = parts
+
+    def __getattr__(self, name):
+        if name in self._parts:
+            return lambda: self._parts[name]
+        raise AttributeError(name)
+
+
+class SparseTensor:
+    """COO / CSR sparse tensors (the reference's ``SparseTensor``), held as torch sparse tensors.  The runtime's kernels are
+    dense: a sparse feed or initializer is expanded when it enters a session."""
+
+    def __init__(self, t: torch.Tensor):
+        self._t = t
+
+    @staticmethod
+    def sparse_coo_from_numpy(dense_shape, values: np.ndarray, coo_indices: np.ndarray, ort_device: Optional[OrtDevice] = None) -> "SparseTensor":
+        shape = [int(d) for d in dense_shape]
+        idx = torch.as_tensor(np.asarray(coo_indices, dtype=np.int64))
+        if idx.dim() == 1:      # linear indices into the flattened tensor
+            idx = torch.stack(torch.unravel_index(idx, shape)) if shape else idx.reshape(0, -1)
+        else:                   # [nnz, rank] coordinates
+            idx = idx.t().contiguous()
+        t = torch.sparse_coo_tensor(idx, torch.as_tensor(np.asarray(values)), shape).coalesce()
+        return SparseTensor(t.to(ort_device._torch()) if ort_device is not None else t)
+
+    @staticmethod
+    def sparse_csr_from_numpy(dense_shape, values: np.ndarray, inner_indices: np.ndarray, outer_indices: np.ndarray,
+                              ort_device: Optional[OrtDevice] = None) -> "SparseTensor":
+        t = torch.sparse_csr_tensor(torch.as_tensor(np.asarray(outer_indices, dtype=np.int64)), torch.as_tensor(np.asarray(inner_indices, dtype=np.int64)),
+                                    torch.as_tensor(np.asarray(values)), [int(d) for d in dense_shape])
+        return SparseTensor(t.to(ort_device._torch()) if ort_device is not None else t)
+
+    def values(self) -> np.ndarray:
+        return self._t.values().cpu().numpy()
+
+    def as_coo_view(self):
+        if self._t.layout != torch.sparse_coo:
+            raise InvalidArgument("not a COO tensor")
+        return _SparseView(indices=self._t.indices().t().contiguous().cpu().numpy())
+
+    def as_csrc_view(self):
+        if self._t.layout != torch.sparse_csr:
+            raise InvalidArgument("not a CSR tensor")
+        return _SparseView(inner=self._t.col_indices().cpu().numpy(), outer=self._t.crow_indices().cpu().numpy())
+
+    def to_cuda(self, ort_device: OrtDevice) -> "SparseTensor":
+        return SparseTensor(self._t.to(ort_device._torch()))
+
+    def to_dense(self) -> np.ndarray:
+        return self._t.to_dense().cpu().numpy()
+
+    def format(self) -> str:
+        return "COO" if self._t.layout == torch.sparse_coo else "CSR"
+
+    def dense_shape(self) -> List[int]:
+        return list(self._t.shape)
+
+    def data_type(self) -> str:
+        return f"sparse_tensor({_TORCH_TYPE_NAMES.get(self._t.dtype, str(self._t.dtype))})"
+
+    def device_name(self) -> str:
+        return "Cuda" if self._t.is_cuda else "Cpu"
+
+
+_TORCH_TYPE_NAMES = {torch.float32: "float", torch.float16: "float16", torch.float64: "double", torch.int64: "int64", torch.int32: "int32",
+                     torch.int8: "int8", torch.uint8: "uint8", torch.bool: "bool", torch.bfloat16: "bfloat16"}
 
 
 class NodeArg:
@@ -410,6 +600,47 @@ class SessionOptions:
             raise InvalidArgument("names and ort_values differ in length")
         for n, v in zip(names, ort_values):
             self._c.add_external_initializer(n, _to_torch(v))
+
+    def add_external_initializers_from_files_in_memory(self, names: Sequence[str], buffers: Sequence[Any], lengths: Sequence[int]) -> None:
+        """External-data FILES handed over as memory: `names` are the file names the model's initializers point to.  The
+        bytes are kept for the model load, which reads the initializers' (offset, length) ranges from them."""
+        if not (len(names) == len(buffers) == len(lengths)):
+            raise InvalidArgument("names, buffers and lengths differ in length")
+        files = dict(getattr(self, "_external_files", {}))
+        for n, b, ln in zip(names, buffers, lengths):
+            files[os.fspath(n)] = bytes(memoryview(b)[:int(ln)])
+        object.__setattr__(self, "_external_files", files)
+
+    def add_provider_for_devices(self, ep_devices: Sequence["OrtEpDevice"], provider_options: Optional[Dict[str, str]] = None) -> None:
+        """Pin the session to the provider of the given devices (all of one provider)."""
+        names = {d.ep_name for d in ep_devices}
+        if len(names) != 1:
+            raise InvalidArgument("add_provider_for_devices needs devices of exactly one execution provider")
+        opts = dict(provider_options or {})
+        dev = ep_devices[0].device
+        if dev.device_type() == "cuda":
+            opts.setdefault("device_id", str(dev.device_id()))
+        chosen = list(getattr(self, "_providers_for_devices", []))
+        chosen.append((names.pop(), opts))
+        object.__setattr__(self, "_providers_for_devices", chosen)
+
+    def add_provider(self, name: str, provider_options: Optional[Dict[str, str]] = None) -> None:
+        chosen = list(getattr(self, "_providers_for_devices", []))
+        chosen.append((name, dict(provider_options or {})))
+        object.__setattr__(self, "_providers_for_devices", chosen)
+
+    def set_provider_selection_policy(self, policy) -> None:
+        """Automatic provider selection: PREFER_GPU / MAX_PERFORMANCE pick the CUDA provider when a GPU is there,
+        PREFER_CPU / MIN_OVERALL_POWER the CPU provider; DEFAULT leaves the choice to the `providers` argument."""
+        object.__setattr__(self, "_selection_policy", OrtExecutionProviderDevicePolicy(int(policy)))
+
+    def set_provider_selection_policy_delegate(self, delegate) -> None:
+        """delegate(ep_devices, model_metadata, runtime_metadata, max_selections) -> the devices to use."""
+        object.__setattr__(self, "_selection_delegate", delegate)
+
+    def set_load_cancellation_flag(self, value: bool) -> None:
+        """A session created while the flag is set fails with ModelLoadCanceled."""
+        object.__setattr__(self, "_load_cancelled", bool(value))
 
     def register_custom_ops_library(self, path: str) -> None:
         if not os.path.exists(path):
@@ -618,6 +849,18 @@ class InferenceSession:
         else:
             raise TypeError(f"Unable to load from type '{type(path_or_bytes)}'")
         available = get_available_providers()
+        so = self._sess_options
+        if getattr(so, "_load_cancelled", False):
+            raise ModelLoadCanceled("the session options' load cancellation flag is set")
+        if providers is None and getattr(so, "_providers_for_devices", None):
+            providers = [n for n, _ in so._providers_for_devices]
+            provider_options = [o for _, o in so._providers_for_devices]
+        if providers is None and getattr(so, "_selection_delegate", None) is not None:
+            picked = so._selection_delegate(get_ep_devices(), {}, {}, 8)
+            providers = list(dict.fromkeys(d.ep_name for d in picked))
+        if providers is None and getattr(so, "_selection_policy", OrtExecutionProviderDevicePolicy.DEFAULT) != OrtExecutionProviderDevicePolicy.DEFAULT:
+            gpu = so._selection_policy in (OrtExecutionProviderDevicePolicy.PREFER_GPU, OrtExecutionProviderDevicePolicy.MAX_PERFORMANCE)
+            providers = ["CUDAExecutionProvider", "CPUExecutionProvider"] if gpu and torch.cuda.is_available() else ["CPUExecutionProvider"]
         names, opts = check_and_normalize_provider_args(providers, provider_options, available)
         if not names:
             names, opts = ["CPUExecutionProvider"], [{}]
@@ -652,7 +895,44 @@ class InferenceSession:
                 self._model_bytes = ort_format.ort_to_onnx(self._model_bytes).serialize()
             except (ValueError, struct_error) as e:
                 raise InvalidProtobuf(f"cannot read the ORT-format model: {e}") from None
-        if self._model_path is not None:
+        ext_files = getattr(self._sess_options, "_external_files", None)
+        if ext_files:
+            # external-data files handed over as memory: put their bytes into the initializers that point to them
+            from . import onnx_lite as ol
+            model = ol.load_model(self._model_path if self._model_path is not None else self._model_bytes)
+
+            def inline(graph):
+                for t in graph.initializers:
+                    loc = (t.external or {}).get("location")
+                    if loc is None or loc == "*session*":
+                        continue
+                    data = ext_files.get(loc, ext_files.get(os.path.basename(loc)))
+                    if data is None:
+                        continue
+                    off = int(t.external.get("offset", 0))
+                    ln = int(t.external["length"]) if "length" in t.external else len(data) - off
+                    if off + ln > len(data):
+                        raise InvalidArgument(f"initializer '{t.name}' reads bytes [{off}, {off + ln}) of '{loc}', which holds {len(data)}")
+                    t.raw, t.external = data[off:off + ln], None
+                for node in graph.nodes:
+                    for a in node.attributes:
+                        if a.type == ol.ATTR_GRAPH:
+                            inline(a.value)
+            inline(model.graph)
+            model_dir = os.path.dirname(self._model_path) if self._model_path is not None else None
+            self._model_bytes = model.serialize()
+            if model_dir and any((t.external or {}).get("location") not in (None, "*session*") for t in model.graph.initializers):
+                # some initializers still live in real files next to the model: keep loading from that directory
+                tmp = os.path.join(model_dir, f".ortb200_inline_{os.getpid()}.onnx")
+                with open(tmp, "wb") as f:
+                    f.write(self._model_bytes)
+                try:
+                    sess.load(tmp)
+                finally:
+                    os.remove(tmp)
+            else:
+                sess.load_bytes(self._model_bytes)
+        elif self._model_path is not None:
             sess.load(self._model_path)
         else:
             sess.load_bytes(self._model_bytes)
@@ -750,6 +1030,21 @@ class InferenceSession:
         feeds = [_to_torch(v) for v in input_dict_ort_values.values()]
         outs = self._sess.run(ro, names, feeds, list(output_names or []))
         return [OrtValue(o) for o in outs]
+
+    def run_with_ortvaluevector(self, run_options, feed_names: Sequence[str], feeds: "OrtValueVector", fetch_names: Sequence[str],
+                                fetches: "OrtValueVector", fetch_devices: Sequence[OrtDevice]) -> None:
+        """Run with OrtValue vectors: `fetches` is filled with one OrtValue per fetch name, placed on `fetch_devices`."""
+        if len(feed_names) != len(feeds):
+            raise InvalidArgument("feed_names and feeds differ in length")
+        if len(fetch_devices) != len(fetch_names):
+            raise InvalidArgument("fetch_names and fetch_devices differ in length")
+        ro = run_options._c if run_options is not None else C.RunOptions()
+        outs = self._sess.run(ro, list(feed_names), [_to_torch(v) for v in feeds], list(fetch_names))
+        fetches.clear()
+        for o, dev in zip(outs, fetch_devices):
+            if isinstance(o, torch.Tensor):
+                o = o.to(dev._torch() if isinstance(dev, OrtDevice) else torch.device(dev))
+            fetches.push_back(OrtValue(o))
 
     def run_async(self, output_names, input_feed, callback, user_data, run_options=None) -> None:
         def work():

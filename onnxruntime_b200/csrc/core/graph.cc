@@ -289,6 +289,28 @@ std::vector<std::string> Node::attr_strings(const std::string& n) const {
   auto* a = FindAttr(*this, n);
   return a ? a->strings : std::vector<std::string>{};
 }
+at::Tensor DenseFromSparseProto(const pb::SparseTensorProto& s) {
+  at::Tensor values = TensorFromProto(s.values, "").reshape({-1});
+  at::Tensor idx = TensorFromProto(s.indices, "").to(at::kLong);
+  at::Tensor dense = at::zeros({NumElements(s.dims)}, values.options());
+  if (idx.dim() == 2) {  // [nnz, rank] coordinates -> linear positions
+    ORTB_ENFORCE_ARG(idx.size(1) == static_cast<int64_t>(s.dims.size()), "sparse tensor '", s.values.name, "': indices do not match the rank");
+    at::Tensor lin = at::zeros({idx.size(0)}, at::kLong);
+    int64_t stride = 1;
+    for (int64_t d = static_cast<int64_t>(s.dims.size()) - 1; d >= 0; --d) {
+      lin = lin + idx.select(1, d) * stride;
+      stride *= s.dims[static_cast<size_t>(d)];
+    }
+    idx = lin;
+  }
+  ORTB_ENFORCE_ARG(idx.numel() == values.numel(), "sparse tensor '", s.values.name, "': ", idx.numel(), " indices for ", values.numel(), " values");
+  if (idx.numel() > 0) {
+    ORTB_ENFORCE_ARG(idx.min().item<int64_t>() >= 0 && idx.max().item<int64_t>() < dense.numel(), "sparse tensor '", s.values.name, "': index out of range");
+    dense.index_put_({idx.reshape({-1})}, values);
+  }
+  return dense.reshape(s.dims);
+}
+
 bool ConstantHoldsStrings(const Node& n) {
   if (n.has_attr("value_string") || n.has_attr("value_strings")) return true;
   auto* a = FindAttr(n, "value");
@@ -296,6 +318,7 @@ bool ConstantHoldsStrings(const Node& n) {
 }
 at::Tensor Node::attr_tensor(const std::string& n) const {
   auto* a = FindAttr(*this, n);
+  if (a && a->sparse_tensor) return DenseFromSparseProto(*a->sparse_tensor);  // Constant.sparse_value
   if (!a || !a->t) return at::Tensor();
   return TensorFromProto(*a->t, "");
 }
@@ -372,6 +395,11 @@ std::shared_ptr<Graph> Graph::FromProto(const pb::GraphProto& g, const std::map<
         out->value_info_[t.name] = vi;
       }
     }
+  }
+  // sparse initializers: the kernels are dense, so they are expanded here
+  for (auto& s : g.sparse_initializer) {
+    ORTB_ENFORCE_ARG(!s.values.name.empty(), "sparse initializer without a name");
+    out->initializers_[s.values.name] = DenseFromSparseProto(s);
   }
   for (auto& v : g.input) out->inputs_.push_back({v.name, v.type});
   for (auto& v : g.output) out->outputs_.push_back({v.name, v.type});

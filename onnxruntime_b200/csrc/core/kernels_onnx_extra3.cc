@@ -226,6 +226,15 @@ void RegisterOnnxExtraKernels3(KernelRegistry& r) {
   r.RegisterFn("", "MelWeightMatrix", 17, kMax, MelWeightMatrixImpl, {0, 1, 2, 3, 4});
   r.RegisterFn("", "MaxRoiPool", 1, kMax, MaxRoiPoolImpl);
   r.RegisterFn("com.microsoft", "GatherBlockQuantized", 1, kMax, GatherBlockQuantizedImpl);
+  // SparseToDenseMatMul (contrib_ops/cpu/math/sparse_dense_matmul.cc): sparse tensors are expanded when they enter a
+  // session, so this is alpha * op(A) @ op(B) on dense operands
+  r.RegisterFn("com.microsoft", "SparseToDenseMatMul", 1, kMax, [](Ctx& ctx) {
+    const Node& n = ctx.node();
+    at::Tensor a = ctx.RequiredInput(0), b = ctx.RequiredInput(1);
+    if (n.attr_i("transA", 0)) a = a.transpose(-1, -2);
+    if (n.attr_i("transB", 0)) b = b.transpose(-1, -2);
+    ctx.SetOutput(0, at::matmul(a, b) * n.attr_f("alpha", 1.f));
+  });
   // optional values carry tensors here: an absent input is the empty optional
   r.RegisterFn("", "Optional", 15, kMax, [](Ctx& ctx) {
     if (ctx.HasInput(0)) ctx.SetOutput(0, ctx.Input(0));

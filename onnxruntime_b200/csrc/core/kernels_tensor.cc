@@ -203,6 +203,7 @@ at::Tensor ScatterND(const at::Tensor& data, const at::Tensor& indices_in, const
 
 at::Tensor ConstantValue(const Node& n) {
   if (n.has_attr("value")) return n.attr_tensor("value");  // a string tensor comes back as ids of the string table
+  if (n.has_attr("sparse_value")) return n.attr_tensor("sparse_value");  // expanded: the kernels are dense
   if (n.has_attr("value_string")) return InternStrings({n.attr_s("value_string")}, {});
   if (n.has_attr("value_strings")) {
     const std::vector<std::string> v = n.attr_strings("value_strings");

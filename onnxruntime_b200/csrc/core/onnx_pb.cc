@@ -308,6 +308,7 @@ void parse_value_info(const char* d, size_t n, int depth, ValueInfoProto* v) {
 }
 
 void parse_graph(const char* d, size_t n, int depth, GraphProto* g);
+void parse_sparse_tensor(const char* d, size_t n, int depth, SparseTensorProto* s);
 
 void parse_attribute(const char* d, size_t n, int depth, AttributeProto* a) {
   Reader r(d, n, depth);
@@ -347,6 +348,13 @@ void parse_attribute(const char* d, size_t n, int depth, AttributeProto* a) {
         auto b = r.bytes();
         a->graphs.push_back(std::make_shared<GraphProto>());
         parse_graph(b.first, b.second, depth + 1, a->graphs.back().get());
+        break;
+      }
+      case 22: {
+        r.expect(w, 2, "AttributeProto.sparse_tensor");
+        auto b = r.bytes();
+        a->sparse_tensor = std::make_shared<SparseTensorProto>();
+        parse_sparse_tensor(b.first, b.second, depth + 1, a->sparse_tensor.get());
         break;
       }
       case 13: r.expect(w, 2, "AttributeProto.doc_string"); a->doc_string = r.str(); break;
@@ -406,6 +414,21 @@ void parse_node(const char* d, size_t n, int depth, NodeProto* node) {
   }
 }
 
+void parse_sparse_tensor(const char* d, size_t n, int depth, SparseTensorProto* s) {
+  Reader r(d, n, depth);
+  uint32_t f, w;
+  while (r.next(&f, &w)) {
+    if (f == 3) {
+      read_repeated_varint(r, w, &s->dims, [](uint64_t v) { return static_cast<int64_t>(v); });
+    } else if ((f == 1 || f == 2) && w == 2) {
+      auto b = r.bytes();
+      parse_tensor(b.first, b.second, depth + 1, f == 1 ? &s->values : &s->indices);
+    } else {
+      r.skip(w);
+    }
+  }
+}
+
 void parse_graph(const char* d, size_t n, int depth, GraphProto* g) {
   Reader r(d, n, depth);
   uint32_t f, w;
@@ -420,6 +443,7 @@ void parse_graph(const char* d, size_t n, int depth, GraphProto* g) {
       case 11: g->input.emplace_back(); parse_value_info(b.first, b.second, depth + 1, &g->input.back()); break;
       case 12: g->output.emplace_back(); parse_value_info(b.first, b.second, depth + 1, &g->output.back()); break;
       case 13: g->value_info.emplace_back(); parse_value_info(b.first, b.second, depth + 1, &g->value_info.back()); break;
+      case 15: g->sparse_initializer.emplace_back(); parse_sparse_tensor(b.first, b.second, depth + 1, &g->sparse_initializer.back()); break;
       default: break;
     }
   }

@@ -98,6 +98,12 @@ struct ValueInfoProto {
 
 struct GraphProto;
 
+// COO sparse tensor: `indices` are linear positions [nnz] or coordinates [nnz, rank] into a tensor of shape `dims`
+struct SparseTensorProto {
+  TensorProto values, indices;
+  std::vector<int64_t> dims;
+};
+
 struct AttributeProto {
   std::string name;
   int32_t type = 0;
@@ -105,6 +111,7 @@ struct AttributeProto {
   int64_t i = 0;
   std::string s;
   std::shared_ptr<TensorProto> t;
+  std::shared_ptr<SparseTensorProto> sparse_tensor;
   std::shared_ptr<GraphProto> g;
   std::vector<float> floats;
   std::vector<int64_t> ints;
@@ -127,6 +134,7 @@ struct GraphProto {
   std::vector<NodeProto> node;
   std::string name, doc_string;
   std::vector<TensorProto> initializer;
+  std::vector<SparseTensorProto> sparse_initializer;  // read only: the loader expands them into dense initializers
   std::vector<ValueInfoProto> input, output, value_info;
 };
 

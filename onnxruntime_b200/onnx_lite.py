@@ -101,6 +101,24 @@ class Tensor:
 
 
 @dataclass
+class SparseTensor:
+    """COO sparse initializer: `indices` are linear positions [nnz] or coordinates [nnz, rank]; the name is the values tensor's."""
+    values: Tensor
+    indices: Tensor
+    dims: Tuple[int, ...]
+
+    def serialize(self) -> bytes:
+        return _f_bytes(1, self.values.serialize()) + _f_bytes(2, self.indices.serialize()) + _packed_varints(3, self.dims)
+
+
+def make_sparse_tensor(name: str, dense) -> SparseTensor:
+    """Sparse initializer holding the non-zeros of a dense numpy array (coordinates form)."""
+    dense = np.asarray(dense)
+    coords = np.argwhere(dense != 0).astype(np.int64)
+    return SparseTensor(make_tensor(name, dense[dense != 0]), make_tensor("", coords.reshape(-1, dense.ndim)), tuple(dense.shape))
+
+
+@dataclass
 class ValueInfo:
     name: str
     elem_type: int = 0
@@ -186,11 +204,13 @@ class Graph:
     outputs: List[ValueInfo]
     initializers: List[Tensor] = field(default_factory=list)
     value_info: List[ValueInfo] = field(default_factory=list)
+    sparse_initializers: List["SparseTensor"] = field(default_factory=list)
 
     def serialize(self) -> bytes:
         out = b"".join(_f_bytes(1, n.serialize()) for n in self.nodes)
         out += _f_str(2, self.name)
         out += b"".join(_f_bytes(5, t.serialize()) for t in self.initializers)
+        out += b"".join(_f_bytes(15, t.serialize()) for t in self.sparse_initializers)
         out += b"".join(_f_bytes(11, v.serialize()) for v in self.inputs)
         out += b"".join(_f_bytes(12, v.serialize()) for v in self.outputs)
         out += b"".join(_f_bytes(13, v.serialize()) for v in self.value_info)

@@ -259,3 +259,21 @@ def test_label_encoder_numeric():
     xf = np.array([0.5, 2.0, 1.5], np.float32)
     (z,) = run_node("LabelEncoder", {"x": xf}, domain="ai.onnx.ml", keys_floats=[1.5, 0.5], values_int64s=[15, 5], default_int64=-7)
     np.testing.assert_array_equal(z, [5, -7, 15])
+
+
+def test_sparse_initializer_and_sparse_to_dense_matmul():
+    import onnxruntime_b200 as ort
+    from onnxruntime_b200 import onnx_lite as ol
+    A = np.zeros((5, 6), np.float32)
+    A[0, 2], A[3, 3], A[4, 0] = 1.5, -2.0, 4.0
+    B = rng.standard_normal((6, 3)).astype(np.float32)
+    g = ol.make_graph([ol.make_node("SparseToDenseMatMul", ["A", "B"], ["Y"], domain=MS, alpha=0.5)], "g",
+                      [ol.make_tensor_value_info("B", ol.TensorProto.FLOAT, [6, 3])], [ol.make_tensor_value_info("Y", ol.TensorProto.FLOAT, None)])
+    g.sparse_initializers.append(ol.make_sparse_tensor("A", A))
+    sess = ort.InferenceSession(ol.make_model(g, opset=17).serialize(), providers=["CPUExecutionProvider"])
+    np.testing.assert_allclose(sess.run(None, {"B": B})[0], 0.5 * A @ B, rtol=1e-6)
+    # linear-index form of the indices
+    sp = ol.SparseTensor(ol.make_tensor("A", np.array([1.5, -2.0, 4.0], np.float32)), ol.make_tensor("", np.array([2, 21, 24], np.int64)), (5, 6))
+    g.sparse_initializers[0] = sp
+    sess = ort.InferenceSession(ol.make_model(g, opset=17).serialize(), providers=["CPUExecutionProvider"])
+    np.testing.assert_allclose(sess.run(None, {"B": B})[0], 0.5 * A @ B, rtol=1e-6)

@@ -438,3 +438,60 @@ s.run(None, {"x": np.array([[-1, 2, 3], [4, -5, 6]], np.float32)})
     out = subprocess.run([sys.executable, "-c", script], capture_output=True, text=True, env=env, timeout=300)
     assert out.returncode == 0 and "node '" not in out.stdout
     assert "output 'r' Float [2, 3]" in (tmp_path / "relu0.txt").read_text()
+
+
+def test_python_api_vectors_sparse_tensors_and_module_functions(tmp_path):
+    import onnxruntime_b200 as ort
+    from onnxruntime_b200 import onnx_lite as ol
+    from helpers import graph_model
+    T = ol.TensorProto
+    model = graph_model([ol.make_node("MatMul", ["a", "b"], ["y"])], [ol.make_tensor_value_info("a", T.FLOAT, [3, 4]), ol.make_tensor_value_info("b", T.FLOAT, [4, 2])],
+                        [ol.make_tensor_value_info("y", T.FLOAT, None)])
+    sess = ort.InferenceSession(model, providers=["CPUExecutionProvider"])
+    a = np.zeros((3, 4), np.float32)
+    a[0, 1], a[2, 3] = 2.0, -1.0
+    b = np.arange(8, dtype=np.float32).reshape(4, 2)
+    # OrtValueVector + run_with_ortvaluevector
+    feeds = ort.OrtValueVector()
+    feeds.push_back(ort.OrtValue.ortvalue_from_numpy(a))
+    feeds.push_back(b)
+    fetches = ort.OrtValueVector()
+    sess.run_with_ortvaluevector(None, ["a", "b"], feeds, ["y"], fetches, [ort.OrtDevice("cpu", 0)])
+    assert len(fetches) == 1
+    np.testing.assert_allclose(fetches[0].numpy(), a @ b)
+    # sparse tensors are expanded on their way in
+    sp = ort.SparseTensor.sparse_coo_from_numpy([3, 4], np.array([2.0, -1.0], np.float32), np.array([1, 11], np.int64))
+    assert sp.format() == "COO" and sp.dense_shape() == [3, 4] and sp.data_type() == "sparse_tensor(float)"
+    np.testing.assert_array_equal(sp.as_coo_view().indices(), [[0, 1], [2, 3]])
+    np.testing.assert_array_equal(sp.to_dense(), a)
+    ov = ort.OrtValue.ort_value_from_sparse_tensor(sp)
+    assert ov.is_sparse_tensor() and ov.as_sparse_tensor().values().tolist() == [2.0, -1.0]
+    np.testing.assert_allclose(sess.run(None, {"a": sp, "b": b})[0], a @ b)
+    csr = ort.SparseTensor.sparse_csr_from_numpy([3, 4], np.array([2.0, -1.0], np.float32), np.array([1, 3]), np.array([0, 1, 1, 2]))
+    assert csr.format() == "CSR" and csr.as_csrc_view().outer().tolist() == [0, 1, 1, 2]
+    np.testing.assert_array_equal(csr.to_dense(), a)
+    # module-level functions
+    assert ort.get_version_string() and "sm_100a" in ort.get_build_info() and ort.has_collective_ops()
+    devices = ort.get_ep_devices()
+    assert devices[0].ep_name == "CPUExecutionProvider"
+    ort.set_seed(7)
+    ort.disable_telemetry_events()
+    # provider selection through the options object
+    so = ort.SessionOptions()
+    so.add_provider_for_devices([devices[0]])
+    assert ort.InferenceSession(model, so).get_providers() == ["CPUExecutionProvider"]
+    so = ort.SessionOptions()
+    so.set_provider_selection_policy(ort.OrtExecutionProviderDevicePolicy.PREFER_CPU)
+    assert ort.InferenceSession(model, so).get_providers() == ["CPUExecutionProvider"]
+    so = ort.SessionOptions()
+    so.set_load_cancellation_flag(True)
+    with pytest.raises(ort.ModelLoadCanceled):
+        ort.InferenceSession(model, so)
+    # external data handed over as memory
+    w = np.arange(8, dtype=np.float32).reshape(4, 2)
+    ext = graph_model([ol.make_node("MatMul", ["a", "w"], ["y"])], [ol.make_tensor_value_info("a", T.FLOAT, [3, 4])], [ol.make_tensor_value_info("y", T.FLOAT, None)],
+                      [ol.make_external_tensor("w", T.FLOAT, [4, 2], location="weights.bin", offset=16, length=32)])
+    so = ort.SessionOptions()
+    blob = bytes(16) + w.tobytes()
+    so.add_external_initializers_from_files_in_memory(["weights.bin"], [blob], [len(blob)])
+    np.testing.assert_allclose(ort.InferenceSession(ext, so).run(None, {"a": a})[0], a @ w)
