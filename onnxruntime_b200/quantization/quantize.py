@@ -117,17 +117,137 @@ class MinMaxCalibrator:
             r[0], r[1] = min(r[0], lo), max(r[1], hi)
 
 
+class HistogramCalibrator(MinMaxCalibrator):
+    """Keeps a histogram of |x| per tensor (2048 bins, range grown as needed) instead of the bare extremes; the entropy and
+    percentile calibrators of the reference (onnxruntime/python/tools/quantization/calibrate.py) cut the range from it."""
+
+    BINS = 2048
+
+    def __init__(self, model: ol.Model, tensors: Sequence[str]):
+        super().__init__(model, tensors)
+        self.hist: Dict[str, np.ndarray] = {}
+        self.limit: Dict[str, float] = {}
+
+    def collect(self, feeds: Dict[str, np.ndarray]) -> None:
+        graph_inputs = {i.name for i in self.sess.get_inputs()}
+        outs = self.sess.run(self.tensors, {k: v for k, v in feeds.items() if k in graph_inputs})
+        for name, v in zip(self.tensors, outs):
+            a = np.abs(np.asarray(v, dtype=np.float32)).reshape(-1)
+            top = float(a.max()) if a.size else 0.0
+            if name not in self.hist:
+                self.limit[name] = max(top, 1e-12)
+                self.hist[name] = np.zeros(self.BINS, np.float64)
+            elif top > self.limit[name]:
+                # re-bin the old counts into the wider range
+                old_edges = np.linspace(0, self.limit[name], self.BINS + 1)
+                centres = (old_edges[:-1] + old_edges[1:]) / 2
+                self.hist[name] = np.histogram(centres, bins=self.BINS, range=(0, top), weights=self.hist[name])[0]
+                self.limit[name] = top
+            self.hist[name] += np.histogram(a, bins=self.BINS, range=(0, self.limit[name]))[0]
+
+    def _finish(self, pick) -> None:
+        for name, h in self.hist.items():
+            edge = pick(h, np.linspace(0, self.limit[name], self.BINS + 1))
+            self.ranges[name] = [-edge, edge]
+
+
+class PercentileCalibrator(HistogramCalibrator):
+    """Symmetric range that keeps `percentile` percent of the observed |x| mass."""
+
+    def __init__(self, model: ol.Model, tensors: Sequence[str], percentile: float = 99.999):
+        super().__init__(model, tensors)
+        self.percentile = float(percentile)
+
+    def compute_ranges(self) -> Dict[str, List[float]]:
+        def pick(h, edges):
+            cdf = np.cumsum(h) / max(h.sum(), 1.0)
+            return float(edges[min(int(np.searchsorted(cdf, self.percentile / 100.0)) + 1, len(edges) - 1)])
+        self._finish(pick)
+        return self.ranges
+
+
+class EntropyCalibrator(HistogramCalibrator):
+    """Symmetric range that minimises the KL divergence between the histogram and its 128-level quantisation."""
+
+    def __init__(self, model: ol.Model, tensors: Sequence[str], num_quantized_bins: int = 128):
+        super().__init__(model, tensors)
+        self.levels = int(num_quantized_bins)
+
+    def compute_ranges(self) -> Dict[str, List[float]]:
+        levels = self.levels
+
+        def pick(h, edges):
+            best, best_i = None, len(h)
+            for i in range(levels, len(h) + 1, 16):
+                p = h[:i].copy()
+                p[i - 1] += h[i:].sum()                      # the clipped tail lands in the last kept bin
+                if p.sum() == 0:
+                    continue
+                # quantise the kept bins to `levels` levels and expand back over the non-empty bins
+                chunks = np.array_split(np.arange(i), levels)
+                q = np.zeros(i)
+                for c in chunks:
+                    mass, nz = h[c].sum(), (h[c] > 0).sum()
+                    if nz:
+                        q[c] = np.where(h[c] > 0, mass / nz, 0.0)
+                pn, qn = p / p.sum(), q / max(q.sum(), 1e-30)
+                mask = pn > 0
+                kl = float(np.sum(pn[mask] * np.log(pn[mask] / np.maximum(qn[mask], 1e-30))))
+                if best is None or kl < best:
+                    best, best_i = kl, i
+            return float(edges[best_i])
+        self._finish(pick)
+        return self.ranges
+
+
+class CalibrationMethod:
+    MinMax, Entropy, Percentile = 0, 1, 2
+
+
+class QuantFormat:
+    QOperator, QDQ = 0, 1
+
+
+class QuantType:
+    QInt8, QUInt8 = 0, 1
+
+
+class CalibrationDataReader:
+    """Iterator of feed dicts for quantize_static: subclass and implement get_next() (None when exhausted)."""
+
+    def get_next(self) -> Optional[Dict[str, np.ndarray]]:
+        raise NotImplementedError
+
+    def __iter__(self):
+        return self
+
+    def __next__(self):
+        feeds = self.get_next()
+        if feeds is None:
+            raise StopIteration
+        return feeds
+
+
 def quantize_static(model_input, calibration_feeds: Iterable[Dict[str, np.ndarray]], model_output: Optional[str] = None,
-                    op_types: Sequence[str] = ("MatMul", "Gemm", "Conv"), per_channel: bool = False) -> ol.Model:
-    """QDQ format: uint8 asymmetric activations, int8 symmetric weights (per tensor, or per output channel)."""
+                    op_types: Sequence[str] = ("MatMul", "Gemm", "Conv"), per_channel: bool = False,
+                    calibrate_method: int = CalibrationMethod.MinMax, percentile: float = 99.999) -> ol.Model:
+    """QDQ format: uint8 asymmetric activations, int8 symmetric weights (per tensor, or per output channel).  The activation
+    ranges come from the extremes (MinMax), or from a histogram cut by KL divergence (Entropy) or by mass (Percentile)."""
     model = _load(model_input)
     g = model.graph
     inits = {t.name: t for t in g.initializers}
     targets = [n for n in g.nodes if n.op_type in op_types and n.domain == ""]
     acts = [n.inputs[0] for n in targets if n.inputs[0] not in inits]
-    calib = MinMaxCalibrator(model, acts)
+    if calibrate_method == CalibrationMethod.Entropy:
+        calib = EntropyCalibrator(model, acts)
+    elif calibrate_method == CalibrationMethod.Percentile:
+        calib = PercentileCalibrator(model, acts, percentile)
+    else:
+        calib = MinMaxCalibrator(model, acts)
     for feeds in calibration_feeds:
         calib.collect(feeds)
+    if calibrate_method != CalibrationMethod.MinMax:
+        calib.compute_ranges()
     new_nodes: List[ol.Node] = []
     qdq_of: Dict[str, str] = {}
     for n in g.nodes:

@@ -236,3 +236,90 @@ def test_ort_format_round_trip_and_conversion_tool(tmp_path):
     np.testing.assert_allclose(conv.run(None, feeds)[0], ref.run(None, feeds)[0], rtol=1e-6, atol=1e-6)
     with pytest.raises(Exception):
         ort.InferenceSession(buf[:60], providers=["CPUExecutionProvider"])
+
+
+def test_entropy_and_percentile_calibration_and_bnb4_quantizer():
+    """Histogram calibrators cut outliers that min-max keeps; NF4 / FP4 weights run through MatMulBnb4
+    (reference: onnxruntime/python/tools/quantization/calibrate.py, matmul_bnb4_quantizer.py)."""
+    import numpy as np
+    import onnxruntime_b200 as ort
+    from onnxruntime_b200 import onnx_lite as ol
+    from onnxruntime_b200.quantization import (CalibrationDataReader, CalibrationMethod, MatMulBnb4Quantizer, dequantize_bnb4, quantize_bnb4,
+                                               quantize_static)
+    model, rng = _two_layer_mlp()
+    x = rng.standard_normal((64, 16)).astype(np.float32)
+    (ref,) = ort.InferenceSession(model, providers=["CPUExecutionProvider"]).run(None, {"x": x})
+    spiky = x.copy()
+    spiky[0, 0] = 400.0          # one outlier: min-max stretches the input range over it
+
+    class Reader(CalibrationDataReader):
+        def __init__(self):
+            self.items = iter([{"x": spiky}, {"x": x}])
+
+        def get_next(self):
+            return next(self.items, None)
+
+    errs = {}
+    for method in (CalibrationMethod.MinMax, CalibrationMethod.Entropy, CalibrationMethod.Percentile):
+        q = quantize_static(model, Reader(), calibrate_method=method, percentile=99.9)
+        (y,) = ort.InferenceSession(q.serialize(), providers=["CPUExecutionProvider"]).run(None, {"x": x})
+        errs[method] = float(np.abs(y - ref).max() / np.abs(ref).max())
+    assert errs[CalibrationMethod.Entropy] < errs[CalibrationMethod.MinMax] and errs[CalibrationMethod.Percentile] < errs[CalibrationMethod.MinMax]
+    assert errs[CalibrationMethod.Entropy] < 0.1
+    # NF4 round trip and the rewritten graph
+    w = rng.standard_normal((16, 24)).astype(np.float32)
+    for qt in (0, 1):
+        packed, absmax = quantize_bnb4(w, qt, 32)
+        back = dequantize_bnb4(packed, absmax, 16, 24, qt, 32)
+        assert np.abs(back - w).max() < (0.2 if qt == 1 else 0.35) * np.abs(w).max()
+    qm = MatMulBnb4Quantizer(model, quant_type=1, block_size=32, nodes_to_exclude=["fc2"]).process()
+    assert [n.op_type for n in qm.graph.nodes] == ["MatMulBnb4", "Relu", "MatMul"]
+    (y,) = ort.InferenceSession(qm.serialize(), providers=["CPUExecutionProvider"]).run(None, {"x": x})
+    assert np.abs(y - ref).max() < 0.25 * np.abs(ref).max()
+
+
+def test_offline_tuning_profile_explorer_and_io_binding_helper(tmp_path, capsys):
+    import json
+    import numpy as np
+    import torch
+    import onnxruntime_b200 as ort
+    from onnxruntime_b200 import onnx_lite as ol
+    from onnxruntime_b200.tools import offline_tuning, profile_explorer
+    from onnxruntime_b200.transformers.io_binding_helper import CudaSession, IOBindingHelper, TypeHelper
+    model, rng = _two_layer_mlp()
+    path = tmp_path / "m.onnx"
+    path.write_bytes(model)
+    results = [{"ep": "CUDAExecutionProvider", "results": {"Gemm": {"8x16x16": 3}}, "validators": {"arch": "sm_100a"}}]
+    (tmp_path / "t.json").write_text(json.dumps(results))
+    assert offline_tuning.main(["embed", str(tmp_path / "tuned.onnx"), str(path), str(tmp_path / "t.json")]) == 0
+    assert offline_tuning.extract(ol.load_model(str(tmp_path / "tuned.onnx"))) == results
+    assert offline_tuning.main(["extract", str(tmp_path / "tuned.onnx"), str(tmp_path / "out.json")]) == 0
+    assert json.loads((tmp_path / "out.json").read_text()) == results
+    assert offline_tuning.main(["extract", str(path), str(tmp_path / "none.json")]) == 1
+    # a profile of two runs -> per-operator table
+    so = ort.SessionOptions()
+    so.enable_profiling = True
+    so.profile_file_prefix = str(tmp_path / "prof")
+    sess = ort.InferenceSession(model, so, providers=["CPUExecutionProvider"])
+    x = rng.standard_normal((4, 16)).astype(np.float32)
+    sess.run(None, {"x": x})
+    sess.run(None, {"x": x})
+    prof = sess.end_profiling()
+    rows = profile_explorer.summarise(profile_explorer.load_events(prof))
+    by_op = {r[0]: r for r in rows}
+    assert by_op["MatMul"][2] % 2 == 0 and by_op["MatMul"][2] >= 2 and abs(sum(r[5] for r in rows) - 100.0) < 1e-6
+    assert profile_explorer.main([prof, "--csv", str(tmp_path / "p.csv"), "--top", "3"]) == 0
+    assert "MatMul" in capsys.readouterr().out and (tmp_path / "p.csv").read_text().startswith("name,provider")
+    # io binding helpers on the CPU device
+    assert TypeHelper.get_input_type(sess, "x") == "tensor(float)" and TypeHelper.ort_type_to_torch_type("tensor(float16)") == torch.float16
+    assert TypeHelper.numpy_type_to_torch_type(np.int64) == torch.int64 and TypeHelper.torch_type_to_numpy_type(torch.float32) == np.float32
+    plain = ort.InferenceSession(model, providers=["CPUExecutionProvider"])
+    out_name = plain.get_outputs()[0].name
+    (ref,) = plain.run(None, {"x": x})
+    bufs = IOBindingHelper.get_output_buffers(plain, {out_name: ref.shape}, "cpu")
+    binding = IOBindingHelper.prepare_io_binding(plain, {"x": torch.from_numpy(x)}, bufs)
+    plain.run_with_iobinding(binding)
+    np.testing.assert_allclose(bufs[out_name].numpy(), ref, rtol=1e-6)
+    cs = CudaSession(plain, torch.device("cpu"))
+    cs.allocate_buffers({out_name: ref.shape})
+    np.testing.assert_allclose(cs.infer({"x": torch.from_numpy(x)})[out_name].numpy(), ref, rtol=1e-6)
