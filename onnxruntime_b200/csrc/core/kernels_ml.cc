@@ -94,7 +94,8 @@ std::vector<double> AttrDoubles(const Node& n, const std::string& name) {
 // ------------------------------------------------------------------------------------------------ tree ensembles
 struct TreeEnsemble {
   struct TreeNode {
-    int mode = 0;  // 0 leaf, 1 <=, 2 <, 3 >=, 4 >, 5 ==, 6 !=
+    int mode = 0;  // 0 leaf, 1 <=, 2 <, 3 >=, 4 >, 5 ==, 6 !=, 7 member of `members`
+    std::vector<double> members;
     int64_t feature = 0;
     double value = 0;
     int64_t yes = -1, no = -1;  // indices into `nodes`
@@ -179,6 +180,7 @@ struct TreeEnsemble {
             case 3: go = v >= t.value; break;
             case 4: go = v > t.value; break;
             case 5: go = v == t.value; break;
+            case 7: go = std::find(t.members.begin(), t.members.end(), v) != t.members.end(); break;
             default: go = v != t.value; break;
           }
         }
@@ -197,6 +199,96 @@ struct TreeEnsemble {
     if (aggregate == 1 && !roots.empty())
       for (auto& v : *out) v /= static_cast<double>(roots.size());
   }
+};
+
+// ai.onnx.ml TreeEnsemble (opset 5): one operator for regression and classification scores, with tensor-valued
+// attributes; interior nodes and leaves are numbered separately (nodes_trueleafs / nodes_falseleafs say which array a
+// child index points into), set membership is a node mode, aggregate and post transform are integer codes.
+class TreeEnsembleV5Kernel final : public OpKernel {
+ public:
+  explicit TreeEnsembleV5Kernel(const OpKernelInfo& info) : OpKernel(info) {
+    const Node& n = info.node;
+    auto doubles = [&](const char* name) {
+      at::Tensor t = n.attr_tensor(name);
+      std::vector<double> v;
+      if (t.defined()) {
+        t = t.to(at::kCPU, at::kDouble).contiguous().reshape({-1});
+        v.assign(t.data_ptr<double>(), t.data_ptr<double>() + t.numel());
+      }
+      return v;
+    };
+    const std::vector<double> splits = doubles("nodes_splits"), weights = doubles("leaf_weights"), member_values = doubles("membership_values");
+    std::vector<int64_t> modes;
+    {
+      at::Tensor m = n.attr_tensor("nodes_modes");
+      ORTB_ENFORCE_ARG(m.defined(), "TreeEnsemble: nodes_modes is required");
+      m = m.to(at::kCPU, at::kLong).contiguous().reshape({-1});
+      modes.assign(m.data_ptr<int64_t>(), m.data_ptr<int64_t>() + m.numel());
+    }
+    const std::vector<int64_t> features = n.attr_ints("nodes_featureids"), yes = n.attr_ints("nodes_truenodeids"), no = n.attr_ints("nodes_falsenodeids"),
+                               yes_leaf = n.attr_ints("nodes_trueleafs"), no_leaf = n.attr_ints("nodes_falseleafs"),
+                               miss = n.attr_ints("nodes_missing_value_tracks_true"), targets = n.attr_ints("leaf_targetids"),
+                               roots = n.attr_ints("tree_roots");
+    const size_t M = modes.size(), L = weights.size();
+    ORTB_ENFORCE_ARG(splits.size() == M && features.size() == M && yes.size() == M && no.size() == M && yes_leaf.size() == M && no_leaf.size() == M &&
+                         targets.size() == L,
+                     "TreeEnsemble: the nodes_* / leaf_* attributes differ in length");
+    static const int mode_map[7] = {1, 2, 3, 4, 5, 6, 7};
+    trees_.nodes.resize(M + L);
+    size_t member_pos = 0;
+    for (size_t i = 0; i < M; ++i) {
+      auto& t = trees_.nodes[i];
+      ORTB_ENFORCE_ARG(modes[i] >= 0 && modes[i] <= 6, "TreeEnsemble: unknown node mode ", modes[i]);
+      t.mode = mode_map[modes[i]];
+      t.feature = features[i];
+      t.value = splits[i];
+      t.missing_true = i < miss.size() && miss[i] != 0;
+      auto child = [&](int64_t idx, int64_t is_leaf) {
+        const int64_t limit = is_leaf ? static_cast<int64_t>(L) : static_cast<int64_t>(M);
+        ORTB_ENFORCE_ARG(idx >= 0 && idx < limit, "TreeEnsemble: a branch points to a node that does not exist");
+        return is_leaf ? static_cast<int64_t>(M) + idx : idx;
+      };
+      t.yes = child(yes[i], yes_leaf[i]);
+      t.no = child(no[i], no_leaf[i]);
+      if (t.mode == 7) {  // this node's set: the values up to the next NaN
+        while (member_pos < member_values.size() && !std::isnan(member_values[member_pos])) t.members.push_back(member_values[member_pos++]);
+        ++member_pos;
+      }
+    }
+    for (size_t j = 0; j < L; ++j) trees_.nodes[M + j].weights.emplace_back(targets[j], weights[j]);
+    for (int64_t r : roots) {
+      // a tree that is a single leaf names the leaf array when there are no interior nodes at all
+      ORTB_ENFORCE_ARG(r >= 0 && r < static_cast<int64_t>(M == 0 ? L : M), "TreeEnsemble: tree root out of range");
+      trees_.roots.push_back(M == 0 ? static_cast<int64_t>(M) + r : r);
+    }
+    trees_.n_outputs = n.attr_i("n_targets", 1);
+    static const int agg_map[4] = {1, 0, 2, 3};  // attribute: 0 AVERAGE, 1 SUM, 2 MIN, 3 MAX
+    const int64_t agg = n.attr_i("aggregate_function", 1);
+    ORTB_ENFORCE_ARG(agg >= 0 && agg <= 3, "TreeEnsemble: unknown aggregate_function ", agg);
+    trees_.aggregate = agg_map[agg];
+    static const Post posts[5] = {Post::NONE, Post::SOFTMAX, Post::LOGISTIC, Post::SOFTMAX_ZERO, Post::PROBIT};
+    const int64_t post = n.attr_i("post_transform", 0);
+    ORTB_ENFORCE_ARG(post >= 0 && post <= 4, "TreeEnsemble: unknown post_transform ", post);
+    trees_.post = posts[post];
+  }
+
+  void Compute(Ctx& ctx) const override {
+    const at::Tensor& x_in = ctx.RequiredInput(0);
+    at::Tensor x = HostDouble(x_in.dim() == 1 ? x_in.unsqueeze(0) : x_in);
+    ORTB_ENFORCE_ARG(x.dim() == 2, "TreeEnsemble: input must be [N, features]");
+    const int64_t N = x.size(0), F = x.size(1), T = trees_.n_outputs;
+    at::Tensor y = at::empty({N, T}, at::kDouble);
+    std::vector<double> s;
+    for (int64_t i = 0; i < N; ++i) {
+      trees_.Evaluate(x.data_ptr<double>() + i * F, F, &s);
+      std::vector<double> z = PostProcess(s, trees_.post, -1);
+      for (int64_t k = 0; k < T; ++k) y.data_ptr<double>()[i * T + k] = z[static_cast<size_t>(k)];
+    }
+    ctx.SetOutput(0, y.to(x_in.is_floating_point() ? x_in.scalar_type() : at::kFloat).to(x_in.device()));
+  }
+
+ private:
+  TreeEnsemble trees_;
 };
 
 class TreeEnsembleKernel final : public OpKernel {
@@ -513,6 +605,15 @@ void RegisterMlKernels(KernelRegistry& r) {
     d.since_min = 1;
     d.since_max = kMax;
     d.factory = [classifier](const OpKernelInfo& info) { return std::make_unique<TreeEnsembleKernel>(info, classifier); };
+    r.Register(std::move(d));
+  }
+  {
+    KernelDef d;
+    d.domain = ML;
+    d.op_type = "TreeEnsemble";
+    d.since_min = 5;
+    d.since_max = kMax;
+    d.factory = [](const OpKernelInfo& info) { return std::make_unique<TreeEnsembleV5Kernel>(info); };
     r.Register(std::move(d));
   }
   r.RegisterFn(ML, "LinearRegressor", 1, kMax, [](Ctx& ctx) { LinearImpl(ctx, false); });

@@ -318,3 +318,31 @@ def test_zipmap_returns_a_list_of_dicts():
                         [ol.make_tensor_value_info("label", ol.TensorProto.STRING, None), ol.make_tensor_value_info("probs", 0, None)])
     label, probs = ort.InferenceSession(model, providers=["CPUExecutionProvider"]).run(None, {"X": np.array([[2.0, 0.0], [0.0, 3.0]], np.float32)})
     assert label.tolist() == ["a", "b"] and probs[0]["a"] > 0.9 and probs[1]["b"] > 0.9
+
+
+def test_tree_ensemble_opset5_spec_examples():
+    """ai.onnx.ml TreeEnsemble (opset 5): one tree with set-membership nodes, and one with plain <= splits (the attribute
+    sets of the specification's examples; expected values worked out by hand)."""
+    from onnxruntime_b200 import onnx_lite as ol
+    import onnxruntime_b200 as ort
+    def run(x, **attrs):
+        node = ol.make_node("TreeEnsemble", ["X"], ["Y"], domain=ML, **attrs)
+        g = ol.make_graph([node], "g", [ol.make_tensor_value_info("X", ol.TensorProto.FLOAT, list(x.shape))], [ol.make_tensor_value_info("Y", 0, None)])
+        m = ol.make_model(g, opset=17)
+        m.opset_imports[ML] = 5
+        return ort.InferenceSession(m.serialize(), providers=["CPUExecutionProvider"]).run(None, {"X": x})[0]
+    x = np.array([1.2, 3.4, -0.12, 12, 7, 9], np.float32).reshape(-1, 1)
+    y = run(x, n_targets=2, aggregate_function=1, membership_values=np.array([1.2, 3.7, 8, 9, np.nan, 12, 7, np.nan], np.float32),
+            nodes_missing_value_tracks_true=[0, 0, 0], nodes_hitrates=np.array([1, 1, 1], np.float32), post_transform=0, tree_roots=[0],
+            nodes_modes=np.array([0, 6, 6], np.uint8), nodes_featureids=[0, 0, 0], nodes_splits=np.array([11, 232344.0, np.nan], np.float32),
+            nodes_trueleafs=[0, 1, 1], nodes_truenodeids=[1, 0, 1], nodes_falseleafs=[1, 0, 1], nodes_falsenodeids=[2, 2, 3],
+            leaf_targetids=[0, 1, 0, 1], leaf_weights=np.array([1, 10, 1000, 100], np.float32))
+    # node 0: x <= 11 ? node 1 : leaf 2;  node 1: x in {1.2, 3.7, 8, 9} ? leaf 0 : node 2;  node 2: x in {12, 7} ? leaf 1 : leaf 3
+    np.testing.assert_array_equal(y, [[1, 0], [0, 100], [0, 100], [1000, 0], [0, 10], [1, 0]])
+    x = np.array([[1.2, 3.4, -0.12], [-0.67, 0.88, 1.29], [4.5, 0.9, 2.11]], np.float32)
+    y = run(x, n_targets=2, aggregate_function=1, nodes_missing_value_tracks_true=[0, 0, 0], post_transform=0, tree_roots=[0],
+            nodes_modes=np.array([0, 0, 0], np.uint8), nodes_featureids=[0, 0, 0], nodes_splits=np.array([3.14, 1.2, 4.2], np.float32),
+            nodes_trueleafs=[0, 1, 1], nodes_truenodeids=[1, 0, 1], nodes_falseleafs=[0, 1, 1], nodes_falsenodeids=[2, 2, 3],
+            leaf_targetids=[0, 1, 0, 1], leaf_weights=np.array([5.23, 12.12, -12.23, 7.21], np.float32))
+    # node 0: x0 <= 3.14 ? node 1 : node 2;  node 1: x0 <= 1.2 ? leaf 0 : leaf 2;  node 2: x0 <= 4.2 ? leaf 1 : leaf 3
+    np.testing.assert_allclose(y, [[5.23, 0], [5.23, 0], [0, 7.21]], rtol=1e-6)
