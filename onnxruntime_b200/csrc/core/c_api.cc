@@ -1,4 +1,5 @@
 // Implementation of ortb200_c_api.h over the C++ session (no Python involved).
+#include "string_table.h"
 #include "ortb200_c_api.h"
 
 #include <ATen/ATen.h>
@@ -25,6 +26,7 @@ struct ortb200_session {
 struct ortb200_value {
   at::Tensor tensor;
   at::Tensor host;   // host copy made on request
+  bool is_string = false;  // tensor holds ids of the string table
 };
 
 namespace {
@@ -319,6 +321,7 @@ void RunCommon(ortb200_session* session, const ortb::RunOptions& ro, const char*
     ORTB_ENFORCE_ARG(res[i].t.defined(), "output ", i, " is not a tensor (sequences are not exposed by the C API)");
     auto* v = new ortb200_value();
     v->tensor = res[i].t.is_contiguous() ? res[i].t : res[i].t.contiguous();
+    v->is_string = res[i].is_string;
     for (size_t k = 0; k < num_inputs; ++k)
       if (feeds[k].t.defined() && feeds[k].t.numel() > 0 && v->tensor.data_ptr() == feeds[k].t.data_ptr()) v->tensor = v->tensor.clone();
     outputs[i] = v;
@@ -636,6 +639,96 @@ ORTB200_EXPORT int ortb200_create_tensor(int32_t elem_type, const int64_t* dims,
     *out = v;
   });
 }
+// ---- tensors of strings (reference: CreateTensorAsOrtValue with ONNX_TENSOR_ELEMENT_DATA_TYPE_STRING, FillStringTensor,
+// GetStringTensorDataLength / GetStringTensorContent / GetStringTensorElement)
+ORTB200_EXPORT int ortb200_create_string_tensor(const char* const* strings, const int64_t* dims, int32_t ndim, ortb200_value** out) {
+  return Guarded([&] {
+    ORTB_ENFORCE_ARG(out != nullptr && ndim >= 0 && ndim <= 8 && (ndim == 0 || dims != nullptr), "bad shape arguments");
+    std::vector<int64_t> shape(dims, dims + ndim);
+    int64_t n = 1;
+    for (int64_t d : shape) {
+      ORTB_ENFORCE_ARG(d >= 0, "negative dimension");
+      n *= d;
+    }
+    ORTB_ENFORCE_ARG(n == 0 || strings != nullptr, "strings is null");
+    std::vector<std::string> items;
+    for (int64_t i = 0; i < n; ++i) {
+      ORTB_ENFORCE_ARG(strings[i] != nullptr, "string ", i, " is null");
+      items.emplace_back(strings[i]);
+    }
+    auto* v = new ortb200_value();
+    v->tensor = ortb::InternStrings(items, shape);
+    v->is_string = true;
+    *out = v;
+  });
+}
+ORTB200_EXPORT int ortb200_value_is_string(const ortb200_value* value, int* out) {
+  return Guarded([&] {
+    ORTB_ENFORCE_ARG(value && out, "null argument");
+    *out = value->is_string ? 1 : 0;
+  });
+}
+ORTB200_EXPORT int ortb200_value_string_count(const ortb200_value* value, size_t* out) {
+  return Guarded([&] {
+    ORTB_ENFORCE_ARG(value && out && value->is_string, "not a tensor of strings");
+    *out = static_cast<size_t>(value->tensor.numel());
+  });
+}
+ORTB200_EXPORT int ortb200_value_string_element(const ortb200_value* value, size_t index, const char** out, size_t* length) {
+  return Guarded([&] {
+    ORTB_ENFORCE_ARG(value && out && value->is_string, "not a tensor of strings");
+    ORTB_ENFORCE_ARG(index < static_cast<size_t>(value->tensor.numel()), "string index out of range");
+    at::Tensor ids = value->tensor.to(at::kCPU, at::kLong).contiguous().reshape({-1});
+    const std::string& s = ortb::StringOfId(ids.data_ptr<int64_t>()[index]);  // the table never frees or moves a string
+    *out = s.c_str();
+    if (length) *length = s.size();
+  });
+}
+ORTB200_EXPORT int ortb200_value_shape(const ortb200_value* value, int64_t* dims, int32_t* ndim) {
+  return Guarded([&] {
+    ORTB_ENFORCE_ARG(value && dims && ndim && value->tensor.defined(), "null argument");
+    ORTB_ENFORCE_ARG(value->tensor.dim() <= 8, "more than 8 dimensions");
+    *ndim = static_cast<int32_t>(value->tensor.dim());
+    for (int64_t i = 0; i < value->tensor.dim(); ++i) dims[i] = value->tensor.size(i);
+  });
+}
+// Run with runtime-owned values as inputs (tensors of strings can only be fed this way).
+ORTB200_EXPORT int ortb200_run_with_values(ortb200_session* session, const ortb200_run_options* options, const char* const* input_names,
+                                           ortb200_value* const* inputs, size_t num_inputs, const char* const* output_names, size_t num_outputs,
+                                           ortb200_value** outputs) {
+  return Guarded([&] {
+    ORTB_ENFORCE_ARG(session && outputs && (num_inputs == 0 || (input_names && inputs)), "null argument");
+    std::vector<std::string> in_names, out_names;
+    std::vector<ortb::Value> feeds;
+    for (size_t i = 0; i < num_inputs; ++i) {
+      ORTB_ENFORCE_ARG(input_names[i] && inputs[i], "input ", i, " is null");
+      in_names.emplace_back(input_names[i]);
+      ortb::Value v;
+      v.t = inputs[i]->tensor;
+      v.is_string = inputs[i]->is_string;
+      feeds.push_back(std::move(v));
+    }
+    if (output_names != nullptr) {
+      for (size_t i = 0; i < num_outputs; ++i) out_names.emplace_back(output_names[i]);
+    } else {
+      ORTB_ENFORCE_ARG(num_outputs == session->output_names.size(), "num_outputs must equal the model's output count");
+    }
+    ortb::RunOptions defaults;
+    std::vector<ortb::Value> res = session->impl->Run(options ? options->ro : defaults, in_names, feeds, out_names);
+    ORTB_ENFORCE(res.size() == num_outputs, "unexpected number of outputs");
+    for (size_t i = 0; i < num_outputs; ++i) outputs[i] = nullptr;
+    for (size_t i = 0; i < num_outputs; ++i) {
+      ORTB_ENFORCE_ARG(res[i].t.defined(), "output ", i, " is not a tensor (sequences and maps are not exposed by the C API)");
+      auto* v = new ortb200_value();
+      v->tensor = res[i].t.contiguous();
+      v->is_string = res[i].is_string;
+      for (size_t k = 0; k < num_inputs; ++k)
+        if (v->tensor.numel() > 0 && v->tensor.data_ptr() == inputs[k]->tensor.data_ptr()) v->tensor = v->tensor.clone();
+      outputs[i] = v;
+    }
+  });
+}
+
 ORTB200_EXPORT int ortb200_value_byte_size(const ortb200_value* value, size_t* out) {
   return Guarded([&] {
     ORTB_ENFORCE_ARG(value && out, "null argument");

@@ -160,6 +160,19 @@ int ortb200_value_copy_from_host(ortb200_value* value, const void* src, size_t b
 int ortb200_value_copy_to_host(ortb200_value* value, void* dst, size_t bytes);
 int ortb200_value_byte_size(const ortb200_value* value, size_t* out);
 
+/* Tensors of strings.  ortb200_create_string_tensor copies the NUL-terminated strings (row-major, product(dims) of them).
+ * An output of string type answers 1 to ortb200_value_is_string; its elements are read one by one, the returned pointers
+ * stay valid for the life of the process.  ortb200_value_tensor on such a value shows the runtime's internal ids.
+ * ortb200_run_with_values runs with runtime-owned values as inputs, which is how tensors of strings are fed. */
+int ortb200_create_string_tensor(const char* const* strings, const int64_t* dims, int32_t ndim, ortb200_value** out);
+int ortb200_value_is_string(const ortb200_value* value, int* out);
+int ortb200_value_string_count(const ortb200_value* value, size_t* out);
+int ortb200_value_string_element(const ortb200_value* value, size_t index, const char** out, size_t* length);
+int ortb200_value_shape(const ortb200_value* value, int64_t* dims /* room for 8 */, int32_t* ndim);
+int ortb200_run_with_values(ortb200_session* session, const ortb200_run_options* options, const char* const* input_names,
+                            ortb200_value* const* inputs, size_t num_inputs, const char* const* output_names, size_t num_outputs,
+                            ortb200_value** outputs);
+
 /* Environment */
 int ortb200_available_provider_count(size_t* out);
 int ortb200_available_provider_name(size_t index, const char** out);

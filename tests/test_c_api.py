@@ -226,3 +226,79 @@ def test_c_program_uses_options_metadata_and_io_binding(tmp_path):
     assert lines[7] == "bound 1 y 0 2 10 6"
     assert lines[8] == "bound2 2 2 6"
     assert lines[9] == "avail 1 CPUExecutionProvider"
+
+
+C_SOURCE_STRINGS = r"""
+#include <stdio.h>
+#include <string.h>
+#include "ortb200_c_api.h"
+
+#define CHECK(x) do { int rc_ = (x); if (rc_ != 0) { printf("ERR %d %s\n", rc_, ortb200_last_error()); return 1; } } while (0)
+
+int main(int argc, char** argv) {
+  ortb200_session* s = NULL;
+  CHECK(ortb200_create_session(argv[1], NULL, 0, "CPUExecutionProvider", 0, NULL, &s));
+  const char* words[] = {"Monday", "tuesday", "WEDNESDAY", "monday"};
+  int64_t dims[1] = {4};
+  ortb200_value* in = NULL;
+  CHECK(ortb200_create_string_tensor(words, dims, 1, &in));
+  int is_str = 0;
+  CHECK(ortb200_value_is_string(in, &is_str));
+  const char* names[] = {"x"};
+  ortb200_value* ins[] = {in};
+  ortb200_value* outs[2] = {NULL, NULL};
+  CHECK(ortb200_run_with_values(s, NULL, names, ins, 1, NULL, 2, outs));
+  size_t n = 0;
+  CHECK(ortb200_value_is_string(outs[0], &is_str));
+  CHECK(ortb200_value_string_count(outs[0], &n));
+  printf("strings %d %zu:", is_str, n);
+  for (size_t i = 0; i < n; ++i) {
+    const char* p; size_t len;
+    CHECK(ortb200_value_string_element(outs[0], i, &p, &len));
+    printf(" %s/%zu", p, len);
+  }
+  printf("\n");
+  int64_t shape[8]; int32_t nd = 0;
+  CHECK(ortb200_value_shape(outs[1], shape, &nd));
+  CHECK(ortb200_value_is_string(outs[1], &is_str));
+  ortb200_tensor_view v;
+  CHECK(ortb200_value_tensor(outs[1], 1, &v));
+  printf("ids %d %d %lld:", is_str, nd, (long long)shape[0]);
+  for (int64_t i = 0; i < shape[0]; ++i) printf(" %lld", (long long)((int64_t*)v.data)[i]);
+  printf("\n");
+  int rc = ortb200_value_string_count(outs[1], &n);
+  printf("not-strings %d\n", rc != 0);
+  ortb200_release_value(in); ortb200_release_value(outs[0]); ortb200_release_value(outs[1]);
+  ortb200_release_session(s);
+  return 0;
+}
+"""
+
+
+def test_c_program_feeds_and_reads_string_tensors(tmp_path):
+    T = ol.TensorProto
+    nodes = [ol.make_node("StringNormalizer", ["x"], ["y"], case_change_action="UPPER", stopwords=["monday"], is_case_sensitive=0),
+             ol.make_node("LabelEncoder", ["y"], ["ids"], domain="ai.onnx.ml", keys_strings=["TUESDAY", "WEDNESDAY"], values_int64s=[2, 3], default_int64=-1)]
+    g = ol.make_graph(nodes, "g", [ol.make_tensor_value_info("x", T.STRING, ["n"])],
+                      [ol.make_tensor_value_info("y", T.STRING, None), ol.make_tensor_value_info("ids", T.INT64, None)])
+    m = ol.make_model(g, opset=17)
+    m.opset_imports["ai.onnx.ml"] = 4
+    model = tmp_path / "m.onnx"
+    model.write_bytes(m.serialize())
+    src = tmp_path / "client.c"
+    src.write_text(C_SOURCE_STRINGS)
+    exe = tmp_path / "client"
+    import torch
+    torch_lib = os.path.join(os.path.dirname(torch.__file__), "lib")
+    cmd = ["gcc", "-std=c99", "-o", str(exe), str(src), f"-I{INC}", f"-L{LIB}", "-lortb200", f"-Wl,-rpath,{LIB}",
+           f"-Wl,-rpath,{torch_lib}", f"-Wl,-rpath-link,{torch_lib}", f"-Wl,-rpath-link,{LIB}"]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    assert res.returncode == 0, res.stderr[-3000:]
+    env = dict(os.environ)
+    env.pop("PYTHONPATH", None)
+    run = subprocess.run([str(exe), str(model)], capture_output=True, text=True, env=env, timeout=300)
+    assert run.returncode == 0, run.stdout[-2000:] + run.stderr[-2000:]
+    lines = run.stdout.strip().splitlines()
+    assert lines[0] == "strings 1 2: TUESDAY/7 WEDNESDAY/9"
+    assert lines[1] == "ids 0 1 2: 2 3"
+    assert lines[2] == "not-strings 1"
