@@ -46,6 +46,9 @@ at::Tensor FusedActivation(const at::Tensor& x, const std::string& name, const s
   if (name == "Softplus") return at::softplus(x);
   if (name == "Elu") return at::elu(x, p(0, 1.0f));
   if (name == "Gelu") return at::gelu(x);
+  if (name == "Softsign") return x / (1 + x.abs());
+  if (name == "ThresholdedRelu") return at::where(x > p(0, 1.0f), x, at::zeros_like(x));
+  if (name == "Selu") return p(2, 1.05070102f) * at::where(x > 0, x, p(0, 1.67326319f) * (at::exp(x) - 1));
   ORTB_THROW(INVALID_ARGUMENT, "unsupported fused activation '", name, "'");
 }
 
@@ -253,6 +256,18 @@ void RegisterContribKernels3(KernelRegistry& r) {
       params.push_back(n.attr_f("activation_beta", 0.f));
     }
     ctx.SetOutput(0, FusedActivation(FusedMatMulCore(ctx), n.attr_s("activation", ""), params));
+  });
+  // FusedGemm (contrib_ops/cpu/fused_gemm.cc): Gemm followed by an activation
+  r.RegisterFn(MS, "FusedGemm", 1, kMax, [](Ctx& ctx) {
+    const Node& n = ctx.node();
+    at::Tensor a = ctx.RequiredInput(0), b = ctx.RequiredInput(1);
+    if (n.attr_i("transA", 0)) a = a.t();
+    if (n.attr_i("transB", 0)) b = b.t();
+    at::Tensor y = at::matmul(a, b) * n.attr_f("alpha", 1.f);
+    if (ctx.HasInput(2)) y = y + ctx.Input(2) * n.attr_f("beta", 1.f);
+    const std::vector<float> params = {n.attr_f("activation_alpha", n.attr_s("activation", "") == "LeakyRelu" ? 0.01f : (n.attr_s("activation", "") == "HardSigmoid" ? 0.2f : (n.attr_s("activation", "") == "Selu" ? 1.67326319f : 1.0f))),
+                                       n.attr_f("activation_beta", 0.5f), n.attr_f("activation_gamma", 1.05070102f)};
+    ctx.SetOutput(0, FusedActivation(y, n.attr_s("activation", ""), params));
   });
   r.RegisterFn(MS, "GemmFastGelu", 1, kMax, [](Ctx& ctx) {
     at::Tensor y = at::matmul(ctx.RequiredInput(0), ctx.RequiredInput(1));

@@ -170,8 +170,10 @@ const std::vector<Pass>& AllPasses() {
     AddBasicPasses(v);
     AddFusionPasses(v);
     AddMorePasses(v);
+    AddQdqPrepPasses(v);  // every quantised node unit gets its own DequantizeLinear before the QDQ fusions look
     AddQdqPasses(v);  // after the transformer fusions: those match the un-simplified MatMul / Add / Softmax forms
     AddMorePasses2(v);  // MatMul scale / transpose folding and the conv fusions come last for the same reason
+    AddMorePasses3(v);
     AddGpuPasses(v);
     return v;
   }();

@@ -74,6 +74,8 @@ void AddGpuPasses(std::vector<Pass>& v);
 void AddMorePasses(std::vector<Pass>& v);
 void AddQdqPasses(std::vector<Pass>& v);
 void AddMorePasses2(std::vector<Pass>& v);
+void AddMorePasses3(std::vector<Pass>& v);
+void AddQdqPrepPasses(std::vector<Pass>& v);
 
 // Replace the nodes of `m` by `fused` (already added to the graph); rewires nothing else.
 void RemoveMatched(Graph& g, const Match& m);

@@ -330,7 +330,7 @@ void InferenceSession::ApplyThreadingAndWarnings() {
       "ep.context_file_path", "ep.context_embed_mode", "session.use_ort_model_bytes_directly", "session.strict_shape_type_inference",
       "session.qdqisint8allowed", "session.enable_dq_matmulnbits_fusion", "session.qdq_matmulnbits_accuracy_level",
       "session.dynamic_block_base", "session.force_spinning_stop", "session.collect_node_memory_stats_to_file",
-      "session.disable_quant_qdq", "ep.context_node_name_prefix"};
+      "session.disable_quant_qdq", "ep.context_node_name_prefix", "session.enable_quant_qdq_cleanup"};
   for (auto& kv : so_.config.entries) {
     if (kv.first.rfind("ortb200.", 0) == 0 || kv.first.rfind("ep.cuda.", 0) == 0) continue;
     if (!known.count(kv.first)) ORTB_LOG(logger_, kWarning) << "session config entry '" << kv.first << "' is not known to this runtime and is ignored";

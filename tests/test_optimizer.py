@@ -560,3 +560,94 @@ def test_allgather_matmul_fusion_on_graph_level():
     model = graph_model(nodes, [ol.make_tensor_value_info("x", T.FLOAT16, ["b", 16])], [ol.make_tensor_value_info("y", T.FLOAT16, None)],
                         [ol.make_tensor("w", w)])
     assert not C.optimize_model(model, 99, [], True, 2)[1].get("AllGatherMatMulFusion")
+
+
+def test_cast_chain_and_pre_shape_elimination():
+    nodes = [ol.make_node("Cast", ["h"], ["f"], to=T.FLOAT), ol.make_node("Cast", ["f"], ["d"], to=T.DOUBLE),
+             ol.make_node("Cast", ["f2"], ["s_in"], to=T.FLOAT16), ol.make_node("Shape", ["s_in"], ["s"]),
+             ol.make_node("Cast", ["h"], ["f2"], to=T.FLOAT), ol.make_node("Reshape", ["d", "s"], ["y"])]
+    h = rng.randn(3, 4).astype(np.float16)
+    model = graph_model([nodes[0], nodes[1], nodes[4], nodes[2], nodes[3], nodes[5]], [ol.make_tensor_value_info("h", T.FLOAT16, [3, 4])], Y)
+    before, after = both(model, {"h": h})
+    assert before["Cast"] == 4 and after == {"Cast": 1, "Shape": 1, "Reshape": 1}
+    # a narrowing first cast is kept: fp32 -> fp16 -> fp32 rounds
+    nodes = [ol.make_node("Cast", ["x"], ["a"], to=T.FLOAT16), ol.make_node("Cast", ["a"], ["y"], to=T.FLOAT)]
+    _, after = both(graph_model(nodes, X, Y), xs)
+    assert after == {"Cast": 2}
+
+
+def test_pad_fusion_into_conv_and_average_pool():
+    x = rng.randn(1, 3, 8, 8).astype(np.float32)
+    w = rng.randn(4, 3, 3, 3).astype(np.float32)
+    inputs = [ol.make_tensor_value_info("x", T.FLOAT, [1, 3, 8, 8])]
+    pads = ol.make_tensor("pads", np.array([0, 0, 1, 2, 0, 0, 2, 1], np.int64))
+    nodes = [ol.make_node("Pad", ["x", "pads"], ["p"], mode="constant"), ol.make_node("Conv", ["p", "w"], ["y"], pads=[1, 0, 0, 1])]
+    before, after = both(graph_model(nodes, inputs, Y, [pads, ol.make_tensor("w", w)]), {"x": x})
+    assert before == {"Pad": 1, "Conv": 1} and after == {"Conv": 1}
+    nodes = [ol.make_node("Pad", ["x", "pads"], ["p"], mode="constant"), ol.make_node("AveragePool", ["p"], ["y"], kernel_shape=[3, 3], count_include_pad=1)]
+    _, after = both(graph_model(nodes, inputs, Y, [pads]), {"x": x})
+    assert after == {"AveragePool": 1}
+    # pads that do not average in (count_include_pad = 0), a non-zero fill and padded batch / channel dims stay
+    for node, extra in ((ol.make_node("AveragePool", ["p"], ["y"], kernel_shape=[3, 3]), [pads]),
+                        (ol.make_node("Conv", ["p", "w"], ["y"]), [pads, ol.make_tensor("w", w), ol.make_tensor("v", np.array(1.5, np.float32))])):
+        pad_inputs = ["x", "pads"] + (["v"] if len(extra) == 3 else [])
+        _, after = both(graph_model([ol.make_node("Pad", pad_inputs, ["p"], mode="constant"), node], inputs, Y, extra), {"x": x})
+        assert after.get("Pad") == 1
+
+
+def test_matmul_batchnorm_fusion():
+    x2 = rng.randn(5, 16).astype(np.float32)
+    w = rng.randn(16, 6).astype(np.float32)
+    inits = [ol.make_tensor("w", w), c("scale", rng.rand(6) + 0.5), c("beta", rng.randn(6)), c("mean", rng.randn(6)), c("var", rng.rand(6) + 0.1)]
+    nodes = [ol.make_node("MatMul", ["x", "w"], ["m"]), ol.make_node("BatchNormalization", ["m", "scale", "beta", "mean", "var"], ["y"], epsilon=1e-3)]
+    before, after = both(graph_model(nodes, [ol.make_tensor_value_info("x", T.FLOAT, ["n", 16])], Y, inits), {"x": x2})
+    assert before == {"MatMul": 1, "BatchNormalization": 1} and after == {"Gemm": 1}
+
+
+def test_label_encoder_fusion():
+    nodes = [ol.make_node("LabelEncoder", ["x"], ["a"], domain="ai.onnx.ml", keys_int64s=[1, 2, 3], values_strings=["one", "two", "three"], default_string="none"),
+             ol.make_node("LabelEncoder", ["a"], ["y"], domain="ai.onnx.ml", keys_strings=["one", "three", "none"], values_floats=[1.5, 3.5, -1.0], default_float=9.0)]
+    g = ol.make_graph(nodes, "g", [ol.make_tensor_value_info("x", T.INT64, ["n"])], Y)
+    m = ol.make_model(g, opset=17)
+    m.opset_imports["ai.onnx.ml"] = 4
+    before, after = both(m.serialize(), {"x": np.array([1, 2, 3, 7], np.int64)})
+    assert before == {"LabelEncoder": 2} and after == {"LabelEncoder": 1}
+    out = ort.InferenceSession(m.serialize(), providers=["CPUExecutionProvider"]).run(None, {"x": np.array([1, 2, 3, 7], np.int64)})[0]
+    np.testing.assert_array_equal(out, np.array([1.5, 9.0, 3.5, -1.0], np.float32))
+
+
+def test_gemm_activation_fusion_and_shared_dequantize_is_duplicated():
+    x2 = rng.randn(5, 16).astype(np.float32)
+    inits = [ol.make_tensor("w", rng.randn(16, 6).astype(np.float32)), c("b", rng.randn(6))]
+    for act, attrs in (("Relu", {}), ("LeakyRelu", {"alpha": 0.2}), ("Selu", {}), ("HardSigmoid", {"alpha": 0.3, "beta": 0.4}), ("Softsign", {})):
+        nodes = [ol.make_node("Gemm", ["x", "w", "b"], ["g"], alpha=0.5), ol.make_node(act, ["g"], ["y"], **attrs)]
+        before, after = both(graph_model(nodes, [ol.make_tensor_value_info("x", T.FLOAT, ["n", 16])], Y, inits), {"x": x2})
+        assert after == {"FusedGemm": 1}, act
+    # one DequantizeLinear of a constant feeding two MatMuls: each consumer gets its own copy
+    wq = rng.randint(-100, 100, (16, 6)).astype(np.int8)
+    nodes = [ol.make_node("DequantizeLinear", ["wq", "s", "z"], ["wd"]), ol.make_node("MatMul", ["x", "wd"], ["a"]),
+             ol.make_node("MatMul", ["x", "wd"], ["b2"]), ol.make_node("Sub", ["a", "b2"], ["y"])]
+    model = graph_model(nodes, [ol.make_tensor_value_info("x", T.FLOAT, ["n", 16])], Y, [ol.make_tensor("wq", wq), c("s", 0.02), ol.make_tensor("z", np.array(0, np.int8))])
+    out, stats = C.optimize_model(model, 1, ["ConstantFolding", "CommonSubexpressionElimination"], False)
+    assert stats.get("EnsureUniqueDQForNodeUnit") == 1
+    assert [n["op_type"] for n in C.model_nodes(out)].count("DequantizeLinear") == 2
+
+
+def test_qdq_final_cleanup():
+    inits = [c("s", 0.05), ol.make_tensor("z", np.array(3, np.uint8))]
+    q = rng.randint(0, 255, (4, 8)).astype(np.uint8)
+    nodes = [ol.make_node("Transpose", ["q"], ["t"], perm=[1, 0]), ol.make_node("DequantizeLinear", ["t", "s", "z"], ["d"]),
+             ol.make_node("QuantizeLinear", ["d", "s", "z"], ["q2"]), ol.make_node("Transpose", ["q2"], ["y"], perm=[1, 0])]
+    model = graph_model(nodes, [ol.make_tensor_value_info("q", T.UINT8, [4, 8])], Y, inits)
+    before, after = both(model, {"q": q}, disabled=["TransposePairFusion"])
+    assert before["DequantizeLinear"] == 1 and "DequantizeLinear" not in after and "QuantizeLinear" not in after
+    # Q -> DQ stands for a rounding step: kept unless the session asks for the clean-up
+    nodes = [ol.make_node("Relu", ["x"], ["r"]), ol.make_node("QuantizeLinear", ["r", "s", "z"], ["qq"]), ol.make_node("DequantizeLinear", ["qq", "s", "z"], ["dd"]),
+             ol.make_node("Relu", ["dd"], ["y"])]
+    model = graph_model(nodes, X, Y, inits)
+    _, after = both(model, xs, disabled=["QDQFusion"])
+    assert after.get("QuantizeLinear") == 1
+    so = ort.SessionOptions()
+    so.add_session_config_entry("session.enable_quant_qdq_cleanup", "1")
+    sess = ort.InferenceSession(model, so, providers=["CPUExecutionProvider"], disabled_optimizers=["QDQFusion"])
+    assert "QuantizeLinear" not in op_counts(sess)
