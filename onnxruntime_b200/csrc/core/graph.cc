@@ -380,6 +380,14 @@ std::shared_ptr<Graph> Graph::FromProto(const pb::GraphProto& g, const std::map<
     } else {
       out->initializers_[t.name] = TensorFromProto(t, model_dir);
       if (t.data_type == pb::STRING) out->string_values_.insert(t.name);
+      if (t.data_type == pb::UINT4 || t.data_type == pb::INT4) {
+        // two values per byte, low nibble first -> one value per byte with the declared shape
+        at::Tensor packed = out->initializers_[t.name].to(at::kInt);
+        at::Tensor v = at::stack({at::bitwise_and(packed, 15), at::bitwise_right_shift(packed, 4)}, 1).reshape({-1}).narrow(0, 0, NumElements(t.dims));
+        if (t.data_type == pb::INT4) v = at::bitwise_xor(v, 8) - 8;  // sign extension
+        out->initializers_[t.name] = v.to(t.data_type == pb::INT4 ? at::kChar : at::kByte).reshape(t.dims).contiguous();
+        out->four_bit_values_[t.name] = t.data_type;
+      }
       if (t.data_type == pb::UINT4 || t.data_type == pb::INT4 || t.data_type == pb::FLOAT4E2M1) {
         ValueInfo vi;
         vi.name = t.name;
@@ -448,6 +456,19 @@ pb::GraphProto Graph::ToProto() const {
   }
   for (auto& kv : initializers_) {
     if (pending_external_.count(kv.first) && kv.second.numel() == 0) continue;
+    if (four_bit_values_.count(kv.first)) {
+      pb::TensorProto p;
+      p.name = kv.first;
+      p.data_type = four_bit_values_.at(kv.first);
+      p.dims = kv.second.sizes().vec();
+      at::Tensor v = at::bitwise_and(kv.second.to(at::kCPU, at::kInt).reshape({-1}), 15);
+      if (v.numel() % 2) v = at::cat({v, at::zeros({1}, v.options())});
+      v = v.reshape({-1, 2});
+      at::Tensor packed = at::bitwise_or(v.select(1, 0), at::bitwise_left_shift(v.select(1, 1), 4)).to(at::kByte).contiguous();
+      p.set_raw(std::string(static_cast<const char*>(packed.data_ptr()), static_cast<size_t>(packed.numel())));
+      g.initializer.push_back(std::move(p));
+      continue;
+    }
     if (string_values_.count(kv.first)) {
       pb::TensorProto p;
       p.name = kv.first;

@@ -107,6 +107,12 @@ class Graph {
   void RemoveInitializer(const std::string& name);
   const std::map<std::string, at::Tensor>& Initializers() const { return initializers_; }
   // initializers that hold strings (ids of the string table); GetConstant() hides them from the graph rewrites
+  // initializers declared as UINT4 / INT4: held one value per byte (uint8 / int8) and packed again when the graph is saved
+  int32_t FourBitTypeOf(const std::string& name) const {
+    auto it = four_bit_values_.find(name);
+    return it == four_bit_values_.end() ? 0 : it->second;
+  }
+  void MarkFourBitValue(const std::string& name, int32_t elem_type) { four_bit_values_[name] = elem_type; }
   bool IsStringValue(const std::string& name) const { return string_values_.count(name) != 0; }
   void MarkStringValue(const std::string& name) { string_values_.insert(name); }
   // names of initializers whose data is supplied by the session (external initializers)
@@ -148,6 +154,7 @@ class Graph {
   std::vector<std::unique_ptr<Node>> graveyard_;  // removed nodes awaiting PurgeRemoved()
   std::map<std::string, at::Tensor> initializers_;
   std::set<std::string> string_values_;
+  std::map<std::string, int32_t> four_bit_values_;
   std::set<std::string> pending_external_;
   std::vector<ValueInfo> inputs_, outputs_;
   std::map<std::string, ValueInfo> value_info_;

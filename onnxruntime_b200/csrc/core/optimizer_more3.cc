@@ -333,6 +333,64 @@ int QDQFinalCleanup(PassContext& c) {
   return count;
 }
 
+// DequantizeLinear(4-bit constant W [K, N], block-wise along K: axis 0, block_size 16 / 32 / 64 ...) -> MatMul(A, .)
+//   ==>  com.microsoft MatMulNBits(A, B [N, K / block, block / 2], scales, zero points)
+// (reference: qdq_transformer/selectors_actions/qdq_actions.cc DQMatMulToMatMulNBitsAction).  On with
+// "session.enable_dq_matmulnbits_fusion" = "1"; when the key is absent, on for GPU sessions (which have a 4-bit GEMM).
+int DQMatMulNBitsFusion(PassContext& c) {
+  Graph& g = c.g;
+  int count = 0;
+  const std::string key = c.config.Get("session.enable_dq_matmulnbits_fusion", "");
+  if (!(key == "1" || (key.empty() && c.gpu))) return 0;
+  const int64_t accuracy = std::stoll(c.config.Get("session.qdq_matmulnbits_accuracy_level", "4"));
+  for (Node* mm : g.Nodes()) {
+    if (!IsOnnx(mm, "MatMul")) continue;
+    Node* dq = g.Producer(mm->inputs[1]);
+    if (!IsOnnx(dq, "DequantizeLinear") || g.NumConsumers(dq->outputs[0]) != 1 || g.IsGraphOutput(dq->outputs[0])) continue;
+    const int32_t wt = g.FourBitTypeOf(dq->inputs[0]);
+    const at::Tensor *w = g.GetConstant(dq->inputs[0]), *scale = g.GetConstant(dq->inputs[1]);
+    const at::Tensor* zp = dq->has_input(2) ? g.GetConstant(dq->inputs[2]) : nullptr;
+    if (!wt || !w || !scale || w->dim() != 2 || (dq->has_input(2) && (!zp || g.FourBitTypeOf(dq->inputs[2]) != wt))) continue;
+    const int64_t K = w->size(0), N = w->size(1), bs = dq->attr_i("block_size", 0);
+    int64_t axis = dq->attr_i("axis", 1);
+    if (axis < 0) axis += 2;
+    if (axis != 0 || bs < 16 || (bs & (bs - 1)) != 0) continue;
+    const int64_t nb = (K + bs - 1) / bs;
+    if (scale->dim() != 2 || scale->size(0) != nb || scale->size(1) != N || !(scale->scalar_type() == at::kFloat || scale->scalar_type() == at::kHalf)) continue;
+    if (zp && (zp->dim() != 2 || zp->size(0) != nb || zp->size(1) != N)) continue;
+    const int64_t shift = wt == pb::INT4 ? 8 : 0;  // signed codes become unsigned: q + 8 with zero point + 8
+    // B: per output feature, per block, block / 2 bytes, the earlier K index in the low nibble
+    at::Tensor wt_nk = (w->to(at::kInt) + shift).t().contiguous();
+    if (nb * bs != K) wt_nk = at::constant_pad_nd(wt_nk, {0, nb * bs - K}, 0);
+    at::Tensor pairs = wt_nk.reshape({N, nb, bs / 2, 2});
+    at::Tensor B = at::bitwise_or(pairs.select(3, 0), at::bitwise_left_shift(pairs.select(3, 1), 4)).to(at::kByte).contiguous();
+    at::Tensor scales = scale->t().contiguous().reshape({N * nb});
+    const std::string bn = g.UniqueName(dq->inputs[0] + "_nbits"), sn = g.UniqueName(dq->inputs[1] + "_nbits");
+    g.AddInitializer(bn, B);
+    g.AddInitializer(sn, scales);
+    std::vector<std::string> inputs = {mm->inputs[0], bn, sn};
+    if (zp || !shift) {  // signed weights without zero points need none: the operator's default zero point is 8
+      at::Tensor z = zp ? (zp->to(at::kInt) + shift).t().contiguous() : at::zeros({N, nb}, at::kInt);
+      if (nb % 2) z = at::constant_pad_nd(z, {0, 1}, 0);
+      at::Tensor zpairs = z.reshape({N, -1, 2});
+      at::Tensor Z = at::bitwise_or(zpairs.select(2, 0), at::bitwise_left_shift(zpairs.select(2, 1), 4)).to(at::kByte).contiguous().reshape({-1});
+      const std::string zn = g.UniqueName(dq->inputs[0] + "_nbits_zp");
+      g.AddInitializer(zn, Z);
+      inputs.push_back(zn);
+    }
+    Node* f = g.AddNode("MatMulNBits", inputs, {mm->outputs[0]}, kMSDomain, g.UniqueName("MatMulNBits_dq"));
+    f->set_attr_i("K", K);
+    f->set_attr_i("N", N);
+    f->set_attr_i("bits", 4);
+    f->set_attr_i("block_size", bs);
+    f->set_attr_i("accuracy_level", accuracy);
+    g.RemoveNode(mm);
+    g.RemoveNode(dq);
+    ++count;
+  }
+  return count;
+}
+
 }  // namespace
 
 void AddMorePasses3(std::vector<Pass>& v) {
@@ -341,6 +399,7 @@ void AddMorePasses3(std::vector<Pass>& v) {
   v.push_back({"PadFusion", 1, false, PadFusion});
   v.push_back({"MatMulBNFusion", 1, false, MatMulBNFusion});
   v.push_back({"LabelEncoderFusion", 1, false, LabelEncoderFusion});
+  v.push_back({"DQMatMulNBitsFusion", 1, false, DQMatMulNBitsFusion});
   v.push_back({"GemmActivationFusion", 2, false, GemmActivationFusion});
   v.push_back({"QDQFinalCleanup", 2, false, QDQFinalCleanup});
 }

@@ -651,3 +651,50 @@ def test_qdq_final_cleanup():
     so.add_session_config_entry("session.enable_quant_qdq_cleanup", "1")
     sess = ort.InferenceSession(model, so, providers=["CPUExecutionProvider"], disabled_optimizers=["QDQFusion"])
     assert "QuantizeLinear" not in op_counts(sess)
+
+
+def _pack4(values):
+    v = (np.asarray(values).astype(np.int64).reshape(-1) & 15).astype(np.uint8)
+    if v.size % 2:
+        v = np.append(v, np.uint8(0))
+    return (v[0::2] | (v[1::2] << 4)).tobytes()
+
+
+@pytest.mark.parametrize("signed,with_zp", [(False, True), (False, False), (True, False), (True, True)])
+def test_int4_dequantize_and_dq_matmul_nbits_fusion(signed, with_zp, tmp_path):
+    """4-bit initializers load as one value per element; DequantizeLinear (block-wise along K) -> MatMul becomes
+    MatMulNBits when the session asks for it, with the same result; the saved model keeps the 4-bit type."""
+    K, N, bs = 48, 8, 16
+    lo, hi = (-8, 8) if signed else (0, 16)
+    w = rng.randint(lo, hi, (K, N))
+    zp = rng.randint(lo, hi, (K // bs, N))
+    scale = (rng.rand(K // bs, N) * 0.05 + 0.01).astype(np.float32)
+    t4 = T.INT4 if signed else T.UINT4
+    inits = [ol.Tensor("w", t4, (K, N), _pack4(w)), ol.make_tensor("s", scale)]
+    dq_in = ["w", "s"]
+    if with_zp:
+        inits.append(ol.Tensor("z", t4, (K // bs, N), _pack4(zp)))
+        dq_in.append("z")
+    nodes = [ol.make_node("DequantizeLinear", dq_in, ["wd"], axis=0, block_size=bs), ol.make_node("MatMul", ["x", "wd"], ["y"])]
+    model = ol.make_model(ol.make_graph(nodes, "g", [ol.make_tensor_value_info("x", T.FLOAT, ["n", K])], Y, inits), opset=21).serialize()
+    x = rng.randn(5, K).astype(np.float32)
+    ref = x @ ((w - (np.repeat(zp, bs, 0) if with_zp else 0)) * np.repeat(scale, bs, 0))
+    so = ort.SessionOptions()
+    so.graph_optimization_level = ort.GraphOptimizationLevel.ORT_DISABLE_ALL
+    plain = ort.InferenceSession(model, so, providers=["CPUExecutionProvider"])
+    np.testing.assert_allclose(plain.run(None, {"x": x})[0], ref, rtol=1e-4, atol=1e-4)
+    so = ort.SessionOptions()
+    so.add_session_config_entry("session.enable_dq_matmulnbits_fusion", "1")
+    so.optimized_model_filepath = str(tmp_path / "fused.onnx")
+    fused = ort.InferenceSession(model, so, providers=["CPUExecutionProvider"])
+    assert op_counts(fused) == {"MatMulNBits": 1}
+    np.testing.assert_allclose(fused.run(None, {"x": x})[0], ref, rtol=1e-4, atol=1e-4)
+    # without the key a CPU session keeps the pair; a model saved from it still declares the 4-bit type
+    so = ort.SessionOptions()
+    so.optimized_model_filepath = str(tmp_path / "kept.onnx")
+    kept = ort.InferenceSession(model, so, providers=["CPUExecutionProvider"], disabled_optimizers=["ConstantFolding"])
+    assert op_counts(kept).get("DequantizeLinear") == 1
+    saved = ol.load_model(str(tmp_path / "kept.onnx"))
+    wt = [t for t in saved.graph.initializers if t.name == "w"][0]
+    assert wt.data_type == t4 and tuple(wt.dims) == (K, N) and bytes(wt.raw) == _pack4(w)
+    np.testing.assert_allclose(ort.InferenceSession(str(tmp_path / "kept.onnx"), providers=["CPUExecutionProvider"]).run(None, {"x": x})[0], ref, rtol=1e-4, atol=1e-4)
