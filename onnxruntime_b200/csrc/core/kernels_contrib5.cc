@@ -2,6 +2,8 @@
 // DecoderAttention (sequence-first self / cross attention with runtime switches) and BifurcationDetector.
 #include <ATen/ATen.h>
 
+#include <limits>
+
 #include <algorithm>
 #include <cctype>
 #include <cmath>
@@ -177,7 +179,39 @@ void BifurcationDetectorImpl(Ctx& ctx) {
 
 }  // namespace
 
+// WordConvEmbedding (contrib_ops/cpu/word_conv_embedding.cc): every word (a row of character ids, 0 or out-of-range ids
+// = padding) -> character embeddings (padding contributes zero vectors) -> convolution over the characters with window
+// W.shape[2] and stride 1 -> tanh -> maximum over the max(length - window + 1, 1) positions that lie inside the word.
+void WordConvEmbeddingImpl(Ctx& ctx) {
+  const Node& n = ctx.node();
+  const at::Tensor& seq = ctx.RequiredInput(0);
+  const at::Tensor& W = ctx.RequiredInput(1);
+  const at::Tensor& B = ctx.RequiredInput(2);
+  const at::Tensor& C = ctx.RequiredInput(3);
+  ORTB_ENFORCE_ARG(seq.dim() > 1, "WordConvEmbedding: Sequence input must have rank greater than 1");
+  ORTB_ENFORCE_ARG(W.dim() == 4 && W.size(1) == 1 && C.dim() == 2, "WordConvEmbedding: W must be [filters, 1, window, char_embedding], C [chars, char_embedding]");
+  const int64_t F = W.size(0), window = W.size(2), E = W.size(3), WL = seq.size(-1);
+  ORTB_ENFORCE_ARG(C.size(1) == E, "WordConvEmbedding: char embedding size of C (", C.size(1), ") and of W (", E, ") differ");
+  ORTB_ENFORCE_ARG(B.numel() >= F, "WordConvEmbedding: bias has fewer entries than W has filters");
+  ORTB_ENFORCE_ARG(window <= WL, "WordConvEmbedding: Conv kernel width must not exceed word length");
+  ORTB_ENFORCE_ARG(!n.has_attr("embedding_size") || n.attr_i("embedding_size", F) == F, "WordConvEmbedding: embedding_size does not match W");
+  ORTB_ENFORCE_ARG(!n.has_attr("conv_window_size") || n.attr_i("conv_window_size", window) == window, "WordConvEmbedding: conv_window_size does not match W");
+  ORTB_ENFORCE_ARG(!n.has_attr("char_embedding_size") || n.attr_i("char_embedding_size", E) == E, "WordConvEmbedding: char_embedding_size does not match C");
+  at::Tensor ids = seq.reshape({-1, WL}).to(at::kLong);
+  at::Tensor valid = ids.gt(0).logical_and(ids.lt(C.size(0)));
+  at::Tensor emb = C.index_select(0, at::where(valid, ids, at::zeros_like(ids)).reshape({-1})).reshape({ids.size(0), WL, E}) * valid.unsqueeze(-1).to(C.scalar_type());
+  at::Tensor windows = emb.unfold(1, window, 1).permute({0, 1, 3, 2}).reshape({ids.size(0), WL - window + 1, window * E});  // [words, positions, window * E]
+  at::Tensor y = at::tanh(at::matmul(windows, W.reshape({F, window * E}).t()) + B.narrow(0, 0, F));                        // [words, positions, F]
+  at::Tensor positions = at::clamp_min(valid.sum(1) - window + 1, 1);                                                         // inside the word
+  at::Tensor outside = at::arange(WL - window + 1, ids.options()).unsqueeze(0).ge(positions.unsqueeze(1));
+  y = y.masked_fill(outside.unsqueeze(-1), -std::numeric_limits<float>::infinity()).amax(1);
+  std::vector<int64_t> shape = seq.sizes().vec();
+  shape.back() = F;
+  ctx.SetOutput(0, y.reshape(shape));
+}
+
 void RegisterContribKernels5(KernelRegistry& r) {
+  r.RegisterFn(MS, "WordConvEmbedding", 1, kMax, WordConvEmbeddingImpl);
   r.RegisterFn(MS, "MatMulNBitsMlp", 1, kMax, NBitsMlpImpl);
   r.RegisterFn(MS, "MatMulNBitsQkv", 1, kMax, NBitsQkvImpl);
   r.RegisterFn(MS, "DecoderAttention", 1, kMax, DecoderAttentionImpl, {8, 9, 10, 11});

@@ -323,3 +323,28 @@ def test_bifurcation_detector():
     _, idx = run_node("BifurcationDetector", {"s": src, "c": np.array([11], np.int64), "p": np.array([0], np.int64)},
                       n_outputs=2, domain=MS, min_ngram_size=1, max_ngram_size=3)
     assert int(idx[0]) == -1                                    # 11 occurs twice
+
+
+def test_word_conv_embedding_reference_vectors():
+    """Inputs and expected outputs of the reference's own test (onnxruntime/test/contrib_ops/word_conv_embedding_test.cc)."""
+    import numpy as np
+    import pytest
+    from helpers import run_node
+    seq = np.array([[1, 2, 3, 4, 0], [4, 3, 2, 1, 0]], np.int32)
+    C = np.array([[0.1, 0.2, 0.3], [0.2, 0.3, 0.1], [0.3, 0.1, 0.2], [0.4, 0.5, 0.6], [0.7, 0.8, 0.9]], np.float32)
+    W = np.array([0.1, 0.2, 0.3, 0.2, 0.3, 0.1, 0.3, 0.1, 0.2, 1.0, 1.1, 1.2], np.float32).reshape(2, 1, 2, 3)
+    B = np.array([0.1, 0.2], np.float32)
+    (y,) = run_node("WordConvEmbedding", {"Sequence": seq, "W": W, "B": B, "C": C}, domain="com.microsoft")
+    np.testing.assert_allclose(y, [[0.711393774, 0.996334076], [0.711393774, 0.981612563]], rtol=1e-5)
+    (y,) = run_node("WordConvEmbedding", {"Sequence": seq, "W": W, "B": B, "C": C}, domain="com.microsoft", embedding_size=2, conv_window_size=2,
+                    char_embedding_size=3)
+    assert y.shape == (2, 2)
+    with pytest.raises(Exception, match="embedding_size"):
+        run_node("WordConvEmbedding", {"Sequence": seq, "W": W, "B": B, "C": C}, domain="com.microsoft", embedding_size=3)
+    # an id outside the character table counts as padding: one window over (char 1, zero vector)
+    (y,) = run_node("WordConvEmbedding", {"Sequence": np.array([[1, 99]], np.int32), "W": np.ones((1, 1, 2, 1), np.float32), "B": np.zeros(1, np.float32),
+                                          "C": np.array([[123.0], [2.0]], np.float32)}, domain="com.microsoft")
+    np.testing.assert_allclose(y, [[np.tanh(2.0)]], rtol=1e-6)
+    with pytest.raises(Exception, match="must not exceed word length"):
+        run_node("WordConvEmbedding", {"Sequence": np.array([[1, 2]], np.int32), "W": np.ones((1, 1, 3, 1), np.float32), "B": np.zeros(1, np.float32),
+                                       "C": np.array([[0.0], [1.0], [2.0]], np.float32)}, domain="com.microsoft")
