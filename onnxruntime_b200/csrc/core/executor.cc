@@ -32,7 +32,7 @@ struct NvtxRange {
 namespace {
 bool IsShapeOnlyOp(const Node& n) { return n.domain.empty() && (n.op_type == "Shape" || n.op_type == "Size"); }
 bool IsControlFlow(const Node& n) {
-  return n.domain.empty() && (n.op_type == "If" || n.op_type == "Loop" || n.op_type == "Scan");
+  return n.domain.empty() && (n.op_type == "If" || n.op_type == "Loop" || n.op_type == "Scan" || n.op_type == "SequenceMap");
 }
 bool Contains(const std::vector<int>& v, int x) { return std::find(v.begin(), v.end(), x) != v.end(); }
 const char* kGpuSuffix = "\x01gpu";

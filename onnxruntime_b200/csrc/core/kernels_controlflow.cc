@@ -149,6 +149,39 @@ class LoopKernel final : public ControlFlowBase {
   mutable Body body_;
 };
 
+// SequenceMap (opset 17): the body runs once per position of the first input sequence; further inputs are sequences of
+// the same length (their elements at that position) or tensors (passed to every call); every body output becomes a sequence.
+class SequenceMapKernel final : public ControlFlowBase {
+ public:
+  explicit SequenceMapKernel(const OpKernelInfo& info) : ControlFlowBase(info) { body_ = MakeBody("body"); }
+  void Compute(Ctx& ctx) const override {
+    std::lock_guard<std::mutex> lk(mu_);
+    const Value& first = ctx.InputValue(0);
+    ORTB_ENFORCE_ARG(first.seq != nullptr, "SequenceMap: the first input must be a sequence");
+    const size_t len = first.seq->size();
+    const int n_in = ctx.InputCount(), n_out = static_cast<int>(body_.graph->Outputs().size());
+    for (int i = 1; i < n_in; ++i) {
+      const Value& v = ctx.InputValue(i);
+      ORTB_ENFORCE_ARG(!v.seq || v.seq->size() == len, "SequenceMap: input sequences differ in length");
+    }
+    std::vector<std::vector<at::Tensor>> outs(static_cast<size_t>(n_out));
+    for (size_t pos = 0; pos < len; ++pos) {
+      std::vector<Value> in(static_cast<size_t>(n_in));
+      for (int i = 0; i < n_in; ++i) {
+        const Value& v = ctx.InputValue(i);
+        if (v.seq) in[static_cast<size_t>(i)].t = (*v.seq)[pos];
+        else in[static_cast<size_t>(i)] = v;
+      }
+      std::vector<Value> out = RunBody(body_, ctx, in);
+      for (int k = 0; k < n_out; ++k) outs[static_cast<size_t>(k)].push_back(ToSessionDevice(out[static_cast<size_t>(k)].t));
+    }
+    for (int k = 0; k < n_out && k < ctx.OutputCount(); ++k) ctx.SetOutputSeq(k, outs[static_cast<size_t>(k)]);
+  }
+
+ private:
+  mutable Body body_;
+};
+
 class ScanKernel final : public ControlFlowBase {
  public:
   explicit ScanKernel(const OpKernelInfo& info) : ControlFlowBase(info) { body_ = MakeBody("body"); }
@@ -541,6 +574,7 @@ void RegisterControlFlowKernels(KernelRegistry& r) {
   RegisterClass<IfKernel>(r, "If", 1, {0});
   RegisterClass<LoopKernel>(r, "Loop", 1, {0, 1});
   RegisterClass<ScanKernel>(r, "Scan", 9, {});
+  RegisterClass<SequenceMapKernel>(r, "SequenceMap", 17, {});
   for (const char* op : {"GreedySearch", "Sampling", "BeamSearch", "WhisperBeamSearch"}) {
     KernelDef d;
     d.domain = kMSDomain;

@@ -83,7 +83,7 @@ int EliminateNoop(PassContext& c) {
 bool Foldable(const Node& n) {
   static const std::set<std::string> never = {
       "RandomNormal", "RandomNormalLike", "RandomUniform", "RandomUniformLike", "Multinomial", "Bernoulli",
-      "If", "Loop", "Scan", "QuantizeLinear", "DequantizeLinear", "DynamicQuantizeLinear", "MemcpyToHost",
+      "If", "Loop", "Scan", "SequenceMap", "QuantizeLinear", "DequantizeLinear", "DynamicQuantizeLinear", "MemcpyToHost",
       "MemcpyFromHost", "AllReduce", "AllGather", "AllToAll", "ShardedMoE", "SequenceConstruct", "SequenceEmpty",
       "SplitToSequence", "SequenceInsert", "SequenceErase", "SequenceAt", "SequenceLength", "ConcatFromSequence"};
   if (never.count(n.op_type)) return false;

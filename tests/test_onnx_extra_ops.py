@@ -277,3 +277,24 @@ def test_sparse_initializer_and_sparse_to_dense_matmul():
     g.sparse_initializers[0] = sp
     sess = ort.InferenceSession(ol.make_model(g, opset=17).serialize(), providers=["CPUExecutionProvider"])
     np.testing.assert_allclose(sess.run(None, {"B": B})[0], 0.5 * A @ B, rtol=1e-6)
+
+
+def test_sequence_map_runs_the_body_per_element():
+    import onnxruntime_b200 as ort
+    from onnxruntime_b200 import onnx_lite as ol
+    T = ol.TensorProto
+    body = ol.make_graph([ol.make_node("Mul", ["elem", "scale"], ["scaled"]), ol.make_node("Add", ["scaled", "other"], ["out0"]),
+                          ol.make_node("Shape", ["elem"], ["out1"])], "body",
+                         [ol.make_tensor_value_info("elem", T.FLOAT, None), ol.make_tensor_value_info("other", T.FLOAT, None)],
+                         [ol.make_tensor_value_info("out0", T.FLOAT, None), ol.make_tensor_value_info("out1", T.INT64, None)])
+    nodes = [ol.make_node("SplitToSequence", ["x", "split"], ["xs"], axis=0), ol.make_node("SplitToSequence", ["y", "split"], ["ys"], axis=0),
+             ol.make_node("SequenceMap", ["xs", "ys"], ["s0", "s1"], body=body),
+             ol.make_node("ConcatFromSequence", ["s0"], ["z"], axis=0), ol.make_node("ConcatFromSequence", ["s1"], ["shapes"], axis=0, new_axis=1)]
+    g = ol.make_graph(nodes, "g", [ol.make_tensor_value_info("x", T.FLOAT, [6, 3]), ol.make_tensor_value_info("y", T.FLOAT, [6, 3])],
+                      [ol.make_tensor_value_info("z", T.FLOAT, None), ol.make_tensor_value_info("shapes", T.INT64, None)],
+                      [ol.make_tensor("split", np.array([1, 2, 3], np.int64)), ol.make_tensor("scale", np.array(2.0, np.float32))])
+    sess = ort.InferenceSession(ol.make_model(g, opset=17).serialize(), providers=["CPUExecutionProvider"])
+    x, y = rng.standard_normal((6, 3)).astype(np.float32), rng.standard_normal((6, 3)).astype(np.float32)
+    z, shapes = sess.run(None, {"x": x, "y": y})
+    np.testing.assert_allclose(z, 2 * x + y, rtol=1e-6)
+    np.testing.assert_array_equal(shapes, [[1, 3], [2, 3], [3, 3]])
