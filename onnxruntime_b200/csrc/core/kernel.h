@@ -159,6 +159,8 @@ class KernelRegistry {
   void Register(KernelDef def);
   void RegisterFn(const std::string& domain, const std::string& op, int since_min, int since_max, KernelFn fn,
                   std::vector<int> host_inputs = {});
+  // the newest kernel of (from_domain, op) also serves (to_domain, op), any version
+  void RegisterAlias(const std::string& from_domain, const std::string& op, const std::string& to_domain);
   const KernelDef* Find(const Node& node, const Graph& graph) const;
   bool HasOp(const std::string& domain, const std::string& op) const;
   std::vector<std::string> ListOps() const;

@@ -41,6 +41,19 @@ void KernelRegistry::RegisterFn(const std::string& domain, const std::string& op
   Register(std::move(d));
 }
 
+void KernelRegistry::RegisterAlias(const std::string& from_domain, const std::string& op, const std::string& to_domain) {
+  auto it = defs_.find({from_domain, op});
+  if (it == defs_.end() || it->second.empty()) return;
+  const KernelDef* newest = &it->second.front();
+  for (auto& d : it->second)
+    if (d.since_max > newest->since_max || (d.since_max == newest->since_max && d.since_min > newest->since_min)) newest = &d;
+  KernelDef copy = *newest;
+  copy.domain = to_domain;
+  copy.since_min = 1;
+  copy.since_max = 1 << 30;
+  Register(std::move(copy));
+}
+
 const KernelDef* KernelRegistry::Find(const Node& node, const Graph& graph) const {
   auto it = defs_.find({node.domain, node.op_type});
   if (it == defs_.end()) return nullptr;
@@ -83,6 +96,8 @@ void EnsureKernelsRegistered() {
     RegisterStringKernels(g);
     RegisterControlFlowKernels(g);
     RegisterCollectiveKernels(g);
+    // com.microsoft operators that are early forms of ONNX operators with the same semantics (contrib_ops/cpu_contrib_kernels.cc)
+    for (const char* op : {"GatherND", "GridSample", "Pad", "QLinearConv", "Range"}) g.RegisterAlias("", op, "com.microsoft");
     RegisterCudaKernels(KernelRegistry::Cuda());
   });
 }

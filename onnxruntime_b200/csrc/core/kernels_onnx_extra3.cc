@@ -226,6 +226,23 @@ void RegisterOnnxExtraKernels3(KernelRegistry& r) {
   r.RegisterFn("", "MelWeightMatrix", 17, kMax, MelWeightMatrixImpl, {0, 1, 2, 3, 4});
   r.RegisterFn("", "MaxRoiPool", 1, kMax, MaxRoiPoolImpl);
   r.RegisterFn("com.microsoft", "GatherBlockQuantized", 1, kMax, GatherBlockQuantizedImpl);
+  // com.microsoft Unique (contrib_ops/cpu/unique.cc): 1-D input -> distinct values in order of first appearance, for
+  // every input element the position of its value among them, and the count of every distinct value
+  r.RegisterFn("com.microsoft", "Unique", 1, kMax, [](Ctx& ctx) {
+    const at::Tensor& x = ctx.RequiredInput(0);
+    ORTB_ENFORCE_ARG(x.dim() == 1, "Unique: input must be 1-D");
+    auto res = at::_unique2(x, /*sorted=*/true, /*return_inverse=*/true, /*return_counts=*/true);
+    at::Tensor values = std::get<0>(res), inverse = std::get<1>(res), counts = std::get<2>(res);
+    // re-order from sorted to first-appearance order
+    at::Tensor first = at::full({values.numel()}, x.numel(), inverse.options());
+    first.scatter_reduce_(0, inverse, at::arange(x.numel(), inverse.options()), "amin");
+    at::Tensor order = at::argsort(first);             // sorted position -> appearance rank
+    at::Tensor rank = at::empty_like(order);
+    rank.scatter_(0, order, at::arange(order.numel(), order.options()));
+    ctx.SetOutput(0, values.index_select(0, order));
+    if (ctx.OutputCount() > 1) ctx.SetOutput(1, rank.index_select(0, inverse));
+    if (ctx.OutputCount() > 2) ctx.SetOutput(2, counts.index_select(0, order));
+  });
   // SparseToDenseMatMul (contrib_ops/cpu/math/sparse_dense_matmul.cc): sparse tensors are expanded when they enter a
   // session, so this is alpha * op(A) @ op(B) on dense operands
   r.RegisterFn("com.microsoft", "SparseToDenseMatMul", 1, kMax, [](Ctx& ctx) {

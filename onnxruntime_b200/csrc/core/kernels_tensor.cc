@@ -357,7 +357,7 @@ void RegisterTensorKernels(KernelRegistry& r) {
     const Node& n = ctx.node();
     std::vector<int64_t> pads, axes;
     at::Scalar value = 0;
-    if (n.since_version >= 11) {
+    if (n.since_version >= 11 || !n.domain.empty()) {  // the com.microsoft form takes pads as an input, like opset 11
       pads = ToVec(ctx.RequiredInput(1));
       if (ctx.HasInput(2) && ctx.Input(2).numel() > 0) value = ctx.Input(2).cpu().reshape({-1})[0].item();
       if (ctx.HasInput(3)) axes = ToVec(ctx.Input(3));

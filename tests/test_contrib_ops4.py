@@ -348,3 +348,20 @@ def test_word_conv_embedding_reference_vectors():
     with pytest.raises(Exception, match="must not exceed word length"):
         run_node("WordConvEmbedding", {"Sequence": np.array([[1, 2]], np.int32), "W": np.ones((1, 1, 3, 1), np.float32), "B": np.zeros(1, np.float32),
                                        "C": np.array([[0.0], [1.0], [2.0]], np.float32)}, domain="com.microsoft")
+
+
+def test_contrib_aliases_of_onnx_operators_and_unique():
+    import numpy as np
+    from helpers import run_node
+    MS = "com.microsoft"
+    (r,) = run_node("Range", {"s": np.array(1.0, np.float32), "l": np.array(4.0, np.float32), "d": np.array(0.5, np.float32)}, domain=MS)
+    np.testing.assert_allclose(r, np.arange(1.0, 4.0, 0.5, dtype=np.float32))
+    data = np.arange(24, dtype=np.float32).reshape(2, 3, 4)
+    (g,) = run_node("GatherND", {"data": data, "idx": np.array([[0, 1], [1, 2]], np.int64)}, domain=MS)
+    np.testing.assert_array_equal(g, data[[0, 1], [1, 2]])
+    (p,) = run_node("Pad", {"x": np.ones((2, 2), np.float32), "pads": np.array([0, 1, 0, 1], np.int64), "v": np.array(7.0, np.float32)}, domain=MS, mode="constant")
+    np.testing.assert_array_equal(p, [[7, 1, 1, 7], [7, 1, 1, 7]])
+    y, idx, counts = run_node("Unique", {"x": np.array([5, 2, 5, 9, 2, 5], np.int64)}, n_outputs=3, domain=MS)
+    np.testing.assert_array_equal(y, [5, 2, 9])
+    np.testing.assert_array_equal(idx, [0, 1, 0, 2, 1, 0])
+    np.testing.assert_array_equal(counts, [3, 2, 1])
