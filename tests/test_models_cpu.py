@@ -131,3 +131,101 @@ def test_fp8_bert_graph_tracks_the_fp16_graph():
     assert np.abs(a - b)[valid].max() < 0.3 and np.abs(a - b)[valid].mean() < 0.05
     from helpers import op_counts
     assert op_counts(sess)["GemmFloat8"] == 8
+
+
+def test_gpt2_graph_prefill_and_decode_with_past_match_the_numpy_model():
+    """GPT-2 builder (LayerNormalization + com.microsoft Attention with past / present + FastGelu): a prompt pass followed by
+    token-by-token passes over the returned state gives the logits of one full pass of the numpy restatement."""
+    import numpy as np
+    import onnxruntime_b200 as ort
+    from onnxruntime_b200.models import gpt2
+    cfg = gpt2.Gpt2Config(vocab_size=97, hidden_size=32, num_layers=2, num_heads=4, max_position=32)
+    w = gpt2.init_weights(cfg, seed=3)
+    sess = ort.InferenceSession(gpt2.build_gpt2(cfg, w), providers=["CPUExecutionProvider"])
+    assert [o.name for o in sess.get_outputs()] == ["logits", "present_0", "present_1"]
+    rng = np.random.RandomState(0)
+    ids = rng.randint(0, cfg.vocab_size, (2, 9))
+    ref = gpt2.reference_forward(cfg, w, ids)
+    outs = sess.run(None, gpt2.step_feeds(cfg, ids[:, :6], gpt2.empty_past(cfg, 2)))
+    np.testing.assert_allclose(outs[0], ref[:, :6], rtol=2e-4, atol=2e-5)
+    past = {f"past_{i}": outs[1 + i] for i in range(cfg.num_layers)}
+    assert past["past_0"].shape == (2, 2, 4, 6, 8)
+    for t in range(6, 9):
+        outs = sess.run(None, gpt2.step_feeds(cfg, ids[:, t:t + 1], past))
+        np.testing.assert_allclose(outs[0][:, 0], ref[:, t], rtol=2e-4, atol=2e-5)
+        past = {f"past_{i}": outs[1 + i] for i in range(cfg.num_layers)}
+    assert past["past_1"].shape[3] == 9
+
+
+def test_gpt2_under_the_greedy_search_operator(tmp_path):
+    """The GPT-2 graph has the interface of the generation operators: wrapped into GreedySearch it decodes what a plain
+    arg-max loop over the numpy model decodes."""
+    import numpy as np
+    from onnxruntime_b200 import onnx_lite as ol
+    from onnxruntime_b200.models import gpt2
+    from onnxruntime_b200.transformers import convert_generation as cg
+    cfg = gpt2.Gpt2Config(vocab_size=61, hidden_size=32, num_layers=2, num_heads=4, max_position=32)
+    w = gpt2.init_weights(cfg, seed=5)
+    for k in w:                      # larger weights: well separated logits
+        if k.endswith("weight") or k in ("wte", "wpe"):
+            w[k] = w[k] * 8
+    model = cg.convert(ol.load_model(gpt2.build_gpt2(cfg, w)), op="greedy", eos_token_id=cfg.vocab_size + 5)
+    sess = ort.InferenceSession(model.serialize(), providers=["CPUExecutionProvider"])
+    prompt = np.array([[7, 3, 11], [2, 40, 9]], np.int32)
+    (seqs,) = sess.run(None, {"input_ids": prompt, "max_length": np.array([10], np.int32), "min_length": np.array([0], np.int32),
+                              "repetition_penalty": np.array([1.0], np.float32), "attention_mask": np.ones((2, 3), np.int32)})
+    want = prompt.astype(np.int64)
+    for _ in range(7):
+        nxt = gpt2.reference_forward(cfg, w, want)[:, -1].argmax(-1)
+        want = np.concatenate([want, nxt[:, None]], 1)
+    np.testing.assert_array_equal(seqs, want.astype(np.int32))
+
+
+def test_encoder_decoder_builder_under_greedy_and_beam_search():
+    """T5-shaped encoder / decoder graph pair: the decoder step over the encoder pass's states reproduces the numpy
+    model's logits, and the GreedySearch / BeamSearch (one beam) wrappers decode what an arg-max loop over it decodes."""
+    import numpy as np
+    from onnxruntime_b200.models import encoder_decoder as ed
+    from onnxruntime_b200.transformers import convert_generation as cg
+    cfg = ed.EncoderDecoderConfig(vocab_size=53)
+    w = ed.init_weights(cfg, seed=1, scale=0.3)
+    encoder, decoder = ed.build_encoder_decoder(cfg, w)
+    rng = np.random.RandomState(2)
+    enc_ids = rng.randint(1, cfg.vocab_size, (2, 7)).astype(np.int32)
+    enc_mask = np.ones((2, 7), np.int32)
+    enc_mask[1, 5:] = 0
+    start = 1
+    # graphs by hand: encoder pass, then two decoder steps
+    es = ort.InferenceSession(encoder.serialize(), providers=["CPUExecutionProvider"])
+    ds = ort.InferenceSession(decoder.serialize(), providers=["CPUExecutionProvider"])
+    dec = np.full((2, 1), start, np.int32)
+    eo = es.run(None, {"encoder_input_ids": enc_ids, "encoder_attention_mask": enc_mask, "decoder_input_ids": dec})
+    names = [o.name for o in es.get_outputs()]
+    ref = ed.reference_logits(cfg, w, enc_ids, enc_mask, dec)
+    np.testing.assert_allclose(eo[0], ref, rtol=2e-4, atol=2e-5)
+    state = dict(zip(names, eo))
+    toks = dec
+    for _ in range(2):
+        nxt = ed.reference_logits(cfg, w, enc_ids, enc_mask, toks)[:, -1].argmax(-1).astype(np.int32)[:, None]
+        feeds = {"input_ids": nxt, "encoder_attention_mask": enc_mask}
+        for i in range(cfg.decoder_layers):
+            feeds[f"past_key_self_{i}"], feeds[f"past_value_self_{i}"] = state[f"present_key_self_{i}"], state[f"present_value_self_{i}"]
+            feeds[f"past_key_cross_{i}"], feeds[f"past_value_cross_{i}"] = state[f"present_key_cross_{i}"], state[f"present_value_cross_{i}"]
+        do = ds.run(None, feeds)
+        toks = np.concatenate([toks, nxt], 1)
+        np.testing.assert_allclose(do[0][:, 0], ed.reference_logits(cfg, w, enc_ids, enc_mask, toks)[:, -1], rtol=2e-4, atol=2e-5)
+        for n, v in zip([o.name for o in ds.get_outputs()][1:], do[1:]):
+            state[n] = v
+    # the generation operators
+    want = np.full((2, 1), start, np.int64)
+    for _ in range(6):
+        want = np.concatenate([want, ed.reference_logits(cfg, w, enc_ids, enc_mask, want)[:, -1].argmax(-1)[:, None]], 1)
+    common = {"input_ids": enc_ids, "max_length": np.array([7], np.int32), "min_length": np.array([0], np.int32),
+              "repetition_penalty": np.array([1.0], np.float32), "attention_mask": enc_mask}
+    greedy = cg.convert(decoder, op="greedy", encoder=encoder, model_type=1, eos_token_id=cfg.vocab_size + 3, decoder_start_token_id=start)
+    (seqs,) = ort.InferenceSession(greedy.serialize(), providers=["CPUExecutionProvider"]).run(None, common)
+    np.testing.assert_array_equal(seqs, want.astype(np.int32))
+    beam = cg.convert(decoder, op="beam", encoder=encoder, model_type=1, eos_token_id=cfg.vocab_size + 3, decoder_start_token_id=start)
+    seqs, _ = ort.InferenceSession(beam.serialize(), providers=["CPUExecutionProvider"]).run(
+        None, dict(common, num_beams=np.array([1], np.int32), num_return_sequences=np.array([1], np.int32), length_penalty=np.array([1.0], np.float32)))
+    np.testing.assert_array_equal(seqs[:, 0], want.astype(np.int32))
