@@ -34,6 +34,8 @@ class EncoderDecoderConfig:
     decoder_layers: int = 2
     max_position: int = 64
     layer_norm_eps: float = 1e-5
+    audio_features: int = 0        # > 0: Whisper shape - the encoder reads [batch, audio_features, frames] through two
+                                   # Conv1d + GELU layers (the second with stride 2) instead of token ids, and has no mask
 
 
 def init_weights(cfg: EncoderDecoderConfig, seed: int = 0, scale: float = 0.05) -> Dict[str, np.ndarray]:
@@ -54,6 +56,9 @@ def init_weights(cfg: EncoderDecoderConfig, seed: int = 0, scale: float = 0.05) 
             n(f"{name}.{p}.bias", H)
 
     n("embed", cfg.vocab_size, H)
+    if cfg.audio_features:
+        n("enc.conv1.weight", H, cfg.audio_features, 3), n("enc.conv1.bias", H)
+        n("enc.conv2.weight", H, H, 3), n("enc.conv2.bias", H)
     n("enc.pos", cfg.max_position, H)
     n("dec.pos", cfg.max_position, H)
     for i in range(cfg.encoder_layers):
@@ -89,10 +94,10 @@ class _G:
         self.inits[name] = ol.make_tensor(name, np.asarray(value, dtype=dtype))
         return name
 
-    def op(self, op_type, inputs, outputs=None, **attrs) -> str:
+    def op(self, op_type, inputs, outputs=None, domain="", **attrs) -> str:
         self.count += 1
         outs = outputs or [f"{op_type.lower()}_{self.count}"]
-        self.nodes.append(ol.make_node(op_type, inputs, outs, name=f"{op_type}_{self.count}", **attrs))
+        self.nodes.append(ol.make_node(op_type, inputs, outs, name=f"{op_type}_{self.count}", domain=domain, **attrs))
         return outs[0]
 
     def linear(self, x, name):
@@ -128,9 +133,17 @@ class _G:
     def ffn(self, x, p):
         return self.linear(self.op("Relu", [self.linear(x, p + ".fc1")]), p + ".fc2")
 
+    def audio_stem(self, features):  # [B, mels, frames] -> [B, frames / 2, H] + positions
+        c1 = self.op("Gelu", [self.op("Conv", [features, self.wt("enc.conv1.weight"), self.wt("enc.conv1.bias")], kernel_shape=[3], pads=[1, 1])], domain="com.microsoft")
+        c2 = self.op("Gelu", [self.op("Conv", [c1, self.wt("enc.conv2.weight"), self.wt("enc.conv2.bias")], kernel_shape=[3], pads=[1, 1], strides=[2])], domain="com.microsoft")
+        x = self.op("Transpose", [c2], perm=[0, 2, 1])
+        seq = self.op("Gather", [self.op("Shape", [x]), self.const(1, np.int64)], axis=0)
+        pos = self.op("Range", [self.const(0, np.int64), seq, self.const(1, np.int64)])
+        return self.op("Add", [x, self.op("Gather", [self.wt("enc.pos"), pos], axis=0)])
+
     def encoder(self, ids, mask):
-        x = self.embed(ids, "enc.pos")
-        bias = self.key_mask_bias(mask)
+        x = self.audio_stem(ids) if self.cfg.audio_features else self.embed(ids, "enc.pos")
+        bias = self.key_mask_bias(mask) if mask is not None else None
         for i in range(self.cfg.encoder_layers):
             p = f"enc.{i}"
             h = self.ln(x, p + ".ln1")
@@ -154,7 +167,8 @@ def build_encoder_decoder(cfg: EncoderDecoderConfig, weights: Optional[Dict[str,
 
     # ---- encoder + first decoder pass
     g = _G(cfg, w)
-    enc, enc_bias = g.encoder("encoder_input_ids", "encoder_attention_mask")
+    audio = cfg.audio_features > 0
+    enc, enc_bias = g.encoder("encoder_input_features" if audio else "encoder_input_ids", None if audio else "encoder_attention_mask")
     g.op("Identity", [enc], ["encoder_hidden_states"])
     x = g.embed("decoder_input_ids", "dec.pos")
     sd = g.op("Gather", [g.op("Shape", ["decoder_input_ids"]), g.const(1, np.int64)], axis=0)
@@ -177,18 +191,21 @@ def build_encoder_decoder(cfg: EncoderDecoderConfig, weights: Optional[Dict[str,
     g.logits(x)
     ins = [vi("encoder_input_ids", T.INT32, ["batch", "enc_seq"]), vi("encoder_attention_mask", T.INT32, ["batch", "enc_seq"]),
            vi("decoder_input_ids", T.INT32, ["batch", "dec_seq"])]
+    if audio:
+        ins = [vi("encoder_input_features", T.FLOAT, ["batch", cfg.audio_features, "frames"]), vi("decoder_input_ids", T.INT32, ["batch", "dec_seq"])]
     encoder = ol.make_model(ol.make_graph(g.nodes, "encoder_decoder_init", ins, outs, list(g.inits.values())), opset=opset)
+    encoder.opset_imports["com.microsoft"] = 1
 
     # ---- decoder step
     d = _G(cfg, w)
-    ins = [vi("input_ids", T.INT32, ["rows", 1]), vi("encoder_attention_mask", T.INT32, ["rows", "enc_seq"])]
+    ins = [vi("input_ids", T.INT32, ["rows", 1])] + ([] if audio else [vi("encoder_attention_mask", T.INT32, ["rows", "enc_seq"])])
     for i in range(L):
         ins += [vi(f"past_key_self_{i}", T.FLOAT, ["rows", N, "past", hd]), vi(f"past_value_self_{i}", T.FLOAT, ["rows", N, "past", hd])]
     for i in range(L):
         ins += [vi(f"past_key_cross_{i}", T.FLOAT, ["rows", N, "enc_seq", hd]), vi(f"past_value_cross_{i}", T.FLOAT, ["rows", N, "enc_seq", hd])]
     past_len = d.op("Gather", [d.op("Shape", ["past_key_self_0"]), d.const(2, np.int64)], axis=0)
     x = d.embed("input_ids", "dec.pos", offset=past_len)
-    enc_bias = d.key_mask_bias("encoder_attention_mask")
+    enc_bias = None if audio else d.key_mask_bias("encoder_attention_mask")
     outs = [vi("logits", T.FLOAT, ["rows", 1, cfg.vocab_size])]
     for i in range(L):
         p = f"dec.{i}"
@@ -206,8 +223,9 @@ def build_encoder_decoder(cfg: EncoderDecoderConfig, weights: Optional[Dict[str,
     return encoder, decoder
 
 
-def reference_logits(cfg: EncoderDecoderConfig, w: Dict[str, np.ndarray], enc_ids: np.ndarray, enc_mask: np.ndarray, dec_ids: np.ndarray) -> np.ndarray:
-    """Decoder logits [B, Sd, V] of one full pass (float64)."""
+def reference_logits(cfg: EncoderDecoderConfig, w: Dict[str, np.ndarray], enc_ids: np.ndarray, enc_mask: Optional[np.ndarray], dec_ids: np.ndarray) -> np.ndarray:
+    """Decoder logits [B, Sd, V] of one full pass (float64).  With cfg.audio_features, `enc_ids` holds the features
+    [B, audio_features, frames] and `enc_mask` is None."""
     f = {k: v.astype(np.float64) for k, v in w.items()}
     H, N = cfg.hidden_size, cfg.num_heads
     hd = H // N
@@ -232,8 +250,25 @@ def reference_logits(cfg: EncoderDecoderConfig, w: Dict[str, np.ndarray], enc_id
     def ffn(x, p):
         return lin(np.maximum(lin(x, p + ".fc1"), 0), p + ".fc2")
 
-    enc_bias = np.where(enc_mask[:, None, None, :] != 0, 0.0, -10000.0)
-    x = f["embed"][enc_ids] + f["enc.pos"][np.arange(enc_ids.shape[1])]
+    def conv1d(x, name, stride):  # x [B, C, L], kernel 3, padding 1
+        wt, b = f[name + ".weight"], f[name + ".bias"]
+        xp = np.pad(x, ((0, 0), (0, 0), (1, 1)))
+        cols = np.stack([xp[:, :, k:k + x.shape[2]] for k in range(3)], -1)          # [B, C, L, 3]
+        y = np.einsum("bclk,ock->bol", cols, wt) + b[None, :, None]
+        return y[:, :, ::stride]
+
+    def gelu(x):
+        from math import sqrt
+        erf = np.vectorize(math.erf)
+        return 0.5 * x * (1.0 + erf(x / sqrt(2.0)))
+
+    if cfg.audio_features:
+        x = gelu(conv1d(gelu(conv1d(enc_ids.astype(np.float64), "enc.conv1", 1)), "enc.conv2", 2)).transpose(0, 2, 1)
+        enc_bias = 0.0
+        x = x + f["enc.pos"][np.arange(x.shape[1])]
+    else:
+        enc_bias = np.where(enc_mask[:, None, None, :] != 0, 0.0, -10000.0)
+        x = f["embed"][enc_ids] + f["enc.pos"][np.arange(enc_ids.shape[1])]
     for i in range(cfg.encoder_layers):
         p = f"enc.{i}"
         h = ln(x, p + ".ln1")

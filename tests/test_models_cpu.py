@@ -229,3 +229,30 @@ def test_encoder_decoder_builder_under_greedy_and_beam_search():
     seqs, _ = ort.InferenceSession(beam.serialize(), providers=["CPUExecutionProvider"]).run(
         None, dict(common, num_beams=np.array([1], np.int32), num_return_sequences=np.array([1], np.int32), length_penalty=np.array([1.0], np.float32)))
     np.testing.assert_array_equal(seqs[:, 0], want.astype(np.int32))
+
+
+def test_whisper_shaped_builder_under_whisper_beam_search():
+    """Audio front end (two Conv1d + GELU, stride 2) in front of the same encoder-decoder: the WhisperBeamSearch wrapper
+    with one beam decodes what the arg-max loop over the numpy model decodes."""
+    import numpy as np
+    from onnxruntime_b200.models import encoder_decoder as ed
+    from onnxruntime_b200.transformers import convert_generation as cg
+    cfg = ed.EncoderDecoderConfig(vocab_size=41, audio_features=6, encoder_layers=1, decoder_layers=2)
+    w = ed.init_weights(cfg, seed=4, scale=0.3)
+    encoder, decoder = ed.build_encoder_decoder(cfg, w)
+    rng = np.random.RandomState(5)
+    feats = rng.randn(2, 6, 20).astype(np.float32)
+    start = 2
+    es = ort.InferenceSession(encoder.serialize(), providers=["CPUExecutionProvider"])
+    dec = np.full((2, 1), start, np.int32)
+    eo = es.run(None, {"encoder_input_features": feats, "decoder_input_ids": dec})
+    assert eo[1].shape == (2, 10, cfg.hidden_size)
+    np.testing.assert_allclose(eo[0], ed.reference_logits(cfg, w, feats, None, dec), rtol=5e-4, atol=5e-5)
+    want = np.full((2, 1), start, np.int64)
+    for _ in range(5):
+        want = np.concatenate([want, ed.reference_logits(cfg, w, feats, None, want)[:, -1].argmax(-1)[:, None]], 1)
+    model = cg.convert(decoder, op="whisper", encoder=encoder, eos_token_id=cfg.vocab_size + 3, decoder_start_token_id=start)
+    seqs, _ = ort.InferenceSession(model.serialize(), providers=["CPUExecutionProvider"]).run(
+        None, {"input_features": feats, "max_length": np.array([6], np.int32), "min_length": np.array([0], np.int32), "num_beams": np.array([1], np.int32),
+               "num_return_sequences": np.array([1], np.int32), "length_penalty": np.array([1.0], np.float32), "repetition_penalty": np.array([1.0], np.float32)})
+    np.testing.assert_array_equal(seqs[:, 0], want.astype(np.int32))
