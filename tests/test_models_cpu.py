@@ -256,3 +256,21 @@ def test_whisper_shaped_builder_under_whisper_beam_search():
         None, {"input_features": feats, "max_length": np.array([6], np.int32), "min_length": np.array([0], np.int32), "num_beams": np.array([1], np.int32),
                "num_return_sequences": np.array([1], np.int32), "length_penalty": np.array([1.0], np.float32), "repetition_penalty": np.array([1.0], np.float32)})
     np.testing.assert_array_equal(seqs[:, 0], want.astype(np.int32))
+
+
+def test_diffusion_unet_stage_matches_torch():
+    """ResNet block + spatial transformer in the fused diffusion operators (GroupNorm + SiLU, NhwcConv, MultiHeadAttention,
+    BiasSplitGelu, BiasAdd) against a plain torch restatement."""
+    import numpy as np
+    from onnxruntime_b200.models import diffusion
+    cfg = diffusion.UNetStageConfig()
+    w = diffusion.init_weights(cfg, seed=2)
+    sess = ort.InferenceSession(diffusion.build_unet_stage(cfg, w), providers=["CPUExecutionProvider"])
+    rng = np.random.RandomState(1)
+    sample = rng.randn(2, cfg.channels, 6, 5).astype(np.float32)
+    temb = rng.randn(2, cfg.time_dim).astype(np.float32)
+    text = rng.randn(2, 7, cfg.text_dim).astype(np.float32)
+    (y,) = sess.run(None, {"sample": sample, "time_embedding": temb, "encoder_hidden_states": text})
+    ref = diffusion.reference_forward(cfg, w, sample, temb, text)
+    assert y.shape == sample.shape
+    np.testing.assert_allclose(y, ref, rtol=2e-4, atol=2e-4)
