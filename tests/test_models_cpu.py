@@ -274,3 +274,23 @@ def test_diffusion_unet_stage_matches_torch():
     ref = diffusion.reference_forward(cfg, w, sample, temb, text)
     assert y.shape == sample.shape
     np.testing.assert_allclose(y, ref, rtol=2e-4, atol=2e-4)
+
+
+def test_phi_style_decoder_with_partial_rotary_matches_the_numpy_model():
+    """Parallel attention / MLP block, rotary embedding on part of every head inside GroupQueryAttention: prompt pass plus
+    token-by-token passes over the returned caches against one full pass of the numpy restatement."""
+    import numpy as np
+    from onnxruntime_b200.models import phi
+    cfg = phi.PhiConfig()
+    w = phi.init_weights(cfg, seed=7)
+    sess = ort.InferenceSession(phi.build_phi(cfg, w), providers=["CPUExecutionProvider"])
+    rng = np.random.RandomState(3)
+    ids = rng.randint(0, cfg.vocab_size, (2, 8))
+    ref = phi.reference_forward(cfg, w, ids)
+    names = [o.name for o in sess.get_outputs()]
+    outs = sess.run(None, phi.step_feeds(cfg, ids[:, :5], phi.empty_past(cfg, 2)))
+    np.testing.assert_allclose(outs[0], ref[:, :5], rtol=3e-4, atol=3e-5)
+    for t in range(5, 8):
+        past = {n.replace("present", "past_key_values"): v for n, v in zip(names[1:], outs[1:])}
+        outs = sess.run(None, phi.step_feeds(cfg, ids[:, t:t + 1], past))
+        np.testing.assert_allclose(outs[0][:, 0], ref[:, t], rtol=3e-4, atol=3e-5)
