@@ -294,3 +294,20 @@ def test_phi_style_decoder_with_partial_rotary_matches_the_numpy_model():
         past = {n.replace("present", "past_key_values"): v for n, v in zip(names[1:], outs[1:])}
         outs = sess.run(None, phi.step_feeds(cfg, ids[:, t:t + 1], past))
         np.testing.assert_allclose(outs[0][:, 0], ref[:, t], rtol=3e-4, atol=3e-5)
+
+
+def test_longformer_style_encoder_matches_the_numpy_model():
+    import numpy as np
+    from onnxruntime_b200.models import longformer as lf
+    cfg = lf.LongformerConfig()
+    w = lf.init_weights(cfg, seed=9)
+    sess = ort.InferenceSession(lf.build_longformer(cfg, w), providers=["CPUExecutionProvider"])
+    rng = np.random.RandomState(4)
+    ids = rng.randint(0, cfg.vocab_size, (2, 12))
+    mask = np.zeros((2, 12), np.float32)
+    mask[1, 10:] = -10000.0
+    glob = np.zeros((2, 12), np.int32)
+    glob[:, 0] = 1
+    glob[0, 7] = 1
+    (y,) = sess.run(None, {"input_ids": ids, "attention_mask": mask, "global_attention_mask": glob})
+    np.testing.assert_allclose(y, lf.reference_forward(cfg, w, ids, mask, glob), rtol=3e-4, atol=3e-5)
