@@ -88,6 +88,7 @@ void EnsureKernelsRegistered() {
     RegisterContribKernels3(g);
     RegisterContribKernels4(g);
     RegisterContribKernels5(g);
+    RegisterContribKernels6(g);
     RegisterOnnxExtraKernels(g);
     RegisterOnnxExtraKernels2(g);
     RegisterOnnxExtraKernels3(g);

@@ -365,3 +365,59 @@ def test_contrib_aliases_of_onnx_operators_and_unique():
     np.testing.assert_array_equal(y, [5, 2, 9])
     np.testing.assert_array_equal(idx, [0, 1, 0, 2, 1, 0])
     np.testing.assert_array_equal(counts, [3, 2, 1])
+
+
+def test_attn_lstm_against_a_numpy_restatement():
+    """AttnLSTM (LSTM cell wrapped by Bahdanau attention) against the documented equations, forward and bidirectional,
+    with sequence lengths, memory lengths, peepholes and the attention layer."""
+    import numpy as np
+    from helpers import run_node
+    rng = np.random.RandomState(0)
+    S, B, I, H, steps, depth, att, aw = 5, 3, 4, 6, 7, 5, 8, 3
+
+    def sig(x):
+        return 1 / (1 + np.exp(-x))
+
+    def run_dir(X, W, R, Bb, P, QW, MW, V, M, mlens, AW, lens, reverse):
+        mask = np.arange(steps)[None, :] < mlens[:, None]
+        values = M * mask[..., None]
+        keys = values @ MW
+        h, c = np.zeros((B, H)), np.zeros((B, H))
+        attn = np.zeros((B, AW.shape[1]))
+        Y = np.zeros((S, B, H))
+        bias = Bb[:4 * H] + Bb[4 * H:]
+        for step in range(S):
+            for b in range(B):
+                if step >= lens[b]:
+                    continue
+                t = lens[b] - 1 - step if reverse else step
+                g = np.concatenate([X[t, b], attn[b]]) @ W.T + h[b] @ R.T + bias
+                gi, go, gf, gc = g[:H], g[H:2 * H], g[2 * H:3 * H], g[3 * H:]
+                it, ft = sig(gi + P[:H] * c[b]), sig(gf + P[2 * H:] * c[b])
+                cn = ft * c[b] + it * np.tanh(gc)
+                hn = sig(go + P[H:2 * H] * cn) * np.tanh(cn)
+                score = (np.tanh(keys[b] + hn @ QW) * V).sum(-1)
+                score = np.where(mask[b], score, -np.inf)
+                al = np.exp(score - score.max())
+                al = al / al.sum()
+                attn[b] = np.concatenate([hn, al @ values[b]]) @ AW
+                h[b], c[b] = hn, cn
+                Y[t, b] = hn
+        return Y, h, c
+
+    for direction, D in (("forward", 1), ("bidirectional", 2)):
+        X = rng.randn(S, B, I)
+        W, R, Bb = rng.randn(D, 4 * H, I + aw) * 0.3, rng.randn(D, 4 * H, H) * 0.3, rng.randn(D, 8 * H) * 0.1
+        P, QW, MW, V = rng.randn(D, 3 * H) * 0.2, rng.randn(D, H, att) * 0.3, rng.randn(D, depth, att) * 0.3, rng.randn(D, att)
+        M, AW = rng.randn(B, steps, depth), rng.randn(D, depth + H, aw) * 0.3
+        lens, mlens = np.array([5, 3, 4], np.int32), np.array([7, 4, 6], np.int32)
+        f = lambda a: a.astype(np.float32)
+        y, yh, yc = run_node("AttnLSTM", {"X": f(X), "W": f(W), "R": f(R), "B": f(Bb), "sequence_lens": lens, "initial_h": None, "initial_c": None,
+                                          "P": f(P), "QW": f(QW), "MW": f(MW), "V": f(V), "M": f(M), "memory_seq_lens": mlens, "AW": f(AW)},
+                             n_outputs=3, domain="com.microsoft", hidden_size=H, direction=direction)
+        assert y.shape == (S, D, B, H)
+        for d in range(D):
+            Y, hl, cl = run_dir(X, W[d], R[d], Bb[d], P[d], QW[d], MW[d], V[d], M, mlens, AW[d], lens, reverse=(d == 1))
+            np.testing.assert_allclose(y[:, d], Y, rtol=2e-4, atol=2e-5)
+            np.testing.assert_allclose(yh[d], hl, rtol=2e-4, atol=2e-5)
+            np.testing.assert_allclose(yc[d], cl, rtol=2e-4, atol=2e-5)
