@@ -240,6 +240,8 @@ def _to_torch(value: Any) -> torch.Tensor:
         value = value._tensor
     if isinstance(value, torch.Tensor):
         return value.to_dense() if value.layout != torch.strided else value
+    if isinstance(value, dict):      # a map-typed input (ai.onnx.ml CastMap / DictVectorizer): converted by the native layer
+        return value
     if _is_string_array(value):
         arr = np.asarray(value, dtype=object)
         flat = [s.decode("utf-8") if isinstance(s, bytes) else str(s) for s in arr.reshape(-1)]

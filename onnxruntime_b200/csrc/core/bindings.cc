@@ -52,6 +52,36 @@ std::vector<Value> ToValues(const std::vector<py::object>& objs) {
       // capi._StringTensor: strings + shape -> ids of the string table
       v.t = InternStrings(o.attr("strings").cast<std::vector<std::string>>(), o.attr("shape").cast<std::vector<int64_t>>());
       v.is_string = true;
+    } else if (py::isinstance<py::dict>(o)) {
+      // one map: int64 or string keys, numeric or string values (ai.onnx.ml CastMap / DictVectorizer inputs)
+      py::dict d = o.cast<py::dict>();
+      auto m = std::make_shared<MapRows>();
+      std::vector<int64_t> keys;
+      std::vector<double> vals;
+      std::vector<int64_t> string_vals;
+      bool values_are_strings = false;
+      for (auto kv : d) {
+        if (py::isinstance<py::str>(kv.first)) {
+          m->string_keys = true;
+          keys.push_back(InternString(kv.first.cast<std::string>()));
+        } else {
+          keys.push_back(kv.first.cast<int64_t>());
+        }
+        if (py::isinstance<py::str>(kv.second)) {
+          values_are_strings = true;
+          string_vals.push_back(InternString(kv.second.cast<std::string>()));
+        } else {
+          vals.push_back(kv.second.cast<double>());
+        }
+      }
+      m->keys = at::tensor(keys, at::kLong);
+      if (values_are_strings) {
+        m->values = at::tensor(string_vals, at::kLong).reshape({1, -1});
+        m->string_values = true;
+      } else {
+        m->values = at::tensor(vals, at::kDouble).reshape({1, -1});
+      }
+      v.maps = std::move(m);
     } else if (py::isinstance<py::list>(o) || py::isinstance<py::tuple>(o)) {
       v.seq = std::make_shared<std::vector<at::Tensor>>(o.cast<std::vector<at::Tensor>>());
     } else {

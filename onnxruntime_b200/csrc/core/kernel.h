@@ -33,7 +33,8 @@ using RunOptionsRef = RunOptions;
 struct MapRows {
   at::Tensor keys;           // [C] int64 (ids of the string table when string_keys)
   bool string_keys = false;
-  at::Tensor values;         // [N, C] float
+  at::Tensor values;         // [N, C] float (ids of the string table when string_values)
+  bool string_values = false;
 };
 
 struct Value {
@@ -83,6 +84,7 @@ class OpKernelContext {
     return in_[i].t;
   }
   const Value& InputValue(int i) const { return in_[i]; }
+  const MapRows* InputMaps(int i) const { return i < static_cast<int>(in_.size()) ? in_[i].maps.get() : nullptr; }
   bool InputIsString(int i) const { return i < static_cast<int>(in_.size()) && in_[i].is_string; }
   // output i is a tensor of strings: `ids` index the string table
   void SetOutputStrings(int i, at::Tensor ids) {

@@ -6,6 +6,7 @@
 #include <ATen/ATen.h>
 
 #include <algorithm>
+#include <cstdio>
 #include <cmath>
 #include <limits>
 #include <map>
@@ -637,6 +638,66 @@ void RegisterMlKernels(KernelRegistry& r) {
     m.keys = at::tensor(keys, at::kLong);
     m.values = x.contiguous();
     ctx.SetOutputMaps(0, std::move(m));
+  });
+  // CastMap: map<int64, string | float> -> [1, C] tensor.  DENSE: the values in ascending key order; SPARSE: position = key,
+  // max_map entries, zeros elsewhere.  cast_to: TO_FLOAT / TO_INT64 / TO_STRING.
+  r.RegisterFn(ML, "CastMap", 1, kMax, [](Ctx& ctx) {
+    const Node& n = ctx.node();
+    const MapRows* m = ctx.InputMaps(0);
+    ORTB_ENFORCE_ARG(m != nullptr && !m->string_keys && m->values.size(0) == 1, "CastMap: the input must be one map with int64 keys");
+    const std::string to = n.attr_s("cast_to", "TO_FLOAT"), form = n.attr_s("map_form", "DENSE");
+    at::Tensor order = at::argsort(m->keys);
+    at::Tensor keys = m->keys.index_select(0, order), vals = m->values[0].index_select(0, order);
+    // every value as a double (strings are parsed) and as a string id (numbers are printed), then the asked-for one is used
+    std::vector<std::string> text;
+    at::Tensor numeric;
+    if (m->string_values) {
+      text = StringsOfTensor(vals);
+      numeric = at::empty({vals.numel()}, at::kDouble);
+      if (to != "TO_STRING")
+        for (size_t i = 0; i < text.size(); ++i) numeric[static_cast<int64_t>(i)] = std::stod(text[i]);
+    } else {
+      numeric = vals.to(at::kDouble);
+      if (to == "TO_STRING")
+        for (int64_t i = 0; i < numeric.numel(); ++i) {
+          const double v = numeric[i].item<double>();
+          char buf[64];
+          if (v == std::floor(v) && std::fabs(v) < 1e15) std::snprintf(buf, sizeof(buf), "%lld", static_cast<long long>(v));
+          else std::snprintf(buf, sizeof(buf), "%g", v);
+          text.emplace_back(buf);
+        }
+    }
+    int64_t width = keys.numel();
+    at::Tensor position = at::arange(width, at::kLong);
+    if (form == "SPARSE") {
+      width = n.attr_i("max_map", 1);
+      position = keys;
+      ORTB_ENFORCE_ARG(keys.numel() == 0 || (keys.min().item<int64_t>() >= 0 && keys.max().item<int64_t>() < width), "CastMap: a key lies outside [0, max_map)");
+    }
+    if (to == "TO_STRING") {
+      at::Tensor ids = at::full({width}, InternString(form == "SPARSE" ? "0" : ""), at::kLong);
+      std::vector<int64_t> v;
+      for (auto& s : text) v.push_back(InternString(s));
+      ids.index_put_({position}, at::tensor(v, at::kLong));
+      ctx.SetOutputStrings(0, ids.reshape({1, width}));
+      return;
+    }
+    at::Tensor out = at::zeros({width}, at::kDouble).index_put_({position}, numeric);
+    ctx.SetOutput(0, out.reshape({1, width}).to(to == "TO_INT64" ? at::kLong : at::kFloat));
+  });
+  // DictVectorizer: map<string | int64, number> -> [1, vocabulary] tensor with the map's value at every vocabulary entry (0 when absent)
+  r.RegisterFn(ML, "DictVectorizer", 1, kMax, [](Ctx& ctx) {
+    const Node& n = ctx.node();
+    const MapRows* m = ctx.InputMaps(0);
+    ORTB_ENFORCE_ARG(m != nullptr && !m->string_values, "DictVectorizer: the input must be a map with numeric values");
+    std::vector<int64_t> vocab = n.attr_ints("int64_vocabulary");
+    if (m->string_keys) {
+      vocab.clear();
+      for (auto& s : n.attr_strings("string_vocabulary")) vocab.push_back(InternString(s));
+    }
+    at::Tensor hit = at::tensor(vocab, at::kLong).unsqueeze(1).eq(m->keys.unsqueeze(0)).to(at::kDouble);   // [V, C]
+    at::Tensor out = at::matmul(m->values.to(at::kDouble), hit.t());                                         // [N, V]
+    ctx.SetOutput(0, out.to(at::kFloat));
   });
   r.RegisterFn(ML, "Scaler", 1, kMax, [](Ctx& ctx) {
     at::Tensor x = ctx.RequiredInput(0).to(at::kFloat);

@@ -27,6 +27,8 @@ def run_node(op_type: str, inputs: Dict[str, Optional[np.ndarray]], n_outputs: i
             continue
         if n in initializers:
             inits.append(ol.make_tensor(n, v))
+        elif isinstance(v, dict):     # a map-typed input: no tensor type to declare
+            graph_inputs.append(ol.make_tensor_value_info(n, 0, None))
         else:
             graph_inputs.append(ol.make_tensor_value_info(n, ol.np_dtype_to_onnx(v.dtype), list(v.shape)))
     graph = ol.make_graph([node], "test", graph_inputs, [ol.make_tensor_value_info(o, 0, None) for o in out_names], inits)

@@ -346,3 +346,16 @@ def test_tree_ensemble_opset5_spec_examples():
             leaf_targetids=[0, 1, 0, 1], leaf_weights=np.array([5.23, 12.12, -12.23, 7.21], np.float32))
     # node 0: x0 <= 3.14 ? node 1 : node 2;  node 1: x0 <= 1.2 ? leaf 0 : leaf 2;  node 2: x0 <= 4.2 ? leaf 1 : leaf 3
     np.testing.assert_allclose(y, [[5.23, 0], [5.23, 0], [0, 7.21]], rtol=1e-6)
+
+
+def test_cast_map_and_dict_vectorizer_take_python_dicts():
+    (y,) = run_node("DictVectorizer", {"X": {"b": 2.5, "zz": 9.0, "a": 1.0}}, domain=ML, string_vocabulary=["a", "b", "c"])
+    np.testing.assert_array_equal(y, [[1.0, 2.5, 0.0]])
+    (y,) = run_node("DictVectorizer", {"X": {7: 0.5, 3: 4.0}}, domain=ML, int64_vocabulary=[3, 5, 7])
+    np.testing.assert_array_equal(y, [[4.0, 0.0, 0.5]])
+    (y,) = run_node("CastMap", {"X": {4: "2.5", 1: "7"}}, domain=ML, cast_to="TO_FLOAT", map_form="DENSE")
+    np.testing.assert_array_equal(y, [[7.0, 2.5]])
+    (y,) = run_node("CastMap", {"X": {4: 2.0, 1: 7.0}}, domain=ML, cast_to="TO_INT64", map_form="SPARSE", max_map=6)
+    np.testing.assert_array_equal(y, [[0, 7, 0, 0, 2, 0]])
+    (y,) = run_node("CastMap", {"X": {0: 1.5, 2: 3.0}}, domain=ML, cast_to="TO_STRING", map_form="DENSE")
+    assert y.tolist() == [["1.5", "3"]]
