@@ -792,6 +792,32 @@ def register_custom_op(domain: str, op_type: str, fn) -> None:
     C.register_python_op(domain, op_type, fn)
 
 
+def _image_decoder(encoded_stream, pixel_format="RGB", **_unused):
+    """ONNX ImageDecoder (opset 20): encoded image bytes (JPEG, PNG, BMP, ...) -> [H, W, C] uint8 in RGB, BGR or Grayscale.
+    Decoding is Pillow's, so this operator runs as a Python callable registered with the kernel registry when the package
+    is imported (the registry has no image codec of its own)."""
+    import io
+
+    from PIL import Image
+    fmt = pixel_format.decode() if isinstance(pixel_format, bytes) else str(pixel_format)
+    img = Image.open(io.BytesIO(bytes(encoded_stream.cpu().numpy().astype(np.uint8).tobytes())))
+    if fmt == "Grayscale":
+        arr = np.asarray(img.convert("L"))[:, :, None]
+    else:
+        arr = np.asarray(img.convert("RGB"))
+        if fmt == "BGR":
+            arr = arr[:, :, ::-1]
+        elif fmt != "RGB":
+            raise InvalidArgument(f"ImageDecoder: unknown pixel_format '{fmt}'")
+    return torch.from_numpy(np.array(arr, copy=True))
+
+
+try:
+    C.register_python_op("", "ImageDecoder", _image_decoder)
+except Exception:  # pragma: no cover - the native module decides whether Python operators are available
+    pass
+
+
 # --------------------------------------------------------------- provider args
 def check_and_normalize_provider_args(providers, provider_options, available) -> Tuple[List[str], List[Dict[str, str]]]:
     """Same contract as the reference helper (onnxruntime_inference_collection.py:119)."""

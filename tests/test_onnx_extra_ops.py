@@ -298,3 +298,22 @@ def test_sequence_map_runs_the_body_per_element():
     z, shapes = sess.run(None, {"x": x, "y": y})
     np.testing.assert_allclose(z, 2 * x + y, rtol=1e-6)
     np.testing.assert_array_equal(shapes, [[1, 3], [2, 3], [3, 3]])
+
+
+def test_image_decoder_png_and_jpeg():
+    import io
+    from PIL import Image
+    img = (rng.random((9, 7, 3)) * 255).astype(np.uint8)
+    buf = io.BytesIO()
+    Image.fromarray(img).save(buf, format="PNG")
+    png = np.frombuffer(buf.getvalue(), np.uint8).copy()
+    (y,) = run_node("ImageDecoder", {"x": png}, opset=20, pixel_format="RGB")
+    np.testing.assert_array_equal(y, img)
+    (y,) = run_node("ImageDecoder", {"x": png}, opset=20, pixel_format="BGR")
+    np.testing.assert_array_equal(y, img[:, :, ::-1])
+    (y,) = run_node("ImageDecoder", {"x": png}, opset=20, pixel_format="Grayscale")
+    assert y.shape == (9, 7, 1) and y.dtype == np.uint8
+    buf = io.BytesIO()
+    Image.fromarray(np.full((8, 8, 3), 200, np.uint8)).save(buf, format="JPEG", quality=95)
+    (y,) = run_node("ImageDecoder", {"x": np.frombuffer(buf.getvalue(), np.uint8).copy()}, opset=20)
+    assert y.shape == (8, 8, 3) and abs(int(y.mean()) - 200) <= 2
