@@ -357,15 +357,19 @@ class OrtValue:
         return self._tensor.data_ptr()
 
     def device_name(self) -> str:
-        return "cuda" if self._tensor.is_cuda else "cpu"
+        return "cuda" if getattr(self._tensor, "is_cuda", False) else "cpu"
 
     def shape(self) -> List[int]:
         return list(self._tensor.shape)
 
     def data_type(self) -> str:
+        if isinstance(self._tensor, _StringTensor):
+            return "tensor(string)"
         return _TORCH_TO_TYPESTR.get(self._tensor.dtype, "tensor(unknown)")
 
     def element_type(self) -> int:
+        if isinstance(self._tensor, _StringTensor):
+            return 8
         for k, v in _ONNX_ELEM_TO_TORCH.items():
             if v == self._tensor.dtype:
                 return k
@@ -393,6 +397,8 @@ class OrtValue:
         return False
 
     def numpy(self) -> np.ndarray:
+        if isinstance(self._tensor, _StringTensor):
+            return self._tensor.numpy()
         return _to_numpy(self._tensor)
 
     def update_inplace(self, np_arr: np.ndarray) -> None:
@@ -1057,7 +1063,8 @@ class InferenceSession:
         names = list(input_dict_ort_values.keys())
         feeds = [_to_torch(v) for v in input_dict_ort_values.values()]
         outs = self._sess.run(ro, names, feeds, list(output_names or []))
-        return [OrtValue(o) for o in outs]
+        # a string output comes back as ("__strings__", values, shape)
+        return [OrtValue(_StringTensor(o[1], o[2]) if isinstance(o, tuple) and len(o) == 3 and o[0] == "__strings__" else o) for o in outs]
 
     def run_with_ortvaluevector(self, run_options, feed_names: Sequence[str], feeds: "OrtValueVector", fetch_names: Sequence[str],
                                 fetches: "OrtValueVector", fetch_devices: Sequence[OrtDevice]) -> None:

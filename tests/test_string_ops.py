@@ -131,3 +131,13 @@ def test_string_initializer_through_ort_format():
     assert [s.decode() for s in back.graph.initializers[0].strings] == ["zero", "one", "two"]
     sess = ort.InferenceSession(buf, providers=["CPUExecutionProvider"])
     assert sess.run(None, {"idx": np.array([2, 2, 0], np.int64)})[0].tolist() == ["two", "two", "zero"]
+
+
+def test_string_tensors_through_ort_values():
+    model = graph_model([ol.make_node("StringNormalizer", ["x"], ["y"], case_change_action="UPPER")], [ol.make_tensor_value_info("x", T.STRING, ["n"])],
+                        [ol.make_tensor_value_info("y", T.STRING, None)])
+    sess = ort.InferenceSession(model, providers=["CPUExecutionProvider"])
+    v = ort.OrtValue.ortvalue_from_numpy(S("ab", "cd"))
+    assert v.data_type() == "tensor(string)" and v.shape() == [2] and v.numpy().tolist() == ["ab", "cd"]
+    (out,) = sess.run_with_ort_values(None, {"x": v})
+    assert out.data_type() == "tensor(string)" and out.numpy().tolist() == ["AB", "CD"]
