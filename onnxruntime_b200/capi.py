@@ -238,6 +238,8 @@ def _to_torch(value: Any) -> torch.Tensor:
         return value._t.to_dense()
     if isinstance(value, OrtValue):
         value = value._tensor
+    if isinstance(value, _StringTensor):
+        return value
     if isinstance(value, torch.Tensor):
         return value.to_dense() if value.layout != torch.strided else value
     if isinstance(value, dict):      # a map-typed input (ai.onnx.ml CastMap / DictVectorizer): converted by the native layer
