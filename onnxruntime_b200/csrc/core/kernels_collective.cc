@@ -189,10 +189,15 @@ class ShardedMoeKernel final : public OpKernel {
     attrs_ = contrib::ParseMoeAttrs(info.node);
     start_ = info.node.attr_i("local_experts_start_index", 0);
     tensor_shards_ = info.node.attr_i("tensor_shards", 1);
+    tokens_sharded_ = info.node.attr_i("tokens_sharded", 0) != 0;
   }
   void Compute(Ctx& ctx) const override {
     InferenceSession* s = ctx.session();
     const at::Tensor& x = ctx.RequiredInput(0);
+    if (tokens_sharded_ && s && s->world_size > 1) {
+      ComputeTokenSharded(ctx);
+      return;
+    }
     at::Tensor x2 = x.reshape({-1, x.size(-1)});
     auto opt = [&](int i) { return ctx.HasInput(i) ? ctx.Input(i) : at::Tensor(); };
     // to the [E, out, in] layout of the dense MoE math
@@ -212,9 +217,61 @@ class ShardedMoeKernel final : public OpKernel {
     ctx.SetOutput(0, y.reshape(x.sizes()));
   }
 
+  // tokens_sharded = 1 (an attribute of this runtime, not of the reference): every rank holds its own tokens.  A token's row
+  // (with its router logits) travels once to every rank that owns one of its top-k experts (all-to-all dispatch), that rank
+  // adds up its experts' weighted outputs for the row, and the partial sums travel back (all-to-all combine) to be added per
+  // token.  Rows per (source, destination) pair vary, so both exchanges are padded to the largest pair count, which the ranks
+  // learn from an all-gather of their count vectors.  Experts must be split evenly over the ranks, rank r owning the r-th part.
+  void ComputeTokenSharded(Ctx& ctx) const {
+    InferenceSession* s = ctx.session();
+    const int64_t world = s->world_size;
+    const at::Tensor& x_in = ctx.RequiredInput(0);
+    at::Tensor x = x_in.reshape({-1, x_in.size(-1)}).to(at::kFloat);
+    at::Tensor logits = ctx.RequiredInput(1).reshape({x.size(0), -1}).to(at::kFloat);
+    const int64_t T = x.size(0), H = x.size(1), E = logits.size(1);
+    auto opt = [&](int i) { return ctx.HasInput(i) ? ctx.Input(i) : at::Tensor(); };
+    at::Tensor fc1 = ctx.RequiredInput(2).transpose(1, 2), fc2 = ctx.RequiredInput(4).transpose(1, 2);
+    at::Tensor fc3 = ctx.HasInput(6) ? ctx.Input(6).transpose(1, 2) : at::Tensor();
+    const int64_t e_local = fc1.size(0);
+    ORTB_ENFORCE_ARG(e_local * world == E && start_ == s->rank * e_local, "ShardedMoE (tokens_sharded): experts must be split evenly, rank r owning part r");
+    ORTB_ENFORCE_ARG(tensor_shards_ == 1, "ShardedMoE (tokens_sharded): tensor-sharded experts are not supported in this mode");
+    auto lopt = at::TensorOptions().dtype(at::kLong).device(x.device());
+    // which ranks does every token need?
+    at::Tensor owner = std::get<1>(logits.topk(attrs_.k, 1)).floor_divide(e_local);                   // [T, k]
+    at::Tensor need = at::zeros({T, world}, lopt.dtype(at::kBool)).scatter_(1, owner, true);          // [T, world]
+    at::Tensor counts = need.sum(0).to(at::kLong);                                                   // rows this rank sends to every rank
+    at::Tensor all_counts = AllGatherAxis(s, counts.reshape({1, world}), 0).to(at::kCPU);            // [source, destination]
+    const int64_t cap = std::max<int64_t>(all_counts.max().item<int64_t>(), 1);
+    // dispatch: [destination, cap, H + E], rows beyond a pair's count are zero
+    at::Tensor send = at::zeros({world, cap, H + E}, x.options());
+    std::vector<at::Tensor> rows_for(static_cast<size_t>(world));
+    at::Tensor payload = at::cat({x, logits}, 1);
+    for (int64_t d = 0; d < world; ++d) {
+      rows_for[static_cast<size_t>(d)] = need.select(1, d).nonzero().reshape({-1});
+      const int64_t n = rows_for[static_cast<size_t>(d)].numel();
+      if (n > 0) send[d].narrow(0, 0, n).copy_(payload.index_select(0, rows_for[static_cast<size_t>(d)]));
+    }
+    at::Tensor recv = AllToAllEqual(s, send.reshape({world * cap, H + E})).reshape({world, cap, H + E});
+    // this rank's experts on everything it received (padding rows included: their results are never read)
+    at::Tensor got = recv.reshape({world * cap, H + E});
+    at::Tensor fc2_bias = opt(5);
+    if (fc2_bias.defined() && fc2_bias.size(0) != e_local) fc2_bias = fc2_bias.narrow(0, start_, e_local);
+    at::Tensor partial = contrib::MoeForward(got.narrow(1, 0, H), got.narrow(1, H, E), fc1, opt(3), fc2, fc2_bias, fc3, opt(7), attrs_, start_,
+                                             start_ + e_local).to(at::kFloat);
+    // combine: the partial sums go back to where the rows came from
+    at::Tensor back = AllToAllEqual(s, partial.reshape({world * cap, H})).reshape({world, cap, H});
+    at::Tensor out = at::zeros({T, H}, x.options());
+    for (int64_t d = 0; d < world; ++d) {
+      const at::Tensor& rows = rows_for[static_cast<size_t>(d)];
+      if (rows.numel() > 0) out.index_add_(0, rows, back[d].narrow(0, 0, rows.numel()));
+    }
+    ctx.SetOutput(0, out.to(x_in.scalar_type()).reshape(x_in.sizes()));
+  }
+
  private:
   contrib::MoeAttrs attrs_;
   int64_t start_ = 0, tensor_shards_ = 1;
+  bool tokens_sharded_ = false;
 };
 
 }  // namespace

@@ -480,8 +480,9 @@ class MoeKernel final : public WithFallback {
     const at::Tensor& logits_in = ctx.RequiredInput(1);
     const int dt = DtypeCode(x.scalar_type());
     const bool fc3_bias = ctx.HasInput(b3_);
+    // tokens_sharded: the dispatch / combine form lives in the generic kernel (process-group all-to-all around the experts)
     if (!ok_ || dt < 0 || x.scalar_type() != w13_.scalar_type() || x.size(-1) != H_ || fc3_bias ||
-        attrs_.k > 8 || logits_in.size(-1) > 256) {
+        attrs_.k > 8 || logits_in.size(-1) > 256 || node_.attr_i("tokens_sharded", 0) != 0) {
       Fallback(ctx);
       return;
     }

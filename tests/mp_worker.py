@@ -93,6 +93,33 @@ def case_sharded_moe(info, device, out):
     torch.save({"y": torch.from_numpy(y), "ref": torch.from_numpy(ref)}, os.path.join(out, f"rank{r}.pt"))
 
 
+def case_sharded_moe_tokens(info, device, out):
+    """ShardedMoE with tokens_sharded = 1: every rank feeds its own tokens; the rows travel to the experts' ranks and back."""
+    r, w = info.rank, info.world_size
+    rng = np.random.RandomState(0)
+    Tn, H, I, E, k = 10, 16, 24, 3 * w, 2
+    x_all = rng.randn(w, Tn, H).astype(np.float32)
+    logits_all = np.stack([np.stack([rng.permutation(np.linspace(-2.0, 2.0, E)) for _ in range(Tn)]) for _ in range(w)]).astype(np.float32)
+    logits_all[0, :, :] = logits_all[0, :, ::-1] if w > 1 else logits_all[0]
+    fc1, fc2, fc3 = rng.randn(E, H, I).astype(np.float32) * 0.2, rng.randn(E, I, H).astype(np.float32) * 0.2, rng.randn(E, H, I).astype(np.float32) * 0.2
+    el = E // w
+    sl = slice(r * el, (r + 1) * el)
+    g = ol.make_graph([ol.make_node("ShardedMoE", ["x", "p", "fc1", "", "fc2", "", "fc3"], ["y"], domain="com.microsoft", k=k, activation_type="silu",
+                                    normalize_routing_weights=1, local_experts_start_index=r * el, tokens_sharded=1)], "g",
+                      [ol.make_tensor_value_info("x", T.FLOAT, [Tn, H]), ol.make_tensor_value_info("p", T.FLOAT, [Tn, E])],
+                      [ol.make_tensor_value_info("y", T.FLOAT, None)],
+                      [ol.make_tensor("fc1", fc1[sl]), ol.make_tensor("fc2", fc2[sl]), ol.make_tensor("fc3", fc3[sl])])
+    y = session(ol.make_model(g).serialize(), info, device).run(None, {"x": x_all[r], "p": logits_all[r]})[0]
+    g2 = ol.make_graph([ol.make_node("MoE", ["x", "p", "fc1", "", "fc2", "", "fc3"], ["y"], domain="com.microsoft", k=k, activation_type="silu",
+                                     normalize_routing_weights=1)], "g",
+                       [ol.make_tensor_value_info("x", T.FLOAT, [Tn, H]), ol.make_tensor_value_info("p", T.FLOAT, [Tn, E])],
+                       [ol.make_tensor_value_info("y", T.FLOAT, None)],
+                       [ol.make_tensor("fc1", fc1.transpose(0, 2, 1).copy()), ol.make_tensor("fc2", fc2.transpose(0, 2, 1).copy()),
+                        ol.make_tensor("fc3", fc3.transpose(0, 2, 1).copy())])
+    ref = ort.InferenceSession(ol.make_model(g2).serialize(), providers=["CPUExecutionProvider"]).run(None, {"x": x_all[r], "p": logits_all[r]})[0]
+    torch.save({"y": torch.from_numpy(y), "ref": torch.from_numpy(ref)}, os.path.join(out, f"rank{r}.pt"))
+
+
 def case_sharded_moe_gpu(info, device, out):
     """ShardedMoE in fp16 on GPUs, with the fused cross-rank combine (symmetric workspace) and with the library all-reduce,
     against the single-device MoE on the full expert set (the design of the reference's own parity test,

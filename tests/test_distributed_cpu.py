@@ -55,6 +55,15 @@ def test_sharded_moe_matches_single_device_moe(tmp_path):
         np.testing.assert_allclose(out[r]["y"].numpy(), out[r]["ref"].numpy(), rtol=1e-4, atol=1e-5)
 
 
+def test_sharded_moe_with_sharded_tokens_dispatches_and_combines(tmp_path):
+    """tokens_sharded = 1: every rank feeds different tokens; rows go to the ranks of their experts and the partial sums come
+    back.  Each rank's result equals the single-device MoE over the full expert set on that rank's tokens."""
+    out = launch("sharded_moe_tokens", "cpu", 2, tmp_path)
+    for r in range(2):
+        np.testing.assert_allclose(out[r]["y"].numpy(), out[r]["ref"].numpy(), rtol=1e-4, atol=1e-5)
+    assert not np.allclose(out[0]["ref"].numpy(), out[1]["ref"].numpy())
+
+
 def test_llama_tensor_parallel_matches_single_rank(tmp_path):
     out = launch("llama_tp", "cpu", 2, tmp_path)
     assert "AllReduce" in out[0]["ops"]
