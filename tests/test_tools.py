@@ -323,3 +323,17 @@ def test_offline_tuning_profile_explorer_and_io_binding_helper(tmp_path, capsys)
     cs = CudaSession(plain, torch.device("cpu"))
     cs.allocate_buffers({out_name: ref.shape})
     np.testing.assert_allclose(cs.infer({"x": torch.from_numpy(x)})[out_name].numpy(), ref, rtol=1e-6)
+
+
+def test_symbolic_shape_inference_front_end(tmp_path):
+    import numpy as np
+    from onnxruntime_b200 import onnx_lite as ol
+    from onnxruntime_b200.tools.symbolic_shape_infer import SymbolicShapeInference, main
+    model, _ = _two_layer_mlp()
+    out = SymbolicShapeInference.infer_shapes(model)
+    shapes = {v.name: list(v.shape) for v in out.graph.value_info if v.shape is not None}
+    assert any(len(s) == 2 for s in shapes.values()) and len(shapes) >= 2
+    src, dst = tmp_path / "m.onnx", tmp_path / "s.onnx"
+    src.write_bytes(model)
+    assert main(["--input", str(src), "--output", str(dst)]) == 0
+    assert len(ol.load_model(str(dst)).graph.value_info) >= len(shapes)
