@@ -230,14 +230,19 @@ class CalibrationDataReader:
 
 def quantize_static(model_input, calibration_feeds: Iterable[Dict[str, np.ndarray]], model_output: Optional[str] = None,
                     op_types: Sequence[str] = ("MatMul", "Gemm", "Conv"), per_channel: bool = False,
-                    calibrate_method: int = CalibrationMethod.MinMax, percentile: float = 99.999) -> ol.Model:
+                    calibrate_method: int = CalibrationMethod.MinMax, percentile: float = 99.999,
+                    quant_format: int = QuantFormat.QDQ) -> ol.Model:
     """QDQ format: uint8 asymmetric activations, int8 symmetric weights (per tensor, or per output channel).  The activation
-    ranges come from the extremes (MinMax), or from a histogram cut by KL divergence (Entropy) or by mass (Percentile)."""
+    ranges come from the extremes (MinMax), or from a histogram cut by KL divergence (Entropy) or by mass (Percentile).
+    quant_format = QuantFormat.QOperator writes MatMul nodes with a constant weight as QuantizeLinear -> QLinearMatMul ->
+    DequantizeLinear (their output ranges are calibrated too); other operators keep the QDQ form."""
     model = _load(model_input)
     g = model.graph
     inits = {t.name: t for t in g.initializers}
     targets = [n for n in g.nodes if n.op_type in op_types and n.domain == ""]
     acts = [n.inputs[0] for n in targets if n.inputs[0] not in inits]
+    if quant_format == QuantFormat.QOperator:
+        acts += [n.outputs[0] for n in targets if n.op_type == "MatMul" and len(n.inputs) > 1 and n.inputs[1] in inits]
     if calibrate_method == CalibrationMethod.Entropy:
         calib = EntropyCalibrator(model, acts)
     elif calibrate_method == CalibrationMethod.Percentile:
@@ -256,6 +261,25 @@ def quantize_static(model_input, calibration_feeds: Iterable[Dict[str, np.ndarra
             continue
         ins = list(n.inputs)
         a = ins[0]
+        w_t = inits.get(ins[1]) if len(ins) > 1 else None
+        if (quant_format == QuantFormat.QOperator and n.op_type == "MatMul" and w_t is not None and ol.to_array(w_t).dtype == np.float32
+                and ol.to_array(w_t).ndim == 2 and a in calib.ranges and n.outputs[0] in calib.ranges):
+            def act_params(name):
+                lo, hi = min(calib.ranges[name][0], 0.0), max(calib.ranges[name][1], 0.0)
+                scale = np.float32((hi - lo) / 255.0) if hi > lo else np.float32(1.0)
+                return scale, np.uint8(np.clip(np.rint(-lo / scale), 0, 255))
+            (xs, xz), (ys, yz) = act_params(a), act_params(n.outputs[0])
+            q, ws, wz = quantize_weight(ol.to_array(w_t), signed=True, per_channel=per_channel, axis=1)
+            base, out = ins[1], n.outputs[0]
+            tag = (n.name or out)
+            g.initializers += [ol.make_tensor(tag + "_x_scale", np.array(xs, np.float32)), ol.make_tensor(tag + "_x_zp", np.array(xz, np.uint8)),
+                               ol.make_tensor(tag + "_y_scale", np.array(ys, np.float32)), ol.make_tensor(tag + "_y_zp", np.array(yz, np.uint8)),
+                               ol.make_tensor(base + "_quantized", q), ol.make_tensor(base + "_scale", ws), ol.make_tensor(base + "_zero_point", wz)]
+            new_nodes.append(ol.make_node("QuantizeLinear", [a, tag + "_x_scale", tag + "_x_zp"], [tag + "_xq"], name=tag + "_QuantizeLinear"))
+            new_nodes.append(ol.make_node("QLinearMatMul", [tag + "_xq", tag + "_x_scale", tag + "_x_zp", base + "_quantized", base + "_scale", base + "_zero_point",
+                                                            tag + "_y_scale", tag + "_y_zp"], [tag + "_yq"], name=tag + "_QLinearMatMul"))
+            new_nodes.append(ol.make_node("DequantizeLinear", [tag + "_yq", tag + "_y_scale", tag + "_y_zp"], [out], name=tag + "_DequantizeLinear"))
+            continue
         if a in calib.ranges:
             if a not in qdq_of:
                 lo, hi = min(calib.ranges[a][0], 0.0), max(calib.ranges[a][1], 0.0)

@@ -337,3 +337,20 @@ def test_symbolic_shape_inference_front_end(tmp_path):
     src.write_bytes(model)
     assert main(["--input", str(src), "--output", str(dst)]) == 0
     assert len(ol.load_model(str(dst)).graph.value_info) >= len(shapes)
+
+
+def test_quantize_static_qoperator_format():
+    import numpy as np
+    import onnxruntime_b200 as ort
+    from onnxruntime_b200.quantization import QuantFormat, quantize_static
+    model, rng = _two_layer_mlp()
+    x = rng.standard_normal((32, 16)).astype(np.float32)
+    (ref,) = ort.InferenceSession(model, providers=["CPUExecutionProvider"]).run(None, {"x": x})
+    for per_channel in (False, True):
+        q = quantize_static(model, [{"x": x}], quant_format=QuantFormat.QOperator, per_channel=per_channel)
+        ops = [n.op_type for n in q.graph.nodes]
+        assert ops.count("QLinearMatMul") == 2 and "MatMul" not in ops
+        so = ort.SessionOptions()
+        so.graph_optimization_level = ort.GraphOptimizationLevel.ORT_DISABLE_ALL
+        (y,) = ort.InferenceSession(q.serialize(), so, providers=["CPUExecutionProvider"]).run(None, {"x": x})
+        assert np.abs(y - ref).max() < 0.06 * np.abs(ref).max()
