@@ -17,6 +17,11 @@ import numpy as np
 
 from .. import onnx_lite as ol
 
+try:
+    import torch
+except ImportError:  # pragma: no cover
+    torch = None
+
 
 def quantize_blockwise(w_kn: np.ndarray, block_size: int = 32, bits: int = 4, symmetric: bool = True
                        ) -> Tuple[np.ndarray, np.ndarray, Optional[np.ndarray]]:
@@ -54,6 +59,40 @@ def quantize_blockwise(w_kn: np.ndarray, block_size: int = 32, bits: int = 4, sy
     return packed, scales.astype(np.float32), zp
 
 
+def quantize_blockwise_hqq(w_kn: np.ndarray, block_size: int = 32, bits: int = 4, iters: int = 20, lp_norm: float = 0.7, beta: float = 10.0,
+                           kappa: float = 1.01) -> Tuple[np.ndarray, np.ndarray, np.ndarray]:
+    """Half-quadratic quantisation (the HQQ option of the reference's quantizer, ``HQQWeightOnlyQuantizer``): starting from the
+    min-max scale of every block, the zero point is re-fitted for a few iterations against an l_p (p < 1) shrinkage of the
+    reconstruction error, which moves it away from what outliers dictate.  Zero points stay FLOAT (MatMulNBits takes zero
+    points of the scales' type): returns (packed uint8, scales float32 [N, n_blocks], zero_points float32 [N, n_blocks])."""
+    assert bits in (4, 8) and block_size >= 16 and block_size & (block_size - 1) == 0
+    K, N = w_kn.shape
+    nb = (K + block_size - 1) // block_size
+    w = np.zeros((N, nb * block_size), dtype=np.float32)
+    w[:, :K] = np.asarray(w_kn, dtype=np.float32).T
+    w = w.reshape(N, nb, block_size)
+    qmax = float((1 << bits) - 1)
+    lo, hi = w.min(-1, keepdims=True), w.max(-1, keepdims=True)
+    inv_scale = qmax / np.maximum(hi - lo, 1e-8)          # quantisation multiplies by this
+    zero = -lo * inv_scale
+    best_err, best_zero = None, zero
+    for _ in range(iters):
+        q = np.clip(np.rint(w * inv_scale + zero), 0, qmax)
+        recon = (q - zero) / inv_scale
+        resid = w - recon
+        shrunk = np.sign(resid) * np.maximum(np.abs(resid) - (1.0 / beta) * np.power(np.abs(resid) + 1e-8, lp_norm - 1.0), 0.0)
+        zero = np.mean(q - (w - shrunk) * inv_scale, -1, keepdims=True)
+        beta *= kappa
+        err = float(np.abs(w - recon).mean())
+        if best_err is not None and err >= best_err:
+            break
+        best_err, best_zero = err, zero
+    zero = best_zero
+    q = np.clip(np.rint(w * inv_scale + zero), 0, qmax).astype(np.uint8)
+    packed = (q[..., 0::2] | (q[..., 1::2] << 4)).astype(np.uint8) if bits == 4 else q
+    return packed, (1.0 / inv_scale)[..., 0].astype(np.float32), zero[..., 0].astype(np.float32)
+
+
 def dequantize_blockwise(packed: np.ndarray, scales: np.ndarray, zero_points: Optional[np.ndarray], K: int, bits: int = 4,
                          block_size: int = 32) -> np.ndarray:
     """Inverse of :func:`quantize_blockwise`: float32 ``[N, K]``."""
@@ -76,7 +115,11 @@ class MatMulNBitsQuantizer:
     ``.save(path)``.  ``model`` is ModelProto bytes, a path, or an ``onnx_lite.Model``."""
 
     def __init__(self, model: Union[str, bytes, ol.Model], block_size: int = 32, is_symmetric: bool = True, bits: int = 4,
-                 nodes_to_exclude: Iterable[str] = (), nodes_to_include: Optional[Iterable[str]] = None, min_elements: int = 0):
+                 nodes_to_exclude: Iterable[str] = (), nodes_to_include: Optional[Iterable[str]] = None, min_elements: int = 0,
+                 algorithm: str = "rtn"):
+        if algorithm not in ("rtn", "hqq"):
+            raise ValueError("algorithm must be 'rtn' (round to nearest) or 'hqq' (half-quadratic, float zero points)")
+        self.algorithm = algorithm
         self.model = model if isinstance(model, ol.Model) else ol.load_model(model)
         self.block_size, self.symmetric, self.bits = block_size, is_symmetric, bits
         self.exclude = set(nodes_to_exclude)
@@ -105,10 +148,13 @@ class MatMulNBitsQuantizer:
             is_torch = not isinstance(arr, np.ndarray)
             w32 = arr.float().numpy() if is_torch else arr.astype(np.float32)
             K, N = w32.shape
-            packed, scales, zp = quantize_blockwise(w32, self.block_size, self.bits, self.symmetric)
+            if self.algorithm == "hqq":
+                packed, scales, zp = quantize_blockwise_hqq(w32, self.block_size, self.bits)
+            else:
+                packed, scales, zp = quantize_blockwise(w32, self.block_size, self.bits, self.symmetric)
             base = n.inputs[1]
             if is_torch:
-                import torch
+                import torch  # noqa: F811
                 scales_t = ol.make_tensor(base + "_scales", torch.from_numpy(scales).to(arr.dtype))
             else:
                 scales_t = ol.make_tensor(base + "_scales", scales.astype(arr.dtype))
@@ -116,6 +162,8 @@ class MatMulNBitsQuantizer:
             g.initializers.append(scales_t)
             ins = [n.inputs[0], base + "_Q" + str(self.bits), base + "_scales"]
             if zp is not None:
+                if zp.dtype != np.uint8:   # float zero points take the type of the scales
+                    zp = torch.from_numpy(zp).to(arr.dtype) if is_torch else zp.astype(arr.dtype)
                 g.initializers.append(ol.make_tensor(base + "_zero_points", zp))
                 ins.append(base + "_zero_points")
             new_nodes.append(ol.make_node("MatMulNBits", ins, list(n.outputs), name=(n.name + "_Q" + str(self.bits)) if n.name else "",

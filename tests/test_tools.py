@@ -354,3 +354,25 @@ def test_quantize_static_qoperator_format():
         so.graph_optimization_level = ort.GraphOptimizationLevel.ORT_DISABLE_ALL
         (y,) = ort.InferenceSession(q.serialize(), so, providers=["CPUExecutionProvider"]).run(None, {"x": x})
         assert np.abs(y - ref).max() < 0.06 * np.abs(ref).max()
+
+
+def test_hqq_weight_quantization_beats_round_to_nearest_on_outliers():
+    import numpy as np
+    import onnxruntime_b200 as ort
+    from onnxruntime_b200.quantization import MatMulNBitsQuantizer, dequantize_blockwise, quantize_blockwise, quantize_blockwise_hqq
+    rng = np.random.default_rng(0)
+    w = rng.standard_normal((128, 24)).astype(np.float32)
+    w[rng.integers(0, 128, 40), rng.integers(0, 24, 40)] *= 6.0        # outliers stretch the min-max range
+    p0, s0, z0 = quantize_blockwise(w, 32, 4, symmetric=False)
+    p1, s1, z1 = quantize_blockwise_hqq(w, 32, 4)
+    e_rtn = np.abs(dequantize_blockwise(p0, s0, z0, 128, 4, 32).T - w).mean()
+    e_hqq = np.abs(dequantize_blockwise(p1, s1, z1, 128, 4, 32).T - w).mean()
+    assert z1.dtype == np.float32 and e_hqq <= e_rtn * 1.001
+    model, mrng = _two_layer_mlp()
+    x = mrng.standard_normal((6, 16)).astype(np.float32)
+    (ref,) = ort.InferenceSession(model, providers=["CPUExecutionProvider"]).run(None, {"x": x})
+    q = MatMulNBitsQuantizer(model, block_size=16, algorithm="hqq").process()
+    node = [n for n in q.graph.nodes if n.op_type == "MatMulNBits"][0]
+    assert len(node.inputs) == 4                                        # float zero points ride along
+    (y,) = ort.InferenceSession(q.serialize(), providers=["CPUExecutionProvider"]).run(None, {"x": x})
+    assert np.abs(y - ref).max() < 0.15 * np.abs(ref).max()
