@@ -313,8 +313,9 @@ void GraphExecutor::Build() {
     }
 
     // kernel lookup: hand-written sm_100a kernel first for GPU nodes, then the ATen-backed one
+    // ("ortb200.generic_kernels_only" = "1" keeps a session on the differentiable tensor-library set: training)
     const KernelDef* def = nullptr;
-    if (st.on_gpu) def = KernelRegistry::Cuda().Find(*n, *graph_);
+    if (st.on_gpu && session_->config().Get("ortb200.generic_kernels_only", "0") != "1") def = KernelRegistry::Cuda().Find(*n, *graph_);
     if (!def) def = KernelRegistry::Generic().Find(*n, *graph_);
     if (!def)
       ORTB_THROW(NOT_IMPLEMENTED, "Could not find an implementation for ", n->op_type, "(", n->since_version,

@@ -426,7 +426,18 @@ std::shared_ptr<Graph> Graph::FromProto(const pb::GraphProto& g, const std::map<
       } else if (a.type == pb::ATTR_GRAPHS) {
         ORTB_NOT_IMPLEMENTED("attribute '", a.name, "' of node '", n.name, "' holds a list of graphs");
       } else {
-        node->attrs[a.name] = a;
+        // Tensor attributes are read at run time (ConstantOfShape, Constant ...), long after the parsed model bytes
+        // are gone: give each its own copy of the bytes its raw_data view points at.
+        pb::AttributeProto& held = node->attrs[a.name];
+        held = a;
+        auto own = [](pb::TensorProto& t) {
+          if (t.has_raw) t.set_raw(std::string(t.raw, t.raw_size));
+        };
+        if (held.t) {
+          held.t = std::make_shared<pb::TensorProto>(*held.t);
+          own(*held.t);
+        }
+        for (auto& t : held.tensors) own(t);
       }
     }
     node->since_version = static_cast<int>(out->Opset(node->domain));

@@ -181,6 +181,7 @@ void RegisterContribKernels3(KernelRegistry& r);
 void RegisterContribKernels4(KernelRegistry& r);
 void RegisterContribKernels5(KernelRegistry& r);
 void RegisterContribKernels6(KernelRegistry& r);
+void RegisterTrainingKernels(KernelRegistry& r);
 // convolution / pooling with the attributes of `node` (kernels_nn.cc)
 at::Tensor ConvWithNodeAttrs(const Node& node, const at::Tensor& x, const at::Tensor& w, const c10::optional<at::Tensor>& bias);
 at::Tensor ConvTransposeWithNodeAttrs(const Node& node, const at::Tensor& x, const at::Tensor& w,

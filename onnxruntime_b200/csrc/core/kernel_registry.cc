@@ -89,6 +89,7 @@ void EnsureKernelsRegistered() {
     RegisterContribKernels4(g);
     RegisterContribKernels5(g);
     RegisterContribKernels6(g);
+    RegisterTrainingKernels(g);
     RegisterOnnxExtraKernels(g);
     RegisterOnnxExtraKernels2(g);
     RegisterOnnxExtraKernels3(g);

@@ -27,7 +27,7 @@ def run_node(op_type: str, inputs: Dict[str, Optional[np.ndarray]], n_outputs: i
             continue
         if n in initializers:
             inits.append(ol.make_tensor(n, v))
-        elif isinstance(v, dict):     # a map-typed input: no tensor type to declare
+        elif isinstance(v, (dict, list)):     # a map- or sequence-typed input: no tensor type to declare
             graph_inputs.append(ol.make_tensor_value_info(n, 0, None))
         else:
             graph_inputs.append(ol.make_tensor_value_info(n, ol.np_dtype_to_onnx(v.dtype), list(v.shape)))
