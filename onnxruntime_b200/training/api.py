@@ -182,6 +182,43 @@ class Module:
                 p.data.copy_(buffer[at:at + n].reshape(p.data.shape).to(p.data.dtype))
                 at += n
 
+    def all_reduce_gradients(self, group=None, average: bool = True, bucket_bytes: int = 256 << 20) -> None:
+        """Data parallelism: sums (or averages) the gradient buffers over the ranks of ``group`` (``torch.distributed``;
+        NCCL over NVLink for GPU modules, gloo on the CPU).  Gradients of one dtype travel as flat buckets of up to
+        ``bucket_bytes``, so the cost is a few collective launches rather than one per parameter (the role of the
+        reference's ``NcclAllReduce`` nodes that its data-parallel graph transform adds)."""
+        import torch.distributed as dist
+        if not dist.is_available() or not dist.is_initialized() or dist.get_world_size(group) == 1:
+            return
+        world = dist.get_world_size(group)
+        pending: List[torch.Tensor] = []
+        size = 0
+
+        def flush() -> None:
+            nonlocal pending, size
+            if not pending:
+                return
+            flat = torch.cat([g.reshape(-1) for g in pending])
+            dist.all_reduce(flat, group=group)
+            if average:
+                flat.div_(world)
+            at = 0
+            for g in pending:
+                g.copy_(flat[at:at + g.numel()].reshape(g.shape))
+                at += g.numel()
+            pending, size = [], 0
+        by_dtype: Dict[torch.dtype, List[torch.Tensor]] = {}
+        for p in self.parameters():
+            if p.requires_grad:
+                by_dtype.setdefault(p.grad.dtype, []).append(p.grad)
+        for grads in by_dtype.values():
+            for g in grads:
+                if size and size + g.numel() * g.element_size() > bucket_bytes:
+                    flush()
+                pending.append(g)
+                size += g.numel() * g.element_size()
+            flush()
+
     def _tensor(self, v) -> torch.Tensor:
         t = v if isinstance(v, torch.Tensor) else torch.as_tensor(np.asarray(v))
         return t.to(self._device)

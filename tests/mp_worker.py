@@ -384,6 +384,52 @@ def case_allgather_gemm(info, device, out):
     torch.save(res, os.path.join(out, f"rank{r}.pt"))
 
 
+def case_data_parallel_training(info, device, out):
+    """Each rank trains on its shard of the batch: (a) the training API with bucketed gradient all-reduce, (b) ORTModule
+    under torch's DistributedDataParallel.  Both must follow the single-process full-batch run."""
+    from onnxruntime_b200 import training
+    from onnxruntime_b200.training import api
+    r, w = info.rank, info.world_size
+    rng = np.random.RandomState(0)
+    f = lambda *s: (rng.randn(*s) * 0.4).astype(np.float32)  # noqa: E731
+    init = {"w1": f(8, 16), "b1": f(16), "w2": f(16, 5)}
+    g = ol.make_graph([ol.make_node("MatMul", ["x", "w1"], ["h"]), ol.make_node("Add", ["h", "b1"], ["hb"]), ol.make_node("Tanh", ["hb"], ["t"]),
+                       ol.make_node("MatMul", ["t", "w2"], ["logits"])], "mlp", [ol.make_tensor_value_info("x", T.FLOAT, ["n", 8])],
+                      [ol.make_tensor_value_info("logits", T.FLOAT, ["n", 5])], [ol.make_tensor(k, v) for k, v in init.items()])
+    model = ol.make_model(g, opset=17)
+    per = 8
+    x_all, y_all = f(w * per, 8), rng.randint(0, 5, w * per).astype(np.int64)
+    xs, ys = x_all[r * per:(r + 1) * per], y_all[r * per:(r + 1) * per]
+    art = training.generate_artifacts(model, loss=training.LossType.CrossEntropyLoss, optimizer=training.OptimType.AdamW, target_name="labels",
+                                      optimizer_options={"weight_decay": 0.0})
+    state = api.CheckpointState.load_checkpoint(art["checkpoint"])
+    module = api.Module(art["training_model.onnx"], state)
+    optim = api.Optimizer(art["optimizer_model.onnx"], module)
+    optim.set_learning_rate(0.05)
+    for _ in range(5):
+        module(xs, ys)
+        module.all_reduce_gradients(bucket_bytes=300)      # small buckets: more than one collective per step
+        optim.step()
+        module.lazy_reset_grad()
+    # single-process full batch in torch
+    ref = {k: torch.tensor(v, requires_grad=True) for k, v in init.items()}
+    topt = torch.optim.AdamW(list(ref.values()), lr=0.05, weight_decay=0.0)
+    for _ in range(5):
+        topt.zero_grad()
+        logits = torch.tanh(torch.tensor(x_all) @ ref["w1"] + ref["b1"]) @ ref["w2"]
+        torch.nn.functional.cross_entropy(logits, torch.tensor(y_all)).backward()
+        topt.step()
+    # (b) ORTModule under DDP: one backward pass, gradients averaged by DDP's own buckets
+    ddp = torch.nn.parallel.DistributedDataParallel(training.ORTModule(model))
+    torch.nn.functional.cross_entropy(ddp(torch.tensor(xs)), torch.tensor(ys)).backward()
+    full = {k: torch.tensor(v, requires_grad=True) for k, v in init.items()}
+    logits = torch.tanh(torch.tensor(x_all) @ full["w1"] + full["b1"]) @ full["w2"]
+    torch.nn.functional.cross_entropy(logits, torch.tensor(y_all)).backward()
+    torch.save({"api": {k: p.data.clone() for k, p in state.parameters.items()}, "ref": {k: v.detach() for k, v in ref.items()},
+                "ddp_grad": {n: p.grad.clone() for n, p in ddp.module.named_onnx_parameters()},
+                "full_grad": {k: v.grad for k, v in full.items()}}, os.path.join(out, f"rank{r}.pt"))
+
+
 def main():
     case, device, out = sys.argv[1], sys.argv[2], sys.argv[3]
     info = init_distributed("gloo" if device == "cpu" else "nccl", timeout_s=120)

@@ -102,3 +102,14 @@ def test_mixtral_shaped_decoder_with_expert_parallelism(tmp_path):
     a, b, ref = out[0]["logits"], out[1]["logits"], out[0]["ref"]
     assert (a - b).abs().max() == 0
     assert (a - ref).abs().max() / ref.abs().max() < 1e-4
+
+
+def test_data_parallel_training_follows_the_full_batch_run(tmp_path):
+    """Training API with bucketed gradient all-reduce and ORTModule under DistributedDataParallel, 2 gloo ranks."""
+    out = launch("data_parallel_training", "cpu", 2, tmp_path)
+    for r in range(2):
+        for k, ref in out[r]["ref"].items():
+            np.testing.assert_allclose(out[r]["api"][k].numpy(), ref.numpy(), rtol=2e-3, atol=2e-4, err_msg=k)
+            np.testing.assert_allclose(out[r]["ddp_grad"][k].numpy(), out[r]["full_grad"][k].numpy(), rtol=1e-4, atol=1e-6, err_msg=k)
+    for k in out[0]["api"]:
+        np.testing.assert_array_equal(out[0]["api"][k].numpy(), out[1]["api"][k].numpy())
