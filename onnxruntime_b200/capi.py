@@ -1097,6 +1097,10 @@ class InferenceSession:
 
     def run_with_iobinding(self, iobinding: "IOBinding", run_options: Optional[RunOptions] = None) -> None:
         ro = run_options._c if run_options is not None else C.RunOptions()
+        if iobinding._has_strings():
+            iobinding._run_by_name(ro)
+            return
+        iobinding._string_results = None
         self._sess.run_with_binding(ro, iobinding._c)
 
     # --- extras of this runtime
@@ -1215,37 +1219,75 @@ class IOBinding:
         self._session = session
         self._c = C.IOBinding(session._sess)
         self._keep: List[Any] = []
+        # Tensors of strings have no device buffer to bind: a binding that holds one runs through the by-name path,
+        # with every bound input kept here by name and bound output buffers filled by copy.
+        self._inputs: Dict[str, Any] = {}
+        self._out_buffers: Dict[str, Optional[torch.Tensor]] = {}
+        self._string_results: Optional[List[Any]] = None
+        self._string_outputs: Optional[bool] = None
+        self._string_inputs = 0
+
+    def _has_strings(self) -> bool:   # on the path of every bound run: two attribute reads
+        if self._string_outputs is None:
+            self._string_outputs = any(o.type == "tensor(string)" for o in self._session.get_outputs())
+        return self._string_outputs or self._string_inputs > 0
+
+    def _run_by_name(self, run_options) -> None:
+        wanted = list(self._out_buffers) or [o.name for o in self._session.get_outputs()]
+        outs = self._session._sess.run(run_options, list(self._inputs), list(self._inputs.values()), wanted)
+        for name, value in zip(wanted, outs):
+            buf = self._out_buffers.get(name)
+            if buf is not None and isinstance(value, torch.Tensor):
+                buf.copy_(value)
+        self._string_results = [_StringTensor(o[1], o[2]) if isinstance(o, tuple) and len(o) == 3 and o[0] == "__strings__" else o
+                                for o in outs]
 
     def bind_cpu_input(self, name: str, arr_on_cpu: np.ndarray) -> None:
-        self._c.bind_input(name, _to_torch(arr_on_cpu))
+        t = _to_torch(arr_on_cpu)
+        self._inputs[name] = t
+        if isinstance(t, _StringTensor):
+            self._string_inputs += 1
+        else:
+            self._c.bind_input(name, t)
 
     def bind_input(self, name: str, device_type: str, device_id: int, element_type, shape: Sequence[int],
                    buffer_ptr: int) -> None:
         t = _tensor_from_pointer(buffer_ptr, element_type, shape, device_type, device_id)
         self._keep.append(t)
+        self._inputs[name] = t
         self._c.bind_input(name, t)
 
     def bind_ortvalue_input(self, name: str, ortvalue: OrtValue) -> None:
-        self._c.bind_input(name, _to_torch(ortvalue))
+        t = _to_torch(ortvalue)
+        self._inputs[name] = t
+        if isinstance(t, _StringTensor):
+            self._string_inputs += 1
+        else:
+            self._c.bind_input(name, t)
 
     def bind_torch_input(self, name: str, tensor: torch.Tensor) -> None:
+        self._inputs[name] = tensor
         self._c.bind_input(name, tensor)
 
     def bind_output(self, name: str, device_type: str = "cpu", device_id: int = 0, element_type=None,
                     shape: Optional[Sequence[int]] = None, buffer_ptr: Optional[int] = None) -> None:
         if buffer_ptr is None:
+            self._out_buffers[name] = None
             self._c.bind_output_to_device(name, device_type.lower(), device_id)
             return
         if element_type is None or shape is None:
             raise InvalidArgument("`element_type` and `shape` are to be provided if pre-allocated memory is provided")
         t = _tensor_from_pointer(buffer_ptr, element_type, shape, device_type, device_id)
         self._keep.append(t)
+        self._out_buffers[name] = t
         self._c.bind_output(name, t)
 
     def bind_ortvalue_output(self, name: str, ortvalue: OrtValue) -> None:
-        self._c.bind_output(name, _to_torch(ortvalue))
+        self._out_buffers[name] = _to_torch(ortvalue)
+        self._c.bind_output(name, self._out_buffers[name])
 
     def bind_torch_output(self, name: str, tensor: torch.Tensor) -> None:
+        self._out_buffers[name] = tensor
         self._c.bind_output(name, tensor)
 
     def synchronize_inputs(self) -> None:
@@ -1255,15 +1297,23 @@ class IOBinding:
         self._c.synchronize_outputs()
 
     def get_outputs(self) -> List[OrtValue]:
+        if self._string_results is not None:
+            return [OrtValue(t) for t in self._string_results]
         return [OrtValue(t) for t in self._c.results()]
 
     def copy_outputs_to_cpu(self) -> List[np.ndarray]:
+        if self._string_results is not None:
+            return [t.numpy() if isinstance(t, _StringTensor) else _to_numpy(t) for t in self._string_results]
         return [_to_numpy(t) for t in self._c.results()]
 
     def clear_binding_inputs(self) -> None:
+        self._inputs.clear()
+        self._string_inputs = 0
         self._c.clear_inputs()
 
     def clear_binding_outputs(self) -> None:
+        self._out_buffers.clear()
+        self._string_results = None
         self._c.clear_outputs()
         self._keep.clear()
 

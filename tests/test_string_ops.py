@@ -141,3 +141,25 @@ def test_string_tensors_through_ort_values():
     assert v.data_type() == "tensor(string)" and v.shape() == [2] and v.numpy().tolist() == ["ab", "cd"]
     (out,) = sess.run_with_ort_values(None, {"x": v})
     assert out.data_type() == "tensor(string)" and out.numpy().tolist() == ["AB", "CD"]
+
+
+def test_strings_through_io_binding():
+    """A binding that holds a tensor of strings (input or output) runs by name; bound numeric output buffers are filled."""
+    import torch
+    from onnxruntime_b200 import onnx_lite as ol
+    T = ol.TensorProto
+    g = ol.make_graph([ol.make_node("StringConcat", ["a", "b"], ["joined"], ), ol.make_node("LabelEncoder", ["a"], ["ids"], domain="ai.onnx.ml",
+                                                                                          keys_strings=["x", "y"], values_int64s=[7, 9], default_int64=-1)],
+                      "g", [ol.make_tensor_value_info("a", T.STRING, [3]), ol.make_tensor_value_info("b", T.STRING, [3])],
+                      [ol.make_tensor_value_info("joined", T.STRING, [3]), ol.make_tensor_value_info("ids", T.INT64, [3])])
+    sess = ort.InferenceSession(ol.make_model(g, opset=20, extra_opsets={"ai.onnx.ml": 4}).serialize(), providers=["CPUExecutionProvider"])
+    binding = sess.io_binding()
+    binding.bind_cpu_input("a", np.array(["x", "q", "y"], dtype=object))
+    binding.bind_ortvalue_input("b", ort.OrtValue.ortvalue_from_numpy(np.array(["-1", "-2", "-3"], dtype=object)))
+    ids = torch.zeros(3, dtype=torch.int64)
+    binding.bind_output("joined")
+    binding.bind_torch_output("ids", ids)
+    sess.run_with_iobinding(binding)
+    joined, ids_out = binding.copy_outputs_to_cpu()
+    assert joined.tolist() == ["x-1", "q-2", "y-3"] and ids.tolist() == [7, -1, 9] and ids_out.tolist() == [7, -1, 9]
+    assert binding.get_outputs()[0].numpy().tolist() == ["x-1", "q-2", "y-3"]
