@@ -368,16 +368,93 @@ def _sce(b, n, dy, needs):
     b.add_grad(n.inputs[0], b.one("SoftmaxCrossEntropyLossGrad", ins, MS, **_copy_attrs(n, ("reduction", "ignore_index"))))
 
 
+# ---- fallback: differentiate the node itself -------------------------------------------------------------------
+_NODE_SESSIONS: Dict[bytes, object] = {}
+
+
+def _node_grad(*values, node: bytes = b"", n_inputs: int = 0, wrt=(), **_unused):
+    """Kernel of ``com.ortb200.NodeGrad``: re-runs one forward node (held as a serialized single-node model in the
+    ``node`` attribute) on the differentiable tensor-library kernels with autograd recording, and returns the gradients
+    of its inputs ``wrt`` for the output gradients that follow the forward inputs in ``values``."""
+    import torch
+
+    from .. import capi
+    key = bytes(node)
+    sess = _NODE_SESSIONS.get(key)
+    if sess is None:
+        so = capi.SessionOptions()
+        so.graph_optimization_level = capi.GraphOptimizationLevel.ORT_DISABLE_ALL
+        so.add_session_config_entry("ortb200.generic_kernels_only", "1")
+        on_gpu = any(isinstance(v, torch.Tensor) and v.is_cuda for v in values)
+        sess = capi.InferenceSession(key, so, providers=(["CUDAExecutionProvider"] if on_gpu else []) + ["CPUExecutionProvider"])
+        _NODE_SESSIONS[key] = sess
+    n_inputs = int(n_inputs)
+    fwd, dys = list(values[:n_inputs]), list(values[n_inputs:])
+    names = [i.name for i in sess.get_inputs()]
+    out_names = [o.name for o in sess.get_outputs()]
+    wrt = [int(i) for i in wrt]
+    with torch.enable_grad():
+        leaves = {}
+        feeds = []
+        present = [v for v in fwd if v is not None]
+        for slot, v in enumerate(fwd):
+            if v is None:
+                continue
+            if slot in wrt and v.is_floating_point():
+                v = v.detach().requires_grad_(True)
+                leaves[slot] = v
+            feeds.append(v)
+        assert len(feeds) == len(names) == len(present)
+        outs = sess._sess.run(capi.C.RunOptions(), names, feeds, out_names)
+        pairs = [(o, d) for o, d in zip(outs, dys) if d is not None and isinstance(o, torch.Tensor) and o.requires_grad]
+        if not pairs:
+            raise RuntimeError("NodeGrad: the node's outputs do not depend differentiably on the requested inputs")
+        order = [s for s in wrt if s in leaves]
+        grads = torch.autograd.grad([o for o, _ in pairs], [leaves[s] for s in order], [d.to(o.dtype) for o, d in pairs], allow_unused=True)
+    by_slot = dict(zip(order, grads))
+    result = []
+    for s in wrt:
+        g = by_slot.get(s)
+        result.append(g if g is not None else torch.zeros_like(fwd[s]))
+    return result[0] if len(result) == 1 else tuple(result)
+
+
+def _register_node_grad() -> None:
+    from .. import capi
+    try:
+        capi.C.register_python_op(OWN, "NodeGrad", _node_grad)
+    except Exception:  # pragma: no cover - a build without Python operators
+        pass
+
+
+_register_node_grad()
+
+
+def _fallback_rule(b: _Builder, n: ol.Node, dy, needs, model: ol.Model) -> None:
+    ins = [i for i in n.inputs]
+    single = ol.make_graph([copy.deepcopy(n)], "node", [ol.make_tensor_value_info(i, 0, None) for i in ins if i],
+                           [ol.make_tensor_value_info(o, 0, None) for o in n.outputs if o])
+    blob = ol.Model(single, dict(model.opset_imports), model.ir_version).serialize()
+    wrt = [i for i, need in enumerate(needs) if need]
+    dys = [d if d is not None else "" for d, o in zip(dy, n.outputs) if o]
+    outs = b.emit("NodeGrad", ins + dys, len(wrt), OWN, node=blob, n_inputs=len(ins), wrt=wrt)
+    for slot, g in zip(wrt, outs):
+        b.add_grad(n.inputs[slot], g)
+
+
 def supported_ops() -> List[str]:
     """Operators a gradient can be taken through."""
     return sorted(_RULES)
 
 
 def build_gradient_graph(model: ol.Model, requires_grad: Sequence[str], loss: str,
-                         input_grads: Sequence[str] = ()) -> ol.Model:
+                         input_grads: Sequence[str] = (), recompute_fallback: bool = True) -> ol.Model:
     """Returns a copy of ``model`` whose graph also computes, for every name in ``requires_grad`` (initializers or graph
     inputs) and ``input_grads``, the output ``<name>_grad`` = d ``loss`` / d name.  The loss may have any shape; its own
-    gradient is a tensor of ones.  Raises ``NotImplementedError`` naming the first operator on the path that has no rule."""
+    gradient is a tensor of ones.  An operator without a rule of its own gets a ``com.ortb200.NodeGrad`` node, which re-runs
+    that one node with autograd recording and differentiates it (so every operator whose tensor-library kernel is
+    differentiable is covered, at the price of computing it twice); with ``recompute_fallback=False`` such an operator
+    raises ``NotImplementedError`` naming it instead."""
     model = copy.deepcopy(model)
     g = model.graph
     opset = int(model.opset_imports.get("", 17))
@@ -407,7 +484,10 @@ def build_gradient_graph(model: ol.Model, requires_grad: Sequence[str], loss: st
             continue
         rule = _RULES.get(n.op_type)
         if rule is None:
-            raise NotImplementedError(f"no gradient rule for operator '{n.op_type}' (node '{n.name}')")
+            if not recompute_fallback:
+                raise NotImplementedError(f"no gradient rule for operator '{n.op_type}' (node '{n.name}')")
+            _fallback_rule(b, n, dy, needs, model)
+            continue
         if dy[0] is None and n.op_type not in ("Split",):
             continue
         rule(b, n, dy, needs)

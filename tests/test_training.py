@@ -105,7 +105,35 @@ def test_unsupported_operator_is_named():
     g = ol.make_graph([ol.make_node("Erf", ["w"], ["y"]), ol.make_node("ReduceSum", ["y"], ["loss"], keepdims=0)], "g", [],
                       [ol.make_tensor_value_info("loss", T.FLOAT, [])], [ol.make_tensor("w", np.ones((2, 2), np.float32))])
     with pytest.raises(NotImplementedError, match="Erf"):
-        training.build_gradient_graph(ol.make_model(g, opset=17), ["w"], "loss")
+        training.build_gradient_graph(ol.make_model(g, opset=17), ["w"], "loss", recompute_fallback=False)
+
+
+def test_operators_without_a_rule_are_differentiated_by_recomputation():
+    """MaxPool, BatchNormalization (inference form), AveragePool and Erf have no rule: NodeGrad re-runs and differentiates them."""
+    rng = np.random.default_rng(4)
+    w = (rng.standard_normal((4, 3, 3, 3)) * 0.3).astype(np.float32)
+    bn = [(rng.random(4) + 0.5).astype(np.float32), _f(rng, 4) * 0.1, _f(rng, 4) * 0.1, (rng.random(4) + 0.5).astype(np.float32)]
+    nodes = [ol.make_node("Conv", ["x", "w"], ["c"], pads=[1, 1, 1, 1]),
+             ol.make_node("BatchNormalization", ["c", "bn_s", "bn_b", "bn_m", "bn_v"], ["n"], epsilon=1e-5),
+             ol.make_node("MaxPool", ["n"], ["p"], kernel_shape=[2, 2], strides=[2, 2]),
+             ol.make_node("AveragePool", ["p"], ["a"], kernel_shape=[2, 2], strides=[1, 1]),
+             ol.make_node("Erf", ["a"], ["e"]), ol.make_node("ReduceSum", ["e"], ["loss"], keepdims=0)]
+    inits = [ol.make_tensor("w", w)] + [ol.make_tensor(k, v) for k, v in zip(("bn_s", "bn_b", "bn_m", "bn_v"), bn)]
+    g = ol.make_graph(nodes, "cnn", [ol.make_tensor_value_info("x", T.FLOAT, [2, 3, 8, 8])], [ol.make_tensor_value_info("loss", T.FLOAT, [])], inits)
+    gm = training.build_gradient_graph(ol.make_model(g, opset=17), ["w", "bn_s", "bn_b"], "loss", input_grads=["x"])
+    assert sum(n.op_type == "NodeGrad" for n in gm.graph.nodes) == 4
+    x = _f(rng, 2, 3, 8, 8)
+    sess = ort.InferenceSession(gm.serialize(), providers=["CPUExecutionProvider"])
+    got = dict(zip([o.name for o in sess.get_outputs()], sess.run(None, {"x": x})))
+    xt, wt = torch.tensor(x, requires_grad=True), torch.tensor(w, requires_grad=True)
+    st, bt = torch.tensor(bn[0], requires_grad=True), torch.tensor(bn[1], requires_grad=True)
+    c = torch.nn.functional.conv2d(xt, wt, padding=1)
+    n = torch.nn.functional.batch_norm(c, torch.tensor(bn[2]), torch.tensor(bn[3]), st, bt, training=False, eps=1e-5)
+    loss = torch.erf(torch.nn.functional.avg_pool2d(torch.nn.functional.max_pool2d(n, 2, 2), 2, 1)).sum()
+    loss.backward()
+    assert abs(float(got["loss"]) - loss.item()) < 1e-4
+    for name, ref in (("w", wt), ("bn_s", st), ("bn_b", bt), ("x", xt)):
+        np.testing.assert_allclose(got[name + "_grad"], ref.grad.numpy(), rtol=1e-3, atol=1e-5, err_msg=name)
 
 
 def test_ortmodule_trains_with_a_torch_optimizer():
