@@ -56,7 +56,7 @@ def _append_loss(model: ol.Model, loss: LossType, output: str, target: str, redu
             g.nodes.append(ol.make_node("Sub", [output, target], ["loss_diff"]))
             g.nodes.append(ol.make_node("Mul", ["loss_diff", "loss_diff"], ["loss_elem"]))
         elif loss == LossType.L1Loss:
-            # |d| = d * tanh(k d) for large k has no kink issue in the rule table; use sqrt(d^2 + eps) instead
+            # |d| as sqrt(d^2 + eps): differentiable at 0 with the rules of the builder
             g.initializers.append(ol.make_tensor("loss_eps", np.asarray(1e-12, dtype=np.float32)))
             g.nodes.append(ol.make_node("Sub", [output, target], ["loss_diff"]))
             g.nodes.append(ol.make_node("Mul", ["loss_diff", "loss_diff"], ["loss_sq"]))
@@ -109,7 +109,7 @@ def generate_artifacts(model: Union[str, bytes, ol.Model], requires_grad: Option
     floats = (T.FLOAT, T.FLOAT16, T.BFLOAT16, T.DOUBLE)
     frozen = set(frozen_params or [])
     if requires_grad is None:
-        requires_grad = [t.name for t in g.initializers if t.data_type in floats and t.name not in frozen]
+        requires_grad = [t.name for t in g.initializers if t.data_type in floats and t.name not in frozen and int(np.prod(t.dims)) > 1]
     requires_grad = [n for n in requires_grad if n not in frozen]
     known = {t.name for t in g.initializers}
     for n in list(requires_grad) + list(frozen):

@@ -38,13 +38,21 @@ def lift_initializers(model: ol.Model, names: Sequence[str]) -> ol.Model:
 
 class ORTModule(torch.nn.Module):
     def __init__(self, model: Union[str, bytes, ol.Model], trainable: Optional[Sequence[str]] = None,
-                 providers: Sequence[str] = ("CPUExecutionProvider",), output_names: Optional[Sequence[str]] = None):
+                 providers: Sequence[str] = ("CPUExecutionProvider",), output_names: Optional[Sequence[str]] = None,
+                 recompute: bool = False):
+        """``recompute=True`` keeps no activations of the graph between the forward and the backward pass: the forward
+        pass runs without recording and is run again, recording, when the gradients are asked for (the trade the
+        reference's memory optimizer makes per subgraph, made here for the whole graph)."""
         super().__init__()
+        self._recompute = bool(recompute)
         import copy
         from .. import capi
         m = copy.deepcopy(model) if isinstance(model, ol.Model) else ol.load_model(model)
         floats = (ol.TensorProto.FLOAT, ol.TensorProto.FLOAT16, ol.TensorProto.BFLOAT16, ol.TensorProto.DOUBLE)
-        names = [t.name for t in m.graph.initializers if t.data_type in floats and (trainable is None or t.name in trainable)]
+        # by default every float initializer with more than one element: one-element floats are the constants of the
+        # graph (an exponent, an epsilon, a scale), not weights
+        names = [t.name for t in m.graph.initializers if t.data_type in floats and
+                 ((trainable is None and int(np.prod(t.dims)) > 1) or (trainable is not None and t.name in trainable))]
         self._param_names: List[str] = names
         self._attr_of: Dict[str, str] = {}
         for t in m.graph.initializers:
@@ -80,5 +88,13 @@ class ORTModule(torch.nn.Module):
         names = list(feeds) + self._param_names
         values = [v if isinstance(v, torch.Tensor) else torch.as_tensor(np.asarray(v)) for v in feeds.values()]
         values += [getattr(self, self._attr_of[n]) for n in self._param_names]
-        outs = self._session._sess.run(self._C.RunOptions(), names, values, self._outputs)
-        return outs[0] if len(outs) == 1 else tuple(outs)
+        def run(*tensors):
+            outs = self._session._sess.run(self._C.RunOptions(), names, list(tensors), self._outputs)
+            return outs[0] if len(outs) == 1 else tuple(outs)
+        if self._recompute and torch.is_grad_enabled():
+            from torch.utils.checkpoint import checkpoint, set_checkpoint_early_stop
+            # no early stop: it works by raising a Python exception from a saved-tensor hook, which here would fire
+            # in the middle of a native kernel
+            with set_checkpoint_early_stop(False):
+                return checkpoint(run, *values, use_reentrant=False)
+        return run(*values)
