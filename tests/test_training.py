@@ -426,3 +426,67 @@ def test_bert_encoder_trains_and_the_two_gradient_paths_agree():
         opt.step()
         losses.append(loss.item())
     assert losses[-1] < 0.3 * losses[0]
+
+
+def _llama_torch(cfg, w, ids):
+    """Plain PyTorch restatement of the exported decoder (prompt pass, no past): RMSNorm, packed QKV, half-split rotary
+    embedding, causal grouped-query attention, SwiGLU, tied to the exporter's weight names."""
+    N, Nk, H = cfg.num_heads, cfg.num_kv_heads, cfg.head_dim
+    B, S = ids.shape
+
+    def rms(x, g):
+        return x * torch.rsqrt((x * x).mean(-1, keepdim=True) + cfg.rms_eps) * g
+
+    def rope(x):                                  # [B, heads, S, H]
+        cos, sin = w["cos_cache"][:S], w["sin_cache"][:S]
+        a, b = x[..., : H // 2], x[..., H // 2:]
+        return torch.cat([a * cos - b * sin, b * cos + a * sin], -1)
+    h = w["model.embed_tokens.weight"][ids]
+    for i in range(cfg.num_layers):
+        p = f"model.layers.{i}."
+        qkv = rms(h, w[p + "input_layernorm.weight"]) @ w[p + "attn.qkv_proj.weight"]
+        q, k, v = qkv.split([N * H, Nk * H, Nk * H], -1)
+        q = rope(q.reshape(B, S, N, H).transpose(1, 2))
+        k = rope(k.reshape(B, S, Nk, H).transpose(1, 2)).repeat_interleave(N // Nk, 1)
+        v = v.reshape(B, S, Nk, H).transpose(1, 2).repeat_interleave(N // Nk, 1)
+        att = (q @ k.transpose(-1, -2)) / H ** 0.5 + torch.full((S, S), float("-inf")).triu(1)
+        o = (torch.softmax(att, -1) @ v).transpose(1, 2).reshape(B, S, N * H)
+        h = h + o @ w[p + "attn.o_proj.weight"]
+        x = rms(h, w[p + "post_attention_layernorm.weight"])
+        h = h + (torch.nn.functional.silu(x @ w[p + "mlp.gate_proj.weight"]) * (x @ w[p + "mlp.up_proj.weight"])) @ w[p + "mlp.down_proj.weight"]
+    return rms(h, w["model.norm.weight"]) @ w["lm_head.weight"]
+
+
+def test_llama_decoder_fine_tunes_through_the_fused_operators():
+    """The Llama export (GroupQueryAttention with rotary embedding, SkipSimplifiedLayerNormalization, SwiGLU) as an
+    ORTModule: gradients equal those of a plain PyTorch restatement; next-token loss falls under AdamW."""
+    from onnxruntime_b200.models import llama
+    cfg = llama.LlamaConfig.tiny(vocab_size=64, hidden_size=32, num_heads=4, num_kv_heads=2, head_dim=8, ffn_size=64,
+                                 max_seq_len=32, dtype="fp32")
+    model, _ = llama.build_llama(cfg, with_argmax=False, last_token_logits=False, weight_std=0.1)
+    m = ol.load_model(model)
+    mod = training.ORTModule(m, output_names=["logits"], trainable=[t.name for t in m.graph.initializers if "cache" not in t.name])
+    B, S = 3, 10
+    ids = torch.randint(0, 64, (B, S), generator=torch.Generator().manual_seed(0))
+    feeds = dict(input_ids=ids, seqlens_k=torch.full((B,), S - 1, dtype=torch.int32), total_sequence_length=torch.tensor(S, dtype=torch.int32))
+    for i in range(cfg.num_layers):
+        feeds[f"past_key_values.{i}.key"] = torch.zeros(B, 2, 0, 8)
+        feeds[f"past_key_values.{i}.value"] = torch.zeros(B, 2, 0, 8)
+
+    def loss_of(logits):
+        return torch.nn.functional.cross_entropy(logits[:, :-1].reshape(-1, 64), ids[:, 1:].reshape(-1))
+    loss = loss_of(mod(**feeds))
+    loss.backward()
+    w = {t.name: torch.tensor(np.array(ol.to_array(t)), requires_grad=t.data_type == T.FLOAT) for t in m.graph.initializers}
+    ref = loss_of(_llama_torch(cfg, w, ids))
+    ref.backward()
+    assert abs(loss.item() - ref.item()) < 1e-4
+    for name, p in mod.named_onnx_parameters():
+        np.testing.assert_allclose(p.grad.numpy(), w[name].grad.numpy(), rtol=2e-3, atol=2e-6, err_msg=name)
+    opt = torch.optim.AdamW(mod.parameters(), lr=3e-3)
+    for _ in range(25):
+        opt.zero_grad()
+        cur = loss_of(mod(**feeds))
+        cur.backward()
+        opt.step()
+    assert cur.item() < 0.25 * loss.item()
