@@ -430,6 +430,29 @@ def case_data_parallel_training(info, device, out):
                 "full_grad": {k: v.grad for k, v in full.items()}}, os.path.join(out, f"rank{r}.pt"))
 
 
+def case_megatron_training(info, device, out):
+    """Column-parallel then row-parallel MLP with MegatronF / MegatronG: loss and gradients against the unsplit model."""
+    from onnxruntime_b200 import training
+    r, w = info.rank, info.world_size
+    rng = np.random.RandomState(0)
+    f = lambda *s: (rng.randn(*s) * 0.4).astype(np.float32)  # noqa: E731
+    init = {"w0": f(8, 8), "w1": f(8, 16), "b1": f(16), "w2": f(16, 8)}
+    g = ol.make_graph([ol.make_node("MatMul", ["x", "w0"], ["h0"]), ol.make_node("MatMul", ["h0", "w1"], ["h"]), ol.make_node("Add", ["h", "b1"], ["hb"]),
+                       ol.make_node("Tanh", ["hb"], ["t"]), ol.make_node("MatMul", ["t", "w2"], ["y"])], "mlp",
+                      [ol.make_tensor_value_info("x", T.FLOAT, ["n", 8])], [ol.make_tensor_value_info("y", T.FLOAT, ["n", 8])],
+                      [ol.make_tensor(k, v) for k, v in init.items()])
+    x, target = torch.tensor(f(6, 8)), torch.tensor(f(6, 8))
+    sharded = training.megatron.shard_mlp(ol.make_model(g, opset=17), ["w1"], ["w2"], r, w, column_biases=["b1"])
+    mod = training.ORTModule(sharded)
+    loss = ((mod(x) - target) ** 2).mean()
+    loss.backward()
+    ref = {k: torch.tensor(v, requires_grad=True) for k, v in init.items()}
+    ref_loss = (((torch.tanh(x @ ref["w0"] @ ref["w1"] + ref["b1"]) @ ref["w2"]) - target) ** 2).mean()
+    ref_loss.backward()
+    torch.save({"loss": loss.detach(), "ref_loss": ref_loss.detach(), "grads": {n: p.grad.clone() for n, p in mod.named_onnx_parameters()},
+                "ref_grads": {k: v.grad for k, v in ref.items()}}, os.path.join(out, f"rank{r}.pt"))
+
+
 def main():
     case, device, out = sys.argv[1], sys.argv[2], sys.argv[3]
     info = init_distributed("gloo" if device == "cpu" else "nccl", timeout_s=120)

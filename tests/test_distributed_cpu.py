@@ -113,3 +113,17 @@ def test_data_parallel_training_follows_the_full_batch_run(tmp_path):
             np.testing.assert_allclose(out[r]["ddp_grad"][k].numpy(), out[r]["full_grad"][k].numpy(), rtol=1e-4, atol=1e-6, err_msg=k)
     for k in out[0]["api"]:
         np.testing.assert_array_equal(out[0]["api"][k].numpy(), out[1]["api"][k].numpy())
+
+
+def test_megatron_split_mlp_trains_with_the_gradients_of_the_whole(tmp_path):
+    """MegatronF / MegatronG around a column- and a row-parallel weight: every rank holds its shard's gradient, and the
+    replicated weight in front of the split gets the full gradient (the backward all-reduce of MegatronF)."""
+    out = launch("megatron_training", "cpu", 2, tmp_path)
+    for r in range(2):
+        o = out[r]
+        assert abs(o["loss"].item() - o["ref_loss"].item()) < 1e-5
+        ref = o["ref_grads"]
+        np.testing.assert_allclose(o["grads"]["w0"].numpy(), ref["w0"].numpy(), rtol=1e-4, atol=1e-6)
+        np.testing.assert_allclose(o["grads"]["w1"].numpy(), np.split(ref["w1"].numpy(), 2, 1)[r], rtol=1e-4, atol=1e-6)
+        np.testing.assert_allclose(o["grads"]["b1"].numpy(), np.split(ref["b1"].numpy(), 2, 0)[r], rtol=1e-4, atol=1e-6)
+        np.testing.assert_allclose(o["grads"]["w2"].numpy(), np.split(ref["w2"].numpy(), 2, 0)[r], rtol=1e-4, atol=1e-6)
