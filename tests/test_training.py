@@ -490,3 +490,34 @@ def test_llama_decoder_fine_tunes_through_the_fused_operators():
         cur.backward()
         opt.step()
     assert cur.item() < 0.25 * loss.item()
+
+
+@pytest.mark.parametrize("loss_type", ["MSELoss", "L1Loss", "BCEWithLogitsLoss"])
+def test_artifact_losses_and_the_sgd_optimizer(loss_type):
+    rng = np.random.default_rng(10)
+    w, b = _f(rng, 6, 3) * 0.5, _f(rng, 3) * 0.1
+    g = ol.make_graph([ol.make_node("Gemm", ["x", "w", "b"], ["y"])], "lin", [ol.make_tensor_value_info("x", T.FLOAT, ["n", 6])],
+                      [ol.make_tensor_value_info("y", T.FLOAT, ["n", 3])], [ol.make_tensor("w", w), ol.make_tensor("b", b)])
+    art = training.generate_artifacts(ol.make_model(g, opset=17), loss=training.LossType[loss_type], optimizer=training.OptimType.SGD)
+    state = api.CheckpointState.load_checkpoint(art["checkpoint"])
+    module = api.Module(art["training_model.onnx"], state, art["eval_model.onnx"])
+    optim = api.Optimizer(art["optimizer_model.onnx"], module)
+    optim.set_learning_rate(0.1)
+    x = _f(rng, 16, 6)
+    target = (rng.random((16, 3)) > 0.5).astype(np.float32) if loss_type == "BCEWithLogitsLoss" else _f(rng, 16, 3)
+    wt, bt = torch.tensor(w, requires_grad=True), torch.tensor(b, requires_grad=True)
+    fn = {"MSELoss": torch.nn.functional.mse_loss, "L1Loss": torch.nn.functional.l1_loss,
+          "BCEWithLogitsLoss": torch.nn.functional.binary_cross_entropy_with_logits}[loss_type]
+    for _ in range(4):
+        loss, _y = module(x, target)
+        ref = fn(torch.tensor(x) @ wt + bt, torch.tensor(target))
+        assert abs(float(np.asarray(loss).reshape(-1)[0]) - ref.item()) < 1e-5
+        optim.step()
+        module.lazy_reset_grad()
+        ref.backward()
+        with torch.no_grad():
+            wt -= 0.1 * wt.grad
+            bt -= 0.1 * bt.grad
+        wt.grad = bt.grad = None
+    np.testing.assert_allclose(state.parameters["w"].data.numpy(), wt.detach().numpy(), rtol=1e-4, atol=1e-6)
+    np.testing.assert_allclose(state.parameters["b"].data.numpy(), bt.detach().numpy(), rtol=1e-4, atol=1e-6)
