@@ -93,6 +93,62 @@ def quantize_blockwise_hqq(w_kn: np.ndarray, block_size: int = 32, bits: int = 4
     return packed, (1.0 / inv_scale)[..., 0].astype(np.float32), zero[..., 0].astype(np.float32)
 
 
+def quantize_blockwise_gptq(w_kn: np.ndarray, hessian: np.ndarray, block_size: int = 32, bits: int = 4, percdamp: float = 0.01,
+                            update_block: int = 128) -> Tuple[np.ndarray, np.ndarray, np.ndarray]:
+    """GPTQ (the GPTQ option of the reference's quantizer, ``GPTQWeightOnlyQuantConfig``): the columns of the weight are
+    rounded one after the other along K, and the rounding error of each is pushed onto the columns not yet rounded
+    through the inverse of ``hessian`` = X^T X of calibration activations [K, K], so that the error of X W, not of W, is
+    kept small.  Asymmetric min-max grid per block of ``block_size`` along K, fixed when the block is reached.  Same
+    return layout as ``quantize_blockwise(..., symmetric=False)``."""
+    assert bits in (4, 8) and block_size >= 16 and block_size & (block_size - 1) == 0
+    K, N = w_kn.shape
+    assert K % block_size == 0, "GPTQ needs K to be a multiple of the block size"
+    nb = K // block_size
+    qmax = float((1 << bits) - 1)
+    W = np.asarray(w_kn, dtype=np.float64).T.copy()          # [N, K]
+    H = np.asarray(hessian, dtype=np.float64).copy()
+    dead = np.diag(H) == 0
+    H[dead, dead] = 1.0
+    W[:, dead] = 0.0
+    H[np.diag_indices(K)] += percdamp * np.mean(np.diag(H))
+    Hinv = np.linalg.cholesky(np.linalg.inv(H)).T             # upper factor of H^-1
+    q_int = np.zeros((N, K), dtype=np.uint8)
+    scales = np.zeros((N, nb), dtype=np.float64)
+    zps = np.zeros((N, nb), dtype=np.float64)
+    for i1 in range(0, K, update_block):
+        i2 = min(i1 + update_block, K)
+        W1 = W[:, i1:i2].copy()
+        Err = np.zeros_like(W1)
+        Hi = Hinv[i1:i2, i1:i2]
+        for i in range(i2 - i1):
+            col = i1 + i
+            blk = col // block_size
+            if col % block_size == 0:                           # fix the grid of this block from its present values
+                seg = np.concatenate([W1[:, i:i + block_size], W[:, i2:col + block_size]], 1)[:, :block_size]
+                lo, hi = np.minimum(seg.min(1), 0.0), np.maximum(seg.max(1), 0.0)
+                sc = (hi - lo) / qmax
+                sc[sc == 0] = 1.0
+                scales[:, blk] = sc
+                zps[:, blk] = np.clip(np.rint(-lo / sc), 0, qmax)
+            w = W1[:, i]
+            q = np.clip(np.rint(w / scales[:, blk] + zps[:, blk]), 0, qmax)
+            q_int[:, col] = q.astype(np.uint8)
+            err = (w - (q - zps[:, blk]) * scales[:, blk]) / Hi[i, i]
+            W1[:, i:] -= np.outer(err, Hi[i, i:])
+            Err[:, i] = err
+        W[:, i2:] -= Err @ Hinv[i1:i2, i2:]
+    q3 = q_int.reshape(N, nb, block_size)
+    zp_vals = zps.astype(np.uint8)
+    if bits == 4:
+        z = np.zeros((N, (nb + 1) // 2 * 2), dtype=np.uint8)
+        z[:, :nb] = zp_vals
+        zp = (z[:, 0::2] | (z[:, 1::2] << 4)).astype(np.uint8)
+        packed = (q3[..., 0::2] | (q3[..., 1::2] << 4)).astype(np.uint8)
+    else:
+        zp, packed = zp_vals, q3
+    return packed, scales.astype(np.float32), zp
+
+
 def dequantize_blockwise(packed: np.ndarray, scales: np.ndarray, zero_points: Optional[np.ndarray], K: int, bits: int = 4,
                          block_size: int = 32) -> np.ndarray:
     """Inverse of :func:`quantize_blockwise`: float32 ``[N, K]``."""
@@ -116,10 +172,15 @@ class MatMulNBitsQuantizer:
 
     def __init__(self, model: Union[str, bytes, ol.Model], block_size: int = 32, is_symmetric: bool = True, bits: int = 4,
                  nodes_to_exclude: Iterable[str] = (), nodes_to_include: Optional[Iterable[str]] = None, min_elements: int = 0,
-                 algorithm: str = "rtn"):
-        if algorithm not in ("rtn", "hqq"):
-            raise ValueError("algorithm must be 'rtn' (round to nearest) or 'hqq' (half-quadratic, float zero points)")
+                 algorithm: str = "rtn", calibration_data_reader=None):
+        if algorithm not in ("rtn", "hqq", "gptq"):
+            raise ValueError("algorithm must be 'rtn' (round to nearest), 'hqq' (half-quadratic, float zero points) or "
+                             "'gptq' (error feedback through calibration activations; needs calibration_data_reader)")
+        if algorithm == "gptq" and calibration_data_reader is None:
+            raise ValueError("algorithm 'gptq' needs a calibration_data_reader (an object with get_next() -> feeds or None)")
         self.algorithm = algorithm
+        self.calibration_data_reader = calibration_data_reader
+        self._hessians = {}
         self.model = model if isinstance(model, ol.Model) else ol.load_model(model)
         self.block_size, self.symmetric, self.bits = block_size, is_symmetric, bits
         self.exclude = set(nodes_to_exclude)
@@ -127,7 +188,35 @@ class MatMulNBitsQuantizer:
         self.min_elements = min_elements
         self.quantized_nodes = []
 
+    def _collect_hessians(self) -> None:
+        """Runs the float model over the calibration feeds with the activation of every candidate MatMul as an extra
+        output and accumulates X^T X (rows = all leading dimensions) per activation."""
+        import copy
+
+        from .. import capi
+        g = self.model.graph
+        inits = {t.name for t in g.initializers}
+        acts = []
+        for n in g.nodes:
+            if n.op_type == "MatMul" and len(n.inputs) == 2 and n.inputs[1] in inits and n.inputs[0] not in acts:
+                acts.append(n.inputs[0])
+        probe = copy.deepcopy(self.model)
+        have = {o.name for o in probe.graph.outputs}
+        probe.graph.outputs.extend(ol.make_tensor_value_info(a, 0, None) for a in acts if a not in have)
+        so = capi.SessionOptions()
+        so.graph_optimization_level = capi.GraphOptimizationLevel.ORT_DISABLE_ALL
+        sess = capi.InferenceSession(probe.serialize(), so, providers=["CPUExecutionProvider"])
+        while True:
+            feeds = self.calibration_data_reader.get_next()
+            if feeds is None:
+                break
+            for a, x in zip(acts, sess.run(acts, feeds)):
+                x2 = np.asarray(x, dtype=np.float64).reshape(-1, x.shape[-1])
+                self._hessians[a] = self._hessians.get(a, 0.0) + x2.T @ x2
+
     def process(self) -> ol.Model:
+        if self.algorithm == "gptq" and not self._hessians:
+            self._collect_hessians()
         g = self.model.graph
         inits = {t.name: t for t in g.initializers}
         uses = {}
@@ -148,7 +237,9 @@ class MatMulNBitsQuantizer:
             is_torch = not isinstance(arr, np.ndarray)
             w32 = arr.float().numpy() if is_torch else arr.astype(np.float32)
             K, N = w32.shape
-            if self.algorithm == "hqq":
+            if self.algorithm == "gptq" and n.inputs[0] in self._hessians:
+                packed, scales, zp = quantize_blockwise_gptq(w32, self._hessians[n.inputs[0]], self.block_size, self.bits)
+            elif self.algorithm == "hqq":
                 packed, scales, zp = quantize_blockwise_hqq(w32, self.block_size, self.bits)
             else:
                 packed, scales, zp = quantize_blockwise(w32, self.block_size, self.bits, self.symmetric)

@@ -376,3 +376,34 @@ def test_hqq_weight_quantization_beats_round_to_nearest_on_outliers():
     assert len(node.inputs) == 4                                        # float zero points ride along
     (y,) = ort.InferenceSession(q.serialize(), providers=["CPUExecutionProvider"]).run(None, {"x": x})
     assert np.abs(y - ref).max() < 0.15 * np.abs(ref).max()
+
+
+def test_gptq_weight_quantization_keeps_the_layer_output_closer_than_round_to_nearest():
+    import numpy as np
+    import onnxruntime_b200 as ort
+    from onnxruntime_b200.quantization import MatMulNBitsQuantizer, dequantize_blockwise, quantize_blockwise, quantize_blockwise_gptq
+    rng = np.random.default_rng(0)
+    K, N = 128, 24
+    w = rng.standard_normal((K, N)).astype(np.float32)
+    mix = rng.standard_normal((K, K)) * (rng.random(K) ** 3)[None, :]            # correlated activations of uneven scale
+    x = (rng.standard_normal((512, K)) @ mix).astype(np.float32)
+    p0, s0, z0 = quantize_blockwise(w, 32, 4, symmetric=False)
+    p1, s1, z1 = quantize_blockwise_gptq(w, x.T.astype(np.float64) @ x, 32, 4)
+    assert p1.shape == p0.shape and s1.shape == s0.shape and z1.shape == z0.shape and z1.dtype == np.uint8
+    e_rtn = np.linalg.norm(x @ dequantize_blockwise(p0, s0, z0, K, 4, 32).T - x @ w)
+    e_gptq = np.linalg.norm(x @ dequantize_blockwise(p1, s1, z1, K, 4, 32).T - x @ w)
+    assert e_gptq < 0.9 * e_rtn, (e_gptq, e_rtn)
+
+    class Reader:
+        def __init__(self, batches):
+            self.it = iter(batches)
+
+        def get_next(self):
+            return next(self.it, None)
+    model, mrng = _two_layer_mlp()
+    batches = [{"x": mrng.standard_normal((32, 16)).astype(np.float32)} for _ in range(4)]
+    (ref,) = ort.InferenceSession(model, providers=["CPUExecutionProvider"]).run(None, batches[0])
+    q = MatMulNBitsQuantizer(model, block_size=16, algorithm="gptq", calibration_data_reader=Reader(batches)).process()
+    assert sum(n.op_type == "MatMulNBits" for n in q.graph.nodes) == 2
+    (y,) = ort.InferenceSession(q.serialize(), providers=["CPUExecutionProvider"]).run(None, batches[0])
+    assert np.abs(y - ref).max() < 0.15 * np.abs(ref).max()
